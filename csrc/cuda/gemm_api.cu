@@ -1,0 +1,35 @@
+// Entry point of the GEMM family: argument checks, then dispatch to an instantiation.
+#include "gemm_api.h"
+#include "gemm_tc.cuh"
+
+namespace plow {
+int gemm_dispatch_bf16(const PlowGemmDesc& d, cudaStream_t s);
+int gemm_dispatch_fp8(const PlowGemmDesc& d, cudaStream_t s);
+
+GemmArgs to_args(const PlowGemmDesc& d) {
+  GemmArgs a;
+  a.x = d.x; a.w = d.w; a.y = d.y; a.sx = d.sx; a.sw = d.sw; a.residual = d.residual;
+  a.yq = d.yq; a.syq = d.syq; a.grp_off = d.grp_off; a.tile_prefix = d.tile_prefix;
+  a.status = d.status; a.M = d.M; a.N = d.N; a.K = d.K; a.ldy = d.ldy; a.ld_sx = d.ld_sx;
+  a.ld_syq = d.ld_syq; a.E = d.E; a.out_f32 = d.out_f32; a.out_scale = d.out_scale;
+  return a;
+}
+}  // namespace plow
+
+extern "C" int plow_gemm(const PlowGemmDesc* d, void* stream) {
+  if (!d || !d->x || !d->w || !d->status || (!d->y && !d->yq)) return -1;
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0) return -1;
+  const int es = d->dtype == 1 ? 1 : 2;
+  // TMA: 16-byte aligned bases and row pitches
+  if ((reinterpret_cast<uintptr_t>(d->x) & 15) || (reinterpret_cast<uintptr_t>(d->w) & 15)) return -3;
+  if (((d->ldx * es) & 15) || ((d->ldw * es) & 15)) return -3;
+  if (d->dtype == 1 && (!d->sx || !d->sw)) return -4;
+  if (d->E > 0 && !d->grp_off) return -5;
+  if (d->E > 0 && !d->swap && !d->tile_prefix) return -5;
+  if (d->E > 0 && (d->N % 128)) return -6;
+  if (d->dual && (d->N % 128)) return -6;
+  if (d->yq && !d->syq) return -7;
+  if (d->yq && !d->swap && d->bn != 128) return -7;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  return d->dtype == 1 ? plow::gemm_dispatch_fp8(*d, s) : plow::gemm_dispatch_bf16(*d, s);
+}

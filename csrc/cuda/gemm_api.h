@@ -1,0 +1,38 @@
+// C ABI of the tcgen05 GEMM family (loaded from Python through ctypes).
+#pragma once
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct PlowGemmDesc {
+  const void* x;          // [M, K] activations (bf16 or e4m3), row pitch ldx elements
+  const void* w;          // [w_rows, K] weights, row pitch ldw elements
+  void* y;                // [M, N] output (bf16, or f32 when out_f32); may be NULL with yq set
+  const float* sx;        // e4m3: activation scales, transposed [ceil(K/128)][ld_sx]
+  const float* sw;        // e4m3: weight scales [w_rows/128][ceil(K/128)]
+  const void* residual;   // optional bf16 [M, N] (pitch ldy)
+  void* yq;               // optional e4m3 output [M, N] (pitch ldy)
+  float* syq;             // scales of yq, transposed [N/128][ld_syq]
+  const int32_t* grp_off; // grouped: [E+1] row offsets (device)
+  const int32_t* tile_prefix;  // grouped, swap=0: [E+1] prefix of 128-row tile counts (device)
+  int32_t* status;        // device status word, 0 = ok
+  int32_t M, N, K;
+  int32_t ldx, ldw, ldy, ld_sx, ld_syq;
+  int32_t E;              // experts (0 = dense)
+  int64_t w_rows;         // rows of w (E * N * (dual ? 2 : 1), or N)
+  int32_t dtype;          // 0 = bf16, 1 = e4m3 block-scaled
+  int32_t dual;           // 1: silu(x w_gate^T) * (x w_up^T), w = [gate; up] per expert
+  int32_t swap;           // 1: weights on the 128 TMEM lanes (small M)
+  int32_t bn;             // UMMA N tile (tokens when swap, features otherwise)
+  int32_t out_f32;
+  float out_scale;
+} PlowGemmDesc;
+
+// Launches on `stream` (a cudaStream_t).  Returns 0, or a host-side error code (<0 bad
+// arguments, >=1000 tensor-map / launch failures).
+int plow_gemm(const PlowGemmDesc* d, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

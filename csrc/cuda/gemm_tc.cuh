@@ -1,0 +1,550 @@
+// Persistent warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   y[M, N] = x[M, K] * w[N, K]^T          (both operands K-major, fp32 accumulate in TMEM)
+//
+// One CTA per SM walks a static tile schedule.  Warp 0 issues TMA loads into a ring of
+// 128-byte-swizzled shared-memory stages, one elected thread of warp 1 issues tcgen05.mma
+// and commits completion to mbarriers, warps 2-5 read accumulators back with tcgen05.ld and
+// run the epilogue.  Variants, all in this one template:
+//   * bf16 inputs (kind::f16) or e4m3 inputs with 128x128 weight scales and 1x128 activation
+//     scales (kind::f8f6f4).  fp32 block scales cannot be applied by the tensor core, so the
+//     fp8 path accumulates one 128-wide K block per TMEM buffer and the epilogue warps fold
+//     it into fp32 registers with the block's scale (two-level accumulation) while the MMA
+//     warp runs the next block into the other buffer.
+//   * SWAP: weights ride the 128 TMEM lanes and tokens the UMMA N dimension (16..128), so
+//     small-M decode GEMMs stream weights at full tile efficiency.
+//   * grouped (MoE): rows of x are sorted by expert, `grp_off[E+1]` gives each expert's row
+//     range and w stacks the experts' matrices; tiles that run past an expert's rows are
+//     masked at the store, so no padding of the token buffer is needed.
+//   * DUAL: gate and up projections accumulate side by side and the epilogue writes
+//     silu(gate) * up, optionally re-quantised to e4m3 with 1x128 scales for the next GEMM.
+//
+// Parity notes: the reference's prefill GEMM is a 128x128x32 mma.sync/wgmma tile loop with a
+// GLU epilogue (runtime/nvidia/op_gemm.cuh:1218-1260, op_gemm_sm90.cuh) and its block-scaled
+// fp8 decode GEMM is a swap-AB wgmma kernel with two-level accumulation
+// (runtime/nvidia/op_gemm_fp8_block_sm90.cuh:77-91); grouped MoE tiles follow the
+// (rowoff, cnt, tile_prefix) table of runtime/nvidia/op_moe.cuh.
+#pragma once
+#include "ptx.cuh"
+#include "tmap.cuh"
+
+namespace plow {
+
+struct GemmArgs {
+  const void* x;         // activations [rows, K]
+  const void* w;         // weights [E * Nw, K], Nw = dual ? 2N : N
+  void* y;               // output [rows, N] bf16 (or f32 when out_f32)
+  const float* sx;       // fp8: activation scales, transposed [KB][ld_sx]
+  const float* sw;       // fp8: weight scales [(E*Nw)/128][KB]
+  const void* residual;  // optional bf16 [rows, N], added before the store
+  void* yq;              // optional e4m3 output [rows, N]
+  float* syq;            // its scales, transposed [N/128][ld_syq]
+  const int* grp_off;    // grouped: [E+1] row offsets into x (device memory)
+  const int* tile_prefix;// grouped, non-swap: [E+1] prefix of 128-row tile counts
+  int* status;           // device status word (0 = ok)
+  int M;                 // rows of x (upper bound when grouped)
+  int N;                 // output features per expert
+  int K;
+  int ldy;               // elements
+  int ld_sx;
+  int ld_syq;
+  int E;                 // 0 = dense
+  int out_f32;
+  float out_scale;       // multiplies the result (1.0 = none)
+};
+
+constexpr int kGemmThreads = 192;
+constexpr int kStageBytesP = 128 * 128;
+
+template <int BN, bool DUAL, bool SWAP>
+struct GemmCfg {
+  static constexpr int kPT = (DUAL && SWAP) ? 2 : 1;    // 128-row tiles per stage
+  static constexpr int kQT = (DUAL && !SWAP) ? 2 : 1;   // BN-row tiles per stage
+  static constexpr int kStageBytes = kPT * kStageBytesP + kQT * BN * 128;
+  static constexpr int kAccCols = BN * (DUAL ? 2 : 1);
+  static constexpr int kTmemCols =
+      2 * kAccCols <= 32 ? 32 : 2 * kAccCols <= 64 ? 64 : 2 * kAccCols <= 128 ? 128
+                                                   : 2 * kAccCols <= 256 ? 256 : 512;
+  static constexpr int kStages =
+      (200 * 1024 / kStageBytes) > 10 ? 10 : (200 * 1024 / kStageBytes);
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 2048 /*bars+scratch*/;
+  static_assert(2 * kAccCols <= 512, "accumulators exceed TMEM");
+  static_assert(kStages >= 2, "tile too large for shared memory");
+};
+
+struct Tile {
+  int tok0, tok_end;  // token rows (TMA coordinate, exclusive valid end)
+  int wrow0;          // first weight row (absolute, in the stacked matrix)
+  int feat0;          // first output feature of the tile within N
+};
+
+template <int BN, bool DUAL, bool SWAP>
+struct TileSched {
+  const GemmArgs& a;
+  int item, sub;
+  int n_wt;  // weight tiles per expert
+  __device__ TileSched(const GemmArgs& a_) : a(a_), item(blockIdx.x), sub(0) {
+    n_wt = SWAP ? (a.N + 127) / 128 : (a.N + BN - 1) / BN;
+  }
+  __device__ bool next(Tile& t) {
+    const int nw_per = DUAL ? 2 * a.N : a.N;
+    if (a.E == 0) {
+      const int n_tt = SWAP ? (a.M + BN - 1) / BN : (a.M + 127) / 128;
+      // token tile fastest when SWAP (few token tiles), weight-tile-major otherwise so CTAs
+      // running at the same time share one weight tile in L2
+      if (item >= n_tt * n_wt) return false;
+      int tt, wt;
+      if (SWAP) { wt = item % n_wt; tt = item / n_wt; } else { tt = item % n_tt; wt = item / n_tt; }
+      t.tok0 = tt * (SWAP ? BN : 128);
+      t.tok_end = a.M;
+      t.feat0 = wt * (SWAP ? 128 : BN);
+      t.wrow0 = t.feat0;
+      item += gridDim.x;
+      return true;
+    }
+    if (SWAP) {
+      while (true) {
+        if (item >= a.E * n_wt) return false;
+        const int e = item / n_wt, wt = item % n_wt;
+        const int r0 = a.grp_off[e], r1 = a.grp_off[e + 1];
+        const int tok = r0 + sub * BN;
+        if (tok < r1) {
+          t.tok0 = tok; t.tok_end = r1; t.feat0 = wt * 128; t.wrow0 = e * nw_per + wt * 128;
+          ++sub;
+          return true;
+        }
+        sub = 0;
+        item += gridDim.x;
+      }
+    } else {
+      const int n_mt = a.tile_prefix[a.E];
+      if (item >= n_mt * n_wt) return false;
+      const int mt = item % n_mt, wt = item / n_mt;
+      int lo = 0, hi = a.E;  // largest e with tile_prefix[e] <= mt
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (a.tile_prefix[mid] <= mt) lo = mid; else hi = mid;
+      }
+      const int e = lo;
+      t.tok0 = a.grp_off[e] + (mt - a.tile_prefix[e]) * 128;
+      t.tok_end = a.grp_off[e + 1];
+      t.feat0 = wt * BN;
+      t.wrow0 = e * nw_per + wt * BN;
+      item += gridDim.x;
+      return true;
+    }
+  }
+};
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + __expf(-v)); }
+
+template <int BN, bool FP8, bool DUAL, bool SWAP>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
+               const __grid_constant__ CUtensorMap tm_w) {
+  using Cfg = GemmCfg<BN, DUAL, SWAP>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kAccCols = Cfg::kAccCols;
+  constexpr int kKElems = FP8 ? 128 : 64;  // K elements per 128-byte stage row
+  constexpr int kUmmaK = FP8 ? 32 : 16;
+  constexpr int kUmmaN = SWAP ? BN : (DUAL ? 2 * BN : BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* ctrl = smem + kStages * Cfg::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);        // [kStages]
+  uint64_t* empty_bar = full_bar + kStages;                      // [kStages]
+  uint64_t* acc_full = empty_bar + kStages;                      // [2]
+  uint64_t* acc_empty = acc_full + 2;                            // [2]
+  uint64_t* drain_bar = acc_empty + 2;                           // [1]
+  uint64_t* xchg_bar = drain_bar + 1;                            // [2] epilogue-warp exchange
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(xchg_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  volatile int* never_flag = abort_flag + 1;                     // stays 0
+  float* red_scratch = reinterpret_cast<float*>(ctrl + 512);     // [2][4][16] quant amax exchange
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int KB = (a.K + kKElems - 1) / kKElems;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    mbar_init(drain_bar, 1);
+    mbar_init(&xchg_bar[0], 4);
+    mbar_init(&xchg_bar[1], 4);
+    *abort_flag = 0;
+    *never_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(&tm_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const CUtensorMap* tm_p = SWAP ? &tm_w : &tm_x;  // operand on the 128 TMEM lanes
+  const CUtensorMap* tm_q = SWAP ? &tm_x : &tm_w;  // operand on the UMMA N dimension
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      TileSched<BN, DUAL, SWAP> sched(a);
+      Tile t;
+      uint32_t it = 0;
+      bool ok = true;
+      while (ok && sched.next(t)) {
+        const int p_row = SWAP ? t.wrow0 : t.tok0;
+        const int q_row = SWAP ? t.tok0 : t.wrow0;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) {
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT); ok = false; break;
+          }
+          uint8_t* st = smem + s * Cfg::kStageBytes;
+          mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
+          const int kx = kb * kKElems;
+          tma_load_2d(st, tm_p, kx, p_row, &full_bar[s]);
+          if (DUAL && SWAP) tma_load_2d(st + kStageBytesP, tm_p, kx, p_row + a.N, &full_bar[s]);
+          uint8_t* sq = st + Cfg::kPT * kStageBytesP;
+          tma_load_2d(sq, tm_q, kx, q_row, &full_bar[s]);
+          if (DUAL && !SWAP) tma_load_2d(sq + BN * 128, tm_q, kx, q_row + a.N, &full_bar[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      TileSched<BN, DUAL, SWAP> sched(a);
+      Tile t;
+      const uint32_t idesc = umma_idesc(128, kUmmaN, FP8 ? 0u : 1u, FP8 ? 0u : 1u);
+      uint32_t it = 0;      // stage counter
+      uint32_t accit = 0;   // accumulator-buffer counter (per tile for bf16, per K block for fp8)
+      bool ok = true;
+      while (ok && sched.next(t)) {
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (FP8 || kb == 0) {
+            const int b = accit & 1;
+            if (!mbar_wait(&acc_empty[b], ((accit >> 1) & 1) ^ 1, abort_flag)) {
+              *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_FREE_WAIT); ok = false; break;
+            }
+          }
+          if (!mbar_wait(&full_bar[s], ph, abort_flag)) {
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); ok = false; break;
+          }
+          tc_fence_after();
+          const int b = accit & 1;
+          const uint32_t d0 = tmem_base + b * kAccCols;
+          const uint32_t sp = smem_u32(smem + s * Cfg::kStageBytes);
+          const uint32_t sq = sp + Cfg::kPT * kStageBytesP;
+          const uint64_t pdesc = umma_desc_k128(sp);
+          const uint64_t qdesc = umma_desc_k128(sq);
+#pragma unroll
+          for (int k4 = 0; k4 < 128 / (kUmmaK * (FP8 ? 1 : 2)); ++k4) {
+            const uint32_t acc = FP8 ? (k4 > 0) : (kb > 0 || k4 > 0);
+            const uint64_t adv = static_cast<uint64_t>(k4 * 2);  // 32 bytes >> 4
+            if (FP8) {
+              tc_mma_f8(d0, pdesc + adv, qdesc + adv, idesc, acc);
+              if (DUAL && SWAP)
+                tc_mma_f8(d0 + BN, umma_desc_k128(sp + kStageBytesP) + adv, qdesc + adv, idesc, acc);
+            } else {
+              tc_mma_f16(d0, pdesc + adv, qdesc + adv, idesc, acc);
+              if (DUAL && SWAP)
+                tc_mma_f16(d0 + BN, umma_desc_k128(sp + kStageBytesP) + adv, qdesc + adv, idesc, acc);
+            }
+          }
+          tc_commit(&empty_bar[s]);
+          if (FP8 || kb == KB - 1) { tc_commit(&acc_full[accit & 1]); ++accit; }
+        }
+      }
+      if (!ok) {  // drain whatever was issued before giving up
+        tc_commit(drain_bar);
+        mbar_wait(drain_bar, 0, never_flag);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps (2..5)
+    const int lq = warp & 3;               // TMEM lane quarter this warp may read
+    const int li = lq * 32 + lane;         // lane (row of D) owned by this thread
+    const uint32_t lane_addr = static_cast<uint32_t>(lq * 32) << 16;
+    TileSched<BN, DUAL, SWAP> sched(a);
+    Tile t;
+    uint32_t accit = 0;
+    uint32_t xchg_it = 0;
+    bool ok = true;
+    constexpr int kAccRegs = FP8 ? kAccCols : 1;
+    float acc[kAccRegs];
+    const __nv_bfloat16* resid = reinterpret_cast<const __nv_bfloat16*>(a.residual);
+    while (ok && sched.next(t)) {
+      const int tok_i = t.tok0 + li;       // non-swap: this thread's token
+      const int feat_i = t.feat0 + li;     // swap: this thread's feature
+      if constexpr (FP8) {
+#pragma unroll
+        for (int i = 0; i < kAccRegs; ++i) acc[i] = 0.f;
+        const int wblk_g = t.wrow0 >> 7;
+        const int wblk_u = (t.wrow0 + a.N) >> 7;
+        for (int kb = 0; kb < KB; ++kb, ++accit) {
+          const int b = accit & 1;
+          if (!mbar_wait(&acc_full[b], (accit >> 1) & 1, abort_flag)) {
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
+          }
+          tc_fence_after();
+          const uint32_t tb = tmem_base + lane_addr + b * kAccCols;
+          const float swg = a.sw[static_cast<size_t>(wblk_g) * KB + kb];
+          float swu = 0.f;
+          if constexpr (DUAL) swu = a.sw[static_cast<size_t>(wblk_u) * KB + kb];
+          const float* sxr = a.sx + static_cast<size_t>(kb) * a.ld_sx;
+          float fi = 0.f;
+          if constexpr (!SWAP) fi = sxr[min(tok_i, a.M - 1)];
+#pragma unroll
+          for (int c = 0; c < kAccCols; c += 16) {
+            uint32_t v[16];
+            tmem_ld16(tb + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int col = c + j;
+              const bool is_up = DUAL && col >= BN;
+              float f;
+              if constexpr (SWAP)
+                f = sxr[min(t.tok0 + (is_up ? col - BN : col), a.M - 1)] * (is_up ? swu : swg);
+              else
+                f = fi * (is_up ? swu : swg);
+              acc[col] = fmaf(__uint_as_float(v[j]), f, acc[col]);
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[b]);
+        }
+        if (!ok) break;
+      } else {
+        const int b = accit & 1;
+        if (!mbar_wait(&acc_full[b], (accit >> 1) & 1, abort_flag)) {
+          *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
+        }
+        tc_fence_after();
+      }
+      const uint32_t tb = tmem_base + lane_addr + (accit & 1) * kAccCols;
+      // result of 16 columns starting at c, before out_scale
+      auto load16 = [&](int c, float* r) {
+        if constexpr (FP8) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if constexpr (DUAL) r[j] = silu_f(acc[c + j]) * acc[BN + c + j];
+            else r[j] = acc[c + j];
+          }
+        } else {
+          uint32_t g[16];
+          tmem_ld16(tb + c, g);
+          if constexpr (DUAL) {
+            uint32_t u[16];
+            tmem_ld16(tb + BN + c, u);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = silu_f(__uint_as_float(g[j])) * __uint_as_float(u[j]);
+          } else {
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = __uint_as_float(g[j]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) r[j] *= a.out_scale;
+      };
+
+      if constexpr (SWAP) {
+        // thread = feature, columns = tokens
+        const bool fok = feat_i < a.N;
+#pragma unroll
+        for (int c = 0; c < BN; c += 16) {
+          if (t.tok0 + c >= t.tok_end) break;   // uniform across the CTA
+          float r[16];
+          load16(c, r);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int tok = t.tok0 + c + j;
+            const bool ok_e = fok && tok < t.tok_end;
+            const size_t o = static_cast<size_t>(tok) * a.ldy + feat_i;
+            if (ok_e && resid) r[j] += __bfloat162float(resid[o]);
+            if (ok_e && a.y) {
+              if (a.out_f32) reinterpret_cast<float*>(a.y)[o] = r[j];
+              else reinterpret_cast<__nv_bfloat16*>(a.y)[o] = __float2bfloat16(r[j]);
+            }
+          }
+          if (a.yq) {
+            // the 1x128 quant group of a token is the 128 lanes of this tile: reduce |r|
+            // inside each warp, exchange the four warp maxima through shared memory
+            float* scratch = red_scratch + (xchg_it & 1) * 64;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float v = fok ? fabsf(r[j]) : 0.f;
+#pragma unroll
+              for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+              if (lane == 0) scratch[lq * 16 + j] = v;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
+            if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) {
+              *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
+            }
+            ++xchg_it;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float m = fmaxf(fmaxf(scratch[j], scratch[16 + j]),
+                                    fmaxf(scratch[32 + j], scratch[48 + j]));
+              const float sc = fmaxf(m, 1e-10f) * (1.0f / 448.0f);
+              const int tok = t.tok0 + c + j;
+              if (fok && tok < t.tok_end) {
+                reinterpret_cast<__nv_fp8_e4m3*>(a.yq)[static_cast<size_t>(tok) * a.ldy + feat_i] =
+                    __nv_fp8_e4m3(r[j] / sc);
+                if (li == 0) a.syq[static_cast<size_t>(t.feat0 >> 7) * a.ld_syq + tok] = sc;
+              }
+            }
+          }
+        }
+        if (!ok) break;
+      } else {
+        // thread = token, columns = features (contiguous in memory)
+        const bool tok_ok = tok_i < t.tok_end;
+        float amax = 0.f;
+#pragma unroll
+        for (int c = 0; c < BN; c += 16) {
+          float r[16];
+          load16(c, r);
+          const int f0 = t.feat0 + c;
+          const size_t o = static_cast<size_t>(tok_i) * a.ldy + f0;
+          if (tok_ok && resid) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (f0 + j < a.N) r[j] += __bfloat162float(resid[o + j]);
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(r[j]));
+          if (tok_ok && a.y) {
+            if (a.out_f32) {
+              float* yp = reinterpret_cast<float*>(a.y) + o;
+              if (f0 + 16 <= a.N && (a.ldy & 3) == 0) {
+#pragma unroll
+                for (int j = 0; j < 16; j += 4)
+                  *reinterpret_cast<float4*>(yp + j) = make_float4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+              } else {
+                for (int j = 0; j < 16; ++j) if (f0 + j < a.N) yp[j] = r[j];
+              }
+            } else {
+              __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(a.y) + o;
+              if (f0 + 16 <= a.N && (a.ldy & 7) == 0) {
+                uint32_t pk[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(r[2 * j], r[2 * j + 1]);
+                  pk[j] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(yp) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4*>(yp + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+              } else {
+                for (int j = 0; j < 16; ++j) if (f0 + j < a.N) yp[j] = __float2bfloat16(r[j]);
+              }
+            }
+          }
+        }
+        if constexpr (BN == 128) {
+          if (a.yq) {
+            // the thread owns the whole 1x128 group: second pass re-reads the accumulators
+            const float sc = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
+            const float inv = 1.0f / sc;
+#pragma unroll
+            for (int c = 0; c < BN; c += 16) {
+              float r[16];
+              load16(c, r);
+              const int f0 = t.feat0 + c;
+              if (tok_ok && resid) {
+                const size_t o = static_cast<size_t>(tok_i) * a.ldy + f0;
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  if (f0 + j < a.N) r[j] += __bfloat162float(resid[o + j]);
+              }
+              if (tok_ok && f0 + 16 <= a.N) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  __nv_fp8x4_e4m3 q(make_float4(r[4 * j] * inv, r[4 * j + 1] * inv,
+                                                r[4 * j + 2] * inv, r[4 * j + 3] * inv));
+                  pk[j] = *reinterpret_cast<uint32_t*>(&q);
+                }
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.yq) +
+                                          static_cast<size_t>(tok_i) * a.ldy + f0) =
+                    make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              }
+            }
+            if (tok_ok) a.syq[static_cast<size_t>(t.feat0 >> 7) * a.ld_syq + tok_i] = sc;
+          }
+        }
+      }
+      if constexpr (!FP8) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[accit & 1]);
+        ++accit;
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // give TMA copies that were in flight when a role gave up time to land (bounded)
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) {}
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int BN, bool FP8, bool DUAL, bool SWAP>
+int launch_gemm_tc(const GemmArgs& a, int ldx_elems, int ldw_elems, int64_t w_rows,
+                   cudaStream_t stream) {
+  using Cfg = GemmCfg<BN, DUAL, SWAP>;
+  const int es = FP8 ? 1 : 2;
+  CUtensorMap tm_x, tm_w;
+  const uint32_t box_x = SWAP ? BN : 128;
+  const uint32_t box_w = SWAP ? 128 : BN;
+  int r = make_tmap_2d(&tm_x, a.x, es, a.M, a.K, static_cast<uint64_t>(ldx_elems) * es, box_x);
+  if (r) return 1000 + r;
+  r = make_tmap_2d(&tm_w, a.w, es, w_rows, a.K, static_cast<uint64_t>(ldw_elems) * es, box_w);
+  if (r) return 2000 + r;
+  auto kern = gemm_tc_kernel<BN, FP8, DUAL, SWAP>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) return 3000 + static_cast<int>(e);
+    attr_set = true;
+  }
+  int grid = sm_count();
+  if (a.E == 0) {
+    const int n_wt = SWAP ? (a.N + 127) / 128 : (a.N + BN - 1) / BN;
+    const int n_tt = SWAP ? (a.M + BN - 1) / BN : (a.M + 127) / 128;
+    const long long tiles = static_cast<long long>(n_wt) * n_tt;
+    if (tiles < grid) grid = static_cast<int>(tiles);
+  }
+  if (grid < 1) grid = 1;
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(a, tm_x, tm_w);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
+}
+
+}  // namespace plow

@@ -1,0 +1,84 @@
+"""tcgen05 GEMM family: Python front end of ``plow_gemm`` (csrc/cuda/gemm_api.h).
+
+``linear`` picks the orientation from the row count: up to 128 rows the weights ride the
+TMEM lanes (``swap``) and the rows become the UMMA N dimension, so a decode step streams each
+weight tile exactly once at full tensor-core tile efficiency; larger row counts put tokens on
+the lanes.  The reference makes the same split between its GEMV family (M <= 8..128 rows) and
+its tiled prefill GEMM (runtime/nvidia/op_gemm.cuh:76, op_gemv_wide_sm90.cuh).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import native
+
+_BF16, _FP8 = 0, 1
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _pick_bn_swap(rows: int, fp8: bool, dual: bool) -> int:
+    cap = 64 if (fp8 and dual) else 128
+    for bn in (32, 64, 128):
+        if rows <= bn and bn <= cap:
+            return bn
+    return cap
+
+
+def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=None,
+         grp_off=None, tile_prefix=None, n_experts=0, swap=None, bn=None, out_f32=False,
+         out_scale=1.0, quant_out=False, rows_hint=None, ld_syq=None):
+    """y = x @ w.T with the epilogue options of the kernel.
+
+    x [M, K] bf16 or e4m3; w [(E*)N(*2), K] same dtype.  ``dual`` computes silu(gate)*up with
+    w = [gate; up] stacked per expert.  Grouped mode (``n_experts`` > 0): rows of x are sorted
+    by expert and ``grp_off`` [E+1] int32 (device) gives the ranges.  ``quant_out`` returns
+    (yq e4m3, syq transposed scales) instead of bf16.  ``rows_hint``: expected rows per expert
+    used to pick the token tile in grouped swap mode.
+    """
+    lib = native.cuda_lib()
+    assert x.is_cuda and w.is_cuda and x.dim() == 2 and w.dim() == 2
+    fp8 = x.dtype == torch.float8_e4m3fn
+    assert w.dtype == x.dtype and (fp8 or x.dtype == torch.bfloat16)
+    M, K = x.shape
+    w_rows = w.shape[0]
+    E = int(n_experts)
+    if n_out is None:
+        n_out = w_rows // (max(E, 1) * (2 if dual else 1))
+    N = int(n_out)
+    if swap is None:
+        per = rows_hint if rows_hint is not None else M
+        swap = per <= 128
+    if bn is None:
+        if swap:
+            bn = _pick_bn_swap(rows_hint if rows_hint is not None else M, fp8, dual)
+        else:
+            bn = (64 if dual else 128) if fp8 else (128 if dual else (256 if N >= 2048 else 128))
+    y = yq = syq = None
+    if quant_out:
+        yq = torch.empty(M, N, dtype=torch.float8_e4m3fn, device=x.device)
+        ld_syq = ld_syq or M
+        syq = torch.empty((N + 127) // 128, ld_syq, dtype=torch.float32, device=x.device)
+    else:
+        y = out if out is not None else torch.empty(
+            M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    status = native.status_word(x.device)
+    d = native.GemmDesc(
+        x=_ptr(x), w=_ptr(w), y=_ptr(y), sx=_ptr(sx), sw=_ptr(sw), residual=_ptr(residual),
+        yq=_ptr(yq), syq=_ptr(syq), grp_off=_ptr(grp_off), tile_prefix=_ptr(tile_prefix),
+        status=status.data_ptr(), M=M, N=N, K=K, ldx=x.stride(0), ldw=w.stride(0), ldy=N,
+        ld_sx=(sx.stride(0) if sx is not None else 0), ld_syq=(ld_syq or 0), E=E, w_rows=w_rows,
+        dtype=_FP8 if fp8 else _BF16, dual=int(dual), swap=int(swap), bn=int(bn),
+        out_f32=int(out_f32), out_scale=float(out_scale))
+    rc = lib.plow_gemm(C.byref(d), native.stream_ptr())
+    if rc != 0:
+        raise native.NativeLibraryError(f"plow_gemm failed with code {rc} (bn={bn} swap={swap} dual={dual} fp8={fp8})")
+    return (yq, syq) if quant_out else y
+
+
+def linear(x, w, **kw):
+    return gemm(x, w, **kw)

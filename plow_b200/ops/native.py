@@ -1,0 +1,92 @@
+"""ctypes bindings of the in-tree native libraries.
+
+The CUDA library is loaded lazily and *loudly*: on a machine with a GPU a missing or unloadable
+``libplow_cuda.so`` raises instead of falling back to PyTorch, so a silent eager path can never
+stand in for the hand-written kernels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from functools import lru_cache
+from pathlib import Path
+
+LIBDIR = Path(__file__).resolve().parent.parent / "lib"
+
+
+class NativeLibraryError(RuntimeError):
+    pass
+
+
+class GemmDesc(C.Structure):
+    """Mirror of ``PlowGemmDesc`` (csrc/cuda/gemm_api.h)."""
+    _fields_ = [
+        ("x", C.c_void_p), ("w", C.c_void_p), ("y", C.c_void_p), ("sx", C.c_void_p),
+        ("sw", C.c_void_p), ("residual", C.c_void_p), ("yq", C.c_void_p), ("syq", C.c_void_p),
+        ("grp_off", C.c_void_p), ("tile_prefix", C.c_void_p), ("status", C.c_void_p),
+        ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
+        ("ldx", C.c_int32), ("ldw", C.c_int32), ("ldy", C.c_int32), ("ld_sx", C.c_int32),
+        ("ld_syq", C.c_int32), ("E", C.c_int32),
+        ("w_rows", C.c_int64),
+        ("dtype", C.c_int32), ("dual", C.c_int32), ("swap", C.c_int32), ("bn", C.c_int32),
+        ("out_f32", C.c_int32), ("out_scale", C.c_float),
+    ]
+
+
+def _ensure_built(name: str) -> Path:
+    path = LIBDIR / name
+    if not path.exists() and os.environ.get("PLOW_NO_AUTOBUILD") != "1":
+        from .. import build
+        (build.build_cuda if "cuda" in name else build.build_cpu)()
+    if not path.exists():
+        raise NativeLibraryError(f"{path} is missing; run `python -m plow_b200.build`")
+    return path
+
+
+@lru_cache(maxsize=None)
+def cuda_lib() -> C.CDLL:
+    """The sm_100a kernel library.  Raises if it cannot be loaded."""
+    import torch  # noqa: F401  (loads libcudart / initialises the allocator first)
+    lib = C.CDLL(str(_ensure_built("libplow_cuda.so")), mode=C.RTLD_GLOBAL)
+    lib.plow_gemm.argtypes = [C.POINTER(GemmDesc), C.c_void_p]
+    lib.plow_gemm.restype = C.c_int
+    return lib
+
+
+@lru_cache(maxsize=None)
+def cpu_lib() -> C.CDLL:
+    """The CPU packet interpreter + golden ops."""
+    return C.CDLL(str(_ensure_built("libplow_cpu.so")))
+
+
+def stream_ptr() -> int:
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+_status = {}
+
+
+def status_word(device=None):
+    """One int32 device word per GPU that kernels write error codes into (0 = ok)."""
+    import torch
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev not in _status:
+        _status[dev] = torch.zeros(4, dtype=torch.int32, device=dev)
+    return _status[dev]
+
+
+STATUS_NAMES = {
+    0: "ok", 1: "tma stage never landed", 2: "smem stage never freed", 3: "accumulator never completed",
+    4: "accumulator never drained", 5: "peer flag never arrived", 6: "device bounds check failed",
+    7: "in-grid counter wait ran out",
+}
+
+
+def check_status(device=None) -> None:
+    """Synchronising read of the status word; raises on a recorded device-side error."""
+    s = status_word(device)
+    code = int(s[0].item())
+    if code != 0:
+        s.zero_()
+        raise NativeLibraryError(f"device kernel reported status {code}: {STATUS_NAMES.get(code, '?')}")
