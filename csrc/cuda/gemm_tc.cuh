@@ -56,19 +56,22 @@ struct GemmArgs {
 constexpr int kGemmThreads = 192;
 constexpr int kStageBytesP = 128 * 128;
 
-template <int BN, bool DUAL, bool SWAP>
+template <int BN, bool DUAL, bool SWAP, bool FP8 = false>
 struct GemmCfg {
   static constexpr int kPT = (DUAL && SWAP) ? 2 : 1;    // 128-row tiles per stage
   static constexpr int kQT = (DUAL && !SWAP) ? 2 : 1;   // BN-row tiles per stage
   static constexpr int kStageBytes = kPT * kStageBytesP + kQT * BN * 128;
   static constexpr int kAccCols = BN * (DUAL ? 2 : 1);
+  // accumulator buffers in TMEM: two for bf16 (tile i+1 runs while tile i drains), up to
+  // four K-block partials for fp8 so the promotion warps may lag the MMA warp
+  static constexpr int kNBuf = (FP8 && 4 * kAccCols <= 512) ? 4 : 2;
   static constexpr int kTmemCols =
-      2 * kAccCols <= 32 ? 32 : 2 * kAccCols <= 64 ? 64 : 2 * kAccCols <= 128 ? 128
-                                                   : 2 * kAccCols <= 256 ? 256 : 512;
+      kNBuf * kAccCols <= 32 ? 32 : kNBuf * kAccCols <= 64 ? 64 : kNBuf * kAccCols <= 128 ? 128
+                                                   : kNBuf * kAccCols <= 256 ? 256 : 512;
   static constexpr int kStages =
       (200 * 1024 / kStageBytes) > 10 ? 10 : (200 * 1024 / kStageBytes);
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 2048 /*bars+scratch*/;
-  static_assert(2 * kAccCols <= 512, "accumulators exceed TMEM");
+  static_assert(kNBuf * kAccCols <= 512, "accumulators exceed TMEM");
   static_assert(kStages >= 2, "tile too large for shared memory");
 };
 
@@ -142,9 +145,10 @@ template <int BN, bool FP8, bool DUAL, bool SWAP>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
                const __grid_constant__ CUtensorMap tm_w) {
-  using Cfg = GemmCfg<BN, DUAL, SWAP>;
+  using Cfg = GemmCfg<BN, DUAL, SWAP, FP8>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kAccCols = Cfg::kAccCols;
+  constexpr int kNBuf = Cfg::kNBuf;
   constexpr int kKElems = FP8 ? 128 : 64;  // K elements per 128-byte stage row
   constexpr int kUmmaK = FP8 ? 32 : 16;
   constexpr int kUmmaN = SWAP ? BN : (DUAL ? 2 * BN : BN);
@@ -155,9 +159,9 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
   uint8_t* ctrl = smem + kStages * Cfg::kStageBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);        // [kStages]
   uint64_t* empty_bar = full_bar + kStages;                      // [kStages]
-  uint64_t* acc_full = empty_bar + kStages;                      // [2]
-  uint64_t* acc_empty = acc_full + 2;                            // [2]
-  uint64_t* drain_bar = acc_empty + 2;                           // [1]
+  uint64_t* acc_full = empty_bar + kStages;                      // [kNBuf]
+  uint64_t* acc_empty = acc_full + kNBuf;                        // [kNBuf]
+  uint64_t* drain_bar = acc_empty + kNBuf;                       // [1]
   uint64_t* xchg_bar = drain_bar + 1;                            // [2] epilogue-warp exchange
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(xchg_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
@@ -170,7 +174,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < kNBuf; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
     mbar_init(drain_bar, 1);
     mbar_init(&xchg_bar[0], 4);
     mbar_init(&xchg_bar[1], 4);
@@ -233,8 +237,8 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (FP8 || kb == 0) {
-            const int b = accit & 1;
-            if (!mbar_wait(&acc_empty[b], ((accit >> 1) & 1) ^ 1, abort_flag)) {
+            const int b = accit % kNBuf;
+            if (!mbar_wait(&acc_empty[b], ((accit / kNBuf) & 1) ^ 1, abort_flag)) {
               *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_FREE_WAIT); ok = false; break;
             }
           }
@@ -242,7 +246,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); ok = false; break;
           }
           tc_fence_after();
-          const int b = accit & 1;
+          const int b = accit % kNBuf;
           const uint32_t d0 = tmem_base + b * kAccCols;
           const uint32_t sp = smem_u32(smem + s * Cfg::kStageBytes);
           const uint32_t sq = sp + Cfg::kPT * kStageBytesP;
@@ -263,7 +267,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             }
           }
           tc_commit(&empty_bar[s]);
-          if (FP8 || kb == KB - 1) { tc_commit(&acc_full[accit & 1]); ++accit; }
+          if (FP8 || kb == KB - 1) { tc_commit(&acc_full[accit % kNBuf]); ++accit; }
         }
       }
       if (!ok) {  // drain whatever was issued before giving up
@@ -292,39 +296,63 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         for (int i = 0; i < kAccRegs; ++i) acc[i] = 0.f;
         const int wblk_g = t.wrow0 >> 7;
         const int wblk_u = (t.wrow0 + a.N) >> 7;
+        // Scales are fetched two K blocks ahead so their latency hides behind the wait for
+        // the partial.  SWAP: lane l keeps the activation scales of tokens tok0 + l + 32 i
+        // and columns pick theirs up with a shuffle; otherwise each thread owns one token.
+        constexpr int kNS = SWAP ? (BN + 31) / 32 : 1;
+        struct Sc { float sa[kNS]; float wg, wu; };
+        auto fetch = [&](int kb, Sc& o) {
+          if (kb >= KB) return;
+          const float* sxr = a.sx + static_cast<size_t>(kb) * a.ld_sx;
+#pragma unroll
+          for (int i = 0; i < kNS; ++i)
+            o.sa[i] = sxr[min(SWAP ? t.tok0 + i * 32 + lane : tok_i, a.M - 1)];
+          o.wg = a.sw[static_cast<size_t>(wblk_g) * KB + kb];
+          if constexpr (DUAL) o.wu = a.sw[static_cast<size_t>(wblk_u) * KB + kb];
+        };
+        Sc s0, s1, s2;
+        fetch(0, s0);
+        fetch(1, s1);
         for (int kb = 0; kb < KB; ++kb, ++accit) {
-          const int b = accit & 1;
-          if (!mbar_wait(&acc_full[b], (accit >> 1) & 1, abort_flag)) {
+          fetch(kb + 2, s2);
+          const int b = accit % kNBuf;
+          if (!mbar_wait(&acc_full[b], (accit / kNBuf) & 1, abort_flag)) {
             *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
           }
           tc_fence_after();
           const uint32_t tb = tmem_base + lane_addr + b * kAccCols;
-          const float swg = a.sw[static_cast<size_t>(wblk_g) * KB + kb];
-          float swu = 0.f;
-          if constexpr (DUAL) swu = a.sw[static_cast<size_t>(wblk_u) * KB + kb];
-          const float* sxr = a.sx + static_cast<size_t>(kb) * a.ld_sx;
-          float fi = 0.f;
-          if constexpr (!SWAP) fi = sxr[min(tok_i, a.M - 1)];
 #pragma unroll
-          for (int c = 0; c < kAccCols; c += 16) {
-            uint32_t v[16];
-            tmem_ld16(tb + c, v);
+          for (int c = 0; c < BN; c += (DUAL ? 16 : 32)) {
+            uint32_t v0[16], v1[16];
+            tmem_ld16(tb + c, v0);
+            tmem_ld16(tb + (DUAL ? BN + c : c + 16), v1);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const int col = c + j;
-              const bool is_up = DUAL && col >= BN;
-              float f;
-              if constexpr (SWAP)
-                f = sxr[min(t.tok0 + (is_up ? col - BN : col), a.M - 1)] * (is_up ? swu : swg);
-              else
-                f = fi * (is_up ? swu : swg);
-              acc[col] = fmaf(__uint_as_float(v[j]), f, acc[col]);
+              if constexpr (DUAL) {
+                float sa;
+                if constexpr (SWAP) sa = __shfl_sync(0xffffffffu, s0.sa[(c + j) / 32], (c + j) & 31);
+                else sa = s0.sa[0];
+                acc[c + j] = fmaf(__uint_as_float(v0[j]), sa * s0.wg, acc[c + j]);
+                acc[BN + c + j] = fmaf(__uint_as_float(v1[j]), sa * s0.wu, acc[BN + c + j]);
+              } else {
+                float sa0, sa1;
+                if constexpr (SWAP) {
+                  sa0 = __shfl_sync(0xffffffffu, s0.sa[(c + j) / 32], (c + j) & 31);
+                  sa1 = __shfl_sync(0xffffffffu, s0.sa[(c + 16 + j) / 32], (c + 16 + j) & 31);
+                } else {
+                  sa0 = sa1 = s0.sa[0];
+                }
+                acc[c + j] = fmaf(__uint_as_float(v0[j]), sa0 * s0.wg, acc[c + j]);
+                acc[c + 16 + j] = fmaf(__uint_as_float(v1[j]), sa1 * s0.wg, acc[c + 16 + j]);
+              }
             }
           }
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[b]);
+          s0 = s1;
+          s1 = s2;
         }
         if (!ok) break;
       } else {
@@ -517,7 +545,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
 template <int BN, bool FP8, bool DUAL, bool SWAP>
 int launch_gemm_tc(const GemmArgs& a, int ldx_elems, int ldw_elems, int64_t w_rows,
                    cudaStream_t stream) {
-  using Cfg = GemmCfg<BN, DUAL, SWAP>;
+  using Cfg = GemmCfg<BN, DUAL, SWAP, FP8>;
   const int es = FP8 ? 1 : 2;
   CUtensorMap tm_x, tm_w;
   const uint32_t box_x = SWAP ? BN : 128;
