@@ -1,0 +1,603 @@
+// CPU backend: packet reader/validator, counter-gated multi-threaded interpreter, golden f32 ops.
+//
+// The interpreter executes exactly the model every backend shares: a worker owns a set of
+// compute-unit streams and, for the entry at the head of each, polls its wait counters, runs
+// its slice range, publishes with a release increment of its instruction's counter.  Streams
+// are in instruction order, so the globally earliest unfinished instruction always has all of
+// its entries at stream heads and the walk cannot deadlock; a watchdog deadline turns a
+// malformed program into an error code instead of a hang.
+//
+// All arithmetic is plain f32: this backend is the hermetic serving path for CPU-only boxes
+// and the numeric oracle the GPU kernels are compared against.  Reference counterparts:
+// crates/plowrt/src/exec/cpu/{interp,engine}.rs, runtime/cpu/dev/golden/*.c,
+// crates/plowrt/src/exec/health.rs (counter monitor).
+#include <atomic>
+#include <chrono>
+#include <cmath>
+#include <condition_variable>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "plow_packet.h"
+
+namespace {
+
+struct Pkt {
+  std::vector<uint8_t> raw;
+  const PlowPktHeader* hdr = nullptr;
+  const PlowTensorEnt* tensors = nullptr;
+  const PlowProgramEnt* programs = nullptr;
+  const PlowSectionEnt* sections = nullptr;
+  const char* strtab = nullptr;
+};
+
+bool in_range(const Pkt& p, uint64_t ofs, uint64_t n) {
+  return ofs >= sizeof(PlowPktHeader) && ofs + n <= p.raw.size() && ofs + n >= ofs;
+}
+
+std::string validate(Pkt& p) {
+  if (p.raw.size() < sizeof(PlowPktHeader)) return "truncated header";
+  p.hdr = reinterpret_cast<const PlowPktHeader*>(p.raw.data());
+  const PlowPktHeader& h = *p.hdr;
+  if (std::memcmp(h.magic, PLOW_PKT_MAGIC, 8) != 0) return "bad magic";
+  if (h.version != PLOW_PKT_VERSION) return "unsupported packet version";
+  if (h.header_bytes != sizeof(PlowPktHeader) || h.file_bytes != p.raw.size()) return "size mismatch";
+  if (!in_range(p, h.tensor_ofs, uint64_t(h.n_tensor) * sizeof(PlowTensorEnt))) return "tensor table out of range";
+  if (!in_range(p, h.program_ofs, uint64_t(h.n_program) * sizeof(PlowProgramEnt))) return "program table out of range";
+  if (!in_range(p, h.section_ofs, uint64_t(h.n_section) * sizeof(PlowSectionEnt))) return "section table out of range";
+  if (!in_range(p, h.strtab_ofs, h.strtab_bytes)) return "string table out of range";
+  p.tensors = reinterpret_cast<const PlowTensorEnt*>(p.raw.data() + h.tensor_ofs);
+  p.programs = reinterpret_cast<const PlowProgramEnt*>(p.raw.data() + h.program_ofs);
+  p.sections = reinterpret_cast<const PlowSectionEnt*>(p.raw.data() + h.section_ofs);
+  p.strtab = reinterpret_cast<const char*>(p.raw.data() + h.strtab_ofs);
+  if (h.strtab_bytes == 0 || p.strtab[h.strtab_bytes - 1] != 0) return "string table not terminated";
+  for (uint32_t i = 0; i < h.n_tensor; ++i) {
+    if (p.tensors[i].name_ofs >= h.strtab_bytes) return "tensor name out of range";
+    if (p.tensors[i].rank > 4) return "tensor rank > 4";
+  }
+  for (uint32_t k = 0; k < h.n_program; ++k) {
+    const PlowProgramEnt& g = p.programs[k];
+    if (!in_range(p, g.inst_ofs, uint64_t(g.n_inst) * sizeof(PlowInst))) return "inst range";
+    if (!in_range(p, g.stream_ofs, uint64_t(g.n_stream) * sizeof(PlowStreamEnt))) return "stream range";
+    if (!in_range(p, g.cu_ofs, uint64_t(g.n_cu + 1) * 4)) return "cu_ofs range";
+    if (!in_range(p, g.wait_ofs, uint64_t(g.n_wait) * sizeof(PlowWait)) && g.n_wait) return "wait range";
+    if (!in_range(p, g.succ_ofs, uint64_t(g.n_succ) * 4) && g.n_succ) return "succ range";
+    if (!in_range(p, g.actmap_ofs, uint64_t(h.n_tensor) * 8)) return "actmap range";
+    const PlowInst* insts = reinterpret_cast<const PlowInst*>(p.raw.data() + g.inst_ofs);
+    const PlowStreamEnt* st = reinterpret_cast<const PlowStreamEnt*>(p.raw.data() + g.stream_ofs);
+    const uint32_t* cu = reinterpret_cast<const uint32_t*>(p.raw.data() + g.cu_ofs);
+    const PlowWait* waits = reinterpret_cast<const PlowWait*>(p.raw.data() + g.wait_ofs);
+    const uint32_t* succs = reinterpret_cast<const uint32_t*>(p.raw.data() + g.succ_ofs);
+    if (cu[0] != 0 || cu[g.n_cu] != g.n_stream) return "cu_ofs does not cover the stream";
+    for (uint32_t c = 0; c < g.n_cu; ++c)
+      if (cu[c] > cu[c + 1]) return "cu_ofs not monotone";
+    for (uint32_t i = 0; i < g.n_inst; ++i) {
+      if (insts[i].op >= PLOW_OP__COUNT) return "unknown opcode";
+      for (int j = 0; j < 8; ++j)
+        if (insts[i].t[j] != PLOW_T_NONE && insts[i].t[j] >= h.n_tensor) return "tensor handle out of range";
+    }
+    for (uint32_t s = 0; s < g.n_stream; ++s) {
+      if (st[s].inst >= g.n_inst) return "stream entry names a missing instruction";
+      if (uint32_t(st[s].slice0) + st[s].nslice > insts[st[s].inst].nslice) return "slice range exceeds instruction";
+      if (uint64_t(st[s].wait_ofs) + st[s].n_wait > g.n_wait) return "wait range out of bounds";
+      if (uint64_t(st[s].succ_ofs) + st[s].n_succ > g.n_succ) return "succ range out of bounds";
+    }
+    for (uint32_t w = 0; w < g.n_wait; ++w)
+      if (waits[w].ctr >= g.n_ctr) return "wait counter out of range";
+    for (uint32_t s = 0; s < g.n_succ; ++s)
+      if (succs[s] >= g.n_ctr) return "succ counter out of range";
+  }
+  return "";
+}
+
+// ---------------------------------------------------------------------------------------------
+struct StepIO {
+  int32_t rows;
+  int32_t n_sample;
+  const int32_t* page_table;  // [n_slots, max_pages]
+  int32_t max_pages;
+  const int32_t* kvlen;       // [n_slots] (unused by the causal path; pos drives the mask)
+  int32_t n_slots;
+  const int32_t* pos;         // [rows]
+  const int32_t* seq;         // [rows]
+};
+
+struct Engine {
+  Pkt* pkt;
+  int n_threads;
+  std::vector<void*> bound;          // per tensor handle
+  std::vector<uint8_t> arena;
+  std::vector<std::thread> workers;
+  std::mutex mu;
+  std::condition_variable cv_start, cv_done;
+  uint64_t generation = 0;
+  int pending = 0;
+  bool quit = false;
+  // per run
+  const PlowProgramEnt* prog = nullptr;
+  StepIO io{};
+  std::vector<std::atomic<uint32_t>> counters;
+  std::atomic<int> status{0};
+  std::vector<PlowTraceRec> trace;
+  bool trace_on = false;
+  double watchdog_s = 30.0;
+};
+
+inline uint64_t now_ns() {
+  return std::chrono::duration_cast<std::chrono::nanoseconds>(
+             std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+struct Ctx {
+  Engine* e;
+  const PlowInst* in;
+  int s0, s1, ns;  // slice range [s0, s1) of ns
+  void* T(int j) const {
+    uint16_t h = in->t[j];
+    if (h == PLOW_T_NONE) return nullptr;
+    const PlowTensorEnt& te = e->pkt->tensors[h];
+    if (te.tclass == PLOW_TC_ACT) {
+      const uint64_t* actmap = reinterpret_cast<const uint64_t*>(e->pkt->raw.data() + e->prog->actmap_ofs);
+      return e->arena.data() + actmap[h];
+    }
+    return e->bound[h];
+  }
+  // work range of this entry over W items
+  void range(int64_t W, int64_t& a, int64_t& b) const {
+    a = W * s0 / ns;
+    b = W * s1 / ns;
+  }
+};
+
+inline float dotf(const float* a, const float* b, int n) {
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  int i = 0;
+  for (; i + 8 <= n; i += 8)
+    for (int j = 0; j < 8; ++j) acc[j] += a[i + j] * b[i + j];
+  float s = 0.f;
+  for (; i < n; ++i) s += a[i] * b[i];
+  for (int j = 0; j < 8; ++j) s += acc[j];
+  return s;
+}
+
+void op_embed(const Ctx& c) {
+  float* out = (float*)c.T(0);
+  const float* tab = (const float*)c.T(1);
+  const int32_t* ids = (const int32_t*)c.T(2);
+  const int H = c.in->i[0];
+  const float scale = c.in->w[0].f;
+  int64_t a, b;
+  c.range(c.e->io.rows, a, b);
+  for (int64_t r = a; r < b; ++r) {
+    const float* src = tab + int64_t(ids[r]) * H;
+    for (int j = 0; j < H; ++j) out[r * H + j] = scale == 1.0f ? src[j] : src[j] * scale;
+  }
+}
+
+inline void rmsnorm_row(float* out, const float* x, const float* g, int W, float eps, int mode) {
+  float ss = 0.f;
+  for (int j = 0; j < W; ++j) ss += x[j] * x[j];
+  const float r = 1.0f / std::sqrt(ss / W + eps);
+  for (int j = 0; j < W; ++j) {
+    const float gm = g ? (mode ? 1.0f + g[j] : g[j]) : 1.0f;
+    out[j] = x[j] * r * gm;
+  }
+}
+
+void op_rmsnorm(const Ctx& c, int64_t rows) {
+  float* out = (float*)c.T(0);
+  const float* x = (const float*)c.T(1);
+  const float* g = (const float*)c.T(2);
+  const int W = c.in->i[0], mode = c.in->i[1];
+  const int co = c.in->i[6], pitch = c.in->i[7] ? c.in->i[7] : W;
+  int64_t a, b;
+  c.range(rows, a, b);
+  for (int64_t r = a; r < b; ++r) rmsnorm_row(out + r * W, x + r * pitch + co, g, W, c.in->w[0].f, mode);
+}
+
+void op_add_norm(const Ctx& c) {
+  float* h = (float*)c.T(0);
+  const float* x = (const float*)c.T(1);
+  const float* d = (const float*)c.T(2);
+  const float* g = (const float*)c.T(3);
+  float* xo = (float*)c.T(4);
+  const int W = c.in->i[0];
+  int64_t a, b;
+  c.range(c.e->io.rows, a, b);
+  for (int64_t r = a; r < b; ++r) {
+    for (int j = 0; j < W; ++j) xo[r * W + j] = x[r * W + j] + d[r * W + j];
+    rmsnorm_row(h + r * W, xo + r * W, g, W, c.in->w[0].f, c.in->i[1]);
+  }
+}
+
+void op_residual(const Ctx& c) {
+  float* o = (float*)c.T(0);
+  const float* x = (const float*)c.T(1);
+  const float* d = (const float*)c.T(2);
+  const int W = c.in->i[0];
+  int64_t a, b;
+  c.range(c.e->io.rows, a, b);
+  for (int64_t k = a * W; k < b * W; ++k) o[k] = x[k] + d[k];
+}
+
+void op_gemm(const Ctx& c, int64_t rows) {
+  float* y = (float*)c.T(0);
+  const float* x = (const float*)c.T(1);
+  const float* w = (const float*)c.T(2);
+  const int N = c.in->i[0], K = c.in->i[1];
+  const uint32_t flags = c.in->i[2];
+  const int co = c.in->i[6], pitch = c.in->i[7] ? c.in->i[7] : K;
+  const bool dual = flags & PLOW_GEMM_DUAL_SILU;
+  int64_t a, b;
+  c.range(N, a, b);
+  for (int64_t m = 0; m < rows; ++m) {
+    const float* xr = x + m * pitch + co;
+    for (int64_t n = a; n < b; ++n) {
+      float v = dotf(xr, w + n * K, K);
+      if (dual) {
+        const float u = dotf(xr, w + (n + N) * K, K);
+        v = v / (1.0f + std::exp(-v)) * u;
+      }
+      y[m * N + n] = v;
+    }
+  }
+}
+
+inline void rope_head(float* out, const float* x, const float* tab, int hd, int rot, int pair) {
+  // tab row: [cos(rot/2) | sin(rot/2)]
+  const int half = rot / 2;
+  const float* cs = tab;
+  const float* sn = tab + half;
+  if (pair == 0) {
+    for (int i = 0; i < half; ++i) {
+      const float a = x[i], b = x[i + half];
+      out[i] = a * cs[i] - b * sn[i];
+      out[i + half] = b * cs[i] + a * sn[i];
+    }
+  } else {
+    for (int i = 0; i < half; ++i) {
+      const float a = x[2 * i], b = x[2 * i + 1];
+      out[2 * i] = a * cs[i] - b * sn[i];
+      out[2 * i + 1] = b * cs[i] + a * sn[i];
+    }
+  }
+  for (int i = rot; i < hd; ++i) out[i] = x[i];
+}
+
+void op_rope_kv(const Ctx& c) {
+  float* qo = (float*)c.T(0);
+  const float* qkv = (const float*)c.T(1);
+  float* kc = (float*)c.T(2);
+  float* vc = (float*)c.T(3);
+  const float* qn = (const float*)c.T(4);
+  const float* kn = (const float*)c.T(5);
+  const float* rope = (const float*)c.T(6);
+  const int nq = c.in->i[0], nkv = c.in->i[1], hd = c.in->i[2], rot = c.in->i[3], pair = c.in->i[4];
+  const int gmode = c.in->i[6];
+  const float eps = c.in->w[0].f;
+  const StepIO& io = c.e->io;
+  const int W = (nq + 2 * nkv) * hd;
+  std::vector<float> tmp(hd);
+  int64_t a, b;
+  c.range(io.rows, a, b);
+  for (int64_t r = a; r < b; ++r) {
+    const int pos = io.pos[r], slot = io.seq[r];
+    const float* tab = rope + int64_t(pos) * rot;
+    const int page = io.page_table[int64_t(slot) * io.max_pages + pos / PLOW_KV_PAGE];
+    const int64_t cell = (int64_t(page) * PLOW_KV_PAGE + pos % PLOW_KV_PAGE) * nkv * hd;
+    const float* row = qkv + r * W;
+    for (int h = 0; h < nq; ++h) {
+      const float* src = row + h * hd;
+      if (qn) { rmsnorm_row(tmp.data(), src, qn, hd, eps, gmode); src = tmp.data(); }
+      rope_head(qo + (r * nq + h) * hd, src, tab, hd, rot, pair);
+    }
+    for (int h = 0; h < nkv; ++h) {
+      const float* src = row + (nq + h) * hd;
+      if (kn) { rmsnorm_row(tmp.data(), src, kn, hd, eps, gmode); src = tmp.data(); }
+      rope_head(kc + cell + h * hd, src, tab, hd, rot, pair);
+      std::memcpy(vc + cell + h * hd, row + (nq + nkv + h) * hd, sizeof(float) * hd);
+    }
+  }
+}
+
+void op_attn(const Ctx& c) {
+  float* out = (float*)c.T(0);
+  const float* q = (const float*)c.T(1);
+  const float* kc = (const float*)c.T(2);
+  const float* vc = (const float*)c.T(3);
+  const int nq = c.in->i[0], nkv = c.in->i[1], hd = c.in->i[2], window = c.in->i[3];
+  const float scale = c.in->w[0].f;
+  const StepIO& io = c.e->io;
+  const int group = nq / nkv;
+  std::vector<float> sc;
+  int64_t a, b;
+  c.range(int64_t(io.rows) * nq, a, b);
+  for (int64_t item = a; item < b; ++item) {
+    const int64_t r = item / nq;
+    const int h = int(item % nq), kvh = h / group;
+    const int pos = io.pos[r], slot = io.seq[r];
+    const int t0 = window > 0 ? std::max(0, pos - window + 1) : 0;
+    const int n = pos - t0 + 1;
+    sc.resize(n);
+    const float* qr = q + (r * nq + h) * hd;
+    float mx = -INFINITY;
+    for (int t = t0; t <= pos; ++t) {
+      const int page = io.page_table[int64_t(slot) * io.max_pages + t / PLOW_KV_PAGE];
+      const float* kr = kc + ((int64_t(page) * PLOW_KV_PAGE + t % PLOW_KV_PAGE) * nkv + kvh) * hd;
+      const float s = dotf(qr, kr, hd) * scale;
+      sc[t - t0] = s;
+      mx = std::max(mx, s);
+    }
+    float den = 0.f;
+    for (int i = 0; i < n; ++i) { sc[i] = std::exp(sc[i] - mx); den += sc[i]; }
+    float* o = out + (r * nq + h) * hd;
+    for (int d = 0; d < hd; ++d) o[d] = 0.f;
+    for (int t = t0; t <= pos; ++t) {
+      const int page = io.page_table[int64_t(slot) * io.max_pages + t / PLOW_KV_PAGE];
+      const float* vr = vc + ((int64_t(page) * PLOW_KV_PAGE + t % PLOW_KV_PAGE) * nkv + kvh) * hd;
+      const float p = sc[t - t0] / den;
+      for (int d = 0; d < hd; ++d) o[d] += p * vr[d];
+    }
+  }
+}
+
+void op_row_gather(const Ctx& c) {
+  float* out = (float*)c.T(0);
+  const float* x = (const float*)c.T(1);
+  const int32_t* rows = (const int32_t*)c.T(2);
+  const int W = c.in->i[0];
+  int64_t a, b;
+  c.range(c.e->io.n_sample, a, b);
+  for (int64_t s = a; s < b; ++s) std::memcpy(out + s * W, x + int64_t(rows[s]) * W, sizeof(float) * W);
+}
+
+void op_argmax(const Ctx& c) {
+  int32_t* out = (int32_t*)c.T(0);
+  const float* lg = (const float*)c.T(1);
+  const int V = c.in->i[0];
+  int64_t a, b;
+  c.range(c.e->io.n_sample, a, b);
+  for (int64_t s = a; s < b; ++s) {
+    const float* row = lg + s * V;
+    int best = 0;
+    for (int j = 1; j < V; ++j)
+      if (row[j] > row[best]) best = j;  // strict: lowest index wins ties
+    out[s] = best;
+  }
+}
+
+void op_glu(const Ctx& c) {
+  float* out = (float*)c.T(0);
+  const float* g = (const float*)c.T(1);
+  const float* u = (const float*)c.T(2);
+  const PlowTensorEnt& te = c.e->pkt->tensors[c.in->t[0]];
+  const int W = int(te.dims[1]);
+  int64_t a, b;
+  c.range(c.e->io.rows, a, b);
+  for (int64_t k = a * W; k < b * W; ++k) out[k] = g[k] / (1.0f + std::exp(-g[k])) * u[k];
+}
+
+int exec_entry(Engine* e, const PlowInst* in, const PlowStreamEnt& se) {
+  Ctx c{e, in, se.slice0, se.slice0 + se.nslice, in->nslice};
+  switch (in->op) {
+    case PLOW_OP_NOP: return 0;
+    case PLOW_OP_EMBED: op_embed(c); return 0;
+    case PLOW_OP_RMSNORM: {
+      const PlowTensorEnt& te = e->pkt->tensors[in->t[0]];
+      op_rmsnorm(c, te.dims[0] == -2 ? e->io.n_sample : e->io.rows);
+      return 0;
+    }
+    case PLOW_OP_ADD_NORM: op_add_norm(c); return 0;
+    case PLOW_OP_RESIDUAL: op_residual(c); return 0;
+    case PLOW_OP_GEMM: {
+      const PlowTensorEnt& te = e->pkt->tensors[in->t[0]];
+      op_gemm(c, te.dims[0] == -2 ? e->io.n_sample : e->io.rows);
+      return 0;
+    }
+    case PLOW_OP_ROPE_KV: op_rope_kv(c); return 0;
+    case PLOW_OP_ATTN: op_attn(c); return 0;
+    case PLOW_OP_ROW_GATHER: op_row_gather(c); return 0;
+    case PLOW_OP_ARGMAX: op_argmax(c); return 0;
+    case PLOW_OP_GLU: op_glu(c); return 0;
+    default: return 100 + in->op;  // op not implemented on the CPU backend
+  }
+}
+
+void run_worker_program(Engine* e, int tid) {
+  const PlowProgramEnt& g = *e->prog;
+  const uint8_t* base = e->pkt->raw.data();
+  const PlowInst* insts = reinterpret_cast<const PlowInst*>(base + g.inst_ofs);
+  const PlowStreamEnt* st = reinterpret_cast<const PlowStreamEnt*>(base + g.stream_ofs);
+  const uint32_t* cu = reinterpret_cast<const uint32_t*>(base + g.cu_ofs);
+  const PlowWait* waits = reinterpret_cast<const PlowWait*>(base + g.wait_ofs);
+  const uint32_t* succs = reinterpret_cast<const uint32_t*>(base + g.succ_ofs);
+  std::vector<uint32_t> pc, end, ids;
+  for (uint32_t c = tid; c < g.n_cu; c += e->n_threads) { pc.push_back(cu[c]); end.push_back(cu[c + 1]); ids.push_back(c); }
+  uint64_t last_progress = now_ns();
+  size_t live = pc.size();
+  while (live > 0 && e->status.load(std::memory_order_relaxed) == 0) {
+    bool progressed = false;
+    live = 0;
+    for (size_t k = 0; k < pc.size(); ++k) {
+      if (pc[k] >= end[k]) continue;
+      ++live;
+      const PlowStreamEnt& se = st[pc[k]];
+      const uint64_t t_arrive = e->trace_on ? now_ns() : 0;
+      bool ready = true;
+      for (uint32_t w = 0; w < se.n_wait; ++w) {
+        const PlowWait& pw = waits[se.wait_ofs + w];
+        if (e->counters[size_t(pw.ctr) * PLOW_CTR_STRIDE_U32].load(std::memory_order_acquire) < pw.target) { ready = false; break; }
+      }
+      if (!ready) continue;
+      const uint64_t t_ready = e->trace_on ? now_ns() : 0;
+      const int rc = exec_entry(e, &insts[se.inst], se);
+      if (rc) { e->status.store(rc); return; }
+      for (uint32_t s = 0; s < se.n_succ; ++s)
+        e->counters[size_t(succs[se.succ_ofs + s]) * PLOW_CTR_STRIDE_U32].fetch_add(1, std::memory_order_release);
+      if (e->trace_on) {
+        PlowTraceRec& tr = e->trace[pc[k]];
+        tr.cu = ids[k]; tr.pc = pc[k] - cu[ids[k]]; tr.inst = se.inst; tr.op = insts[se.inst].op;
+        tr.t_arrive = t_arrive; tr.t_ready = t_ready; tr.t_end = now_ns();
+      }
+      ++pc[k];
+      progressed = true;
+    }
+    if (progressed) last_progress = now_ns();
+    else if (live) {
+      if ((now_ns() - last_progress) * 1e-9 > e->watchdog_s) { e->status.store(2); return; }  // unsatisfiable wait
+      std::this_thread::yield();
+    }
+  }
+}
+
+void worker_main(Engine* e, int tid) {
+  uint64_t seen = 0;
+  while (true) {
+    {
+      std::unique_lock<std::mutex> lk(e->mu);
+      e->cv_start.wait(lk, [&] { return e->quit || e->generation != seen; });
+      if (e->quit) return;
+      seen = e->generation;
+    }
+    run_worker_program(e, tid);
+    {
+      std::lock_guard<std::mutex> lk(e->mu);
+      if (--e->pending == 0) e->cv_done.notify_all();
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+uint64_t plow_abi_sizeof(const char* name) {
+  const std::string n(name);
+  if (n == "PlowInst") return sizeof(PlowInst);
+  if (n == "PlowStreamEnt") return sizeof(PlowStreamEnt);
+  if (n == "PlowWait") return sizeof(PlowWait);
+  if (n == "PlowTraceRec") return sizeof(PlowTraceRec);
+  if (n == "PlowPktHeader") return sizeof(PlowPktHeader);
+  if (n == "PlowTensorEnt") return sizeof(PlowTensorEnt);
+  if (n == "PlowProgramEnt") return sizeof(PlowProgramEnt);
+  if (n == "PlowSectionEnt") return sizeof(PlowSectionEnt);
+  return 0;
+}
+
+int plow_abi_constant(const char* name) {
+  const std::string n(name);
+#define C(x) if (n == #x) return int(x);
+  C(PLOW_OP_NOP) C(PLOW_OP_EMBED) C(PLOW_OP_RMSNORM) C(PLOW_OP_ADD_NORM) C(PLOW_OP_GEMM) C(PLOW_OP_ROPE_KV)
+  C(PLOW_OP_ATTN) C(PLOW_OP_ROW_GATHER) C(PLOW_OP_ARGMAX) C(PLOW_OP_SAMPLE) C(PLOW_OP_RESIDUAL) C(PLOW_OP_GLU)
+  C(PLOW_OP_QUANT_ACT) C(PLOW_OP_MLA_KV_WRITE) C(PLOW_OP_MLA_Q_ROPE) C(PLOW_OP_MLA_DECODE) C(PLOW_OP_MLA_PREFILL)
+  C(PLOW_OP_MLA_ABSORB_Q) C(PLOW_OP_MLA_FOLD_V) C(PLOW_OP_DSA_INDEX) C(PLOW_OP_DSA_TOPK) C(PLOW_OP_ROUTER_TOPK)
+  C(PLOW_OP_MOE_ALIGN) C(PLOW_OP_MOE_GATHER) C(PLOW_OP_MOE_GEMM) C(PLOW_OP_MOE_COMBINE) C(PLOW_OP_GDN_CONV)
+  C(PLOW_OP_GDN_GATES) C(PLOW_OP_GDN_STEP) C(PLOW_OP_GDN_CHUNK) C(PLOW_OP_GATED_NORM) C(PLOW_OP_SIGMOID_GATE)
+  C(PLOW_OP_XREDUCE) C(PLOW_OP_XREDUCE_ADD_NORM) C(PLOW_OP_XGATHER) C(PLOW_OP_XREDUCE_SCATTER)
+  C(PLOW_OP_XA2A_DISPATCH) C(PLOW_OP_XA2A_COMBINE) C(PLOW_OP_XARGMAX_FIN) C(PLOW_OP_GEMM_XREDUCE)
+  C(PLOW_OP_XGATHER_GEMM) C(PLOW_OP__COUNT)
+  C(PLOW_PKT_VERSION) C(PLOW_CTR_STRIDE_U32) C(PLOW_KV_PAGE) C(PLOW_T_NONE)
+  C(PLOW_GEMM_DUAL_SILU) C(PLOW_GEMM_FP8_BLOCK) C(PLOW_GEMM_OUT_F32) C(PLOW_GEMM_RESIDUAL) C(PLOW_GEMM_QUANT_OUT)
+  C(PLOW_TC_WEIGHT) C(PLOW_TC_DERIVED) C(PLOW_TC_GEN) C(PLOW_TC_KV) C(PLOW_TC_STATE) C(PLOW_TC_ACT) C(PLOW_TC_INPUT)
+  C(PLOW_TC_OUTPUT) C(PLOW_TC_PEER)
+#undef C
+  return -1;
+}
+
+void* plow_pkt_open(const char* path, char* err, int errlen) {
+  FILE* f = std::fopen(path, "rb");
+  if (!f) { std::snprintf(err, errlen, "cannot open %s", path); return nullptr; }
+  std::fseek(f, 0, SEEK_END);
+  long n = std::ftell(f);
+  std::fseek(f, 0, SEEK_SET);
+  Pkt* p = new Pkt;
+  p->raw.resize(n);
+  const size_t got = std::fread(p->raw.data(), 1, n, f);
+  std::fclose(f);
+  if (got != size_t(n)) { std::snprintf(err, errlen, "short read"); delete p; return nullptr; }
+  const std::string e = validate(*p);
+  if (!e.empty()) { std::snprintf(err, errlen, "%s", e.c_str()); delete p; return nullptr; }
+  return p;
+}
+void plow_pkt_close(void* p) { delete static_cast<Pkt*>(p); }
+int plow_pkt_n_tensor(void* p) { return static_cast<Pkt*>(p)->hdr->n_tensor; }
+int plow_pkt_n_program(void* p) { return static_cast<Pkt*>(p)->hdr->n_program; }
+const char* plow_pkt_tensor_name(void* p, int i) {
+  Pkt* k = static_cast<Pkt*>(p);
+  return k->strtab + k->tensors[i].name_ofs;
+}
+
+void* plow_cpu_engine_create(void* pkt, int n_threads) {
+  Engine* e = new Engine;
+  e->pkt = static_cast<Pkt*>(pkt);
+  e->n_threads = n_threads < 1 ? 1 : n_threads;
+  e->bound.assign(e->pkt->hdr->n_tensor, nullptr);
+  e->arena.resize(e->pkt->hdr->act_arena_bytes + 256);
+  for (int t = 0; t < e->n_threads; ++t) e->workers.emplace_back(worker_main, e, t);
+  return e;
+}
+void plow_cpu_engine_destroy(void* h) {
+  Engine* e = static_cast<Engine*>(h);
+  {
+    std::lock_guard<std::mutex> lk(e->mu);
+    e->quit = true;
+  }
+  e->cv_start.notify_all();
+  for (auto& w : e->workers) w.join();
+  delete e;
+}
+int plow_cpu_bind(void* h, int handle, void* ptr) {
+  Engine* e = static_cast<Engine*>(h);
+  if (handle < 0 || size_t(handle) >= e->bound.size()) return -1;
+  e->bound[handle] = ptr;
+  return 0;
+}
+void plow_cpu_set_watchdog(void* h, double seconds) { static_cast<Engine*>(h)->watchdog_s = seconds; }
+void plow_cpu_set_trace(void* h, int on) { static_cast<Engine*>(h)->trace_on = on != 0; }
+
+// Runs one program to completion.  Returns 0, 1 = unbound tensor, 2 = watchdog (unsatisfiable
+// wait), 100+op = opcode without a CPU body.
+int plow_cpu_run(void* h, int program, const StepIO* io) {
+  Engine* e = static_cast<Engine*>(h);
+  if (program < 0 || uint32_t(program) >= e->pkt->hdr->n_program) return -1;
+  e->prog = &e->pkt->programs[program];
+  if (io->rows > int32_t(e->prog->rows)) return -2;
+  e->io = *io;
+  const PlowProgramEnt& g = *e->prog;
+  const PlowInst* insts = reinterpret_cast<const PlowInst*>(e->pkt->raw.data() + g.inst_ofs);
+  for (uint32_t i = 0; i < g.n_inst; ++i)
+    for (int j = 0; j < 8; ++j) {
+      const uint16_t t = insts[i].t[j];
+      if (t != PLOW_T_NONE && e->pkt->tensors[t].tclass != PLOW_TC_ACT && !e->bound[t]) return 1;
+    }
+  std::vector<std::atomic<uint32_t>> ctr(size_t(g.n_ctr) * PLOW_CTR_STRIDE_U32);
+  for (auto& c : ctr) c.store(0, std::memory_order_relaxed);
+  e->counters.swap(ctr);
+  e->status.store(0);
+  if (e->trace_on) e->trace.assign(g.n_stream, PlowTraceRec{});
+  {
+    std::lock_guard<std::mutex> lk(e->mu);
+    e->pending = e->n_threads;
+    ++e->generation;
+  }
+  e->cv_start.notify_all();
+  {
+    std::unique_lock<std::mutex> lk(e->mu);
+    e->cv_done.wait(lk, [&] { return e->pending == 0; });
+  }
+  return e->status.load();
+}
+int plow_cpu_trace(void* h, PlowTraceRec* out, int cap) {
+  Engine* e = static_cast<Engine*>(h);
+  const int n = std::min<int>(cap, int(e->trace.size()));
+  std::memcpy(out, e->trace.data(), sizeof(PlowTraceRec) * n);
+  return n;
+}
+void* plow_cpu_arena(void* h) { return static_cast<Engine*>(h)->arena.data(); }
+
+}  // extern "C"

@@ -1,0 +1,330 @@
+"""Model-agnostic op-graph IR and the model zoo that builds it from a :class:`ModelSpec`.
+
+A graph is a topologically ordered list of :class:`Node` over named :class:`Value` s.  Shapes are
+symbolic in the row count (``R`` = rows of the token batch, ``S`` = sampled rows), which the
+scheduler binds per program (prefill bucket / decode rung).  Builders emit *primitive* ops
+(linear, rmsnorm, rope, add ...); :mod:`plow_b200.compiler.rewrite` fuses them into the ISA's
+vocabulary.  Weight values carry the checkpoint tensor name — names are the weight contract.
+
+Reference counterpart: crates/nn-graph (op.rs, graph.rs, builder.rs, models/*.rs).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+from ..models.config import ModelSpec
+
+R = "R"   # rows of the running program
+S = "S"   # sampled rows (one per sequence that finishes a chunk)
+
+
+@dataclass
+class Value:
+    name: str
+    shape: tuple
+    dtype: str                 # f32 | bf16 | e4m3 | i32
+    kind: str = "act"          # weight | derived | gen | kv | state | act | input | output | peer
+    shard_axis: int | None = None   # tensor-parallel shard axis of a weight
+    meta: dict = field(default_factory=dict)
+
+
+@dataclass
+class Node:
+    op: str
+    inputs: list
+    outputs: list
+    attrs: dict = field(default_factory=dict)
+    layer: int = -1
+    site: str = ""             # fusion site name once rewritten
+
+
+class Graph:
+    def __init__(self, spec: ModelSpec, tp: int = 1, ep: int = 1, rank: int = 0):
+        self.spec = spec
+        self.tp, self.ep, self.rank = tp, ep, rank
+        self.values: dict[str, Value] = {}
+        self.nodes: list[Node] = []
+        self._n = 0
+
+    # ---- construction ---------------------------------------------------------------------
+    def value(self, name, shape, dtype, kind="act", **kw) -> str:
+        if name in self.values:
+            return name
+        self.values[name] = Value(name, tuple(shape), dtype, kind, **kw)
+        return name
+
+    def tmp(self, base, shape, dtype=None) -> str:
+        self._n += 1
+        return self.value(f"act.{base}.{self._n}", shape, dtype or self.spec.dtype)
+
+    def add(self, op, inputs, outputs, layer=-1, **attrs) -> Node:
+        for v in list(inputs) + list(outputs):
+            if v is not None and v not in self.values:
+                raise KeyError(f"{op}: unknown value {v}")
+        n = Node(op, list(inputs), list(outputs), attrs, layer)
+        self.nodes.append(n)
+        return n
+
+    def weight(self, name, shape, shard_axis=None, dtype=None) -> str:
+        return self.value(name, shape, dtype or self.weight_dtype(), "weight", shard_axis=shard_axis)
+
+    def weight_dtype(self) -> str:
+        return self.spec.dtype
+
+    # ---- queries --------------------------------------------------------------------------
+    def producers(self) -> dict:
+        return {o: n for n in self.nodes for o in n.outputs}
+
+    def consumers(self) -> dict:
+        c: dict[str, list] = {}
+        for n in self.nodes:
+            for i in n.inputs:
+                if i is not None:
+                    c.setdefault(i, []).append(n)
+        return c
+
+    def check_topological(self) -> None:
+        seen = {k for k, v in self.values.items() if v.kind != "act"}
+        for n in self.nodes:
+            for i in n.inputs:
+                if i is not None and self.values[i].kind == "act" and i not in seen:
+                    raise ValueError(f"{n.op} reads {i} before it is produced")
+            seen.update(n.outputs)
+
+    def bind(self, shape, rows, samples):
+        return tuple(rows if d == R else samples if d == S else d for d in shape)
+
+
+# ------------------------------------------------------------------------------------------------
+# builders
+# ------------------------------------------------------------------------------------------------
+def build_graph(spec: ModelSpec, tp: int = 1, ep: int = 1, rank: int = 0) -> Graph:
+    g = Graph(spec, tp, ep, rank)
+    H, V = spec.hidden, spec.vocab
+    ids = g.value("in.ids", (R,), "i32", "input")
+    g.value("in.pos", (R,), "i32", "input")
+    g.value("in.seq", (R,), "i32", "input")
+    g.value("in.sample_rows", (S,), "i32", "input")
+    emb = g.weight("model.embed_tokens.weight", (V, H))
+    x = g.tmp("x", (R, H))
+    g.add("embed", [emb, ids], [x], scale=spec.embed_scale)
+    for li, layer in enumerate(spec.layers):
+        p = f"model.layers.{li}"
+        ln1 = g.weight(f"{p}.input_layernorm.weight", (H,), dtype="f32" if spec.dtype == "f32" else "bf16")
+        h = g.tmp("h", (R, H))
+        g.add("rmsnorm", [x, ln1], [h], layer=li, eps=spec.rms_eps, plus_one=spec.norm_plus_one)
+        if layer.attn.kind == "gqa":
+            o = _gqa_attention(g, li, p, h, layer.attn)
+        elif layer.attn.kind == "mla":
+            o = _mla_attention(g, li, p, h, layer.attn)
+        else:
+            o = _gdn_attention(g, li, p, h, layer.attn)
+        if tp > 1:
+            o = _xreduce(g, o, li)
+        x2 = g.tmp("x", (R, H))
+        g.add("add", [x, o], [x2], layer=li)
+        ln2 = g.weight(f"{p}.post_attention_layernorm.weight", (H,), dtype="f32" if spec.dtype == "f32" else "bf16")
+        h2 = g.tmp("h", (R, H))
+        g.add("rmsnorm", [x2, ln2], [h2], layer=li, eps=spec.rms_eps, plus_one=spec.norm_plus_one)
+        if layer.ffn.kind == "dense":
+            d = _dense_ffn(g, li, f"{p}.mlp", h2, layer.ffn.inter)
+            if tp > 1:
+                d = _xreduce(g, d, li)
+        else:
+            d = _moe_ffn(g, li, f"{p}.mlp", h2, layer.ffn)
+        x3 = g.tmp("x", (R, H))
+        g.add("add", [x2, d], [x3], layer=li)
+        x = x3
+    fn = g.weight("model.norm.weight", (H,), dtype="f32" if spec.dtype == "f32" else "bf16")
+    hf = g.tmp("h", (R, H))
+    g.add("rmsnorm", [x, fn], [hf], eps=spec.rms_eps, plus_one=spec.norm_plus_one)
+    hs = g.tmp("hs", (S, H))
+    g.add("row_gather", [hf, "in.sample_rows"], [hs])
+    head = emb if spec.tie_embeddings else g.weight("lm_head.weight", (V, H))
+    logits = g.value("out.logits", (S, V), "f32", "output")
+    g.add("linear", [hs, head], [logits], out_f32=True)
+    out_ids = g.value("out.ids", (S,), "i32", "output")
+    g.add("argmax", [logits], [out_ids])
+    g.check_topological()
+    return g
+
+
+def _xreduce(g: Graph, v: str, li: int) -> str:
+    out = g.tmp("xr", g.values[v].shape)
+    g.add("xreduce", [v], [out], layer=li)
+    return out
+
+
+def _linear(g: Graph, li, x, wname, n_out, k_in, shard_axis=None, rows=R, **attrs) -> str:
+    tp = g.tp
+    n_l = n_out // tp if shard_axis == 0 else n_out
+    k_l = k_in // tp if shard_axis == 1 else k_in
+    w = g.weight(wname, (n_l, k_l), shard_axis=shard_axis)
+    y = g.tmp("y", (rows, n_l))
+    g.add("linear", [x, w], [y], layer=li, **attrs)
+    return y
+
+
+def _gqa_attention(g: Graph, li, p, h, a) -> str:
+    spec, tp = g.spec, g.tp
+    H = spec.hidden
+    nq, nkv, hd = a.n_heads // tp, max(1, a.n_kv_heads // tp), a.head_dim
+    qd = a.n_heads * hd * (2 if a.gated else 1)
+    q = _linear(g, li, h, f"{p}.self_attn.q_proj.weight", qd, H, shard_axis=0)
+    k = _linear(g, li, h, f"{p}.self_attn.k_proj.weight", a.n_kv_heads * hd, H, shard_axis=0)
+    v = _linear(g, li, h, f"{p}.self_attn.v_proj.weight", a.n_kv_heads * hd, H, shard_axis=0)
+    gate = None
+    if a.gated:
+        qs, gate = g.tmp("q", ("R", nq * hd)), g.tmp("gate", (R, nq * hd))
+        g.add("split_q_gate", [q], [qs, gate], layer=li, heads=nq, head_dim=hd)
+        q = qs
+    if a.qk_norm:
+        qn = g.weight(f"{p}.self_attn.q_norm.weight", (hd,), dtype="f32" if spec.dtype == "f32" else "bf16")
+        kn = g.weight(f"{p}.self_attn.k_norm.weight", (hd,), dtype="f32" if spec.dtype == "f32" else "bf16")
+        q2, k2 = g.tmp("q", (R, nq * hd)), g.tmp("k", (R, nkv * hd))
+        g.add("headnorm", [q, qn], [q2], layer=li, heads=nq, head_dim=hd, eps=spec.rms_eps, plus_one=spec.norm_plus_one)
+        g.add("headnorm", [k, kn], [k2], layer=li, heads=nkv, head_dim=hd, eps=spec.rms_eps, plus_one=spec.norm_plus_one)
+        q, k = q2, k2
+    rope = g.value("gen.rope", (spec.rope.max_pos, max(2, spec.rope.rot_dim)), "f32", "gen",
+                   meta=dict(theta=spec.rope.theta, rot_dim=spec.rope.rot_dim, scaling=spec.rope.scaling))
+    qr, kr = g.tmp("q", (R, nq * hd)), g.tmp("k", (R, nkv * hd))
+    g.add("rope", [q, rope, "in.pos"], [qr], layer=li, heads=nq, head_dim=hd, rot_dim=spec.rope.rot_dim, pair_mode=spec.rope.pair_mode)
+    g.add("rope", [k, rope, "in.pos"], [kr], layer=li, heads=nkv, head_dim=hd, rot_dim=spec.rope.rot_dim, pair_mode=spec.rope.pair_mode)
+    kc = g.value(f"kv.{li}.k", ("P", 64, nkv, hd), spec.kv_dtype if spec.kv_dtype != "fp8" else "e4m3", "kv")
+    vc = g.value(f"kv.{li}.v", ("P", 64, nkv, hd), spec.kv_dtype if spec.kv_dtype != "fp8" else "e4m3", "kv")
+    g.add("kv_write", [kr, v, "in.pos", "in.seq"], [kc, vc], layer=li, heads=nkv, head_dim=hd)
+    ao = g.tmp("attn", (R, nq * hd))
+    g.add("attention", [qr, kc, vc], [ao], layer=li, heads=nq, kv_heads=nkv, head_dim=hd, window=a.window,
+          scale=hd ** -0.5)
+    if gate is not None:
+        ag = g.tmp("attn", (R, nq * hd))
+        g.add("sigmoid_gate", [ao, gate], [ag], layer=li)
+        ao = ag
+    return _linear(g, li, ao, f"{p}.self_attn.o_proj.weight", H, a.n_heads * hd, shard_axis=1)
+
+
+def _dense_ffn(g: Graph, li, p, h, inter, rows=R) -> str:
+    H = g.spec.hidden
+    gt = _linear(g, li, h, f"{p}.gate_proj.weight", inter, H, shard_axis=0, rows=rows)
+    up = _linear(g, li, h, f"{p}.up_proj.weight", inter, H, shard_axis=0, rows=rows)
+    m = g.tmp("glu", (rows, inter // g.tp))
+    g.add("silu_mul", [gt, up], [m], layer=li)
+    return _linear(g, li, m, f"{p}.down_proj.weight", H, inter, shard_axis=1, rows=rows)
+
+
+def _mla_attention(g: Graph, li, p, h, a) -> str:
+    """Multi-head latent attention in absorbed form for decode (scores against the latent cache)
+    and materialised K/V for prefill; both are expressed by one ``mla_attention`` node whose
+    lowering picks the kernel per program role (reference: crates/devgen/src/mla.rs:6211-6323)."""
+    spec, tp = g.spec, g.tp
+    H = spec.hidden
+    nh = a.n_heads // tp
+    qh = a.qk_nope + a.qk_rope
+    nd = "f32" if spec.dtype == "f32" else "bf16"
+    if a.q_lora:
+        qa = _linear(g, li, h, f"{p}.self_attn.q_a_proj.weight", a.q_lora, H)
+        qn = g.weight(f"{p}.self_attn.q_a_layernorm.weight", (a.q_lora,), dtype=nd)
+        qan = g.tmp("qa", (R, a.q_lora))
+        g.add("rmsnorm", [qa, qn], [qan], layer=li, eps=spec.rms_eps, plus_one=False)
+        q = _linear(g, li, qan, f"{p}.self_attn.q_b_proj.weight", a.n_heads * qh, a.q_lora, shard_axis=0)
+    else:
+        q = _linear(g, li, h, f"{p}.self_attn.q_proj.weight", a.n_heads * qh, H, shard_axis=0)
+    kva = _linear(g, li, h, f"{p}.self_attn.kv_a_proj_with_mqa.weight", a.kv_lora + a.qk_rope, H)
+    kvn = g.weight(f"{p}.self_attn.kv_a_layernorm.weight", (a.kv_lora,), dtype=nd)
+    rope = g.value("gen.rope", (spec.rope.max_pos, max(2, spec.rope.rot_dim)), "f32", "gen",
+                   meta=dict(theta=spec.rope.theta, rot_dim=spec.rope.rot_dim, scaling=spec.rope.scaling))
+    kvd = "e4m3" if spec.kv_dtype == "fp8" else spec.kv_dtype
+    cache = g.value(f"kv.{li}.latent", ("P", 64, a.kv_lora + a.qk_rope), kvd, "kv")
+    inputs = [kva, kvn, rope, "in.pos", "in.seq"]
+    outs = [cache]
+    if spec.kv_dtype == "fp8":
+        outs.append(g.value(f"kv.{li}.latent_scale", ("P", 64), "f32", "kv"))
+    g.add("mla_kv_write", inputs, outs, layer=li, kv_lora=a.kv_lora, qk_rope=a.qk_rope, eps=spec.rms_eps,
+          pair_mode=spec.rope.pair_mode)
+    wkv_b = g.weight(f"{p}.self_attn.kv_b_proj.weight", (nh * (a.qk_nope + a.v_head), a.kv_lora), shard_axis=0)
+    ao = g.tmp("attn", (R, nh * a.v_head))
+    extra = []
+    if a.index_heads:
+        extra = [_dsa_select(g, li, p, h, qan if a.q_lora else h, a)]
+    g.add("mla_attention", [q, rope, "in.pos", wkv_b] + outs + extra, [ao], layer=li, heads=nh, kv_lora=a.kv_lora,
+          qk_nope=a.qk_nope, qk_rope=a.qk_rope, v_head=a.v_head, scale=qh ** -0.5, pair_mode=spec.rope.pair_mode,
+          sparse=bool(a.index_heads), topk=a.index_topk)
+    return _linear(g, li, ao, f"{p}.self_attn.o_proj.weight", H, a.n_heads * a.v_head, shard_axis=1)
+
+
+def _dsa_select(g: Graph, li, p, h, q_in, a) -> str:
+    """DSA lightning indexer: per-token top-k KV positions (reference: runtime/nvidia/op_dsa.cuh,
+    dev_isa.h:516-534)."""
+    spec = g.spec
+    H = spec.hidden
+    qi = _linear(g, li, q_in, f"{p}.self_attn.indexer.wq_b.weight", a.index_heads * a.index_dim,
+                 a.q_lora if a.q_lora else H)
+    ki = _linear(g, li, h, f"{p}.self_attn.indexer.wk.weight", a.index_dim, H)
+    wts = _linear(g, li, h, f"{p}.self_attn.indexer.weights_proj.weight", a.index_heads, H, out_f32=True)
+    kn_w = g.weight(f"{p}.self_attn.indexer.k_norm.weight", (a.index_dim,), dtype="f32")
+    kn_b = g.weight(f"{p}.self_attn.indexer.k_norm.bias", (a.index_dim,), dtype="f32")
+    kcache = g.value(f"kv.{li}.index_k", ("P", 64, a.index_dim), "e4m3" if spec.kv_dtype == "fp8" else spec.kv_dtype, "kv")
+    ksc = g.value(f"kv.{li}.index_k_scale", ("P", 64), "f32", "kv")
+    g.add("dsa_k_write", [ki, kn_w, kn_b, "gen.rope", "in.pos", "in.seq"], [kcache, ksc], layer=li,
+          dim=a.index_dim, rot_dim=spec.rope.rot_dim)
+    sel = g.tmp("dsa_sel", (R, a.index_topk), "i32")
+    g.add("dsa_topk", [qi, wts, kcache, ksc, "gen.rope", "in.pos", "in.seq"], [sel], layer=li,
+          heads=a.index_heads, dim=a.index_dim, topk=a.index_topk, rot_dim=spec.rope.rot_dim)
+    return sel
+
+
+def _moe_ffn(g: Graph, li, p, h, f) -> str:
+    """Router -> (dispatch) -> grouped expert GLU/down -> (combine) + shared expert.
+    Expert weights are stacked per layer as derived tensors ``cat/<p>.experts.{gate_up,down}``;
+    under expert parallelism a rank holds a contiguous range of experts (reference planner:
+    crates/packet/src/moe_ep.rs)."""
+    spec, ep = g.spec, g.ep
+    H = spec.hidden
+    E, k, F = f.n_experts, f.top_k, f.moe_inter
+    e_local = E // ep
+    gate_w = g.weight(f"{p}.gate.weight", (E, H), dtype="f32" if spec.dtype == "f32" else "bf16")
+    logits = g.tmp("router", (R, E), "f32")
+    g.add("linear", [h, gate_w], [logits], layer=li, out_f32=True, router=True)
+    inputs = [logits]
+    if f.has_bias:
+        inputs.append(g.weight(f"{p}.gate.e_score_correction_bias", (E,), dtype="f32"))
+    table = g.tmp("route", (R, k, 2), "i32")
+    g.add("router_topk", inputs, [table], layer=li, n_experts=E, top_k=k, n_group=f.n_group,
+          topk_group=f.topk_group, score=f.score, norm_topk=f.norm_topk, route_scale=f.route_scale)
+    w1 = g.value(f"cat/{p}.experts.gate_up.weight", (e_local * 2 * F, H), g.weight_dtype(), "derived",
+                 meta=dict(op="stack_experts", parts=["gate_proj", "up_proj"], prefix=f"{p}.experts", n=E,
+                           ep=ep, rank=g.rank))
+    w2 = g.value(f"cat/{p}.experts.down.weight", (e_local * H, F), g.weight_dtype(), "derived",
+                 meta=dict(op="stack_experts", parts=["down_proj"], prefix=f"{p}.experts", n=E, ep=ep, rank=g.rank))
+    y = g.tmp("moe", (R, H))
+    shared = None
+    if f.n_shared:
+        shared = _dense_ffn(g, li, f"{p}.shared_experts" if spec.family == "mla_moe" else f"{p}.shared_expert",
+                            h, F * f.n_shared)
+    g.add("moe_experts", [h, table, w1, w2] + ([shared] if shared else []), [y], layer=li, n_experts=E,
+          e_local=e_local, top_k=k, inter=F, ep=ep, has_shared=bool(shared))
+    return y
+
+
+def _gdn_attention(g: Graph, li, p, h, a) -> str:
+    """Gated delta-rule linear attention (reference semantics: runtime/nvidia/op_qwen_gdn.cuh,
+    dev_isa.h:1259-1280): causal depthwise conv + SiLU over packed qkv, L2-normalised q/k,
+    state S[V,K] per (sequence, v-head), gated RMSNorm on the way out."""
+    spec, tp = g.spec, g.tp
+    H = spec.hidden
+    hk, hv, d = a.gdn_k_heads // tp, a.gdn_v_heads // tp, a.gdn_head_dim
+    qkvz = _linear(g, li, h, f"{p}.linear_attn.in_proj_qkvz.weight", 2 * a.gdn_k_heads * d + 2 * a.gdn_v_heads * d, H, shard_axis=0)
+    ba = _linear(g, li, h, f"{p}.linear_attn.in_proj_ba.weight", 2 * a.gdn_v_heads, H, shard_axis=0)
+    conv_w = g.weight(f"{p}.linear_attn.conv1d.weight", ((2 * hk + hv) * d, a.gdn_conv), dtype="f32")
+    a_log = g.weight(f"{p}.linear_attn.A_log", (hv,), dtype="f32")
+    dt_bias = g.weight(f"{p}.linear_attn.dt_bias", (hv,), dtype="f32")
+    conv_state = g.value(f"state.{li}.conv", ("B", (2 * hk + hv) * d, a.gdn_conv - 1), "f32", "state")
+    ssm_state = g.value(f"state.{li}.ssm", ("B", hv, d, d), "f32", "state")
+    o = g.tmp("gdn", (R, hv * d))
+    g.add("gdn", [qkvz, ba, conv_w, a_log, dt_bias, "in.pos", "in.seq"], [o, conv_state, ssm_state], layer=li,
+          k_heads=hk, v_heads=hv, head_dim=d, conv=a.gdn_conv)
+    nw = g.weight(f"{p}.linear_attn.norm.weight", (d,), dtype="f32")
+    on = g.tmp("gdn", (R, hv * d))
+    g.add("gated_norm", [o, qkvz, nw], [on], layer=li, heads=hv, head_dim=d, eps=spec.rms_eps,
+          z_offset=2 * hk * d + hv * d)
+    return _linear(g, li, on, f"{p}.linear_attn.out_proj.weight", H, a.gdn_v_heads * d, shard_axis=1)

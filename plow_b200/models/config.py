@@ -1,0 +1,293 @@
+"""Checkpoint ``config.json`` -> :class:`ModelSpec` (the per-layer plan the compiler lowers).
+
+Families understood (by ``model_type`` / ``architectures``):
+
+* dense GQA decoders: llama, mistral, qwen2, qwen3 (per-head q/k RMSNorm), gemma-style ``1+γ`` norms;
+* MLA + MoE decoders: deepseek_v3 / deepseek_v2, kimi_k2, glm_moe_dsa (adds the DSA indexer);
+* hybrid linear-attention MoE decoders: qwen3_next (gated delta rule + gated full attention).
+
+The reference derives the same plan in crates/plowc/src/hf_config.rs (LayerPlan from config.json)
+and dispatches emitters on ``model_type`` in crates/devgen/src/lib.rs:9518-9646.
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+
+
+@dataclass
+class RopeSpec:
+    theta: float = 10000.0
+    rot_dim: int = 0              # rotated dims per head (partial rotary when < head_dim)
+    pair_mode: str = "half"       # "half": (i, i + rot/2) NeoX; "interleaved": (2i, 2i+1) GPT-J
+    scaling: dict | None = None   # {"type": "llama3"|"yarn"|"linear", ...}
+    max_pos: int = 4096
+
+
+@dataclass
+class AttnSpec:
+    kind: str = "gqa"             # gqa | mla | gdn
+    n_heads: int = 0
+    n_kv_heads: int = 0
+    head_dim: int = 0
+    qk_norm: bool = False
+    window: int = 0               # 0 = full attention
+    gated: bool = False           # per-head output gate (qwen3_next full attention)
+    # MLA
+    q_lora: int = 0
+    kv_lora: int = 0
+    qk_nope: int = 0
+    qk_rope: int = 0
+    v_head: int = 0
+    # DSA indexer
+    index_heads: int = 0
+    index_dim: int = 0
+    index_topk: int = 0
+    # gated delta rule
+    gdn_k_heads: int = 0
+    gdn_v_heads: int = 0
+    gdn_head_dim: int = 0
+    gdn_conv: int = 4
+
+
+@dataclass
+class FfnSpec:
+    kind: str = "dense"           # dense | moe
+    inter: int = 0
+    act: str = "silu"
+    n_experts: int = 0
+    top_k: int = 0
+    n_shared: int = 0
+    moe_inter: int = 0
+    n_group: int = 1
+    topk_group: int = 1
+    score: str = "softmax"        # softmax | sigmoid
+    norm_topk: bool = True
+    route_scale: float = 1.0
+    has_bias: bool = False        # e_score_correction_bias
+
+
+@dataclass
+class LayerSpec:
+    attn: AttnSpec
+    ffn: FfnSpec
+
+
+@dataclass
+class ModelSpec:
+    family: str
+    model_type: str
+    hidden: int
+    vocab: int
+    n_layers: int
+    rms_eps: float
+    tie_embeddings: bool
+    rope: RopeSpec
+    layers: list = field(default_factory=list)
+    norm_plus_one: bool = False   # Gemma (1 + γ)
+    embed_scale: float = 1.0
+    dtype: str = "bf16"           # compute dtype of activations
+    weight_quant: str = "none"    # none | fp8_block128
+    kv_dtype: str = "bf16"        # bf16 | fp8 | f32
+    max_ctx: int = 4096
+    bos_token_id: int | None = None
+    eos_token_ids: list = field(default_factory=list)
+
+    def to_json(self) -> str:
+        return json.dumps(asdict(self), sort_keys=True)
+
+    @staticmethod
+    def from_json(s: str) -> "ModelSpec":
+        d = json.loads(s)
+        layers = [LayerSpec(AttnSpec(**l["attn"]), FfnSpec(**l["ffn"])) for l in d.pop("layers")]
+        rope = RopeSpec(**d.pop("rope"))
+        return ModelSpec(rope=rope, layers=layers, **d)
+
+    # ---- sizes -------------------------------------------------------------------------
+    def kv_bytes_per_token(self) -> int:
+        """Bytes of KV cache one token occupies across all layers."""
+        es = {"bf16": 2, "fp8": 1, "f32": 4}[self.kv_dtype]
+        n = 0
+        for l in self.layers:
+            a = l.attn
+            if a.kind == "gqa":
+                n += 2 * a.n_kv_heads * a.head_dim * es
+            elif a.kind == "mla":
+                n += (a.kv_lora + a.qk_rope) * es + (4 if self.kv_dtype == "fp8" else 0)
+                if a.index_heads:
+                    n += a.index_dim * (1 if self.kv_dtype == "fp8" else 2) + 4
+        return n
+
+    def param_count(self) -> int:
+        h = self.hidden
+        n = self.vocab * h * (1 if self.tie_embeddings else 2)
+        for l in self.layers:
+            a, f = l.attn, l.ffn
+            if a.kind == "gqa":
+                qd = a.n_heads * a.head_dim * (2 if a.gated else 1)
+                n += h * (qd + 2 * a.n_kv_heads * a.head_dim) + a.n_heads * a.head_dim * h
+            elif a.kind == "mla":
+                qh = a.qk_nope + a.qk_rope
+                n += (h * a.q_lora + a.q_lora * a.n_heads * qh) if a.q_lora else h * a.n_heads * qh
+                n += h * (a.kv_lora + a.qk_rope) + a.kv_lora * a.n_heads * (a.qk_nope + a.v_head)
+                n += a.n_heads * a.v_head * h
+            elif a.kind == "gdn":
+                kd, vd = a.gdn_k_heads * a.gdn_head_dim, a.gdn_v_heads * a.gdn_head_dim
+                n += h * (2 * kd + 2 * vd) + h * 2 * a.gdn_v_heads + vd * h
+            if f.kind == "dense":
+                n += 3 * h * f.inter
+            else:
+                n += f.n_experts * 3 * h * f.moe_inter + f.n_shared * 3 * h * f.moe_inter + h * f.n_experts
+        return n
+
+
+def _rope_from(cfg: dict, head_dim: int, rot_dim: int | None = None, pair: str = "half") -> RopeSpec:
+    sc = cfg.get("rope_scaling") or cfg.get("rope_parameters")
+    scaling = None
+    if isinstance(sc, dict) and (sc.get("rope_type") or sc.get("type")) not in (None, "default"):
+        scaling = dict(sc)
+        scaling["type"] = sc.get("rope_type") or sc.get("type")
+    theta = cfg.get("rope_theta")
+    if theta is None and isinstance(sc, dict):
+        theta = sc.get("rope_theta")
+    return RopeSpec(theta=float(theta or 10000.0), rot_dim=rot_dim if rot_dim is not None else head_dim,
+                    pair_mode=pair, scaling=scaling, max_pos=int(cfg.get("max_position_embeddings", 4096)))
+
+
+def _eos(cfg: dict) -> list:
+    e = cfg.get("eos_token_id")
+    if e is None:
+        return []
+    return list(e) if isinstance(e, (list, tuple)) else [int(e)]
+
+
+def _quant(cfg: dict) -> str:
+    q = cfg.get("quantization_config") or {}
+    if q.get("quant_method") == "fp8" and q.get("weight_block_size") == [128, 128]:
+        return "fp8_block128"
+    return cfg.get("plow_weight_quant", "none")
+
+
+def spec_from_config(cfg: dict) -> ModelSpec:
+    mt = cfg.get("model_type", "")
+    if mt in ("llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "plow_dense"):
+        return _dense_gqa(cfg, mt)
+    if mt in ("deepseek_v3", "deepseek_v2", "kimi_k2", "glm_moe_dsa", "glm5_next", "deepseek_v32", "plow_mla_moe"):
+        return _mla_moe(cfg, mt)
+    if mt in ("qwen3_next", "qwen3_5", "plow_gdn_hybrid"):
+        return _gdn_hybrid(cfg, mt)
+    raise ValueError(f"unsupported model_type '{mt}'")
+
+
+def load_spec(path) -> ModelSpec:
+    p = Path(path)
+    if p.is_dir():
+        p = p / "config.json"
+    return spec_from_config(json.loads(p.read_text()))
+
+
+def _dense_gqa(cfg: dict, mt: str) -> ModelSpec:
+    h = cfg["hidden_size"]
+    nh = cfg["num_attention_heads"]
+    nkv = cfg.get("num_key_value_heads", nh)
+    hd = cfg.get("head_dim") or h // nh
+    n_layers = cfg["num_hidden_layers"]
+    attn = AttnSpec(kind="gqa", n_heads=nh, n_kv_heads=nkv, head_dim=hd, qk_norm=(mt == "qwen3" or cfg.get("qk_norm", False)),
+                    window=int(cfg.get("sliding_window") or 0) if cfg.get("use_sliding_window", mt == "mistral") else 0)
+    ffn = FfnSpec(kind="dense", inter=cfg["intermediate_size"], act=cfg.get("hidden_act", "silu"))
+    gem = mt.startswith("gemma")
+    return ModelSpec(
+        family="dense_gqa", model_type=mt, hidden=h, vocab=cfg["vocab_size"], n_layers=n_layers,
+        rms_eps=float(cfg.get("rms_norm_eps", 1e-6)), tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+        rope=_rope_from(cfg, hd), layers=[LayerSpec(attn, ffn) for _ in range(n_layers)],
+        norm_plus_one=gem, embed_scale=(h ** 0.5 if gem else 1.0),
+        dtype=cfg.get("plow_dtype", "bf16"), weight_quant=_quant(cfg), kv_dtype=cfg.get("plow_kv_dtype", cfg.get("plow_dtype", "bf16")),
+        max_ctx=int(cfg.get("max_position_embeddings", 4096)), bos_token_id=cfg.get("bos_token_id"), eos_token_ids=_eos(cfg))
+
+
+def _mla_moe(cfg: dict, mt: str) -> ModelSpec:
+    h = cfg["hidden_size"]
+    nh = cfg["num_attention_heads"]
+    n_layers = cfg["num_hidden_layers"]
+    first_dense = int(cfg.get("first_k_dense_replace", 0))
+    idx_heads = int(cfg.get("index_n_heads", 0))
+    attn = AttnSpec(kind="mla", n_heads=nh, n_kv_heads=1, head_dim=cfg["qk_nope_head_dim"] + cfg["qk_rope_head_dim"],
+                    q_lora=int(cfg.get("q_lora_rank") or 0), kv_lora=cfg["kv_lora_rank"],
+                    qk_nope=cfg["qk_nope_head_dim"], qk_rope=cfg["qk_rope_head_dim"], v_head=cfg["v_head_dim"],
+                    index_heads=idx_heads, index_dim=int(cfg.get("index_head_dim", 0)),
+                    index_topk=int(cfg.get("index_topk", 0)))
+    dense = FfnSpec(kind="dense", inter=cfg["intermediate_size"], act=cfg.get("hidden_act", "silu"))
+    moe = FfnSpec(kind="moe", act=cfg.get("hidden_act", "silu"), n_experts=cfg.get("n_routed_experts", 0),
+                  top_k=cfg.get("num_experts_per_tok", 0), n_shared=cfg.get("n_shared_experts", 0),
+                  moe_inter=cfg.get("moe_intermediate_size", 0), n_group=cfg.get("n_group", 1),
+                  topk_group=cfg.get("topk_group", 1), score=cfg.get("scoring_func", "sigmoid"),
+                  norm_topk=bool(cfg.get("norm_topk_prob", True)), route_scale=float(cfg.get("routed_scaling_factor", 1.0)),
+                  has_bias=cfg.get("topk_method", "noaux_tc") == "noaux_tc")
+    layers = [LayerSpec(attn, dense if (i < first_dense or not moe.n_experts) else moe) for i in range(n_layers)]
+    return ModelSpec(
+        family="mla_moe", model_type=mt, hidden=h, vocab=cfg["vocab_size"], n_layers=n_layers,
+        rms_eps=float(cfg.get("rms_norm_eps", 1e-6)), tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+        rope=_rope_from(cfg, cfg["qk_rope_head_dim"], pair="interleaved"), layers=layers,
+        dtype=cfg.get("plow_dtype", "bf16"), weight_quant=_quant(cfg), kv_dtype=cfg.get("plow_kv_dtype", "fp8" if _quant(cfg) != "none" else cfg.get("plow_dtype", "bf16")),
+        max_ctx=int(cfg.get("max_position_embeddings", 4096)), bos_token_id=cfg.get("bos_token_id"), eos_token_ids=_eos(cfg))
+
+
+def _gdn_hybrid(cfg: dict, mt: str) -> ModelSpec:
+    h = cfg["hidden_size"]
+    n_layers = cfg["num_hidden_layers"]
+    interval = int(cfg.get("full_attention_interval", 4))
+    hd = cfg.get("head_dim", 256)
+    rot = int(hd * float(cfg.get("partial_rotary_factor", 0.25)))
+    full = AttnSpec(kind="gqa", n_heads=cfg["num_attention_heads"], n_kv_heads=cfg["num_key_value_heads"],
+                    head_dim=hd, qk_norm=True, gated=True)
+    lin = AttnSpec(kind="gdn", gdn_k_heads=cfg["linear_num_key_heads"], gdn_v_heads=cfg["linear_num_value_heads"],
+                   gdn_head_dim=cfg.get("linear_key_head_dim", 128), gdn_conv=cfg.get("linear_conv_kernel_dim", 4))
+    moe = FfnSpec(kind="moe", n_experts=cfg["num_experts"], top_k=cfg["num_experts_per_tok"],
+                  n_shared=1 if cfg.get("shared_expert_intermediate_size") else 0,
+                  moe_inter=cfg["moe_intermediate_size"], score="softmax", norm_topk=bool(cfg.get("norm_topk_prob", True)))
+    layers = [LayerSpec(full if (i + 1) % interval == 0 else lin, moe) for i in range(n_layers)]
+    return ModelSpec(
+        family="gdn_hybrid", model_type=mt, hidden=h, vocab=cfg["vocab_size"], n_layers=n_layers,
+        rms_eps=float(cfg.get("rms_norm_eps", 1e-6)), tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+        rope=_rope_from(cfg, hd, rot_dim=rot), layers=layers, norm_plus_one=True,
+        dtype=cfg.get("plow_dtype", "bf16"), weight_quant=_quant(cfg), kv_dtype=cfg.get("plow_kv_dtype", cfg.get("plow_dtype", "bf16")),
+        max_ctx=int(cfg.get("max_position_embeddings", 4096)), bos_token_id=cfg.get("bos_token_id"), eos_token_ids=_eos(cfg))
+
+
+# ---- the five benchmark configurations -------------------------------------------------------
+def tiny_dense_config() -> dict:
+    """CPU plumbing model: 4 layers, hidden 512, 8 q / 2 kv heads, hd 64, FFN 1408, fp32."""
+    return dict(model_type="llama", hidden_size=512, num_attention_heads=8, num_key_value_heads=2, head_dim=64,
+                num_hidden_layers=4, intermediate_size=1408, rms_norm_eps=1e-6, rope_theta=10000.0,
+                vocab_size=32000, tie_word_embeddings=True, max_position_embeddings=4096, plow_dtype="f32",
+                plow_kv_dtype="f32", eos_token_id=2, bos_token_id=1)
+
+
+def dense_8b_config() -> dict:
+    return dict(model_type="llama", hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                num_hidden_layers=32, intermediate_size=14336, rms_norm_eps=1e-5, rope_theta=500000.0,
+                vocab_size=128256, tie_word_embeddings=False, max_position_embeddings=8192, eos_token_id=128001)
+
+
+def mla_moe_671b_config(n_experts: int = 256, n_layers: int = 61, dsa: bool = False) -> dict:
+    cfg = dict(model_type="deepseek_v3", hidden_size=7168, num_attention_heads=128, num_hidden_layers=n_layers,
+               q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
+               intermediate_size=18432, first_k_dense_replace=3, n_routed_experts=n_experts, n_shared_experts=1,
+               num_experts_per_tok=8, moe_intermediate_size=2048, n_group=8, topk_group=4, scoring_func="sigmoid",
+               norm_topk_prob=True, routed_scaling_factor=2.5, topk_method="noaux_tc", rms_norm_eps=1e-6,
+               rope_theta=10000.0, vocab_size=129280, tie_word_embeddings=False, max_position_embeddings=163840,
+               quantization_config=dict(quant_method="fp8", weight_block_size=[128, 128]), eos_token_id=1)
+    if dsa:
+        cfg.update(model_type="glm_moe_dsa", index_n_heads=64, index_head_dim=128, index_topk=2048)
+    return cfg
+
+
+def gdn_hybrid_80b_config() -> dict:
+    return dict(model_type="qwen3_next", hidden_size=2048, num_hidden_layers=48, full_attention_interval=4,
+                num_attention_heads=16, num_key_value_heads=2, head_dim=256, partial_rotary_factor=0.25,
+                linear_num_key_heads=16, linear_num_value_heads=32, linear_key_head_dim=128,
+                linear_value_head_dim=128, linear_conv_kernel_dim=4, num_experts=512, num_experts_per_tok=10,
+                moe_intermediate_size=512, shared_expert_intermediate_size=512, norm_topk_prob=True,
+                rms_norm_eps=1e-6, rope_theta=10000000.0, vocab_size=151936, tie_word_embeddings=False,
+                max_position_embeddings=262144, eos_token_id=151645)

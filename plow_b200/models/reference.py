@@ -1,0 +1,315 @@
+"""Plain PyTorch reference implementations (the numeric oracle) and random-init checkpoints.
+
+Every model here consumes a ``state_dict`` keyed by the HF checkpoint tensor names and runs in
+whatever dtype the tensors are promoted to (tests use fp32).  They are written for clarity, not
+speed: full-sequence causal attention, dense expert loops.
+"""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import torch
+import torch.nn.functional as F
+
+from ..utils.rope import rope_table
+from .config import ModelSpec, spec_from_config
+
+
+# ------------------------------------------------------------------------------------------------
+def rmsnorm(x, g, eps, plus_one=False):
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    if g is not None:
+        y = y * ((1.0 + g.float()) if plus_one else g.float())
+    return y.to(x.dtype)
+
+
+def apply_rope(x, tab, pos, rot_dim, pair_mode):
+    """x [..., T, heads, hd]; tab [max_pos, rot]; pos [T]."""
+    half = rot_dim // 2
+    cs = tab[pos, :half].to(x.dtype)[:, None, :]
+    sn = tab[pos, half:rot_dim].to(x.dtype)[:, None, :]
+    xr, xp = x[..., :rot_dim], x[..., rot_dim:]
+    if pair_mode == "half":
+        a, b = xr[..., :half], xr[..., half:]
+        out = torch.cat([a * cs - b * sn, b * cs + a * sn], dim=-1)
+    else:
+        a, b = xr[..., 0::2], xr[..., 1::2]
+        out = torch.stack([a * cs - b * sn, b * cs + a * sn], dim=-1).flatten(-2)
+    return torch.cat([out, xp], dim=-1)
+
+
+def causal_attention(q, k, v, scale, window=0):
+    """q [T, nq, hd], k/v [T, nkv, hd(v)] -> [T, nq, hdv]; full causal mask (+ sliding window)."""
+    T, nq, _ = q.shape
+    nkv = k.shape[1]
+    k = k.repeat_interleave(nq // nkv, dim=1)
+    v = v.repeat_interleave(nq // nkv, dim=1)
+    s = torch.einsum("thd,shd->hts", q.float(), k.float()) * scale
+    i = torch.arange(T, device=q.device)
+    mask = i[None, :] > i[:, None]
+    if window:
+        mask = mask | (i[None, :] <= i[:, None] - window)
+    s = s.masked_fill(mask[None], float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.einsum("hts,shd->thd", p, v.float()).to(q.dtype)
+
+
+# ------------------------------------------------------------------------------------------------
+class ReferenceModel:
+    """Full-sequence forward of any supported family over a name-keyed state dict."""
+
+    def __init__(self, spec: ModelSpec, state: dict, device="cpu", dtype=torch.float32):
+        self.spec = spec
+        self.w = {k: v.to(device=device, dtype=dtype if v.is_floating_point() else v.dtype) for k, v in state.items()}
+        self.device, self.dtype = device, dtype
+        r = spec.rope
+        self.rope = torch.from_numpy(rope_table(min(r.max_pos, 1 << 17), r.rot_dim, r.theta, r.scaling)).to(device)
+
+    def lin(self, x, name):
+        return x @ self.w[name].t()
+
+    @torch.no_grad()
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        """ids [T] -> logits [T, V] (float32)."""
+        spec = self.spec
+        T = ids.shape[0]
+        pos = torch.arange(T, device=self.device)
+        x = self.w["model.embed_tokens.weight"][ids] * spec.embed_scale
+        for li, layer in enumerate(spec.layers):
+            p = f"model.layers.{li}"
+            h = rmsnorm(x, self.w[f"{p}.input_layernorm.weight"], spec.rms_eps, spec.norm_plus_one)
+            if layer.attn.kind == "gqa":
+                o = self._gqa(p, h, pos, layer.attn)
+            elif layer.attn.kind == "mla":
+                o = self._mla(p, h, pos, layer.attn)
+            else:
+                o = self._gdn(p, h, layer.attn)
+            x = x + o
+            h = rmsnorm(x, self.w[f"{p}.post_attention_layernorm.weight"], spec.rms_eps, spec.norm_plus_one)
+            x = x + (self._dense(f"{p}.mlp", h) if layer.ffn.kind == "dense" else self._moe(f"{p}.mlp", h, layer.ffn))
+        x = rmsnorm(x, self.w["model.norm.weight"], spec.rms_eps, spec.norm_plus_one)
+        head = self.w["model.embed_tokens.weight"] if spec.tie_embeddings else self.w["lm_head.weight"]
+        return (x @ head.t()).float()
+
+    # ---- blocks --------------------------------------------------------------------------------
+    def _dense(self, p, h):
+        return self.lin(F.silu(self.lin(h, f"{p}.gate_proj.weight")) * self.lin(h, f"{p}.up_proj.weight"), f"{p}.down_proj.weight")
+
+    def _gqa(self, p, h, pos, a):
+        spec = self.spec
+        T = h.shape[0]
+        q = self.lin(h, f"{p}.self_attn.q_proj.weight")
+        gate = None
+        if a.gated:
+            q = q.view(T, a.n_heads, 2 * a.head_dim)
+            q, gate = q[..., :a.head_dim], q[..., a.head_dim:].reshape(T, -1)
+        q = q.reshape(T, a.n_heads, a.head_dim)
+        k = self.lin(h, f"{p}.self_attn.k_proj.weight").view(T, a.n_kv_heads, a.head_dim)
+        v = self.lin(h, f"{p}.self_attn.v_proj.weight").view(T, a.n_kv_heads, a.head_dim)
+        if a.qk_norm:
+            q = rmsnorm(q, self.w[f"{p}.self_attn.q_norm.weight"], spec.rms_eps, spec.norm_plus_one)
+            k = rmsnorm(k, self.w[f"{p}.self_attn.k_norm.weight"], spec.rms_eps, spec.norm_plus_one)
+        q = apply_rope(q, self.rope, pos, spec.rope.rot_dim, spec.rope.pair_mode)
+        k = apply_rope(k, self.rope, pos, spec.rope.rot_dim, spec.rope.pair_mode)
+        o = causal_attention(q, k, v, a.head_dim ** -0.5, a.window).reshape(T, -1)
+        if gate is not None:
+            o = o * torch.sigmoid(gate)
+        return self.lin(o, f"{p}.self_attn.o_proj.weight")
+
+    def _mla(self, p, h, pos, a):
+        spec = self.spec
+        T = h.shape[0]
+        qh = a.qk_nope + a.qk_rope
+        if a.q_lora:
+            qa = rmsnorm(self.lin(h, f"{p}.self_attn.q_a_proj.weight"), self.w[f"{p}.self_attn.q_a_layernorm.weight"], spec.rms_eps)
+            q = self.lin(qa, f"{p}.self_attn.q_b_proj.weight")
+        else:
+            q = self.lin(h, f"{p}.self_attn.q_proj.weight")
+        q = q.view(T, a.n_heads, qh)
+        kva = self.lin(h, f"{p}.self_attn.kv_a_proj_with_mqa.weight")
+        c_kv = rmsnorm(kva[:, :a.kv_lora], self.w[f"{p}.self_attn.kv_a_layernorm.weight"], spec.rms_eps)
+        k_rope = apply_rope(kva[:, a.kv_lora:].view(T, 1, a.qk_rope), self.rope, pos, a.qk_rope, spec.rope.pair_mode)
+        q_nope, q_rope = q[..., :a.qk_nope], apply_rope(q[..., a.qk_nope:], self.rope, pos, a.qk_rope, spec.rope.pair_mode)
+        kvb = self.lin(c_kv, f"{p}.self_attn.kv_b_proj.weight").view(T, a.n_heads, a.qk_nope + a.v_head)
+        k = torch.cat([kvb[..., :a.qk_nope], k_rope.expand(T, a.n_heads, a.qk_rope)], dim=-1)
+        v = kvb[..., a.qk_nope:]
+        o = causal_attention(torch.cat([q_nope, q_rope], -1), k, v, qh ** -0.5).reshape(T, -1)
+        return self.lin(o, f"{p}.self_attn.o_proj.weight")
+
+    def route(self, logits, f, bias=None):
+        """Router semantics shared with the kernels (group-limited noaux_tc selection): returns
+        (expert ids [T,k], gates [T,k]).  Selection uses score + bias, gates use the unbiased score."""
+        scores = torch.sigmoid(logits.float()) if f.score == "sigmoid" else torch.softmax(logits.float(), -1)
+        sel = scores + (bias.float() if bias is not None else 0.0)
+        T, E = sel.shape
+        if f.n_group > 1:
+            grp = sel.view(T, f.n_group, E // f.n_group)
+            gscore = grp.topk(2, dim=-1).values.sum(-1)
+            keep = torch.zeros_like(gscore, dtype=torch.bool)
+            keep.scatter_(1, _stable_topk(gscore, f.topk_group), True)
+            sel = sel.masked_fill(~keep[:, :, None].expand_as(grp).reshape(T, E), float("-inf"))
+        idx = _stable_topk(sel, f.top_k)
+        g = scores.gather(1, idx)
+        if f.norm_topk:
+            g = g / g.sum(-1, keepdim=True).clamp_min(1e-20)
+        return idx, g * f.route_scale
+
+    def _moe(self, p, h, f):
+        bias = self.w.get(f"{p}.gate.e_score_correction_bias")
+        idx, g = self.route(h.float() @ self.w[f"{p}.gate.weight"].float().t(), f, bias)
+        out = torch.zeros_like(h, dtype=torch.float32)
+        for j in range(f.top_k):
+            for e in idx[:, j].unique().tolist():
+                m = idx[:, j] == e
+                out[m] += g[m, j, None] * self._dense(f"{p}.experts.{e}", h[m]).float()
+        if f.n_shared:
+            sp = f"{p}.shared_experts" if self.spec.family == "mla_moe" else f"{p}.shared_expert"
+            out = out + self._dense(sp, h).float()
+        return out.to(h.dtype)
+
+    def _gdn(self, p, h, a):
+        T = h.shape[0]
+        hk, hv, d = a.gdn_k_heads, a.gdn_v_heads, a.gdn_head_dim
+        qkvz = self.lin(h, f"{p}.linear_attn.in_proj_qkvz.weight")
+        ba = self.lin(h, f"{p}.linear_attn.in_proj_ba.weight")
+        qkv, z = qkvz[:, :(2 * hk + hv) * d], qkvz[:, (2 * hk + hv) * d:]
+        w = self.w[f"{p}.linear_attn.conv1d.weight"].float()          # [C, W]
+        xp = F.pad(qkv.float().t()[None], (a.gdn_conv - 1, 0))         # causal depthwise conv
+        qkv = F.silu(F.conv1d(xp, w[:, None, :], groups=w.shape[0]))[0].t()
+        q = qkv[:, :hk * d].view(T, hk, d)
+        k = qkv[:, hk * d:2 * hk * d].view(T, hk, d)
+        v = qkv[:, 2 * hk * d:].view(T, hv, d)
+        q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6)
+        k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+        b, al = ba[:, :hv].float(), ba[:, hv:].float()
+        beta = torch.sigmoid(b)
+        alpha = torch.exp(-torch.exp(self.w[f"{p}.linear_attn.A_log"].float()) * F.softplus(al + self.w[f"{p}.linear_attn.dt_bias"].float()))
+        rep = hv // hk
+        S = torch.zeros(hv, d, d, dtype=torch.float32, device=h.device)   # [v-head, V, K]
+        out = torch.zeros(T, hv, d, dtype=torch.float32, device=h.device)
+        for t in range(T):
+            kt, qt = k[t].repeat_interleave(rep, 0), q[t].repeat_interleave(rep, 0)
+            S = S * alpha[t, :, None, None]
+            pred = torch.einsum("hvk,hk->hv", S, kt)
+            S = S + beta[t, :, None, None] * torch.einsum("hv,hk->hvk", v[t] - pred, kt)
+            out[t] = torch.einsum("hvk,hk->hv", S, qt) * d ** -0.5
+        on = rmsnorm(out, self.w[f"{p}.linear_attn.norm.weight"], self.spec.rms_eps) * F.silu(z.float().view(T, hv, d))
+        return self.lin(on.reshape(T, -1).to(h.dtype), f"{p}.linear_attn.out_proj.weight")
+
+
+def _stable_topk(x, k):
+    """top-k with the lowest index winning ties (the kernels' packed-key rule)."""
+    order = torch.sort(x, dim=-1, descending=True, stable=True).indices
+    return order[..., :k]
+
+
+# ------------------------------------------------------------------------------------------------
+def param_shapes(spec: ModelSpec) -> dict:
+    """Checkpoint tensor name -> shape for a spec (HF naming)."""
+    H, V = spec.hidden, spec.vocab
+    s = {"model.embed_tokens.weight": (V, H), "model.norm.weight": (H,)}
+    if not spec.tie_embeddings:
+        s["lm_head.weight"] = (V, H)
+    for li, layer in enumerate(spec.layers):
+        p = f"model.layers.{li}"
+        a, f = layer.attn, layer.ffn
+        s[f"{p}.input_layernorm.weight"] = (H,)
+        s[f"{p}.post_attention_layernorm.weight"] = (H,)
+        if a.kind == "gqa":
+            s[f"{p}.self_attn.q_proj.weight"] = (a.n_heads * a.head_dim * (2 if a.gated else 1), H)
+            s[f"{p}.self_attn.k_proj.weight"] = (a.n_kv_heads * a.head_dim, H)
+            s[f"{p}.self_attn.v_proj.weight"] = (a.n_kv_heads * a.head_dim, H)
+            s[f"{p}.self_attn.o_proj.weight"] = (H, a.n_heads * a.head_dim)
+            if a.qk_norm:
+                s[f"{p}.self_attn.q_norm.weight"] = (a.head_dim,)
+                s[f"{p}.self_attn.k_norm.weight"] = (a.head_dim,)
+        elif a.kind == "mla":
+            qh = a.qk_nope + a.qk_rope
+            if a.q_lora:
+                s[f"{p}.self_attn.q_a_proj.weight"] = (a.q_lora, H)
+                s[f"{p}.self_attn.q_a_layernorm.weight"] = (a.q_lora,)
+                s[f"{p}.self_attn.q_b_proj.weight"] = (a.n_heads * qh, a.q_lora)
+            else:
+                s[f"{p}.self_attn.q_proj.weight"] = (a.n_heads * qh, H)
+            s[f"{p}.self_attn.kv_a_proj_with_mqa.weight"] = (a.kv_lora + a.qk_rope, H)
+            s[f"{p}.self_attn.kv_a_layernorm.weight"] = (a.kv_lora,)
+            s[f"{p}.self_attn.kv_b_proj.weight"] = (a.n_heads * (a.qk_nope + a.v_head), a.kv_lora)
+            s[f"{p}.self_attn.o_proj.weight"] = (H, a.n_heads * a.v_head)
+            if a.index_heads:
+                s[f"{p}.self_attn.indexer.wq_b.weight"] = (a.index_heads * a.index_dim, a.q_lora or H)
+                s[f"{p}.self_attn.indexer.wk.weight"] = (a.index_dim, H)
+                s[f"{p}.self_attn.indexer.weights_proj.weight"] = (a.index_heads, H)
+                s[f"{p}.self_attn.indexer.k_norm.weight"] = (a.index_dim,)
+                s[f"{p}.self_attn.indexer.k_norm.bias"] = (a.index_dim,)
+        else:
+            d = a.gdn_head_dim
+            s[f"{p}.linear_attn.in_proj_qkvz.weight"] = (2 * a.gdn_k_heads * d + 2 * a.gdn_v_heads * d, H)
+            s[f"{p}.linear_attn.in_proj_ba.weight"] = (2 * a.gdn_v_heads, H)
+            s[f"{p}.linear_attn.conv1d.weight"] = ((2 * a.gdn_k_heads + a.gdn_v_heads) * d, a.gdn_conv)
+            s[f"{p}.linear_attn.A_log"] = (a.gdn_v_heads,)
+            s[f"{p}.linear_attn.dt_bias"] = (a.gdn_v_heads,)
+            s[f"{p}.linear_attn.norm.weight"] = (d,)
+            s[f"{p}.linear_attn.out_proj.weight"] = (H, a.gdn_v_heads * d)
+        if f.kind == "dense":
+            for nm, shp in (("gate_proj", (f.inter, H)), ("up_proj", (f.inter, H)), ("down_proj", (H, f.inter))):
+                s[f"{p}.mlp.{nm}.weight"] = shp
+        else:
+            s[f"{p}.mlp.gate.weight"] = (f.n_experts, H)
+            if f.has_bias:
+                s[f"{p}.mlp.gate.e_score_correction_bias"] = (f.n_experts,)
+            for e in range(f.n_experts):
+                for nm, shp in (("gate_proj", (f.moe_inter, H)), ("up_proj", (f.moe_inter, H)), ("down_proj", (H, f.moe_inter))):
+                    s[f"{p}.mlp.experts.{e}.{nm}.weight"] = shp
+            if f.n_shared:
+                sp = f"{p}.mlp.shared_experts" if spec.family == "mla_moe" else f"{p}.mlp.shared_expert"
+                w = f.moe_inter * f.n_shared
+                for nm, shp in (("gate_proj", (w, H)), ("up_proj", (w, H)), ("down_proj", (H, w))):
+                    s[f"{sp}.{nm}.weight"] = shp
+    return s
+
+
+def random_state(spec: ModelSpec, seed: int = 0, std: float = 0.02, dtype=torch.float32) -> dict:
+    """Weights N(0, std), norm weights 1 (0 for (1+γ) models), router bias 0, A_log/dt_bias small."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in param_shapes(spec).items():
+        if name.endswith("norm.weight") or name.endswith("layernorm.weight"):
+            t = torch.zeros(shape) if (spec.norm_plus_one and "linear_attn.norm" not in name) else torch.ones(shape)
+        elif name.endswith("e_score_correction_bias") or name.endswith("k_norm.bias"):
+            t = torch.zeros(shape)
+        elif name.endswith("A_log"):
+            t = torch.log(torch.rand(shape, generator=g) * 15 + 1)
+        elif name.endswith("dt_bias"):
+            t = torch.rand(shape, generator=g)
+        else:
+            t = torch.randn(shape, generator=g) * std
+        out[name] = t.to(dtype if t.dim() > 1 and not name.endswith("conv1d.weight") else torch.float32)
+    return out
+
+
+def write_checkpoint(cfg: dict, out_dir, seed: int = 0, dtype=torch.float32, shard_bytes: int = 2 << 30) -> Path:
+    """Random-init HF-layout checkpoint: config.json + model-0000x.safetensors (+ index)."""
+    from safetensors.torch import save_file
+    out = Path(out_dir)
+    out.mkdir(parents=True, exist_ok=True)
+    spec = spec_from_config(cfg)
+    state = random_state(spec, seed, dtype=dtype)
+    (out / "config.json").write_text(json.dumps(cfg, indent=1))
+    shards, cur, size = [], {}, 0
+    for k, v in state.items():
+        nb = v.numel() * v.element_size()
+        if cur and size + nb > shard_bytes:
+            shards.append(cur)
+            cur, size = {}, 0
+        cur[k] = v.contiguous()
+        size += nb
+    shards.append(cur)
+    index = {}
+    for i, sh in enumerate(shards):
+        fn = f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+        save_file(sh, str(out / fn))
+        index.update({k: fn for k in sh})
+    (out / "model.safetensors.index.json").write_text(json.dumps(dict(metadata={}, weight_map=index)))
+    return out

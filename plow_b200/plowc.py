@@ -1,0 +1,126 @@
+"""``plowc`` — compile a checkpoint directory into a packet directory.
+
+    python -m plow_b200.plowc --hf-dir CKPT --out ASSETS --gpu b200 --arch sm_100a --num-gpus 8 --parallel ep
+
+writes ``model.pkt`` (tensor table + one program per prefill bucket / decode rung + metadata
+sections), ``weights.json`` (which checkpoint tensors the packet binds), ``build.json`` (knobs,
+fusion coverage, verifier results, decode lower bound), copies ``tokenizer.json`` and links
+``checkpoint/``.  Same outputs as the reference's ``plowc --emit devblob``
+(crates/plowc/src/main.rs:1933-2284); ``--arch`` other than sm_100a / cpu is refused.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import sys
+from pathlib import Path
+
+from .compiler import costmodel, emit, graph, hwspec, packet as pk, rewrite, verify
+from .models.config import load_spec
+
+
+def compile_dir(hf_dir, out_dir, gpu="b200", arch="sm_100a", num_gpus=1, parallel="tp", n_cu=None,
+                max_rows=8192, prefill_buckets=None, decode_rungs=None, max_seqs=64, disable_rules=(),
+                emit_trace=False) -> dict:
+    hwspec.check_arch(arch)
+    hw = hwspec.lookup("cpu" if arch == "cpu" else gpu)
+    spec = load_spec(hf_dir)
+    if parallel not in ("tp", "ep", "dp"):
+        raise ValueError(f"--parallel {parallel}: supported strategies are tp, ep (experts over ranks, attention data-parallel) and dp")
+    tp = num_gpus if parallel == "tp" else 1
+    ep = num_gpus if parallel == "ep" else 1
+    n_cu = n_cu or hw.sm_count
+    buckets = emit.default_buckets(max_rows)
+    if prefill_buckets:
+        buckets["prefill"] = sorted(prefill_buckets)
+    if decode_rungs:
+        buckets["decode"] = sorted(decode_rungs)
+    buckets["max_seqs"] = max_seqs
+    out = Path(out_dir)
+    out.mkdir(parents=True, exist_ok=True)
+    report = dict(model_type=spec.model_type, family=spec.family, arch=arch, gpu=hw.name, n_cu=n_cu, tp=tp, ep=ep,
+                  parallel=parallel, buckets=buckets, ranks=[])
+    n_ranks = num_gpus if parallel in ("tp", "ep") else 1
+    for rank in range(n_ranks):
+        g = graph.build_graph(spec, tp=tp, ep=ep, rank=rank)
+        n_prim = len(g.nodes)
+        sites = rewrite.fuse(g, disable=set(disable_rules))
+        pkt = emit.emit_packet(g, sites, hw, n_cu, buckets, rank=rank)
+        checks = verify.verify_packet(pkt)
+        if not checks["ok"]:
+            raise RuntimeError(f"verifier refused the packet: {checks['failures']}")   # nothing is written
+        name = "model.pkt" if rank == 0 else f"model.rank{rank}.pkt"
+        digest = pk.write_packet(pkt, out / name)
+        report["ranks"].append(dict(rank=rank, packet=name, sha256=digest.hex(), primitive_nodes=n_prim,
+                                    fused_nodes=len(g.nodes), fusion_coverage=rewrite.coverage(sites),
+                                    programs=[dict(role=p.role, rows=p.rows, insts=len(p.insts), stream=len(p.stream),
+                                                   waits=len(p.waits), arena_bytes=p.arena_bytes,
+                                                   est_us=round(getattr(p, "est_us", 0.0), 2)) for p in pkt.programs],
+                                    verify=checks))
+        if rank == 0:
+            weights = sorted(t.name for t in pkt.tensors if t.tclass == pk.TClass.WEIGHT)
+            derived = pkt.section_json("derived_weights.json")
+            (out / "weights.json").write_text(json.dumps(dict(weights=weights, derived=derived), indent=1))
+    report["decode_floor_us"] = {str(b): round(costmodel.decode_step_floor_us(spec, hw, b, 2048, ep=ep, tp=tp), 1)
+                                 for b in (1, 8, 64)}
+    (out / "build.json").write_text(json.dumps(report, indent=1))
+    src = Path(hf_dir).resolve()
+    link = out / "checkpoint"
+    if link.is_symlink() or link.exists():
+        link.unlink() if link.is_symlink() else shutil.rmtree(link)
+    os.symlink(src, link, target_is_directory=True)
+    for fn in ("tokenizer.json", "tokenizer_config.json", "chat_template.jinja", "generation_config.json"):
+        if (src / fn).exists():
+            shutil.copy(src / fn, out / fn)
+    return report
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="plowc", description=__doc__.split("\n\n")[0])
+    sub = ap.add_subparsers(dest="cmd")
+    ap.add_argument("--hf-dir", "--model", dest="hf_dir")
+    ap.add_argument("--out", default="assets")
+    ap.add_argument("--emit", default="devblob", choices=["devblob", "packets"])
+    ap.add_argument("--gpu", default="b200")
+    ap.add_argument("--arch", default="sm_100a")
+    ap.add_argument("--num-gpus", type=int, default=1)
+    ap.add_argument("--parallel", default="tp")
+    ap.add_argument("--n-cu", type=int)
+    ap.add_argument("--max-rows", type=int, default=8192)
+    ap.add_argument("--max-seqs", type=int, default=64)
+    ap.add_argument("--prefill-buckets", type=lambda s: [int(x) for x in s.split(",")])
+    ap.add_argument("--decode-rungs", type=lambda s: [int(x) for x in s.split(",")])
+    ap.add_argument("--disable-rule", action="append", default=[])
+    v = sub.add_parser("viz", help="write an HTML view of the fused graph")
+    v.add_argument("hf_dir")
+    v.add_argument("--out", default="graph.html")
+    k = sub.add_parser("knob-scope", help="list compile knobs and the programs they affect")
+    args = ap.parse_args(argv)
+    if args.cmd == "viz":
+        from .compiler import viz
+        spec = load_spec(args.hf_dir)
+        g = graph.build_graph(spec)
+        rewrite.fuse(g)
+        Path(args.out).write_text(viz.to_html(g))
+        return 0
+    if args.cmd == "knob-scope":
+        from . import config as knobs
+        print(json.dumps(knobs.knob_table("emit"), indent=1))
+        return 0
+    if not args.hf_dir:
+        ap.error("--hf-dir is required")
+    try:
+        rep = compile_dir(args.hf_dir, args.out, args.gpu, args.arch, args.num_gpus, args.parallel, args.n_cu,
+                          args.max_rows, args.prefill_buckets, args.decode_rungs, args.max_seqs, args.disable_rule)
+    except (ValueError, KeyError, RuntimeError) as e:
+        print(f"plowc: error: {e}", file=sys.stderr)
+        return 2
+    print(json.dumps(dict(out=args.out, ranks=len(rep["ranks"]), programs=len(rep["ranks"][0]["programs"]),
+                          fusion=rep["ranks"][0]["fusion_coverage"])))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,117 @@
+"""Engine interface shared by the CPU interpreter backend and the sm_100a backend.
+
+An engine owns weights, the KV page pool and the per-step launch; the scheduler above it only
+speaks token batches.  A :class:`TokenBatch` is the unified row format: every row carries its
+token id, its position and the slot (sequence) it belongs to, so prefill chunks of several
+requests, decode rows and mixed steps are all the same thing to the engine (the reference's
+unified token batch: crates/plow-asset/src/token_batch.rs, exec/gpu/token_batch.rs:227).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from ..compiler import packet as pk
+from .kv_pages import PAGE, PagePool
+
+
+@dataclass
+class TokenBatch:
+    ids: np.ndarray           # int32 [rows]
+    pos: np.ndarray           # int32 [rows]
+    seq: np.ndarray           # int32 [rows] slot of each row
+    sample_rows: np.ndarray   # int32 [n_sample] rows whose logits are wanted
+    decode: bool = False      # one row per sequence
+    want_logits: bool = False
+
+    @property
+    def rows(self) -> int:
+        return int(self.ids.shape[0])
+
+
+@dataclass
+class StepResult:
+    ids: np.ndarray                    # int32 [n_sample] greedy tokens
+    logits: np.ndarray | None = None   # float32 [n_sample, V] when requested
+    device_ms: float = 0.0
+
+
+class EngineHealth:
+    HEALTHY, DEGRADED, DEAD = "healthy", "degraded", "dead"
+
+
+class EngineError(RuntimeError):
+    """A step failed; `fatal` means the backend is poisoned and every live slot must fail."""
+
+    def __init__(self, msg, fatal=False):
+        super().__init__(msg)
+        self.fatal = fatal
+
+
+class EngineBase:
+    """Slot + page bookkeeping common to all backends."""
+
+    def __init__(self, packet: pk.Packet, max_slots: int, n_pages: int, max_ctx: int, prefix_cache: bool = True):
+        from ..models.config import ModelSpec
+        self.packet = packet
+        self.spec = ModelSpec.from_json(packet.sections["model.json"].decode())
+        self.max_slots = max_slots
+        self.max_ctx = max_ctx
+        self.max_pages_per_seq = (max_ctx + PAGE - 1) // PAGE
+        self.pool = PagePool(n_pages, namespace=packet.content_hash[:8], enable_prefix=prefix_cache)
+        self.page_table = np.zeros((max_slots, self.max_pages_per_seq), dtype=np.int32)
+        self.kvlen = np.zeros(max_slots, dtype=np.int32)
+        self.tokens: dict[int, list] = {}
+        self.health = EngineHealth.HEALTHY
+        self.buckets = packet.section_json("serve.json")["buckets"]
+
+    # ---- slots ---------------------------------------------------------------------------------
+    def begin_slot(self, slot: int, prompt: list) -> int:
+        """Seat a request; returns how many prompt tokens are already in the cache."""
+        cached = self.pool.begin(slot, prompt)
+        self.tokens[slot] = list(prompt[:cached])
+        self.kvlen[slot] = cached
+        self._sync_pages(slot)
+        return cached
+
+    def reserve(self, slot: int, n_tokens: int) -> None:
+        if n_tokens > self.max_ctx:
+            raise EngineError(f"slot {slot}: {n_tokens} tokens exceed max_ctx {self.max_ctx}")
+        self.pool.ensure(slot, n_tokens)
+        self._sync_pages(slot)
+
+    def _sync_pages(self, slot: int) -> None:
+        pages = self.pool.seqs[slot].pages
+        self.page_table[slot, :len(pages)] = pages
+
+    def commit(self, slot: int, new_tokens: list) -> None:
+        """Record tokens whose KV is now in the cache and publish finished pages."""
+        self.tokens[slot].extend(new_tokens)
+        self.kvlen[slot] = len(self.tokens[slot])
+        self.pool.publish(slot, self.tokens[slot])
+
+    def retire_slot(self, slot: int) -> None:
+        self.pool.release(slot)
+        self.tokens.pop(slot, None)
+        self.kvlen[slot] = 0
+
+    def kv_tokens_free(self) -> int:
+        return self.pool.available() * PAGE
+
+    # ---- programs ------------------------------------------------------------------------------
+    def pick_program(self, rows: int, decode: bool) -> int:
+        role = pk.Role.DECODE if decode else pk.Role.PREFILL
+        best = None
+        for i, p in enumerate(self.packet.programs):
+            if p.role == role and p.rows >= rows and (best is None or p.rows < self.packet.programs[best].rows):
+                best = i
+        if best is None:
+            raise EngineError(f"no {'decode' if decode else 'prefill'} program covers {rows} rows")
+        return best
+
+    def max_rows(self, decode: bool) -> int:
+        return max(self.buckets["decode" if decode else "prefill"])
+
+    def step(self, batch: TokenBatch) -> StepResult:   # pragma: no cover - interface
+        raise NotImplementedError
