@@ -237,8 +237,11 @@ def rule_mla_down_fuse(g: Graph, sites: list) -> bool:
     return False
 
 
+# gemm-xreduce goes first of the two collective rules: a row-parallel GEMM reduces its tiles
+# through peer memory from its own epilogue; only reductions that do not follow a GEMM (MoE
+# combine under TP) fold into the add+norm pass.
 RULES = [rule_qkv_fuse, rule_rope_kv_fuse, rule_gated_mlp_fuse, rule_residual_rmsnorm_fuse,
-         rule_xreduce_add_norm_fuse, rule_gemm_xreduce_fuse, rule_mla_down_fuse]
+         rule_gemm_xreduce_fuse, rule_xreduce_add_norm_fuse, rule_mla_down_fuse]
 
 
 def fuse(g: Graph, disable: set | None = None, max_iters: int = 100000) -> list:

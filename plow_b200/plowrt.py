@@ -1,0 +1,184 @@
+"""``plowrt`` — load a packet directory and serve / bench / inspect it.
+
+Subcommands: ``serve`` (OpenAI API), ``bench`` (drive the production scheduler without HTTP),
+``show`` (packet summary), ``disasm`` (instruction listing), ``simulate`` (walk the counter
+protocol on the host), ``devices``, ``knob-scope``, ``inventory`` (which opcodes a packet needs and
+which backend bodies exist).  Reference: crates/plowrt/src/main.rs:58-940.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+from pathlib import Path
+
+from . import config as cfgmod
+from .compiler import disasm as disasm_mod, packet as pk, schedule
+
+
+def load_engine(assets, cfg: cfgmod.RuntimeConfig):
+    backend = cfg.backend
+    if backend == "auto":
+        import torch
+        backend = "cuda" if torch.cuda.is_available() else "cpu"
+    if backend == "cpu":
+        from .runtime.cpu_engine import CpuEngine
+        return CpuEngine(assets, max_slots=cfg.max_slots, max_ctx=cfg.max_ctx, n_pages=cfg.n_pages or None,
+                         prefix_cache=cfg.prefix_cache)
+    from .runtime.gpu_engine import GpuEngine
+    return GpuEngine(assets, max_slots=cfg.max_slots, max_ctx=cfg.max_ctx, n_pages=cfg.n_pages or None,
+                     kv_fraction=cfg.kv_fraction, prefix_cache=cfg.prefix_cache, cuda_graphs=cfg.cuda_graphs)
+
+
+def make_entry(name, assets, cfg):
+    from .runtime.scheduler import ModelMux, SchedConfig
+    from .serve.app import ModelEntry
+    from .serve.template import ChatTemplate
+    from .text.tokenizer import load_tokenizer
+    build = Path(assets) / "build.json"
+    if build.exists():
+        for p in cfgmod.check_assets(json.loads(build.read_text()), cfg):
+            print(f"plowrt: warning: {p}", file=sys.stderr)
+    eng = load_engine(assets, cfg)
+    tok = load_tokenizer(assets)
+    mux = ModelMux(eng, tok, SchedConfig(token_budget=min(cfg.token_budget, eng.max_rows(False)), objective=cfg.objective,
+                                         tbt_target_ms=cfg.tbt_target_ms, queue_ttl_s=cfg.queue_ttl_s)).start()
+    return ModelEntry(name, mux, tok, ChatTemplate.from_assets(assets))
+
+
+def cmd_serve(args) -> int:
+    import uvicorn
+    from .obs.trace import Timeline
+    from .serve.app import AppState, create_app
+    cfg = cfgmod.RuntimeConfig.load(cli=dict(host=args.host, port=args.port, max_slots=args.max_slots, max_ctx=args.max_ctx,
+                                             backend=args.backend, objective=args.objective, trace=args.trace or None,
+                                             api_keys=args.api_key or None, dp=args.dp))
+    state = AppState(api_keys=cfg.api_keys, timeline=Timeline(cfg.trace), loader=lambda n, p: make_entry(n, p, cfg))
+    name = args.name or Path(args.assets).resolve().name
+    if cfg.dp > 1:
+        from .parallel.dp import DpRouter
+        entries = [make_entry(name, args.assets, cfg) for _ in range(cfg.dp)]
+        state.add(entries[0])
+        state.router = DpRouter([e.mux for e in entries])
+    else:
+        state.add(make_entry(name, args.assets, cfg))
+    uvicorn.run(create_app(state), host=cfg.host, port=cfg.port, log_level="warning")
+    return 0
+
+
+def cmd_bench(args) -> int:
+    import numpy as np
+    from .runtime.scheduler import GenParams
+    cfg = cfgmod.RuntimeConfig.load(cli=dict(max_slots=args.concurrency, max_ctx=args.input_len + args.output_len + 64,
+                                             backend=args.backend))
+    entry = make_entry("bench", args.assets, cfg)
+    rng = np.random.default_rng(args.seed)
+    V = entry.mux.engine.spec.vocab
+    prompts = [rng.integers(3, V, size=args.input_len).tolist() for _ in range(args.num_prompts)]
+    t0 = time.perf_counter()
+    reqs = [entry.mux.submit(p, GenParams(max_tokens=args.output_len, ignore_eos=True)) for p in prompts]
+    n_out = 0
+    for r in reqs:
+        while True:
+            ch = r.out.get()
+            if ch.kind == "token":
+                n_out += 1
+            elif ch.kind == "done":
+                break
+            else:
+                print(f"request failed: {ch.error}", file=sys.stderr)
+                break
+    dt = time.perf_counter() - t0
+    snap = entry.mux.metrics.snapshot()
+    print(json.dumps(dict(output_tok_s=n_out / dt, total_tok_s=(n_out + args.num_prompts * args.input_len) / dt,
+                          ttft_ms=snap["ttft_ms"], tpot_ms=snap["tpot_ms"], wall_s=dt, requests=args.num_prompts)))
+    entry.mux.stop()
+    return 0
+
+
+def cmd_show(args) -> int:
+    pkt = pk.read_packet(Path(args.assets) / "model.pkt" if Path(args.assets).is_dir() else args.assets)
+    print(json.dumps(dict(tensors=len(pkt.tensors), programs=[dict(role=p.role, rows=p.rows, rank=p.rank, insts=len(p.insts),
+                                                                    stream=len(p.stream), arena=p.arena_bytes) for p in pkt.programs],
+                          sections=sorted(pkt.sections), n_cu=pkt.n_cu, sha256=pkt.content_hash.hex()), indent=1))
+    return 0
+
+
+def cmd_disasm(args) -> int:
+    pkt = pk.read_packet(Path(args.assets) / "model.pkt" if Path(args.assets).is_dir() else args.assets)
+    print(disasm_mod.disasm(pkt, args.program, limit=args.limit))
+    return 0
+
+
+def cmd_simulate(args) -> int:
+    pkt = pk.read_packet(Path(args.assets) / "model.pkt" if Path(args.assets).is_dir() else args.assets)
+    ok = True
+    for i, p in enumerate(pkt.programs):
+        r = schedule.simulate(p)
+        ok &= r["completed"]
+        print(f"program {i} role={p.role} rows={p.rows}: {'ok' if r['completed'] else 'DEADLOCK'} entries={len(r['order'])}")
+    return 0 if ok else 1
+
+
+def cmd_inventory(args) -> int:
+    pkt = pk.read_packet(Path(args.assets) / "model.pkt" if Path(args.assets).is_dir() else args.assets)
+    ops = sorted({pk.Op(i.op).name for p in pkt.programs for i in p.insts})
+    print(json.dumps(dict(opcodes=ops, must_understand=(pkt.section_json("abi.json") or {}).get("must_understand", [])), indent=1))
+    return 0
+
+
+def cmd_devices(_args) -> int:
+    import torch
+    devs = []
+    if torch.cuda.is_available():
+        for i in range(torch.cuda.device_count()):
+            p = torch.cuda.get_device_properties(i)
+            devs.append(dict(index=i, name=p.name, sm=f"{p.major}{p.minor}", sms=p.multi_processor_count, mem_gb=round(p.total_memory / 2 ** 30, 1)))
+    print(json.dumps(dict(cuda=devs, cpu_threads=__import__("os").cpu_count()), indent=1))
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="plowrt")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    s = sub.add_parser("serve")
+    s.add_argument("--assets", required=True)
+    s.add_argument("--name")
+    s.add_argument("--host")
+    s.add_argument("--port", type=int)
+    s.add_argument("--max-slots", type=int)
+    s.add_argument("--max-ctx", type=int)
+    s.add_argument("--backend")
+    s.add_argument("--objective")
+    s.add_argument("--dp", type=int)
+    s.add_argument("--trace", action="store_true")
+    s.add_argument("--api-key", action="append")
+    s.set_defaults(fn=cmd_serve)
+    b = sub.add_parser("bench")
+    b.add_argument("--assets", required=True)
+    b.add_argument("--input-len", type=int, default=128)
+    b.add_argument("--output-len", type=int, default=64)
+    b.add_argument("--num-prompts", type=int, default=8)
+    b.add_argument("--concurrency", type=int, default=8)
+    b.add_argument("--backend")
+    b.add_argument("--seed", type=int, default=0)
+    b.set_defaults(fn=cmd_bench)
+    for name, fn in (("show", cmd_show), ("simulate", cmd_simulate), ("inventory", cmd_inventory)):
+        p = sub.add_parser(name)
+        p.add_argument("assets")
+        p.set_defaults(fn=fn)
+    d = sub.add_parser("disasm")
+    d.add_argument("assets")
+    d.add_argument("--program", type=int, default=0)
+    d.add_argument("--limit", type=int, default=200)
+    d.set_defaults(fn=cmd_disasm)
+    sub.add_parser("devices").set_defaults(fn=cmd_devices)
+    k = sub.add_parser("knob-scope")
+    k.set_defaults(fn=lambda a: print(json.dumps(cfgmod.knob_table("runtime"), indent=1)) or 0)
+    args = ap.parse_args(argv)
+    return args.fn(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,463 @@
+"""Continuous-batching scheduler: one dispatcher per model.
+
+Per tick the dispatcher (1) drains arrivals, (2) seats queued requests while the KV budget allows
+(backpressure only *before* a request starts; queued requests past their TTL are shed, live ones
+never are), (3) plans the tick with a token budget — decode rows first (one per live sequence),
+then mid-prefill spans packed across requests, shortest remaining prefill first with aging — and
+(4) runs it on the engine, then handles produced tokens (stop ids, stop strings, limits,
+streaming deltas).  When prefill work is pending, prefill chunks and decode steps alternate so
+time-between-tokens stays bounded (SLO mode sizes the chunk from a TBT target).
+
+Reference counterparts: crates/plowrt/src/serve/mux.rs:1-32 (dispatcher), sched/step.rs:1-140
+(token-budget plan, SRPF with aging), sched/admission.rs:1-25 (KV-budget seating, TTL shed),
+sched/rungs.rs (decode rung ladder), sched/slo.rs (TBT-budgeted prefill), serve/overload.rs.
+"""
+from __future__ import annotations
+
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from ..text import sample as sampling
+from ..text.tokenizer import IncrementalDetok
+from .engine import EngineBase, EngineError, EngineHealth, TokenBatch
+from .kv_pages import PAGE, OutOfPages
+
+
+@dataclass
+class GenParams:
+    max_tokens: int = 128
+    temperature: float = 0.0
+    top_p: float = 1.0
+    top_k: int = 0
+    min_p: float = 0.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+    seed: int | None = None
+    stop: list = field(default_factory=list)            # stop strings
+    stop_token_ids: list = field(default_factory=list)
+    ignore_eos: bool = False
+    min_tokens: int = 0
+    logprobs: int | None = None
+    session_id: str | None = None
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0.0 and self.presence_penalty == 0.0 and self.frequency_penalty == 0.0 \
+            and self.repetition_penalty == 1.0 and self.logprobs is None
+
+
+@dataclass
+class Chunk:
+    kind: str                 # token | done | error
+    text: str = ""
+    token_id: int | None = None
+    finish_reason: str | None = None
+    logprob: float | None = None
+    top_logprobs: list | None = None
+    usage: dict | None = None
+    error: str | None = None
+
+
+@dataclass
+class Request:
+    rid: str
+    prompt: list
+    params: GenParams
+    out: "queue.Queue[Chunk]" = field(default_factory=queue.Queue)
+    arrived: float = field(default_factory=time.monotonic)
+    deadline: float | None = None
+    # runtime state
+    slot: int = -1
+    done_prefill: int = 0            # prompt tokens whose KV is computed (incl. cached)
+    cached_tokens: int = 0
+    generated: list = field(default_factory=list)
+    detok: IncrementalDetok | None = None
+    text: str = ""
+    first_token_at: float | None = None
+    last_token_at: float | None = None
+    rng: np.random.Generator | None = None
+    waited_ticks: int = 0
+    preempted: int = 0
+    cancelled: bool = False
+    pf_len: int = 0                  # tokens to (re)prefill, fixed when the request is seated
+
+    def all_tokens(self) -> list:
+        return self.prompt + self.generated
+
+
+@dataclass
+class SchedConfig:
+    token_budget: int = 8192          # rows per tick
+    max_queue: int = 4096
+    queue_ttl_s: float = 120.0
+    objective: str = "auto"           # latency | throughput | auto
+    tbt_target_ms: float = 0.0        # 0 = off; otherwise prefill chunks are sized to this budget
+    aging_ticks: int = 32             # after this many waits a long prefill jumps the SRPF order
+    reserve_tokens: int = PAGE        # KV head-room required per live sequence before seating more
+
+
+class Metrics:
+    def __init__(self):
+        self.lock = threading.Lock()
+        self.c = dict(requests_total=0, requests_finished=0, requests_failed=0, requests_shed=0, preemptions=0,
+                      prompt_tokens=0, generation_tokens=0, cached_tokens=0, ticks=0, prefill_ticks=0, decode_ticks=0)
+        self.ttft: list = []
+        self.tpot: list = []
+        self.e2e: list = []
+        self.queue_time: list = []
+        self.step_ms: list = []
+
+    def inc(self, k, v=1):
+        with self.lock:
+            self.c[k] = self.c.get(k, 0) + v
+
+    def obs(self, name, v):
+        with self.lock:
+            lst = getattr(self, name)
+            lst.append(v)
+            if len(lst) > 65536:
+                del lst[:32768]
+
+    def snapshot(self) -> dict:
+        with self.lock:
+            def pct(a, q):
+                return float(np.percentile(a, q)) if a else None
+            return dict(counters=dict(self.c),
+                        ttft_ms=dict(p50=pct(self.ttft, 50), p99=pct(self.ttft, 99), n=len(self.ttft)),
+                        tpot_ms=dict(p50=pct(self.tpot, 50), p99=pct(self.tpot, 99), n=len(self.tpot)),
+                        e2e_ms=dict(p50=pct(self.e2e, 50), p99=pct(self.e2e, 99)),
+                        queue_ms=dict(p50=pct(self.queue_time, 50), p99=pct(self.queue_time, 99)),
+                        step_ms=dict(p50=pct(self.step_ms, 50), p99=pct(self.step_ms, 99)))
+
+
+class ModelMux:
+    """Dispatcher + slot table for one engine."""
+
+    def __init__(self, engine: EngineBase, tokenizer, cfg: SchedConfig | None = None, eos_ids=None):
+        self.engine = engine
+        self.tok = tokenizer
+        self.cfg = cfg or SchedConfig()
+        self.eos_ids = set(eos_ids if eos_ids is not None else engine.spec.eos_token_ids)
+        self.ingress: "queue.Queue[Request]" = queue.Queue()
+        self.waiting: list = []
+        self.live: dict[int, Request] = {}
+        self.free_slots = list(range(engine.max_slots - 1, -1, -1))
+        self.metrics = Metrics()
+        self._stop = threading.Event()
+        self._thread: threading.Thread | None = None
+        self._last_was_prefill = False
+        self._n = 0
+        self.draining = False
+
+    # ---- public --------------------------------------------------------------------------------
+    def start(self) -> "ModelMux":
+        self._thread = threading.Thread(target=self._loop, name="plow-mux", daemon=True)
+        self._thread.start()
+        return self
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=10)
+
+    def submit(self, prompt: list, params: GenParams, rid: str | None = None) -> Request:
+        self._n += 1
+        req = Request(rid=rid or f"req-{self._n}", prompt=list(prompt), params=params)
+        if self.engine.health == EngineHealth.DEAD:
+            req.out.put(Chunk("error", error="engine is dead", finish_reason="error"))
+            return req
+        if self.draining or self.ingress.qsize() + len(self.waiting) >= self.cfg.max_queue:
+            self.metrics.inc("requests_shed")
+            req.out.put(Chunk("error", error="overloaded", finish_reason="overloaded"))
+            return req
+        if len(prompt) + 1 > self.engine.max_ctx:
+            req.out.put(Chunk("error", error="context_length_exceeded", finish_reason="error"))
+            return req
+        self.metrics.inc("requests_total")
+        self.ingress.put(req)
+        return req
+
+    def generate(self, prompt: list, params: GenParams) -> tuple:
+        """Blocking helper: returns (token ids, text, finish_reason, usage)."""
+        req = self.submit(prompt, params)
+        ids, text = [], []
+        while True:
+            ch = req.out.get()
+            if ch.kind == "token":
+                ids.append(ch.token_id)
+                text.append(ch.text)
+            elif ch.kind == "done":
+                text.append(ch.text)
+                return ids, "".join(text), ch.finish_reason, ch.usage
+            else:
+                raise EngineError(ch.error or "request failed")
+
+    def drain(self, timeout_s: float = 30.0) -> bool:
+        """Stop admitting, wait for live requests; preempt (finish as `length`) after the timeout."""
+        self.draining = True
+        t0 = time.monotonic()
+        while (self.live or self.waiting or not self.ingress.empty()) and time.monotonic() - t0 < timeout_s:
+            time.sleep(0.005)
+        for r in list(self.live.values()):
+            self._finish(r, "preempted")
+        return not self.live
+
+    # ---- loop ----------------------------------------------------------------------------------
+    def _loop(self) -> None:
+        while not self._stop.is_set():
+            try:
+                if not self.tick():
+                    try:
+                        self.waiting.append(self.ingress.get(timeout=0.02))
+                    except queue.Empty:
+                        pass
+            except EngineError as e:
+                self._on_engine_error(e)
+
+    def tick(self) -> bool:
+        """One scheduling step; returns False when there was nothing to do."""
+        while True:
+            try:
+                self.waiting.append(self.ingress.get_nowait())
+            except queue.Empty:
+                break
+        self._shed_expired()
+        self._admit()
+        if not self.live:
+            return False
+        self.metrics.inc("ticks")
+        prefilling = [r for r in self.live.values() if r.done_prefill < r.pf_len and not r.cancelled]
+        decoding = [r for r in self.live.values() if r.done_prefill >= r.pf_len and not r.cancelled]
+        for r in [r for r in self.live.values() if r.cancelled]:
+            self._finish(r, "cancelled")
+        run_prefill = bool(prefilling) and (not decoding or not self._last_was_prefill or self.cfg.objective == "throughput")
+        t0 = time.perf_counter()
+        if run_prefill:
+            self._prefill_tick(prefilling)
+            self._last_was_prefill = True
+        elif decoding:
+            self._decode_tick(decoding)
+            self._last_was_prefill = False
+        else:
+            return False
+        self.metrics.obs("step_ms", (time.perf_counter() - t0) * 1e3)
+        return True
+
+    # ---- admission -----------------------------------------------------------------------------
+    def _shed_expired(self) -> None:
+        now = time.monotonic()
+        keep = []
+        for r in self.waiting:
+            if now - r.arrived > self.cfg.queue_ttl_s and r.preempted == 0:
+                self.metrics.inc("requests_shed")
+                r.out.put(Chunk("error", error="queue ttl exceeded", finish_reason="overloaded"))
+            else:
+                keep.append(r)
+        self.waiting = keep
+
+    def _admit(self) -> None:
+        """Seat queued requests while slots and KV pages allow (arrival order; a request that does
+        not fit blocks the ones behind it so large prompts cannot starve)."""
+        eng = self.engine
+        while self.waiting and self.free_slots:
+            r = self.waiting[0]
+            toks = r.all_tokens()
+            need_pages = (len(toks) + 1 + PAGE - 1) // PAGE
+            headroom = len(self.live) * ((self.cfg.reserve_tokens + PAGE - 1) // PAGE)
+            if need_pages + headroom > eng.pool.available() + eng.pool.cached_prefix_len(toks) // PAGE:
+                break
+            self.waiting.pop(0)
+            slot = self.free_slots.pop()
+            try:
+                cached = eng.begin_slot(slot, toks)
+            except OutOfPages:
+                self.free_slots.append(slot)
+                self.waiting.insert(0, r)
+                break
+            r.slot, r.done_prefill, r.cached_tokens = slot, cached, max(r.cached_tokens, cached)
+            r.pf_len = len(toks)   # a preempted request re-prefills its prompt plus what it generated
+            r.detok = r.detok or IncrementalDetok(self.tok)
+            r.rng = r.rng or np.random.default_rng(r.params.seed)
+            self.live[slot] = r
+            self.metrics.obs("queue_time", (time.monotonic() - r.arrived) * 1e3)
+            self.metrics.inc("cached_tokens", cached)
+
+    # ---- prefill -------------------------------------------------------------------------------
+    def _prefill_budget(self) -> int:
+        b = min(self.cfg.token_budget, self.engine.max_rows(False))
+        if self.cfg.tbt_target_ms > 0 and self.metrics.step_ms:
+            # crude service model: rows per ms observed on recent prefill ticks
+            b = max(PAGE, min(b, int(self.cfg.tbt_target_ms * getattr(self, "_rows_per_ms", 64.0))))
+        return b
+
+    def _prefill_tick(self, reqs: list) -> None:
+        eng = self.engine
+        budget = self._prefill_budget()
+        for r in reqs:
+            r.waited_ticks += 1
+        # shortest remaining prefill first; aged requests first of all
+        order = sorted(reqs, key=lambda r: (0 if r.waited_ticks > self.cfg.aging_ticks else 1, r.pf_len - r.done_prefill))
+        ids, pos, seq, sample_rows, spans = [], [], [], [], []
+        for r in order:
+            if budget <= 0 or len(spans) >= eng.buckets.get("max_seqs", 64):
+                break
+            toks = r.all_tokens()[:r.pf_len]
+            n = min(budget, r.pf_len - r.done_prefill)
+            if n <= 0:
+                continue
+            try:
+                eng.reserve(r.slot, r.done_prefill + n + 1)
+            except OutOfPages:
+                if not spans:
+                    self._preempt_one(exclude=r)
+                continue
+            start = r.done_prefill
+            ids += toks[start:start + n]
+            pos += list(range(start, start + n))
+            seq += [r.slot] * n
+            final = start + n == len(toks)
+            if final:
+                sample_rows.append(len(ids) - 1)
+            spans.append((r, start, n, final, toks))
+            budget -= n
+            r.waited_ticks = 0
+        if not spans:
+            return
+        want_logits = any(not s[0].params.greedy for s in spans if s[3])
+        if not sample_rows:
+            sample_rows_arr = np.array([len(ids) - 1], dtype=np.int32)   # engines always sample >= 1 row
+        else:
+            sample_rows_arr = np.array(sample_rows, dtype=np.int32)
+        batch = TokenBatch(np.array(ids, dtype=np.int32), np.array(pos, dtype=np.int32), np.array(seq, dtype=np.int32),
+                           sample_rows_arr, decode=False, want_logits=want_logits)
+        t0 = time.perf_counter()
+        res = eng.step(batch)
+        dt = (time.perf_counter() - t0) * 1e3
+        self._rows_per_ms = 0.8 * getattr(self, "_rows_per_ms", len(ids) / max(dt, 1e-3)) + 0.2 * len(ids) / max(dt, 1e-3)
+        self.metrics.inc("prefill_ticks")
+        k = 0
+        for (r, start, n, final, toks) in spans:
+            eng.commit(r.slot, toks[start:start + n])
+            r.done_prefill = start + n
+            self.metrics.inc("prompt_tokens", n)
+            if final:
+                lg = res.logits[k] if res.logits is not None else None
+                self._produce(r, int(res.ids[k]), lg)
+                k += 1
+
+    # ---- decode --------------------------------------------------------------------------------
+    def _decode_tick(self, reqs: list) -> None:
+        eng = self.engine
+        cap = eng.max_rows(True)
+        reqs = sorted(reqs, key=lambda r: r.slot)[:cap]
+        ready = []
+        for r in reqs:
+            n_ctx = len(r.prompt) + len(r.generated)
+            try:
+                eng.reserve(r.slot, n_ctx + 1)
+                ready.append(r)
+            except OutOfPages:
+                self._preempt_one(exclude=None, prefer=r)
+        reqs = [r for r in ready if r.slot in self.live and self.live[r.slot] is r]
+        if not reqs:
+            return
+        ids = np.array([r.generated[-1] for r in reqs], dtype=np.int32)
+        pos = np.array([len(r.prompt) + len(r.generated) - 1 for r in reqs], dtype=np.int32)
+        seq = np.array([r.slot for r in reqs], dtype=np.int32)
+        want_logits = any(not r.params.greedy for r in reqs)
+        batch = TokenBatch(ids, pos, seq, np.arange(len(reqs), dtype=np.int32), decode=True, want_logits=want_logits)
+        res = eng.step(batch)
+        self.metrics.inc("decode_ticks")
+        for k, r in enumerate(reqs):
+            eng.commit(r.slot, [int(ids[k])])
+            self._produce(r, int(res.ids[k]), res.logits[k] if res.logits is not None else None)
+
+    # ---- tokens --------------------------------------------------------------------------------
+    def _produce(self, r: Request, greedy_id: int, logits) -> None:
+        p = r.params
+        tok, lp, top = greedy_id, None, None
+        if not p.greedy and logits is not None:
+            lg = sampling.apply_penalties(logits, r.generated, p.presence_penalty, p.frequency_penalty, p.repetition_penalty)
+            tok = sampling.sample(lg, r.rng, p.temperature, p.top_k, p.top_p, p.min_p)
+            if p.logprobs is not None:
+                lp, top = sampling.logprobs_of(lg, tok, p.logprobs)
+        now = time.monotonic()
+        if r.first_token_at is None:
+            r.first_token_at = now
+            self.metrics.obs("ttft", (now - r.arrived) * 1e3)
+        else:
+            self.metrics.obs("tpot", (now - r.last_token_at) * 1e3)
+        r.last_token_at = now
+        r.generated.append(tok)
+        self.metrics.inc("generation_tokens")
+        n_gen = len(r.generated)
+        is_eos = (tok in self.eos_ids and not p.ignore_eos) or tok in p.stop_token_ids
+        if is_eos and n_gen > p.min_tokens:
+            r.generated.pop()          # the stop token is not part of the text
+            self._finish(r, "stop")
+            return
+        delta = r.detok.push(tok)
+        r.text += delta
+        if p.stop:
+            hit = min((r.text.find(s) for s in p.stop if s and s in r.text), default=-1)
+            if hit >= 0 and n_gen > p.min_tokens:
+                already = len(r.text) - len(delta)
+                r.out.put(Chunk("token", text=r.text[already:hit] if hit > already else "", token_id=tok, logprob=lp, top_logprobs=top))
+                r.text = r.text[:hit]
+                self._finish(r, "stop")
+                return
+        r.out.put(Chunk("token", text=delta, token_id=tok, logprob=lp, top_logprobs=top))
+        if n_gen >= p.max_tokens:
+            self._finish(r, "length")
+        elif len(r.prompt) + n_gen + 1 > self.engine.max_ctx:
+            self._finish(r, "length")
+
+    def _finish(self, r: Request, reason: str) -> None:
+        tail = r.detok.flush() if r.detok else ""
+        usage = dict(prompt_tokens=len(r.prompt), completion_tokens=len(r.generated),
+                     total_tokens=len(r.prompt) + len(r.generated),
+                     prompt_tokens_details=dict(cached_tokens=r.cached_tokens))
+        r.out.put(Chunk("done", text=tail if reason != "stop" else "", finish_reason=reason, usage=usage))
+        if r.slot >= 0 and self.live.get(r.slot) is r:
+            self.engine.retire_slot(r.slot)
+            del self.live[r.slot]
+            self.free_slots.append(r.slot)
+        self.metrics.inc("requests_finished")
+        self.metrics.obs("e2e", (time.monotonic() - r.arrived) * 1e3)
+
+    def _preempt_one(self, exclude=None, prefer=None) -> None:
+        """Free pages by sending the youngest live request back to the queue (it re-prefills its
+        prompt plus what it generated; the prefix cache usually makes that cheap)."""
+        cands = [r for r in self.live.values() if r is not exclude]
+        if not cands:
+            return
+        victim = prefer or max(cands, key=lambda r: r.arrived)
+        self.engine.retire_slot(victim.slot)
+        del self.live[victim.slot]
+        self.free_slots.append(victim.slot)
+        victim.slot, victim.done_prefill = -1, 0
+        victim.preempted += 1
+        self.metrics.inc("preemptions")
+        self.waiting.insert(0, victim)
+
+    def _on_engine_error(self, e: EngineError) -> None:
+        self.metrics.inc("requests_failed", len(self.live))
+        if e.fatal:
+            self.engine.health = EngineHealth.DEAD
+        for r in list(self.live.values()):
+            r.out.put(Chunk("error", error=str(e), finish_reason="error"))
+            try:
+                self.engine.retire_slot(r.slot)
+            except Exception:
+                pass
+            self.free_slots.append(r.slot)
+        self.live.clear()
+        if e.fatal:
+            for r in self.waiting:
+                r.out.put(Chunk("error", error="engine is dead", finish_reason="error"))
+            self.waiting.clear()

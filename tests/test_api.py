@@ -1,0 +1,109 @@
+"""OpenAI-compatible API exercised hermetically on the CPU backend (TestClient, no sockets)."""
+import json
+
+import pytest
+from fastapi.testclient import TestClient
+
+from plow_b200.runtime.cpu_engine import CpuEngine
+from plow_b200.runtime.scheduler import ModelMux
+from plow_b200.serve.app import AppState, ModelEntry, create_app
+from plow_b200.serve.template import ChatTemplate
+from plow_b200.text.tokenizer import ByteTokenizer
+
+
+@pytest.fixture(scope="module")
+def client(tiny_assets):
+    eng = CpuEngine(tiny_assets / "assets", max_slots=4, max_ctx=512)
+    tok = ByteTokenizer()
+    mux = ModelMux(eng, tok, eos_ids=[]).start()
+    state = AppState()
+    state.add(ModelEntry("tiny", mux, tok, ChatTemplate()))
+    with TestClient(create_app(state)) as c:
+        yield c
+    mux.stop()
+
+
+def test_models_health_version(client):
+    r = client.get("/v1/models").json()
+    assert r["object"] == "list" and r["data"][0]["id"] == "tiny" and "created" in r["data"][0]
+    assert client.get("/health").json()["status"] == "ok"
+    assert "system_fingerprint" in client.get("/version").json()
+
+
+def test_chat_completion_and_usage(client):
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 8, "temperature": 0}
+    r = client.post("/v1/chat/completions", json=body)
+    assert r.status_code == 200
+    j = r.json()
+    assert j["object"] == "chat.completion" and j["choices"][0]["finish_reason"] == "length"
+    assert j["usage"]["completion_tokens"] == 8 and "cached_tokens" in j["usage"]["prompt_tokens_details"]
+    assert j["choices"][0]["message"]["role"] == "assistant"
+    again = client.post("/v1/chat/completions", json=body).json()
+    assert again["choices"][0]["message"]["content"] == j["choices"][0]["message"]["content"]
+
+
+def test_chat_stream_sse(client):
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 6, "temperature": 0,
+            "stream": True, "stream_options": {"include_usage": True}}
+    with client.stream("POST", "/v1/chat/completions", json=body) as r:
+        frames = [l[6:] for l in r.iter_lines() if l.startswith("data: ")]
+    assert frames[-1] == "[DONE]"
+    objs = [json.loads(f) for f in frames[:-1]]
+    assert objs[0]["choices"][0]["delta"]["role"] == "assistant"
+    assert any(o["choices"] and o["choices"][0]["finish_reason"] == "length" for o in objs)
+    assert objs[-1]["usage"]["completion_tokens"] == 6
+
+
+def test_completions_token_prompt_and_logprobs(client):
+    r = client.post("/v1/completions", json={"model": "tiny", "prompt": [5, 6, 7, 8], "max_tokens": 4, "temperature": 0.5,
+                                             "seed": 1, "logprobs": 2}).json()
+    ch = r["choices"][0]
+    assert len(ch["token_ids"]) == 4 and len(ch["logprobs"]["content"]) == 4
+    assert len(ch["logprobs"]["content"][0]["top_logprobs"]) == 2
+
+
+def test_errors_use_openai_envelope(client):
+    r = client.post("/v1/chat/completions", json={"model": "nope", "messages": [{"role": "user", "content": "x"}]})
+    assert r.status_code == 404 and r.json()["error"]["code"] == "model_not_found"
+    r = client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "x"}], "n": 2})
+    assert r.status_code == 400 and r.json()["error"]["code"] == "unsupported_parameter"
+    r = client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "x"}],
+                                                  "response_format": {"type": "json_object"}})
+    assert r.status_code == 400
+    r = client.post("/v1/completions", json={"model": "tiny", "prompt": [1] * 600})
+    assert r.status_code == 400 and r.json()["error"]["code"] == "context_length_exceeded"
+    r = client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "x"}], "temperature": 9})
+    assert r.status_code == 400
+
+
+def test_tokenize_detokenize_metrics(client):
+    t = client.post("/tokenize", json={"model": "tiny", "prompt": "abc"}).json()
+    assert t["count"] == 3
+    assert client.post("/detokenize", json={"model": "tiny", "tokens": t["tokens"]}).json()["prompt"] == "abc"
+    m = client.get("/metrics").text
+    assert "vllm:generation_tokens_total" in m and "vllm:time_to_first_token_seconds_bucket" in m
+    assert "tiny" in client.get("/v1/metrics").json()
+    assert "tiny" in client.get("/v1/placement").json()
+
+
+def test_auth(tiny_assets):
+    eng = CpuEngine(tiny_assets / "assets", max_slots=1, max_ctx=128)
+    tok = ByteTokenizer()
+    mux = ModelMux(eng, tok, eos_ids=[]).start()
+    st = AppState(api_keys=["sekret"])
+    st.add(ModelEntry("tiny", mux, tok, ChatTemplate()))
+    with TestClient(create_app(st)) as c:
+        assert c.get("/v1/models").status_code == 401
+        assert c.get("/v1/models", headers={"Authorization": "Bearer sekret"}).status_code == 200
+        assert c.get("/health").status_code == 200
+    mux.stop()
+
+
+def test_chat_template_features():
+    t = ChatTemplate("{% for m in messages %}[{{ m.role|upper }}]{{ m.content.strip() }}{% endfor %}"
+                     "{% if messages[-1].role != 'user' %}{{ raise_exception('last must be user') }}{% endif %}"
+                     "{{ strftime_now('%Y')|length }}")
+    assert t.render([{"role": "user", "content": " hi "}]) == "[USER]hi4"
+    from plow_b200.serve.template import ChatTemplateError
+    with pytest.raises(ChatTemplateError):
+        t.render([{"role": "assistant", "content": "x"}])

@@ -1,0 +1,115 @@
+"""Graph builders, fusion rules (positive and negative), scheduler, verifier."""
+import pytest
+
+from plow_b200.compiler import emit, graph, hwspec, packet as pk, rewrite, schedule, verify
+from plow_b200.models import config
+
+
+def _fused(cfg, **kw):
+    spec = config.spec_from_config(cfg)
+    g = graph.build_graph(spec, **kw)
+    sites = rewrite.fuse(g)
+    return g, sites
+
+
+def test_dense_fusion_coverage():
+    g, sites = _fused(config.tiny_dense_config())
+    cov = rewrite.coverage(sites)
+    assert cov == {"qkv-fuse": 4, "rope-kv-fuse": 4, "gated-mlp-fuse": 4, "residual-rmsnorm-fuse": 8}
+    ops = [n.op for n in g.nodes]
+    assert "silu_mul" not in ops and "rope" not in ops and "kv_write" not in ops
+    assert ops.count("add_norm") == 8 and ops.count("linear_glu") == 4
+
+
+def test_qwen3_headnorm_is_swallowed_by_rope_kv():
+    cfg = dict(config.tiny_dense_config(), model_type="qwen3")
+    g, sites = _fused(cfg)
+    assert rewrite.coverage(sites)["rope-kv-fuse"] == 4
+    rk = next(n for n in g.nodes if n.op == "rope_kv")
+    assert rk.inputs[1] is not None and rk.inputs[2] is not None and rk.attrs["eps"] > 0
+    assert not any(n.op == "headnorm" for n in g.nodes)
+
+
+def test_negative_fusions():
+    spec = config.spec_from_config(config.tiny_dense_config())
+    g = graph.build_graph(spec)
+    # a second consumer of the gate projection must block gated-mlp-fuse on that layer
+    sm = next(n for n in g.nodes if n.op == "silu_mul")
+    extra = g.tmp("probe", g.values[sm.inputs[0]].shape)
+    g.add("add", [sm.inputs[0], sm.inputs[0]], [extra], layer=sm.layer)
+    sites = rewrite.fuse(g)
+    assert rewrite.coverage(sites)["gated-mlp-fuse"] == 3
+    # a disabled rule does not fire
+    g2 = graph.build_graph(spec)
+    sites2 = rewrite.fuse(g2, disable={"qkv-fuse"})
+    assert "qkv-fuse" not in rewrite.coverage(sites2) and "rope-kv-fuse" not in rewrite.coverage(sites2)
+
+
+def test_tp_graph_has_fused_collectives():
+    g, sites = _fused(config.dense_8b_config(), tp=8)
+    cov = rewrite.coverage(sites)
+    assert cov["gemm-xreduce-fuse"] == 64
+    q = next(n for n in g.nodes if n.op == "linear" and n.site == "qkv-fuse")
+    assert g.values[q.inputs[1]].shape == ((32 + 16) * 128 // 8, 4096)
+
+
+@pytest.mark.parametrize("cfg_fn,kw", [(lambda: config.mla_moe_671b_config(n_layers=5), dict(ep=8)),
+                                       (lambda: config.mla_moe_671b_config(n_layers=4, dsa=True), dict(ep=8)),
+                                       (config.gdn_hybrid_80b_config, dict(tp=2, ep=4))])
+def test_big_families_build_and_verify(cfg_fn, kw):
+    cfg = cfg_fn()
+    if "num_hidden_layers" in cfg and cfg["num_hidden_layers"] > 8:
+        cfg["num_hidden_layers"] = 8
+    spec = config.spec_from_config(cfg)
+    g = graph.build_graph(spec, **kw)
+    rewrite.fuse(g)
+    pkt = emit.emit_packet(g, [], hwspec.lookup("b200"), 148, dict(prefill=[128], decode=[8, 64], max_seqs=8))
+    res = verify.verify_packet(pkt)
+    assert res["ok"], res["failures"]
+    ops = {pk.Op(i.op).name for p in pkt.programs for i in p.insts}
+    assert "ROUTER_TOPK" in ops and "MOE_GEMM" in ops
+
+
+def test_schedule_protocol_and_arena(tiny_assets):
+    pkt = pk.read_packet(tiny_assets / "assets" / "model.pkt")
+    assert verify.verify_packet(pkt)["ok"]
+    for p in pkt.programs:
+        sim = schedule.simulate(p)
+        assert sim["completed"]
+        # op-major completion: an instruction's entries never complete before its producers'
+        done_at = {}
+        for step, (_c, inst) in enumerate(sim["order"]):
+            done_at[inst] = step
+        for e in p.stream:
+            for (ctr, _t) in p.waits[e.wait_ofs:e.wait_ofs + e.n_wait]:
+                assert done_at[ctr] < done_at[e.inst] or ctr == e.inst
+
+
+def test_verifier_refuses_broken_protocol(tiny_assets):
+    pkt = pk.read_packet(tiny_assets / "assets" / "model.pkt")
+    p = pkt.programs[0]
+    c, t = p.waits[0]
+    p.waits[0] = (c, t + 1)          # a wait no producer can satisfy
+    res = verify.verify_packet(pkt)
+    assert not res["ok"]
+
+
+def test_arch_refusal():
+    with pytest.raises(ValueError, match="sm_100a"):
+        hwspec.check_arch("sm_90a")
+    hw = hwspec.lookup("b200")
+    assert hw.sm_count == 148 and hw.isa.tcgen05 and not hw.isa.wgmma
+
+
+def test_rope_tables_scaling():
+    import numpy as np
+    from plow_b200.utils.rope import rope_table
+    t = rope_table(64, 64, 10000.0)
+    assert t.dtype == np.float32 and t.shape == (64, 64)
+    assert np.allclose(t[0, :32], 1.0) and np.allclose(t[0, 32:], 0.0)
+    l3 = rope_table(64, 64, 500000.0, dict(type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                          original_max_position_embeddings=8192))
+    ya = rope_table(64, 64, 10000.0, dict(type="yarn", factor=40.0, original_max_position_embeddings=4096,
+                                          beta_fast=32, beta_slow=1, mscale=1.0, mscale_all_dim=1.0))
+    assert np.isfinite(l3).all() and np.isfinite(ya).all()
+    assert not np.allclose(l3[5], rope_table(64, 64, 500000.0)[5])

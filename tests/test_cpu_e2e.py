@@ -1,0 +1,125 @@
+"""Config 1 (CPU plumbing): tiny dense GQA decoder, fp32, plowc -> packet -> plowrt engine ->
+scheduler; logits must match the PyTorch reference to 1e-4 and greedy tokens must agree."""
+import numpy as np
+import pytest
+import torch
+
+from plow_b200.runtime.cpu_engine import CpuEngine
+from plow_b200.runtime.engine import TokenBatch
+from plow_b200.runtime.scheduler import GenParams, ModelMux, SchedConfig
+from plow_b200.text.tokenizer import ByteTokenizer
+
+
+def _prompts(n=4, length=128, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, 32000, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def test_prefill_and_decode_logits_match_reference(tiny_assets, tiny_reference):
+    eng = CpuEngine(tiny_assets / "assets", max_slots=4, max_ctx=256)
+    prompts = _prompts()
+    # packed prefill of 2 prompts in one token batch, logits on each last row
+    ids, pos, seq, samp = [], [], [], []
+    for s, p in enumerate(prompts[:2]):
+        eng.begin_slot(s, p)
+        eng.reserve(s, len(p) + 2)
+        ids += p
+        pos += list(range(len(p)))
+        seq += [s] * len(p)
+        samp.append(len(ids) - 1)
+    res = eng.step(TokenBatch(np.array(ids, np.int32), np.array(pos, np.int32), np.array(seq, np.int32),
+                              np.array(samp, np.int32), want_logits=True))
+    for s, p in enumerate(prompts[:2]):
+        ref = tiny_reference.forward(torch.tensor(p))[-1]
+        assert (torch.from_numpy(res.logits[s]) - ref).abs().max().item() < 1e-4
+        assert int(res.ids[s]) == int(ref.argmax())
+        eng.commit(s, p)
+    # one decode step for both sequences
+    nxt = [int(res.ids[0]), int(res.ids[1])]
+    res2 = eng.step(TokenBatch(np.array(nxt, np.int32), np.array([128, 128], np.int32), np.array([0, 1], np.int32),
+                               np.array([0, 1], np.int32), decode=True, want_logits=True))
+    for s in range(2):
+        ref = tiny_reference.forward(torch.tensor(prompts[s] + [nxt[s]]))[-1]
+        assert (torch.from_numpy(res2.logits[s]) - ref).abs().max().item() < 1e-4
+    eng.close()
+
+
+def test_greedy_64_tokens_through_scheduler(tiny_assets, tiny_reference):
+    eng = CpuEngine(tiny_assets / "assets", max_slots=4, max_ctx=256)
+    mux = ModelMux(eng, ByteTokenizer(), SchedConfig(token_budget=256), eos_ids=[]).start()
+    prompts = _prompts()
+    reqs = [mux.submit(p, GenParams(max_tokens=64)) for p in prompts]
+    outs = []
+    for r in reqs:
+        ids = []
+        while True:
+            ch = r.out.get(timeout=120)
+            if ch.kind == "token":
+                ids.append(ch.token_id)
+            else:
+                assert ch.kind == "done" and ch.finish_reason == "length"
+                assert ch.usage["completion_tokens"] == 64 and ch.usage["prompt_tokens"] == 128
+                break
+        outs.append(ids)
+    mux.stop()
+    seq = list(prompts[0])
+    for _ in range(64):
+        seq.append(int(tiny_reference.forward(torch.tensor(seq))[-1].argmax()))
+    assert outs[0] == seq[128:]
+    eng.pool.check()
+    assert eng.pool.available() == eng.pool.n_pages
+    eng.close()
+
+
+def test_prefix_cache_hit_gives_same_tokens(tiny_assets):
+    eng = CpuEngine(tiny_assets / "assets", max_slots=2, max_ctx=512)
+    mux = ModelMux(eng, ByteTokenizer(), eos_ids=[]).start()
+    p = _prompts(1, 200, seed=3)[0]
+    a = mux.generate(p, GenParams(max_tokens=8))
+    b = mux.generate(p, GenParams(max_tokens=8))
+    assert a[0] == b[0]
+    assert a[3]["prompt_tokens_details"]["cached_tokens"] == 0
+    assert b[3]["prompt_tokens_details"]["cached_tokens"] == 192
+    mux.stop()
+    eng.close()
+
+
+def test_preemption_requeues_and_finishes(tiny_assets):
+    # 6 pages only: two 130-token prompts need 3 pages each, growth forces a preemption
+    eng = CpuEngine(tiny_assets / "assets", max_slots=2, max_ctx=512, n_pages=6, prefix_cache=False)
+    mux = ModelMux(eng, ByteTokenizer(), SchedConfig(reserve_tokens=0), eos_ids=[]).start()
+    ps = _prompts(2, 130, seed=5)
+    solo = ModelMux(CpuEngine(tiny_assets / "assets", max_slots=1, max_ctx=512), ByteTokenizer(), eos_ids=[]).start()
+    want = [solo.generate(p, GenParams(max_tokens=70))[0] for p in ps]
+    solo.stop()
+    reqs = [mux.submit(p, GenParams(max_tokens=70)) for p in ps]
+    got = []
+    for r in reqs:
+        ids = []
+        while True:
+            ch = r.out.get(timeout=120)
+            if ch.kind == "token":
+                ids.append(ch.token_id)
+            else:
+                assert ch.kind == "done"
+                break
+        got.append(ids)
+    assert mux.metrics.c["preemptions"] >= 1
+    assert got == want
+    mux.stop()
+    eng.pool.check()
+
+
+def test_stop_string_and_sampling_seed(tiny_assets):
+    eng = CpuEngine(tiny_assets / "assets", max_slots=2, max_ctx=256)
+    tok = ByteTokenizer()
+    mux = ModelMux(eng, tok, eos_ids=[]).start()
+    p = tok.encode("hello world")
+    a = mux.generate(p, GenParams(max_tokens=12, temperature=0.8, top_p=0.9, seed=7))
+    b = mux.generate(p, GenParams(max_tokens=12, temperature=0.8, top_p=0.9, seed=7))
+    c = mux.generate(p, GenParams(max_tokens=12, temperature=0.8, top_p=0.9, seed=8))
+    assert a[0] == b[0] and a[0] != c[0]
+    ids, text, reason, usage = mux.generate(p, GenParams(max_tokens=5, stop_token_ids=[a[0][2]], temperature=0.8, top_p=0.9, seed=7))
+    assert reason == "stop" and ids == a[0][:2] and usage["completion_tokens"] == 2
+    mux.stop()
+    eng.close()
