@@ -1,0 +1,566 @@
+// Row-wise sm_100a kernels: everything between the GEMMs and the attention kernels that is
+// bound by HBM bandwidth, written so each activation row is read once and every consumer format
+// (bf16 for the residual stream, e4m3 + 1x128 scales for the next block-scaled GEMM) is produced in
+// the same pass.
+//
+//   embed, rmsnorm(+quant), add_norm(+quant), quant_act, MLA query prep / query quant /
+//   latent-cache write, router top-k (sigmoid or softmax, group-limited), MoE align / gather /
+//   combine, argmax.
+//
+// Reference counterparts: runtime/nvidia/op_norm.cuh (d_rmsnorm, d_add_norm, d_headnorm_rope),
+// op_elementwise.cuh (embed, argmax packed-u64), quant_group.cuh (1x128 groups, s = max(amax,1e-10)/448),
+// op_moe.cuh (moe_router_topk_pf / align_pf / combine_pf), crates/packet/src/moe.rs:97-160 (router oracle).
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float t = l < nw ? sh[l] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+// ---- embed ------------------------------------------------------------------------------------
+__global__ void embed_kernel(__nv_bfloat16* out, const __nv_bfloat16* tab, const int* ids, int H, float scale) {
+  const int r = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(tab + static_cast<size_t>(ids[r]) * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    uint4 v = src[i];
+    if (scale != 1.0f) {
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(h[j]);
+        h[j] = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+      }
+    }
+    dst[i] = v;
+  }
+}
+
+// ---- rmsnorm / add_norm with optional e4m3 1x128 output ---------------------------------------
+// One CTA per row, 8 elements per thread per trip.  W % 8 == 0; quant output needs W % 128 == 0
+// (16 threads own one 128-wide group, reduced with shuffles inside the half-warp).
+template <bool ADD>
+__global__ void __launch_bounds__(512)
+norm_kernel(__nv_bfloat16* h_out, uint8_t* xq, float* sxq, int ld_sx, __nv_bfloat16* x_out,
+            const __nv_bfloat16* x_in, const __nv_bfloat16* delta, const __nv_bfloat16* gamma, int W,
+            int x_pitch, float eps, int plus_one) {
+  extern __shared__ float rowbuf[];      // W floats
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const __nv_bfloat16* xr = x_in + static_cast<size_t>(r) * x_pitch;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < W; i += blockDim.x * 8) {
+    uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(h[j]); f[2 * j] = t.x; f[2 * j + 1] = t.y; }
+    if (ADD) {
+      uint4 d = *reinterpret_cast<const uint4*>(delta + static_cast<size_t>(r) * W + i);
+      const __nv_bfloat162* dh = reinterpret_cast<const __nv_bfloat162*>(&d);
+      uint4 o;
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 t = __bfloat1622float2(dh[j]);
+        // the sum is rounded to bf16 before the norm reads it, as the unfused pair would do
+        oh[j] = __floats2bfloat162_rn(f[2 * j] + t.x, f[2 * j + 1] + t.y);
+        float2 b = __bfloat1622float2(oh[j]);
+        f[2 * j] = b.x; f[2 * j + 1] = b.y;
+      }
+      *reinterpret_cast<uint4*>(x_out + static_cast<size_t>(r) * W + i) = o;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { rowbuf[i + j] = f[j]; ss += f[j] * f[j]; }
+  }
+  const float tot = block_sum(ss, red);
+  const float rs = rsqrtf(tot / W + eps);
+  const int Wpad = (W + 255) & ~255;   // whole warps take every trip so the shuffles below are uniform
+  for (int i = threadIdx.x * 8; i < Wpad; i += blockDim.x * 8) {
+    const bool act = i < W;
+    float y[8];
+    float amax = 0.f;
+    if (!act) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = 0.f;
+    } else if (gamma) {
+      uint4 gv = *reinterpret_cast<const uint4*>(gamma + i);
+      const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 g = __bfloat1622float2(gh[j]);
+        if (plus_one) { g.x += 1.f; g.y += 1.f; }
+        y[2 * j] = rowbuf[i + 2 * j] * rs * g.x;
+        y[2 * j + 1] = rowbuf[i + 2 * j + 1] * rs * g.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = rowbuf[i + j] * rs;
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      oh[j] = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+      float2 b = __bfloat1622float2(oh[j]);     // quantise what the bf16 consumer would see
+      y[2 * j] = b.x; y[2 * j + 1] = b.y;
+      amax = fmaxf(amax, fmaxf(fabsf(b.x), fabsf(b.y)));
+    }
+    if (h_out && act) *reinterpret_cast<uint4*>(h_out + static_cast<size_t>(r) * W + i) = o;
+    if (xq) {
+#pragma unroll
+      for (int o2 = 8; o2 > 0; o2 >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o2));
+      const float sc = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
+      const float inv = 1.0f / sc;
+      __nv_fp8x4_e4m3 q0(make_float4(y[0] * inv, y[1] * inv, y[2] * inv, y[3] * inv));
+      __nv_fp8x4_e4m3 q1(make_float4(y[4] * inv, y[5] * inv, y[6] * inv, y[7] * inv));
+      if (act) {
+        *reinterpret_cast<uint2*>(xq + static_cast<size_t>(r) * W + i) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&q0), *reinterpret_cast<uint32_t*>(&q1));
+        if ((threadIdx.x & 15) == 0) sxq[static_cast<size_t>(i >> 7) * ld_sx + r] = sc;
+      }
+    }
+  }
+}
+
+__global__ void quant_act_kernel(uint8_t* xq, float* sxq, int ld_sx, const __nv_bfloat16* x, int K, int x_pitch) {
+  const int r = blockIdx.x;
+  const int Kpad = (K + 255) & ~255;
+  for (int i = threadIdx.x * 8; i < Kpad; i += blockDim.x * 8) {
+    const bool act = i < K;
+    uint4 v = act ? *reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * x_pitch + i) : make_uint4(0, 0, 0, 0);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    float y[8], amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(h[j]); y[2 * j] = t.x; y[2 * j + 1] = t.y; amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y))); }
+#pragma unroll
+    for (int o2 = 8; o2 > 0; o2 >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o2));
+    const float sc = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
+    const float inv = 1.0f / sc;
+    __nv_fp8x4_e4m3 q0(make_float4(y[0] * inv, y[1] * inv, y[2] * inv, y[3] * inv));
+    __nv_fp8x4_e4m3 q1(make_float4(y[4] * inv, y[5] * inv, y[6] * inv, y[7] * inv));
+    if (act) {
+      *reinterpret_cast<uint2*>(xq + static_cast<size_t>(r) * K + i) = make_uint2(*reinterpret_cast<uint32_t*>(&q0), *reinterpret_cast<uint32_t*>(&q1));
+      if ((threadIdx.x & 15) == 0) sxq[static_cast<size_t>(i >> 7) * ld_sx + r] = sc;
+    }
+  }
+}
+
+// ---- MLA --------------------------------------------------------------------------------------
+// q [T][heads*(nope+rope)] -> q_nope_t [heads][T][nope] (the grouped absorb GEMM's A operand) and
+// roped q_rope [heads][T][rope].  pair_mode 1 = interleaved (2i, 2i+1), 0 = half split.
+__global__ void mla_q_prep_kernel(__nv_bfloat16* q_nope_t, __nv_bfloat16* q_rope, const __nv_bfloat16* q, int q_pitch,
+                                  const float* rope_tab, const int* pos, int T, int heads, int nope, int rope, int pair_mode) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  const __nv_bfloat16* src = q + static_cast<size_t>(t) * q_pitch + static_cast<size_t>(h) * (nope + rope);
+  __nv_bfloat16* dn = q_nope_t + (static_cast<size_t>(h) * T + t) * nope;
+  for (int i = threadIdx.x; i < nope; i += blockDim.x) dn[i] = src[i];
+  const float* tab = rope_tab + static_cast<size_t>(pos[t]) * rope;
+  const int half = rope / 2;
+  __nv_bfloat16* dr = q_rope + (static_cast<size_t>(h) * T + t) * rope;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const int ia = pair_mode ? 2 * i : i, ib = pair_mode ? 2 * i + 1 : i + half;
+    const float a = __bfloat162float(src[nope + ia]), b = __bfloat162float(src[nope + ib]);
+    const float c = tab[i], s = tab[half + i];
+    dr[ia] = __float2bfloat16(a * c - b * s);
+    dr[ib] = __float2bfloat16(b * c + a * s);
+  }
+}
+
+// q_abs [heads][T][latent] bf16 + q_rope [heads][T][rope] -> q8 [heads][T][latent+rope] e4m3, sq [heads][T]
+__global__ void mla_q_quant_kernel(uint8_t* q8, float* sq, const __nv_bfloat16* q_abs, const __nv_bfloat16* q_rope,
+                                   int T, int latent, int rope) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  const size_t row = static_cast<size_t>(h) * T + t;
+  const int W = latent + rope;
+  __shared__ float red[32];
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = __bfloat162float(i < latent ? q_abs[row * latent + i] : q_rope[row * rope + i - latent]);
+    amax = fmaxf(amax, fabsf(v));
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = 0.f;
+  for (int w = 0; w < (blockDim.x + 31) / 32; ++w) amax = fmaxf(amax, red[w]);
+  const float sc = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
+  const float inv = 1.0f / sc;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = __bfloat162float(i < latent ? q_abs[row * latent + i] : q_rope[row * rope + i - latent]);
+    q8[row * W + i] = __nv_fp8_e4m3(v * inv).__x;
+  }
+  if (threadIdx.x == 0) sq[row] = sc;
+}
+
+// kva [T][pitch] (latent | rope at col_ofs) -> RMSNorm(latent)*gamma, RoPE(rope) -> one e4m3 row of
+// latent+rope bytes with one f32 scale, written to the token's cell of the paged cache.
+__global__ void mla_kv_write_kernel(uint8_t* kv8, float* kv_scale, const __nv_bfloat16* kva, int pitch, int col_ofs,
+                                    const __nv_bfloat16* gamma, const float* rope_tab, const int* pos, const int* slot_of,
+                                    const int* page_table, int max_pages, int latent, int rope, float eps, int pair_mode) {
+  extern __shared__ float rowf[];   // latent + rope
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const __nv_bfloat16* src = kva + static_cast<size_t>(t) * pitch + col_ofs;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < latent; i += blockDim.x) { const float v = __bfloat162float(src[i]); rowf[i] = v; ss += v * v; }
+  const float tot = block_sum(ss, red);
+  const float rs = rsqrtf(tot / latent + eps);
+  const int p = pos[t];
+  const float* tab = rope_tab + static_cast<size_t>(p) * rope;
+  const int half = rope / 2;
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < latent; i += blockDim.x) {
+    const float v = __bfloat162float(__float2bfloat16(rowf[i] * rs * __bfloat162float(gamma[i])));
+    rowf[i] = v;
+    amax = fmaxf(amax, fabsf(v));
+  }
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const int ia = pair_mode ? 2 * i : i, ib = pair_mode ? 2 * i + 1 : i + half;
+    const float a = __bfloat162float(src[latent + ia]), b = __bfloat162float(src[latent + ib]);
+    const float c = tab[i], s = tab[half + i];
+    const float ra = __bfloat162float(__float2bfloat16(a * c - b * s)), rb = __bfloat162float(__float2bfloat16(b * c + a * s));
+    rowf[latent + ia] = ra; rowf[latent + ib] = rb;
+    amax = fmaxf(amax, fmaxf(fabsf(ra), fabsf(rb)));
+  }
+  amax = warp_max(amax);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = 0.f;
+  for (int w = 0; w < (blockDim.x + 31) / 32; ++w) amax = fmaxf(amax, red[w]);
+  const float sc = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
+  const float inv = 1.0f / sc;
+  const int page = page_table[static_cast<size_t>(slot_of[t]) * max_pages + p / 64];
+  const size_t cell = static_cast<size_t>(page) * 64 + (p & 63);
+  const int W = latent + rope;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) kv8[cell * W + i] = __nv_fp8_e4m3(rowf[i] * inv).__x;
+  if (threadIdx.x == 0) kv_scale[cell] = sc;
+}
+
+// ---- router -----------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t ordered_bits(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// One warp per token.  table[t][j] = {expert id, gate bits}.  Selection key = score + bias, gate =
+// unbiased score; groups are contiguous; group score = sum of the group's top-2 biased scores;
+// ties go to the lowest group / expert id; gates renormalised over the k winners then scaled.
+__global__ void router_topk_kernel(int2* table, const float* logits, const float* bias, int T, int E, int k,
+                                   int n_group, int topk_group, int sigmoid, int norm_topk, float route_scale) {
+  extern __shared__ float sm[];    // per warp: score[E], sel[E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= T) return;
+  float* score = sm + warp * 2 * E;
+  float* sel = score + E;
+  const float* lg = logits + static_cast<size_t>(t) * E;
+  if (sigmoid) {
+    for (int e = lane; e < E; e += 32) score[e] = 1.0f / (1.0f + __expf(-lg[e]));
+  } else {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+    mx = warp_max(mx);
+    float s = 0.f;
+    for (int e = lane; e < E; e += 32) { const float v = __expf(lg[e] - mx); score[e] = v; s += v; }
+    s = warp_sum(s);
+    for (int e = lane; e < E; e += 32) score[e] /= s;
+  }
+  for (int e = lane; e < E; e += 32) sel[e] = score[e] + (bias ? bias[e] : 0.f);
+  __syncwarp();
+  if (n_group > 1) {
+    const int gs = E / n_group;
+    float gsc = -INFINITY;
+    if (lane < n_group) {
+      float a = -INFINITY, b = -INFINITY;
+      for (int i = 0; i < gs; ++i) {
+        const float v = sel[lane * gs + i];
+        if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+      }
+      gsc = a + b;
+    }
+    int rank = 0;
+    for (int g = 0; g < n_group; ++g) {
+      const float o = __shfl_sync(0xffffffffu, gsc, g);
+      if (lane < n_group && (o > gsc || (o == gsc && g < lane))) ++rank;
+    }
+    const bool keep = lane < n_group && rank < topk_group;
+    const uint32_t mask = __ballot_sync(0xffffffffu, keep);
+    for (int e = lane; e < E; e += 32)
+      if (!((mask >> (e / gs)) & 1u)) sel[e] = -INFINITY;
+    __syncwarp();
+  }
+  float gsum = 0.f;
+  float my_gate = 0.f;
+  int my_eid = -1;
+  for (int j = 0; j < k; ++j) {
+    unsigned long long best = 0ull;
+    for (int e = lane; e < E; e += 32) {
+      const unsigned long long key = (static_cast<unsigned long long>(ordered_bits(sel[e])) << 32) | static_cast<uint32_t>(E - 1 - e);
+      best = key > best ? key : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+      best = other > best ? other : best;
+    }
+    const int e = E - 1 - static_cast<int>(best & 0xffffffffu);
+    const float g = score[e];
+    gsum += g;
+    if (lane == j) { my_gate = g; my_eid = e; }
+    __syncwarp();
+    if (lane == 0) sel[e] = -INFINITY;
+    __syncwarp();
+  }
+  if (lane < k) {
+    float g = my_gate;
+    if (norm_topk) g = g / fmaxf(gsum, 1e-20f);
+    g *= route_scale;
+    table[static_cast<size_t>(t) * k + lane] = make_int2(my_eid, __float_as_int(g));
+  }
+}
+
+// ---- MoE align / gather / combine -------------------------------------------------------------
+// One CTA.  Counts the (token, slot) pairs routed to this rank's experts [e_base, e_base+e_local),
+// writes grp_off[e_local+1], tile_prefix[e_local+1] (128-row tiles) and the pair<->row maps.
+__global__ void moe_align_kernel(const int2* table, int n_pairs, int e_base, int e_local, int* grp_off, int* tile_prefix,
+                                 int* row_of_pair, int* pair_of_row) {
+  extern __shared__ int cnt[];     // e_local counts, then e_local cursors
+  int* cur = cnt + e_local;
+  for (int e = threadIdx.x; e < e_local; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = table[p].x - e_base;
+    if (e >= 0 && e < e_local) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0, tiles = 0;
+    for (int e = 0; e < e_local; ++e) {
+      grp_off[e] = off; tile_prefix[e] = tiles; cur[e] = off;
+      off += cnt[e]; tiles += (cnt[e] + 127) >> 7;
+    }
+    grp_off[e_local] = off; tile_prefix[e_local] = tiles;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = table[p].x - e_base;
+    int row = -1;
+    if (e >= 0 && e < e_local) { row = atomicAdd(&cur[e], 1); pair_of_row[row] = p; }
+    row_of_pair[p] = row;
+  }
+}
+
+// Rows of the quantised activations gathered into expert order (scales are transposed [kb][row]).
+__global__ void moe_gather_kernel(uint8_t* xs, float* sxs, int ld_sxs, const uint8_t* xq, const float* sx, int ld_sx,
+                                  const int* pair_of_row, const int* n_rows, int top_k, int K) {
+  const int row = blockIdx.x;
+  if (row >= *n_rows) return;
+  const int tok = pair_of_row[row] / top_k;
+  const uint4* src = reinterpret_cast<const uint4*>(xq + static_cast<size_t>(tok) * K);
+  uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(row) * K);
+  for (int i = threadIdx.x; i < K / 16; i += blockDim.x) dst[i] = src[i];
+  for (int kb = threadIdx.x; kb < K / 128; kb += blockDim.x) sxs[static_cast<size_t>(kb) * ld_sxs + row] = sx[static_cast<size_t>(kb) * ld_sx + tok];
+}
+
+// out[t] = shared[t] (optional) + sum_j gate[t][j] * y[row_of_pair[t*k+j]]   (fixed slot order, f32)
+__global__ void moe_combine_kernel(__nv_bfloat16* out, const __nv_bfloat16* y, const __nv_bfloat16* shared,
+                                   const int2* table, const int* row_of_pair, int top_k, int H) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float acc[8];
+    if (shared) {
+      uint4 v = *reinterpret_cast<const uint4*>(shared + static_cast<size_t>(t) * H + i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h[j]); acc[2 * j] = f.x; acc[2 * j + 1] = f.y; }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    }
+    for (int s = 0; s < top_k; ++s) {
+      const int row = row_of_pair[t * top_k + s];
+      if (row < 0) continue;
+      const float g = __int_as_float(table[t * top_k + s].y);
+      uint4 v = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(row) * H + i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h[j]); acc[2 * j] += g * f.x; acc[2 * j + 1] += g * f.y; }
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + i) = o;
+  }
+}
+
+// ---- argmax / gather --------------------------------------------------------------------------
+__global__ void argmax_kernel(int* out, const float* logits, int V) {
+  __shared__ unsigned long long red[32];
+  const float* row = logits + static_cast<size_t>(blockIdx.x) * V;
+  unsigned long long best = 0ull;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const unsigned long long key = (static_cast<unsigned long long>(ordered_bits(row[i])) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(i));
+    best = key > best ? key : best;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o); best = other > best ? other : best; }
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = threadIdx.x < (blockDim.x + 31) / 32 ? red[threadIdx.x] : 0ull;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o); best = other > best ? other : best; }
+    if (threadIdx.x == 0) out[blockIdx.x] = static_cast<int>(~static_cast<uint32_t>(best & 0xffffffffu));
+  }
+}
+
+__global__ void row_gather_kernel(__nv_bfloat16* out, const __nv_bfloat16* x, const int* rows, int W) {
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(rows[blockIdx.x]) * W);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(blockIdx.x) * W);
+  for (int i = threadIdx.x; i < W / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// [heads][T][W] -> [T][heads*W] (attention output back to token-major for o_proj)
+__global__ void head_to_token_kernel(__nv_bfloat16* out, const __nv_bfloat16* x, int T, int heads, int W) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (static_cast<size_t>(h) * T + t) * W);
+  uint4* dst = reinterpret_cast<uint4*>(out + (static_cast<size_t>(t) * heads + h) * W);
+  for (int i = threadIdx.x; i < W / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+inline int ok() { cudaError_t e = cudaGetLastError(); return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e); }
+
+}  // namespace
+
+#define S(x) reinterpret_cast<cudaStream_t>(x)
+typedef __nv_bfloat16 bf16;
+
+extern "C" {
+
+int plow_embed(void* out, const void* tab, const int* ids, int R, int H, float scale, void* st) {
+  if (H % 8) return -1;
+  embed_kernel<<<R, 256, 0, S(st)>>>((bf16*)out, (const bf16*)tab, ids, H, scale);
+  return ok();
+}
+
+int plow_rmsnorm(void* h_out, void* xq, float* sxq, int ld_sx, const void* x, const void* gamma, int R, int W,
+                 int x_pitch, float eps, int plus_one, void* st) {
+  if (W % 8 || (xq && W % 128) || W * 4 > 200 * 1024) return -1;
+  static bool attr = false;
+  if (!attr) { cudaFuncSetAttribute(norm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr = true; }
+  const int threads = W >= 4096 ? 512 : (W >= 1024 ? 128 : 64);
+  norm_kernel<false><<<R, threads, W * 4, S(st)>>>((bf16*)h_out, (uint8_t*)xq, sxq, ld_sx, nullptr, (const bf16*)x, nullptr,
+                                                   (const bf16*)gamma, W, x_pitch ? x_pitch : W, eps, plus_one);
+  return ok();
+}
+
+int plow_add_norm(void* h_out, void* xq, float* sxq, int ld_sx, void* x_out, const void* x_in, const void* delta,
+                  const void* gamma, int R, int W, float eps, int plus_one, void* st) {
+  if (W % 8 || (xq && W % 128) || W * 4 > 200 * 1024) return -1;
+  static bool attr = false;
+  if (!attr) { cudaFuncSetAttribute(norm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr = true; }
+  const int threads = W >= 4096 ? 512 : (W >= 1024 ? 128 : 64);
+  norm_kernel<true><<<R, threads, W * 4, S(st)>>>((bf16*)h_out, (uint8_t*)xq, sxq, ld_sx, (bf16*)x_out, (const bf16*)x_in,
+                                                  (const bf16*)delta, (const bf16*)gamma, W, W, eps, plus_one);
+  return ok();
+}
+
+int plow_quant_act(void* xq, float* sxq, int ld_sx, const void* x, int R, int K, int x_pitch, void* st) {
+  if (K % 128) return -1;
+  quant_act_kernel<<<R, K >= 4096 ? 512 : 128, 0, S(st)>>>((uint8_t*)xq, sxq, ld_sx, (const bf16*)x, K, x_pitch ? x_pitch : K);
+  return ok();
+}
+
+int plow_mla_q_prep(void* q_nope_t, void* q_rope, const void* q, int q_pitch, const float* rope_tab, const int* pos, int T,
+                    int heads, int nope, int rope, int pair_mode, void* st) {
+  mla_q_prep_kernel<<<dim3(T, heads), 64, 0, S(st)>>>((bf16*)q_nope_t, (bf16*)q_rope, (const bf16*)q, q_pitch, rope_tab, pos, T,
+                                                      heads, nope, rope, pair_mode);
+  return ok();
+}
+
+int plow_mla_q_quant(void* q8, float* sq, const void* q_abs, const void* q_rope, int T, int heads, int latent, int rope, void* st) {
+  mla_q_quant_kernel<<<dim3(T, heads), 128, 0, S(st)>>>((uint8_t*)q8, sq, (const bf16*)q_abs, (const bf16*)q_rope, T, latent, rope);
+  return ok();
+}
+
+int plow_mla_kv_write(void* kv8, float* kv_scale, const void* kva, int pitch, int col_ofs, const void* gamma,
+                      const float* rope_tab, const int* pos, const int* slot_of, const int* page_table, int max_pages, int T,
+                      int latent, int rope, float eps, int pair_mode, void* st) {
+  mla_kv_write_kernel<<<T, 128, (latent + rope) * 4, S(st)>>>((uint8_t*)kv8, kv_scale, (const bf16*)kva, pitch, col_ofs,
+                                                              (const bf16*)gamma, rope_tab, pos, slot_of, page_table, max_pages,
+                                                              latent, rope, eps, pair_mode);
+  return ok();
+}
+
+int plow_router_topk(void* table, const float* logits, const float* bias, int T, int E, int k, int n_group, int topk_group,
+                     int sigmoid, int norm_topk, float route_scale, void* st) {
+  if (k > 32 || n_group > 32 || E % (n_group > 0 ? n_group : 1)) return -1;
+  const int wpb = 4;
+  router_topk_kernel<<<(T + wpb - 1) / wpb, wpb * 32, wpb * 2 * E * 4, S(st)>>>((int2*)table, logits, bias, T, E, k, n_group,
+                                                                                topk_group, sigmoid, norm_topk, route_scale);
+  return ok();
+}
+
+int plow_moe_align(const void* table, int n_pairs, int e_base, int e_local, int* grp_off, int* tile_prefix, int* row_of_pair,
+                   int* pair_of_row, void* st) {
+  moe_align_kernel<<<1, 1024, 2 * e_local * 4, S(st)>>>((const int2*)table, n_pairs, e_base, e_local, grp_off, tile_prefix,
+                                                        row_of_pair, pair_of_row);
+  return ok();
+}
+
+int plow_moe_gather(void* xs, float* sxs, int ld_sxs, const void* xq, const float* sx, int ld_sx, const int* pair_of_row,
+                    const int* n_rows, int max_rows, int top_k, int K, void* st) {
+  if (K % 128) return -1;
+  moe_gather_kernel<<<max_rows, 128, 0, S(st)>>>((uint8_t*)xs, sxs, ld_sxs, (const uint8_t*)xq, sx, ld_sx, pair_of_row, n_rows, top_k, K);
+  return ok();
+}
+
+int plow_moe_combine(void* out, const void* y, const void* shared, const void* table, const int* row_of_pair, int T, int top_k,
+                     int H, void* st) {
+  if (H % 8) return -1;
+  moe_combine_kernel<<<T, 256, 0, S(st)>>>((bf16*)out, (const bf16*)y, (const bf16*)shared, (const int2*)table, row_of_pair, top_k, H);
+  return ok();
+}
+
+int plow_argmax(int* out, const float* logits, int R, int V, void* st) {
+  argmax_kernel<<<R, 1024, 0, S(st)>>>(out, logits, V);
+  return ok();
+}
+
+int plow_row_gather(void* out, const void* x, const int* rows, int n, int W, void* st) {
+  if (W % 8) return -1;
+  row_gather_kernel<<<n, 128, 0, S(st)>>>((bf16*)out, (const bf16*)x, rows, W);
+  return ok();
+}
+
+int plow_head_to_token(void* out, const void* x, int T, int heads, int W, void* st) {
+  if (W % 8) return -1;
+  head_to_token_kernel<<<dim3(T, heads), 32, 0, S(st)>>>((bf16*)out, (const bf16*)x, T, heads, W);
+  return ok();
+}
+
+}  // extern "C"

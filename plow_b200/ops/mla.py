@@ -1,0 +1,64 @@
+"""Multi-head latent attention ops: query prep, latent-cache write, absorbed decode.
+
+Decode path (reference op sequence: crates/devgen/src/mla.rs:6211-6323):
+  q [T, heads*192] -> q_prep -> (q_nope_t [h][T][128], q_rope [h][T][64])
+  q_abs = grouped GEMM(q_nope_t, W_uk^T per head)        [h][T][512]
+  q8, sq = q_quant(q_abs, q_rope)                        e4m3 [h][T][576]
+  kv_write: RMSNorm(latent) + RoPE(k_rope) -> one e4m3 row + f32 scale per token in the paged cache
+  oacc = mla_decode(q8, sq, cache)                       [h][T][512]
+  o = grouped GEMM(oacc, W_uv per head) -> [T, heads*128]
+"""
+from __future__ import annotations
+
+import torch
+
+from . import native
+
+BF16, FP8 = torch.bfloat16, torch.float8_e4m3fn
+
+
+def q_prep(q, rope_tab, pos, heads, nope, rope, pair_mode=1):
+    T = q.shape[0]
+    q_nope_t = torch.empty(heads, T, nope, dtype=BF16, device=q.device)
+    q_rope = torch.empty(heads, T, rope, dtype=BF16, device=q.device)
+    native.call("plow_mla_q_prep", q_nope_t, q_rope, q, q.stride(0), rope_tab, pos, T, heads, nope, rope, pair_mode)
+    return q_nope_t, q_rope
+
+
+def q_quant(q_abs, q_rope):
+    heads, T, latent = q_abs.shape
+    rope = q_rope.shape[2]
+    q8 = torch.empty(heads, T, latent + rope, dtype=FP8, device=q_abs.device)
+    sq = torch.empty(heads, T, dtype=torch.float32, device=q_abs.device)
+    native.call("plow_mla_q_quant", q8, sq, q_abs, q_rope, T, heads, latent, rope)
+    return q8, sq
+
+
+def kv_write(kv8, kv_scale, kva, col_ofs, gamma, rope_tab, pos, slot_of, page_table, latent, rope, eps, pair_mode=1):
+    T = kva.shape[0]
+    native.call("plow_mla_kv_write", kv8, kv_scale, kva, kva.stride(0), col_ofs, gamma, rope_tab, pos, slot_of, page_table,
+                page_table.shape[1], T, latent, rope, float(eps), pair_mode)
+
+
+class DecodeWorkspace:
+    """Scratch of the split-KV decode kernel, sized once for (max rows, max context)."""
+
+    def __init__(self, max_T, max_ctx, tiles_per_split=32, heads=128, latent=512, device="cuda"):
+        self.tiles_per_split = tiles_per_split
+        self.max_splits = max(1, -(-((max_ctx + 63) // 64) // tiles_per_split))
+        self.items = torch.empty(2 * max_T * self.max_splits * 8, dtype=torch.int32, device=device)
+        self.n_items = torch.zeros(1, dtype=torch.int32, device=device)
+        self.opart = torch.empty(max_T, self.max_splits, heads, latent, dtype=BF16, device=device)
+        self.lse = torch.empty(max_T, self.max_splits, heads, dtype=torch.float32, device=device)
+
+
+def decode(q8, sq, kv8, kv_scale, page_table, slot_of, kvlen, ws: DecodeWorkspace, softmax_scale, out=None):
+    """q8 [128][T][576] e4m3, sq [128][T]; kv8 [pages][64][576]; returns oacc bf16 [128][T][512]."""
+    heads, T, _ = q8.shape
+    assert heads == 128 and kv8.shape[1:] == (64, 576)
+    if out is None:
+        out = torch.empty(heads, T, 512, dtype=BF16, device=q8.device)
+    native.call("plow_mla_decode", q8, sq, kv8, kv_scale, kv8.shape[0], page_table, page_table.shape[1], slot_of, kvlen, T,
+                ws.tiles_per_split, ws.max_splits, ws.items, ws.n_items, ws.opart, ws.lse, out, float(softmax_scale),
+                native.status_word(q8.device))
+    return out

@@ -90,3 +90,44 @@ def check_status(device=None) -> None:
     if code != 0:
         s.zero_()
         raise NativeLibraryError(f"device kernel reported status {code}: {STATUS_NAMES.get(code, '?')}")
+
+
+# ---- compact ctypes signatures: p = pointer, i = int32, l = int64, f = float ----------------------
+_SIGS = {
+    "plow_embed": "pppiifp",
+    "plow_rmsnorm": "pppipp" "iiifip",
+    "plow_add_norm": "pppippppiifip",
+    "plow_quant_act": "ppipiiip",
+    "plow_mla_q_prep": "pppippiiiiip",
+    "plow_mla_q_quant": "ppppiiiip",
+    "plow_mla_kv_write": "pppiipppppiiiifip",
+    "plow_router_topk": "pppiiiiiiifp",
+    "plow_moe_align": "piiippppp",
+    "plow_moe_gather": "ppippipp" "iiip",
+    "plow_moe_combine": "pppppiiip",
+    "plow_argmax": "ppiip",
+    "plow_row_gather": "pppiip",
+    "plow_head_to_token": "ppiiip",
+    "plow_mla_decode": "pppplpipp" "iiipppppfpp",
+}
+_CT = {"p": C.c_void_p, "i": C.c_int32, "l": C.c_int64, "f": C.c_float}
+
+
+def _arg(v):
+    if v is None:
+        return None
+    if hasattr(v, "data_ptr"):
+        return v.data_ptr()
+    return v
+
+
+def call(name: str, *args) -> None:
+    """Invoke a kernel launcher of libplow_cuda.so on the current stream (appended as last arg)."""
+    lib = cuda_lib()
+    fn = getattr(lib, name)
+    if fn.argtypes is None:
+        fn.argtypes = [_CT[c] for c in _SIGS[name]]
+        fn.restype = C.c_int
+    rc = fn(*[_arg(a) for a in args], stream_ptr())
+    if rc != 0:
+        raise NativeLibraryError(f"{name} failed with code {rc}")
