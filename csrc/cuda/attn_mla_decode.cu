@@ -12,9 +12,12 @@
 // (request, split) and each accumulates 256 latent columns; both compute S.
 //
 // The same shared-memory KV tile feeds both products: as the K-major B operand of QK^T and as
-// the MN-major B operand of P.V (tokens are the reduction dimension there).  P is written by
-// the softmax threads to shared memory as e4m3 with the 64-byte swizzle the UMMA descriptor
-// expects.  The per-token scale sk[t] is folded into P; to keep P in e4m3 range it is divided
+// the MN-major B operand of P.V (tokens are the reduction dimension there).  The A operands
+// live in TMEM: the latent part of Q (128 columns, stored once per item by the softmax threads)
+// and P, which the softmax threads write as e4m3 over the first 16 columns of the S buffer it
+// was computed from.  Only Q's 64 rope bytes per head stay in shared memory, which leaves room
+// for five KV stages: a stage is pinned from its TMA issue until the P.V that reads it retires,
+// i.e. for the whole QK^T -> softmax -> P.V latency chain, so depth is what hides that chain.  The per-token scale sk[t] is folded into P; to keep P in e4m3 range it is divided
 // by a running maximum SK of the scales seen so far, which is handled exactly like the running
 // row maximum of online softmax (the accumulator is rescaled in TMEM when either changes).
 //
@@ -33,19 +36,20 @@ constexpr int kMlaLatent = 512;
 constexpr int kMlaRope = 64;
 constexpr int kMlaRow = 576;
 constexpr int kMlaPage = 64;
-constexpr int kMlaStages = 3;
-constexpr int kQBytes = 4 * 128 * 128 + 128 * 64;            // 73728
+constexpr int kMlaStages = 5;
+constexpr int kQBytes = 128 * 64;                            // rope part of Q only (64-byte swizzle)
 constexpr int kKvTileBytes = 4 * 64 * 128 + 64 * 64;         // 36864
 constexpr int kKvStageBytes = 37 * 1024;                     // tile + 256 B of scales, 1 KiB aligned
-constexpr int kPBytes = 128 * 64;
-constexpr int kMlaSmem = 1024 + kQBytes + kMlaStages * kKvStageBytes + 2 * kPBytes + 1024 + 4096;
+constexpr int kMlaSmem = 1024 + kQBytes + kMlaStages * kKvStageBytes + 1024 + 4096;
 constexpr int kMlaThreads = 320;   // TMA warp, MMA warp, 8 softmax warps (two threads per head)
 
 struct MlaItem { int req, half, split, tile0, ntiles, pad0, pad1, pad2; };
 
 struct MlaArgs {
+  const uint8_t* q8;        // [heads][T][576] e4m3 queries
   const float* sq;          // [heads][T] query scales
   const float* kv_scale;    // [n_pages][64]
+  const float* kv_smax;     // [n_pages][4]: [0] = upper bound of the page's 64 scales
   const int* page_table;    // [n_slots][max_pages]
   const int* slot_of;       // [T] slot of each query row
   const int* kvlen;         // [T] tokens visible to each query row (including itself)
@@ -54,6 +58,7 @@ struct MlaArgs {
   __nv_bfloat16* opart;     // [T][max_splits][heads][512]
   float* lse;               // [T][max_splits][heads]   (log2 domain)
   int* status;
+  long long* trace;         // optional phase timestamps of CTA 0 (debug aid), NULL when off
   int T, max_pages, max_splits;
   float scale_log2e;        // softmax scale * log2(e)
 };
@@ -77,23 +82,21 @@ __global__ void mla_build_items(const int* kvlen, int T, int tiles_per_split, in
 }
 
 __global__ void __launch_bounds__(kMlaThreads, 1)
-mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_q,
-                  const __grid_constant__ CUtensorMap tm_qr, const __grid_constant__ CUtensorMap tm_kv,
-                  const __grid_constant__ CUtensorMap tm_kvr) {
+mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
+                  const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_kvr) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* q_smem = smem;
   uint8_t* kv_smem = smem + kQBytes;
-  uint8_t* p_smem = kv_smem + kMlaStages * kKvStageBytes;
-  uint8_t* ctrl = p_smem + 2 * kPBytes;
+  uint8_t* ctrl = kv_smem + kMlaStages * kKvStageBytes;
   uint64_t* q_full = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* q_empty = q_full + 1;
-  uint64_t* kv_full = q_empty + 1;           // [3]
-  uint64_t* kv_empty = kv_full + kMlaStages; // [3]
+  uint64_t* kv_full = q_empty + 1;           // [kMlaStages]
+  uint64_t* kv_empty = kv_full + kMlaStages; // [kMlaStages]
   uint64_t* s_full = kv_empty + kMlaStages;  // [2]
-  uint64_t* s_empty = s_full + 2;            // [2]
-  uint64_t* p_full = s_empty + 2;            // [2]
+  uint64_t* qt_full = s_full + 2;            // [1] latent Q stored to TMEM by the softmax warps
+  uint64_t* p_full = qt_full + 1;            // [2]
   uint64_t* pv_done = p_full + 2;            // [2] indexed by tile parity (see the softmax warps)
   uint64_t* o_free = pv_done + 2;            // [1]
   uint64_t* drain_bar = o_free + 1;          // [1]
@@ -110,7 +113,8 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_q,
     mbar_init(q_full, 1);
     mbar_init(q_empty, 1);
     for (int s = 0; s < kMlaStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 8); mbar_init(&p_full[b], 8); mbar_init(&xchg_bar[b], 8); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 8); mbar_init(&xchg_bar[b], 8); }
+    mbar_init(qt_full, 8);
     mbar_init(&pv_done[0], 1);
     mbar_init(&pv_done[1], 1);
     mbar_init(o_free, 8);
@@ -118,15 +122,16 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_q,
     *abort_flag = 0;
     *never_flag = 0;
     fence_mbar_init();
-    tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_qr); tma_prefetch_desc(&tm_kv); tma_prefetch_desc(&tm_kvr);
+    tma_prefetch_desc(&tm_qr); tma_prefetch_desc(&tm_kv); tma_prefetch_desc(&tm_kvr);
   }
   if (warp == 1) { tmem_alloc(tmem_holder, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tm_s = tmem_base;          // S buffers: columns [0,64) and [64,128)
+  const uint32_t tm_s = tmem_base;          // S buffers: columns [0,64) and [64,128); P aliases the first 16 of each
   const uint32_t tm_o = tmem_base + 128;    // O: 256 columns
+  const uint32_t tm_q = tmem_base + 384;    // latent Q as e4m3 A operand: 128 columns (4 bytes of K per column)
   const int n_items = *a.n_items;
 
   if (warp == 0) {
@@ -138,8 +143,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_q,
         const MlaItem w = a.items[it];
         if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT); break; }
         mbar_expect_tx(q_full, kQBytes);
-        for (int c = 0; c < 4; ++c) tma_load_3d(q_smem + c * 16384, &tm_q, c * 128, w.req, 0, q_full);
-        tma_load_3d(q_smem + 65536, &tm_qr, 512, w.req, 0, q_full);
+        tma_load_3d(q_smem, &tm_qr, 512, w.req, 0, q_full);
         const int* pt = a.page_table + static_cast<size_t>(a.slot_of[w.req]) * a.max_pages;
         int page_next = pt[w.tile0];
         for (int i = 0; i < w.ntiles; ++i, ++kv_it) {
@@ -152,10 +156,11 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_q,
             *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT); ok = false; break;
           }
           uint8_t* st = kv_smem + s * kKvStageBytes;
-          mbar_expect_tx(&kv_full[s], kKvTileBytes + 256);
+          mbar_expect_tx(&kv_full[s], kKvTileBytes + 256 + 16);
           for (int c = 0; c < 4; ++c) tma_load_2d(st + c * 8192, &tm_kv, c * 128, page * kMlaPage, &kv_full[s]);
           tma_load_2d(st + 32768, &tm_kvr, 512, page * kMlaPage, &kv_full[s]);
           bulk_load_1d(st + kKvTileBytes, a.kv_scale + static_cast<size_t>(page) * kMlaPage, 256, &kv_full[s]);
+          bulk_load_1d(st + kKvTileBytes + 256, a.kv_smax + static_cast<size_t>(page) * 4, 16, &kv_full[s]);
         }
       }
     }
@@ -169,17 +174,18 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_q,
       auto issue_qk = [&](uint32_t kvi, uint32_t ti) -> bool {
         const int s = kvi % kMlaStages;
         if (!mbar_wait(&kv_full[s], (kvi / kMlaStages) & 1, abort_flag)) { atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); return false; }
-        if (!mbar_wait(&s_empty[ti & 1], ((ti >> 1) & 1) ^ 1, abort_flag)) { atomicCAS(a.status, 0, PLOW_ERR_TMEM_FREE_WAIT); return false; }
         tc_fence_after();
+        // S buffer ti&1 (and the P written over it) was last read by P.V of tile ti-2, which was
+        // issued before this point and executes in order ahead of these MMAs.
         const uint32_t d = tm_s + (ti & 1) * 64;
-        const uint32_t qa = smem_u32(q_smem), ka = smem_u32(kv_smem + s * kKvStageBytes);
+        const uint32_t ka = smem_u32(kv_smem + s * kKvStageBytes);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const uint64_t qd = umma_desc_k128(qa + c * 16384), kd = umma_desc_k128(ka + c * 8192);
+          const uint64_t kd = umma_desc_k128(ka + c * 8192);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) tc_mma_f8(d, qd + 2 * k, kd + 2 * k, idesc_qk, (c | k) != 0);
+          for (int k = 0; k < 4; ++k) tc_mma_f8_ts(d, tm_q + (c * 4 + k) * 8, kd + 2 * k, idesc_qk, (c | k) != 0);
         }
-        const uint64_t qd = umma_desc_k64(qa + 65536), kd = umma_desc_k64(ka + 32768);
+        const uint64_t qd = umma_desc_k64(smem_u32(q_smem)), kd = umma_desc_k64(ka + 32768);
         tc_mma_f8(d, qd, kd, idesc_qk, 1);
         tc_mma_f8(d, qd + 2, kd + 2, idesc_qk, 1);
         tc_commit(&s_full[ti & 1]);
@@ -188,6 +194,8 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_q,
       for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x, ++item_it) {
         const MlaItem w = a.items[it];
         if (!mbar_wait(q_full, item_it & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); break; }
+        if (!mbar_wait(qt_full, item_it & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); break; }
+        tc_fence_after();
         if (!issue_qk(kv_it, tile_it)) { *abort_flag = 1; break; }
         for (int i = 0; i < w.ntiles; ++i) {
           if (i + 1 < w.ntiles) {
@@ -200,12 +208,13 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_q,
           if (!mbar_wait(&p_full[ti & 1], (ti >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
           tc_fence_after();
           const int s = (kv_it + i) % kMlaStages;
-          const uint32_t pa = smem_u32(p_smem + (ti & 1) * kPBytes);
+          const uint32_t pt = tm_s + (ti & 1) * 64;   // P: 16 columns = 64 tokens of e4m3
           const uint32_t va = smem_u32(kv_smem + s * kKvStageBytes) + w.half * 2 * 8192;
-          tc_mma_f8(tm_o, umma_desc_k64(pa), umma_desc_mn128(va, 8192, 1024), idesc_pv, i > 0);
-          tc_mma_f8(tm_o, umma_desc_k64(pa) + 2, umma_desc_mn128(va + 4096, 8192, 1024), idesc_pv, 1);
+          tc_mma_f8_ts(tm_o, pt, umma_desc_mn128(va, 8192, 1024), idesc_pv, i > 0);
+          tc_mma_f8_ts(tm_o, pt + 8, umma_desc_mn128(va + 4096, 8192, 1024), idesc_pv, 1);
           tc_commit(&kv_empty[s]);
           tc_commit(&pv_done[ti & 1]);
+          if (a.trace && blockIdx.x == 0 && ti < 64) a.trace[ti * 8 + 7] = clock64();
         }
         kv_it += w.ntiles;
         tile_it += w.ntiles;
@@ -238,71 +247,93 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_q,
       const MlaItem w = a.items[it];
       const int kv_len = a.kvlen[w.req];
       const float qs = a.sq[static_cast<size_t>(li) * a.T + w.req] * a.scale_log2e;
-      float m = 0.f, l = 0.f, SK = 1.f;
-      for (int i = 0; i < w.ntiles; ++i) {
-        const uint32_t ti = tile_it + i;
-        if (!mbar_wait(&s_full[ti & 1], (ti >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
+      float m = 0.f, l = 0.f, SK = 1.f, M = 0.f;
+      {
+        // latent Q of this (head, request) into TMEM: this thread owns bytes [256 ch, 256 ch + 256)
+        // of the row, i.e. TMEM columns [64 ch, 64 ch + 64).  The previous item's QK^T must have
+        // retired before its Q is overwritten.
+        if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_FREE_WAIT); ok = false; break; }
         tc_fence_after();
-        uint32_t sv[32];
-        tmem_ld32(tm_s + lane_addr + (ti & 1) * 64 + ch * 32, sv);
-        tmem_ld_wait();
+        const uint4* qrow = reinterpret_cast<const uint4*>(a.q8 + (static_cast<size_t>(li) * a.T + w.req) * kMlaRow + ch * 256);
+        uint32_t qv[64];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { const uint4 v = qrow[j]; qv[4 * j] = v.x; qv[4 * j + 1] = v.y; qv[4 * j + 2] = v.z; qv[4 * j + 3] = v.w; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) tmem_st16(tm_q + lane_addr + ch * 64 + j * 16, qv + j * 16);
+        tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&s_empty[ti & 1]);
+        if (lane == 0) mbar_arrive(qt_full);
+      }
+      for (int i = 0; i < w.ntiles; ++i) {
+        const uint32_t ti = tile_it + i;
+        const bool tr = a.trace && blockIdx.x == 0 && warp == 2 && lane == 0 && ti < 64;
+        if (tr) a.trace[ti * 8 + 0] = clock64();
+        // (a) per-token scales (they arrived with the KV tile, usually long before S is ready)
         const int s = (kv_it + i) % kMlaStages;
-        // the per-token scales arrived with the tile: observe the stage barrier directly so the
-        // bulk copy's writes are ordered before the reads below
         if (!mbar_wait(&kv_full[s], ((kv_it + i) / kMlaStages) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); ok = false; break; }
-        const float4* sk4 = reinterpret_cast<const float4*>(kv_smem + s * kKvStageBytes + kKvTileBytes) + ch * 8;
+        const float* sk_base = reinterpret_cast<const float*>(kv_smem + s * kKvStageBytes + kKvTileBytes);
+        const float4* sk4 = reinterpret_cast<const float4*>(sk_base) + ch * 8;
+        const float skmax = sk_base[64];       // upper bound of this page's scales, kept by the cache writer
         const int valid = min(kMlaPage, kv_len - (w.tile0 + i) * kMlaPage) - ch * 32;   // valid columns of this half
-        float x[32], skv[32];
-        float mx = -INFINITY, skmax = 0.f;
+        float skv[32];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float4 k4 = sk4[j];
           skv[4 * j] = k4.x; skv[4 * j + 1] = k4.y; skv[4 * j + 2] = k4.z; skv[4 * j + 3] = k4.w;
         }
+        // (b) scores
+        if (!mbar_wait(&s_full[ti & 1], (ti >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
+        tc_fence_after();
+        if (tr) a.trace[ti * 8 + 1] = clock64();
+        uint32_t sv[32];
+        tmem_ld32(tm_s + lane_addr + (ti & 1) * 64 + ch * 32, sv);
+        tmem_ld_wait();
+        float x[32];
+        float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         if (valid >= 32) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             x[j] = __uint_as_float(sv[j]) * (qs * skv[j]);
-            mx = fmaxf(mx, x[j]);
-            skmax = fmaxf(skmax, skv[j]);
+            mxa[j & 3] = fmaxf(mxa[j & 3], x[j]);
           }
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const bool in = j < valid;
-            x[j] = in ? __uint_as_float(sv[j]) * (qs * skv[j]) : -INFINITY;
-            mx = fmaxf(mx, x[j]);
-            skmax = in ? fmaxf(skmax, skv[j]) : skmax;
+            x[j] = j < valid ? __uint_as_float(sv[j]) * (qs * skv[j]) : -INFINITY;
+            mxa[j & 3] = fmaxf(mxa[j & 3], x[j]);
           }
         }
-        float omx, osk;
-        if (!exchange(mx, skmax, omx, osk)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
+        float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
+        float omx, unused0;
+        if (tr) a.trace[ti * 8 + 2] = clock64();
+        if (!exchange(mx, 0.f, omx, unused0)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
         mx = fmaxf(mx, omx);
-        skmax = fmaxf(skmax, osk);
-        // Lazy rescaling: the running maximum m is only raised when a tile exceeds it by more
-        // than kTau (log2 units), so p = 2^(x - m) stays below 2^kTau, well inside e4m3 range,
-        // and the accumulator in TMEM is almost never touched.  The running scale bound SK is
-        // raised with 2x head-room for the same reason.  Any (m, SK) is valid as long as O and
-        // l are kept consistent with it; both threads of a row see the same (mx, skmax) and
-        // therefore take the same decision.
+        if (tr) a.trace[ti * 8 + 3] = clock64();
+        // Lazy rescaling with one running offset M = m + log2(SK): probabilities are formed as
+        // p' = 2^(x - M) * sk <= 2^kTau * sk / SK <= 2^kTau, inside e4m3 range, and l' = sum 2^(x - M)
+        // is kept with the same offset, so O / l' needs no further correction at the end.  m is
+        // only raised when a tile exceeds it by more than kTau (log2 units) and SK (an upper bound
+        // of the scales seen, with 2x head-room) only when a page exceeds it, so the accumulator in
+        // TMEM is almost never touched.  Both threads of a row see the same (mx, skmax) and take
+        // the same decision.
         constexpr float kTau = 7.0f;
         if (i == 0) {
           m = mx;
           SK = skmax * 2.0f;
+          M = m + log2f(SK);
         } else {
           const bool up_m = mx > m + kTau;
           const bool up_sk = skmax > SK;
           if (__any_sync(0xffffffffu, up_m || up_sk)) {
             const float m_new = up_m ? mx : m;
             const float SK_new = up_sk ? skmax * 2.0f : SK;
-            const float alpha_l = exp2f(m - m_new);
-            const float alpha_o = alpha_l * (SK / SK_new);
-            l *= alpha_l;
+            const float M_new = m_new + log2f(SK_new);
+            const float alpha = exp2f(M - M_new);
+            l *= alpha;
             m = m_new;
             SK = SK_new;
+            M = M_new;
             // accumulator must be quiescent: P.V of the previous tile has retired.  QK^T of this
             // tile was issued after P.V of tile ti-2, so at most tile ti-1 is pending on its
             // parity's barrier and the phase below cannot alias.
@@ -314,7 +345,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_q,
               tmem_ld32(tm_o + lane_addr + ch * 128 + c, o);
               tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha_o);
+              for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
               tmem_st16(tm_o + lane_addr + ch * 128 + c, o);
               tmem_st16(tm_o + lane_addr + ch * 128 + c + 16, o + 16);
             }
@@ -322,33 +353,47 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_q,
             tc_fence_before();
           }
         }
-        const float inv_sk = 1.0f / SK;
-        float sum = 0.f;
+        // (c) exponentials.  The MUFU unit sustains 16 ex2 per clock per SM (512 clocks for a
+        // 128 x 64 tile); one column in four is evaluated on the FMA pipe instead (round-down
+        // magic add for floor, cubic for 2^frac, exponent spliced in with integer ops; 1e-4
+        // relative error, far below e4m3's), so both pipes run side by side.
+        float suma = 0.f, sumb = 0.f;
         uint32_t pk[8];
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
           float p[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
+            const float t = x[j + u] - M;
             float e;
-            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x[j + u] - m));
-            sum += e;
-            p[u] = e * (skv[j + u] * inv_sk);
+            if (u == 3) {
+              const float tc = fmaxf(t, -126.0f);
+              const float r = __fadd_rd(tc, 12582912.0f);            // 1.5 * 2^23 + floor(t)
+              const float f = tc - (r - 12582912.0f);                // frac in [0, 1)
+              const float pf = fmaf(fmaf(fmaf(0.07908570f, f, 0.22451635f), f, 0.69639057f), f, 0.99989671f);
+              e = __int_as_float(__float_as_int(pf) + (__float_as_int(r) << 23));
+              sumb += e;
+            } else {
+              asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
+              suma += e;
+            }
+            p[u] = e * skv[j + u];
           }
           __nv_fp8x4_e4m3 q4(make_float4(p[0], p[1], p[2], p[3]));
           pk[j >> 2] = *reinterpret_cast<uint32_t*>(&q4);
         }
-        l += sum;
-        // P row (64 bytes) with the 64-byte swizzle: 16-byte unit c lands at c ^ ((row >> 1) & 3);
-        // this thread owns units 2 ch and 2 ch + 1
-        uint8_t* prow = p_smem + (ti & 1) * kPBytes + li * 64;
-        const int sw = (li >> 1) & 3;
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-          *reinterpret_cast<uint4*>(prow + (((2 * ch + c) ^ sw) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-        fence_proxy_async_smem();
+        l += suma + sumb;
+        if (tr) a.trace[ti * 8 + 4] = clock64();
+        // P (e4m3, 4 tokens per 32-bit column) over the first 16 columns of the S buffer it came
+        // from; this thread owns tokens [32 ch, 32 ch + 32) = columns [8 ch, 8 ch + 8).  The
+        // partner thread finished reading its S columns before the exchange above completed.
+        tmem_st8(tm_s + lane_addr + (ti & 1) * 64 + ch * 8, pk);
+        tmem_st_wait();
+        if (tr) a.trace[ti * 8 + 5] = clock64();
+        tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[ti & 1]);
+        if (tr) a.trace[ti * 8 + 6] = clock64();
       }
       if (!ok) break;
       // ---- finalize this item: O * SK / l, log-sum-exp in the log2 domain
@@ -358,7 +403,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_q,
       const uint32_t ti_last = tile_it + w.ntiles - 1;
       if (!mbar_wait(&pv_done[ti_last & 1], (ti_last >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); break; }
       tc_fence_after();
-      const float fin = l > 0.f ? SK / l : 0.f;
+      const float fin = l > 0.f ? 1.0f / l : 0.f;
       const size_t obase = ((static_cast<size_t>(w.req) * a.max_splits + w.split) * kMlaHeads + li) * kMlaLatent + w.half * 256 + ch * 128;
 #pragma unroll 1
       for (int c = 0; c < 128; c += 32) {
@@ -375,7 +420,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int q = 0; q < 4; ++q) dst[q] = make_uint4(h2[4 * q], h2[4 * q + 1], h2[4 * q + 2], h2[4 * q + 3]);
       }
-      if (w.half == 0 && ch == 0) a.lse[(static_cast<size_t>(w.req) * a.max_splits + w.split) * kMlaHeads + li] = m + log2f(fmaxf(l, 1e-30f));
+      if (w.half == 0 && ch == 0) a.lse[(static_cast<size_t>(w.req) * a.max_splits + w.split) * kMlaHeads + li] = M + log2f(fmaxf(l, 1e-30f));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(o_free);
@@ -420,23 +465,27 @@ __global__ void mla_merge_kernel(const __nv_bfloat16* opart, const float* lse, c
 
 }  // namespace plow
 
+static long long* g_mla_trace = nullptr;
+
 extern "C" {
+
+// Debug aid: device buffer of 64*8 int64 that CTA 0 fills with clock64() phase stamps (NULL = off).
+void plow_mla_set_trace(void* p) { g_mla_trace = static_cast<long long*>(p); }
 
 // Scratch the caller provides: items (8 ints per item, capacity 2*T*max_splits), n_items (1 int),
 // opart bf16 [T][max_splits][128][512], lse f32 [T][max_splits][128].
 // q8 e4m3 [128 heads][T][576]; sq f32 [128][T]; kv e4m3 [n_pages][64][576]; kv_scale f32 [n_pages][64];
+// kv_smax f32 [n_pages][4] (element 0: an upper bound of the page's scales, maintained by the cache writer);
 // out bf16 [128][T][512].
-int plow_mla_decode(const void* q8, const float* sq, const void* kv, const float* kv_scale, int64_t n_pages,
+int plow_mla_decode(const void* q8, const float* sq, const void* kv, const float* kv_scale, const float* kv_smax, int64_t n_pages,
                     const int* page_table, int max_pages, const int* slot_of, const int* kvlen, int T,
                     int tiles_per_split, int max_splits, void* items, int* n_items, void* opart, float* lse,
                     void* out, float softmax_scale, int* status, void* stream_) {
   using namespace plow;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (T <= 0 || max_splits <= 0 || tiles_per_split <= 0) return -1;
-  CUtensorMap tq, tqr, tkv, tkvr;
-  int r = make_tmap_3d(&tq, q8, 1, kMlaRow, T, kMlaHeads, kMlaRow, static_cast<uint64_t>(T) * kMlaRow, 1, 128, 128);
-  if (r) return 1000 + r;
-  r = make_tmap_3d(&tqr, q8, 1, kMlaRow, T, kMlaHeads, kMlaRow, static_cast<uint64_t>(T) * kMlaRow, 1, 128, 64);
+  CUtensorMap tqr, tkv, tkvr;
+  int r = make_tmap_3d(&tqr, q8, 1, kMlaRow, T, kMlaHeads, kMlaRow, static_cast<uint64_t>(T) * kMlaRow, 1, 128, 64);
   if (r) return 1100 + r;
   r = make_tmap_2d(&tkv, kv, 1, static_cast<uint64_t>(n_pages) * kMlaPage, kMlaRow, kMlaRow, kMlaPage, 128);
   if (r) return 1200 + r;
@@ -449,15 +498,15 @@ int plow_mla_decode(const void* q8, const float* sq, const void* kv, const float
   }
   mla_build_items<<<1, 32, 0, stream>>>(kvlen, T, tiles_per_split, max_splits, static_cast<MlaItem*>(items), n_items);
   MlaArgs a;
-  a.sq = sq; a.kv_scale = kv_scale; a.page_table = page_table; a.slot_of = slot_of; a.kvlen = kvlen;
+  a.q8 = static_cast<const uint8_t*>(q8); a.sq = sq; a.kv_scale = kv_scale; a.kv_smax = kv_smax; a.page_table = page_table; a.slot_of = slot_of; a.kvlen = kvlen;
   a.items = static_cast<const MlaItem*>(items); a.n_items = n_items;
-  a.opart = static_cast<__nv_bfloat16*>(opart); a.lse = lse; a.status = status;
+  a.opart = static_cast<__nv_bfloat16*>(opart); a.lse = lse; a.status = status; a.trace = g_mla_trace;
   a.T = T; a.max_pages = max_pages; a.max_splits = max_splits;
   a.scale_log2e = softmax_scale * 1.4426950408889634f;
   int grid = sm_count();
   const int cap = 2 * T * max_splits;
   if (cap < grid) grid = cap;
-  mla_decode_kernel<<<grid, kMlaThreads, kMlaSmem, stream>>>(a, tq, tqr, tkv, tkvr);
+  mla_decode_kernel<<<grid, kMlaThreads, kMlaSmem, stream>>>(a, tqr, tkv, tkvr);
   mla_merge_kernel<<<dim3(T, kMlaHeads), 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(opart), lse, kvlen, T,
                                                           max_splits, tiles_per_split, static_cast<__nv_bfloat16*>(out));
   cudaError_t e = cudaGetLastError();

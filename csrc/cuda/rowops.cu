@@ -216,7 +216,7 @@ __global__ void mla_q_quant_kernel(uint8_t* q8, float* sq, const __nv_bfloat16* 
 
 // kva [T][pitch] (latent | rope at col_ofs) -> RMSNorm(latent)*gamma, RoPE(rope) -> one e4m3 row of
 // latent+rope bytes with one f32 scale, written to the token's cell of the paged cache.
-__global__ void mla_kv_write_kernel(uint8_t* kv8, float* kv_scale, const __nv_bfloat16* kva, int pitch, int col_ofs,
+__global__ void mla_kv_write_kernel(uint8_t* kv8, float* kv_scale, float* kv_smax, const __nv_bfloat16* kva, int pitch, int col_ofs,
                                     const __nv_bfloat16* gamma, const float* rope_tab, const int* pos, const int* slot_of,
                                     const int* page_table, int max_pages, int latent, int rope, float eps, int pair_mode) {
   extern __shared__ float rowf[];   // latent + rope
@@ -256,7 +256,12 @@ __global__ void mla_kv_write_kernel(uint8_t* kv8, float* kv_scale, const __nv_bf
   const size_t cell = static_cast<size_t>(page) * 64 + (p & 63);
   const int W = latent + rope;
   for (int i = threadIdx.x; i < W; i += blockDim.x) kv8[cell * W + i] = __nv_fp8_e4m3(rowf[i] * inv).__x;
-  if (threadIdx.x == 0) kv_scale[cell] = sc;
+  if (threadIdx.x == 0) {
+    kv_scale[cell] = sc;
+    // per-page upper bound of the scales (positive floats order like their bit patterns).  The
+    // bound is never lowered when a page is recycled: the decode kernel only needs sk <= bound.
+    if (kv_smax) atomicMax(reinterpret_cast<int*>(kv_smax) + static_cast<size_t>(page) * 4, __float_as_int(sc));
+  }
 }
 
 // ---- router -----------------------------------------------------------------------------------
@@ -507,10 +512,10 @@ int plow_mla_q_quant(void* q8, float* sq, const void* q_abs, const void* q_rope,
   return ok();
 }
 
-int plow_mla_kv_write(void* kv8, float* kv_scale, const void* kva, int pitch, int col_ofs, const void* gamma,
+int plow_mla_kv_write(void* kv8, float* kv_scale, float* kv_smax, const void* kva, int pitch, int col_ofs, const void* gamma,
                       const float* rope_tab, const int* pos, const int* slot_of, const int* page_table, int max_pages, int T,
                       int latent, int rope, float eps, int pair_mode, void* st) {
-  mla_kv_write_kernel<<<T, 128, (latent + rope) * 4, S(st)>>>((uint8_t*)kv8, kv_scale, (const bf16*)kva, pitch, col_ofs,
+  mla_kv_write_kernel<<<T, 128, (latent + rope) * 4, S(st)>>>((uint8_t*)kv8, kv_scale, kv_smax, (const bf16*)kva, pitch, col_ofs,
                                                               (const bf16*)gamma, rope_tab, pos, slot_of, page_table, max_pages,
                                                               latent, rope, eps, pair_mode);
   return ok();

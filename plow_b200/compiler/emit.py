@@ -211,8 +211,14 @@ class Lowering:
             return int(v)
 
         handles = [self.t(x) for x in (n.outputs + n.inputs)][:8]
-        ins = pk.Inst(op, f=tuple([float(n.attrs.get(k, 0.0)) for k in fkeys] + [0.0] * (3 - len(fkeys))),
-                      t=handles + [pk.T_NONE] * (8 - len(handles)), i=[iv(k) for k in ikeys][:7] + [n.layer & 0xFFFF])
+        ivals = ([iv(k) for k in ikeys] + [0] * 7)[:7]
+        fvals = [float(n.attrs.get(k, 0.0)) for k in fkeys] + [0.0] * (3 - len(fkeys))
+        if n.op == "mla_kv_write":
+            # the latent row is usually a column range of the fused [q_a | kv_a] projection
+            ivals[5], ivals[6] = self.xview(n.inputs[0])
+        if n.op in ("mla_attention", "dsa_topk"):
+            fvals[1] = float(n.attrs.get("topk", 0))
+        ins = pk.Inst(op, f=tuple(fvals[:3]), t=handles + [pk.T_NONE] * (8 - len(handles)), i=ivals + [n.layer & 0xFFFF])
         return schedule.LInst(ins, rd(*n.inputs), rd(*n.outputs), 5.0, max(1, rows), cls)
 
 

@@ -34,9 +34,9 @@ def q_quant(q_abs, q_rope):
     return q8, sq
 
 
-def kv_write(kv8, kv_scale, kva, col_ofs, gamma, rope_tab, pos, slot_of, page_table, latent, rope, eps, pair_mode=1):
+def kv_write(kv8, kv_scale, kv_smax, kva, col_ofs, gamma, rope_tab, pos, slot_of, page_table, latent, rope, eps, pair_mode=1):
     T = kva.shape[0]
-    native.call("plow_mla_kv_write", kv8, kv_scale, kva, kva.stride(0), col_ofs, gamma, rope_tab, pos, slot_of, page_table,
+    native.call("plow_mla_kv_write", kv8, kv_scale, kv_smax, kva, kva.stride(0), col_ofs, gamma, rope_tab, pos, slot_of, page_table,
                 page_table.shape[1], T, latent, rope, float(eps), pair_mode)
 
 
@@ -52,13 +52,14 @@ class DecodeWorkspace:
         self.lse = torch.empty(max_T, self.max_splits, heads, dtype=torch.float32, device=device)
 
 
-def decode(q8, sq, kv8, kv_scale, page_table, slot_of, kvlen, ws: DecodeWorkspace, softmax_scale, out=None):
-    """q8 [128][T][576] e4m3, sq [128][T]; kv8 [pages][64][576]; returns oacc bf16 [128][T][512]."""
+def decode(q8, sq, kv8, kv_scale, kv_smax, page_table, slot_of, kvlen, ws: DecodeWorkspace, softmax_scale, out=None):
+    """q8 [128][T][576] e4m3, sq [128][T]; kv8 [pages][64][576]; kv_smax f32 [pages][4] (element 0 bounds the
+    page's scales from above); returns oacc bf16 [128][T][512]."""
     heads, T, _ = q8.shape
     assert heads == 128 and kv8.shape[1:] == (64, 576)
     if out is None:
         out = torch.empty(heads, T, 512, dtype=BF16, device=q8.device)
-    native.call("plow_mla_decode", q8, sq, kv8, kv_scale, kv8.shape[0], page_table, page_table.shape[1], slot_of, kvlen, T,
+    native.call("plow_mla_decode", q8, sq, kv8, kv_scale, kv_smax, kv8.shape[0], page_table, page_table.shape[1], slot_of, kvlen, T,
                 ws.tiles_per_split, ws.max_splits, ws.items, ws.n_items, ws.opart, ws.lse, out, float(softmax_scale),
                 native.status_word(q8.device))
     return out

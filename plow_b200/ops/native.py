@@ -100,7 +100,7 @@ _SIGS = {
     "plow_quant_act": "ppipiiip",
     "plow_mla_q_prep": "pppippiiiiip",
     "plow_mla_q_quant": "ppppiiiip",
-    "plow_mla_kv_write": "pppiipppppiiiifip",
+    "plow_mla_kv_write": "ppppiipppppiiiifip",
     "plow_router_topk": "pppiiiiiiifp",
     "plow_moe_align": "piiippppp",
     "plow_moe_gather": "ppippipp" "iiip",
@@ -108,7 +108,7 @@ _SIGS = {
     "plow_argmax": "ppiip",
     "plow_row_gather": "pppiip",
     "plow_head_to_token": "ppiiip",
-    "plow_mla_decode": "pppplpipp" "iiipppppfpp",
+    "plow_mla_decode": "ppppplpipp" "iiipppppfpp",
 }
 _CT = {"p": C.c_void_p, "i": C.c_int32, "l": C.c_int64, "f": C.c_float}
 

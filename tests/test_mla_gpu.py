@@ -71,9 +71,10 @@ def test_mla_decode_vs_reference(lens, tps):
     q8 = (q / sq[..., None]).to(torch.float8_e4m3fn)
     kvlen = torch.tensor(lens, dtype=torch.int32, device="cuda")
     slot_of = torch.arange(T, dtype=torch.int32, device="cuda")
+    smax = torch.zeros(kv8.shape[0], 4, device='cuda'); smax[:, 0] = ksc.amax(1)
     ws = mla.DecodeWorkspace(T, max_ctx + 64, tiles_per_split=tps)
     scale = 1.0 / math.sqrt(192)
-    out = mla.decode(q8, sq, kv8, ksc, pt, slot_of, kvlen, ws, scale)
+    out = mla.decode(q8, sq, kv8, ksc, smax, pt, slot_of, kvlen, ws, scale)
     native.check_status()
     qd = q8.float() * sq[..., None]
     for r, n in enumerate(lens):
@@ -97,7 +98,8 @@ def test_kv_write_roundtrip():
     pt = torch.arange(3 * 16, dtype=torch.int32, device="cuda").view(3, 16).flip(1).contiguous()
     kv8 = torch.zeros(48, 64, 576, device="cuda").to(torch.float8_e4m3fn)
     ksc = torch.zeros(48, 64, device="cuda")
-    mla.kv_write(kv8, ksc, kva, 1536, gamma, tab, pos, slot, pt, 512, 64, 1e-6, 1)
+    smax = torch.zeros(48, 4, device='cuda')
+    mla.kv_write(kv8, ksc, smax, kva, 1536, gamma, tab, pos, slot, pt, 512, 64, 1e-6, 1)
     src = kva[:, 1536:].float()
     lat = src[:, :512] * torch.rsqrt(src[:, :512].pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float()
     rope = _rope_ref(src[:, 512:], tab, pos)
