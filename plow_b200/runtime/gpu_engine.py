@@ -1,0 +1,494 @@
+"""sm_100a backend: executes packet programs with the hand-written kernels in ``libplow_cuda.so``.
+
+A program's instruction list is walked in order and every opcode is dispatched to a launcher
+(`role objects`: tcgen05 GEMMs, attention kernels, row-wise kernels); the whole walk for a decode
+rung is captured once in a CUDA graph and replayed, so a decode step costs one graph launch, one
+H2D copy of the step inputs from pinned memory and one D2H read of the sampled ids.  Activations
+live at the arena offsets the compiler planned (stable addresses make the capture valid);
+padding rows of a rung point at a scratch slot so they never touch live KV.
+
+Weights come from a :class:`WeightSource`: the checkpoint (names are the contract; block-scaled
+e4m3 twins are produced on the device at load) or a synthetic on-device generator for benches at
+the 671B shape, where no checkpoint exists.  Reference counterpart: crates/plowrt/src/exec/gpu.rs
+(GpuEngine::load :4164, step_slots :9593, segment roles exec/gpu/*.rs).
+"""
+from __future__ import annotations
+
+import json
+import math
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from ..compiler import packet as pk
+from ..compiler.packet import Op
+from ..ops import gemm as gemm_ops, mla as mla_ops, native, quant, rowops
+from ..utils.rope import rope_table
+from .engine import EngineBase, EngineError, StepResult, TokenBatch
+from .kv_pages import PAGE
+
+BF16, FP8, F32, I32 = torch.bfloat16, torch.float8_e4m3fn, torch.float32, torch.int32
+_TORCH_DT = {pk.DType.F32: F32, pk.DType.BF16: BF16, pk.DType.E4M3: FP8, pk.DType.I32: I32, pk.DType.U8: torch.uint8}
+
+
+# ------------------------------------------------------------------------------------------------
+class WeightSource:
+    """Provides device tensors for WEIGHT / DERIVED packet entries."""
+
+    def bf16(self, ent, recipe) -> torch.Tensor:
+        raise NotImplementedError
+
+    def fp8(self, ent, recipe):
+        """(e4m3 [N, K], f32 scales [N/128, K/128])"""
+        w = self.bf16(ent, recipe)
+        q, s = quant.quant_weight_128x128(w)
+        return q, s
+
+
+class CheckpointWeights(WeightSource):
+    def __init__(self, ckpt_dir, device, tp=1, rank=0):
+        from .weights import Checkpoint
+        self.ckpt = Checkpoint(ckpt_dir)
+        self.device, self.tp, self.rank = device, tp, rank
+
+    def bf16(self, ent, recipe):
+        from .weights import materialize
+        w = materialize(ent.name, ent, recipe, self.ckpt, self.tp, self.rank)
+        dt = F32 if pk.DType(ent.dtype) == pk.DType.F32 else BF16
+        return w.to(device=self.device, dtype=dt).contiguous()
+
+
+class SyntheticWeights(WeightSource):
+    """N(0, std) weights generated on the device (norm weights 1, biases 0).  e4m3 tensors are
+    drawn directly in the quantised domain with one constant block scale, so a 100 GB shard is
+    produced in about a minute without a bf16 copy ever existing."""
+
+    def __init__(self, device, seed=0, std=0.02):
+        self.device, self.std = device, std
+        self.gen = torch.Generator(device=device).manual_seed(seed)
+
+    def _shape(self, ent):
+        return tuple(int(d) for d in ent.dims)
+
+    def bf16(self, ent, recipe):
+        shape = self._shape(ent)
+        dt = F32 if pk.DType(ent.dtype) == pk.DType.F32 else BF16
+        n = ent.name
+        if n.endswith("norm.weight") or n.endswith("layernorm.weight"):
+            return torch.ones(shape, dtype=dt, device=self.device)
+        if n.endswith("bias"):
+            return torch.zeros(shape, dtype=dt, device=self.device)
+        out = torch.empty(shape, dtype=dt, device=self.device)
+        flat = out.view(-1)
+        step = 1 << 28
+        for i in range(0, flat.numel(), step):
+            flat[i:i + step] = torch.randn(min(step, flat.numel() - i), device=self.device, generator=self.gen) * self.std
+        return out
+
+    def fp8(self, ent, recipe):
+        n, k = self._shape(ent)
+        clip = 4.0
+        q = torch.empty(n, k, dtype=FP8, device=self.device)
+        flat = q.view(-1)
+        step = 1 << 28
+        for i in range(0, flat.numel(), step):
+            m = min(step, flat.numel() - i)
+            flat[i:i + m] = (torch.randn(m, device=self.device, generator=self.gen).clamp_(-clip, clip) * (448.0 / clip)).to(FP8)
+        s = torch.full(((n + 127) // 128, (k + 127) // 128), self.std * clip / 448.0, dtype=F32, device=self.device)
+        return q, s
+
+
+# ------------------------------------------------------------------------------------------------
+class _Prog:
+    """Per-program device state: arena views, quant side buffers, captured graph."""
+
+    def __init__(self):
+        self.t = {}          # handle -> tensor
+        self.q = {}          # handle -> (xq, sx) for activations consumed by e4m3 GEMMs
+        self.graph = None
+        self.needs_q = set()
+        self.scratch = {}
+
+
+class GpuEngine(EngineBase):
+    def __init__(self, assets_dir=None, packet=None, weights: WeightSource | None = None, max_slots=64, n_pages=None,
+                 max_ctx=8192, kv_fraction=0.9, prefix_cache=True, cuda_graphs=True, device=None, rank=0,
+                 comm=None, rungs=None):
+        if not torch.cuda.is_available():
+            raise EngineError("GpuEngine needs a CUDA device", fatal=True)
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        torch.cuda.set_device(self.device)
+        native.cuda_lib()     # raises loudly when the kernel library is missing
+        if packet is None:
+            name = "model.pkt" if rank == 0 else f"model.rank{rank}.pkt"
+            packet = pk.read_packet(Path(assets_dir) / name)
+        self.rank, self.comm = rank, comm
+        shards = packet.section_json("weight_shards.json") or {}
+        self.tp, self.ep = shards.get("tp", 1), shards.get("ep", 1)
+        if weights is None:
+            weights = CheckpointWeights(Path(assets_dir) / "checkpoint", self.device, self.tp, rank)
+        self.weights = weights
+        self.cuda_graphs = cuda_graphs
+        self.derived = packet.section_json("derived_weights.json") or {}
+        self.gen_meta = packet.section_json("gen_tensors.json") or {}
+        pages_per_seq = (max_ctx + PAGE - 1) // PAGE
+        if n_pages is None:
+            n_pages = max_slots * pages_per_seq
+        super().__init__(packet, max_slots, n_pages, max_ctx, prefix_cache)
+        self.scratch_slot = max_slots                  # padding rows of a rung live here
+        self.scratch_page = n_pages                    # one extra page nobody else maps
+        self._load_static()
+        self.progs: dict[int, _Prog] = {}
+        self.step_ms_last = 0.0
+        self.launches_last = 0
+
+    # ---- static tensors ------------------------------------------------------------------------
+    def _load_static(self) -> None:
+        dev = self.device
+        pkt = self.packet
+        self.static: dict[int, torch.Tensor] = {}
+        self.static_q: dict[int, tuple] = {}
+        fp8_handles = set()
+        for p in pkt.programs:
+            for ins in p.insts:
+                if ins.op in (Op.GEMM, Op.GEMM_XREDUCE) and ins.i[2] & pk.GEMM_FP8_BLOCK:
+                    fp8_handles.add(ins.t[2])
+                if ins.op == Op.MOE_GEMM and self.spec.weight_quant == "fp8_block128":
+                    fp8_handles.update([ins.t[3], ins.t[4]])
+        max_rows = max(p.rows for p in pkt.programs)
+        self.max_rows_all = max_rows
+        n_slots = self.max_slots + 1
+        self.d_page_table = torch.zeros(n_slots, self.max_pages_per_seq, dtype=I32, device=dev)
+        self.d_page_table[self.scratch_slot, :] = self.scratch_page
+        # step inputs: one pinned staging block + one device block, copied with a single H2D
+        self.h_in = torch.zeros(4, max_rows, dtype=I32).pin_memory()
+        self.d_in = torch.zeros(4, max_rows, dtype=I32, device=dev)      # ids, pos, seq, sample_rows
+        self.d_kvlen_row = torch.zeros(max_rows, dtype=I32, device=dev)   # pos + 1 per row
+        self.h_out = torch.zeros(max_rows, dtype=I32).pin_memory()
+        self.d_out_ids = torch.zeros(max_rows, dtype=I32, device=dev)
+        self.d_logits = None
+        for h, t in enumerate(pkt.tensors):
+            tc = t.tclass
+            if tc in (pk.TClass.WEIGHT, pk.TClass.DERIVED):
+                recipe = self.derived.get(t.name)
+                if h in fp8_handles:
+                    self.static_q[h] = self.weights.fp8(t, recipe)
+                else:
+                    self.static[h] = self.weights.bf16(t, recipe)
+            elif tc == pk.TClass.GEN:
+                m = self.gen_meta[t.name]
+                tab = rope_table(min(int(t.dims[0]), max(self.max_ctx, 64)), m["rot_dim"], m["theta"], m.get("scaling"))
+                self.static[h] = torch.from_numpy(tab).to(dev)
+            elif tc == pk.TClass.KV:
+                dims = [self.pool.n_pages + 1 if d == -3 else int(d) for d in t.dims]
+                dt = _TORCH_DT[pk.DType(t.dtype)]
+                self.static[h] = torch.zeros(dims, dtype=dt, device=dev) if dt != FP8 else torch.zeros(dims, dtype=torch.uint8, device=dev).view(FP8)
+            elif tc == pk.TClass.INPUT:
+                self.static[h] = self.d_in[{"in.ids": 0, "in.pos": 1, "in.seq": 2, "in.sample_rows": 3}[t.name]]
+            elif tc == pk.TClass.OUTPUT:
+                if t.name == "out.ids":
+                    self.static[h] = self.d_out_ids
+                else:
+                    self.d_logits = torch.zeros(max(p.rows if p.role == pk.Role.DECODE else min(p.rows, self.buckets.get("max_seqs", 64))
+                                                    for p in pkt.programs), self.spec.vocab, dtype=F32, device=dev)
+                    self.static[h] = self.d_logits
+        # per-page scale upper bounds for fp8 latent caches (one per layer cache)
+        self.kv_smax: dict[int, torch.Tensor] = {}
+        self._mla_derived: dict[int, tuple] = {}
+        self._mla_ws = None
+
+    # ---- program preparation -------------------------------------------------------------------
+    def _prepare(self, idx: int) -> _Prog:
+        if idx in self.progs:
+            return self.progs[idx]
+        prog = self.packet.programs[idx]
+        st = _Prog()
+        dev = self.device
+        rows = prog.rows
+        samples = rows if prog.role == pk.Role.DECODE else max(1, min(rows, self.buckets.get("max_seqs", 64)))
+        st.rows, st.samples, st.role = rows, samples, prog.role
+        arena = torch.empty(max(prog.arena_bytes, 256), dtype=torch.uint8, device=dev)
+        st.arena = arena
+        for h, t in enumerate(self.packet.tensors):
+            if t.tclass == pk.TClass.ACT and prog.actmap[h] != pk.U64_MAX:
+                dims = [rows if d == -1 else samples if d == -2 else int(d) for d in t.dims]
+                dt = _TORCH_DT[pk.DType(t.dtype)]
+                n = int(np.prod(dims)) * torch.empty((), dtype=dt).element_size()
+                st.t[h] = arena[prog.actmap[h]:prog.actmap[h] + n].view(dt).view(dims)
+        # which activations feed an e4m3 GEMM: their producer emits the quantised twin in the same pass
+        for ins in prog.insts:
+            if ins.op in (Op.GEMM, Op.GEMM_XREDUCE) and ins.i[2] & pk.GEMM_FP8_BLOCK:
+                st.needs_q.add((ins.t[1], ins.i[6], ins.i[1]))      # (handle, col offset, K)
+            if ins.op == Op.MOE_GEMM and self.spec.weight_quant == "fp8_block128":
+                st.needs_q.add((ins.t[1], 0, self.spec.hidden))
+        self.progs[idx] = st
+        return st
+
+    def tensor(self, st: _Prog, h: int):
+        if h == pk.T_NONE:
+            return None
+        return st.t[h] if h in st.t else self.static[h]
+
+    # ---- op handlers ---------------------------------------------------------------------------
+    def _wants_q(self, st, h, co=0):
+        return any(k[0] == h and k[1] == co for k in st.needs_q)
+
+    def _quant_of(self, st, h, co, K, x):
+        """e4m3 twin of activation columns [co, co+K) of handle h (made on demand if the producer did not)."""
+        key = (h, co)
+        if key not in st.q:
+            xin = x if (co == 0 and x.shape[1] == K) else x[:, co:co + K]
+            st.q[key] = rowops.quant_act(xin) if xin.is_contiguous() else rowops.quant_act(xin.contiguous())
+        return st.q[key]
+
+    def _op_embed(self, st, ins):
+        native.call("plow_embed", self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1]), self.tensor(st, ins.t[2]),
+                    st.rows, ins.i[0], float(ins.f[0]))
+
+    def _norm_common(self, st, out_h, fn):
+        want = self._wants_q(st, out_h)
+        res = fn(want)
+        if want:
+            st.q[(out_h, 0)] = (res[-2], res[-1])
+
+    def _op_rmsnorm(self, st, ins):
+        out, x, g = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1]), self.tensor(st, ins.t[2])
+        W, co = ins.i[0], ins.i[6]
+        R = out.shape[0]
+        want = self._wants_q(st, ins.t[0]) and W % 128 == 0
+        xq = sx = None
+        if want:
+            xq = torch.empty(R, W, dtype=FP8, device=self.device)
+            sx = torch.empty(W // 128, R, dtype=F32, device=self.device)
+            st.q[(ins.t[0], 0)] = (xq, sx)
+        xin = x if co == 0 else x[:, co:]
+        native.call("plow_rmsnorm", out, xq, sx, R, xin, g, R, W, x.stride(0), float(ins.f[0]), int(ins.i[1]))
+
+    def _op_add_norm(self, st, ins):
+        h_out, x_in, delta, g, x_out = (self.tensor(st, ins.t[k]) for k in range(5))
+        R, W = h_out.shape
+        want = self._wants_q(st, ins.t[0]) and W % 128 == 0
+        xq = sx = None
+        if want:
+            xq = torch.empty(R, W, dtype=FP8, device=self.device)
+            sx = torch.empty(W // 128, R, dtype=F32, device=self.device)
+            st.q[(ins.t[0], 0)] = (xq, sx)
+        native.call("plow_add_norm", h_out, xq, sx, R, x_out, x_in, delta, g, R, W, float(ins.f[0]), int(ins.i[1]))
+
+    def _op_residual(self, st, ins):
+        out, a, b = (self.tensor(st, ins.t[k]) for k in range(3))
+        torch.add(a, b, out=out)
+
+    def _op_gemm(self, st, ins):
+        y, x = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])
+        N, K, flags, swap, bn, co = ins.i[0], ins.i[1], ins.i[2], ins.i[3], ins.i[4], ins.i[6]
+        dual = bool(flags & pk.GEMM_DUAL_SILU)
+        M = y.shape[0]
+        if flags & pk.GEMM_FP8_BLOCK:
+            wq, sw = self.static_q[ins.t[2]]
+            xq, sx = self._quant_of(st, ins.t[1], co, K, x)
+            want = self._wants_q(st, ins.t[0]) and (swap or bn == 128) and N % 128 == 0
+            if want:
+                # SwiGLU / projection result re-quantised in the GEMM epilogue for the next e4m3 GEMM
+                yq, syq = gemm_ops.gemm(xq[:M], wq, sx=sx, sw=sw, dual=dual, n_out=N, swap=bool(swap), bn=bn, quant_out=True)
+                st.q[(ins.t[0], 0)] = (yq, syq)
+                # the bf16 value is still part of the program's dataflow when another op reads it
+                if self._bf16_needed(st, ins.t[0]):
+                    gemm_ops.gemm(xq[:M], wq, sx=sx, sw=sw, dual=dual, n_out=N, swap=bool(swap), bn=bn, out=y)
+            else:
+                gemm_ops.gemm(xq[:M], wq, sx=sx, sw=sw, dual=dual, n_out=N, swap=bool(swap), bn=bn, out=y,
+                              out_f32=bool(flags & pk.GEMM_OUT_F32))
+        else:
+            w = self.static[ins.t[2]]
+            xin = x if co == 0 and x.shape[1] == K else x[:, co:co + K]
+            if w.dtype != BF16:
+                w = self._bf16_weight(ins.t[2])
+            gemm_ops.gemm(xin, w, dual=dual, n_out=N, swap=bool(swap), bn=min(bn, 128) if swap else bn, out=y,
+                          out_f32=bool(flags & pk.GEMM_OUT_F32))
+
+    def _bf16_weight(self, h):
+        key = ("bf16", h)
+        if key not in self.static:
+            self.static[key] = self.static[h].to(BF16)
+        return self.static[key]
+
+    def _bf16_needed(self, st, h) -> bool:
+        prog = st.prog
+        for ins in prog.insts:
+            reads = ins.t[1:]
+            if h in reads:
+                if ins.op in (Op.GEMM, Op.GEMM_XREDUCE) and ins.i[2] & pk.GEMM_FP8_BLOCK and ins.t[1] == h:
+                    continue
+                return True
+        return False
+
+    def _op_row_gather(self, st, ins):
+        out, x, rows = (self.tensor(st, ins.t[k]) for k in range(3))
+        native.call("plow_row_gather", out, x, rows, st.samples, ins.i[0])
+
+    def _op_argmax(self, st, ins):
+        out, lg = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])
+        native.call("plow_argmax", out, lg, st.samples, ins.i[0])
+
+    # -- MLA
+    def _mla_prep(self, layer: int, wkv_b_h: int, heads: int, kv_lora: int, nope: int, v_head: int):
+        """Per-head absorbed projections from kv_b_proj: W_uk^T [h][kv_lora][nope] and W_uv [h][v][kv_lora]."""
+        if layer not in self._mla_derived:
+            w = self.static[wkv_b_h] if wkv_b_h in self.static else quant.dequant_weight_128x128(*self.static_q[wkv_b_h]).to(BF16)
+            w3 = w.view(heads, nope + v_head, kv_lora)
+            wuk_t = w3[:, :nope, :].transpose(1, 2).contiguous().view(heads * kv_lora, nope).to(BF16)
+            wuv = w3[:, nope:, :].contiguous().view(heads * v_head, kv_lora).to(BF16)
+            self._mla_derived[layer] = (wuk_t, wuv)
+        return self._mla_derived[layer]
+
+    def _op_mla_kv_write(self, st, ins):
+        fp8 = self.spec.kv_dtype == "fp8"
+        if not fp8:
+            raise EngineError("bf16 latent cache has no sm_100a body yet; compile with plow_kv_dtype=fp8")
+        cache, scale, kva, gamma, rope = (self.tensor(st, ins.t[k]) for k in range(5))
+        layer = ins.i[7]
+        if layer not in self.kv_smax:
+            self.kv_smax[layer] = torch.zeros(cache.shape[0], 4, dtype=F32, device=self.device)
+        mla_ops.kv_write(cache, scale, self.kv_smax[layer], kva, ins.i[5], gamma, rope, self.d_in[1], self.d_in[2],
+                         self.d_page_table, ins.i[0], ins.i[1], float(ins.f[0]), ins.i[2])
+
+    def _op_mla_attention(self, st, ins):
+        ao, q, rope, _pos, wkv_b = (self.tensor(st, ins.t[k]) for k in range(5))
+        cache, scale = self.tensor(st, ins.t[5]), self.tensor(st, ins.t[6])
+        heads, kv_lora, nope, qk_rope, v_head, pair = ins.i[0], ins.i[1], ins.i[2], ins.i[3], ins.i[4], ins.i[5]
+        layer = ins.i[7]
+        if heads != 128 or kv_lora != 512 or qk_rope != 64:
+            raise EngineError("the sm_100a MLA kernel is specialised for 128 heads, 512 latent and 64 rope dims per rank")
+        T = st.rows
+        wuk_t, wuv = self._mla_prep(layer, ins.t[4], heads, kv_lora, nope, v_head)
+        q_nope_t, q_rope = mla_ops.q_prep(q, rope, self.d_in[1], heads, nope, qk_rope, pair)
+        off = st.scratch.setdefault("head_off", (torch.arange(heads + 1, dtype=I32, device=self.device) * T))
+        q_abs = gemm_ops.gemm(q_nope_t.view(heads * T, nope), wuk_t, n_experts=heads, n_out=kv_lora, grp_off=off,
+                              swap=True, bn=gemm_ops._pick_bn_swap(T, False, False), rows_hint=T)
+        q8, sq = mla_ops.q_quant(q_abs.view(heads, T, kv_lora), q_rope)
+        if self._mla_ws is None or self._mla_ws.opart.shape[0] < T:
+            self._mla_ws = mla_ops.DecodeWorkspace(max(T, self.max_rows_all), self.max_ctx + PAGE, device=self.device)
+        oacc = mla_ops.decode(q8, sq, cache, scale, self.kv_smax[layer], self.d_page_table, self.d_in[2], self.d_kvlen_row,
+                              self._mla_ws, float(ins.f[0]))
+        tp = None
+        if T > 128:
+            tiles = st.scratch.setdefault("head_tiles", (torch.arange(heads + 1, dtype=I32, device=self.device) * ((T + 127) // 128)))
+            tp = tiles
+        o_h = gemm_ops.gemm(oacc.view(heads * T, kv_lora), wuv, n_experts=heads, n_out=v_head, grp_off=off, tile_prefix=tp,
+                            swap=T <= 128, bn=gemm_ops._pick_bn_swap(T, False, False) if T <= 128 else 128, rows_hint=T)
+        native.call("plow_head_to_token", ao, o_h, T, heads, v_head)
+
+    # -- MoE
+    def _op_router_topk(self, st, ins):
+        table, logits = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])
+        bias = self.tensor(st, ins.t[2]) if ins.t[2] != pk.T_NONE else None
+        native.call("plow_router_topk", table, logits, bias, st.rows, ins.i[0], ins.i[1], max(1, ins.i[2]), max(1, ins.i[3]),
+                    ins.i[4], ins.i[5], float(ins.f[0]))
+
+    def _op_moe_experts(self, st, ins):
+        y, h, table = (self.tensor(st, ins.t[k]) for k in range(3))
+        shared = self.tensor(st, ins.t[5]) if ins.t[5] != pk.T_NONE else None
+        E, e_local, k, F, ep = ins.i[0], ins.i[1], ins.i[2], ins.i[3], max(1, ins.i[4])
+        T, H = st.rows, self.spec.hidden
+        fp8 = self.spec.weight_quant == "fp8_block128"
+        if self.comm is not None and ep > 1:
+            return self.comm.moe_experts(self, st, ins)
+        e_base = self.rank * e_local if ep > 1 else 0
+        grp_off, tile_prefix, row_of_pair, pair_of_row = rowops.moe_align(table, e_base, e_local)
+        per = max(1, (T * k + e_local - 1) // e_local)
+        swap = per <= 64
+        if fp8:
+            xq, sx = self._quant_of(st, ins.t[1], 0, H, h)
+            xs, sxs = rowops.moe_gather(xq, sx, pair_of_row, grp_off[e_local:], T * k, k)
+            w1, s1 = self.static_q[ins.t[3]]
+            w2, s2 = self.static_q[ins.t[4]]
+            if swap:
+                bn = 32 if per <= 32 else 64
+                hq, shq = gemm_ops.gemm(xs, w1, sx=sxs, sw=s1, dual=True, n_out=F, n_experts=e_local, grp_off=grp_off,
+                                        swap=True, bn=bn, quant_out=True, ld_syq=T * k)
+                yo = gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=e_local, grp_off=grp_off, swap=True, bn=bn)
+            else:
+                hb = gemm_ops.gemm(xs, w1, sx=sxs, sw=s1, dual=True, n_out=F, n_experts=e_local, grp_off=grp_off,
+                                   tile_prefix=tile_prefix, swap=False, bn=64)
+                hq, shq = rowops.quant_act(hb)
+                yo = gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=e_local, grp_off=grp_off, tile_prefix=tile_prefix,
+                                   swap=False, bn=128)
+        else:
+            w1, w2 = self._bf16_weight(ins.t[3]), self._bf16_weight(ins.t[4])
+            xs = h[(pair_of_row // k).long().clamp_(0, T - 1)]
+            bn = 32 if per <= 32 else 64
+            hb = gemm_ops.gemm(xs, w1, dual=True, n_out=F, n_experts=e_local, grp_off=grp_off, tile_prefix=tile_prefix,
+                               swap=swap, bn=bn if swap else 128)
+            yo = gemm_ops.gemm(hb, w2, n_out=H, n_experts=e_local, grp_off=grp_off, tile_prefix=tile_prefix, swap=swap,
+                               bn=bn if swap else 128)
+        native.call("plow_moe_combine", y, yo, shared, table, row_of_pair, T, k, H)
+
+    HANDLERS = {
+        Op.EMBED: "_op_embed", Op.RMSNORM: "_op_rmsnorm", Op.ADD_NORM: "_op_add_norm", Op.RESIDUAL: "_op_residual",
+        Op.GEMM: "_op_gemm", Op.ROW_GATHER: "_op_row_gather", Op.ARGMAX: "_op_argmax",
+        Op.MLA_KV_WRITE: "_op_mla_kv_write", Op.MLA_DECODE: "_op_mla_attention", Op.MLA_PREFILL: "_op_mla_attention",
+        Op.ROUTER_TOPK: "_op_router_topk", Op.MOE_GEMM: "_op_moe_experts", Op.NOP: None,
+    }
+
+    def _run_insts(self, st: _Prog) -> None:
+        st.q.clear()
+        for ins in st.prog.insts:
+            name = self.HANDLERS.get(Op(ins.op), "missing")
+            if name is None:
+                continue
+            if name == "missing":
+                fn = getattr(self, "_ext_" + Op(ins.op).name.lower(), None)
+                if fn is None:
+                    raise EngineError(f"opcode {Op(ins.op).name} has no sm_100a body in this build")
+                fn(st, ins)
+            else:
+                getattr(self, name)(st, ins)
+
+    # ---- step ----------------------------------------------------------------------------------
+    def _sync_pages(self, slot: int) -> None:
+        super()._sync_pages(slot)
+        pages = self.pool.seqs[slot].pages
+        if pages:
+            self.d_page_table[slot, :len(pages)] = torch.tensor(pages, dtype=I32).to(self.device, non_blocking=True)
+
+    def step(self, batch: TokenBatch) -> StepResult:
+        rows, ns = batch.rows, int(batch.sample_rows.shape[0])
+        idx = self.pick_program(rows, batch.decode)
+        st = self._prepare(idx)
+        st.prog = self.packet.programs[idx]
+        R = st.rows
+        hin = self.h_in
+        hin[0, :rows] = torch.from_numpy(batch.ids)
+        hin[1, :rows] = torch.from_numpy(batch.pos)
+        hin[2, :rows] = torch.from_numpy(batch.seq)
+        hin[0, rows:R] = 0
+        hin[1, rows:R] = 0
+        hin[2, rows:R] = self.scratch_slot
+        hin[3, :ns] = torch.from_numpy(batch.sample_rows)
+        hin[3, ns:st.samples] = 0
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        self.d_in[:, :R].copy_(hin[:, :R], non_blocking=True)
+        torch.add(self.d_in[1, :R], 1, out=self.d_kvlen_row[:R])
+        try:
+            if self.cuda_graphs and batch.decode:
+                if st.graph is None:
+                    self._run_insts(st)                      # warm-up (allocations, attribute sets)
+                    torch.cuda.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        self._run_insts(st)
+                    st.graph = g
+                st.graph.replay()
+            else:
+                self._run_insts(st)
+            self.h_out[:st.samples].copy_(self.d_out_ids[:st.samples], non_blocking=True)
+            ev1.record()
+            ev1.synchronize()
+        except native.NativeLibraryError as e:
+            raise EngineError(str(e), fatal=False)
+        self.step_ms_last = ev0.elapsed_time(ev1)
+        native.check_status(self.device)
+        logits = self.d_logits[:ns].float().cpu().numpy() if batch.want_logits else None
+        return StepResult(ids=self.h_out[:ns].numpy().copy(), logits=logits, device_ms=self.step_ms_last)
