@@ -1,0 +1,236 @@
+// Expert-parallel token dispatch and combine over NVLink peer memory (one process per GPU).
+//
+// Every rank owns a symmetric region (same layout on all ranks, peers mapped into this address
+// space).  Per MoE layer:
+//   1. ep_counts   - histogram of this rank's (token, slot) pairs per expert, stored into every
+//                    peer's count matrix, then one release flag per peer.
+//   2. ep_push     - waits for all ranks' counts, derives the same global layout everywhere
+//                    (rows of an expert ordered by source rank), and writes each local pair's
+//                    quantised row + scales straight into the owning rank's expert-sorted
+//                    buffer (st over NVLink); one release add per CTA on the owner's arrival
+//                    counter.  The grouped expert GEMM of the owner waits on that counter from
+//                    inside the kernel (GemmArgs::wait_*), so no host or stream sync separates
+//                    dispatch from the expert GEMM.
+//   3. ep_y_ready  - after the down projection, a release flag to every peer.
+//   4. ep_combine  - each rank pulls its tokens' expert outputs from the owners' memory (ld over
+//                    NVLink) and forms shared + sum_j gate_j * y_j in fixed slot order, f32.
+// All flags are monotonic epochs kept in device memory, so the sequence can be replayed from a
+// CUDA graph.  Every wait is bounded by a deadline; on expiry the kernel records
+// PLOW_ERR_PEER_WAIT in the status word and returns, and the host fails the step.
+//
+// The reference's expert parallelism keeps whole experts per rank and combines with an
+// all-reduce (crates/devgen/src/mla.rs:13016-13021, crates/packet/src/moe_ep.rs); its flag
+// protocol (release store per peer, relaxed polling with a deadline, status line) is
+// runtime/nvidia/op_collective.cuh:216-240.  Plain peer loads/stores only: no multimem and no
+// TMA multicast anywhere in this file.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace {
+using namespace plow;
+
+struct EpLayout {         // byte offsets inside the symmetric region (identical on all ranks)
+  uint64_t cnt_all;       // int32 [W][E]
+  uint64_t cnt_flag;      // u32 [W] (stride 32 words)
+  uint64_t data_ctr;      // u32
+  uint64_t y_flag;        // u32 [W] (stride 32 words)
+  uint64_t recv_x;        // u8  [Rmax][H]
+  uint64_t recv_sx;       // f32 [H/128][Rmax]
+  uint64_t y;             // bf16 [Rmax][H]
+};
+
+struct EpArgs {
+  uint8_t* peer[8];
+  EpLayout L;
+  int W, me, E, e_local, Rmax, H;
+  uint32_t* epoch;        // device word: layer-call counter (monotonic)
+  int* status;
+  unsigned long long deadline_ns;
+};
+
+__device__ __forceinline__ bool wait_ge(const uint32_t* p, uint32_t target, unsigned long long deadline_ns) {
+  const unsigned long long t0 = globaltimer_ns();
+  while (ld_acquire_sys(p) < target) {
+    if (globaltimer_ns() - t0 > deadline_ns) return false;
+    __nanosleep(64);
+  }
+  return true;
+}
+
+__global__ void ep_counts_kernel(EpArgs a, const int2* table, int n_pairs, int* cursor) {
+  extern __shared__ int hist[];
+  for (int e = threadIdx.x; e < a.E; e += blockDim.x) { hist[e] = 0; cursor[e] = 0; }
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&hist[table[p].x], 1);
+  __syncthreads();
+  const uint32_t ep = *a.epoch + 1;
+  for (int d = 0; d < a.W; ++d) {
+    int* dst = reinterpret_cast<int*>(a.peer[d] + a.L.cnt_all) + a.me * a.E;
+    for (int e = threadIdx.x; e < a.E; e += blockDim.x) dst[e] = hist[e];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < a.W)
+    st_release_sys(reinterpret_cast<uint32_t*>(a.peer[threadIdx.x] + a.L.cnt_flag) + a.me * 32, ep);
+  if (threadIdx.x == 0) *a.epoch = ep;
+}
+
+// grid: any; 256 threads.  One warp per pair.
+__global__ void ep_push_kernel(EpArgs a, const int2* table, int n_pairs, int top_k, const uint8_t* xq, const float* sx,
+                               int ld_sx, int* cursor, int* grp_off, int* tile_prefix, int* pair_dest) {
+  extern __shared__ int sm[];                 // cnt [W][E], base [E]
+  int* cnt = sm;
+  int* base = sm + a.W * a.E;
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  __syncthreads();
+  const uint32_t ep = *a.epoch;
+  if (threadIdx.x < a.W) {
+    if (!wait_ge(reinterpret_cast<const uint32_t*>(a.peer[a.me] + a.L.cnt_flag) + threadIdx.x * 32, ep, a.deadline_ns)) fail = 1;
+  }
+  __syncthreads();
+  if (fail) { if (threadIdx.x == 0) atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); return; }
+  const int* call = reinterpret_cast<const int*>(a.peer[a.me] + a.L.cnt_all);
+  for (int i = threadIdx.x; i < a.W * a.E; i += blockDim.x) cnt[i] = call[i];
+  __syncthreads();
+  // base[e] = first row, on the owner of e, of the rows this rank sends for expert e
+  for (int e = threadIdx.x; e < a.E; e += blockDim.x) {
+    const int e0 = (e / a.e_local) * a.e_local;
+    int off = 0;
+    for (int f = e0; f < e; ++f)
+      for (int s = 0; s < a.W; ++s) off += cnt[s * a.E + f];
+    for (int s = 0; s < a.me; ++s) off += cnt[s * a.E + e];
+    base[e] = off;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    int off = 0, tiles = 0;
+    for (int el = 0; el < a.e_local; ++el) {
+      const int e = a.me * a.e_local + el;
+      int c = 0;
+      for (int s = 0; s < a.W; ++s) c += cnt[s * a.E + e];
+      grp_off[el] = off; tile_prefix[el] = tiles;
+      off += c; tiles += (c + 127) >> 7;
+    }
+    grp_off[a.e_local] = off; tile_prefix[a.e_local] = tiles;
+    if (off > a.Rmax) atomicCAS(a.status, 0, PLOW_ERR_BOUNDS);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  const int KB = a.H / 128;
+  for (int p = blockIdx.x * wpb + warp; p < n_pairs; p += gridDim.x * wpb) {
+    const int e = table[p].x;
+    const int d = e / a.e_local;
+    int idx = 0;
+    if (lane == 0) idx = atomicAdd(&cursor[e], 1);
+    idx = __shfl_sync(0xffffffffu, idx, 0);
+    const int row = base[e] + idx;
+    if (row >= a.Rmax) { if (lane == 0) atomicCAS(a.status, 0, PLOW_ERR_BOUNDS); continue; }
+    const int tok = p / top_k;
+    const uint4* src = reinterpret_cast<const uint4*>(xq + static_cast<size_t>(tok) * a.H);
+    uint4* dst = reinterpret_cast<uint4*>(a.peer[d] + a.L.recv_x + static_cast<size_t>(row) * a.H);
+    for (int i = lane; i < a.H / 16; i += 32) dst[i] = src[i];
+    float* dsx = reinterpret_cast<float*>(a.peer[d] + a.L.recv_sx);
+    for (int kb = lane; kb < KB; kb += 32) dsx[static_cast<size_t>(kb) * a.Rmax + row] = sx[static_cast<size_t>(kb) * ld_sx + tok];
+    if (lane == 0) pair_dest[p] = (d << 24) | row;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < a.W) red_add_release_sys(reinterpret_cast<uint32_t*>(a.peer[threadIdx.x] + a.L.data_ctr), 1u);
+}
+
+__global__ void ep_y_ready_kernel(EpArgs a) {
+  __threadfence_system();
+  const uint32_t ep = *a.epoch;
+  if (threadIdx.x < a.W) st_release_sys(reinterpret_cast<uint32_t*>(a.peer[threadIdx.x] + a.L.y_flag) + a.me * 32, ep);
+}
+
+__global__ void ep_combine_kernel(EpArgs a, __nv_bfloat16* out, const __nv_bfloat16* shared, const int2* table,
+                                  const int* pair_dest, int top_k) {
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  __syncthreads();
+  const uint32_t ep = *a.epoch;
+  if (threadIdx.x < a.W) {
+    if (!wait_ge(reinterpret_cast<const uint32_t*>(a.peer[a.me] + a.L.y_flag) + threadIdx.x * 32, ep, a.deadline_ns)) fail = 1;
+  }
+  __syncthreads();
+  if (fail) { if (threadIdx.x == 0) atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); return; }
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x * 8; i < a.H; i += blockDim.x * 8) {
+    float acc[8];
+    if (shared) {
+      const uint4 v = *reinterpret_cast<const uint4*>(shared + static_cast<size_t>(t) * a.H + i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); acc[2 * j] = f.x; acc[2 * j + 1] = f.y; }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    }
+    for (int s = 0; s < top_k; ++s) {
+      const int pd = pair_dest[t * top_k + s];
+      const int d = pd >> 24, row = pd & 0xffffff;
+      const float g = __int_as_float(table[t * top_k + s].y);
+      const __nv_bfloat16* y = reinterpret_cast<const __nv_bfloat16*>(a.peer[d] + a.L.y);
+      const uint4 v = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(row) * a.H + i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); acc[2 * j] += g * f.x; acc[2 * j + 1] += g * f.y; }
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * a.H + i) = o;
+  }
+}
+
+// A wait that nothing satisfies: used by the failure-detection test to exercise the deadline path
+// without faulting or hanging anything.
+__global__ void ep_wait_probe_kernel(const uint32_t* flag, uint32_t target, unsigned long long deadline_ns, int* status) {
+  if (threadIdx.x == 0 && !wait_ge(flag, target, deadline_ns)) atomicCAS(status, 0, PLOW_ERR_PEER_WAIT);
+}
+
+inline int ok() { cudaError_t e = cudaGetLastError(); return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e); }
+
+}  // namespace
+
+extern "C" {
+
+// `args` is a host copy of EpArgs laid out as: 8 peer pointers, 7 u64 layout offsets, 6 ints (W, me, E, e_local, Rmax, H),
+// epoch pointer, status pointer, u64 deadline (see plow_b200/parallel/ep.py for the ctypes mirror).
+int plow_ep_counts(const void* args, const void* table, int n_pairs, int* cursor, void* st) {
+  const EpArgs& a = *static_cast<const EpArgs*>(args);
+  ep_counts_kernel<<<1, 1024, a.E * 4, reinterpret_cast<cudaStream_t>(st)>>>(a, static_cast<const int2*>(table), n_pairs, cursor);
+  return ok();
+}
+int plow_ep_push(const void* args, const void* table, int n_pairs, int top_k, const void* xq, const float* sx, int ld_sx,
+                 int* cursor, int* grp_off, int* tile_prefix, int* pair_dest, int n_cta, void* st) {
+  const EpArgs& a = *static_cast<const EpArgs*>(args);
+  ep_push_kernel<<<n_cta, 256, (a.W + 1) * a.E * 4, reinterpret_cast<cudaStream_t>(st)>>>(
+      a, static_cast<const int2*>(table), n_pairs, top_k, static_cast<const uint8_t*>(xq), sx, ld_sx, cursor, grp_off,
+      tile_prefix, pair_dest);
+  return ok();
+}
+int plow_ep_y_ready(const void* args, void* st) {
+  const EpArgs& a = *static_cast<const EpArgs*>(args);
+  ep_y_ready_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(st)>>>(a);
+  return ok();
+}
+int plow_ep_combine(const void* args, void* out, const void* shared, const void* table, const int* pair_dest, int T, int top_k,
+                    void* st) {
+  const EpArgs& a = *static_cast<const EpArgs*>(args);
+  ep_combine_kernel<<<T, 256, 0, reinterpret_cast<cudaStream_t>(st)>>>(a, static_cast<__nv_bfloat16*>(out),
+                                                                    static_cast<const __nv_bfloat16*>(shared),
+                                                                    static_cast<const int2*>(table), pair_dest, top_k);
+  return ok();
+}
+int plow_wait_probe(const void* flag, unsigned int target, unsigned long long deadline_ns, int* status, void* st) {
+  ep_wait_probe_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(st)>>>(static_cast<const uint32_t*>(flag), target, deadline_ns, status);
+  return ok();
+}
+
+}  // extern "C"

@@ -27,6 +27,10 @@ typedef struct PlowGemmDesc {
   int32_t bn;             // UMMA N tile (tokens when swap, features otherwise)
   int32_t out_f32;
   float out_scale;
+  const void* wait_ctr;   // optional arrival gate: start once *wait_ctr >= *wait_epoch * wait_mult
+  const void* wait_epoch;
+  int32_t wait_mult;
+  int32_t wait_deadline_ms;
 } PlowGemmDesc;
 
 // Launches on `stream` (a cudaStream_t).  Returns 0, or a host-side error code (<0 bad

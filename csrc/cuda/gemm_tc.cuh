@@ -42,6 +42,12 @@ struct GemmArgs {
   const int* grp_off;    // grouped: [E+1] row offsets into x (device memory)
   const int* tile_prefix;// grouped, non-swap: [E+1] prefix of 128-row tile counts
   int* status;           // device status word (0 = ok)
+  // optional arrival gate (expert-parallel dispatch): rows of x are written by peer GPUs; the
+  // kernel starts reading them once *wait_ctr >= *wait_epoch * wait_mult (bounded wait)
+  const uint32_t* wait_ctr;
+  const uint32_t* wait_epoch;
+  uint32_t wait_mult;
+  uint32_t wait_deadline_ms;
   int M;                 // rows of x (upper bound when grouped)
   int N;                 // output features per expert
   int K;
@@ -203,6 +209,19 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
       Tile t;
       uint32_t it = 0;
       bool ok = true;
+      if (a.wait_ctr) {
+        // peers write the token rows with generic stores; after the acquire the async proxy (TMA)
+        // must be ordered behind it too
+        const uint32_t target = *a.wait_epoch * a.wait_mult;
+        const unsigned long long t0 = globaltimer_ns();
+        while (ld_acquire_sys(a.wait_ctr) < target) {
+          if (globaltimer_ns() - t0 > static_cast<unsigned long long>(a.wait_deadline_ms) * 1000000ull) {
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); ok = false; break;
+          }
+          __nanosleep(64);
+        }
+        fence_proxy_async_all();
+      }
       while (ok && sched.next(t)) {
         const int p_row = SWAP ? t.wrow0 : t.tok0;
         const int q_row = SWAP ? t.tok0 : t.wrow0;
@@ -288,6 +307,20 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
     constexpr int kAccRegs = FP8 ? kAccCols : 1;
     float acc[kAccRegs];
     const __nv_bfloat16* resid = reinterpret_cast<const __nv_bfloat16*>(a.residual);
+    if (a.wait_ctr) {
+      if (lane == 0) {
+        const uint32_t target = *a.wait_epoch * a.wait_mult;
+        const unsigned long long t0 = globaltimer_ns();
+        while (ld_acquire_sys(a.wait_ctr) < target && !*abort_flag) {
+          if (globaltimer_ns() - t0 > static_cast<unsigned long long>(a.wait_deadline_ms) * 1000000ull) {
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); break;
+          }
+          __nanosleep(64);
+        }
+      }
+      __syncwarp();
+      if (*abort_flag) ok = false;
+    }
     while (ok && sched.next(t)) {
       const int tok_i = t.tok0 + li;       // non-swap: this thread's token
       const int feat_i = t.feat0 + li;     // swap: this thread's feature

@@ -31,14 +31,16 @@ def _pick_bn_swap(rows: int, fp8: bool, dual: bool) -> int:
 
 def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=None,
          grp_off=None, tile_prefix=None, n_experts=0, swap=None, bn=None, out_f32=False,
-         out_scale=1.0, quant_out=False, rows_hint=None, ld_syq=None):
+         out_scale=1.0, quant_out=False, rows_hint=None, ld_syq=None, wait=None, yq_out=None, syq_out=None):
     """y = x @ w.T with the epilogue options of the kernel.
 
     x [M, K] bf16 or e4m3; w [(E*)N(*2), K] same dtype.  ``dual`` computes silu(gate)*up with
     w = [gate; up] stacked per expert.  Grouped mode (``n_experts`` > 0): rows of x are sorted
     by expert and ``grp_off`` [E+1] int32 (device) gives the ranges.  ``quant_out`` returns
     (yq e4m3, syq transposed scales) instead of bf16.  ``rows_hint``: expected rows per expert
-    used to pick the token tile in grouped swap mode.
+    used to pick the token tile in grouped swap mode.  ``wait`` = (counter ptr, epoch ptr, multiplier,
+    deadline ms): the kernel starts reading x once ``*counter >= *epoch * multiplier`` (rows written by
+    peer GPUs during expert-parallel dispatch).
     """
     lib = native.cuda_lib()
     assert x.is_cuda and w.is_cuda and x.dim() == 2 and w.dim() == 2
@@ -60,9 +62,9 @@ def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=N
             bn = (64 if dual else 128) if fp8 else (128 if dual else (256 if N >= 2048 else 128))
     y = yq = syq = None
     if quant_out:
-        yq = torch.empty(M, N, dtype=torch.float8_e4m3fn, device=x.device)
+        yq = yq_out if yq_out is not None else torch.empty(M, N, dtype=torch.float8_e4m3fn, device=x.device)
         ld_syq = ld_syq or M
-        syq = torch.empty((N + 127) // 128, ld_syq, dtype=torch.float32, device=x.device)
+        syq = syq_out if syq_out is not None else torch.empty((N + 127) // 128, ld_syq, dtype=torch.float32, device=x.device)
     else:
         y = out if out is not None else torch.empty(
             M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
@@ -73,7 +75,10 @@ def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=N
         status=status.data_ptr(), M=M, N=N, K=K, ldx=x.stride(0), ldw=w.stride(0), ldy=N,
         ld_sx=(sx.stride(0) if sx is not None else 0), ld_syq=(ld_syq or 0), E=E, w_rows=w_rows,
         dtype=_FP8 if fp8 else _BF16, dual=int(dual), swap=int(swap), bn=int(bn),
-        out_f32=int(out_f32), out_scale=float(out_scale))
+        out_f32=int(out_f32), out_scale=float(out_scale),
+        wait_ctr=(wait[0] if wait else None), wait_epoch=(wait[1] if wait else None),
+        wait_mult=(int(wait[2]) if wait else 0), wait_deadline_ms=(int(wait[3]) if wait else 0))
+    native.LAUNCHES["n"] += 1
     rc = lib.plow_gemm(C.byref(d), native.stream_ptr())
     if rc != 0:
         raise native.NativeLibraryError(f"plow_gemm failed with code {rc} (bn={bn} swap={swap} dual={dual} fp8={fp8})")

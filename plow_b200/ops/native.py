@@ -30,6 +30,7 @@ class GemmDesc(C.Structure):
         ("w_rows", C.c_int64),
         ("dtype", C.c_int32), ("dual", C.c_int32), ("swap", C.c_int32), ("bn", C.c_int32),
         ("out_f32", C.c_int32), ("out_scale", C.c_float),
+        ("wait_ctr", C.c_void_p), ("wait_epoch", C.c_void_p), ("wait_mult", C.c_int32), ("wait_deadline_ms", C.c_int32),
     ]
 
 
@@ -109,8 +110,13 @@ _SIGS = {
     "plow_row_gather": "pppiip",
     "plow_head_to_token": "ppiiip",
     "plow_mla_decode": "ppppplpipp" "iiipppppfpp",
+    "plow_ep_counts": "ppipp",
+    "plow_ep_push": "ppiippippppip",
+    "plow_ep_y_ready": "pp",
+    "plow_ep_combine": "pppppiip",
+    "plow_wait_probe": "piLpp",
 }
-_CT = {"p": C.c_void_p, "i": C.c_int32, "l": C.c_int64, "f": C.c_float}
+_CT = {"p": C.c_void_p, "i": C.c_int32, "l": C.c_int64, "f": C.c_float, "L": C.c_uint64}
 
 
 def _arg(v):
@@ -121,9 +127,14 @@ def _arg(v):
     return v
 
 
+LAUNCHES = {"n": 0}                       # kernels launched through this module (bench bookkeeping)
+_KERNELS_PER_CALL = {"plow_mla_decode": 3}
+
+
 def call(name: str, *args) -> None:
     """Invoke a kernel launcher of libplow_cuda.so on the current stream (appended as last arg)."""
     lib = cuda_lib()
+    LAUNCHES["n"] += _KERNELS_PER_CALL.get(name, 1)
     fn = getattr(lib, name)
     if fn.argtypes is None:
         fn.argtypes = [_CT[c] for c in _SIGS[name]]
