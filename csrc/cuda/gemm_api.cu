@@ -12,6 +12,7 @@ GemmArgs to_args(const PlowGemmDesc& d) {
   a.yq = d.yq; a.syq = d.syq; a.grp_off = d.grp_off; a.tile_prefix = d.tile_prefix;
   a.status = d.status; a.M = d.M; a.N = d.N; a.K = d.K; a.ldy = d.ldy; a.ld_sx = d.ld_sx;
   a.ld_syq = d.ld_syq; a.E = d.E; a.out_f32 = d.out_f32; a.out_scale = d.out_scale;
+  a.ws = d.ws; a.ws_ctr = d.ws_ctr; a.splits = (d.swap && d.E == 0 && d.ws && d.ws_ctr) ? d.splits : 1;
   a.wait_ctr = static_cast<const uint32_t*>(d.wait_ctr); a.wait_epoch = static_cast<const uint32_t*>(d.wait_epoch);
   a.wait_mult = static_cast<uint32_t>(d.wait_mult); a.wait_deadline_ms = static_cast<uint32_t>(d.wait_deadline_ms);
   return a;

@@ -27,6 +27,10 @@ typedef struct PlowGemmDesc {
   int32_t bn;             // UMMA N tile (tokens when swap, features otherwise)
   int32_t out_f32;
   float out_scale;
+  float* ws;              // split-K workspace (fp32) and per-tile counters (zeroed once by the caller)
+  int32_t* ws_ctr;
+  int32_t splits;         // >1: split-K over CTAs (dense swap mode only)
+  int32_t ws_pad;
   const void* wait_ctr;   // optional arrival gate: start once *wait_ctr >= *wait_epoch * wait_mult
   const void* wait_epoch;
   int32_t wait_mult;

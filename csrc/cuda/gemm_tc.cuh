@@ -44,6 +44,12 @@ struct GemmArgs {
   int* status;           // device status word (0 = ok)
   // optional arrival gate (expert-parallel dispatch): rows of x are written by peer GPUs; the
   // kernel starts reading them once *wait_ctr >= *wait_epoch * wait_mult (bounded wait)
+  // split-K (dense swap mode): each tile is cut into `splits` K ranges run by different CTAs;
+  // partials go to `ws` (fp32, [tile][split][128 lanes][cols]) and the CTA that arrives last on the
+  // tile's counter sums them in split order and runs the epilogue (no CTA ever waits for another)
+  float* ws;
+  int* ws_ctr;
+  int splits;
   const uint32_t* wait_ctr;
   const uint32_t* wait_epoch;
   uint32_t wait_mult;
@@ -85,6 +91,8 @@ struct Tile {
   int tok0, tok_end;  // token rows (TMA coordinate, exclusive valid end)
   int wrow0;          // first weight row (absolute, in the stacked matrix)
   int feat0;          // first output feature of the tile within N
+  int kb0, kb1;       // K-block range of this work item
+  int tile_id, ks;    // split-K: output tile index and split index
 };
 
 template <int BN, bool DUAL, bool SWAP>
@@ -92,18 +100,29 @@ struct TileSched {
   const GemmArgs& a;
   int item, sub;
   int n_wt;  // weight tiles per expert
-  __device__ TileSched(const GemmArgs& a_) : a(a_), item(blockIdx.x), sub(0) {
+  int KB;
+  __device__ TileSched(const GemmArgs& a_, int KB_) : a(a_), item(blockIdx.x), sub(0), KB(KB_) {
     n_wt = SWAP ? (a.N + 127) / 128 : (a.N + BN - 1) / BN;
   }
   __device__ bool next(Tile& t) {
     const int nw_per = DUAL ? 2 * a.N : a.N;
+    t.kb0 = 0; t.kb1 = KB; t.tile_id = 0; t.ks = 0;
     if (a.E == 0) {
       const int n_tt = SWAP ? (a.M + BN - 1) / BN : (a.M + 127) / 128;
+      const int S = (SWAP && a.splits > 1) ? a.splits : 1;
       // token tile fastest when SWAP (few token tiles), weight-tile-major otherwise so CTAs
       // running at the same time share one weight tile in L2
-      if (item >= n_tt * n_wt) return false;
+      if (item >= n_tt * n_wt * S) return false;
       int tt, wt;
-      if (SWAP) { wt = item % n_wt; tt = item / n_wt; } else { tt = item % n_tt; wt = item / n_tt; }
+      int tile = item;
+      if (S > 1) {
+        tile = item / S;
+        t.ks = item % S;
+        t.kb0 = t.ks * KB / S;
+        t.kb1 = (t.ks + 1) * KB / S;
+        t.tile_id = tile;
+      }
+      if (SWAP) { wt = tile % n_wt; tt = tile / n_wt; } else { tt = tile % n_tt; wt = tile / n_tt; }
       t.tok0 = tt * (SWAP ? BN : 128);
       t.tok_end = a.M;
       t.feat0 = wt * (SWAP ? 128 : BN);
@@ -205,7 +224,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (elect_one()) {
-      TileSched<BN, DUAL, SWAP> sched(a);
+      TileSched<BN, DUAL, SWAP> sched(a, KB);
       Tile t;
       uint32_t it = 0;
       bool ok = true;
@@ -225,7 +244,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
       while (ok && sched.next(t)) {
         const int p_row = SWAP ? t.wrow0 : t.tok0;
         const int q_row = SWAP ? t.tok0 : t.wrow0;
-        for (int kb = 0; kb < KB; ++kb, ++it) {
+        for (int kb = t.kb0; kb < t.kb1; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) {
@@ -245,17 +264,17 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      TileSched<BN, DUAL, SWAP> sched(a);
+      TileSched<BN, DUAL, SWAP> sched(a, KB);
       Tile t;
       const uint32_t idesc = umma_idesc(128, kUmmaN, FP8 ? 0u : 1u, FP8 ? 0u : 1u);
       uint32_t it = 0;      // stage counter
       uint32_t accit = 0;   // accumulator-buffer counter (per tile for bf16, per K block for fp8)
       bool ok = true;
       while (ok && sched.next(t)) {
-        for (int kb = 0; kb < KB; ++kb, ++it) {
+        for (int kb = t.kb0; kb < t.kb1; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
-          if (FP8 || kb == 0) {
+          if (FP8 || kb == t.kb0) {
             const int b = accit % kNBuf;
             if (!mbar_wait(&acc_empty[b], ((accit / kNBuf) & 1) ^ 1, abort_flag)) {
               *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_FREE_WAIT); ok = false; break;
@@ -273,7 +292,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           const uint64_t qdesc = umma_desc_k128(sq);
 #pragma unroll
           for (int k4 = 0; k4 < 128 / (kUmmaK * (FP8 ? 1 : 2)); ++k4) {
-            const uint32_t acc = FP8 ? (k4 > 0) : (kb > 0 || k4 > 0);
+            const uint32_t acc = FP8 ? (k4 > 0) : (kb > t.kb0 || k4 > 0);
             const uint64_t adv = static_cast<uint64_t>(k4 * 2);  // 32 bytes >> 4
             if (FP8) {
               tc_mma_f8(d0, pdesc + adv, qdesc + adv, idesc, acc);
@@ -286,7 +305,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             }
           }
           tc_commit(&empty_bar[s]);
-          if (FP8 || kb == KB - 1) { tc_commit(&acc_full[accit % kNBuf]); ++accit; }
+          if (FP8 || kb == t.kb1 - 1) { tc_commit(&acc_full[accit % kNBuf]); ++accit; }
         }
       }
       if (!ok) {  // drain whatever was issued before giving up
@@ -299,7 +318,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
     const int lq = warp & 3;               // TMEM lane quarter this warp may read
     const int li = lq * 32 + lane;         // lane (row of D) owned by this thread
     const uint32_t lane_addr = static_cast<uint32_t>(lq * 32) << 16;
-    TileSched<BN, DUAL, SWAP> sched(a);
+    TileSched<BN, DUAL, SWAP> sched(a, KB);
     Tile t;
     uint32_t accit = 0;
     uint32_t xchg_it = 0;
@@ -344,9 +363,9 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           if constexpr (DUAL) o.wu = a.sw[static_cast<size_t>(wblk_u) * KB + kb];
         };
         Sc s0, s1, s2;
-        fetch(0, s0);
-        fetch(1, s1);
-        for (int kb = 0; kb < KB; ++kb, ++accit) {
+        fetch(t.kb0, s0);
+        fetch(t.kb0 + 1, s1);
+        for (int kb = t.kb0; kb < t.kb1; ++kb, ++accit) {
           fetch(kb + 2, s2);
           const int b = accit % kNBuf;
           if (!mbar_wait(&acc_full[b], (accit / kNBuf) & 1, abort_flag)) {
@@ -396,9 +415,79 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         tc_fence_after();
       }
       const uint32_t tb = tmem_base + lane_addr + (accit & 1) * kAccCols;
-      // result of 16 columns starting at c, before out_scale
-      auto load16 = [&](int c, float* r) {
+      // raw accumulator columns [c, c + 16) of the kAccCols (gate | up) columns
+      auto raw16 = [&](int c, float* r) {
         if constexpr (FP8) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = acc[c + j];
+        } else {
+          uint32_t g[16];
+          tmem_ld16(tb + c, g);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = __uint_as_float(g[j]);
+        }
+      };
+      // split-K: publish this CTA's partial, wait (bounded) until the tile's other splits have
+      // published theirs, then reduce and finish only this CTA's share of the token columns, so the
+      // reduction traffic is spread over all the CTAs of the tile.  All tiles x splits CTAs are
+      // resident at once (the launcher keeps the grid within one CTA per SM).
+      int col_lo = 0, col_hi = BN;
+      const float* ws_tile = nullptr;
+      if constexpr (SWAP) {
+        if (a.splits > 1 && a.E == 0) {
+          float4* wp = reinterpret_cast<float4*>(a.ws + ((static_cast<size_t>(t.tile_id) * a.splits + t.ks) * 128 + li) * kAccCols);
+#pragma unroll
+          for (int c = 0; c < kAccCols; c += 16) {
+            float r[16];
+            raw16(c, r);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wp[(c >> 2) + j] = make_float4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          }
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
+          if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) {
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
+          }
+          ++xchg_it;
+          uint32_t* ctr = reinterpret_cast<uint32_t*>(a.ws_ctr) + t.tile_id * 32;   // one counter per 128-byte line
+          if (li == 0) red_add_release_gpu(ctr, 1u);
+          if (lane == 0) {
+            const unsigned long long t0 = globaltimer_ns();
+            while (ld_acquire_gpu(ctr) < static_cast<uint32_t>(a.splits)) {
+              if (*abort_flag || globaltimer_ns() - t0 > kWaitDeadlineNs) {
+                *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_GRID_WAIT); break;
+              }
+              __nanosleep(32);
+            }
+          }
+          __syncwarp();
+          if (*abort_flag) { ok = false; break; }
+          col_lo = t.ks * BN / a.splits;
+          col_hi = (t.ks + 1) * BN / a.splits;
+          ws_tile = a.ws + (static_cast<size_t>(t.tile_id) * a.splits * 128 + li) * kAccCols;
+        }
+      }
+      // result of 16 columns starting at c (gate/up folded, out_scale applied)
+      auto load16 = [&](int c, float* r) {
+        if (ws_tile) {
+          // partials are summed in split order (deterministic); loads of different splits are
+          // independent, so the reduction runs at L2 bandwidth
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float g = 0.f, u = 0.f;
+            if (c + j >= col_lo && c + j < col_hi) {
+#pragma unroll 8
+              for (int ks = 0; ks < a.splits; ++ks) {
+                const float* p = ws_tile + static_cast<size_t>(ks) * 128 * kAccCols;
+                g += __ldcg(p + c + j);
+                if constexpr (DUAL) u += __ldcg(p + BN + c + j);
+              }
+            }
+            r[j] = DUAL ? silu_f(g) * u : g;
+          }
+        } else if constexpr (FP8) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if constexpr (DUAL) r[j] = silu_f(acc[c + j]) * acc[BN + c + j];
@@ -429,12 +518,13 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
 #pragma unroll
         for (int c = 0; c < BN; c += 16) {
           if (t.tok0 + c >= t.tok_end) break;   // uniform across the CTA
+          if (c + 16 <= col_lo || c >= col_hi) continue;
           float r[16];
           load16(c, r);
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int tok = t.tok0 + c + j;
-            const bool ok_e = fok && tok < t.tok_end;
+            const bool ok_e = fok && tok < t.tok_end && c + j >= col_lo && c + j < col_hi;
             const size_t o = static_cast<size_t>(tok) * a.ldy + feat_i;
             if (ok_e && resid) r[j] += __bfloat162float(resid[o]);
             if (ok_e && a.y) {
@@ -465,7 +555,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
                                     fmaxf(scratch[32 + j], scratch[48 + j]));
               const float sc = fmaxf(m, 1e-10f) * (1.0f / 448.0f);
               const int tok = t.tok0 + c + j;
-              if (fok && tok < t.tok_end) {
+              if (fok && tok < t.tok_end && c + j >= col_lo && c + j < col_hi) {
                 reinterpret_cast<__nv_fp8_e4m3*>(a.yq)[static_cast<size_t>(tok) * a.ldy + feat_i] =
                     __nv_fp8_e4m3(r[j] / sc);
                 if (li == 0) a.syq[static_cast<size_t>(t.feat0 >> 7) * a.ld_syq + tok] = sc;
@@ -474,6 +564,19 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           }
         }
         if (!ok) break;
+        if (ws_tile) {
+          // the split that leaves last re-arms the tile's counters for the next launch
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
+          if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) {
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
+          }
+          ++xchg_it;
+          if (li == 0) {
+            int* done = a.ws_ctr + (256 + t.tile_id) * 32;
+            if (atomicAdd(done, 1) == a.splits - 1) { *done = 0; a.ws_ctr[t.tile_id * 32] = 0; __threadfence(); }
+          }
+        }
       } else {
         // thread = token, columns = features (contiguous in memory)
         const bool tok_ok = tok_i < t.tok_end;
@@ -599,7 +702,7 @@ int launch_gemm_tc(const GemmArgs& a, int ldx_elems, int ldw_elems, int64_t w_ro
   if (a.E == 0) {
     const int n_wt = SWAP ? (a.N + 127) / 128 : (a.N + BN - 1) / BN;
     const int n_tt = SWAP ? (a.M + BN - 1) / BN : (a.M + 127) / 128;
-    const long long tiles = static_cast<long long>(n_wt) * n_tt;
+    const long long tiles = static_cast<long long>(n_wt) * n_tt * (SWAP && a.splits > 1 ? a.splits : 1);
     if (tiles < grid) grid = static_cast<int>(tiles);
   }
   if (grid < 1) grid = 1;

@@ -30,6 +30,7 @@ class GemmDesc(C.Structure):
         ("w_rows", C.c_int64),
         ("dtype", C.c_int32), ("dual", C.c_int32), ("swap", C.c_int32), ("bn", C.c_int32),
         ("out_f32", C.c_int32), ("out_scale", C.c_float),
+        ("ws", C.c_void_p), ("ws_ctr", C.c_void_p), ("splits", C.c_int32), ("ws_pad", C.c_int32),
         ("wait_ctr", C.c_void_p), ("wait_epoch", C.c_void_p), ("wait_mult", C.c_int32), ("wait_deadline_ms", C.c_int32),
     ]
 

@@ -87,6 +87,20 @@ class EpComm:
         self.data_ctr_ptr = self.buf.data_ptr() + lay["data_ctr"]
 
     # ---- fused arm -----------------------------------------------------------------------------
+    def dispatch(self, eng, st, ins):
+        """Counts + push for the MoE instruction `ins`; called as soon as the routing table exists so
+        the transfer overlaps the shared-expert GEMMs that sit between router and experts."""
+        if self.impl != "fused":
+            return
+        h, table = eng.tensor(st, ins.t[1]), eng.tensor(st, ins.t[2])
+        T, k, H = st.rows, self.k, self.H
+        xq, sx = eng._quant_of(st, ins.t[1], 0, H, h)
+        ap = C.addressof(self.args)
+        native.call("plow_ep_counts", ap, table, T * k, self.cursor)
+        native.call("plow_ep_push", ap, table, T * k, k, xq, sx, sx.stride(0), self.cursor, self.grp_off, self.tile_prefix,
+                    self.pair_dest, self.n_cta)
+        st.scratch["ep_dispatched"] = ins.i[7]
+
     def moe_experts(self, eng, st, ins):
         if self.impl == "nccl":
             return self._moe_nccl(eng, st, ins)
@@ -94,11 +108,10 @@ class EpComm:
         shared = eng.tensor(st, ins.t[5]) if ins.t[5] != 0xFFFF else None
         F = ins.i[3]
         T, k, H = st.rows, self.k, self.H
-        xq, sx = eng._quant_of(st, ins.t[1], 0, H, h)
         ap = C.addressof(self.args)
-        native.call("plow_ep_counts", ap, table, T * k, self.cursor)
-        native.call("plow_ep_push", ap, table, T * k, k, xq, sx, sx.stride(0), self.cursor, self.grp_off, self.tile_prefix,
-                    self.pair_dest, self.n_cta)
+        if st.scratch.get("ep_dispatched") != ins.i[7]:
+            self.dispatch(eng, st, ins)
+        st.scratch["ep_dispatched"] = None
         w1, s1 = eng.static_q[ins.t[3]]
         w2, s2 = eng.static_q[ins.t[4]]
         wait = (self.data_ctr_ptr, self.epoch.data_ptr(), self.world * self.n_cta, self.deadline_ms)

@@ -385,6 +385,10 @@ class GpuEngine(EngineBase):
         bias = self.tensor(st, ins.t[2]) if ins.t[2] != pk.T_NONE else None
         native.call("plow_router_topk", table, logits, bias, st.rows, ins.i[0], ins.i[1], max(1, ins.i[2]), max(1, ins.i[3]),
                     ins.i[4], ins.i[5], float(ins.f[0]))
+        if self.comm is not None and self.ep > 1:
+            moe = next((m for m in st.prog.insts if m.op == Op.MOE_GEMM and m.t[2] == ins.t[0]), None)
+            if moe is not None:
+                self.comm.dispatch(self, st, moe)
 
     def _op_moe_experts(self, st, ins):
         y, h, table = (self.tensor(st, ins.t[k]) for k in range(3))

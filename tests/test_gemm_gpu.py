@@ -124,3 +124,26 @@ def test_quant_epilogue(m, swap, bn, fp8):
     assert _relerr(got, ref) < 6e-2   # e4m3 has 3 mantissa bits
     sref = ref.view(m, n // 128, 128).abs().amax(2).clamp_min(1e-10) / 448.0
     assert _relerr(syq[:, :m].t(), sref) < 2e-2
+
+
+@pytest.mark.parametrize("m,n,k,fp8,dual,splits", [(64, 256, 7168, True, False, 7), (64, 512, 2048, True, True, 4),
+                                                    (33, 384, 4096, False, False, 5), (64, 128, 7168, False, False, 28),
+                                                    (20, 256, 1024, False, True, 3)])
+def test_split_k(m, n, k, fp8, dual, splits):
+    from plow_b200.ops import gemm, native, quant
+    x, w = _mk(m, n, k, dual=dual)
+    if fp8:
+        xq, sx = quant.quant_act_1x128(x)
+        wq, sw = quant.quant_weight_128x128(w)
+        xr, wr = quant.dequant_act_1x128(xq, sx), quant.dequant_weight_128x128(wq, sw)
+    else:
+        xq, wq, sx, sw = x.bfloat16(), w.bfloat16(), None, None
+        xr, wr = xq.float(), wq.float()
+    ref = _ref(xr, wr, n, dual)
+    for _ in range(2):      # twice: the tile counters must have reset themselves
+        y = gemm.gemm(xq, wq, sx=sx, sw=sw, dual=dual, swap=True, bn=64, splits=splits, out_f32=True)
+        native.check_status()
+        assert _relerr(y, ref) < 2e-3
+    if fp8 or not dual:
+        yq, syq = gemm.gemm(xq, wq, sx=sx, sw=sw, dual=dual, swap=True, bn=64, splits=splits, quant_out=True)
+        assert _relerr(quant.dequant_act_1x128(yq, syq), ref) < 6e-2
