@@ -66,19 +66,26 @@ struct MlaArgs {
 // ---------------------------------------------------------------------------------------------
 __global__ void mla_build_items(const int* kvlen, int T, int tiles_per_split, int max_splits,
                                 MlaItem* items, int* n_items) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  int n = 0;
-  // longest splits first would balance better; requests are walked in order and splits are
-  // uniform, so the persistent grid's round-robin already spreads long requests
-  for (int r = 0; r < T; ++r) {
+  // one thread per request: split count, then its offset as the sum of the counts before it
+  extern __shared__ int cnt[];
+  for (int r = threadIdx.x; r < T; r += blockDim.x) {
     const int tiles = (kvlen[r] + kMlaPage - 1) / kMlaPage;
-    int split = 0;
-    for (int t0 = 0; t0 < tiles && split < max_splits; t0 += tiles_per_split, ++split) {
-      const int nt = (split == max_splits - 1) ? tiles - t0 : min(tiles_per_split, tiles - t0);
-      for (int half = 0; half < 2; ++half) items[n++] = MlaItem{r, half, split, t0, nt, 0, 0, 0};
-    }
+    int ns = (tiles + tiles_per_split - 1) / tiles_per_split;
+    cnt[r] = ns > max_splits ? max_splits : ns;
   }
-  *n_items = n;
+  __syncthreads();
+  for (int r = threadIdx.x; r < T; r += blockDim.x) {
+    int off = 0;
+    for (int q = 0; q < r; ++q) off += cnt[q];
+    const int tiles = (kvlen[r] + kMlaPage - 1) / kMlaPage;
+    for (int split = 0; split < cnt[r]; ++split) {
+      const int t0 = split * tiles_per_split;
+      const int nt = (split == max_splits - 1) ? tiles - t0 : min(tiles_per_split, tiles - t0);
+      items[2 * (off + split)] = MlaItem{r, 0, split, t0, nt, 0, 0, 0};
+      items[2 * (off + split) + 1] = MlaItem{r, 1, split, t0, nt, 0, 0, 0};
+    }
+    if (r == T - 1) *n_items = 2 * (off + cnt[r]);
+  }
 }
 
 __global__ void __launch_bounds__(kMlaThreads, 1)
@@ -496,7 +503,7 @@ int plow_mla_decode(const void* q8, const float* sq, const void* kv, const float
     if (cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem) != cudaSuccess) return 3000;
     attr = true;
   }
-  mla_build_items<<<1, 32, 0, stream>>>(kvlen, T, tiles_per_split, max_splits, static_cast<MlaItem*>(items), n_items);
+  mla_build_items<<<1, 256, T * sizeof(int), stream>>>(kvlen, T, tiles_per_split, max_splits, static_cast<MlaItem*>(items), n_items);
   MlaArgs a;
   a.q8 = static_cast<const uint8_t*>(q8); a.sq = sq; a.kv_scale = kv_scale; a.kv_smax = kv_smax; a.page_table = page_table; a.slot_of = slot_of; a.kvlen = kvlen;
   a.items = static_cast<const MlaItem*>(items); a.n_items = n_items;
@@ -507,8 +514,9 @@ int plow_mla_decode(const void* q8, const float* sq, const void* kv, const float
   const int cap = 2 * T * max_splits;
   if (cap < grid) grid = cap;
   mla_decode_kernel<<<grid, kMlaThreads, kMlaSmem, stream>>>(a, tqr, tkv, tkvr);
-  mla_merge_kernel<<<dim3(T, kMlaHeads), 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(opart), lse, kvlen, T,
-                                                          max_splits, tiles_per_split, static_cast<__nv_bfloat16*>(out));
+  if (out)   // NULL: the caller merges the splits itself (plow_mla_fold does it while folding W_uv)
+    mla_merge_kernel<<<dim3(T, kMlaHeads), 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(opart), lse, kvlen, T,
+                                                            max_splits, tiles_per_split, static_cast<__nv_bfloat16*>(out));
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }

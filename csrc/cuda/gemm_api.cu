@@ -6,8 +6,10 @@ namespace plow {
 int gemm_dispatch_bf16(const PlowGemmDesc& d, cudaStream_t s);
 int gemm_dispatch_fp8(const PlowGemmDesc& d, cudaStream_t s);
 
+static long long* g_gemm_trace = nullptr;
 GemmArgs to_args(const PlowGemmDesc& d) {
   GemmArgs a;
+  a.trace = g_gemm_trace;
   a.x = d.x; a.w = d.w; a.y = d.y; a.sx = d.sx; a.sw = d.sw; a.residual = d.residual;
   a.yq = d.yq; a.syq = d.syq; a.grp_off = d.grp_off; a.tile_prefix = d.tile_prefix;
   a.status = d.status; a.M = d.M; a.N = d.N; a.K = d.K; a.ldy = d.ldy; a.ld_sx = d.ld_sx;
@@ -18,6 +20,9 @@ GemmArgs to_args(const PlowGemmDesc& d) {
   return a;
 }
 }  // namespace plow
+
+// Debug aid: device buffer of 64*8 int64 that CTA 0 fills with clock64() phase stamps (NULL = off).
+extern "C" void plow_gemm_set_trace(void* p) { plow::g_gemm_trace = static_cast<long long*>(p); }
 
 extern "C" int plow_gemm(const PlowGemmDesc* d, void* stream) {
   if (!d || !d->x || !d->w || !d->status || (!d->y && !d->yq)) return -1;

@@ -50,6 +50,7 @@ struct GemmArgs {
   float* ws;
   int* ws_ctr;
   int splits;
+  long long* trace;       // optional clock64() phase stamps of CTA 0 (debug aid), NULL when off
   const uint32_t* wait_ctr;
   const uint32_t* wait_epoch;
   uint32_t wait_mult;
@@ -81,8 +82,8 @@ struct GemmCfg {
       kNBuf * kAccCols <= 32 ? 32 : kNBuf * kAccCols <= 64 ? 64 : kNBuf * kAccCols <= 128 ? 128
                                                    : kNBuf * kAccCols <= 256 ? 256 : 512;
   static constexpr int kStages =
-      (200 * 1024 / kStageBytes) > 10 ? 10 : (200 * 1024 / kStageBytes);
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 2048 /*bars+scratch*/;
+      (196 * 1024 / kStageBytes) > 10 ? 10 : (196 * 1024 / kStageBytes);
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 2048 /*bars+scratch*/ + 4096 /*scale factors*/;
   static_assert(kNBuf * kAccCols <= 512, "accumulators exceed TMEM");
   static_assert(kStages >= 2, "tile too large for shared memory");
 };
@@ -191,7 +192,8 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(xchg_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   volatile int* never_flag = abort_flag + 1;                     // stays 0
-  float* red_scratch = reinterpret_cast<float*>(ctrl + 512);     // [2][4][16] quant amax exchange
+  float* red_scratch = reinterpret_cast<float*>(ctrl + 512);     // [2][4][16] quant amax exchange (+ split-K flag)
+  float* fac_smem = reinterpret_cast<float*>(ctrl + 2048);       // [4 warps][256] fp8 block-scale factors
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -251,6 +253,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT); ok = false; break;
           }
           uint8_t* st = smem + s * Cfg::kStageBytes;
+          if (a.trace && blockIdx.x == 0 && it < 64) a.trace[it * 8 + 6] = clock64();
           mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
           const int kx = kb * kKElems;
           tma_load_2d(st, tm_p, kx, p_row, &full_bar[s]);
@@ -274,6 +277,8 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         for (int kb = t.kb0; kb < t.kb1; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
+          const bool tr = a.trace && blockIdx.x == 0 && it < 64;
+          if (tr) a.trace[it * 8 + 0] = clock64();
           if (FP8 || kb == t.kb0) {
             const int b = accit % kNBuf;
             if (!mbar_wait(&acc_empty[b], ((accit / kNBuf) & 1) ^ 1, abort_flag)) {
@@ -284,6 +289,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); ok = false; break;
           }
           tc_fence_after();
+          if (tr) a.trace[it * 8 + 1] = clock64();
           const int b = accit % kNBuf;
           const uint32_t d0 = tmem_base + b * kAccCols;
           const uint32_t sp = smem_u32(smem + s * Cfg::kStageBytes);
@@ -306,6 +312,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           }
           tc_commit(&empty_bar[s]);
           if (FP8 || kb == t.kb1 - 1) { tc_commit(&acc_full[accit % kNBuf]); ++accit; }
+          if (tr) a.trace[it * 8 + 2] = clock64();
         }
       }
       if (!ok) {  // drain whatever was issued before giving up
@@ -349,8 +356,10 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         const int wblk_g = t.wrow0 >> 7;
         const int wblk_u = (t.wrow0 + a.N) >> 7;
         // Scales are fetched two K blocks ahead so their latency hides behind the wait for
-        // the partial.  SWAP: lane l keeps the activation scales of tokens tok0 + l + 32 i
-        // and columns pick theirs up with a shuffle; otherwise each thread owns one token.
+        // the partial.  SWAP: lane l fetches the activation scales of tokens tok0 + l + 32 i; per
+        // K block the warp stages the BN combined factors (activation x weight scale) in its own
+        // slice of shared memory and every lane reads them back as broadcast float4s.  Otherwise
+        // each thread owns one token and needs a single factor.
         constexpr int kNS = SWAP ? (BN + 31) / 32 : 1;
         struct Sc { float sa[kNS]; float wg, wu; };
         auto fetch = [&](int kb, Sc& o) {
@@ -362,47 +371,63 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           o.wg = a.sw[static_cast<size_t>(wblk_g) * KB + kb];
           if constexpr (DUAL) o.wu = a.sw[static_cast<size_t>(wblk_u) * KB + kb];
         };
+        float* fw = fac_smem + (warp - 2) * 256;   // [gate BN | up BN] factors of this warp
         Sc s0, s1, s2;
         fetch(t.kb0, s0);
         fetch(t.kb0 + 1, s1);
         for (int kb = t.kb0; kb < t.kb1; ++kb, ++accit) {
           fetch(kb + 2, s2);
+          if constexpr (SWAP) {
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < kNS; ++i) {
+              fw[i * 32 + lane] = s0.sa[i] * s0.wg;
+              if constexpr (DUAL) fw[128 + i * 32 + lane] = s0.sa[i] * s0.wu;
+            }
+            __syncwarp();
+          }
           const int b = accit % kNBuf;
+          const bool tre = a.trace && blockIdx.x == 0 && warp == 2 && lane == 0 && accit < 64;
+          if (tre) a.trace[accit * 8 + 3] = clock64();
           if (!mbar_wait(&acc_full[b], (accit / kNBuf) & 1, abort_flag)) {
             *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
           }
           tc_fence_after();
+          if (tre) a.trace[accit * 8 + 4] = clock64();
           const uint32_t tb = tmem_base + lane_addr + b * kAccCols;
 #pragma unroll
-          for (int c = 0; c < BN; c += (DUAL ? 16 : 32)) {
-            uint32_t v0[16], v1[16];
-            tmem_ld16(tb + c, v0);
-            tmem_ld16(tb + (DUAL ? BN + c : c + 16), v1);
+          for (int c = 0; c < kAccCols; c += 64) {
+            // up to 64 columns per batch: all loads in flight, one wait
+            uint32_t v[64];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              if (c + q * 16 < kAccCols) tmem_ld16(tb + c + q * 16, v + q * 16);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if constexpr (DUAL) {
-                float sa;
-                if constexpr (SWAP) sa = __shfl_sync(0xffffffffu, s0.sa[(c + j) / 32], (c + j) & 31);
-                else sa = s0.sa[0];
-                acc[c + j] = fmaf(__uint_as_float(v0[j]), sa * s0.wg, acc[c + j]);
-                acc[BN + c + j] = fmaf(__uint_as_float(v1[j]), sa * s0.wu, acc[BN + c + j]);
-              } else {
-                float sa0, sa1;
-                if constexpr (SWAP) {
-                  sa0 = __shfl_sync(0xffffffffu, s0.sa[(c + j) / 32], (c + j) & 31);
-                  sa1 = __shfl_sync(0xffffffffu, s0.sa[(c + 16 + j) / 32], (c + 16 + j) & 31);
-                } else {
-                  sa0 = sa1 = s0.sa[0];
+            for (int q = 0; q < 4; ++q) {
+              if (c + q * 16 < kAccCols) {
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) {
+                  const int col = c + q * 16 + j;
+                  float4 f;
+                  if constexpr (SWAP) {
+                    f = *reinterpret_cast<const float4*>(fw + (col < BN ? col : 128 + col - BN));
+                  } else {
+                    const float fs = s0.sa[0] * ((DUAL && col >= BN) ? s0.wu : s0.wg);
+                    f = make_float4(fs, fs, fs, fs);
+                  }
+                  acc[col] = fmaf(__uint_as_float(v[q * 16 + j]), f.x, acc[col]);
+                  acc[col + 1] = fmaf(__uint_as_float(v[q * 16 + j + 1]), f.y, acc[col + 1]);
+                  acc[col + 2] = fmaf(__uint_as_float(v[q * 16 + j + 2]), f.z, acc[col + 2]);
+                  acc[col + 3] = fmaf(__uint_as_float(v[q * 16 + j + 3]), f.w, acc[col + 3]);
                 }
-                acc[c + j] = fmaf(__uint_as_float(v0[j]), sa0 * s0.wg, acc[c + j]);
-                acc[c + 16 + j] = fmaf(__uint_as_float(v1[j]), sa1 * s0.wg, acc[c + 16 + j]);
               }
             }
           }
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[b]);
+          if (tre) a.trace[accit * 8 + 5] = clock64();
           s0 = s1;
           s1 = s2;
         }

@@ -40,6 +40,26 @@ def kv_write(kv8, kv_scale, kv_smax, kva, col_ofs, gamma, rope_tab, pos, slot_of
                 page_table.shape[1], T, latent, rope, float(eps), pair_mode)
 
 
+def absorb(q, wuk_t, rope_tab, pos, heads, pair_mode=1):
+    """q [T, heads*192] bf16 -> (q8 e4m3 [heads][T][576], sq [heads][T]): W_uk absorb + RoPE + quantise, one kernel."""
+    T = q.shape[0]
+    q8 = torch.empty(heads, T, 576, dtype=FP8, device=q.device)
+    sq = torch.empty(heads, T, dtype=torch.float32, device=q.device)
+    native.call("plow_mla_absorb", q, q.stride(0), wuk_t, rope_tab, pos, q8, sq, T, heads, pair_mode, native.status_word(q.device))
+    return q8, sq
+
+
+def fold(ws, kvlen, wuv, T, heads, ao, want_fp8=False):
+    """Merge the decode splits, multiply by W_uv per head, write token-major [T, heads*128] (+ e4m3 twin)."""
+    aq = saq = None
+    if want_fp8:
+        aq = torch.empty(T, heads * 128, dtype=FP8, device=ao.device)
+        saq = torch.empty(heads, T, dtype=torch.float32, device=ao.device)
+    native.call("plow_mla_fold", ws.opart, ws.lse, kvlen, wuv, ao, aq, saq, T, T, heads, ws.max_splits, ws.tiles_per_split,
+                native.status_word(ao.device))
+    return aq, saq
+
+
 class DecodeWorkspace:
     """Scratch of the split-KV decode kernel, sized once for (max rows, max context)."""
 
@@ -52,12 +72,12 @@ class DecodeWorkspace:
         self.lse = torch.empty(max_T, self.max_splits, heads, dtype=torch.float32, device=device)
 
 
-def decode(q8, sq, kv8, kv_scale, kv_smax, page_table, slot_of, kvlen, ws: DecodeWorkspace, softmax_scale, out=None):
+def decode(q8, sq, kv8, kv_scale, kv_smax, page_table, slot_of, kvlen, ws: DecodeWorkspace, softmax_scale, out=None, merge=True):
     """q8 [128][T][576] e4m3, sq [128][T]; kv8 [pages][64][576]; kv_smax f32 [pages][4] (element 0 bounds the
     page's scales from above); returns oacc bf16 [128][T][512]."""
     heads, T, _ = q8.shape
     assert heads == 128 and kv8.shape[1:] == (64, 576)
-    if out is None:
+    if out is None and merge:
         out = torch.empty(heads, T, 512, dtype=BF16, device=q8.device)
     native.call("plow_mla_decode", q8, sq, kv8, kv_scale, kv_smax, kv8.shape[0], page_table, page_table.shape[1], slot_of, kvlen, T,
                 ws.tiles_per_split, ws.max_splits, ws.items, ws.n_items, ws.opart, ws.lse, out, float(softmax_scale),

@@ -111,6 +111,8 @@ _SIGS = {
     "plow_row_gather": "pppiip",
     "plow_head_to_token": "ppiiip",
     "plow_mla_decode": "ppppplpipp" "iiipppppfpp",
+    "plow_mla_absorb": "pipppppiiipp",
+    "plow_mla_fold": "pppppppiiiiipp",
     "plow_ep_counts": "ppipp",
     "plow_ep_push": "ppiippippppip",
     "plow_ep_y_ready": "pp",
@@ -129,7 +131,7 @@ def _arg(v):
 
 
 LAUNCHES = {"n": 0}                       # kernels launched through this module (bench bookkeeping)
-_KERNELS_PER_CALL = {"plow_mla_decode": 3}
+_KERNELS_PER_CALL = {"plow_mla_decode": 2}
 
 
 def call(name: str, *args) -> None:

@@ -362,22 +362,19 @@ class GpuEngine(EngineBase):
             raise EngineError("the sm_100a MLA kernel is specialised for 128 heads, 512 latent and 64 rope dims per rank")
         T = st.rows
         wuk_t, wuv = self._mla_prep(layer, ins.t[4], heads, kv_lora, nope, v_head)
-        q_nope_t, q_rope = mla_ops.q_prep(q, rope, self.d_in[1], heads, nope, qk_rope, pair)
-        off = st.scratch.setdefault("head_off", (torch.arange(heads + 1, dtype=I32, device=self.device) * T))
-        q_abs = gemm_ops.gemm(q_nope_t.view(heads * T, nope), wuk_t, n_experts=heads, n_out=kv_lora, grp_off=off,
-                              swap=True, bn=gemm_ops._pick_bn_swap(T, False, False), rows_hint=T)
-        q8, sq = mla_ops.q_quant(q_abs.view(heads, T, kv_lora), q_rope)
+        if nope != 128 or v_head != 128:
+            raise EngineError("the fused MLA projection kernels are specialised for 128 nope / 128 v dims")
+        q8, sq = mla_ops.absorb(q, wuk_t, rope, self.d_in[1], heads, pair)
         if self._mla_ws is None or self._mla_ws.opart.shape[0] < T:
             self._mla_ws = mla_ops.DecodeWorkspace(max(T, self.max_rows_all), self.max_ctx + PAGE, device=self.device)
-        oacc = mla_ops.decode(q8, sq, cache, scale, self.kv_smax[layer], self.d_page_table, self.d_in[2], self.d_kvlen_row,
-                              self._mla_ws, float(ins.f[0]))
-        tp = None
-        if T > 128:
-            tiles = st.scratch.setdefault("head_tiles", (torch.arange(heads + 1, dtype=I32, device=self.device) * ((T + 127) // 128)))
-            tp = tiles
-        o_h = gemm_ops.gemm(oacc.view(heads * T, kv_lora), wuv, n_experts=heads, n_out=v_head, grp_off=off, tile_prefix=tp,
-                            swap=T <= 128, bn=gemm_ops._pick_bn_swap(T, False, False) if T <= 128 else 128, rows_hint=T)
-        native.call("plow_head_to_token", ao, o_h, T, heads, v_head)
+        if self._mla_ws.max_splits > 8:
+            raise EngineError("max_ctx needs more than 8 KV splits; raise tiles_per_split")
+        mla_ops.decode(q8, sq, cache, scale, self.kv_smax[layer], self.d_page_table, self.d_in[2], self.d_kvlen_row,
+                       self._mla_ws, float(ins.f[0]), merge=False)
+        want = self._wants_q(st, ins.t[0])
+        aq, saq = mla_ops.fold(self._mla_ws, self.d_kvlen_row, wuv, T, heads, ao, want_fp8=want)
+        if want:
+            st.q[(ins.t[0], 0)] = (aq, saq)
 
     # -- MoE
     def _op_router_topk(self, st, ins):

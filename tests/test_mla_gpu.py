@@ -109,3 +109,40 @@ def test_kv_write_roundtrip():
         got = kv8[page, int(pos[t]) % 64].float() * ksc[page, int(pos[t]) % 64]
         assert _rel(got, ref[t]) < 4e-2
         assert abs(float(ksc[page, int(pos[t]) % 64]) - float(ref[t].abs().max() / 448)) < 5e-3 * float(ref[t].abs().max() / 448) + 1e-8
+
+
+def test_absorb_and_fold_fused_kernels():
+    from plow_b200.ops import mla, native
+    from plow_b200.utils.rope import rope_table
+    torch.manual_seed(0)
+    H, T = 128, 70
+    q = torch.randn(T, H * 192, device="cuda").bfloat16()
+    wuk_t = (torch.randn(H * 512, 128, device="cuda") * 0.1).bfloat16()
+    tab = torch.from_numpy(rope_table(4096, 64, 10000.0)).cuda()
+    pos = torch.randint(0, 4096, (T,), device="cuda", dtype=torch.int32)
+    q8, sq = mla.absorb(q, wuk_t, tab, pos, H, 1)
+    native.check_status()
+    q3 = q.view(T, H, 192).float()
+    qabs = torch.einsum("thd,hcd->htc", q3[..., :128], wuk_t.view(H, 512, 128).float())
+    qrope = _rope_ref(q3[..., 128:].permute(1, 0, 2), tab, pos)
+    full = torch.cat([qabs, qrope], -1)
+    assert _rel(sq, full.abs().amax(-1) / 448) < 5e-3
+    assert _rel(q8.float() * sq[..., None], full) < 4e-2
+    # fold: 3 requests with 1, 2 and 3 splits
+    lens = [100, 40 * 64, 70 * 64 + 5]
+    T2 = len(lens)
+    ws = mla.DecodeWorkspace(T2, 8192, tiles_per_split=32)
+    ws.opart.copy_(torch.randn_like(ws.opart.float()).bfloat16())
+    ws.lse.copy_(torch.randn_like(ws.lse) * 3)
+    kvlen = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    wuv = (torch.randn(H * 128, 512, device="cuda") * 0.1).bfloat16()
+    ao = torch.empty(T2, H * 128, dtype=torch.bfloat16, device="cuda")
+    aq, saq = mla.fold(ws, kvlen, wuv, T2, H, ao, want_fp8=True)
+    native.check_status()
+    for t, n in enumerate(lens):
+        ns = min(ws.max_splits, -(-((n + 63) // 64) // 32))
+        w = torch.softmax(ws.lse[t, :ns].float() * 0.6931471805599453, 0)          # 2^lse weights
+        merged = (w[:, :, None] * ws.opart[t, :ns].float()).sum(0).bfloat16().float()   # [heads, 512]
+        ref = torch.einsum("hc,hvc->hv", merged, wuv.view(H, 128, 512).float()).reshape(-1)
+        assert _rel(ao[t], ref) < 1e-2
+        assert _rel(aq[t].float().view(H, 128) * saq[:, t, None], ref.view(H, 128)) < 4e-2
