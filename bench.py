@@ -79,6 +79,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=61, help="debug only: anything but 61 is not the named config")
     ap.add_argument("--batch-per-gpu", type=int, default=64)
     ap.add_argument("--ttft-prompts", type=int, default=2)
+    ap.add_argument("--init", default="scaled", choices=["scaled", "plain"],
+                    help="scaled: depth-scaled random init (balanced routing, like a trained checkpoint); plain: N(0,0.02) everywhere")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -117,7 +119,7 @@ def main() -> int:
         comm = EpComm(rank, world, spec, max_rows=512, impl=args.impl)
     dev = torch.device("cuda", local)
     t_load = time.time()
-    eng = GpuEngine(packet=pkt, weights=SyntheticWeights(dev, seed=1234 + rank), max_slots=B + 1, max_ctx=max_ctx,
+    eng = GpuEngine(packet=pkt, weights=SyntheticWeights(dev, seed=1234 + rank, scaled_init_layers=(args.layers if args.init == "scaled" else 0)), max_slots=B + 1, max_ctx=max_ctx,
                     prefix_cache=False, rank=rank, comm=comm)
     load_s = time.time() - t_load
 
@@ -139,6 +141,13 @@ def main() -> int:
                 flat[i:i + m] = (torch.randn(m, device=dev, generator=gen) * 64.0).to(FP8)
         elif t.name.endswith(".latent_scale"):
             eng.static[h].fill_(1.0 / 64.0)
+    # the cache writer keeps a per-page upper bound of the scales; the synthetic pages need one too
+    from plow_b200.compiler.packet import Op as _Op
+    for ins in pkt.programs[0].insts:
+        if ins.op == _Op.MLA_KV_WRITE:
+            sm = torch.zeros(eng.static[ins.t[0]].shape[0], 4, dtype=torch.float32, device=dev)
+            sm[:, 0] = 1.0 / 64.0
+            eng.kv_smax[ins.i[7]] = sm
     eng_prefill_ttft = []
 
     # ---- TTFT: real chunked prefill of fresh prompts in the spare slot (512-row ticks) ----
@@ -184,6 +193,43 @@ def main() -> int:
     torch.cuda.synchronize()
     launches_per_step = native.LAUNCHES["n"] - n0
 
+    if os.environ.get("PLOW_EP_TRACE") and comm is not None:
+        # debug aid: re-capture the decode graph with device-side trace marks in the EP kernels
+        comm.device_trace(True)
+        import ctypes as _C
+        _lib = native.cuda_lib()
+        _lib.plow_gemm_set_trace.argtypes = [_C.c_void_p]
+        gtr = torch.zeros(64 * 8, dtype=torch.int64, device=dev)
+        _lib.plow_gemm_set_trace(gtr.data_ptr())
+        st.graph = None
+        one_step(W)
+        comm._trace.zero_()
+        barrier()
+        one_step(W)
+        torch.cuda.synchronize()
+        rows = comm.device_trace_rows()
+        comm.device_trace(False)
+        _lib.plow_gemm_set_trace(None)
+        gt = gtr.cpu()
+        print(f"rank {rank}: last gated GEMM waited {(int(gt[15]) - int(gt[7])) / 1e3:.1f} us (counter {int(gt[23])} -> target {int(gt[31])})", file=sys.stderr)
+        st.graph = None
+        if rank == 0:
+            import collections
+            seg = collections.defaultdict(list)
+            names = {(1, 2): "counts", (2, 3): "gap_counts_push", (3, 4): "push_wait_counts", (4, 5): "push_copy", (5, 6): "gemms(+wait)",
+                     (6, 7): "gap_yready_combine", (7, 8): "combine_wait_y", (8, 9): "combine_pull", (9, 1): "rest_of_layer"}
+            for (ta, a_), (tb, b_) in zip(rows, rows[1:]):
+                seg[names.get((ta, tb), f"{ta}->{tb}")].append((b_ - a_) / 1e3)
+            print("EP device trace us (rank 0, mean over layers):", json.dumps({k: round(sum(v) / len(v), 1) for k, v in seg.items()}), file=sys.stderr)
+    if os.environ.get("PLOW_EP_TIMING") and comm is not None:
+        # debug aid: one eager walk of the decode program with CUDA events around the EP phases
+        comm.timing = {}
+        barrier()
+        eng._run_insts(st)
+        rep = comm.timing_report()
+        comm.timing = None
+        if rank == 0:
+            print("EP phase us (rank 0):", json.dumps(rep), file=sys.stderr)
     sampler = ClockSampler(local).start()
     barrier()
     t0 = time.perf_counter()
@@ -198,6 +244,15 @@ def main() -> int:
     # every rank prefills a prompt of the same length at the same time (EP layers are collective)
     for n in list(np.random.default_rng(11).integers(1024, 8193, size=args.ttft_prompts)):
         ttfts.append(prefill_once(int(n)))
+    route = None
+    if comm is not None and getattr(comm, "grp_off", None) is not None:
+        go = comm.grp_off.cpu().numpy().astype(np.int64)       # rows per local expert in the last MoE layer
+        per = np.diff(go)
+        rs = torch.tensor([float(go[-1]), float(per.max())], dtype=torch.float64, device=dev)
+        mx = rs.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        route = {"rows_rank0": int(go[-1]), "max_rows_any_rank": int(mx[0]), "max_rows_one_expert": int(mx[1]),
+                 "mean_rows_per_rank": B * 8}
     dev_total = float(np.sum(dev_ms))
     stats = torch.tensor([dev_total, wall, float(np.median(dev_ms))], dtype=torch.float64, device=dev)
     if world > 1:
@@ -211,7 +266,9 @@ def main() -> int:
         out = {
             "metric": METRIC, "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": W,
             "ms_per_step": round(dev_total / args.steps, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "fp8 (e4m3 block-scaled weights, e4m3 latent KV, bf16 activations)", "data": "synthetic",
+            "dtype": "fp8 (e4m3 block-scaled weights, e4m3 latent KV, bf16 activations)", "data": ("synthetic: random token ids, random e4m3 latent cache, random-init weights "
+                     + ("(N(0,0.02); unit-variance embeddings and residual-output projections scaled by 1/(2L), which keeps "
+                        "expert routing balanced as in a trained checkpoint)" if args.init == "scaled" else "(N(0,0.02) everywhere; routing collapses with depth)")),
             "impl": args.impl,
             "config": {"model": f"MLA-MoE 671B-shape ({32 * world} routed experts, {args.layers} layers)", "global_batch": B * world,
                        "seq_len": "ctx uniform 1024-8192 + decoded tokens", "parallelism": f"ep{world} + dp-attention",
@@ -221,7 +278,7 @@ def main() -> int:
             "ttft_prompts": len(ttfts),
             "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": int(4 * 4 * B), "d2h_bytes_per_step": int(4 * B)},
             "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": int(launches_per_step),
-            "clocks": clocks, "load_s": round(load_s, 1),
+            "clocks": clocks, "load_s": round(load_s, 1), "ep_routing_last_layer": route,
             "hbm_peak_gbs": hbm, "hbm_peak_source": src,
         }
         print(json.dumps(out))

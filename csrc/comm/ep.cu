@@ -49,20 +49,29 @@ struct EpArgs {
   uint32_t* epoch;        // device word: layer-call counter (monotonic)
   int* status;
   unsigned long long deadline_ns;
+  unsigned long long* trace;   // optional [1 + 2n] u64: count, then (tag, globaltimer) pairs (debug aid), NULL when off
 };
+
+__device__ __forceinline__ void trace_mark(const EpArgs& a, unsigned long long tag) {
+  if (a.trace) {
+    const unsigned long long i = atomicAdd(a.trace, 1ull);
+    if (i < 4000) { a.trace[1 + 2 * i] = tag; a.trace[2 + 2 * i] = globaltimer_ns(); }
+  }
+}
 
 __device__ __forceinline__ bool wait_ge(const uint32_t* p, uint32_t target, unsigned long long deadline_ns) {
   const unsigned long long t0 = globaltimer_ns();
   while (ld_acquire_sys(p) < target) {
     if (globaltimer_ns() - t0 > deadline_ns) return false;
-    __nanosleep(64);
+    __nanosleep(256);   // back off: the polled line is also the target of the peers' stores
   }
   return true;
 }
 
 __global__ void ep_counts_kernel(EpArgs a, const int2* table, int n_pairs, int* cursor) {
   extern __shared__ int hist[];
-  for (int e = threadIdx.x; e < a.E; e += blockDim.x) { hist[e] = 0; cursor[e] = 0; }
+  if (threadIdx.x == 0) trace_mark(a, 1);
+  for (int e = threadIdx.x; e < a.E; e += blockDim.x) { hist[e] = 0; cursor[e] = 0; }   // cursor[E] is the push kernel's CTA counter
   __syncthreads();
   for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&hist[table[p].x], 1);
   __syncthreads();
@@ -75,7 +84,7 @@ __global__ void ep_counts_kernel(EpArgs a, const int2* table, int n_pairs, int* 
   __syncthreads();
   if (threadIdx.x < a.W)
     st_release_sys(reinterpret_cast<uint32_t*>(a.peer[threadIdx.x] + a.L.cnt_flag) + a.me * 32, ep);
-  if (threadIdx.x == 0) *a.epoch = ep;
+  if (threadIdx.x == 0) { *a.epoch = ep; trace_mark(a, 2); }
 }
 
 // grid: any; 256 threads.  One warp per pair.
@@ -88,11 +97,13 @@ __global__ void ep_push_kernel(EpArgs a, const int2* table, int n_pairs, int top
   if (threadIdx.x == 0) fail = 0;
   __syncthreads();
   const uint32_t ep = *a.epoch;
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 3);
   if (threadIdx.x < a.W) {
     if (!wait_ge(reinterpret_cast<const uint32_t*>(a.peer[a.me] + a.L.cnt_flag) + threadIdx.x * 32, ep, a.deadline_ns)) fail = 1;
   }
   __syncthreads();
   if (fail) { if (threadIdx.x == 0) atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); return; }
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 4);
   const int* call = reinterpret_cast<const int*>(a.peer[a.me] + a.L.cnt_all);
   for (int i = threadIdx.x; i < a.W * a.E; i += blockDim.x) cnt[i] = call[i];
   __syncthreads();
@@ -136,12 +147,29 @@ __global__ void ep_push_kernel(EpArgs a, const int2* table, int n_pairs, int top
     for (int kb = lane; kb < KB; kb += 32) dsx[static_cast<size_t>(kb) * a.Rmax + row] = sx[static_cast<size_t>(kb) * ld_sx + tok];
     if (lane == 0) pair_dest[p] = (d << 24) | row;
   }
+  // One arrival per (source rank, owner): the CTA that finishes last signals for the whole kernel.
+  // Every CTA makes its remote stores visible system-wide before it counts itself in, and the last
+  // CTA's release add is ordered after all of those counts, so an owner that acquires the counter
+  // sees every row this rank sent.  (One add per CTA made 256 remote atomics per layer fight with the
+  // owner's pollers for one line: 1.3 ms per layer at 8 ranks.)
   __threadfence_system();
   __syncthreads();
-  if (threadIdx.x < a.W) red_add_release_sys(reinterpret_cast<uint32_t*>(a.peer[threadIdx.x] + a.L.data_ctr), 1u);
+  __shared__ int is_last;
+  if (threadIdx.x == 0) {
+    const int old = atomicAdd(&cursor[a.E], 1);
+    is_last = old == static_cast<int>(gridDim.x) - 1;
+    if (is_last) cursor[a.E] = 0;
+  }
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    if (threadIdx.x < a.W) red_add_release_sys(reinterpret_cast<uint32_t*>(a.peer[threadIdx.x] + a.L.data_ctr), 1u);
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 5);
 }
 
 __global__ void ep_y_ready_kernel(EpArgs a) {
+  if (threadIdx.x == 0) trace_mark(a, 6);
   __threadfence_system();
   const uint32_t ep = *a.epoch;
   if (threadIdx.x < a.W) st_release_sys(reinterpret_cast<uint32_t*>(a.peer[threadIdx.x] + a.L.y_flag) + a.me * 32, ep);
@@ -153,11 +181,13 @@ __global__ void ep_combine_kernel(EpArgs a, __nv_bfloat16* out, const __nv_bfloa
   if (threadIdx.x == 0) fail = 0;
   __syncthreads();
   const uint32_t ep = *a.epoch;
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 7);
   if (threadIdx.x < a.W) {
     if (!wait_ge(reinterpret_cast<const uint32_t*>(a.peer[a.me] + a.L.y_flag) + threadIdx.x * 32, ep, a.deadline_ns)) fail = 1;
   }
   __syncthreads();
   if (fail) { if (threadIdx.x == 0) atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); return; }
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 8);
   const int t = blockIdx.x;
   for (int i = threadIdx.x * 8; i < a.H; i += blockDim.x * 8) {
     float acc[8];
@@ -186,6 +216,7 @@ __global__ void ep_combine_kernel(EpArgs a, __nv_bfloat16* out, const __nv_bfloa
     for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
     *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * a.H + i) = o;
   }
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 9);
 }
 
 // A wait that nothing satisfies: used by the failure-detection test to exercise the deadline path

@@ -281,7 +281,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
         if (!mbar_wait(&kv_full[s], ((kv_it + i) / kMlaStages) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); ok = false; break; }
         const float* sk_base = reinterpret_cast<const float*>(kv_smem + s * kKvStageBytes + kKvTileBytes);
         const float4* sk4 = reinterpret_cast<const float4*>(sk_base) + ch * 8;
-        const float skmax = sk_base[64];       // upper bound of this page's scales, kept by the cache writer
+        const float skmax = fmaxf(sk_base[64], 1e-30f);   // upper bound of this page's scales, kept by the cache writer
         const int valid = min(kMlaPage, kv_len - (w.tile0 + i) * kMlaPage) - ch * 32;   // valid columns of this half
         float skv[32];
 #pragma unroll

@@ -235,12 +235,14 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         // must be ordered behind it too
         const uint32_t target = *a.wait_epoch * a.wait_mult;
         const unsigned long long t0 = globaltimer_ns();
+        if (a.trace && blockIdx.x == 0) { a.trace[7] = static_cast<long long>(t0); a.trace[23] = ld_acquire_sys(a.wait_ctr); a.trace[31] = target; }
         while (ld_acquire_sys(a.wait_ctr) < target) {
           if (globaltimer_ns() - t0 > static_cast<unsigned long long>(a.wait_deadline_ms) * 1000000ull) {
             *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); ok = false; break;
           }
-          __nanosleep(64);
+          __nanosleep(256);
         }
+        if (a.trace && blockIdx.x == 0) a.trace[15] = static_cast<long long>(globaltimer_ns());
         fence_proxy_async_all();
       }
       while (ok && sched.next(t)) {
@@ -333,20 +335,8 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
     constexpr int kAccRegs = FP8 ? kAccCols : 1;
     float acc[kAccRegs];
     const __nv_bfloat16* resid = reinterpret_cast<const __nv_bfloat16*>(a.residual);
-    if (a.wait_ctr) {
-      if (lane == 0) {
-        const uint32_t target = *a.wait_epoch * a.wait_mult;
-        const unsigned long long t0 = globaltimer_ns();
-        while (ld_acquire_sys(a.wait_ctr) < target && !*abort_flag) {
-          if (globaltimer_ns() - t0 > static_cast<unsigned long long>(a.wait_deadline_ms) * 1000000ull) {
-            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); break;
-          }
-          __nanosleep(64);
-        }
-      }
-      __syncwarp();
-      if (*abort_flag) ok = false;
-    }
+    // The arrival gate is polled by the producer thread only: the epilogue warps touch the peers' rows
+    // (their scales) after an accumulator-full barrier, which is ordered behind the producer's acquire.
     while (ok && sched.next(t)) {
       const int tok_i = t.tok0 + li;       // non-swap: this thread's token
       const int feat_i = t.feat0 + li;     // swap: this thread's feature

@@ -33,7 +33,8 @@ class EpArgs(C.Structure):
     _fields_ = [("peer", C.c_uint64 * 8), ("cnt_all", C.c_uint64), ("cnt_flag", C.c_uint64), ("data_ctr", C.c_uint64),
                 ("y_flag", C.c_uint64), ("recv_x", C.c_uint64), ("recv_sx", C.c_uint64), ("y", C.c_uint64),
                 ("W", C.c_int32), ("me", C.c_int32), ("E", C.c_int32), ("e_local", C.c_int32), ("Rmax", C.c_int32),
-                ("H", C.c_int32), ("epoch", C.c_uint64), ("status", C.c_uint64), ("deadline_ns", C.c_uint64)]
+                ("H", C.c_int32), ("epoch", C.c_uint64), ("status", C.c_uint64), ("deadline_ns", C.c_uint64),
+                ("trace", C.c_uint64)]
 
 
 def _align(x, a=256):
@@ -50,6 +51,7 @@ class EpComm:
         self.n_cta = n_cta
         self.deadline_ms = deadline_ms
         self.Rmax = world * max_rows * self.k
+        self.timing = None            # set to a dict to collect CUDA-event phase times (debug aid, eager mode only)
         if impl != "fused":
             return
         import torch.distributed._symmetric_memory as symm
@@ -66,7 +68,7 @@ class EpComm:
         dist.barrier()
         self.lay = lay
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.dev)
-        self.cursor = torch.zeros(self.E, dtype=I32, device=self.dev)
+        self.cursor = torch.zeros(self.E + 1, dtype=I32, device=self.dev)   # +1: CTA counter of the push kernel
         self.grp_off = torch.zeros(self.e_local + 1, dtype=I32, device=self.dev)
         self.tile_prefix = torch.zeros(self.e_local + 1, dtype=I32, device=self.dev)
         self.pair_dest = torch.zeros(max_rows * self.k, dtype=I32, device=self.dev)
@@ -80,6 +82,7 @@ class EpComm:
         a.epoch = self.epoch.data_ptr()
         a.status = native.status_word(self.dev).data_ptr()
         a.deadline_ns = deadline_ms * 1_000_000
+        a.trace = 0
         self.args = a
         self.recv_x = self.buf[lay["recv_x"]:lay["recv_x"] + self.Rmax * self.H].view(FP8).view(self.Rmax, self.H)
         self.recv_sx = self.buf[lay["recv_sx"]:lay["recv_sx"] + KB * self.Rmax * 4].view(F32).view(KB, self.Rmax)
@@ -96,10 +99,42 @@ class EpComm:
         T, k, H = st.rows, self.k, self.H
         xq, sx = eng._quant_of(st, ins.t[1], 0, H, h)
         ap = C.addressof(self.args)
+        self._mark("t0")
         native.call("plow_ep_counts", ap, table, T * k, self.cursor)
+        self._mark("counts")
         native.call("plow_ep_push", ap, table, T * k, k, xq, sx, sx.stride(0), self.cursor, self.grp_off, self.tile_prefix,
                     self.pair_dest, self.n_cta)
+        self._mark("push")
         st.scratch["ep_dispatched"] = ins.i[7]
+
+    def device_trace(self, on: bool):
+        """Debug aid: device-side (tag, globaltimer) marks of the EP kernels.  Only effective for eager launches
+        issued after the call (captured graphs keep the arguments they were captured with)."""
+        if on:
+            self._trace = torch.zeros(1 + 2 * 4000, dtype=torch.int64, device=self.dev)
+            self.args.trace = self._trace.data_ptr()
+        else:
+            self.args.trace = 0
+
+    def device_trace_rows(self):
+        t = self._trace.cpu()
+        n = min(int(t[0]), 4000)
+        return [(int(t[1 + 2 * i]), int(t[2 + 2 * i])) for i in range(n)]
+
+    def _mark(self, name):
+        if self.timing is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.timing.setdefault("_ev", []).append((name, ev))
+
+    def timing_report(self):
+        evs = self.timing.pop("_ev", [])
+        torch.cuda.synchronize()
+        out = {}
+        for (n0, e0), (n1, e1) in zip(evs, evs[1:]):
+            if n1 != "t0":
+                out.setdefault(n1, []).append(e0.elapsed_time(e1) * 1e3)
+        return {k: round(sum(v) / len(v), 1) for k, v in out.items()}
 
     def moe_experts(self, eng, st, ins):
         if self.impl == "nccl":
@@ -112,9 +147,10 @@ class EpComm:
         if st.scratch.get("ep_dispatched") != ins.i[7]:
             self.dispatch(eng, st, ins)
         st.scratch["ep_dispatched"] = None
+        self._mark("shared_etc")
         w1, s1 = eng.static_q[ins.t[3]]
         w2, s2 = eng.static_q[ins.t[4]]
-        wait = (self.data_ctr_ptr, self.epoch.data_ptr(), self.world * self.n_cta, self.deadline_ms)
+        wait = (self.data_ctr_ptr, self.epoch.data_ptr(), self.world, self.deadline_ms)
         per = max(1, self.world * T * k // self.E)
         R = self.world * T * k                      # rows this rank can receive for this program
         rx, rsx, ry = self.recv_x[:R], self.recv_sx, self.y[:R]
@@ -122,7 +158,9 @@ class EpComm:
             bn = 32 if per <= 32 else 64
             hq, shq = gemm_ops.gemm(rx, w1, sx=rsx, sw=s1, dual=True, n_out=F, n_experts=self.e_local, grp_off=self.grp_off,
                                     swap=True, bn=bn, quant_out=True, ld_syq=R, wait=wait)
+            self._mark("gemm1")
             gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=self.e_local, grp_off=self.grp_off, swap=True, bn=bn, out=ry)
+            self._mark("gemm2")
         else:
             hb = gemm_ops.gemm(rx, w1, sx=rsx, sw=s1, dual=True, n_out=F, n_experts=self.e_local, grp_off=self.grp_off,
                                tile_prefix=self.tile_prefix, swap=False, bn=64, wait=wait)
@@ -130,7 +168,9 @@ class EpComm:
             gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=self.e_local, grp_off=self.grp_off,
                           tile_prefix=self.tile_prefix, swap=False, bn=128, out=ry)
         native.call("plow_ep_y_ready", ap)
+        self._mark("y_ready")
         native.call("plow_ep_combine", ap, y_out, shared, table, self.pair_dest, T, k)
+        self._mark("combine")
 
     # ---- NCCL baseline arm ---------------------------------------------------------------------
     def _moe_nccl(self, eng, st, ins):

@@ -64,9 +64,26 @@ class SyntheticWeights(WeightSource):
     drawn directly in the quantised domain with one constant block scale, so a 100 GB shard is
     produced in about a minute without a bf16 copy ever existing."""
 
-    def __init__(self, device, seed=0, std=0.02):
+    def __init__(self, device, seed=0, std=0.02, scaled_init_layers: int = 0):
+        """`scaled_init_layers` = L > 0 selects the usual depth-scaled random init: unit-variance
+        embeddings and residual-output projections (o_proj, down_proj) drawn with std / (2 L).  With
+        plain N(0, std) everywhere the hidden states of different tokens become collinear after a few
+        dozen random layers and every token routes to the same experts, which no trained
+        (load-balanced) checkpoint does; the scaled init keeps routing token-specific.  Shapes, dtypes
+        and bytes moved are identical either way."""
         self.device, self.std = device, std
+        self.L = scaled_init_layers
         self.gen = torch.Generator(device=device).manual_seed(seed)
+
+    def _std_for(self, name: str) -> float:
+        if not self.L:
+            return self.std
+        if name.endswith("embed_tokens.weight"):
+            return 1.0
+        if name.endswith("o_proj.weight") or name.endswith("down_proj.weight") or name.endswith("experts.down.weight") \
+                or name.endswith("out_proj.weight"):
+            return self.std / (2.0 * self.L)
+        return self.std
 
     def _shape(self, ent):
         return tuple(int(d) for d in ent.dims)
@@ -83,7 +100,7 @@ class SyntheticWeights(WeightSource):
         flat = out.view(-1)
         step = 1 << 28
         for i in range(0, flat.numel(), step):
-            flat[i:i + step] = torch.randn(min(step, flat.numel() - i), device=self.device, generator=self.gen) * self.std
+            flat[i:i + step] = torch.randn(min(step, flat.numel() - i), device=self.device, generator=self.gen) * self._std_for(n)
         return out
 
     def fp8(self, ent, recipe):
@@ -95,7 +112,7 @@ class SyntheticWeights(WeightSource):
         for i in range(0, flat.numel(), step):
             m = min(step, flat.numel() - i)
             flat[i:i + m] = (torch.randn(m, device=self.device, generator=self.gen).clamp_(-clip, clip) * (448.0 / clip)).to(FP8)
-        s = torch.full(((n + 127) // 128, (k + 127) // 128), self.std * clip / 448.0, dtype=F32, device=self.device)
+        s = torch.full(((n + 127) // 128, (k + 127) // 128), self._std_for(ent.name) * clip / 448.0, dtype=F32, device=self.device)
         return q, s
 
 
