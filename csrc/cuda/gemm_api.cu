@@ -15,6 +15,9 @@ GemmArgs to_args(const PlowGemmDesc& d) {
   a.status = d.status; a.M = d.M; a.N = d.N; a.K = d.K; a.ldy = d.ldy; a.ld_sx = d.ld_sx;
   a.ld_syq = d.ld_syq; a.E = d.E; a.out_f32 = d.out_f32; a.out_scale = d.out_scale;
   a.ws = d.ws; a.ws_ctr = d.ws_ctr; a.splits = (d.swap && d.E == 0 && d.ws && d.ws_ctr) ? d.splits : 1;
+  for (int i = 0; i < 8; ++i) a.ar_peer[i] = static_cast<uint8_t*>(d.ar_peer[i]);
+  a.ar_part_ofs = d.ar_part_ofs; a.ar_flag_ofs = d.ar_flag_ofs; a.ar_done_ofs = d.ar_done_ofs; a.ar_y_ofs = d.ar_y_ofs;
+  a.ar_epoch = static_cast<uint32_t*>(d.ar_epoch); a.ar_world = d.ar_world; a.ar_me = d.ar_me;
   a.wait_ctr = static_cast<const uint32_t*>(d.wait_ctr); a.wait_epoch = static_cast<const uint32_t*>(d.wait_epoch);
   a.wait_mult = static_cast<uint32_t>(d.wait_mult); a.wait_deadline_ms = static_cast<uint32_t>(d.wait_deadline_ms);
   return a;
@@ -38,6 +41,7 @@ extern "C" int plow_gemm(const PlowGemmDesc* d, void* stream) {
   if (d->dual && (d->N % 128)) return -6;
   if (d->yq && !d->syq) return -7;
   if (d->yq && !d->swap && d->bn != 128) return -7;
+  if (d->ar_world > 1 && (!d->swap || d->dual || d->E || d->M > d->bn || d->splits > 1 || d->yq || d->out_f32 || !d->ar_epoch || (d->N % 8) || (d->ldy % 8))) return -8;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return d->dtype == 1 ? plow::gemm_dispatch_fp8(*d, s) : plow::gemm_dispatch_bf16(*d, s);
 }

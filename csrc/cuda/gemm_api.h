@@ -31,6 +31,12 @@ typedef struct PlowGemmDesc {
   int32_t* ws_ctr;
   int32_t splits;         // >1: split-K over CTAs (dense swap mode only)
   int32_t ws_pad;
+  // fused all-reduce over tensor-parallel ranks (swap mode, M <= bn, not dual): symmetric region of every
+  // rank, byte offsets of the partial / flag / arrival / output areas inside it, launch-epoch word
+  void* ar_peer[8];
+  uint64_t ar_part_ofs, ar_flag_ofs, ar_done_ofs, ar_y_ofs;
+  void* ar_epoch;
+  int32_t ar_world, ar_me;
   const void* wait_ctr;   // optional arrival gate: start once *wait_ctr >= *wait_epoch * wait_mult
   const void* wait_epoch;
   int32_t wait_mult;

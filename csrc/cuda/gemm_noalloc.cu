@@ -61,7 +61,7 @@ extern "C" int plow_gemm_splitk_noalloc(const void* x, const void* w, void* y, i
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   // the array keeps whatever the previous call (possibly an aborted one) left: re-arm the counters
   if (cudaMemsetAsync(scratch + kWsBytes, 0, kCtrBytes, stream) != cudaSuccess) return 4999;
-  GemmArgs a{};   // trace and arrival gate stay off
+  GemmArgs a{};   // trace, arrival gate and fused all-reduce stay off
   a.x = x; a.w = w; a.y = y; a.status = status;
   a.M = M; a.N = N; a.K = K; a.ldy = N; a.E = 0; a.out_f32 = 0; a.out_scale = 1.0f;
   a.ws = reinterpret_cast<float*>(scratch);

@@ -50,6 +50,12 @@ struct GemmArgs {
   float* ws;
   int* ws_ctr;
   int splits;
+  // fused all-reduce (tensor-parallel row-parallel GEMM, swap mode): this rank's partial tiles are
+  // reduced through peer memory from inside the kernel, see the `ar_*` phase at the end of the kernel
+  uint8_t* ar_peer[8];    // symmetric region of every rank (peer-mapped), NULL world = off
+  unsigned long long ar_part_ofs, ar_flag_ofs, ar_done_ofs, ar_y_ofs;
+  uint32_t* ar_epoch;     // device word, launch counter
+  int ar_world, ar_me;
   long long* trace;       // optional clock64() phase stamps of CTA 0 (debug aid), NULL when off
   const uint32_t* wait_ctr;
   const uint32_t* wait_epoch;
@@ -198,6 +204,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int KB = (a.K + kKElems - 1) / kKElems;
+  const uint32_t ar_ep = a.ar_world > 1 ? *a.ar_epoch + 1 : 0;   // this launch's all-reduce epoch
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -536,6 +543,20 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           if (c + 16 <= col_lo || c >= col_hi) continue;
           float r[16];
           load16(c, r);
+          if (a.ar_world > 1) {
+            // fused all-reduce, phase 1: this rank's partial of the tile, bf16, [tile][feature][token]
+            uint32_t pk[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(r[2 * j], r[2 * j + 1]);
+              pk[j] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            uint4* pp = reinterpret_cast<uint4*>(a.ar_peer[a.ar_me] + a.ar_part_ofs +
+                                                 (static_cast<size_t>((t.feat0 >> 7) * 128 + li) * BN + c) * 2);
+            pp[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            pp[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            continue;
+          }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int tok = t.tok0 + c + j;
@@ -579,6 +600,19 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           }
         }
         if (!ok) break;
+        if (a.ar_world > 1) {
+          // tell the tile's owner (tile mod world) that this rank's partial is in place
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
+          if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) {
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
+          }
+          ++xchg_it;
+          const int tile = t.feat0 >> 7;
+          if (li == 0)
+            st_release_sys(reinterpret_cast<uint32_t*>(a.ar_peer[tile % a.ar_world] + a.ar_flag_ofs) + tile * 8 + a.ar_me, ar_ep);
+        }
         if (ws_tile) {
           // the split that leaves last re-arms the tile's counters for the next launch
           __syncwarp();
@@ -674,6 +708,97 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[accit & 1]);
         ++accit;
+      }
+    }
+    // ---- fused all-reduce, phase 2 (swap mode): the owner of a tile (tile mod world) sums the ranks'
+    // partials in rank order (f32, rounded to bf16 once, so every rank receives identical bits) and
+    // stores the result into every rank's output; then one arrival per (tile, rank).  Reference
+    // numerics: runtime/nvidia/op_collective.cuh:18-20.  Plain peer loads/stores, bounded waits.
+    if constexpr (SWAP && !DUAL) {
+      if (a.ar_world > 1 && ok) {
+        const int W = a.ar_world;
+        const int n_tiles = (a.N + 127) / 128;
+        const unsigned long long dl = static_cast<unsigned long long>(a.wait_deadline_ms ? a.wait_deadline_ms : 2000) * 1000000ull;
+        int idx = 0;
+        for (int tile = a.ar_me; tile < n_tiles && ok; tile += W, ++idx) {
+          if (idx % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
+          if (li < W) {
+            const uint32_t* f = reinterpret_cast<const uint32_t*>(a.ar_peer[a.ar_me] + a.ar_flag_ofs) + tile * 8 + li;
+            const unsigned long long t0 = globaltimer_ns();
+            while (ld_acquire_sys(f) < ar_ep) {
+              if (*abort_flag || globaltimer_ns() - t0 > dl) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); break; }
+              __nanosleep(128);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
+          if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag) || *abort_flag) { ok = false; break; }
+          ++xchg_it;
+          const int feat = tile * 128 + li;
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 16) {
+            if (c >= a.M) break;
+            float acc16[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc16[j] = 0.f;
+            for (int r = 0; r < W; ++r) {
+              const uint4* pp = reinterpret_cast<const uint4*>(a.ar_peer[r] + a.ar_part_ofs +
+                                                               (static_cast<size_t>(tile * 128 + li) * BN + c) * 2);
+              const uint4 v0 = pp[0], v1 = pp[1];
+              const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&v0);
+              const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&v1);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f0 = __bfloat1622float2(h0[j]), f1 = __bfloat1622float2(h1[j]);
+                acc16[2 * j] += f0.x; acc16[2 * j + 1] += f0.y; acc16[8 + 2 * j] += f1.x; acc16[8 + 2 * j + 1] += f1.y;
+              }
+            }
+            // transpose the 128-feature x 16-token chunk through shared memory so every peer gets
+            // whole 256-byte row segments (16-byte stores) instead of scattered 2-byte stores
+            __nv_bfloat16* tsm = reinterpret_cast<__nv_bfloat16*>(fac_smem);       // [16 tokens][128 features]
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float v = acc16[j];
+              if (resid && feat < a.N && c + j < a.M) v += __bfloat162float(resid[static_cast<size_t>(c + j) * a.ldy + feat]);
+              tsm[j * 128 + li] = __float2bfloat16(v);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
+            if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) { ok = false; break; }
+            ++xchg_it;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              const int u = li * 2 + q;              // 256 units of 16 bytes
+              const int row = u >> 4, col = (u & 15) * 8;
+              if (c + row < a.M && tile * 128 + col + 8 <= a.N) {
+                const uint4 v = *reinterpret_cast<const uint4*>(tsm + row * 128 + col);
+                const size_t o = static_cast<size_t>(c + row) * a.ldy + tile * 128 + col;
+                for (int p = 0; p < W; ++p) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.ar_peer[p] + a.ar_y_ofs) + o) = v;
+              }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
+            if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) { ok = false; break; }
+            ++xchg_it;
+          }
+          if (!ok) break;
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
+          if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) { ok = false; break; }
+          ++xchg_it;
+          if (li < W) red_add_release_sys(reinterpret_cast<uint32_t*>(a.ar_peer[li] + a.ar_done_ofs), 1u);
+        }
+        // the kernel ends on this rank only when every tile of this launch has landed here
+        if (blockIdx.x == 0 && li == 0) {
+          const uint32_t* d = reinterpret_cast<const uint32_t*>(a.ar_peer[a.ar_me] + a.ar_done_ofs);
+          const unsigned long long t0 = globaltimer_ns();
+          while (ld_acquire_sys(d) < ar_ep * static_cast<uint32_t>(n_tiles)) {
+            if (globaltimer_ns() - t0 > dl) { atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); break; }
+            __nanosleep(128);
+          }
+          *a.ar_epoch = ar_ep;
+        }
       }
     }
   }

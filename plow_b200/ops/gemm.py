@@ -60,7 +60,7 @@ def pick_splits(M, N, K, fp8, dual, bn) -> int:
 
 def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=None,
          grp_off=None, tile_prefix=None, n_experts=0, swap=None, bn=None, out_f32=False,
-         out_scale=1.0, quant_out=False, rows_hint=None, ld_syq=None, wait=None, yq_out=None, syq_out=None, splits=None):
+         out_scale=1.0, quant_out=False, rows_hint=None, ld_syq=None, wait=None, yq_out=None, syq_out=None, splits=None, ar=None):
     """y = x @ w.T with the epilogue options of the kernel.
 
     x [M, K] bf16 or e4m3; w [(E*)N(*2), K] same dtype.  ``dual`` computes silu(gate)*up with
@@ -69,7 +69,8 @@ def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=N
     (yq e4m3, syq transposed scales) instead of bf16.  ``rows_hint``: expected rows per expert
     used to pick the token tile in grouped swap mode.  ``wait`` = (counter ptr, epoch ptr, multiplier,
     deadline ms): the kernel starts reading x once ``*counter >= *epoch * multiplier`` (rows written by
-    peer GPUs during expert-parallel dispatch).
+    peer GPUs during expert-parallel dispatch).  ``ar``: fuse the tensor-parallel all-reduce of the
+    result into the kernel (see plow_b200/parallel/tp.py).
     """
     lib = native.cuda_lib()
     assert x.is_cuda and w.is_cuda and x.dim() == 2 and w.dim() == 2
@@ -98,6 +99,8 @@ def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=N
         y = out if out is not None else torch.empty(
             M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
     ws = ws_ctr = None
+    if ar is not None:
+        splits = 1
     if swap and E == 0:
         if splits is None:
             splits = pick_splits(M, N, K, fp8, dual, bn)
@@ -117,6 +120,13 @@ def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=N
         wait_ctr=(wait[0] if wait else None), wait_epoch=(wait[1] if wait else None),
         wait_mult=(int(wait[2]) if wait else 0), wait_deadline_ms=(int(wait[3]) if wait else 0))
     native.LAUNCHES["n"] += 1
+    if ar is not None:
+        # ar: dict(peers=[ptr...], part_ofs, flag_ofs, done_ofs, y_ofs, epoch_ptr, world, me)
+        for i, pz in enumerate(ar["peers"]):
+            d.ar_peer[i] = pz
+        d.ar_part_ofs, d.ar_flag_ofs, d.ar_done_ofs, d.ar_y_ofs = ar["part_ofs"], ar["flag_ofs"], ar["done_ofs"], ar["y_ofs"]
+        d.ar_epoch, d.ar_world, d.ar_me = ar["epoch_ptr"], ar["world"], ar["me"]
+        d.wait_deadline_ms = ar.get("deadline_ms", 2000)
     rc = lib.plow_gemm(C.byref(d), native.stream_ptr())
     if rc != 0:
         raise native.NativeLibraryError(f"plow_gemm failed with code {rc} (bn={bn} swap={swap} dual={dual} fp8={fp8})")

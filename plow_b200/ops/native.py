@@ -31,6 +31,8 @@ class GemmDesc(C.Structure):
         ("dtype", C.c_int32), ("dual", C.c_int32), ("swap", C.c_int32), ("bn", C.c_int32),
         ("out_f32", C.c_int32), ("out_scale", C.c_float),
         ("ws", C.c_void_p), ("ws_ctr", C.c_void_p), ("splits", C.c_int32), ("ws_pad", C.c_int32),
+        ("ar_peer", C.c_void_p * 8), ("ar_part_ofs", C.c_uint64), ("ar_flag_ofs", C.c_uint64), ("ar_done_ofs", C.c_uint64),
+        ("ar_y_ofs", C.c_uint64), ("ar_epoch", C.c_void_p), ("ar_world", C.c_int32), ("ar_me", C.c_int32),
         ("wait_ctr", C.c_void_p), ("wait_epoch", C.c_void_p), ("wait_mult", C.c_int32), ("wait_deadline_ms", C.c_int32),
     ]
 
