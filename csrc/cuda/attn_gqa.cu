@@ -1,0 +1,511 @@
+// Grouped-query flash attention over a paged bf16 KV cache, on tcgen05 — one kernel for prefill and
+// decode — plus the fused head-norm + RoPE + cache-write row op that feeds it.
+//
+// The step's query rows arrive as q[row][head][HD]; each row carries (slot, position) and attends
+// to the cached positions t <= position of its slot (optionally t > position - window), which makes
+// prefill causal and decode a one-row special case of the same rule.  The 128 TMEM lanes of a CTA
+// hold (token, group head) pairs of ONE kv head: 128/group consecutive tokens of a sequence times
+// the `group` query heads that share the kv head.  Per 64-token cache page:
+//     S[128 x 64]  = Q[128 x HD] . K[64 x HD]^T           (UMMA, both operands in shared memory)
+//     P            = 2^(S*scale*log2e - m)                (lane = row: no cross-thread reduction)
+//     O[128 x HD] += P[128 x 64] . V[64 x HD]             (UMMA, P read from TMEM as the A operand,
+//                                                          V as an MN-major B operand)
+// K and V tiles come straight from the paged cache by TMA (3-D maps: HD x kv_heads x tokens), Q by
+// one 3-D TMA per 64-column slab whose box is (64, group, 128/group), so shared memory receives the
+// rows already ordered token-major / head-minor.  The accumulator is rescaled lazily (only when the
+// running maximum grows by more than 2^7), as in the latent-attention decode kernel.
+//
+// Work items (row chunk, kv head, kv split) are built on the device from (slot, position), so the
+// op can sit inside a captured decode graph; splits write normalised f32 partials + log-sum-exp and
+// `gqa_merge_kernel` folds them (gm = max m_s; O = sum O_s 2^(lse_s - gm) / sum 2^(lse_s - gm)).
+// Reference semantics: runtime/common/dev_isa.h:185-222 (split-KV partials + FLASH_MERGE, decode
+// with kv_len / window) and :74-84 (HEADNORM_ROPE writing the cache row directly); the reference's
+// own sm_120 kernels are mma.sync flash kernels (runtime/nvidia/op_attention*.cuh).
+#include <cuda_bf16.h>
+
+#include "ptx.cuh"
+#include "tmap.cuh"
+
+namespace plow {
+
+constexpr int kGqaPage = 64;
+constexpr int kGqaThreads = 192;   // TMA warp, MMA warp, 4 softmax warps
+
+struct GqaItem { int r0, nt, kvh, split, tile0, ntiles, slot, ns; };
+
+struct GqaArgs {
+  const int* page_table;   // [n_slots][max_pages]
+  const int* pos;          // [rows]
+  const GqaItem* items;
+  const int* n_items;
+  float* opart;            // [rows][nq][max_splits][HD] normalised partial outputs
+  float* lse;              // [rows][nq][max_splits] log2-domain log-sum-exp
+  __nv_bfloat16* out;      // [rows][nq*HD]
+  int* status;
+  int rows, nq, nkv, group, max_pages, max_splits, window;
+  float scale_log2e;
+};
+
+template <int HD> struct GqaCfg {
+  static constexpr int kSlabs = HD / 64;                 // 64-column (128-byte) slabs per row
+  static constexpr int kQBytes = kSlabs * 128 * 128;
+  static constexpr int kKBytes = kSlabs * 64 * 128;      // one K (or V) tile
+  static constexpr int kStageBytes = 2 * kKBytes;
+  static constexpr int kStages = HD == 128 ? 5 : 2;
+  static constexpr int kSmem = 1024 + kQBytes + kStages * kStageBytes + 1024;
+  static constexpr int kTmemCols = HD == 128 ? 256 : 512; // S: 2 x 64, O: HD
+};
+
+// ---------------------------------------------------------------------------------------------
+// A chunk starts at every multiple of tq rows and wherever the (slot, position) run breaks, so a
+// row can tell locally whether it starts one; that thread emits the chunk's items.
+__global__ void gqa_build_items(const int* seq, const int* pos, int rows, int tq, int nkv, int window,
+                                int tiles_per_split, int max_splits, GqaItem* items, int* n_items,
+                                int* row_ns, int cap, int* status) {
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += gridDim.x * blockDim.x) {
+    if (pos[r] < 0) { row_ns[r] = 0; continue; }
+    const bool start = (r % tq == 0) || pos[r - 1] < 0 || seq[r] != seq[r - 1] || pos[r] != pos[r - 1] + 1;
+    if (!start) continue;
+    int nt = 1;
+    while ((r + nt) % tq != 0 && r + nt < rows && seq[r + nt] == seq[r] && pos[r + nt] == pos[r + nt - 1] + 1) ++nt;
+    const int hi = pos[r + nt - 1];
+    const int lo = window > 0 ? max(0, pos[r] - window + 1) : 0;
+    const int tile_lo = lo / kGqaPage;
+    const int tiles = hi / kGqaPage + 1 - tile_lo;
+    int ns = min(max_splits, (tiles + tiles_per_split - 1) / tiles_per_split);
+    const int per = (tiles + ns - 1) / ns;
+    ns = (tiles + per - 1) / per;
+    for (int j = 0; j < nt; ++j) row_ns[r + j] = ns;
+    const int base = atomicAdd(n_items, nkv * ns);
+    if (base + nkv * ns > cap) { atomicCAS(status, 0, PLOW_ERR_BOUNDS); continue; }
+    for (int h = 0; h < nkv; ++h)
+      for (int s = 0; s < ns; ++s)
+        items[base + h * ns + s] = GqaItem{r, nt, h, s, tile_lo + s * per, min(per, tiles - s * per), seq[r], ns};
+  }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kGqaThreads, 1)
+gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v) {
+  using Cfg = GqaCfg<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* q_smem = smem;
+  uint8_t* kv_smem = smem + Cfg::kQBytes;
+  uint8_t* ctrl = kv_smem + Cfg::kStages * Cfg::kStageBytes;
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(ctrl);
+  uint64_t* q_empty = q_full + 1;
+  uint64_t* kv_full = q_empty + 1;                 // [kStages]
+  uint64_t* kv_empty = kv_full + Cfg::kStages;     // [kStages]
+  uint64_t* s_full = kv_empty + Cfg::kStages;      // [2]
+  uint64_t* p_full = s_full + 2;                   // [2]
+  uint64_t* pv_done = p_full + 2;                  // [2] by tile parity
+  uint64_t* o_free = pv_done + 2;                  // [1]
+  uint64_t* drain_bar = o_free + 1;                // [1]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  volatile int* never_flag = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
+    for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 4); mbar_init(&pv_done[b], 1); }
+    mbar_init(o_free, 4);
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    *never_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 1) { tmem_alloc(tmem_holder, Cfg::kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tm_s = tmem_base;         // S buffers [0,64) and [64,128); P (bf16 pairs) over the first 32 of each
+  const uint32_t tm_o = tmem_base + 128;   // O: HD columns
+  const int n_items = *a.n_items;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      uint32_t item_it = 0, kv_it = 0;
+      bool ok = true;
+      for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x, ++item_it) {
+        const GqaItem w = a.items[it];
+        if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT); break; }
+        mbar_expect_tx(q_full, Cfg::kQBytes);
+        for (int c = 0; c < Cfg::kSlabs; ++c) tma_load_3d(q_smem + c * 16384, &tm_q, c * 64, w.kvh * a.group, w.r0, q_full);
+        const int* pt = a.page_table + static_cast<size_t>(w.slot) * a.max_pages;
+        int page_next = pt[w.tile0];
+        for (int i = 0; i < w.ntiles; ++i, ++kv_it) {
+          const int s = kv_it % Cfg::kStages;
+          const int page = page_next;
+          if (i + 1 < w.ntiles) page_next = pt[w.tile0 + i + 1];
+          if (!mbar_wait(&kv_empty[s], ((kv_it / Cfg::kStages) & 1) ^ 1, abort_flag)) {
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT); ok = false; break;
+          }
+          uint8_t* st = kv_smem + s * Cfg::kStageBytes;
+          mbar_expect_tx(&kv_full[s], Cfg::kStageBytes);
+          for (int c = 0; c < Cfg::kSlabs; ++c) {
+            tma_load_3d(st + c * 8192, &tm_k, c * 64, w.kvh, page * kGqaPage, &kv_full[s]);
+            tma_load_3d(st + Cfg::kKBytes + c * 8192, &tm_v, c * 64, w.kvh, page * kGqaPage, &kv_full[s]);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc_qk = umma_idesc(128, 64, 1, 1);
+      const uint32_t idesc_pv = umma_idesc(128, HD, 1, 1, 0, 1);
+      uint32_t item_it = 0, kv_it = 0, tile_it = 0;
+      bool ok = true;
+      auto issue_qk = [&](uint32_t kvi, uint32_t ti) -> bool {
+        const int s = kvi % Cfg::kStages;
+        if (!mbar_wait(&kv_full[s], (kvi / Cfg::kStages) & 1, abort_flag)) { atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); return false; }
+        tc_fence_after();
+        // S buffer ti&1 (and the P written over it) was last read by P.V of tile ti-2, issued
+        // before this point; the tensor pipe executes in order.
+        const uint32_t d = tm_s + (ti & 1) * 64;
+        const uint32_t qa = smem_u32(q_smem), ka = smem_u32(kv_smem + s * Cfg::kStageBytes);
+#pragma unroll
+        for (int c = 0; c < Cfg::kSlabs; ++c) {
+          const uint64_t qd = umma_desc_k128(qa + c * 16384), kd = umma_desc_k128(ka + c * 8192);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) tc_mma_f16(d, qd + 2 * k, kd + 2 * k, idesc_qk, (c | k) != 0);
+        }
+        tc_commit(&s_full[ti & 1]);
+        return true;
+      };
+      for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x, ++item_it) {
+        const GqaItem w = a.items[it];
+        if (!mbar_wait(q_full, item_it & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); break; }
+        tc_fence_after();
+        if (!issue_qk(kv_it, tile_it)) { *abort_flag = 1; break; }
+        for (int i = 0; i < w.ntiles; ++i) {
+          if (i + 1 < w.ntiles) {
+            if (!issue_qk(kv_it + i + 1, tile_it + i + 1)) { *abort_flag = 1; ok = false; break; }
+          } else {
+            tc_commit(q_empty);   // all QK^T of this item are issued: Q may be overwritten once they retire
+          }
+          const uint32_t ti = tile_it + i;
+          if (i == 0 && !mbar_wait(o_free, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_FREE_WAIT); ok = false; break; }
+          if (!mbar_wait(&p_full[ti & 1], (ti >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
+          tc_fence_after();
+          const int s = (kv_it + i) % Cfg::kStages;
+          const uint32_t pt = tm_s + (ti & 1) * 64;   // P: 32 columns = 64 tokens of bf16
+          const uint32_t va = smem_u32(kv_smem + s * Cfg::kStageBytes + Cfg::kKBytes);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)   // 16 tokens per MMA: two 8-token groups of 1024 bytes
+            tc_mma_f16_ts(tm_o, pt + j * 8, umma_desc_mn128(va + j * 2048, 8192, 1024), idesc_pv, (i | j) != 0);
+          tc_commit(&kv_empty[s]);
+          tc_commit(&pv_done[ti & 1]);
+        }
+        kv_it += w.ntiles;
+        tile_it += w.ntiles;
+      }
+      if (!ok || *abort_flag) { tc_commit(drain_bar); mbar_wait(drain_bar, 0, never_flag); }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / epilogue warps
+    const int lq = warp & 3;           // TMEM lane quarter this warp may access
+    const int li = lq * 32 + lane;     // row of the tile: token li / group, query head li % group
+    const uint32_t lane_addr = static_cast<uint32_t>(lq * 32) << 16;
+    uint32_t item_it = 0, tile_it = 0;
+    bool ok = true;
+    for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x, ++item_it) {
+      const GqaItem w = a.items[it];
+      const int n_valid = w.nt * a.group;
+      const bool warp_active = lq * 32 < n_valid;       // whole warp: rows past the chunk are never read
+      const int tok = min(li / a.group, w.nt - 1);
+      const int hi = a.pos[w.r0 + tok];
+      const int lo = a.window > 0 ? max(0, hi - a.window + 1) : 0;
+      float m = -1e30f, l = 0.f;
+      for (int i = 0; i < w.ntiles; ++i) {
+        const uint32_t ti = tile_it + i;
+        if (!mbar_wait(&s_full[ti & 1], (ti >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
+        tc_fence_after();
+        if (warp_active) {
+          uint32_t sv[64];
+          tmem_ld32(tm_s + lane_addr + (ti & 1) * 64, sv);
+          tmem_ld32(tm_s + lane_addr + (ti & 1) * 64 + 32, sv + 32);
+          tmem_ld_wait();
+          const int t0 = (w.tile0 + i) * kGqaPage;
+          float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          if (t0 >= lo && t0 + kGqaPage - 1 <= hi) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+              const float x = __uint_as_float(sv[j]) * a.scale_log2e;
+              sv[j] = __float_as_uint(x);
+              mxa[j & 3] = fmaxf(mxa[j & 3], x);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+              const int t = t0 + j;
+              const float x = (t >= lo && t <= hi) ? __uint_as_float(sv[j]) * a.scale_log2e : -INFINITY;
+              sv[j] = __float_as_uint(x);
+              mxa[j & 3] = fmaxf(mxa[j & 3], x);
+            }
+          }
+          const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
+          // lazy rescale: m only moves when a tile exceeds it by more than 2^kTau, so P <= 2^kTau
+          // and the accumulator in TMEM is rarely touched
+          constexpr float kTau = 7.0f;
+          const bool up = mx > m + kTau;
+          if (__any_sync(0xffffffffu, up)) {
+            const float m_new = up ? mx : m;
+            const float alpha = exp2f(m - m_new);
+            l *= alpha;
+            m = m_new;
+            if (i > 0) {
+              // the accumulator must be quiescent: P.V of the previous tile has retired
+              if (!mbar_wait(&pv_done[(ti - 1) & 1], ((ti - 1) >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
+              tc_fence_after();
+#pragma unroll 1
+              for (int c = 0; c < HD; c += 32) {
+                uint32_t o[32];
+                tmem_ld32(tm_o + lane_addr + c, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+                tmem_st16(tm_o + lane_addr + c, o);
+                tmem_st16(tm_o + lane_addr + c + 16, o + 16);
+              }
+              tmem_st_wait();
+              tc_fence_before();
+            }
+          }
+          float sa = 0.f, sb = 0.f;
+          uint32_t pk[32];
+#pragma unroll
+          for (int j = 0; j < 64; j += 2) {
+            const float e0 = exp2f(__uint_as_float(sv[j]) - m), e1 = exp2f(__uint_as_float(sv[j + 1]) - m);
+            sa += e0; sb += e1;
+            const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+            pk[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+          l += sa + sb;
+          tmem_st16(tm_s + lane_addr + (ti & 1) * 64, pk);
+          tmem_st16(tm_s + lane_addr + (ti & 1) * 64 + 16, pk + 16);
+          tmem_st_wait();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[ti & 1]);
+      }
+      if (!ok) break;
+      // ---- finalize: O / l, written directly (one split) or as a partial with its log-sum-exp
+      const uint32_t ti_last = tile_it + w.ntiles - 1;
+      if (!mbar_wait(&pv_done[ti_last & 1], (ti_last >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); break; }
+      tc_fence_after();
+      if (warp_active) {
+        const bool row_ok = li < n_valid;
+        const int row = w.r0 + li / a.group;
+        const int head = w.kvh * a.group + li % a.group;
+        const float fin = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t o[32];
+          __syncwarp();
+          tmem_ld32(tm_o + lane_addr + c, o);
+          tmem_ld_wait();
+          if (!row_ok) continue;
+          if (w.ns == 1) {
+            uint32_t h2[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(o[2 * j]) * fin, __uint_as_float(o[2 * j + 1]) * fin);
+              h2[j] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(a.out + (static_cast<size_t>(row) * a.nq + head) * HD + c);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) dst[q] = make_uint4(h2[4 * q], h2[4 * q + 1], h2[4 * q + 2], h2[4 * q + 3]);
+          } else {
+            float4* dst = reinterpret_cast<float4*>(a.opart + ((static_cast<size_t>(row) * a.nq + head) * a.max_splits + w.split) * HD + c);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              dst[q] = make_float4(__uint_as_float(o[4 * q]) * fin, __uint_as_float(o[4 * q + 1]) * fin,
+                                   __uint_as_float(o[4 * q + 2]) * fin, __uint_as_float(o[4 * q + 3]) * fin);
+          }
+        }
+        if (row_ok && w.ns > 1)
+          a.lse[(static_cast<size_t>(row) * a.nq + head) * a.max_splits + w.split] = l > 0.f ? m + log2f(l) : -INFINITY;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_free);
+      tile_it += w.ntiles;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) {}
+  }
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, Cfg::kTmemCols); }
+}
+
+// out[row][head][:] = sum_s 2^(lse_s - gm) opart_s / sum_s 2^(lse_s - gm) for rows that were split.
+__global__ void gqa_merge_kernel(const float* opart, const float* lse, const int* row_ns, int nq, int max_splits,
+                                 int hd, __nv_bfloat16* out) {
+  const int row = blockIdx.x, head = blockIdx.y;
+  const int ns = row_ns[row];
+  if (ns <= 1) return;
+  const size_t base = (static_cast<size_t>(row) * nq + head) * max_splits;
+  float gm = -INFINITY;
+  for (int s = 0; s < ns; ++s) gm = fmaxf(gm, lse[base + s]);
+  if (gm == -INFINITY) gm = 0.f;
+  float wsum = 0.f;
+  for (int s = 0; s < ns; ++s) wsum += exp2f(lse[base + s] - gm);
+  const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
+  for (int c = threadIdx.x; c < hd; c += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < ns; ++s) acc += exp2f(lse[base + s] - gm) * opart[(base + s) * hd + c];
+    out[(static_cast<size_t>(row) * nq + head) * hd + c] = __float2bfloat16(acc * inv);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// One warp per (row, head) of the fused qkv row: optional per-head RMSNorm, RoPE, then q goes to
+// q_out[row][head][hd] and k / v go straight into their cache cells.
+__global__ void rope_kv_kernel(__nv_bfloat16* q_out, const __nv_bfloat16* qkv, int ld_qkv, __nv_bfloat16* kc,
+                               __nv_bfloat16* vc, const __nv_bfloat16* qn, const __nv_bfloat16* kn,
+                               const float* rope_tab, const int* pos, const int* seq, const int* page_table,
+                               int max_pages, int rows, int nq, int nkv, int hd, int rot, int pair_mode,
+                               int plus_one, float eps) {
+  extern __shared__ float rk_smem[];
+  const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = nq + 2 * nkv;
+  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + wib;
+  if (item >= static_cast<long long>(rows) * heads) return;
+  const int r = static_cast<int>(item / heads), h = static_cast<int>(item % heads);
+  const int p = pos[r];
+  if (p < 0) return;
+  float* buf = rk_smem + wib * hd;
+  const __nv_bfloat16* src = qkv + static_cast<size_t>(r) * ld_qkv + static_cast<size_t>(h) * hd;
+  __nv_bfloat16* dst;
+  const __nv_bfloat16* gamma = nullptr;
+  const bool is_v = h >= nq + nkv;
+  if (h < nq) {
+    dst = q_out + (static_cast<size_t>(r) * nq + h) * hd;
+    gamma = qn;
+  } else {
+    const int kh = is_v ? h - nq - nkv : h - nq;
+    const int page = page_table[static_cast<size_t>(seq[r]) * max_pages + p / kGqaPage];
+    const size_t cell = ((static_cast<size_t>(page) * kGqaPage + p % kGqaPage) * nkv + kh) * hd;
+    dst = (is_v ? vc : kc) + cell;
+    gamma = kn;
+  }
+  if (is_v) {
+    for (int i = lane; i < hd / 8; i += 32) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    return;
+  }
+  float ss = 0.f;
+  for (int i = lane; i < hd; i += 32) { const float v = __bfloat162float(src[i]); buf[i] = v; ss += v * v; }
+  if (gamma) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rs = rsqrtf(ss / hd + eps);
+    __syncwarp();
+    // the normalised value is rounded to bf16 before the rotation, as the unfused pair would do
+    for (int i = lane; i < hd; i += 32) {
+      const float g = __bfloat162float(gamma[i]);
+      buf[i] = __bfloat162float(__float2bfloat16(buf[i] * rs * (plus_one ? 1.0f + g : g)));
+    }
+  }
+  __syncwarp();
+  const int half = rot / 2;
+  const float* tab = rope_tab + static_cast<size_t>(p) * rot;
+  for (int i = lane; i < half; i += 32) {
+    const int ia = pair_mode ? 2 * i : i, ib = pair_mode ? 2 * i + 1 : i + half;
+    const float x = buf[ia], y = buf[ib], c = tab[i], s = tab[half + i];
+    dst[ia] = __float2bfloat16(x * c - y * s);
+    dst[ib] = __float2bfloat16(y * c + x * s);
+  }
+  for (int i = rot + lane; i < hd; i += 32) dst[i] = __float2bfloat16(buf[i]);
+}
+
+template <int HD>
+int launch_gqa(const GqaArgs& a, const void* q, const void* kc, const void* vc, int64_t n_pages, int grid, cudaStream_t stream) {
+  using Cfg = GqaCfg<HD>;
+  CUtensorMap tq, tk, tv;
+  int r = make_tmap_3d(&tq, q, 2, HD, a.nq, a.rows, HD * 2, static_cast<uint64_t>(a.nq) * HD * 2, a.group, 128 / a.group, 128);
+  if (r) return 1100 + r;
+  r = make_tmap_3d(&tk, kc, 2, HD, a.nkv, static_cast<uint64_t>(n_pages) * kGqaPage, HD * 2, static_cast<uint64_t>(a.nkv) * HD * 2, 1, kGqaPage, 128);
+  if (r) return 1200 + r;
+  r = make_tmap_3d(&tv, vc, 2, HD, a.nkv, static_cast<uint64_t>(n_pages) * kGqaPage, HD * 2, static_cast<uint64_t>(a.nkv) * HD * 2, 1, kGqaPage, 128);
+  if (r) return 1300 + r;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(gqa_attn_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem) != cudaSuccess) return 3000;
+    attr = true;
+  }
+  gqa_attn_kernel<HD><<<grid, kGqaThreads, Cfg::kSmem, stream>>>(a, tq, tk, tv);
+  return 0;
+}
+
+}  // namespace plow
+
+extern "C" {
+
+// q bf16 [rows][nq][hd]; kc / vc bf16 [n_pages][64][nkv][hd]; seq / pos int32 [rows] (pos < 0: inactive row);
+// out bf16 [rows][nq*hd].  Scratch from the caller: items (8 ints each, capacity item_cap), n_items (1 int),
+// row_ns int32 [rows], opart f32 [rows][nq][max_splits][hd], lse f32 [rows][nq][max_splits].
+int plow_gqa_attention(const void* q, const void* kc, const void* vc, int64_t n_pages, const int* page_table,
+                       int max_pages, const int* seq, const int* pos, int rows, int nq, int nkv, int hd, int window,
+                       int tiles_per_split, int max_splits, void* items, int item_cap, int* n_items, int* row_ns,
+                       float* opart, float* lse, void* out, float softmax_scale, int* status, void* stream_) {
+  using namespace plow;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (rows <= 0 || nq <= 0 || nkv <= 0 || nq % nkv || max_splits <= 0 || tiles_per_split <= 0) return -1;
+  const int group = nq / nkv;
+  if (group > 128 || (group & (group - 1))) return -2;
+  if (hd != 128 && hd != 256) return -3;
+  const int tq = 128 / group;
+  cudaMemsetAsync(n_items, 0, sizeof(int), stream);
+  gqa_build_items<<<(rows + 255) / 256, 256, 0, stream>>>(seq, pos, rows, tq, nkv, window, tiles_per_split, max_splits,
+                                                         static_cast<GqaItem*>(items), n_items, row_ns, item_cap, status);
+  GqaArgs a;
+  a.page_table = page_table; a.pos = pos; a.items = static_cast<const GqaItem*>(items); a.n_items = n_items;
+  a.opart = opart; a.lse = lse; a.out = static_cast<__nv_bfloat16*>(out); a.status = status;
+  a.rows = rows; a.nq = nq; a.nkv = nkv; a.group = group; a.max_pages = max_pages; a.max_splits = max_splits; a.window = window;
+  a.scale_log2e = softmax_scale * 1.4426950408889634f;
+  int grid = sm_count();
+  if (item_cap < grid) grid = item_cap;
+  int r = hd == 128 ? launch_gqa<128>(a, q, kc, vc, n_pages, grid, stream) : launch_gqa<256>(a, q, kc, vc, n_pages, grid, stream);
+  if (r) return r;
+  if (max_splits > 1)
+    gqa_merge_kernel<<<dim3(rows, nq), 128, 0, stream>>>(opart, lse, row_ns, nq, max_splits, hd, static_cast<__nv_bfloat16*>(out));
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
+}
+
+// qkv bf16 [rows][ld_qkv] = [q heads | k heads | v heads]; qn / kn: optional per-head RMSNorm weights [hd];
+// rope_tab f32 [max_pos][rot] = [cos(rot/2) | sin(rot/2)]; pair_mode 0 = half split, 1 = interleaved.
+int plow_rope_kv(void* q_out, const void* qkv, int ld_qkv, void* kc, void* vc, const void* qn, const void* kn,
+                 const float* rope_tab, const int* pos, const int* seq, const int* page_table, int max_pages,
+                 int rows, int nq, int nkv, int hd, int rot, int pair_mode, int plus_one, float eps, void* stream_) {
+  using namespace plow;
+  if (rows <= 0 || hd % 8 || rot > hd || rot % 2) return -1;
+  const long long items = static_cast<long long>(rows) * (nq + 2 * nkv);
+  const int wpb = 8;
+  rope_kv_kernel<<<static_cast<unsigned>((items + wpb - 1) / wpb), wpb * 32, wpb * hd * sizeof(float),
+                   reinterpret_cast<cudaStream_t>(stream_)>>>(
+      static_cast<__nv_bfloat16*>(q_out), static_cast<const __nv_bfloat16*>(qkv), ld_qkv, static_cast<__nv_bfloat16*>(kc),
+      static_cast<__nv_bfloat16*>(vc), static_cast<const __nv_bfloat16*>(qn), static_cast<const __nv_bfloat16*>(kn),
+      rope_tab, pos, seq, page_table, max_pages, rows, nq, nkv, hd, rot, pair_mode, plus_one, eps);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
+}
+
+}  // extern "C"

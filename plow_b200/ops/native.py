@@ -120,6 +120,8 @@ _SIGS = {
     "plow_ep_y_ready": "pp",
     "plow_ep_combine": "pppppiip",
     "plow_wait_probe": "piLpp",
+    "plow_gqa_attention": "ppplpipp" "iiiiiii" "pi" "ppppp" "fpp",
+    "plow_rope_kv": "ppi" "pppppppp" "i" "iiiiiii" "fp",
 }
 _CT = {"p": C.c_void_p, "i": C.c_int32, "l": C.c_int64, "f": C.c_float, "L": C.c_uint64}
 
@@ -133,7 +135,7 @@ def _arg(v):
 
 
 LAUNCHES = {"n": 0}                       # kernels launched through this module (bench bookkeeping)
-_KERNELS_PER_CALL = {"plow_mla_decode": 2}
+_KERNELS_PER_CALL = {"plow_mla_decode": 2, "plow_gqa_attention": 2}
 
 
 def call(name: str, *args) -> None:

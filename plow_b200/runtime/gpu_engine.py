@@ -23,7 +23,7 @@ import torch
 
 from ..compiler import packet as pk
 from ..compiler.packet import Op
-from ..ops import gemm as gemm_ops, mla as mla_ops, native, quant, rowops
+from ..ops import gemm as gemm_ops, gqa as gqa_ops, mla as mla_ops, native, quant, rowops
 from ..utils.rope import rope_table
 from .engine import EngineBase, EngineError, StepResult, TokenBatch
 from .kv_pages import PAGE
@@ -393,6 +393,28 @@ class GpuEngine(EngineBase):
         if want:
             st.q[(ins.t[0], 0)] = (aq, saq)
 
+    # -- GQA
+    def _op_rope_kv(self, st, ins):
+        q_out, qkv, kc, vc = (self.tensor(st, ins.t[k]) for k in range(4))
+        qn = self.tensor(st, ins.t[4]) if ins.t[4] != pk.T_NONE else None
+        kn = self.tensor(st, ins.t[5]) if ins.t[5] != pk.T_NONE else None
+        rope = self.tensor(st, ins.t[6])
+        nq, nkv, hd, rot, pair, plus_one = ins.i[0], ins.i[1], ins.i[2], ins.i[3], ins.i[4], ins.i[6]
+        if kc.dtype != BF16:
+            raise EngineError("the sm_100a GQA kernels read a bf16 KV cache; compile with plow_kv_dtype=bf16")
+        gqa_ops.rope_kv(qkv, kc, vc, rope, self.d_in[1], self.d_in[2], self.d_page_table, nq, nkv, hd, rot=rot,
+                        pair_mode=pair, qn=qn, kn=kn, eps=float(ins.f[0]), plus_one=bool(plus_one),
+                        q_out=q_out.view(st.rows, nq, hd))
+
+    def _op_attn(self, st, ins):
+        ao, q, kc, vc = (self.tensor(st, ins.t[k]) for k in range(4))
+        nq, nkv, hd, window = ins.i[0], ins.i[1], ins.i[2], ins.i[3]
+        key = ("gqa_ws", nq, nkv, hd)
+        if key not in st.scratch:
+            st.scratch[key] = gqa_ops.AttnWorkspace(st.rows, nq, nkv, hd, self.max_ctx + PAGE, self.device)
+        gqa_ops.attention(q.view(st.rows, nq, hd), kc, vc, self.d_page_table, self.d_in[2], self.d_in[1], st.scratch[key],
+                          scale=float(ins.f[0]), window=window, out=ao)
+
     # -- MoE
     def _op_router_topk(self, st, ins):
         table, logits = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])
@@ -445,6 +467,7 @@ class GpuEngine(EngineBase):
     HANDLERS = {
         Op.EMBED: "_op_embed", Op.RMSNORM: "_op_rmsnorm", Op.ADD_NORM: "_op_add_norm", Op.RESIDUAL: "_op_residual",
         Op.GEMM: "_op_gemm", Op.ROW_GATHER: "_op_row_gather", Op.ARGMAX: "_op_argmax",
+        Op.ROPE_KV: "_op_rope_kv", Op.ATTN: "_op_attn",
         Op.MLA_KV_WRITE: "_op_mla_kv_write", Op.MLA_DECODE: "_op_mla_attention", Op.MLA_PREFILL: "_op_mla_attention",
         Op.ROUTER_TOPK: "_op_router_topk", Op.MOE_GEMM: "_op_moe_experts", Op.NOP: None,
     }

@@ -1,0 +1,105 @@
+"""GQA flash attention + fused RoPE/cache-write kernels against plain PyTorch fp32 (GPU)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _err(a, b):
+    return (a.float() - b.float()).abs().max().item() / max(1e-6, b.float().abs().max().item())
+
+
+@pytest.mark.parametrize("nq,nkv,hd", [(32, 8, 128), (8, 8, 128), (16, 2, 256)])
+def test_decode(nq, nkv, hd):
+    from plow_b200.ops import gqa, native
+    torch.manual_seed(0)
+    n_seq = 5
+    lens = [1, 63, 64, 200, 777]
+    pages_per = 13
+    n_pages = n_seq * pages_per + 1
+    kc = torch.randn(n_pages, 64, nkv, hd, device="cuda").bfloat16()
+    vc = torch.randn(n_pages, 64, nkv, hd, device="cuda").bfloat16()
+    perm = torch.randperm(n_pages - 1, device="cuda").int() + 1
+    pt = perm[: n_seq * pages_per].view(n_seq, pages_per).contiguous()
+    seq = torch.arange(n_seq, dtype=torch.int32, device="cuda")
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device="cuda")
+    q = torch.randn(n_seq, nq, hd, device="cuda").bfloat16()
+    ref = gqa.reference(q, kc, vc, pt, seq, pos)
+    for splits in (1, 4):
+        ws = gqa.AttnWorkspace(n_seq, nq, nkv, hd, 13 * 64, q.device, tiles_per_split=2, max_splits=splits)
+        out = gqa.attention(q, kc, vc, pt, seq, pos, ws)
+        torch.cuda.synchronize()
+        native.check_status()
+        assert _err(out, ref) < 2e-2, (splits, _err(out, ref))
+
+
+@pytest.mark.parametrize("window", [0, 100])
+def test_prefill_causal_mixed_batch(window):
+    from plow_b200.ops import gqa, native
+    torch.manual_seed(1)
+    nq, nkv, hd = 32, 8, 128
+    # three sequences: a fresh 150-token prompt, a 70-token chunk appended at position 90, one decode row; one idle row
+    pages_per = 6
+    n_pages = 4 * pages_per + 1
+    kc = torch.randn(n_pages, 64, nkv, hd, device="cuda").bfloat16()
+    vc = torch.randn(n_pages, 64, nkv, hd, device="cuda").bfloat16()
+    pt = (torch.arange(4 * pages_per, dtype=torch.int32, device="cuda").view(4, pages_per) + 1).contiguous()
+    seq = torch.tensor([0] * 150 + [2] * 70 + [1] + [3], dtype=torch.int32, device="cuda")
+    pos = torch.tensor(list(range(150)) + list(range(90, 160)) + [300] + [-1], dtype=torch.int32, device="cuda")
+    rows = seq.numel()
+    q = torch.randn(rows, nq, hd, device="cuda").bfloat16()
+    ref = gqa.reference(q, kc, vc, pt, seq, pos, window=window)
+    for splits in (1, 3):
+        ws = gqa.AttnWorkspace(rows, nq, nkv, hd, pages_per * 64, q.device, tiles_per_split=1, max_splits=splits)
+        out = torch.zeros(rows, nq * hd, dtype=torch.bfloat16, device="cuda")
+        gqa.attention(q, kc, vc, pt, seq, pos, ws, window=window, out=out)
+        torch.cuda.synchronize()
+        native.check_status()
+        assert _err(out, ref) < 2e-2, (splits, _err(out, ref))
+
+
+@pytest.mark.parametrize("pair_mode,rot,norm", [(0, 128, False), (1, 64, True)])
+def test_rope_kv(pair_mode, rot, norm):
+    from plow_b200.ops import gqa
+    torch.manual_seed(2)
+    nq, nkv, hd, rows = 8, 2, 128, 37
+    qkv = torch.randn(rows, (nq + 2 * nkv) * hd, device="cuda").bfloat16()
+    tab = torch.randn(512, rot, device="cuda")
+    pos = torch.randint(0, 300, (rows,), dtype=torch.int32, device="cuda")
+    seq = torch.arange(rows, dtype=torch.int32, device="cuda")
+    pt = (torch.arange(rows * 5, dtype=torch.int32, device="cuda").view(rows, 5)).contiguous()
+    kc = torch.zeros(rows * 5, 64, nkv, hd, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    qn = torch.randn(hd, device="cuda").bfloat16() if norm else None
+    kn = torch.randn(hd, device="cuda").bfloat16() if norm else None
+    q_out = gqa.rope_kv(qkv, kc, vc, tab, pos, seq, pt, nq, nkv, hd, rot=rot, pair_mode=pair_mode, qn=qn, kn=kn, eps=1e-6)
+    torch.cuda.synchronize()
+
+    def ref_head(x, g, p):
+        x = x.float()
+        if g is not None:
+            x = (x * torch.rsqrt((x * x).mean() + 1e-6) * g.float()).bfloat16().float()
+        half = rot // 2
+        c, s = tab[p, :half], tab[p, half:]
+        y = x.clone()
+        if pair_mode == 0:
+            a, b = x[:half], x[half:rot]
+            y[:half] = a * c - b * s
+            y[half:rot] = b * c + a * s
+        else:
+            a, b = x[0:rot:2], x[1:rot:2]
+            y[0:rot:2] = a * c - b * s
+            y[1:rot:2] = b * c + a * s
+        return y
+    v = qkv.view(rows, nq + 2 * nkv, hd)
+    for r in (0, 5, rows - 1):
+        p = int(pos[r])
+        cell_k = kc[int(pt[r, p // 64]), p % 64]
+        cell_v = vc[int(pt[r, p // 64]), p % 64]
+        for h in (0, nq - 1):
+            assert _err(q_out[r, h], ref_head(v[r, h], qn, p)) < 1e-2
+        for h in range(nkv):
+            assert _err(cell_k[h], ref_head(v[r, nq + h], kn, p)) < 1e-2
+            assert torch.equal(cell_v[h], v[r, nq + nkv + h])
