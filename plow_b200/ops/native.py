@@ -120,6 +120,12 @@ _SIGS = {
     "plow_ep_y_ready": "pp",
     "plow_ep_combine": "pppppiip",
     "plow_wait_probe": "piLpp",
+    "plow_sample": "ppiiipppppp" "Lp",
+    "plow_dsa_k_write": "pppipppppp" "iiiifp",
+    "plow_dsa_select": "ppippp" "ipipplp" "pppiiiiiipp",
+    "plow_gdn": "ppppipi" "ppppp" "iiiiip",
+    "plow_gated_norm": "pppiipiiifp",
+    "plow_sigmoid_gate": "ppplp",
     "plow_gqa_attention": "ppplpipp" "iiiiiii" "pi" "ppppp" "fpp",
     "plow_rope_kv": "ppi" "pppppppp" "i" "iiiiiii" "fp",
 }
@@ -135,7 +141,7 @@ def _arg(v):
 
 
 LAUNCHES = {"n": 0}                       # kernels launched through this module (bench bookkeeping)
-_KERNELS_PER_CALL = {"plow_mla_decode": 2, "plow_gqa_attention": 2}
+_KERNELS_PER_CALL = {"plow_mla_decode": 2, "plow_gqa_attention": 2, "plow_dsa_select": 3}
 
 
 def call(name: str, *args) -> None:
