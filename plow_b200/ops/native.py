@@ -120,6 +120,7 @@ _SIGS = {
     "plow_ep_y_ready": "pp",
     "plow_ep_combine": "pppppiip",
     "plow_wait_probe": "piLpp",
+    "plow_interp_run": "pppppppppp" "IIIIp",
     "plow_sample": "ppiiipppppp" "Lp",
     "plow_dsa_k_write": "pppipppppp" "iiiifp",
     "plow_dsa_select": "ppippp" "ipipplp" "pppiiiiiipp",
@@ -129,7 +130,7 @@ _SIGS = {
     "plow_gqa_attention": "ppplpipp" "iiiiiii" "pi" "ppppp" "fpp",
     "plow_rope_kv": "ppi" "pppppppp" "i" "iiiiiii" "fp",
 }
-_CT = {"p": C.c_void_p, "i": C.c_int32, "l": C.c_int64, "f": C.c_float, "L": C.c_uint64}
+_CT = {"p": C.c_void_p, "i": C.c_int32, "l": C.c_int64, "f": C.c_float, "L": C.c_uint64, "I": C.c_uint32}
 
 
 def _arg(v):

@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import json
 import math
+import os
 from pathlib import Path
 
 import numpy as np
@@ -25,6 +26,7 @@ from ..compiler import packet as pk
 from ..compiler.packet import Op
 from ..ops import gemm as gemm_ops, gqa as gqa_ops, mla as mla_ops, native, quant, rowops
 from ..utils.rope import rope_table
+from .device_interp import DeviceInterp
 from .engine import EngineBase, EngineError, StepResult, TokenBatch
 from .kv_pages import PAGE
 
@@ -126,12 +128,14 @@ class _Prog:
         self.graph = None
         self.needs_q = set()
         self.scratch = {}
+        self.interp = None
+        self.segments = None
 
 
 class GpuEngine(EngineBase):
     def __init__(self, assets_dir=None, packet=None, weights: WeightSource | None = None, max_slots=64, n_pages=None,
                  max_ctx=8192, kv_fraction=0.9, prefix_cache=True, cuda_graphs=True, device=None, rank=0,
-                 comm=None, rungs=None):
+                 comm=None, rungs=None, device_interp=None):
         if not torch.cuda.is_available():
             raise EngineError("GpuEngine needs a CUDA device", fatal=True)
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
@@ -141,6 +145,8 @@ class GpuEngine(EngineBase):
             name = "model.pkt" if rank == 0 else f"model.rank{rank}.pkt"
             packet = pk.read_packet(Path(assets_dir) / name)
         self.rank, self.comm = rank, comm
+        # row-class segments run inside the persistent on-device interpreter (PLOW_DEVICE_INTERP=0 turns it off)
+        self.device_interp = (os.environ.get("PLOW_DEVICE_INTERP", "1") != "0") if device_interp is None else bool(device_interp)
         shards = packet.section_json("weight_shards.json") or {}
         self.tp, self.ep = shards.get("tp", 1), shards.get("ep", 1)
         if weights is None:
@@ -296,6 +302,12 @@ class GpuEngine(EngineBase):
     def _op_residual(self, st, ins):
         out, a, b = (self.tensor(st, ins.t[k]) for k in range(3))
         torch.add(a, b, out=out)
+
+    def _op_glu(self, st, ins):
+        # only reached when gated-mlp fusion is disabled at compile time and the interpreter is off
+        out, g, u = (self.tensor(st, ins.t[k]) for k in range(3))
+        torch.mul(torch.nn.functional.silu(g.float()), u.float(), out=st.scratch.setdefault(("glu", ins.t[0]), torch.empty_like(out, dtype=F32)))
+        out.copy_(st.scratch[("glu", ins.t[0])])
 
     def _op_gemm(self, st, ins):
         y, x = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])
@@ -467,24 +479,53 @@ class GpuEngine(EngineBase):
     HANDLERS = {
         Op.EMBED: "_op_embed", Op.RMSNORM: "_op_rmsnorm", Op.ADD_NORM: "_op_add_norm", Op.RESIDUAL: "_op_residual",
         Op.GEMM: "_op_gemm", Op.ROW_GATHER: "_op_row_gather", Op.ARGMAX: "_op_argmax",
-        Op.ROPE_KV: "_op_rope_kv", Op.ATTN: "_op_attn",
+        Op.ROPE_KV: "_op_rope_kv", Op.ATTN: "_op_attn", Op.GLU: "_op_glu",
         Op.MLA_KV_WRITE: "_op_mla_kv_write", Op.MLA_DECODE: "_op_mla_attention", Op.MLA_PREFILL: "_op_mla_attention",
         Op.ROUTER_TOPK: "_op_router_topk", Op.MOE_GEMM: "_op_moe_experts", Op.NOP: None,
     }
 
+    def _interp_segments(self, st: _Prog):
+        """Cut the program into interpreter segments and role instructions (once per program)."""
+        if st.segments is None:
+            def tensor_of(h):
+                t = st.t.get(h, self.static.get(h))
+                return t if isinstance(t, torch.Tensor) else None
+
+            def eligible(j):
+                ins = st.prog.insts[j]
+                outs = [ins.t[0]] + ([ins.t[4]] if ins.op == Op.ADD_NORM else [])
+                if any(h != pk.T_NONE and self._wants_q(st, h) for h in outs):
+                    return False        # the role kernel emits the e4m3 twin in the same pass
+                acts = [tensor_of(h) for h in ins.t[:5] if h != pk.T_NONE]
+                return all(t is not None for t in acts) and all(
+                    t.dtype in (BF16, I32) or (ins.op == Op.ARGMAX and t.dtype == F32) for t in acts)
+            st.interp = DeviceInterp(self.packet, st.prog, tensor_of, st.rows, st.samples, self.device)
+            st.segments = DeviceInterp.segments(st.prog, eligible)
+        return st.segments
+
     def _run_insts(self, st: _Prog) -> None:
         st.q.clear()
+        if self.device_interp and self.spec.dtype == "bf16":
+            for lo, hi, on_device in self._interp_segments(st):
+                if on_device:
+                    st.interp.run(lo, hi)
+                else:
+                    self._run_one(st, st.prog.insts[lo])
+            return
         for ins in st.prog.insts:
-            name = self.HANDLERS.get(Op(ins.op), "missing")
-            if name is None:
-                continue
-            if name == "missing":
-                fn = getattr(self, "_ext_" + Op(ins.op).name.lower(), None)
-                if fn is None:
-                    raise EngineError(f"opcode {Op(ins.op).name} has no sm_100a body in this build")
-                fn(st, ins)
-            else:
-                getattr(self, name)(st, ins)
+            self._run_one(st, ins)
+
+    def _run_one(self, st: _Prog, ins) -> None:
+        name = self.HANDLERS.get(Op(ins.op), "missing")
+        if name is None:
+            return
+        if name == "missing":
+            fn = getattr(self, "_ext_" + Op(ins.op).name.lower(), None)
+            if fn is None:
+                raise EngineError(f"opcode {Op(ins.op).name} has no sm_100a body in this build")
+            fn(st, ins)
+        else:
+            getattr(self, name)(st, ins)
 
     # ---- step ----------------------------------------------------------------------------------
     def _sync_pages(self, slot: int) -> None:

@@ -20,16 +20,32 @@ def dense_assets(tmp_path_factory):
     d = tmp_path_factory.mktemp("dense")
     reference.write_checkpoint(CFG, d / "ckpt", seed=0, dtype=torch.bfloat16)
     plowc.compile_dir(d / "ckpt", d / "assets", max_rows=256, prefill_buckets=[128, 256], decode_rungs=[4, 8], max_seqs=8)
+    # second build with the row fusions off: RESIDUAL -> RMSNORM and GLU stay separate instructions, so the
+    # on-device interpreter gets multi-instruction segments whose units wait on one another's counters
+    plowc.compile_dir(d / "ckpt", d / "assets_unfused", max_rows=256, prefill_buckets=[128, 256], decode_rungs=[4, 8],
+                      max_seqs=8, disable_rules=("residual-rmsnorm-fuse", "gated-mlp-fuse"))
     return d
 
 
-def test_dense_engine_matches_reference(dense_assets):
+def test_interpreter_segments_cover_row_ops(dense_assets):
+    from plow_b200.compiler import packet as pk
+    from plow_b200.compiler.packet import Op
+    from plow_b200.runtime.device_interp import DeviceInterp
+    pkt = pk.read_packet(dense_assets / "assets_unfused" / "model.pkt")
+    segs = DeviceInterp.segments(pkt.programs[0])
+    assert sum(hi - lo for lo, hi, _ in segs) == len(pkt.programs[0].insts)
+    assert any(dev and hi - lo >= 2 for lo, hi, dev in segs)
+    assert all(Op(pkt.programs[0].insts[lo].op) in (Op.GEMM, Op.ROPE_KV, Op.ATTN) for lo, hi, dev in segs if not dev)
+
+
+@pytest.mark.parametrize("assets,interp", [("assets", True), ("assets", False), ("assets_unfused", True), ("assets_unfused", False)])
+def test_dense_engine_matches_reference(dense_assets, assets, interp):
     from safetensors.torch import load_file
     from plow_b200.models import config, reference
     from plow_b200.runtime.engine import TokenBatch
     from plow_b200.runtime.gpu_engine import GpuEngine
     d = dense_assets
-    eng = GpuEngine(d / "assets", max_slots=4, max_ctx=512)
+    eng = GpuEngine(d / assets, max_slots=4, max_ctx=512, device_interp=interp)
     state = {}
     for f in glob.glob(str(d / "ckpt" / "*.safetensors")):
         state.update(load_file(f))
@@ -65,3 +81,5 @@ def test_dense_engine_matches_reference(dense_assets):
             want = ref.forward(torch.tensor(cur[s]))[-1]
             got = torch.from_numpy(r.logits[s])
             assert ((got - want).norm() / want.norm()).item() < 0.05
+    if interp:
+        assert all(st.interp is not None and st.interp.launches > 0 for st in eng.progs.values())
