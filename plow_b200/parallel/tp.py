@@ -24,7 +24,8 @@ def _align(x, a=256):
 
 
 class TpComm:
-    def __init__(self, rank: int, world: int, max_rows: int = 128, max_n: int = 16384, impl: str = "fused", deadline_ms: int = 2000):
+    def __init__(self, rank: int, world: int, max_rows: int = 128, max_n: int = 16384, impl: str = "fused", deadline_ms: int = 2000,
+                 max_k: int = 16384):
         self.rank, self.world, self.impl = rank, world, impl
         self.dev = torch.device("cuda", torch.cuda.current_device())
         self.max_rows, self.max_n, self.deadline_ms = max_rows, max_n, deadline_ms
@@ -33,7 +34,8 @@ class TpComm:
         import torch.distributed._symmetric_memory as symm
         tiles = (max_n + 127) // 128
         lay, off = {}, 0
-        for name, nbytes in (("part", tiles * 128 * 128 * 2), ("flag", tiles * 8 * 4), ("done", 128), ("y", max_rows * max_n * 2)):
+        for name, nbytes in (("part", tiles * 128 * 128 * 2), ("flag", tiles * 8 * 4), ("done", 128), ("y", max_rows * max_n * 2),
+                             ("ag_ctr", 128), ("xg0", max_rows * max_k * 2), ("xg1", max_rows * max_k * 2)):
             lay[name] = off
             off = _align(off + nbytes)
         self.lay = lay
@@ -43,15 +45,19 @@ class TpComm:
         torch.cuda.synchronize()
         dist.barrier()
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.ag_epoch = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.ag_done = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self._ag_calls = 0
         self.peers = list(self.hdl.buffer_ptrs)
+        import ctypes
+        self._peer_arr = (ctypes.c_void_p * 8)(*(self.peers + [None] * (8 - len(self.peers))))
 
     def gemm_allreduce(self, x, w, n_out, sx=None, sw=None, residual=None):
         """y = all_reduce_sum(x_shard @ w_shard.T) (+ residual).  x [M, K/tp], w [N, K/tp]; M <= 128.
         Returns a [M, N] bf16 view of the symmetric output area (valid until the next call)."""
         M = x.shape[0]
-        assert M <= self.max_rows and n_out <= self.max_n
-        bn = gemm_ops._pick_bn_swap(M, sx is not None, False)
-        if self.impl == "fused" and bn <= 64:
+        bn = gemm_ops._pick_bn_swap(M, sx is not None, False) if M <= 128 else 128
+        if self.impl == "fused" and M <= 64 and bn <= 64 and M <= self.max_rows and n_out <= self.max_n and n_out % 8 == 0:
             y = self.buf[self.lay["y"]:self.lay["y"] + M * n_out * 2].view(BF16).view(M, n_out)
             ar = dict(peers=self.peers, part_ofs=self.lay["part"], flag_ofs=self.lay["flag"], done_ofs=self.lay["done"],
                       y_ofs=self.lay["y"], epoch_ptr=self.epoch.data_ptr(), world=self.world, me=self.rank,
@@ -63,3 +69,32 @@ class TpComm:
         if residual is not None:
             y = y + residual
         return y
+
+    def allgather_gemm(self, x_band, w, n_out, dual=False):
+        """y = gather_rows(x_band over ranks) @ w.T for a column-parallel w [N/tp(*2), K] (bf16).
+
+        x_band [rows/tp, K] is this rank's band of the sequence-parallel activation.  The band is pushed into
+        every rank's gathered buffer by one kernel (csrc/comm/tp_ag.cu) and the GEMM waits for all bands from
+        inside the kernel; ``impl="nccl"`` gathers with all_gather_into_tensor and runs the same GEMM."""
+        band, K = x_band.shape
+        M = band * self.world
+        assert x_band.dtype == BF16 and x_band.is_contiguous()
+        if self.impl != "fused":
+            xg = torch.empty(M, K, dtype=BF16, device=self.dev)
+            dist.all_gather_into_tensor(xg, x_band)
+            return gemm_ops.gemm(xg, w, dual=dual, n_out=n_out)
+        # two gathered buffers used alternately: a rank can be at most one call ahead of a peer that is still
+        # reading (its next push needs that peer's band of the call in between), so parity is enough
+        ofs = self.lay["xg1" if self._ag_calls & 1 else "xg0"]
+        self._ag_calls += 1
+        assert M <= self.max_rows and K * 2 * M <= self.lay["xg1"] - self.lay["xg0"]
+        native.call("plow_ag_push", self._peer_arr, ofs, self.lay["ag_ctr"], self.ag_epoch, self.ag_done, self.world,
+                    self.rank, x_band, K * 2, band, K * 2)
+        xg = self.buf[ofs:ofs + M * K * 2].view(BF16).view(M, K)
+        ctr = self.buf.data_ptr() + self.lay["ag_ctr"]
+        return gemm_ops.gemm(xg, w, dual=dual, n_out=n_out, wait=(ctr, self.ag_epoch.data_ptr(), self.world, self.deadline_ms))
+
+    def all_reduce(self, x):
+        """Stand-alone all-reduce (instructions the compiler did not fuse into a GEMM): NCCL."""
+        dist.all_reduce(x)
+        return x

@@ -135,7 +135,7 @@ class _Prog:
 class GpuEngine(EngineBase):
     def __init__(self, assets_dir=None, packet=None, weights: WeightSource | None = None, max_slots=64, n_pages=None,
                  max_ctx=8192, kv_fraction=0.9, prefix_cache=True, cuda_graphs=True, device=None, rank=0,
-                 comm=None, rungs=None, device_interp=None):
+                 comm=None, rungs=None, device_interp=None, tp_comm=None):
         if not torch.cuda.is_available():
             raise EngineError("GpuEngine needs a CUDA device", fatal=True)
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
@@ -144,7 +144,7 @@ class GpuEngine(EngineBase):
         if packet is None:
             name = "model.pkt" if rank == 0 else f"model.rank{rank}.pkt"
             packet = pk.read_packet(Path(assets_dir) / name)
-        self.rank, self.comm = rank, comm
+        self.rank, self.comm, self.tp_comm = rank, comm, tp_comm
         # row-class segments run inside the persistent on-device interpreter (PLOW_DEVICE_INTERP=0 turns it off)
         self.device_interp = (os.environ.get("PLOW_DEVICE_INTERP", "1") != "0") if device_interp is None else bool(device_interp)
         shards = packet.section_json("weight_shards.json") or {}
@@ -404,6 +404,35 @@ class GpuEngine(EngineBase):
         aq, saq = mla_ops.fold(self._mla_ws, self.d_kvlen_row, wuv, T, heads, ao, want_fp8=want)
         if want:
             st.q[(ins.t[0], 0)] = (aq, saq)
+
+    # -- tensor parallel (row-parallel projections end in an all-reduce)
+    def _need_tp(self):
+        if self.tp_comm is None:
+            raise EngineError("this packet was compiled for tensor parallelism; pass tp_comm=TpComm(...)")
+        return self.tp_comm
+
+    def _ext_gemm_xreduce(self, st, ins):
+        tp = self._need_tp()
+        y, x = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])
+        N, K, flags, co = ins.i[0], ins.i[1], ins.i[2], ins.i[6]
+        if flags & pk.GEMM_FP8_BLOCK:
+            wq, sw = self.static_q[ins.t[2]]
+            xq, sx = self._quant_of(st, ins.t[1], co, K, x)
+            r = tp.gemm_allreduce(xq[:y.shape[0]], wq, N, sx=sx, sw=sw)
+        else:
+            w = self.static[ins.t[2]]
+            xin = x if co == 0 and x.shape[1] == K else x[:, co:co + K]
+            r = tp.gemm_allreduce(xin, w if w.dtype == BF16 else self._bf16_weight(ins.t[2]), N)
+        y.copy_(r)
+
+    def _ext_xreduce(self, st, ins):
+        out, x = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])
+        if out.data_ptr() != x.data_ptr():
+            out.copy_(x)
+        self._need_tp().all_reduce(out)
+
+    def _ext_xreduce_add_norm(self, st, ins):
+        raise EngineError("XREDUCE_ADD_NORM is emitted only when gemm-xreduce fusion is disabled; not supported by this engine")
 
     # -- GQA
     def _op_rope_kv(self, st, ins):
