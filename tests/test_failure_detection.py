@@ -1,0 +1,146 @@
+"""Failure detection without a device fault: heartbeats / abort flag on the host (gloo ranks on CPU), a collective
+that errors out under a short process-group timeout, and the bounded device-side wait returning a status."""
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+import torch
+
+
+def test_gate_detects_silent_rank_and_abort():
+    from plow_b200.parallel.health import DictStore, RankFailure, RankHealth
+    t = [0.0]
+    store = DictStore()
+    a = RankHealth(store, 0, 3, timeout_s=1.0, clock=lambda: t[0])
+    b = RankHealth(store, 1, 3, timeout_s=1.0, clock=lambda: t[0])
+    c = RankHealth(store, 2, 3, timeout_s=1.0, clock=lambda: t[0])
+    for _ in range(3):
+        t[0] += 0.4
+        a.gate(); b.gate(); c.gate()
+    # rank 2 stops beating (left between steps): the others notice once the timeout has passed
+    t[0] += 0.6
+    a.gate(); b.gate()            # rank 2's last beat is observed here
+    t[0] += 0.6
+    a.gate(); b.gate()            # 0.6 s of silence: still inside the timeout
+    t[0] += 0.6
+    with pytest.raises(RankFailure) as e:
+        a.gate()
+    assert e.value.dead == (2,)
+    b.abort("peer lost")
+    with pytest.raises(RankFailure) as e:
+        a.gate()
+    assert e.value.aborted_by == 1
+
+
+WORKER = r'''
+import os, sys, time, datetime
+import torch, torch.distributed as dist
+sys.path.insert(0, os.environ["PLOW_ROOT"])
+from plow_b200.parallel.health import RankHealth, RankFailure
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+store = dist.TCPStore("127.0.0.1", int(os.environ["STORE_PORT"]), world, rank == 0, timeout=datetime.timedelta(seconds=20))
+dist.init_process_group("gloo", store=dist.PrefixStore("pg", store), rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+h = RankHealth(store, rank, world, timeout_s=1.0)
+x = torch.ones(4)
+for step in range(3):
+    h.gate()
+    dist.all_reduce(x)
+    time.sleep(0.1)
+mode = os.environ["MODE"]
+if rank == world - 1:
+    if mode == "exit":
+        sys.exit(0)                  # leaves between steps, nothing in flight
+    if mode == "raise":
+        h.abort("injected failure")
+        raise SystemExit(3)
+t0 = time.time()
+try:
+    while time.time() - t0 < 10:
+        h.gate()                     # detects the loss before the next collective is launched
+        time.sleep(0.2)
+    print(f"RANK{rank} NOT_DETECTED")
+except RankFailure as e:
+    print(f"RANK{rank} DETECTED dead={list(e.dead)} aborted_by={e.aborted_by} after={time.time() - t0:.1f}s")
+if mode == "collective" or os.environ.get("ALSO_COLLECTIVE"):
+    pass
+'''
+
+
+@pytest.mark.parametrize("mode", ["exit", "raise"])
+def test_rank_loss_detected_by_survivors(tmp_path, mode):
+    f = tmp_path / "w.py"
+    f.write_text(WORKER)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    port = 29700 + (os.getpid() % 200) + (0 if mode == "exit" else 1)
+    procs = []
+    for r in range(3):
+        env = dict(os.environ, PLOW_ROOT=root, RANK=str(r), WORLD_SIZE="3", STORE_PORT=str(port), MODE=mode)
+        procs.append(subprocess.Popen([sys.executable, str(f)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = []
+    for p in procs:
+        try:
+            outs.append(p.communicate(timeout=90)[0])
+        except subprocess.TimeoutExpired:
+            p.kill()
+            outs.append("TIMEOUT")
+    for r in (0, 1):
+        assert f"RANK{r} DETECTED" in outs[r], outs
+    if mode == "raise":
+        assert "aborted_by=2" in outs[0]
+    else:
+        assert "dead=[2]" in outs[0]
+
+
+COLL = r'''
+import os, sys, datetime, time
+import torch, torch.distributed as dist
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{os.environ['STORE_PORT']}", rank=rank, world_size=world,
+                        timeout=datetime.timedelta(seconds=2))
+x = torch.ones(4)
+dist.all_reduce(x)
+if rank == 1:
+    time.sleep(8)        # never joins the second collective in time
+    sys.exit(0)
+try:
+    dist.all_reduce(x)
+    print("NO_ERROR")
+except Exception as e:
+    print("COLLECTIVE_ERROR", type(e).__name__)
+'''
+
+
+def test_short_process_group_timeout_ends_collective(tmp_path):
+    f = tmp_path / "c.py"
+    f.write_text(COLL)
+    port = 29950 + (os.getpid() % 40)
+    procs = [subprocess.Popen([sys.executable, str(f)], env=dict(os.environ, RANK=str(r), WORLD_SIZE="2", STORE_PORT=str(port)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    out0 = procs[0].communicate(timeout=60)[0]
+    procs[1].communicate(timeout=60)
+    assert "COLLECTIVE_ERROR" in out0, out0
+
+
+@pytest.mark.gpu
+def test_device_wait_runs_out_and_reports_status():
+    """A flag that nothing sets: the bounded wait gives up after its deadline, records the peer-wait status and
+    returns; the context stays usable."""
+    from plow_b200.ops import native
+    flag = torch.zeros(32, dtype=torch.int32, device="cuda")
+    st = native.status_word()
+    st.zero_()
+    t0 = time.time()
+    native.call("plow_wait_probe", flag, 1, 200_000_000, st)      # 0.2 s deadline
+    torch.cuda.synchronize()
+    assert 0.15 < time.time() - t0 < 5.0
+    with pytest.raises(native.NativeLibraryError) as e:
+        native.check_status()
+    assert "peer flag never arrived" in str(e.value)
+    # same probe with the flag already set returns at once with a clean status; later kernels still run
+    flag.fill_(1)
+    native.call("plow_wait_probe", flag, 1, 200_000_000, st)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0
