@@ -47,7 +47,7 @@ class DeviceInterp:
             out = packet.tensors[ins.t[0]] if ins.t[0] != pk.T_NONE else None
             d0 = int(out.dims[0]) if out is not None else -1
             aux[k, 0] = rows if d0 == -1 else samples if d0 == -2 else d0
-            aux[k, 1] = int(out.dims[1]) if out is not None and out.rank > 1 else 0
+            aux[k, 1] = int(out.dims[1]) if out is not None and len(out.dims) > 1 else 0
         self.aux = torch.from_numpy(aux).to(device)
         self.ctr = torch.zeros(max(1, prog.n_ctr) * 32, dtype=torch.int32, device=device)
         self.trace = torch.zeros(len(prog.stream), 40, dtype=torch.uint8, device=device) if trace else None

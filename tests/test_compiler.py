@@ -113,3 +113,23 @@ def test_rope_tables_scaling():
                                           beta_fast=32, beta_slow=1, mscale=1.0, mscale_all_dim=1.0))
     assert np.isfinite(l3).all() and np.isfinite(ya).all()
     assert not np.allclose(l3[5], rope_table(64, 64, 500000.0)[5])
+
+
+def test_device_interp_tables_build_on_cpu(tiny_assets):
+    """The on-device interpreter's host side: packet tables serialise to the ABI strides and every program is cut
+    into row segments + role instructions that cover it exactly (no device needed to build them)."""
+    import torch
+    from plow_b200.compiler import packet as pk
+    from plow_b200.compiler.packet import Op
+    from plow_b200.runtime.device_interp import DeviceInterp, ROW_OPS
+    pkt = pk.read_packet(tiny_assets / "assets" / "model.pkt")
+    prog = pkt.programs[0]
+    bound = {h: torch.zeros(4) for h in range(len(pkt.tensors))}
+    di = DeviceInterp(pkt, prog, lambda h: bound.get(h), rows=prog.rows, samples=4, device="cpu")
+    assert di.insts.numel() == 64 * len(prog.insts) and di.stream.numel() == 24 * len(prog.stream)
+    assert di.aux.shape == (len(prog.insts), 2) and int(di.aux[0, 0]) == prog.rows
+    segs = DeviceInterp.segments(prog)
+    assert [lo for lo, _, _ in segs] == sorted(lo for lo, _, _ in segs) and segs[0][0] == 0 and segs[-1][1] == len(prog.insts)
+    assert all(segs[k][1] == segs[k + 1][0] for k in range(len(segs) - 1))
+    for lo, hi, dev in segs:
+        assert all((Op(prog.insts[j].op) in ROW_OPS) == dev for j in range(lo, hi))
