@@ -458,13 +458,16 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
       const float* ws_tile = nullptr;
       if constexpr (SWAP) {
         if (a.splits > 1 && a.E == 0) {
-          float4* wp = reinterpret_cast<float4*>(a.ws + ((static_cast<size_t>(t.tile_id) * a.splits + t.ks) * 128 + li) * kAccCols);
+          const bool trs = a.trace && blockIdx.x == 0 && li == 0;
+          if (trs) a.trace[60 * 8 + 0] = clock64();
+          // workspace layout [tile][split][column][128 lanes]: a warp's 32 lanes touch 128 contiguous bytes
+          float* wp = a.ws + (static_cast<size_t>(t.tile_id) * a.splits + t.ks) * kAccCols * 128 + li;
 #pragma unroll
           for (int c = 0; c < kAccCols; c += 16) {
             float r[16];
             raw16(c, r);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) wp[(c >> 2) + j] = make_float4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            for (int j = 0; j < 16; ++j) wp[static_cast<size_t>(c + j) * 128] = r[j];
           }
           __threadfence();
           __syncwarp();
@@ -474,6 +477,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           }
           ++xchg_it;
           uint32_t* ctr = reinterpret_cast<uint32_t*>(a.ws_ctr) + t.tile_id * 32;   // one counter per 128-byte line
+          if (trs) a.trace[60 * 8 + 1] = clock64();
           if (li == 0) red_add_release_gpu(ctr, 1u);
           if (lane == 0) {
             const unsigned long long t0 = globaltimer_ns();
@@ -485,30 +489,38 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             }
           }
           __syncwarp();
+          if (trs) a.trace[60 * 8 + 2] = clock64();
           if (*abort_flag) { ok = false; break; }
           col_lo = t.ks * BN / a.splits;
           col_hi = (t.ks + 1) * BN / a.splits;
-          ws_tile = a.ws + (static_cast<size_t>(t.tile_id) * a.splits * 128 + li) * kAccCols;
+          ws_tile = a.ws + static_cast<size_t>(t.tile_id) * a.splits * kAccCols * 128 + li;
         }
       }
       // result of 16 columns starting at c (gate/up folded, out_scale applied)
       auto load16 = [&](int c, float* r) {
         if (ws_tile) {
-          // partials are summed in split order (deterministic); loads of different splits are
-          // independent, so the reduction runs at L2 bandwidth
+          // partials are summed in split order (deterministic).  The 16 (or 32) loads of one split are
+          // issued together before any add, so a split costs one L2 round trip, not one per column.
+          float g[16], u[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float g = 0.f, u = 0.f;
-            if (c + j >= col_lo && c + j < col_hi) {
-#pragma unroll 8
-              for (int ks = 0; ks < a.splits; ++ks) {
-                const float* p = ws_tile + static_cast<size_t>(ks) * 128 * kAccCols;
-                g += __ldcg(p + c + j);
-                if constexpr (DUAL) u += __ldcg(p + BN + c + j);
-              }
+          for (int j = 0; j < 16; ++j) { g[j] = 0.f; u[j] = 0.f; }
+          for (int ks = 0; ks < a.splits; ++ks) {
+            const float* p = ws_tile + static_cast<size_t>(ks) * kAccCols * 128;
+            float v[16], w2[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const bool in = c + j >= col_lo && c + j < col_hi;
+              v[j] = in ? __ldcg(p + static_cast<size_t>(c + j) * 128) : 0.f;
+              if constexpr (DUAL) w2[j] = in ? __ldcg(p + static_cast<size_t>(BN + c + j) * 128) : 0.f;
             }
-            r[j] = DUAL ? silu_f(g) * u : g;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              g[j] += v[j];
+              if constexpr (DUAL) u[j] += w2[j];
+            }
           }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = DUAL ? silu_f(g[j]) * u[j] : g[j];
         } else if constexpr (FP8) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -615,6 +627,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         }
         if (ws_tile) {
           // the split that leaves last re-arms the tile's counters for the next launch
+          if (a.trace && blockIdx.x == 0 && li == 0) a.trace[60 * 8 + 3] = clock64();
           __syncwarp();
           if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
           if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) {

@@ -31,6 +31,7 @@ struct InterpArgs {
   const uint32_t* succs;
   void* const* tensors;      // device pointer per tensor handle, resolved for this program
   const int2* aux;           // per instruction: (rows the op runs over, row width where the op needs one)
+  const uint32_t* pc0;       // per unit: first stream index whose instruction is >= inst_lo (host-built per segment)
   uint32_t* ctr;             // n_ctr * PLOW_CTR_STRIDE_U32, zeroed before the launch for [inst_lo, inst_hi)
   PlowTraceRec* trace;       // optional, one record per stream entry
   int* status;
@@ -63,6 +64,21 @@ template <class T> __device__ __forceinline__ T* tptr(const InterpArgs& a, const
 // y = x * rsqrt(mean(x^2) + eps) * gamma for one row, all threads of the CTA
 __device__ void norm_row(__nv_bfloat16* out, const __nv_bfloat16* x, const __nv_bfloat16* g, int W, float eps, int mode, float* red) {
   float ss = 0.f;
+  const bool vec = (W & 1) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(g)) & 3) == 0;
+  if (vec) {
+    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(x);
+    for (int j = threadIdx.x; j < W / 2; j += kInterpThreads) { const float2 v = __bfloat1622float2(x2[j]); ss += v.x * v.x + v.y * v.y; }
+    const float rs = rsqrtf(cta_sum(ss, red) / W + eps);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(g);
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(out);
+    for (int j = threadIdx.x; j < W / 2; j += kInterpThreads) {
+      const float2 v = __bfloat1622float2(x2[j]);
+      float2 gm = g ? __bfloat1622float2(g2[j]) : make_float2(1.f, 1.f);
+      if (g && mode) { gm.x += 1.f; gm.y += 1.f; }
+      o2[j] = __floats2bfloat162_rn(v.x * rs * gm.x, v.y * rs * gm.y);
+    }
+    return;
+  }
   for (int j = threadIdx.x; j < W; j += kInterpThreads) { const float v = __bfloat162float(x[j]); ss += v * v; }
   const float rs = rsqrtf(cta_sum(ss, red) / W + eps);
   for (int j = threadIdx.x; j < W; j += kInterpThreads) {
@@ -185,9 +201,12 @@ interp_kernel(const InterpArgs a) {
   if (threadIdx.x == 0) give_up = 0;
   __syncthreads();
   const unsigned long long deadline = static_cast<unsigned long long>(a.deadline_ms ? a.deadline_ms : 2000) * 1000000ull;
-  for (uint32_t pc = a.cu_ofs[cu]; pc < a.cu_ofs[cu + 1]; ++pc) {
+  // a unit's stream is ordered by instruction: start at the segment's first entry, stop at its last
+  const uint32_t pc_end = a.cu_ofs[cu + 1];
+  for (uint32_t pc = a.pc0[cu]; pc < pc_end; ++pc) {
     const PlowStreamEnt se = a.stream[pc];
-    if (se.inst < a.inst_lo || se.inst >= a.inst_hi) continue;
+    if (se.inst >= a.inst_hi) break;
+    if (se.inst < a.inst_lo) continue;
     unsigned long long t_arrive = 0, t_ready = 0;
     if (threadIdx.x == 0) {
       if (a.trace) t_arrive = globaltimer_ns();
@@ -233,10 +252,10 @@ extern "C" {
 // Every pointer is device memory.  `ctr` entries of [inst_lo, inst_hi) are zeroed here (memset node) before
 // the cooperative launch.  Returns -2 when the program's unit count does not fit on the device at once.
 int plow_interp_run(const void* insts, const void* stream, const void* cu_ofs, const void* waits, const void* succs,
-                    const void* tensors, const void* aux, void* ctr, void* trace, int* status, uint32_t inst_lo,
+                    const void* tensors, const void* aux, const void* pc0, void* ctr, void* trace, int* status, uint32_t inst_lo,
                     uint32_t inst_hi, uint32_t n_cu, uint32_t deadline_ms, void* stream_) {
   using namespace plow;
-  if (!insts || !stream || !cu_ofs || !tensors || !aux || !ctr || !status || inst_hi <= inst_lo || n_cu == 0) return -1;
+  if (!insts || !stream || !cu_ofs || !tensors || !aux || !pc0 || !ctr || !status || inst_hi <= inst_lo || n_cu == 0) return -1;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
   static int capacity = 0;
   if (!capacity) {
@@ -253,7 +272,7 @@ int plow_interp_run(const void* insts, const void* stream, const void* cu_ofs, c
   a.insts = static_cast<const PlowInst*>(insts); a.stream = static_cast<const PlowStreamEnt*>(stream);
   a.cu_ofs = static_cast<const uint32_t*>(cu_ofs); a.waits = static_cast<const PlowWait*>(waits);
   a.succs = static_cast<const uint32_t*>(succs); a.tensors = static_cast<void* const*>(tensors);
-  a.aux = static_cast<const int2*>(aux); a.ctr = static_cast<uint32_t*>(ctr); a.trace = static_cast<PlowTraceRec*>(trace);
+  a.aux = static_cast<const int2*>(aux); a.pc0 = static_cast<const uint32_t*>(pc0); a.ctr = static_cast<uint32_t*>(ctr); a.trace = static_cast<PlowTraceRec*>(trace);
   a.status = status; a.inst_lo = inst_lo; a.inst_hi = inst_hi; a.n_cu = n_cu; a.deadline_ms = deadline_ms;
   void* params[] = {&a};
   cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(interp_kernel), dim3(n_cu), dim3(kInterpThreads), params, 0, st);

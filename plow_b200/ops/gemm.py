@@ -43,17 +43,17 @@ def _splitk_ws(device):
 
 def pick_splits(M, N, K, fp8, dual, bn) -> int:
     """Split-K factor for a dense swap-mode GEMM: fill the SMs when the tile count alone cannot.
-    Measured on B200 at M=64: a win for few-tile shapes (q_a/kv_a down-projection 31 -> 19 us, router
-    25 -> 16 us), a loss once a GEMM already has >32 tiles or carries gate+up accumulators."""
-    if dual:
-        return 1
+
+    A swap-mode tile is 128 weight rows; a projection with fewer than 148 tiles leaves SMs idle while every
+    busy SM is limited by its own load rate, so the K range of each tile is cut over ``s`` CTAs (all resident
+    at once: tiles * s <= SM count) that reduce their partials through L2."""
     tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)
     kb = (K + (127 if fp8 else 63)) // (128 if fp8 else 64)
-    s = min(SM_COUNT // max(tiles, 1), kb // 2, bn // 2)
+    s = min(SM_COUNT // max(tiles, 1), kb // 4, bn // 4, 16)
     if s < 2:
         return 1
     acc = bn * (2 if dual else 1)
-    if tiles * s * acc * 128 > (16 << 20) or tiles > 32:
+    if tiles * s * acc * 128 > (16 << 20) or tiles > 256:
         return 1
     return s
 

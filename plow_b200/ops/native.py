@@ -121,7 +121,7 @@ _SIGS = {
     "plow_ep_combine": "pppppiip",
     "plow_wait_probe": "piLpp",
     "plow_ag_push": "pLLppiipiiip",
-    "plow_interp_run": "pppppppppp" "IIIIp",
+    "plow_interp_run": "ppppppppppp" "IIIIp",
     "plow_sample": "ppiiipppppp" "Lp",
     "plow_dsa_k_write": "pppipppppp" "iiiifp",
     "plow_dsa_select": "ppippp" "ipipplp" "pppiiiiiipp",

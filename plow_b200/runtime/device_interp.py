@@ -53,6 +53,17 @@ class DeviceInterp:
         self.trace = torch.zeros(len(prog.stream), 40, dtype=torch.uint8, device=device) if trace else None
         self.n_cu = prog.n_cu
         self.launches = 0
+        self._pc0 = {}
+
+    def _pc0_for(self, lo: int):
+        """Per unit, the first stream index whose instruction is >= lo (streams are ordered by instruction)."""
+        if lo not in self._pc0:
+            import bisect
+            prog = self.prog
+            insts = [s.inst for s in prog.stream]
+            v = [bisect.bisect_left(insts, lo, prog.cu_ofs[c], prog.cu_ofs[c + 1]) for c in range(prog.n_cu)]
+            self._pc0[lo] = torch.tensor(v, dtype=torch.int32, device=self.device)
+        return self._pc0[lo]
 
     @staticmethod
     def segments(prog, eligible=None):
@@ -73,7 +84,7 @@ class DeviceInterp:
 
     def run(self, lo: int, hi: int) -> None:
         native.call("plow_interp_run", self.insts, self.stream, self.cu_ofs, self.waits, self.succs, self.tensors, self.aux,
-                    self.ctr, self.trace, native.status_word(self.device), lo, hi, self.n_cu, self.deadline_ms)
+                    self._pc0_for(lo), self.ctr, self.trace, native.status_word(self.device), lo, hi, self.n_cu, self.deadline_ms)
         self.launches += 1
 
     def trace_records(self):
