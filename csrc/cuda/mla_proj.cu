@@ -210,49 +210,85 @@ mla_fold_kernel(const FoldArgs a, const __grid_constant__ CUtensorMap tm_w) {
     const int t = t0 + li;
     const bool live = t < a.T;
     const uint32_t lane_addr = static_cast<uint32_t>(lq * 32) << 16;
-    // merge weights of this (token, head)
-    float wgt[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    int ns = 1;
-    if (live) {
-      const int tiles = (a.kvlen[t] + 63) / 64;
-      ns = (tiles + a.tiles_per_split - 1) / a.tiles_per_split;
-      ns = ns < 1 ? 1 : (ns > a.max_splits ? a.max_splits : ns);
-      if (ns > 8) ns = 8;
-      float mx = -INFINITY;
-      for (int s = 0; s < ns; ++s) mx = fmaxf(mx, a.lse[(static_cast<size_t>(t) * a.max_splits + s) * a.heads + h]);
-      float sum = 0.f;
-      for (int s = 0; s < ns; ++s) { wgt[s] = exp2f(a.lse[(static_cast<size_t>(t) * a.max_splits + s) * a.heads + h] - mx); sum += wgt[s]; }
-      for (int s = 0; s < ns; ++s) wgt[s] /= sum;
+    // merge weights of this (token, head), shared with the other merge warps through shared memory
+    float* wsm = reinterpret_cast<float*>(smem + 131072 + 256);       // [128 rows][8 splits]
+    int* nsm = reinterpret_cast<int*>(wsm + 128 * 8);                 // [128 rows]
+    {
+      float wgt[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      int ns = 0;
+      if (live) {
+        const int tiles = (a.kvlen[t] + 63) / 64;
+        ns = (tiles + a.tiles_per_split - 1) / a.tiles_per_split;
+        ns = ns < 1 ? 1 : (ns > a.max_splits ? a.max_splits : ns);
+        if (ns > 8) ns = 8;
+        float l8[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) l8[s] = s < ns ? a.lse[(static_cast<size_t>(t) * a.max_splits + s) * a.heads + h] : -INFINITY;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) mx = fmaxf(mx, l8[s]);
+        float sum = 0.f;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) { wgt[s] = s < ns ? exp2f(l8[s] - mx) : 0.f; sum += wgt[s]; }
+        const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) wgt[s] *= inv;
+      }
+#pragma unroll
+      for (int s = 0; s < 8; ++s) wsm[li * 8 + s] = wgt[s];
+      nsm[li] = ns;
     }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const int n_live = min(128, a.T - t0);
     bool ok = true;
     for (int p = 0; p < 2 && ok; ++p) {
       if (p == 1 && !mbar_wait(&done[0], 0, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
-      // A operand: the warp walks its 32 token rows; for one row the 32 lanes fetch the row's 256
-      // latent columns of this phase as one coalesced 512-byte read per split (lane = 16-byte unit),
-      // merge the splits with the row's weights (held by the lane that owns the row, broadcast by
-      // shuffle) and store the unit at its swizzled place: unit u of chunk c at (u ^ (row & 7)) * 16.
-#pragma unroll 4
-      for (int rr = 0; rr < 32; ++rr) {
-        const int row = lq * 32 + rr;
-        const int tr = t0 + row;
-        const int ns_r = __shfl_sync(0xffffffffu, ns, rr);
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      // A operand: warp w fills rows w, w+4, w+8, ... (so the live rows are spread over all four warps), eight
+      // rows at a time.  For one row the 32 lanes fetch the row's 256 latent columns of this phase as one
+      // coalesced 512-byte read per split (lane = 16-byte unit); the eight rows' loads of a split are issued
+      // together, so a batch costs one memory round trip per split.  The merged unit goes to its swizzled
+      // place: unit u of chunk c at (u ^ (row & 7)) * 16.
+      for (int kb = 0; kb < 32; kb += 8) {
+        if (lq + 4 * kb >= n_live) break;          // rows ascend: nothing live further on (warp-uniform)
+        float acc[8][8];
+        int nsr[8];
+        int ns_b = 0;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-          const float ws_ = __shfl_sync(0xffffffffu, wgt[s], rr);
-          if (tr < a.T && s < ns_r) {
-            const uint4 v = *reinterpret_cast<const uint4*>(a.opart + ((static_cast<size_t>(tr) * a.max_splits + s) * a.heads + h) * 512 + p * 256 + lane * 8);
-            const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&v);
+        for (int i = 0; i < 8; ++i) {
+          const int row = lq + 4 * (kb + i);
+          nsr[i] = row < n_live ? nsm[row] : 0;
+          ns_b = max(ns_b, nsr[i]);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(hh[j]); acc[2 * j] += ws_ * f.x; acc[2 * j + 1] += ws_ * f.y; }
+          for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+        }
+        for (int sp = 0; sp < ns_b; ++sp) {
+          uint4 v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int row = lq + 4 * (kb + i);
+            v[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (sp < nsr[i])
+              v[i] = *reinterpret_cast<const uint4*>(a.opart + ((static_cast<size_t>(t0 + row) * a.max_splits + sp) * a.heads + h) * 512 + p * 256 + lane * 8);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int row = lq + 4 * (kb + i);
+            const float wv = wsm[(row & 127) * 8 + sp];
+            const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(hh[j]); acc[i][2 * j] += wv * f.x; acc[i][2 * j + 1] += wv * f.y; }
           }
         }
-        uint4 o;
-        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-        const int c = lane >> 3, uu = lane & 7;
-        *reinterpret_cast<uint4*>(sa + c * 16384 + row * 128 + ((uu ^ (row & 7)) << 4)) = o;
+        for (int i = 0; i < 8; ++i) {
+          const int row = lq + 4 * (kb + i);
+          uint4 o;
+          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[i][2 * j], acc[i][2 * j + 1]);
+          const int c = lane >> 3, uu = lane & 7;
+          *reinterpret_cast<uint4*>(sa + c * 16384 + row * 128 + ((uu ^ (row & 7)) << 4)) = o;
+        }
       }
       fence_proxy_async_smem();
       __syncwarp();
@@ -338,7 +374,7 @@ int plow_mla_fold(const void* opart, const float* lse, const int* kvlen, const v
   CUtensorMap tw;
   int r = make_tmap_2d(&tw, wuv, 2, static_cast<uint64_t>(heads) * 128, 512, 1024, 128);
   if (r) return 1000 + r;
-  const int smem = 1024 + 131072 + 256;
+  const int smem = 1024 + 131072 + 256 + 128 * 8 * 4 + 128 * 4;
   static bool attr = false;
   if (!attr) { if (cudaFuncSetAttribute(mla_fold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 3000; attr = true; }
   FoldArgs a;
