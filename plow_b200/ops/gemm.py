@@ -33,6 +33,26 @@ _SPLITK_WS = {}
 SM_COUNT = 148
 
 
+_TUNED = {}
+
+
+def _tuned(M, N, K, fp8, dual):
+    """Measured (bn, splits) for a dense swap-mode shape from the tuning store, or None."""
+    if "db" not in _TUNED:
+        try:
+            from ..compiler.tunedb import TuneDb
+            db = TuneDb()
+            _TUNED["db"] = db if db.root.exists() else None
+        except Exception:
+            _TUNED["db"] = None
+    db = _TUNED["db"]
+    if db is None:
+        return None
+    from ..compiler.tunedb import gemm_key
+    rec = db.lookup("gemm", gemm_key(M, N, K, "e4m3" if fp8 else "bf16", dual))
+    return rec["config"] if rec else None
+
+
 def _splitk_ws(device):
     """fp32 partial workspace + self-resetting per-tile counters, one pair per device."""
     if device not in _SPLITK_WS:
@@ -85,6 +105,10 @@ def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=N
     if swap is None:
         per = rows_hint if rows_hint is not None else M
         swap = per <= 128
+    if swap and E == 0 and bn is None and splits is None and ar is None:
+        cfg = _tuned(M, N, K, fp8, dual)
+        if cfg and cfg.get("swap", True) and cfg["bn"] >= M:
+            bn, splits = cfg["bn"], cfg.get("splits", 1)
     if bn is None:
         if swap:
             bn = _pick_bn_swap(rows_hint if rows_hint is not None else M, fp8, dual)

@@ -96,6 +96,10 @@ def main(argv=None) -> int:
     v = sub.add_parser("viz", help="write an HTML view of the fused graph")
     v.add_argument("hf_dir")
     v.add_argument("--out", default="graph.html")
+    tn = sub.add_parser("tune", help="measure decode GEMM tiles on this GPU and write the tuning store")
+    tn.add_argument("hf_dir")
+    tn.add_argument("--rows", type=lambda s: [int(x) for x in s.split(",")], default=[8, 64])
+    tn.add_argument("--db")
     k = sub.add_parser("knob-scope", help="list compile knobs and the programs they affect")
     args = ap.parse_args(argv)
     if args.cmd == "viz":
@@ -104,6 +108,24 @@ def main(argv=None) -> int:
         g = graph.build_graph(spec)
         rewrite.fuse(g)
         Path(args.out).write_text(viz.to_html(g))
+        return 0
+    if args.cmd == "tune":
+        from .compiler import tunedb
+        spec = load_spec(args.hf_dir)
+        g = graph.build_graph(spec)
+        rewrite.fuse(g)
+        fp8 = spec.weight_quant == "fp8_block128"
+        shapes = set()
+        for n in g.nodes:
+            if n.op in ("linear", "linear_glu"):
+                w = g.values[n.inputs[1]]
+                if len(w.shape) == 2 and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0:
+                    dual = n.op == "linear_glu"
+                    for m in args.rows:
+                        shapes.add((m, w.shape[0] // (2 if dual else 1), w.shape[1], fp8, dual))
+        db = tunedb.TuneDb(args.db, tunedb.device_fingerprint())
+        for key, (cfg, us) in tunedb.tune_gemm(db, sorted(shapes)):
+            print(f"{key}: {cfg} {us:.1f} us")
         return 0
     if args.cmd == "knob-scope":
         from . import config as knobs

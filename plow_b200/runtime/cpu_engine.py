@@ -110,6 +110,9 @@ class CpuEngine(EngineBase):
         return StepResult(ids=self.out_ids[:ns].copy(),
                           logits=self.out_logits[:ns].copy() if batch.want_logits else None)
 
+    def kv_arrays(self) -> dict:
+        return {t.name: self._keep[h] for h, t in enumerate(self.packet.tensors) if t.tclass == pk.TClass.KV}
+
     def close(self) -> None:
         if getattr(self, "_eng", None):
             self.lib.plow_cpu_engine_destroy(self._eng)

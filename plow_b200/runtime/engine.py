@@ -115,3 +115,7 @@ class EngineBase:
 
     def step(self, batch: TokenBatch) -> StepResult:   # pragma: no cover - interface
         raise NotImplementedError
+
+    def kv_arrays(self) -> dict:                       # pragma: no cover - interface
+        """name -> page-indexed array of every KV / state tensor (for KV images)."""
+        raise NotImplementedError

@@ -556,6 +556,11 @@ class GpuEngine(EngineBase):
         else:
             getattr(self, name)(st, ins)
 
+    def kv_arrays(self) -> dict:
+        out = {t.name: self.static[h] for h, t in enumerate(self.packet.tensors) if t.tclass == pk.TClass.KV}
+        out.update({f"smax.{layer}": v for layer, v in self.kv_smax.items()})   # per-page scale bounds of fp8 latent caches
+        return out
+
     # ---- step ----------------------------------------------------------------------------------
     def _sync_pages(self, slot: int) -> None:
         super()._sync_pages(slot)

@@ -95,6 +95,7 @@ class AppState:
         self.api_keys = set(api_keys or [])
         self.timeline = timeline
         self.loader = loader          # callable(name, path) -> ModelEntry for the admin routes
+        self.manager = None           # serve.manager.ModelManager: residency within a memory budget (optional)
         self.fingerprint = f"plow-b200-{__version__}"
         self.router = None            # data-parallel router (optional)
 
@@ -184,8 +185,24 @@ def create_app(state: AppState) -> FastAPI:
     async def models_status():
         return {m.name: {"state": "resident", "health": m.mux.engine.health, "live": len(m.mux.live)} for m in state.models.values()}
 
+    @app.get("/v1/models/available")
+    async def models_available():
+        if state.manager is not None:
+            return {"models": state.manager.available(), "status": state.manager.status()}
+        return {"models": sorted(state.models)}
+
     @app.post("/v1/models/load")
     async def models_load(body: dict):
+        if state.manager is not None:
+            from .manager import ResidencyError
+            try:
+                entry = await asyncio.get_running_loop().run_in_executor(None, state.manager.acquire, body.get("model"), body.get("path"))
+            except ResidencyError as e:
+                raise ApiError(409, str(e), code="residency")
+            state.add(entry)
+            for gone in [n for n in state.models if n not in state.manager.resident]:
+                state.models.pop(gone, None)
+            return {"model": body.get("model"), "state": "resident", "evictions": state.manager.evictions}
         if state.loader is None:
             raise ApiError(400, "this server was started without a model loader", code="admin_disabled")
         name, path = body.get("model"), body.get("path")
