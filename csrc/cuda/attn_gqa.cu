@@ -382,7 +382,7 @@ __global__ void rope_kv_kernel(__nv_bfloat16* q_out, const __nv_bfloat16* qkv, i
                                __nv_bfloat16* vc, const __nv_bfloat16* qn, const __nv_bfloat16* kn,
                                const float* rope_tab, const int* pos, const int* seq, const int* page_table,
                                int max_pages, int rows, int nq, int nkv, int hd, int rot, int pair_mode,
-                               int plus_one, float eps) {
+                               int plus_one, float eps, __nv_bfloat16* gate_out) {
   extern __shared__ float rk_smem[];
   const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = nq + 2 * nkv;
@@ -392,13 +392,19 @@ __global__ void rope_kv_kernel(__nv_bfloat16* q_out, const __nv_bfloat16* qkv, i
   const int p = pos[r];
   if (p < 0) return;
   float* buf = rk_smem + wib * hd;
-  const __nv_bfloat16* src = qkv + static_cast<size_t>(r) * ld_qkv + static_cast<size_t>(h) * hd;
+  // gated attention: every query head is stored as [Q (hd) | gate (hd)]; K and V follow the 2*hd-wide query heads
+  const int qw = gate_out ? 2 * hd : hd;
+  const __nv_bfloat16* src = qkv + static_cast<size_t>(r) * ld_qkv +
+                             (h < nq ? static_cast<size_t>(h) * qw : static_cast<size_t>(nq) * qw + static_cast<size_t>(h - nq) * hd);
   __nv_bfloat16* dst;
   const __nv_bfloat16* gamma = nullptr;
   const bool is_v = h >= nq + nkv;
   if (h < nq) {
     dst = q_out + (static_cast<size_t>(r) * nq + h) * hd;
     gamma = qn;
+    if (gate_out)
+      for (int i = lane; i < hd / 8; i += 32)
+        reinterpret_cast<uint4*>(gate_out + (static_cast<size_t>(r) * nq + h) * hd)[i] = reinterpret_cast<const uint4*>(src + hd)[i];
   } else {
     const int kh = is_v ? h - nq - nkv : h - nq;
     const int page = page_table[static_cast<size_t>(seq[r]) * max_pages + p / kGqaPage];
@@ -492,9 +498,10 @@ int plow_gqa_attention(const void* q, const void* kc, const void* vc, int64_t n_
 
 // qkv bf16 [rows][ld_qkv] = [q heads | k heads | v heads]; qn / kn: optional per-head RMSNorm weights [hd];
 // rope_tab f32 [max_pos][rot] = [cos(rot/2) | sin(rot/2)]; pair_mode 0 = half split, 1 = interleaved.
+// gate_out (optional) bf16 [rows][nq*hd]: gated attention, query heads are then [Q | gate] pairs of width 2*hd.
 int plow_rope_kv(void* q_out, const void* qkv, int ld_qkv, void* kc, void* vc, const void* qn, const void* kn,
                  const float* rope_tab, const int* pos, const int* seq, const int* page_table, int max_pages,
-                 int rows, int nq, int nkv, int hd, int rot, int pair_mode, int plus_one, float eps, void* stream_) {
+                 int rows, int nq, int nkv, int hd, int rot, int pair_mode, int plus_one, float eps, void* gate_out, void* stream_) {
   using namespace plow;
   if (rows <= 0 || hd % 8 || rot > hd || rot % 2) return -1;
   const long long items = static_cast<long long>(rows) * (nq + 2 * nkv);
@@ -503,7 +510,8 @@ int plow_rope_kv(void* q_out, const void* qkv, int ld_qkv, void* kc, void* vc, c
                    reinterpret_cast<cudaStream_t>(stream_)>>>(
       static_cast<__nv_bfloat16*>(q_out), static_cast<const __nv_bfloat16*>(qkv), ld_qkv, static_cast<__nv_bfloat16*>(kc),
       static_cast<__nv_bfloat16*>(vc), static_cast<const __nv_bfloat16*>(qn), static_cast<const __nv_bfloat16*>(kn),
-      rope_tab, pos, seq, page_table, max_pages, rows, nq, nkv, hd, rot, pair_mode, plus_one, eps);
+      rope_tab, pos, seq, page_table, max_pages, rows, nq, nkv, hd, rot, pair_mode, plus_one, eps,
+      static_cast<__nv_bfloat16*>(gate_out));
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }

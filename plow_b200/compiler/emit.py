@@ -135,12 +135,14 @@ class Lowering:
                                           max(1, N // 64), "gemm" if op == Op.GEMM else "comm"))
             elif n.op == "rope_kv":
                 qkv, qn, kn, rope = n.inputs[0], n.inputs[1], n.inputs[2], n.inputs[3]
-                q_out, kc, vc = n.outputs
+                q_out, kc, vc = n.outputs[:3]
+                gate = n.outputs[3] if len(n.outputs) > 3 else None
                 ins = pk.Inst(Op.ROPE_KV, f=(a.get("eps", 0.0), 0, 0),
-                              t=[self.t(q_out), self.t(qkv), self.t(kc), self.t(vc), self.t(qn), self.t(kn), self.t(rope)],
+                              t=[self.t(q_out), self.t(qkv), self.t(kc), self.t(vc), self.t(qn), self.t(kn), self.t(rope)]
+                              + ([self.t(gate)] if gate else []),
                               i=[a["heads"], a["kv_heads"], a["head_dim"], a["rot_dim"], PAIR_MODE[a["pair_mode"]],
-                                 n.layer, int(a.get("plus_one", False))])
-                out.append(schedule.LInst(ins, rd(qkv, qn, kn, rope), rd(q_out, kc, vc),
+                                 n.layer, int(a.get("plus_one", False)), int(bool(gate))])
+                out.append(schedule.LInst(ins, rd(qkv, qn, kn, rope), rd(q_out, kc, vc, gate),
                                           costmodel.rowwise_cost(rows, self.width(qkv), 2, es).time_us(self.hw), rows))
             elif n.op == "attention":
                 q, kc, vc = n.inputs

@@ -112,6 +112,14 @@ def rule_rope_kv_fuse(g: Graph, sites: list) -> bool:
             qn, kn = hq.inputs[1], hk.inputs[1]
             q_in, k_in = hq.inputs[0], hk.inputs[0]
             swallowed += [hq, hk]
+        # gated attention: the q projection carries [Q | gate] per head; the split is folded into the fused op
+        gate_out = None
+        sg = prod.get(q_in)
+        if sg is not None and sg.op == "split_q_gate":
+            if not _single_use(cons, sg.outputs[0], q_user):
+                continue
+            gate_out, q_in, q_user = sg.outputs[1], sg.inputs[0], sg
+            swallowed.append(sg)
         vq, vk, vv = prod.get(q_in), prod.get(k_in), prod.get(v)
         if not all(x is not None and x.op == "view" for x in (vq, vk, vv)):
             continue
@@ -123,8 +131,8 @@ def rule_rope_kv_fuse(g: Graph, sites: list) -> bool:
         qkv = vq.inputs[0]
         swallowed += [vq, vk, vv]
         fused = Node("rope_kv", [qkv, qn, kn, rq.inputs[1], "in.pos", "in.seq"],
-                     [rq.outputs[0], n.outputs[0], n.outputs[1]],
-                     dict(heads=rq.attrs["heads"], kv_heads=rk.attrs["heads"], head_dim=rq.attrs["head_dim"],
+                     [rq.outputs[0], n.outputs[0], n.outputs[1]] + ([gate_out] if gate_out else []),
+                     dict(gated=bool(gate_out), heads=rq.attrs["heads"], kv_heads=rk.attrs["heads"], head_dim=rq.attrs["head_dim"],
                           rot_dim=rq.attrs["rot_dim"], pair_mode=rq.attrs["pair_mode"],
                           eps=(hq.attrs["eps"] if has_norm else 0.0),
                           plus_one=(hq.attrs.get("plus_one", False) if has_norm else False)),

@@ -17,13 +17,14 @@ BF16 = torch.bfloat16
 
 
 def rope_kv(qkv, kc, vc, rope_tab, pos, seq, page_table, nq, nkv, hd, rot=None, pair_mode=0,
-            qn=None, kn=None, eps=1e-6, plus_one=False, q_out=None):
-    """qkv [rows, (nq+2*nkv)*hd] bf16 -> q_out [rows, nq, hd]; K (roped) and V rows land in their cache cells."""
+            qn=None, kn=None, eps=1e-6, plus_one=False, q_out=None, gate_out=None):
+    """qkv [rows, (nq+2*nkv)*hd] bf16 -> q_out [rows, nq, hd]; K (roped) and V rows land in their cache cells.
+    With ``gate_out`` [rows, nq*hd] the query heads are [Q | gate] pairs (gated attention) and the gates are copied out."""
     rows = qkv.shape[0]
     if q_out is None:
         q_out = torch.empty(rows, nq, hd, dtype=BF16, device=qkv.device)
     native.call("plow_rope_kv", q_out, qkv, qkv.stride(0), kc, vc, qn, kn, rope_tab, pos, seq, page_table,
-                page_table.shape[1], rows, nq, nkv, hd, hd if rot is None else rot, pair_mode, int(plus_one), float(eps))
+                page_table.shape[1], rows, nq, nkv, hd, hd if rot is None else rot, pair_mode, int(plus_one), float(eps), gate_out)
     return q_out
 
 

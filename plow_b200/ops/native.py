@@ -129,7 +129,7 @@ _SIGS = {
     "plow_gated_norm": "pppiipiiifp",
     "plow_sigmoid_gate": "ppplp",
     "plow_gqa_attention": "ppplpipp" "iiiiiii" "pi" "ppppp" "fpp",
-    "plow_rope_kv": "ppi" "pppppppp" "i" "iiiiiii" "fp",
+    "plow_rope_kv": "ppi" "pppppppp" "i" "iiiiiii" "fpp",
 }
 _CT = {"p": C.c_void_p, "i": C.c_int32, "l": C.c_int64, "f": C.c_float, "L": C.c_uint64, "I": C.c_uint32}
 

@@ -24,7 +24,7 @@ import torch
 
 from ..compiler import packet as pk
 from ..compiler.packet import Op
-from ..ops import gemm as gemm_ops, gqa as gqa_ops, mla as mla_ops, native, quant, rowops
+from ..ops import gdn as gdn_ops, gemm as gemm_ops, gqa as gqa_ops, mla as mla_ops, native, quant, rowops
 from ..utils.rope import rope_table
 from .device_interp import DeviceInterp
 from .engine import EngineBase, EngineError, StepResult, TokenBatch
@@ -158,6 +158,8 @@ class GpuEngine(EngineBase):
         pages_per_seq = (max_ctx + PAGE - 1) // PAGE
         if n_pages is None:
             n_pages = max_slots * pages_per_seq
+        if any(t.tclass == pk.TClass.STATE for t in packet.tensors):
+            prefix_cache = False      # recurrent state is per slot, not per page: a prefix hit would skip its update
         super().__init__(packet, max_slots, n_pages, max_ctx, prefix_cache)
         self.scratch_slot = max_slots                  # padding rows of a rung live here
         self.scratch_page = n_pages                    # one extra page nobody else maps
@@ -207,6 +209,10 @@ class GpuEngine(EngineBase):
                 dims = [self.pool.n_pages + 1 if d == -3 else int(d) for d in t.dims]
                 dt = _TORCH_DT[pk.DType(t.dtype)]
                 self.static[h] = torch.zeros(dims, dtype=dt, device=dev) if dt != FP8 else torch.zeros(dims, dtype=torch.uint8, device=dev).view(FP8)
+            elif tc == pk.TClass.STATE:
+                # recurrent state, one entry per slot (+ the scratch slot padding rows point at)
+                dims = [self.max_slots + 1 if d == -4 else int(d) for d in t.dims]
+                self.static[h] = torch.zeros(dims, dtype=_TORCH_DT[pk.DType(t.dtype)], device=dev)
             elif tc == pk.TClass.INPUT:
                 self.static[h] = self.d_in[{"in.ids": 0, "in.pos": 1, "in.seq": 2, "in.sample_rows": 3}[t.name]]
             elif tc == pk.TClass.OUTPUT:
@@ -441,11 +447,12 @@ class GpuEngine(EngineBase):
         kn = self.tensor(st, ins.t[5]) if ins.t[5] != pk.T_NONE else None
         rope = self.tensor(st, ins.t[6])
         nq, nkv, hd, rot, pair, plus_one = ins.i[0], ins.i[1], ins.i[2], ins.i[3], ins.i[4], ins.i[6]
+        gate = self.tensor(st, ins.t[7]) if ins.i[7] and ins.t[7] != pk.T_NONE else None
         if kc.dtype != BF16:
             raise EngineError("the sm_100a GQA kernels read a bf16 KV cache; compile with plow_kv_dtype=bf16")
         gqa_ops.rope_kv(qkv, kc, vc, rope, self.d_in[1], self.d_in[2], self.d_page_table, nq, nkv, hd, rot=rot,
                         pair_mode=pair, qn=qn, kn=kn, eps=float(ins.f[0]), plus_one=bool(plus_one),
-                        q_out=q_out.view(st.rows, nq, hd))
+                        q_out=q_out.view(st.rows, nq, hd), gate_out=gate)
 
     def _op_attn(self, st, ins):
         ao, q, kc, vc = (self.tensor(st, ins.t[k]) for k in range(4))
@@ -455,6 +462,20 @@ class GpuEngine(EngineBase):
             st.scratch[key] = gqa_ops.AttnWorkspace(st.rows, nq, nkv, hd, self.max_ctx + PAGE, self.device)
         gqa_ops.attention(q.view(st.rows, nq, hd), kc, vc, self.d_page_table, self.d_in[2], self.d_in[1], st.scratch[key],
                           scale=float(ins.f[0]), window=window, out=ao)
+
+    # -- gated delta rule (hybrid linear-attention layers)
+    def _op_gdn(self, st, ins):
+        out, conv_state, ssm_state, qkvz, ba, conv_w, a_log, dt_bias = (self.tensor(st, ins.t[k]) for k in range(8))
+        hk, hv, hd, conv = ins.i[0], ins.i[1], ins.i[2], ins.i[3]
+        gdn_ops.gdn(qkvz, ba, conv_w, a_log, dt_bias, conv_state, ssm_state, self.d_in[1], self.d_in[2], hk, hv, hd, conv, out=out)
+
+    def _op_gated_norm(self, st, ins):
+        out, o, z, gamma = (self.tensor(st, ins.t[k]) for k in range(4))
+        gdn_ops.gated_norm(o, z, ins.i[2], gamma, ins.i[0], ins.i[1], float(ins.f[0]), out=out)
+
+    def _op_sigmoid_gate(self, st, ins):
+        out, a, gate = (self.tensor(st, ins.t[k]) for k in range(3))
+        gdn_ops.sigmoid_gate(a, gate, out=out)
 
     # -- MoE
     def _op_router_topk(self, st, ins):
@@ -509,6 +530,7 @@ class GpuEngine(EngineBase):
         Op.EMBED: "_op_embed", Op.RMSNORM: "_op_rmsnorm", Op.ADD_NORM: "_op_add_norm", Op.RESIDUAL: "_op_residual",
         Op.GEMM: "_op_gemm", Op.ROW_GATHER: "_op_row_gather", Op.ARGMAX: "_op_argmax",
         Op.ROPE_KV: "_op_rope_kv", Op.ATTN: "_op_attn", Op.GLU: "_op_glu",
+        Op.GDN_STEP: "_op_gdn", Op.GATED_NORM: "_op_gated_norm", Op.SIGMOID_GATE: "_op_sigmoid_gate",
         Op.MLA_KV_WRITE: "_op_mla_kv_write", Op.MLA_DECODE: "_op_mla_attention", Op.MLA_PREFILL: "_op_mla_attention",
         Op.ROUTER_TOPK: "_op_router_topk", Op.MOE_GEMM: "_op_moe_experts", Op.NOP: None,
     }

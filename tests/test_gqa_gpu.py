@@ -103,3 +103,30 @@ def test_rope_kv(pair_mode, rot, norm):
         for h in range(nkv):
             assert _err(cell_k[h], ref_head(v[r, nq + h], kn, p)) < 1e-2
             assert torch.equal(cell_v[h], v[r, nq + nkv + h])
+
+
+def test_rope_kv_gated_heads():
+    """Gated attention: query heads arrive as [Q | gate] pairs; Q is roped into q_out, the gates are copied out, K/V follow."""
+    from plow_b200.ops import gqa
+    torch.manual_seed(4)
+    nq, nkv, hd, rows, rot = 4, 1, 256, 9, 64
+    qkv = torch.randn(rows, nq * 2 * hd + 2 * nkv * hd, device="cuda").bfloat16()
+    tab = torch.randn(64, rot, device="cuda")
+    pos = torch.arange(rows, dtype=torch.int32, device="cuda")
+    seq = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    pt = torch.tensor([[3, 4]], dtype=torch.int32, device="cuda")
+    kc = torch.zeros(6, 64, nkv, hd, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    gate = torch.zeros(rows, nq * hd, dtype=torch.bfloat16, device="cuda")
+    q_out = gqa.rope_kv(qkv, kc, vc, tab, pos, seq, pt, nq, nkv, hd, rot=rot, pair_mode=0, gate_out=gate)
+    torch.cuda.synchronize()
+    qh = qkv[:, :nq * 2 * hd].view(rows, nq, 2 * hd)
+    assert torch.equal(gate.view(rows, nq, hd), qh[..., hd:])
+    half = rot // 2
+    x = qh[..., :hd].float()
+    c, s = tab[pos.long(), :half][:, None, :], tab[pos.long(), half:][:, None, :]
+    want = x.clone()
+    want[..., :half] = x[..., :half] * c - x[..., half:rot] * s
+    want[..., half:rot] = x[..., half:rot] * c + x[..., :half] * s
+    assert _err(q_out, want) < 1e-2
+    assert torch.equal(vc[3, :rows, 0], qkv[:, nq * 2 * hd + hd:])
