@@ -263,6 +263,32 @@ dsa_topk_kernel(int* sel, const float* scores, int ld_scores, const int* pos, in
     if (dsa_key(sc[i], i) >= prefix && at < top_k) out[at++] = i;
 }
 
+// One warp per (query row, selected slot): copies the selected token's latent-cache row (row_bytes) and scale into
+// the row's compact cache, whose pages the dense decode kernel then walks; the per-page scale bound is kept with an
+// integer atomic max (scales are positive floats).  Unselected slots (-1) are left alone: the compact length hides them.
+__global__ void dsa_gather_kernel(uint8_t* ckv, float* cscale, float* csmax, int* clen, const int* sel, int top_k,
+                                  const uint8_t* cache, const float* scale, const int* pos, const int* seq,
+                                  const int* page_table, int max_pages, int rows, int row_bytes) {
+  const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + wib;
+  if (item >= static_cast<long long>(rows) * top_k) return;
+  const int r = static_cast<int>(item / top_k), j = static_cast<int>(item % top_k);
+  if (j == 0 && lane == 0) clen[r] = max(0, min(pos[r] + 1, top_k));
+  const int t = sel[item];
+  if (t < 0) return;
+  const int page = page_table[static_cast<size_t>(seq[r]) * max_pages + t / kIdxPage];
+  const size_t src = static_cast<size_t>(page) * kIdxPage + t % kIdxPage;
+  const size_t dst = static_cast<size_t>(r) * top_k + j;                 // compact pages are contiguous per row
+  const uint4* s4 = reinterpret_cast<const uint4*>(cache + src * row_bytes);
+  uint4* d4 = reinterpret_cast<uint4*>(ckv + dst * row_bytes);
+  for (int u = lane; u < row_bytes / 16; u += 32) d4[u] = s4[u];
+  if (lane == 0) {
+    const float sc = scale[src];
+    cscale[dst] = sc;
+    atomicMax(reinterpret_cast<int*>(csmax + (dst / kIdxPage) * 4), __float_as_int(sc));
+  }
+}
+
 }  // namespace plow
 
 extern "C" {
@@ -305,6 +331,24 @@ int plow_dsa_select(int* sel, float* scores, int ld_scores, void* q8, float* wq,
   dsa_score_kernel<<<dim3((max_len + 127) / 128, rows), 128, kSmem, stream>>>(scores, ld_scores, wq, cache_scale, pos, seq, page_table,
                                                                             max_pages, status, tk, tq);
   dsa_topk_kernel<<<rows, 1024, 0, stream>>>(sel, scores, ld_scores, pos, top_k);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
+}
+
+// Gather the selected cache rows of every query row into its compact cache: ckv [rows*top_k/64 pages][64][row_bytes],
+// cscale f32 [pages][64], csmax f32 [pages][4] (zeroed here), clen int32 [rows] = min(pos+1, top_k).  top_k % 64 == 0.
+int plow_dsa_gather(void* ckv, float* cscale, float* csmax, int* clen, const int* sel, int top_k, const void* cache,
+                    const float* scale, const int* pos, const int* seq, const int* page_table, int max_pages, int rows,
+                    int row_bytes, void* stream_) {
+  using namespace plow;
+  if (rows <= 0 || top_k <= 0 || top_k % kIdxPage || row_bytes % 16) return -1;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const size_t pages = static_cast<size_t>(rows) * (top_k / kIdxPage);
+  cudaMemsetAsync(csmax, 0, pages * 4 * sizeof(float), stream);
+  const long long items = static_cast<long long>(rows) * top_k;
+  dsa_gather_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
+      static_cast<uint8_t*>(ckv), cscale, csmax, clen, sel, top_k, static_cast<const uint8_t*>(cache), scale, pos, seq,
+      page_table, max_pages, rows, row_bytes);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }

@@ -36,6 +36,28 @@ def select(q, w, cache, cache_scale, rope_tab, pos, seq, page_table, top_k, ws: 
     return out
 
 
+class CompactCache:
+    """Per-row compact latent cache the dense MLA decode kernel walks after a sparse selection."""
+
+    def __init__(self, rows, top_k, row_bytes, device):
+        assert top_k % 64 == 0
+        self.rows, self.top_k, self.pages_per = rows, top_k, top_k // 64
+        n = rows * self.pages_per
+        self.kv = torch.zeros(n, 64, row_bytes, dtype=torch.uint8, device=device).view(FP8)
+        self.scale = torch.zeros(n, 64, dtype=torch.float32, device=device)
+        self.smax = torch.zeros(n, 4, dtype=torch.float32, device=device)
+        self.kvlen = torch.zeros(rows, dtype=torch.int32, device=device)
+        self.page_table = torch.arange(n, dtype=torch.int32, device=device).view(rows, self.pages_per).contiguous()
+        self.slot_of = torch.arange(rows, dtype=torch.int32, device=device)
+
+
+def gather(cc: CompactCache, sel, cache, scale, pos, seq, page_table):
+    """Copy every row's selected tokens (sel [rows, top_k], -1 padded) into its compact cache."""
+    rows = sel.shape[0]
+    native.call("plow_dsa_gather", cc.kv, cc.scale, cc.smax, cc.kvlen, sel, cc.top_k, cache, scale, pos, seq, page_table,
+                page_table.shape[1], rows, cache.shape[2])
+
+
 def _rope(x, tab, rot, pair_mode):
     half = rot // 2
     c, s = tab[..., :half], tab[..., half:]

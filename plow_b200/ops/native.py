@@ -125,6 +125,7 @@ _SIGS = {
     "plow_sample": "ppiiipppppp" "Lp",
     "plow_dsa_k_write": "pppipppppp" "iiiifp",
     "plow_dsa_select": "ppippp" "ipipplp" "pppiiiiiipp",
+    "plow_dsa_gather": "pppppi" "pppppi" "iip",
     "plow_gdn": "ppppipi" "ppppp" "iiiiip",
     "plow_gated_norm": "pppiipiiifp",
     "plow_sigmoid_gate": "ppplp",

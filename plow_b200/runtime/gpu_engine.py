@@ -24,7 +24,7 @@ import torch
 
 from ..compiler import packet as pk
 from ..compiler.packet import Op
-from ..ops import gdn as gdn_ops, gemm as gemm_ops, gqa as gqa_ops, mla as mla_ops, native, quant, rowops
+from ..ops import dsa as dsa_ops, gdn as gdn_ops, gemm as gemm_ops, gqa as gqa_ops, mla as mla_ops, native, quant, rowops
 from ..utils.rope import rope_table
 from .device_interp import DeviceInterp
 from .engine import EngineBase, EngineError, StepResult, TokenBatch
@@ -404,10 +404,25 @@ class GpuEngine(EngineBase):
             self._mla_ws = mla_ops.DecodeWorkspace(max(T, self.max_rows_all), self.max_ctx + PAGE, device=self.device)
         if self._mla_ws.max_splits > 8:
             raise EngineError("max_ctx needs more than 8 KV splits; raise tiles_per_split")
-        mla_ops.decode(q8, sq, cache, scale, self.kv_smax[layer], self.d_page_table, self.d_in[2], self.d_kvlen_row,
-                       self._mla_ws, float(ins.f[0]), merge=False)
+        sparse = bool(ins.i[6]) and ins.t[7] != pk.T_NONE and T <= self.SPARSE_MAX_ROWS
+        if sparse:
+            # sparse attention: the indexer's selection is gathered into a compact per-row cache and the same decode
+            # kernel walks it (reference: runtime/nvidia/op_dsa.cuh, crates/devgen/src/mla.rs:7093).  Programs with more
+            # rows than SPARSE_MAX_ROWS (large prefill buckets) attend densely.
+            top_k = self.tensor(st, ins.t[7]).shape[1]
+            key = ("dsa_cc", T, top_k)
+            if key not in st.scratch:
+                st.scratch[key] = dsa_ops.CompactCache(T, top_k, cache.shape[2], self.device)
+            cc = st.scratch[key]
+            dsa_ops.gather(cc, self.tensor(st, ins.t[7]), cache, scale, self.d_in[1], self.d_in[2], self.d_page_table)
+            mla_ops.decode(q8, sq, cc.kv, cc.scale, cc.smax, cc.page_table, cc.slot_of, cc.kvlen, self._mla_ws, float(ins.f[0]), merge=False)
+            kvlen = cc.kvlen
+        else:
+            mla_ops.decode(q8, sq, cache, scale, self.kv_smax[layer], self.d_page_table, self.d_in[2], self.d_kvlen_row,
+                           self._mla_ws, float(ins.f[0]), merge=False)
+            kvlen = self.d_kvlen_row
         want = self._wants_q(st, ins.t[0])
-        aq, saq = mla_ops.fold(self._mla_ws, self.d_kvlen_row, wuv, T, heads, ao, want_fp8=want)
+        aq, saq = mla_ops.fold(self._mla_ws, kvlen, wuv, T, heads, ao, want_fp8=want)
         if want:
             st.q[(ins.t[0], 0)] = (aq, saq)
 
@@ -477,6 +492,23 @@ class GpuEngine(EngineBase):
         out, a, gate = (self.tensor(st, ins.t[k]) for k in range(3))
         gdn_ops.sigmoid_gate(a, gate, out=out)
 
+    # -- sparse-attention indexer
+    SPARSE_MAX_ROWS = 256
+
+    def _op_dsa_index(self, st, ins):
+        kcache, ksc, ki, kn_w, kn_b, rope = (self.tensor(st, ins.t[k]) for k in range(6))
+        dsa_ops.k_write(kcache, ksc, ki, kn_w, kn_b, rope, self.d_in[1], self.d_in[2], self.d_page_table, ins.i[1])
+
+    def _op_dsa_topk(self, st, ins):
+        sel, qi, wts, kcache, ksc, rope = (self.tensor(st, ins.t[k]) for k in range(6))
+        if st.rows > self.SPARSE_MAX_ROWS:
+            return                      # the attention of this program runs densely and does not read the selection
+        key = ("dsa_ws", st.rows)
+        if key not in st.scratch:
+            st.scratch[key] = dsa_ops.SelectWorkspace(st.rows, self.max_ctx + PAGE, self.device)
+        dsa_ops.select(qi, wts, kcache, ksc, rope, self.d_in[1], self.d_in[2], self.d_page_table, ins.i[2], st.scratch[key],
+                       ins.i[3], out=sel)
+
     # -- MoE
     def _op_router_topk(self, st, ins):
         table, logits = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])
@@ -530,6 +562,7 @@ class GpuEngine(EngineBase):
         Op.EMBED: "_op_embed", Op.RMSNORM: "_op_rmsnorm", Op.ADD_NORM: "_op_add_norm", Op.RESIDUAL: "_op_residual",
         Op.GEMM: "_op_gemm", Op.ROW_GATHER: "_op_row_gather", Op.ARGMAX: "_op_argmax",
         Op.ROPE_KV: "_op_rope_kv", Op.ATTN: "_op_attn", Op.GLU: "_op_glu",
+        Op.DSA_INDEX: "_op_dsa_index", Op.DSA_TOPK: "_op_dsa_topk",
         Op.GDN_STEP: "_op_gdn", Op.GATED_NORM: "_op_gated_norm", Op.SIGMOID_GATE: "_op_sigmoid_gate",
         Op.MLA_KV_WRITE: "_op_mla_kv_write", Op.MLA_DECODE: "_op_mla_attention", Op.MLA_PREFILL: "_op_mla_attention",
         Op.ROUTER_TOPK: "_op_router_topk", Op.MOE_GEMM: "_op_moe_experts", Op.NOP: None,

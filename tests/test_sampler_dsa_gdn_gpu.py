@@ -148,3 +148,53 @@ def test_gdn_prefill_then_decode_and_gated_norm():
     g = torch.randn(42, hv * d, device=dev).bfloat16()
     sg = gdn.sigmoid_gate(out, g)
     assert (sg.float() - out.float() * torch.sigmoid(g.float())).abs().max().item() < 2e-2
+
+
+def test_dsa_gather_feeds_dense_decode_kernel():
+    """Sparse MLA: gathering each row's selected tokens into its compact cache and decoding over it equals decoding over
+    a cache that holds exactly those tokens."""
+    import math
+    from plow_b200.ops import dsa, mla, native
+    torch.manual_seed(6)
+    dev = "cuda"
+    T, ctx, top_k = 3, 700, 128
+    pages_per = (ctx + 63) // 64
+    n_pages = T * pages_per + 1
+    kv8 = torch.randn(n_pages, 64, 576, device=dev).to(torch.float8_e4m3fn)
+    ksc = torch.rand(n_pages, 64, device=dev) * 0.01 + 0.005
+    pt = (torch.arange(T * pages_per, dtype=torch.int32, device=dev).view(T, pages_per) + 1).contiguous()
+    seq = torch.arange(T, dtype=torch.int32, device=dev)
+    pos = torch.tensor([ctx - 1, 99, 400], dtype=torch.int32, device=dev)
+    sel = torch.full((T, top_k), -1, dtype=torch.int32, device=dev)
+    for r in range(T):
+        n = int(pos[r]) + 1
+        pick = torch.arange(n) if n <= top_k else torch.randperm(n)[:top_k].sort().values
+        sel[r, :len(pick)] = pick.int().to(dev)
+    cc = dsa.CompactCache(T, top_k, 576, dev)
+    dsa.gather(cc, sel, kv8, ksc, pos, seq, pt)
+    torch.cuda.synchronize()
+    assert cc.kvlen.tolist() == [128, 100, 128]
+    # oracle cache: the selected rows copied with torch indexing
+    okv = torch.zeros_like(cc.kv.view(torch.uint8))
+    osc = torch.zeros_like(cc.scale)
+    for r in range(T):
+        n = int(cc.kvlen[r])
+        t = sel[r, :n].long()
+        pages = pt[r][(t // 64)].long()
+        flat_kv = okv.view(T, top_k, 576)
+        flat_kv[r, :n] = kv8.view(torch.uint8)[pages, t % 64]
+        osc.view(T, top_k)[r, :n] = ksc[pages, t % 64]
+    assert torch.equal(okv.view(T, top_k, 576)[0], cc.kv.view(torch.uint8).view(T, top_k, 576)[0])
+    osmax = torch.zeros_like(cc.smax)
+    osmax[:, 0] = osc.amax(1)
+    assert torch.allclose(osmax[:, 0], cc.smax[:, 0])
+    q8 = torch.randn(128, T, 576, device=dev).to(torch.float8_e4m3fn)
+    sq = torch.rand(128, T, device=dev) * 0.01
+    ws = mla.DecodeWorkspace(T, top_k + 64, tiles_per_split=64)
+    a = torch.empty(128, T, 512, dtype=torch.bfloat16, device=dev)
+    b = torch.empty_like(a)
+    mla.decode(q8, sq, cc.kv, cc.scale, cc.smax, cc.page_table, cc.slot_of, cc.kvlen, ws, 1 / math.sqrt(192), out=a)
+    mla.decode(q8, sq, okv.view(torch.float8_e4m3fn), osc, osmax, cc.page_table, cc.slot_of, cc.kvlen, ws, 1 / math.sqrt(192), out=b)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert torch.equal(a, b)
