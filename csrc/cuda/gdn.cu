@@ -53,7 +53,6 @@ gdn_kernel(__nv_bfloat16* out, float* conv_state, float* ssm_state, const __nv_b
   const int C = (2 * hk + hv) * kD;
   const int cq = kh * kD + i, ck = hk * kD + kh * kD + i, cv = 2 * hk * kD + h * kD + i;
   const bool fresh = pos[r0] == 0;
-  const bool owns_qk = (h % rep) == 0;
   // ---- state in: coalesced global -> padded smem -> one row per thread
   float S[kD];
   float* Sg = ssm_state + (static_cast<size_t>(slot) * hv + h) * kD * kD;
@@ -126,12 +125,31 @@ gdn_kernel(__nv_bfloat16* out, float* conv_state, float* ssm_state, const __nv_b
   for (int c = 0; c < kD; ++c) tile[i * (kD + 1) + c] = S[c];
   __syncthreads();
   for (int e = i; e < kD * kD; e += kD) Sg[e] = tile[(e >> 7) * (kD + 1) + (e & 127)];
+}
+
+// Conv history update, one thread per (run start, channel): new history = the last W-1 inputs of (old history ++ run).
+// It runs after gdn_kernel because several v heads of that kernel read the q / k channels of the key head they share;
+// updating them from inside it would race with a CTA that has not read the old history yet.
+__global__ void gdn_conv_state_kernel(float* conv_state, const __nv_bfloat16* qkvz, int ld_qkvz, const int* pos, const int* seq,
+                                      int rows, int C) {
+  constexpr int W = kConvMax;
+  const int r0 = blockIdx.x;
+  if (pos[r0] < 0) return;
+  if (r0 > 0 && pos[r0 - 1] >= 0 && seq[r0 - 1] == seq[r0] && pos[r0 - 1] + 1 == pos[r0]) return;
+  int n = 1;
+  while (r0 + n < rows && seq[r0 + n] == seq[r0] && pos[r0 + n] == pos[r0 + n - 1] + 1) ++n;
+  const bool fresh = pos[r0] == 0;
+  float* cs = conv_state + static_cast<size_t>(seq[r0]) * C * (W - 1);
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float h[W - 1];
 #pragma unroll
-  for (int j = 0; j < kConvMax - 1; ++j) {
-    if (j < W - 1) {
-      cs[cv * (W - 1) + j] = hvv[j];
-      if (owns_qk) { cs[cq * (W - 1) + j] = hq[j]; cs[ck * (W - 1) + j] = hkk[j]; }
+    for (int j = 0; j < W - 1; ++j) {
+      const int back = (W - 1) - j;            // this slot holds the input `back` steps before the next token
+      h[j] = back <= n ? __bfloat162float(qkvz[static_cast<size_t>(r0 + n - back) * ld_qkvz + c])
+                       : (fresh ? 0.f : cs[c * (W - 1) + j + n]);
     }
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j) cs[c * (W - 1) + j] = h[j];
   }
 }
 
@@ -180,6 +198,8 @@ int plow_gdn(void* out, float* conv_state, float* ssm_state, const void* qkvz, i
   gdn_kernel<<<dim3(rows, hv), kD, kSmem, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(out), conv_state, ssm_state, static_cast<const __nv_bfloat16*>(qkvz), ld_qkvz,
       static_cast<const __nv_bfloat16*>(ba), ld_ba, conv_w, a_log, dt_bias, pos, seq, rows, hk, hv, conv);
+  gdn_conv_state_kernel<<<rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      conv_state, static_cast<const __nv_bfloat16*>(qkvz), ld_qkvz, pos, seq, rows, (2 * hk + hv) * kD);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }

@@ -645,13 +645,17 @@ class GpuEngine(EngineBase):
         try:
             if self.cuda_graphs and batch.decode:
                 if st.graph is None:
-                    self._run_insts(st)                      # warm-up (allocations, attribute sets)
+                    # the first step of a rung runs eagerly (allocations, attribute sets) and IS the step; the graph is
+                    # captured afterwards without being replayed, because a program with recurrent state (gated delta
+                    # rule) is not idempotent: executing it twice would advance the state twice
+                    self._run_insts(st)
                     torch.cuda.synchronize()
                     g = torch.cuda.CUDAGraph()
                     with torch.cuda.graph(g):
                         self._run_insts(st)
                     st.graph = g
-                st.graph.replay()
+                else:
+                    st.graph.replay()
             else:
                 self._run_insts(st)
             self.h_out[:st.samples].copy_(self.d_out_ids[:st.samples], non_blocking=True)
