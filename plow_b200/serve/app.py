@@ -25,6 +25,7 @@ from .. import __version__
 from ..obs import prometheus
 from ..runtime.engine import EngineHealth
 from ..runtime.scheduler import GenParams
+from . import tools as tools_mod
 from .template import ChatTemplateError
 
 REFUSED_PARAMS = ("response_format", "echo", "best_of", "logit_bias", "suffix", "functions", "function_call")
@@ -84,9 +85,11 @@ def _finish(reason: str) -> tuple:
 
 
 class ModelEntry:
-    def __init__(self, name, mux, tokenizer, template, created=None):
+    def __init__(self, name, mux, tokenizer, template, created=None, tool_family=None, reasoning=False):
         self.name, self.mux, self.tok, self.template = name, mux, tokenizer, template
         self.created = created or int(time.time())
+        self.tool_family = tool_family        # serve.tools parser family (None = detect from the text)
+        self.reasoning = reasoning            # split <think>…</think> into reasoning_content
 
 
 class AppState:
@@ -281,22 +284,54 @@ def create_app(state: AppState) -> FastAPI:
         rid, created = f"chatcmpl-{uuid.uuid4().hex[:24]}", int(time.time())
         base = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": m.name,
                 "system_fingerprint": state.fingerprint}
+        want_reasoning = bool(getattr(m, "reasoning", False)) or bool(body.get("separate_reasoning"))
+        want_tools = bool(body.get("tools")) and body.get("tool_choice") != "none"
         if body.get("stream"):
             include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
+            splitter = tools_mod.StreamSplitter() if want_reasoning else None
+
+            def _delta(text, final=False):
+                if splitter is None:
+                    return {"content": text} if text else {}
+                r, c = splitter.feed(text, final)
+                d = {}
+                if r:
+                    d["reasoning_content"] = r
+                if c:
+                    d["content"] = c
+                return d
 
             async def sse():
                 yield "data: " + json.dumps({**base, "choices": [{"index": 0, "delta": {"role": "assistant", "content": ""}, "finish_reason": None}]}) + "\n\n"
+                acc = []
                 while True:
                     if await request.is_disconnected():
                         req.cancelled = True
                         return
                     ch = await _next_chunk(req)
                     if ch.kind == "token":
-                        if ch.text:
-                            yield "data: " + json.dumps({**base, "choices": [{"index": 0, "delta": {"content": ch.text}, "finish_reason": None}]}) + "\n\n"
+                        acc.append(ch.text)
+                        if want_tools:
+                            continue          # tool calls are parsed from the whole message and sent with the last chunk
+                        d = _delta(ch.text)
+                        if d:
+                            yield "data: " + json.dumps({**base, "choices": [{"index": 0, "delta": d, "finish_reason": None}]}) + "\n\n"
                     elif ch.kind == "done":
                         fr, xfr = _finish(ch.finish_reason)
-                        last = {**base, "choices": [{"index": 0, "delta": ({"content": ch.text} if ch.text else {}), "finish_reason": fr}]}
+                        acc.append(ch.text)
+                        if want_tools:
+                            full = "".join(acc)
+                            reasoning, rest = tools_mod.split_reasoning(full) if want_reasoning else (None, full)
+                            content, calls = tools_mod.extract_tool_calls(rest, getattr(m, "tool_family", None))
+                            d = {"content": content} if content else {}
+                            if reasoning:
+                                d["reasoning_content"] = reasoning
+                            if calls:
+                                d["tool_calls"] = [dict(c, index=i) for i, c in enumerate(calls)]
+                                fr = "tool_calls"
+                        else:
+                            d = _delta(ch.text, final=True)
+                        last = {**base, "choices": [{"index": 0, "delta": d, "finish_reason": fr}]}
                         if xfr:
                             last["x_plow_finish_reason"] = xfr
                         yield "data: " + json.dumps(last) + "\n\n"
@@ -310,9 +345,21 @@ def create_app(state: AppState) -> FastAPI:
             return StreamingResponse(sse(), media_type="text/event-stream")
         text, toks, lps, reason, usage = await _collect(req)
         fr, xfr = _finish(reason)
+        message = {"role": "assistant", "content": text}
+        if want_reasoning:
+            reasoning, text = tools_mod.split_reasoning(text)
+            message["content"] = text
+            if reasoning is not None:
+                message["reasoning_content"] = reasoning
+        if want_tools:
+            content, calls = tools_mod.extract_tool_calls(text, getattr(m, "tool_family", None))
+            if calls:
+                message["content"] = content or None
+                message["tool_calls"] = calls
+                fr = "tool_calls"
         out = {"id": rid, "object": "chat.completion", "created": created, "model": m.name,
                "system_fingerprint": state.fingerprint,
-               "choices": [{"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": fr,
+               "choices": [{"index": 0, "message": message, "finish_reason": fr,
                             "logprobs": _lp_block(m, lps)}], "usage": usage}
         if xfr:
             out["x_plow_finish_reason"] = xfr

@@ -1,0 +1,42 @@
+"""Tool-call parsers per model family and the reasoning split (whole-message and streaming)."""
+import json
+
+
+def test_family_parsers():
+    from plow_b200.serve import tools as t
+    c, calls = t.extract_tool_calls('Sure.<tool_call>\n{"name": "get_weather", "arguments": {"city": "Paris"}}\n</tool_call>', "hermes")
+    assert c == "Sure." and calls[0]["function"]["name"] == "get_weather" and json.loads(calls[0]["function"]["arguments"]) == {"city": "Paris"}
+    c, calls = t.extract_tool_calls('<|python_tag|>{"name": "f", "parameters": {"x": 1}}; {"name": "g", "parameters": {}}<|eom_id|>', "llama3")
+    assert [k["function"]["name"] for k in calls] == ["f", "g"]
+    c, calls = t.extract_tool_calls('ok [TOOL_CALLS][{"name": "add", "arguments": {"a": 1, "b": 2}}]', "mistral")
+    assert c == "ok" and json.loads(calls[0]["function"]["arguments"])["b"] == 2
+    ds = 'Let me check.<｜tool▁calls▁begin｜><｜tool▁call▁begin｜>function<｜tool▁sep｜>search\n```json\n{"q": "b200"}\n```<｜tool▁call▁end｜><｜tool▁calls▁end｜>'
+    c, calls = t.extract_tool_calls(ds)                      # family detected from the text
+    assert c == "Let me check." and calls[0]["function"]["name"] == "search"
+    glm = '<tool_call>lookup\n<arg_key>id</arg_key>\n<arg_value>42</arg_value>\n<arg_key>name</arg_key>\n<arg_value>plow</arg_value>\n</tool_call>'
+    c, calls = t.extract_tool_calls(glm, "glm")
+    assert json.loads(calls[0]["function"]["arguments"]) == {"id": 42, "name": "plow"}
+    kimi = '<|tool_calls_section_begin|><|tool_call_begin|>functions.run:0<|tool_call_argument_begin|>{"cmd": "ls"}<|tool_call_end|><|tool_calls_section_end|>'
+    c, calls = t.extract_tool_calls(kimi)
+    assert calls[0]["function"]["name"] == "run" and c == ""
+    oss = '<|channel|>commentary to=functions.get_time <|constrain|>json<|message|>{"tz": "UTC"}<|call|>'
+    c, calls = t.extract_tool_calls(oss, "gptoss")
+    assert calls[0]["function"]["name"] == "get_time"
+    assert t.extract_tool_calls("just text") == ("just text", [])
+    assert t.extract_tool_calls('<tool_call>{broken</tool_call>', "hermes") == ('<tool_call>{broken</tool_call>', [])
+
+
+def test_reasoning_split_whole_and_streaming():
+    from plow_b200.serve import tools as t
+    assert t.split_reasoning("<think>a b</think>answer") == ("a b", "answer")
+    assert t.split_reasoning("no tags") == (None, "no tags")
+    assert t.split_reasoning("plan</think>go", starts_in_reasoning=True) == ("plan", "go")
+    assert t.split_reasoning("<think>cut off") == ("cut off", "")
+    s = t.StreamSplitter()
+    pieces = ["<th", "ink>step", " one</th", "ink>The ans", "wer <b>"]
+    r, c = "", ""
+    for i, p in enumerate(pieces):
+        dr, dc = s.feed(p, final=i == len(pieces) - 1)
+        r += dr
+        c += dc
+    assert r == "step one" and c == "The answer <b>"
