@@ -240,10 +240,6 @@ def main() -> int:
     barrier()
     wall = time.perf_counter() - t0
     clocks = sampler.stop()
-    ttfts = []
-    # every rank prefills a prompt of the same length at the same time (EP layers are collective)
-    for n in list(np.random.default_rng(11).integers(1024, 8193, size=args.ttft_prompts)):
-        ttfts.append(prefill_once(int(n)))
     route = None
     if comm is not None and getattr(comm, "grp_off", None) is not None:
         go = comm.grp_off.cpu().numpy().astype(np.int64)       # rows per local expert in the last MoE layer
@@ -253,6 +249,10 @@ def main() -> int:
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         route = {"rows_rank0": int(go[-1]), "max_rows_any_rank": int(mx[0]), "max_rows_one_expert": int(mx[1]),
                  "mean_rows_per_rank": B * 8}
+    ttfts = []
+    # every rank prefills a prompt of the same length at the same time (EP layers are collective)
+    for n in list(np.random.default_rng(11).integers(1024, 8193, size=args.ttft_prompts)):
+        ttfts.append(prefill_once(int(n)))
     dev_total = float(np.sum(dev_ms))
     stats = torch.tensor([dev_total, wall, float(np.median(dev_ms))], dtype=torch.float64, device=dev)
     if world > 1:

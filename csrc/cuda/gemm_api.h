@@ -41,6 +41,9 @@ typedef struct PlowGemmDesc {
   const void* wait_epoch;
   int32_t wait_mult;
   int32_t wait_deadline_ms;
+  int32_t ar_oneshot;     // fused all-reduce form: 0 = two-shot (owner reduces, stores to every rank), 1 = one-shot (push + local reduce)
+  int32_t ar_pad;
+  uint64_t ar_half_bytes; // one-shot: bytes of one parity half of the partial area; ar_epoch points at 4 device words
 } PlowGemmDesc;
 
 // Launches on `stream` (a cudaStream_t).  Returns 0, or a host-side error code (<0 bad

@@ -54,8 +54,10 @@ struct GemmArgs {
   // reduced through peer memory from inside the kernel, see the `ar_*` phase at the end of the kernel
   uint8_t* ar_peer[8];    // symmetric region of every rank (peer-mapped), NULL world = off
   unsigned long long ar_part_ofs, ar_flag_ofs, ar_done_ofs, ar_y_ofs;
-  uint32_t* ar_epoch;     // device word, launch counter
+  uint32_t* ar_epoch;     // device words: [0] launch counter, [1] arrivals on `done` seen so far (two-shot), [2] CTAs through (one-shot)
   int ar_world, ar_me;
+  int ar_oneshot;          // 1: every rank pushes its partial to all ranks and reduces locally (decode sizes)
+  unsigned long long ar_half_bytes;   // one-shot: size of one parity half of the partial area
   long long* trace;       // optional clock64() phase stamps of CTA 0 (debug aid), NULL when off
   const uint32_t* wait_ctr;
   const uint32_t* wait_epoch;
@@ -563,6 +565,17 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
               __nv_bfloat162 h2 = __floats2bfloat162_rn(r[2 * j], r[2 * j + 1]);
               pk[j] = *reinterpret_cast<uint32_t*>(&h2);
             }
+            if (a.ar_oneshot) {
+              // one-shot: the partial goes straight into every rank's [parity][tile][source rank][feature][token] slot
+              const size_t po = a.ar_part_ofs + (ar_ep & 1) * a.ar_half_bytes +
+                                (static_cast<size_t>(((t.feat0 >> 7) * a.ar_world + a.ar_me) * 128 + li) * BN + c) * 2;
+              for (int p = 0; p < a.ar_world; ++p) {
+                uint4* pp = reinterpret_cast<uint4*>(a.ar_peer[p] + po);
+                pp[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                pp[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+              }
+              continue;
+            }
             uint4* pp = reinterpret_cast<uint4*>(a.ar_peer[a.ar_me] + a.ar_part_ofs +
                                                  (static_cast<size_t>((t.feat0 >> 7) * 128 + li) * BN + c) * 2);
             pp[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
@@ -622,8 +635,55 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           }
           ++xchg_it;
           const int tile = t.feat0 >> 7;
-          if (li == 0)
+          if (a.ar_oneshot) {
+            // tell every rank, then reduce this tile from the local slots as soon as every rank's flag is here
+            if (li < a.ar_world)
+              st_release_sys(reinterpret_cast<uint32_t*>(a.ar_peer[li] + a.ar_flag_ofs) + tile * 8 + a.ar_me, ar_ep);
+            if (li < a.ar_world) {
+              const uint32_t* f = reinterpret_cast<const uint32_t*>(a.ar_peer[a.ar_me] + a.ar_flag_ofs) + tile * 8 + li;
+              const unsigned long long t0 = globaltimer_ns();
+              const unsigned long long dl = static_cast<unsigned long long>(a.wait_deadline_ms ? a.wait_deadline_ms : 2000) * 1000000ull;
+              while (ld_acquire_sys(f) < ar_ep) {
+                if (*abort_flag || globaltimer_ns() - t0 > dl) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); break; }
+                __nanosleep(64);
+              }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
+            if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag) || *abort_flag) { ok = false; break; }
+            ++xchg_it;
+            const uint8_t* base = a.ar_peer[a.ar_me] + a.ar_part_ofs + (ar_ep & 1) * a.ar_half_bytes;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+              if (t.tok0 + c >= t.tok_end) break;
+              float acc16[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc16[j] = 0.f;
+              for (int r = 0; r < a.ar_world; ++r) {      // rank order: every rank forms the same sum, bit for bit
+                const uint4* pp = reinterpret_cast<const uint4*>(base + (static_cast<size_t>((tile * a.ar_world + r) * 128 + li) * BN + c) * 2);
+                const uint4 v0 = pp[0], v1 = pp[1];
+                const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&v0);
+                const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&v1);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 f0 = __bfloat1622float2(h0[j]), f1 = __bfloat1622float2(h1[j]);
+                  acc16[2 * j] += f0.x; acc16[2 * j + 1] += f0.y; acc16[8 + 2 * j] += f1.x; acc16[8 + 2 * j + 1] += f1.y;
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int tok = t.tok0 + c + j;
+                if (fok && tok < t.tok_end) {
+                  const size_t o = static_cast<size_t>(tok) * a.ldy + feat_i;
+                  float v = acc16[j];
+                  if (resid) v += __bfloat162float(resid[o]);
+                  reinterpret_cast<__nv_bfloat16*>(a.y)[o] = __float2bfloat16(v);
+                }
+              }
+            }
+          } else if (li == 0) {
             st_release_sys(reinterpret_cast<uint32_t*>(a.ar_peer[tile % a.ar_world] + a.ar_flag_ofs) + tile * 8 + a.ar_me, ar_ep);
+          }
         }
         if (ws_tile) {
           // the split that leaves last re-arms the tile's counters for the next launch
@@ -728,7 +788,14 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
     // stores the result into every rank's output; then one arrival per (tile, rank).  Reference
     // numerics: runtime/nvidia/op_collective.cuh:18-20.  Plain peer loads/stores, bounded waits.
     if constexpr (SWAP && !DUAL) {
-      if (a.ar_world > 1 && ok) {
+      if (a.ar_world > 1 && ok && a.ar_oneshot) {
+        // the launch counter moves on once every CTA of this launch is through (ar_epoch[2] counts them)
+        if (li == 0) {
+          __threadfence();
+          if (atomicAdd(&a.ar_epoch[2], 1u) == gridDim.x - 1) { a.ar_epoch[2] = 0; __threadfence(); a.ar_epoch[0] = ar_ep; }
+        }
+      }
+      if (a.ar_world > 1 && ok && !a.ar_oneshot) {
         const int W = a.ar_world;
         const int n_tiles = (a.N + 127) / 128;
         const unsigned long long dl = static_cast<unsigned long long>(a.wait_deadline_ms ? a.wait_deadline_ms : 2000) * 1000000ull;
@@ -806,10 +873,14 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         if (blockIdx.x == 0 && li == 0) {
           const uint32_t* d = reinterpret_cast<const uint32_t*>(a.ar_peer[a.ar_me] + a.ar_done_ofs);
           const unsigned long long t0 = globaltimer_ns();
-          while (ld_acquire_sys(d) < ar_ep * static_cast<uint32_t>(n_tiles)) {
+          // ar_epoch[1] = arrivals seen by the launches before this one (shapes, hence tile counts, differ between
+          // launches); no peer can be a launch ahead, because every tile needs this rank's partial of that launch
+          const uint32_t target = a.ar_epoch[1] + static_cast<uint32_t>(n_tiles);
+          while (ld_acquire_sys(d) - target > 0x7fffffffu) {      // wrap-safe "d < target"
             if (globaltimer_ns() - t0 > dl) { atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); break; }
             __nanosleep(128);
           }
+          a.ar_epoch[1] = target;
           *a.ar_epoch = ar_ep;
         }
       }

@@ -151,6 +151,7 @@ def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=N
         d.ar_part_ofs, d.ar_flag_ofs, d.ar_done_ofs, d.ar_y_ofs = ar["part_ofs"], ar["flag_ofs"], ar["done_ofs"], ar["y_ofs"]
         d.ar_epoch, d.ar_world, d.ar_me = ar["epoch_ptr"], ar["world"], ar["me"]
         d.wait_deadline_ms = ar.get("deadline_ms", 2000)
+        d.ar_oneshot, d.ar_half_bytes = int(ar.get("oneshot", 0)), int(ar.get("half_bytes", 0))
     rc = lib.plow_gemm(C.byref(d), native.stream_ptr())
     if rc != 0:
         raise native.NativeLibraryError(f"plow_gemm failed with code {rc} (bn={bn} swap={swap} dual={dual} fp8={fp8})")

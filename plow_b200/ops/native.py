@@ -34,6 +34,7 @@ class GemmDesc(C.Structure):
         ("ar_peer", C.c_void_p * 8), ("ar_part_ofs", C.c_uint64), ("ar_flag_ofs", C.c_uint64), ("ar_done_ofs", C.c_uint64),
         ("ar_y_ofs", C.c_uint64), ("ar_epoch", C.c_void_p), ("ar_world", C.c_int32), ("ar_me", C.c_int32),
         ("wait_ctr", C.c_void_p), ("wait_epoch", C.c_void_p), ("wait_mult", C.c_int32), ("wait_deadline_ms", C.c_int32),
+        ("ar_oneshot", C.c_int32), ("ar_pad", C.c_int32), ("ar_half_bytes", C.c_uint64),
     ]
 
 

@@ -25,8 +25,9 @@ def _align(x, a=256):
 
 class TpComm:
     def __init__(self, rank: int, world: int, max_rows: int = 128, max_n: int = 16384, impl: str = "fused", deadline_ms: int = 2000,
-                 max_k: int = 16384):
+                 max_k: int = 16384, oneshot_bytes: int = 4 << 20):
         self.rank, self.world, self.impl = rank, world, impl
+        self.oneshot_bytes = oneshot_bytes     # messages up to this size use the one-shot form (decode), larger ones two-shot
         self.dev = torch.device("cuda", torch.cuda.current_device())
         self.max_rows, self.max_n, self.deadline_ms = max_rows, max_n, deadline_ms
         if impl != "fused":
@@ -34,7 +35,8 @@ class TpComm:
         import torch.distributed._symmetric_memory as symm
         tiles = (max_n + 127) // 128
         lay, off = {}, 0
-        for name, nbytes in (("part", tiles * 128 * 128 * 2), ("flag", tiles * 8 * 4), ("done", 128), ("y", max_rows * max_n * 2),
+        self.half_bytes = _align(tiles * world * 128 * 64 * 2)        # one-shot slots: [tile][source rank][128][<=64 tokens] bf16
+        for name, nbytes in (("part", max(tiles * 128 * 128 * 2, 2 * self.half_bytes)), ("flag", tiles * 8 * 4), ("done", 128), ("y", max_rows * max_n * 2),
                              ("ag_ctr", 128), ("xg0", max_rows * max_k * 2), ("xg1", max_rows * max_k * 2)):
             lay[name] = off
             off = _align(off + nbytes)
@@ -44,7 +46,7 @@ class TpComm:
         self.hdl = symm.rendezvous(self.buf, dist.group.WORLD)
         torch.cuda.synchronize()
         dist.barrier()
-        self.epoch = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.epoch = torch.zeros(4, dtype=torch.int32, device=self.dev)      # [launch counter, arrivals seen, CTAs through, -]
         self.ag_epoch = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.ag_done = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self._ag_calls = 0
@@ -52,22 +54,33 @@ class TpComm:
         import ctypes
         self._peer_arr = (ctypes.c_void_p * 8)(*(self.peers + [None] * (8 - len(self.peers))))
 
-    def gemm_allreduce(self, x, w, n_out, sx=None, sw=None, residual=None):
+    def gemm_allreduce(self, x, w, n_out, sx=None, sw=None, residual=None, out=None):
         """y = all_reduce_sum(x_shard @ w_shard.T) (+ residual).  x [M, K/tp], w [N, K/tp]; M <= 128.
         Returns a [M, N] bf16 view of the symmetric output area (valid until the next call)."""
         M = x.shape[0]
         bn = gemm_ops._pick_bn_swap(M, sx is not None, False) if M <= 128 else 128
         if self.impl == "fused" and M <= 64 and bn <= 64 and M <= self.max_rows and n_out <= self.max_n and n_out % 8 == 0:
-            y = self.buf[self.lay["y"]:self.lay["y"] + M * n_out * 2].view(BF16).view(M, n_out)
+            oneshot = (self.world - 1) * M * n_out * 2 <= self.oneshot_bytes
             ar = dict(peers=self.peers, part_ofs=self.lay["part"], flag_ofs=self.lay["flag"], done_ofs=self.lay["done"],
                       y_ofs=self.lay["y"], epoch_ptr=self.epoch.data_ptr(), world=self.world, me=self.rank,
-                      deadline_ms=self.deadline_ms)
+                      deadline_ms=self.deadline_ms, oneshot=int(oneshot), half_bytes=self.half_bytes)
+            if oneshot:
+                # every rank reduces locally, so the result can land in any tensor of this rank
+                y = out if out is not None else torch.empty(M, n_out, dtype=BF16, device=self.dev)
+            else:
+                y = self.buf[self.lay["y"]:self.lay["y"] + M * n_out * 2].view(BF16).view(M, n_out)
             gemm_ops.gemm(x, w, sx=sx, sw=sw, n_out=n_out, swap=True, bn=bn, out=y, residual=residual, ar=ar)
+            if out is not None and not oneshot:
+                out.copy_(y)
+                return out
             return y
         y = gemm_ops.gemm(x, w, sx=sx, sw=sw, n_out=n_out, swap=M <= 128, bn=bn if M <= 128 else None, splits=1)
         dist.all_reduce(y)
         if residual is not None:
             y = y + residual
+        if out is not None:
+            out.copy_(y)
+            return out
         return y
 
     def allgather_gemm(self, x_band, w, n_out, dual=False):

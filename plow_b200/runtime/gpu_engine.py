@@ -439,12 +439,11 @@ class GpuEngine(EngineBase):
         if flags & pk.GEMM_FP8_BLOCK:
             wq, sw = self.static_q[ins.t[2]]
             xq, sx = self._quant_of(st, ins.t[1], co, K, x)
-            r = tp.gemm_allreduce(xq[:y.shape[0]], wq, N, sx=sx, sw=sw)
+            tp.gemm_allreduce(xq[:y.shape[0]], wq, N, sx=sx, sw=sw, out=y)
         else:
             w = self.static[ins.t[2]]
             xin = x if co == 0 and x.shape[1] == K else x[:, co:co + K]
-            r = tp.gemm_allreduce(xin, w if w.dtype == BF16 else self._bf16_weight(ins.t[2]), N)
-        y.copy_(r)
+            tp.gemm_allreduce(xin, w if w.dtype == BF16 else self._bf16_weight(ins.t[2]), N, out=y)
 
     def _ext_xreduce(self, st, ins):
         out, x = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])

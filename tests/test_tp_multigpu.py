@@ -19,7 +19,8 @@ torch.cuda.set_device(rank)
 dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
 from plow_b200.ops import native, quant
 from plow_b200.parallel.tp import TpComm
-fused = TpComm(rank, world, impl="fused")
+fused = TpComm(rank, world, impl="fused")                       # one-shot form for these message sizes
+fused2 = TpComm(rank, world, impl="fused", oneshot_bytes=0)      # two-shot form (owner reduces, stores to every rank)
 nccl = TpComm(rank, world, impl="nccl")
 out = {}
 for (M, N, K, fp8) in [(64, 7168, 8192, True), (17, 1024, 2048, False), (64, 4096, 7168, False)]:
@@ -34,14 +35,15 @@ for (M, N, K, fp8) in [(64, 7168, 8192, True), (17, 1024, 2048, False), (64, 409
         xr, wr = xq.float(), wq.float()
     part = (xr @ wr.t()).bfloat16().float()
     ref = part.clone(); dist.all_reduce(ref)
-    for call in range(2):
-        y = fused.gemm_allreduce(xq, wq, N, sx=sx, sw=sw).clone()
-        torch.cuda.synchronize(); native.check_status()
-        err = ((y.float() - ref).norm() / ref.norm()).item()
-        gathered = [torch.empty_like(y) for _ in range(world)]
-        dist.all_gather(gathered, y)
-        same = all(torch.equal(gathered[0], t) for t in gathered)
-        out[f"{M}x{N}x{K}{'fp8' if fp8 else 'bf16'}#{call}"] = dict(err=err, identical=same)
+    for form, comm in (("oneshot", fused), ("twoshot", fused2)):
+        for call in range(3):
+            y = comm.gemm_allreduce(xq, wq, N, sx=sx, sw=sw).clone()
+            torch.cuda.synchronize(); native.check_status()
+            err = ((y.float() - ref).norm() / ref.norm()).item()
+            gathered = [torch.empty_like(y) for _ in range(world)]
+            dist.all_gather(gathered, y)
+            same = all(torch.equal(gathered[0], t) for t in gathered)
+            out[f"{M}x{N}x{K}{'fp8' if fp8 else 'bf16'}/{form}#{call}"] = dict(err=err, identical=same)
     yn = nccl.gemm_allreduce(xq, wq, N, sx=sx, sw=sw)
     out[f"{M}x{N}x{K}nccl"] = dict(err=((yn.float() - ref).norm() / ref.norm()).item(), identical=True)
     def timeit(f, n=20):
@@ -54,6 +56,7 @@ for (M, N, K, fp8) in [(64, 7168, 8192, True), (17, 1024, 2048, False), (64, 409
         t = torch.tensor([s.elapsed_time(e) * 1000 / n], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t)
     out[f"{M}x{N}x{K}us"] = dict(fused=timeit(lambda: fused.gemm_allreduce(xq, wq, N, sx=sx, sw=sw)),
+                                 twoshot=timeit(lambda: fused2.gemm_allreduce(xq, wq, N, sx=sx, sw=sw)),
                                  nccl=timeit(lambda: nccl.gemm_allreduce(xq, wq, N, sx=sx, sw=sw)))
 if rank == 0: print(json.dumps(out))
 dist.destroy_process_group()
