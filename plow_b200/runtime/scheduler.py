@@ -99,6 +99,7 @@ class SchedConfig:
     tbt_target_ms: float = 0.0        # 0 = off; otherwise prefill chunks are sized to this budget
     aging_ticks: int = 32             # after this many waits a long prefill jumps the SRPF order
     reserve_tokens: int = PAGE        # KV head-room required per live sequence before seating more
+    ride: bool = True                 # decode rows ride the prefill launch (mixed step) instead of waiting a tick
 
 
 class Metrics:
@@ -238,7 +239,8 @@ class ModelMux:
         run_prefill = bool(prefilling) and (not decoding or not self._last_was_prefill or self.cfg.objective == "throughput")
         t0 = time.perf_counter()
         if run_prefill:
-            self._prefill_tick(prefilling)
+            riders = decoding if (self.cfg.ride and self.cfg.objective != "throughput") else []
+            self._prefill_tick(prefilling, riders)
             self._last_was_prefill = True
         elif decoding:
             self._decode_tick(decoding)
@@ -295,7 +297,10 @@ class ModelMux:
             b = max(PAGE, min(b, int(self.cfg.tbt_target_ms * getattr(self, "_rows_per_ms", 64.0))))
         return b
 
-    def _prefill_tick(self, reqs: list) -> None:
+    def _prefill_tick(self, reqs: list, riders: list = ()) -> None:
+        """One prefill launch.  ``riders`` are decoding requests whose next row is appended to the same token batch
+        (a mixed step: the unified row format makes a decode row just another row), so running prompts do not
+        stall token generation for a whole tick (reference: crates/plowrt/src/sched/ride.rs, mixed_step.h)."""
         eng = self.engine
         budget = self._prefill_budget()
         for r in reqs:
@@ -328,7 +333,23 @@ class ModelMux:
             r.waited_ticks = 0
         if not spans:
             return
-        want_logits = any(not s[0].params.greedy for s in spans if s[3])
+        # riders: one row each, as long as sample slots and rows remain
+        rode = []
+        max_samples = eng.buckets.get("max_seqs", 64)
+        for r in sorted(riders, key=lambda r: r.slot):
+            if len(sample_rows) + 1 > max_samples - 1 or len(ids) + 1 > eng.max_rows(False):
+                break
+            n_ctx = len(r.prompt) + len(r.generated)
+            try:
+                eng.reserve(r.slot, n_ctx + 1)
+            except OutOfPages:
+                continue
+            ids.append(r.generated[-1])
+            pos.append(n_ctx - 1)
+            seq.append(r.slot)
+            sample_rows.append(len(ids) - 1)
+            rode.append(r)
+        want_logits = any(not s[0].params.greedy for s in spans if s[3]) or any(not r.params.greedy for r in rode)
         if not sample_rows:
             sample_rows_arr = np.array([len(ids) - 1], dtype=np.int32)   # engines always sample >= 1 row
         else:
@@ -349,6 +370,12 @@ class ModelMux:
                 lg = res.logits[k] if res.logits is not None else None
                 self._produce(r, int(res.ids[k]), lg)
                 k += 1
+        for r in rode:
+            if r.slot in self.live and self.live[r.slot] is r:
+                eng.commit(r.slot, [r.generated[-1]])
+                self._produce(r, int(res.ids[k]), res.logits[k] if res.logits is not None else None)
+                self.metrics.inc("rider_rows")
+            k += 1
 
     # ---- decode --------------------------------------------------------------------------------
     def _decode_tick(self, reqs: list) -> None:

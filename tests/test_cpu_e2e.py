@@ -123,3 +123,38 @@ def test_stop_string_and_sampling_seed(tiny_assets):
     assert reason == "stop" and ids == a[0][:2] and usage["completion_tokens"] == 2
     mux.stop()
     eng.close()
+
+
+def test_decode_rows_ride_prefill_launches(tiny_assets):
+    """A long prompt is prefilled in small chunks while another request is decoding: with riding on, the decoder's rows
+    are appended to the prefill launches (mixed steps) and both requests produce exactly the tokens they produce
+    without riding."""
+    def run(ride):
+        eng = CpuEngine(tiny_assets / "assets", max_slots=4, max_ctx=512, prefix_cache=False)
+        mux = ModelMux(eng, ByteTokenizer(), SchedConfig(token_budget=64, ride=ride), eos_ids=[])
+        rng = np.random.default_rng(9)
+        a = mux.submit(rng.integers(0, 32000, 20).tolist(), GenParams(max_tokens=24))
+        for _ in range(4):
+            mux.tick()                                   # request a is decoding by now
+        b = mux.submit(rng.integers(0, 32000, 300).tolist(), GenParams(max_tokens=4))
+        for _ in range(200):
+            if not mux.tick() and not mux.waiting and not mux.live:
+                break
+        outs = []
+        for r in (a, b):
+            ids = []
+            while True:
+                ch = r.out.get(timeout=10)
+                if ch.kind == "token":
+                    ids.append(ch.token_id)
+                else:
+                    assert ch.kind == "done", ch.error
+                    break
+            outs.append(ids)
+        riders = mux.metrics.snapshot()["counters"].get("rider_rows", 0)
+        eng.close()
+        return outs, riders
+    plain, r0 = run(False)
+    rode, r1 = run(True)
+    assert plain == rode
+    assert r0 == 0 and r1 >= 3
