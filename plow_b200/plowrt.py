@@ -139,6 +139,35 @@ def cmd_devices(_args) -> int:
     return 0
 
 
+def cmd_dist(args) -> int:
+    """Asset distribution subcommands (bundles, local store with generations, directory registry)."""
+    from .dist import store as d
+    st = d.Store(args.store, trusted_keys=args.trust or None, require_signature=bool(args.trust))
+    c = args.cmd
+    if c == "keygen":
+        print(json.dumps(dict(key=args.path, public_key=d.keygen(args.path))))
+    elif c == "pack":
+        print(d.pack(args.assets, args.out, args.name, key_path=args.key, with_weights=args.with_weights))
+    elif c == "load":
+        print(st.load(args.bundle))
+    elif c == "ls":
+        print(json.dumps(st.ls(), indent=1))
+    elif c == "rollback":
+        print(st.rollback(args.name))
+    elif c == "rm":
+        st.rm(args.name, args.generation)
+    elif c == "gc":
+        print(json.dumps(st.gc(args.keep)))
+    elif c in ("publish", "push"):
+        print(json.dumps(d.Registry(args.registry).publish(args.bundle)))
+    elif c == "pull":
+        pkg = d.Registry(args.registry).pull(args.name, args.out)
+        print(st.load(pkg) if args.load else pkg)
+    elif c == "catalog":
+        print(json.dumps(d.Registry(args.registry).catalog(), indent=1))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="plowrt")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -176,6 +205,26 @@ def main(argv=None) -> int:
     sub.add_parser("devices").set_defaults(fn=cmd_devices)
     k = sub.add_parser("knob-scope")
     k.set_defaults(fn=lambda a: print(json.dumps(cfgmod.knob_table("runtime"), indent=1)) or 0)
+    def dist_parser(name, *pos, **opts):
+        p = sub.add_parser(name)
+        for a in pos:
+            p.add_argument(a)
+        for o, kw in opts.items():
+            p.add_argument("--" + o.replace("_", "-"), **kw)
+        p.add_argument("--store")
+        p.add_argument("--trust", action="append", help="hex ed25519 public key; when given, unsigned or foreign bundles are refused")
+        p.set_defaults(fn=cmd_dist)
+    dist_parser("keygen", "path")
+    dist_parser("pack", "assets", name=dict(required=True), out=dict(default="."), key=dict(), with_weights=dict(action="store_true"))
+    dist_parser("load", "bundle")
+    dist_parser("ls")
+    dist_parser("rollback", "name")
+    dist_parser("rm", "name", generation=dict())
+    dist_parser("gc", keep=dict(type=int, default=2))
+    dist_parser("publish", "bundle", registry=dict(required=True))
+    dist_parser("push", "bundle", registry=dict(required=True))
+    dist_parser("pull", "name", registry=dict(required=True), out=dict(default="."), load=dict(action="store_true"))
+    dist_parser("catalog", registry=dict(required=True))
     args = ap.parse_args(argv)
     return args.fn(args)
 
