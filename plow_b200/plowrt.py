@@ -205,8 +205,8 @@ def main(argv=None) -> int:
     sub.add_parser("devices").set_defaults(fn=cmd_devices)
     k = sub.add_parser("knob-scope")
     k.set_defaults(fn=lambda a: print(json.dumps(cfgmod.knob_table("runtime"), indent=1)) or 0)
-    def dist_parser(name, *pos, **opts):
-        p = sub.add_parser(name)
+    def dist_parser(cmd_name, *pos, **opts):
+        p = sub.add_parser(cmd_name)
         for a in pos:
             p.add_argument(a)
         for o, kw in opts.items():
