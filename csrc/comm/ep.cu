@@ -188,27 +188,46 @@ __global__ void ep_combine_kernel(EpArgs a, __nv_bfloat16* out, const __nv_bfloa
   __syncthreads();
   if (fail) { if (threadIdx.x == 0) atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); return; }
   if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 8);
+  // Slot metadata first, then all of a thread's remote loads at once: the eight pulls of a 16-byte unit are
+  // independent, so they cost one NVLink round trip instead of eight.  One unit per thread (grid.y covers H).
+  constexpr int kMaxK = 16;
+  __shared__ int s_dest[kMaxK];
+  __shared__ float s_gate[kMaxK];
   const int t = blockIdx.x;
-  for (int i = threadIdx.x * 8; i < a.H; i += blockDim.x * 8) {
+  if (threadIdx.x < top_k && threadIdx.x < kMaxK) {
+    s_dest[threadIdx.x] = pair_dest[t * top_k + threadIdx.x];
+    s_gate[threadIdx.x] = __int_as_float(table[t * top_k + threadIdx.x].y);
+  }
+  __syncthreads();
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (i < a.H) {
+    uint4 v[kMaxK];
+#pragma unroll
+    for (int s = 0; s < kMaxK; ++s) {
+      if (s < top_k) {
+        const int pd = s_dest[s];
+        const __nv_bfloat16* y = reinterpret_cast<const __nv_bfloat16*>(a.peer[pd >> 24] + a.L.y);
+        v[s] = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(pd & 0xffffff) * a.H + i);
+      }
+    }
     float acc[8];
     if (shared) {
-      const uint4 v = *reinterpret_cast<const uint4*>(shared + static_cast<size_t>(t) * a.H + i);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+      const uint4 sv = *reinterpret_cast<const uint4*>(shared + static_cast<size_t>(t) * a.H + i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&sv);
 #pragma unroll
       for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); acc[2 * j] = f.x; acc[2 * j + 1] = f.y; }
     } else {
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     }
-    for (int s = 0; s < top_k; ++s) {
-      const int pd = pair_dest[t * top_k + s];
-      const int d = pd >> 24, row = pd & 0xffffff;
-      const float g = __int_as_float(table[t * top_k + s].y);
-      const __nv_bfloat16* y = reinterpret_cast<const __nv_bfloat16*>(a.peer[d] + a.L.y);
-      const uint4 v = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(row) * a.H + i);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); acc[2 * j] += g * f.x; acc[2 * j + 1] += g * f.y; }
+    for (int s = 0; s < kMaxK; ++s) {          // fixed slot order
+      if (s < top_k) {
+        const float g = s_gate[s];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[s]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); acc[2 * j] += g * f.x; acc[2 * j + 1] += g * f.y; }
+      }
     }
     uint4 o;
     __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
@@ -254,7 +273,8 @@ int plow_ep_y_ready(const void* args, void* st) {
 int plow_ep_combine(const void* args, void* out, const void* shared, const void* table, const int* pair_dest, int T, int top_k,
                     void* st) {
   const EpArgs& a = *static_cast<const EpArgs*>(args);
-  ep_combine_kernel<<<T, 256, 0, reinterpret_cast<cudaStream_t>(st)>>>(a, static_cast<__nv_bfloat16*>(out),
+  if (top_k > 16 || a.H % 8) return -1;
+  ep_combine_kernel<<<dim3(T, (a.H / 8 + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(st)>>>(a, static_cast<__nv_bfloat16*>(out),
                                                                     static_cast<const __nv_bfloat16*>(shared),
                                                                     static_cast<const int2*>(table), pair_dest, top_k);
   return ok();

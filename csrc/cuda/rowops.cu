@@ -393,34 +393,50 @@ __global__ void moe_gather_kernel(uint8_t* xs, float* sxs, int ld_sxs, const uin
 // out[t] = shared[t] (optional) + sum_j gate[t][j] * y[row_of_pair[t*k+j]]   (fixed slot order, f32)
 __global__ void moe_combine_kernel(__nv_bfloat16* out, const __nv_bfloat16* y, const __nv_bfloat16* shared,
                                    const int2* table, const int* row_of_pair, int top_k, int H) {
+  // slot metadata first, then all of a thread's loads at once (one 16-byte unit per thread, grid.y covers H)
+  constexpr int kMaxK = 16;
+  __shared__ int s_row[kMaxK];
+  __shared__ float s_gate[kMaxK];
   const int t = blockIdx.x;
-  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
-    float acc[8];
-    if (shared) {
-      uint4 v = *reinterpret_cast<const uint4*>(shared + static_cast<size_t>(t) * H + i);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+  if (threadIdx.x < top_k && threadIdx.x < kMaxK) {
+    s_row[threadIdx.x] = row_of_pair[t * top_k + threadIdx.x];
+    s_gate[threadIdx.x] = __int_as_float(table[t * top_k + threadIdx.x].y);
+  }
+  __syncthreads();
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (i >= H) return;
+  uint4 v[kMaxK];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h[j]); acc[2 * j] = f.x; acc[2 * j + 1] = f.y; }
-    } else {
+  for (int s = 0; s < kMaxK; ++s) {
+    v[s] = make_uint4(0u, 0u, 0u, 0u);
+    if (s < top_k && s_row[s] >= 0) v[s] = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(s_row[s]) * H + i);
+  }
+  float acc[8];
+  if (shared) {
+    const uint4 sv = *reinterpret_cast<const uint4*>(shared + static_cast<size_t>(t) * H + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&sv);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    }
-    for (int s = 0; s < top_k; ++s) {
-      const int row = row_of_pair[t * top_k + s];
-      if (row < 0) continue;
-      const float g = __int_as_float(table[t * top_k + s].y);
-      uint4 v = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(row) * H + i);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h[j]); acc[2 * j] = f.x; acc[2 * j + 1] = f.y; }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  }
+#pragma unroll
+  for (int s = 0; s < kMaxK; ++s) {            // fixed slot order
+    if (s < top_k && s_row[s] >= 0) {
+      const float g = s_gate[s];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[s]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h[j]); acc[2 * j] += g * f.x; acc[2 * j + 1] += g * f.y; }
     }
-    uint4 o;
-    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-    *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + i) = o;
   }
+  uint4 o;
+  __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+  *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + i) = o;
 }
+
 
 // ---- argmax / gather --------------------------------------------------------------------------
 __global__ void argmax_kernel(int* out, const float* logits, int V) {
@@ -546,8 +562,8 @@ int plow_moe_gather(void* xs, float* sxs, int ld_sxs, const void* xq, const floa
 
 int plow_moe_combine(void* out, const void* y, const void* shared, const void* table, const int* row_of_pair, int T, int top_k,
                      int H, void* st) {
-  if (H % 8) return -1;
-  moe_combine_kernel<<<T, 256, 0, S(st)>>>((bf16*)out, (const bf16*)y, (const bf16*)shared, (const int2*)table, row_of_pair, top_k, H);
+  if (H % 8 || top_k > 16) return -1;
+  moe_combine_kernel<<<dim3(T, (H / 8 + 255) / 256), 256, 0, S(st)>>>((bf16*)out, (const bf16*)y, (const bf16*)shared, (const int2*)table, row_of_pair, top_k, H);
   return ok();
 }
 
