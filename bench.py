@@ -44,11 +44,11 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.mark_at = index, [], None, 0
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
                                           "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
@@ -59,10 +59,18 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
+    def mark(self):
+        """Start of the timed region: the sampler is started earlier (nvidia-smi takes a moment to come up), only the
+        samples taken from here on are reported."""
+        self.mark_at = len(self.rows)
+        return self
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
+        rows = self.rows[self.mark_at:] or self.rows[-1:]      # a very short region: the sample that straddles it
+        self.rows = rows
         sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
         mx = max([int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()] or [0])
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -182,6 +190,7 @@ def main() -> int:
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local).start()        # started before the warm-up; mark() opens the reported window
     for k in range(W):
         one_step(k)
     n0 = native.LAUNCHES["n"]
@@ -230,8 +239,8 @@ def main() -> int:
         comm.timing = None
         if rank == 0:
             print("EP phase us (rank 0):", json.dumps(rep), file=sys.stderr)
-    sampler = ClockSampler(local).start()
     barrier()
+    sampler.mark()
     t0 = time.perf_counter()
     dev_ms = []
     for k in range(args.steps):
