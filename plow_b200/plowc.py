@@ -96,6 +96,11 @@ def main(argv=None) -> int:
     v = sub.add_parser("viz", help="write an HTML view of the fused graph")
     v.add_argument("hf_dir")
     v.add_argument("--out", default="graph.html")
+    sp = sub.add_parser("stage-plan", help="cut the layers into pipeline stages of balanced modelled time")
+    sp.add_argument("hf_dir")
+    sp.add_argument("--stages", type=int, default=2)
+    sp.add_argument("--batch", type=int, default=64)
+    sp.add_argument("--ctx", type=int, default=2048)
     tn = sub.add_parser("tune", help="measure decode GEMM tiles on this GPU and write the tuning store")
     tn.add_argument("hf_dir")
     tn.add_argument("--rows", type=lambda s: [int(x) for x in s.split(",")], default=[8, 64])
@@ -108,6 +113,12 @@ def main(argv=None) -> int:
         g = graph.build_graph(spec)
         rewrite.fuse(g)
         Path(args.out).write_text(viz.to_html(g))
+        return 0
+    if args.cmd == "stage-plan":
+        from .compiler import stage_plan
+        spec = load_spec(args.hf_dir)
+        costs = stage_plan.layer_costs_us(spec, hwspec.lookup(args.gpu), args.batch, args.ctx)
+        print(json.dumps(stage_plan.plan_stages(costs, args.stages), indent=1))
         return 0
     if args.cmd == "tune":
         from .compiler import tunedb
