@@ -19,6 +19,7 @@ GemmArgs to_args(const PlowGemmDesc& d) {
   a.ar_part_ofs = d.ar_part_ofs; a.ar_flag_ofs = d.ar_flag_ofs; a.ar_done_ofs = d.ar_done_ofs; a.ar_y_ofs = d.ar_y_ofs;
   a.ar_epoch = static_cast<uint32_t*>(d.ar_epoch); a.ar_world = d.ar_world; a.ar_me = d.ar_me;
   a.ar_oneshot = d.ar_oneshot; a.ar_half_bytes = d.ar_half_bytes;
+  a.ar_mc = static_cast<uint8_t*>(d.ar_mc); a.ar_tdone_ofs = d.ar_tdone_ofs;
   a.wait_ctr = static_cast<const uint32_t*>(d.wait_ctr); a.wait_epoch = static_cast<const uint32_t*>(d.wait_epoch);
   a.wait_mult = static_cast<uint32_t>(d.wait_mult); a.wait_deadline_ms = static_cast<uint32_t>(d.wait_deadline_ms);
   return a;
@@ -43,7 +44,8 @@ extern "C" int plow_gemm(const PlowGemmDesc* d, void* stream) {
   if (d->yq && !d->syq) return -7;
   if (d->yq && !d->swap && d->bn != 128) return -7;
   if (d->ar_world > 1 && (!d->swap || d->dual || d->E || d->M > d->bn || d->splits > 1 || d->yq || d->out_f32 || !d->ar_epoch || (d->N % 8) || (d->ldy % 8))) return -8;
-  if (d->ar_world > 1 && d->ar_oneshot &&
+  if (d->ar_world > 1 && d->ar_oneshot == 2 && !d->ar_mc) return -8;
+  if (d->ar_world > 1 && d->ar_oneshot == 1 &&
       static_cast<uint64_t>((d->N + 127) / 128) * d->ar_world * 128 * d->bn * 2 > d->ar_half_bytes) return -8;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return d->dtype == 1 ? plow::gemm_dispatch_fp8(*d, s) : plow::gemm_dispatch_bf16(*d, s);

@@ -44,6 +44,8 @@ typedef struct PlowGemmDesc {
   int32_t ar_oneshot;     // fused all-reduce form: 0 = two-shot (owner reduces, stores to every rank), 1 = one-shot (push + local reduce)
   int32_t ar_pad;
   uint64_t ar_half_bytes; // one-shot: bytes of one parity half of the partial area; ar_epoch points at 4 device words
+  void* ar_mc;            // ar_oneshot == 2: multicast (NVSwitch) mapping of the symmetric region
+  uint64_t ar_tdone_ofs;  // ar_oneshot == 2: u32 [tiles] per-tile epoch words inside the region
 } PlowGemmDesc;
 
 // Launches on `stream` (a cudaStream_t).  Returns 0, or a host-side error code (<0 bad

@@ -57,6 +57,9 @@ struct GemmArgs {
   uint32_t* ar_epoch;     // device words: [0] launch counter, [1] arrivals on `done` seen so far (two-shot), [2] CTAs through (one-shot)
   int ar_world, ar_me;
   int ar_oneshot;          // 1: every rank pushes its partial to all ranks and reduces locally (decode sizes)
+                           // 2: two-shot through NVSwitch multicast: multimem.ld_reduce by the tile's owner, multimem.st of the result
+  uint8_t* ar_mc;          // multicast mapping of the symmetric region (mode 2)
+  unsigned long long ar_tdone_ofs;   // mode 2: u32 [tiles] epoch word per tile, written to every rank when the tile has landed
   unsigned long long ar_half_bytes;   // one-shot: size of one parity half of the partial area
   long long* trace;       // optional clock64() phase stamps of CTA 0 (debug aid), NULL when off
   const uint32_t* wait_ctr;
@@ -565,7 +568,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
               __nv_bfloat162 h2 = __floats2bfloat162_rn(r[2 * j], r[2 * j + 1]);
               pk[j] = *reinterpret_cast<uint32_t*>(&h2);
             }
-            if (a.ar_oneshot) {
+            if (a.ar_oneshot == 1) {
               // one-shot: the partial goes straight into every rank's [parity][tile][source rank][feature][token] slot
               const size_t po = a.ar_part_ofs + (ar_ep & 1) * a.ar_half_bytes +
                                 (static_cast<size_t>(((t.feat0 >> 7) * a.ar_world + a.ar_me) * 128 + li) * BN + c) * 2;
@@ -635,7 +638,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           }
           ++xchg_it;
           const int tile = t.feat0 >> 7;
-          if (a.ar_oneshot) {
+          if (a.ar_oneshot == 1) {
             // tell every rank, then reduce this tile from the local slots as soon as every rank's flag is here
             if (li < a.ar_world)
               st_release_sys(reinterpret_cast<uint32_t*>(a.ar_peer[li] + a.ar_flag_ofs) + tile * 8 + a.ar_me, ar_ep);
@@ -682,7 +685,10 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
               }
             }
           } else if (li == 0) {
-            st_release_sys(reinterpret_cast<uint32_t*>(a.ar_peer[tile % a.ar_world] + a.ar_flag_ofs) + tile * 8 + a.ar_me, ar_ep);
+            if (a.ar_oneshot == 2)   // one multicast store puts this rank's flag of the tile on every rank
+              multimem_st_u32(a.ar_mc + a.ar_flag_ofs + (static_cast<size_t>(tile) * 8 + a.ar_me) * 4, ar_ep);
+            else
+              st_release_sys(reinterpret_cast<uint32_t*>(a.ar_peer[tile % a.ar_world] + a.ar_flag_ofs) + tile * 8 + a.ar_me, ar_ep);
           }
         }
         if (ws_tile) {
@@ -788,14 +794,15 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
     // stores the result into every rank's output; then one arrival per (tile, rank).  Reference
     // numerics: runtime/nvidia/op_collective.cuh:18-20.  Plain peer loads/stores, bounded waits.
     if constexpr (SWAP && !DUAL) {
-      if (a.ar_world > 1 && ok && a.ar_oneshot) {
+      if (a.ar_world > 1 && ok && a.ar_oneshot == 1) {
         // the launch counter moves on once every CTA of this launch is through (ar_epoch[2] counts them)
         if (li == 0) {
           __threadfence();
           if (atomicAdd(&a.ar_epoch[2], 1u) == gridDim.x - 1) { a.ar_epoch[2] = 0; __threadfence(); a.ar_epoch[0] = ar_ep; }
         }
       }
-      if (a.ar_world > 1 && ok && !a.ar_oneshot) {
+      if (a.ar_world > 1 && ok && a.ar_oneshot != 1) {
+        const bool mc = a.ar_oneshot == 2;
         const int W = a.ar_world;
         const int n_tiles = (a.N + 127) / 128;
         const unsigned long long dl = static_cast<unsigned long long>(a.wait_deadline_ms ? a.wait_deadline_ms : 2000) * 1000000ull;
@@ -821,10 +828,16 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             float acc16[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) acc16[j] = 0.f;
-            for (int r = 0; r < W; ++r) {
-              const uint4* pp = reinterpret_cast<const uint4*>(a.ar_peer[r] + a.ar_part_ofs +
-                                                               (static_cast<size_t>(tile * 128 + li) * BN + c) * 2);
-              const uint4 v0 = pp[0], v1 = pp[1];
+            for (int r = 0; r < (mc ? 1 : W); ++r) {
+              const size_t po = a.ar_part_ofs + (static_cast<size_t>(tile * 128 + li) * BN + c) * 2;
+              uint4 v0, v1;
+              if (mc) {      // the switch sums the ranks' copies (f32 accumulation, one rounding)
+                v0 = multimem_ld_reduce_bf16x8(a.ar_mc + po);
+                v1 = multimem_ld_reduce_bf16x8(a.ar_mc + po + 16);
+              } else {
+                const uint4* pp = reinterpret_cast<const uint4*>(a.ar_peer[r] + po);
+                v0 = pp[0]; v1 = pp[1];
+              }
               const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&v0);
               const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&v1);
 #pragma unroll
@@ -853,7 +866,8 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
               if (c + row < a.M && tile * 128 + col + 8 <= a.N) {
                 const uint4 v = *reinterpret_cast<const uint4*>(tsm + row * 128 + col);
                 const size_t o = static_cast<size_t>(c + row) * a.ldy + tile * 128 + col;
-                for (int p = 0; p < W; ++p) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.ar_peer[p] + a.ar_y_ofs) + o) = v;
+                if (mc) multimem_st_bf16x8(a.ar_mc + a.ar_y_ofs + o * 2, v);
+                else for (int p = 0; p < W; ++p) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.ar_peer[p] + a.ar_y_ofs) + o) = v;
               }
             }
             __syncwarp();
@@ -867,10 +881,26 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
           if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) { ok = false; break; }
           ++xchg_it;
-          if (li < W) red_add_release_sys(reinterpret_cast<uint32_t*>(a.ar_peer[li] + a.ar_done_ofs), 1u);
+          if (mc) { if (li == 0) multimem_st_u32(a.ar_mc + a.ar_tdone_ofs + static_cast<size_t>(tile) * 4, ar_ep); }
+          else if (li < W) red_add_release_sys(reinterpret_cast<uint32_t*>(a.ar_peer[li] + a.ar_done_ofs), 1u);
         }
         // the kernel ends on this rank only when every tile of this launch has landed here
-        if (blockIdx.x == 0 && li == 0) {
+        if (mc && blockIdx.x == 0) {
+          // every tile's epoch word must have landed here (written by the tile's owner through the switch)
+          const uint32_t* td = reinterpret_cast<const uint32_t*>(a.ar_peer[a.ar_me] + a.ar_tdone_ofs);
+          const unsigned long long t0 = globaltimer_ns();
+          for (int tile = li; tile < n_tiles; tile += 128) {
+            while (ld_acquire_sys(td + tile) < ar_ep) {
+              if (globaltimer_ns() - t0 > dl) { atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); break; }
+              __nanosleep(128);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
+          if (mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) { ++xchg_it; if (li == 0) *a.ar_epoch = ar_ep; }
+        } else if (mc) {
+          // other CTAs have nothing left to do
+        } else if (blockIdx.x == 0 && li == 0) {
           const uint32_t* d = reinterpret_cast<const uint32_t*>(a.ar_peer[a.ar_me] + a.ar_done_ofs);
           const unsigned long long t0 = globaltimer_ns();
           // ar_epoch[1] = arrivals seen by the launches before this one (shapes, hence tile counts, differ between

@@ -152,6 +152,7 @@ def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=N
         d.ar_epoch, d.ar_world, d.ar_me = ar["epoch_ptr"], ar["world"], ar["me"]
         d.wait_deadline_ms = ar.get("deadline_ms", 2000)
         d.ar_oneshot, d.ar_half_bytes = int(ar.get("oneshot", 0)), int(ar.get("half_bytes", 0))
+        d.ar_mc, d.ar_tdone_ofs = ar.get("mc_ptr") or None, int(ar.get("tdone_ofs", 0))
     rc = lib.plow_gemm(C.byref(d), native.stream_ptr())
     if rc != 0:
         raise native.NativeLibraryError(f"plow_gemm failed with code {rc} (bn={bn} swap={swap} dual={dual} fp8={fp8})")

@@ -35,6 +35,7 @@ class GemmDesc(C.Structure):
         ("ar_y_ofs", C.c_uint64), ("ar_epoch", C.c_void_p), ("ar_world", C.c_int32), ("ar_me", C.c_int32),
         ("wait_ctr", C.c_void_p), ("wait_epoch", C.c_void_p), ("wait_mult", C.c_int32), ("wait_deadline_ms", C.c_int32),
         ("ar_oneshot", C.c_int32), ("ar_pad", C.c_int32), ("ar_half_bytes", C.c_uint64),
+        ("ar_mc", C.c_void_p), ("ar_tdone_ofs", C.c_uint64),
     ]
 
 

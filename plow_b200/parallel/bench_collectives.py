@@ -65,8 +65,9 @@ def main():
     from ..ops import native, quant
     from .tp import TpComm
     hbm, tflops, src = _peaks()
-    fused = TpComm(rank, world, impl="fused", max_rows=128, max_n=8192, max_k=8192)
-    fused2 = TpComm(rank, world, impl="fused", max_rows=128, max_n=8192, max_k=8192, oneshot_bytes=0)
+    fused = TpComm(rank, world, impl="fused", max_rows=128, max_n=8192, max_k=8192, form="oneshot")
+    fused2 = TpComm(rank, world, impl="fused", max_rows=128, max_n=8192, max_k=8192, form="twoshot")
+    fused3 = TpComm(rank, world, impl="fused", max_rows=128, max_n=8192, max_k=8192, form="nvls") if fused.mc_ptr else None
     nccl = TpComm(rank, world, impl="nccl")
     # row-parallel projections of the dense 8B shape (o_proj, down) and of the MLA shape (o_proj), K sharded over ranks
     for name, M, N, Kfull, fp8 in (("dense8b_o_proj", 64, 4096, 4096, False), ("dense8b_down", 64, 4096, 14336, False),
@@ -81,6 +82,7 @@ def main():
             xq, wq, sx, sw = x.bfloat16(), w.bfloat16(), None, None
         tf = _graph_time(lambda: fused.gemm_allreduce(xq, wq, N, sx=sx, sw=sw), a.reps, a.iters)
         t2 = _graph_time(lambda: fused2.gemm_allreduce(xq, wq, N, sx=sx, sw=sw), a.reps, a.iters)
+        t3 = _graph_time(lambda: fused3.gemm_allreduce(xq, wq, N, sx=sx, sw=sw), a.reps, a.iters) if fused3 else None
         tn = _graph_time(lambda: nccl.gemm_allreduce(xq, wq, N, sx=sx, sw=sw), a.reps, a.iters)
         native.check_status()
         es = 1 if fp8 else 2
@@ -88,7 +90,7 @@ def main():
         roof = max(2.0 * M * N * K / (tflops * 1e6), link / (NVLINK_GBS * 1e3), N * K * es / (hbm * 1e3))
         if rank == 0:
             print(json.dumps(dict(case=f"gemm_allreduce/{name}", world=world, M=M, N=N, K_per_rank=K, fused_us=round(tf, 2),
-                                  fused_twoshot_us=round(t2, 2), nccl_us=round(tn, 2), roofline_us=round(roof, 2),
+                                  fused_twoshot_us=round(t2, 2), fused_nvls_us=(round(t3, 2) if t3 else None), nccl_us=round(tn, 2), roofline_us=round(roof, 2),
                                   achieved=round(roof / tf, 3), peaks=src)))
     # column-parallel projections behind a sequence-parallel seam: gather the row bands, then GEMM
     for name, M, Nfull, K in (("dense8b_qkv", 64, 6144, 4096), ("dense8b_gate_up", 64, 28672, 4096)):

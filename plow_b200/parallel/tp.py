@@ -25,8 +25,10 @@ def _align(x, a=256):
 
 class TpComm:
     def __init__(self, rank: int, world: int, max_rows: int = 128, max_n: int = 16384, impl: str = "fused", deadline_ms: int = 2000,
-                 max_k: int = 16384, oneshot_bytes: int = 4 << 20):
-        self.rank, self.world, self.impl = rank, world, impl
+                 max_k: int = 16384, oneshot_bytes: int = 4 << 20, form: str = "auto"):
+        """form: "auto" (NVSwitch multicast reduce at 4+ ranks when the mapping exists, else one-shot for decode-size
+        messages, else two-shot), or "oneshot" / "twoshot" / "nvls" to force one."""
+        self.rank, self.world, self.impl, self.form = rank, world, impl, form
         self.oneshot_bytes = oneshot_bytes     # messages up to this size use the one-shot form (decode), larger ones two-shot
         self.dev = torch.device("cuda", torch.cuda.current_device())
         self.max_rows, self.max_n, self.deadline_ms = max_rows, max_n, deadline_ms
@@ -36,7 +38,7 @@ class TpComm:
         tiles = (max_n + 127) // 128
         lay, off = {}, 0
         self.half_bytes = _align(tiles * world * 128 * 64 * 2)        # one-shot slots: [tile][source rank][128][<=64 tokens] bf16
-        for name, nbytes in (("part", max(tiles * 128 * 128 * 2, 2 * self.half_bytes)), ("flag", tiles * 8 * 4), ("done", 128), ("y", max_rows * max_n * 2),
+        for name, nbytes in (("part", max(tiles * 128 * 128 * 2, 2 * self.half_bytes)), ("flag", tiles * 8 * 4), ("done", 128), ("tdone", tiles * 4), ("y", max_rows * max_n * 2),
                              ("ag_ctr", 128), ("xg0", max_rows * max_k * 2), ("xg1", max_rows * max_k * 2)):
             lay[name] = off
             off = _align(off + nbytes)
@@ -51,6 +53,10 @@ class TpComm:
         self.ag_done = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self._ag_calls = 0
         self.peers = list(self.hdl.buffer_ptrs)
+        try:
+            self.mc_ptr = int(self.hdl.multicast_ptr) if self.hdl.has_multicast_support(self.dev.type, self.dev.index) else 0
+        except Exception:
+            self.mc_ptr = int(getattr(self.hdl, "multicast_ptr", 0) or 0)
         import ctypes
         self._peer_arr = (ctypes.c_void_p * 8)(*(self.peers + [None] * (8 - len(self.peers))))
 
@@ -60,10 +66,16 @@ class TpComm:
         M = x.shape[0]
         bn = gemm_ops._pick_bn_swap(M, sx is not None, False) if M <= 128 else 128
         if self.impl == "fused" and M <= 64 and bn <= 64 and M <= self.max_rows and n_out <= self.max_n and n_out % 8 == 0:
-            oneshot = (self.world - 1) * M * n_out * 2 <= self.oneshot_bytes
+            form = self.form
+            if form == "auto":
+                form = "nvls" if (self.mc_ptr and self.world >= 4) else ("oneshot" if (self.world - 1) * M * n_out * 2 <= self.oneshot_bytes else "twoshot")
+            if form == "nvls" and not self.mc_ptr:
+                raise RuntimeError("this symmetric allocation has no NVSwitch multicast mapping")
+            oneshot = form == "oneshot"
             ar = dict(peers=self.peers, part_ofs=self.lay["part"], flag_ofs=self.lay["flag"], done_ofs=self.lay["done"],
                       y_ofs=self.lay["y"], epoch_ptr=self.epoch.data_ptr(), world=self.world, me=self.rank,
-                      deadline_ms=self.deadline_ms, oneshot=int(oneshot), half_bytes=self.half_bytes)
+                      deadline_ms=self.deadline_ms, oneshot={"oneshot": 1, "twoshot": 0, "nvls": 2}[form], half_bytes=self.half_bytes,
+                      mc_ptr=self.mc_ptr, tdone_ofs=self.lay["tdone"])
             if oneshot:
                 # every rank reduces locally, so the result can land in any tensor of this rank
                 y = out if out is not None else torch.empty(M, n_out, dtype=BF16, device=self.dev)

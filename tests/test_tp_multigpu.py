@@ -19,8 +19,9 @@ torch.cuda.set_device(rank)
 dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
 from plow_b200.ops import native, quant
 from plow_b200.parallel.tp import TpComm
-fused = TpComm(rank, world, impl="fused")                       # one-shot form for these message sizes
-fused2 = TpComm(rank, world, impl="fused", oneshot_bytes=0)      # two-shot form (owner reduces, stores to every rank)
+fused = TpComm(rank, world, impl="fused", form="oneshot")        # push partials to every rank, reduce locally
+fused2 = TpComm(rank, world, impl="fused", form="twoshot")       # owner reduces from peer memory, stores to every rank
+fused3 = TpComm(rank, world, impl="fused", form="nvls") if fused.mc_ptr and os.environ.get("PLOW_TEST_NVLS", "1") == "1" else None
 nccl = TpComm(rank, world, impl="nccl")
 out = {}
 for (M, N, K, fp8) in [(64, 7168, 8192, True), (17, 1024, 2048, False), (64, 4096, 7168, False)]:
@@ -35,7 +36,7 @@ for (M, N, K, fp8) in [(64, 7168, 8192, True), (17, 1024, 2048, False), (64, 409
         xr, wr = xq.float(), wq.float()
     part = (xr @ wr.t()).bfloat16().float()
     ref = part.clone(); dist.all_reduce(ref)
-    for form, comm in (("oneshot", fused), ("twoshot", fused2)):
+    for form, comm in (("oneshot", fused), ("twoshot", fused2)) + ((("nvls", fused3),) if fused3 else ()):
         for call in range(3):
             y = comm.gemm_allreduce(xq, wq, N, sx=sx, sw=sw).clone()
             torch.cuda.synchronize(); native.check_status()
@@ -57,6 +58,7 @@ for (M, N, K, fp8) in [(64, 7168, 8192, True), (17, 1024, 2048, False), (64, 409
         return float(t)
     out[f"{M}x{N}x{K}us"] = dict(fused=timeit(lambda: fused.gemm_allreduce(xq, wq, N, sx=sx, sw=sw)),
                                  twoshot=timeit(lambda: fused2.gemm_allreduce(xq, wq, N, sx=sx, sw=sw)),
+                                 nvls=(timeit(lambda: fused3.gemm_allreduce(xq, wq, N, sx=sx, sw=sw)) if fused3 else None),
                                  nccl=timeit(lambda: nccl.gemm_allreduce(xq, wq, N, sx=sx, sw=sw)))
 if rank == 0: print(json.dumps(out))
 dist.destroy_process_group()
