@@ -91,7 +91,7 @@ def main():
         if rank == 0:
             print(json.dumps(dict(case=f"gemm_allreduce/{name}", world=world, M=M, N=N, K_per_rank=K, fused_us=round(tf, 2),
                                   fused_twoshot_us=round(t2, 2), fused_nvls_us=(round(t3, 2) if t3 else None), nccl_us=round(tn, 2), roofline_us=round(roof, 2),
-                                  achieved=round(roof / tf, 3), peaks=src)))
+                                  achieved=round(roof / min(x for x in (tf, t2, t3) if x), 3), peaks=src)))
     # column-parallel projections behind a sequence-parallel seam: gather the row bands, then GEMM
     for name, M, Nfull, K in (("dense8b_qkv", 64, 6144, 4096), ("dense8b_gate_up", 64, 28672, 4096)):
         N = Nfull // world // 128 * 128
