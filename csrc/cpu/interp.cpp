@@ -382,6 +382,173 @@ void op_glu(const Ctx& c) {
   for (int64_t k = a * W; k < b * W; ++k) out[k] = g[k] / (1.0f + std::exp(-g[k])) * u[k];
 }
 
+
+// ---- multi-head latent attention (golden f32; cache row = [c_kv (kv_lora) | k_rope (qk_rope)]) -----------------
+// Reference semantics: runtime/nvidia/op_mla.cuh:23-42 (absorbed scores over the latent cache, W_uv folded once).
+void op_mla_kv_write(const Ctx& c) {
+  float* cache = (float*)c.T(0);
+  const float* kva = (const float*)c.T(1);
+  const float* gamma = (const float*)c.T(2);
+  const float* rope = (const float*)c.T(3);
+  const int L = c.in->i[0], R = c.in->i[1], pair = c.in->i[2], co = c.in->i[5];
+  const StepIO& io = c.e->io;
+  const int pitch = c.in->i[6] ? int(c.in->i[6]) : L + R;
+  const float eps = c.in->w[0].f;
+  int64_t a, b;
+  c.range(io.rows, a, b);
+  for (int64_t r = a; r < b; ++r) {
+    const int pos = io.pos[r], slot = io.seq[r];
+    const int page = io.page_table[int64_t(slot) * io.max_pages + pos / PLOW_KV_PAGE];
+    float* dst = cache + (int64_t(page) * PLOW_KV_PAGE + pos % PLOW_KV_PAGE) * (L + R);
+    const float* src = kva + r * pitch + co;
+    rmsnorm_row(dst, src, gamma, L, eps, 0);
+    rope_head(dst + L, src + L, rope + int64_t(pos) * R, R, R, pair);
+  }
+}
+
+void op_mla_attn(const Ctx& c) {
+  float* out = (float*)c.T(0);
+  const float* q = (const float*)c.T(1);
+  const float* rope = (const float*)c.T(2);
+  const float* wkvb = (const float*)c.T(4);
+  const float* cache = (const float*)c.T(5);
+  const int H = c.in->i[0], L = c.in->i[1], NP = c.in->i[2], RP = c.in->i[3], V = c.in->i[4], pair = c.in->i[5];
+  const float scale = c.in->w[0].f;
+  const StepIO& io = c.e->io;
+  const int qh = NP + RP, row = L + RP;
+  std::vector<float> qabs(L), qr(RP), olat(L), sc;
+  int64_t a, b;
+  c.range(int64_t(io.rows) * H, a, b);
+  for (int64_t item = a; item < b; ++item) {
+    const int64_t r = item / H;
+    const int h = int(item % H);
+    const int pos = io.pos[r], slot = io.seq[r];
+    const float* qv = q + (r * H + h) * qh;
+    const float* wuk = wkvb + int64_t(h) * (NP + V) * L;        // [NP][L]
+    const float* wuv = wuk + int64_t(NP) * L;                   // [V][L]
+    for (int j = 0; j < L; ++j) {
+      float s = 0.f;
+      for (int d = 0; d < NP; ++d) s += qv[d] * wuk[int64_t(d) * L + j];
+      qabs[j] = s;
+    }
+    rope_head(qr.data(), qv + NP, rope + int64_t(pos) * RP, RP, RP, pair);
+    sc.resize(pos + 1);
+    float mx = -INFINITY;
+    for (int t = 0; t <= pos; ++t) {
+      const int page = io.page_table[int64_t(slot) * io.max_pages + t / PLOW_KV_PAGE];
+      const float* kr = cache + (int64_t(page) * PLOW_KV_PAGE + t % PLOW_KV_PAGE) * row;
+      sc[t] = (dotf(qabs.data(), kr, L) + dotf(qr.data(), kr + L, RP)) * scale;
+      mx = std::max(mx, sc[t]);
+    }
+    float den = 0.f;
+    std::fill(olat.begin(), olat.end(), 0.f);
+    for (int t = 0; t <= pos; ++t) {
+      const float p = std::exp(sc[t] - mx);
+      den += p;
+      const int page = io.page_table[int64_t(slot) * io.max_pages + t / PLOW_KV_PAGE];
+      const float* kr = cache + (int64_t(page) * PLOW_KV_PAGE + t % PLOW_KV_PAGE) * row;
+      for (int j = 0; j < L; ++j) olat[j] += p * kr[j];
+    }
+    float* o = out + (r * H + h) * V;
+    for (int d = 0; d < V; ++d) o[d] = dotf(wuv + int64_t(d) * L, olat.data(), L) / den;
+  }
+}
+
+// ---- MoE router + experts (golden).  Selection key = score + bias, gate = unbiased score; group-limited: group score =
+// sum of its two largest biased scores, lowest id wins ties (crates/packet/src/moe.rs:97-160).
+void op_router_topk(const Ctx& c) {
+  int32_t* table = (int32_t*)c.T(0);
+  const float* logits = (const float*)c.T(1);
+  const float* bias = (const float*)c.T(2);
+  const int E = c.in->i[0], K = c.in->i[1], NG = std::max(1, int(c.in->i[2])), TG = std::max(1, int(c.in->i[3]));
+  const bool sigmoid = c.in->i[4] != 0, norm = c.in->i[5] != 0;
+  const float route_scale = c.in->w[0].f;
+  std::vector<float> score(E), sel(E);
+  std::vector<char> keep(NG);
+  int64_t a, b;
+  c.range(c.e->io.rows, a, b);
+  for (int64_t r = a; r < b; ++r) {
+    const float* lg = logits + r * E;
+    if (sigmoid) {
+      for (int e = 0; e < E; ++e) score[e] = 1.0f / (1.0f + std::exp(-lg[e]));
+    } else {
+      float mx = -INFINITY, den = 0.f;
+      for (int e = 0; e < E; ++e) mx = std::max(mx, lg[e]);
+      for (int e = 0; e < E; ++e) { score[e] = std::exp(lg[e] - mx); den += score[e]; }
+      for (int e = 0; e < E; ++e) score[e] /= den;
+    }
+    for (int e = 0; e < E; ++e) sel[e] = score[e] + (bias ? bias[e] : 0.f);
+    if (NG > 1) {
+      const int per = E / NG;
+      std::vector<float> gs(NG);
+      for (int g = 0; g < NG; ++g) {
+        float m1 = -INFINITY, m2 = -INFINITY;
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+          if (sel[e] > m1) { m2 = m1; m1 = sel[e]; } else if (sel[e] > m2) { m2 = sel[e]; }
+        }
+        gs[g] = m1 + m2;
+      }
+      std::fill(keep.begin(), keep.end(), 0);
+      for (int k = 0; k < TG; ++k) {
+        int best = -1;
+        for (int g = 0; g < NG; ++g) if (!keep[g] && (best < 0 || gs[g] > gs[best])) best = g;
+        keep[best] = 1;
+      }
+      for (int e = 0; e < E; ++e) if (!keep[e / per]) sel[e] = -INFINITY;
+    }
+    float gsum = 0.f;
+    int32_t* row = table + r * K * 2;
+    std::vector<char> used(E, 0);
+    for (int k = 0; k < K; ++k) {
+      int best = -1;
+      for (int e = 0; e < E; ++e) if (!used[e] && (best < 0 || sel[e] > sel[best])) best = e;
+      used[best] = 1;
+      row[2 * k] = best;
+      gsum += score[best];
+    }
+    for (int k = 0; k < K; ++k) {
+      float g = score[row[2 * k]];
+      if (norm) g /= std::max(gsum, 1e-20f);
+      g *= route_scale;
+      std::memcpy(&row[2 * k + 1], &g, 4);
+    }
+  }
+}
+
+void op_moe(const Ctx& c) {
+  float* y = (float*)c.T(0);
+  const float* h = (const float*)c.T(1);
+  const int32_t* table = (const int32_t*)c.T(2);
+  const float* w1 = (const float*)c.T(3);      // [E][2F][H]: gate rows then up rows per expert
+  const float* w2 = (const float*)c.T(4);      // [E][H][F]
+  const float* shared = (const float*)c.T(5);
+  const int K = c.in->i[2], F = c.in->i[3];
+  const PlowTensorEnt& te = c.e->pkt->tensors[c.in->t[0]];
+  const int H = int(te.dims[1]);
+  std::vector<float> glu(F), acc(H);
+  int64_t a, b;
+  c.range(c.e->io.rows, a, b);
+  for (int64_t r = a; r < b; ++r) {
+    const float* x = h + r * H;
+    for (int j = 0; j < H; ++j) acc[j] = shared ? shared[r * H + j] : 0.f;
+    for (int k = 0; k < K; ++k) {                // fixed slot order
+      const int e = table[(r * K + k) * 2];
+      float gate;
+      std::memcpy(&gate, &table[(r * K + k) * 2 + 1], 4);
+      if (e < 0) continue;
+      const float* wg = w1 + int64_t(e) * 2 * F * H;
+      const float* wu = wg + int64_t(F) * H;
+      for (int f = 0; f < F; ++f) {
+        const float gv = dotf(wg + int64_t(f) * H, x, H), uv = dotf(wu + int64_t(f) * H, x, H);
+        glu[f] = gv / (1.0f + std::exp(-gv)) * uv;
+      }
+      const float* wd = w2 + int64_t(e) * H * F;
+      for (int j = 0; j < H; ++j) acc[j] += gate * dotf(wd + int64_t(j) * F, glu.data(), F);
+    }
+    for (int j = 0; j < H; ++j) y[r * H + j] = acc[j];
+  }
+}
+
 int exec_entry(Engine* e, const PlowInst* in, const PlowStreamEnt& se) {
   Ctx c{e, in, se.slice0, se.slice0 + se.nslice, in->nslice};
   switch (in->op) {
@@ -404,6 +571,11 @@ int exec_entry(Engine* e, const PlowInst* in, const PlowStreamEnt& se) {
     case PLOW_OP_ROW_GATHER: op_row_gather(c); return 0;
     case PLOW_OP_ARGMAX: op_argmax(c); return 0;
     case PLOW_OP_GLU: op_glu(c); return 0;
+    case PLOW_OP_MLA_KV_WRITE: op_mla_kv_write(c); return 0;
+    case PLOW_OP_MLA_DECODE:
+    case PLOW_OP_MLA_PREFILL: op_mla_attn(c); return 0;
+    case PLOW_OP_ROUTER_TOPK: op_router_topk(c); return 0;
+    case PLOW_OP_MOE_GEMM: op_moe(c); return 0;
     default: return 100 + in->op;  // op not implemented on the CPU backend
   }
 }

@@ -158,3 +158,43 @@ def test_decode_rows_ride_prefill_launches(tiny_assets):
     rode, r1 = run(True)
     assert plain == rode
     assert r0 == 0 and r1 >= 3
+
+
+def test_mla_moe_model_on_cpu_backend_matches_reference(tmp_path):
+    """The C++ interpreter's golden MLA (absorbed scores over the latent cache) and MoE (group-limited sigmoid router,
+    slot-ordered combine, shared expert) ops: prefill + decode logits vs the PyTorch fp32 reference."""
+    import glob
+    from safetensors.torch import load_file
+    from plow_b200 import plowc
+    from plow_b200.models import config, reference
+    from plow_b200.runtime.engine import TokenBatch
+    cfg = dict(model_type="deepseek_v3", hidden_size=256, num_attention_heads=4, num_hidden_layers=2,
+               q_lora_rank=64, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+               intermediate_size=512, first_k_dense_replace=1, n_routed_experts=8, n_shared_experts=1,
+               num_experts_per_tok=2, moe_intermediate_size=64, n_group=2, topk_group=1, scoring_func="sigmoid",
+               norm_topk_prob=True, routed_scaling_factor=2.5, topk_method="noaux_tc", rms_norm_eps=1e-6,
+               rope_theta=10000.0, vocab_size=512, tie_word_embeddings=False, max_position_embeddings=1024, eos_token_id=1,
+               plow_dtype="f32", plow_kv_dtype="f32")
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=0)
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", arch="cpu", n_cu=4, max_rows=128, decode_rungs=[1, 2, 4], max_seqs=4)
+    eng = CpuEngine(tmp_path / "assets", max_slots=2, max_ctx=256)
+    state = {}
+    for f in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        state.update(load_file(f))
+    ref = reference.ReferenceModel(config.spec_from_config(cfg), {k: v.float() for k, v in state.items()})
+    rng = np.random.default_rng(2)
+    p = rng.integers(0, 512, 70).tolist()
+    eng.begin_slot(0, p)
+    eng.reserve(0, len(p) + 4)
+    r = eng.step(TokenBatch(np.asarray(p, np.int32), np.arange(len(p), dtype=np.int32), np.zeros(len(p), np.int32),
+                            np.asarray([len(p) - 1], np.int32), want_logits=True))
+    want = ref.forward(torch.tensor(p))[-1]
+    assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item())
+    eng.commit(0, p)
+    nxt = int(want.argmax())
+    assert int(r.ids[0]) == nxt
+    r = eng.step(TokenBatch(np.asarray([nxt], np.int32), np.asarray([len(p)], np.int32), np.zeros(1, np.int32), np.zeros(1, np.int32),
+                            decode=True, want_logits=True))
+    want = ref.forward(torch.tensor(p + [nxt]))[-1]
+    assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item())
+    eng.close()
