@@ -44,6 +44,7 @@ class GenParams:
     min_tokens: int = 0
     logprobs: int | None = None
     session_id: str | None = None
+    deadline_ms: float | None = None      # total time budget from arrival; None = no deadline
 
     @property
     def greedy(self) -> bool:
@@ -139,6 +140,19 @@ class Metrics:
 class ModelMux:
     """Dispatcher + slot table for one engine."""
 
+    def load_estimate(self, window_s: float = 10.0) -> dict:
+        """Arrival rate (req/s over the window), service rate (finished req/s from the recent e2e times with the current
+        concurrency) and utilisation rho = lambda / mu — the admission estimators of the reference (sched/admission.rs)."""
+        now = time.monotonic()
+        self._arrivals = [t for t in self._arrivals if now - t <= window_s]
+        lam = len(self._arrivals) / window_s
+        with self.metrics.lock:
+            e2e = list(self.metrics.e2e[-64:])
+        mean_s = (sum(e2e) / len(e2e) / 1e3) if e2e else None
+        mu = (max(1, self.engine.max_slots) / mean_s) if mean_s else None
+        return dict(arrival_rps=round(lam, 3), service_rps=(round(mu, 3) if mu else None), rho=(round(lam / mu, 3) if mu else None),
+                    queued=len(self.waiting) + self.ingress.qsize(), live=len(self.live))
+
     def __init__(self, engine: EngineBase, tokenizer, cfg: SchedConfig | None = None, eos_ids=None):
         self.engine = engine
         self.tok = tokenizer
@@ -154,6 +168,7 @@ class ModelMux:
         self._last_was_prefill = False
         self._n = 0
         self.draining = False
+        self._arrivals: list = []          # arrival times of recent requests (rate estimator)
 
     # ---- public --------------------------------------------------------------------------------
     def start(self) -> "ModelMux":
@@ -169,6 +184,9 @@ class ModelMux:
     def submit(self, prompt: list, params: GenParams, rid: str | None = None) -> Request:
         self._n += 1
         req = Request(rid=rid or f"req-{self._n}", prompt=list(prompt), params=params)
+        if params.deadline_ms:
+            req.deadline = req.arrived + params.deadline_ms / 1e3
+        self._arrivals.append(req.arrived)
         if self.engine.health == EngineHealth.DEAD:
             req.out.put(Chunk("error", error="engine is dead", finish_reason="error"))
             return req
@@ -236,6 +254,13 @@ class ModelMux:
         decoding = [r for r in self.live.values() if r.done_prefill >= r.pf_len and not r.cancelled]
         for r in [r for r in self.live.values() if r.cancelled]:
             self._finish(r, "cancelled")
+        now = time.monotonic()
+        for r in [r for r in self.live.values() if r.deadline is not None and now > r.deadline]:
+            # a request past its deadline stops where it is: what was generated is delivered (reference: serve/deadlines.rs)
+            self.metrics.inc("deadline_exceeded")
+            self._finish(r, "deadline")
+        prefilling = [r for r in prefilling if r.slot in self.live]
+        decoding = [r for r in decoding if r.slot in self.live]
         run_prefill = bool(prefilling) and (not decoding or not self._last_was_prefill or self.cfg.objective == "throughput")
         t0 = time.perf_counter()
         if run_prefill:
@@ -255,7 +280,7 @@ class ModelMux:
         now = time.monotonic()
         keep = []
         for r in self.waiting:
-            if now - r.arrived > self.cfg.queue_ttl_s and r.preempted == 0:
+            if (now - r.arrived > self.cfg.queue_ttl_s or (r.deadline is not None and now > r.deadline)) and r.preempted == 0:
                 self.metrics.inc("requests_shed")
                 r.out.put(Chunk("error", error="queue ttl exceeded", finish_reason="overloaded"))
             else:

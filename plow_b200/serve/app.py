@@ -72,14 +72,14 @@ def _gen_params(body: dict, default_max: int) -> GenParams:
                      repetition_penalty=float(body.get("repetition_penalty") or 1.0), seed=body.get("seed"),
                      stop=list(stop), stop_token_ids=list(body.get("stop_token_ids") or []),
                      ignore_eos=bool(body.get("ignore_eos", False)), min_tokens=int(body.get("min_tokens") or 0),
-                     logprobs=lp)
+                     logprobs=lp, deadline_ms=(float(body["deadline_ms"]) if body.get("deadline_ms") else None))
 
 
 def _finish(reason: str) -> tuple:
     """(finish_reason, x_plow_finish_reason)"""
     if reason in ("stop", "length"):
         return reason, None
-    if reason in ("preempted", "cancelled"):
+    if reason in ("preempted", "cancelled", "deadline"):
         return "length", reason
     return "stop", reason
 
@@ -161,6 +161,10 @@ def create_app(state: AppState) -> FastAPI:
         if not state.timeline or not state.timeline.enabled:
             raise ApiError(404, "tracing is off (start with --trace)", code="trace_disabled")
         return PlainTextResponse(state.timeline.to_json(), media_type="application/json")
+
+    @app.get("/v1/load")
+    async def load_estimate():
+        return {m.name: m.mux.load_estimate() for m in state.models.values()}
 
     @app.get("/v1/placement")
     async def placement():

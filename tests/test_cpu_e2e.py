@@ -198,3 +198,27 @@ def test_mla_moe_model_on_cpu_backend_matches_reference(tmp_path):
     want = ref.forward(torch.tensor(p + [nxt]))[-1]
     assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item())
     eng.close()
+
+
+def test_deadline_stops_generation_and_load_estimate(tiny_assets):
+    eng = CpuEngine(tiny_assets / "assets", max_slots=2, max_ctx=256)
+    mux = ModelMux(eng, ByteTokenizer(), SchedConfig(token_budget=256), eos_ids=[])
+    r = mux.submit(_prompts()[0], GenParams(max_tokens=200, deadline_ms=1.0))
+    import time as _t
+    mux.tick()                      # prefill + first token
+    _t.sleep(0.01)
+    for _ in range(5):
+        mux.tick()
+    got, reason = 0, None
+    while True:
+        ch = r.out.get(timeout=10)
+        if ch.kind == "token":
+            got += 1
+        else:
+            reason = ch.finish_reason
+            break
+    assert reason == "deadline" and 1 <= got < 200
+    est = mux.load_estimate()
+    assert est["arrival_rps"] > 0 and est["live"] == 0
+    assert mux.metrics.snapshot()["counters"]["deadline_exceeded"] == 1
+    eng.close()
