@@ -69,22 +69,24 @@ __global__ void mla_build_items(const int* kvlen, int T, int tiles_per_split, in
   // one thread per request: split count, then its offset as the sum of the counts before it
   extern __shared__ int cnt[];
   for (int r = threadIdx.x; r < T; r += blockDim.x) {
+    int per;
     const int tiles = (kvlen[r] + kMlaPage - 1) / kMlaPage;
-    int ns = (tiles + tiles_per_split - 1) / tiles_per_split;
-    cnt[r] = ns > max_splits ? max_splits : ns;
+    cnt[r] = tiles > 0 ? kv_splits(tiles, tiles_per_split, max_splits, &per) : 0;     // nothing cached: no work item
   }
   __syncthreads();
   for (int r = threadIdx.x; r < T; r += blockDim.x) {
     int off = 0;
     for (int q = 0; q < r; ++q) off += cnt[q];
     const int tiles = (kvlen[r] + kMlaPage - 1) / kMlaPage;
-    for (int split = 0; split < cnt[r]; ++split) {
-      const int t0 = split * tiles_per_split;
-      const int nt = (split == max_splits - 1) ? tiles - t0 : min(tiles_per_split, tiles - t0);
+    int per = 1;
+    const int ns = tiles > 0 ? kv_splits(tiles, tiles_per_split, max_splits, &per) : 0;
+    for (int split = 0; split < ns; ++split) {
+      const int t0 = split * per;
+      const int nt = min(per, tiles - t0);
       items[2 * (off + split)] = MlaItem{r, 0, split, t0, nt, 0, 0, 0};
       items[2 * (off + split) + 1] = MlaItem{r, 1, split, t0, nt, 0, 0, 0};
     }
-    if (r == T - 1) *n_items = 2 * (off + cnt[r]);
+    if (r == T - 1) *n_items = 2 * (off + ns);
   }
 }
 
@@ -451,8 +453,8 @@ __global__ void mla_merge_kernel(const __nv_bfloat16* opart, const float* lse, c
                                  int max_splits, int tiles_per_split, __nv_bfloat16* out /*[heads][T][512]*/) {
   const int t = blockIdx.x, h = blockIdx.y;
   const int tiles = (kvlen[t] + kMlaPage - 1) / kMlaPage;
-  int ns = (tiles + tiles_per_split - 1) / tiles_per_split;
-  ns = ns < 1 ? 1 : (ns > max_splits ? max_splits : ns);
+  int per_unused;
+  const int ns = kv_splits(tiles, tiles_per_split, max_splits, &per_unused);
   float mx = -INFINITY;
   for (int s = 0; s < ns; ++s) mx = fmaxf(mx, lse[(static_cast<size_t>(t) * max_splits + s) * kMlaHeads + h]);
   float wsum = 0.f;

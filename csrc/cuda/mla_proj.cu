@@ -218,8 +218,8 @@ mla_fold_kernel(const FoldArgs a, const __grid_constant__ CUtensorMap tm_w) {
       int ns = 0;
       if (live) {
         const int tiles = (a.kvlen[t] + 63) / 64;
-        ns = (tiles + a.tiles_per_split - 1) / a.tiles_per_split;
-        ns = ns < 1 ? 1 : (ns > a.max_splits ? a.max_splits : ns);
+        int per_unused;
+        ns = kv_splits(tiles, a.tiles_per_split, a.max_splits, &per_unused);
         if (ns > 8) ns = 8;
         float l8[8];
 #pragma unroll

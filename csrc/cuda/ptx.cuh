@@ -302,6 +302,19 @@ __device__ __forceinline__ void red_add_release_gpu(uint32_t* p, uint32_t v) {
 }
 
 
+// Split count of a request with `tiles` KV tiles for the split-KV attention kernels: as many splits as
+// `tiles_per_split` asks for (at most max_splits), then the tiles are dealt evenly, so the work items of one request
+// differ by at most one tile.  Returns the number of non-empty splits; *per = tiles per split.  Shared by the kernel
+// that builds the work list and the kernels that merge the splits, which must agree.
+__host__ __device__ inline int kv_splits(int tiles, int tiles_per_split, int max_splits, int* per) {
+  int ns = (tiles + tiles_per_split - 1) / tiles_per_split;
+  ns = ns < 1 ? 1 : (ns > max_splits ? max_splits : ns);
+  const int p = (tiles + ns - 1) / ns;
+  *per = p < 1 ? 1 : p;
+  const int used = (tiles + *per - 1) / *per;
+  return used < 1 ? 1 : used;
+}
+
 // ---------------------------------------------------------------- NVSwitch multicast (multimem) on a multicast-mapped address
 // one store that lands in every rank's copy
 __device__ __forceinline__ void multimem_st_u32(void* mc, uint32_t v) {

@@ -401,7 +401,10 @@ class GpuEngine(EngineBase):
             raise EngineError("the fused MLA projection kernels are specialised for 128 nope / 128 v dims")
         q8, sq = mla_ops.absorb(q, wuk_t, rope, self.d_in[1], heads, pair)
         if self._mla_ws is None or self._mla_ws.opart.shape[0] < T:
-            self._mla_ws = mla_ops.DecodeWorkspace(max(T, self.max_rows_all), self.max_ctx + PAGE, device=self.device)
+            # up to 8 splits per request (the fold kernel's limit); a request's tiles are dealt evenly over its splits
+            max_tiles = (self.max_ctx + PAGE + 63) // 64
+            self._mla_ws = mla_ops.DecodeWorkspace(max(T, self.max_rows_all), self.max_ctx + PAGE, tiles_per_split=max(int(os.environ.get('PLOW_MLA_TPS', '32')), -(-max_tiles // 8)),
+                                                   device=self.device)
         if self._mla_ws.max_splits > 8:
             raise EngineError("max_ctx needs more than 8 KV splits; raise tiles_per_split")
         sparse = bool(ins.i[6]) and ins.t[7] != pk.T_NONE and T <= self.SPARSE_MAX_ROWS
