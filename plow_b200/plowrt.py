@@ -43,7 +43,8 @@ def make_entry(name, assets, cfg):
     eng = load_engine(assets, cfg)
     tok = load_tokenizer(assets)
     mux = ModelMux(eng, tok, SchedConfig(token_budget=min(cfg.token_budget, eng.max_rows(False)), objective=cfg.objective,
-                                         tbt_target_ms=cfg.tbt_target_ms, queue_ttl_s=cfg.queue_ttl_s)).start()
+                                         tbt_target_ms=cfg.tbt_target_ms, queue_ttl_s=cfg.queue_ttl_s, ride=cfg.ride,
+                                         spec_depth=cfg.spec_depth)).start()
     return ModelEntry(name, mux, tok, ChatTemplate.from_assets(assets))
 
 
@@ -180,6 +181,7 @@ def main(argv=None) -> int:
     s.add_argument("--max-ctx", type=int)
     s.add_argument("--backend")
     s.add_argument("--objective")
+    s.add_argument("--spec-depth", type=int, dest="spec_depth")
     s.add_argument("--dp", type=int)
     s.add_argument("--trace", action="store_true")
     s.add_argument("--api-key", action="append")

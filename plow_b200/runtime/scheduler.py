@@ -101,6 +101,7 @@ class SchedConfig:
     aging_ticks: int = 32             # after this many waits a long prefill jumps the SRPF order
     reserve_tokens: int = PAGE        # KV head-room required per live sequence before seating more
     ride: bool = True                 # decode rows ride the prefill launch (mixed step) instead of waiting a tick
+    spec_depth: int = 0               # > 0: speculative decoding for greedy requests (prompt-lookup drafts, span verify)
 
 
 class Metrics:
@@ -403,8 +404,56 @@ class ModelMux:
             k += 1
 
     # ---- decode --------------------------------------------------------------------------------
+    def _spec_tick(self, reqs: list) -> bool:
+        """Speculative decode step: every greedy request contributes its pending token plus up to ``spec_depth`` drafted
+        tokens as consecutive rows of one launch; the longest prefix the model agrees with is emitted.  Used while the
+        rows fit the program's sample capacity (low concurrency, where latency matters); returns False to fall back."""
+        from .spec import NgramDrafter
+        eng = self.engine
+        depth = self.cfg.spec_depth
+        max_samples = eng.buckets.get("max_seqs", 64)
+        if not reqs or any(not r.params.greedy for r in reqs) or len(reqs) * (depth + 1) > max_samples:
+            return False
+        drafter = getattr(self, "_drafter", None) or NgramDrafter()
+        self._drafter = drafter
+        ids, pos, seq, spans = [], [], [], []
+        for r in sorted(reqs, key=lambda r: r.slot):
+            n_ctx = len(r.prompt) + len(r.generated)
+            room = min(depth, r.params.max_tokens - len(r.generated) - 1, eng.max_ctx - n_ctx - 2)
+            draft = drafter.propose(r.all_tokens(), max(0, room)) if room > 0 else []
+            try:
+                eng.reserve(r.slot, n_ctx + len(draft) + 1)
+            except OutOfPages:
+                return False
+            rows = [r.generated[-1]] + draft
+            spans.append((r, len(ids), draft))
+            ids += rows
+            pos += list(range(n_ctx - 1, n_ctx - 1 + len(rows)))
+            seq += [r.slot] * len(rows)
+        if len(ids) == len(spans):
+            return False                      # nothing drafted: the plain decode program is cheaper
+        res = eng.step(TokenBatch(np.array(ids, np.int32), np.array(pos, np.int32), np.array(seq, np.int32),
+                                  np.arange(len(ids), dtype=np.int32), decode=False))
+        self.metrics.inc("spec_ticks")
+        for (r, at, draft) in spans:
+            got = [int(x) for x in res.ids[at:at + 1 + len(draft)]]
+            j = 0
+            while j < len(draft) and draft[j] == got[j]:
+                j += 1
+            self.metrics.inc("spec_proposed", len(draft))
+            self.metrics.inc("spec_accepted", j)
+            pending = r.generated[-1]
+            for tok_in, tok_out in zip([pending] + draft[:j], got[:j + 1]):
+                if r.slot not in self.live or self.live[r.slot] is not r:
+                    break                      # finished (stop / length) while emitting the accepted span
+                eng.commit(r.slot, [tok_in])
+                self._produce(r, tok_out, None)
+        return True
+
     def _decode_tick(self, reqs: list) -> None:
         eng = self.engine
+        if self.cfg.spec_depth > 0 and self._spec_tick(reqs):
+            return
         cap = eng.max_rows(True)
         reqs = sorted(reqs, key=lambda r: r.slot)[:cap]
         ready = []

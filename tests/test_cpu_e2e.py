@@ -222,3 +222,32 @@ def test_deadline_stops_generation_and_load_estimate(tiny_assets):
     assert est["arrival_rps"] > 0 and est["live"] == 0
     assert mux.metrics.snapshot()["counters"]["deadline_exceeded"] == 1
     eng.close()
+
+
+def test_speculative_decoding_in_the_scheduler(tiny_assets):
+    """spec_depth > 0: greedy requests are verified in spans; the tokens equal plain decoding and fewer launches are used."""
+    def run(depth):
+        eng = CpuEngine(tiny_assets / "assets", max_slots=2, max_ctx=512, prefix_cache=False)
+        mux = ModelMux(eng, ByteTokenizer(), SchedConfig(token_budget=256, spec_depth=depth), eos_ids=[])
+        rng = np.random.default_rng(5)
+        motif = rng.integers(0, 32000, 12).tolist()
+        r = mux.submit((motif * 8)[:90], GenParams(max_tokens=24))
+        for _ in range(100):
+            if not mux.tick() and not mux.live and not mux.waiting:
+                break
+        ids = []
+        while True:
+            ch = r.out.get(timeout=10)
+            if ch.kind == "token":
+                ids.append(ch.token_id)
+            else:
+                assert ch.kind == "done" and ch.finish_reason == "length"
+                break
+        c = mux.metrics.snapshot()["counters"]
+        eng.close()
+        return ids, c
+    plain, c0 = run(0)
+    spec, c1 = run(4)
+    assert plain == spec and len(spec) == 24
+    assert c1.get("spec_ticks", 0) >= 1 and c1.get("spec_accepted", 0) >= 1
+    assert c1.get("decode_ticks", 0) + c1.get("spec_ticks", 0) < c0["decode_ticks"]
