@@ -54,7 +54,7 @@ def cmd_serve(args) -> int:
     from .serve.app import AppState, create_app
     cfg = cfgmod.RuntimeConfig.load(cli=dict(host=args.host, port=args.port, max_slots=args.max_slots, max_ctx=args.max_ctx,
                                              backend=args.backend, objective=args.objective, trace=args.trace or None,
-                                             api_keys=args.api_key or None, dp=args.dp))
+                                             api_keys=args.api_key or None, dp=args.dp, spec_depth=args.spec_depth))
     state = AppState(api_keys=cfg.api_keys, timeline=Timeline(cfg.trace), loader=lambda n, p: make_entry(n, p, cfg))
     name = args.name or Path(args.assets).resolve().name
     if cfg.dp > 1:
