@@ -17,7 +17,7 @@ from . import config as cfgmod
 from .compiler import disasm as disasm_mod, packet as pk, schedule
 
 
-def load_engine(assets, cfg: cfgmod.RuntimeConfig):
+def load_engine(assets, cfg: cfgmod.RuntimeConfig, device=None):
     backend = cfg.backend
     if backend == "auto":
         import torch
@@ -28,7 +28,7 @@ def load_engine(assets, cfg: cfgmod.RuntimeConfig):
                          prefix_cache=cfg.prefix_cache)
     from .runtime.gpu_engine import GpuEngine
     return GpuEngine(assets, max_slots=cfg.max_slots, max_ctx=cfg.max_ctx, n_pages=cfg.n_pages or None,
-                     kv_fraction=cfg.kv_fraction, prefix_cache=cfg.prefix_cache, cuda_graphs=cfg.cuda_graphs)
+                     kv_fraction=cfg.kv_fraction, prefix_cache=cfg.prefix_cache, cuda_graphs=cfg.cuda_graphs, device=device)
 
 
 def make_entry(name, assets, cfg):
@@ -42,9 +42,16 @@ def make_entry(name, assets, cfg):
             print(f"plowrt: warning: {p}", file=sys.stderr)
     eng = load_engine(assets, cfg)
     tok = load_tokenizer(assets)
-    mux = ModelMux(eng, tok, SchedConfig(token_budget=min(cfg.token_budget, eng.max_rows(False)), objective=cfg.objective,
-                                         tbt_target_ms=cfg.tbt_target_ms, queue_ttl_s=cfg.queue_ttl_s, ride=cfg.ride,
-                                         spec_depth=cfg.spec_depth)).start()
+    sched = SchedConfig(token_budget=min(cfg.token_budget, eng.max_rows(False)), objective=cfg.objective,
+                        tbt_target_ms=cfg.tbt_target_ms, queue_ttl_s=cfg.queue_ttl_s, ride=cfg.ride, spec_depth=cfg.spec_depth)
+    mux = ModelMux(eng, tok, sched)
+    if cfg.pd:
+        # prefill / decode disaggregation: this engine only prefills; a second engine (the next GPU when there is one)
+        # imports each sequence's KV image and decodes it
+        import torch
+        dev2 = f"cuda:{(torch.cuda.current_device() + 1) % torch.cuda.device_count()}" if torch.cuda.is_available() and cfg.backend != "cpu" else None
+        mux.pd_target = ModelMux(load_engine(assets, cfg, device=dev2), tok, sched).start()
+    mux.start()
     return ModelEntry(name, mux, tok, ChatTemplate.from_assets(assets))
 
 
@@ -54,7 +61,7 @@ def cmd_serve(args) -> int:
     from .serve.app import AppState, create_app
     cfg = cfgmod.RuntimeConfig.load(cli=dict(host=args.host, port=args.port, max_slots=args.max_slots, max_ctx=args.max_ctx,
                                              backend=args.backend, objective=args.objective, trace=args.trace or None,
-                                             api_keys=args.api_key or None, dp=args.dp, spec_depth=args.spec_depth))
+                                             api_keys=args.api_key or None, dp=args.dp, spec_depth=args.spec_depth, pd=args.pd or None))
     state = AppState(api_keys=cfg.api_keys, timeline=Timeline(cfg.trace), loader=lambda n, p: make_entry(n, p, cfg))
     name = args.name or Path(args.assets).resolve().name
     if cfg.dp > 1:
@@ -182,6 +189,7 @@ def main(argv=None) -> int:
     s.add_argument("--backend")
     s.add_argument("--objective")
     s.add_argument("--spec-depth", type=int, dest="spec_depth")
+    s.add_argument("--pd", action="store_true", help="prefill on one engine, decode on a second one (KV image hand-off)")
     s.add_argument("--dp", type=int)
     s.add_argument("--trace", action="store_true")
     s.add_argument("--api-key", action="append")

@@ -170,6 +170,8 @@ class ModelMux:
         self._n = 0
         self.draining = False
         self._arrivals: list = []          # arrival times of recent requests (rate estimator)
+        self.pd_target: "ModelMux | None" = None     # prefill/decode disaggregation: where finished prefills continue
+        self.adopt_q: "queue.Queue" = queue.Queue()  # (request, KV image) pairs handed over by a prefill mux
 
     # ---- public --------------------------------------------------------------------------------
     def start(self) -> "ModelMux":
@@ -247,6 +249,7 @@ class ModelMux:
             except queue.Empty:
                 break
         self._shed_expired()
+        self._adopt()
         self._admit()
         if not self.live:
             return False
@@ -275,6 +278,36 @@ class ModelMux:
             return False
         self.metrics.obs("step_ms", (time.perf_counter() - t0) * 1e3)
         return True
+
+    # ---- prefill / decode disaggregation ---------------------------------------------------------
+    def _handoff(self, r: Request) -> None:
+        """This mux only prefills: export the sequence's KV image, free the slot here and queue the request on the
+        decode mux, which imports the image and continues (reference: serve/pd.rs:1-8)."""
+        from .kv_image import export_slot
+        img = export_slot(self.engine, r.slot)
+        self.engine.retire_slot(r.slot)
+        del self.live[r.slot]
+        self.free_slots.append(r.slot)
+        r.slot = -1
+        self.metrics.inc("pd_handoffs")
+        self.metrics.inc("pd_bytes", img.nbytes())
+        self.pd_target.adopt_q.put((r, img))
+
+    def _adopt(self) -> None:
+        from .kv_image import import_slot
+        while self.free_slots and not self.adopt_q.empty():
+            r, img = self.adopt_q.queue[0]
+            slot = self.free_slots.pop()
+            try:
+                import_slot(self.engine, slot, img)
+            except OutOfPages:
+                self.engine.retire_slot(slot)
+                self.free_slots.append(slot)
+                return                                   # retry when pages free up
+            self.adopt_q.get_nowait()
+            r.slot, r.done_prefill, r.pf_len = slot, len(r.prompt), len(r.prompt)
+            self.live[slot] = r
+            self.metrics.inc("pd_adopted")
 
     # ---- admission -----------------------------------------------------------------------------
     def _shed_expired(self) -> None:
@@ -396,6 +429,8 @@ class ModelMux:
                 lg = res.logits[k] if res.logits is not None else None
                 self._produce(r, int(res.ids[k]), lg)
                 k += 1
+                if self.pd_target is not None and r.slot >= 0 and self.live.get(r.slot) is r:
+                    self._handoff(r)
         for r in rode:
             if r.slot in self.live and self.live[r.slot] is r:
                 eng.commit(r.slot, [r.generated[-1]])

@@ -78,3 +78,35 @@ def test_speculative_decoding_matches_greedy(engines):
     assert stats.steps <= 24 and stats.emitted >= 23
     assert NgramDrafter(2).propose([1, 2, 3, 9, 1, 2], 3) == [3, 9, 1]
     assert plan_depth(0.0, 8) == 0 and plan_depth(0.9, 8) >= 3
+
+
+def test_pd_disaggregation_between_two_muxes(engines):
+    """A prefill mux hands every finished prompt to a decode mux through a KV image; the client sees one stream whose
+    tokens equal single-engine decoding."""
+    from plow_b200.runtime.scheduler import GenParams, ModelMux, SchedConfig
+    from plow_b200.text.tokenizer import ByteTokenizer
+    a, b = engines
+    rng = np.random.default_rng(11)
+    prompts = [rng.integers(0, 32000, n).tolist() for n in (90, 33)]
+    want = [_plain(a, 0, p, 10) for p in prompts]
+    pre = ModelMux(a, ByteTokenizer(), SchedConfig(token_budget=64), eos_ids=[])
+    dec = ModelMux(b, ByteTokenizer(), SchedConfig(token_budget=64), eos_ids=[])
+    pre.pd_target = dec
+    reqs = [pre.submit(p, GenParams(max_tokens=10)) for p in prompts]
+    for _ in range(200):
+        busy = pre.tick() | dec.tick()
+        if not busy and not pre.live and not dec.live and not pre.waiting and dec.adopt_q.empty():
+            break
+    for r, w in zip(reqs, want):
+        ids = []
+        while True:
+            ch = r.out.get(timeout=10)
+            if ch.kind == "token":
+                ids.append(ch.token_id)
+            else:
+                assert ch.kind == "done" and ch.finish_reason == "length"
+                break
+        assert ids == w
+    pc, dc = pre.metrics.snapshot()["counters"], dec.metrics.snapshot()["counters"]
+    assert pc["pd_handoffs"] == 2 and dc["pd_adopted"] == 2 and pc.get("decode_ticks", 0) == 0 and dc["decode_ticks"] >= 9
+    assert a.pool.available() == a.pool.n_pages and b.pool.available() == b.pool.n_pages
