@@ -49,6 +49,37 @@ class EngineError(RuntimeError):
         self.fatal = fatal
 
 
+class HostKvStore:
+    """Second KV tier in host memory: published pages evicted from the device pool are kept here (LRU, bounded) and
+    copied back when a later prompt matches their chain hash (reference: crates/plowrt/src/memory/kv_store.rs, the
+    content-addressed block store with device and pinned-host slabs)."""
+
+    def __init__(self, engine: "EngineBase", capacity_pages: int):
+        from collections import OrderedDict
+        self.engine, self.capacity = engine, capacity_pages
+        self.blocks: "OrderedDict[bytes, tuple]" = OrderedDict()       # hash -> (tokens, {name: host array})
+        pool = engine.pool
+        pool.on_evict, pool.host_has, pool.on_restore = self.save, self.has, self.restore
+
+    def has(self, h: bytes) -> bool:
+        return h in self.blocks
+
+    def save(self, page: int, h: bytes, tokens: tuple) -> None:
+        from .kv_image import _to_numpy
+        self.blocks[h] = (tokens, {n: _to_numpy(a, [page])[0] for n, a in self.engine.kv_arrays().items()})
+        self.blocks.move_to_end(h)
+        while len(self.blocks) > self.capacity:
+            self.blocks.popitem(last=False)
+
+    def restore(self, page: int, h: bytes):
+        from .kv_image import _from_numpy
+        tokens, arrays = self.blocks[h]
+        self.blocks.move_to_end(h)
+        for n, a in self.engine.kv_arrays().items():
+            _from_numpy(a, [page], arrays[n][None])
+        return tokens
+
+
 class EngineBase:
     """Slot + page bookkeeping common to all backends."""
 
@@ -95,6 +126,11 @@ class EngineBase:
         self.pool.release(slot)
         self.tokens.pop(slot, None)
         self.kvlen[slot] = 0
+
+    def enable_host_kv(self, capacity_pages: int) -> "HostKvStore":
+        """Keep evicted prefix pages in host memory (call after the backend has bound its KV tensors)."""
+        self.host_kv = HostKvStore(self, capacity_pages)
+        return self.host_kv
 
     def kv_tokens_free(self) -> int:
         return self.pool.available() * PAGE

@@ -57,7 +57,12 @@ class PagePool:
         self.page_hash: dict[int, bytes] = {}
         self.lru: OrderedDict[bytes, None] = OrderedDict()   # published blocks with refs == 0
         self.seqs: dict[int, SeqPages] = {}
-        self.stats = dict(hits=0, misses=0, evictions=0)
+        self.stats = dict(hits=0, misses=0, evictions=0, spilled=0, restored=0)
+        # second tier (host memory): on_evict(page, hash, tokens) saves a published page that is about to be reused,
+        # host_has(hash) / on_restore(page, hash) -> tokens bring it back on a later prefix match
+        self.on_evict = None
+        self.host_has = None
+        self.on_restore = None
 
     # ---- capacity ------------------------------------------------------------------------------
     def available(self) -> int:
@@ -71,6 +76,9 @@ class PagePool:
             blk = self.blocks.pop(h)
             self.page_hash.pop(blk.page, None)
             self.stats["evictions"] += 1
+            if self.on_evict is not None:
+                self.on_evict(blk.page, h, blk.tokens)
+                self.stats["spilled"] += 1
             return blk.page
         raise OutOfPages("KV page pool exhausted")
 
@@ -89,6 +97,17 @@ class PagePool:
             toks = tuple(prompt[i * PAGE:(i + 1) * PAGE])
             h = chain_hash(prev, toks, self.namespace)
             blk = self.blocks.get(h)
+            if blk is None and self.host_has is not None and self.host_has(h) and self.available() > 0:
+                # the page was evicted to host memory: take a device page and copy it back
+                page = self._take()
+                if self.on_restore(page, h) == toks:
+                    blk = _Block(page=page, tokens=toks, refs=0)
+                    self.blocks[h] = blk
+                    self.page_hash[page] = h
+                    self.lru[h] = None
+                    self.stats["restored"] += 1
+                else:
+                    self.free.append(page)
             if blk is None or blk.tokens != toks:
                 self.stats["misses"] += 1
                 break

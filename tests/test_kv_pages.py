@@ -69,3 +69,34 @@ def test_random_walk_invariants():
             except OutOfPages:
                 pool.release(s)
         pool.check()
+
+
+def test_host_tier_restores_evicted_prefix_pages(tiny_assets):
+    """A prefix page evicted from a tiny device pool is spilled to host memory and copied back on the next match: the
+    second run of the prompt computes only its tail and produces the same tokens."""
+    import numpy as np
+    from plow_b200.runtime.cpu_engine import CpuEngine
+    from plow_b200.runtime.engine import TokenBatch
+    eng = CpuEngine(tiny_assets / "assets", max_slots=2, max_ctx=256, n_pages=4)
+    eng.enable_host_kv(8)
+    rng = np.random.default_rng(4)
+    a = rng.integers(0, 32000, 150).tolist()
+    b = rng.integers(0, 32000, 200).tolist()
+
+    def run(slot, prompt):
+        cached = eng.begin_slot(slot, prompt)
+        eng.reserve(slot, len(prompt) + 1)
+        part = prompt[cached:]
+        r = eng.step(TokenBatch(np.asarray(part, np.int32), np.arange(cached, len(prompt), dtype=np.int32),
+                                np.full(len(part), slot, np.int32), np.asarray([len(part) - 1], np.int32)))
+        eng.commit(slot, part)
+        eng.retire_slot(slot)
+        return int(r.ids[0]), cached
+    t1, c1 = run(0, a)
+    assert c1 == 0
+    run(1, b)                              # needs all four pages: a's two published pages are evicted (spilled)
+    assert eng.pool.stats["spilled"] >= 2
+    t2, c2 = run(0, a)
+    assert c2 == 128 and t2 == t1 and eng.pool.stats["restored"] == 2
+    eng.pool.check()
+    eng.close()
