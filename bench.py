@@ -87,6 +87,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=61, help="debug only: anything but 61 is not the named config")
     ap.add_argument("--batch-per-gpu", type=int, default=64)
     ap.add_argument("--ttft-prompts", type=int, default=2)
+    ap.add_argument("--prefill-chunk", type=int, default=2048, help="rows of the prefill program used for the TTFT prompts")
     ap.add_argument("--init", default="scaled", choices=["scaled", "plain"],
                     help="scaled: depth-scaled random init (balanced routing, like a trained checkpoint); plain: N(0,0.02) everywhere")
     args = ap.parse_args()
@@ -120,11 +121,11 @@ def main() -> int:
     g = graph.build_graph(spec, ep=world, rank=rank)
     sites = rewrite.fuse(g)
     max_ctx = 8192 + 512 + 64
-    pkt = emit.emit_packet(g, sites, hwspec.lookup("b200"), 148, dict(prefill=[512], decode=[B], max_seqs=8), rank=rank)
+    pkt = emit.emit_packet(g, sites, hwspec.lookup("b200"), 148, dict(prefill=sorted({512, args.prefill_chunk}), decode=[B], max_seqs=8), rank=rank)
     comm = None
     if world > 1:
         from plow_b200.parallel.ep import EpComm
-        comm = EpComm(rank, world, spec, max_rows=512, impl=args.impl)
+        comm = EpComm(rank, world, spec, max_rows=max(512, args.prefill_chunk), impl=args.impl)
     dev = torch.device("cuda", local)
     t_load = time.time()
     eng = GpuEngine(packet=pkt, weights=SyntheticWeights(dev, seed=1234 + rank, scaled_init_layers=(args.layers if args.init == "scaled" else 0)), max_slots=B + 1, max_ctx=max_ctx,
@@ -166,8 +167,8 @@ def main() -> int:
         eng.reserve(slot, n_tokens + 2)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        for a in range(0, n_tokens, 512):
-            b = min(n_tokens, a + 512)
+        for a in range(0, n_tokens, args.prefill_chunk):
+            b = min(n_tokens, a + args.prefill_chunk)
             eng.step(TokenBatch(prompt[a:b], np.arange(a, b, dtype=np.int32), np.full(b - a, slot, np.int32),
                                 np.array([b - a - 1], np.int32)))
         dt = (time.perf_counter() - t0) * 1e3
@@ -258,9 +259,13 @@ def main() -> int:
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         route = {"rows_rank0": int(go[-1]), "max_rows_any_rank": int(mx[0]), "max_rows_one_expert": int(mx[1]),
                  "mean_rows_per_rank": B * 8}
-    ttfts = []
-    # every rank prefills a prompt of the same length at the same time (EP layers are collective)
+    ttfts, ttft_lens = [], []
+    # every rank prefills a prompt of the same length at the same time (EP layers are collective); one untimed prompt
+    # that touches every prefill bucket first (lazy scratch allocations are not part of a steady-state TTFT)
+    if args.ttft_prompts:
+        prefill_once(args.prefill_chunk + 100)
     for n in list(np.random.default_rng(11).integers(1024, 8193, size=args.ttft_prompts)):
+        ttft_lens.append(int(n))
         ttfts.append(prefill_once(int(n)))
     dev_total = float(np.sum(dev_ms))
     stats = torch.tensor([dev_total, wall, float(np.median(dev_ms))], dtype=torch.float64, device=dev)
@@ -284,7 +289,7 @@ def main() -> int:
                        "l2": "no flush needed: each step streams >90 GB of weights and KV per GPU (L2 is 126 MB)",
                        "named_config": bool(world == 8 and args.layers == 61)},
             "p50_tpot_ms": round(tpot, 3), "p50_ttft_ms": round(float(np.median(ttfts)), 1) if ttfts else None,
-            "ttft_prompts": len(ttfts),
+            "ttft_prompts": len(ttfts), "ttft_ms_all": [round(t, 1) for t in ttfts], "ttft_prompt_tokens": ttft_lens,
             "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": int(4 * 4 * B), "d2h_bytes_per_step": int(4 * B)},
             "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": int(launches_per_step),
             "clocks": clocks, "load_s": round(load_s, 1), "ep_routing_last_layer": route,
