@@ -107,3 +107,42 @@ def test_chat_template_features():
     from plow_b200.serve.template import ChatTemplateError
     with pytest.raises(ChatTemplateError):
         t.render([{"role": "assistant", "content": "x"}])
+
+
+def test_bench_api_client_against_a_live_server(tiny_assets):
+    """The load generator drives a real uvicorn server (CPU backend) with Poisson arrivals and a shared prefix and
+    reports TTFT / TPOT percentiles; the second wave hits the prefix cache."""
+    import asyncio
+    import socket
+    import threading
+    import time as _t
+    import uvicorn
+    from plow_b200.serve import bench_api
+    eng = CpuEngine(tiny_assets / "assets", max_slots=4, max_ctx=512)
+    tok = ByteTokenizer()
+    mux = ModelMux(eng, tok, eos_ids=[]).start()
+    state = AppState()
+    state.add(ModelEntry("tiny", mux, tok, ChatTemplate()))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    server = uvicorn.Server(uvicorn.Config(create_app(state), host="127.0.0.1", port=port, log_level="error"))
+    th = threading.Thread(target=server.run, daemon=True)
+    th.start()
+    for _ in range(100):
+        if server.started:
+            break
+        _t.sleep(0.05)
+    try:
+        prompts = bench_api.make_prompts(6, 32000, 100, 160, shared_frac=1.0, shared_len=64, seed=1)
+        assert all(p[:64] == prompts[0][:64] for p in prompts)
+        res = asyncio.run(bench_api.run(f"http://127.0.0.1:{port}", "tiny", prompts, 6, rate=20.0))
+        assert res["requests"] == 6 and res["failed"] == 0 and res["output_tok_s"] > 0
+        assert res["ttft_ms"]["p50"] is not None and res["tpot_ms"]["p99"] is not None
+        closed = asyncio.run(bench_api.run(f"http://127.0.0.1:{port}", "tiny", prompts[:3], 4, rate=0.0, concurrency=2))
+        assert closed["failed"] == 0 and closed["concurrency"] == 2
+        assert eng.pool.stats["hits"] >= 1
+    finally:
+        server.should_exit = True
+        th.join(timeout=10)
+        mux.stop()
