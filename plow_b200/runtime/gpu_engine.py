@@ -455,7 +455,10 @@ class GpuEngine(EngineBase):
         self._need_tp().all_reduce(out)
 
     def _ext_xreduce_add_norm(self, st, ins):
-        raise EngineError("XREDUCE_ADD_NORM is emitted only when gemm-xreduce fusion is disabled; not supported by this engine")
+        # emitted when the GEMM -> all-reduce fusion is disabled at compile time: reduce the partial in place, then the
+        # same residual + RMSNorm row kernel as ADD_NORM (same operand order: h_out, x_in, partial, gamma, x_out)
+        self._need_tp().all_reduce(self.tensor(st, ins.t[2]))
+        self._op_add_norm(st, ins)
 
     # -- GQA
     def _op_rope_kv(self, st, ins):
