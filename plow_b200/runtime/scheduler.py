@@ -45,11 +45,12 @@ class GenParams:
     logprobs: int | None = None
     session_id: str | None = None
     deadline_ms: float | None = None      # total time budget from arrival; None = no deadline
+    json_mode: bool = False               # response_format json_object: tokens are filtered by a JSON recogniser
 
     @property
     def greedy(self) -> bool:
         return self.temperature <= 0.0 and self.presence_penalty == 0.0 and self.frequency_penalty == 0.0 \
-            and self.repetition_penalty == 1.0 and self.logprobs is None
+            and self.repetition_penalty == 1.0 and self.logprobs is None and not self.json_mode
 
 
 @dataclass
@@ -517,7 +518,17 @@ class ModelMux:
     def _produce(self, r: Request, greedy_id: int, logits) -> None:
         p = r.params
         tok, lp, top = greedy_id, None, None
-        if not p.greedy and logits is not None:
+        if p.json_mode and logits is not None:
+            if getattr(r, "guided", None) is None:
+                from ..text.guided import GuidedJson
+                eos = next(iter(self.eos_ids), 0)
+                r.guided = GuidedJson(lambda t: self.tok.decode([t]), eos)
+            lg = sampling.apply_penalties(logits, r.generated, p.presence_penalty, p.frequency_penalty, p.repetition_penalty)
+            tok = r.guided.pick(np.asarray(lg))
+            if r.guided.state.complete and tok == r.guided.eos_id:
+                self._finish(r, "stop")
+                return
+        elif not p.greedy and logits is not None:
             lg = sampling.apply_penalties(logits, r.generated, p.presence_penalty, p.frequency_penalty, p.repetition_penalty)
             tok = sampling.sample(lg, r.rng, p.temperature, p.top_k, p.top_p, p.min_p)
             if p.logprobs is not None:

@@ -28,7 +28,7 @@ from ..runtime.scheduler import GenParams
 from . import tools as tools_mod
 from .template import ChatTemplateError
 
-REFUSED_PARAMS = ("response_format", "echo", "best_of", "logit_bias", "suffix", "functions", "function_call")
+REFUSED_PARAMS = ("echo", "best_of", "logit_bias", "suffix", "functions", "function_call")
 
 
 class ApiError(Exception):
@@ -46,6 +46,14 @@ def _gen_params(body: dict, default_max: int) -> GenParams:
             raise ApiError(400, f"parameter '{k}' is not supported", code="unsupported_parameter")
     if body.get("n", 1) != 1:
         raise ApiError(400, "only n=1 is supported", code="unsupported_parameter")
+    rf = body.get("response_format")
+    json_mode = False
+    if rf is not None:
+        kind = rf.get("type") if isinstance(rf, dict) else rf
+        if kind == "json_object":
+            json_mode = True
+        elif kind != "text":
+            raise ApiError(400, f"response_format '{kind}' is not supported (text, json_object)", code="unsupported_parameter")
     t = body.get("temperature")
     temperature = 1.0 if t is None else float(t)
     if temperature < 0 or temperature > 2:
@@ -72,7 +80,8 @@ def _gen_params(body: dict, default_max: int) -> GenParams:
                      repetition_penalty=float(body.get("repetition_penalty") or 1.0), seed=body.get("seed"),
                      stop=list(stop), stop_token_ids=list(body.get("stop_token_ids") or []),
                      ignore_eos=bool(body.get("ignore_eos", False)), min_tokens=int(body.get("min_tokens") or 0),
-                     logprobs=lp, deadline_ms=(float(body["deadline_ms"]) if body.get("deadline_ms") else None))
+                     logprobs=lp, deadline_ms=(float(body["deadline_ms"]) if body.get("deadline_ms") else None),
+                     json_mode=json_mode)
 
 
 def _finish(reason: str) -> tuple:

@@ -40,3 +40,33 @@ def test_reasoning_split_whole_and_streaming():
         r += dr
         c += dc
     assert r == "step one" and c == "The answer <b>"
+
+
+def test_json_prefix_recogniser_and_guided_pick():
+    import numpy as np
+    from plow_b200.text.guided import GuidedJson, JsonPrefix
+    good = ['{"a": 1}', '{"a": [1, 2, {"b": null}], "c": "x\\n"}', '{}', '{"k": [], "z": {}}', '{"a": -1.5e3, "b": false}  ']
+    bad = ['{"a": 1,}', '[1]', '{"a" 1}', '{"a": 01}', '{"a": 1} x', '{,', '{"a": tru3}']
+    for s in good:
+        p = JsonPrefix()
+        assert p.feed_text(s) and p.complete, s
+    for s in bad:
+        assert not JsonPrefix().feed_text(s), s
+    p = JsonPrefix()
+    assert p.feed_text('{"a": tru') and not p.complete
+    # a byte-level "model" that prefers garbage: the guide still produces a valid document
+    vocab = [chr(c) for c in range(32, 127)]
+    g = GuidedJson(lambda t: vocab[t] if t < len(vocab) else "", eos_id=len(vocab), top_candidates=16)
+    rng = np.random.default_rng(0)
+    text = ""
+    for step in range(200):
+        logits = rng.standard_normal(len(vocab) + 1)
+        if step > 12:
+            logits[vocab.index("}")] += 6.0          # the model eventually wants to close
+            logits[vocab.index('"')] += 3.0
+        tok = g.pick(logits)
+        if tok == len(vocab):
+            break
+        text += vocab[tok]
+    import json
+    assert isinstance(json.loads(text), dict), text
