@@ -459,6 +459,38 @@ __global__ void argmax_kernel(int* out, const float* logits, int V) {
   }
 }
 
+// Vocabulary-sharded arg-max: the row's best (ordered score << 32 | ~global index) key of this rank's shard; the ranks'
+// keys are folded with a max (lowest global index wins ties), see argmax_fin_kernel.
+__global__ void argmax_key_kernel(unsigned long long* keys, const float* logits, int V, int vocab_ofs) {
+  __shared__ unsigned long long red[32];
+  const float* row = logits + static_cast<size_t>(blockIdx.x) * V;
+  unsigned long long best = 0ull;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const unsigned long long key = (static_cast<unsigned long long>(ordered_bits(row[i])) << 32) |
+                                   static_cast<uint32_t>(~static_cast<uint32_t>(i + vocab_ofs));
+    best = key > best ? key : best;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o); best = other > best ? other : best; }
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = threadIdx.x < (blockDim.x + 31) / 32 ? red[threadIdx.x] : 0ull;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o); best = other > best ? other : best; }
+    if (threadIdx.x == 0) keys[blockIdx.x] = best;
+  }
+}
+
+// keys [world][R] gathered from the ranks -> ids [R]
+__global__ void argmax_fin_kernel(int* out, const unsigned long long* keys, int R, int world) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= R) return;
+  unsigned long long best = 0ull;
+  for (int w = 0; w < world; ++w) { const unsigned long long k = keys[static_cast<size_t>(w) * R + r]; best = k > best ? k : best; }
+  out[r] = static_cast<int>(~static_cast<uint32_t>(best & 0xffffffffu));
+}
+
 __global__ void row_gather_kernel(__nv_bfloat16* out, const __nv_bfloat16* x, const int* rows, int W) {
   const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(rows[blockIdx.x]) * W);
   uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(blockIdx.x) * W);
@@ -569,6 +601,16 @@ int plow_moe_combine(void* out, const void* y, const void* shared, const void* t
 
 int plow_argmax(int* out, const float* logits, int R, int V, void* st) {
   argmax_kernel<<<R, 1024, 0, S(st)>>>(out, logits, V);
+  return ok();
+}
+
+int plow_argmax_key(void* keys, const float* logits, int R, int V, int vocab_ofs, void* st) {
+  argmax_key_kernel<<<R, 1024, 0, S(st)>>>(static_cast<unsigned long long*>(keys), logits, V, vocab_ofs);
+  return ok();
+}
+
+int plow_argmax_fin(int* out, const void* keys, int R, int world, void* st) {
+  argmax_fin_kernel<<<(R + 127) / 128, 128, 0, S(st)>>>(out, static_cast<const unsigned long long*>(keys), R, world);
   return ok();
 }
 

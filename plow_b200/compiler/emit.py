@@ -20,7 +20,7 @@ from .packet import Op
 DIM_ROWS, DIM_SAMPLES, DIM_PAGES, DIM_SLOTS = -1, -2, -3, -4
 _SYM = {R: DIM_ROWS, S: DIM_SAMPLES, "P": DIM_PAGES, "B": DIM_SLOTS}
 _DT = {"f32": pk.DType.F32, "bf16": pk.DType.BF16, "f16": pk.DType.F16, "e4m3": pk.DType.E4M3,
-       "i32": pk.DType.I32, "u8": pk.DType.U8, "fp8": pk.DType.E4M3}
+       "i32": pk.DType.I32, "u8": pk.DType.U8, "fp8": pk.DType.E4M3, "i64": pk.DType.I64}
 _TC = {"weight": pk.TClass.WEIGHT, "derived": pk.TClass.DERIVED, "gen": pk.TClass.GEN, "kv": pk.TClass.KV,
        "state": pk.TClass.STATE, "act": pk.TClass.ACT, "input": pk.TClass.INPUT, "output": pk.TClass.OUTPUT,
        "peer": pk.TClass.PEER}
@@ -158,8 +158,16 @@ class Lowering:
                               i=[self.width(n.outputs[0])])
                 out.append(schedule.LInst(ins, rd(*n.inputs), rd(n.outputs[0]), 1.0, samples))
             elif n.op == "argmax":
-                ins = pk.Inst(Op.ARGMAX, t=[self.t(n.outputs[0]), self.t(n.inputs[0])], i=[self.width(n.inputs[0])])
+                ins = pk.Inst(Op.ARGMAX, t=[self.t(n.outputs[0]), self.t(n.inputs[0])],
+                              i=[self.width(n.inputs[0]), int(a.get("packed", False)), int(a.get("vocab_ofs", 0))])
                 out.append(schedule.LInst(ins, rd(n.inputs[0]), rd(n.outputs[0]), 2.0, samples))
+            elif n.op == "xargmax_fin":
+                ins = pk.Inst(Op.XARGMAX_FIN, t=[self.t(n.outputs[0]), self.t(n.inputs[0])], i=[g.tp])
+                out.append(schedule.LInst(ins, rd(n.inputs[0]), rd(n.outputs[0]), 5.0, samples, "comm"))
+            elif n.op == "xgather":
+                ins = pk.Inst(Op.XGATHER, t=[self.t(n.outputs[0]), self.t(n.inputs[0])], i=[a["width"], g.tp])
+                out.append(schedule.LInst(ins, rd(n.inputs[0]), rd(n.outputs[0]),
+                                          costmodel.allreduce_cost(samples, a["width"] * g.tp, g.tp, 4).time_us(self.hw), samples, "comm"))
             elif n.op in ("xreduce", "xreduce_add_norm"):
                 if n.op == "xreduce":
                     ins = pk.Inst(Op.XREDUCE, t=[self.t(n.outputs[0]), self.t(n.inputs[0])],

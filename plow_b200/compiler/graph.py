@@ -140,11 +140,23 @@ def build_graph(spec: ModelSpec, tp: int = 1, ep: int = 1, rank: int = 0) -> Gra
     g.add("rmsnorm", [x, fn], [hf], eps=spec.rms_eps, plus_one=spec.norm_plus_one)
     hs = g.tmp("hs", (S, H))
     g.add("row_gather", [hf, "in.sample_rows"], [hs])
-    head = emb if spec.tie_embeddings else g.weight("lm_head.weight", (V, H))
     logits = g.value("out.logits", (S, V), "f32", "output")
-    g.add("linear", [hs, head], [logits], out_f32=True)
     out_ids = g.value("out.ids", (S,), "i32", "output")
-    g.add("argmax", [logits], [out_ids])
+    if tp > 1 and not spec.tie_embeddings and V % (tp * 128) == 0:
+        # vocabulary-sharded lm_head: each rank streams V/tp rows, takes the arg-max of its shard as a packed
+        # (score, ~global index) key and the ranks fold the keys; full logits are gathered for sampled requests
+        # (reference: asset/shard.rs:1-40 "lm_head replicated or vocab-sharded + XArgmaxFin", dev_isa.h:224-238)
+        head = g.weight("lm_head.weight", (V // tp, H), shard_axis=0)
+        local = g.tmp("logits_l", (S, V // tp), "f32")
+        g.add("linear", [hs, head], [local], out_f32=True)
+        keys = g.tmp("amax_key", (S,), "i64")
+        g.add("argmax", [local], [keys], packed=True, vocab_ofs=g.rank * (V // tp))
+        g.add("xargmax_fin", [keys], [out_ids])
+        g.add("xgather", [local], [logits], width=V // tp)
+    else:
+        head = emb if spec.tie_embeddings else g.weight("lm_head.weight", (V, H))
+        g.add("linear", [hs, head], [logits], out_f32=True)
+        g.add("argmax", [logits], [out_ids])
     g.check_topological()
     return g
 

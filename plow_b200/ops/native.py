@@ -112,6 +112,8 @@ _SIGS = {
     "plow_moe_gather": "ppippipp" "iiip",
     "plow_moe_combine": "pppppiiip",
     "plow_argmax": "ppiip",
+    "plow_argmax_key": "ppiiip",
+    "plow_argmax_fin": "ppiip",
     "plow_row_gather": "pppiip",
     "plow_head_to_token": "ppiiip",
     "plow_mla_decode": "ppppplpipp" "iiipppppfpp",

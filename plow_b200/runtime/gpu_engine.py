@@ -31,7 +31,8 @@ from .engine import EngineBase, EngineError, StepResult, TokenBatch
 from .kv_pages import PAGE
 
 BF16, FP8, F32, I32 = torch.bfloat16, torch.float8_e4m3fn, torch.float32, torch.int32
-_TORCH_DT = {pk.DType.F32: F32, pk.DType.BF16: BF16, pk.DType.E4M3: FP8, pk.DType.I32: I32, pk.DType.U8: torch.uint8}
+_TORCH_DT = {pk.DType.F32: F32, pk.DType.BF16: BF16, pk.DType.E4M3: FP8, pk.DType.I32: I32, pk.DType.U8: torch.uint8,
+             pk.DType.I64: torch.int64}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -364,7 +365,28 @@ class GpuEngine(EngineBase):
 
     def _op_argmax(self, st, ins):
         out, lg = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])
-        native.call("plow_argmax", out, lg, st.samples, ins.i[0])
+        if ins.i[1]:        # vocabulary-sharded lm_head: packed (score, ~global index) key of this rank's shard
+            native.call("plow_argmax_key", out, lg, st.samples, ins.i[0], ins.i[2])
+        else:
+            native.call("plow_argmax", out, lg, st.samples, ins.i[0])
+
+    def _ext_xargmax_fin(self, st, ins):
+        """Fold the ranks' packed arg-max keys: a tiny all-gather, then a max per row (lowest global index on ties)."""
+        import torch.distributed as dist
+        out, keys = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])
+        world = ins.i[0]
+        buf = st.scratch.setdefault(("amax_all", ins.t[1]), torch.empty(world, keys.shape[0], dtype=torch.int64, device=self.device))
+        dist.all_gather_into_tensor(buf.view(-1), keys.contiguous())
+        native.call("plow_argmax_fin", out, buf, st.samples, world)
+
+    def _ext_xgather(self, st, ins):
+        """out[:, r*width:(r+1)*width] = rank r's block (full logits for the host sampler)."""
+        import torch.distributed as dist
+        out, local = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])
+        width, world = ins.i[0], ins.i[1]
+        buf = st.scratch.setdefault(("xg", ins.t[1]), torch.empty(world, local.shape[0], width, dtype=local.dtype, device=self.device))
+        dist.all_gather_into_tensor(buf.view(-1), local.contiguous().view(-1))
+        out[:local.shape[0]].view(local.shape[0], world, width).copy_(buf.permute(1, 0, 2))
 
     # -- MLA
     def _mla_prep(self, layer: int, wkv_b_h: int, heads: int, kv_lora: int, nope: int, v_head: int):
@@ -582,6 +604,8 @@ class GpuEngine(EngineBase):
 
             def eligible(j):
                 ins = st.prog.insts[j]
+                if ins.op == Op.ARGMAX and ins.i[1]:
+                    return False        # packed-key variant (vocabulary-sharded lm_head) is a role kernel
                 outs = [ins.t[0]] + ([ins.t[4]] if ins.op == Op.ADD_NORM else [])
                 if any(h != pk.T_NONE and self._wants_q(st, h) for h in outs):
                     return False        # the role kernel emits the e4m3 twin in the same pass
