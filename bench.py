@@ -88,6 +88,7 @@ def main() -> int:
     ap.add_argument("--batch-per-gpu", type=int, default=64)
     ap.add_argument("--ttft-prompts", type=int, default=2)
     ap.add_argument("--prefill-chunk", type=int, default=2048, help="rows of the prefill program used for the TTFT prompts")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the NCCL-arm run that follows the timed region at N > 1")
     ap.add_argument("--init", default="scaled", choices=["scaled", "plain"],
                     help="scaled: depth-scaled random init (balanced routing, like a trained checkpoint); plain: N(0,0.02) everywhere")
     args = ap.parse_args()
@@ -135,7 +136,7 @@ def main() -> int:
     # ---- synthetic live requests: contexts uniform in [1024, 8192], random e4m3 latent rows ----
     rng = np.random.default_rng(7 + rank)
     ctx = rng.integers(1024, 8193, size=B)
-    total_steps = W + args.steps
+    total_steps = 3 * W + 2 * args.steps + 2
     for s in range(B):
         eng.pool.begin(s, [0])
         eng.tokens[s] = [0] * int(ctx[s])
@@ -203,43 +204,6 @@ def main() -> int:
     torch.cuda.synchronize()
     launches_per_step = native.LAUNCHES["n"] - n0
 
-    if os.environ.get("PLOW_EP_TRACE") and comm is not None:
-        # debug aid: re-capture the decode graph with device-side trace marks in the EP kernels
-        comm.device_trace(True)
-        import ctypes as _C
-        _lib = native.cuda_lib()
-        _lib.plow_gemm_set_trace.argtypes = [_C.c_void_p]
-        gtr = torch.zeros(64 * 8, dtype=torch.int64, device=dev)
-        _lib.plow_gemm_set_trace(gtr.data_ptr())
-        st.graph = None
-        one_step(W)
-        comm._trace.zero_()
-        barrier()
-        one_step(W)
-        torch.cuda.synchronize()
-        rows = comm.device_trace_rows()
-        comm.device_trace(False)
-        _lib.plow_gemm_set_trace(None)
-        gt = gtr.cpu()
-        print(f"rank {rank}: last gated GEMM waited {(int(gt[15]) - int(gt[7])) / 1e3:.1f} us (counter {int(gt[23])} -> target {int(gt[31])})", file=sys.stderr)
-        st.graph = None
-        if rank == 0:
-            import collections
-            seg = collections.defaultdict(list)
-            names = {(1, 2): "counts", (2, 3): "gap_counts_push", (3, 4): "push_wait_counts", (4, 5): "push_copy", (5, 6): "gemms(+wait)",
-                     (6, 7): "gap_yready_combine", (7, 8): "combine_wait_y", (8, 9): "combine_pull", (9, 1): "rest_of_layer"}
-            for (ta, a_), (tb, b_) in zip(rows, rows[1:]):
-                seg[names.get((ta, tb), f"{ta}->{tb}")].append((b_ - a_) / 1e3)
-            print("EP device trace us (rank 0, mean over layers):", json.dumps({k: round(sum(v) / len(v), 1) for k, v in seg.items()}), file=sys.stderr)
-    if os.environ.get("PLOW_EP_TIMING") and comm is not None:
-        # debug aid: one eager walk of the decode program with CUDA events around the EP phases
-        comm.timing = {}
-        barrier()
-        eng._run_insts(st)
-        rep = comm.timing_report()
-        comm.timing = None
-        if rank == 0:
-            print("EP phase us (rank 0):", json.dumps(rep), file=sys.stderr)
     barrier()
     sampler.mark()
     t0 = time.perf_counter()
@@ -250,6 +214,23 @@ def main() -> int:
     barrier()
     wall = time.perf_counter() - t0
     clocks = sampler.stop()
+
+    # ---- same-box baseline: the NCCL arm of the same model (all-gather + local experts + reduce-scatter, NCCL at its
+    # defaults), same engine, weights, requests, warm-up and step count; only the expert-parallel layer differs ----
+    base = None
+    if comm is not None and args.impl == "fused" and not args.no_baseline:
+        comm.impl = "nccl"
+        st.graph = None
+        for k in range(W):
+            one_step(W + args.steps + k)
+        barrier()
+        b_ms = [one_step(2 * W + args.steps + k).device_ms for k in range(args.steps)]
+        barrier()
+        comm.impl = "fused"
+        st.graph = None
+        bt = torch.tensor([float(np.sum(b_ms))], dtype=torch.float64, device=dev)
+        dist.all_reduce(bt, op=dist.ReduceOp.MAX)
+        base = float(bt.item())
     route = None
     if comm is not None and getattr(comm, "grp_off", None) is not None:
         go = comm.grp_off.cpu().numpy().astype(np.int64)       # rows per local expert in the last MoE layer
@@ -279,7 +260,9 @@ def main() -> int:
         hbm, src = hwspec.lookup("b200").hbm_peak()
         out = {
             "metric": METRIC, "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": W,
-            "ms_per_step": round(dev_total / args.steps, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": round(dev_total / args.steps, 3), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (None if base is None else {"impl": "nccl", "value": round(tokens / (base / 1e3), 1),
+                                                       "ms_per_step": round(base / args.steps, 3), "ratio": round(base / dev_total, 4)}),
             "dtype": "fp8 (e4m3 block-scaled weights, e4m3 latent KV, bf16 activations)", "data": ("synthetic: random token ids, random e4m3 latent cache, random-init weights "
                      + ("(N(0,0.02); unit-variance embeddings and residual-output projections scaled by 1/(2L), which keeps "
                         "expert routing balanced as in a trained checkpoint)" if args.init == "scaled" else "(N(0,0.02) everywhere; routing collapses with depth)")),

@@ -69,6 +69,8 @@ __device__ __forceinline__ bool wait_ge(const uint32_t* p, uint32_t target, unsi
 }
 
 __global__ void ep_counts_kernel(EpArgs a, const int2* table, int n_pairs, int* cursor) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   extern __shared__ int hist[];
   if (threadIdx.x == 0) trace_mark(a, 1);
   for (int e = threadIdx.x; e < a.E; e += blockDim.x) { hist[e] = 0; cursor[e] = 0; }   // cursor[E] is the push kernel's CTA counter
@@ -88,8 +90,12 @@ __global__ void ep_counts_kernel(EpArgs a, const int2* table, int n_pairs, int* 
 }
 
 // grid: any; 256 threads.  One warp per pair.
+// shared_rows > 0: the shared expert is stacked behind this rank's routed experts as group e_local; its rows are this
+// rank's own first `shared_rows` tokens, copied (locally) behind the routed rows, and grp_off / tile_prefix get one more entry.
 __global__ void ep_push_kernel(EpArgs a, const int2* table, int n_pairs, int top_k, const uint8_t* xq, const float* sx,
-                               int ld_sx, int* cursor, int* grp_off, int* tile_prefix, int* pair_dest) {
+                               int ld_sx, int* cursor, int* grp_off, int* tile_prefix, int* pair_dest, int shared_rows) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   extern __shared__ int sm[];                 // cnt [W][E], base [E]
   int* cnt = sm;
   int* base = sm + a.W * a.E;
@@ -126,11 +132,29 @@ __global__ void ep_push_kernel(EpArgs a, const int2* table, int n_pairs, int top
       off += c; tiles += (c + 127) >> 7;
     }
     grp_off[a.e_local] = off; tile_prefix[a.e_local] = tiles;
-    if (off > a.Rmax) atomicCAS(a.status, 0, PLOW_ERR_BOUNDS);
+    if (shared_rows > 0) { grp_off[a.e_local + 1] = off + shared_rows; tile_prefix[a.e_local + 1] = tiles + ((shared_rows + 127) >> 7); }
+    if (off + shared_rows > a.Rmax) atomicCAS(a.status, 0, PLOW_ERR_BOUNDS);
+  }
+  __shared__ int routed_rows;     // rows this rank receives for its routed experts (same value in every CTA)
+  if (threadIdx.x == 0) {
+    int off = 0;
+    for (int el = 0; el < a.e_local; ++el)
+      for (int s = 0; s < a.W; ++s) off += cnt[s * a.E + a.me * a.e_local + el];
+    routed_rows = off;
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   const int KB = a.H / 128;
+  if (routed_rows + shared_rows <= a.Rmax) {
+    for (int t = blockIdx.x * wpb + warp; t < shared_rows; t += gridDim.x * wpb) {
+      const int row = routed_rows + t;
+      const uint4* src = reinterpret_cast<const uint4*>(xq + static_cast<size_t>(t) * a.H);
+      uint4* dst = reinterpret_cast<uint4*>(a.peer[a.me] + a.L.recv_x + static_cast<size_t>(row) * a.H);
+      for (int i = lane; i < a.H / 16; i += 32) dst[i] = src[i];
+      float* dsx = reinterpret_cast<float*>(a.peer[a.me] + a.L.recv_sx);
+      for (int kb = lane; kb < KB; kb += 32) dsx[static_cast<size_t>(kb) * a.Rmax + row] = sx[static_cast<size_t>(kb) * ld_sx + t];
+    }
+  }
   for (int p = blockIdx.x * wpb + warp; p < n_pairs; p += gridDim.x * wpb) {
     const int e = table[p].x;
     const int d = e / a.e_local;
@@ -169,14 +193,20 @@ __global__ void ep_push_kernel(EpArgs a, const int2* table, int n_pairs, int top
 }
 
 __global__ void ep_y_ready_kernel(EpArgs a) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   if (threadIdx.x == 0) trace_mark(a, 6);
   __threadfence_system();
   const uint32_t ep = *a.epoch;
   if (threadIdx.x < a.W) st_release_sys(reinterpret_cast<uint32_t*>(a.peer[threadIdx.x] + a.L.y_flag) + a.me * 32, ep);
 }
 
+// shared_base != NULL: the shared expert ran as the last group of this rank's grouped GEMM; its output row of token t
+// is row *shared_base + t of this rank's own y buffer (`shared` is ignored).
 __global__ void ep_combine_kernel(EpArgs a, __nv_bfloat16* out, const __nv_bfloat16* shared, const int2* table,
-                                  const int* pair_dest, int top_k) {
+                                  const int* pair_dest, int top_k, const int* shared_base) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   __shared__ int fail;
   if (threadIdx.x == 0) fail = 0;
   __syncthreads();
@@ -211,6 +241,7 @@ __global__ void ep_combine_kernel(EpArgs a, __nv_bfloat16* out, const __nv_bfloa
       }
     }
     float acc[8];
+    if (shared_base) shared = reinterpret_cast<const __nv_bfloat16*>(a.peer[a.me] + a.L.y) + static_cast<size_t>(*shared_base) * a.H;
     if (shared) {
       const uint4 sv = *reinterpret_cast<const uint4*>(shared + static_cast<size_t>(t) * a.H + i);
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&sv);
@@ -241,6 +272,8 @@ __global__ void ep_combine_kernel(EpArgs a, __nv_bfloat16* out, const __nv_bfloa
 // A wait that nothing satisfies: used by the failure-detection test to exercise the deadline path
 // without faulting or hanging anything.
 __global__ void ep_wait_probe_kernel(const uint32_t* flag, uint32_t target, unsigned long long deadline_ns, int* status) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   if (threadIdx.x == 0 && !wait_ge(flag, target, deadline_ns)) atomicCAS(status, 0, PLOW_ERR_PEER_WAIT);
 }
 
@@ -254,33 +287,33 @@ extern "C" {
 // epoch pointer, status pointer, u64 deadline (see plow_b200/parallel/ep.py for the ctypes mirror).
 int plow_ep_counts(const void* args, const void* table, int n_pairs, int* cursor, void* st) {
   const EpArgs& a = *static_cast<const EpArgs*>(args);
-  ep_counts_kernel<<<1, 1024, a.E * 4, reinterpret_cast<cudaStream_t>(st)>>>(a, static_cast<const int2*>(table), n_pairs, cursor);
+  plow::launch_pdl(ep_counts_kernel, dim3(1), dim3(1024), a.E * 4, reinterpret_cast<cudaStream_t>(st), a, static_cast<const int2*>(table), n_pairs, cursor);
   return ok();
 }
 int plow_ep_push(const void* args, const void* table, int n_pairs, int top_k, const void* xq, const float* sx, int ld_sx,
-                 int* cursor, int* grp_off, int* tile_prefix, int* pair_dest, int n_cta, void* st) {
+                 int* cursor, int* grp_off, int* tile_prefix, int* pair_dest, int n_cta, int shared_rows, void* st) {
   const EpArgs& a = *static_cast<const EpArgs*>(args);
-  ep_push_kernel<<<n_cta, 256, (a.W + 1) * a.E * 4, reinterpret_cast<cudaStream_t>(st)>>>(
+  plow::launch_pdl(ep_push_kernel, dim3(n_cta), dim3(256), (a.W + 1) * a.E * 4, reinterpret_cast<cudaStream_t>(st), 
       a, static_cast<const int2*>(table), n_pairs, top_k, static_cast<const uint8_t*>(xq), sx, ld_sx, cursor, grp_off,
-      tile_prefix, pair_dest);
+      tile_prefix, pair_dest, shared_rows);
   return ok();
 }
 int plow_ep_y_ready(const void* args, void* st) {
   const EpArgs& a = *static_cast<const EpArgs*>(args);
-  ep_y_ready_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(st)>>>(a);
+  plow::launch_pdl(ep_y_ready_kernel, dim3(1), dim3(32), 0, reinterpret_cast<cudaStream_t>(st), a);
   return ok();
 }
 int plow_ep_combine(const void* args, void* out, const void* shared, const void* table, const int* pair_dest, int T, int top_k,
-                    void* st) {
+                    const int* shared_base, void* st) {
   const EpArgs& a = *static_cast<const EpArgs*>(args);
   if (top_k > 16 || a.H % 8) return -1;
-  ep_combine_kernel<<<dim3(T, (a.H / 8 + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(st)>>>(a, static_cast<__nv_bfloat16*>(out),
+  plow::launch_pdl(ep_combine_kernel, dim3(T, (a.H / 8 + 255) / 256), dim3(256), 0, reinterpret_cast<cudaStream_t>(st), a, static_cast<__nv_bfloat16*>(out),
                                                                     static_cast<const __nv_bfloat16*>(shared),
-                                                                    static_cast<const int2*>(table), pair_dest, top_k);
+                                                                    static_cast<const int2*>(table), pair_dest, top_k, shared_base);
   return ok();
 }
 int plow_wait_probe(const void* flag, unsigned int target, unsigned long long deadline_ns, int* status, void* st) {
-  ep_wait_probe_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(st)>>>(static_cast<const uint32_t*>(flag), target, deadline_ns, status);
+  plow::launch_pdl(ep_wait_probe_kernel, dim3(1), dim3(32), 0, reinterpret_cast<cudaStream_t>(st), static_cast<const uint32_t*>(flag), target, deadline_ns, status);
   return ok();
 }
 

@@ -29,6 +29,8 @@ struct AgArgs {
 };
 
 __global__ void ag_push_kernel(const AgArgs a, const uint8_t* src, int ld_src_bytes) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const int units = a.row_bytes / 16;
   const long long total = static_cast<long long>(a.band_rows) * units;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -66,7 +68,7 @@ int plow_ag_push(const void* const* peers, uint64_t x_ofs, uint64_t ctr_ofs, voi
   const long long total = static_cast<long long>(band_rows) * (row_bytes / 16);
   int grid = static_cast<int>((total + 255) / 256);
   if (grid > 64) grid = 64;
-  ag_push_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a, static_cast<const uint8_t*>(src), ld_src_bytes);
+  plow::launch_pdl(ag_push_kernel, dim3(grid), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), a, static_cast<const uint8_t*>(src), ld_src_bytes);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }

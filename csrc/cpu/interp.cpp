@@ -523,6 +523,9 @@ void op_moe(const Ctx& c) {
   const float* w2 = (const float*)c.T(4);      // [E][H][F]
   const float* shared = (const float*)c.T(5);
   const int K = c.in->i[2], F = c.in->i[3];
+  // i[6]: the shared expert is stacked behind the e_local routed ones and applies to every row with gate 1;
+  // it is added first, where the separately computed shared output would have been
+  const int shared_group = c.in->i[6] ? c.in->i[1] : -1;
   const PlowTensorEnt& te = c.e->pkt->tensors[c.in->t[0]];
   const int H = int(te.dims[1]);
   std::vector<float> glu(F), acc(H);
@@ -531,10 +534,13 @@ void op_moe(const Ctx& c) {
   for (int64_t r = a; r < b; ++r) {
     const float* x = h + r * H;
     for (int j = 0; j < H; ++j) acc[j] = shared ? shared[r * H + j] : 0.f;
-    for (int k = 0; k < K; ++k) {                // fixed slot order
-      const int e = table[(r * K + k) * 2];
-      float gate;
-      std::memcpy(&gate, &table[(r * K + k) * 2 + 1], 4);
+    for (int k = shared_group >= 0 ? -1 : 0; k < K; ++k) {                // fixed slot order
+      int e = shared_group;
+      float gate = 1.0f;
+      if (k >= 0) {
+        e = table[(r * K + k) * 2];
+        std::memcpy(&gate, &table[(r * K + k) * 2 + 1], 4);
+      }
       if (e < 0) continue;
       const float* wg = w1 + int64_t(e) * 2 * F * H;
       const float* wu = wg + int64_t(F) * H;

@@ -62,6 +62,8 @@ template <int HD> struct GqaCfg {
 __global__ void gqa_build_items(const int* seq, const int* pos, int rows, int tq, int nkv, int window,
                                 int tiles_per_split, int max_splits, GqaItem* items, int* n_items,
                                 int* row_ns, int cap, int* status) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += gridDim.x * blockDim.x) {
     if (pos[r] < 0) { row_ns[r] = 0; continue; }
     const bool start = (r % tq == 0) || pos[r - 1] < 0 || seq[r] != seq[r - 1] || pos[r] != pos[r - 1] + 1;
@@ -88,6 +90,8 @@ template <int HD>
 __global__ void __launch_bounds__(kGqaThreads, 1)
 gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   using Cfg = GqaCfg<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -358,6 +362,8 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
 // out[row][head][:] = sum_s 2^(lse_s - gm) opart_s / sum_s 2^(lse_s - gm) for rows that were split.
 __global__ void gqa_merge_kernel(const float* opart, const float* lse, const int* row_ns, int nq, int max_splits,
                                  int hd, __nv_bfloat16* out) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const int row = blockIdx.x, head = blockIdx.y;
   const int ns = row_ns[row];
   if (ns <= 1) return;
@@ -383,6 +389,8 @@ __global__ void rope_kv_kernel(__nv_bfloat16* q_out, const __nv_bfloat16* qkv, i
                                const float* rope_tab, const int* pos, const int* seq, const int* page_table,
                                int max_pages, int rows, int nq, int nkv, int hd, int rot, int pair_mode,
                                int plus_one, float eps, __nv_bfloat16* gate_out) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   extern __shared__ float rk_smem[];
   const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = nq + 2 * nkv;
@@ -451,12 +459,9 @@ int launch_gqa(const GqaArgs& a, const void* q, const void* kc, const void* vc, 
   if (r) return 1200 + r;
   r = make_tmap_3d(&tv, vc, 2, HD, a.nkv, static_cast<uint64_t>(n_pages) * kGqaPage, HD * 2, static_cast<uint64_t>(a.nkv) * HD * 2, 1, kGqaPage, 128);
   if (r) return 1300 + r;
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(gqa_attn_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem) != cudaSuccess) return 3000;
-    attr = true;
-  }
-  gqa_attn_kernel<HD><<<grid, kGqaThreads, Cfg::kSmem, stream>>>(a, tq, tk, tv);
+  static DeviceOnce attr;
+  if (ensure_smem(attr, gqa_attn_kernel<HD>, Cfg::kSmem) != cudaSuccess) return 3000;
+  plow::launch_pdl(gqa_attn_kernel<HD>, dim3(grid), dim3(kGqaThreads), Cfg::kSmem, stream, a, tq, tk, tv);
   return 0;
 }
 
@@ -479,7 +484,7 @@ int plow_gqa_attention(const void* q, const void* kc, const void* vc, int64_t n_
   if (hd != 128 && hd != 256) return -3;
   const int tq = 128 / group;
   cudaMemsetAsync(n_items, 0, sizeof(int), stream);
-  gqa_build_items<<<(rows + 255) / 256, 256, 0, stream>>>(seq, pos, rows, tq, nkv, window, tiles_per_split, max_splits,
+  plow::launch_pdl(gqa_build_items, dim3((rows + 255) / 256), dim3(256), 0, stream, seq, pos, rows, tq, nkv, window, tiles_per_split, max_splits,
                                                          static_cast<GqaItem*>(items), n_items, row_ns, item_cap, status);
   GqaArgs a;
   a.page_table = page_table; a.pos = pos; a.items = static_cast<const GqaItem*>(items); a.n_items = n_items;
@@ -491,7 +496,7 @@ int plow_gqa_attention(const void* q, const void* kc, const void* vc, int64_t n_
   int r = hd == 128 ? launch_gqa<128>(a, q, kc, vc, n_pages, grid, stream) : launch_gqa<256>(a, q, kc, vc, n_pages, grid, stream);
   if (r) return r;
   if (max_splits > 1)
-    gqa_merge_kernel<<<dim3(rows, nq), 128, 0, stream>>>(opart, lse, row_ns, nq, max_splits, hd, static_cast<__nv_bfloat16*>(out));
+    plow::launch_pdl(gqa_merge_kernel, dim3(rows, nq), dim3(128), 0, stream, opart, lse, row_ns, nq, max_splits, hd, static_cast<__nv_bfloat16*>(out));
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }
@@ -506,8 +511,7 @@ int plow_rope_kv(void* q_out, const void* qkv, int ld_qkv, void* kc, void* vc, c
   if (rows <= 0 || hd % 8 || rot > hd || rot % 2) return -1;
   const long long items = static_cast<long long>(rows) * (nq + 2 * nkv);
   const int wpb = 8;
-  rope_kv_kernel<<<static_cast<unsigned>((items + wpb - 1) / wpb), wpb * 32, wpb * hd * sizeof(float),
-                   reinterpret_cast<cudaStream_t>(stream_)>>>(
+  plow::launch_pdl(rope_kv_kernel, dim3(static_cast<unsigned>((items + wpb - 1) / wpb)), dim3(wpb * 32), wpb * hd * sizeof(float), reinterpret_cast<cudaStream_t>(stream_), 
       static_cast<__nv_bfloat16*>(q_out), static_cast<const __nv_bfloat16*>(qkv), ld_qkv, static_cast<__nv_bfloat16*>(kc),
       static_cast<__nv_bfloat16*>(vc), static_cast<const __nv_bfloat16*>(qn), static_cast<const __nv_bfloat16*>(kn),
       rope_tab, pos, seq, page_table, max_pages, rows, nq, nkv, hd, rot, pair_mode, plus_one, eps,

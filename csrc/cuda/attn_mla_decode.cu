@@ -58,7 +58,7 @@ struct MlaArgs {
   __nv_bfloat16* opart;     // [T][max_splits][heads][512]
   float* lse;               // [T][max_splits][heads]   (log2 domain)
   int* status;
-  long long* trace;         // optional phase timestamps of CTA 0 (debug aid), NULL when off
+  long long* trace;         // phase timestamps of CTA 0; only read by builds with -DPLOW_DEVICE_TRACE
   int T, max_pages, max_splits;
   float scale_log2e;        // softmax scale * log2(e)
 };
@@ -68,6 +68,8 @@ __global__ void mla_build_items(const int* kvlen, int T, int tiles_per_split, in
                                 MlaItem* items, int* n_items) {
   // one thread per request: split count, then its offset as the sum of the counts before it
   extern __shared__ int cnt[];
+  pdl_launch_dependents();
+  pdl_wait();
   for (int r = threadIdx.x; r < T; r += blockDim.x) {
     int per;
     const int tiles = (kvlen[r] + kMlaPage - 1) / kMlaPage;
@@ -117,6 +119,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -141,6 +144,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
   const uint32_t tm_s = tmem_base;          // S buffers: columns [0,64) and [64,128); P aliases the first 16 of each
   const uint32_t tm_o = tmem_base + 128;    // O: 256 columns
   const uint32_t tm_q = tmem_base + 384;    // latent Q as e4m3 A operand: 128 columns (4 bytes of K per column)
+  pdl_wait();     // work list, queries and this step's cache rows come from the kernels before this one
   const int n_items = *a.n_items;
 
   if (warp == 0) {
@@ -223,7 +227,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
           tc_mma_f8_ts(tm_o, pt + 8, umma_desc_mn128(va + 4096, 8192, 1024), idesc_pv, 1);
           tc_commit(&kv_empty[s]);
           tc_commit(&pv_done[ti & 1]);
-          if (a.trace && blockIdx.x == 0 && ti < 64) a.trace[ti * 8 + 7] = clock64();
+          PLOW_TRACE(if (a.trace && blockIdx.x == 0 && ti < 64) a.trace[ti * 8 + 7] = clock64();)
         }
         kv_it += w.ntiles;
         tile_it += w.ntiles;
@@ -276,8 +280,8 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
       }
       for (int i = 0; i < w.ntiles; ++i) {
         const uint32_t ti = tile_it + i;
-        const bool tr = a.trace && blockIdx.x == 0 && warp == 2 && lane == 0 && ti < 64;
-        if (tr) a.trace[ti * 8 + 0] = clock64();
+        PLOW_TRACE(const bool tr = a.trace && blockIdx.x == 0 && warp == 2 && lane == 0 && ti < 64;)
+        PLOW_TRACE(if (tr) a.trace[ti * 8 + 0] = clock64();)
         // (a) per-token scales (they arrived with the KV tile, usually long before S is ready)
         const int s = (kv_it + i) % kMlaStages;
         if (!mbar_wait(&kv_full[s], ((kv_it + i) / kMlaStages) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); ok = false; break; }
@@ -294,7 +298,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
         // (b) scores
         if (!mbar_wait(&s_full[ti & 1], (ti >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
         tc_fence_after();
-        if (tr) a.trace[ti * 8 + 1] = clock64();
+        PLOW_TRACE(if (tr) a.trace[ti * 8 + 1] = clock64();)
         uint32_t sv[32];
         tmem_ld32(tm_s + lane_addr + (ti & 1) * 64 + ch * 32, sv);
         tmem_ld_wait();
@@ -315,10 +319,10 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
         }
         float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
         float omx, unused0;
-        if (tr) a.trace[ti * 8 + 2] = clock64();
+        PLOW_TRACE(if (tr) a.trace[ti * 8 + 2] = clock64();)
         if (!exchange(mx, 0.f, omx, unused0)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
         mx = fmaxf(mx, omx);
-        if (tr) a.trace[ti * 8 + 3] = clock64();
+        PLOW_TRACE(if (tr) a.trace[ti * 8 + 3] = clock64();)
         // Lazy rescaling with one running offset M = m + log2(SK): probabilities are formed as
         // p' = 2^(x - M) * sk <= 2^kTau * sk / SK <= 2^kTau, inside e4m3 range, and l' = sum 2^(x - M)
         // is kept with the same offset, so O / l' needs no further correction at the end.  m is
@@ -392,17 +396,17 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
           pk[j >> 2] = *reinterpret_cast<uint32_t*>(&q4);
         }
         l += suma + sumb;
-        if (tr) a.trace[ti * 8 + 4] = clock64();
+        PLOW_TRACE(if (tr) a.trace[ti * 8 + 4] = clock64();)
         // P (e4m3, 4 tokens per 32-bit column) over the first 16 columns of the S buffer it came
         // from; this thread owns tokens [32 ch, 32 ch + 32) = columns [8 ch, 8 ch + 8).  The
         // partner thread finished reading its S columns before the exchange above completed.
         tmem_st8(tm_s + lane_addr + (ti & 1) * 64 + ch * 8, pk);
         tmem_st_wait();
-        if (tr) a.trace[ti * 8 + 5] = clock64();
+        PLOW_TRACE(if (tr) a.trace[ti * 8 + 5] = clock64();)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[ti & 1]);
-        if (tr) a.trace[ti * 8 + 6] = clock64();
+        PLOW_TRACE(if (tr) a.trace[ti * 8 + 6] = clock64();)
       }
       if (!ok) break;
       // ---- finalize this item: O * SK / l, log-sum-exp in the log2 domain
@@ -451,6 +455,8 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
 // Merge the splits of each (request, head): out[h][t][:] = sum_s 2^(lse_s - LSE) * opart_s.
 __global__ void mla_merge_kernel(const __nv_bfloat16* opart, const float* lse, const int* kvlen, int T,
                                  int max_splits, int tiles_per_split, __nv_bfloat16* out /*[heads][T][512]*/) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const int tiles = (kvlen[t] + kMlaPage - 1) / kMlaPage;
   int per_unused;
@@ -474,12 +480,27 @@ __global__ void mla_merge_kernel(const __nv_bfloat16* opart, const float* lse, c
 
 }  // namespace plow
 
+#ifdef PLOW_DEVICE_TRACE
 static long long* g_mla_trace = nullptr;
+#endif
 
 extern "C" {
 
-// Debug aid: device buffer of 64*8 int64 that CTA 0 fills with clock64() phase stamps (NULL = off).
+#ifdef PLOW_DEVICE_TRACE
+// Builds with -DPLOW_DEVICE_TRACE only: device buffer of 64*8 int64 that CTA 0 fills with clock64() phase stamps.
 void plow_mla_set_trace(void* p) { g_mla_trace = static_cast<long long*>(p); }
+#endif
+
+// The work list depends only on the rows' KV lengths, which are the same for every layer of a step: the engine
+// builds it once per step with this entry and passes build_items = 0 to plow_mla_decode for every layer.
+int plow_mla_build_items(const int* kvlen, int T, int tiles_per_split, int max_splits, void* items, int* n_items, void* stream_) {
+  using namespace plow;
+  if (T <= 0 || max_splits <= 0 || tiles_per_split <= 0) return -1;
+  cudaError_t e = launch_pdl(mla_build_items, dim3(1), dim3(256), T * sizeof(int), reinterpret_cast<cudaStream_t>(stream_),
+                             kvlen, T, tiles_per_split, max_splits, static_cast<MlaItem*>(items), n_items);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
+}
 
 // Scratch the caller provides: items (8 ints per item, capacity 2*T*max_splits), n_items (1 int),
 // opart bf16 [T][max_splits][128][512], lse f32 [T][max_splits][128].
@@ -489,7 +510,7 @@ void plow_mla_set_trace(void* p) { g_mla_trace = static_cast<long long*>(p); }
 int plow_mla_decode(const void* q8, const float* sq, const void* kv, const float* kv_scale, const float* kv_smax, int64_t n_pages,
                     const int* page_table, int max_pages, const int* slot_of, const int* kvlen, int T,
                     int tiles_per_split, int max_splits, void* items, int* n_items, void* opart, float* lse,
-                    void* out, float softmax_scale, int* status, void* stream_) {
+                    void* out, float softmax_scale, int build_items, int* status, void* stream_) {
   using namespace plow;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (T <= 0 || max_splits <= 0 || tiles_per_split <= 0) return -1;
@@ -500,26 +521,30 @@ int plow_mla_decode(const void* q8, const float* sq, const void* kv, const float
   if (r) return 1200 + r;
   r = make_tmap_2d(&tkvr, kv, 1, static_cast<uint64_t>(n_pages) * kMlaPage, kMlaRow, kMlaRow, kMlaPage, 64);
   if (r) return 1300 + r;
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem) != cudaSuccess) return 3000;
-    attr = true;
-  }
-  mla_build_items<<<1, 256, T * sizeof(int), stream>>>(kvlen, T, tiles_per_split, max_splits, static_cast<MlaItem*>(items), n_items);
+  static DeviceOnce attr;
+  if (ensure_smem(attr, mla_decode_kernel, kMlaSmem) != cudaSuccess) return 3000;
+  if (build_items)
+    launch_pdl(mla_build_items, dim3(1), dim3(256), T * sizeof(int), stream, kvlen, T, tiles_per_split, max_splits,
+               static_cast<MlaItem*>(items), n_items);
   MlaArgs a;
   a.q8 = static_cast<const uint8_t*>(q8); a.sq = sq; a.kv_scale = kv_scale; a.kv_smax = kv_smax; a.page_table = page_table; a.slot_of = slot_of; a.kvlen = kvlen;
   a.items = static_cast<const MlaItem*>(items); a.n_items = n_items;
-  a.opart = static_cast<__nv_bfloat16*>(opart); a.lse = lse; a.status = status; a.trace = g_mla_trace;
+  a.opart = static_cast<__nv_bfloat16*>(opart); a.lse = lse; a.status = status;
+#ifdef PLOW_DEVICE_TRACE
+  a.trace = g_mla_trace;
+#else
+  a.trace = nullptr;
+#endif
   a.T = T; a.max_pages = max_pages; a.max_splits = max_splits;
   a.scale_log2e = softmax_scale * 1.4426950408889634f;
   int grid = sm_count();
   const int cap = 2 * T * max_splits;
   if (cap < grid) grid = cap;
-  mla_decode_kernel<<<grid, kMlaThreads, kMlaSmem, stream>>>(a, tqr, tkv, tkvr);
-  if (out)   // NULL: the caller merges the splits itself (plow_mla_fold does it while folding W_uv)
-    mla_merge_kernel<<<dim3(T, kMlaHeads), 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(opart), lse, kvlen, T,
-                                                            max_splits, tiles_per_split, static_cast<__nv_bfloat16*>(out));
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(mla_decode_kernel, dim3(grid), dim3(kMlaThreads), kMlaSmem, stream, a, tqr, tkv, tkvr);
+  if (e == cudaSuccess && out)   // NULL: the caller merges the splits itself (plow_mla_fold does it while folding W_uv)
+    e = launch_pdl(mla_merge_kernel, dim3(T, kMlaHeads), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(opart),
+                   static_cast<const float*>(lse), kvlen, T, max_splits, tiles_per_split, static_cast<__nv_bfloat16*>(out));
+  if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }
 

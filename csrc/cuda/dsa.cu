@@ -29,6 +29,8 @@ __global__ void dsa_k_write_kernel(uint8_t* cache, float* cache_scale, const __n
                                    const float* gamma, const float* beta, const float* rope_tab, const int* pos,
                                    const int* seq, const int* page_table, int max_pages, int rows, int rot,
                                    int pair_mode, float eps) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   __shared__ float buf[8][kIdxDim];
   const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.x * 8 + wib;
@@ -86,6 +88,8 @@ __global__ void dsa_k_write_kernel(uint8_t* cache, float* cache_scale, const __n
 // weight are folded into w_out[r][h] = w[r][h] * scale so the score kernel multiplies once.
 __global__ void dsa_q_prep_kernel(uint8_t* q8, float* w_out, const __nv_bfloat16* q, int ld_q, const float* w, int ld_w,
                                   const float* rope_tab, const int* pos, int rows, int rot, int pair_mode) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   __shared__ float buf[8][kIdxDim];
   const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x * 8 + wib;
@@ -127,6 +131,8 @@ __global__ void __launch_bounds__(128)
 dsa_score_kernel(float* scores, int ld_scores, const float* w, const float* kscale, const int* pos, const int* seq,
                  const int* page_table, int max_pages, int* status, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_q) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const int r = blockIdx.y, t0 = blockIdx.x * 128;
   const int len = pos[r] + 1;
   if (t0 >= len) return;
@@ -206,6 +212,8 @@ __device__ __forceinline__ unsigned long long dsa_key(float s, int idx) {
 // One CTA per row.  Keys are unique (the index is part of the key), so exactly top_k survive.
 __global__ void __launch_bounds__(1024)
 dsa_topk_kernel(int* sel, const float* scores, int ld_scores, const int* pos, int top_k) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   __shared__ uint32_t hist[256];
   __shared__ uint32_t sh_digit, sh_above;
   __shared__ int scan[32];
@@ -269,6 +277,8 @@ dsa_topk_kernel(int* sel, const float* scores, int ld_scores, const int* pos, in
 __global__ void dsa_gather_kernel(uint8_t* ckv, float* cscale, float* csmax, int* clen, const int* sel, int top_k,
                                   const uint8_t* cache, const float* scale, const int* pos, const int* seq,
                                   const int* page_table, int max_pages, int rows, int row_bytes) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + wib;
   if (item >= static_cast<long long>(rows) * top_k) return;
@@ -299,7 +309,7 @@ int plow_dsa_k_write(void* cache, float* cache_scale, const void* k, int ld_k, c
                      int rows, int rot, int pair_mode, float eps, void* stream) {
   using namespace plow;
   if (rows <= 0 || rot > kIdxDim || rot % 2) return -1;
-  dsa_k_write_kernel<<<(rows + 7) / 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  plow::launch_pdl(dsa_k_write_kernel, dim3((rows + 7) / 8), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
       static_cast<uint8_t*>(cache), cache_scale, static_cast<const __nv_bfloat16*>(k), ld_k, gamma, beta, rope_tab, pos, seq,
       page_table, max_pages, rows, rot, pair_mode, eps);
   cudaError_t e = cudaGetLastError();
@@ -315,7 +325,7 @@ int plow_dsa_select(int* sel, float* scores, int ld_scores, void* q8, float* wq,
   using namespace plow;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (rows <= 0 || top_k <= 0 || max_len <= 0 || max_len > ld_scores || max_len > (1 << 20)) return -1;
-  dsa_q_prep_kernel<<<(rows * kIdxHeads + 7) / 8, 256, 0, stream>>>(static_cast<uint8_t*>(q8), wq, static_cast<const __nv_bfloat16*>(q),
+  plow::launch_pdl(dsa_q_prep_kernel, dim3((rows * kIdxHeads + 7) / 8), dim3(256), 0, stream, static_cast<uint8_t*>(q8), wq, static_cast<const __nv_bfloat16*>(q),
                                                                     ld_q, w, ld_w, rope_tab, pos, rows, rot, pair_mode);
   CUtensorMap tk, tq;
   int rc = make_tmap_2d(&tk, cache, 1, static_cast<uint64_t>(n_pages) * kIdxPage, kIdxDim, kIdxDim, kIdxPage, 128);
@@ -323,14 +333,11 @@ int plow_dsa_select(int* sel, float* scores, int ld_scores, void* q8, float* wq,
   rc = make_tmap_2d(&tq, q8, 1, static_cast<uint64_t>(rows) * kIdxHeads, kIdxDim, kIdxDim, kIdxHeads, 128);
   if (rc) return 1200 + rc;
   constexpr int kSmem = 1024 + 24576 + 64 + 256 + 64;
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(dsa_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return 3000;
-    attr = true;
-  }
-  dsa_score_kernel<<<dim3((max_len + 127) / 128, rows), 128, kSmem, stream>>>(scores, ld_scores, wq, cache_scale, pos, seq, page_table,
+  static DeviceOnce attr;
+  if (ensure_smem(attr, dsa_score_kernel, kSmem) != cudaSuccess) return 3000;
+  plow::launch_pdl(dsa_score_kernel, dim3((max_len + 127) / 128, rows), dim3(128), kSmem, stream, scores, ld_scores, wq, cache_scale, pos, seq, page_table,
                                                                             max_pages, status, tk, tq);
-  dsa_topk_kernel<<<rows, 1024, 0, stream>>>(sel, scores, ld_scores, pos, top_k);
+  plow::launch_pdl(dsa_topk_kernel, dim3(rows), dim3(1024), 0, stream, sel, scores, ld_scores, pos, top_k);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }
@@ -346,7 +353,7 @@ int plow_dsa_gather(void* ckv, float* cscale, float* csmax, int* clen, const int
   const size_t pages = static_cast<size_t>(rows) * (top_k / kIdxPage);
   cudaMemsetAsync(csmax, 0, pages * 4 * sizeof(float), stream);
   const long long items = static_cast<long long>(rows) * top_k;
-  dsa_gather_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
+  plow::launch_pdl(dsa_gather_kernel, dim3(static_cast<unsigned>((items + 7) / 8)), dim3(256), 0, stream, 
       static_cast<uint8_t*>(ckv), cscale, csmax, clen, sel, top_k, static_cast<const uint8_t*>(cache), scale, pos, seq,
       page_table, max_pages, rows, row_bytes);
   cudaError_t e = cudaGetLastError();

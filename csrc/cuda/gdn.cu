@@ -16,6 +16,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "launch.cuh"
+
 namespace {
 
 constexpr int kD = 128;          // head dim = threads per CTA
@@ -37,6 +39,8 @@ __global__ void __launch_bounds__(kD)
 gdn_kernel(__nv_bfloat16* out, float* conv_state, float* ssm_state, const __nv_bfloat16* qkvz, int ld_qkvz,
            const __nv_bfloat16* ba, int ld_ba, const float* conv_w, const float* a_log, const float* dt_bias,
            const int* pos, const int* seq, int rows, int hk, int hv, int conv) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const int r0 = blockIdx.x, h = blockIdx.y;
   if (pos[r0] < 0) return;
   if (r0 > 0 && pos[r0 - 1] >= 0 && seq[r0 - 1] == seq[r0] && pos[r0 - 1] + 1 == pos[r0]) return;   // not a run start
@@ -132,6 +136,8 @@ gdn_kernel(__nv_bfloat16* out, float* conv_state, float* ssm_state, const __nv_b
 // updating them from inside it would race with a CTA that has not read the old history yet.
 __global__ void gdn_conv_state_kernel(float* conv_state, const __nv_bfloat16* qkvz, int ld_qkvz, const int* pos, const int* seq,
                                       int rows, int C) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   constexpr int W = kConvMax;
   const int r0 = blockIdx.x;
   if (pos[r0] < 0) return;
@@ -156,6 +162,8 @@ __global__ void gdn_conv_state_kernel(float* conv_state, const __nv_bfloat16* qk
 // One warp per (row, head): out = RMSNorm(o) * gamma * SiLU(z).
 __global__ void gated_norm_kernel(__nv_bfloat16* out, const __nv_bfloat16* o, const __nv_bfloat16* z, int ld_z, int z_ofs,
                                   const float* gamma, int rows, int heads, int hd, float eps) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + wib;
   if (item >= static_cast<long long>(rows) * heads) return;
@@ -174,6 +182,8 @@ __global__ void gated_norm_kernel(__nv_bfloat16* out, const __nv_bfloat16* o, co
 
 // out = a * sigmoid(gate)   (gated full-attention layers of the hybrid model)
 __global__ void sigmoid_gate_kernel(__nv_bfloat16* out, const __nv_bfloat16* a, const __nv_bfloat16* gate, long long n) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < n) out[i] = __float2bfloat16(__bfloat162float(a[i]) / (1.0f + __expf(-__bfloat162float(gate[i]))));
 }
@@ -190,15 +200,12 @@ int plow_gdn(void* out, float* conv_state, float* ssm_state, const void* qkvz, i
              int hk, int hv, int head_dim, int conv, void* stream) {
   if (rows <= 0 || head_dim != kD || conv != kConvMax || hk <= 0 || hv % hk) return -1;
   constexpr int kSmem = (kD * (kD + 1) + 2 * kD + 8) * sizeof(float);
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(gdn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return 3000;
-    attr = true;
-  }
-  gdn_kernel<<<dim3(rows, hv), kD, kSmem, reinterpret_cast<cudaStream_t>(stream)>>>(
+  static plow::DeviceOnce attr;
+  if (plow::ensure_smem(attr, gdn_kernel, kSmem) != cudaSuccess) return 3000;
+  plow::launch_pdl(gdn_kernel, dim3(rows, hv), dim3(kD), kSmem, reinterpret_cast<cudaStream_t>(stream), 
       static_cast<__nv_bfloat16*>(out), conv_state, ssm_state, static_cast<const __nv_bfloat16*>(qkvz), ld_qkvz,
       static_cast<const __nv_bfloat16*>(ba), ld_ba, conv_w, a_log, dt_bias, pos, seq, rows, hk, hv, conv);
-  gdn_conv_state_kernel<<<rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  plow::launch_pdl(gdn_conv_state_kernel, dim3(rows), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
       conv_state, static_cast<const __nv_bfloat16*>(qkvz), ld_qkvz, pos, seq, rows, (2 * hk + hv) * kD);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
@@ -208,7 +215,7 @@ int plow_gated_norm(void* out, const void* o, const void* z, int ld_z, int z_ofs
                     int hd, float eps, void* stream) {
   if (rows <= 0) return -1;
   const long long items = static_cast<long long>(rows) * heads;
-  gated_norm_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  plow::launch_pdl(gated_norm_kernel, dim3(static_cast<unsigned>((items + 7) / 8)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
       static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(z), ld_z, z_ofs,
       gamma, rows, heads, hd, eps);
   cudaError_t e = cudaGetLastError();
@@ -217,7 +224,7 @@ int plow_gated_norm(void* out, const void* o, const void* z, int ld_z, int z_ofs
 
 int plow_sigmoid_gate(void* out, const void* a, const void* gate, int64_t n, void* stream) {
   if (n <= 0) return -1;
-  sigmoid_gate_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  plow::launch_pdl(sigmoid_gate_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
       static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(gate), n);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);

@@ -6,10 +6,16 @@ namespace plow {
 int gemm_dispatch_bf16(const PlowGemmDesc& d, cudaStream_t s);
 int gemm_dispatch_fp8(const PlowGemmDesc& d, cudaStream_t s);
 
+#ifdef PLOW_DEVICE_TRACE
 static long long* g_gemm_trace = nullptr;
+#endif
 GemmArgs to_args(const PlowGemmDesc& d) {
   GemmArgs a;
+#ifdef PLOW_DEVICE_TRACE
   a.trace = g_gemm_trace;
+#else
+  a.trace = nullptr;
+#endif
   a.x = d.x; a.w = d.w; a.y = d.y; a.sx = d.sx; a.sw = d.sw; a.residual = d.residual;
   a.yq = d.yq; a.syq = d.syq; a.grp_off = d.grp_off; a.tile_prefix = d.tile_prefix;
   a.status = d.status; a.M = d.M; a.N = d.N; a.K = d.K; a.ldy = d.ldy; a.ld_sx = d.ld_sx;
@@ -26,8 +32,10 @@ GemmArgs to_args(const PlowGemmDesc& d) {
 }
 }  // namespace plow
 
-// Debug aid: device buffer of 64*8 int64 that CTA 0 fills with clock64() phase stamps (NULL = off).
+#ifdef PLOW_DEVICE_TRACE
+// Builds with -DPLOW_DEVICE_TRACE only: device buffer of 64*8 int64 that CTA 0 fills with clock64() phase stamps.
 extern "C" void plow_gemm_set_trace(void* p) { plow::g_gemm_trace = static_cast<long long*>(p); }
+#endif
 
 extern "C" int plow_gemm(const PlowGemmDesc* d, void* stream) {
   if (!d || !d->x || !d->w || !d->status || (!d->y && !d->yq)) return -1;
@@ -47,6 +55,11 @@ extern "C" int plow_gemm(const PlowGemmDesc* d, void* stream) {
   if (d->ar_world > 1 && d->ar_oneshot == 2 && !d->ar_mc) return -8;
   if (d->ar_world > 1 && d->ar_oneshot == 1 &&
       static_cast<uint64_t>((d->N + 127) / 128) * d->ar_world * 128 * d->bn * 2 > d->ar_half_bytes) return -8;
+  if (d->swap && d->E == 0 && d->splits > 1 && d->ws && d->ws_ctr) {
+    // the CTAs of a split-K tile wait for one another: all tiles x splits of them must be resident at once
+    const long long tiles = static_cast<long long>((d->N + 127) / 128) * ((d->M + d->bn - 1) / d->bn);
+    if (tiles > 256 || tiles * d->splits > plow::sm_count()) return -9;
+  }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return d->dtype == 1 ? plow::gemm_dispatch_fp8(*d, s) : plow::gemm_dispatch_bf16(*d, s);
 }

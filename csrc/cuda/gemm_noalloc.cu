@@ -51,9 +51,10 @@ extern "C" int plow_gemm_splitk_noalloc(const void* x, const void* w, void* y, i
   if (splits < 1) splits = 1;
   if (splits > kb) splits = kb;
   if (splits > bn) splits = bn;
+  if (tiles > 128) return PLOW_NOALLOC_E_TOO_LARGE;   // checked first: tiles * splits below must not overflow
   const int sms = sm_count();
   if (tiles * splits > sms) splits = sms / tiles;      // every CTA of a tile must be resident at once
-  if (splits < 1 || tiles > 128) return PLOW_NOALLOC_E_TOO_LARGE;
+  if (splits < 1) return PLOW_NOALLOC_E_TOO_LARGE;
   if (static_cast<size_t>(tiles) * splits * 128 * bn * sizeof(float) > kWsBytes) return PLOW_NOALLOC_E_TOO_LARGE;
   unsigned char* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);

@@ -61,7 +61,7 @@ struct GemmArgs {
   uint8_t* ar_mc;          // multicast mapping of the symmetric region (mode 2)
   unsigned long long ar_tdone_ofs;   // mode 2: u32 [tiles] epoch word per tile, written to every rank when the tile has landed
   unsigned long long ar_half_bytes;   // one-shot: size of one parity half of the partial area
-  long long* trace;       // optional clock64() phase stamps of CTA 0 (debug aid), NULL when off
+  long long* trace;       // clock64() phase stamps of CTA 0; only read by builds with -DPLOW_DEVICE_TRACE
   const uint32_t* wait_ctr;
   const uint32_t* wait_epoch;
   uint32_t wait_mult;
@@ -209,7 +209,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int KB = (a.K + kKElems - 1) / kKElems;
-  const uint32_t ar_ep = a.ar_world > 1 ? *a.ar_epoch + 1 : 0;   // this launch's all-reduce epoch
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -238,45 +238,61 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (elect_one()) {
-      TileSched<BN, DUAL, SWAP> sched(a, KB);
-      Tile t;
-      uint32_t it = 0;
       bool ok = true;
+      // Dense swap mode: the weights ride the lanes and nothing on the device ever writes them, so the weight
+      // halves of the first stages are requested before the dependency wait and stream in while the producing
+      // kernel is still finishing; the activation halves of those stages follow right after the wait.
+      const bool early = SWAP && a.E == 0;
+      uint32_t npre = 0;
+      auto run = [&](int phase) {
+        TileSched<BN, DUAL, SWAP> sched(a, KB);
+        Tile t;
+        uint32_t it = 0;
+        while (ok && sched.next(t)) {
+          const int p_row = SWAP ? t.wrow0 : t.tok0;
+          const int q_row = SWAP ? t.tok0 : t.wrow0;
+          for (int kb = t.kb0; kb < t.kb1; ++kb, ++it) {
+            if (phase == 0 && it >= static_cast<uint32_t>(kStages)) return;
+            const int s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1;
+            uint8_t* st = smem + s * Cfg::kStageBytes;
+            const int kx = kb * kKElems;
+            if (phase == 0 || it >= npre) {
+              if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT); ok = false; break;
+              }
+              PLOW_TRACE(if (a.trace && blockIdx.x == 0 && it < 64) a.trace[it * 8 + 6] = clock64();)
+              mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
+              tma_load_2d(st, tm_p, kx, p_row, &full_bar[s]);
+              if (DUAL && SWAP) tma_load_2d(st + kStageBytesP, tm_p, kx, p_row + a.N, &full_bar[s]);
+              if (phase == 0) ++npre;
+            }
+            if (phase == 1) {
+              uint8_t* sq = st + Cfg::kPT * kStageBytesP;
+              tma_load_2d(sq, tm_q, kx, q_row, &full_bar[s]);
+              if (DUAL && !SWAP) tma_load_2d(sq + BN * 128, tm_q, kx, q_row + a.N, &full_bar[s]);
+            }
+          }
+        }
+      };
+      if (early) run(0);
+      pdl_wait();
       if (a.wait_ctr) {
         // peers write the token rows with generic stores; after the acquire the async proxy (TMA)
         // must be ordered behind it too
         const uint32_t target = *a.wait_epoch * a.wait_mult;
         const unsigned long long t0 = globaltimer_ns();
-        if (a.trace && blockIdx.x == 0) { a.trace[7] = static_cast<long long>(t0); a.trace[23] = ld_acquire_sys(a.wait_ctr); a.trace[31] = target; }
+        PLOW_TRACE(if (a.trace && blockIdx.x == 0) { a.trace[7] = static_cast<long long>(t0); a.trace[23] = ld_acquire_sys(a.wait_ctr); a.trace[31] = target; })
         while (ld_acquire_sys(a.wait_ctr) < target) {
           if (globaltimer_ns() - t0 > static_cast<unsigned long long>(a.wait_deadline_ms) * 1000000ull) {
             *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); ok = false; break;
           }
           __nanosleep(256);
         }
-        if (a.trace && blockIdx.x == 0) a.trace[15] = static_cast<long long>(globaltimer_ns());
+        PLOW_TRACE(if (a.trace && blockIdx.x == 0) a.trace[15] = static_cast<long long>(globaltimer_ns());)
         fence_proxy_async_all();
       }
-      while (ok && sched.next(t)) {
-        const int p_row = SWAP ? t.wrow0 : t.tok0;
-        const int q_row = SWAP ? t.tok0 : t.wrow0;
-        for (int kb = t.kb0; kb < t.kb1; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) {
-            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT); ok = false; break;
-          }
-          uint8_t* st = smem + s * Cfg::kStageBytes;
-          if (a.trace && blockIdx.x == 0 && it < 64) a.trace[it * 8 + 6] = clock64();
-          mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
-          const int kx = kb * kKElems;
-          tma_load_2d(st, tm_p, kx, p_row, &full_bar[s]);
-          if (DUAL && SWAP) tma_load_2d(st + kStageBytesP, tm_p, kx, p_row + a.N, &full_bar[s]);
-          uint8_t* sq = st + Cfg::kPT * kStageBytesP;
-          tma_load_2d(sq, tm_q, kx, q_row, &full_bar[s]);
-          if (DUAL && !SWAP) tma_load_2d(sq + BN * 128, tm_q, kx, q_row + a.N, &full_bar[s]);
-        }
-      }
+      if (ok) run(1);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
@@ -291,8 +307,8 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         for (int kb = t.kb0; kb < t.kb1; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
-          const bool tr = a.trace && blockIdx.x == 0 && it < 64;
-          if (tr) a.trace[it * 8 + 0] = clock64();
+          PLOW_TRACE(const bool tr = a.trace && blockIdx.x == 0 && it < 64;)
+          PLOW_TRACE(if (tr) a.trace[it * 8 + 0] = clock64();)
           if (FP8 || kb == t.kb0) {
             const int b = accit % kNBuf;
             if (!mbar_wait(&acc_empty[b], ((accit / kNBuf) & 1) ^ 1, abort_flag)) {
@@ -303,7 +319,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); ok = false; break;
           }
           tc_fence_after();
-          if (tr) a.trace[it * 8 + 1] = clock64();
+          PLOW_TRACE(if (tr) a.trace[it * 8 + 1] = clock64();)
           const int b = accit % kNBuf;
           const uint32_t d0 = tmem_base + b * kAccCols;
           const uint32_t sp = smem_u32(smem + s * Cfg::kStageBytes);
@@ -326,7 +342,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           }
           tc_commit(&empty_bar[s]);
           if (FP8 || kb == t.kb1 - 1) { tc_commit(&acc_full[accit % kNBuf]); ++accit; }
-          if (tr) a.trace[it * 8 + 2] = clock64();
+          PLOW_TRACE(if (tr) a.trace[it * 8 + 2] = clock64();)
         }
       }
       if (!ok) {  // drain whatever was issued before giving up
@@ -336,6 +352,8 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
     }
   } else {
     // ------------------------------------------------------------ epilogue warps (2..5)
+    pdl_wait();    // activation scales, residual, workspace counters and the epoch word below come from earlier kernels
+    const uint32_t ar_ep = a.ar_world > 1 ? *a.ar_epoch + 1 : 0;   // this launch's all-reduce epoch
     const int lq = warp & 3;               // TMEM lane quarter this warp may read
     const int li = lq * 32 + lane;         // lane (row of D) owned by this thread
     const uint32_t lane_addr = static_cast<uint32_t>(lq * 32) << 16;
@@ -389,13 +407,13 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             __syncwarp();
           }
           const int b = accit % kNBuf;
-          const bool tre = a.trace && blockIdx.x == 0 && warp == 2 && lane == 0 && accit < 64;
-          if (tre) a.trace[accit * 8 + 3] = clock64();
+          PLOW_TRACE(const bool tre = a.trace && blockIdx.x == 0 && warp == 2 && lane == 0 && accit < 64;)
+          PLOW_TRACE(if (tre) a.trace[accit * 8 + 3] = clock64();)
           if (!mbar_wait(&acc_full[b], (accit / kNBuf) & 1, abort_flag)) {
             *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
           }
           tc_fence_after();
-          if (tre) a.trace[accit * 8 + 4] = clock64();
+          PLOW_TRACE(if (tre) a.trace[accit * 8 + 4] = clock64();)
           const uint32_t tb = tmem_base + lane_addr + b * kAccCols;
 #pragma unroll
           for (int c = 0; c < kAccCols; c += 64) {
@@ -429,7 +447,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[b]);
-          if (tre) a.trace[accit * 8 + 5] = clock64();
+          PLOW_TRACE(if (tre) a.trace[accit * 8 + 5] = clock64();)
           s0 = s1;
           s1 = s2;
         }
@@ -463,8 +481,8 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
       const float* ws_tile = nullptr;
       if constexpr (SWAP) {
         if (a.splits > 1 && a.E == 0) {
-          const bool trs = a.trace && blockIdx.x == 0 && li == 0;
-          if (trs) a.trace[60 * 8 + 0] = clock64();
+          PLOW_TRACE(const bool trs = a.trace && blockIdx.x == 0 && li == 0;)
+          PLOW_TRACE(if (trs) a.trace[60 * 8 + 0] = clock64();)
           // workspace layout [tile][split][column][128 lanes]: a warp's 32 lanes touch 128 contiguous bytes
           float* wp = a.ws + (static_cast<size_t>(t.tile_id) * a.splits + t.ks) * kAccCols * 128 + li;
 #pragma unroll
@@ -482,7 +500,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           }
           ++xchg_it;
           uint32_t* ctr = reinterpret_cast<uint32_t*>(a.ws_ctr) + t.tile_id * 32;   // one counter per 128-byte line
-          if (trs) a.trace[60 * 8 + 1] = clock64();
+          PLOW_TRACE(if (trs) a.trace[60 * 8 + 1] = clock64();)
           if (li == 0) red_add_release_gpu(ctr, 1u);
           if (lane == 0) {
             const unsigned long long t0 = globaltimer_ns();
@@ -494,7 +512,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             }
           }
           __syncwarp();
-          if (trs) a.trace[60 * 8 + 2] = clock64();
+          PLOW_TRACE(if (trs) a.trace[60 * 8 + 2] = clock64();)
           if (*abort_flag) { ok = false; break; }
           col_lo = t.ks * BN / a.splits;
           col_hi = (t.ks + 1) * BN / a.splits;
@@ -693,7 +711,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         }
         if (ws_tile) {
           // the split that leaves last re-arms the tile's counters for the next launch
-          if (a.trace && blockIdx.x == 0 && li == 0) a.trace[60 * 8 + 3] = clock64();
+          PLOW_TRACE(if (a.trace && blockIdx.x == 0 && li == 0) a.trace[60 * 8 + 3] = clock64();)
           __syncwarp();
           if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
           if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) {
@@ -945,12 +963,10 @@ int launch_gemm_tc(const GemmArgs& a, int ldx_elems, int ldw_elems, int64_t w_ro
   r = make_tmap_2d(&tm_w, a.w, es, w_rows, a.K, static_cast<uint64_t>(ldw_elems) * es, box_w);
   if (r) return 2000 + r;
   auto kern = gemm_tc_kernel<BN, FP8, DUAL, SWAP>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kSmemBytes);
+  static DeviceOnce attr_set;
+  {
+    cudaError_t e = ensure_smem(attr_set, kern, Cfg::kSmemBytes);
     if (e != cudaSuccess) return 3000 + static_cast<int>(e);
-    attr_set = true;
   }
   int grid = sm_count();
   if (a.E == 0) {
@@ -960,8 +976,8 @@ int launch_gemm_tc(const GemmArgs& a, int ldx_elems, int ldw_elems, int64_t w_ro
     if (tiles < grid) grid = static_cast<int>(tiles);
   }
   if (grid < 1) grid = 1;
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(a, tm_x, tm_w);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, a, tm_x, tm_w);
+  if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }
 

@@ -42,6 +42,7 @@ mla_absorb_kernel(const AbsorbArgs a, const __grid_constant__ CUtensorMap tm_q, 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(holder + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.x, t0 = blockIdx.y * 128;
+  pdl_launch_dependents();
   if (threadIdx.x == 0) { mbar_init(full, 1); mbar_init(done, 1); *abort_flag = 0; fence_mbar_init(); }
   if (warp == 0) { tmem_alloc(holder, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -50,10 +51,12 @@ mla_absorb_kernel(const AbsorbArgs a, const __grid_constant__ CUtensorMap tm_q, 
   const uint32_t tm = *holder;
   if (warp == 0) {
     if (elect_one()) {
+      // the head's W_uk (a weight) is requested before the dependency wait, the queries after it
       mbar_expect_tx(full, 32768 + 131072);
-      for (int kc = 0; kc < 2; ++kc) tma_load_2d(sa + kc * 16384, &tm_q, h * 192 + kc * 64, t0, full);
       for (int nh = 0; nh < 2; ++nh)
         for (int kc = 0; kc < 2; ++kc) tma_load_2d(sb + (nh * 2 + kc) * 32768, &tm_w, kc * 64, h * 512 + nh * 256, full);
+      pdl_wait();
+      for (int kc = 0; kc < 2; ++kc) tma_load_2d(sa + kc * 16384, &tm_q, h * 192 + kc * 64, t0, full);
       if (mbar_wait(full, 0, abort_flag)) {
         tc_fence_after();
         const uint32_t idesc = umma_idesc(128, 256, 1, 1);
@@ -74,6 +77,7 @@ mla_absorb_kernel(const AbsorbArgs a, const __grid_constant__ CUtensorMap tm_q, 
     const int t = t0 + li;
     const uint32_t lane_addr = static_cast<uint32_t>(lq * 32) << 16;
     // RoPE of this token's 64 rope dims while the MMA runs
+    pdl_wait();
     float rp[64];
     const bool live = t < a.T;
     {
@@ -177,6 +181,7 @@ mla_fold_kernel(const FoldArgs a, const __grid_constant__ CUtensorMap tm_w) {
   volatile int* abort_flag = reinterpret_cast<volatile int*>(holder + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.x, t0 = blockIdx.y * 128;
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     mbar_init(b_full, 1); mbar_init(a_ready, 4); mbar_init(&done[0], 1); mbar_init(&done[1], 1);
     *abort_flag = 0; fence_mbar_init();
@@ -210,6 +215,7 @@ mla_fold_kernel(const FoldArgs a, const __grid_constant__ CUtensorMap tm_w) {
     const int t = t0 + li;
     const bool live = t < a.T;
     const uint32_t lane_addr = static_cast<uint32_t>(lq * 32) << 16;
+    pdl_wait();      // partials and log-sum-exps come from the attention kernel (warp 0 only touches W_uv, a weight)
     // merge weights of this (token, head), shared with the other merge warps through shared memory
     float* wsm = reinterpret_cast<float*>(smem + 131072 + 256);       // [128 rows][8 splits]
     int* nsm = reinterpret_cast<int*>(wsm + 128 * 8);                 // [128 rows]
@@ -356,13 +362,14 @@ int plow_mla_absorb(const void* q, int q_pitch, const void* wuk_t, const float* 
   r = make_tmap_2d(&tw, wuk_t, 2, static_cast<uint64_t>(heads) * 512, 128, 256, 256);
   if (r) return 1100 + r;
   const int smem = 1024 + 32768 + 131072 + 256;
-  static bool attr = false;
-  if (!attr) { if (cudaFuncSetAttribute(mla_absorb_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 3000; attr = true; }
+  static DeviceOnce attr;
+  if (ensure_smem(attr, mla_absorb_kernel, smem) != cudaSuccess) return 3000;
   AbsorbArgs a;
   a.q = static_cast<const __nv_bfloat16*>(q); a.rope_tab = rope_tab; a.pos = pos; a.q8 = static_cast<uint8_t*>(q8); a.sq = sq;
   a.status = status; a.T = T; a.heads = heads; a.q_pitch = q_pitch; a.pair_mode = pair_mode;
-  mla_absorb_kernel<<<dim3(heads, (T + 127) / 128), kProjThreads, smem, reinterpret_cast<cudaStream_t>(stream_)>>>(a, tq, tw);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(mla_absorb_kernel, dim3(heads, (T + 127) / 128), dim3(kProjThreads), smem,
+                             reinterpret_cast<cudaStream_t>(stream_), a, tq, tw);
+  if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }
 
@@ -375,14 +382,15 @@ int plow_mla_fold(const void* opart, const float* lse, const int* kvlen, const v
   int r = make_tmap_2d(&tw, wuv, 2, static_cast<uint64_t>(heads) * 128, 512, 1024, 128);
   if (r) return 1000 + r;
   const int smem = 1024 + 131072 + 256 + 128 * 8 * 4 + 128 * 4;
-  static bool attr = false;
-  if (!attr) { if (cudaFuncSetAttribute(mla_fold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 3000; attr = true; }
+  static DeviceOnce attr;
+  if (ensure_smem(attr, mla_fold_kernel, smem) != cudaSuccess) return 3000;
   FoldArgs a;
   a.opart = static_cast<const __nv_bfloat16*>(opart); a.lse = lse; a.kvlen = kvlen; a.ao = static_cast<__nv_bfloat16*>(ao);
   a.aq = static_cast<uint8_t*>(aq); a.saq = saq; a.status = status; a.T = T; a.heads = heads; a.max_splits = max_splits;
   a.tiles_per_split = tiles_per_split; a.ld_saq = ld_saq;
-  mla_fold_kernel<<<dim3(heads, (T + 127) / 128), kProjThreads, smem, reinterpret_cast<cudaStream_t>(stream_)>>>(a, tw);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(mla_fold_kernel, dim3(heads, (T + 127) / 128), dim3(kProjThreads), smem,
+                             reinterpret_cast<cudaStream_t>(stream_), a, tw);
+  if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }
 

@@ -12,6 +12,15 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "launch.cuh"
+
+// Phase stamps are compiled out unless the library is built with -DPLOW_DEVICE_TRACE.
+#ifdef PLOW_DEVICE_TRACE
+#define PLOW_TRACE(...) __VA_ARGS__
+#else
+#define PLOW_TRACE(...)
+#endif
+
 namespace plow {
 
 // Status codes written to the per-launch status word (0 = ok).

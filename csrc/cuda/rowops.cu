@@ -15,6 +15,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "launch.cuh"
+
 namespace {
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -40,6 +42,8 @@ __device__ __forceinline__ float block_sum(float v, float* sh) {
 
 // ---- embed ------------------------------------------------------------------------------------
 __global__ void embed_kernel(__nv_bfloat16* out, const __nv_bfloat16* tab, const int* ids, int H, float scale) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const int r = blockIdx.x;
   const uint4* src = reinterpret_cast<const uint4*>(tab + static_cast<size_t>(ids[r]) * H);
   uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * H);
@@ -65,6 +69,8 @@ __global__ void __launch_bounds__(512)
 norm_kernel(__nv_bfloat16* h_out, uint8_t* xq, float* sxq, int ld_sx, __nv_bfloat16* x_out,
             const __nv_bfloat16* x_in, const __nv_bfloat16* delta, const __nv_bfloat16* gamma, int W,
             int x_pitch, float eps, int plus_one) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   extern __shared__ float rowbuf[];      // W floats
   __shared__ float red[32];
   const int r = blockIdx.x;
@@ -145,6 +151,8 @@ norm_kernel(__nv_bfloat16* h_out, uint8_t* xq, float* sxq, int ld_sx, __nv_bfloa
 }
 
 __global__ void quant_act_kernel(uint8_t* xq, float* sxq, int ld_sx, const __nv_bfloat16* x, int K, int x_pitch) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const int r = blockIdx.x;
   const int Kpad = (K + 255) & ~255;
   for (int i = threadIdx.x * 8; i < Kpad; i += blockDim.x * 8) {
@@ -172,6 +180,8 @@ __global__ void quant_act_kernel(uint8_t* xq, float* sxq, int ld_sx, const __nv_
 // roped q_rope [heads][T][rope].  pair_mode 1 = interleaved (2i, 2i+1), 0 = half split.
 __global__ void mla_q_prep_kernel(__nv_bfloat16* q_nope_t, __nv_bfloat16* q_rope, const __nv_bfloat16* q, int q_pitch,
                                   const float* rope_tab, const int* pos, int T, int heads, int nope, int rope, int pair_mode) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const __nv_bfloat16* src = q + static_cast<size_t>(t) * q_pitch + static_cast<size_t>(h) * (nope + rope);
   __nv_bfloat16* dn = q_nope_t + (static_cast<size_t>(h) * T + t) * nope;
@@ -191,6 +201,8 @@ __global__ void mla_q_prep_kernel(__nv_bfloat16* q_nope_t, __nv_bfloat16* q_rope
 // q_abs [heads][T][latent] bf16 + q_rope [heads][T][rope] -> q8 [heads][T][latent+rope] e4m3, sq [heads][T]
 __global__ void mla_q_quant_kernel(uint8_t* q8, float* sq, const __nv_bfloat16* q_abs, const __nv_bfloat16* q_rope,
                                    int T, int latent, int rope) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const size_t row = static_cast<size_t>(h) * T + t;
   const int W = latent + rope;
@@ -219,6 +231,8 @@ __global__ void mla_q_quant_kernel(uint8_t* q8, float* sq, const __nv_bfloat16* 
 __global__ void mla_kv_write_kernel(uint8_t* kv8, float* kv_scale, float* kv_smax, const __nv_bfloat16* kva, int pitch, int col_ofs,
                                     const __nv_bfloat16* gamma, const float* rope_tab, const int* pos, const int* slot_of,
                                     const int* page_table, int max_pages, int latent, int rope, float eps, int pair_mode) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   extern __shared__ float rowf[];   // latent + rope
   __shared__ float red[32];
   const int t = blockIdx.x;
@@ -275,6 +289,8 @@ __device__ __forceinline__ uint32_t ordered_bits(float f) {
 // ties go to the lowest group / expert id; gates renormalised over the k winners then scaled.
 __global__ void router_topk_kernel(int2* table, const float* logits, const float* bias, int T, int E, int k,
                                    int n_group, int topk_group, int sigmoid, int norm_topk, float route_scale) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   extern __shared__ float sm[];    // per warp: score[E], sel[E]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -350,8 +366,14 @@ __global__ void router_topk_kernel(int2* table, const float* logits, const float
 // ---- MoE align / gather / combine -------------------------------------------------------------
 // One CTA.  Counts the (token, slot) pairs routed to this rank's experts [e_base, e_base+e_local),
 // writes grp_off[e_local+1], tile_prefix[e_local+1] (128-row tiles) and the pair<->row maps.
+// shared_rows > 0 appends one more group (index e_local) that holds tokens [shared_tok_base, shared_tok_base +
+// shared_rows) in order: the shared expert stacked behind the routed ones.  Its rows get pair_of_row = token * top_k,
+// so the gather kernel (token = pair / top_k) copies them like any other row; grp_off / tile_prefix then have
+// e_local + 2 entries and pair_of_row n_pairs + shared_rows.
 __global__ void moe_align_kernel(const int2* table, int n_pairs, int e_base, int e_local, int* grp_off, int* tile_prefix,
-                                 int* row_of_pair, int* pair_of_row) {
+                                 int* row_of_pair, int* pair_of_row, int shared_rows, int shared_tok_base, int top_k) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   extern __shared__ int cnt[];     // e_local counts, then e_local cursors
   int* cur = cnt + e_local;
   for (int e = threadIdx.x; e < e_local; e += blockDim.x) cnt[e] = 0;
@@ -368,19 +390,24 @@ __global__ void moe_align_kernel(const int2* table, int n_pairs, int e_base, int
       off += cnt[e]; tiles += (cnt[e] + 127) >> 7;
     }
     grp_off[e_local] = off; tile_prefix[e_local] = tiles;
+    if (shared_rows > 0) { grp_off[e_local + 1] = off + shared_rows; tile_prefix[e_local + 1] = tiles + ((shared_rows + 127) >> 7); }
   }
   __syncthreads();
+  const int routed = grp_off[e_local];
   for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
     const int e = table[p].x - e_base;
     int row = -1;
     if (e >= 0 && e < e_local) { row = atomicAdd(&cur[e], 1); pair_of_row[row] = p; }
     row_of_pair[p] = row;
   }
+  for (int t = threadIdx.x; t < shared_rows; t += blockDim.x) pair_of_row[routed + t] = (shared_tok_base + t) * top_k;
 }
 
 // Rows of the quantised activations gathered into expert order (scales are transposed [kb][row]).
 __global__ void moe_gather_kernel(uint8_t* xs, float* sxs, int ld_sxs, const uint8_t* xq, const float* sx, int ld_sx,
                                   const int* pair_of_row, const int* n_rows, int top_k, int K) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const int row = blockIdx.x;
   if (row >= *n_rows) return;
   const int tok = pair_of_row[row] / top_k;
@@ -391,8 +418,12 @@ __global__ void moe_gather_kernel(uint8_t* xs, float* sxs, int ld_sxs, const uin
 }
 
 // out[t] = shared[t] (optional) + sum_j gate[t][j] * y[row_of_pair[t*k+j]]   (fixed slot order, f32)
+// shared_base != NULL: the shared expert ran as a group of the grouped GEMM and its row of token t is
+// shared[*shared_base + t] (the group's first row is only known on the device).
 __global__ void moe_combine_kernel(__nv_bfloat16* out, const __nv_bfloat16* y, const __nv_bfloat16* shared,
-                                   const int2* table, const int* row_of_pair, int top_k, int H) {
+                                   const int2* table, const int* row_of_pair, int top_k, int H, const int* shared_base) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   // slot metadata first, then all of a thread's loads at once (one 16-byte unit per thread, grid.y covers H)
   constexpr int kMaxK = 16;
   __shared__ int s_row[kMaxK];
@@ -413,7 +444,8 @@ __global__ void moe_combine_kernel(__nv_bfloat16* out, const __nv_bfloat16* y, c
   }
   float acc[8];
   if (shared) {
-    const uint4 sv = *reinterpret_cast<const uint4*>(shared + static_cast<size_t>(t) * H + i);
+    const size_t srow = static_cast<size_t>(t) + (shared_base ? *shared_base : 0);
+    const uint4 sv = *reinterpret_cast<const uint4*>(shared + srow * H + i);
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&sv);
 #pragma unroll
     for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h[j]); acc[2 * j] = f.x; acc[2 * j + 1] = f.y; }
@@ -440,6 +472,8 @@ __global__ void moe_combine_kernel(__nv_bfloat16* out, const __nv_bfloat16* y, c
 
 // ---- argmax / gather --------------------------------------------------------------------------
 __global__ void argmax_kernel(int* out, const float* logits, int V) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   __shared__ unsigned long long red[32];
   const float* row = logits + static_cast<size_t>(blockIdx.x) * V;
   unsigned long long best = 0ull;
@@ -462,6 +496,8 @@ __global__ void argmax_kernel(int* out, const float* logits, int V) {
 // Vocabulary-sharded arg-max: the row's best (ordered score << 32 | ~global index) key of this rank's shard; the ranks'
 // keys are folded with a max (lowest global index wins ties), see argmax_fin_kernel.
 __global__ void argmax_key_kernel(unsigned long long* keys, const float* logits, int V, int vocab_ofs) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   __shared__ unsigned long long red[32];
   const float* row = logits + static_cast<size_t>(blockIdx.x) * V;
   unsigned long long best = 0ull;
@@ -484,6 +520,8 @@ __global__ void argmax_key_kernel(unsigned long long* keys, const float* logits,
 
 // keys [world][R] gathered from the ranks -> ids [R]
 __global__ void argmax_fin_kernel(int* out, const unsigned long long* keys, int R, int world) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= R) return;
   unsigned long long best = 0ull;
@@ -492,6 +530,8 @@ __global__ void argmax_fin_kernel(int* out, const unsigned long long* keys, int 
 }
 
 __global__ void row_gather_kernel(__nv_bfloat16* out, const __nv_bfloat16* x, const int* rows, int W) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(rows[blockIdx.x]) * W);
   uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(blockIdx.x) * W);
   for (int i = threadIdx.x; i < W / 8; i += blockDim.x) dst[i] = src[i];
@@ -499,10 +539,33 @@ __global__ void row_gather_kernel(__nv_bfloat16* out, const __nv_bfloat16* x, co
 
 // [heads][T][W] -> [T][heads*W] (attention output back to token-major for o_proj)
 __global__ void head_to_token_kernel(__nv_bfloat16* out, const __nv_bfloat16* x, int T, int heads, int W) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const uint4* src = reinterpret_cast<const uint4*>(x + (static_cast<size_t>(h) * T + t) * W);
   uint4* dst = reinterpret_cast<uint4*>(out + (static_cast<size_t>(t) * heads + h) * W);
   for (int i = threadIdx.x; i < W / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---- residual add / SiLU-GLU on bf16 rows (8 elements per thread) ------------------------------
+// mode 0: out = a + b;  mode 1: out = silu(a) * b.  Both are computed in f32 and rounded once.
+__global__ void eltwise2_kernel(__nv_bfloat16* out, const __nv_bfloat16* a, const __nv_bfloat16* b, size_t n8, int mode) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const uint4 va = reinterpret_cast<const uint4*>(a)[i], vb = reinterpret_cast<const uint4*>(b)[i];
+    const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&va);
+    const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&vb);
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = __bfloat1622float2(ha[j]), y = __bfloat1622float2(hb[j]);
+      if (mode == 0) oh[j] = __floats2bfloat162_rn(x.x + y.x, x.y + y.y);
+      else oh[j] = __floats2bfloat162_rn(x.x / (1.0f + __expf(-x.x)) * y.x, x.y / (1.0f + __expf(-x.y)) * y.y);
+    }
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
 }
 
 inline int ok() { cudaError_t e = cudaGetLastError(); return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e); }
@@ -516,17 +579,17 @@ extern "C" {
 
 int plow_embed(void* out, const void* tab, const int* ids, int R, int H, float scale, void* st) {
   if (H % 8) return -1;
-  embed_kernel<<<R, 256, 0, S(st)>>>((bf16*)out, (const bf16*)tab, ids, H, scale);
+  plow::launch_pdl(embed_kernel, dim3(R), dim3(256), 0, S(st), (bf16*)out, (const bf16*)tab, ids, H, scale);
   return ok();
 }
 
 int plow_rmsnorm(void* h_out, void* xq, float* sxq, int ld_sx, const void* x, const void* gamma, int R, int W,
                  int x_pitch, float eps, int plus_one, void* st) {
   if (W % 8 || (xq && W % 128) || W * 4 > 200 * 1024) return -1;
-  static bool attr = false;
-  if (!attr) { cudaFuncSetAttribute(norm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr = true; }
+  static plow::DeviceOnce attr;
+  if (plow::ensure_smem(attr, norm_kernel<false>, 200 * 1024) != cudaSuccess) return 3000;
   const int threads = W >= 4096 ? 512 : (W >= 1024 ? 128 : 64);
-  norm_kernel<false><<<R, threads, W * 4, S(st)>>>((bf16*)h_out, (uint8_t*)xq, sxq, ld_sx, nullptr, (const bf16*)x, nullptr,
+  plow::launch_pdl(norm_kernel<false>, dim3(R), dim3(threads), W * 4, S(st), (bf16*)h_out, (uint8_t*)xq, sxq, ld_sx, nullptr, (const bf16*)x, nullptr,
                                                    (const bf16*)gamma, W, x_pitch ? x_pitch : W, eps, plus_one);
   return ok();
 }
@@ -534,36 +597,36 @@ int plow_rmsnorm(void* h_out, void* xq, float* sxq, int ld_sx, const void* x, co
 int plow_add_norm(void* h_out, void* xq, float* sxq, int ld_sx, void* x_out, const void* x_in, const void* delta,
                   const void* gamma, int R, int W, float eps, int plus_one, void* st) {
   if (W % 8 || (xq && W % 128) || W * 4 > 200 * 1024) return -1;
-  static bool attr = false;
-  if (!attr) { cudaFuncSetAttribute(norm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr = true; }
+  static plow::DeviceOnce attr;
+  if (plow::ensure_smem(attr, norm_kernel<true>, 200 * 1024) != cudaSuccess) return 3000;
   const int threads = W >= 4096 ? 512 : (W >= 1024 ? 128 : 64);
-  norm_kernel<true><<<R, threads, W * 4, S(st)>>>((bf16*)h_out, (uint8_t*)xq, sxq, ld_sx, (bf16*)x_out, (const bf16*)x_in,
+  plow::launch_pdl(norm_kernel<true>, dim3(R), dim3(threads), W * 4, S(st), (bf16*)h_out, (uint8_t*)xq, sxq, ld_sx, (bf16*)x_out, (const bf16*)x_in,
                                                   (const bf16*)delta, (const bf16*)gamma, W, W, eps, plus_one);
   return ok();
 }
 
 int plow_quant_act(void* xq, float* sxq, int ld_sx, const void* x, int R, int K, int x_pitch, void* st) {
   if (K % 128) return -1;
-  quant_act_kernel<<<R, K >= 4096 ? 512 : 128, 0, S(st)>>>((uint8_t*)xq, sxq, ld_sx, (const bf16*)x, K, x_pitch ? x_pitch : K);
+  plow::launch_pdl(quant_act_kernel, dim3(R), dim3(K >= 4096 ? 512 : 128), 0, S(st), (uint8_t*)xq, sxq, ld_sx, (const bf16*)x, K, x_pitch ? x_pitch : K);
   return ok();
 }
 
 int plow_mla_q_prep(void* q_nope_t, void* q_rope, const void* q, int q_pitch, const float* rope_tab, const int* pos, int T,
                     int heads, int nope, int rope, int pair_mode, void* st) {
-  mla_q_prep_kernel<<<dim3(T, heads), 64, 0, S(st)>>>((bf16*)q_nope_t, (bf16*)q_rope, (const bf16*)q, q_pitch, rope_tab, pos, T,
+  plow::launch_pdl(mla_q_prep_kernel, dim3(T, heads), dim3(64), 0, S(st), (bf16*)q_nope_t, (bf16*)q_rope, (const bf16*)q, q_pitch, rope_tab, pos, T,
                                                       heads, nope, rope, pair_mode);
   return ok();
 }
 
 int plow_mla_q_quant(void* q8, float* sq, const void* q_abs, const void* q_rope, int T, int heads, int latent, int rope, void* st) {
-  mla_q_quant_kernel<<<dim3(T, heads), 128, 0, S(st)>>>((uint8_t*)q8, sq, (const bf16*)q_abs, (const bf16*)q_rope, T, latent, rope);
+  plow::launch_pdl(mla_q_quant_kernel, dim3(T, heads), dim3(128), 0, S(st), (uint8_t*)q8, sq, (const bf16*)q_abs, (const bf16*)q_rope, T, latent, rope);
   return ok();
 }
 
 int plow_mla_kv_write(void* kv8, float* kv_scale, float* kv_smax, const void* kva, int pitch, int col_ofs, const void* gamma,
                       const float* rope_tab, const int* pos, const int* slot_of, const int* page_table, int max_pages, int T,
                       int latent, int rope, float eps, int pair_mode, void* st) {
-  mla_kv_write_kernel<<<T, 128, (latent + rope) * 4, S(st)>>>((uint8_t*)kv8, kv_scale, kv_smax, (const bf16*)kva, pitch, col_ofs,
+  plow::launch_pdl(mla_kv_write_kernel, dim3(T), dim3(128), (latent + rope) * 4, S(st), (uint8_t*)kv8, kv_scale, kv_smax, (const bf16*)kva, pitch, col_ofs,
                                                               (const bf16*)gamma, rope_tab, pos, slot_of, page_table, max_pages,
                                                               latent, rope, eps, pair_mode);
   return ok();
@@ -573,56 +636,65 @@ int plow_router_topk(void* table, const float* logits, const float* bias, int T,
                      int sigmoid, int norm_topk, float route_scale, void* st) {
   if (k > 32 || n_group > 32 || E % (n_group > 0 ? n_group : 1)) return -1;
   const int wpb = 4;
-  router_topk_kernel<<<(T + wpb - 1) / wpb, wpb * 32, wpb * 2 * E * 4, S(st)>>>((int2*)table, logits, bias, T, E, k, n_group,
+  plow::launch_pdl(router_topk_kernel, dim3((T + wpb - 1) / wpb), dim3(wpb * 32), wpb * 2 * E * 4, S(st), (int2*)table, logits, bias, T, E, k, n_group,
                                                                                 topk_group, sigmoid, norm_topk, route_scale);
   return ok();
 }
 
 int plow_moe_align(const void* table, int n_pairs, int e_base, int e_local, int* grp_off, int* tile_prefix, int* row_of_pair,
-                   int* pair_of_row, void* st) {
-  moe_align_kernel<<<1, 1024, 2 * e_local * 4, S(st)>>>((const int2*)table, n_pairs, e_base, e_local, grp_off, tile_prefix,
-                                                        row_of_pair, pair_of_row);
+                   int* pair_of_row, int shared_rows, int shared_tok_base, int top_k, void* st) {
+  plow::launch_pdl(moe_align_kernel, dim3(1), dim3(1024), 2 * e_local * 4, S(st), (const int2*)table, n_pairs, e_base, e_local, grp_off, tile_prefix,
+                                                        row_of_pair, pair_of_row, shared_rows, shared_tok_base, top_k);
   return ok();
 }
 
 int plow_moe_gather(void* xs, float* sxs, int ld_sxs, const void* xq, const float* sx, int ld_sx, const int* pair_of_row,
                     const int* n_rows, int max_rows, int top_k, int K, void* st) {
   if (K % 128) return -1;
-  moe_gather_kernel<<<max_rows, 128, 0, S(st)>>>((uint8_t*)xs, sxs, ld_sxs, (const uint8_t*)xq, sx, ld_sx, pair_of_row, n_rows, top_k, K);
+  plow::launch_pdl(moe_gather_kernel, dim3(max_rows), dim3(128), 0, S(st), (uint8_t*)xs, sxs, ld_sxs, (const uint8_t*)xq, sx, ld_sx, pair_of_row, n_rows, top_k, K);
   return ok();
 }
 
 int plow_moe_combine(void* out, const void* y, const void* shared, const void* table, const int* row_of_pair, int T, int top_k,
-                     int H, void* st) {
+                     int H, const int* shared_base, void* st) {
   if (H % 8 || top_k > 16) return -1;
-  moe_combine_kernel<<<dim3(T, (H / 8 + 255) / 256), 256, 0, S(st)>>>((bf16*)out, (const bf16*)y, (const bf16*)shared, (const int2*)table, row_of_pair, top_k, H);
+  plow::launch_pdl(moe_combine_kernel, dim3(T, (H / 8 + 255) / 256), dim3(256), 0, S(st), (bf16*)out, (const bf16*)y, (const bf16*)shared, (const int2*)table, row_of_pair, top_k, H, shared_base);
   return ok();
 }
 
 int plow_argmax(int* out, const float* logits, int R, int V, void* st) {
-  argmax_kernel<<<R, 1024, 0, S(st)>>>(out, logits, V);
+  plow::launch_pdl(argmax_kernel, dim3(R), dim3(1024), 0, S(st), out, logits, V);
   return ok();
 }
 
 int plow_argmax_key(void* keys, const float* logits, int R, int V, int vocab_ofs, void* st) {
-  argmax_key_kernel<<<R, 1024, 0, S(st)>>>(static_cast<unsigned long long*>(keys), logits, V, vocab_ofs);
+  plow::launch_pdl(argmax_key_kernel, dim3(R), dim3(1024), 0, S(st), static_cast<unsigned long long*>(keys), logits, V, vocab_ofs);
   return ok();
 }
 
 int plow_argmax_fin(int* out, const void* keys, int R, int world, void* st) {
-  argmax_fin_kernel<<<(R + 127) / 128, 128, 0, S(st)>>>(out, static_cast<const unsigned long long*>(keys), R, world);
+  plow::launch_pdl(argmax_fin_kernel, dim3((R + 127) / 128), dim3(128), 0, S(st), out, static_cast<const unsigned long long*>(keys), R, world);
   return ok();
 }
 
 int plow_row_gather(void* out, const void* x, const int* rows, int n, int W, void* st) {
   if (W % 8) return -1;
-  row_gather_kernel<<<n, 128, 0, S(st)>>>((bf16*)out, (const bf16*)x, rows, W);
+  plow::launch_pdl(row_gather_kernel, dim3(n), dim3(128), 0, S(st), (bf16*)out, (const bf16*)x, rows, W);
+  return ok();
+}
+
+// out = a + b (mode 0) or silu(a) * b (mode 1) over n bf16 elements (n % 8 == 0, 16-byte aligned pointers)
+int plow_eltwise2(void* out, const void* a, const void* b, long long n, int mode, void* st) {
+  if (n % 8 || n <= 0) return -1;
+  const size_t n8 = static_cast<size_t>(n) / 8;
+  const unsigned grid = static_cast<unsigned>(n8 / 256 + 1 < 1184 ? n8 / 256 + 1 : 1184);
+  plow::launch_pdl(eltwise2_kernel, dim3(grid), dim3(256), 0, S(st), (bf16*)out, (const bf16*)a, (const bf16*)b, n8, mode);
   return ok();
 }
 
 int plow_head_to_token(void* out, const void* x, int T, int heads, int W, void* st) {
   if (W % 8) return -1;
-  head_to_token_kernel<<<dim3(T, heads), 32, 0, S(st)>>>((bf16*)out, (const bf16*)x, T, heads, W);
+  plow::launch_pdl(head_to_token_kernel, dim3(T, heads), dim3(32), 0, S(st), (bf16*)out, (const bf16*)x, T, heads, W);
   return ok();
 }
 

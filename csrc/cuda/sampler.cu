@@ -9,6 +9,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "launch.cuh"
+
 namespace {
 
 constexpr int kThreads = 1024;
@@ -86,6 +88,8 @@ __global__ void __launch_bounds__(kThreads)
 sample_kernel(int* out, const float* logits, int ld, int V, const float* temperature, const int* top_k,
               const float* top_p, const float* min_p, const float* u_in, const unsigned long long* seed,
               unsigned long long step) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
   __shared__ float red[33];
   __shared__ float hist[256];
   __shared__ uint32_t sh_u;
@@ -200,7 +204,7 @@ extern "C" {
 int plow_sample(int* out, const float* logits, int ld, int rows, int V, const float* temperature, const int* top_k,
                 const float* top_p, const float* min_p, const float* u, const void* seed, uint64_t step, void* stream) {
   if (rows <= 0 || V <= 0) return -1;
-  sample_kernel<<<rows, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  plow::launch_pdl(sample_kernel, dim3(rows), dim3(kThreads), 0, reinterpret_cast<cudaStream_t>(stream), 
       out, logits, ld, V, temperature, top_k, top_p, min_p, u, static_cast<const unsigned long long*>(seed), step);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);

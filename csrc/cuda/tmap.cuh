@@ -10,6 +10,8 @@
 #include <mutex>
 #include <unordered_map>
 
+#include "launch.cuh"
+
 namespace plow {
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -73,14 +75,12 @@ inline int make_tmap_3d(CUtensorMap* out, const void* base, int esize, uint64_t 
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// SM count of the current device (cached per device: a process may drive several GPUs).
 inline int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
+  static int n[kMaxDevices] = {};
+  const int dev = current_device();
+  if (!n[dev]) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+  return n[dev];
 }
 
 }  // namespace plow

@@ -29,7 +29,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",
 ]
-CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-march=native", "-fopenmp", "-Wall", "-Wno-unused-function"]
+CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-march=x86-64-v3", "-fopenmp", "-Wall", "-Wno-unused-function"]
 
 
 def _nvcc() -> str | None:

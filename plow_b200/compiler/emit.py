@@ -194,7 +194,7 @@ class Lowering:
         "dsa_k_write": (Op.DSA_INDEX, ["dim", "rot_dim"], [], "row"),
         "dsa_topk": (Op.DSA_TOPK, ["heads", "dim", "topk", "rot_dim"], [], "attn"),
         "router_topk": (Op.ROUTER_TOPK, ["n_experts", "top_k", "n_group", "topk_group", "score", "norm_topk"], ["route_scale"], "row"),
-        "moe_experts": (Op.MOE_GEMM, ["n_experts", "e_local", "top_k", "inter", "ep", "has_shared"], [], "gemm"),
+        "moe_experts": (Op.MOE_GEMM, ["n_experts", "e_local", "top_k", "inter", "ep", "has_shared", "shared_group"], [], "gemm"),
         "gdn": (Op.GDN_STEP, ["k_heads", "v_heads", "head_dim", "conv"], [], "attn"),
         "gated_norm": (Op.GATED_NORM, ["heads", "head_dim", "z_offset"], ["eps"], "row"),
         "sigmoid_gate": (Op.SIGMOID_GATE, [], [], "row"),

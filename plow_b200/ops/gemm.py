@@ -30,7 +30,7 @@ def _pick_bn_swap(rows: int, fp8: bool, dual: bool) -> int:
 
 
 _SPLITK_WS = {}
-SM_COUNT = 148
+SM_COUNT = 148          # B200; used only where no device is present (the device's own count is read otherwise)
 
 
 _TUNED = {}
@@ -61,6 +61,21 @@ def _splitk_ws(device):
     return _SPLITK_WS[device]
 
 
+def reset_workspace(device) -> None:
+    """Zero the split-K arrival counters of `device` (the kernels re-arm them only when a launch finishes cleanly)."""
+    import torch as _t
+    dev = _t.device(device)
+    if dev in _SPLITK_WS:
+        _SPLITK_WS[dev][1].zero_()
+
+
+def sm_count(device=None) -> int:
+    import torch as _t
+    if not _t.cuda.is_available():
+        return SM_COUNT
+    return _t.cuda.get_device_properties(device if device is not None else _t.cuda.current_device()).multi_processor_count
+
+
 def pick_splits(M, N, K, fp8, dual, bn) -> int:
     """Split-K factor for a dense swap-mode GEMM: fill the SMs when the tile count alone cannot.
 
@@ -69,7 +84,7 @@ def pick_splits(M, N, K, fp8, dual, bn) -> int:
     at once: tiles * s <= SM count) that reduce their partials through L2."""
     tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)
     kb = (K + (127 if fp8 else 63)) // (128 if fp8 else 64)
-    s = min(SM_COUNT // max(tiles, 1), kb // 4, bn // 4, 16)
+    s = min(sm_count() // max(tiles, 1), kb // 4, bn // 4, 16)
     if s < 2:
         return 1
     acc = bn * (2 if dual else 1)

@@ -108,21 +108,23 @@ _SIGS = {
     "plow_mla_q_quant": "ppppiiiip",
     "plow_mla_kv_write": "ppppiipppppiiiifip",
     "plow_router_topk": "pppiiiiiiifp",
-    "plow_moe_align": "piiippppp",
+    "plow_moe_align": "piiippppiiip",
     "plow_moe_gather": "ppippipp" "iiip",
-    "plow_moe_combine": "pppppiiip",
+    "plow_moe_combine": "pppppiiipp",
     "plow_argmax": "ppiip",
     "plow_argmax_key": "ppiiip",
     "plow_argmax_fin": "ppiip",
     "plow_row_gather": "pppiip",
     "plow_head_to_token": "ppiiip",
-    "plow_mla_decode": "ppppplpipp" "iiipppppfpp",
+    "plow_eltwise2": "pppl" "ip",
+    "plow_mla_decode": "ppppplpipp" "iiipppppfipp",
+    "plow_mla_build_items": "piiippp",
     "plow_mla_absorb": "pipppppiiipp",
     "plow_mla_fold": "pppppppiiiiipp",
     "plow_ep_counts": "ppipp",
-    "plow_ep_push": "ppiippippppip",
+    "plow_ep_push": "ppiippippppiip",
     "plow_ep_y_ready": "pp",
-    "plow_ep_combine": "pppppiip",
+    "plow_ep_combine": "pppppiipp",
     "plow_wait_probe": "piLpp",
     "plow_ag_push": "pLLppiipiiip",
     "plow_interp_run": "ppppppppppp" "IIIIp",
@@ -148,7 +150,7 @@ def _arg(v):
 
 
 LAUNCHES = {"n": 0}                       # kernels launched through this module (bench bookkeeping)
-_KERNELS_PER_CALL = {"plow_mla_decode": 2, "plow_gqa_attention": 2, "plow_dsa_select": 3}
+_KERNELS_PER_CALL = {"plow_gqa_attention": 2, "plow_dsa_select": 3}
 
 
 def call(name: str, *args) -> None:

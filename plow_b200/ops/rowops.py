@@ -68,14 +68,19 @@ def table_gates(table):
     return table[..., 1].contiguous().view(torch.float32)
 
 
-def moe_align(table, e_base, e_local):
+def moe_align(table, e_base, e_local, shared_rows=0, shared_tok_base=0):
+    """Expert-sorted row layout of the pairs routed to experts [e_base, e_base + e_local).  ``shared_rows`` > 0 appends
+    one more group (index e_local) holding tokens [shared_tok_base, shared_tok_base + shared_rows): the shared expert
+    stacked behind the routed ones; grp_off / tile_prefix then have e_local + 2 entries."""
     n_pairs = table.shape[0] * table.shape[1]
     dev = table.device
-    grp_off = torch.empty(e_local + 1, dtype=torch.int32, device=dev)
-    tile_prefix = torch.empty(e_local + 1, dtype=torch.int32, device=dev)
+    ng = e_local + (1 if shared_rows else 0)
+    grp_off = torch.empty(ng + 1, dtype=torch.int32, device=dev)
+    tile_prefix = torch.empty(ng + 1, dtype=torch.int32, device=dev)
     row_of_pair = torch.empty(n_pairs, dtype=torch.int32, device=dev)
-    pair_of_row = torch.empty(n_pairs, dtype=torch.int32, device=dev)
-    native.call("plow_moe_align", table, n_pairs, e_base, e_local, grp_off, tile_prefix, row_of_pair, pair_of_row)
+    pair_of_row = torch.empty(n_pairs + shared_rows, dtype=torch.int32, device=dev)
+    native.call("plow_moe_align", table, n_pairs, e_base, e_local, grp_off, tile_prefix, row_of_pair, pair_of_row,
+                int(shared_rows), int(shared_tok_base), table.shape[1])
     return grp_off, tile_prefix, row_of_pair, pair_of_row
 
 
@@ -87,9 +92,11 @@ def moe_gather(xq, sx, pair_of_row, n_rows_dev, max_rows, top_k):
     return xs, sxs
 
 
-def moe_combine(y, shared, table, row_of_pair, T, H):
-    out = torch.empty(T, H, dtype=BF16, device=y.device)
-    native.call("plow_moe_combine", out, y, shared, table, row_of_pair, T, table.shape[1], H)
+def moe_combine(y, shared, table, row_of_pair, T, H, shared_base=None, out=None):
+    """``shared_base`` (int32 device scalar): the shared expert's rows start at y-row ``*shared_base`` of ``shared``."""
+    if out is None:
+        out = torch.empty(T, H, dtype=BF16, device=y.device)
+    native.call("plow_moe_combine", out, y, shared, table, row_of_pair, T, table.shape[1], H, shared_base)
     return out
 
 

@@ -50,7 +50,7 @@ class EpComm:
         self.e_local = self.E // world
         self.n_cta = n_cta
         self.deadline_ms = deadline_ms
-        self.Rmax = world * max_rows * self.k
+        self.Rmax = world * max_rows * self.k + max_rows      # routed rows from every rank + this rank's own rows for a stacked shared expert
         self.timing = None            # set to a dict to collect CUDA-event phase times (debug aid, eager mode only)
         if impl != "fused":
             return
@@ -69,8 +69,8 @@ class EpComm:
         self.lay = lay
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.cursor = torch.zeros(self.E + 1, dtype=I32, device=self.dev)   # +1: CTA counter of the push kernel
-        self.grp_off = torch.zeros(self.e_local + 1, dtype=I32, device=self.dev)
-        self.tile_prefix = torch.zeros(self.e_local + 1, dtype=I32, device=self.dev)
+        self.grp_off = torch.zeros(self.e_local + 2, dtype=I32, device=self.dev)        # +1: stacked shared expert
+        self.tile_prefix = torch.zeros(self.e_local + 2, dtype=I32, device=self.dev)
         self.pair_dest = torch.zeros(max_rows * self.k, dtype=I32, device=self.dev)
         a = EpArgs()
         ptrs = list(self.hdl.buffer_ptrs)
@@ -103,7 +103,7 @@ class EpComm:
         native.call("plow_ep_counts", ap, table, T * k, self.cursor)
         self._mark("counts")
         native.call("plow_ep_push", ap, table, T * k, k, xq, sx, sx.stride(0), self.cursor, self.grp_off, self.tile_prefix,
-                    self.pair_dest, self.n_cta)
+                    self.pair_dest, self.n_cta, T if ins.i[6] else 0)
         self._mark("push")
         st.scratch["ep_dispatched"] = ins.i[7]
 
@@ -142,6 +142,8 @@ class EpComm:
         y_out, h, table = (eng.tensor(st, ins.t[k]) for k in range(3))
         shared = eng.tensor(st, ins.t[5]) if ins.t[5] != 0xFFFF else None
         F = ins.i[3]
+        sg = bool(ins.i[6])               # shared expert stacked behind the local routed experts (group e_local)
+        ng = self.e_local + (1 if sg else 0)
         T, k, H = st.rows, self.k, self.H
         ap = C.addressof(self.args)
         if st.scratch.get("ep_dispatched") != ins.i[7]:
@@ -152,24 +154,24 @@ class EpComm:
         w2, s2 = eng.static_q[ins.t[4]]
         wait = (self.data_ctr_ptr, self.epoch.data_ptr(), self.world, self.deadline_ms)
         per = max(1, self.world * T * k // self.E)
-        R = self.world * T * k                      # rows this rank can receive for this program
+        R = self.world * T * k + (T if sg else 0)   # rows this rank can receive for this program
         rx, rsx, ry = self.recv_x[:R], self.recv_sx, self.y[:R]
         if per <= 64:
             bn = 32 if per <= 32 else 64
-            hq, shq = gemm_ops.gemm(rx, w1, sx=rsx, sw=s1, dual=True, n_out=F, n_experts=self.e_local, grp_off=self.grp_off,
+            hq, shq = gemm_ops.gemm(rx, w1, sx=rsx, sw=s1, dual=True, n_out=F, n_experts=ng, grp_off=self.grp_off,
                                     swap=True, bn=bn, quant_out=True, ld_syq=R, wait=wait)
             self._mark("gemm1")
-            gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=self.e_local, grp_off=self.grp_off, swap=True, bn=bn, out=ry)
+            gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=ng, grp_off=self.grp_off, swap=True, bn=bn, out=ry)
             self._mark("gemm2")
         else:
-            hb = gemm_ops.gemm(rx, w1, sx=rsx, sw=s1, dual=True, n_out=F, n_experts=self.e_local, grp_off=self.grp_off,
+            hb = gemm_ops.gemm(rx, w1, sx=rsx, sw=s1, dual=True, n_out=F, n_experts=ng, grp_off=self.grp_off,
                                tile_prefix=self.tile_prefix, swap=False, bn=64, wait=wait)
             hq, shq = rowops.quant_act(hb)
-            gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=self.e_local, grp_off=self.grp_off,
+            gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=ng, grp_off=self.grp_off,
                           tile_prefix=self.tile_prefix, swap=False, bn=128, out=ry)
         native.call("plow_ep_y_ready", ap)
         self._mark("y_ready")
-        native.call("plow_ep_combine", ap, y_out, shared, table, self.pair_dest, T, k)
+        native.call("plow_ep_combine", ap, y_out, shared, table, self.pair_dest, T, k, self.grp_off[self.e_local:] if sg else None)
         self._mark("combine")
 
     # ---- NCCL baseline arm ---------------------------------------------------------------------
@@ -182,27 +184,34 @@ class EpComm:
         tg = torch.empty(W * T, k, 2, dtype=I32, device=self.dev)
         dist.all_gather_into_tensor(hg, h.contiguous())
         dist.all_gather_into_tensor(tg, table.contiguous())
-        grp_off, tile_prefix, row_of_pair, pair_of_row = rowops.moe_align(tg, self.rank * self.e_local, self.e_local)
+        sg = bool(ins.i[6])               # shared expert stacked behind the local routed experts: its rows are this rank's tokens
+        ng = self.e_local + (1 if sg else 0)
+        n_rows = W * T * k + (T if sg else 0)
+        grp_off, tile_prefix, row_of_pair, pair_of_row = rowops.moe_align(tg, self.rank * self.e_local, self.e_local,
+                                                                          shared_rows=T if sg else 0, shared_tok_base=self.rank * T)
         xq, sx = rowops.quant_act(hg)
-        xs, sxs = rowops.moe_gather(xq, sx, pair_of_row, grp_off[self.e_local:], W * T * k, k)
+        xs, sxs = rowops.moe_gather(xq, sx, pair_of_row, grp_off[ng:], n_rows, k)
         w1, s1 = eng.static_q[ins.t[3]]
         w2, s2 = eng.static_q[ins.t[4]]
         per = max(1, W * T * k // self.E)
         if per <= 64:
             bn = 32 if per <= 32 else 64
-            hq, shq = gemm_ops.gemm(xs, w1, sx=sxs, sw=s1, dual=True, n_out=F, n_experts=self.e_local, grp_off=grp_off,
-                                    swap=True, bn=bn, quant_out=True, ld_syq=W * T * k)
-            yo = gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=self.e_local, grp_off=grp_off, swap=True, bn=bn)
+            hq, shq = gemm_ops.gemm(xs, w1, sx=sxs, sw=s1, dual=True, n_out=F, n_experts=ng, grp_off=grp_off,
+                                    swap=True, bn=bn, quant_out=True, ld_syq=n_rows)
+            yo = gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=ng, grp_off=grp_off, swap=True, bn=bn)
         else:
-            hb = gemm_ops.gemm(xs, w1, sx=sxs, sw=s1, dual=True, n_out=F, n_experts=self.e_local, grp_off=grp_off,
+            hb = gemm_ops.gemm(xs, w1, sx=sxs, sw=s1, dual=True, n_out=F, n_experts=ng, grp_off=grp_off,
                                tile_prefix=tile_prefix, swap=False, bn=64)
             hq, shq = rowops.quant_act(hb)
-            yo = gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=self.e_local, grp_off=grp_off, tile_prefix=tile_prefix,
+            yo = gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=ng, grp_off=grp_off, tile_prefix=tile_prefix,
                                swap=False, bn=128)
         part = rowops.moe_combine(yo, None, tg, row_of_pair, W * T, H)
         mine = torch.empty(T, H, dtype=BF16, device=self.dev)
         dist.reduce_scatter_tensor(mine, part)
-        if shared is not None:
+        if sg:
+            idx = grp_off[self.e_local:self.e_local + 1].long() + torch.arange(T, device=self.dev)
+            torch.add(mine, torch.index_select(yo, 0, idx), out=y_out)
+        elif shared is not None:
             torch.add(mine, shared, out=y_out)
         else:
             y_out.copy_(mine)

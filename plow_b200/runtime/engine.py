@@ -153,5 +153,14 @@ class EngineBase:
         raise NotImplementedError
 
     def kv_arrays(self) -> dict:                       # pragma: no cover - interface
-        """name -> page-indexed array of every KV / state tensor (for KV images)."""
+        """name -> page-indexed array of every KV tensor (for KV images and the host tier)."""
         raise NotImplementedError
+
+    def state_arrays(self) -> dict:
+        """name -> slot-indexed array of every recurrent-state tensor (empty for pure-attention models).  KV images
+        carry a sequence's state entry next to its pages."""
+        return {}
+
+    @property
+    def has_recurrent_state(self) -> bool:
+        return any(t.tclass == pk.TClass.STATE for t in self.packet.tensors)

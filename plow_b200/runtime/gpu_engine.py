@@ -185,8 +185,13 @@ class GpuEngine(EngineBase):
         max_rows = max(p.rows for p in pkt.programs)
         self.max_rows_all = max_rows
         n_slots = self.max_slots + 1
-        self.d_page_table = torch.zeros(n_slots, self.max_pages_per_seq, dtype=I32, device=dev)
-        self.d_page_table[self.scratch_slot, :] = self.scratch_page
+        # host mirror of the page table in pinned memory; rows touched since the last step are uploaded at the start of
+        # the next one (one async copy per row, or one for the whole table when many changed)
+        self.h_page_table = torch.zeros(n_slots, self.max_pages_per_seq, dtype=I32).pin_memory()
+        self.h_page_table[self.scratch_slot, :] = self.scratch_page
+        self.page_table = self.h_page_table.numpy()
+        self.d_page_table = self.h_page_table.to(dev)
+        self._dirty_slots: set = set()
         # step inputs: one pinned staging block + one device block, copied with a single H2D
         self.h_in = torch.zeros(4, max_rows, dtype=I32).pin_memory()
         self.d_in = torch.zeros(4, max_rows, dtype=I32, device=dev)      # ids, pos, seq, sample_rows
@@ -308,13 +313,12 @@ class GpuEngine(EngineBase):
 
     def _op_residual(self, st, ins):
         out, a, b = (self.tensor(st, ins.t[k]) for k in range(3))
-        torch.add(a, b, out=out)
+        native.call("plow_eltwise2", out, a, b, out.numel(), 0)
 
     def _op_glu(self, st, ins):
         # only reached when gated-mlp fusion is disabled at compile time and the interpreter is off
         out, g, u = (self.tensor(st, ins.t[k]) for k in range(3))
-        torch.mul(torch.nn.functional.silu(g.float()), u.float(), out=st.scratch.setdefault(("glu", ins.t[0]), torch.empty_like(out, dtype=F32)))
-        out.copy_(st.scratch[("glu", ins.t[0])])
+        native.call("plow_eltwise2", out, g, u, out.numel(), 1)
 
     def _op_gemm(self, st, ins):
         y, x = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])
@@ -442,9 +446,14 @@ class GpuEngine(EngineBase):
             dsa_ops.gather(cc, self.tensor(st, ins.t[7]), cache, scale, self.d_in[1], self.d_in[2], self.d_page_table)
             mla_ops.decode(q8, sq, cc.kv, cc.scale, cc.smax, cc.page_table, cc.slot_of, cc.kvlen, self._mla_ws, float(ins.f[0]), merge=False)
             kvlen = cc.kvlen
+            st.scratch["mla_items"] = False
         else:
+            # the work list depends on the rows' lengths only: the first dense attention of a walk builds it for all layers
+            if not st.scratch.get("mla_items"):
+                mla_ops.build_items(self.d_kvlen_row, T, self._mla_ws)
+                st.scratch["mla_items"] = True
             mla_ops.decode(q8, sq, cache, scale, self.kv_smax[layer], self.d_page_table, self.d_in[2], self.d_kvlen_row,
-                           self._mla_ws, float(ins.f[0]), merge=False)
+                           self._mla_ws, float(ins.f[0]), merge=False, build_items=False)
             kvlen = self.d_kvlen_row
         want = self._wants_q(st, ins.t[0])
         aq, saq = mla_ops.fold(self._mla_ws, kvlen, wuv, T, heads, ao, want_fp8=want)
@@ -551,39 +560,45 @@ class GpuEngine(EngineBase):
         y, h, table = (self.tensor(st, ins.t[k]) for k in range(3))
         shared = self.tensor(st, ins.t[5]) if ins.t[5] != pk.T_NONE else None
         E, e_local, k, F, ep = ins.i[0], ins.i[1], ins.i[2], ins.i[3], max(1, ins.i[4])
+        sg = bool(ins.i[6])          # the shared expert is group e_local of the stacked expert weights
         T, H = st.rows, self.spec.hidden
         fp8 = self.spec.weight_quant == "fp8_block128"
         if self.comm is not None and ep > 1:
             return self.comm.moe_experts(self, st, ins)
         e_base = self.rank * e_local if ep > 1 else 0
-        grp_off, tile_prefix, row_of_pair, pair_of_row = rowops.moe_align(table, e_base, e_local)
+        ng = e_local + (1 if sg else 0)
+        n_rows = T * k + (T if sg else 0)
+        grp_off, tile_prefix, row_of_pair, pair_of_row = rowops.moe_align(table, e_base, e_local, shared_rows=T if sg else 0)
         per = max(1, (T * k + e_local - 1) // e_local)
         swap = per <= 64
         if fp8:
             xq, sx = self._quant_of(st, ins.t[1], 0, H, h)
-            xs, sxs = rowops.moe_gather(xq, sx, pair_of_row, grp_off[e_local:], T * k, k)
+            xs, sxs = rowops.moe_gather(xq, sx, pair_of_row, grp_off[ng:], n_rows, k)
             w1, s1 = self.static_q[ins.t[3]]
             w2, s2 = self.static_q[ins.t[4]]
             if swap:
                 bn = 32 if per <= 32 else 64
-                hq, shq = gemm_ops.gemm(xs, w1, sx=sxs, sw=s1, dual=True, n_out=F, n_experts=e_local, grp_off=grp_off,
-                                        swap=True, bn=bn, quant_out=True, ld_syq=T * k)
-                yo = gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=e_local, grp_off=grp_off, swap=True, bn=bn)
+                hq, shq = gemm_ops.gemm(xs, w1, sx=sxs, sw=s1, dual=True, n_out=F, n_experts=ng, grp_off=grp_off,
+                                        swap=True, bn=bn, quant_out=True, ld_syq=n_rows)
+                yo = gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=ng, grp_off=grp_off, swap=True, bn=bn)
             else:
-                hb = gemm_ops.gemm(xs, w1, sx=sxs, sw=s1, dual=True, n_out=F, n_experts=e_local, grp_off=grp_off,
+                hb = gemm_ops.gemm(xs, w1, sx=sxs, sw=s1, dual=True, n_out=F, n_experts=ng, grp_off=grp_off,
                                    tile_prefix=tile_prefix, swap=False, bn=64)
                 hq, shq = rowops.quant_act(hb)
-                yo = gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=e_local, grp_off=grp_off, tile_prefix=tile_prefix,
+                yo = gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=ng, grp_off=grp_off, tile_prefix=tile_prefix,
                                    swap=False, bn=128)
         else:
             w1, w2 = self._bf16_weight(ins.t[3]), self._bf16_weight(ins.t[4])
             xs = h[(pair_of_row // k).long().clamp_(0, T - 1)]
             bn = 32 if per <= 32 else 64
-            hb = gemm_ops.gemm(xs, w1, dual=True, n_out=F, n_experts=e_local, grp_off=grp_off, tile_prefix=tile_prefix,
+            hb = gemm_ops.gemm(xs, w1, dual=True, n_out=F, n_experts=ng, grp_off=grp_off, tile_prefix=tile_prefix,
                                swap=swap, bn=bn if swap else 128)
-            yo = gemm_ops.gemm(hb, w2, n_out=H, n_experts=e_local, grp_off=grp_off, tile_prefix=tile_prefix, swap=swap,
+            yo = gemm_ops.gemm(hb, w2, n_out=H, n_experts=ng, grp_off=grp_off, tile_prefix=tile_prefix, swap=swap,
                                bn=bn if swap else 128)
-        native.call("plow_moe_combine", y, yo, shared, table, row_of_pair, T, k, H)
+        if sg:
+            native.call("plow_moe_combine", y, yo, yo, table, row_of_pair, T, k, H, grp_off[e_local:])
+        else:
+            native.call("plow_moe_combine", y, yo, shared, table, row_of_pair, T, k, H, None)
 
     HANDLERS = {
         Op.EMBED: "_op_embed", Op.RMSNORM: "_op_rmsnorm", Op.ADD_NORM: "_op_add_norm", Op.RESIDUAL: "_op_residual",
@@ -618,6 +633,7 @@ class GpuEngine(EngineBase):
 
     def _run_insts(self, st: _Prog) -> None:
         st.q.clear()
+        st.scratch["mla_items"] = False
         if self.device_interp and self.spec.dtype == "bf16":
             for lo, hi, on_device in self._interp_segments(st):
                 if on_device:
@@ -645,12 +661,33 @@ class GpuEngine(EngineBase):
         out.update({f"smax.{layer}": v for layer, v in self.kv_smax.items()})   # per-page scale bounds of fp8 latent caches
         return out
 
+    def _recover_after_device_status(self) -> None:
+        try:
+            torch.cuda.synchronize(self.device)
+            gemm_ops.reset_workspace(self.device)
+            native.status_word(self.device).zero_()
+            for st in self.progs.values():
+                st.graph = None
+        except Exception:
+            self.health = "dead"
+
+    def state_arrays(self) -> dict:
+        return {t.name: self.static[h] for h, t in enumerate(self.packet.tensors) if t.tclass == pk.TClass.STATE}
+
     # ---- step ----------------------------------------------------------------------------------
     def _sync_pages(self, slot: int) -> None:
         super()._sync_pages(slot)
-        pages = self.pool.seqs[slot].pages
-        if pages:
-            self.d_page_table[slot, :len(pages)] = torch.tensor(pages, dtype=I32).to(self.device, non_blocking=True)
+        self._dirty_slots.add(slot)
+
+    def _upload_pages(self) -> None:
+        if not self._dirty_slots:
+            return
+        if len(self._dirty_slots) * 8 >= self.h_page_table.shape[0]:
+            self.d_page_table.copy_(self.h_page_table, non_blocking=True)
+        else:
+            for slot in self._dirty_slots:
+                self.d_page_table[slot].copy_(self.h_page_table[slot], non_blocking=True)
+        self._dirty_slots.clear()
 
     def step(self, batch: TokenBatch) -> StepResult:
         rows, ns = batch.rows, int(batch.sample_rows.shape[0])
@@ -669,6 +706,7 @@ class GpuEngine(EngineBase):
         hin[3, ns:st.samples] = 0
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
+        self._upload_pages()
         self.d_in[:, :R].copy_(hin[:, :R], non_blocking=True)
         torch.add(self.d_in[1, :R], 1, out=self.d_kvlen_row[:R])
         try:
@@ -690,9 +728,13 @@ class GpuEngine(EngineBase):
             self.h_out[:st.samples].copy_(self.d_out_ids[:st.samples], non_blocking=True)
             ev1.record()
             ev1.synchronize()
+            native.check_status(self.device)
         except native.NativeLibraryError as e:
+            # a bounded wait ran out or a bounds check fired: the step failed, the context is fine.  Shared scratch
+            # that kernels only re-arm on a clean finish (split-K arrival counters) is zeroed and captured graphs
+            # are dropped, so the next step starts from a known state.
+            self._recover_after_device_status()
             raise EngineError(str(e), fatal=False)
         self.step_ms_last = ev0.elapsed_time(ev1)
-        native.check_status(self.device)
         logits = self.d_logits[:ns].float().cpu().numpy() if batch.want_logits else None
         return StepResult(ids=self.h_out[:ns].numpy().copy(), logits=logits, device_ms=self.step_ms_last)

@@ -77,6 +77,9 @@ def export_slot(engine: EngineBase, slot: int) -> KvImage:
     img = KvImage(engine.packet.content_hash.hex(), tokens)
     for name, arr in engine.kv_arrays().items():
         img.arrays[name] = _to_numpy(arr, pages)
+    # recurrent state (gated delta rule: conv history + S matrix) is per slot, not per page
+    for name, arr in engine.state_arrays().items():
+        img.arrays["slot/" + name] = _to_numpy(arr, [slot])
     return img
 
 
@@ -84,6 +87,9 @@ def import_slot(engine: EngineBase, slot: int, img: KvImage) -> int:
     """Seat ``img`` in ``slot``; returns how many tokens were already cached on this engine."""
     if img.packet_hash != engine.packet.content_hash.hex():
         raise EngineError("KV image belongs to a different packet")
+    state = engine.state_arrays()
+    if state and any("slot/" + n not in img.arrays for n in state):
+        raise EngineError("KV image carries no recurrent state for this packet")
     cached = engine.begin_slot(slot, img.tokens)
     engine.reserve(slot, len(img.tokens) + 1)
     first = cached // PAGE                      # pages fully covered by the destination's prefix cache stay untouched
@@ -91,5 +97,7 @@ def import_slot(engine: EngineBase, slot: int, img: KvImage) -> int:
     if pages:
         for name, arr in engine.kv_arrays().items():
             _from_numpy(arr, pages, img.arrays[name][first:img.n_pages])
+    for name, arr in state.items():
+        _from_numpy(arr, [slot], img.arrays["slot/" + name])
     engine.commit(slot, img.tokens[cached:])
     return cached

@@ -170,6 +170,8 @@ class ModelMux:
         self._last_was_prefill = False
         self._n = 0
         self.draining = False
+        self._drain_deadline = None          # set by drain(); acted on by the dispatcher thread
+        self._submit_lock = threading.Lock()
         self._arrivals: list = []          # arrival times of recent requests (rate estimator)
         self.pd_target: "ModelMux | None" = None     # prefill/decode disaggregation: where finished prefills continue
         self.adopt_q: "queue.Queue" = queue.Queue()  # (request, KV image) pairs handed over by a prefill mux
@@ -186,11 +188,14 @@ class ModelMux:
             self._thread.join(timeout=10)
 
     def submit(self, prompt: list, params: GenParams, rid: str | None = None) -> Request:
-        self._n += 1
-        req = Request(rid=rid or f"req-{self._n}", prompt=list(prompt), params=params)
+        with self._submit_lock:             # handlers of several HTTP worker threads submit concurrently
+            self._n += 1
+            n = self._n
+        req = Request(rid=rid or f"req-{n}", prompt=list(prompt), params=params)
         if params.deadline_ms:
             req.deadline = req.arrived + params.deadline_ms / 1e3
-        self._arrivals.append(req.arrived)
+        with self._submit_lock:
+            self._arrivals.append(req.arrived)
         if self.engine.health == EngineHealth.DEAD:
             req.out.put(Chunk("error", error="engine is dead", finish_reason="error"))
             return req
@@ -224,8 +229,18 @@ class ModelMux:
         """Stop admitting, wait for live requests; preempt (finish as `length`) after the timeout."""
         self.draining = True
         t0 = time.monotonic()
+        running = self._thread is not None and self._thread.is_alive()
+        if running:
+            # slots and page tables belong to the dispatcher thread: after the deadline IT finishes what is still live
+            self._drain_deadline = t0 + timeout_s
+            while (self.live or self.waiting or not self.ingress.empty()) and time.monotonic() - t0 < timeout_s + 5.0 \
+                    and self._thread.is_alive():
+                time.sleep(0.005)
+            self._drain_deadline = None
+            return not self.live
         while (self.live or self.waiting or not self.ingress.empty()) and time.monotonic() - t0 < timeout_s:
-            time.sleep(0.005)
+            if not self.tick():
+                break
         for r in list(self.live.values()):
             self._finish(r, "preempted")
         return not self.live
@@ -241,6 +256,11 @@ class ModelMux:
                         pass
             except EngineError as e:
                 self._on_engine_error(e)
+            except Exception as e:      # a scheduler bug must not leave every request hanging behind a dead thread
+                self.metrics.inc("dispatcher_errors")
+                self._on_engine_error(EngineError(f"dispatcher: {type(e).__name__}: {e}", fatal=False))
+                if self.engine.health == EngineHealth.HEALTHY:
+                    self.engine.health = EngineHealth.DEGRADED
 
     def tick(self) -> bool:
         """One scheduling step; returns False when there was nothing to do."""
@@ -249,6 +269,13 @@ class ModelMux:
                 self.waiting.append(self.ingress.get_nowait())
             except queue.Empty:
                 break
+        if self._drain_deadline is not None and time.monotonic() > self._drain_deadline:
+            for r in list(self.live.values()):
+                self._finish(r, "preempted")
+            for r in self.waiting:
+                r.out.put(Chunk("done", text="", finish_reason="preempted", usage=dict(prompt_tokens=len(r.prompt), completion_tokens=len(r.generated), total_tokens=len(r.prompt) + len(r.generated))))
+            self.waiting = []
+            return False
         self._shed_expired()
         self._adopt()
         self._admit()
@@ -331,8 +358,18 @@ class ModelMux:
             toks = r.all_tokens()
             need_pages = (len(toks) + 1 + PAGE - 1) // PAGE
             headroom = len(self.live) * ((self.cfg.reserve_tokens + PAGE - 1) // PAGE)
-            if need_pages + headroom > eng.pool.available() + eng.pool.cached_prefix_len(toks) // PAGE:
-                break
+            # pages are reserved lazily, chunk by chunk: what seated requests have yet to reserve for the rest of their
+            # prompts is spoken for, or two long prompts get admitted against the same free pages
+            owed = 0
+            for q in self.live.values():
+                want = (q.pf_len + 1 + PAGE - 1) // PAGE
+                have = len(eng.pool.seqs[q.slot].pages) if q.slot in eng.pool.seqs else 0
+                owed += max(0, want - have)
+            if need_pages + headroom + owed > eng.pool.available() + eng.pool.cached_prefix_len(toks) // PAGE:
+                if not self.live and need_pages <= eng.pool.n_pages:
+                    pass            # nothing else is running: the request gets the pool to itself
+                else:
+                    break
             self.waiting.pop(0)
             slot = self.free_slots.pop()
             try:
@@ -371,6 +408,8 @@ class ModelMux:
         for r in order:
             if budget <= 0 or len(spans) >= eng.buckets.get("max_seqs", 64):
                 break
+            if r.slot < 0 or self.live.get(r.slot) is not r:
+                continue            # preempted earlier in this tick to make room
             toks = r.all_tokens()[:r.pf_len]
             n = min(budget, r.pf_len - r.done_prefill)
             if n <= 0:
@@ -391,6 +430,8 @@ class ModelMux:
             spans.append((r, start, n, final, toks))
             budget -= n
             r.waited_ticks = 0
+        if any(sp[0].slot < 0 or self.live.get(sp[0].slot) is not sp[0] for sp in spans):
+            return                  # a request already packed lost its slot to a preemption: re-plan next tick
         if not spans:
             return
         # riders: one row each, as long as sample slots and rows remain
@@ -399,6 +440,8 @@ class ModelMux:
         for r in sorted(riders, key=lambda r: r.slot):
             if len(sample_rows) + 1 > max_samples - 1 or len(ids) + 1 > eng.max_rows(False):
                 break
+            if r.slot < 0 or self.live.get(r.slot) is not r:
+                continue            # preempted earlier in this tick
             n_ctx = len(r.prompt) + len(r.generated)
             try:
                 eng.reserve(r.slot, n_ctx + 1)
@@ -450,6 +493,8 @@ class ModelMux:
         max_samples = eng.buckets.get("max_seqs", 64)
         if not reqs or any(not r.params.greedy for r in reqs) or len(reqs) * (depth + 1) > max_samples:
             return False
+        if getattr(eng, "has_recurrent_state", False):
+            return False            # rejected draft rows would already have advanced the per-slot state in place
         drafter = getattr(self, "_drafter", None) or NgramDrafter()
         self._drafter = drafter
         ids, pos, seq, spans = [], [], [], []

@@ -84,5 +84,7 @@ def materialize(name: str, ent, recipe: dict | None, ckpt: Checkpoint, tp: int =
         for e in expert_range(recipe["n"], recipe.get("ep", 1), recipe.get("rank", 0)):
             for part in recipe["parts"]:
                 rows.append(ckpt.get(f"{recipe['prefix']}.{e}.{part}.weight"))
+        for name in recipe.get("tail", []):      # shared expert stacked behind the routed ones (replicated on every rank)
+            rows.append(ckpt.get(name))
         return torch.cat(rows, dim=0).contiguous()
     raise ValueError(f"unknown derived-weight recipe '{recipe['op']}'")
