@@ -108,7 +108,7 @@ __global__ void ep_push_kernel(EpArgs a, const int2* table, int n_pairs, int top
     if (!wait_ge(reinterpret_cast<const uint32_t*>(a.peer[a.me] + a.L.cnt_flag) + threadIdx.x * 32, ep, a.deadline_ns)) fail = 1;
   }
   __syncthreads();
-  if (fail) { if (threadIdx.x == 0) atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); return; }
+  if (fail) { if (threadIdx.x == 0) atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT | kTagEp); return; }
   if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 4);
   const int* call = reinterpret_cast<const int*>(a.peer[a.me] + a.L.cnt_all);
   for (int i = threadIdx.x; i < a.W * a.E; i += blockDim.x) cnt[i] = call[i];
@@ -133,7 +133,7 @@ __global__ void ep_push_kernel(EpArgs a, const int2* table, int n_pairs, int top
     }
     grp_off[a.e_local] = off; tile_prefix[a.e_local] = tiles;
     if (shared_rows > 0) { grp_off[a.e_local + 1] = off + shared_rows; tile_prefix[a.e_local + 1] = tiles + ((shared_rows + 127) >> 7); }
-    if (off + shared_rows > a.Rmax) atomicCAS(a.status, 0, PLOW_ERR_BOUNDS);
+    if (off + shared_rows > a.Rmax) atomicCAS(a.status, 0, PLOW_ERR_BOUNDS | kTagEp);
   }
   __shared__ int routed_rows;     // rows this rank receives for its routed experts (same value in every CTA)
   if (threadIdx.x == 0) {
@@ -162,7 +162,7 @@ __global__ void ep_push_kernel(EpArgs a, const int2* table, int n_pairs, int top
     if (lane == 0) idx = atomicAdd(&cursor[e], 1);
     idx = __shfl_sync(0xffffffffu, idx, 0);
     const int row = base[e] + idx;
-    if (row >= a.Rmax) { if (lane == 0) atomicCAS(a.status, 0, PLOW_ERR_BOUNDS); continue; }
+    if (row >= a.Rmax) { if (lane == 0) atomicCAS(a.status, 0, PLOW_ERR_BOUNDS | kTagEp); continue; }
     const int tok = p / top_k;
     const uint4* src = reinterpret_cast<const uint4*>(xq + static_cast<size_t>(tok) * a.H);
     uint4* dst = reinterpret_cast<uint4*>(a.peer[d] + a.L.recv_x + static_cast<size_t>(row) * a.H);
@@ -216,7 +216,7 @@ __global__ void ep_combine_kernel(EpArgs a, __nv_bfloat16* out, const __nv_bfloa
     if (!wait_ge(reinterpret_cast<const uint32_t*>(a.peer[a.me] + a.L.y_flag) + threadIdx.x * 32, ep, a.deadline_ns)) fail = 1;
   }
   __syncthreads();
-  if (fail) { if (threadIdx.x == 0) atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); return; }
+  if (fail) { if (threadIdx.x == 0) atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT | kTagEp); return; }
   if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 8);
   // Slot metadata first, then all of a thread's remote loads at once: the eight pulls of a 16-byte unit are
   // independent, so they cost one NVLink round trip instead of eight.  One unit per thread (grid.y covers H).
@@ -274,7 +274,7 @@ __global__ void ep_combine_kernel(EpArgs a, __nv_bfloat16* out, const __nv_bfloa
 __global__ void ep_wait_probe_kernel(const uint32_t* flag, uint32_t target, unsigned long long deadline_ns, int* status) {
   plow::pdl_launch_dependents();
   plow::pdl_wait();
-  if (threadIdx.x == 0 && !wait_ge(flag, target, deadline_ns)) atomicCAS(status, 0, PLOW_ERR_PEER_WAIT);
+  if (threadIdx.x == 0 && !wait_ge(flag, target, deadline_ns)) atomicCAS(status, 0, PLOW_ERR_PEER_WAIT | kTagEp);
 }
 
 inline int ok() { cudaError_t e = cudaGetLastError(); return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e); }

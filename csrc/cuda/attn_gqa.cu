@@ -79,7 +79,7 @@ __global__ void gqa_build_items(const int* seq, const int* pos, int rows, int tq
     ns = (tiles + per - 1) / per;
     for (int j = 0; j < nt; ++j) row_ns[r + j] = ns;
     const int base = atomicAdd(n_items, nkv * ns);
-    if (base + nkv * ns > cap) { atomicCAS(status, 0, PLOW_ERR_BOUNDS); continue; }
+    if (base + nkv * ns > cap) { atomicCAS(status, 0, PLOW_ERR_BOUNDS | kTagGqa); continue; }
     for (int h = 0; h < nkv; ++h)
       for (int s = 0; s < ns; ++s)
         items[base + h * ns + s] = GqaItem{r, nt, h, s, tile_lo + s * per, min(per, tiles - s * per), seq[r], ns};
@@ -142,7 +142,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
       bool ok = true;
       for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x, ++item_it) {
         const GqaItem w = a.items[it];
-        if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT); break; }
+        if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagGqa); break; }
         mbar_expect_tx(q_full, Cfg::kQBytes);
         for (int c = 0; c < Cfg::kSlabs; ++c) tma_load_3d(q_smem + c * 16384, &tm_q, c * 64, w.kvh * a.group, w.r0, q_full);
         const int* pt = a.page_table + static_cast<size_t>(w.slot) * a.max_pages;
@@ -152,7 +152,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
           const int page = page_next;
           if (i + 1 < w.ntiles) page_next = pt[w.tile0 + i + 1];
           if (!mbar_wait(&kv_empty[s], ((kv_it / Cfg::kStages) & 1) ^ 1, abort_flag)) {
-            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT); ok = false; break;
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagGqa); ok = false; break;
           }
           uint8_t* st = kv_smem + s * Cfg::kStageBytes;
           mbar_expect_tx(&kv_full[s], Cfg::kStageBytes);
@@ -172,7 +172,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
       bool ok = true;
       auto issue_qk = [&](uint32_t kvi, uint32_t ti) -> bool {
         const int s = kvi % Cfg::kStages;
-        if (!mbar_wait(&kv_full[s], (kvi / Cfg::kStages) & 1, abort_flag)) { atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); return false; }
+        if (!mbar_wait(&kv_full[s], (kvi / Cfg::kStages) & 1, abort_flag)) { atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT | kTagGqa); return false; }
         tc_fence_after();
         // S buffer ti&1 (and the P written over it) was last read by P.V of tile ti-2, issued
         // before this point; the tensor pipe executes in order.
@@ -189,7 +189,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
       };
       for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x, ++item_it) {
         const GqaItem w = a.items[it];
-        if (!mbar_wait(q_full, item_it & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); break; }
+        if (!mbar_wait(q_full, item_it & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT | kTagGqa); break; }
         tc_fence_after();
         if (!issue_qk(kv_it, tile_it)) { *abort_flag = 1; break; }
         for (int i = 0; i < w.ntiles; ++i) {
@@ -199,8 +199,8 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
             tc_commit(q_empty);   // all QK^T of this item are issued: Q may be overwritten once they retire
           }
           const uint32_t ti = tile_it + i;
-          if (i == 0 && !mbar_wait(o_free, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_FREE_WAIT); ok = false; break; }
-          if (!mbar_wait(&p_full[ti & 1], (ti >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
+          if (i == 0 && !mbar_wait(o_free, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_FREE_WAIT | kTagGqa); ok = false; break; }
+          if (!mbar_wait(&p_full[ti & 1], (ti >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagGqa); ok = false; break; }
           tc_fence_after();
           const int s = (kv_it + i) % Cfg::kStages;
           const uint32_t pt = tm_s + (ti & 1) * 64;   // P: 32 columns = 64 tokens of bf16
@@ -233,7 +233,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
       float m = -1e30f, l = 0.f;
       for (int i = 0; i < w.ntiles; ++i) {
         const uint32_t ti = tile_it + i;
-        if (!mbar_wait(&s_full[ti & 1], (ti >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
+        if (!mbar_wait(&s_full[ti & 1], (ti >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagGqa); ok = false; break; }
         tc_fence_after();
         if (warp_active) {
           uint32_t sv[64];
@@ -270,7 +270,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
             m = m_new;
             if (i > 0) {
               // the accumulator must be quiescent: P.V of the previous tile has retired
-              if (!mbar_wait(&pv_done[(ti - 1) & 1], ((ti - 1) >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
+              if (!mbar_wait(&pv_done[(ti - 1) & 1], ((ti - 1) >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagGqa); ok = false; break; }
               tc_fence_after();
 #pragma unroll 1
               for (int c = 0; c < HD; c += 32) {
@@ -307,7 +307,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
       if (!ok) break;
       // ---- finalize: O / l, written directly (one split) or as a partial with its log-sum-exp
       const uint32_t ti_last = tile_it + w.ntiles - 1;
-      if (!mbar_wait(&pv_done[ti_last & 1], (ti_last >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); break; }
+      if (!mbar_wait(&pv_done[ti_last & 1], (ti_last >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagGqa); break; }
       tc_fence_after();
       if (warp_active) {
         const bool row_ok = li < n_valid;

@@ -154,7 +154,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
       bool ok = true;
       for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x, ++item_it) {
         const MlaItem w = a.items[it];
-        if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT); break; }
+        if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagMlaDecode); break; }
         mbar_expect_tx(q_full, kQBytes);
         tma_load_3d(q_smem, &tm_qr, 512, w.req, 0, q_full);
         const int* pt = a.page_table + static_cast<size_t>(a.slot_of[w.req]) * a.max_pages;
@@ -166,7 +166,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
           const int page = page_next;
           if (i + 1 < w.ntiles) page_next = pt[w.tile0 + i + 1];
           if (!mbar_wait(&kv_empty[s], ((kv_it / kMlaStages) & 1) ^ 1, abort_flag)) {
-            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT); ok = false; break;
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagMlaDecode); ok = false; break;
           }
           uint8_t* st = kv_smem + s * kKvStageBytes;
           mbar_expect_tx(&kv_full[s], kKvTileBytes + 256 + 16);
@@ -186,7 +186,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
       bool ok = true;
       auto issue_qk = [&](uint32_t kvi, uint32_t ti) -> bool {
         const int s = kvi % kMlaStages;
-        if (!mbar_wait(&kv_full[s], (kvi / kMlaStages) & 1, abort_flag)) { atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); return false; }
+        if (!mbar_wait(&kv_full[s], (kvi / kMlaStages) & 1, abort_flag)) { atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT | kTagMlaDecode); return false; }
         tc_fence_after();
         // S buffer ti&1 (and the P written over it) was last read by P.V of tile ti-2, which was
         // issued before this point and executes in order ahead of these MMAs.
@@ -206,8 +206,8 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
       };
       for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x, ++item_it) {
         const MlaItem w = a.items[it];
-        if (!mbar_wait(q_full, item_it & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); break; }
-        if (!mbar_wait(qt_full, item_it & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); break; }
+        if (!mbar_wait(q_full, item_it & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT | kTagMlaDecode); break; }
+        if (!mbar_wait(qt_full, item_it & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagMlaDecode); break; }
         tc_fence_after();
         if (!issue_qk(kv_it, tile_it)) { *abort_flag = 1; break; }
         for (int i = 0; i < w.ntiles; ++i) {
@@ -217,8 +217,8 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
             tc_commit(q_empty);   // every QK^T of this item is issued: Q may be overwritten once they retire
           }
           const uint32_t ti = tile_it + i;
-          if (i == 0 && !mbar_wait(o_free, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_FREE_WAIT); ok = false; break; }
-          if (!mbar_wait(&p_full[ti & 1], (ti >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
+          if (i == 0 && !mbar_wait(o_free, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_FREE_WAIT | kTagMlaDecode); ok = false; break; }
+          if (!mbar_wait(&p_full[ti & 1], (ti >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagMlaDecode); ok = false; break; }
           tc_fence_after();
           const int s = (kv_it + i) % kMlaStages;
           const uint32_t pt = tm_s + (ti & 1) * 64;   // P: 16 columns = 64 tokens of e4m3
@@ -265,7 +265,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
         // latent Q of this (head, request) into TMEM: this thread owns bytes [256 ch, 256 ch + 256)
         // of the row, i.e. TMEM columns [64 ch, 64 ch + 64).  The previous item's QK^T must have
         // retired before its Q is overwritten.
-        if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_FREE_WAIT); ok = false; break; }
+        if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_FREE_WAIT | kTagMlaDecode); ok = false; break; }
         tc_fence_after();
         const uint4* qrow = reinterpret_cast<const uint4*>(a.q8 + (static_cast<size_t>(li) * a.T + w.req) * kMlaRow + ch * 256);
         uint32_t qv[64];
@@ -284,7 +284,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
         PLOW_TRACE(if (tr) a.trace[ti * 8 + 0] = clock64();)
         // (a) per-token scales (they arrived with the KV tile, usually long before S is ready)
         const int s = (kv_it + i) % kMlaStages;
-        if (!mbar_wait(&kv_full[s], ((kv_it + i) / kMlaStages) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); ok = false; break; }
+        if (!mbar_wait(&kv_full[s], ((kv_it + i) / kMlaStages) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT | kTagMlaDecode); ok = false; break; }
         const float* sk_base = reinterpret_cast<const float*>(kv_smem + s * kKvStageBytes + kKvTileBytes);
         const float4* sk4 = reinterpret_cast<const float4*>(sk_base) + ch * 8;
         const float skmax = fmaxf(sk_base[64], 1e-30f);   // upper bound of this page's scales, kept by the cache writer
@@ -296,7 +296,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
           skv[4 * j] = k4.x; skv[4 * j + 1] = k4.y; skv[4 * j + 2] = k4.z; skv[4 * j + 3] = k4.w;
         }
         // (b) scores
-        if (!mbar_wait(&s_full[ti & 1], (ti >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
+        if (!mbar_wait(&s_full[ti & 1], (ti >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagMlaDecode); ok = false; break; }
         tc_fence_after();
         PLOW_TRACE(if (tr) a.trace[ti * 8 + 1] = clock64();)
         uint32_t sv[32];
@@ -320,7 +320,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
         float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
         float omx, unused0;
         PLOW_TRACE(if (tr) a.trace[ti * 8 + 2] = clock64();)
-        if (!exchange(mx, 0.f, omx, unused0)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
+        if (!exchange(mx, 0.f, omx, unused0)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagMlaDecode); ok = false; break; }
         mx = fmaxf(mx, omx);
         PLOW_TRACE(if (tr) a.trace[ti * 8 + 3] = clock64();)
         // Lazy rescaling with one running offset M = m + log2(SK): probabilities are formed as
@@ -350,7 +350,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
             // accumulator must be quiescent: P.V of the previous tile has retired.  QK^T of this
             // tile was issued after P.V of tile ti-2, so at most tile ti-1 is pending on its
             // parity's barrier and the phase below cannot alias.
-            if (!mbar_wait(&pv_done[(ti - 1) & 1], ((ti - 1) >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
+            if (!mbar_wait(&pv_done[(ti - 1) & 1], ((ti - 1) >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagMlaDecode); ok = false; break; }
             tc_fence_after();
 #pragma unroll 1
             for (int c = 0; c < 128; c += 32) {
@@ -411,10 +411,10 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
       if (!ok) break;
       // ---- finalize this item: O * SK / l, log-sum-exp in the log2 domain
       float ol, unused;
-      if (!exchange(l, 0.f, ol, unused)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); break; }
+      if (!exchange(l, 0.f, ol, unused)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagMlaDecode); break; }
       l += ol;
       const uint32_t ti_last = tile_it + w.ntiles - 1;
-      if (!mbar_wait(&pv_done[ti_last & 1], (ti_last >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); break; }
+      if (!mbar_wait(&pv_done[ti_last & 1], (ti_last >> 1) & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagMlaDecode); break; }
       tc_fence_after();
       const float fin = l > 0.f ? 1.0f / l : 0.f;
       const size_t obase = ((static_cast<size_t>(w.req) * a.max_splits + w.split) * kMlaHeads + li) * kMlaLatent + w.half * 256 + ch * 128;

@@ -174,7 +174,7 @@ dsa_score_kernel(float* scores, int ld_scores, const float* w, const float* ksca
       for (int k = 0; k < 4; ++k) tc_mma_f8(tm, kd + 2 * k, qd + 2 * k, idesc, k > 0);
     } else {
       *abort_flag = 1;
-      atomicCAS(status, 0, PLOW_ERR_TMA_WAIT);
+      atomicCAS(status, 0, PLOW_ERR_TMA_WAIT | kTagDsa);
     }
     tc_commit(mma_bar);
   }
@@ -196,7 +196,7 @@ dsa_score_kernel(float* scores, int ld_scores, const float* w, const float* ksca
       scores[static_cast<size_t>(r) * ld_scores + t] = acc * kscale[static_cast<size_t>(page) * kIdxPage + (t % kIdxPage)];
     }
   } else if (threadIdx.x == 0) {
-    atomicCAS(status, 0, PLOW_ERR_TMEM_WAIT);
+    atomicCAS(status, 0, PLOW_ERR_TMEM_WAIT | kTagDsa);
   }
   tc_fence_before();
   __syncthreads();

@@ -20,7 +20,9 @@ GemmArgs to_args(const PlowGemmDesc& d) {
   a.yq = d.yq; a.syq = d.syq; a.grp_off = d.grp_off; a.tile_prefix = d.tile_prefix;
   a.status = d.status; a.M = d.M; a.N = d.N; a.K = d.K; a.ldy = d.ldy; a.ld_sx = d.ld_sx;
   a.ld_syq = d.ld_syq; a.E = d.E; a.out_f32 = d.out_f32; a.out_scale = d.out_scale;
-  a.ws = d.ws; a.ws_ctr = d.ws_ctr; a.splits = (d.swap && d.E == 0 && d.ws && d.ws_ctr) ? d.splits : 1;
+  a.ws = d.ws; a.ws_ctr = d.ws_ctr;
+  a.stream = (d.stream && d.swap && d.ws && d.ws_ctr && d.ar_world <= 1) ? 1 : 0;
+  a.splits = (!a.stream && d.swap && d.E == 0 && d.ws && d.ws_ctr) ? d.splits : 1;
   for (int i = 0; i < 8; ++i) a.ar_peer[i] = static_cast<uint8_t*>(d.ar_peer[i]);
   a.ar_part_ofs = d.ar_part_ofs; a.ar_flag_ofs = d.ar_flag_ofs; a.ar_done_ofs = d.ar_done_ofs; a.ar_y_ofs = d.ar_y_ofs;
   a.ar_epoch = static_cast<uint32_t*>(d.ar_epoch); a.ar_world = d.ar_world; a.ar_me = d.ar_me;
@@ -55,7 +57,7 @@ extern "C" int plow_gemm(const PlowGemmDesc* d, void* stream) {
   if (d->ar_world > 1 && d->ar_oneshot == 2 && !d->ar_mc) return -8;
   if (d->ar_world > 1 && d->ar_oneshot == 1 &&
       static_cast<uint64_t>((d->N + 127) / 128) * d->ar_world * 128 * d->bn * 2 > d->ar_half_bytes) return -8;
-  if (d->swap && d->E == 0 && d->splits > 1 && d->ws && d->ws_ctr) {
+  if (d->swap && d->E == 0 && d->splits > 1 && d->ws && d->ws_ctr && !d->stream) {
     // the CTAs of a split-K tile wait for one another: all tiles x splits of them must be resident at once
     const long long tiles = static_cast<long long>((d->N + 127) / 128) * ((d->M + d->bn - 1) / d->bn);
     if (tiles > 256 || tiles * d->splits > plow::sm_count()) return -9;

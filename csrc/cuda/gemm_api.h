@@ -30,7 +30,7 @@ typedef struct PlowGemmDesc {
   float* ws;              // split-K workspace (fp32) and per-tile counters (zeroed once by the caller)
   int32_t* ws_ctr;
   int32_t splits;         // >1: split-K over CTAs (dense swap mode only)
-  int32_t ws_pad;
+  int32_t stream;         // 1: stream scheduling (swap mode): equal K-block ranges per CTA, partials through ws / ws_ctr
   // fused all-reduce over tensor-parallel ranks (swap mode, M <= bn, not dual): symmetric region of every
   // rank, byte offsets of the partial / flag / arrival / output areas inside it, launch-epoch word
   void* ar_peer[8];

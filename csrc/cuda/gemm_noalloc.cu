@@ -68,6 +68,7 @@ extern "C" int plow_gemm_splitk_noalloc(const void* x, const void* w, void* y, i
   a.ws = reinterpret_cast<float*>(scratch);
   a.ws_ctr = reinterpret_cast<int*>(scratch + kWsBytes);
   a.splits = splits;
+  a.stream = 0;
   if (bn == 32) return launch_gemm_tc<32, false, false, true>(a, K, K, N, stream);
   if (bn == 64) return launch_gemm_tc<64, false, false, true>(a, K, K, N, stream);
   return launch_gemm_tc<128, false, false, true>(a, K, K, N, stream);

@@ -50,6 +50,12 @@ struct GemmArgs {
   float* ws;
   int* ws_ctr;
   int splits;
+  // stream scheduling (swap mode): the linear (tile, K block) space is cut into equal contiguous ranges, one per
+  // CTA, so every SM streams the same number of weight bytes whatever the tile count.  A tile whose K range is
+  // shared is finished by the CTA that holds its first K blocks (the last thing that CTA does); the CTAs holding
+  // the later K blocks run them first thing and publish fp32 partials to `ws` ([CTA][column][128 lanes]) with a
+  // flag in `ws_ctr` ([CTA] x 32 ints), so the finishing CTA practically never waits.
+  int stream;
   // fused all-reduce (tensor-parallel row-parallel GEMM, swap mode): this rank's partial tiles are
   // reduced through peer memory from inside the kernel, see the `ar_*` phase at the end of the kernel
   uint8_t* ar_peer[8];    // symmetric region of every rank (peer-mapped), NULL world = off
@@ -86,9 +92,11 @@ struct GemmCfg {
   static constexpr int kQT = (DUAL && !SWAP) ? 2 : 1;   // BN-row tiles per stage
   static constexpr int kStageBytes = kPT * kStageBytesP + kQT * BN * 128;
   static constexpr int kAccCols = BN * (DUAL ? 2 : 1);
-  // accumulator buffers in TMEM: two for bf16 (tile i+1 runs while tile i drains), up to
-  // four K-block partials for fp8 so the promotion warps may lag the MMA warp
-  static constexpr int kNBuf = (FP8 && 4 * kAccCols <= 512) ? 4 : 2;
+  // accumulator buffers in TMEM: two for bf16 (tile i+1 runs while tile i drains); for fp8 as many K-block
+  // partials as TMEM holds (up to eight), so the MMA warp keeps consuming stages while the promotion warps are
+  // away writing a finished tile (measured: the end of a tile takes the four warps 2.5-9 us at decode shapes,
+  // which four buffers could not cover: the tensor pipe and with it the weight stream stalled at every tile)
+  static constexpr int kNBuf = !FP8 ? 2 : (8 * kAccCols <= 512 ? 8 : (4 * kAccCols <= 512 ? 4 : 2));
   static constexpr int kTmemCols =
       kNBuf * kAccCols <= 32 ? 32 : kNBuf * kAccCols <= 64 ? 64 : kNBuf * kAccCols <= 128 ? 128
                                                    : kNBuf * kAccCols <= 256 ? 256 : 512;
@@ -105,6 +113,8 @@ struct Tile {
   int feat0;          // first output feature of the tile within N
   int kb0, kb1;       // K-block range of this work item
   int tile_id, ks;    // split-K: output tile index and split index
+  int contrib;        // stream scheduling: this piece only publishes its partial sums
+  int n_follow;       // stream scheduling: CTAs after this one that hold later K blocks of the tile
 };
 
 template <int BN, bool DUAL, bool SWAP>
@@ -113,12 +123,60 @@ struct TileSched {
   int item, sub;
   int n_wt;  // weight tiles per expert
   int KB;
+  // stream scheduling
+  long long s_pos, s_hi;     // next iteration to hand out / end of this CTA's range (units of K blocks)
+  long long s_per;           // iterations per CTA
+  int s_e, s_pre;            // grouped: running expert and the number of work units before it
+  __device__ int subtiles(int e) const { return (a.grp_off[e + 1] - a.grp_off[e] + BN - 1) / BN; }
   __device__ TileSched(const GemmArgs& a_, int KB_) : a(a_), item(blockIdx.x), sub(0), KB(KB_) {
     n_wt = SWAP ? (a.N + 127) / 128 : (a.N + BN - 1) / BN;
+    s_pos = s_hi = 0; s_per = 1; s_e = 0; s_pre = 0;
+    if (SWAP && a.stream) {
+      long long units;
+      if (a.E == 0) {
+        units = static_cast<long long>((a.M + BN - 1) / BN) * n_wt;
+      } else {
+        units = 0;
+        for (int e = 0; e < a.E; ++e) units += static_cast<long long>(subtiles(e)) * n_wt;
+      }
+      const long long iters = units * KB;
+      s_per = (iters + gridDim.x - 1) / gridDim.x;
+      if (s_per < 1) s_per = 1;
+      s_pos = static_cast<long long>(blockIdx.x) * s_per;
+      if (s_pos > iters) s_pos = iters;
+      s_hi = s_pos + s_per < iters ? s_pos + s_per : iters;
+    }
+  }
+  __device__ bool next_stream(Tile& t) {
+    if (s_pos >= s_hi) return false;
+    const int nw_per = DUAL ? 2 * a.N : a.N;
+    const long long u = s_pos / KB;
+    const long long u0 = u * KB;
+    t.kb0 = static_cast<int>(s_pos - u0);
+    t.kb1 = s_hi - u0 < KB ? static_cast<int>(s_hi - u0) : KB;
+    s_pos = u0 + t.kb1;
+    t.contrib = t.kb0 > 0;
+    t.n_follow = 0;
+    if (t.kb0 == 0 && t.kb1 < KB) t.n_follow = static_cast<int>((u0 + KB - 1) / s_per) - static_cast<int>(blockIdx.x);
+    t.tile_id = 0; t.ks = 0;
+    if (a.E == 0) {
+      const int wt = static_cast<int>(u % n_wt), tt = static_cast<int>(u / n_wt);
+      t.tok0 = tt * BN; t.tok_end = a.M; t.feat0 = wt * 128; t.wrow0 = t.feat0;
+      return true;
+    }
+    // grouped: units are ordered expert, weight tile, token sub-tile; the running expert only moves forward
+    int st = subtiles(s_e);
+    while (u >= s_pre + static_cast<long long>(st) * n_wt) { s_pre += st * n_wt; ++s_e; st = subtiles(s_e); }
+    const int local = static_cast<int>(u - s_pre);
+    const int wt = local / st, sb = local % st;
+    t.tok0 = a.grp_off[s_e] + sb * BN; t.tok_end = a.grp_off[s_e + 1];
+    t.feat0 = wt * 128; t.wrow0 = s_e * nw_per + wt * 128;
+    return true;
   }
   __device__ bool next(Tile& t) {
     const int nw_per = DUAL ? 2 * a.N : a.N;
-    t.kb0 = 0; t.kb1 = KB; t.tile_id = 0; t.ks = 0;
+    t.kb0 = 0; t.kb1 = KB; t.tile_id = 0; t.ks = 0; t.contrib = 0; t.n_follow = 0;
+    if (SWAP && a.stream) return next_stream(t);
     if (a.E == 0) {
       const int n_tt = SWAP ? (a.M + BN - 1) / BN : (a.M + 127) / 128;
       const int S = (SWAP && a.splits > 1) ? a.splits : 1;
@@ -176,7 +234,8 @@ struct TileSched {
   }
 };
 
-__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + __expf(-v)); }
+// silu with the approximate reciprocal (2 ulp): the exact division cost the epilogue warps ~350 clocks per value
+__device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
 template <int BN, bool FP8, bool DUAL, bool SWAP>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -259,7 +318,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             const int kx = kb * kKElems;
             if (phase == 0 || it >= npre) {
               if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) {
-                *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT); ok = false; break;
+                *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagGemm); ok = false; break;
               }
               PLOW_TRACE(if (a.trace && blockIdx.x == 0 && it < 64) a.trace[it * 8 + 6] = clock64();)
               mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
@@ -285,7 +344,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         PLOW_TRACE(if (a.trace && blockIdx.x == 0) { a.trace[7] = static_cast<long long>(t0); a.trace[23] = ld_acquire_sys(a.wait_ctr); a.trace[31] = target; })
         while (ld_acquire_sys(a.wait_ctr) < target) {
           if (globaltimer_ns() - t0 > static_cast<unsigned long long>(a.wait_deadline_ms) * 1000000ull) {
-            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); ok = false; break;
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT | kTagGemm); ok = false; break;
           }
           __nanosleep(256);
         }
@@ -297,6 +356,9 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
+      // grouped mode: the tile walk below reads grp_off / tile_prefix, which an earlier kernel of the step wrote
+      // (a dense walk depends on the launch arguments only and needs no wait)
+      if (a.E > 0) pdl_wait();
       TileSched<BN, DUAL, SWAP> sched(a, KB);
       Tile t;
       const uint32_t idesc = umma_idesc(128, kUmmaN, FP8 ? 0u : 1u, FP8 ? 0u : 1u);
@@ -312,11 +374,11 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           if (FP8 || kb == t.kb0) {
             const int b = accit % kNBuf;
             if (!mbar_wait(&acc_empty[b], ((accit / kNBuf) & 1) ^ 1, abort_flag)) {
-              *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_FREE_WAIT); ok = false; break;
+              *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_FREE_WAIT | kTagGemm); ok = false; break;
             }
           }
           if (!mbar_wait(&full_bar[s], ph, abort_flag)) {
-            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); ok = false; break;
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT | kTagGemm); ok = false; break;
           }
           tc_fence_after();
           PLOW_TRACE(if (tr) a.trace[it * 8 + 1] = clock64();)
@@ -367,7 +429,9 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
     const __nv_bfloat16* resid = reinterpret_cast<const __nv_bfloat16*>(a.residual);
     // The arrival gate is polled by the producer thread only: the epilogue warps touch the peers' rows
     // (their scales) after an accumulator-full barrier, which is ordered behind the producer's acquire.
+    PLOW_TRACE(int tile_no = 0;)
     while (ok && sched.next(t)) {
+      PLOW_TRACE(const bool trt = a.trace && blockIdx.x == 0 && li == 0 && tile_no < 2; if (trt) a.trace[(71 + tile_no) * 8 + 6] = clock64(); ++tile_no;)
       const int tok_i = t.tok0 + li;       // non-swap: this thread's token
       const int feat_i = t.feat0 + li;     // swap: this thread's feature
       if constexpr (FP8) {
@@ -395,6 +459,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         Sc s0, s1, s2;
         fetch(t.kb0, s0);
         fetch(t.kb0 + 1, s1);
+        PLOW_TRACE(if (trt) a.trace[(70 + tile_no) * 8 + 7] = clock64();)
         for (int kb = t.kb0; kb < t.kb1; ++kb, ++accit) {
           fetch(kb + 2, s2);
           if constexpr (SWAP) {
@@ -410,7 +475,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           PLOW_TRACE(const bool tre = a.trace && blockIdx.x == 0 && warp == 2 && lane == 0 && accit < 64;)
           PLOW_TRACE(if (tre) a.trace[accit * 8 + 3] = clock64();)
           if (!mbar_wait(&acc_full[b], (accit / kNBuf) & 1, abort_flag)) {
-            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagGemm); ok = false; break;
           }
           tc_fence_after();
           PLOW_TRACE(if (tre) a.trace[accit * 8 + 4] = clock64();)
@@ -455,7 +520,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
       } else {
         const int b = accit & 1;
         if (!mbar_wait(&acc_full[b], (accit >> 1) & 1, abort_flag)) {
-          *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
+          *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagGemm); ok = false; break;
         }
         tc_fence_after();
       }
@@ -473,6 +538,49 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           for (int j = 0; j < 16; ++j) r[j] = __uint_as_float(g[j]);
         }
       };
+      // stream scheduling: a piece that does not hold the first K blocks of its tile only publishes its partial
+      // sums and moves on; the piece that does hold them adds the followers' partials before the epilogue.
+      const float* fix = nullptr;     // partials of the CTAs that follow, [follower][column][128 lanes]
+      int fix_n = 0;
+      bool piece_done = false;
+      if constexpr (SWAP) {
+        if (a.stream && t.contrib) {
+          float* wp = a.ws + static_cast<size_t>(blockIdx.x) * kAccCols * 128 + li;
+#pragma unroll
+          for (int c = 0; c < kAccCols; c += 16) {
+            float r[16];
+            raw16(c, r);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) wp[static_cast<size_t>(c + j) * 128] = r[j];
+          }
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
+          if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) {
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagGemm); ok = false; break;
+          }
+          ++xchg_it;
+          if (li == 0) red_add_release_gpu(reinterpret_cast<uint32_t*>(a.ws_ctr) + blockIdx.x * 32, 1u);
+          piece_done = true;
+        } else if (a.stream && t.n_follow > 0) {
+          if (lane == 0) {
+            const unsigned long long t0 = globaltimer_ns();
+            for (int f = 1; f <= t.n_follow; ++f) {
+              const uint32_t* flag = reinterpret_cast<const uint32_t*>(a.ws_ctr) + (blockIdx.x + f) * 32;
+              while (ld_acquire_gpu(flag) == 0u) {
+                if (*abort_flag || globaltimer_ns() - t0 > kWaitDeadlineNs) {
+                  *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_GRID_WAIT | kTagGemm); break;
+                }
+                __nanosleep(32);
+              }
+            }
+          }
+          __syncwarp();
+          if (*abort_flag) { ok = false; break; }
+          fix = a.ws + static_cast<size_t>(blockIdx.x + 1) * kAccCols * 128 + li;
+          fix_n = t.n_follow;
+        }
+      }
       // split-K: publish this CTA's partial, wait (bounded) until the tile's other splits have
       // published theirs, then reduce and finish only this CTA's share of the token columns, so the
       // reduction traffic is spread over all the CTAs of the tile.  All tiles x splits CTAs are
@@ -496,7 +604,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           __syncwarp();
           if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
           if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) {
-            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagGemm); ok = false; break;
           }
           ++xchg_it;
           uint32_t* ctr = reinterpret_cast<uint32_t*>(a.ws_ctr) + t.tile_id * 32;   // one counter per 128-byte line
@@ -506,7 +614,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             const unsigned long long t0 = globaltimer_ns();
             while (ld_acquire_gpu(ctr) < static_cast<uint32_t>(a.splits)) {
               if (*abort_flag || globaltimer_ns() - t0 > kWaitDeadlineNs) {
-                *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_GRID_WAIT); break;
+                *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_GRID_WAIT | kTagGemm); break;
               }
               __nanosleep(32);
             }
@@ -544,6 +652,27 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) r[j] = DUAL ? silu_f(g[j]) * u[j] : g[j];
+        } else if (fix_n > 0) {
+          // this piece's own sums plus the followers' partials (follower order: deterministic)
+          float g[16], u[16];
+          raw16(c, g);
+          if constexpr (DUAL) raw16(BN + c, u);
+          for (int f = 0; f < fix_n; ++f) {
+            const float* p = fix + static_cast<size_t>(f) * kAccCols * 128;
+            float v[16], w2[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              v[j] = __ldcg(p + static_cast<size_t>(c + j) * 128);
+              if constexpr (DUAL) w2[j] = __ldcg(p + static_cast<size_t>(BN + c + j) * 128);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              g[j] += v[j];
+              if constexpr (DUAL) u[j] += w2[j];
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = DUAL ? silu_f(g[j]) * u[j] : g[j];
         } else if constexpr (FP8) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -569,7 +698,9 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         for (int j = 0; j < 16; ++j) r[j] *= a.out_scale;
       };
 
+      PLOW_TRACE(if (trt) a.trace[(70 + tile_no) * 8 + 0] = clock64();)
       if constexpr (SWAP) {
+       if (!piece_done) {
         // thread = feature, columns = tokens
         const bool fok = feat_i < a.N;
 #pragma unroll
@@ -578,6 +709,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           if (c + 16 <= col_lo || c >= col_hi) continue;
           float r[16];
           load16(c, r);
+          PLOW_TRACE(if (trt && c == 0) a.trace[(70 + tile_no) * 8 + 1] = clock64();)
           if (a.ar_world > 1) {
             // fused all-reduce, phase 1: this rank's partial of the tile, bf16, [tile][feature][token]
             uint32_t pk[8];
@@ -620,31 +752,35 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             float* scratch = red_scratch + (xchg_it & 1) * 64;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              float v = fok ? fabsf(r[j]) : 0.f;
-#pragma unroll
-              for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-              if (lane == 0) scratch[lq * 16 + j] = v;
+              // |r| >= 0, so the float order is the order of its bit pattern: one warp-wide integer max per value
+              const uint32_t vb = __reduce_max_sync(0xffffffffu, fok ? __float_as_uint(fabsf(r[j])) : 0u);
+              if (lane == 0) scratch[lq * 16 + j] = __uint_as_float(vb);
             }
+            PLOW_TRACE(if (trt && c == 0) a.trace[(70 + tile_no) * 8 + 2] = clock64();)
             __syncwarp();
             if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
             if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) {
-              *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
+              *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagGemm); ok = false; break;
             }
             ++xchg_it;
+            PLOW_TRACE(if (trt && c == 0) a.trace[(70 + tile_no) * 8 + 3] = clock64();)
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const float m = fmaxf(fmaxf(scratch[j], scratch[16 + j]),
                                     fmaxf(scratch[32 + j], scratch[48 + j]));
               const float sc = fmaxf(m, 1e-10f) * (1.0f / 448.0f);
+              const float inv = __fdividef(448.0f, fmaxf(m, 1e-10f));
               const int tok = t.tok0 + c + j;
               if (fok && tok < t.tok_end && c + j >= col_lo && c + j < col_hi) {
                 reinterpret_cast<__nv_fp8_e4m3*>(a.yq)[static_cast<size_t>(tok) * a.ldy + feat_i] =
-                    __nv_fp8_e4m3(r[j] / sc);
+                    __nv_fp8_e4m3(r[j] * inv);
                 if (li == 0) a.syq[static_cast<size_t>(t.feat0 >> 7) * a.ld_syq + tok] = sc;
               }
             }
           }
+          PLOW_TRACE(if (trt && c == 0) a.trace[(70 + tile_no) * 8 + 4] = clock64();)
         }
+        PLOW_TRACE(if (trt) a.trace[(70 + tile_no) * 8 + 5] = clock64();)
         if (!ok) break;
         if (a.ar_world > 1) {
           // tell the tile's owner (tile mod world) that this rank's partial is in place
@@ -652,7 +788,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           __syncwarp();
           if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
           if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) {
-            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagGemm); ok = false; break;
           }
           ++xchg_it;
           const int tile = t.feat0 >> 7;
@@ -665,7 +801,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
               const unsigned long long t0 = globaltimer_ns();
               const unsigned long long dl = static_cast<unsigned long long>(a.wait_deadline_ms ? a.wait_deadline_ms : 2000) * 1000000ull;
               while (ld_acquire_sys(f) < ar_ep) {
-                if (*abort_flag || globaltimer_ns() - t0 > dl) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); break; }
+                if (*abort_flag || globaltimer_ns() - t0 > dl) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT | kTagGemm); break; }
                 __nanosleep(64);
               }
             }
@@ -715,7 +851,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           __syncwarp();
           if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
           if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) {
-            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break;
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagGemm); ok = false; break;
           }
           ++xchg_it;
           if (li == 0) {
@@ -723,6 +859,17 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             if (atomicAdd(done, 1) == a.splits - 1) { *done = 0; a.ws_ctr[t.tile_id * 32] = 0; __threadfence(); }
           }
         }
+        if (fix_n > 0) {
+          // every warp is past its flag polls and its reads of the partials: re-arm the followers' flags
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
+          if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) {
+            *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagGemm); ok = false; break;
+          }
+          ++xchg_it;
+          if (li < fix_n) reinterpret_cast<uint32_t*>(a.ws_ctr)[(blockIdx.x + 1 + li) * 32] = 0u;
+        }
+       }
       } else {
         // thread = token, columns = features (contiguous in memory)
         const bool tok_ok = tok_i < t.tok_end;
@@ -831,7 +978,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             const uint32_t* f = reinterpret_cast<const uint32_t*>(a.ar_peer[a.ar_me] + a.ar_flag_ofs) + tile * 8 + li;
             const unsigned long long t0 = globaltimer_ns();
             while (ld_acquire_sys(f) < ar_ep) {
-              if (*abort_flag || globaltimer_ns() - t0 > dl) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); break; }
+              if (*abort_flag || globaltimer_ns() - t0 > dl) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT | kTagGemm); break; }
               __nanosleep(128);
             }
           }
@@ -909,7 +1056,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           const unsigned long long t0 = globaltimer_ns();
           for (int tile = li; tile < n_tiles; tile += 128) {
             while (ld_acquire_sys(td + tile) < ar_ep) {
-              if (globaltimer_ns() - t0 > dl) { atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); break; }
+              if (globaltimer_ns() - t0 > dl) { atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT | kTagGemm); break; }
               __nanosleep(128);
             }
           }
@@ -925,7 +1072,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           // launches); no peer can be a launch ahead, because every tile needs this rank's partial of that launch
           const uint32_t target = a.ar_epoch[1] + static_cast<uint32_t>(n_tiles);
           while (ld_acquire_sys(d) - target > 0x7fffffffu) {      // wrap-safe "d < target"
-            if (globaltimer_ns() - t0 > dl) { atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT); break; }
+            if (globaltimer_ns() - t0 > dl) { atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT | kTagGemm); break; }
             __nanosleep(128);
           }
           a.ar_epoch[1] = target;
@@ -969,7 +1116,14 @@ int launch_gemm_tc(const GemmArgs& a, int ldx_elems, int ldw_elems, int64_t w_ro
     if (e != cudaSuccess) return 3000 + static_cast<int>(e);
   }
   int grid = sm_count();
-  if (a.E == 0) {
+  if (SWAP && a.stream) {
+    if (a.E == 0) {
+      // at least two K blocks per CTA; the ranges are cut evenly over the grid
+      const int kk = FP8 ? 128 : 64;
+      const long long iters = static_cast<long long>((a.N + 127) / 128) * ((a.M + BN - 1) / BN) * ((a.K + kk - 1) / kk);
+      if (iters / 2 < grid) grid = static_cast<int>(iters / 2 > 0 ? iters / 2 : 1);
+    }
+  } else if (a.E == 0) {
     const int n_wt = SWAP ? (a.N + 127) / 128 : (a.N + BN - 1) / BN;
     const int n_tt = SWAP ? (a.M + BN - 1) / BN : (a.M + 127) / 128;
     const long long tiles = static_cast<long long>(n_wt) * n_tt * (SWAP && a.splits > 1 ? a.splits : 1);

@@ -186,7 +186,7 @@ __device__ void run_slices(const InterpArgs& a, const PlowInst& in, uint32_t ins
       break;
     }
     default:
-      if (threadIdx.x == 0) atomicCAS(a.status, 0, PLOW_ERR_BOUNDS);   // an opcode without a body in this interpreter
+      if (threadIdx.x == 0) atomicCAS(a.status, 0, PLOW_ERR_BOUNDS | kTagInterp);   // an opcode without a body in this interpreter
       break;
   }
 }
@@ -217,7 +217,7 @@ interp_kernel(const InterpArgs a) {
         const unsigned long long t0 = globaltimer_ns();
         while (ld_acquire_gpu(c) < pw.target) {
           if (globaltimer_ns() - t0 > deadline || *reinterpret_cast<volatile int*>(a.status) != 0) {
-            atomicCAS(a.status, 0, PLOW_ERR_GRID_WAIT);
+            atomicCAS(a.status, 0, PLOW_ERR_GRID_WAIT | kTagInterp);
             give_up = 1;
             break;
           }

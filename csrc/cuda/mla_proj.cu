@@ -68,7 +68,7 @@ mla_absorb_kernel(const AbsorbArgs a, const __grid_constant__ CUtensorMap tm_q, 
           }
         tc_commit(done);
       } else {
-        *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT);
+        *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT | kTagMlaProj);
       }
     }
   } else {
@@ -148,7 +148,7 @@ mla_absorb_kernel(const AbsorbArgs a, const __grid_constant__ CUtensorMap tm_q, 
         a.sq[static_cast<size_t>(h) * a.T + t] = sc;
       }
     } else {
-      *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT);
+      *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagMlaProj);
     }
   }
   tc_fence_before();
@@ -195,11 +195,11 @@ mla_fold_kernel(const FoldArgs a, const __grid_constant__ CUtensorMap tm_w) {
     if (elect_one()) {
       const uint32_t idesc = umma_idesc(128, 128, 1, 1);
       for (int p = 0; p < 2; ++p) {
-        if (p == 1 && !mbar_wait(&done[0], 0, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); break; }
+        if (p == 1 && !mbar_wait(&done[0], 0, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagMlaProj); break; }
         mbar_expect_tx(b_full, 65536);
         for (int c = 0; c < 4; ++c) tma_load_2d(sb + c * 16384, &tm_w, p * 256 + c * 64, h * 128, b_full);
         if (!mbar_wait(b_full, p, abort_flag) || !mbar_wait(a_ready, p, abort_flag)) {
-          *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT); break;
+          *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT | kTagMlaProj); break;
         }
         tc_fence_after();
         for (int c = 0; c < 4; ++c) {
@@ -248,7 +248,7 @@ mla_fold_kernel(const FoldArgs a, const __grid_constant__ CUtensorMap tm_w) {
     const int n_live = min(128, a.T - t0);
     bool ok = true;
     for (int p = 0; p < 2 && ok; ++p) {
-      if (p == 1 && !mbar_wait(&done[0], 0, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT); ok = false; break; }
+      if (p == 1 && !mbar_wait(&done[0], 0, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagMlaProj); ok = false; break; }
       // A operand: warp w fills rows w, w+4, w+8, ... (so the live rows are spread over all four warps), eight
       // rows at a time.  For one row the 32 lanes fetch the row's 256 latent columns of this phase as one
       // coalesced 512-byte read per split (lane = 16-byte unit); the eight rows' loads of a split are issued
@@ -340,7 +340,7 @@ mla_fold_kernel(const FoldArgs a, const __grid_constant__ CUtensorMap tm_w) {
         }
       }
     } else if (ok) {
-      *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT);
+      *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagMlaProj);
     }
   }
   tc_fence_before();

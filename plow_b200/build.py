@@ -22,8 +22,11 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent.parent
 CSRC = ROOT / "csrc"
-LIBDIR = Path(__file__).resolve().parent / "lib"
-OBJDIR = ROOT / "build"
+# PLOW_LIBDIR / PLOW_EXTRA_NVCC_FLAGS build a variant beside the default one, e.g.
+#   PLOW_LIBDIR=/tmp/plow_trace PLOW_EXTRA_NVCC_FLAGS=-DPLOW_DEVICE_TRACE python -m plow_b200.build
+LIBDIR = Path(os.environ["PLOW_LIBDIR"]) if os.environ.get("PLOW_LIBDIR") else Path(__file__).resolve().parent / "lib"
+OBJDIR = ROOT / "build" if not os.environ.get("PLOW_LIBDIR") else \
+    ROOT / "build" / ("variant_" + hashlib.sha256(os.environ["PLOW_LIBDIR"].encode()).hexdigest()[:8])
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -49,7 +52,7 @@ def _digest(src: Path, extra: list[str]) -> str:
 
 
 def _compile(cmd_prefix: list[str], src: Path, flags: list[str], verbose: bool) -> Path:
-    OBJDIR.mkdir(exist_ok=True)
+    OBJDIR.mkdir(parents=True, exist_ok=True)
     obj = OBJDIR / f"{src.parent.name}_{src.stem}.{_digest(src, flags)}.o"
     if obj.exists():
         return obj
@@ -65,9 +68,9 @@ def _compile(cmd_prefix: list[str], src: Path, flags: list[str], verbose: bool) 
 
 
 def _link(cmd: list[str], objs: list[Path], out: Path, extra: list[str]) -> None:
-    LIBDIR.mkdir(exist_ok=True)
+    LIBDIR.mkdir(parents=True, exist_ok=True)
     stamp = hashlib.sha256(" ".join(sorted(o.name for o in objs)).encode()).hexdigest()[:16]
-    stamp_file = OBJDIR / (out.name + ".stamp")
+    stamp_file = OBJDIR / (out.name + "." + hashlib.sha256(str(out).encode()).hexdigest()[:8] + ".stamp")
     if out.exists() and stamp_file.exists() and stamp_file.read_text() == stamp:
         return
     r = subprocess.run(cmd + ["-shared", "-o", str(out)] + [str(o) for o in objs] + extra,
@@ -96,7 +99,7 @@ def build_cuda(verbose: bool = False) -> Path | None:
     if nvcc is None:
         return out if out.exists() else None
     srcs = sorted((CSRC / "cuda").glob("*.cu")) + sorted((CSRC / "comm").glob("*.cu"))
-    flags = NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else [])
+    flags = NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + os.environ.get("PLOW_EXTRA_NVCC_FLAGS", "").split()
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(srcs)))) as ex:
         objs = list(ex.map(lambda s: _compile([nvcc], s, flags, verbose), srcs))
     _link([nvcc], objs, out, [])

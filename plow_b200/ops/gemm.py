@@ -29,6 +29,9 @@ def _pick_bn_swap(rows: int, fp8: bool, dual: bool) -> int:
     return cap
 
 
+import os as _os
+
+_STREAM_DEFAULT = _os.environ.get("PLOW_GEMM_STREAM", "1") != "0"
 _SPLITK_WS = {}
 SM_COUNT = 148          # B200; used only where no device is present (the device's own count is read otherwise)
 
@@ -95,7 +98,8 @@ def pick_splits(M, N, K, fp8, dual, bn) -> int:
 
 def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=None,
          grp_off=None, tile_prefix=None, n_experts=0, swap=None, bn=None, out_f32=False,
-         out_scale=1.0, quant_out=False, rows_hint=None, ld_syq=None, wait=None, yq_out=None, syq_out=None, splits=None, ar=None):
+         out_scale=1.0, quant_out=False, rows_hint=None, ld_syq=None, wait=None, yq_out=None, syq_out=None, splits=None, ar=None,
+         stream=None):
     """y = x @ w.T with the epilogue options of the kernel.
 
     x [M, K] bf16 or e4m3; w [(E*)N(*2), K] same dtype.  ``dual`` computes silu(gate)*up with
@@ -105,7 +109,9 @@ def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=N
     used to pick the token tile in grouped swap mode.  ``wait`` = (counter ptr, epoch ptr, multiplier,
     deadline ms): the kernel starts reading x once ``*counter >= *epoch * multiplier`` (rows written by
     peer GPUs during expert-parallel dispatch).  ``ar``: fuse the tensor-parallel all-reduce of the
-    result into the kernel (see plow_b200/parallel/tp.py).
+    result into the kernel (see plow_b200/parallel/tp.py).  ``stream`` (swap mode; default on unless ``splits`` is
+    given or PLOW_GEMM_STREAM=0): stream scheduling, every CTA runs the same number of K blocks and tiles whose K range
+    is shared between CTAs are finished through fp32 partials in the workspace.
     """
     lib = native.cuda_lib()
     assert x.is_cuda and w.is_cuda and x.dim() == 2 and w.dim() == 2
@@ -140,7 +146,21 @@ def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=N
     ws = ws_ctr = None
     if ar is not None:
         splits = 1
-    if swap and E == 0:
+    if stream is None:
+        stream = bool(swap) and ar is None and splits is None and _STREAM_DEFAULT
+        if stream and E == 0:
+            # dense: worth it when the tile count is within a factor of a few of the SM count (a tile is then shared
+            # by at most ~3 CTAs) and every CTA still gets a decent run of K blocks; few-tile problems keep the
+            # split-K form, whose reduction is spread over the splits
+            units = ((N + 127) // 128) * ((M + bn - 1) // bn)
+            kb = (K + (127 if fp8 else 63)) // (128 if fp8 else 64)
+            sms = sm_count(x.device)
+            stream = units * 3 >= sms and units * kb >= 16 * sms
+    stream = bool(stream) and bool(swap) and ar is None
+    if stream:
+        splits = 1
+        ws, ws_ctr = _splitk_ws(x.device)
+    elif swap and E == 0:
         if splits is None:
             splits = pick_splits(M, N, K, fp8, dual, bn)
         if splits > 1:
@@ -155,7 +175,7 @@ def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=N
         ld_sx=(sx.stride(0) if sx is not None else 0), ld_syq=(ld_syq or 0), E=E, w_rows=w_rows,
         dtype=_FP8 if fp8 else _BF16, dual=int(dual), swap=int(swap), bn=int(bn),
         out_f32=int(out_f32), out_scale=float(out_scale),
-        ws=_ptr(ws), ws_ctr=_ptr(ws_ctr), splits=int(splits or 1), ws_pad=0,
+        ws=_ptr(ws), ws_ctr=_ptr(ws_ctr), splits=int(splits or 1), stream=int(stream),
         wait_ctr=(wait[0] if wait else None), wait_epoch=(wait[1] if wait else None),
         wait_mult=(int(wait[2]) if wait else 0), wait_deadline_ms=(int(wait[3]) if wait else 0))
     native.LAUNCHES["n"] += 1

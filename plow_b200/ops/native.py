@@ -11,7 +11,8 @@ import os
 from functools import lru_cache
 from pathlib import Path
 
-LIBDIR = Path(__file__).resolve().parent.parent / "lib"
+# PLOW_LIBDIR points at an alternative build of the libraries (e.g. one compiled with -DPLOW_DEVICE_TRACE)
+LIBDIR = Path(os.environ["PLOW_LIBDIR"]) if os.environ.get("PLOW_LIBDIR") else Path(__file__).resolve().parent.parent / "lib"
 
 
 class NativeLibraryError(RuntimeError):
@@ -30,7 +31,7 @@ class GemmDesc(C.Structure):
         ("w_rows", C.c_int64),
         ("dtype", C.c_int32), ("dual", C.c_int32), ("swap", C.c_int32), ("bn", C.c_int32),
         ("out_f32", C.c_int32), ("out_scale", C.c_float),
-        ("ws", C.c_void_p), ("ws_ctr", C.c_void_p), ("splits", C.c_int32), ("ws_pad", C.c_int32),
+        ("ws", C.c_void_p), ("ws_ctr", C.c_void_p), ("splits", C.c_int32), ("stream", C.c_int32),
         ("ar_peer", C.c_void_p * 8), ("ar_part_ofs", C.c_uint64), ("ar_flag_ofs", C.c_uint64), ("ar_done_ofs", C.c_uint64),
         ("ar_y_ofs", C.c_uint64), ("ar_epoch", C.c_void_p), ("ar_world", C.c_int32), ("ar_me", C.c_int32),
         ("wait_ctr", C.c_void_p), ("wait_epoch", C.c_void_p), ("wait_mult", C.c_int32), ("wait_deadline_ms", C.c_int32),
@@ -89,13 +90,20 @@ STATUS_NAMES = {
 }
 
 
+KERNEL_FAMILIES = {0: "?", 1: "gemm", 2: "mla_decode", 3: "mla_absorb/fold", 4: "gqa_attention", 5: "dsa", 6: "ep dispatch/combine",
+                   7: "all-gather push", 8: "gdn", 9: "interpreter"}
+
+
 def check_status(device=None) -> None:
-    """Synchronising read of the status word; raises on a recorded device-side error."""
+    """Synchronising read of the status word; raises on a recorded device-side error.  The word is
+    ``code | (kernel family << 8)`` (csrc/cuda/ptx.cuh)."""
     s = status_word(device)
-    code = int(s[0].item())
-    if code != 0:
+    word = int(s[0].item())
+    if word != 0:
         s.zero_()
-        raise NativeLibraryError(f"device kernel reported status {code}: {STATUS_NAMES.get(code, '?')}")
+        code, fam = word & 0xFF, word >> 8
+        raise NativeLibraryError(f"device kernel reported status {code}: {STATUS_NAMES.get(code, '?')} "
+                                 f"(kernel family: {KERNEL_FAMILIES.get(fam, fam)})")
 
 
 # ---- compact ctypes signatures: p = pointer, i = int32, l = int64, f = float ----------------------

@@ -449,7 +449,7 @@ class GpuEngine(EngineBase):
             st.scratch["mla_items"] = False
         else:
             # the work list depends on the rows' lengths only: the first dense attention of a walk builds it for all layers
-            if not st.scratch.get("mla_items"):
+            if not st.scratch.get("mla_items") or os.environ.get("PLOW_MLA_ITEMS_PER_LAYER") == "1":
                 mla_ops.build_items(self.d_kvlen_row, T, self._mla_ws)
                 st.scratch["mla_items"] = True
             mla_ops.decode(q8, sq, cache, scale, self.kv_smax[layer], self.d_page_table, self.d_in[2], self.d_kvlen_row,
@@ -628,7 +628,16 @@ class GpuEngine(EngineBase):
                 return all(t is not None for t in acts) and all(
                     t.dtype in (BF16, I32) or (ins.op == Op.ARGMAX and t.dtype == F32) for t in acts)
             st.interp = DeviceInterp(self.packet, st.prog, tensor_of, st.rows, st.samples, self.device)
-            st.segments = DeviceInterp.segments(st.prog, eligible)
+            # a cooperative interpreter launch costs ~25 us whatever it runs (measured: one ADD_NORM of 64 rows takes
+            # 26 us in it against 5.5 us as a role kernel), so runs shorter than `min_run` instructions stay role kernels
+            min_run = int(os.environ.get("PLOW_INTERP_MIN_RUN", "2"))
+            segs = []
+            for lo, hi, on_device in DeviceInterp.segments(st.prog, eligible):
+                if on_device and hi - lo < min_run:
+                    segs.extend((j, j + 1, False) for j in range(lo, hi))
+                else:
+                    segs.append((lo, hi, on_device))
+            st.segments = segs
         return st.segments
 
     def _run_insts(self, st: _Prog) -> None:
