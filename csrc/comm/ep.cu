@@ -287,33 +287,33 @@ extern "C" {
 // epoch pointer, status pointer, u64 deadline (see plow_b200/parallel/ep.py for the ctypes mirror).
 int plow_ep_counts(const void* args, const void* table, int n_pairs, int* cursor, void* st) {
   const EpArgs& a = *static_cast<const EpArgs*>(args);
-  plow::launch_pdl(ep_counts_kernel, dim3(1), dim3(1024), a.E * 4, reinterpret_cast<cudaStream_t>(st), a, static_cast<const int2*>(table), n_pairs, cursor);
+  plow::launch_serial(ep_counts_kernel, dim3(1), dim3(1024), a.E * 4, reinterpret_cast<cudaStream_t>(st), a, static_cast<const int2*>(table), n_pairs, cursor);
   return ok();
 }
 int plow_ep_push(const void* args, const void* table, int n_pairs, int top_k, const void* xq, const float* sx, int ld_sx,
                  int* cursor, int* grp_off, int* tile_prefix, int* pair_dest, int n_cta, int shared_rows, void* st) {
   const EpArgs& a = *static_cast<const EpArgs*>(args);
-  plow::launch_pdl(ep_push_kernel, dim3(n_cta), dim3(256), (a.W + 1) * a.E * 4, reinterpret_cast<cudaStream_t>(st), 
+  plow::launch_serial(ep_push_kernel, dim3(n_cta), dim3(256), (a.W + 1) * a.E * 4, reinterpret_cast<cudaStream_t>(st), 
       a, static_cast<const int2*>(table), n_pairs, top_k, static_cast<const uint8_t*>(xq), sx, ld_sx, cursor, grp_off,
       tile_prefix, pair_dest, shared_rows);
   return ok();
 }
 int plow_ep_y_ready(const void* args, void* st) {
   const EpArgs& a = *static_cast<const EpArgs*>(args);
-  plow::launch_pdl(ep_y_ready_kernel, dim3(1), dim3(32), 0, reinterpret_cast<cudaStream_t>(st), a);
+  plow::launch_serial(ep_y_ready_kernel, dim3(1), dim3(32), 0, reinterpret_cast<cudaStream_t>(st), a);
   return ok();
 }
 int plow_ep_combine(const void* args, void* out, const void* shared, const void* table, const int* pair_dest, int T, int top_k,
                     const int* shared_base, void* st) {
   const EpArgs& a = *static_cast<const EpArgs*>(args);
   if (top_k > 16 || a.H % 8) return -1;
-  plow::launch_pdl(ep_combine_kernel, dim3(T, (a.H / 8 + 255) / 256), dim3(256), 0, reinterpret_cast<cudaStream_t>(st), a, static_cast<__nv_bfloat16*>(out),
+  plow::launch_serial(ep_combine_kernel, dim3(T, (a.H / 8 + 255) / 256), dim3(256), 0, reinterpret_cast<cudaStream_t>(st), a, static_cast<__nv_bfloat16*>(out),
                                                                     static_cast<const __nv_bfloat16*>(shared),
                                                                     static_cast<const int2*>(table), pair_dest, top_k, shared_base);
   return ok();
 }
 int plow_wait_probe(const void* flag, unsigned int target, unsigned long long deadline_ns, int* status, void* st) {
-  plow::launch_pdl(ep_wait_probe_kernel, dim3(1), dim3(32), 0, reinterpret_cast<cudaStream_t>(st), static_cast<const uint32_t*>(flag), target, deadline_ns, status);
+  plow::launch_serial(ep_wait_probe_kernel, dim3(1), dim3(32), 0, reinterpret_cast<cudaStream_t>(st), static_cast<const uint32_t*>(flag), target, deadline_ns, status);
   return ok();
 }
 

@@ -68,7 +68,7 @@ int plow_ag_push(const void* const* peers, uint64_t x_ofs, uint64_t ctr_ofs, voi
   const long long total = static_cast<long long>(band_rows) * (row_bytes / 16);
   int grid = static_cast<int>((total + 255) / 256);
   if (grid > 64) grid = 64;
-  plow::launch_pdl(ag_push_kernel, dim3(grid), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), a, static_cast<const uint8_t*>(src), ld_src_bytes);
+  plow::launch_serial(ag_push_kernel, dim3(grid), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), a, static_cast<const uint8_t*>(src), ld_src_bytes);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }

@@ -461,7 +461,7 @@ int launch_gqa(const GqaArgs& a, const void* q, const void* kc, const void* vc, 
   if (r) return 1300 + r;
   static DeviceOnce attr;
   if (ensure_smem(attr, gqa_attn_kernel<HD>, Cfg::kSmem) != cudaSuccess) return 3000;
-  plow::launch_pdl(gqa_attn_kernel<HD>, dim3(grid), dim3(kGqaThreads), Cfg::kSmem, stream, a, tq, tk, tv);
+  plow::launch_serial(gqa_attn_kernel<HD>, dim3(grid), dim3(kGqaThreads), Cfg::kSmem, stream, a, tq, tk, tv);
   return 0;
 }
 
@@ -484,7 +484,7 @@ int plow_gqa_attention(const void* q, const void* kc, const void* vc, int64_t n_
   if (hd != 128 && hd != 256) return -3;
   const int tq = 128 / group;
   cudaMemsetAsync(n_items, 0, sizeof(int), stream);
-  plow::launch_pdl(gqa_build_items, dim3((rows + 255) / 256), dim3(256), 0, stream, seq, pos, rows, tq, nkv, window, tiles_per_split, max_splits,
+  plow::launch_serial(gqa_build_items, dim3((rows + 255) / 256), dim3(256), 0, stream, seq, pos, rows, tq, nkv, window, tiles_per_split, max_splits,
                                                          static_cast<GqaItem*>(items), n_items, row_ns, item_cap, status);
   GqaArgs a;
   a.page_table = page_table; a.pos = pos; a.items = static_cast<const GqaItem*>(items); a.n_items = n_items;
@@ -496,7 +496,7 @@ int plow_gqa_attention(const void* q, const void* kc, const void* vc, int64_t n_
   int r = hd == 128 ? launch_gqa<128>(a, q, kc, vc, n_pages, grid, stream) : launch_gqa<256>(a, q, kc, vc, n_pages, grid, stream);
   if (r) return r;
   if (max_splits > 1)
-    plow::launch_pdl(gqa_merge_kernel, dim3(rows, nq), dim3(128), 0, stream, opart, lse, row_ns, nq, max_splits, hd, static_cast<__nv_bfloat16*>(out));
+    plow::launch_serial(gqa_merge_kernel, dim3(rows, nq), dim3(128), 0, stream, opart, lse, row_ns, nq, max_splits, hd, static_cast<__nv_bfloat16*>(out));
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }
@@ -511,7 +511,7 @@ int plow_rope_kv(void* q_out, const void* qkv, int ld_qkv, void* kc, void* vc, c
   if (rows <= 0 || hd % 8 || rot > hd || rot % 2) return -1;
   const long long items = static_cast<long long>(rows) * (nq + 2 * nkv);
   const int wpb = 8;
-  plow::launch_pdl(rope_kv_kernel, dim3(static_cast<unsigned>((items + wpb - 1) / wpb)), dim3(wpb * 32), wpb * hd * sizeof(float), reinterpret_cast<cudaStream_t>(stream_), 
+  plow::launch_serial(rope_kv_kernel, dim3(static_cast<unsigned>((items + wpb - 1) / wpb)), dim3(wpb * 32), wpb * hd * sizeof(float), reinterpret_cast<cudaStream_t>(stream_), 
       static_cast<__nv_bfloat16*>(q_out), static_cast<const __nv_bfloat16*>(qkv), ld_qkv, static_cast<__nv_bfloat16*>(kc),
       static_cast<__nv_bfloat16*>(vc), static_cast<const __nv_bfloat16*>(qn), static_cast<const __nv_bfloat16*>(kn),
       rope_tab, pos, seq, page_table, max_pages, rows, nq, nkv, hd, rot, pair_mode, plus_one, eps,

@@ -496,7 +496,7 @@ void plow_mla_set_trace(void* p) { g_mla_trace = static_cast<long long*>(p); }
 int plow_mla_build_items(const int* kvlen, int T, int tiles_per_split, int max_splits, void* items, int* n_items, void* stream_) {
   using namespace plow;
   if (T <= 0 || max_splits <= 0 || tiles_per_split <= 0) return -1;
-  cudaError_t e = launch_pdl(mla_build_items, dim3(1), dim3(256), T * sizeof(int), reinterpret_cast<cudaStream_t>(stream_),
+  cudaError_t e = launch_serial(mla_build_items, dim3(1), dim3(256), T * sizeof(int), reinterpret_cast<cudaStream_t>(stream_),
                              kvlen, T, tiles_per_split, max_splits, static_cast<MlaItem*>(items), n_items);
   if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
@@ -524,7 +524,7 @@ int plow_mla_decode(const void* q8, const float* sq, const void* kv, const float
   static DeviceOnce attr;
   if (ensure_smem(attr, mla_decode_kernel, kMlaSmem) != cudaSuccess) return 3000;
   if (build_items)
-    launch_pdl(mla_build_items, dim3(1), dim3(256), T * sizeof(int), stream, kvlen, T, tiles_per_split, max_splits,
+    launch_serial(mla_build_items, dim3(1), dim3(256), T * sizeof(int), stream, kvlen, T, tiles_per_split, max_splits,
                static_cast<MlaItem*>(items), n_items);
   MlaArgs a;
   a.q8 = static_cast<const uint8_t*>(q8); a.sq = sq; a.kv_scale = kv_scale; a.kv_smax = kv_smax; a.page_table = page_table; a.slot_of = slot_of; a.kvlen = kvlen;
@@ -540,9 +540,9 @@ int plow_mla_decode(const void* q8, const float* sq, const void* kv, const float
   int grid = sm_count();
   const int cap = 2 * T * max_splits;
   if (cap < grid) grid = cap;
-  cudaError_t e = launch_pdl(mla_decode_kernel, dim3(grid), dim3(kMlaThreads), kMlaSmem, stream, a, tqr, tkv, tkvr);
+  cudaError_t e = launch_serial(mla_decode_kernel, dim3(grid), dim3(kMlaThreads), kMlaSmem, stream, a, tqr, tkv, tkvr);
   if (e == cudaSuccess && out)   // NULL: the caller merges the splits itself (plow_mla_fold does it while folding W_uv)
-    e = launch_pdl(mla_merge_kernel, dim3(T, kMlaHeads), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(opart),
+    e = launch_serial(mla_merge_kernel, dim3(T, kMlaHeads), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(opart),
                    static_cast<const float*>(lse), kvlen, T, max_splits, tiles_per_split, static_cast<__nv_bfloat16*>(out));
   if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);

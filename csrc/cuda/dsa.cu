@@ -309,7 +309,7 @@ int plow_dsa_k_write(void* cache, float* cache_scale, const void* k, int ld_k, c
                      int rows, int rot, int pair_mode, float eps, void* stream) {
   using namespace plow;
   if (rows <= 0 || rot > kIdxDim || rot % 2) return -1;
-  plow::launch_pdl(dsa_k_write_kernel, dim3((rows + 7) / 8), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
+  plow::launch_serial(dsa_k_write_kernel, dim3((rows + 7) / 8), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
       static_cast<uint8_t*>(cache), cache_scale, static_cast<const __nv_bfloat16*>(k), ld_k, gamma, beta, rope_tab, pos, seq,
       page_table, max_pages, rows, rot, pair_mode, eps);
   cudaError_t e = cudaGetLastError();
@@ -325,7 +325,7 @@ int plow_dsa_select(int* sel, float* scores, int ld_scores, void* q8, float* wq,
   using namespace plow;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (rows <= 0 || top_k <= 0 || max_len <= 0 || max_len > ld_scores || max_len > (1 << 20)) return -1;
-  plow::launch_pdl(dsa_q_prep_kernel, dim3((rows * kIdxHeads + 7) / 8), dim3(256), 0, stream, static_cast<uint8_t*>(q8), wq, static_cast<const __nv_bfloat16*>(q),
+  plow::launch_serial(dsa_q_prep_kernel, dim3((rows * kIdxHeads + 7) / 8), dim3(256), 0, stream, static_cast<uint8_t*>(q8), wq, static_cast<const __nv_bfloat16*>(q),
                                                                     ld_q, w, ld_w, rope_tab, pos, rows, rot, pair_mode);
   CUtensorMap tk, tq;
   int rc = make_tmap_2d(&tk, cache, 1, static_cast<uint64_t>(n_pages) * kIdxPage, kIdxDim, kIdxDim, kIdxPage, 128);
@@ -335,9 +335,9 @@ int plow_dsa_select(int* sel, float* scores, int ld_scores, void* q8, float* wq,
   constexpr int kSmem = 1024 + 24576 + 64 + 256 + 64;
   static DeviceOnce attr;
   if (ensure_smem(attr, dsa_score_kernel, kSmem) != cudaSuccess) return 3000;
-  plow::launch_pdl(dsa_score_kernel, dim3((max_len + 127) / 128, rows), dim3(128), kSmem, stream, scores, ld_scores, wq, cache_scale, pos, seq, page_table,
+  plow::launch_serial(dsa_score_kernel, dim3((max_len + 127) / 128, rows), dim3(128), kSmem, stream, scores, ld_scores, wq, cache_scale, pos, seq, page_table,
                                                                             max_pages, status, tk, tq);
-  plow::launch_pdl(dsa_topk_kernel, dim3(rows), dim3(1024), 0, stream, sel, scores, ld_scores, pos, top_k);
+  plow::launch_serial(dsa_topk_kernel, dim3(rows), dim3(1024), 0, stream, sel, scores, ld_scores, pos, top_k);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }
@@ -353,7 +353,7 @@ int plow_dsa_gather(void* ckv, float* cscale, float* csmax, int* clen, const int
   const size_t pages = static_cast<size_t>(rows) * (top_k / kIdxPage);
   cudaMemsetAsync(csmax, 0, pages * 4 * sizeof(float), stream);
   const long long items = static_cast<long long>(rows) * top_k;
-  plow::launch_pdl(dsa_gather_kernel, dim3(static_cast<unsigned>((items + 7) / 8)), dim3(256), 0, stream, 
+  plow::launch_serial(dsa_gather_kernel, dim3(static_cast<unsigned>((items + 7) / 8)), dim3(256), 0, stream, 
       static_cast<uint8_t*>(ckv), cscale, csmax, clen, sel, top_k, static_cast<const uint8_t*>(cache), scale, pos, seq,
       page_table, max_pages, rows, row_bytes);
   cudaError_t e = cudaGetLastError();

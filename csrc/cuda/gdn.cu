@@ -202,10 +202,10 @@ int plow_gdn(void* out, float* conv_state, float* ssm_state, const void* qkvz, i
   constexpr int kSmem = (kD * (kD + 1) + 2 * kD + 8) * sizeof(float);
   static plow::DeviceOnce attr;
   if (plow::ensure_smem(attr, gdn_kernel, kSmem) != cudaSuccess) return 3000;
-  plow::launch_pdl(gdn_kernel, dim3(rows, hv), dim3(kD), kSmem, reinterpret_cast<cudaStream_t>(stream), 
+  plow::launch_serial(gdn_kernel, dim3(rows, hv), dim3(kD), kSmem, reinterpret_cast<cudaStream_t>(stream), 
       static_cast<__nv_bfloat16*>(out), conv_state, ssm_state, static_cast<const __nv_bfloat16*>(qkvz), ld_qkvz,
       static_cast<const __nv_bfloat16*>(ba), ld_ba, conv_w, a_log, dt_bias, pos, seq, rows, hk, hv, conv);
-  plow::launch_pdl(gdn_conv_state_kernel, dim3(rows), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
+  plow::launch_serial(gdn_conv_state_kernel, dim3(rows), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
       conv_state, static_cast<const __nv_bfloat16*>(qkvz), ld_qkvz, pos, seq, rows, (2 * hk + hv) * kD);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
@@ -215,7 +215,7 @@ int plow_gated_norm(void* out, const void* o, const void* z, int ld_z, int z_ofs
                     int hd, float eps, void* stream) {
   if (rows <= 0) return -1;
   const long long items = static_cast<long long>(rows) * heads;
-  plow::launch_pdl(gated_norm_kernel, dim3(static_cast<unsigned>((items + 7) / 8)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
+  plow::launch_serial(gated_norm_kernel, dim3(static_cast<unsigned>((items + 7) / 8)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
       static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(z), ld_z, z_ofs,
       gamma, rows, heads, hd, eps);
   cudaError_t e = cudaGetLastError();
@@ -224,7 +224,7 @@ int plow_gated_norm(void* out, const void* o, const void* z, int ld_z, int z_ofs
 
 int plow_sigmoid_gate(void* out, const void* a, const void* gate, int64_t n, void* stream) {
   if (n <= 0) return -1;
-  plow::launch_pdl(sigmoid_gate_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
+  plow::launch_serial(sigmoid_gate_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
       static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(gate), n);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);

@@ -102,7 +102,8 @@ struct GemmCfg {
                                                    : kNBuf * kAccCols <= 256 ? 256 : 512;
   static constexpr int kStages =
       (196 * 1024 / kStageBytes) > 10 ? 10 : (196 * 1024 / kStageBytes);
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 2048 /*bars+scratch*/ + 4096 /*scale factors*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 2048 /*bars+scratch*/ + 4096 /*scale factors*/ +
+                                    8192 /*two transpose buffers of the swap-mode store*/;
   static_assert(kNBuf * kAccCols <= 512, "accumulators exceed TMEM");
   static_assert(kStages >= 2, "tile too large for shared memory");
 };
@@ -264,6 +265,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
   volatile int* never_flag = abort_flag + 1;                     // stays 0
   float* red_scratch = reinterpret_cast<float*>(ctrl + 512);     // [2][4][16] quant amax exchange (+ split-K flag)
   float* fac_smem = reinterpret_cast<float*>(ctrl + 2048);       // [4 warps][256] fp8 block-scale factors
+  uint8_t* tr_smem = ctrl + 2048 + 4096;                         // [2][4 KiB] token-major staging of a 128-feature x 16-token chunk
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -735,15 +737,40 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             pp[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
             continue;
           }
+          // A thread holds one feature of 16 tokens, so a direct store is 16 scattered 2-byte writes per thread
+          // (measured ~2300 clocks per chunk, which stalled the weight stream at every tile).  The common case goes
+          // through shared memory instead: the chunk is laid out token-major and leaves as 16-byte row segments.
+          const bool whole = !ws_tile && t.feat0 + 128 <= a.N && (a.ldy & 15) == 0;
+          if (whole && a.y && !a.out_f32 && !resid) {
+            __nv_bfloat16* tb16 = reinterpret_cast<__nv_bfloat16*>(tr_smem + (xchg_it & 1) * 4096);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int tok = t.tok0 + c + j;
-            const bool ok_e = fok && tok < t.tok_end && c + j >= col_lo && c + j < col_hi;
-            const size_t o = static_cast<size_t>(tok) * a.ldy + feat_i;
-            if (ok_e && resid) r[j] += __bfloat162float(resid[o]);
-            if (ok_e && a.y) {
-              if (a.out_f32) reinterpret_cast<float*>(a.y)[o] = r[j];
-              else reinterpret_cast<__nv_bfloat16*>(a.y)[o] = __float2bfloat16(r[j]);
+            for (int j = 0; j < 16; ++j) tb16[j * 128 + li] = __float2bfloat16(r[j]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&xchg_bar[xchg_it & 1]);
+            if (!mbar_wait(&xchg_bar[xchg_it & 1], (xchg_it >> 1) & 1, abort_flag)) {
+              *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagGemm); ok = false; break;
+            }
+            ++xchg_it;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              const int u = li * 2 + q;                 // 256 units of 16 bytes: 16 per token row
+              const int row = u >> 4, col = (u & 15) * 8;
+              const int tok = t.tok0 + c + row;
+              if (tok < t.tok_end)
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.y) + static_cast<size_t>(tok) * a.ldy + t.feat0 + col) =
+                    *reinterpret_cast<const uint4*>(tb16 + row * 128 + col);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int tok = t.tok0 + c + j;
+              const bool ok_e = fok && tok < t.tok_end && c + j >= col_lo && c + j < col_hi;
+              const size_t o = static_cast<size_t>(tok) * a.ldy + feat_i;
+              if (ok_e && resid) r[j] += __bfloat162float(resid[o]);
+              if (ok_e && a.y) {
+                if (a.out_f32) reinterpret_cast<float*>(a.y)[o] = r[j];
+                else reinterpret_cast<__nv_bfloat16*>(a.y)[o] = __float2bfloat16(r[j]);
+              }
             }
           }
           if (a.yq) {

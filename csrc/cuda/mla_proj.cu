@@ -367,7 +367,7 @@ int plow_mla_absorb(const void* q, int q_pitch, const void* wuk_t, const float* 
   AbsorbArgs a;
   a.q = static_cast<const __nv_bfloat16*>(q); a.rope_tab = rope_tab; a.pos = pos; a.q8 = static_cast<uint8_t*>(q8); a.sq = sq;
   a.status = status; a.T = T; a.heads = heads; a.q_pitch = q_pitch; a.pair_mode = pair_mode;
-  cudaError_t e = launch_pdl(mla_absorb_kernel, dim3(heads, (T + 127) / 128), dim3(kProjThreads), smem,
+  cudaError_t e = launch_serial(mla_absorb_kernel, dim3(heads, (T + 127) / 128), dim3(kProjThreads), smem,
                              reinterpret_cast<cudaStream_t>(stream_), a, tq, tw);
   if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
@@ -388,7 +388,7 @@ int plow_mla_fold(const void* opart, const float* lse, const int* kvlen, const v
   a.opart = static_cast<const __nv_bfloat16*>(opart); a.lse = lse; a.kvlen = kvlen; a.ao = static_cast<__nv_bfloat16*>(ao);
   a.aq = static_cast<uint8_t*>(aq); a.saq = saq; a.status = status; a.T = T; a.heads = heads; a.max_splits = max_splits;
   a.tiles_per_split = tiles_per_split; a.ld_saq = ld_saq;
-  cudaError_t e = launch_pdl(mla_fold_kernel, dim3(heads, (T + 127) / 128), dim3(kProjThreads), smem,
+  cudaError_t e = launch_serial(mla_fold_kernel, dim3(heads, (T + 127) / 128), dim3(kProjThreads), smem,
                              reinterpret_cast<cudaStream_t>(stream_), a, tw);
   if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);

@@ -579,7 +579,7 @@ extern "C" {
 
 int plow_embed(void* out, const void* tab, const int* ids, int R, int H, float scale, void* st) {
   if (H % 8) return -1;
-  plow::launch_pdl(embed_kernel, dim3(R), dim3(256), 0, S(st), (bf16*)out, (const bf16*)tab, ids, H, scale);
+  plow::launch_serial(embed_kernel, dim3(R), dim3(256), 0, S(st), (bf16*)out, (const bf16*)tab, ids, H, scale);
   return ok();
 }
 
@@ -589,7 +589,7 @@ int plow_rmsnorm(void* h_out, void* xq, float* sxq, int ld_sx, const void* x, co
   static plow::DeviceOnce attr;
   if (plow::ensure_smem(attr, norm_kernel<false>, 200 * 1024) != cudaSuccess) return 3000;
   const int threads = W >= 4096 ? 512 : (W >= 1024 ? 128 : 64);
-  plow::launch_pdl(norm_kernel<false>, dim3(R), dim3(threads), W * 4, S(st), (bf16*)h_out, (uint8_t*)xq, sxq, ld_sx, nullptr, (const bf16*)x, nullptr,
+  plow::launch_serial(norm_kernel<false>, dim3(R), dim3(threads), W * 4, S(st), (bf16*)h_out, (uint8_t*)xq, sxq, ld_sx, nullptr, (const bf16*)x, nullptr,
                                                    (const bf16*)gamma, W, x_pitch ? x_pitch : W, eps, plus_one);
   return ok();
 }
@@ -600,33 +600,33 @@ int plow_add_norm(void* h_out, void* xq, float* sxq, int ld_sx, void* x_out, con
   static plow::DeviceOnce attr;
   if (plow::ensure_smem(attr, norm_kernel<true>, 200 * 1024) != cudaSuccess) return 3000;
   const int threads = W >= 4096 ? 512 : (W >= 1024 ? 128 : 64);
-  plow::launch_pdl(norm_kernel<true>, dim3(R), dim3(threads), W * 4, S(st), (bf16*)h_out, (uint8_t*)xq, sxq, ld_sx, (bf16*)x_out, (const bf16*)x_in,
+  plow::launch_serial(norm_kernel<true>, dim3(R), dim3(threads), W * 4, S(st), (bf16*)h_out, (uint8_t*)xq, sxq, ld_sx, (bf16*)x_out, (const bf16*)x_in,
                                                   (const bf16*)delta, (const bf16*)gamma, W, W, eps, plus_one);
   return ok();
 }
 
 int plow_quant_act(void* xq, float* sxq, int ld_sx, const void* x, int R, int K, int x_pitch, void* st) {
   if (K % 128) return -1;
-  plow::launch_pdl(quant_act_kernel, dim3(R), dim3(K >= 4096 ? 512 : 128), 0, S(st), (uint8_t*)xq, sxq, ld_sx, (const bf16*)x, K, x_pitch ? x_pitch : K);
+  plow::launch_serial(quant_act_kernel, dim3(R), dim3(K >= 4096 ? 512 : 128), 0, S(st), (uint8_t*)xq, sxq, ld_sx, (const bf16*)x, K, x_pitch ? x_pitch : K);
   return ok();
 }
 
 int plow_mla_q_prep(void* q_nope_t, void* q_rope, const void* q, int q_pitch, const float* rope_tab, const int* pos, int T,
                     int heads, int nope, int rope, int pair_mode, void* st) {
-  plow::launch_pdl(mla_q_prep_kernel, dim3(T, heads), dim3(64), 0, S(st), (bf16*)q_nope_t, (bf16*)q_rope, (const bf16*)q, q_pitch, rope_tab, pos, T,
+  plow::launch_serial(mla_q_prep_kernel, dim3(T, heads), dim3(64), 0, S(st), (bf16*)q_nope_t, (bf16*)q_rope, (const bf16*)q, q_pitch, rope_tab, pos, T,
                                                       heads, nope, rope, pair_mode);
   return ok();
 }
 
 int plow_mla_q_quant(void* q8, float* sq, const void* q_abs, const void* q_rope, int T, int heads, int latent, int rope, void* st) {
-  plow::launch_pdl(mla_q_quant_kernel, dim3(T, heads), dim3(128), 0, S(st), (uint8_t*)q8, sq, (const bf16*)q_abs, (const bf16*)q_rope, T, latent, rope);
+  plow::launch_serial(mla_q_quant_kernel, dim3(T, heads), dim3(128), 0, S(st), (uint8_t*)q8, sq, (const bf16*)q_abs, (const bf16*)q_rope, T, latent, rope);
   return ok();
 }
 
 int plow_mla_kv_write(void* kv8, float* kv_scale, float* kv_smax, const void* kva, int pitch, int col_ofs, const void* gamma,
                       const float* rope_tab, const int* pos, const int* slot_of, const int* page_table, int max_pages, int T,
                       int latent, int rope, float eps, int pair_mode, void* st) {
-  plow::launch_pdl(mla_kv_write_kernel, dim3(T), dim3(128), (latent + rope) * 4, S(st), (uint8_t*)kv8, kv_scale, kv_smax, (const bf16*)kva, pitch, col_ofs,
+  plow::launch_serial(mla_kv_write_kernel, dim3(T), dim3(128), (latent + rope) * 4, S(st), (uint8_t*)kv8, kv_scale, kv_smax, (const bf16*)kva, pitch, col_ofs,
                                                               (const bf16*)gamma, rope_tab, pos, slot_of, page_table, max_pages,
                                                               latent, rope, eps, pair_mode);
   return ok();
@@ -636,14 +636,14 @@ int plow_router_topk(void* table, const float* logits, const float* bias, int T,
                      int sigmoid, int norm_topk, float route_scale, void* st) {
   if (k > 32 || n_group > 32 || E % (n_group > 0 ? n_group : 1)) return -1;
   const int wpb = 4;
-  plow::launch_pdl(router_topk_kernel, dim3((T + wpb - 1) / wpb), dim3(wpb * 32), wpb * 2 * E * 4, S(st), (int2*)table, logits, bias, T, E, k, n_group,
+  plow::launch_serial(router_topk_kernel, dim3((T + wpb - 1) / wpb), dim3(wpb * 32), wpb * 2 * E * 4, S(st), (int2*)table, logits, bias, T, E, k, n_group,
                                                                                 topk_group, sigmoid, norm_topk, route_scale);
   return ok();
 }
 
 int plow_moe_align(const void* table, int n_pairs, int e_base, int e_local, int* grp_off, int* tile_prefix, int* row_of_pair,
                    int* pair_of_row, int shared_rows, int shared_tok_base, int top_k, void* st) {
-  plow::launch_pdl(moe_align_kernel, dim3(1), dim3(1024), 2 * e_local * 4, S(st), (const int2*)table, n_pairs, e_base, e_local, grp_off, tile_prefix,
+  plow::launch_serial(moe_align_kernel, dim3(1), dim3(1024), 2 * e_local * 4, S(st), (const int2*)table, n_pairs, e_base, e_local, grp_off, tile_prefix,
                                                         row_of_pair, pair_of_row, shared_rows, shared_tok_base, top_k);
   return ok();
 }
@@ -651,35 +651,35 @@ int plow_moe_align(const void* table, int n_pairs, int e_base, int e_local, int*
 int plow_moe_gather(void* xs, float* sxs, int ld_sxs, const void* xq, const float* sx, int ld_sx, const int* pair_of_row,
                     const int* n_rows, int max_rows, int top_k, int K, void* st) {
   if (K % 128) return -1;
-  plow::launch_pdl(moe_gather_kernel, dim3(max_rows), dim3(128), 0, S(st), (uint8_t*)xs, sxs, ld_sxs, (const uint8_t*)xq, sx, ld_sx, pair_of_row, n_rows, top_k, K);
+  plow::launch_serial(moe_gather_kernel, dim3(max_rows), dim3(128), 0, S(st), (uint8_t*)xs, sxs, ld_sxs, (const uint8_t*)xq, sx, ld_sx, pair_of_row, n_rows, top_k, K);
   return ok();
 }
 
 int plow_moe_combine(void* out, const void* y, const void* shared, const void* table, const int* row_of_pair, int T, int top_k,
                      int H, const int* shared_base, void* st) {
   if (H % 8 || top_k > 16) return -1;
-  plow::launch_pdl(moe_combine_kernel, dim3(T, (H / 8 + 255) / 256), dim3(256), 0, S(st), (bf16*)out, (const bf16*)y, (const bf16*)shared, (const int2*)table, row_of_pair, top_k, H, shared_base);
+  plow::launch_serial(moe_combine_kernel, dim3(T, (H / 8 + 255) / 256), dim3(256), 0, S(st), (bf16*)out, (const bf16*)y, (const bf16*)shared, (const int2*)table, row_of_pair, top_k, H, shared_base);
   return ok();
 }
 
 int plow_argmax(int* out, const float* logits, int R, int V, void* st) {
-  plow::launch_pdl(argmax_kernel, dim3(R), dim3(1024), 0, S(st), out, logits, V);
+  plow::launch_serial(argmax_kernel, dim3(R), dim3(1024), 0, S(st), out, logits, V);
   return ok();
 }
 
 int plow_argmax_key(void* keys, const float* logits, int R, int V, int vocab_ofs, void* st) {
-  plow::launch_pdl(argmax_key_kernel, dim3(R), dim3(1024), 0, S(st), static_cast<unsigned long long*>(keys), logits, V, vocab_ofs);
+  plow::launch_serial(argmax_key_kernel, dim3(R), dim3(1024), 0, S(st), static_cast<unsigned long long*>(keys), logits, V, vocab_ofs);
   return ok();
 }
 
 int plow_argmax_fin(int* out, const void* keys, int R, int world, void* st) {
-  plow::launch_pdl(argmax_fin_kernel, dim3((R + 127) / 128), dim3(128), 0, S(st), out, static_cast<const unsigned long long*>(keys), R, world);
+  plow::launch_serial(argmax_fin_kernel, dim3((R + 127) / 128), dim3(128), 0, S(st), out, static_cast<const unsigned long long*>(keys), R, world);
   return ok();
 }
 
 int plow_row_gather(void* out, const void* x, const int* rows, int n, int W, void* st) {
   if (W % 8) return -1;
-  plow::launch_pdl(row_gather_kernel, dim3(n), dim3(128), 0, S(st), (bf16*)out, (const bf16*)x, rows, W);
+  plow::launch_serial(row_gather_kernel, dim3(n), dim3(128), 0, S(st), (bf16*)out, (const bf16*)x, rows, W);
   return ok();
 }
 
@@ -688,13 +688,13 @@ int plow_eltwise2(void* out, const void* a, const void* b, long long n, int mode
   if (n % 8 || n <= 0) return -1;
   const size_t n8 = static_cast<size_t>(n) / 8;
   const unsigned grid = static_cast<unsigned>(n8 / 256 + 1 < 1184 ? n8 / 256 + 1 : 1184);
-  plow::launch_pdl(eltwise2_kernel, dim3(grid), dim3(256), 0, S(st), (bf16*)out, (const bf16*)a, (const bf16*)b, n8, mode);
+  plow::launch_serial(eltwise2_kernel, dim3(grid), dim3(256), 0, S(st), (bf16*)out, (const bf16*)a, (const bf16*)b, n8, mode);
   return ok();
 }
 
 int plow_head_to_token(void* out, const void* x, int T, int heads, int W, void* st) {
   if (W % 8) return -1;
-  plow::launch_pdl(head_to_token_kernel, dim3(T, heads), dim3(32), 0, S(st), (bf16*)out, (const bf16*)x, T, heads, W);
+  plow::launch_serial(head_to_token_kernel, dim3(T, heads), dim3(32), 0, S(st), (bf16*)out, (const bf16*)x, T, heads, W);
   return ok();
 }
 

@@ -204,7 +204,7 @@ extern "C" {
 int plow_sample(int* out, const float* logits, int ld, int rows, int V, const float* temperature, const int* top_k,
                 const float* top_p, const float* min_p, const float* u, const void* seed, uint64_t step, void* stream) {
   if (rows <= 0 || V <= 0) return -1;
-  plow::launch_pdl(sample_kernel, dim3(rows), dim3(kThreads), 0, reinterpret_cast<cudaStream_t>(stream), 
+  plow::launch_serial(sample_kernel, dim3(rows), dim3(kThreads), 0, reinterpret_cast<cudaStream_t>(stream), 
       out, logits, ld, V, temperature, top_k, top_p, min_p, u, static_cast<const unsigned long long*>(seed), step);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
