@@ -55,6 +55,7 @@ struct MlaArgs {
   const int* kvlen;         // [T] tokens visible to each query row (including itself)
   const MlaItem* items;
   const int* n_items;
+  int* claim;               // work counter of this launch: CTAs take items from it one at a time (zeroed by the build kernel)
   __nv_bfloat16* opart;     // [T][max_splits][heads][512]
   float* lse;               // [T][max_splits][heads]   (log2 domain)
   int* status;
@@ -64,31 +65,46 @@ struct MlaArgs {
 };
 
 // ---------------------------------------------------------------------------------------------
+constexpr int kMlaClaimSlots = 256;   // one work counter per launch between two builds of the list (layers of a step)
+
 __global__ void mla_build_items(const int* kvlen, int T, int tiles_per_split, int max_splits,
-                                MlaItem* items, int* n_items) {
-  // one thread per request: split count, then its offset as the sum of the counts before it
-  extern __shared__ int cnt[];
+                                MlaItem* items, int* n_items, int* claims) {
+  // one thread per request: split count and tiles per split, then its offset in the list.  Up to 256 requests the
+  // list is ordered by decreasing tiles per item (longest first), which together with the dynamic hand-out in the
+  // attention kernel keeps the last CTAs from finishing long after the rest; larger batches keep request order.
+  extern __shared__ int cnt[];     // [T] splits, then [T] tiles per split
+  int* pers = cnt + T;
   pdl_launch_dependents();
   pdl_wait();
+  for (int i = threadIdx.x; i < kMlaClaimSlots; i += blockDim.x) claims[i] = 0;
   for (int r = threadIdx.x; r < T; r += blockDim.x) {
-    int per;
+    int per = 0;
     const int tiles = (kvlen[r] + kMlaPage - 1) / kMlaPage;
     cnt[r] = tiles > 0 ? kv_splits(tiles, tiles_per_split, max_splits, &per) : 0;     // nothing cached: no work item
+    pers[r] = tiles > 0 ? per : 0;
   }
   __syncthreads();
+  const bool by_size = T <= 256;
   for (int r = threadIdx.x; r < T; r += blockDim.x) {
+    const int my = pers[r];
     int off = 0;
-    for (int q = 0; q < r; ++q) off += cnt[q];
+    for (int q = 0; q < T; ++q) {
+      const bool before = by_size ? (pers[q] > my || (pers[q] == my && q < r)) : q < r;
+      off += before ? cnt[q] : 0;
+    }
     const int tiles = (kvlen[r] + kMlaPage - 1) / kMlaPage;
-    int per = 1;
-    const int ns = tiles > 0 ? kv_splits(tiles, tiles_per_split, max_splits, &per) : 0;
+    const int ns = cnt[r], per = my > 0 ? my : 1;
     for (int split = 0; split < ns; ++split) {
       const int t0 = split * per;
       const int nt = min(per, tiles - t0);
       items[2 * (off + split)] = MlaItem{r, 0, split, t0, nt, 0, 0, 0};
       items[2 * (off + split) + 1] = MlaItem{r, 1, split, t0, nt, 0, 0, 0};
     }
-    if (r == T - 1) *n_items = 2 * (off + ns);
+  }
+  if (threadIdx.x == 0) {
+    int tot = 0;
+    for (int q = 0; q < T; ++q) tot += cnt[q];
+    *n_items = 2 * tot;
   }
 }
 
@@ -112,7 +128,9 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
   uint64_t* o_free = pv_done + 2;            // [1]
   uint64_t* drain_bar = o_free + 1;          // [1]
   uint64_t* xchg_bar = drain_bar + 1;        // [2] softmax half-row exchange
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(xchg_bar + 2);
+  uint64_t* it_full = xchg_bar + 2;          // [4] the producer has published the item index of item n in slot n & 3
+  volatile int* item_slot = reinterpret_cast<volatile int*>(it_full + 4);   // [4]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(const_cast<int*>(item_slot) + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   volatile int* never_flag = abort_flag + 1;
   float2* xchg = reinterpret_cast<float2*>(ctrl + 1024);   // [2 parity][2 half][128 rows] (max, sk max)
@@ -131,6 +149,7 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
     mbar_init(&pv_done[1], 1);
     mbar_init(o_free, 8);
     mbar_init(drain_bar, 1);
+    for (int b = 0; b < 4; ++b) mbar_init(&it_full[b], 1);
     *abort_flag = 0;
     *never_flag = 0;
     fence_mbar_init();
@@ -146,15 +165,27 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
   const uint32_t tm_q = tmem_base + 384;    // latent Q as e4m3 A operand: 128 columns (4 bytes of K per column)
   pdl_wait();     // work list, queries and this step's cache rows come from the kernels before this one
   const int n_items = *a.n_items;
+  // Items are handed out dynamically: requests differ eightfold in length, and a static deal left some CTAs with
+  // half again the average work.  The producer thread takes the next index from the launch's counter and publishes
+  // it (or -1 at the end) through shared memory; the other roles pick it up from there.
+  auto consumer_item = [&](uint32_t n) -> int {
+    if (!mbar_wait(&it_full[n & 3], (n >> 2) & 1, abort_flag)) return -2;
+    return item_slot[n & 3];
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       uint32_t item_it = 0, kv_it = 0;
       bool ok = true;
-      for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x, ++item_it) {
+      for (;; ++item_it) {
+        int it = ok ? atomicAdd(a.claim, 1) : n_items;
+        if (it >= n_items) it = -1;
+        item_slot[item_it & 3] = it;
+        mbar_arrive(&it_full[item_it & 3]);     // release: the slot write is visible to whoever sees the phase complete
+        if (it < 0) break;
         const MlaItem w = a.items[it];
-        if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagMlaDecode); break; }
+        if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagMlaDecode); ok = false; continue; }
         mbar_expect_tx(q_full, kQBytes);
         tma_load_3d(q_smem, &tm_qr, 512, w.req, 0, q_full);
         const int* pt = a.page_table + static_cast<size_t>(a.slot_of[w.req]) * a.max_pages;
@@ -204,7 +235,9 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
         tc_commit(&s_full[ti & 1]);
         return true;
       };
-      for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x, ++item_it) {
+      for (; ok; ++item_it) {
+        const int it = consumer_item(item_it);
+        if (it < 0) { if (it == -2) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagMlaDecode); } break; }
         const MlaItem w = a.items[it];
         if (!mbar_wait(q_full, item_it & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT | kTagMlaDecode); break; }
         if (!mbar_wait(qt_full, item_it & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagMlaDecode); break; }
@@ -256,7 +289,9 @@ mla_decode_kernel(const MlaArgs a, const __grid_constant__ CUtensorMap tm_qr,
       ++xit;
       return true;
     };
-    for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x, ++item_it) {
+    for (; ok; ++item_it) {
+      const int it = consumer_item(item_it);
+      if (it < 0) { if (it == -2) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagMlaDecode); } break; }
       const MlaItem w = a.items[it];
       const int kv_len = a.kvlen[w.req];
       const float qs = a.sq[static_cast<size_t>(li) * a.T + w.req] * a.scale_log2e;
@@ -493,11 +528,12 @@ void plow_mla_set_trace(void* p) { g_mla_trace = static_cast<long long*>(p); }
 
 // The work list depends only on the rows' KV lengths, which are the same for every layer of a step: the engine
 // builds it once per step with this entry and passes build_items = 0 to plow_mla_decode for every layer.
-int plow_mla_build_items(const int* kvlen, int T, int tiles_per_split, int max_splits, void* items, int* n_items, void* stream_) {
+// `claims`: int[256] work counters, zeroed here; every decode launch until the next build takes its own (claim_slot).
+int plow_mla_build_items(const int* kvlen, int T, int tiles_per_split, int max_splits, void* items, int* n_items, int* claims, void* stream_) {
   using namespace plow;
   if (T <= 0 || max_splits <= 0 || tiles_per_split <= 0) return -1;
-  cudaError_t e = launch_serial(mla_build_items, dim3(1), dim3(256), T * sizeof(int), reinterpret_cast<cudaStream_t>(stream_),
-                             kvlen, T, tiles_per_split, max_splits, static_cast<MlaItem*>(items), n_items);
+  cudaError_t e = launch_serial(mla_build_items, dim3(1), dim3(256), 2 * T * sizeof(int), reinterpret_cast<cudaStream_t>(stream_),
+                             kvlen, T, tiles_per_split, max_splits, static_cast<MlaItem*>(items), n_items, claims);
   if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }
@@ -510,10 +546,10 @@ int plow_mla_build_items(const int* kvlen, int T, int tiles_per_split, int max_s
 int plow_mla_decode(const void* q8, const float* sq, const void* kv, const float* kv_scale, const float* kv_smax, int64_t n_pages,
                     const int* page_table, int max_pages, const int* slot_of, const int* kvlen, int T,
                     int tiles_per_split, int max_splits, void* items, int* n_items, void* opart, float* lse,
-                    void* out, float softmax_scale, int build_items, int* status, void* stream_) {
+                    void* out, float softmax_scale, int build_items, int* claims, int claim_slot, int* status, void* stream_) {
   using namespace plow;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  if (T <= 0 || max_splits <= 0 || tiles_per_split <= 0) return -1;
+  if (T <= 0 || max_splits <= 0 || tiles_per_split <= 0 || !claims) return -1;
   CUtensorMap tqr, tkv, tkvr;
   int r = make_tmap_3d(&tqr, q8, 1, kMlaRow, T, kMlaHeads, kMlaRow, static_cast<uint64_t>(T) * kMlaRow, 1, 128, 64);
   if (r) return 1100 + r;
@@ -524,11 +560,12 @@ int plow_mla_decode(const void* q8, const float* sq, const void* kv, const float
   static DeviceOnce attr;
   if (ensure_smem(attr, mla_decode_kernel, kMlaSmem) != cudaSuccess) return 3000;
   if (build_items)
-    launch_serial(mla_build_items, dim3(1), dim3(256), T * sizeof(int), stream, kvlen, T, tiles_per_split, max_splits,
-               static_cast<MlaItem*>(items), n_items);
+    launch_serial(mla_build_items, dim3(1), dim3(256), 2 * T * sizeof(int), stream, kvlen, T, tiles_per_split, max_splits,
+                  static_cast<MlaItem*>(items), n_items, claims);
   MlaArgs a;
   a.q8 = static_cast<const uint8_t*>(q8); a.sq = sq; a.kv_scale = kv_scale; a.kv_smax = kv_smax; a.page_table = page_table; a.slot_of = slot_of; a.kvlen = kvlen;
   a.items = static_cast<const MlaItem*>(items); a.n_items = n_items;
+  a.claim = claims + (build_items ? 0 : ((claim_slot % kMlaClaimSlots) + kMlaClaimSlots) % kMlaClaimSlots);
   a.opart = static_cast<__nv_bfloat16*>(opart); a.lse = lse; a.status = status;
 #ifdef PLOW_DEVICE_TRACE
   a.trace = g_mla_trace;

@@ -68,6 +68,7 @@ class DecodeWorkspace:
         self.max_splits = max(1, -(-((max_ctx + 63) // 64) // tiles_per_split))
         self.items = torch.empty(2 * max_T * self.max_splits * 8, dtype=torch.int32, device=device)
         self.n_items = torch.zeros(1, dtype=torch.int32, device=device)
+        self.claims = torch.zeros(256, dtype=torch.int32, device=device)    # work counters of the launches that share one list
         self.opart = torch.empty(max_T, self.max_splits, heads, latent, dtype=BF16, device=device)
         self.lse = torch.empty(max_T, self.max_splits, heads, dtype=torch.float32, device=device)
 
@@ -75,11 +76,11 @@ class DecodeWorkspace:
 def build_items(kvlen, T, ws: DecodeWorkspace):
     """Work list of the split-KV decode kernel for rows with `kvlen` visible tokens.  It depends on the lengths only, so
     one call serves every layer of a step (pass ``build_items=False`` to :func:`decode`)."""
-    native.call("plow_mla_build_items", kvlen, T, ws.tiles_per_split, ws.max_splits, ws.items, ws.n_items)
+    native.call("plow_mla_build_items", kvlen, T, ws.tiles_per_split, ws.max_splits, ws.items, ws.n_items, ws.claims)
 
 
 def decode(q8, sq, kv8, kv_scale, kv_smax, page_table, slot_of, kvlen, ws: DecodeWorkspace, softmax_scale, out=None, merge=True,
-           build_items=True):
+           build_items=True, claim_slot=0):
     """q8 [128][T][576] e4m3, sq [128][T]; kv8 [pages][64][576]; kv_smax f32 [pages][4] (element 0 bounds the
     page's scales from above); returns oacc bf16 [128][T][512]."""
     heads, T, _ = q8.shape
@@ -88,5 +89,5 @@ def decode(q8, sq, kv8, kv_scale, kv_smax, page_table, slot_of, kvlen, ws: Decod
         out = torch.empty(heads, T, 512, dtype=BF16, device=q8.device)
     native.call("plow_mla_decode", q8, sq, kv8, kv_scale, kv_smax, kv8.shape[0], page_table, page_table.shape[1], slot_of, kvlen, T,
                 ws.tiles_per_split, ws.max_splits, ws.items, ws.n_items, ws.opart, ws.lse, out, float(softmax_scale),
-                int(build_items), native.status_word(q8.device))
+                int(build_items), ws.claims, int(claim_slot), native.status_word(q8.device))
     return out

@@ -125,8 +125,8 @@ _SIGS = {
     "plow_row_gather": "pppiip",
     "plow_head_to_token": "ppiiip",
     "plow_eltwise2": "pppl" "ip",
-    "plow_mla_decode": "ppppplpipp" "iiipppppfipp",
-    "plow_mla_build_items": "piiippp",
+    "plow_mla_decode": "ppppplpipp" "iiipppppfipipp",
+    "plow_mla_build_items": "piiipppp",
     "plow_mla_absorb": "pipppppiiipp",
     "plow_mla_fold": "pppppppiiiiipp",
     "plow_ep_counts": "ppipp",

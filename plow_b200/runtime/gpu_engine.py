@@ -453,7 +453,7 @@ class GpuEngine(EngineBase):
                 mla_ops.build_items(self.d_kvlen_row, T, self._mla_ws)
                 st.scratch["mla_items"] = True
             mla_ops.decode(q8, sq, cache, scale, self.kv_smax[layer], self.d_page_table, self.d_in[2], self.d_kvlen_row,
-                           self._mla_ws, float(ins.f[0]), merge=False, build_items=False)
+                           self._mla_ws, float(ins.f[0]), merge=False, build_items=False, claim_slot=layer)
             kvlen = self.d_kvlen_row
         want = self._wants_q(st, ins.t[0])
         aq, saq = mla_ops.fold(self._mla_ws, kvlen, wuv, T, heads, ao, want_fp8=want)
