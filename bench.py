@@ -78,6 +78,66 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": reasons, "samples": len(sm)}
 
 
+def serving_phase(eng, spec, world, rank, n_req, n_out, chunk, slots, dev) -> dict:
+    """One wave of `n_req` requests per GPU through ModelMux (the scheduler the HTTP server uses)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from plow_b200.runtime.scheduler import GenParams, ModelMux, SchedConfig
+    from plow_b200.text.tokenizer import ByteTokenizer
+    for s in list(eng.pool.seqs):
+        eng.retire_slot(s)
+    if world > 1:
+        from plow_b200.parallel.group import StepGroup
+        eng.step_group = StepGroup(rank, world, timeout_s=120.0)
+        eng.lockstep = True
+        stats_pg = dist.new_group(backend="gloo")
+    eng.max_slots = slots
+    mux = ModelMux(eng, ByteTokenizer(), SchedConfig(token_budget=chunk, objective="auto", queue_ttl_s=3600.0))
+    rng = np.random.default_rng(1000 + rank)
+    prompts = [rng.integers(3, spec.vocab, size=int(n)).tolist() for n in rng.integers(1024, 8193, size=n_req)]
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    mux.start()
+    reqs = [mux.submit(p, GenParams(max_tokens=n_out, ignore_eos=True)) for p in prompts]
+    n_tok, failed = 0, 0
+    for r in reqs:
+        while True:
+            ch = r.out.get(timeout=1800)
+            if ch.kind == "token":
+                n_tok += 1
+            elif ch.kind == "done":
+                break
+            else:
+                failed += 1
+                break
+    wall = time.perf_counter() - t0
+    # The dispatcher thread keeps joining the other ranks' steps while this thread waits for the slowest rank.  The
+    # totals travel over a CPU (gloo) group: a device collective issued from this thread would sit in the stream between
+    # two steps of this rank and wait for ranks that are still stepping.
+    snap = mux.metrics.snapshot()
+    ttft, tpot = snap["ttft_ms"], snap["tpot_ms"]
+    t = torch.tensor([float(n_tok), float(failed), float(sum(len(p) for p in prompts)), ttft["p50"] or 0.0, tpot["p50"] or 0.0,
+                      ttft["p99"] or 0.0, tpot["p99"] or 0.0], dtype=torch.float64)
+    w = torch.tensor([wall], dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=stats_pg)
+        dist.all_reduce(w, op=dist.ReduceOp.MAX, group=stats_pg)
+    mux.stop()
+    eng.step_group, eng.lockstep = None, False
+    tot_tok, tot_failed, tot_prompt, max_wall = float(t[0]), float(t[1]), float(t[2]), float(w[0])
+    pair = t[3:] / world
+    return {"requests": n_req * world, "output_tokens": int(tot_tok), "prompt_tokens": int(tot_prompt), "failed": int(tot_failed),
+            "wall_s": round(max_wall, 2), "output_tok_s": round(tot_tok / max_wall, 1),
+            "p50_ttft_ms": round(float(pair[0]), 1), "p50_tpot_ms": round(float(pair[1]), 3),
+            "p99_ttft_ms": round(float(pair[2]), 1), "p99_tpot_ms": round(float(pair[3]), 3),
+            "note": "one wave: every request arrives at t = 0, so TTFT includes the queue behind the other prompts' prefill; "
+                    "percentiles are per rank, averaged over ranks",
+            "counters": {k: snap["counters"].get(k) for k in ("prefill_ticks", "decode_ticks", "preemptions", "rider_rows")}}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -88,6 +148,10 @@ def main() -> int:
     ap.add_argument("--batch-per-gpu", type=int, default=64)
     ap.add_argument("--ttft-prompts", type=int, default=2)
     ap.add_argument("--prefill-chunk", type=int, default=2048, help="rows of the prefill program used for the TTFT prompts")
+    ap.add_argument("--serve-requests", type=int, default=-1,
+                    help="requests per GPU of the serving phase that measures TTFT / TPOT under load through the scheduler "
+                         "(-1: as many as decode slots; 0: skip the phase)")
+    ap.add_argument("--serve-output", type=int, default=512, help="output tokens per request in the serving phase")
     ap.add_argument("--no-baseline", action="store_true", help="skip the NCCL-arm run that follows the timed region at N > 1")
     ap.add_argument("--init", default="scaled", choices=["scaled", "plain"],
                     help="scaled: depth-scaled random init (balanced routing, like a trained checkpoint); plain: N(0,0.02) everywhere")
@@ -122,7 +186,7 @@ def main() -> int:
     g = graph.build_graph(spec, ep=world, rank=rank)
     sites = rewrite.fuse(g)
     max_ctx = 8192 + 512 + 64
-    pkt = emit.emit_packet(g, sites, hwspec.lookup("b200"), 148, dict(prefill=sorted({512, args.prefill_chunk}), decode=[B], max_seqs=8), rank=rank)
+    pkt = emit.emit_packet(g, sites, hwspec.lookup("b200"), 148, dict(prefill=sorted({512, args.prefill_chunk}), decode=[B], max_seqs=max(8, B)), rank=rank)
     comm = None
     if world > 1:
         from plow_b200.parallel.ep import EpComm
@@ -248,6 +312,17 @@ def main() -> int:
     for n in list(np.random.default_rng(11).integers(1024, 8193, size=args.ttft_prompts)):
         ttft_lens.append(int(n))
         ttfts.append(prefill_once(int(n)))
+    # ---- serving phase: the named workload through the scheduler.  Every GPU gets `serve_requests` requests at once
+    # (prompts uniform in [1024, 8192] random token ids, `serve_output` output tokens each, greedy, EOS ignored); the
+    # continuous-batching scheduler of each rank prefills in chunks, decodes, and the ranks step in lockstep
+    # (plow_b200/parallel/group.py).  TTFT / TPOT are the scheduler's own per-request measurements.
+    serve = None
+    n_serve = B if args.serve_requests < 0 else args.serve_requests
+    if n_serve:
+        try:
+            serve = serving_phase(eng, spec, world, rank, n_serve, args.serve_output, args.prefill_chunk, B, dev)
+        except Exception as e:          # the decode-step figures above stand on their own
+            serve = {"error": f"{type(e).__name__}: {e}"[:300]}
     dev_total = float(np.sum(dev_ms))
     stats = torch.tensor([dev_total, wall, float(np.median(dev_ms))], dtype=torch.float64, device=dev)
     if world > 1:
@@ -271,8 +346,10 @@ def main() -> int:
                        "seq_len": "ctx uniform 1024-8192 + decoded tokens", "parallelism": f"ep{world} + dp-attention",
                        "l2": "no flush needed: each step streams >90 GB of weights and KV per GPU (L2 is 126 MB)",
                        "named_config": bool(world == 8 and args.layers == 61)},
-            "p50_tpot_ms": round(tpot, 3), "p50_ttft_ms": round(float(np.median(ttfts)), 1) if ttfts else None,
-            "ttft_prompts": len(ttfts), "ttft_ms_all": [round(t, 1) for t in ttfts], "ttft_prompt_tokens": ttft_lens,
+            "p50_tpot_ms": (serve or {}).get("p50_tpot_ms"), "p50_ttft_ms": (serve or {}).get("p50_ttft_ms"),
+            "serving": serve, "decode_step_p50_ms": round(tpot, 3),
+            "idle_ttft_ms": round(float(np.median(ttfts)), 1) if ttfts else None, "idle_ttft_ms_all": [round(t, 1) for t in ttfts],
+            "idle_ttft_prompt_tokens": ttft_lens,
             "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": int(4 * 4 * B), "d2h_bytes_per_step": int(4 * B)},
             "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": int(launches_per_step),
             "clocks": clocks, "load_s": round(load_s, 1), "ep_routing_last_layer": route,

@@ -418,6 +418,20 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
     // ------------------------------------------------------------ epilogue warps (2..5)
     pdl_wait();    // activation scales, residual, workspace counters and the epoch word below come from earlier kernels
     const uint32_t ar_ep = a.ar_world > 1 ? *a.ar_epoch + 1 : 0;   // this launch's all-reduce epoch
+    if (a.wait_ctr) {
+      // expert-parallel dispatch: the activation scales these warps prefetch are written by peer GPUs together with
+      // the rows, so they too start only once the arrival counter says everything has landed (one poller per warp,
+      // with back-off: the polled line is also the target of the peers' remote adds)
+      if ((threadIdx.x & 31) == 0) {
+        const uint32_t target = *a.wait_epoch * a.wait_mult;
+        const unsigned long long t0 = globaltimer_ns();
+        while (ld_acquire_sys(a.wait_ctr) < target) {
+          if (*abort_flag || globaltimer_ns() - t0 > static_cast<unsigned long long>(a.wait_deadline_ms) * 1000000ull) break;
+          __nanosleep(512);
+        }
+      }
+      __syncwarp();
+    }
     const int lq = warp & 3;               // TMEM lane quarter this warp may read
     const int li = lq * 32 + lane;         // lane (row of D) owned by this thread
     const uint32_t lane_addr = static_cast<uint32_t>(lq * 32) << 16;

@@ -152,6 +152,17 @@ class EngineBase:
     def step(self, batch: TokenBatch) -> StepResult:   # pragma: no cover - interface
         raise NotImplementedError
 
+    def bind_thread(self) -> None:
+        """Called by a thread before it drives the engine (the current CUDA device is per host thread)."""
+
+    # ---- rank groups ---------------------------------------------------------------------------
+    lockstep = False          # True: the scheduler must call idle_step() whenever it has nothing to run
+
+    def idle_step(self) -> bool:
+        """Join the other ranks' step with an empty batch (engines in a lockstep rank group).  Returns False when no
+        rank had work, so the caller may sleep."""
+        return False
+
     def kv_arrays(self) -> dict:                       # pragma: no cover - interface
         """name -> page-indexed array of every KV tensor (for KV images and the host tier)."""
         raise NotImplementedError

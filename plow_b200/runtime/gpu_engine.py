@@ -136,7 +136,7 @@ class _Prog:
 class GpuEngine(EngineBase):
     def __init__(self, assets_dir=None, packet=None, weights: WeightSource | None = None, max_slots=64, n_pages=None,
                  max_ctx=8192, kv_fraction=0.9, prefix_cache=True, cuda_graphs=True, device=None, rank=0,
-                 comm=None, rungs=None, device_interp=None, tp_comm=None):
+                 comm=None, rungs=None, device_interp=None, tp_comm=None, step_group=None, leader_group=None):
         if not torch.cuda.is_available():
             raise EngineError("GpuEngine needs a CUDA device", fatal=True)
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
@@ -146,6 +146,11 @@ class GpuEngine(EngineBase):
             name = "model.pkt" if rank == 0 else f"model.rank{rank}.pkt"
             packet = pk.read_packet(Path(assets_dir) / name)
         self.rank, self.comm, self.tp_comm = rank, comm, tp_comm
+        # rank groups (plow_b200/parallel/group.py): step_group = every rank schedules its own requests and the ranks
+        # agree on the program before each launch (expert parallelism with data-parallel attention); leader_group =
+        # rank 0 schedules, the others replay its steps (tensor parallelism)
+        self.step_group, self.leader_group = step_group, leader_group
+        self.lockstep = step_group is not None
         # row-class segments run inside the persistent on-device interpreter (PLOW_DEVICE_INTERP=0 turns it off)
         self.device_interp = (os.environ.get("PLOW_DEVICE_INTERP", "1") != "0") if device_interp is None else bool(device_interp)
         shards = packet.section_json("weight_shards.json") or {}
@@ -698,12 +703,46 @@ class GpuEngine(EngineBase):
                 self.d_page_table[slot].copy_(self.h_page_table[slot], non_blocking=True)
         self._dirty_slots.clear()
 
-    def step(self, batch: TokenBatch) -> StepResult:
+    def bind_thread(self) -> None:
+        # a new host thread starts on device 0: kernels launched through ctypes go to the *current* device, so a
+        # dispatcher thread of a rank on another GPU must select it first
+        torch.cuda.set_device(self.device)
+
+    def set_page_row(self, slot: int, row) -> None:
+        """Follower ranks: install the leader's page-table row of `slot`."""
+        n = min(len(row), self.h_page_table.shape[1])
+        self.page_table[slot, :n] = row[:n]
+        self._dirty_slots.add(slot)
+
+    def idle_step(self) -> bool:
+        if self.step_group is None:
+            return False
+        e = np.zeros(0, np.int32)
+        return self.step(TokenBatch(e, e, e, e, decode=True)) is not None
+
+    def step(self, batch: TokenBatch, replay: bool = False) -> StepResult:
         rows, ns = batch.rows, int(batch.sample_rows.shape[0])
-        idx = self.pick_program(rows, batch.decode)
+        decode = batch.decode
+        if self.step_group is not None:
+            # every rank launches the same program: agree on role and row count first (a rank without work joins with
+            # an empty batch; when no rank has work nothing is launched)
+            decode, g_rows, busy, g_samples = self.step_group.agree(batch.decode, rows, rows > 0, samples=ns)
+            if not busy:
+                return None
+            prog_rows = g_rows
+        else:
+            prog_rows = rows
+        if self.leader_group is not None and self.rank == 0 and not replay:
+            self.leader_group.publish(dict(
+                batch=dict(ids=batch.ids, pos=batch.pos, seq=batch.seq, sample_rows=batch.sample_rows, decode=batch.decode,
+                           want_logits=batch.want_logits),
+                pages={int(s): self.page_table[s].copy() for s in self._dirty_slots}))
+        idx = self.pick_program(max(prog_rows, 1), decode)
         st = self._prepare(idx)
         st.prog = self.packet.programs[idx]
         R = st.rows
+        if ns > st.samples:
+            raise EngineError(f"step samples {ns} rows but the program samples {st.samples}: compile with max_seqs >= the decode width")
         hin = self.h_in
         hin[0, :rows] = torch.from_numpy(batch.ids)
         hin[1, :rows] = torch.from_numpy(batch.pos)
@@ -711,7 +750,8 @@ class GpuEngine(EngineBase):
         hin[0, rows:R] = 0
         hin[1, rows:R] = 0
         hin[2, rows:R] = self.scratch_slot
-        hin[3, :ns] = torch.from_numpy(batch.sample_rows)
+        if ns:
+            hin[3, :ns] = torch.from_numpy(batch.sample_rows)
         hin[3, ns:st.samples] = 0
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
@@ -719,7 +759,7 @@ class GpuEngine(EngineBase):
         self.d_in[:, :R].copy_(hin[:, :R], non_blocking=True)
         torch.add(self.d_in[1, :R], 1, out=self.d_kvlen_row[:R])
         try:
-            if self.cuda_graphs and batch.decode:
+            if self.cuda_graphs and decode:
                 if st.graph is None:
                     # the first step of a rung runs eagerly (allocations, attribute sets) and IS the step; the graph is
                     # captured afterwards without being replayed, because a program with recurrent state (gated delta

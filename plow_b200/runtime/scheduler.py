@@ -186,6 +186,9 @@ class ModelMux:
         self._stop.set()
         if self._thread:
             self._thread.join(timeout=10)
+        grp = getattr(self.engine, "step_group", None) or getattr(self.engine, "leader_group", None)
+        if grp is not None:
+            grp.stop()          # releases the other ranks from their next agreement / receive
 
     def submit(self, prompt: list, params: GenParams, rid: str | None = None) -> Request:
         with self._submit_lock:             # handlers of several HTTP worker threads submit concurrently
@@ -247,13 +250,25 @@ class ModelMux:
 
     # ---- loop ----------------------------------------------------------------------------------
     def _loop(self) -> None:
+        from ..parallel.group import GroupStopped
+        lockstep = getattr(self.engine, "lockstep", False)
+        self.engine.bind_thread()
         while not self._stop.is_set():
             try:
                 if not self.tick():
+                    if lockstep:
+                        # the other ranks of the group may have work: every launch of theirs needs this rank too
+                        if not self.engine.idle_step():
+                            time.sleep(0.001)
+                        continue
                     try:
                         self.waiting.append(self.ingress.get(timeout=0.02))
                     except queue.Empty:
                         pass
+            except GroupStopped as e:
+                # the rank group is gone (a member stopped or failed): nothing can run any more
+                self._on_engine_error(EngineError(f"rank group stopped: {e}", fatal=True))
+                return
             except EngineError as e:
                 self._on_engine_error(e)
             except Exception as e:      # a scheduler bug must not leave every request hanging behind a dead thread

@@ -35,18 +35,26 @@ class SharedSeedWeights(SyntheticWeights):
     def _full(self, ent, fp8):
         import zlib
         dims = [int(d) for d in ent.dims]
-        stacked = ent.name.startswith("cat/") and ".experts." in ent.name
+        # stacked expert matrices: "<...>.experts.<part>" holds e_local experts, "<...>.experts_shared.<part>" holds
+        # e_local experts followed by the (replicated) shared expert
+        shared = ent.name.startswith("cat/") and ".experts_shared." in ent.name
+        stacked = shared or (ent.name.startswith("cat/") and ".experts." in ent.name)
+        e_local = self.n_experts // self.ep
+        blk = dims[0] // (e_local + (1 if shared else 0)) if stacked else 0
         if stacked:
-            dims[0] *= self.ep
+            dims[0] = blk * (self.n_experts + (1 if shared else 0))      # the whole model's stack, same on every rank
         self.gen.manual_seed(zlib.crc32(ent.name.encode()))
         e = pk.TensorEnt(ent.name, ent.dtype, ent.tclass, tuple(dims))
         out = SyntheticWeights.fp8(self, e, None) if fp8 else SyntheticWeights.bf16(self, e, None)
         if stacked:
-            per = dims[0] // self.ep
-            sl = slice(self.rank * per, (self.rank + 1) * per)
+            rows = list(range(self.rank * e_local * blk, (self.rank + 1) * e_local * blk))
+            if shared:
+                rows += list(range(self.n_experts * blk, (self.n_experts + 1) * blk))
+            idx = torch.tensor(rows, device=self.device)
             if fp8:
-                return out[0][sl].contiguous(), out[1][self.rank * per // 128:(self.rank + 1) * per // 128].contiguous()
-            return out[sl].contiguous()
+                sidx = torch.tensor(sorted({r // 128 for r in rows}), device=self.device)
+                return out[0].view(torch.uint8)[idx].view(torch.float8_e4m3fn).contiguous(), out[1][sidx].contiguous()
+            return out[idx].contiguous()
         return out
     def bf16(self, ent, recipe): return self._full(ent, False)
     def fp8(self, ent, recipe): return self._full(ent, True)
@@ -92,7 +100,7 @@ def test_ep_matches_single_gpu(impl, tmp_path):
     f = tmp_path / "worker.py"
     f.write_text(WORKER)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, PLOW_ROOT=root, PLOW_IMPL=impl, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, PLOW_ROOT=root, PLOW_IMPL=impl)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                         "--master-addr", "127.0.0.1", "--master-port", "29611", str(f)], env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]

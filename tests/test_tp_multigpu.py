@@ -71,7 +71,7 @@ def test_fused_gemm_allreduce(tmp_path):
     f = tmp_path / "worker.py"
     f.write_text(WORKER)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, PLOW_ROOT=root, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, PLOW_ROOT=root)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
                         "--master-port", "29621", str(f)], env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
@@ -180,7 +180,7 @@ def _run(worker_src, tmp_path, port, extra_env=None, nproc=2, timeout=420):
     f = tmp_path / "worker.py"
     f.write_text(worker_src)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, PLOW_ROOT=root, NCCL_NVLS_ENABLE="0", **(extra_env or {}))
+    env = dict(os.environ, PLOW_ROOT=root, **(extra_env or {}))
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
                         "127.0.0.1", "--master-port", str(port), str(f)], env=env, capture_output=True, text=True, timeout=timeout)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
