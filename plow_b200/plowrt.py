@@ -64,6 +64,27 @@ def cmd_serve(args) -> int:
                                              api_keys=args.api_key or None, dp=args.dp, spec_depth=args.spec_depth, pd=args.pd or None))
     state = AppState(api_keys=cfg.api_keys, timeline=Timeline(cfg.trace), loader=lambda n, p: make_entry(n, p, cfg))
     name = args.name or Path(args.assets).resolve().name
+    n_ranks, mode = (args.ep, "ep") if args.ep else (args.tp, "tp") if args.tp else (args.dp_procs, "dp") if args.dp_procs else (0, "")
+    if n_ranks:
+        # one rank-worker process per GPU; this process keeps HTTP, routing and supervision (serve/rank_group.py)
+        from .parallel.dp import DpRouter
+        from .serve.app import ModelEntry
+        from .serve.rank_group import RankGroup
+        from .serve.template import ChatTemplate
+        from .text.tokenizer import load_tokenizer
+        wargs = []
+        for flag, val in (("--max-slots", args.max_slots), ("--max-ctx", args.max_ctx), ("--backend", args.backend)):
+            if val is not None:
+                wargs += [flag, str(val)]
+        group = RankGroup(args.assets, n_ranks, mode, worker_args=wargs)
+        state.add(ModelEntry(name, group.muxes[0], load_tokenizer(args.assets), ChatTemplate.from_assets(args.assets)))
+        if len(group.muxes) > 1:
+            state.router = DpRouter(group.muxes)
+        try:
+            uvicorn.run(create_app(state), host=cfg.host, port=cfg.port, log_level="warning")
+        finally:
+            group.shutdown()
+        return 0
     if cfg.dp > 1:
         from .parallel.dp import DpRouter
         entries = [make_entry(name, args.assets, cfg) for _ in range(cfg.dp)]
@@ -191,9 +212,24 @@ def main(argv=None) -> int:
     s.add_argument("--spec-depth", type=int, dest="spec_depth")
     s.add_argument("--pd", action="store_true", help="prefill on one engine, decode on a second one (KV image hand-off)")
     s.add_argument("--dp", type=int)
+    s.add_argument("--ep", type=int, help="expert parallelism over N GPUs (one rank-worker process each, attention data-parallel)")
+    s.add_argument("--tp", type=int, help="tensor parallelism over N GPUs (one rank-worker process each)")
+    s.add_argument("--dp-procs", type=int, dest="dp_procs", help="N data-parallel replicas, each in a process of its own")
     s.add_argument("--trace", action="store_true")
     s.add_argument("--api-key", action="append")
     s.set_defaults(fn=cmd_serve)
+    w = sub.add_parser("rank-worker", help="one rank of a multi-GPU group (started by `serve --ep/--tp/--dp-procs`)")
+    w.add_argument("--assets", required=True)
+    w.add_argument("--rank", type=int, required=True)
+    w.add_argument("--world", type=int, required=True)
+    w.add_argument("--mode", choices=["ep", "tp", "dp"], required=True)
+    w.add_argument("--master-port", type=int, required=True, dest="master_port")
+    w.add_argument("--leader", required=True, help="host:port of the leader's control listener")
+    w.add_argument("--max-slots", type=int, dest="max_slots")
+    w.add_argument("--max-ctx", type=int, dest="max_ctx")
+    w.add_argument("--backend")
+    w.add_argument("--group-timeout", type=float, default=60.0, dest="group_timeout")
+    w.set_defaults(fn=lambda a: __import__("plow_b200.serve.rank_group", fromlist=["worker_main"]).worker_main(a))
     b = sub.add_parser("bench")
     b.add_argument("--assets", required=True)
     b.add_argument("--input-len", type=int, default=128)

@@ -190,11 +190,14 @@ class ModelMux:
         if grp is not None:
             grp.stop()          # releases the other ranks from their next agreement / receive
 
-    def submit(self, prompt: list, params: GenParams, rid: str | None = None) -> Request:
+    def submit(self, prompt: list, params: GenParams, rid: str | None = None, out=None) -> Request:
+        """``out``: where the request's chunks go (anything with ``put``); a fresh queue by default."""
         with self._submit_lock:             # handlers of several HTTP worker threads submit concurrently
             self._n += 1
             n = self._n
         req = Request(rid=rid or f"req-{n}", prompt=list(prompt), params=params)
+        if out is not None:
+            req.out = out
         if params.deadline_ms:
             req.deadline = req.arrived + params.deadline_ms / 1e3
         with self._submit_lock:

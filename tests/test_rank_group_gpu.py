@@ -1,0 +1,100 @@
+"""Multi-GPU serving through rank-worker processes: an expert-parallel MLA-MoE model over 2 GPUs (each worker with
+its own scheduler, lockstep steps) and a tensor-parallel dense model over 2 GPUs (rank 0 schedules, rank 1 replays),
+driven the way `plowrt serve --ep 2` / `--tp 2` drives them, compared with a single-GPU engine on the same checkpoint."""
+import os
+import time
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _collect(req, timeout=300):
+    toks = []
+    while True:
+        ch = req.out.get(timeout=timeout)
+        if ch.kind == "token":
+            toks.append(ch.token_id)
+        elif ch.kind == "done":
+            return toks, ch.finish_reason
+        else:
+            return toks, "error:" + str(ch.error)
+
+
+def _single_gpu_tokens(assets, prompts, n_out):
+    from plow_b200.runtime.gpu_engine import GpuEngine
+    from plow_b200.runtime.scheduler import GenParams, ModelMux
+    from plow_b200.text.tokenizer import ByteTokenizer
+    mux = ModelMux(GpuEngine(assets, max_slots=8, max_ctx=512), ByteTokenizer()).start()
+    out = [_collect(mux.submit(p, GenParams(max_tokens=n_out, ignore_eos=True)))[0] for p in prompts]
+    mux.stop()
+    return out
+
+
+def _agreement(got, want):
+    same = sum(int(a == b) for g, w in zip(got, want) for a, b in zip(g, w))
+    return same / max(1, sum(len(w) for w in want))
+
+
+def test_expert_parallel_serving_over_two_rank_workers(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from plow_b200 import plowc
+    from plow_b200.models import reference
+    from plow_b200.parallel.dp import DpRouter
+    from plow_b200.runtime.scheduler import GenParams
+    from plow_b200.runtime.smoke import small_mla_moe_config
+    from plow_b200.serve.rank_group import RankGroup
+    cfg = small_mla_moe_config()
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=0, dtype=torch.bfloat16)
+    kw = dict(max_rows=256, prefill_buckets=[128, 256], decode_rungs=[8], max_seqs=8)
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "ep2", num_gpus=2, parallel="ep", **kw)
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "one", **kw)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(3, 1024, (n,), generator=g).tolist() for n in (40, 75, 18, 130, 9, 60)]
+    group = RankGroup(tmp_path / "ep2", 2, "ep", worker_args=["--max-slots", "8", "--max-ctx", "512"], env={"PYTHONPATH": ROOT},
+                      startup_timeout_s=300)
+    try:
+        router = DpRouter(group.muxes)
+        reqs = [router.route(None, p).submit(p, GenParams(max_tokens=8, ignore_eos=True)) for p in prompts]
+        outs = [_collect(r) for r in reqs]
+        assert all(fin == "length" and len(t) == 8 for t, fin in outs), outs
+        assert {r.rid.split("-")[0] for r in reqs} == {"r0", "r1"}          # both ranks served requests
+    finally:
+        group.shutdown()
+    want = _single_gpu_tokens(tmp_path / "one", prompts, 8)
+    assert _agreement([t for t, _ in outs], want) >= 0.9
+
+
+def test_tensor_parallel_serving_leader_and_follower(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from plow_b200 import plowc
+    from plow_b200.models import reference
+    from plow_b200.runtime.scheduler import GenParams
+    from plow_b200.serve.rank_group import RankGroup
+    cfg = dict(model_type="llama", hidden_size=512, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+               num_hidden_layers=2, intermediate_size=1024, rms_norm_eps=1e-5, rope_theta=10000.0, vocab_size=1024,
+               tie_word_embeddings=False, max_position_embeddings=2048, eos_token_id=2, plow_kv_dtype="bf16")
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=0, dtype=torch.bfloat16)
+    kw = dict(max_rows=256, prefill_buckets=[128, 256], decode_rungs=[4], max_seqs=4)
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "tp2", num_gpus=2, parallel="tp", **kw)
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "one", **kw)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(3, 1024, (n,), generator=g).tolist() for n in (33, 70, 12)]
+    group = RankGroup(tmp_path / "tp2", 2, "tp", worker_args=["--max-slots", "4", "--max-ctx", "512"], env={"PYTHONPATH": ROOT},
+                      startup_timeout_s=300)
+    try:
+        assert len(group.muxes) == 1
+        outs = [_collect(group.muxes[0].submit(p, GenParams(max_tokens=8, ignore_eos=True))) for p in prompts]
+        assert all(fin == "length" and len(t) == 8 for t, fin in outs), outs
+    finally:
+        group.shutdown()
+    t0 = time.monotonic()
+    while any(p.poll() is None for p in group.procs) and time.monotonic() - t0 < 30:
+        time.sleep(0.2)
+    assert all(p.poll() is not None for p in group.procs)       # the follower left with the leader
+    want = _single_gpu_tokens(tmp_path / "one", prompts, 8)
+    assert _agreement([t for t, _ in outs], want) >= 0.9
