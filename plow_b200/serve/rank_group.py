@@ -73,7 +73,7 @@ class _QsizeOnly:
         self._mux = mux
 
     def qsize(self):
-        return self._mux.stats.get("queued", 0)
+        return 0              # queued requests are part of RemoteMux.live (everything in flight on the worker)
 
 
 class RemoteMux:
@@ -96,11 +96,12 @@ class RemoteMux:
     # -- what serve/app.py and the data-parallel router use
     @property
     def live(self):
-        return range(self.stats.get("live", 0))
+        # requests this leader has in flight on the worker: exact and current, unlike the periodic stats message
+        return range(len(self._reqs))
 
     @property
     def waiting(self):
-        return range(self.stats.get("waiting", 0))
+        return range(0)
 
     def submit(self, prompt, params: GenParams, rid: str | None = None) -> Request:
         with self._lock:

@@ -56,11 +56,11 @@ def test_worker_exit_fails_pending_requests_and_marks_group_dead(tiny_assets):
     from plow_b200.runtime.engine import EngineHealth
     from plow_b200.runtime.scheduler import GenParams
     from plow_b200.serve.rank_group import RankGroup
-    group = RankGroup(tiny_assets / "assets", 2, "dp", worker_args=["--backend", "cpu", "--max-slots", "2", "--max-ctx", "256"],
+    group = RankGroup(tiny_assets / "assets", 2, "dp", worker_args=["--backend", "cpu", "--max-slots", "2", "--max-ctx", "4096"],
                       env={"PYTHONPATH": ROOT}, startup_timeout_s=180)
     try:
         req = group.muxes[1].submit([3, 4, 5], GenParams(max_tokens=100000, ignore_eos=True))
-        time.sleep(0.5)
+        assert req.out.get(timeout=60).kind == "token"   # the request is running (thousands of tokens to go)
         group.procs[1].terminate()                       # the exact child this test started; it leaves between steps of a CPU engine
         toks, fin = _collect(req, timeout=60)
         assert fin.startswith("error")
