@@ -44,16 +44,24 @@ struct GqaArgs {
   int* status;
   int rows, nq, nkv, group, max_pages, max_splits, window;
   float scale_log2e;
+  // materialised multi-head latent attention: the last `kr_slabs` key slabs come from a separate tensor shared by
+  // all heads (the rotary part), and the value tile sits `v_x0` columns into the key tensor's head block
+  int kr_slabs, v_x0;
 };
 
-template <int HD> struct GqaCfg {
-  static constexpr int kSlabs = HD / 64;                 // 64-column (128-byte) slabs per row
-  static constexpr int kQBytes = kSlabs * 128 * 128;
-  static constexpr int kKBytes = kSlabs * 64 * 128;      // one K (or V) tile
-  static constexpr int kStageBytes = 2 * kKBytes;
-  static constexpr int kStages = HD == 128 ? 5 : 2;
+// HDQ = width of a query / key row, HDV = width of a value row.  They differ for multi-head latent attention in its
+// materialised form (192 = 128 no-position + 64 rotary dims against 128 value dims).
+template <int HDQ, int HDV> struct GqaCfg {
+  static constexpr int kSlabsQ = HDQ / 64;               // 64-column (128-byte) slabs per query / key row
+  static constexpr int kSlabsV = HDV / 64;
+  static constexpr int kQBytes = kSlabsQ * 128 * 128;
+  static constexpr int kKBytes = kSlabsQ * 64 * 128;     // one K tile
+  static constexpr int kVBytes = kSlabsV * 64 * 128;     // one V tile
+  static constexpr int kStageBytes = kKBytes + kVBytes;
+  static constexpr int kStages = (200 * 1024 - kQBytes) / kStageBytes > 5 ? 5 : (200 * 1024 - kQBytes) / kStageBytes;
   static constexpr int kSmem = 1024 + kQBytes + kStages * kStageBytes + 1024;
-  static constexpr int kTmemCols = HD == 128 ? 256 : 512; // S: 2 x 64, O: HD
+  static constexpr int kTmemCols = HDV <= 128 ? 256 : 512; // S: 2 x 64, O: HDV
+  static_assert(kStages >= 2, "K/V stages do not fit");
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -86,13 +94,14 @@ __global__ void gqa_build_items(const int* seq, const int* pos, int rows, int tq
   }
 }
 
-template <int HD>
+template <int HDQ, int HDV>
 __global__ void __launch_bounds__(kGqaThreads, 1)
 gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v) {
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kr) {
   plow::pdl_launch_dependents();
   plow::pdl_wait();
-  using Cfg = GqaCfg<HD>;
+  using Cfg = GqaCfg<HDQ, HDV>;
+  constexpr int HD = HDV;      // width of the accumulator rows
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* q_smem = smem;
@@ -124,7 +133,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
     *abort_flag = 0;
     *never_flag = 0;
     fence_mbar_init();
-    tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_kr);
   }
   if (warp == 1) { tmem_alloc(tmem_holder, Cfg::kTmemCols); tmem_relinquish(); }
   tc_fence_before();
@@ -144,7 +153,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
         const GqaItem w = a.items[it];
         if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagGqa); break; }
         mbar_expect_tx(q_full, Cfg::kQBytes);
-        for (int c = 0; c < Cfg::kSlabs; ++c) tma_load_3d(q_smem + c * 16384, &tm_q, c * 64, w.kvh * a.group, w.r0, q_full);
+        for (int c = 0; c < Cfg::kSlabsQ; ++c) tma_load_3d(q_smem + c * 16384, &tm_q, c * 64, w.kvh * a.group, w.r0, q_full);
         const int* pt = a.page_table + static_cast<size_t>(w.slot) * a.max_pages;
         int page_next = pt[w.tile0];
         for (int i = 0; i < w.ntiles; ++i, ++kv_it) {
@@ -156,10 +165,12 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
           }
           uint8_t* st = kv_smem + s * Cfg::kStageBytes;
           mbar_expect_tx(&kv_full[s], Cfg::kStageBytes);
-          for (int c = 0; c < Cfg::kSlabs; ++c) {
-            tma_load_3d(st + c * 8192, &tm_k, c * 64, w.kvh, page * kGqaPage, &kv_full[s]);
-            tma_load_3d(st + Cfg::kKBytes + c * 8192, &tm_v, c * 64, w.kvh, page * kGqaPage, &kv_full[s]);
+          for (int c = 0; c < Cfg::kSlabsQ; ++c) {
+            if (c < Cfg::kSlabsQ - a.kr_slabs) tma_load_3d(st + c * 8192, &tm_k, c * 64, w.kvh, page * kGqaPage, &kv_full[s]);
+            else tma_load_3d(st + c * 8192, &tm_kr, (c - (Cfg::kSlabsQ - a.kr_slabs)) * 64, 0, page * kGqaPage, &kv_full[s]);
           }
+          for (int c = 0; c < Cfg::kSlabsV; ++c)
+            tma_load_3d(st + Cfg::kKBytes + c * 8192, &tm_v, a.v_x0 + c * 64, w.kvh, page * kGqaPage, &kv_full[s]);
         }
       }
     }
@@ -179,7 +190,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
         const uint32_t d = tm_s + (ti & 1) * 64;
         const uint32_t qa = smem_u32(q_smem), ka = smem_u32(kv_smem + s * Cfg::kStageBytes);
 #pragma unroll
-        for (int c = 0; c < Cfg::kSlabs; ++c) {
+        for (int c = 0; c < Cfg::kSlabsQ; ++c) {
           const uint64_t qd = umma_desc_k128(qa + c * 16384), kd = umma_desc_k128(ka + c * 8192);
 #pragma unroll
           for (int k = 0; k < 4; ++k) tc_mma_f16(d, qd + 2 * k, kd + 2 * k, idesc_qk, (c | k) != 0);
@@ -451,7 +462,7 @@ __global__ void rope_kv_kernel(__nv_bfloat16* q_out, const __nv_bfloat16* qkv, i
 
 template <int HD>
 int launch_gqa(const GqaArgs& a, const void* q, const void* kc, const void* vc, int64_t n_pages, int grid, cudaStream_t stream) {
-  using Cfg = GqaCfg<HD>;
+  using Cfg = GqaCfg<HD, HD>;
   CUtensorMap tq, tk, tv;
   int r = make_tmap_3d(&tq, q, 2, HD, a.nq, a.rows, HD * 2, static_cast<uint64_t>(a.nq) * HD * 2, a.group, 128 / a.group, 128);
   if (r) return 1100 + r;
@@ -460,8 +471,25 @@ int launch_gqa(const GqaArgs& a, const void* q, const void* kc, const void* vc, 
   r = make_tmap_3d(&tv, vc, 2, HD, a.nkv, static_cast<uint64_t>(n_pages) * kGqaPage, HD * 2, static_cast<uint64_t>(a.nkv) * HD * 2, 1, kGqaPage, 128);
   if (r) return 1300 + r;
   static DeviceOnce attr;
-  if (ensure_smem(attr, gqa_attn_kernel<HD>, Cfg::kSmem) != cudaSuccess) return 3000;
-  plow::launch_serial(gqa_attn_kernel<HD>, dim3(grid), dim3(kGqaThreads), Cfg::kSmem, stream, a, tq, tk, tv);
+  if (ensure_smem(attr, gqa_attn_kernel<HD, HD>, Cfg::kSmem) != cudaSuccess) return 3000;
+  plow::launch_serial(gqa_attn_kernel<HD, HD>, dim3(grid), dim3(kGqaThreads), Cfg::kSmem, stream, a, tq, tk, tv, tk);
+  return 0;
+}
+
+// Materialised multi-head latent attention (prefill): q [rows][heads][192]; kvb [tokens][heads][256] = per head
+// [128 no-position key dims | 128 value dims]; krope [tokens][64] shared by all heads.
+int launch_mla_prefill(const GqaArgs& a, const void* q, const void* kvb, const void* krope, int64_t n_tokens, int grid, cudaStream_t stream) {
+  using Cfg = GqaCfg<192, 128>;
+  CUtensorMap tq, tk, tkr;
+  int r = make_tmap_3d(&tq, q, 2, 192, a.nq, a.rows, 192 * 2, static_cast<uint64_t>(a.nq) * 192 * 2, 1, 128, 128);
+  if (r) return 1100 + r;
+  r = make_tmap_3d(&tk, kvb, 2, 256, a.nkv, static_cast<uint64_t>(n_tokens), 256 * 2, static_cast<uint64_t>(a.nkv) * 256 * 2, 1, kGqaPage, 128);
+  if (r) return 1200 + r;
+  r = make_tmap_3d(&tkr, krope, 2, 64, 1, static_cast<uint64_t>(n_tokens), 64 * 2, 64 * 2, 1, kGqaPage, 128);
+  if (r) return 1300 + r;
+  static DeviceOnce attr;
+  if (ensure_smem(attr, gqa_attn_kernel<192, 128>, Cfg::kSmem) != cudaSuccess) return 3000;
+  plow::launch_serial(gqa_attn_kernel<192, 128>, dim3(grid), dim3(kGqaThreads), Cfg::kSmem, stream, a, tq, tk, tk, tkr);
   return 0;
 }
 
@@ -491,12 +519,43 @@ int plow_gqa_attention(const void* q, const void* kc, const void* vc, int64_t n_
   a.opart = opart; a.lse = lse; a.out = static_cast<__nv_bfloat16*>(out); a.status = status;
   a.rows = rows; a.nq = nq; a.nkv = nkv; a.group = group; a.max_pages = max_pages; a.max_splits = max_splits; a.window = window;
   a.scale_log2e = softmax_scale * 1.4426950408889634f;
+  a.kr_slabs = 0; a.v_x0 = 0;
   int grid = sm_count();
   if (item_cap < grid) grid = item_cap;
   int r = hd == 128 ? launch_gqa<128>(a, q, kc, vc, n_pages, grid, stream) : launch_gqa<256>(a, q, kc, vc, n_pages, grid, stream);
   if (r) return r;
   if (max_splits > 1)
     plow::launch_serial(gqa_merge_kernel, dim3(rows, nq), dim3(128), 0, stream, opart, lse, row_ns, nq, max_splits, hd, static_cast<__nv_bfloat16*>(out));
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
+}
+
+// Multi-head latent attention over materialised keys / values (prefill).  q bf16 [rows][heads][192] (rotary part
+// already rotated); kvb bf16 [n_tokens][heads][256]; krope bf16 [n_tokens][64]; vpt int32 [n_slots][max_pages]: tile i
+// of slot s covers tokens [64 vpt[s][i], 64 vpt[s][i] + 64) of kvb / krope; seq / pos int32 [rows] (pos < 0: the row is
+// not attended here); out bf16 [rows][heads*128].  Scratch as for plow_gqa_attention (opart / lse with hd = 128).
+int plow_mla_prefill_attention(const void* q, const void* kvb, const void* krope, int64_t n_tokens, const int* vpt, int max_pages,
+                               const int* seq, const int* pos, int rows, int heads, int tiles_per_split, int max_splits,
+                               void* items, int item_cap, int* n_items, int* row_ns, float* opart, float* lse, void* out,
+                               float softmax_scale, int* status, void* stream_) {
+  using namespace plow;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (rows <= 0 || heads <= 0 || max_splits <= 0 || tiles_per_split <= 0 || n_tokens <= 0) return -1;
+  cudaMemsetAsync(n_items, 0, sizeof(int), stream);
+  plow::launch_serial(gqa_build_items, dim3((rows + 255) / 256), dim3(256), 0, stream, seq, pos, rows, 128, heads, 0, tiles_per_split,
+                      max_splits, static_cast<GqaItem*>(items), n_items, row_ns, item_cap, status);
+  GqaArgs a;
+  a.page_table = vpt; a.pos = pos; a.items = static_cast<const GqaItem*>(items); a.n_items = n_items;
+  a.opart = opart; a.lse = lse; a.out = static_cast<__nv_bfloat16*>(out); a.status = status;
+  a.rows = rows; a.nq = heads; a.nkv = heads; a.group = 1; a.max_pages = max_pages; a.max_splits = max_splits; a.window = 0;
+  a.scale_log2e = softmax_scale * 1.4426950408889634f;
+  a.kr_slabs = 1; a.v_x0 = 128;
+  int grid = sm_count();
+  if (item_cap < grid) grid = item_cap;
+  int r = launch_mla_prefill(a, q, kvb, krope, n_tokens, grid, stream);
+  if (r) return r;
+  if (max_splits > 1)
+    plow::launch_serial(gqa_merge_kernel, dim3(rows, heads), dim3(128), 0, stream, opart, lse, row_ns, heads, max_splits, 128, static_cast<__nv_bfloat16*>(out));
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }

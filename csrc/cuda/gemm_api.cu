@@ -52,7 +52,7 @@ extern "C" int plow_gemm(const PlowGemmDesc* d, void* stream) {
   if (d->E > 0 && (d->N % 128)) return -6;
   if (d->dual && (d->N % 128)) return -6;
   if (d->yq && !d->syq) return -7;
-  if (d->yq && !d->swap && d->bn != 128) return -7;
+  if (d->yq && !d->swap && d->bn != 128 && !(d->bn == 256 && !d->dual)) return -7;
   if (d->ar_world > 1 && (!d->swap || d->dual || d->E || d->M > d->bn || d->splits > 1 || d->yq || d->out_f32 || !d->ar_epoch || (d->N % 8) || (d->ldy % 8))) return -8;
   if (d->ar_world > 1 && d->ar_oneshot == 2 && !d->ar_mc) return -8;
   if (d->ar_world > 1 && d->ar_oneshot == 1 &&

@@ -92,6 +92,14 @@ struct GemmCfg {
   static constexpr int kQT = (DUAL && !SWAP) ? 2 : 1;   // BN-row tiles per stage
   static constexpr int kStageBytes = kPT * kStageBytesP + kQT * BN * 128;
   static constexpr int kAccCols = BN * (DUAL ? 2 : 1);
+  // Epilogue warps.  The block-scaled kernels at large M (tokens on the lanes) are bound by the promotion of the
+  // per-K-block partials (one warp per scheduler, a latency chain of TMEM load -> wait -> FMAs kept the tensor pipe 45 %
+  // busy): there two warps share each TMEM lane quarter and split the columns, so each sub-partition has two chains
+  // to interleave and half the work per chain.
+  static constexpr int kEpiWarps = (FP8 && !SWAP) ? 8 : 4;
+  static constexpr int kHalves = kEpiWarps / 4;
+  static constexpr int kCH = BN / kHalves;              // columns of each BN-wide block a warp owns
+  static constexpr int kThreads = 64 + 32 * kEpiWarps;
   // accumulator buffers in TMEM: two for bf16 (tile i+1 runs while tile i drains); for fp8 as many K-block
   // partials as TMEM holds (up to eight), so the MMA warp keeps consuming stages while the promotion warps are
   // away writing a finished tile (measured: the end of a tile takes the four warps 2.5-9 us at decode shapes,
@@ -216,16 +224,22 @@ struct TileSched {
         item += gridDim.x;
       }
     } else {
+      // Expert-major order: the CTAs running at one time work on one or two experts, so an expert's weights are
+      // read from HBM once and its token rows (a few MB) stay in L2 across the weight tiles.  (With the token tile
+      // fastest over all experts, every wave of CTAs re-read the whole activation matrix, which at prefill sizes is
+      // larger than L2.)  Within an expert the token tile is fastest: neighbours share one weight tile.
       const int n_mt = a.tile_prefix[a.E];
       if (item >= n_mt * n_wt) return false;
-      const int mt = item % n_mt, wt = item / n_mt;
-      int lo = 0, hi = a.E;  // largest e with tile_prefix[e] <= mt
+      int lo = 0, hi = a.E;  // largest e with tile_prefix[e] * n_wt <= item
       while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
-        if (a.tile_prefix[mid] <= mt) lo = mid; else hi = mid;
+        if (a.tile_prefix[mid] * n_wt <= item) lo = mid; else hi = mid;
       }
       const int e = lo;
-      t.tok0 = a.grp_off[e] + (mt - a.tile_prefix[e]) * 128;
+      const int st = a.tile_prefix[e + 1] - a.tile_prefix[e];
+      const int local = item - a.tile_prefix[e] * n_wt;
+      const int mt = local % st, wt = local / st;
+      t.tok0 = a.grp_off[e] + mt * 128;
       t.tok_end = a.grp_off[e + 1];
       t.feat0 = wt * BN;
       t.wrow0 = e * nw_per + wt * BN;
@@ -239,13 +253,15 @@ struct TileSched {
 __device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
 template <int BN, bool FP8, bool DUAL, bool SWAP>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__((GemmCfg<BN, DUAL, SWAP, FP8>::kThreads), 1)
 gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
                const __grid_constant__ CUtensorMap tm_w) {
   using Cfg = GemmCfg<BN, DUAL, SWAP, FP8>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kAccCols = Cfg::kAccCols;
   constexpr int kNBuf = Cfg::kNBuf;
+  constexpr int kEpiWarps = Cfg::kEpiWarps;
+  constexpr int kCH = Cfg::kCH;
   constexpr int kKElems = FP8 ? 128 : 64;  // K elements per 128-byte stage row
   constexpr int kUmmaK = FP8 ? 32 : 16;
   constexpr int kUmmaN = SWAP ? BN : (DUAL ? 2 * BN : BN);
@@ -260,7 +276,8 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
   uint64_t* acc_empty = acc_full + kNBuf;                        // [kNBuf]
   uint64_t* drain_bar = acc_empty + kNBuf;                       // [1]
   uint64_t* xchg_bar = drain_bar + 1;                            // [2] epilogue-warp exchange
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(xchg_bar + 2);
+  uint64_t* pair_bar = xchg_bar + 2;                             // [4] the two warps of a lane quarter (8-warp epilogue)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pair_bar + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   volatile int* never_flag = abort_flag + 1;                     // stays 0
   float* red_scratch = reinterpret_cast<float*>(ctrl + 512);     // [2][4][16] quant amax exchange (+ split-K flag)
@@ -274,10 +291,11 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < kNBuf; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < kNBuf; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], kEpiWarps); }
     mbar_init(drain_bar, 1);
-    mbar_init(&xchg_bar[0], 4);
-    mbar_init(&xchg_bar[1], 4);
+    mbar_init(&xchg_bar[0], kEpiWarps);
+    mbar_init(&xchg_bar[1], kEpiWarps);
+    for (int q = 0; q < 4; ++q) mbar_init(&pair_bar[q], 2);
     *abort_flag = 0;
     *never_flag = 0;
     fence_mbar_init();
@@ -434,13 +452,16 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
     }
     const int lq = warp & 3;               // TMEM lane quarter this warp may read
     const int li = lq * 32 + lane;         // lane (row of D) owned by this thread
+    const int half = (warp - 2) >> 2;      // which kCH columns of every BN-wide block this warp owns (0 with four warps)
+    const int hc0 = half * kCH;
     const uint32_t lane_addr = static_cast<uint32_t>(lq * 32) << 16;
     TileSched<BN, DUAL, SWAP> sched(a, KB);
     Tile t;
     uint32_t accit = 0;
     uint32_t xchg_it = 0;
+    uint32_t yq_it = 0;
     bool ok = true;
-    constexpr int kAccRegs = FP8 ? kAccCols : 1;
+    constexpr int kAccRegs = FP8 ? kAccCols / Cfg::kHalves : 1;
     float acc[kAccRegs];
     const __nv_bfloat16* resid = reinterpret_cast<const __nv_bfloat16*>(a.residual);
     // The arrival gate is polled by the producer thread only: the epilogue warps touch the peers' rows
@@ -453,8 +474,8 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
       if constexpr (FP8) {
 #pragma unroll
         for (int i = 0; i < kAccRegs; ++i) acc[i] = 0.f;
-        const int wblk_g = t.wrow0 >> 7;
-        const int wblk_u = (t.wrow0 + a.N) >> 7;
+        const int wblk_g = (t.wrow0 + hc0) >> 7;            // a 256-wide tile spans two 128-row scale blocks
+        const int wblk_u = (t.wrow0 + hc0 + a.N) >> 7;
         // Scales are fetched two K blocks ahead so their latency hides behind the wait for
         // the partial.  SWAP: lane l fetches the activation scales of tokens tok0 + l + 32 i; per
         // K block the warp stages the BN combined factors (activation x weight scale) in its own
@@ -495,18 +516,19 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
           }
           tc_fence_after();
           PLOW_TRACE(if (tre) a.trace[accit * 8 + 4] = clock64();)
-          const uint32_t tb = tmem_base + lane_addr + b * kAccCols;
+          const uint32_t tb = tmem_base + lane_addr + b * kAccCols + hc0;
+          // acc index -> TMEM column: the warp's kCH columns of the gate block, then (dual) of the up block
 #pragma unroll
-          for (int c = 0; c < kAccCols; c += 64) {
+          for (int c = 0; c < kAccRegs; c += 64) {
             // up to 64 columns per batch: all loads in flight, one wait
             uint32_t v[64];
 #pragma unroll
             for (int q = 0; q < 4; ++q)
-              if (c + q * 16 < kAccCols) tmem_ld16(tb + c + q * 16, v + q * 16);
+              if (c + q * 16 < kAccRegs) tmem_ld16(tb + ((c + q * 16) / kCH) * BN + (c + q * 16) % kCH, v + q * 16);
             tmem_ld_wait();
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              if (c + q * 16 < kAccCols) {
+              if (c + q * 16 < kAccRegs) {
 #pragma unroll
                 for (int j = 0; j < 16; j += 4) {
                   const int col = c + q * 16 + j;
@@ -514,7 +536,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
                   if constexpr (SWAP) {
                     f = *reinterpret_cast<const float4*>(fw + (col < BN ? col : 128 + col - BN));
                   } else {
-                    const float fs = s0.sa[0] * ((DUAL && col >= BN) ? s0.wu : s0.wg);
+                    const float fs = s0.sa[0] * ((DUAL && col >= kCH) ? s0.wu : s0.wg);
                     f = make_float4(fs, fs, fs, fs);
                   }
                   acc[col] = fmaf(__uint_as_float(v[q * 16 + j]), f.x, acc[col]);
@@ -692,7 +714,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         } else if constexpr (FP8) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            if constexpr (DUAL) r[j] = silu_f(acc[c + j]) * acc[BN + c + j];
+            if constexpr (DUAL) r[j] = silu_f(acc[c + j]) * acc[kCH + c + j];
             else r[j] = acc[c + j];
           }
         } else {
@@ -912,14 +934,14 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         }
        }
       } else {
-        // thread = token, columns = features (contiguous in memory)
+        // thread = token, columns = features (contiguous in memory); cl counts the warp's own columns
         const bool tok_ok = tok_i < t.tok_end;
         float amax = 0.f;
 #pragma unroll
-        for (int c = 0; c < BN; c += 16) {
+        for (int cl = 0; cl < kCH; cl += 16) {
           float r[16];
-          load16(c, r);
-          const int f0 = t.feat0 + c;
+          load16(cl, r);
+          const int f0 = t.feat0 + hc0 + cl;
           const size_t o = static_cast<size_t>(tok_i) * a.ldy + f0;
           if (tok_ok && resid) {
 #pragma unroll
@@ -955,16 +977,29 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
             }
           }
         }
-        if constexpr (BN == 128) {
+        if constexpr (kCH * Cfg::kHalves == 128 || kCH == 128) {
           if (a.yq) {
-            // the thread owns the whole 1x128 group: second pass re-reads the accumulators
+            // the 1x128 group of a token is held by the thread (or by the two threads that share its lane): second
+            // pass re-reads the accumulators
+            if constexpr (kCH == 64) {
+              // exchange the half maxima with the warp that owns the other columns of this lane quarter
+              float* ex = fac_smem + (yq_it & 1) * 256;
+              ex[half * 128 + li] = amax;
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&pair_bar[lq]);
+              if (!mbar_wait(&pair_bar[lq], yq_it & 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMEM_WAIT | kTagGemm); ok = false; break;
+              }
+              amax = fmaxf(amax, ex[(half ^ 1) * 128 + li]);
+              ++yq_it;
+            }
             const float sc = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
             const float inv = 1.0f / sc;
 #pragma unroll
-            for (int c = 0; c < BN; c += 16) {
+            for (int cl = 0; cl < kCH; cl += 16) {
               float r[16];
-              load16(c, r);
-              const int f0 = t.feat0 + c;
+              load16(cl, r);
+              const int f0 = t.feat0 + hc0 + cl;
               if (tok_ok && resid) {
                 const size_t o = static_cast<size_t>(tok_i) * a.ldy + f0;
 #pragma unroll
@@ -984,7 +1019,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
                     make_uint4(pk[0], pk[1], pk[2], pk[3]);
               }
             }
-            if (tok_ok) a.syq[static_cast<size_t>(t.feat0 >> 7) * a.ld_syq + tok_i] = sc;
+            if (tok_ok && (kCH == 128 || half == 0)) a.syq[static_cast<size_t>((t.feat0 + (kCH == 128 ? hc0 : 0)) >> 7) * a.ld_syq + tok_i] = sc;
           }
         }
       }
@@ -1171,7 +1206,7 @@ int launch_gemm_tc(const GemmArgs& a, int ldx_elems, int ldw_elems, int64_t w_ro
     if (tiles < grid) grid = static_cast<int>(tiles);
   }
   if (grid < 1) grid = 1;
-  cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, a, tm_x, tm_w);
+  cudaError_t e = launch_pdl(kern, dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, a, tm_x, tm_w);
   if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }

@@ -17,6 +17,8 @@ int gemm_dispatch_fp8(const PlowGemmDesc& d, cudaStream_t s) {
   PLOW_CASE(64, true, true)
   PLOW_CASE(128, false, false)
   PLOW_CASE(64, true, false)
+  PLOW_CASE(256, false, false)
+  PLOW_CASE(128, true, false)
 #undef PLOW_CASE
   return -2;
 }

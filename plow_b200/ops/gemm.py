@@ -32,6 +32,7 @@ def _pick_bn_swap(rows: int, fp8: bool, dual: bool) -> int:
 import os as _os
 
 _STREAM_DEFAULT = _os.environ.get("PLOW_GEMM_STREAM", "1") != "0"
+_WIDE_DEFAULT = _os.environ.get("PLOW_GEMM_WIDE", "1") != "0"
 _SPLITK_WS = {}
 SM_COUNT = 148          # B200; used only where no device is present (the device's own count is read otherwise)
 
@@ -130,6 +131,12 @@ def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=N
         cfg = _tuned(M, N, K, fp8, dual)
         if cfg and cfg.get("swap", True) and cfg["bn"] >= M:
             bn, splits = cfg["bn"], cfg.get("splits", 1)
+    if fp8 and not swap and dual and _WIDE_DEFAULT and N % 128 == 0 and (bn is None or bn == 64):
+        # large-M SwiGLU tiles: gate | up of 128 columns each (one N = 256 MMA, 256 TMEM columns per partial).  Measured
+        # on the 2048-token prefill shapes: the grouped up-projection runs 1.2x faster than with 64 + 64 columns (fewer
+        # operand bytes per FLOP through L2); the plain projections gain nothing from 256-wide tiles (fewer, longer tiles
+        # leave the last wave of CTAs emptier) and keep 128.
+        bn = 128
     if bn is None:
         if swap:
             bn = _pick_bn_swap(rows_hint if rows_hint is not None else M, fp8, dual)
@@ -188,7 +195,11 @@ def gemm(x, w, *, sx=None, sw=None, out=None, residual=None, dual=False, n_out=N
         d.wait_deadline_ms = ar.get("deadline_ms", 2000)
         d.ar_oneshot, d.ar_half_bytes = int(ar.get("oneshot", 0)), int(ar.get("half_bytes", 0))
         d.ar_mc, d.ar_tdone_ofs = ar.get("mc_ptr") or None, int(ar.get("tdone_ofs", 0))
-    rc = lib.plow_gemm(C.byref(d), native.stream_ptr())
+    if native.PROFILE is not None:
+        label = f"gemm M{M} N{N} K{K} E{E} {'fp8' if fp8 else 'bf16'}{' dual' if dual else ''}{' swap' if swap else ''} bn{bn}"
+        rc = native.profiled(label, lambda: lib.plow_gemm(C.byref(d), native.stream_ptr()))
+    else:
+        rc = lib.plow_gemm(C.byref(d), native.stream_ptr())
     if rc != 0:
         raise native.NativeLibraryError(f"plow_gemm failed with code {rc} (bn={bn} swap={swap} dual={dual} fp8={fp8})")
     return (yq, syq) if quant_out else y

@@ -91,3 +91,59 @@ def decode(q8, sq, kv8, kv_scale, kv_smax, page_table, slot_of, kvlen, ws: Decod
                 ws.tiles_per_split, ws.max_splits, ws.items, ws.n_items, ws.opart, ws.lse, out, float(softmax_scale),
                 int(build_items), ws.claims, int(claim_slot), native.status_word(q8.device))
     return out
+
+
+# ---- materialised prefill ---------------------------------------------------------------------------------------
+class PrefillWorkspace:
+    """Scratch of the materialised prefill: the gathered latent of the step's prefilling requests, the K / V rebuilt
+    from it for ONE layer (reused by every layer), the tile table and the attention work list.
+
+    ``budget`` bounds the cached tokens (summed over the requests, each rounded up to 64) a step may rebuild; K / V
+    take 64 KiB per token (128 heads x 256 dims bf16).
+    """
+
+    def __init__(self, budget, max_rows, n_slots, max_pages, heads=128, latent=512, rope=64, fp8_weight=True, device="cuda"):
+        self.budget, self.max_rows, self.heads, self.latent, self.rope = budget, max_rows, heads, latent, rope
+        self.fp8 = fp8_weight
+        if fp8_weight:
+            self.lat8 = torch.zeros(budget, latent + rope, dtype=FP8, device=device)
+            self.lat_scale = torch.zeros(latent // 128, budget, dtype=torch.float32, device=device)
+            self.lat16 = None
+        else:
+            self.lat8 = self.lat_scale = None
+            self.lat16 = torch.zeros(budget, latent, dtype=BF16, device=device)
+        self.krope = torch.zeros(budget, rope, dtype=BF16, device=device)
+        self.kvb = torch.empty(budget, heads * 256, dtype=BF16, device=device)
+        self.vpt = torch.zeros(n_slots, max_pages, dtype=torch.int32, device=device)
+        chunks = (max_rows + 127) // 128 + n_slots
+        # one (128-row chunk, head) item per CTA visit: with 128 heads even a single chunk fills the GPU, so the keys of
+        # a chunk are never split
+        self.tiles_per_split = 1 << 20
+        self.max_splits = 1
+        self.item_cap = chunks * heads * self.max_splits
+        self.items = torch.empty(self.item_cap * 8, dtype=torch.int32, device=device)
+        self.n_items = torch.zeros(1, dtype=torch.int32, device=device)
+        self.row_ns = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self.opart = self.lse = None
+
+
+def latent_gather(ws: PrefillWorkspace, cache, scale, page_table, spans, n_spans, max_tiles):
+    """cache e4m3 [pages, 64, latent+rope]; scale f32 [pages, 64]; spans int32 [>= n_spans, 4] (device)."""
+    native.call("plow_mla_latent_gather", ws.lat8, ws.lat_scale, ws.budget, ws.lat16, ws.krope, ws.vpt, cache, scale, page_table,
+                page_table.shape[1], spans, int(n_spans), int(max_tiles), ws.latent, ws.rope)
+
+
+def q_rope(q, rope_tab, pos, heads, nope, rope, pair_mode=1):
+    """Rotate the rotary part of every head of q [T, heads*(nope+rope)] in place (rows with pos < 0 untouched)."""
+    native.call("plow_mla_q_rope", q, q.stride(0), rope_tab, pos, q.shape[0], heads, nope, rope, pair_mode)
+
+
+def prefill_attention(q, ws: PrefillWorkspace, n_tokens, seq, pos, softmax_scale, out):
+    """q [T, heads*192] bf16 (rotated); K / V from ws.kvb / ws.krope rows [0, n_tokens); out [T, heads*128] bf16.  Rows
+    with pos < 0 are skipped (their rows of ``out`` are not written)."""
+    T = q.shape[0]
+    assert T <= ws.max_rows and n_tokens <= ws.budget
+    native.call("plow_mla_prefill_attention", q, ws.kvb, ws.krope, int(n_tokens), ws.vpt, ws.vpt.shape[1], seq, pos, T, ws.heads,
+                ws.tiles_per_split, ws.max_splits, ws.items, ws.item_cap, ws.n_items, ws.row_ns, ws.opart, ws.lse, out,
+                float(softmax_scale), native.status_word(q.device))
+    return out

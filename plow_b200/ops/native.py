@@ -145,6 +145,9 @@ _SIGS = {
     "plow_sigmoid_gate": "ppplp",
     "plow_gqa_attention": "ppplpipp" "iiiiiii" "pi" "ppppp" "fpp",
     "plow_rope_kv": "ppi" "pppppppp" "i" "iiiiiii" "fpp",
+    "plow_mla_prefill_attention": "ppplpipp" "iiii" "pi" "ppppp" "fpp",
+    "plow_mla_latent_gather": "ppipppppp" "ipiiiip",
+    "plow_mla_q_rope": "pippiiiiip",
 }
 _CT = {"p": C.c_void_p, "i": C.c_int32, "l": C.c_int64, "f": C.c_float, "L": C.c_uint64, "I": C.c_uint32}
 
@@ -158,7 +161,32 @@ def _arg(v):
 
 
 LAUNCHES = {"n": 0}                       # kernels launched through this module (bench bookkeeping)
-_KERNELS_PER_CALL = {"plow_gqa_attention": 2, "plow_dsa_select": 3}
+PROFILE: list | None = None               # when a list: (label, start event, end event) per launcher call (diagnostic)
+
+
+def profiled(label: str, fn):
+    """Run ``fn()`` between two CUDA events recorded on the current stream and log them under ``label``."""
+    import torch
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    r = fn()
+    b.record()
+    PROFILE.append((label, a, b))
+    return r
+
+
+def profile_summary() -> list:
+    """[(label, calls, total ms)] of the calls logged since PROFILE was set, longest first; clears the log."""
+    import torch
+    torch.cuda.synchronize()
+    agg: dict = {}
+    for label, a, b in PROFILE:
+        e = agg.setdefault(label, [0, 0.0])
+        e[0] += 1
+        e[1] += a.elapsed_time(b)
+    PROFILE.clear()
+    return sorted(((k, c, t) for k, (c, t) in agg.items()), key=lambda x: -x[2])
+_KERNELS_PER_CALL = {"plow_gqa_attention": 2, "plow_dsa_select": 3, "plow_mla_prefill_attention": 3}
 
 
 def call(name: str, *args) -> None:
@@ -169,6 +197,9 @@ def call(name: str, *args) -> None:
     if fn.argtypes is None:
         fn.argtypes = [_CT[c] for c in _SIGS[name]]
         fn.restype = C.c_int
-    rc = fn(*[_arg(a) for a in args], stream_ptr())
+    if PROFILE is not None:
+        rc = profiled(name, lambda: fn(*[_arg(a) for a in args], stream_ptr()))
+    else:
+        rc = fn(*[_arg(a) for a in args], stream_ptr())
     if rc != 0:
         raise NativeLibraryError(f"{name} failed with code {rc}")

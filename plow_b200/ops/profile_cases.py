@@ -88,6 +88,61 @@ def case_gemm_moe(iters):
     return dict(us=us, flops=2.0 * E * rows * 2 * I * H, bytes=1.0 * E * 2 * I * H)
 
 
+def case_gemm_fp8_dual_prefill(iters):
+    """Dense SwiGLU up-projection of a 2048-row prefill chunk (7168 -> 2 x 18432), non-swap tiles."""
+    from . import gemm
+    M, N, K = 2048, 18432, 7168
+    x = torch.randn(M, K, device="cuda").to(FP8)
+    w = torch.randn(2 * N, K, device="cuda").to(FP8)
+    sx = torch.rand(K // 128, M, device="cuda")
+    sw = torch.rand(2 * N // 128, K // 128, device="cuda")
+    us = _time(lambda: gemm.gemm(x, w, sx=sx, sw=sw, dual=True, n_out=N, swap=False), iters)
+    return dict(us=us, flops=2.0 * M * 2 * N * K, bytes=1.0 * (M * K + 2 * N * K) + 2.0 * M * N)
+
+
+def case_gemm_moe_prefill(iters):
+    """Grouped SwiGLU GEMM of a 2048-token prefill chunk: 32 experts + the shared expert as a 33rd group, top-8 routing
+    drawn uniformly (rows per expert vary around 512), non-swap 128-row token tiles."""
+    from . import gemm
+    E, H, I, T, k = 33, 7168, 2048, 2048, 8
+    g = torch.Generator().manual_seed(0)
+    counts = torch.bincount(torch.randint(0, 32, (T * k,), generator=g), minlength=32).tolist() + [T]
+    off = [0]
+    tiles = [0]
+    for c in counts:
+        off.append(off[-1] + c)
+        tiles.append(tiles[-1] + (c + 127) // 128)
+    R = off[-1]
+    w = torch.randn(E * 2 * I, H, device="cuda").to(FP8)
+    sw = torch.rand(E * 2 * I // 128, H // 128, device="cuda")
+    x = torch.randn(R, H, device="cuda").to(FP8)
+    sx = torch.rand(H // 128, R, device="cuda")
+    grp_off = torch.tensor(off, dtype=torch.int32).cuda()
+    tile_prefix = torch.tensor(tiles, dtype=torch.int32).cuda()
+    us = _time(lambda: gemm.gemm(x, w, sx=sx, sw=sw, dual=True, n_out=I, swap=False, rows_hint=512,
+                                 grp_off=grp_off, tile_prefix=tile_prefix, n_experts=E), iters)
+    return dict(us=us, flops=2.0 * R * 2 * I * H, bytes=1.0 * E * 2 * I * H + 1.0 * R * H + 2.0 * R * I)
+
+
+def case_mla_prefill(iters):
+    """Materialised MLA prefill attention: one request, 2048 new rows after a 2048-token cached prefix, 128 heads,
+    192-wide keys / 128-wide values (K / V already rebuilt)."""
+    import math
+    from . import mla
+    T, L, H = 2048, 4096, 128
+    ws = mla.PrefillWorkspace(L, T, 2, L // 64, device="cuda")
+    ws.kvb.copy_(torch.randn(L, H * 256, device="cuda") * 0.5)
+    ws.krope.copy_(torch.randn(L, 64, device="cuda") * 0.5)
+    ws.vpt[1] = torch.arange(L // 64, dtype=torch.int32, device="cuda")
+    q = (torch.randn(T, H * 192, device="cuda") * 0.5).bfloat16()
+    seq = torch.ones(T, dtype=torch.int32, device="cuda")
+    pos = torch.arange(L - T, L, dtype=torch.int32, device="cuda")
+    out = torch.empty(T, H * 128, dtype=torch.bfloat16, device="cuda")
+    us = _time(lambda: mla.prefill_attention(q, ws, L, seq, pos, 1.0 / math.sqrt(192), out), iters)
+    pairs = T * (L - T) + T * (T + 1) / 2                   # attended (query, key) pairs per head
+    return dict(us=us, flops=2.0 * H * pairs * (192 + 128), bytes=2.0 * (T * H * 192 + L * H * 256 + T * H * 128))
+
+
 def case_mla_decode(iters):
     from . import mla
     T, ctx = 74, 4096

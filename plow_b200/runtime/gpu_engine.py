@@ -173,6 +173,8 @@ class GpuEngine(EngineBase):
         self.progs: dict[int, _Prog] = {}
         self.step_ms_last = 0.0
         self.launches_last = 0
+        self.profile_ops = os.environ.get("PLOW_PROFILE_OPS") == "1"     # per-instruction device times of eager steps
+        self.op_times_last: list = []
 
     # ---- static tensors ------------------------------------------------------------------------
     def _load_static(self) -> None:
@@ -237,6 +239,13 @@ class GpuEngine(EngineBase):
         self.kv_smax: dict[int, torch.Tensor] = {}
         self._mla_derived: dict[int, tuple] = {}
         self._mla_ws = None
+        # materialised prefill (K / V rebuilt from the latent once per layer for long runs of new rows)
+        self._mla_pf_ws = None
+        self._mla_plan = None
+        self._mla_plan_rows = 0
+        self._has_mla = any(l.attn.kind == "mla" for l in self.spec.layers)
+        self.h_plan = torch.zeros(2 * max_rows + 4 * n_slots, dtype=I32).pin_memory()
+        self.d_plan = torch.zeros(2 * max_rows + 4 * n_slots, dtype=I32, device=dev)
 
     # ---- program preparation -------------------------------------------------------------------
     def _prepare(self, idx: int) -> _Prog:
@@ -419,6 +428,70 @@ class GpuEngine(EngineBase):
         mla_ops.kv_write(cache, scale, self.kv_smax[layer], kva, ins.i[5], gamma, rope, self.d_in[1], self.d_in[2],
                          self.d_page_table, ins.i[0], ins.i[1], float(ins.f[0]), ins.i[2])
 
+    # A run of at least this many consecutive new rows of one request attends over K / V rebuilt from the latent
+    # (plain multi-head attention: 192-wide keys, 128-wide values) instead of the absorbed form (576 / 512 wide).
+    MLA_PREFILL_MIN_RUN = int(os.environ.get("PLOW_MLA_PREFILL_MIN_RUN", "64"))
+    # cached tokens (summed over the step's prefilling requests) whose K / V one layer may rebuild: 64 KiB per token
+    MLA_PREFILL_BUDGET = int(os.environ.get("PLOW_MLA_PREFILL_BUDGET", "16384"))
+
+    def _plan_mla_prefill(self, batch: TokenBatch, R: int):
+        """Host side of the materialised prefill: which runs of rows take it, where each request's rebuilt K / V start.
+        Returns None when no run qualifies.  Rows outside the chosen runs (decode riders, short runs, padding) stay on
+        the absorbed kernel: they see kvlen 0 there if chosen, and position -1 here if not."""
+        if self.MLA_PREFILL_MIN_RUN <= 0 or batch.rows < self.MLA_PREFILL_MIN_RUN:
+            return None
+        rows, seq, pos = batch.rows, batch.seq, batch.pos
+        brk = np.flatnonzero((seq[1:] != seq[:-1]) | (pos[1:] != pos[:-1] + 1)) + 1
+        starts = np.concatenate(([0], brk))
+        ends = np.concatenate((brk, [rows]))
+        budget = min(self.MLA_PREFILL_BUDGET, ((self.max_ctx + PAGE + 63) // 64) * 64 * 4)
+        pos_mat = np.full(R, -1, np.int32)
+        kv_abs = np.zeros(R, np.int32)
+        kv_abs[:rows] = pos + 1
+        spans, base, seen, max_tiles = [], 0, set(), 0
+        for r0, r1 in zip(starts.tolist(), ends.tolist()):
+            slot, L = int(seq[r0]), int(pos[r1 - 1]) + 1
+            need = -(-L // 64) * 64
+            if r1 - r0 < self.MLA_PREFILL_MIN_RUN or slot in seen or base + need > budget:
+                continue
+            seen.add(slot)
+            spans.append((slot, L, base, 0))
+            pos_mat[r0:r1] = pos[r0:r1]
+            kv_abs[r0:r1] = 0
+            base += need
+            max_tiles = max(max_tiles, need // 64)
+        if not spans:
+            return None
+        n_sp = len(spans)
+        hp = self.h_plan.numpy()
+        hp[:R] = pos_mat
+        hp[R:2 * R] = kv_abs
+        hp[2 * R:2 * R + 4 * n_sp] = np.asarray(spans, np.int32).reshape(-1)
+        n = 2 * R + 4 * n_sp
+        self.d_plan[:n].copy_(self.h_plan[:n], non_blocking=True)
+        return dict(R=R, n_spans=n_sp, total=base, max_tiles=max_tiles, riders=bool((kv_abs[:rows] > 0).any()),
+                    pos=self.d_plan[:R], kvlen=self.d_plan[R:2 * R], spans=self.d_plan[2 * R:2 * R + 4 * n_sp], budget=budget,
+                    gathered=False)
+
+    def _mla_prefill(self, st, ins, plan, ao, q, rope_tab, cache, scale):
+        """Materialised prefill of one layer (see csrc/cuda/mla_prefill.cu)."""
+        heads, kv_lora, nope, qk_rope, pair = ins.i[0], ins.i[1], ins.i[2], ins.i[3], ins.i[5]
+        wh = ins.t[4]
+        fp8_w = wh in self.static_q
+        ws = self._mla_pf_ws
+        if ws is None or ws.budget < plan["budget"] or ws.fp8 != fp8_w:
+            ws = self._mla_pf_ws = mla_ops.PrefillWorkspace(plan["budget"], self.max_rows_all, self.max_slots + 1, self.max_pages_per_seq,
+                                                            heads=heads, latent=kv_lora, rope=qk_rope, fp8_weight=fp8_w, device=self.device)
+        n = plan["total"]
+        mla_ops.latent_gather(ws, cache, scale, self.d_page_table, plan["spans"], plan["n_spans"], plan["max_tiles"])
+        if fp8_w:
+            wq, sw = self.static_q[wh]
+            gemm_ops.gemm(ws.lat8[:n, :kv_lora], wq, sx=ws.lat_scale, sw=sw, out=ws.kvb[:n], swap=False)
+        else:
+            gemm_ops.gemm(ws.lat16[:n], self.static[wh], out=ws.kvb[:n], swap=False)
+        mla_ops.q_rope(q, rope_tab, plan["pos"], heads, nope, qk_rope, pair)
+        mla_ops.prefill_attention(q, ws, n, self.d_in[2], plan["pos"], float(ins.f[0]), ao)
+
     def _op_mla_attention(self, st, ins):
         ao, q, rope, _pos, wkv_b = (self.tensor(st, ins.t[k]) for k in range(5))
         cache, scale = self.tensor(st, ins.t[5]), self.tensor(st, ins.t[6])
@@ -427,9 +500,21 @@ class GpuEngine(EngineBase):
         if heads != 128 or kv_lora != 512 or qk_rope != 64:
             raise EngineError("the sm_100a MLA kernel is specialised for 128 heads, 512 latent and 64 rope dims per rank")
         T = st.rows
-        wuk_t, wuv = self._mla_prep(layer, ins.t[4], heads, kv_lora, nope, v_head)
         if nope != 128 or v_head != 128:
             raise EngineError("the fused MLA projection kernels are specialised for 128 nope / 128 v dims")
+        plan = self._mla_plan
+        if plan is not None and (plan["R"] != T or (bool(ins.i[6]) and ins.t[7] != pk.T_NONE and T <= self.SPARSE_MAX_ROWS)):
+            plan = None
+        kvlen_dense = self.d_kvlen_row if plan is None else plan["kvlen"]
+        if plan is not None and not plan["riders"]:
+            # every live row is in a materialised run: the absorbed kernels have nothing to do
+            if T > self._mla_plan_rows:
+                ao[self._mla_plan_rows:T].zero_()
+            self._mla_prefill(st, ins, plan, ao, q, rope, cache, scale)
+            if self._wants_q(st, ins.t[0]):
+                st.q[(ins.t[0], 0)] = rowops.quant_act(ao)
+            return
+        wuk_t, wuv = self._mla_prep(layer, ins.t[4], heads, kv_lora, nope, v_head)
         q8, sq = mla_ops.absorb(q, wuk_t, rope, self.d_in[1], heads, pair)
         if self._mla_ws is None or self._mla_ws.opart.shape[0] < T:
             # up to 8 splits per request (the fold kernel's limit); a request's tiles are dealt evenly over its splits
@@ -455,15 +540,20 @@ class GpuEngine(EngineBase):
         else:
             # the work list depends on the rows' lengths only: the first dense attention of a walk builds it for all layers
             if not st.scratch.get("mla_items") or os.environ.get("PLOW_MLA_ITEMS_PER_LAYER") == "1":
-                mla_ops.build_items(self.d_kvlen_row, T, self._mla_ws)
+                mla_ops.build_items(kvlen_dense, T, self._mla_ws)
                 st.scratch["mla_items"] = True
-            mla_ops.decode(q8, sq, cache, scale, self.kv_smax[layer], self.d_page_table, self.d_in[2], self.d_kvlen_row,
+            mla_ops.decode(q8, sq, cache, scale, self.kv_smax[layer], self.d_page_table, self.d_in[2], kvlen_dense,
                            self._mla_ws, float(ins.f[0]), merge=False, build_items=False, claim_slot=layer)
-            kvlen = self.d_kvlen_row
-        want = self._wants_q(st, ins.t[0])
+            kvlen = kvlen_dense
+        want = self._wants_q(st, ins.t[0]) and plan is None
         aq, saq = mla_ops.fold(self._mla_ws, kvlen, wuv, T, heads, ao, want_fp8=want)
         if want:
             st.q[(ins.t[0], 0)] = (aq, saq)
+        if plan is not None:
+            # the runs chosen for the materialised form overwrite their rows (the absorbed kernels saw length 0 there)
+            self._mla_prefill(st, ins, plan, ao, q, rope, cache, scale)
+            if self._wants_q(st, ins.t[0]):
+                st.q[(ins.t[0], 0)] = rowops.quant_act(ao)
 
     # -- tensor parallel (row-parallel projections end in an all-reduce)
     def _need_tp(self):
@@ -648,6 +738,19 @@ class GpuEngine(EngineBase):
     def _run_insts(self, st: _Prog) -> None:
         st.q.clear()
         st.scratch["mla_items"] = False
+        if self.profile_ops:
+            # eager walk with an event pair around every instruction (diagnostic: serialises nothing, but the events
+            # themselves cost a few microseconds per instruction)
+            evs = []
+            for ins in st.prog.insts:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                self._run_one(st, ins)
+                b.record()
+                evs.append((ins, a, b))
+            torch.cuda.synchronize(self.device)
+            self.op_times_last = [(Op(ins.op).name, tuple(int(v) for v in ins.i[:3]), a.elapsed_time(b)) for ins, a, b in evs]
+            return
         if self.device_interp and self.spec.dtype == "bf16":
             for lo, hi, on_device in self._interp_segments(st):
                 if on_device:
@@ -758,6 +861,10 @@ class GpuEngine(EngineBase):
         self._upload_pages()
         self.d_in[:, :R].copy_(hin[:, :R], non_blocking=True)
         torch.add(self.d_in[1, :R], 1, out=self.d_kvlen_row[:R])
+        self._mla_plan = None
+        if not decode and rows > 0 and self._has_mla:
+            self._mla_plan = self._plan_mla_prefill(batch, R)
+            self._mla_plan_rows = rows
         try:
             if self.cuda_graphs and decode:
                 if st.graph is None:

@@ -61,7 +61,7 @@ def test_bf16_dual_residual(m, n, k, swap, bn):
 
 
 @pytest.mark.parametrize("m,n,k,swap,bn,dual", [
-    (300, 512, 512, False, 128, False), (260, 256, 1024, False, 64, True),
+    (300, 512, 512, False, 128, False), (260, 256, 1024, False, 64, True), (300, 512, 512, False, 256, False),
     (9, 512, 512, True, 32, False), (60, 256, 7168, True, 64, False), (128, 384, 256, True, 128, False),
     (20, 256, 512, True, 32, True), (50, 512, 2048, True, 64, True),
 ])
@@ -122,6 +122,44 @@ def test_quant_epilogue(m, swap, bn, fp8):
     ref = _ref(xr, wr, n, dual)
     got = quant.dequant_act_1x128(yq, syq)
     assert _relerr(got, ref) < 6e-2   # e4m3 has 3 mantissa bits
+    sref = ref.view(m, n // 128, 128).abs().amax(2).clamp_min(1e-10) / 448.0
+    assert _relerr(syq[:, :m].t(), sref) < 2e-2
+
+
+@pytest.mark.parametrize("dual,bn,grouped", [(True, 128, False), (False, 256, False), (True, 128, True), (False, 256, True),
+                                             (True, 64, True)])
+def test_large_m_fp8_tiles_quant_epilogue(dual, bn, grouped, monkeypatch):
+    """Token-major (non-swap) block-scaled tiles with eight epilogue warps: 256 accumulator columns per partial (gate | up
+    of 128, or 256 plain) and the 64 + 64 form, with the e4m3 + 1x128-scale output, dense and grouped (an empty expert,
+    ragged last tiles)."""
+    from plow_b200.ops import gemm, native, quant
+    if bn == 64:
+        monkeypatch.setattr(gemm, "_WIDE_DEFAULT", False)
+    E, n, k = (5, 512, 1024) if grouped else (0, 512, 1024)
+    counts = torch.tensor([130, 0, 300, 1, 257]) if grouped else torch.tensor([333])
+    off = torch.zeros(len(counts) + 1, dtype=torch.int32)
+    off[1:] = counts.cumsum(0)
+    m = int(off[-1])
+    tp = torch.zeros(len(counts) + 1, dtype=torch.int32)
+    tp[1:] = ((counts + 127) // 128).cumsum(0)
+    x, w = _mk(m, n, k, dual=dual, experts=max(E, 1))
+    xq, sx = quant.quant_act_1x128(x)
+    wq, sw = quant.quant_weight_128x128(w)
+    xr, wr = quant.dequant_act_1x128(xq, sx), quant.dequant_weight_128x128(wq, sw)
+    kw = dict(n_experts=E, grp_off=off.cuda(), tile_prefix=tp.cuda()) if grouped else {}
+    y = gemm.gemm(xq, wq, sx=sx, sw=sw, dual=dual, n_out=n, swap=False, bn=bn, **kw)
+    if bn >= 128:      # the quantising epilogue needs a token's whole 1x128 group inside one tile
+        yq, syq = gemm.gemm(xq, wq, sx=sx, sw=sw, dual=dual, n_out=n, swap=False, bn=bn, quant_out=True, **kw)
+    native.check_status()
+    per = n * (2 if dual else 1)
+    ref = torch.empty(m, n, device="cuda")
+    for e in range(len(counts)):
+        ref[off[e]:off[e + 1]] = _ref(xr[off[e]:off[e + 1]], wr[e * per:(e + 1) * per], n, dual)
+    assert _relerr(y, ref) < 1e-2
+    if bn < 128:
+        return
+    got = quant.dequant_act_1x128(yq, syq)
+    assert _relerr(got, ref) < 6e-2
     sref = ref.view(m, n // 128, 128).abs().amax(2).clamp_min(1e-10) / 448.0
     assert _relerr(syq[:, :m].t(), sref) < 2e-2
 

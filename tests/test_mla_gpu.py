@@ -146,3 +146,82 @@ def test_absorb_and_fold_fused_kernels():
         ref = torch.einsum("hc,hvc->hv", merged, wuv.view(H, 128, 512).float()).reshape(-1)
         assert _rel(ao[t], ref) < 1e-2
         assert _rel(aq[t].float().view(H, 128) * saq[:, t, None], ref.view(H, 128)) < 4e-2
+
+
+@pytest.mark.parametrize("fp8_weight", [True, False])
+def test_materialised_prefill_vs_reference(fp8_weight):
+    """Gather the cached latent, rebuild K / V through kv_b_proj, rotate the queries, attend causally: against the
+    same computation in fp32 PyTorch.  Two requests (one with a cached prefix, lengths off the 64-token grid) plus
+    rows that are masked out (position -1) and must keep their previous output."""
+    from plow_b200.ops import gemm as gemm_ops, mla, native, quant
+    from plow_b200.utils.rope import rope_table
+    H = 128
+    lens = [300, 200]                   # cached tokens per request after this step's rows were written
+    new = [130, 200]                    # the last `new` tokens of each are this step's rows
+    n_slots, max_pages = 3, 8
+    kv8, ksc, pt = _build_cache(lens, 12, max_pages, seed=3)
+    pt_full = torch.zeros(n_slots, max_pages, dtype=torch.int32, device="cuda")
+    pt_full[1], pt_full[2] = pt[0], pt[1]               # requests live in slots 1 and 2
+    slots = [1, 2]
+    g = torch.Generator(device="cuda").manual_seed(4)
+    w = torch.randn(H * 256, 512, device="cuda", generator=g) * 0.05
+    if fp8_weight:
+        wq, sw = quant.quant_weight_128x128(w)
+        w_ref = quant.dequant_weight_128x128(wq, sw).float()
+    else:
+        wq, sw = w.bfloat16(), None
+        w_ref = wq.float()
+    pad = 5                              # masked rows between and after the runs
+    T = sum(new) + 2 * pad
+    q = (torch.randn(T, H * 192, device="cuda", generator=g) * 0.5).bfloat16()
+    seq = torch.zeros(T, dtype=torch.int32, device="cuda")
+    pos = torch.full((T,), -1, dtype=torch.int32, device="cuda")
+    r = 0
+    runs = []
+    for s, L, n in zip(slots, lens, new):
+        seq[r:r + n] = s
+        pos[r:r + n] = torch.arange(L - n, L, dtype=torch.int32, device="cuda")
+        runs.append((r, n, s, L))
+        r += n + pad
+    tab = torch.from_numpy(rope_table(4096, 64, 10000.0)).cuda()
+    spans, base = [], 0
+    for s, L in zip(slots, lens):
+        spans.append([s, L, base, 0])
+        base += -(-L // 64) * 64
+    spans_d = torch.tensor(spans, dtype=torch.int32, device="cuda")
+    ws = mla.PrefillWorkspace(1024, T, n_slots, max_pages, fp8_weight=fp8_weight)
+    mla.latent_gather(ws, kv8, ksc, pt_full, spans_d, len(spans), max(-(-L // 64) for L in lens))
+    if fp8_weight:
+        gemm_ops.gemm(ws.lat8[:base, :512], wq, sx=ws.lat_scale, sw=sw, out=ws.kvb[:base], swap=False)
+    else:
+        gemm_ops.gemm(ws.lat16[:base], wq, out=ws.kvb[:base], swap=False)
+    q_in = q.clone()
+    mla.q_rope(q, tab, pos, H, 128, 64, 1)
+    out = torch.full((T, H * 128), 7.0, device="cuda").bfloat16()
+    scale = 1.0 / math.sqrt(192)
+    mla.prefill_attention(q, ws, base, seq, pos, scale, out)
+    torch.cuda.synchronize()
+    native.check_status()
+    kvd = kv8.float() * ksc[..., None]                        # [pages, 64, 576]
+    worst = 0.0
+    for (r0, n, s, L), sp in zip(runs, spans):
+        pages = pt_full[s, :(L + 63) // 64].long()
+        lat = kvd[pages].reshape(-1, 576)[:L]
+        kvb = (lat[:, :512] @ w_ref.t()).view(L, H, 256)
+        # what the kernel consumed: its own bf16 K / V
+        got_kvb = ws.kvb[sp[2]:sp[2] + L].view(L, H, 256).float()
+        assert _rel(got_kvb, kvb) < (3e-2 if fp8_weight else 1e-2)
+        k = torch.cat([kvb[..., :128], lat[:, None, 512:].expand(L, H, 64)], -1)      # [L, H, 192]
+        v = kvb[..., 128:]
+        q3 = q_in[r0:r0 + n].view(n, H, 192).float()
+        qr = _rope_ref(q3[..., 128:].permute(1, 0, 2), tab, pos[r0:r0 + n]).permute(1, 0, 2)
+        qq = torch.cat([q3[..., :128], qr], -1)
+        sc = torch.einsum("nhd,lhd->hnl", qq, k) * scale
+        mask = torch.arange(L, device="cuda")[None, :] <= pos[r0:r0 + n, None].long()
+        sc = sc.masked_fill(~mask[None], float("-inf"))
+        ref = torch.einsum("hnl,lhd->nhd", sc.softmax(-1), v).reshape(n, H * 128)
+        worst = max(worst, _rel(out[r0:r0 + n], ref))
+    assert worst < 2e-2, worst
+    masked = pos < 0
+    assert torch.all(out[masked].float() == 7.0)
+    assert torch.equal(q[masked], q_in[masked])
