@@ -287,17 +287,11 @@ __device__ __forceinline__ uint32_t ordered_bits(float f) {
 // One warp per token.  table[t][j] = {expert id, gate bits}.  Selection key = score + bias, gate =
 // unbiased score; groups are contiguous; group score = sum of the group's top-2 biased scores;
 // ties go to the lowest group / expert id; gates renormalised over the k winners then scaled.
-__global__ void router_topk_kernel(int2* table, const float* logits, const float* bias, int T, int E, int k,
-                                   int n_group, int topk_group, int sigmoid, int norm_topk, float route_scale) {
-  plow::pdl_launch_dependents();
-  plow::pdl_wait();
-  extern __shared__ float sm[];    // per warp: score[E], sel[E]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (t >= T) return;
-  float* score = sm + warp * 2 * E;
-  float* sel = score + E;
-  const float* lg = logits + static_cast<size_t>(t) * E;
+// One warp: the routing decision of token t from its E logits `lg` (global or shared memory); score / sel are E floats
+// of scratch each.
+__device__ void route_one_token(int2* table, const float* lg, const float* bias, int t, int E, int k, int n_group,
+                                int topk_group, int sigmoid, int norm_topk, float route_scale, float* score, float* sel) {
+  const int lane = threadIdx.x & 31;
   if (sigmoid) {
     for (int e = lane; e < E; e += 32) score[e] = 1.0f / (1.0f + __expf(-lg[e]));
   } else {
@@ -363,6 +357,19 @@ __global__ void router_topk_kernel(int2* table, const float* logits, const float
   }
 }
 
+__global__ void router_topk_kernel(int2* table, const float* logits, const float* bias, int T, int E, int k,
+                                   int n_group, int topk_group, int sigmoid, int norm_topk, float route_scale) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
+  extern __shared__ float sm[];    // per warp: score[E], sel[E]
+  const int warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= T) return;
+  float* score = sm + warp * 2 * E;
+  route_one_token(table, logits + static_cast<size_t>(t) * E, bias, t, E, k, n_group, topk_group, sigmoid, norm_topk,
+                  route_scale, score, score + E);
+}
+
 // ---- MoE align / gather / combine -------------------------------------------------------------
 // One CTA.  Counts the (token, slot) pairs routed to this rank's experts [e_base, e_base+e_local),
 // writes grp_off[e_local+1], tile_prefix[e_local+1] (128-row tiles) and the pair<->row maps.
@@ -370,11 +377,9 @@ __global__ void router_topk_kernel(int2* table, const float* logits, const float
 // shared_rows) in order: the shared expert stacked behind the routed ones.  Its rows get pair_of_row = token * top_k,
 // so the gather kernel (token = pair / top_k) copies them like any other row; grp_off / tile_prefix then have
 // e_local + 2 entries and pair_of_row n_pairs + shared_rows.
-__global__ void moe_align_kernel(const int2* table, int n_pairs, int e_base, int e_local, int* grp_off, int* tile_prefix,
-                                 int* row_of_pair, int* pair_of_row, int shared_rows, int shared_tok_base, int top_k) {
-  plow::pdl_launch_dependents();
-  plow::pdl_wait();
-  extern __shared__ int cnt[];     // e_local counts, then e_local cursors
+// Body of the align step, run by one whole CTA; cnt = 2 * e_local ints of shared memory.
+__device__ void moe_align_cta(const int2* table, int n_pairs, int e_base, int e_local, int* grp_off, int* tile_prefix,
+                              int* row_of_pair, int* pair_of_row, int shared_rows, int shared_tok_base, int top_k, int* cnt) {
   int* cur = cnt + e_local;
   for (int e = threadIdx.x; e < e_local; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
@@ -401,6 +406,115 @@ __global__ void moe_align_kernel(const int2* table, int n_pairs, int e_base, int
     row_of_pair[p] = row;
   }
   for (int t = threadIdx.x; t < shared_rows; t += blockDim.x) pair_of_row[routed + t] = (shared_tok_base + t) * top_k;
+}
+
+__global__ void moe_align_kernel(const int2* table, int n_pairs, int e_base, int e_local, int* grp_off, int* tile_prefix,
+                                 int* row_of_pair, int* pair_of_row, int shared_rows, int shared_tok_base, int top_k) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
+  extern __shared__ int cnt[];     // e_local counts, then e_local cursors
+  moe_align_cta(table, n_pairs, e_base, e_local, grp_off, tile_prefix, row_of_pair, pair_of_row, shared_rows, shared_tok_base,
+                top_k, cnt);
+}
+
+// Decode-size routing in one launch: router projection + top-k + align.  One CTA per token: the token's normalised
+// hidden row is staged in shared memory as f32, each warp forms the dot products of its share of the E router rows
+// (bf16 weights, f32 accumulation: the numerics of the GEMM it replaces), warp 0 makes the routing decision, and the
+// CTA that finishes last (a ticket counter) lays the pairs out by expert.  Replaces a 1-tile GEMM (~20 us: a K = 7168
+// reduction on one tile, split-K over a few CTAs), the top-k kernel and the align kernel.
+// Shared memory: H floats | E logits | 2 E scratch | 2 e_local ints.
+__global__ void __launch_bounds__(512)
+moe_route_kernel(int2* table, float* logits_out, const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, const float* bias,
+                 int T, int H, int E, int k, int n_group, int topk_group, int sigmoid, int norm_topk, float route_scale,
+                 int do_align, int e_base, int e_local, int* grp_off, int* tile_prefix, int* row_of_pair, int* pair_of_row,
+                 int shared_rows, int shared_tok_base, unsigned int* ticket) {
+  plow::pdl_launch_dependents();
+  plow::pdl_wait();
+  extern __shared__ float rsm[];
+  float* xr = rsm;
+  float* lg = xr + H;
+  float* score = lg + E;
+  int* cnt = reinterpret_cast<int*>(score + 2 * E);
+  __shared__ int is_last;
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const __nv_bfloat16* xp = x + static_cast<size_t>(t) * ldx;
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    const uint4 v = reinterpret_cast<const uint4*>(xp)[i];
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h2[j]);
+      xr[i * 8 + 2 * j] = f.x; xr[i * 8 + 2 * j + 1] = f.y;
+    }
+  }
+  __syncthreads();
+  // The loop is bound by L2 latency, not bandwidth: every lane keeps 16 independent 16-byte loads in flight.  A warp
+  // works on four (router row, K part) slots at a time: R = 1, 2 or 4 rows, each cut into 4 / R parts along K.
+  const int per_warp = (E + nw - 1) / nw;
+  const int R = per_warp >= 4 ? 4 : per_warp >= 2 ? 2 : 1, P = 4 / R;
+  const int C = H / 8;                                       // 16-byte chunks per row
+  const int part_len = ((C + 32 * P - 1) / (32 * P)) * 32;   // chunks per part, a multiple of the warp width
+  for (int e0 = warp; e0 < E; e0 += R * nw) {
+    const uint4* wp[4];
+    int lo[4];
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      wp[j] = reinterpret_cast<const uint4*>(w + static_cast<size_t>(min(e0 + (j % R) * nw, E - 1)) * H);
+      lo[j] = (j / R) * part_len;
+    }
+    for (int i0 = lane; i0 < part_len; i0 += 128) {
+      // phase 1: all 16 loads of this batch (4 slots x 4 strides) are issued before any is used
+      uint4 v[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int ii = i0 + u * 32;
+          v[u][j] = (ii < part_len && lo[j] + ii < C) ? __ldg(wp[j] + lo[j] + ii) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int i = min(lo[j] + i0 + u * 32, C - 1);
+          const float4 a = *reinterpret_cast<const float4*>(xr + i * 8), b = *reinterpret_cast<const float4*>(xr + i * 8 + 4);
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v[u][j]);
+          const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]), f2 = __bfloat1622float2(h2[2]),
+                       f3 = __bfloat1622float2(h2[3]);
+          float s = acc[j];
+          s = fmaf(a.x, f0.x, s); s = fmaf(a.y, f0.y, s); s = fmaf(a.z, f1.x, s); s = fmaf(a.w, f1.y, s);
+          s = fmaf(b.x, f2.x, s); s = fmaf(b.y, f2.y, s); s = fmaf(b.z, f3.x, s); s = fmaf(b.w, f3.y, s);
+          acc[j] = s;
+        }
+    }
+    // slots j, j + R, ... hold the K parts of row j
+    if (R == 1) { acc[0] += acc[1] + acc[2] + acc[3]; }
+    else if (R == 2) { acc[0] += acc[2]; acc[1] += acc[3]; }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j >= R) break;
+      const float r = warp_sum(acc[j]);
+      const int e = e0 + j * nw;
+      if (lane == 0 && e < E) { lg[e] = r; if (logits_out) logits_out[static_cast<size_t>(t) * E + e] = r; }
+    }
+  }
+  __syncthreads();
+  if (warp == 0)
+    route_one_token(table, lg, bias, t, E, k, n_group, topk_group, sigmoid, norm_topk, route_scale, score, score + E);
+  if (!do_align) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    is_last = atomicAdd(ticket, 1u) == static_cast<unsigned int>(T) - 1u;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (threadIdx.x == 0) *ticket = 0u;       // re-armed for the next launch (stream order separates launches)
+  moe_align_cta(table, T * k, e_base, e_local, grp_off, tile_prefix, row_of_pair, pair_of_row, shared_rows, shared_tok_base, k,
+                cnt);
 }
 
 // Rows of the quantised activations gathered into expert order (scales are transposed [kb][row]).
@@ -638,6 +752,23 @@ int plow_router_topk(void* table, const float* logits, const float* bias, int T,
   const int wpb = 4;
   plow::launch_serial(router_topk_kernel, dim3((T + wpb - 1) / wpb), dim3(wpb * 32), wpb * 2 * E * 4, S(st), (int2*)table, logits, bias, T, E, k, n_group,
                                                                                 topk_group, sigmoid, norm_topk, route_scale);
+  return ok();
+}
+
+// x bf16 [T][ldx] (normalised hidden rows), w bf16 [E][H].  logits_out (f32 [T][E]) may be null.  With do_align the
+// align outputs are written as by plow_moe_align; `ticket` is one zero-initialised word that the kernel re-arms.
+int plow_moe_route(void* table, float* logits_out, const void* x, int ldx, const void* w, const float* bias, int T, int H, int E,
+                   int k, int n_group, int topk_group, int sigmoid, int norm_topk, float route_scale, int do_align, int e_base,
+                   int e_local, int* grp_off, int* tile_prefix, int* row_of_pair, int* pair_of_row, int shared_rows,
+                   int shared_tok_base, void* ticket, void* st) {
+  if (k > 32 || n_group > 32 || E % (n_group > 0 ? n_group : 1) || H % 8 || (ldx % 8) || T <= 0) return -1;
+  const size_t smem = static_cast<size_t>(H + 3 * E) * 4 + static_cast<size_t>(2 * (do_align ? e_local : 0)) * 4;
+  if (smem > 200 * 1024) return -2;
+  static plow::DeviceOnce attr;
+  if (plow::ensure_smem(attr, moe_route_kernel, 200 * 1024) != cudaSuccess) return -3;
+  plow::launch_serial(moe_route_kernel, dim3(T), dim3(512), smem, S(st), (int2*)table, logits_out, (const bf16*)x, ldx, (const bf16*)w,
+                      bias, T, H, E, k, n_group, topk_group, sigmoid, norm_topk, route_scale, do_align, e_base, e_local, grp_off,
+                      tile_prefix, row_of_pair, pair_of_row, shared_rows, shared_tok_base, (unsigned int*)ticket);
   return ok();
 }
 

@@ -1,9 +1,9 @@
 """Hardware registry: the facts the cost model, the scheduler and the runtime planner share.
 
 Only Blackwell B200 (sm_100a) is a compile target for device code; a ``cpu`` entry exists for the
-hermetic CPU interpreter.  Peaks come in two flavours: nominal (datasheet) and measured (the
-repository's ``MEASURED_PEAKS.json`` when present), and every roofline fraction the tools print
-says which one it used.  Reference counterpart: crates/hwspec (registry.rs, isa.rs,
+hermetic CPU interpreter.  Peaks come in two flavours: nominal (datasheet) and measured (a JSON file
+of measured copy bandwidth / GEMM throughput that the caller names, ``lookup(..., peaks_file=...)`` or
+``--peaks`` on the tools), and every roofline fraction the tools print says which one it used.  Reference counterpart: crates/hwspec (registry.rs, isa.rs,
 nvidia/blackwell.rs:57-118).
 """
 from __future__ import annotations
@@ -75,14 +75,15 @@ SUPPORTED_ARCHS = ("sm_100a", "cpu")
 
 
 def lookup(name: str, peaks_file: str | Path | None = None) -> GpuSpec:
+    """Registry entry for ``name``.  ``peaks_file`` (JSON with hbm_gbs / bf16_tflops / bf16_tflops_sustained measured on
+    the machine at hand) attaches measured peaks; without it only the nominal figures are known."""
     key = name.lower().replace("nvidia ", "")
     if key not in _REGISTRY:
         raise KeyError(f"unknown device '{name}'; known: {sorted(_REGISTRY)}")
     spec = _REGISTRY[key]
-    pf = Path(peaks_file) if peaks_file else Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
-    if key == "b200" and pf.exists():
+    if key == "b200" and peaks_file is not None and Path(peaks_file).exists():
         try:
-            m = json.loads(pf.read_text())
+            m = json.loads(Path(peaks_file).read_text())
             spec = GpuSpec(**{**spec.__dict__, "measured": {k: m[k] for k in
                                                           ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained") if k in m}})
         except (OSError, ValueError):

@@ -117,6 +117,7 @@ _SIGS = {
     "plow_mla_kv_write": "ppppiipppppiiiifip",
     "plow_router_topk": "pppiiiiiiifp",
     "plow_moe_align": "piiippppiiip",
+    "plow_moe_route": "pppipp" "iiiiiiii" "f" "iii" "pppp" "ii" "pp",
     "plow_moe_gather": "ppippipp" "iiip",
     "plow_moe_combine": "pppppiiipp",
     "plow_argmax": "ppiip",

@@ -21,10 +21,10 @@ import torch.distributed as dist
 NVLINK_GBS = 770.0
 
 
-def _peaks():
+def _peaks(path):
+    """(HBM GB/s, sustained bf16 TFLOP/s, source) from the measured-peaks JSON named on the command line."""
     try:
-        root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-        p = json.load(open(os.path.join(root, "MEASURED_PEAKS.json")))
+        p = json.load(open(path))
         return p["hbm_gbs"], p["bf16_tflops_sustained"], "measured"
     except Exception:
         return 6650.0, 1400.0, "fallback"
@@ -58,13 +58,14 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--reps", type=int, default=8)
+    ap.add_argument("--peaks", default="", help="JSON file of measured peaks (hbm_gbs, bf16_tflops_sustained) for the roofline column")
     a = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     from ..ops import native, quant
     from .tp import TpComm
-    hbm, tflops, src = _peaks()
+    hbm, tflops, src = _peaks(a.peaks)
     fused = TpComm(rank, world, impl="fused", max_rows=128, max_n=8192, max_k=8192, form="oneshot")
     fused2 = TpComm(rank, world, impl="fused", max_rows=128, max_n=8192, max_k=8192, form="twoshot")
     fused3 = TpComm(rank, world, impl="fused", max_rows=128, max_n=8192, max_k=8192, form="nvls") if fused.mc_ptr else None

@@ -242,6 +242,7 @@ class GpuEngine(EngineBase):
         # materialised prefill (K / V rebuilt from the latent once per layer for long runs of new rows)
         self._mla_pf_ws = None
         self._mla_plan = None
+        self._route_ticket = None
         self._mla_plan_rows = 0
         self._has_mla = any(l.attn.kind == "mla" for l in self.spec.layers)
         self.h_plan = torch.zeros(2 * max_rows + 4 * n_slots, dtype=I32).pin_memory()
@@ -271,8 +272,35 @@ class GpuEngine(EngineBase):
                 st.needs_q.add((ins.t[1], ins.i[6], ins.i[1]))      # (handle, col offset, K)
             if ins.op == Op.MOE_GEMM and self.spec.weight_quant == "fp8_block128":
                 st.needs_q.add((ins.t[1], 0, self.spec.hidden))
+        self._plan_route_fusion(st, prog)
         self.progs[idx] = st
         return st
+
+    ROUTE_FUSE_MAX_ROWS = int(os.environ.get("PLOW_ROUTE_FUSE_MAX_ROWS", "256"))
+
+    def _plan_route_fusion(self, st: _Prog, prog) -> None:
+        """Decode-size programs: a router projection GEMM followed by ROUTER_TOPK (and the align step of a local MOE_GEMM)
+        runs as one launch (csrc/cuda/rowops.cu, moe_route_kernel).  Records which GEMM instructions to skip and what
+        the top-k instruction does instead."""
+        st.skip, st.route = set(), {}
+        if prog.rows > self.ROUTE_FUSE_MAX_ROWS:
+            return
+        insts = prog.insts
+        for i, g in enumerate(insts[:-1]):
+            tk = insts[i + 1]
+            if g.op != Op.GEMM or tk.op != Op.ROUTER_TOPK or tk.t[1] != g.t[0]:
+                continue
+            N, K, flags, co = g.i[0], g.i[1], g.i[2], g.i[6]
+            w = self.static.get(g.t[2])
+            x = st.t.get(g.t[1])
+            if (flags & (pk.GEMM_FP8_BLOCK | pk.GEMM_DUAL_SILU)) or co != 0 or w is None or w.dtype != BF16 or x is None \
+                    or x.dtype != BF16 or x.shape[1] != K or N != tk.i[0] or K % 8 or N > 1024:
+                continue
+            if any(o is not g and o is not tk and g.t[0] in o.t for o in insts):
+                continue                                  # something else reads the logits
+            moe = next((m for m in insts if m.op == Op.MOE_GEMM and m.t[2] == tk.t[0]), None)
+            st.skip.add(id(g))
+            st.route[id(tk)] = (g, moe)
 
     def tensor(self, st: _Prog, h: int):
         if h == pk.T_NONE:
@@ -335,6 +363,8 @@ class GpuEngine(EngineBase):
         native.call("plow_eltwise2", out, g, u, out.numel(), 1)
 
     def _op_gemm(self, st, ins):
+        if id(ins) in st.skip:
+            return                     # a router projection computed inside the fused routing kernel
         y, x = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])
         N, K, flags, swap, bn, co = ins.i[0], ins.i[1], ins.i[2], ins.i[3], ins.i[4], ins.i[6]
         dual = bool(flags & pk.GEMM_DUAL_SILU)
@@ -342,7 +372,8 @@ class GpuEngine(EngineBase):
         if flags & pk.GEMM_FP8_BLOCK:
             wq, sw = self.static_q[ins.t[2]]
             xq, sx = self._quant_of(st, ins.t[1], co, K, x)
-            want = self._wants_q(st, ins.t[0]) and (swap or bn == 128) and N % 128 == 0
+            wide = dual and gemm_ops._WIDE_DEFAULT and not swap and bn == 64       # gemm() widens these tiles to 128
+            want = self._wants_q(st, ins.t[0]) and (swap or bn == 128 or wide) and N % 128 == 0
             if want:
                 # SwiGLU / projection result re-quantised in the GEMM epilogue for the next e4m3 GEMM
                 yq, syq = gemm_ops.gemm(xq[:M], wq, sx=sx, sw=sw, dual=dual, n_out=N, swap=bool(swap), bn=bn, quant_out=True)
@@ -644,8 +675,33 @@ class GpuEngine(EngineBase):
     def _op_router_topk(self, st, ins):
         table, logits = self.tensor(st, ins.t[0]), self.tensor(st, ins.t[1])
         bias = self.tensor(st, ins.t[2]) if ins.t[2] != pk.T_NONE else None
-        native.call("plow_router_topk", table, logits, bias, st.rows, ins.i[0], ins.i[1], max(1, ins.i[2]), max(1, ins.i[3]),
-                    ins.i[4], ins.i[5], float(ins.f[0]))
+        fused = st.route.get(id(ins))
+        if fused is not None:
+            g, moe = fused
+            x, w = self.tensor(st, g.t[1]), self.static[g.t[2]]
+            local = moe is not None and not (self.comm is not None and max(1, moe.i[4]) > 1)
+            al = (None,) * 4
+            e_base = e_local = shared_rows = 0
+            if local:
+                e_local, k, ep, sg = moe.i[1], moe.i[2], max(1, moe.i[4]), bool(moe.i[6])
+                e_base = self.rank * e_local if ep > 1 else 0
+                shared_rows = st.rows if sg else 0
+                key = ("align", id(moe))
+                if key not in st.scratch:
+                    ng, n_pairs = e_local + (1 if sg else 0), st.rows * k
+                    st.scratch[key] = (torch.empty(ng + 1, dtype=I32, device=self.device), torch.empty(ng + 1, dtype=I32, device=self.device),
+                                       torch.empty(n_pairs, dtype=I32, device=self.device),
+                                       torch.empty(n_pairs + shared_rows, dtype=I32, device=self.device))
+                al = st.scratch[key]
+                st.scratch[("aligned", id(moe))] = True
+            if self._route_ticket is None:
+                self._route_ticket = torch.zeros(1, dtype=I32, device=self.device)
+            native.call("plow_moe_route", table, None, x, x.stride(0), w, bias, st.rows, g.i[1], ins.i[0], ins.i[1], max(1, ins.i[2]),
+                        max(1, ins.i[3]), ins.i[4], ins.i[5], float(ins.f[0]), int(local), e_base, e_local, al[0], al[1], al[2], al[3],
+                        shared_rows, 0, self._route_ticket)
+        else:
+            native.call("plow_router_topk", table, logits, bias, st.rows, ins.i[0], ins.i[1], max(1, ins.i[2]), max(1, ins.i[3]),
+                        ins.i[4], ins.i[5], float(ins.f[0]))
         if self.comm is not None and self.ep > 1:
             moe = next((m for m in st.prog.insts if m.op == Op.MOE_GEMM and m.t[2] == ins.t[0]), None)
             if moe is not None:
@@ -663,7 +719,10 @@ class GpuEngine(EngineBase):
         e_base = self.rank * e_local if ep > 1 else 0
         ng = e_local + (1 if sg else 0)
         n_rows = T * k + (T if sg else 0)
-        grp_off, tile_prefix, row_of_pair, pair_of_row = rowops.moe_align(table, e_base, e_local, shared_rows=T if sg else 0)
+        if st.scratch.pop(("aligned", id(ins)), False):
+            grp_off, tile_prefix, row_of_pair, pair_of_row = st.scratch[("align", id(ins))]      # laid out by the routing kernel
+        else:
+            grp_off, tile_prefix, row_of_pair, pair_of_row = rowops.moe_align(table, e_base, e_local, shared_rows=T if sg else 0)
         per = max(1, (T * k + e_local - 1) // e_local)
         swap = per <= 64
         if fp8:
@@ -677,9 +736,14 @@ class GpuEngine(EngineBase):
                                         swap=True, bn=bn, quant_out=True, ld_syq=n_rows)
                 yo = gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=ng, grp_off=grp_off, swap=True, bn=bn)
             else:
-                hb = gemm_ops.gemm(xs, w1, sx=sxs, sw=s1, dual=True, n_out=F, n_experts=ng, grp_off=grp_off,
-                                   tile_prefix=tile_prefix, swap=False, bn=64)
-                hq, shq = rowops.quant_act(hb)
+                if gemm_ops._WIDE_DEFAULT and F % 128 == 0:
+                    # 128 + 128 column SwiGLU tiles hold a token's whole 1x128 group: the e4m3 twin comes out of the epilogue
+                    hq, shq = gemm_ops.gemm(xs, w1, sx=sxs, sw=s1, dual=True, n_out=F, n_experts=ng, grp_off=grp_off,
+                                            tile_prefix=tile_prefix, swap=False, bn=128, quant_out=True, ld_syq=n_rows)
+                else:
+                    hb = gemm_ops.gemm(xs, w1, sx=sxs, sw=s1, dual=True, n_out=F, n_experts=ng, grp_off=grp_off,
+                                       tile_prefix=tile_prefix, swap=False, bn=64)
+                    hq, shq = rowops.quant_act(hb)
                 yo = gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=ng, grp_off=grp_off, tile_prefix=tile_prefix,
                                    swap=False, bn=128)
         else:

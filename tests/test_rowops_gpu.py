@@ -120,3 +120,49 @@ def test_moe_align_gather_combine():
         m = rop[:, j] >= 0
         ref[m] += gates[m, j, None] * y[rop[m, j].long()].float()
     assert _rel(out, ref) < 5e-3
+
+
+@pytest.mark.parametrize("E,k,ng,tg,sig,shared", [(32, 8, 1, 1, True, True), (64, 6, 8, 3, True, False), (16, 2, 1, 1, False, True)])
+def test_moe_route_fused_matches_gemm_topk_align(E, k, ng, tg, sig, shared):
+    """Router projection + top-k + align in one launch against the three separate steps (fp32 logits of the same bf16
+    operands; the routing tables must agree wherever the top-k margins exceed the summation-order noise, and the
+    layouts must describe the same grouping).  Run twice: the ticket counter re-arms itself."""
+    from plow_b200.ops import native, rowops
+    T, H = 64, 2048
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(E, H, device="cuda", generator=g) * 0.05).bfloat16()
+    bias = torch.randn(E, device="cuda", generator=g) * 0.1 if sig else None
+    logits = x.float() @ w.float().t()
+    ref_table = rowops.router_topk(logits, bias, k, ng, tg, sig, True, 2.5)
+    ng_all = E + (1 if shared else 0)
+    for _ in range(2):
+        table = torch.zeros(T, k, 2, dtype=torch.int32, device="cuda")
+        lg = torch.zeros(T, E, device="cuda")
+        grp_off = torch.zeros(ng_all + 1, dtype=torch.int32, device="cuda")
+        tile_prefix = torch.zeros(ng_all + 1, dtype=torch.int32, device="cuda")
+        row_of_pair = torch.zeros(T * k, dtype=torch.int32, device="cuda")
+        pair_of_row = torch.zeros(T * k + (T if shared else 0), dtype=torch.int32, device="cuda")
+        ticket = getattr(test_moe_route_fused_matches_gemm_topk_align, "_ticket", None)
+        if ticket is None:
+            ticket = torch.zeros(1, dtype=torch.int32, device="cuda")
+            test_moe_route_fused_matches_gemm_topk_align._ticket = ticket
+        native.call("plow_moe_route", table, lg, x, x.stride(0), w, bias, T, H, E, k, ng, tg, int(sig), 1, 2.5, 1, 0, E,
+                    grp_off, tile_prefix, row_of_pair, pair_of_row, T if shared else 0, 0, ticket)
+        torch.cuda.synchronize()
+        native.check_status()
+        assert int(ticket[0]) == 0
+        assert _rel(lg, logits) < 1e-5
+        same = (table[..., 0] == ref_table[..., 0]).all(1)
+        assert same.float().mean() > 0.9                       # near-ties may flip with the summation order
+        assert _rel(rowops.table_gates(table)[same], rowops.table_gates(ref_table)[same]) < 1e-4
+        g2, t2, rop2, por2 = rowops.moe_align(table, 0, E, shared_rows=T if shared else 0)
+        assert torch.equal(grp_off, g2) and torch.equal(tile_prefix, t2)
+        M = int(grp_off[E])
+        eid = table[..., 0].reshape(-1)
+        rows = row_of_pair.long()
+        assert (rows >= 0).all() and sorted(rows.tolist()) == list(range(M))
+        assert torch.equal(pair_of_row[rows], torch.arange(T * k, dtype=torch.int32, device="cuda"))
+        assert ((rows >= grp_off[eid.long()]) & (rows < grp_off[eid.long() + 1])).all()
+        if shared:
+            assert pair_of_row[M:].tolist() == [t * k for t in range(T)]
