@@ -47,6 +47,7 @@ struct GqaArgs {
   // materialised multi-head latent attention: the last `kr_slabs` key slabs come from a separate tensor shared by
   // all heads (the rotary part), and the value tile sits `v_x0` columns into the key tensor's head block
   int kr_slabs, v_x0;
+  int head_major;          // items are [chunk][head] (one split): visit them head by head
 };
 
 // HDQ = width of a query / key row, HDV = width of a value row.  They differ for multi-head latent attention in its
@@ -143,6 +144,12 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
   const uint32_t tm_s = tmem_base;         // S buffers [0,64) and [64,128); P (bf16 pairs) over the first 32 of each
   const uint32_t tm_o = tmem_base + 128;   // O: HD columns
   const int n_items = *a.n_items;
+  // head-major visiting order (every chunk holds one item per head, no splits): the CTAs running at one time then
+  // work on a handful of heads and share those heads' K / V through L2, instead of touching every head's K / V at once
+  const int n_chunks = a.head_major ? n_items / a.nkv : 0;
+  auto item_at = [&](int it) -> GqaItem {
+    return a.items[a.head_major ? (it % n_chunks) * a.nkv + it / n_chunks : it];
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -150,7 +157,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
       uint32_t item_it = 0, kv_it = 0;
       bool ok = true;
       for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x, ++item_it) {
-        const GqaItem w = a.items[it];
+        const GqaItem w = item_at(it);
         if (!mbar_wait(q_empty, (item_it & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagGqa); break; }
         mbar_expect_tx(q_full, Cfg::kQBytes);
         for (int c = 0; c < Cfg::kSlabsQ; ++c) tma_load_3d(q_smem + c * 16384, &tm_q, c * 64, w.kvh * a.group, w.r0, q_full);
@@ -199,7 +206,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
         return true;
       };
       for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x, ++item_it) {
-        const GqaItem w = a.items[it];
+        const GqaItem w = item_at(it);
         if (!mbar_wait(q_full, item_it & 1, abort_flag)) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_TMA_WAIT | kTagGqa); break; }
         tc_fence_after();
         if (!issue_qk(kv_it, tile_it)) { *abort_flag = 1; break; }
@@ -235,7 +242,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
     uint32_t item_it = 0, tile_it = 0;
     bool ok = true;
     for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x, ++item_it) {
-      const GqaItem w = a.items[it];
+      const GqaItem w = item_at(it);
       const int n_valid = w.nt * a.group;
       const bool warp_active = lq * 32 < n_valid;       // whole warp: rows past the chunk are never read
       const int tok = min(li / a.group, w.nt - 1);
@@ -519,7 +526,7 @@ int plow_gqa_attention(const void* q, const void* kc, const void* vc, int64_t n_
   a.opart = opart; a.lse = lse; a.out = static_cast<__nv_bfloat16*>(out); a.status = status;
   a.rows = rows; a.nq = nq; a.nkv = nkv; a.group = group; a.max_pages = max_pages; a.max_splits = max_splits; a.window = window;
   a.scale_log2e = softmax_scale * 1.4426950408889634f;
-  a.kr_slabs = 0; a.v_x0 = 0;
+  a.kr_slabs = 0; a.v_x0 = 0; a.head_major = 0;
   int grid = sm_count();
   if (item_cap < grid) grid = item_cap;
   int r = hd == 128 ? launch_gqa<128>(a, q, kc, vc, n_pages, grid, stream) : launch_gqa<256>(a, q, kc, vc, n_pages, grid, stream);
@@ -549,7 +556,7 @@ int plow_mla_prefill_attention(const void* q, const void* kvb, const void* krope
   a.opart = opart; a.lse = lse; a.out = static_cast<__nv_bfloat16*>(out); a.status = status;
   a.rows = rows; a.nq = heads; a.nkv = heads; a.group = 1; a.max_pages = max_pages; a.max_splits = max_splits; a.window = 0;
   a.scale_log2e = softmax_scale * 1.4426950408889634f;
-  a.kr_slabs = 1; a.v_x0 = 128;
+  a.kr_slabs = 1; a.v_x0 = 128; a.head_major = max_splits == 1 ? 1 : 0;
   int grid = sm_count();
   if (item_cap < grid) grid = item_cap;
   int r = launch_mla_prefill(a, q, kvb, krope, n_tokens, grid, stream);

@@ -122,6 +122,48 @@ class EngineBase:
         self.kvlen[slot] = len(self.tokens[slot])
         self.pool.publish(slot, self.tokens[slot])
 
+    # ---- slot snapshot / rewind / resume (reference: crates/plowrt/src/exec/gpu.rs:8905-9149) ---------------------
+    def snapshot_slot(self, slot: int) -> dict:
+        """What a later rewind_slot needs: the committed tokens (their KV is in the cache) and the cached length."""
+        return dict(tokens=list(self.tokens[slot]), kvlen=int(self.kvlen[slot]))
+
+    def can_rewind(self, slot: int, n_tokens: int) -> bool:
+        """A sequence can be cut back to n_tokens when no published (shared, content-addressed) page lies past the cut
+        and the model keeps no recurrent state (which only exists for the sequence's current end)."""
+        if slot not in self.tokens or n_tokens > len(self.tokens[slot]) or n_tokens < 0:
+            return False
+        if n_tokens == len(self.tokens[slot]):
+            return True
+        if self.has_recurrent_state:
+            return False
+        return n_tokens >= self.pool.seqs[slot].published * PAGE
+
+    def rewind_slot(self, slot: int, n_tokens: int) -> None:
+        """Forget the tokens past n_tokens (rejected drafts, a session whose next turn diverges): their pages go back
+        to the pool and the next step writes position n_tokens."""
+        if not self.can_rewind(slot, n_tokens):
+            raise EngineError(f"slot {slot} cannot be rewound to {n_tokens} tokens")
+        self.pool.truncate(slot, n_tokens)
+        del self.tokens[slot][n_tokens:]
+        self.kvlen[slot] = n_tokens
+        self._sync_pages(slot)
+
+    def resume_slot(self, slot: int, prompt: list) -> int:
+        """Continue a retained sequence with a new prompt: keeps the longest common prefix (at most len(prompt) - 1, so
+        the last prompt token is still computed and yields logits) and returns its length, or -1 when the slot cannot
+        be cut back that far (the caller then retires it and seats the request afresh)."""
+        have = self.tokens.get(slot)
+        if have is None:
+            return -1
+        n = min(len(have), len(prompt) - 1)
+        lcp = 0
+        while lcp < n and have[lcp] == prompt[lcp]:
+            lcp += 1
+        if lcp == 0 or not self.can_rewind(slot, lcp):
+            return -1
+        self.rewind_slot(slot, lcp)
+        return lcp
+
     def retire_slot(self, slot: int) -> None:
         self.pool.release(slot)
         self.tokens.pop(slot, None)

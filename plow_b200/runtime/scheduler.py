@@ -15,6 +15,7 @@ sched/rungs.rs (decode rung ladder), sched/slo.rs (TBT-budgeted prefill), serve/
 from __future__ import annotations
 
 import queue
+from collections import OrderedDict
 import threading
 import time
 from dataclasses import dataclass, field
@@ -44,6 +45,7 @@ class GenParams:
     min_tokens: int = 0
     logprobs: int | None = None
     session_id: str | None = None
+    session_end: bool = False             # the session's last turn: nothing is retained for it
     deadline_ms: float | None = None      # total time budget from arrival; None = no deadline
     json_mode: bool = False               # response_format json_object: tokens are filtered by a JSON recogniser
 
@@ -103,6 +105,8 @@ class SchedConfig:
     reserve_tokens: int = PAGE        # KV head-room required per live sequence before seating more
     ride: bool = True                 # decode rows ride the prefill launch (mixed step) instead of waiting a tick
     spec_depth: int = 0               # > 0: speculative decoding for greedy requests (prompt-lookup drafts, span verify)
+    session_ttl_s: float = 600.0      # a finished request that carried a session id keeps its slot and KV this long
+    max_sessions: int = -1            # retained sessions at most (-1: half of the slots; 0: retention off)
 
 
 class Metrics:
@@ -173,6 +177,9 @@ class ModelMux:
         self._drain_deadline = None          # set by drain(); acted on by the dispatcher thread
         self._submit_lock = threading.Lock()
         self._arrivals: list = []          # arrival times of recent requests (rate estimator)
+        # session id -> (slot, time retained): finished sequences whose KV waits for the session's next request
+        # (reference: crates/plowrt/src/serve/session.rs:1-12)
+        self.retained: "OrderedDict[str, tuple]" = OrderedDict()
         self.pd_target: "ModelMux | None" = None     # prefill/decode disaggregation: where finished prefills continue
         self.adopt_q: "queue.Queue" = queue.Queue()  # (request, KV image) pairs handed over by a prefill mux
 
@@ -295,6 +302,7 @@ class ModelMux:
             self.waiting = []
             return False
         self._shed_expired()
+        self._expire_sessions()
         self._adopt()
         self._admit()
         if not self.live:
@@ -371,9 +379,16 @@ class ModelMux:
         """Seat queued requests while slots and KV pages allow (arrival order; a request that does
         not fit blocks the ones behind it so large prompts cannot starve)."""
         eng = self.engine
-        while self.waiting and self.free_slots:
+        while self.waiting:
             r = self.waiting[0]
             toks = r.all_tokens()
+            sid = r.params.session_id
+            if sid is not None and sid in self.retained and self._resume_session(r, toks):
+                continue
+            if not self.free_slots:
+                if self._evict_session():
+                    continue
+                break
             need_pages = (len(toks) + 1 + PAGE - 1) // PAGE
             headroom = len(self.live) * ((self.cfg.reserve_tokens + PAGE - 1) // PAGE)
             # pages are reserved lazily, chunk by chunk: what seated requests have yet to reserve for the rest of their
@@ -384,6 +399,8 @@ class ModelMux:
                 have = len(eng.pool.seqs[q.slot].pages) if q.slot in eng.pool.seqs else 0
                 owed += max(0, want - have)
             if need_pages + headroom + owed > eng.pool.available() + eng.pool.cached_prefix_len(toks) // PAGE:
+                if self._evict_session():
+                    continue        # a retained session gave its pages back: look again
                 if not self.live and need_pages <= eng.pool.n_pages:
                     pass            # nothing else is running: the request gets the pool to itself
                 else:
@@ -396,13 +413,80 @@ class ModelMux:
                 self.free_slots.append(slot)
                 self.waiting.insert(0, r)
                 break
-            r.slot, r.done_prefill, r.cached_tokens = slot, cached, max(r.cached_tokens, cached)
-            r.pf_len = len(toks)   # a preempted request re-prefills its prompt plus what it generated
-            r.detok = r.detok or IncrementalDetok(self.tok)
-            r.rng = r.rng or np.random.default_rng(r.params.seed)
-            self.live[slot] = r
-            self.metrics.obs("queue_time", (time.monotonic() - r.arrived) * 1e3)
-            self.metrics.inc("cached_tokens", cached)
+            self._seat(r, slot, cached, len(toks))
+
+    def _seat(self, r: Request, slot: int, cached: int, n_tokens: int) -> None:
+        r.slot, r.done_prefill, r.cached_tokens = slot, cached, max(r.cached_tokens, cached)
+        r.pf_len = n_tokens        # a preempted request re-prefills its prompt plus what it generated
+        r.detok = r.detok or IncrementalDetok(self.tok)
+        r.rng = r.rng or np.random.default_rng(r.params.seed)
+        self.live[slot] = r
+        self.metrics.obs("queue_time", (time.monotonic() - r.arrived) * 1e3)
+        self.metrics.inc("cached_tokens", cached)
+
+    # ---- session retention -----------------------------------------------------------------------
+    def _session_cap(self) -> int:
+        return self.engine.max_slots // 2 if self.cfg.max_sessions < 0 else self.cfg.max_sessions
+
+    def _retain(self, r: Request) -> bool:
+        """Keep a finished request's slot for its session instead of retiring it."""
+        sid = r.params.session_id
+        cap = self._session_cap()
+        if sid is None or cap <= 0 or self.draining or r.params.session_end:
+            if sid is not None and sid in self.retained:
+                self._drop_session(sid)
+            return False
+        if sid in self.retained:                 # the session's older sequence is superseded
+            self._drop_session(sid)
+        while len(self.retained) >= cap:
+            self._evict_session()
+        self.retained[sid] = (r.slot, time.monotonic())
+        self.metrics.inc("sessions_retained")
+        return True
+
+    def _drop_session(self, sid: str) -> None:
+        slot, _ = self.retained.pop(sid)
+        self.engine.retire_slot(slot)
+        self.free_slots.append(slot)
+
+    def _evict_session(self) -> bool:
+        """Give the least recently retained session's slot and pages back; False when none is retained."""
+        if not self.retained:
+            return False
+        self._drop_session(next(iter(self.retained)))
+        self.metrics.inc("sessions_evicted")
+        return True
+
+    def _expire_sessions(self) -> None:
+        now = time.monotonic()
+        for sid in [s for s, (_, t) in self.retained.items() if now - t > self.cfg.session_ttl_s]:
+            self._drop_session(sid)
+            self.metrics.inc("sessions_expired")
+
+    def _resume_session(self, r: Request, toks: list) -> bool:
+        """Seat `r` in the slot its session retained, keeping the longest identical prefix; when the slot cannot be cut
+        back that far it is retired and the request takes the ordinary path."""
+        sid = r.params.session_id
+        slot, _ = self.retained[sid]
+        eng = self.engine
+        kept = eng.resume_slot(slot, toks)
+        if kept < 0:
+            self._drop_session(sid)
+            return False
+        need_pages = (len(toks) + 1 + PAGE - 1) // PAGE - len(eng.pool.seqs[slot].pages)
+        while need_pages > eng.pool.available():
+            other = next((s for s in self.retained if s != sid), None)
+            if other is None:
+                break
+            self._drop_session(other)
+        if need_pages > eng.pool.available() and self.live:
+            return False                      # stays retained; the request waits for pages like any other
+        del self.retained[sid]
+        self.waiting.pop(0)
+        self._seat(r, slot, kept, len(toks))
+        self.metrics.inc("session_hits")
+        self.metrics.inc("session_tokens_reused", kept)
+        return True
 
     # ---- prefill -------------------------------------------------------------------------------
     def _prefill_budget(self) -> int:
@@ -634,9 +718,10 @@ class ModelMux:
                      prompt_tokens_details=dict(cached_tokens=r.cached_tokens))
         r.out.put(Chunk("done", text=tail if reason != "stop" else "", finish_reason=reason, usage=usage))
         if r.slot >= 0 and self.live.get(r.slot) is r:
-            self.engine.retire_slot(r.slot)
             del self.live[r.slot]
-            self.free_slots.append(r.slot)
+            if not (reason in ("stop", "length") and self._retain(r)):
+                self.engine.retire_slot(r.slot)
+                self.free_slots.append(r.slot)
         self.metrics.inc("requests_finished")
         self.metrics.obs("e2e", (time.monotonic() - r.arrived) * 1e3)
 

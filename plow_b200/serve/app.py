@@ -288,6 +288,7 @@ def create_app(state: AppState) -> FastAPI:
             raise ApiError(400, "messages must be a non-empty list")
         params = _gen_params(body, default_max=256)
         params.session_id = request.headers.get("x-session-id")
+        params.session_end = request.headers.get("x-session-end", "") in ("1", "true")
         try:
             prompt = m.template.render([dict(x) for x in msgs], tools=body.get("tools"))
         except ChatTemplateError as e:
