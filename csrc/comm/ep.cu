@@ -27,30 +27,11 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "ep_args.h"
 #include "ptx.cuh"
 
 namespace {
 using namespace plow;
-
-struct EpLayout {         // byte offsets inside the symmetric region (identical on all ranks)
-  uint64_t cnt_all;       // int32 [W][E]
-  uint64_t cnt_flag;      // u32 [W] (stride 32 words)
-  uint64_t data_ctr;      // u32
-  uint64_t y_flag;        // u32 [W] (stride 32 words)
-  uint64_t recv_x;        // u8  [Rmax][H]
-  uint64_t recv_sx;       // f32 [H/128][Rmax]
-  uint64_t y;             // bf16 [Rmax][H]
-};
-
-struct EpArgs {
-  uint8_t* peer[8];
-  EpLayout L;
-  int W, me, E, e_local, Rmax, H;
-  uint32_t* epoch;        // device word: layer-call counter (monotonic)
-  int* status;
-  unsigned long long deadline_ns;
-  unsigned long long* trace;   // optional [1 + 2n] u64: count, then (tag, globaltimer) pairs (debug aid), NULL when off
-};
 
 __device__ __forceinline__ void trace_mark(const EpArgs& a, unsigned long long tag) {
   if (a.trace) {
@@ -66,6 +47,25 @@ __device__ __forceinline__ bool wait_ge(const uint32_t* p, uint32_t target, unsi
     __nanosleep(256);   // back off: the polled line is also the target of the peers' stores
   }
   return true;
+}
+
+// One warp copies a row of H bytes: up to eight 16-byte loads per lane are issued before the first store, so a row costs
+// about one load round trip and one store burst instead of H / 512 dependent load -> store pairs (measured: the push of
+// 576 rows took 30 us with the dependent form, most of it latency).
+__device__ __forceinline__ void warp_copy_row(uint4* dst, const uint4* src, int n16, int lane) {
+  for (int i0 = 0; i0 < n16; i0 += 256) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * 32 + lane;
+      if (i < n16) v[u] = src[i];
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * 32 + lane;
+      if (i < n16) dst[i] = v[u];
+    }
+  }
 }
 
 __global__ void ep_counts_kernel(EpArgs a, const int2* table, int n_pairs, int* cursor) {
@@ -96,7 +96,7 @@ __global__ void ep_push_kernel(EpArgs a, const int2* table, int n_pairs, int top
                                int ld_sx, int* cursor, int* grp_off, int* tile_prefix, int* pair_dest, int shared_rows) {
   plow::pdl_launch_dependents();
   plow::pdl_wait();
-  extern __shared__ int sm[];                 // cnt [W][E], base [E]
+  extern __shared__ int sm[];                 // cnt [W][E], base [E], tot [E]
   int* cnt = sm;
   int* base = sm + a.W * a.E;
   __shared__ int fail;
@@ -111,46 +111,48 @@ __global__ void ep_push_kernel(EpArgs a, const int2* table, int n_pairs, int top
   if (fail) { if (threadIdx.x == 0) atomicCAS(a.status, 0, PLOW_ERR_PEER_WAIT | kTagEp); return; }
   if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 4);
   const int* call = reinterpret_cast<const int*>(a.peer[a.me] + a.L.cnt_all);
-  for (int i = threadIdx.x; i < a.W * a.E; i += blockDim.x) cnt[i] = call[i];
+  int* tot = base + a.E;                      // [E] rows of expert e over all source ranks
+  for (int i = threadIdx.x; i < a.W * a.E; i += blockDim.x) cnt[i] = __ldcg(call + i);
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 40);
+  for (int e = threadIdx.x; e < a.E; e += blockDim.x) {
+    int c = 0;
+    for (int s = 0; s < a.W; ++s) c += cnt[s * a.E + e];
+    tot[e] = c;
+  }
   __syncthreads();
   // base[e] = first row, on the owner of e, of the rows this rank sends for expert e
   for (int e = threadIdx.x; e < a.E; e += blockDim.x) {
     const int e0 = (e / a.e_local) * a.e_local;
     int off = 0;
-    for (int f = e0; f < e; ++f)
-      for (int s = 0; s < a.W; ++s) off += cnt[s * a.E + f];
+    for (int f = e0; f < e; ++f) off += tot[f];
     for (int s = 0; s < a.me; ++s) off += cnt[s * a.E + e];
     base[e] = off;
   }
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    int off = 0, tiles = 0;
-    for (int el = 0; el < a.e_local; ++el) {
-      const int e = a.me * a.e_local + el;
-      int c = 0;
-      for (int s = 0; s < a.W; ++s) c += cnt[s * a.E + e];
-      grp_off[el] = off; tile_prefix[el] = tiles;
-      off += c; tiles += (c + 127) >> 7;
-    }
-    grp_off[a.e_local] = off; tile_prefix[a.e_local] = tiles;
-    if (shared_rows > 0) { grp_off[a.e_local + 1] = off + shared_rows; tile_prefix[a.e_local + 1] = tiles + ((shared_rows + 127) >> 7); }
-    if (off + shared_rows > a.Rmax) atomicCAS(a.status, 0, PLOW_ERR_BOUNDS | kTagEp);
-  }
+  // layout of this rank's own experts: one thread per expert (exclusive prefix of rows and of 128-row tiles)
   __shared__ int routed_rows;     // rows this rank receives for its routed experts (same value in every CTA)
-  if (threadIdx.x == 0) {
-    int off = 0;
-    for (int el = 0; el < a.e_local; ++el)
-      for (int s = 0; s < a.W; ++s) off += cnt[s * a.E + a.me * a.e_local + el];
-    routed_rows = off;
+  for (int el = threadIdx.x; el <= a.e_local; el += blockDim.x) {
+    int off = 0, tiles = 0;
+    for (int f = 0; f < el; ++f) { const int c = tot[a.me * a.e_local + f]; off += c; tiles += (c + 127) >> 7; }
+    if (el == a.e_local) routed_rows = off;
+    if (blockIdx.x == 0) {
+      grp_off[el] = off; tile_prefix[el] = tiles;
+      if (el == a.e_local) {
+        if (shared_rows > 0) { grp_off[el + 1] = off + shared_rows; tile_prefix[el + 1] = tiles + ((shared_rows + 127) >> 7); }
+        if (off + shared_rows > a.Rmax) atomicCAS(a.status, 0, PLOW_ERR_BOUNDS | kTagEp);
+      }
+    }
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   const int KB = a.H / 128;
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 41);
   if (routed_rows + shared_rows <= a.Rmax) {
     for (int t = blockIdx.x * wpb + warp; t < shared_rows; t += gridDim.x * wpb) {
       const int row = routed_rows + t;
       const uint4* src = reinterpret_cast<const uint4*>(xq + static_cast<size_t>(t) * a.H);
       uint4* dst = reinterpret_cast<uint4*>(a.peer[a.me] + a.L.recv_x + static_cast<size_t>(row) * a.H);
-      for (int i = lane; i < a.H / 16; i += 32) dst[i] = src[i];
+      warp_copy_row(dst, src, a.H / 16, lane);
       float* dsx = reinterpret_cast<float*>(a.peer[a.me] + a.L.recv_sx);
       for (int kb = lane; kb < KB; kb += 32) dsx[static_cast<size_t>(kb) * a.Rmax + row] = sx[static_cast<size_t>(kb) * ld_sx + t];
     }
@@ -166,7 +168,7 @@ __global__ void ep_push_kernel(EpArgs a, const int2* table, int n_pairs, int top
     const int tok = p / top_k;
     const uint4* src = reinterpret_cast<const uint4*>(xq + static_cast<size_t>(tok) * a.H);
     uint4* dst = reinterpret_cast<uint4*>(a.peer[d] + a.L.recv_x + static_cast<size_t>(row) * a.H);
-    for (int i = lane; i < a.H / 16; i += 32) dst[i] = src[i];
+    warp_copy_row(dst, src, a.H / 16, lane);
     float* dsx = reinterpret_cast<float*>(a.peer[d] + a.L.recv_sx);
     for (int kb = lane; kb < KB; kb += 32) dsx[static_cast<size_t>(kb) * a.Rmax + row] = sx[static_cast<size_t>(kb) * ld_sx + tok];
     if (lane == 0) pair_dest[p] = (d << 24) | row;
@@ -176,8 +178,10 @@ __global__ void ep_push_kernel(EpArgs a, const int2* table, int n_pairs, int top
   // CTA's release add is ordered after all of those counts, so an owner that acquires the counter
   // sees every row this rank sent.  (One add per CTA made 256 remote atomics per layer fight with the
   // owner's pollers for one line: 1.3 ms per layer at 8 ranks.)
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 42);
   __threadfence_system();
   __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 43);
   __shared__ int is_last;
   if (threadIdx.x == 0) {
     const int old = atomicAdd(&cursor[a.E], 1);
@@ -204,7 +208,7 @@ __global__ void ep_y_ready_kernel(EpArgs a) {
 // shared_base != NULL: the shared expert ran as the last group of this rank's grouped GEMM; its output row of token t
 // is row *shared_base + t of this rank's own y buffer (`shared` is ignored).
 __global__ void ep_combine_kernel(EpArgs a, __nv_bfloat16* out, const __nv_bfloat16* shared, const int2* table,
-                                  const int* pair_dest, int top_k, const int* shared_base) {
+                                  const int* pair_dest, int top_k, const int* shared_base, int signal_y) {
   plow::pdl_launch_dependents();
   plow::pdl_wait();
   __shared__ int fail;
@@ -212,6 +216,13 @@ __global__ void ep_combine_kernel(EpArgs a, __nv_bfloat16* out, const __nv_bfloa
   __syncthreads();
   const uint32_t ep = *a.epoch;
   if (blockIdx.x == 0 && threadIdx.x == 0) trace_mark(a, 7);
+  if (signal_y && blockIdx.y == 0 && (blockIdx.x & 31) == 0) {
+    // This rank's expert outputs were written by the kernel before this one in the stream: tell every rank they can
+    // be pulled (a few CTAs repeat the same store, so the signal does not hinge on which CTA is scheduled first),
+    // then wait for the others' signals like every other CTA.
+    __threadfence_system();
+    if (threadIdx.x < a.W) st_release_sys(reinterpret_cast<uint32_t*>(a.peer[threadIdx.x] + a.L.y_flag) + a.me * 32, ep);
+  }
   if (threadIdx.x < a.W) {
     if (!wait_ge(reinterpret_cast<const uint32_t*>(a.peer[a.me] + a.L.y_flag) + threadIdx.x * 32, ep, a.deadline_ns)) fail = 1;
   }
@@ -293,7 +304,12 @@ int plow_ep_counts(const void* args, const void* table, int n_pairs, int* cursor
 int plow_ep_push(const void* args, const void* table, int n_pairs, int top_k, const void* xq, const float* sx, int ld_sx,
                  int* cursor, int* grp_off, int* tile_prefix, int* pair_dest, int n_cta, int shared_rows, void* st) {
   const EpArgs& a = *static_cast<const EpArgs*>(args);
-  plow::launch_serial(ep_push_kernel, dim3(n_cta), dim3(256), (a.W + 1) * a.E * 4, reinterpret_cast<cudaStream_t>(st), 
+  // one warp per row when the step is small (decode): the copy is latency-bound, so width beats reuse; n_cta caps it
+  const int rows = n_pairs + shared_rows;
+  int grid = (rows + 7) / 8;
+  if (grid > n_cta) grid = n_cta;
+  if (grid < 1) grid = 1;
+  plow::launch_serial(ep_push_kernel, dim3(grid), dim3(256), (a.W + 2) * a.E * 4, reinterpret_cast<cudaStream_t>(st), 
       a, static_cast<const int2*>(table), n_pairs, top_k, static_cast<const uint8_t*>(xq), sx, ld_sx, cursor, grp_off,
       tile_prefix, pair_dest, shared_rows);
   return ok();
@@ -304,12 +320,12 @@ int plow_ep_y_ready(const void* args, void* st) {
   return ok();
 }
 int plow_ep_combine(const void* args, void* out, const void* shared, const void* table, const int* pair_dest, int T, int top_k,
-                    const int* shared_base, void* st) {
+                    const int* shared_base, int signal_y, void* st) {
   const EpArgs& a = *static_cast<const EpArgs*>(args);
   if (top_k > 16 || a.H % 8) return -1;
   plow::launch_serial(ep_combine_kernel, dim3(T, (a.H / 8 + 255) / 256), dim3(256), 0, reinterpret_cast<cudaStream_t>(st), a, static_cast<__nv_bfloat16*>(out),
                                                                     static_cast<const __nv_bfloat16*>(shared),
-                                                                    static_cast<const int2*>(table), pair_dest, top_k, shared_base);
+                                                                    static_cast<const int2*>(table), pair_dest, top_k, shared_base, signal_y);
   return ok();
 }
 int plow_wait_probe(const void* flag, unsigned int target, unsigned long long deadline_ns, int* status, void* st) {

@@ -15,6 +15,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "ep_args.h"
 #include "launch.cuh"
 
 namespace {
@@ -427,7 +428,7 @@ __global__ void __launch_bounds__(512)
 moe_route_kernel(int2* table, float* logits_out, const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, const float* bias,
                  int T, int H, int E, int k, int n_group, int topk_group, int sigmoid, int norm_topk, float route_scale,
                  int do_align, int e_base, int e_local, int* grp_off, int* tile_prefix, int* row_of_pair, int* pair_of_row,
-                 int shared_rows, int shared_tok_base, unsigned int* ticket) {
+                 int shared_rows, int shared_tok_base, unsigned int* ticket, const plow::EpArgs epa, int use_ep, int* ep_cursor) {
   plow::pdl_launch_dependents();
   plow::pdl_wait();
   extern __shared__ float rsm[];
@@ -503,7 +504,7 @@ moe_route_kernel(int2* table, float* logits_out, const __nv_bfloat16* x, int ldx
   __syncthreads();
   if (warp == 0)
     route_one_token(table, lg, bias, t, E, k, n_group, topk_group, sigmoid, norm_topk, route_scale, score, score + E);
-  if (!do_align) return;
+  if (!do_align && !use_ep) return;
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -513,6 +514,26 @@ moe_route_kernel(int2* table, float* logits_out, const __nv_bfloat16* x, int ldx
   if (!is_last) return;
   __threadfence();
   if (threadIdx.x == 0) *ticket = 0u;       // re-armed for the next launch (stream order separates launches)
+  if (use_ep) {
+    // expert parallelism: this rank's per-expert pair counts go to every peer's count matrix, followed by one release
+    // flag per peer (what the separate counts kernel of csrc/comm/ep.cu does); `cnt` holds E ints here
+    for (int e = threadIdx.x; e < epa.E; e += blockDim.x) { cnt[e] = 0; ep_cursor[e] = 0; }
+    __syncthreads();
+    for (int p = threadIdx.x; p < T * k; p += blockDim.x) atomicAdd(&cnt[__ldcg(&table[p].x)], 1);
+    __syncthreads();
+    const uint32_t epn = *epa.epoch + 1;
+    for (int d = 0; d < epa.W; ++d) {
+      int* dst = reinterpret_cast<int*>(epa.peer[d] + epa.L.cnt_all) + epa.me * epa.E;
+      for (int e = threadIdx.x; e < epa.E; e += blockDim.x) dst[e] = cnt[e];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < epa.W)
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t*>(epa.peer[threadIdx.x] + epa.L.cnt_flag) + epa.me * 32),
+                   "r"(epn) : "memory");
+    if (threadIdx.x == 0) *epa.epoch = epn;
+    return;
+  }
   moe_align_cta(table, T * k, e_base, e_local, grp_off, tile_prefix, row_of_pair, pair_of_row, shared_rows, shared_tok_base, k,
                 cnt);
 }
@@ -760,15 +781,17 @@ int plow_router_topk(void* table, const float* logits, const float* bias, int T,
 int plow_moe_route(void* table, float* logits_out, const void* x, int ldx, const void* w, const float* bias, int T, int H, int E,
                    int k, int n_group, int topk_group, int sigmoid, int norm_topk, float route_scale, int do_align, int e_base,
                    int e_local, int* grp_off, int* tile_prefix, int* row_of_pair, int* pair_of_row, int shared_rows,
-                   int shared_tok_base, void* ticket, void* st) {
+                   int shared_tok_base, void* ticket, const void* ep_args, int* ep_cursor, void* st) {
   if (k > 32 || n_group > 32 || E % (n_group > 0 ? n_group : 1) || H % 8 || (ldx % 8) || T <= 0) return -1;
-  const size_t smem = static_cast<size_t>(H + 3 * E) * 4 + static_cast<size_t>(2 * (do_align ? e_local : 0)) * 4;
+  if (ep_args && (do_align || !ep_cursor)) return -1;
+  const size_t smem = static_cast<size_t>(H + 3 * E) * 4 + static_cast<size_t>(do_align ? 2 * e_local : (ep_args ? E : 0)) * 4;
   if (smem > 200 * 1024) return -2;
   static plow::DeviceOnce attr;
   if (plow::ensure_smem(attr, moe_route_kernel, 200 * 1024) != cudaSuccess) return -3;
   plow::launch_serial(moe_route_kernel, dim3(T), dim3(512), smem, S(st), (int2*)table, logits_out, (const bf16*)x, ldx, (const bf16*)w,
                       bias, T, H, E, k, n_group, topk_group, sigmoid, norm_topk, route_scale, do_align, e_base, e_local, grp_off,
-                      tile_prefix, row_of_pair, pair_of_row, shared_rows, shared_tok_base, (unsigned int*)ticket);
+                      tile_prefix, row_of_pair, pair_of_row, shared_rows, shared_tok_base, (unsigned int*)ticket,
+                      ep_args ? *static_cast<const plow::EpArgs*>(ep_args) : plow::EpArgs{}, ep_args ? 1 : 0, ep_cursor);
   return ok();
 }
 

@@ -40,8 +40,9 @@ def apply_rope(x, tab, pos, rot_dim, pair_mode):
     return torch.cat([out, xp], dim=-1)
 
 
-def causal_attention(q, k, v, scale, window=0):
-    """q [T, nq, hd], k/v [T, nkv, hd(v)] -> [T, nq, hdv]; full causal mask (+ sliding window)."""
+def causal_attention(q, k, v, scale, window=0, keep=None):
+    """q [T, nq, hd], k/v [T, nkv, hd(v)] -> [T, nq, hdv]; full causal mask (+ sliding window).  ``keep`` (bool [T, T],
+    optional): sparse attention, query t attends only the keys s with keep[t, s]."""
     T, nq, _ = q.shape
     nkv = k.shape[1]
     k = k.repeat_interleave(nq // nkv, dim=1)
@@ -49,6 +50,8 @@ def causal_attention(q, k, v, scale, window=0):
     s = torch.einsum("thd,shd->hts", q.float(), k.float()) * scale
     i = torch.arange(T, device=q.device)
     mask = i[None, :] > i[:, None]
+    if keep is not None:
+        mask = mask | ~keep
     if window:
         mask = mask | (i[None, :] <= i[:, None] - window)
     s = s.masked_fill(mask[None], float("-inf"))
@@ -135,8 +138,38 @@ class ReferenceModel:
         kvb = self.lin(c_kv, f"{p}.self_attn.kv_b_proj.weight").view(T, a.n_heads, a.qk_nope + a.v_head)
         k = torch.cat([kvb[..., :a.qk_nope], k_rope.expand(T, a.n_heads, a.qk_rope)], dim=-1)
         v = kvb[..., a.qk_nope:]
-        o = causal_attention(torch.cat([q_nope, q_rope], -1), k, v, qh ** -0.5).reshape(T, -1)
+        keep = self.dsa_select(p, h, qa if a.q_lora else h, pos, a) if a.index_heads else None
+        o = causal_attention(torch.cat([q_nope, q_rope], -1), k, v, qh ** -0.5, keep=keep).reshape(T, -1)
         return self.lin(o, f"{p}.self_attn.o_proj.weight")
+
+    def dsa_scores(self, p, h, q_in, pos, a):
+        """Sparse-attention indexer scores [T, T] (future keys at -inf): index queries of `index_heads` heads from the
+        query latent, one index key per token (LayerNorm with bias, RoPE on the first rot dims, halves pairing), per-head
+        weights from the hidden state; score[t, s] = sum_h w[t, h] relu(q[t, h] . k[s])."""
+        T = h.shape[0]
+        rot = self.spec.rope.rot_dim
+        qi = self.lin(q_in, f"{p}.self_attn.indexer.wq_b.weight").view(T, a.index_heads, a.index_dim)
+        ki = self.lin(h, f"{p}.self_attn.indexer.wk.weight")
+        ki = torch.nn.functional.layer_norm(ki.float(), (a.index_dim,), self.w[f"{p}.self_attn.indexer.k_norm.weight"].float(),
+                                            self.w[f"{p}.self_attn.indexer.k_norm.bias"].float(), 1e-6).to(h.dtype)
+        wt = self.lin(h, f"{p}.self_attn.indexer.weights_proj.weight").float()
+        qi = apply_rope(qi, self.rope, pos, rot, "half")
+        ki = apply_rope(ki.view(T, 1, a.index_dim), self.rope, pos, rot, "half").view(T, a.index_dim)
+        dots = torch.relu(torch.einsum("thd,sd->ths", qi.float(), ki.float()))
+        sc = (wt[:, :, None] * dots).sum(1)
+        i = torch.arange(T, device=h.device)
+        return sc.masked_fill(i[None, :] > i[:, None], float("-inf"))
+
+    def dsa_select(self, p, h, q_in, pos, a):
+        """bool [T, T]: the index_topk best-scoring visible keys of every query (all of them while fewer are visible);
+        ties go to the lower position."""
+        sc = self.dsa_scores(p, h, q_in, pos, a)
+        T = sc.shape[0]
+        k = min(a.index_topk, T)
+        idx = _stable_topk(sc, k)
+        keep = torch.zeros(T, T, dtype=torch.bool, device=sc.device)
+        keep.scatter_(1, idx, True)
+        return keep & torch.isfinite(sc)
 
     def route(self, logits, f, bias=None):
         """Router semantics shared with the kernels (group-limited noaux_tc selection): returns

@@ -117,7 +117,7 @@ _SIGS = {
     "plow_mla_kv_write": "ppppiipppppiiiifip",
     "plow_router_topk": "pppiiiiiiifp",
     "plow_moe_align": "piiippppiiip",
-    "plow_moe_route": "pppipp" "iiiiiiii" "f" "iii" "pppp" "ii" "pp",
+    "plow_moe_route": "pppipp" "iiiiiiii" "f" "iii" "pppp" "ii" "ppp" "p",
     "plow_moe_gather": "ppippipp" "iiip",
     "plow_moe_combine": "pppppiiipp",
     "plow_argmax": "ppiip",
@@ -133,7 +133,7 @@ _SIGS = {
     "plow_ep_counts": "ppipp",
     "plow_ep_push": "ppiippippppiip",
     "plow_ep_y_ready": "pp",
-    "plow_ep_combine": "pppppiipp",
+    "plow_ep_combine": "pppppiipip",
     "plow_wait_probe": "piLpp",
     "plow_ag_push": "pLLppiipiiip",
     "plow_interp_run": "ppppppppppp" "IIIIp",

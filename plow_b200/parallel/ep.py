@@ -42,7 +42,7 @@ def _align(x, a=256):
 
 
 class EpComm:
-    def __init__(self, rank: int, world: int, spec, max_rows: int, impl: str = "fused", deadline_ms: int = 2000, n_cta: int = 32):
+    def __init__(self, rank: int, world: int, spec, max_rows: int, impl: str = "fused", deadline_ms: int = 2000, n_cta: int = 148):
         self.rank, self.world, self.impl = rank, world, impl
         self.dev = torch.device("cuda", torch.cuda.current_device())
         moe = next(l.ffn for l in spec.layers if l.ffn.kind == "moe")
@@ -90,9 +90,10 @@ class EpComm:
         self.data_ctr_ptr = self.buf.data_ptr() + lay["data_ctr"]
 
     # ---- fused arm -----------------------------------------------------------------------------
-    def dispatch(self, eng, st, ins):
+    def dispatch(self, eng, st, ins, counts_done=False):
         """Counts + push for the MoE instruction `ins`; called as soon as the routing table exists so
-        the transfer overlaps the shared-expert GEMMs that sit between router and experts."""
+        the transfer overlaps the shared-expert GEMMs that sit between router and experts.  ``counts_done``: the fused
+        routing kernel already published this rank's counts (its last CTA does what the counts kernel does)."""
         if self.impl != "fused":
             return
         h, table = eng.tensor(st, ins.t[1]), eng.tensor(st, ins.t[2])
@@ -100,12 +101,16 @@ class EpComm:
         xq, sx = eng._quant_of(st, ins.t[1], 0, H, h)
         ap = C.addressof(self.args)
         self._mark("t0")
-        native.call("plow_ep_counts", ap, table, T * k, self.cursor)
+        if not counts_done:
+            native.call("plow_ep_counts", ap, table, T * k, self.cursor)
         self._mark("counts")
         native.call("plow_ep_push", ap, table, T * k, k, xq, sx, sx.stride(0), self.cursor, self.grp_off, self.tile_prefix,
                     self.pair_dest, self.n_cta, T if ins.i[6] else 0)
         self._mark("push")
         st.scratch["ep_dispatched"] = ins.i[7]
+
+    def args_ptr(self) -> int:
+        return C.addressof(self.args)
 
     def device_trace(self, on: bool):
         """Debug aid: device-side (tag, globaltimer) marks of the EP kernels.  Only effective for eager launches
@@ -169,9 +174,8 @@ class EpComm:
             hq, shq = rowops.quant_act(hb)
             gemm_ops.gemm(hq, w2, sx=shq, sw=s2, n_out=H, n_experts=ng, grp_off=self.grp_off,
                           tile_prefix=self.tile_prefix, swap=False, bn=128, out=ry)
-        native.call("plow_ep_y_ready", ap)
-        self._mark("y_ready")
-        native.call("plow_ep_combine", ap, y_out, shared, table, self.pair_dest, T, k, self.grp_off[self.e_local:] if sg else None)
+        # the combine kernel first signals that this rank's outputs can be pulled, then waits for the other ranks' signals
+        native.call("plow_ep_combine", ap, y_out, shared, table, self.pair_dest, T, k, self.grp_off[self.e_local:] if sg else None, 1)
         self._mark("combine")
 
     # ---- NCCL baseline arm ---------------------------------------------------------------------

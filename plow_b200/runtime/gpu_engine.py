@@ -696,9 +696,14 @@ class GpuEngine(EngineBase):
                 st.scratch[("aligned", id(moe))] = True
             if self._route_ticket is None:
                 self._route_ticket = torch.zeros(1, dtype=I32, device=self.device)
+            ep_fused = moe is not None and not local and getattr(self.comm, "impl", None) == "fused" and self.ep > 1
             native.call("plow_moe_route", table, None, x, x.stride(0), w, bias, st.rows, g.i[1], ins.i[0], ins.i[1], max(1, ins.i[2]),
                         max(1, ins.i[3]), ins.i[4], ins.i[5], float(ins.f[0]), int(local), e_base, e_local, al[0], al[1], al[2], al[3],
-                        shared_rows, 0, self._route_ticket)
+                        shared_rows, 0, self._route_ticket, self.comm.args_ptr() if ep_fused else None,
+                        self.comm.cursor if ep_fused else None)
+            if ep_fused:
+                self.comm.dispatch(self, st, moe, counts_done=True)
+                return
         else:
             native.call("plow_router_topk", table, logits, bias, st.rows, ins.i[0], ins.i[1], max(1, ins.i[2]), max(1, ins.i[3]),
                         ins.i[4], ins.i[5], float(ins.f[0]))

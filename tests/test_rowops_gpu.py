@@ -148,7 +148,7 @@ def test_moe_route_fused_matches_gemm_topk_align(E, k, ng, tg, sig, shared):
             ticket = torch.zeros(1, dtype=torch.int32, device="cuda")
             test_moe_route_fused_matches_gemm_topk_align._ticket = ticket
         native.call("plow_moe_route", table, lg, x, x.stride(0), w, bias, T, H, E, k, ng, tg, int(sig), 1, 2.5, 1, 0, E,
-                    grp_off, tile_prefix, row_of_pair, pair_of_row, T if shared else 0, 0, ticket)
+                    grp_off, tile_prefix, row_of_pair, pair_of_row, T if shared else 0, 0, ticket, None, None)
         torch.cuda.synchronize()
         native.check_status()
         assert int(ticket[0]) == 0
