@@ -172,7 +172,7 @@ def _linear(g: Graph, li, x, wname, n_out, k_in, shard_axis=None, rows=R, **attr
     n_l = n_out // tp if shard_axis == 0 else n_out
     k_l = k_in // tp if shard_axis == 1 else k_in
     w = g.weight(wname, (n_l, k_l), shard_axis=shard_axis)
-    y = g.tmp("y", (rows, n_l))
+    y = g.tmp("y", (rows, n_l), "f32" if attrs.get("out_f32") else None)     # the arena slot must match what the GEMM writes
     g.add("linear", [x, w], [y], layer=li, **attrs)
     return y
 

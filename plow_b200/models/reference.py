@@ -66,6 +66,8 @@ class ReferenceModel:
     def __init__(self, spec: ModelSpec, state: dict, device="cpu", dtype=torch.float32):
         self.spec = spec
         self.w = {k: v.to(device=device, dtype=dtype if v.is_floating_point() else v.dtype) for k, v in state.items()}
+        self.dsa_override: dict = {}      # layer prefix -> bool [T, T] selection to attend instead of the indexer's own
+        self.dsa_last: dict = {}          # layer prefix -> the selection the last forward attended
         self.device, self.dtype = device, dtype
         r = spec.rope
         self.rope = torch.from_numpy(rope_table(min(r.max_pos, 1 << 17), r.rot_dim, r.theta, r.scaling)).to(device)
@@ -138,7 +140,12 @@ class ReferenceModel:
         kvb = self.lin(c_kv, f"{p}.self_attn.kv_b_proj.weight").view(T, a.n_heads, a.qk_nope + a.v_head)
         k = torch.cat([kvb[..., :a.qk_nope], k_rope.expand(T, a.n_heads, a.qk_rope)], dim=-1)
         v = kvb[..., a.qk_nope:]
-        keep = self.dsa_select(p, h, qa if a.q_lora else h, pos, a) if a.index_heads else None
+        keep = None
+        if a.index_heads:
+            keep = self.dsa_override.get(p) if self.dsa_override else None      # tests: attend a given selection
+            if keep is None:
+                keep = self.dsa_select(p, h, qa if a.q_lora else h, pos, a)
+            self.dsa_last[p] = keep
         o = causal_attention(torch.cat([q_nope, q_rope], -1), k, v, qh ** -0.5, keep=keep).reshape(T, -1)
         return self.lin(o, f"{p}.self_attn.o_proj.weight")
 

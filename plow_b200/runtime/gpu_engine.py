@@ -174,6 +174,7 @@ class GpuEngine(EngineBase):
         self.step_ms_last = 0.0
         self.launches_last = 0
         self.profile_ops = os.environ.get("PLOW_PROFILE_OPS") == "1"     # per-instruction device times of eager steps
+        self.taps: dict | None = None      # when a dict: copies of selected intermediates of eager steps, keyed (name, layer)
         self.op_times_last: list = []
 
     # ---- static tensors ------------------------------------------------------------------------
@@ -245,6 +246,7 @@ class GpuEngine(EngineBase):
         self._route_ticket = None
         self._mla_plan_rows = 0
         self._has_mla = any(l.attn.kind == "mla" for l in self.spec.layers)
+        self._dsa_topk = max((l.attn.index_topk for l in self.spec.layers if l.attn.index_heads), default=0)
         self.h_plan = torch.zeros(2 * max_rows + 4 * n_slots, dtype=I32).pin_memory()
         self.d_plan = torch.zeros(2 * max_rows + 4 * n_slots, dtype=I32, device=dev)
 
@@ -534,7 +536,10 @@ class GpuEngine(EngineBase):
         if nope != 128 or v_head != 128:
             raise EngineError("the fused MLA projection kernels are specialised for 128 nope / 128 v dims")
         plan = self._mla_plan
-        if plan is not None and (plan["R"] != T or (bool(ins.i[6]) and ins.t[7] != pk.T_NONE and T <= self.SPARSE_MAX_ROWS)):
+        # sparse attention applies unless this (eager) step's positions all lie below top_k, where the indexer would
+        # select every key anyway and the dense forms compute the same thing for less
+        sparse = bool(ins.i[6]) and ins.t[7] != pk.T_NONE and not st.scratch.get("dsa_dense_ok", False)
+        if plan is not None and (plan["R"] != T or sparse):
             plan = None
         kvlen_dense = self.d_kvlen_row if plan is None else plan["kvlen"]
         if plan is not None and not plan["riders"]:
@@ -546,7 +551,9 @@ class GpuEngine(EngineBase):
                 st.q[(ins.t[0], 0)] = rowops.quant_act(ao)
             return
         wuk_t, wuv = self._mla_prep(layer, ins.t[4], heads, kv_lora, nope, v_head)
-        q8, sq = mla_ops.absorb(q, wuk_t, rope, self.d_in[1], heads, pair)
+        blockwise = sparse and T > self.SPARSE_MAX_ROWS
+        if not blockwise:
+            q8, sq = mla_ops.absorb(q, wuk_t, rope, self.d_in[1], heads, pair)
         if self._mla_ws is None or self._mla_ws.opart.shape[0] < T:
             # up to 8 splits per request (the fold kernel's limit); a request's tiles are dealt evenly over its splits
             max_tiles = (self.max_ctx + PAGE + 63) // 64
@@ -554,11 +561,31 @@ class GpuEngine(EngineBase):
                                                    device=self.device)
         if self._mla_ws.max_splits > 8:
             raise EngineError("max_ctx needs more than 8 KV splits; raise tiles_per_split")
-        sparse = bool(ins.i[6]) and ins.t[7] != pk.T_NONE and T <= self.SPARSE_MAX_ROWS
+        if blockwise:
+            # large prefill buckets: the same select -> gather -> decode -> fold chain, one block of rows at a time (the
+            # compact cache holds top_k tokens per row, so its size is bounded by the block, not by the bucket)
+            sel_all = self.tensor(st, ins.t[7])
+            top_k, B = sel_all.shape[1], self.SPARSE_MAX_ROWS
+            key = ("dsa_cc", B, top_k)
+            if key not in st.scratch:
+                st.scratch[key] = dsa_ops.CompactCache(B, top_k, cache.shape[2], self.device)
+            cc = st.scratch[key]
+            pos_d, seq_d = self.d_in[1], self.d_in[2]
+            for r0 in range(0, T, B):
+                r1 = min(T, r0 + B)
+                n = r1 - r0
+                q8b, sqb = mla_ops.absorb(q[r0:r1], wuk_t, rope, pos_d[r0:r1], heads, pair)
+                dsa_ops.gather(cc, sel_all[r0:r1], cache, scale, pos_d[r0:r1], seq_d[r0:r1], self.d_page_table)
+                mla_ops.decode(q8b, sqb, cc.kv, cc.scale, cc.smax, cc.page_table[:n], cc.slot_of[:n], cc.kvlen[:n], self._mla_ws,
+                               float(ins.f[0]), merge=False)
+                mla_ops.fold(self._mla_ws, cc.kvlen[:n], wuv, n, heads, ao[r0:r1], want_fp8=False)
+            st.scratch["mla_items"] = False
+            if self._wants_q(st, ins.t[0]):
+                st.q[(ins.t[0], 0)] = rowops.quant_act(ao)
+            return
         if sparse:
             # sparse attention: the indexer's selection is gathered into a compact per-row cache and the same decode
-            # kernel walks it (reference: runtime/nvidia/op_dsa.cuh, crates/devgen/src/mla.rs:7093).  Programs with more
-            # rows than SPARSE_MAX_ROWS (large prefill buckets) attend densely.
+            # kernel walks it (reference: runtime/nvidia/op_dsa.cuh, crates/devgen/src/mla.rs:7093)
             top_k = self.tensor(st, ins.t[7]).shape[1]
             key = ("dsa_cc", T, top_k)
             if key not in st.scratch:
@@ -663,13 +690,20 @@ class GpuEngine(EngineBase):
 
     def _op_dsa_topk(self, st, ins):
         sel, qi, wts, kcache, ksc, rope = (self.tensor(st, ins.t[k]) for k in range(6))
-        if st.rows > self.SPARSE_MAX_ROWS:
-            return                      # the attention of this program runs densely and does not read the selection
-        key = ("dsa_ws", st.rows)
+        if st.scratch.get("dsa_dense_ok", False):
+            return                      # every position is below top_k: the attention of this step runs densely
+        B = min(st.rows, self.SPARSE_MAX_ROWS)
+        key = ("dsa_ws", B)
         if key not in st.scratch:
-            st.scratch[key] = dsa_ops.SelectWorkspace(st.rows, self.max_ctx + PAGE, self.device)
-        dsa_ops.select(qi, wts, kcache, ksc, rope, self.d_in[1], self.d_in[2], self.d_page_table, ins.i[2], st.scratch[key],
-                       ins.i[3], out=sel)
+            st.scratch[key] = dsa_ops.SelectWorkspace(B, self.max_ctx + PAGE, self.device)
+        for r0 in range(0, st.rows, B):
+            r1 = min(st.rows, r0 + B)
+            dsa_ops.select(qi[r0:r1], wts[r0:r1], kcache, ksc, rope, self.d_in[1][r0:r1], self.d_in[2][r0:r1], self.d_page_table,
+                           ins.i[2], st.scratch[key], ins.i[3], out=sel[r0:r1])
+        if self.taps is not None and not torch.cuda.is_current_stream_capturing():
+            # eager steps only (run with cuda_graphs=False to tap decode): the selection and what it was computed from
+            self.taps[("dsa_sel", ins.i[7])] = sel.clone()
+            self.taps[("dsa_in", ins.i[7])] = (qi.clone(), wts.clone(), kcache, ksc, rope, ins.i[3])
 
     # -- MoE
     def _op_router_topk(self, st, ins):
@@ -931,6 +965,8 @@ class GpuEngine(EngineBase):
         self.d_in[:, :R].copy_(hin[:, :R], non_blocking=True)
         torch.add(self.d_in[1, :R], 1, out=self.d_kvlen_row[:R])
         self._mla_plan = None
+        # eager (prefill) steps of a sparse-attention model whose positions all lie below top_k attend densely
+        st.scratch["dsa_dense_ok"] = bool(not decode and self._dsa_topk and rows > 0 and int(batch.pos.max()) < self._dsa_topk)
         if not decode and rows > 0 and self._has_mla:
             self._mla_plan = self._plan_mla_prefill(batch, R)
             self._mla_plan_rows = rows
