@@ -18,7 +18,8 @@
 
 namespace plow {
 
-constexpr int kProjThreads = 160;   // warp 0: TMA + MMA issue, warps 1-4: one TMEM lane quarter each
+constexpr int kProjThreads = 160;
+constexpr int kFoldSplits = 16;   // KV splits per request the fold kernel merges at most   // warp 0: TMA + MMA issue, warps 1-4: one TMEM lane quarter each
 
 struct AbsorbArgs {
   const __nv_bfloat16* q;    // [T][q_pitch]
@@ -217,31 +218,33 @@ mla_fold_kernel(const FoldArgs a, const __grid_constant__ CUtensorMap tm_w) {
     const uint32_t lane_addr = static_cast<uint32_t>(lq * 32) << 16;
     pdl_wait();      // partials and log-sum-exps come from the attention kernel (warp 0 only touches W_uv, a weight)
     // merge weights of this (token, head), shared with the other merge warps through shared memory
-    float* wsm = reinterpret_cast<float*>(smem + 131072 + 256);       // [128 rows][8 splits]
-    int* nsm = reinterpret_cast<int*>(wsm + 128 * 8);                 // [128 rows]
+    float* wsm = reinterpret_cast<float*>(smem + 131072 + 256);       // [128 rows][kFoldSplits]
+    int* nsm = reinterpret_cast<int*>(wsm + 128 * kFoldSplits);       // [128 rows]
     {
-      float wgt[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      float wgt[kFoldSplits];
+#pragma unroll
+      for (int s = 0; s < kFoldSplits; ++s) wgt[s] = 0.f;
       int ns = 0;
       if (live) {
         const int tiles = (a.kvlen[t] + 63) / 64;
         int per_unused;
         ns = kv_splits(tiles, a.tiles_per_split, a.max_splits, &per_unused);
-        if (ns > 8) ns = 8;
-        float l8[8];
+        if (ns > kFoldSplits) ns = kFoldSplits;
+        float ls[kFoldSplits];
 #pragma unroll
-        for (int s = 0; s < 8; ++s) l8[s] = s < ns ? a.lse[(static_cast<size_t>(t) * a.max_splits + s) * a.heads + h] : -INFINITY;
+        for (int s = 0; s < kFoldSplits; ++s) ls[s] = s < ns ? a.lse[(static_cast<size_t>(t) * a.max_splits + s) * a.heads + h] : -INFINITY;
         float mx = -INFINITY;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) mx = fmaxf(mx, l8[s]);
+        for (int s = 0; s < kFoldSplits; ++s) mx = fmaxf(mx, ls[s]);
         float sum = 0.f;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) { wgt[s] = s < ns ? exp2f(l8[s] - mx) : 0.f; sum += wgt[s]; }
+        for (int s = 0; s < kFoldSplits; ++s) { wgt[s] = s < ns ? exp2f(ls[s] - mx) : 0.f; sum += wgt[s]; }
         const float inv = sum > 0.f ? 1.0f / sum : 0.f;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) wgt[s] *= inv;
+        for (int s = 0; s < kFoldSplits; ++s) wgt[s] *= inv;
       }
 #pragma unroll
-      for (int s = 0; s < 8; ++s) wsm[li * 8 + s] = wgt[s];
+      for (int s = 0; s < kFoldSplits; ++s) wsm[li * kFoldSplits + s] = wgt[s];
       nsm[li] = ns;
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -279,7 +282,7 @@ mla_fold_kernel(const FoldArgs a, const __grid_constant__ CUtensorMap tm_w) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int row = lq + 4 * (kb + i);
-            const float wv = wsm[(row & 127) * 8 + sp];
+            const float wv = wsm[(row & 127) * kFoldSplits + sp];
             const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
 #pragma unroll
             for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(hh[j]); acc[i][2 * j] += wv * f.x; acc[i][2 * j + 1] += wv * f.y; }
@@ -377,11 +380,11 @@ int plow_mla_absorb(const void* q, int q_pitch, const void* wuk_t, const float* 
 int plow_mla_fold(const void* opart, const float* lse, const int* kvlen, const void* wuv, void* ao, void* aq, float* saq, int ld_saq,
                   int T, int heads, int max_splits, int tiles_per_split, int* status, void* stream_) {
   using namespace plow;
-  if (max_splits > 8) return -1;
+  if (max_splits > kFoldSplits) return -1;
   CUtensorMap tw;
   int r = make_tmap_2d(&tw, wuv, 2, static_cast<uint64_t>(heads) * 128, 512, 1024, 128);
   if (r) return 1000 + r;
-  const int smem = 1024 + 131072 + 256 + 128 * 8 * 4 + 128 * 4;
+  const int smem = 1024 + 131072 + 256 + 128 * kFoldSplits * 4 + 128 * 4;
   static DeviceOnce attr;
   if (ensure_smem(attr, mla_fold_kernel, smem) != cudaSuccess) return 3000;
   FoldArgs a;

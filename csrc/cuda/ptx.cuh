@@ -38,7 +38,7 @@ enum : int {
 // The status word also names the kernel family that reported: code | (family << 8).
 enum : int {
   kTagGemm = 1 << 8, kTagMlaDecode = 2 << 8, kTagMlaProj = 3 << 8, kTagGqa = 4 << 8, kTagDsa = 5 << 8, kTagEp = 6 << 8,
-  kTagAg = 7 << 8, kTagGdn = 8 << 8, kTagInterp = 9 << 8,
+  kTagAg = 7 << 8, kTagGdn = 8 << 8, kTagInterp = 9 << 8, kTagTpAr = 10 << 8,
 };
 
 constexpr unsigned long long kWaitDeadlineNs = 2000000000ull;  // 2 s for on-chip waits

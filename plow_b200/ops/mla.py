@@ -15,6 +15,7 @@ import torch
 from . import native
 
 BF16, FP8 = torch.bfloat16, torch.float8_e4m3fn
+MAX_SPLITS = 16          # KV splits per request the fold / merge kernels handle (kFoldSplits in csrc/cuda/mla_proj.cu)
 
 
 def q_prep(q, rope_tab, pos, heads, nope, rope, pair_mode=1):

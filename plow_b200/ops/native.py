@@ -91,7 +91,7 @@ STATUS_NAMES = {
 
 
 KERNEL_FAMILIES = {0: "?", 1: "gemm", 2: "mla_decode", 3: "mla_absorb/fold", 4: "gqa_attention", 5: "dsa", 6: "ep dispatch/combine",
-                   7: "all-gather push", 8: "gdn", 9: "interpreter"}
+                   7: "all-gather push", 8: "gdn", 9: "interpreter", 10: "tp all-reduce + norm"}
 
 
 def check_status(device=None) -> None:
@@ -136,6 +136,7 @@ _SIGS = {
     "plow_ep_combine": "pppppiipip",
     "plow_wait_probe": "piLpp",
     "plow_ag_push": "pLLppiipiiip",
+    "plow_tp_allreduce_norm": "pLLLp" "iii" "pipppp" "iifiipp",
     "plow_interp_run": "ppppppppppp" "IIIIp",
     "plow_sample": "ppiiipppppp" "Lp",
     "plow_dsa_k_write": "pppipppppp" "iiiifp",

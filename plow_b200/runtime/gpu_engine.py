@@ -555,12 +555,13 @@ class GpuEngine(EngineBase):
         if not blockwise:
             q8, sq = mla_ops.absorb(q, wuk_t, rope, self.d_in[1], heads, pair)
         if self._mla_ws is None or self._mla_ws.opart.shape[0] < T:
-            # up to 8 splits per request (the fold kernel's limit); a request's tiles are dealt evenly over its splits
+            # up to 16 splits per request (the fold kernel's limit); a request's tiles are dealt evenly over its splits
             max_tiles = (self.max_ctx + PAGE + 63) // 64
-            self._mla_ws = mla_ops.DecodeWorkspace(max(T, self.max_rows_all), self.max_ctx + PAGE, tiles_per_split=max(int(os.environ.get('PLOW_MLA_TPS', '32')), -(-max_tiles // 8)),
+            self._mla_ws = mla_ops.DecodeWorkspace(max(T, self.max_rows_all), self.max_ctx + PAGE,
+                                                   tiles_per_split=max(int(os.environ.get('PLOW_MLA_TPS', '32')), -(-max_tiles // mla_ops.MAX_SPLITS)),
                                                    device=self.device)
-        if self._mla_ws.max_splits > 8:
-            raise EngineError("max_ctx needs more than 8 KV splits; raise tiles_per_split")
+        if self._mla_ws.max_splits > mla_ops.MAX_SPLITS:
+            raise EngineError(f"max_ctx needs more than {mla_ops.MAX_SPLITS} KV splits; raise tiles_per_split")
         if blockwise:
             # large prefill buckets: the same select -> gather -> decode -> fold chain, one block of rows at a time (the
             # compact cache holds top_k tokens per row, so its size is bounded by the block, not by the bucket)
@@ -641,7 +642,14 @@ class GpuEngine(EngineBase):
     def _ext_xreduce_add_norm(self, st, ins):
         # emitted when the GEMM -> all-reduce fusion is disabled at compile time: reduce the partial in place, then the
         # same residual + RMSNorm row kernel as ADD_NORM (same operand order: h_out, x_in, partial, gamma, x_out)
-        self._need_tp().all_reduce(self.tensor(st, ins.t[2]))
+        tp = self._need_tp()
+        h_out, x_in, part, g, x_out = (self.tensor(st, ins.t[k]) for k in range(5))
+        if tp._ar_fits(part) and g is not None and g.dtype == BF16 and x_in.is_contiguous() and x_out.is_contiguous():
+            # one kernel over peer memory: all-reduce of the partial, residual add and RMSNorm (csrc/comm/tp_ar.cu); the
+            # e4m3 twin of the normalised rows, when a consumer wants one, is made on demand
+            tp.allreduce_add_norm(part, x_in, g, x_out, h_out, float(ins.f[0]), bool(ins.i[1]))
+            return
+        tp.all_reduce(part)
         self._op_add_norm(st, ins)
 
     # -- GQA

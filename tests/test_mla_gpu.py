@@ -128,10 +128,11 @@ def test_absorb_and_fold_fused_kernels():
     full = torch.cat([qabs, qrope], -1)
     assert _rel(sq, full.abs().amax(-1) / 448) < 5e-3
     assert _rel(q8.float() * sq[..., None], full) < 4e-2
-    # fold: 3 requests with 1, 2 and 3 splits
-    lens = [100, 40 * 64, 70 * 64 + 5]
+    # fold: requests with 1, 2, 3 and 13 splits (the kernel merges up to 16)
+    lens = [100, 40 * 64, 70 * 64 + 5, 400 * 64 + 9]
     T2 = len(lens)
-    ws = mla.DecodeWorkspace(T2, 8192, tiles_per_split=32)
+    ws = mla.DecodeWorkspace(T2, 32768, tiles_per_split=32)
+    assert ws.max_splits == 16
     ws.opart.copy_(torch.randn_like(ws.opart.float()).bfloat16())
     ws.lse.copy_(torch.randn_like(ws.lse) * 3)
     kvlen = torch.tensor(lens, dtype=torch.int32, device="cuda")
@@ -140,7 +141,9 @@ def test_absorb_and_fold_fused_kernels():
     aq, saq = mla.fold(ws, kvlen, wuv, T2, H, ao, want_fp8=True)
     native.check_status()
     for t, n in enumerate(lens):
-        ns = min(ws.max_splits, -(-((n + 63) // 64) // 32))
+        tiles = (n + 63) // 64
+        ns = min(ws.max_splits, -(-tiles // 32))
+        ns = -(-tiles // (-(-tiles // ns)))          # tiles are dealt evenly: the last split may vanish
         w = torch.softmax(ws.lse[t, :ns].float() * 0.6931471805599453, 0)          # 2^lse weights
         merged = (w[:, :, None] * ws.opart[t, :ns].float()).sum(0).bfloat16().float()   # [heads, 512]
         ref = torch.einsum("hc,hvc->hv", merged, wuv.view(H, 128, 512).float()).reshape(-1)
