@@ -69,7 +69,10 @@ def test_engine_matches_reference(mla_assets):
         want = ref.forward(torch.tensor(p))[-1]
         got = torch.from_numpy(res.logits[s])
         rel = ((got - want).norm() / want.norm()).item()
-        assert rel < 0.12, (s, rel)
+        # measured 0.040-0.042 (e4m3 activations, weights and latent cache against fp32 activations over the same rounded
+        # weights); the greedy token must be the reference's
+        assert rel < 0.06, (s, rel)
+        assert int(got.argmax()) == int(want.argmax())
         eng.commit(s, p)
     # decode two steps for both sequences (CUDA graph path), feeding the reference's greedy tokens
     cur = [list(p) for p in prompts]
@@ -84,7 +87,8 @@ def test_engine_matches_reference(mla_assets):
             eng.commit(s, [nxt[s]])
             want = ref.forward(torch.tensor(cur[s]))[-1]
             got = torch.from_numpy(r.logits[s])
-            assert ((got - want).norm() / want.norm()).item() < 0.12
+            assert ((got - want).norm() / want.norm()).item() < 0.06
+            assert int(got.argmax()) == int(want.argmax())
 
 
 def test_dsa_model_identity_selection_matches_dense_reference(tmp_path):
