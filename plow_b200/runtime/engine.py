@@ -194,6 +194,18 @@ class EngineBase:
     def step(self, batch: TokenBatch) -> StepResult:   # pragma: no cover - interface
         raise NotImplementedError
 
+    def step_multi(self, batch: TokenBatch, k: int) -> list:
+        """k greedy decode steps of the same rows in one call: step i feeds the arg-max tokens of step i - 1 at the next
+        position (the caller has reserved k more tokens per sequence and commits afterwards).  Returns the k
+        StepResults.  This default is a host loop; the sm_100a engine chains the steps on the device
+        (reference: crates/plowrt/src/exec/gpu.rs:10317, multi_step)."""
+        out, ids = [], batch.ids
+        for i in range(k):
+            r = self.step(TokenBatch(ids, batch.pos + i, batch.seq, batch.sample_rows, decode=True))
+            out.append(r)
+            ids = np.asarray(r.ids, dtype=np.int32)
+        return out
+
     def bind_thread(self) -> None:
         """Called by a thread before it drives the engine (the current CUDA device is per host thread)."""
 

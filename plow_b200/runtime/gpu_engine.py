@@ -244,6 +244,7 @@ class GpuEngine(EngineBase):
         self._mla_pf_ws = None
         self._mla_plan = None
         self._route_ticket = None
+        self._multi_out = self._h_multi_out = None
         self._mla_plan_rows = 0
         self._has_mla = any(l.attn.kind == "mla" for l in self.spec.layers)
         self._dsa_topk = max((l.attn.index_topk for l in self.spec.layers if l.attn.index_heads), default=0)
@@ -883,6 +884,57 @@ class GpuEngine(EngineBase):
             fn(st, ins)
         else:
             getattr(self, name)(st, ins)
+
+    def step_multi(self, batch: TokenBatch, k: int) -> list:
+        """k greedy decode steps chained on the device: after each graph replay the sampled ids become the next step's
+        input ids and the positions advance by one (three small device ops), and the host reads all k rows of ids
+        once at the end.  Falls back to the host loop while the rung's graph is not captured yet, under a rank group,
+        or when logits are wanted."""
+        rows = batch.rows
+        st = self.progs.get(self.pick_program(max(rows, 1), True)) if batch.decode else None
+        if (k <= 1 or not batch.decode or st is None or st.graph is None or not self.cuda_graphs or batch.want_logits
+                or self.step_group is not None or self.leader_group is not None or int(batch.sample_rows.shape[0]) != rows
+                or not np.array_equal(batch.sample_rows, np.arange(rows, dtype=batch.sample_rows.dtype))):
+            return super().step_multi(batch, k)
+        R = st.rows
+        hin = self.h_in
+        hin[0, :rows] = torch.from_numpy(batch.ids)
+        hin[1, :rows] = torch.from_numpy(batch.pos)
+        hin[2, :rows] = torch.from_numpy(batch.seq)
+        hin[0, rows:R] = 0
+        hin[1, rows:R] = 0
+        hin[2, rows:R] = self.scratch_slot
+        hin[3, :rows] = torch.from_numpy(batch.sample_rows)
+        hin[3, rows:st.samples] = 0
+        if self._multi_out is None or self._multi_out.shape[0] < k or self._multi_out.shape[1] < st.samples:
+            self._multi_out = torch.zeros(max(k, 8), self.d_out_ids.shape[0], dtype=I32, device=self.device)
+            self._h_multi_out = torch.zeros(max(k, 8), self.d_out_ids.shape[0], dtype=I32).pin_memory()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        self._upload_pages()
+        self.d_in[:, :R].copy_(hin[:, :R], non_blocking=True)
+        torch.add(self.d_in[1, :R], 1, out=self.d_kvlen_row[:R])
+        self._mla_plan = None
+        st.scratch["dsa_dense_ok"] = False
+        try:
+            for i in range(k):
+                st.graph.replay()
+                self._multi_out[i, :rows].copy_(self.d_out_ids[:rows])
+                if i + 1 < k:
+                    self.d_in[0, :rows].copy_(self.d_out_ids[:rows])
+                    self.d_in[1, :rows].add_(1)
+                    self.d_kvlen_row[:rows].add_(1)
+            self._h_multi_out[:k, :rows].copy_(self._multi_out[:k, :rows], non_blocking=True)
+            ev1.record()
+            ev1.synchronize()
+            native.check_status(self.device)
+        except native.NativeLibraryError as e:
+            self._recover_after_device_status()
+            raise EngineError(str(e), fatal=False)
+        ms = ev0.elapsed_time(ev1)
+        self.step_ms_last = ms / k
+        ids = self._h_multi_out[:k, :rows].numpy().copy()
+        return [StepResult(ids=ids[i], logits=None, device_ms=ms / k) for i in range(k)]
 
     def kv_arrays(self) -> dict:
         out = {t.name: self.static[h] for h, t in enumerate(self.packet.tensors) if t.tclass == pk.TClass.KV}

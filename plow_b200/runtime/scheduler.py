@@ -105,6 +105,7 @@ class SchedConfig:
     reserve_tokens: int = PAGE        # KV head-room required per live sequence before seating more
     ride: bool = True                 # decode rows ride the prefill launch (mixed step) instead of waiting a tick
     spec_depth: int = 0               # > 0: speculative decoding for greedy requests (prompt-lookup drafts, span verify)
+    multi_step: int = 1               # > 1: greedy decode ticks run this many steps per engine call (tokens fed back on the device)
     session_ttl_s: float = 600.0      # a finished request that carried a session id keeps its slot and KV this long
     max_sessions: int = -1            # retained sessions at most (-1: half of the slots; 0: retention off)
 
@@ -655,11 +656,52 @@ class ModelMux:
         seq = np.array([r.slot for r in reqs], dtype=np.int32)
         want_logits = any(not r.params.greedy for r in reqs)
         batch = TokenBatch(ids, pos, seq, np.arange(len(reqs), dtype=np.int32), decode=True, want_logits=want_logits)
+        k = self._multi_step_depth(reqs)
+        if k > 1:
+            # several steps per engine call: the engine feeds each step's arg-max tokens to the next one, the host
+            # sees them afterwards.  A request that stops early simply drops the tokens computed past its stop.
+            results = eng.step_multi(batch, k)
+            self.metrics.inc("decode_ticks", k)
+            self.metrics.inc("multi_step_calls")
+            fed = ids
+            for res in results:
+                for j, r in enumerate(reqs):
+                    if r.slot in self.live and self.live[r.slot] is r:
+                        eng.commit(r.slot, [int(fed[j])])
+                        self._produce(r, int(res.ids[j]), None)
+                fed = res.ids
+            return
         res = eng.step(batch)
         self.metrics.inc("decode_ticks")
         for k, r in enumerate(reqs):
             eng.commit(r.slot, [int(ids[k])])
             self._produce(r, int(res.ids[k]), res.logits[k] if res.logits is not None else None)
+
+    def _multi_step_depth(self, reqs: list) -> int:
+        """How many decode steps the next engine call may chain: only plain greedy requests (no logprobs, penalties,
+        stop strings or guided output, whose next token the host decides), nobody waiting to be admitted or prefilled
+        (a chained call delays them by its whole length), and no more steps than the shortest remaining budget."""
+        k = self.cfg.multi_step
+        eng = self.engine
+        if k <= 1 or self.waiting or not self.ingress.empty() or getattr(eng, "step_group", None) is not None \
+                or getattr(eng, "leader_group", None) is not None:
+            return 1
+        if any(q.done_prefill < q.pf_len for q in self.live.values()):
+            return 1
+        for r in reqs:
+            p = r.params
+            if not p.greedy or p.stop or p.json_mode:
+                return 1
+            n_ctx = len(r.prompt) + len(r.generated)
+            k = min(k, p.max_tokens - len(r.generated), eng.max_ctx - n_ctx - 1)
+        if k <= 1:
+            return 1
+        try:
+            for r in reqs:
+                eng.reserve(r.slot, len(r.prompt) + len(r.generated) + k)
+        except OutOfPages:
+            return 1
+        return k
 
     # ---- tokens --------------------------------------------------------------------------------
     def _produce(self, r: Request, greedy_id: int, logits) -> None:

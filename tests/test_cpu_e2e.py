@@ -251,3 +251,38 @@ def test_speculative_decoding_in_the_scheduler(tiny_assets):
     assert plain == spec and len(spec) == 24
     assert c1.get("spec_ticks", 0) >= 1 and c1.get("spec_accepted", 0) >= 1
     assert c1.get("decode_ticks", 0) + c1.get("spec_ticks", 0) < c0["decode_ticks"]
+
+
+def test_multi_step_decode_gives_the_same_tokens(tiny_assets):
+    """`multi_step` = 4: greedy decode ticks run four steps per engine call (the engine feeds its own arg-max tokens
+    forward); the tokens, stop handling and usage must equal the step-by-step run, including a request whose budget is
+    not a multiple of four and one that stops on a stop token inside a chained call."""
+    prompts = _prompts(3, 60, seed=9)
+
+    def run(multi):
+        eng = CpuEngine(tiny_assets / "assets", max_slots=4, max_ctx=512)
+        mux = ModelMux(eng, ByteTokenizer(), SchedConfig(multi_step=multi), eos_ids=[]).start()
+        try:
+            first = mux.generate(prompts[0], GenParams(max_tokens=12))
+            stop_tok = first[0][6]            # a token the greedy continuation is known to produce at step 7
+            reqs = [mux.submit(prompts[0], GenParams(max_tokens=12, stop_token_ids=[stop_tok])),
+                    mux.submit(prompts[1], GenParams(max_tokens=10)), mux.submit(prompts[2], GenParams(max_tokens=7))]
+            outs = []
+            for r in reqs:
+                toks = []
+                while True:
+                    c = r.out.get(timeout=60)
+                    if c.kind == "token":
+                        toks.append(c.token_id)
+                    elif c.kind == "done":
+                        outs.append((toks, c.finish_reason, c.usage["completion_tokens"]))
+                        break
+            return first[0], outs, mux.metrics.snapshot()["counters"].get("multi_step_calls", 0)
+        finally:
+            mux.stop()
+            eng.close()
+    a_first, a_outs, a_calls = run(1)
+    b_first, b_outs, b_calls = run(4)
+    assert a_first == b_first and a_outs == b_outs
+    assert a_calls == 0 and b_calls > 0
+    assert a_outs[0][1] == "stop" and len(a_outs[0][0]) <= 7

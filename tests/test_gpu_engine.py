@@ -258,6 +258,50 @@ def test_dsa_model_sparse_selection_matches_reference(tmp_path, n_prompt, bucket
         nxt = int(want.argmax())
 
 
+def test_multi_step_decode_on_device_matches_step_by_step(mla_assets):
+    """Four decode steps chained on the device (sampled ids fed back without a host round trip) produce the tokens of
+    four single steps, and leave the cache in the same state (a fifth step agrees)."""
+    from plow_b200.runtime.engine import TokenBatch
+    from plow_b200.runtime.gpu_engine import GpuEngine
+    d, cfg = mla_assets
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (70, 41)]
+
+    def prefill(eng):
+        ids, pos, seq, samp = [], [], [], []
+        for s, p in enumerate(prompts):
+            eng.begin_slot(s, p)
+            eng.reserve(s, len(p) + 16)
+            ids += p
+            pos += list(range(len(p)))
+            seq += [s] * len(p)
+            samp.append(len(ids) - 1)
+        r = eng.step(TokenBatch(np.array(ids, np.int32), np.array(pos, np.int32), np.array(seq, np.int32), np.array(samp, np.int32)))
+        for s, p in enumerate(prompts):
+            eng.commit(s, p)
+        return np.asarray(r.ids[:2], np.int32)
+
+    def batch(ids, step):
+        return TokenBatch(ids, np.array([len(p) + step for p in prompts], np.int32), np.array([0, 1], np.int32),
+                          np.array([0, 1], np.int32), decode=True)
+    a = GpuEngine(d / "assets", max_slots=4, max_ctx=512)
+    ids = prefill(a)
+    single = []
+    for i in range(6):
+        ids = np.asarray(a.step(batch(ids, i)).ids[:2], np.int32)
+        single.append(ids.tolist())
+    b = GpuEngine(d / "assets", max_slots=4, max_ctx=512)
+    ids = prefill(b)
+    ids = np.asarray(b.step(batch(ids, 0)).ids[:2], np.int32)        # the first decode step captures the rung's graph
+    got = [ids.tolist()]
+    res = b.step_multi(batch(ids, 1), 4)
+    assert len(res) == 4
+    got += [r.ids[:2].tolist() for r in res]
+    ids = np.asarray(res[-1].ids[:2], np.int32)
+    got.append(b.step(batch(ids, 5)).ids[:2].tolist())
+    assert got == single
+
+
 def test_smoke_runs():
     from plow_b200.runtime import smoke
     smoke.run()
