@@ -86,6 +86,7 @@ class Request:
     last_token_at: float | None = None
     rng: np.random.Generator | None = None
     waited_ticks: int = 0
+    aged: bool = False               # waited longer than aging_ticks for a prefill chunk: served before newer requests
     preempted: int = 0
     cancelled: bool = False
     pf_len: int = 0                  # tokens to (re)prefill, fixed when the request is seated
@@ -505,8 +506,13 @@ class ModelMux:
         budget = self._prefill_budget()
         for r in reqs:
             r.waited_ticks += 1
-        # shortest remaining prefill first; aged requests first of all
-        order = sorted(reqs, key=lambda r: (0 if r.waited_ticks > self.cfg.aging_ticks else 1, r.pf_len - r.done_prefill))
+            if r.waited_ticks > self.cfg.aging_ticks:
+                r.aged = True
+        # Shortest remaining prefill first; aged requests first of all.  Ageing is sticky: a request that waited too
+        # long keeps its priority until its prompt is done.  (When it lost the priority with its first chunk, a burst of
+        # long prompts aged together and then took turns, one chunk each: every one of them finished at the very end,
+        # and the median time to first token of a 64-request wave was two thirds of the whole prefill phase.)
+        order = sorted(reqs, key=lambda r: (0 if r.aged else 1, r.pf_len - r.done_prefill))
         ids, pos, seq, sample_rows, spans = [], [], [], [], []
         for r in order:
             if budget <= 0 or len(spans) >= eng.buckets.get("max_seqs", 64):
