@@ -247,6 +247,8 @@ class GpuEngine(EngineBase):
         self._multi_out = self._h_multi_out = None
         self._mla_plan_rows = 0
         self._has_mla = any(l.attn.kind == "mla" for l in self.spec.layers)
+        self._has_gdn = any(l.attn.kind == "gdn" for l in self.spec.layers)
+        self._gdn_plan = None
         self._dsa_topk = max((l.attn.index_topk for l in self.spec.layers if l.attn.index_heads), default=0)
         self.h_plan = torch.zeros(2 * max_rows + 4 * n_slots, dtype=I32).pin_memory()
         self.d_plan = torch.zeros(2 * max_rows + 4 * n_slots, dtype=I32, device=dev)
@@ -507,6 +509,35 @@ class GpuEngine(EngineBase):
                     pos=self.d_plan[:R], kvlen=self.d_plan[R:2 * R], spans=self.d_plan[2 * R:2 * R + 4 * n_sp], budget=budget,
                     gathered=False)
 
+    GDN_CHUNKED_MIN_RUN = int(os.environ.get("PLOW_GDN_CHUNKED_MIN_RUN", "128"))
+
+    def _plan_gdn_prefill(self, batch: TokenBatch, R: int):
+        """Which runs of this (eager) step's rows take the chunked gated-delta-rule prefill; None when none does."""
+        if self.GDN_CHUNKED_MIN_RUN <= 0 or batch.rows < self.GDN_CHUNKED_MIN_RUN:
+            return None
+        rows, seq, pos = batch.rows, batch.seq, batch.pos
+        brk = np.flatnonzero((seq[1:] != seq[:-1]) | (pos[1:] != pos[:-1] + 1)) + 1
+        starts = np.concatenate(([0], brk)).tolist()
+        ends = np.concatenate((brk, [rows])).tolist()
+        chunked, rest, seen = [], [], set()
+        for r0, r1 in zip(starts, ends):
+            slot = int(seq[r0])
+            if r1 - r0 >= self.GDN_CHUNKED_MIN_RUN and slot not in seen:
+                seen.add(slot)
+                chunked.append((slot, r0, r1, int(pos[r0]) == 0))
+            elif rest and rest[-1][1] == r0:
+                rest[-1] = (rest[-1][0], r1)
+            else:
+                rest.append((r0, r1))
+        if not chunked:
+            return None
+        if R > rows:                                  # the program's padding rows
+            if rest and rest[-1][1] == rows:
+                rest[-1] = (rest[-1][0], R)
+            else:
+                rest.append((rows, R))
+        return dict(R=R, chunked=chunked, rest=rest)
+
     def _mla_prefill(self, st, ins, plan, ao, q, rope_tab, cache, scale):
         """Materialised prefill of one layer (see csrc/cuda/mla_prefill.cu)."""
         heads, kv_lora, nope, qk_rope, pair = ins.i[0], ins.i[1], ins.i[2], ins.i[3], ins.i[5]
@@ -680,7 +711,22 @@ class GpuEngine(EngineBase):
     def _op_gdn(self, st, ins):
         out, conv_state, ssm_state, qkvz, ba, conv_w, a_log, dt_bias = (self.tensor(st, ins.t[k]) for k in range(8))
         hk, hv, hd, conv = ins.i[0], ins.i[1], ins.i[2], ins.i[3]
-        gdn_ops.gdn(qkvz, ba, conv_w, a_log, dt_bias, conv_state, ssm_state, self.d_in[1], self.d_in[2], hk, hv, hd, conv, out=out)
+        plan = self._gdn_plan
+        if plan is None or plan["R"] != st.rows:
+            gdn_ops.gdn(qkvz, ba, conv_w, a_log, dt_bias, conv_state, ssm_state, self.d_in[1], self.d_in[2], hk, hv, hd, conv, out=out)
+            return
+        # long runs of new rows: chunked (WY-form) prefill, 64 tokens at a time (ops/gdn.py::chunked_prefill); everything
+        # else (decode riders, short runs, padding rows) stays on the token-by-token kernel, one call per row range
+        for slot, r0, r1, fresh in plan["chunked"]:
+            hist = torch.zeros_like(conv_state[slot], dtype=F32) if fresh else conv_state[slot]
+            S0 = torch.zeros_like(ssm_state[slot], dtype=F32) if fresh else ssm_state[slot]
+            o, h, S1 = gdn_ops.chunked_prefill(qkvz[r0:r1], ba[r0:r1], conv_w, a_log, dt_bias, hist, S0, hk, hv, hd, conv)
+            out[r0:r1].copy_(o)
+            conv_state[slot].copy_(h)
+            ssm_state[slot].copy_(S1)
+        for a, b in plan["rest"]:
+            gdn_ops.gdn(qkvz[a:b], ba[a:b], conv_w, a_log, dt_bias, conv_state, ssm_state, self.d_in[1][a:b], self.d_in[2][a:b],
+                        hk, hv, hd, conv, out=out[a:b])
 
     def _op_gated_norm(self, st, ins):
         out, o, z, gamma = (self.tensor(st, ins.t[k]) for k in range(4))
@@ -1025,6 +1071,7 @@ class GpuEngine(EngineBase):
         self.d_in[:, :R].copy_(hin[:, :R], non_blocking=True)
         torch.add(self.d_in[1, :R], 1, out=self.d_kvlen_row[:R])
         self._mla_plan = None
+        self._gdn_plan = self._plan_gdn_prefill(batch, R) if (not decode and rows > 0 and self._has_gdn) else None
         # eager (prefill) steps of a sparse-attention model whose positions all lie below top_k attend densely
         st.scratch["dsa_dense_ok"] = bool(not decode and self._dsa_topk and rows > 0 and int(batch.pos.max()) < self._dsa_topk)
         if not decode and rows > 0 and self._has_mla:

@@ -286,3 +286,30 @@ def test_multi_step_decode_gives_the_same_tokens(tiny_assets):
     assert a_first == b_first and a_outs == b_outs
     assert a_calls == 0 and b_calls > 0
     assert a_outs[0][1] == "stop" and len(a_outs[0][0]) <= 7
+
+
+@pytest.mark.parametrize("n_pages,budget,lens", [(5, 64, (144, 157, 187)), (5, 96, (144, 157, 187)), (7, 128, (144, 157, 187, 120))])
+def test_prefill_time_preemption_keeps_the_dispatcher_alive(tiny_assets, n_pages, budget, lens):
+    """KV pressure DURING prefill: long prompts admitted against few pages with small chunks.  A request that loses its
+    slot to a preemption inside a tick must not be planned again in that tick (its slot is -1), every request still
+    finishes with its full output, and the dispatcher thread survives."""
+    eng = CpuEngine(tiny_assets / "assets", max_slots=4, max_ctx=512, n_pages=n_pages, prefix_cache=False)
+    mux = ModelMux(eng, ByteTokenizer(), SchedConfig(token_budget=budget, reserve_tokens=0), eos_ids=[]).start()
+    try:
+        rng = np.random.default_rng(11)
+        reqs = [mux.submit(rng.integers(3, 250, size=n).tolist(), GenParams(max_tokens=12)) for n in lens]
+        for r in reqs:
+            n = 0
+            while True:
+                ch = r.out.get(timeout=120)
+                if ch.kind == "token":
+                    n += 1
+                else:
+                    assert ch.kind == "done" and ch.finish_reason == "length", (ch.kind, ch.error)
+                    break
+            assert n == 12
+        assert mux._thread.is_alive()
+        eng.pool.check()
+    finally:
+        mux.stop()
+        eng.close()

@@ -19,7 +19,11 @@ def _cfg():
     return cfg
 
 
-def test_hybrid_engine_matches_reference(tmp_path):
+@pytest.mark.parametrize("n0,cut", [(150, 100), (400, 200)])
+def test_hybrid_engine_matches_reference(tmp_path, n0, cut):
+    """(150, 100): every run is short, the token-by-token kernel serves the prefill.  (400, 200): both chunks of prompt 0
+    are long runs and take the chunked (WY-form) prefill, the second one continuing from the first one's state, while
+    prompt 1 (37 rows) and the padding rows of the same step stay on the kernel."""
     from safetensors.torch import load_file
     from plow_b200 import plowc
     from plow_b200.models import config, reference
@@ -35,20 +39,21 @@ def test_hybrid_engine_matches_reference(tmp_path):
         state.update(load_file(f))
     ref = reference.ReferenceModel(config.spec_from_config(cfg), {k: v.float() for k, v in state.items()})
     g = torch.Generator().manual_seed(1)
-    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (150, 37)]
-    # prompt 0 is prefilled in two chunks (100 + 50) so the recurrent state crosses a step boundary
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (n0, 37)]
+    # prompt 0 is prefilled in two chunks so the recurrent state crosses a step boundary
     for s, p in enumerate(prompts):
         eng.begin_slot(s, p)
         eng.reserve(s, len(p) + 8)
-    first = TokenBatch(np.array(prompts[0][:100], np.int32), np.arange(100, dtype=np.int32), np.zeros(100, np.int32), np.array([99], np.int32))
+    first = TokenBatch(np.array(prompts[0][:cut], np.int32), np.arange(cut, dtype=np.int32), np.zeros(cut, np.int32), np.array([cut - 1], np.int32))
     eng.step(first)
-    eng.commit(0, prompts[0][:100])
-    ids = prompts[0][100:] + prompts[1]
-    pos = list(range(100, 150)) + list(range(37))
-    seq = [0] * 50 + [1] * 37
-    res = eng.step(TokenBatch(np.array(ids, np.int32), np.array(pos, np.int32), np.array(seq, np.int32), np.array([49, 86], np.int32),
-                              want_logits=True))
-    eng.commit(0, prompts[0][100:])
+    assert (eng._gdn_plan is not None) == (cut >= 128)
+    eng.commit(0, prompts[0][:cut])
+    ids = prompts[0][cut:] + prompts[1]
+    pos = list(range(cut, n0)) + list(range(37))
+    seq = [0] * (n0 - cut) + [1] * 37
+    res = eng.step(TokenBatch(np.array(ids, np.int32), np.array(pos, np.int32), np.array(seq, np.int32),
+                              np.array([n0 - cut - 1, n0 - cut + 36], np.int32), want_logits=True))
+    eng.commit(0, prompts[0][cut:])
     eng.commit(1, prompts[1])
     for s, p in enumerate(prompts):
         want = ref.forward(torch.tensor(p))[-1]

@@ -113,3 +113,33 @@ def test_chained_decode_steps_through_the_scheduler(assets):
     b, nb = run(4)
     assert na == 0 and nb >= 1
     assert a == b
+
+
+def test_device_status_fails_the_step_not_the_dispatcher(assets, monkeypatch):
+    """A kernel that gives up on a bounded wait leaves a status word; the engine turns it into a non-fatal EngineError,
+    the scheduler fails the requests of that step with an error chunk, re-arms the shared scratch, and keeps serving.
+    The status is injected on the host (the device word is written by the test, nothing on the GPU waits or faults)."""
+    from plow_b200.ops import native
+    from plow_b200.runtime.scheduler import GenParams
+    eng, mux = _mux(assets)
+    try:
+        ok = mux.generate(_prompts(1, 50, 51, seed=8)[0], GenParams(max_tokens=4))
+        assert len(ok[0]) == 4
+        real = native.check_status
+        fired = {"n": 0}
+
+        def flaky(device=None):
+            if fired["n"] == 0:
+                fired["n"] = 1
+                native.status_word(eng.device)[0] = 5 | (1 << 8)        # a wait-expired code of the GEMM family
+            return real(device)
+        monkeypatch.setattr(native, "check_status", flaky)
+        r = mux.submit(_prompts(1, 60, 61, seed=9)[0], GenParams(max_tokens=4))
+        ch = r.out.get(timeout=60)
+        assert ch.kind == "error" and "status" in (ch.error or "")
+        assert mux._thread.is_alive() and eng.health != "dead"
+        after = mux.generate(_prompts(1, 50, 51, seed=8)[0], GenParams(max_tokens=4))
+        assert after[0] == ok[0]                                      # same prompt, same tokens: the engine recovered
+        assert int(native.status_word(eng.device)[0]) == 0
+    finally:
+        mux.stop()

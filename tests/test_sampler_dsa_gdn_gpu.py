@@ -198,3 +198,36 @@ def test_dsa_gather_feeds_dense_decode_kernel():
     torch.cuda.synchronize()
     native.check_status()
     assert torch.equal(a, b)
+
+
+def test_gdn_chunked_prefill_matches_recurrence():
+    """WY-form chunked prefill (64-token chunks, affine state scan) against the fp32 token-by-token recurrence: 1000
+    tokens that do not fill the last chunk, continuing from a non-zero state, then a decode step of the kernel from the
+    state the chunked path left."""
+    from plow_b200.ops import gdn
+    torch.manual_seed(7)
+    dev = "cuda"
+    hk, hv, d, conv = 2, 4, 128, 4
+    C = (2 * hk + hv) * d
+    conv_w = torch.randn(C, conv, device=dev) * 0.5
+    a_log = torch.randn(hv, device=dev) * 0.5
+    dt_bias = torch.randn(hv, device=dev) * 0.5
+    T0, T1 = 100, 1000
+    qkvz = torch.randn(T0 + T1, C + hv * d, device=dev).bfloat16()
+    ba = torch.randn(T0 + T1, 2 * hv, device=dev).bfloat16()
+    o_ref, h_ref, S_ref = gdn.reference(qkvz, ba, conv_w, a_log, dt_bias, hk, hv)
+    _, h0, S0 = gdn.reference(qkvz[:T0], ba[:T0], conv_w, a_log, dt_bias, hk, hv)
+    out, h1, S1 = gdn.chunked_prefill(qkvz[T0:], ba[T0:], conv_w, a_log, dt_bias, h0, S0, hk, hv)
+    assert (out - o_ref[T0:]).abs().max().item() < 2e-3 * o_ref.abs().max().item() + 1e-4
+    assert (S1 - S_ref).abs().max().item() < 2e-3 * S_ref.abs().max().item() + 1e-4
+    assert (h1 - h_ref).abs().max().item() < 1e-5
+    # the token-by-token kernel continues from that state
+    conv_state = torch.zeros(1, C, conv - 1, device=dev)
+    ssm_state = torch.zeros(1, hv, d, d, device=dev)
+    conv_state[0], ssm_state[0] = h1, S1
+    q2 = torch.randn(1, C + hv * d, device=dev).bfloat16()
+    b2 = torch.randn(1, 2 * hv, device=dev).bfloat16()
+    o2 = gdn.gdn(q2, b2, conv_w, a_log, dt_bias, conv_state, ssm_state, torch.tensor([T0 + T1], dtype=torch.int32, device=dev),
+                 torch.zeros(1, dtype=torch.int32, device=dev), hk, hv)
+    r2, _, _ = gdn.reference(q2, b2, conv_w, a_log, dt_bias, hk, hv, conv_hist=h_ref, S=S_ref)
+    assert (o2[0].float() - r2[0]).abs().max().item() < 2e-2 * r2.abs().max().item() + 1e-3
