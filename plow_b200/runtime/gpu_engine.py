@@ -509,7 +509,10 @@ class GpuEngine(EngineBase):
                     pos=self.d_plan[:R], kvlen=self.d_plan[R:2 * R], spans=self.d_plan[2 * R:2 * R + 4 * n_sp], budget=budget,
                     gathered=False)
 
-    GDN_CHUNKED_MIN_RUN = int(os.environ.get("PLOW_GDN_CHUNKED_MIN_RUN", "128"))
+    # Runs of at least this many new rows take the chunked gated-delta-rule prefill (0 = off, the default: that path is
+    # batched matrix algebra through cuBLAS / cuSOLVER, and the serving default keeps the hand-written token-by-token
+    # kernel on this op; set PLOW_GDN_CHUNKED_MIN_RUN=128 to trade that for a several times faster long-prompt prefill).
+    GDN_CHUNKED_MIN_RUN = int(os.environ.get("PLOW_GDN_CHUNKED_MIN_RUN", "0"))
 
     def _plan_gdn_prefill(self, batch: TokenBatch, R: int):
         """Which runs of this (eager) step's rows take the chunked gated-delta-rule prefill; None when none does."""

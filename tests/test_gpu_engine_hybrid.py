@@ -33,6 +33,7 @@ def test_hybrid_engine_matches_reference(tmp_path, n0, cut):
     reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=0, dtype=torch.bfloat16)
     plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", max_rows=256, prefill_buckets=[128, 256], decode_rungs=[4, 8], max_seqs=8)
     eng = GpuEngine(tmp_path / "assets", max_slots=4, max_ctx=512)
+    eng.GDN_CHUNKED_MIN_RUN = 128              # the chunked prefill is opt-in
     assert eng.pool.enable_prefix is False
     state = {}
     for f in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
