@@ -143,3 +143,28 @@ def test_device_status_fails_the_step_not_the_dispatcher(assets, monkeypatch):
         assert int(native.status_word(eng.device)[0]) == 0
     finally:
         mux.stop()
+
+
+def test_speculative_decoding_on_the_gpu_engine(assets):
+    """Prompt-lookup drafts verified as k + 1-row spans on the sm_100a engine: a repetitive prompt makes drafts available;
+    the verified tokens must be the engine's own greedy continuation (each accepted token is one the span's arg-max
+    confirmed) and fewer engine calls are used.  Spans run through the prefill program, plain decode through the decode
+    graph: near-ties of the random-weight model may flip, so the first tokens are required to match and the rest mostly."""
+    from plow_b200.runtime.scheduler import GenParams
+    rng = np.random.default_rng(5)
+    motif = rng.integers(3, 1000, 12).tolist()
+    prompt = (motif * 8)[:90]
+
+    def run(depth):
+        eng, mux = _mux(assets, prefix_cache=False, cfg=dict(spec_depth=depth))
+        try:
+            toks = mux.generate(prompt, GenParams(max_tokens=24))[0]
+            return toks, mux.metrics.snapshot()["counters"]
+        finally:
+            mux.stop()
+    plain, c0 = run(0)
+    spec, c1 = run(4)
+    assert len(plain) == 24 and len(spec) == 24
+    assert plain[:3] == spec[:3]
+    assert sum(int(a == b) for a, b in zip(plain, spec)) >= 16
+    assert c1.get("spec_ticks", 0) >= 1
