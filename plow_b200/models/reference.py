@@ -80,6 +80,7 @@ class ReferenceModel:
         """ids [T] -> logits [T, V] (float32)."""
         spec = self.spec
         T = ids.shape[0]
+        self.route_margin_last = float("inf")     # smallest routing gap of the last row over the MoE layers of this call
         pos = torch.arange(T, device=self.device)
         x = self.w["model.embed_tokens.weight"][ids] * spec.embed_scale
         for li, layer in enumerate(spec.layers):
@@ -198,7 +199,15 @@ class ReferenceModel:
 
     def _moe(self, p, h, f):
         bias = self.w.get(f"{p}.gate.e_score_correction_bias")
-        idx, g = self.route(h.float() @ self.w[f"{p}.gate.weight"].float().t(), f, bias)
+        logits = h.float() @ self.w[f"{p}.gate.weight"].float().t()
+        idx, g = self.route(logits, f, bias)
+        # how decisively the last row was routed: gap between the weakest chosen and the strongest rejected expert score
+        # (a reduced-precision implementation may legitimately route such a row differently when the gap is tiny)
+        sc = torch.sigmoid(logits[-1]) if f.score == "sigmoid" else torch.softmax(logits[-1], -1)
+        sel = sc + (bias.float() if bias is not None else 0.0)
+        top = torch.sort(sel, descending=True).values
+        if f.top_k < top.numel():
+            self.route_margin_last = min(self.route_margin_last, float(top[f.top_k - 1] - top[f.top_k]))
         out = torch.zeros_like(h, dtype=torch.float32)
         for j in range(f.top_k):
             for e in idx[:, j].unique().tolist():
