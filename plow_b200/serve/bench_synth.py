@@ -6,7 +6,10 @@
         -m plow_b200.serve.bench_synth --config dense8b --requests 256 --concurrency 64   # tensor parallel over the ranks
 
 Shapes: `dense8b` (32-layer GQA decoder, bf16), `gdn80b` (gated-delta-rule / gated-attention hybrid MoE; `--layers`
-cuts it down, the full shape needs several GPUs), `mla_moe` (fp8 MLA-MoE, 32 routed experts).  Weights are random
+cuts it down, the full shape needs several GPUs), `mla_moe` (fp8 MLA-MoE, 32 routed experts), `mla_moe_dsa` (the same
+with a sparse-attention indexer per layer, top-2048).  `--arrival-rate R` switches from the closed loop to Poisson
+arrivals at R requests per second (open loop: requests queue when all slots are busy); `--shared-prefix-frac F
+--shared-prefix-len N` gives a fraction F of the prompts one common N-token prefix (exercises the prefix cache).  Weights are random
 (`SyntheticWeights`), prompts are uniform random token ids, EOS is ignored.  With more than one rank the model is
 compiled for tensor parallelism: rank 0 owns the scheduler and broadcasts every step, the other ranks replay it
 (`parallel/group.py`, LeaderGroup).  At most `--concurrency` requests are in flight; a finished request is replaced by
@@ -27,7 +30,10 @@ import torch.distributed as dist
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", default="dense8b", choices=["dense8b", "gdn80b", "mla_moe"])
+    ap.add_argument("--config", default="dense8b", choices=["dense8b", "gdn80b", "mla_moe", "mla_moe_dsa"])
+    ap.add_argument("--arrival-rate", type=float, default=0.0, help="Poisson arrivals per second (0: closed loop at --concurrency)")
+    ap.add_argument("--shared-prefix-frac", type=float, default=0.0)
+    ap.add_argument("--shared-prefix-len", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (0: the shape's own)")
     ap.add_argument("--requests", type=int, default=256)
     ap.add_argument("--concurrency", type=int, default=64)
@@ -50,7 +56,8 @@ def main() -> None:
     from ..text.tokenizer import ByteTokenizer
 
     cfg = {"dense8b": cfgs.dense_8b_config, "gdn80b": cfgs.gdn_hybrid_80b_config,
-           "mla_moe": lambda: cfgs.mla_moe_671b_config(n_experts=32)}[args.config]()
+           "mla_moe": lambda: cfgs.mla_moe_671b_config(n_experts=32),
+           "mla_moe_dsa": lambda: cfgs.mla_moe_671b_config(n_experts=32, dsa=True)}[args.config]()
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     spec = cfgs.spec_from_config(cfg)
@@ -67,7 +74,8 @@ def main() -> None:
         tp = TpComm(rank, world, impl="fused", max_rows=128, max_n=max(16384, spec.hidden), max_k=16384, ar_width=max(8192, spec.hidden))
         lg = LeaderGroup(rank, world, timeout_s=600.0)
     eng = GpuEngine(packet=pkt, weights=SyntheticWeights(dev, seed=1, scaled_init_layers=len(spec.layers)), max_slots=C,
-                    max_ctx=args.prompt_max + args.output + 64, prefix_cache=False, rank=rank, tp_comm=tp, leader_group=lg)
+                    max_ctx=args.prompt_max + args.output + 64, prefix_cache=args.shared_prefix_frac > 0, rank=rank, tp_comm=tp,
+                    leader_group=lg)
     if world > 1 and rank != 0:
         n = follower_loop(eng, lg)
         native.check_status()
@@ -75,6 +83,11 @@ def main() -> None:
         return
     rng = np.random.default_rng(7)
     prompts = [rng.integers(3, spec.vocab, size=int(n)).tolist() for n in rng.integers(args.prompt_min, args.prompt_max + 1, size=args.requests)]
+    if args.shared_prefix_frac > 0 and args.shared_prefix_len > 0:
+        common = rng.integers(3, spec.vocab, size=args.shared_prefix_len).tolist()
+        for i in range(len(prompts)):
+            if rng.random() < args.shared_prefix_frac and len(prompts[i]) > args.shared_prefix_len:
+                prompts[i][:args.shared_prefix_len] = common
     mux = ModelMux(eng, ByteTokenizer(), SchedConfig(token_budget=args.chunk, objective="auto", queue_ttl_s=36000.0, multi_step=args.multi_step),
                    eos_ids=[]).start()
     lock, state = threading.Lock(), dict(next=0, out=0, failed=0)
@@ -101,11 +114,36 @@ def main() -> None:
             with lock:
                 state["out"] += n
 
+    def drain(r):
+        n = 0
+        while True:
+            ch = r.out.get(timeout=3600)
+            if ch.kind == "token":
+                n += 1
+            elif ch.kind == "done":
+                break
+            else:
+                with lock:
+                    state["failed"] += 1
+                break
+        with lock:
+            state["out"] += n
+
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    threads = [threading.Thread(target=client, daemon=True) for _ in range(C)]
-    for t in threads:
-        t.start()
+    if args.arrival_rate > 0:
+        # open loop: exponential gaps between submissions, one collector thread per request
+        threads = []
+        for p in prompts:
+            r = mux.submit(p, GenParams(max_tokens=args.output, ignore_eos=True))
+            th = threading.Thread(target=drain, args=(r,), daemon=True)
+            th.start()
+            threads.append(th)
+            time.sleep(float(rng.exponential(1.0 / args.arrival_rate)))
+    else:
+        threads = [threading.Thread(target=client, daemon=True) for _ in range(C)]
+        for t in threads:
+            t.start()
     for t in threads:
         t.join()
     wall = time.perf_counter() - t0
@@ -119,7 +157,8 @@ def main() -> None:
                           prompt_tokens=n_prompt, output_tokens=state["out"], failed=state["failed"], wall_s=round(wall, 2),
                           output_tok_s=round(state["out"] / wall, 1), total_tok_s=round((state["out"] + n_prompt) / wall, 1),
                           ttft_ms=snap["ttft_ms"], tpot_ms=snap["tpot_ms"],
-                          counters={k: snap["counters"].get(k) for k in ("prefill_ticks", "decode_ticks", "preemptions", "rider_rows", "multi_step_calls")},
+                          arrival_rate=args.arrival_rate or None,
+                          counters={k: snap["counters"].get(k) for k in ("prefill_ticks", "decode_ticks", "preemptions", "rider_rows", "multi_step_calls", "cached_tokens")},
                           data="synthetic: random token ids, random-init weights")))
     if world > 1:
         dist.destroy_process_group()
