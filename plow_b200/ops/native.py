@@ -135,7 +135,8 @@ _SIGS = {
     "plow_ep_y_ready": "pp",
     "plow_ep_combine": "pppppiipip",
     "plow_wait_probe": "piLpp",
-    "plow_ag_push": "pLLppiipiiip",
+    "plow_ag_push": "pLLppiipiii" "Lipp",
+    "plow_ag_release": "pLiip",
     "plow_tp_allreduce_norm": "pLLLp" "iii" "pipppp" "iifiipp",
     "plow_interp_run": "ppppppppppp" "IIIIp",
     "plow_sample": "ppiiipppppp" "Lp",

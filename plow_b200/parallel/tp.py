@@ -32,6 +32,7 @@ class TpComm:
         self.oneshot_bytes = oneshot_bytes     # messages up to this size use the one-shot form (decode), larger ones two-shot
         self.dev = torch.device("cuda", torch.cuda.current_device())
         self.max_rows, self.max_n, self.deadline_ms = max_rows, max_n, deadline_ms
+        self.max_k = max_k
         # stand-alone all-reduce (+ add + norm) over peer memory: rows x hidden width at most.  The one-shot form reads every
         # rank's partial on every rank, which wins while the message is latency-bound (measured on 2 GPUs: 21.6 us against
         # 45.6 us for NCCL + the norm kernel at 64 x 4096) and loses to NCCL's bandwidth-optimal ring once it is not
@@ -44,7 +45,7 @@ class TpComm:
         lay, off = {}, 0
         self.half_bytes = _align(tiles * world * 128 * 64 * 2)        # one-shot slots: [tile][source rank][128][<=64 tokens] bf16
         for name, nbytes in (("part", max(tiles * 128 * 128 * 2, 2 * self.half_bytes)), ("flag", tiles * 8 * 4), ("done", 128), ("tdone", tiles * 4), ("y", max_rows * max_n * 2),
-                             ("ag_ctr", 128), ("xg0", max_rows * max_k * 2), ("xg1", max_rows * max_k * 2),
+                             ("ag_ctr", 128), ("ag_rel", 128), ("xg0", max_rows * max_k * 2),
                              ("ar_flag", world * ar_rows * 4), ("ar_part", 2 * _align(ar_rows * ar_width * 2))):
             lay[name] = off
             off = _align(off + nbytes)
@@ -58,7 +59,6 @@ class TpComm:
         self.ar_epoch = torch.zeros(2, dtype=torch.int32, device=self.dev)   # [call counter, CTAs through]
         self.ag_epoch = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.ag_done = torch.zeros(1, dtype=torch.int32, device=self.dev)
-        self._ag_calls = 0
         self.peers = list(self.hdl.buffer_ptrs)
         try:
             self.mc_ptr = int(self.hdl.multicast_ptr) if self.hdl.has_multicast_support(self.dev.type, self.dev.index) else 0
@@ -132,16 +132,17 @@ class TpComm:
             xg = torch.empty(M, K, dtype=BF16, device=self.dev)
             dist.all_gather_into_tensor(xg, x_band)
             return gemm_ops.gemm(xg, w, dual=dual, n_out=n_out)
-        # two gathered buffers used alternately: a rank can be at most one call ahead of a peer that is still
-        # reading (its next push needs that peer's band of the call in between), so parity is enough
-        ofs = self.lay["xg1" if self._ag_calls & 1 else "xg0"]
-        self._ag_calls += 1
-        assert M <= self.max_rows and K * 2 * M <= self.lay["xg1"] - self.lay["xg0"]
+        # one gathered buffer: the push of a call waits (on the device, bounded) until every rank has released the
+        # previous call's rows, which each rank does right after its GEMM; no host-side state, so a captured graph replays
+        ofs = self.lay["xg0"]
+        assert M <= self.max_rows and K <= self.max_k
         native.call("plow_ag_push", self._peer_arr, ofs, self.lay["ag_ctr"], self.ag_epoch, self.ag_done, self.world,
-                    self.rank, x_band, K * 2, band, K * 2)
+                    self.rank, x_band, K * 2, band, K * 2, self.lay["ag_rel"], self.deadline_ms, native.status_word(self.dev))
         xg = self.buf[ofs:ofs + M * K * 2].view(BF16).view(M, K)
         ctr = self.buf.data_ptr() + self.lay["ag_ctr"]
-        return gemm_ops.gemm(xg, w, dual=dual, n_out=n_out, wait=(ctr, self.ag_epoch.data_ptr(), self.world, self.deadline_ms))
+        y = gemm_ops.gemm(xg, w, dual=dual, n_out=n_out, wait=(ctr, self.ag_epoch.data_ptr(), self.world, self.deadline_ms))
+        native.call("plow_ag_release", self._peer_arr, self.lay["ag_rel"], self.world, self.rank)
+        return y
 
     def all_reduce(self, x):
         """Stand-alone all-reduce (instructions the compiler did not fuse into a GEMM), in place: the peer-memory row
