@@ -301,6 +301,9 @@ class GpuEngine(EngineBase):
             if (flags & (pk.GEMM_FP8_BLOCK | pk.GEMM_DUAL_SILU)) or co != 0 or w is None or w.dtype != BF16 or x is None \
                     or x.dtype != BF16 or x.shape[1] != K or N != tk.i[0] or K % 8 or N > 1024:
                 continue
+            k_top, n_grp = tk.i[1], max(1, tk.i[2])
+            if k_top > 32 or n_grp > 32 or N % n_grp or (K + 3 * N) * 4 > 190 * 1024:
+                continue                                  # outside what the routing kernel handles: keep the three kernels
             if any(o is not g and o is not tk and g.t[0] in o.t for o in insts):
                 continue                                  # something else reads the logits
             moe = next((m for m in insts if m.op == Op.MOE_GEMM and m.t[2] == tk.t[0]), None)
