@@ -277,7 +277,8 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
   uint64_t* drain_bar = acc_empty + kNBuf;                       // [1]
   uint64_t* xchg_bar = drain_bar + 1;                            // [2] epilogue-warp exchange
   uint64_t* pair_bar = xchg_bar + 2;                             // [4] the two warps of a lane quarter (8-warp epilogue)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pair_bar + 4);
+  uint64_t* gate_bar = pair_bar + 4;                             // [1] producer -> epilogue warps: the arrival gate is open
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(gate_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   volatile int* never_flag = abort_flag + 1;                     // stays 0
   float* red_scratch = reinterpret_cast<float*>(ctrl + 512);     // [2][4][16] quant amax exchange (+ split-K flag)
@@ -296,6 +297,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
     mbar_init(&xchg_bar[0], kEpiWarps);
     mbar_init(&xchg_bar[1], kEpiWarps);
     for (int q = 0; q < 4; ++q) mbar_init(&pair_bar[q], 2);
+    mbar_init(gate_bar, 1);
     *abort_flag = 0;
     *never_flag = 0;
     fence_mbar_init();
@@ -370,6 +372,7 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
         }
         PLOW_TRACE(if (a.trace && blockIdx.x == 0) a.trace[15] = static_cast<long long>(globaltimer_ns());)
         fence_proxy_async_all();
+        mbar_arrive(gate_bar);      // the epilogue warps wait on this instead of polling the counter themselves
       }
       if (ok) run(1);
     }
@@ -438,17 +441,10 @@ gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
     const uint32_t ar_ep = a.ar_world > 1 ? *a.ar_epoch + 1 : 0;   // this launch's all-reduce epoch
     if (a.wait_ctr) {
       // expert-parallel dispatch: the activation scales these warps prefetch are written by peer GPUs together with
-      // the rows, so they too start only once the arrival counter says everything has landed (one poller per warp,
-      // with back-off: the polled line is also the target of the peers' remote adds)
-      if ((threadIdx.x & 31) == 0) {
-        const uint32_t target = *a.wait_epoch * a.wait_mult;
-        const unsigned long long t0 = globaltimer_ns();
-        while (ld_acquire_sys(a.wait_ctr) < target) {
-          if (*abort_flag || globaltimer_ns() - t0 > static_cast<unsigned long long>(a.wait_deadline_ms) * 1000000ull) break;
-          __nanosleep(512);
-        }
-      }
-      __syncwarp();
+      // the rows, so they too start only once everything has landed.  Only the producer thread polls the arrival
+      // counter (one poller per CTA: the polled line is also the target of the peers' remote adds, and five pollers
+      // per CTA on 148 CTAs kept that line busy); it opens this barrier when the gate is through.
+      if (!mbar_wait(gate_bar, 0, abort_flag)) { /* the producer gave up (status recorded there) or the wait ran out */ }
     }
     const int lq = warp & 3;               // TMEM lane quarter this warp may read
     const int li = lq * 32 + lane;         // lane (row of D) owned by this thread
