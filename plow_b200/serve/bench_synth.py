@@ -28,6 +28,20 @@ import torch
 import torch.distributed as dist
 
 
+def _teardown() -> None:
+    """Leave the process group without waiting on it for ever: on this stack `destroy_process_group` has been seen to
+    block in both ranks after a serving run that used symmetric memory from a second host thread; the results are
+    already printed, so the teardown gets 20 s and the process exits either way."""
+    import sys
+    torch.cuda.synchronize()
+    t = threading.Thread(target=dist.destroy_process_group, daemon=True)
+    t.start()
+    t.join(20.0)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", default="dense8b", choices=["dense8b", "gdn80b", "mla_moe", "mla_moe_dsa"])
@@ -44,6 +58,10 @@ def main() -> None:
     ap.add_argument("--multi-step", type=int, default=1)
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if os.environ.get("PLOW_DUMP_STACKS_AFTER_S"):
+        # diagnostic: print every thread's stack if the run is still going after this many seconds
+        import faulthandler
+        faulthandler.dump_traceback_later(float(os.environ["PLOW_DUMP_STACKS_AFTER_S"]), exit=True)
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
@@ -77,9 +95,9 @@ def main() -> None:
                     max_ctx=args.prompt_max + args.output + 64, prefix_cache=args.shared_prefix_frac > 0, rank=rank, tp_comm=tp,
                     leader_group=lg)
     if world > 1 and rank != 0:
-        n = follower_loop(eng, lg)
+        follower_loop(eng, lg)
         native.check_status()
-        dist.destroy_process_group()
+        _teardown()
         return
     rng = np.random.default_rng(7)
     prompts = [rng.integers(3, spec.vocab, size=int(n)).tolist() for n in rng.integers(args.prompt_min, args.prompt_max + 1, size=args.requests)]
@@ -159,9 +177,9 @@ def main() -> None:
                           ttft_ms=snap["ttft_ms"], tpot_ms=snap["tpot_ms"],
                           arrival_rate=args.arrival_rate or None,
                           counters={k: snap["counters"].get(k) for k in ("prefill_ticks", "decode_ticks", "preemptions", "rider_rows", "multi_step_calls", "cached_tokens")},
-                          data="synthetic: random token ids, random-init weights")))
+                          data="synthetic: random token ids, random-init weights")), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        _teardown()
 
 
 if __name__ == "__main__":
