@@ -11,6 +11,7 @@
 // and the numeric oracle the GPU kernels are compared against.  Reference counterparts:
 // crates/plowrt/src/exec/cpu/{interp,engine}.rs, runtime/cpu/dev/golden/*.c,
 // crates/plowrt/src/exec/health.rs (counter monitor).
+#include <algorithm>
 #include <atomic>
 #include <chrono>
 #include <cmath>
@@ -416,6 +417,13 @@ void op_mla_attn(const Ctx& c) {
   const float scale = c.in->w[0].f;
   const StepIO& io = c.e->io;
   const int qh = NP + RP, row = L + RP;
+  // sparse attention: the indexer's selection [rows][top_k] (ascending positions, -1 padded) replaces "every position"
+  // (operand 6 is the cache's scale tensor when the cache is e4m3 and the selection follows it; this backend's caches
+  // are f32 and have no scale tensor, so the selection is operand 6)
+  const int sel_op = c.in->t[7] != PLOW_T_NONE ? 7 : 6;
+  const int32_t* sel = (c.in->i[6] != 0) ? (const int32_t*)c.T(sel_op) : nullptr;
+  const int top_k = sel ? int(c.e->pkt->tensors[c.in->t[sel_op]].dims[1]) : 0;
+  std::vector<int> keys;
   std::vector<float> qabs(L), qr(RP), olat(L), sc;
   int64_t a, b;
   c.range(int64_t(io.rows) * H, a, b);
@@ -432,18 +440,29 @@ void op_mla_attn(const Ctx& c) {
       qabs[j] = s;
     }
     rope_head(qr.data(), qv + NP, rope + int64_t(pos) * RP, RP, RP, pair);
-    sc.resize(pos + 1);
+    keys.clear();
+    if (sel) {
+      for (int j = 0; j < top_k; ++j) {
+        const int t = sel[r * top_k + j];
+        if (t >= 0 && t <= pos) keys.push_back(t);
+      }
+    } else {
+      for (int t = 0; t <= pos; ++t) keys.push_back(t);
+    }
+    sc.resize(keys.size());
     float mx = -INFINITY;
-    for (int t = 0; t <= pos; ++t) {
+    for (size_t n = 0; n < keys.size(); ++n) {
+      const int t = keys[n];
       const int page = io.page_table[int64_t(slot) * io.max_pages + t / PLOW_KV_PAGE];
       const float* kr = cache + (int64_t(page) * PLOW_KV_PAGE + t % PLOW_KV_PAGE) * row;
-      sc[t] = (dotf(qabs.data(), kr, L) + dotf(qr.data(), kr + L, RP)) * scale;
-      mx = std::max(mx, sc[t]);
+      sc[n] = (dotf(qabs.data(), kr, L) + dotf(qr.data(), kr + L, RP)) * scale;
+      mx = std::max(mx, sc[n]);
     }
     float den = 0.f;
     std::fill(olat.begin(), olat.end(), 0.f);
-    for (int t = 0; t <= pos; ++t) {
-      const float p = std::exp(sc[t] - mx);
+    for (size_t n = 0; n < keys.size(); ++n) {
+      const int t = keys[n];
+      const float p = std::exp(sc[n] - mx);
       den += p;
       const int page = io.page_table[int64_t(slot) * io.max_pages + t / PLOW_KV_PAGE];
       const float* kr = cache + (int64_t(page) * PLOW_KV_PAGE + t % PLOW_KV_PAGE) * row;
@@ -451,6 +470,77 @@ void op_mla_attn(const Ctx& c) {
     }
     float* o = out + (r * H + h) * V;
     for (int d = 0; d < V; ++d) o[d] = dotf(wuv + int64_t(d) * L, olat.data(), L) / den;
+  }
+}
+
+// ---- sparse-attention indexer (golden, f32; runtime/common/dev_isa.h:516-534, 1083-1115) ----------------------------
+// Index key of every new row: LayerNorm (with bias) of the projected key, RoPE on the first `rot` dims (halves
+// pairing), stored in the paged index-key cache (the scale tensor is 1 on this backend).
+void op_dsa_index(const Ctx& c) {
+  float* cache = (float*)c.T(0);
+  float* cscale = (float*)c.T(1);
+  const float* k = (const float*)c.T(2);
+  const float* gamma = (const float*)c.T(3);
+  const float* beta = (const float*)c.T(4);
+  const float* rope = (const float*)c.T(5);
+  const int D = c.in->i[0], rot = c.in->i[1];
+  const StepIO& io = c.e->io;
+  std::vector<float> y(D);
+  int64_t a, b;
+  c.range(io.rows, a, b);
+  for (int64_t r = a; r < b; ++r) {
+    const int pos = io.pos[r], slot = io.seq[r];
+    const float* x = k + r * D;
+    float mean = 0.f;
+    for (int j = 0; j < D; ++j) mean += x[j];
+    mean /= D;
+    float var = 0.f;
+    for (int j = 0; j < D; ++j) var += (x[j] - mean) * (x[j] - mean);
+    const float rs = 1.0f / std::sqrt(var / D + 1e-6f);
+    for (int j = 0; j < D; ++j) y[j] = (x[j] - mean) * rs * gamma[j] + beta[j];
+    const int page = io.page_table[int64_t(slot) * io.max_pages + pos / PLOW_KV_PAGE];
+    const int64_t cell = int64_t(page) * PLOW_KV_PAGE + pos % PLOW_KV_PAGE;
+    rope_head(cache + cell * D, y.data(), rope + int64_t(pos) * rot, D, rot, 0);
+    if (cscale) cscale[cell] = 1.0f;
+  }
+}
+
+// Selection of every row: score[t] = sum_h w[h] relu(q_h . k_t) over the visible positions, the top_k best (ties to
+// the lower position), written in ascending position order and padded with -1.
+void op_dsa_topk(const Ctx& c) {
+  int32_t* sel = (int32_t*)c.T(0);
+  const float* q = (const float*)c.T(1);
+  const float* w = (const float*)c.T(2);
+  const float* cache = (const float*)c.T(3);
+  const float* rope = (const float*)c.T(5);
+  const int NH = c.in->i[0], D = c.in->i[1], K = c.in->i[2], rot = c.in->i[3];
+  const StepIO& io = c.e->io;
+  std::vector<float> qr(size_t(NH) * D), sc;
+  std::vector<int> order;
+  int64_t a, b;
+  c.range(io.rows, a, b);
+  for (int64_t r = a; r < b; ++r) {
+    const int pos = io.pos[r], slot = io.seq[r];
+    int32_t* out = sel + r * K;
+    const int n = pos + 1;
+    if (n <= K) {
+      for (int j = 0; j < K; ++j) out[j] = j < n ? j : -1;
+      continue;
+    }
+    for (int h = 0; h < NH; ++h) rope_head(qr.data() + size_t(h) * D, q + (r * NH + h) * D, rope + int64_t(pos) * rot, D, rot, 0);
+    sc.assign(n, 0.f);
+    for (int t = 0; t < n; ++t) {
+      const int page = io.page_table[int64_t(slot) * io.max_pages + t / PLOW_KV_PAGE];
+      const float* kt = cache + (int64_t(page) * PLOW_KV_PAGE + t % PLOW_KV_PAGE) * D;
+      float s = 0.f;
+      for (int h = 0; h < NH; ++h) s += w[r * NH + h] * std::max(0.f, dotf(qr.data() + size_t(h) * D, kt, D));
+      sc[t] = s;
+    }
+    order.resize(n);
+    for (int t = 0; t < n; ++t) order[t] = t;
+    std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return sc[x] > sc[y]; });
+    std::sort(order.begin(), order.begin() + K);
+    for (int j = 0; j < K; ++j) out[j] = order[j];
   }
 }
 
@@ -580,6 +670,8 @@ int exec_entry(Engine* e, const PlowInst* in, const PlowStreamEnt& se) {
     case PLOW_OP_MLA_KV_WRITE: op_mla_kv_write(c); return 0;
     case PLOW_OP_MLA_DECODE:
     case PLOW_OP_MLA_PREFILL: op_mla_attn(c); return 0;
+    case PLOW_OP_DSA_INDEX: op_dsa_index(c); return 0;
+    case PLOW_OP_DSA_TOPK: op_dsa_topk(c); return 0;
     case PLOW_OP_ROUTER_TOPK: op_router_topk(c); return 0;
     case PLOW_OP_MOE_GEMM: op_moe(c); return 0;
     default: return 100 + in->op;  // op not implemented on the CPU backend

@@ -313,3 +313,56 @@ def test_prefill_time_preemption_keeps_the_dispatcher_alive(tiny_assets, n_pages
     finally:
         mux.stop()
         eng.close()
+
+
+def test_sparse_attention_model_on_cpu_backend_matches_reference(tmp_path):
+    """The interpreter's golden indexer ops (index-key cache write, weighted-ReLU scores, exact top-k with ties to the
+    lower position) and sparse MLA attention: a model whose indexer keeps 64 of up to 150 visible keys, prefill + decode,
+    against the fp32 reference running its own indexer.  Both sides are fp32, so the selections coincide and the logits
+    agree to rounding; dense attention over all keys would not."""
+    import glob
+    from safetensors.torch import load_file
+    from plow_b200 import plowc
+    from plow_b200.compiler import packet as pk
+    from plow_b200.models import config, reference
+    from plow_b200.runtime.engine import TokenBatch
+    cfg = dict(model_type="glm_moe_dsa", hidden_size=256, num_attention_heads=4, num_hidden_layers=2,
+               q_lora_rank=64, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+               intermediate_size=512, first_k_dense_replace=1, n_routed_experts=8, n_shared_experts=1,
+               num_experts_per_tok=2, moe_intermediate_size=64, n_group=2, topk_group=1, scoring_func="sigmoid",
+               norm_topk_prob=True, routed_scaling_factor=2.5, topk_method="noaux_tc", rms_norm_eps=1e-6,
+               rope_theta=10000.0, vocab_size=512, tie_word_embeddings=False, max_position_embeddings=1024, eos_token_id=1,
+               index_n_heads=4, index_head_dim=32, index_topk=64, plow_dtype="f32", plow_kv_dtype="f32")
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=0)
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", arch="cpu", n_cu=4, max_rows=256, decode_rungs=[1, 2], max_seqs=4)
+    eng = CpuEngine(tmp_path / "assets", max_slots=2, max_ctx=256)
+    assert any(i.op == pk.Op.DSA_TOPK for i in eng.packet.programs[0].insts)
+    state = {}
+    for f in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        state.update(load_file(f))
+    state = {k: v.float() for k, v in state.items()}
+    spec = config.spec_from_config(cfg)
+    ref = reference.ReferenceModel(spec, state)
+    dense = reference.ReferenceModel(config.spec_from_config({**cfg, "index_n_heads": 0, "model_type": "deepseek_v3"}), state)
+    rng = np.random.default_rng(2)
+    p = rng.integers(0, 512, 150).tolist()
+    eng.begin_slot(0, p)
+    eng.reserve(0, len(p) + 4)
+    r = eng.step(TokenBatch(np.asarray(p, np.int32), np.arange(len(p), dtype=np.int32), np.zeros(len(p), np.int32),
+                            np.asarray([len(p) - 1], np.int32), want_logits=True))
+    want = ref.forward(torch.tensor(p))[-1]
+    err = (torch.from_numpy(r.logits[0]) - want).abs().max().item()
+    assert err < 5e-4 * max(1.0, want.abs().max().item()), err
+    assert (dense.forward(torch.tensor(p))[-1] - want).abs().max().item() > 50 * err      # sparse is not dense
+    eng.commit(0, p)
+    toks = list(p)
+    nxt = int(want.argmax())
+    for _ in range(2):
+        r = eng.step(TokenBatch(np.asarray([nxt], np.int32), np.asarray([len(toks)], np.int32), np.zeros(1, np.int32), np.zeros(1, np.int32),
+                                decode=True, want_logits=True))
+        eng.commit(0, [nxt])
+        toks.append(nxt)
+        want = ref.forward(torch.tensor(toks))[-1]
+        assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 5e-4 * max(1.0, want.abs().max().item())
+        nxt = int(want.argmax())
+    eng.close()
