@@ -98,9 +98,16 @@ class Graph:
 # ------------------------------------------------------------------------------------------------
 # builders
 # ------------------------------------------------------------------------------------------------
-def build_graph(spec: ModelSpec, tp: int = 1, ep: int = 1, rank: int = 0) -> Graph:
+def build_graph(spec: ModelSpec, tp: int = 1, ep: int = 1, rank: int = 0, emit_hidden: bool = False) -> Graph:
+    """``emit_hidden`` makes the decoder's normed hidden state of every row an output (``out.hidden`` [R, H]): the input
+    of a prediction-module drafter.  A spec with ``role == "mtp"`` (ModelSpec.drafter_spec) builds that drafter: rows
+    carry a token and a hidden state (``in.hidden``), ``x = eh_proj([enorm(embed(token)) | hnorm(hidden)])`` runs through
+    one decoder block with a KV cache of its own, and the outputs are the draft ids / logits and the block's hidden state
+    of the sampled rows (``out.hidden`` [S, H]) for the next draft of the chain
+    (reference: crates/devgen/src/mtp.rs, crates/plowrt/src/exec/gpu/spec.rs:1-12)."""
     g = Graph(spec, tp, ep, rank)
     H, V = spec.hidden, spec.vocab
+    ndt = "f32" if spec.dtype == "f32" else "bf16"
     ids = g.value("in.ids", (R,), "i32", "input")
     g.value("in.pos", (R,), "i32", "input")
     g.value("in.seq", (R,), "i32", "input")
@@ -108,36 +115,30 @@ def build_graph(spec: ModelSpec, tp: int = 1, ep: int = 1, rank: int = 0) -> Gra
     emb = g.weight("model.embed_tokens.weight", (V, H))
     x = g.tmp("x", (R, H))
     g.add("embed", [emb, ids], [x], scale=spec.embed_scale)
+    mtp = spec.role == "mtp"
+    if mtp:
+        p0 = f"model.layers.{spec.name_base}"
+        hid = g.value("in.hidden", (R, H), spec.dtype, "input")
+        en, hn = g.tmp("en", (R, H)), g.tmp("hn", (R, H))
+        g.add("rmsnorm", [x, g.weight(f"{p0}.enorm.weight", (H,), dtype=ndt)], [en], eps=spec.rms_eps, plus_one=spec.norm_plus_one)
+        g.add("rmsnorm", [hid, g.weight(f"{p0}.hnorm.weight", (H,), dtype=ndt)], [hn], eps=spec.rms_eps, plus_one=spec.norm_plus_one)
+        # eh_proj([e | h]) as two projections over the column halves of the checkpoint matrix: no concatenation pass
+        halves = []
+        for nm, src, lo in (("e", en, 0), ("h", hn, H)):
+            w = g.value(f"cols/{p0}.eh_proj.weight.{nm}", (H, H), g.weight_dtype(), "derived",
+                        meta=dict(op="cols", src=f"{p0}.eh_proj.weight", start=lo, stop=lo + H))
+            y = g.tmp("y", (R, H))
+            g.add("linear", [src, w], [y])
+            halves.append(y)
+        x = g.tmp("x", (R, H))
+        g.add("add", halves, [x])
     for li, layer in enumerate(spec.layers):
-        p = f"model.layers.{li}"
-        ln1 = g.weight(f"{p}.input_layernorm.weight", (H,), dtype="f32" if spec.dtype == "f32" else "bf16")
-        h = g.tmp("h", (R, H))
-        g.add("rmsnorm", [x, ln1], [h], layer=li, eps=spec.rms_eps, plus_one=spec.norm_plus_one)
-        if layer.attn.kind == "gqa":
-            o = _gqa_attention(g, li, p, h, layer.attn)
-        elif layer.attn.kind == "mla":
-            o = _mla_attention(g, li, p, h, layer.attn)
-        else:
-            o = _gdn_attention(g, li, p, h, layer.attn)
-        if tp > 1:
-            o = _xreduce(g, o, li)
-        x2 = g.tmp("x", (R, H))
-        g.add("add", [x, o], [x2], layer=li)
-        ln2 = g.weight(f"{p}.post_attention_layernorm.weight", (H,), dtype="f32" if spec.dtype == "f32" else "bf16")
-        h2 = g.tmp("h", (R, H))
-        g.add("rmsnorm", [x2, ln2], [h2], layer=li, eps=spec.rms_eps, plus_one=spec.norm_plus_one)
-        if layer.ffn.kind == "dense":
-            d = _dense_ffn(g, li, f"{p}.mlp", h2, layer.ffn.inter)
-            if tp > 1:
-                d = _xreduce(g, d, li)
-        else:
-            d = _moe_ffn(g, li, f"{p}.mlp", h2, layer.ffn)
-        x3 = g.tmp("x", (R, H))
-        g.add("add", [x2, d], [x3], layer=li)
-        x = x3
-    fn = g.weight("model.norm.weight", (H,), dtype="f32" if spec.dtype == "f32" else "bf16")
-    hf = g.tmp("h", (R, H))
+        x = _decoder_layer(g, li, f"model.layers.{spec.name_base + li}", x, layer)
+    fn = g.weight(f"model.layers.{spec.name_base}.shared_head.norm.weight" if mtp else "model.norm.weight", (H,), dtype=ndt)
+    hf = g.value("out.hidden", (R, H), spec.dtype, "output") if emit_hidden and not mtp else g.tmp("h", (R, H))
     g.add("rmsnorm", [x, fn], [hf], eps=spec.rms_eps, plus_one=spec.norm_plus_one)
+    if mtp:
+        g.add("row_gather", [x, "in.sample_rows"], [g.value("out.hidden", (S, H), spec.dtype, "output")])
     hs = g.tmp("hs", (S, H))
     g.add("row_gather", [hf, "in.sample_rows"], [hs])
     logits = g.value("out.logits", (S, V), "f32", "output")
@@ -159,6 +160,38 @@ def build_graph(spec: ModelSpec, tp: int = 1, ep: int = 1, rank: int = 0) -> Gra
         g.add("argmax", [logits], [out_ids])
     g.check_topological()
     return g
+
+
+def _decoder_layer(g: Graph, li: int, p: str, x: str, layer) -> str:
+    """One pre-norm decoder block: ``li`` indexes its KV cache / recurrent state, ``p`` names its checkpoint tensors."""
+    spec, tp = g.spec, g.tp
+    H = spec.hidden
+    ndt = "f32" if spec.dtype == "f32" else "bf16"
+    ln1 = g.weight(f"{p}.input_layernorm.weight", (H,), dtype=ndt)
+    h = g.tmp("h", (R, H))
+    g.add("rmsnorm", [x, ln1], [h], layer=li, eps=spec.rms_eps, plus_one=spec.norm_plus_one)
+    if layer.attn.kind == "gqa":
+        o = _gqa_attention(g, li, p, h, layer.attn)
+    elif layer.attn.kind == "mla":
+        o = _mla_attention(g, li, p, h, layer.attn)
+    else:
+        o = _gdn_attention(g, li, p, h, layer.attn)
+    if tp > 1:
+        o = _xreduce(g, o, li)
+    x2 = g.tmp("x", (R, H))
+    g.add("add", [x, o], [x2], layer=li)
+    ln2 = g.weight(f"{p}.post_attention_layernorm.weight", (H,), dtype=ndt)
+    h2 = g.tmp("h", (R, H))
+    g.add("rmsnorm", [x2, ln2], [h2], layer=li, eps=spec.rms_eps, plus_one=spec.norm_plus_one)
+    if layer.ffn.kind == "dense":
+        d = _dense_ffn(g, li, f"{p}.mlp", h2, layer.ffn.inter)
+        if tp > 1:
+            d = _xreduce(g, d, li)
+    else:
+        d = _moe_ffn(g, li, f"{p}.mlp", h2, layer.ffn)
+    x3 = g.tmp("x", (R, H))
+    g.add("add", [x2, d], [x3], layer=li)
+    return x3
 
 
 def _xreduce(g: Graph, v: str, li: int) -> str:

@@ -40,6 +40,8 @@ KNOBS = [
     Knob("tbt_target_ms", "PLOW_TBT_TARGET_MS", "runtime", "float>=0", 0.0, "time-between-tokens budget for prefill sizing"),
     Knob("ride", "PLOW_RIDE", "runtime", "bool", True, "decode rows ride prefill launches (mixed steps)"),
     Knob("spec_depth", "PLOW_SPEC_DEPTH", "runtime", "int>=0", 0, "speculative decoding depth for greedy requests (0 = off)"),
+    Knob("spec_drafter", "PLOW_SPEC_DRAFTER", "runtime", "enum:auto|ngram|mtp", "auto",
+         "drafter of the speculative steps: the checkpoint's prediction module (assets/mtp, plowc --mtp) or prompt lookup; auto = mtp when compiled"),
     Knob("multi_step", "PLOW_MULTI_STEP", "runtime", "int>=1", 1, "greedy decode steps per engine call (tokens fed back on the device; 1 = off)"),
     Knob("device_interp", "PLOW_DEVICE_INTERP", "runtime", "bool", True, "run row-op segments in the persistent on-device interpreter"),
     Knob("pd", "PLOW_PD", "runtime", "bool", False, "prefill/decode disaggregation inside one server (two engines, KV image hand-off)"),
@@ -102,6 +104,9 @@ class RuntimeConfig:
             _check(k, v)
             vals[k.id] = v
         return RuntimeConfig(vals)
+
+    def replace(self, **kw) -> "RuntimeConfig":
+        return RuntimeConfig({**self.values, **kw})
 
     def __getattr__(self, name):
         try:

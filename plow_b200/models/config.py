@@ -93,6 +93,19 @@ class ModelSpec:
     max_ctx: int = 4096
     bos_token_id: int | None = None
     eos_token_ids: list = field(default_factory=list)
+    mtp_layers: int = 0           # next-token-prediction modules behind the decoder stack (num_nextn_predict_layers)
+    role: str = "main"            # "mtp": this spec is one prediction module compiled as a drafter of its own
+    name_base: int = 0            # checkpoint index of layers[0] (model.layers.<name_base + i>)
+
+    def drafter_spec(self, k: int = 0) -> "ModelSpec":
+        """The k-th prediction module as a one-layer model of its own.  Its block has the plan of the last decoder layer
+        and its weights live at model.layers.<n_layers + k> (enorm, hnorm, eh_proj, shared_head.norm and the block)."""
+        import copy
+        if k >= self.mtp_layers:
+            raise ValueError(f"the checkpoint has {self.mtp_layers} prediction module(s), asked for {k}")
+        d = copy.deepcopy(self)
+        d.layers, d.n_layers, d.mtp_layers, d.role, d.name_base = [copy.deepcopy(self.layers[-1])], 1, 0, "mtp", self.n_layers + k
+        return d
 
     def to_json(self) -> str:
         return json.dumps(asdict(self), sort_keys=True)
@@ -203,7 +216,8 @@ def _dense_gqa(cfg: dict, mt: str) -> ModelSpec:
         rope=_rope_from(cfg, hd), layers=[LayerSpec(attn, ffn) for _ in range(n_layers)],
         norm_plus_one=gem, embed_scale=(h ** 0.5 if gem else 1.0),
         dtype=cfg.get("plow_dtype", "bf16"), weight_quant=_quant(cfg), kv_dtype=cfg.get("plow_kv_dtype", cfg.get("plow_dtype", "bf16")),
-        max_ctx=int(cfg.get("max_position_embeddings", 4096)), bos_token_id=cfg.get("bos_token_id"), eos_token_ids=_eos(cfg))
+        max_ctx=int(cfg.get("max_position_embeddings", 4096)), bos_token_id=cfg.get("bos_token_id"), eos_token_ids=_eos(cfg),
+        mtp_layers=int(cfg.get("num_nextn_predict_layers") or 0))
 
 
 def _mla_moe(cfg: dict, mt: str) -> ModelSpec:
@@ -230,7 +244,8 @@ def _mla_moe(cfg: dict, mt: str) -> ModelSpec:
         rms_eps=float(cfg.get("rms_norm_eps", 1e-6)), tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
         rope=_rope_from(cfg, cfg["qk_rope_head_dim"], pair="interleaved"), layers=layers,
         dtype=cfg.get("plow_dtype", "bf16"), weight_quant=_quant(cfg), kv_dtype=cfg.get("plow_kv_dtype", "fp8" if _quant(cfg) != "none" else cfg.get("plow_dtype", "bf16")),
-        max_ctx=int(cfg.get("max_position_embeddings", 4096)), bos_token_id=cfg.get("bos_token_id"), eos_token_ids=_eos(cfg))
+        max_ctx=int(cfg.get("max_position_embeddings", 4096)), bos_token_id=cfg.get("bos_token_id"), eos_token_ids=_eos(cfg),
+        mtp_layers=int(cfg.get("num_nextn_predict_layers") or 0))
 
 
 def _gdn_hybrid(cfg: dict, mt: str) -> ModelSpec:

@@ -78,26 +78,53 @@ class ReferenceModel:
     @torch.no_grad()
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
         """ids [T] -> logits [T, V] (float32)."""
+        return self.forward_hidden(ids)[0]
+
+    @torch.no_grad()
+    def forward_hidden(self, ids: torch.Tensor):
+        """ids [T] -> (logits [T, V] float32, hidden [T, H] after the final norm: what a prediction module reads)."""
         spec = self.spec
         T = ids.shape[0]
         self.route_margin_last = float("inf")     # smallest routing gap of the last row over the MoE layers of this call
         pos = torch.arange(T, device=self.device)
         x = self.w["model.embed_tokens.weight"][ids] * spec.embed_scale
         for li, layer in enumerate(spec.layers):
-            p = f"model.layers.{li}"
-            h = rmsnorm(x, self.w[f"{p}.input_layernorm.weight"], spec.rms_eps, spec.norm_plus_one)
-            if layer.attn.kind == "gqa":
-                o = self._gqa(p, h, pos, layer.attn)
-            elif layer.attn.kind == "mla":
-                o = self._mla(p, h, pos, layer.attn)
-            else:
-                o = self._gdn(p, h, layer.attn)
-            x = x + o
-            h = rmsnorm(x, self.w[f"{p}.post_attention_layernorm.weight"], spec.rms_eps, spec.norm_plus_one)
-            x = x + (self._dense(f"{p}.mlp", h) if layer.ffn.kind == "dense" else self._moe(f"{p}.mlp", h, layer.ffn))
+            x = self._block(f"model.layers.{li}", x, pos, layer)
         x = rmsnorm(x, self.w["model.norm.weight"], spec.rms_eps, spec.norm_plus_one)
-        head = self.w["model.embed_tokens.weight"] if spec.tie_embeddings else self.w["lm_head.weight"]
-        return (x @ head.t()).float()
+        return (x @ self._head().t()).float(), x
+
+    @torch.no_grad()
+    def mtp_forward(self, next_ids: torch.Tensor, hidden: torch.Tensor, k: int = 0):
+        """Prediction module k over a whole sequence.  Row i reads ``hidden[i]`` (the decoder's normed hidden state at
+        position i, or this module's own output for a chained draft) and ``next_ids[i]`` (token i + 1); its logits
+        predict token i + 2.  Returns (logits [T, V] float32, the module's hidden [T, H] before its head norm).
+        Weights: model.layers.<n_layers + k>.{enorm, hnorm, eh_proj, shared_head.norm} and a decoder block with the plan
+        of the last layer; the embedding and the output head are the decoder's own."""
+        spec = self.spec
+        p = f"model.layers.{spec.n_layers + k}"
+        pos = torch.arange(next_ids.shape[0], device=self.device)
+        e = rmsnorm(self.w["model.embed_tokens.weight"][next_ids] * spec.embed_scale, self.w[f"{p}.enorm.weight"], spec.rms_eps, spec.norm_plus_one)
+        h = rmsnorm(hidden.to(e.dtype), self.w[f"{p}.hnorm.weight"], spec.rms_eps, spec.norm_plus_one)
+        x = torch.cat([e, h], dim=-1) @ self.w[f"{p}.eh_proj.weight"].t()
+        x = self._block(p, x, pos, spec.layers[-1])
+        hn = rmsnorm(x, self.w[f"{p}.shared_head.norm.weight"], spec.rms_eps, spec.norm_plus_one)
+        return (hn @ self._head().t()).float(), x
+
+    def _head(self):
+        return self.w["model.embed_tokens.weight"] if self.spec.tie_embeddings else self.w["lm_head.weight"]
+
+    def _block(self, p, x, pos, layer):
+        spec = self.spec
+        h = rmsnorm(x, self.w[f"{p}.input_layernorm.weight"], spec.rms_eps, spec.norm_plus_one)
+        if layer.attn.kind == "gqa":
+            o = self._gqa(p, h, pos, layer.attn)
+        elif layer.attn.kind == "mla":
+            o = self._mla(p, h, pos, layer.attn)
+        else:
+            o = self._gdn(p, h, layer.attn)
+        x = x + o
+        h = rmsnorm(x, self.w[f"{p}.post_attention_layernorm.weight"], spec.rms_eps, spec.norm_plus_one)
+        return x + (self._dense(f"{p}.mlp", h) if layer.ffn.kind == "dense" else self._moe(f"{p}.mlp", h, layer.ffn))
 
     # ---- blocks --------------------------------------------------------------------------------
     def _dense(self, p, h):
@@ -261,9 +288,15 @@ def param_shapes(spec: ModelSpec) -> dict:
     s = {"model.embed_tokens.weight": (V, H), "model.norm.weight": (H,)}
     if not spec.tie_embeddings:
         s["lm_head.weight"] = (V, H)
-    for li, layer in enumerate(spec.layers):
+    blocks = list(enumerate(spec.layers)) + [(spec.n_layers + k, spec.layers[-1]) for k in range(spec.mtp_layers)]
+    for li, layer in blocks:
         p = f"model.layers.{li}"
         a, f = layer.attn, layer.ffn
+        if li >= spec.n_layers:      # a prediction module: two input norms, the [embedding | hidden] projection, a head norm
+            s[f"{p}.enorm.weight"] = (H,)
+            s[f"{p}.hnorm.weight"] = (H,)
+            s[f"{p}.eh_proj.weight"] = (H, 2 * H)
+            s[f"{p}.shared_head.norm.weight"] = (H,)
         s[f"{p}.input_layernorm.weight"] = (H,)
         s[f"{p}.post_attention_layernorm.weight"] = (H,)
         if a.kind == "gqa":

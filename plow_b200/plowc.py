@@ -23,10 +23,15 @@ from .models.config import load_spec
 
 def compile_dir(hf_dir, out_dir, gpu="b200", arch="sm_100a", num_gpus=1, parallel="tp", n_cu=None,
                 max_rows=8192, prefill_buckets=None, decode_rungs=None, max_seqs=64, disable_rules=(),
-                emit_trace=False) -> dict:
+                emit_trace=False, mtp=False, _spec=None) -> dict:
+    """``mtp=True`` (the checkpoint must carry prediction modules, ``num_nextn_predict_layers``) also writes a drafter
+    packet directory ``<out>/mtp`` (the first module as a one-layer model that reads a token and a hidden state per row)
+    and makes the main packet return its normed hidden states (``out.hidden``) for it."""
     hwspec.check_arch(arch)
     hw = hwspec.lookup("cpu" if arch == "cpu" else gpu)
-    spec = load_spec(hf_dir)
+    spec = _spec or load_spec(hf_dir)
+    if mtp and spec.role == "main" and not spec.mtp_layers:
+        raise ValueError("--mtp: the checkpoint's config.json names no prediction module (num_nextn_predict_layers)")
     if parallel not in ("tp", "ep", "dp"):
         raise ValueError(f"--parallel {parallel}: supported strategies are tp, ep (experts over ranks, attention data-parallel) and dp")
     tp = num_gpus if parallel == "tp" else 1
@@ -44,7 +49,7 @@ def compile_dir(hf_dir, out_dir, gpu="b200", arch="sm_100a", num_gpus=1, paralle
                   parallel=parallel, buckets=buckets, ranks=[])
     n_ranks = num_gpus if parallel in ("tp", "ep") else 1
     for rank in range(n_ranks):
-        g = graph.build_graph(spec, tp=tp, ep=ep, rank=rank)
+        g = graph.build_graph(spec, tp=tp, ep=ep, rank=rank, emit_hidden=bool(mtp))
         n_prim = len(g.nodes)
         sites = rewrite.fuse(g, disable=set(disable_rules))
         pkt = emit.emit_packet(g, sites, hw, n_cu, buckets, rank=rank)
@@ -74,6 +79,11 @@ def compile_dir(hf_dir, out_dir, gpu="b200", arch="sm_100a", num_gpus=1, paralle
     for fn in ("tokenizer.json", "tokenizer_config.json", "chat_template.jinja", "generation_config.json"):
         if (src / fn).exists():
             shutil.copy(src / fn, out / fn)
+    if mtp and spec.role == "main":
+        report["mtp"] = compile_dir(hf_dir, out / "mtp", gpu=gpu, arch=arch, num_gpus=num_gpus, parallel=parallel, n_cu=n_cu,
+                                    max_rows=max_rows, prefill_buckets=prefill_buckets, decode_rungs=decode_rungs,
+                                    max_seqs=max_seqs, disable_rules=disable_rules, _spec=spec.drafter_spec())
+        (out / "build.json").write_text(json.dumps(report, indent=1))
     return report
 
 
@@ -93,6 +103,7 @@ def main(argv=None) -> int:
     ap.add_argument("--prefill-buckets", type=lambda s: [int(x) for x in s.split(",")])
     ap.add_argument("--decode-rungs", type=lambda s: [int(x) for x in s.split(",")])
     ap.add_argument("--disable-rule", action="append", default=[])
+    ap.add_argument("--mtp", action="store_true", help="also compile the checkpoint's prediction module as a drafter (<out>/mtp)")
     v = sub.add_parser("viz", help="write an HTML view of the fused graph")
     v.add_argument("hf_dir")
     v.add_argument("--out", default="graph.html")
@@ -146,7 +157,7 @@ def main(argv=None) -> int:
         ap.error("--hf-dir is required")
     try:
         rep = compile_dir(args.hf_dir, args.out, args.gpu, args.arch, args.num_gpus, args.parallel, args.n_cu,
-                          args.max_rows, args.prefill_buckets, args.decode_rungs, args.max_seqs, args.disable_rule)
+                          args.max_rows, args.prefill_buckets, args.decode_rungs, args.max_seqs, args.disable_rule, mtp=args.mtp)
     except (ValueError, KeyError, RuntimeError) as e:
         print(f"plowc: error: {e}", file=sys.stderr)
         return 2

@@ -45,6 +45,14 @@ def make_entry(name, assets, cfg):
     sched = SchedConfig(token_budget=min(cfg.token_budget, eng.max_rows(False)), objective=cfg.objective,
                         tbt_target_ms=cfg.tbt_target_ms, queue_ttl_s=cfg.queue_ttl_s, ride=cfg.ride, spec_depth=cfg.spec_depth, multi_step=cfg.multi_step)
     mux = ModelMux(eng, tok, sched)
+    mtp_dir = Path(assets) / "mtp"
+    if cfg.spec_depth > 0 and cfg.spec_drafter != "ngram":
+        if (mtp_dir / "model.pkt").exists():
+            # the prediction module runs in an engine of its own (own KV pages, same device) behind the chain drafter
+            from .runtime.spec import MtpDrafter
+            mux.set_drafter(MtpDrafter(load_engine(mtp_dir, cfg.replace(prefix_cache=False))))
+        elif cfg.spec_drafter == "mtp":
+            raise SystemExit(f"plowrt: --spec-drafter mtp: {mtp_dir} does not exist (compile with plowc --mtp)")
     if cfg.pd:
         # prefill / decode disaggregation: this engine only prefills; a second engine (the next GPU when there is one)
         # imports each sequence's KV image and decodes it
@@ -61,7 +69,7 @@ def cmd_serve(args) -> int:
     from .serve.app import AppState, create_app
     cfg = cfgmod.RuntimeConfig.load(cli=dict(host=args.host, port=args.port, max_slots=args.max_slots, max_ctx=args.max_ctx,
                                              backend=args.backend, objective=args.objective, trace=args.trace or None,
-                                             api_keys=args.api_key or None, dp=args.dp, spec_depth=args.spec_depth, multi_step=args.multi_step, pd=args.pd or None))
+                                             api_keys=args.api_key or None, dp=args.dp, spec_depth=args.spec_depth, spec_drafter=args.spec_drafter, multi_step=args.multi_step, pd=args.pd or None))
     state = AppState(api_keys=cfg.api_keys, timeline=Timeline(cfg.trace), loader=lambda n, p: make_entry(n, p, cfg))
     name = args.name or Path(args.assets).resolve().name
     n_ranks, mode = (args.ep, "ep") if args.ep else (args.tp, "tp") if args.tp else (args.dp_procs, "dp") if args.dp_procs else (0, "")
@@ -210,6 +218,7 @@ def main(argv=None) -> int:
     s.add_argument("--backend")
     s.add_argument("--objective")
     s.add_argument("--spec-depth", type=int, dest="spec_depth")
+    s.add_argument("--spec-drafter", dest="spec_drafter", choices=["auto", "ngram", "mtp"])
     s.add_argument("--multi-step", type=int, dest="multi_step", help="greedy decode steps per engine call (default 1)")
     s.add_argument("--pd", action="store_true", help="prefill on one engine, decode on a second one (KV image hand-off)")
     s.add_argument("--dp", type=int)

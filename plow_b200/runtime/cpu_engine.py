@@ -76,6 +76,9 @@ class CpuEngine(EngineBase):
         self.in_sample = np.zeros(max_rows, dtype=np.int32)
         self.out_ids = np.zeros(max_rows, dtype=np.int32)
         self.out_logits = np.zeros((max_rows, self.spec.vocab), dtype=np.float32)
+        self.in_hidden = np.zeros((max_rows, self.spec.hidden), dtype=np.float32)
+        self.out_hidden = np.zeros((max_rows, self.spec.hidden), dtype=np.float32)
+        self.hidden_rows = None        # "rows" | "samples": which rows out.hidden carries (None: the packet has none)
         for h, t in enumerate(pkt.tensors):
             tc = t.tclass
             if tc in (pk.TClass.WEIGHT, pk.TClass.DERIVED):
@@ -89,9 +92,11 @@ class CpuEngine(EngineBase):
                 self._bind(h, np.zeros(dims, dtype=np.float32))
             elif tc == pk.TClass.INPUT:
                 self._bind(h, {"in.ids": self.in_ids, "in.pos": self.in_pos, "in.seq": self.in_seq,
-                               "in.sample_rows": self.in_sample}[t.name])
+                               "in.sample_rows": self.in_sample, "in.hidden": self.in_hidden}[t.name])
             elif tc == pk.TClass.OUTPUT:
-                self._bind(h, {"out.ids": self.out_ids, "out.logits": self.out_logits}[t.name])
+                self._bind(h, {"out.ids": self.out_ids, "out.logits": self.out_logits, "out.hidden": self.out_hidden}[t.name])
+                if t.name == "out.hidden":
+                    self.hidden_rows = "rows" if t.dims[0] == -1 else "samples"
 
     # ---- step ----------------------------------------------------------------------------------
     def step(self, batch: TokenBatch) -> StepResult:
@@ -101,6 +106,8 @@ class CpuEngine(EngineBase):
         self.in_pos[:rows] = batch.pos
         self.in_seq[:rows] = batch.seq
         self.in_sample[:ns] = batch.sample_rows
+        if batch.hidden is not None:
+            self.in_hidden[:rows] = batch.hidden
         io = StepIO(rows=rows, n_sample=ns, page_table=self.page_table.ctypes.data,
                     max_pages=self.max_pages_per_seq, kvlen=self.kvlen.ctypes.data, n_slots=self.max_slots,
                     pos=self.in_pos.ctypes.data, seq=self.in_seq.ctypes.data)
@@ -108,7 +115,9 @@ class CpuEngine(EngineBase):
         if rc != 0:
             raise EngineError(f"cpu interpreter failed with code {rc}", fatal=rc == 2)
         return StepResult(ids=self.out_ids[:ns].copy(),
-                          logits=self.out_logits[:ns].copy() if batch.want_logits else None)
+                          logits=self.out_logits[:ns].copy() if batch.want_logits else None,
+                          hidden=self.out_hidden[:rows if self.hidden_rows == "rows" else ns].copy()
+                          if batch.want_hidden and self.hidden_rows else None)
 
     def kv_arrays(self) -> dict:
         return {t.name: self._keep[h] for h, t in enumerate(self.packet.tensors) if t.tclass == pk.TClass.KV}

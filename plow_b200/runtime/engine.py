@@ -24,6 +24,8 @@ class TokenBatch:
     sample_rows: np.ndarray   # int32 [n_sample] rows whose logits are wanted
     decode: bool = False      # one row per sequence
     want_logits: bool = False
+    hidden: np.ndarray | None = None   # [rows, H] per-row hidden state (a prediction-module drafter's second input)
+    want_hidden: bool = False          # return the packet's out.hidden rows in the StepResult
 
     @property
     def rows(self) -> int:
@@ -34,6 +36,7 @@ class TokenBatch:
 class StepResult:
     ids: np.ndarray                    # int32 [n_sample] greedy tokens
     logits: np.ndarray | None = None   # float32 [n_sample, V] when requested
+    hidden: np.ndarray | None = None   # out.hidden when requested: [rows, H] (a decoder) or [n_sample, H] (a drafter)
     device_ms: float = 0.0
 
 

@@ -207,6 +207,10 @@ class GpuEngine(EngineBase):
         self.h_out = torch.zeros(max_rows, dtype=I32).pin_memory()
         self.d_out_ids = torch.zeros(max_rows, dtype=I32, device=dev)
         self.d_logits = None
+        # hidden-state input (a prediction-module drafter's rows) and output (what such a drafter reads): bound per
+        # program as row views in _prepare
+        self.d_hidden_in = self.d_hidden_out = None
+        self.hidden_rows = None           # "rows" | "samples": which rows out.hidden carries
         for h, t in enumerate(pkt.tensors):
             tc = t.tclass
             if tc in (pk.TClass.WEIGHT, pk.TClass.DERIVED):
@@ -228,10 +232,18 @@ class GpuEngine(EngineBase):
                 dims = [self.max_slots + 1 if d == -4 else int(d) for d in t.dims]
                 self.static[h] = torch.zeros(dims, dtype=_TORCH_DT[pk.DType(t.dtype)], device=dev)
             elif tc == pk.TClass.INPUT:
+                if t.name == "in.hidden":
+                    self.d_hidden_in = torch.zeros(max_rows, self.spec.hidden, dtype=_TORCH_DT[pk.DType(t.dtype)], device=dev)
+                    self.static[h] = self.d_hidden_in
+                    continue
                 self.static[h] = self.d_in[{"in.ids": 0, "in.pos": 1, "in.seq": 2, "in.sample_rows": 3}[t.name]]
             elif tc == pk.TClass.OUTPUT:
                 if t.name == "out.ids":
                     self.static[h] = self.d_out_ids
+                elif t.name == "out.hidden":
+                    self.d_hidden_out = torch.zeros(max_rows, self.spec.hidden, dtype=_TORCH_DT[pk.DType(t.dtype)], device=dev)
+                    self.static[h] = self.d_hidden_out
+                    self.hidden_rows = "rows" if t.dims[0] == -1 else "samples"
                 else:
                     self.d_logits = torch.zeros(max(p.rows if p.role == pk.Role.DECODE else min(p.rows, self.buckets.get("max_seqs", 64))
                                                     for p in pkt.programs), self.spec.vocab, dtype=F32, device=dev)
@@ -271,6 +283,8 @@ class GpuEngine(EngineBase):
                 dt = _TORCH_DT[pk.DType(t.dtype)]
                 n = int(np.prod(dims)) * torch.empty((), dtype=dt).element_size()
                 st.t[h] = arena[prog.actmap[h]:prog.actmap[h] + n].view(dt).view(dims)
+            elif t.name in ("in.hidden", "out.hidden"):
+                st.t[h] = self.static[h][:samples if t.dims[0] == -2 else rows]      # handlers take the row count from the shape
         # which activations feed an e4m3 GEMM: their producer emits the quantised twin in the same pass
         for ins in prog.insts:
             if ins.op in (Op.GEMM, Op.GEMM_XREDUCE) and ins.i[2] & pk.GEMM_FP8_BLOCK:
@@ -966,6 +980,9 @@ class GpuEngine(EngineBase):
         self._upload_pages()
         self.d_in[:, :R].copy_(hin[:, :R], non_blocking=True)
         torch.add(self.d_in[1, :R], 1, out=self.d_kvlen_row[:R])
+        if batch.hidden is not None and self.d_hidden_in is not None and rows:
+            hid = batch.hidden if torch.is_tensor(batch.hidden) else torch.from_numpy(np.ascontiguousarray(batch.hidden))
+            self.d_hidden_in[:rows].copy_(hid[:rows], non_blocking=True)
         self._mla_plan = None
         st.scratch["dsa_dense_ok"] = False
         try:
@@ -1076,6 +1093,9 @@ class GpuEngine(EngineBase):
         self._upload_pages()
         self.d_in[:, :R].copy_(hin[:, :R], non_blocking=True)
         torch.add(self.d_in[1, :R], 1, out=self.d_kvlen_row[:R])
+        if batch.hidden is not None and self.d_hidden_in is not None and rows:
+            hid = batch.hidden if torch.is_tensor(batch.hidden) else torch.from_numpy(np.ascontiguousarray(batch.hidden))
+            self.d_hidden_in[:rows].copy_(hid[:rows], non_blocking=True)
         self._mla_plan = None
         self._gdn_plan = self._plan_gdn_prefill(batch, R) if (not decode and rows > 0 and self._has_gdn) else None
         # eager (prefill) steps of a sparse-attention model whose positions all lie below top_k attend densely
@@ -1111,4 +1131,7 @@ class GpuEngine(EngineBase):
             raise EngineError(str(e), fatal=False)
         self.step_ms_last = ev0.elapsed_time(ev1)
         logits = self.d_logits[:ns].float().cpu().numpy() if batch.want_logits else None
-        return StepResult(ids=self.h_out[:ns].numpy().copy(), logits=logits, device_ms=self.step_ms_last)
+        hidden = None
+        if batch.want_hidden and self.d_hidden_out is not None:
+            hidden = self.d_hidden_out[:rows if self.hidden_rows == "rows" else ns].clone()      # stays on the device
+        return StepResult(ids=self.h_out[:ns].numpy().copy(), logits=logits, device_ms=self.step_ms_last, hidden=hidden)

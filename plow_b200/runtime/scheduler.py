@@ -341,7 +341,7 @@ class ModelMux:
         decode mux, which imports the image and continues (reference: serve/pd.rs:1-8)."""
         from .kv_image import export_slot
         img = export_slot(self.engine, r.slot)
-        self.engine.retire_slot(r.slot)
+        self._retire(r.slot)
         del self.live[r.slot]
         self.free_slots.append(r.slot)
         r.slot = -1
@@ -357,7 +357,7 @@ class ModelMux:
             try:
                 import_slot(self.engine, slot, img)
             except OutOfPages:
-                self.engine.retire_slot(slot)
+                self._retire(slot)
                 self.free_slots.append(slot)
                 return                                   # retry when pages free up
             self.adopt_q.get_nowait()
@@ -448,7 +448,7 @@ class ModelMux:
 
     def _drop_session(self, sid: str) -> None:
         slot, _ = self.retained.pop(sid)
-        self.engine.retire_slot(slot)
+        self._retire(slot)
         self.free_slots.append(slot)
 
     def _evict_session(self) -> bool:
@@ -497,6 +497,22 @@ class ModelMux:
             # crude service model: rows per ms observed on recent prefill ticks
             b = max(PAGE, min(b, int(self.cfg.tbt_target_ms * getattr(self, "_rows_per_ms", 64.0))))
         return b
+
+    # ---- drafter ------------------------------------------------------------------------------
+    def set_drafter(self, drafter) -> None:
+        """Drafter of the speculative steps (``spec_depth`` > 0): an n-gram drafter, or a MtpDrafter over the checkpoint's
+        prediction module, which the prefill, decode and verify steps then feed with the decoder's hidden states."""
+        self._drafter = drafter
+
+    def _mtp(self):
+        d = getattr(self, "_drafter", None)
+        return d if self.cfg.spec_depth > 0 and getattr(d, "needs_hidden", False) else None
+
+    def _retire(self, slot: int) -> None:
+        self.engine.retire_slot(slot)
+        d = getattr(self, "_drafter", None)
+        if getattr(d, "needs_hidden", False):
+            d.retire(slot)
 
     def _prefill_tick(self, reqs: list, riders: list = ()) -> None:
         """One prefill launch.  ``riders`` are decoding requests whose next row is appended to the same token batch
@@ -567,14 +583,17 @@ class ModelMux:
         else:
             sample_rows_arr = np.array(sample_rows, dtype=np.int32)
         batch = TokenBatch(np.array(ids, dtype=np.int32), np.array(pos, dtype=np.int32), np.array(seq, dtype=np.int32),
-                           sample_rows_arr, decode=False, want_logits=want_logits)
+                           sample_rows_arr, decode=False, want_logits=want_logits, want_hidden=self._mtp() is not None)
         t0 = time.perf_counter()
         res = eng.step(batch)
         dt = (time.perf_counter() - t0) * 1e3
         self._rows_per_ms = 0.8 * getattr(self, "_rows_per_ms", len(ids) / max(dt, 1e-3)) + 0.2 * len(ids) / max(dt, 1e-3)
         self.metrics.inc("prefill_ticks")
         k = 0
+        mtp = self._mtp() if res.hidden is not None else None
+        seen, at = [], 0          # what the drafter's prediction module must see: (slot, start, next tokens, hidden rows)
         for (r, start, n, final, toks) in spans:
+            slot = r.slot
             eng.commit(r.slot, toks[start:start + n])
             r.done_prefill = start + n
             self.metrics.inc("prompt_tokens", n)
@@ -584,12 +603,25 @@ class ModelMux:
                 k += 1
                 if self.pd_target is not None and r.slot >= 0 and self.live.get(r.slot) is r:
                     self._handoff(r)
+            if mtp is not None and self.live.get(slot) is r:
+                allt = r.all_tokens()
+                if len(allt) > start + n:           # the token behind the last row: the prompt's next one, or the one just produced
+                    if start == 0:
+                        mtp.begin(slot)
+                    seen.append((slot, start, allt[start + 1:start + n + 1], res.hidden[at:at + n]))
+            at += n
         for r in rode:
             if r.slot in self.live and self.live[r.slot] is r:
-                eng.commit(r.slot, [r.generated[-1]])
+                slot, fed = r.slot, r.generated[-1]
+                eng.commit(r.slot, [fed])
                 self._produce(r, int(res.ids[k]), res.logits[k] if res.logits is not None else None)
                 self.metrics.inc("rider_rows")
+                if mtp is not None and self.live.get(slot) is r:
+                    seen.append((slot, len(r.prompt) + len(r.generated) - 2, [r.generated[-1]], res.hidden[at:at + 1]))
             k += 1
+            at += 1
+        if seen:
+            mtp.observe(seen)
 
     # ---- decode --------------------------------------------------------------------------------
     def _spec_tick(self, reqs: list) -> bool:
@@ -606,11 +638,18 @@ class ModelMux:
             return False            # rejected draft rows would already have advanced the per-slot state in place
         drafter = getattr(self, "_drafter", None) or NgramDrafter()
         self._drafter = drafter
+        mtp = self._mtp()
+        chained = {}
+        if mtp is not None:
+            chained = mtp.propose_many([r.slot for r in reqs if mtp.synced(r.slot, len(r.prompt) + len(r.generated) - 1)], depth)
         ids, pos, seq, spans = [], [], [], []
         for r in sorted(reqs, key=lambda r: r.slot):
             n_ctx = len(r.prompt) + len(r.generated)
             room = min(depth, r.params.max_tokens - len(r.generated) - 1, eng.max_ctx - n_ctx - 2)
-            draft = drafter.propose(r.all_tokens(), max(0, room)) if room > 0 else []
+            if r.slot in chained:
+                draft = chained[r.slot][:max(0, room)]
+            else:
+                draft = drafter.propose(r.all_tokens(), max(0, room)) if room > 0 else []
             try:
                 eng.reserve(r.slot, n_ctx + len(draft) + 1)
             except OutOfPages:
@@ -623,9 +662,11 @@ class ModelMux:
         if len(ids) == len(spans):
             return False                      # nothing drafted: the plain decode program is cheaper
         res = eng.step(TokenBatch(np.array(ids, np.int32), np.array(pos, np.int32), np.array(seq, np.int32),
-                                  np.arange(len(ids), dtype=np.int32), decode=False))
+                                  np.arange(len(ids), dtype=np.int32), decode=False, want_hidden=mtp is not None))
         self.metrics.inc("spec_ticks")
+        seen = []
         for (r, at, draft) in spans:
+            slot, n0 = r.slot, len(r.prompt) + len(r.generated) - 1
             got = [int(x) for x in res.ids[at:at + 1 + len(draft)]]
             j = 0
             while j < len(draft) and draft[j] == got[j]:
@@ -638,6 +679,11 @@ class ModelMux:
                     break                      # finished (stop / length) while emitting the accepted span
                 eng.commit(r.slot, [tok_in])
                 self._produce(r, tok_out, None)
+            if mtp is not None and res.hidden is not None and self.live.get(slot) is r:
+                new = r.all_tokens()[n0 + 1:]                  # the accepted drafts and the token behind them
+                seen.append((slot, n0, new, res.hidden[at:at + len(new)]))
+        if seen:
+            mtp.observe(seen)
         return True
 
     def _decode_tick(self, reqs: list) -> None:
@@ -661,7 +707,9 @@ class ModelMux:
         pos = np.array([len(r.prompt) + len(r.generated) - 1 for r in reqs], dtype=np.int32)
         seq = np.array([r.slot for r in reqs], dtype=np.int32)
         want_logits = any(not r.params.greedy for r in reqs)
-        batch = TokenBatch(ids, pos, seq, np.arange(len(reqs), dtype=np.int32), decode=True, want_logits=want_logits)
+        mtp = self._mtp()
+        batch = TokenBatch(ids, pos, seq, np.arange(len(reqs), dtype=np.int32), decode=True, want_logits=want_logits,
+                           want_hidden=mtp is not None)
         k = self._multi_step_depth(reqs)
         if k > 1:
             # several steps per engine call: the engine feeds each step's arg-max tokens to the next one, the host
@@ -679,9 +727,15 @@ class ModelMux:
             return
         res = eng.step(batch)
         self.metrics.inc("decode_ticks")
+        seen = []
         for k, r in enumerate(reqs):
+            slot = r.slot
             eng.commit(r.slot, [int(ids[k])])
             self._produce(r, int(res.ids[k]), res.logits[k] if res.logits is not None else None)
+            if mtp is not None and res.hidden is not None and self.live.get(slot) is r:
+                seen.append((slot, int(pos[k]), [r.generated[-1]], res.hidden[k:k + 1]))
+        if seen:
+            mtp.observe(seen)
 
     def _multi_step_depth(self, reqs: list) -> int:
         """How many decode steps the next engine call may chain: only plain greedy requests (no logprobs, penalties,
@@ -768,7 +822,7 @@ class ModelMux:
         if r.slot >= 0 and self.live.get(r.slot) is r:
             del self.live[r.slot]
             if not (reason in ("stop", "length") and self._retain(r)):
-                self.engine.retire_slot(r.slot)
+                self._retire(r.slot)
                 self.free_slots.append(r.slot)
         self.metrics.inc("requests_finished")
         self.metrics.obs("e2e", (time.monotonic() - r.arrived) * 1e3)
@@ -780,7 +834,7 @@ class ModelMux:
         if not cands:
             return
         victim = prefer or max(cands, key=lambda r: r.arrived)
-        self.engine.retire_slot(victim.slot)
+        self._retire(victim.slot)
         del self.live[victim.slot]
         self.free_slots.append(victim.slot)
         victim.slot, victim.done_prefill = -1, 0
@@ -795,7 +849,7 @@ class ModelMux:
         for r in list(self.live.values()):
             r.out.put(Chunk("error", error=str(e), finish_reason="error"))
             try:
-                self.engine.retire_slot(r.slot)
+                self._retire(r.slot)
             except Exception:
                 pass
             self.free_slots.append(r.slot)

@@ -5,7 +5,7 @@
 * :func:`shard_slice` applies the Megatron layout: column-parallel weights are split on axis 0
   (output features), row-parallel on axis 1 (input features), everything else is replicated.
 * :func:`materialize` resolves one packet tensor entry: a checkpoint tensor, a derived tensor
-  (row concatenation, stacked expert matrices), its block-scaled e4m3 twin, or a generated table.
+  (row concatenation, stacked expert matrices, a column range), its block-scaled e4m3 twin, or a generated table.
 
 Reference counterpart: crates/plowrt/src/asset/{checkpoint,shard}.rs, memory/container.rs,
 crates/plow-asset/src/derived_weights.rs.
@@ -87,4 +87,6 @@ def materialize(name: str, ent, recipe: dict | None, ckpt: Checkpoint, tp: int =
         for name in recipe.get("tail", []):      # shared expert stacked behind the routed ones (replicated on every rank)
             rows.append(ckpt.get(name))
         return torch.cat(rows, dim=0).contiguous()
+    if recipe["op"] == "cols":                 # a column range of a checkpoint matrix (a half of eh_proj)
+        return ckpt.get_slice(recipe["src"], 1, recipe["start"], recipe["stop"]).contiguous()
     raise ValueError(f"unknown derived-weight recipe '{recipe['op']}'")
