@@ -21,7 +21,14 @@
 // Reference semantics: runtime/common/dev_isa.h:185-222 (split-KV partials + FLASH_MERGE, decode
 // with kv_len / window) and :74-84 (HEADNORM_ROPE writing the cache row directly); the reference's
 // own sm_120 kernels are mma.sync flash kernels (runtime/nvidia/op_attention*.cuh).
+//
+// e4m3 cache (KV8 instantiation): K and V cells are e4m3 bytes with one f32 scale per (token, kv head).  The TMA warp
+// brings the raw byte tiles into a two-deep staging ring; four converter warps turn each tile into the bf16 operand
+// layout the MMAs read (value * scale, written with the same 128-byte swizzle a bf16 TMA load would produce) and hand
+// the stage to the MMA warp.  The math after that point is the bf16 kernel's own: half the cache bytes, same tiles
+// (reference: runtime/common/dev_isa.h:388-398, HEADNORM_ROPE_FP8 / FLASH_DECODE_FP8 / FLASH_PREFILL_FP8).
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 
 #include "ptx.cuh"
 #include "tmap.cuh"
@@ -30,6 +37,8 @@ namespace plow {
 
 constexpr int kGqaPage = 64;
 constexpr int kGqaThreads = 192;   // TMA warp, MMA warp, 4 softmax warps
+constexpr int kGqaThreads8 = 320;  // + 4 converter warps (e4m3 cache)
+constexpr int kGqaRaw = 2;         // raw e4m3 tiles in flight
 
 struct GqaItem { int r0, nt, kvh, split, tile0, ntiles, slot, ns; };
 
@@ -48,19 +57,24 @@ struct GqaArgs {
   // all heads (the rotary part), and the value tile sits `v_x0` columns into the key tensor's head block
   int kr_slabs, v_x0;
   int head_major;          // items are [chunk][head] (one split): visit them head by head
+  const float* kv_scale;   // e4m3 cache: [n_pages][64][2 * nkv] f32, k scales then v scales of a token
 };
 
 // HDQ = width of a query / key row, HDV = width of a value row.  They differ for multi-head latent attention in its
 // materialised form (192 = 128 no-position + 64 rotary dims against 128 value dims).
-template <int HDQ, int HDV> struct GqaCfg {
+template <int HDQ, int HDV, bool KV8 = false> struct GqaCfg {
   static constexpr int kSlabsQ = HDQ / 64;               // 64-column (128-byte) slabs per query / key row
   static constexpr int kSlabsV = HDV / 64;
   static constexpr int kQBytes = kSlabsQ * 128 * 128;
   static constexpr int kKBytes = kSlabsQ * 64 * 128;     // one K tile
   static constexpr int kVBytes = kSlabsV * 64 * 128;     // one V tile
   static constexpr int kStageBytes = kKBytes + kVBytes;
-  static constexpr int kStages = (200 * 1024 - kQBytes) / kStageBytes > 5 ? 5 : (200 * 1024 - kQBytes) / kStageBytes;
-  static constexpr int kSmem = 1024 + kQBytes + kStages * kStageBytes + 1024;
+  static constexpr int kRawK = 64 * HDQ;                 // one raw e4m3 K tile: HDQ / 128 slabs of 64 rows x 128 bytes
+  static constexpr int kRawStage = 64 * (HDQ + HDV);
+  static constexpr int kRawBytes = KV8 ? kGqaRaw * kRawStage : 0;
+  static constexpr int kStages = (200 * 1024 - kQBytes - kRawBytes) / kStageBytes > 5 ? 5 : (200 * 1024 - kQBytes - kRawBytes) / kStageBytes;
+  static constexpr int kSmem = 1024 + kQBytes + kStages * kStageBytes + kRawBytes + 1024;
+  static constexpr int kThreads = KV8 ? kGqaThreads8 : kGqaThreads;
   static constexpr int kTmemCols = HDV <= 128 ? 256 : 512; // S: 2 x 64, O: HDV
   static_assert(kStages >= 2, "K/V stages do not fit");
 };
@@ -95,19 +109,20 @@ __global__ void gqa_build_items(const int* seq, const int* pos, int rows, int tq
   }
 }
 
-template <int HDQ, int HDV>
-__global__ void __launch_bounds__(kGqaThreads, 1)
+template <int HDQ, int HDV, bool KV8 = false>
+__global__ void __launch_bounds__((GqaCfg<HDQ, HDV, KV8>::kThreads), 1)
 gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kr) {
   plow::pdl_launch_dependents();
   plow::pdl_wait();
-  using Cfg = GqaCfg<HDQ, HDV>;
+  using Cfg = GqaCfg<HDQ, HDV, KV8>;
   constexpr int HD = HDV;      // width of the accumulator rows
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* q_smem = smem;
   uint8_t* kv_smem = smem + Cfg::kQBytes;
-  uint8_t* ctrl = kv_smem + Cfg::kStages * Cfg::kStageBytes;
+  uint8_t* raw_smem = kv_smem + Cfg::kStages * Cfg::kStageBytes;     // e4m3 cache: raw byte tiles (1024-aligned: all sizes are)
+  uint8_t* ctrl = raw_smem + Cfg::kRawBytes;
   uint64_t* q_full = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* q_empty = q_full + 1;
   uint64_t* kv_full = q_empty + 1;                 // [kStages]
@@ -117,7 +132,9 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
   uint64_t* pv_done = p_full + 2;                  // [2] by tile parity
   uint64_t* o_free = pv_done + 2;                  // [1]
   uint64_t* drain_bar = o_free + 1;                // [1]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  uint64_t* raw_full = drain_bar + 1;              // [kGqaRaw] (e4m3 cache only)
+  uint64_t* raw_empty = raw_full + kGqaRaw;        // [kGqaRaw]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(raw_empty + kGqaRaw);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   volatile int* never_flag = abort_flag + 1;
 
@@ -131,6 +148,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
     for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 4); mbar_init(&pv_done[b], 1); }
     mbar_init(o_free, 4);
     mbar_init(drain_bar, 1);
+    for (int r = 0; r < kGqaRaw; ++r) { mbar_init(&raw_full[r], 1); mbar_init(&raw_empty[r], 1); }
     *abort_flag = 0;
     *never_flag = 0;
     fence_mbar_init();
@@ -167,6 +185,18 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
           const int s = kv_it % Cfg::kStages;
           const int page = page_next;
           if (i + 1 < w.ntiles) page_next = pt[w.tile0 + i + 1];
+          if constexpr (KV8) {
+            // raw byte tiles into the staging ring; the converter warps own the operand stages
+            const int rs = kv_it % kGqaRaw;
+            if (!mbar_wait(&raw_empty[rs], ((kv_it / kGqaRaw) & 1) ^ 1, abort_flag)) {
+              *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagGqa); ok = false; break;
+            }
+            uint8_t* rw = raw_smem + rs * Cfg::kRawStage;
+            mbar_expect_tx(&raw_full[rs], Cfg::kRawStage);
+            for (int c = 0; c < HDQ / 128; ++c) tma_load_3d(rw + c * 8192, &tm_k, c * 128, w.kvh, page * kGqaPage, &raw_full[rs]);
+            for (int c = 0; c < HDV / 128; ++c) tma_load_3d(rw + Cfg::kRawK + c * 8192, &tm_v, c * 128, w.kvh, page * kGqaPage, &raw_full[rs]);
+            continue;
+          }
           if (!mbar_wait(&kv_empty[s], ((kv_it / Cfg::kStages) & 1) ^ 1, abort_flag)) {
             *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagGqa); ok = false; break;
           }
@@ -233,6 +263,69 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
         tile_it += w.ntiles;
       }
       if (!ok || *abort_flag) { tc_commit(drain_bar); mbar_wait(drain_bar, 0, never_flag); }
+    }
+  } else if (KV8 && warp >= 6) {
+    // ------------------------------------------------------------------ converter warps (e4m3 cache -> bf16 operand stages)
+    // Thread u of the 128 handles work units (row = u % 64, out slab): 64 e4m3 bytes of one token -> 64 bf16 (one
+    // 128-byte operand row).  Raw tiles and operand slabs are both 64 rows x 128 bytes with the 128-byte swizzle: the
+    // 16-byte chunk j of row r sits at chunk j ^ (r & 7).
+    const int u = threadIdx.x - 192;
+    uint32_t kv_it = 0;
+    bool ok = true;
+    for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x) {
+      const GqaItem w = item_at(it);
+      const int* pt = a.page_table + static_cast<size_t>(w.slot) * a.max_pages;
+      for (int i = 0; i < w.ntiles; ++i, ++kv_it) {
+        const int s = kv_it % Cfg::kStages, rs = kv_it % kGqaRaw;
+        const int page = pt[w.tile0 + i];
+        bool mine = mbar_wait(&raw_full[rs], (kv_it / kGqaRaw) & 1, abort_flag) &&
+                    mbar_wait(&kv_empty[s], ((kv_it / Cfg::kStages) & 1) ^ 1, abort_flag);
+        // one decision for all 128 threads (a barrier with an OR over "my wait ran out or somebody gave up")
+        uint32_t stop;
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                     : "=r"(stop) : "r"(static_cast<uint32_t>(!mine || *abort_flag)) : "memory");
+        if (stop) {
+          if (u == 0) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagGqa); }
+          ok = false;
+          break;
+        }
+        const uint8_t* rw = raw_smem + rs * Cfg::kRawStage;
+        uint8_t* st = kv_smem + s * Cfg::kStageBytes;
+        const float* sc = a.kv_scale + (static_cast<size_t>(page) * kGqaPage) * 2 * a.nkv;
+        constexpr int kUnitsK = 64 * Cfg::kSlabsQ, kUnits = 64 * (Cfg::kSlabsQ + Cfg::kSlabsV);
+#pragma unroll
+        for (int unit = u; unit < kUnits; unit += 128) {
+          const bool is_v = unit >= kUnitsK;
+          const int uu = is_v ? unit - kUnitsK : unit;
+          const int row = uu & 63, slab = uu >> 6;                  // out slab = 64 head dims
+          const float scale = sc[row * 2 * a.nkv + (is_v ? a.nkv : 0) + w.kvh];
+          const uint8_t* src = rw + (is_v ? Cfg::kRawK : 0) + (slab >> 1) * 8192 + row * 128;
+          uint8_t* dst = st + (is_v ? Cfg::kKBytes : 0) + slab * 8192 + row * 128;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {                             // 16 e4m3 bytes -> two 16-byte bf16 chunks
+            const int jc = ((slab & 1) * 4 + c) ^ (row & 7);
+            const uint4 rv = *reinterpret_cast<const uint4*>(src + jc * 16);
+            const uint32_t wv[4] = {rv.x, rv.y, rv.z, rv.w};
+            uint32_t o[8];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(wv[q] & 0xffffu), __NV_E4M3);
+              const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(wv[q] >> 16), __NV_E4M3);
+              const float2 fl = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+              const float2 fh = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+              const __nv_bfloat162 bl = __floats2bfloat162_rn(fl.x * scale, fl.y * scale);
+              const __nv_bfloat162 bh = __floats2bfloat162_rn(fh.x * scale, fh.y * scale);
+              o[2 * q] = *reinterpret_cast<const uint32_t*>(&bl);
+              o[2 * q + 1] = *reinterpret_cast<const uint32_t*>(&bh);
+            }
+            *reinterpret_cast<uint4*>(dst + ((2 * c) ^ (row & 7)) * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(dst + ((2 * c + 1) ^ (row & 7)) * 16) = make_uint4(o[4], o[5], o[6], o[7]);
+          }
+        }
+        fence_proxy_async_smem();       // the MMAs read these stores through the async proxy
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (u == 0) { mbar_arrive(&kv_full[s]); mbar_arrive(&raw_empty[rs]); }
+      }
     }
   } else {
     // ------------------------------------------------------------------ softmax / epilogue warps
@@ -406,7 +499,7 @@ __global__ void rope_kv_kernel(__nv_bfloat16* q_out, const __nv_bfloat16* qkv, i
                                __nv_bfloat16* vc, const __nv_bfloat16* qn, const __nv_bfloat16* kn,
                                const float* rope_tab, const int* pos, const int* seq, const int* page_table,
                                int max_pages, int rows, int nq, int nkv, int hd, int rot, int pair_mode,
-                               int plus_one, float eps, __nv_bfloat16* gate_out) {
+                               int plus_one, float eps, __nv_bfloat16* gate_out, float* kv_scale) {
   plow::pdl_launch_dependents();
   plow::pdl_wait();
   extern __shared__ float rk_smem[];
@@ -425,6 +518,8 @@ __global__ void rope_kv_kernel(__nv_bfloat16* q_out, const __nv_bfloat16* qkv, i
   __nv_bfloat16* dst;
   const __nv_bfloat16* gamma = nullptr;
   const bool is_v = h >= nq + nkv;
+  uint8_t* dst8 = nullptr;          // e4m3 cache cell (kv_scale given) and where its scale goes
+  float* dst_scale = nullptr;
   if (h < nq) {
     dst = q_out + (static_cast<size_t>(r) * nq + h) * hd;
     gamma = qn;
@@ -437,8 +532,30 @@ __global__ void rope_kv_kernel(__nv_bfloat16* q_out, const __nv_bfloat16* qkv, i
     const size_t cell = ((static_cast<size_t>(page) * kGqaPage + p % kGqaPage) * nkv + kh) * hd;
     dst = (is_v ? vc : kc) + cell;
     gamma = kn;
+    if (kv_scale) {
+      dst8 = reinterpret_cast<uint8_t*>(is_v ? vc : kc) + cell;
+      dst_scale = kv_scale + (static_cast<size_t>(page) * kGqaPage + p % kGqaPage) * 2 * nkv + (is_v ? nkv : 0) + kh;
+      dst = reinterpret_cast<__nv_bfloat16*>(buf);     // never dereferenced as a cache row below
+    }
   }
+  // e4m3 cell: the finished row (bf16-rounded, as the bf16 cache would hold it) scaled by amax / 448, one scale per cell
+  auto store8 = [&]() {
+    float amax = 0.f;
+    for (int i = lane; i < hd; i += 32) amax = fmaxf(amax, fabsf(buf[i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float sc = fmaxf(amax, 1e-12f) / 448.0f, inv = 1.0f / sc;
+    for (int i = lane; i < hd; i += 32)
+      dst8[i] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(buf[i] * inv, __NV_SATFINITE, __NV_E4M3));
+    if (lane == 0) *dst_scale = sc;
+  };
   if (is_v) {
+    if (dst8) {
+      for (int i = lane; i < hd; i += 32) buf[i] = __bfloat162float(src[i]);
+      __syncwarp();
+      store8();
+      return;
+    }
     for (int i = lane; i < hd / 8; i += 32) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
     return;
   }
@@ -458,6 +575,19 @@ __global__ void rope_kv_kernel(__nv_bfloat16* q_out, const __nv_bfloat16* qkv, i
   __syncwarp();
   const int half = rot / 2;
   const float* tab = rope_tab + static_cast<size_t>(p) * rot;
+  if (dst8) {
+    // rotate in place (each pair is owned by one lane), rounded to bf16 like the bf16 cache row, then quantise
+    for (int i = lane; i < half; i += 32) {
+      const int ia = pair_mode ? 2 * i : i, ib = pair_mode ? 2 * i + 1 : i + half;
+      const float x = buf[ia], y = buf[ib], c = tab[i], s = tab[half + i];
+      buf[ia] = __bfloat162float(__float2bfloat16(x * c - y * s));
+      buf[ib] = __bfloat162float(__float2bfloat16(y * c + x * s));
+    }
+    for (int i = rot + lane; i < hd; i += 32) buf[i] = __bfloat162float(__float2bfloat16(buf[i]));
+    __syncwarp();
+    store8();
+    return;
+  }
   for (int i = lane; i < half; i += 32) {
     const int ia = pair_mode ? 2 * i : i, ib = pair_mode ? 2 * i + 1 : i + half;
     const float x = buf[ia], y = buf[ib], c = tab[i], s = tab[half + i];
@@ -480,6 +610,23 @@ int launch_gqa(const GqaArgs& a, const void* q, const void* kc, const void* vc, 
   static DeviceOnce attr;
   if (ensure_smem(attr, gqa_attn_kernel<HD, HD>, Cfg::kSmem) != cudaSuccess) return 3000;
   plow::launch_serial(gqa_attn_kernel<HD, HD>, dim3(grid), dim3(kGqaThreads), Cfg::kSmem, stream, a, tq, tk, tv, tk);
+  return 0;
+}
+
+// e4m3 cache: kc / vc are bytes [n_pages*64][nkv][HD]; raw tiles of 128 bytes x 64 tokens per load.
+template <int HD>
+int launch_gqa8(const GqaArgs& a, const void* q, const void* kc, const void* vc, int64_t n_pages, int grid, cudaStream_t stream) {
+  using Cfg = GqaCfg<HD, HD, true>;
+  CUtensorMap tq, tk, tv;
+  int r = make_tmap_3d(&tq, q, 2, HD, a.nq, a.rows, HD * 2, static_cast<uint64_t>(a.nq) * HD * 2, a.group, 128 / a.group, 128);
+  if (r) return 1100 + r;
+  r = make_tmap_3d(&tk, kc, 1, HD, a.nkv, static_cast<uint64_t>(n_pages) * kGqaPage, HD, static_cast<uint64_t>(a.nkv) * HD, 1, kGqaPage, 128);
+  if (r) return 1200 + r;
+  r = make_tmap_3d(&tv, vc, 1, HD, a.nkv, static_cast<uint64_t>(n_pages) * kGqaPage, HD, static_cast<uint64_t>(a.nkv) * HD, 1, kGqaPage, 128);
+  if (r) return 1300 + r;
+  static DeviceOnce attr;
+  if (ensure_smem(attr, gqa_attn_kernel<HD, HD, true>, Cfg::kSmem) != cudaSuccess) return 3000;
+  plow::launch_serial(gqa_attn_kernel<HD, HD, true>, dim3(grid), dim3(Cfg::kThreads), Cfg::kSmem, stream, a, tq, tk, tv, tk);
   return 0;
 }
 
@@ -507,16 +654,19 @@ extern "C" {
 // q bf16 [rows][nq][hd]; kc / vc bf16 [n_pages][64][nkv][hd]; seq / pos int32 [rows] (pos < 0: inactive row);
 // out bf16 [rows][nq*hd].  Scratch from the caller: items (8 ints each, capacity item_cap), n_items (1 int),
 // row_ns int32 [rows], opart f32 [rows][nq][max_splits][hd], lse f32 [rows][nq][max_splits].
+// kv_scale != null: kc / vc are e4m3 bytes with one f32 scale per (token, kv head) in kv_scale [n_pages][64][2*nkv]
+// (k scales, then v scales); head dim 128 only.
 int plow_gqa_attention(const void* q, const void* kc, const void* vc, int64_t n_pages, const int* page_table,
                        int max_pages, const int* seq, const int* pos, int rows, int nq, int nkv, int hd, int window,
                        int tiles_per_split, int max_splits, void* items, int item_cap, int* n_items, int* row_ns,
-                       float* opart, float* lse, void* out, float softmax_scale, int* status, void* stream_) {
+                       float* opart, float* lse, void* out, float softmax_scale, const float* kv_scale, int* status, void* stream_) {
   using namespace plow;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (rows <= 0 || nq <= 0 || nkv <= 0 || nq % nkv || max_splits <= 0 || tiles_per_split <= 0) return -1;
   const int group = nq / nkv;
   if (group > 128 || (group & (group - 1))) return -2;
   if (hd != 128 && hd != 256) return -3;
+  if (kv_scale && hd != 128) return -4;
   const int tq = 128 / group;
   cudaMemsetAsync(n_items, 0, sizeof(int), stream);
   plow::launch_serial(gqa_build_items, dim3((rows + 255) / 256), dim3(256), 0, stream, seq, pos, rows, tq, nkv, window, tiles_per_split, max_splits,
@@ -526,10 +676,11 @@ int plow_gqa_attention(const void* q, const void* kc, const void* vc, int64_t n_
   a.opart = opart; a.lse = lse; a.out = static_cast<__nv_bfloat16*>(out); a.status = status;
   a.rows = rows; a.nq = nq; a.nkv = nkv; a.group = group; a.max_pages = max_pages; a.max_splits = max_splits; a.window = window;
   a.scale_log2e = softmax_scale * 1.4426950408889634f;
-  a.kr_slabs = 0; a.v_x0 = 0; a.head_major = 0;
+  a.kr_slabs = 0; a.v_x0 = 0; a.head_major = 0; a.kv_scale = kv_scale;
   int grid = sm_count();
   if (item_cap < grid) grid = item_cap;
-  int r = hd == 128 ? launch_gqa<128>(a, q, kc, vc, n_pages, grid, stream) : launch_gqa<256>(a, q, kc, vc, n_pages, grid, stream);
+  int r = kv_scale ? launch_gqa8<128>(a, q, kc, vc, n_pages, grid, stream)
+          : hd == 128 ? launch_gqa<128>(a, q, kc, vc, n_pages, grid, stream) : launch_gqa<256>(a, q, kc, vc, n_pages, grid, stream);
   if (r) return r;
   if (max_splits > 1)
     plow::launch_serial(gqa_merge_kernel, dim3(rows, nq), dim3(128), 0, stream, opart, lse, row_ns, nq, max_splits, hd, static_cast<__nv_bfloat16*>(out));
@@ -556,7 +707,7 @@ int plow_mla_prefill_attention(const void* q, const void* kvb, const void* krope
   a.opart = opart; a.lse = lse; a.out = static_cast<__nv_bfloat16*>(out); a.status = status;
   a.rows = rows; a.nq = heads; a.nkv = heads; a.group = 1; a.max_pages = max_pages; a.max_splits = max_splits; a.window = 0;
   a.scale_log2e = softmax_scale * 1.4426950408889634f;
-  a.kr_slabs = 1; a.v_x0 = 128; a.head_major = max_splits == 1 ? 1 : 0;
+  a.kr_slabs = 1; a.v_x0 = 128; a.head_major = max_splits == 1 ? 1 : 0; a.kv_scale = nullptr;
   int grid = sm_count();
   if (item_cap < grid) grid = item_cap;
   int r = launch_mla_prefill(a, q, kvb, krope, n_tokens, grid, stream);
@@ -569,10 +720,12 @@ int plow_mla_prefill_attention(const void* q, const void* kvb, const void* krope
 
 // qkv bf16 [rows][ld_qkv] = [q heads | k heads | v heads]; qn / kn: optional per-head RMSNorm weights [hd];
 // rope_tab f32 [max_pos][rot] = [cos(rot/2) | sin(rot/2)]; pair_mode 0 = half split, 1 = interleaved.
+// kv_scale (optional) f32 [n_pages][64][2*nkv]: kc / vc are then e4m3 byte caches and every written cell gets its scale.
 // gate_out (optional) bf16 [rows][nq*hd]: gated attention, query heads are then [Q | gate] pairs of width 2*hd.
 int plow_rope_kv(void* q_out, const void* qkv, int ld_qkv, void* kc, void* vc, const void* qn, const void* kn,
                  const float* rope_tab, const int* pos, const int* seq, const int* page_table, int max_pages,
-                 int rows, int nq, int nkv, int hd, int rot, int pair_mode, int plus_one, float eps, void* gate_out, void* stream_) {
+                 int rows, int nq, int nkv, int hd, int rot, int pair_mode, int plus_one, float eps, void* gate_out,
+                 float* kv_scale, void* stream_) {
   using namespace plow;
   if (rows <= 0 || hd % 8 || rot > hd || rot % 2) return -1;
   const long long items = static_cast<long long>(rows) * (nq + 2 * nkv);
@@ -581,7 +734,7 @@ int plow_rope_kv(void* q_out, const void* qkv, int ld_qkv, void* kc, void* vc, c
       static_cast<__nv_bfloat16*>(q_out), static_cast<const __nv_bfloat16*>(qkv), ld_qkv, static_cast<__nv_bfloat16*>(kc),
       static_cast<__nv_bfloat16*>(vc), static_cast<const __nv_bfloat16*>(qn), static_cast<const __nv_bfloat16*>(kn),
       rope_tab, pos, seq, page_table, max_pages, rows, nq, nkv, hd, rot, pair_mode, plus_one, eps,
-      static_cast<__nv_bfloat16*>(gate_out));
+      static_cast<__nv_bfloat16*>(gate_out), kv_scale);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 4000 + static_cast<int>(e);
 }

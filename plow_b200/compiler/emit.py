@@ -137,9 +137,12 @@ class Lowering:
                 qkv, qn, kn, rope = n.inputs[0], n.inputs[1], n.inputs[2], n.inputs[3]
                 q_out, kc, vc = n.outputs[:3]
                 gate = n.outputs[3] if len(n.outputs) > 3 else None
+                ksc = a.get("kv_scales")
+                if ksc and gate:
+                    raise ValueError("an e4m3 KV cache under gated attention is not supported (no operand slot left for the scales)")
                 ins = pk.Inst(Op.ROPE_KV, f=(a.get("eps", 0.0), 0, 0),
                               t=[self.t(q_out), self.t(qkv), self.t(kc), self.t(vc), self.t(qn), self.t(kn), self.t(rope)]
-                              + ([self.t(gate)] if gate else []),
+                              + ([self.t(gate)] if gate else [self.t(ksc)] if ksc else []),
                               i=[a["heads"], a["kv_heads"], a["head_dim"], a["rot_dim"], PAIR_MODE[a["pair_mode"]],
                                  n.layer, int(a.get("plus_one", False)), int(bool(gate))])
                 out.append(schedule.LInst(ins, rd(qkv, qn, kn, rope), rd(q_out, kc, vc, gate),
@@ -147,7 +150,8 @@ class Lowering:
             elif n.op == "attention":
                 q, kc, vc = n.inputs
                 mode = pk.ATTN_DECODE if role == pk.Role.DECODE else pk.ATTN_CAUSAL
-                ins = pk.Inst(Op.ATTN, f=(a["scale"], 0, 0), t=[self.t(n.outputs[0]), self.t(q), self.t(kc), self.t(vc)],
+                ins = pk.Inst(Op.ATTN, f=(a["scale"], 0, 0), t=[self.t(n.outputs[0]), self.t(q), self.t(kc), self.t(vc)]
+                              + ([self.t(a["kv_scales"])] if a.get("kv_scales") else []),
                               i=[a["heads"], a["kv_heads"], a["head_dim"], a.get("window", 0), mode, n.layer])
                 cost = costmodel.attention_decode_cost(rows * 2048, a["heads"], a["kv_heads"], a["head_dim"], a["head_dim"], es) \
                     if role == pk.Role.DECODE else costmodel.attention_prefill_cost(rows, rows, a["heads"], a["head_dim"], a["head_dim"])

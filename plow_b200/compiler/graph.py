@@ -237,10 +237,13 @@ def _gqa_attention(g: Graph, li, p, h, a) -> str:
     g.add("rope", [k, rope, "in.pos"], [kr], layer=li, heads=nkv, head_dim=hd, rot_dim=spec.rope.rot_dim, pair_mode=spec.rope.pair_mode)
     kc = g.value(f"kv.{li}.k", ("P", 64, nkv, hd), spec.kv_dtype if spec.kv_dtype != "fp8" else "e4m3", "kv")
     vc = g.value(f"kv.{li}.v", ("P", 64, nkv, hd), spec.kv_dtype if spec.kv_dtype != "fp8" else "e4m3", "kv")
-    g.add("kv_write", [kr, v, "in.pos", "in.seq"], [kc, vc], layer=li, heads=nkv, head_dim=hd)
+    # e4m3 cache: one f32 scale per (token, kv head) next to the cells, k scales then v scales of a token
+    # (reference: runtime/common/dev_isa.h:388-398, the fp8 twins of HEADNORM_ROPE / FLASH_DECODE / FLASH_PREFILL)
+    ksc = g.value(f"kv.{li}.s", ("P", 64, 2 * nkv), "f32", "kv") if spec.kv_dtype == "fp8" else None
+    g.add("kv_write", [kr, v, "in.pos", "in.seq"], [kc, vc], layer=li, heads=nkv, head_dim=hd, kv_scales=ksc)
     ao = g.tmp("attn", (R, nq * hd))
     g.add("attention", [qr, kc, vc], [ao], layer=li, heads=nq, kv_heads=nkv, head_dim=hd, window=a.window,
-          scale=hd ** -0.5)
+          scale=hd ** -0.5, kv_scales=ksc)
     if gate is not None:
         ag = g.tmp("attn", (R, nq * hd))
         g.add("sigmoid_gate", [ao, gate], [ag], layer=li)

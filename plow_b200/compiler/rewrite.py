@@ -135,7 +135,8 @@ def rule_rope_kv_fuse(g: Graph, sites: list) -> bool:
                      dict(gated=bool(gate_out), heads=rq.attrs["heads"], kv_heads=rk.attrs["heads"], head_dim=rq.attrs["head_dim"],
                           rot_dim=rq.attrs["rot_dim"], pair_mode=rq.attrs["pair_mode"],
                           eps=(hq.attrs["eps"] if has_norm else 0.0),
-                          plus_one=(hq.attrs.get("plus_one", False) if has_norm else False)),
+                          plus_one=(hq.attrs.get("plus_one", False) if has_norm else False),
+                          kv_scales=n.attrs.get("kv_scales")),
                      n.layer, "rope-kv-fuse")
         _replace(g, swallowed, [fused])
         es = costmodel.dtype_bytes(g.values[qkv].dtype)

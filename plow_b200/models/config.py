@@ -125,7 +125,7 @@ class ModelSpec:
         for l in self.layers:
             a = l.attn
             if a.kind == "gqa":
-                n += 2 * a.n_kv_heads * a.head_dim * es
+                n += 2 * a.n_kv_heads * a.head_dim * es + (8 * a.n_kv_heads if self.kv_dtype == "fp8" else 0)
             elif a.kind == "mla":
                 n += (a.kv_lora + a.qk_rope) * es + (4 if self.kv_dtype == "fp8" else 0)
                 if a.index_heads:

@@ -1,4 +1,5 @@
-"""Grouped-query attention ops over the paged bf16 KV cache (csrc/cuda/attn_gqa.cu).
+"""Grouped-query attention ops over the paged KV cache, bf16 or e4m3 with one scale per (token, kv head)
+(csrc/cuda/attn_gqa.cu).
 
 ``rope_kv`` is the fused head-norm + RoPE + cache-write row op (reference op HEADNORM_ROPE,
 runtime/common/dev_isa.h:74-84); ``attention`` is the tcgen05 flash kernel that serves prefill
@@ -17,14 +18,16 @@ BF16 = torch.bfloat16
 
 
 def rope_kv(qkv, kc, vc, rope_tab, pos, seq, page_table, nq, nkv, hd, rot=None, pair_mode=0,
-            qn=None, kn=None, eps=1e-6, plus_one=False, q_out=None, gate_out=None):
+            qn=None, kn=None, eps=1e-6, plus_one=False, q_out=None, gate_out=None, kv_scale=None):
     """qkv [rows, (nq+2*nkv)*hd] bf16 -> q_out [rows, nq, hd]; K (roped) and V rows land in their cache cells.
-    With ``gate_out`` [rows, nq*hd] the query heads are [Q | gate] pairs (gated attention) and the gates are copied out."""
+    With ``gate_out`` [rows, nq*hd] the query heads are [Q | gate] pairs (gated attention) and the gates are copied out.
+    With ``kv_scale`` f32 [n_pages, 64, 2*nkv] the caches are e4m3 bytes (uint8 / float8 tensors) and every written cell
+    stores amax / 448 there (k scales, then v scales of the token)."""
     rows = qkv.shape[0]
     if q_out is None:
         q_out = torch.empty(rows, nq, hd, dtype=BF16, device=qkv.device)
     native.call("plow_rope_kv", q_out, qkv, qkv.stride(0), kc, vc, qn, kn, rope_tab, pos, seq, page_table,
-                page_table.shape[1], rows, nq, nkv, hd, hd if rot is None else rot, pair_mode, int(plus_one), float(eps), gate_out)
+                page_table.shape[1], rows, nq, nkv, hd, hd if rot is None else rot, pair_mode, int(plus_one), float(eps), gate_out, kv_scale)
     return q_out
 
 
@@ -53,17 +56,30 @@ class AttnWorkspace:
             self.opart = self.lse = None
 
 
-def attention(q, kc, vc, page_table, seq, pos, ws: AttnWorkspace, scale=None, window=0, out=None):
-    """q [rows, nq, hd] bf16; kc / vc [n_pages, 64, nkv, hd] bf16 -> out [rows, nq*hd] bf16."""
+def attention(q, kc, vc, page_table, seq, pos, ws: AttnWorkspace, scale=None, window=0, out=None, kv_scale=None):
+    """q [rows, nq, hd] bf16; kc / vc [n_pages, 64, nkv, hd] bf16 (or e4m3 bytes with ``kv_scale`` f32
+    [n_pages, 64, 2*nkv], head dim 128) -> out [rows, nq*hd] bf16."""
     rows, nq, hd = q.shape
     nkv = kc.shape[2]
     if out is None:
         out = torch.empty(rows, nq * hd, dtype=BF16, device=q.device)
     native.call("plow_gqa_attention", q, kc, vc, kc.shape[0], page_table, page_table.shape[1], seq, pos, rows, nq, nkv, hd,
                 int(window), ws.tiles_per_split, ws.max_splits, ws.items, ws.item_cap, ws.n_items, ws.row_ns,
-                ws.opart, ws.lse, out, float(scale if scale is not None else 1.0 / math.sqrt(hd)),
+                ws.opart, ws.lse, out, float(scale if scale is not None else 1.0 / math.sqrt(hd)), kv_scale,
                 native.status_word(q.device))
     return out
+
+
+def quant_cache(c):
+    """bf16 cache [n_pages, 64, nkv, hd] -> (e4m3 bytes as float8 tensor, f32 scales [n_pages, 64, nkv]) with the
+    writer's rule (scale = amax / 448 per cell); ``dequant_cache`` is what the attention kernel's converter forms."""
+    cf = c.float()
+    sc = cf.abs().amax(dim=-1).clamp_min(1e-12) / 448.0
+    return (cf / sc[..., None]).to(torch.float8_e4m3fn), sc
+
+
+def dequant_cache(c8, sc):
+    return (c8.float() * sc[..., None]).to(BF16)
 
 
 def reference(q, kc, vc, page_table, seq, pos, scale=None, window=0):

@@ -146,8 +146,8 @@ _SIGS = {
     "plow_gdn": "ppppipi" "ppppp" "iiiiip",
     "plow_gated_norm": "pppiipiiifp",
     "plow_sigmoid_gate": "ppplp",
-    "plow_gqa_attention": "ppplpipp" "iiiiiii" "pi" "ppppp" "fpp",
-    "plow_rope_kv": "ppi" "pppppppp" "i" "iiiiiii" "fpp",
+    "plow_gqa_attention": "ppplpipp" "iiiiiii" "pi" "ppppp" "fppp",
+    "plow_rope_kv": "ppi" "pppppppp" "i" "iiiiiii" "fppp",
     "plow_mla_prefill_attention": "ppplpipp" "iiii" "pi" "ppppp" "fpp",
     "plow_mla_latent_gather": "ppipppppp" "ipiiiip",
     "plow_mla_q_rope": "pippiiiiip",

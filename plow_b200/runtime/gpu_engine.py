@@ -712,11 +712,12 @@ class GpuEngine(EngineBase):
         rope = self.tensor(st, ins.t[6])
         nq, nkv, hd, rot, pair, plus_one = ins.i[0], ins.i[1], ins.i[2], ins.i[3], ins.i[4], ins.i[6]
         gate = self.tensor(st, ins.t[7]) if ins.i[7] and ins.t[7] != pk.T_NONE else None
-        if kc.dtype != BF16:
-            raise EngineError("the sm_100a GQA kernels read a bf16 KV cache; compile with plow_kv_dtype=bf16")
+        ksc = self.tensor(st, ins.t[7]) if not ins.i[7] and ins.t[7] != pk.T_NONE else None      # e4m3 cache: per-cell scales
+        if kc.dtype != BF16 and (ksc is None or kc.dtype != FP8 or hd != 128):
+            raise EngineError("the sm_100a GQA kernels read a bf16 KV cache, or an e4m3 one with head dim 128 and no gated attention")
         gqa_ops.rope_kv(qkv, kc, vc, rope, self.d_in[1], self.d_in[2], self.d_page_table, nq, nkv, hd, rot=rot,
                         pair_mode=pair, qn=qn, kn=kn, eps=float(ins.f[0]), plus_one=bool(plus_one),
-                        q_out=q_out.view(st.rows, nq, hd), gate_out=gate)
+                        q_out=q_out.view(st.rows, nq, hd), gate_out=gate, kv_scale=ksc)
 
     def _op_attn(self, st, ins):
         ao, q, kc, vc = (self.tensor(st, ins.t[k]) for k in range(4))
@@ -724,8 +725,9 @@ class GpuEngine(EngineBase):
         key = ("gqa_ws", nq, nkv, hd)
         if key not in st.scratch:
             st.scratch[key] = gqa_ops.AttnWorkspace(st.rows, nq, nkv, hd, self.max_ctx + PAGE, self.device)
+        ksc = self.tensor(st, ins.t[4]) if ins.t[4] != pk.T_NONE else None
         gqa_ops.attention(q.view(st.rows, nq, hd), kc, vc, self.d_page_table, self.d_in[2], self.d_in[1], st.scratch[key],
-                          scale=float(ins.f[0]), window=window, out=ao)
+                          scale=float(ins.f[0]), window=window, out=ao, kv_scale=ksc)
 
     # -- gated delta rule (hybrid linear-attention layers)
     def _op_gdn(self, st, ins):

@@ -83,3 +83,58 @@ def test_dense_engine_matches_reference(dense_assets, assets, interp):
             assert ((got - want).norm() / want.norm()).item() < 0.05
     if interp:
         assert all(st.interp is not None and st.interp.launches > 0 for st in eng.progs.values())
+
+
+def test_dense_engine_with_e4m3_kv_cache(tmp_path):
+    """plow_kv_dtype=fp8 on a GQA model: the writer stores e4m3 cells + per-cell scales, prefill and decode attention read
+    them through the converter warps; logits against the fp32 reference, and half the KV bytes per token (+ scales)."""
+    from safetensors.torch import load_file
+    from plow_b200 import plowc
+    from plow_b200.compiler import packet as pk
+    from plow_b200.models import config, reference
+    from plow_b200.runtime.engine import TokenBatch
+    from plow_b200.runtime.gpu_engine import GpuEngine
+    cfg = dict(CFG, plow_kv_dtype="fp8")
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=0, dtype=torch.bfloat16)
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", max_rows=256, prefill_buckets=[128, 256], decode_rungs=[4, 8], max_seqs=8)
+    spec = config.spec_from_config(cfg)
+    assert spec.kv_bytes_per_token() == 2 * (2 * 2 * 128 + 8 * 2) and config.spec_from_config(CFG).kv_bytes_per_token() == 2 * 2 * 2 * 128 * 2
+    eng = GpuEngine(tmp_path / "assets", max_slots=4, max_ctx=512)
+    kinds = {t.name: pk.DType(t.dtype) for t in eng.packet.tensors if t.tclass == pk.TClass.KV}
+    assert kinds["kv.0.k"] == pk.DType.E4M3 and kinds["kv.0.s"] == pk.DType.F32
+    state = {}
+    for f in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        state.update(load_file(f))
+    ref = reference.ReferenceModel(spec, {k: v.float() for k, v in state.items()})
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (150, 37)]
+    ids, pos, seq, samp = [], [], [], []
+    for s, p in enumerate(prompts):
+        eng.begin_slot(s, p)
+        eng.reserve(s, len(p) + 8)
+        ids += p
+        pos += list(range(len(p)))
+        seq += [s] * len(p)
+        samp.append(len(ids) - 1)
+    res = eng.step(TokenBatch(np.array(ids, np.int32), np.array(pos, np.int32), np.array(seq, np.int32),
+                              np.array(samp, np.int32), want_logits=True))
+    for s, p in enumerate(prompts):
+        want = ref.forward(torch.tensor(p))[-1]
+        rel = ((torch.from_numpy(res.logits[s]) - want).norm() / want.norm()).item()
+        assert rel < 0.06, (s, rel)
+        eng.commit(s, p)
+    cur = [list(p) for p in prompts]
+    for step in range(3):
+        nxt = [int(ref.forward(torch.tensor(c))[-1].argmax()) for c in cur]
+        for s in range(2):
+            eng.reserve(s, len(cur[s]) + 2)
+        r = eng.step(TokenBatch(np.array(nxt, np.int32), np.array([len(c) for c in cur], np.int32), np.array([0, 1], np.int32),
+                                np.array([0, 1], np.int32), decode=True, want_logits=True))
+        for s in range(2):
+            cur[s].append(nxt[s])
+            eng.commit(s, [nxt[s]])
+            want = ref.forward(torch.tensor(cur[s]))[-1]
+            rel = ((torch.from_numpy(r.logits[s]) - want).norm() / want.norm()).item()
+            assert rel < 0.06, (step, s, rel)
+    from plow_b200.ops import native
+    assert int(native.status_word(eng.device)[0]) == 0
