@@ -23,10 +23,14 @@
 // own sm_120 kernels are mma.sync flash kernels (runtime/nvidia/op_attention*.cuh).
 //
 // e4m3 cache (KV8 instantiation): K and V cells are e4m3 bytes with one f32 scale per (token, kv head).  The TMA warp
-// brings the raw byte tiles into a two-deep staging ring; four converter warps turn each tile into the bf16 operand
-// layout the MMAs read (value * scale, written with the same 128-byte swizzle a bf16 TMA load would produce) and hand
-// the stage to the MMA warp.  The math after that point is the bf16 kernel's own: half the cache bytes, same tiles
-// (reference: runtime/common/dev_isa.h:388-398, HEADNORM_ROPE_FP8 / FLASH_DECODE_FP8 / FLASH_PREFILL_FP8).
+// brings the raw byte tiles into a staging ring; converter warps rewrite each tile as bf16 operands in the layout the
+// MMAs read (the 128-byte swizzle a bf16 TMA load would produce) and hand the stage to the MMA warp.  The rewrite is
+// The rewrite is three integer instructions per element pair: the e4m3 byte s.eeee.mmm placed as the bf16
+// s.0000eeee.mmm0000 is exactly value * 2^-120 (normal and subnormal codes alike), so no float conversion is needed;
+// the per-token scales and the 2^120 go where a multiplication already is or costs one instruction: S columns are
+// multiplied by k_scale[j] * scale * log2e * 2^120 instead of the constant, P columns by v_scale[j] * 2^60 before
+// they are rounded to bf16, and the output by 2^60.  Half the cache bytes, same tiles
+// (reference: runtime/common/dev_isa.h:388-398, HEADNORM_ROPE_FP8 / FLASH_*_FP8).
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
@@ -38,7 +42,7 @@ namespace plow {
 constexpr int kGqaPage = 64;
 constexpr int kGqaThreads = 192;   // TMA warp, MMA warp, 4 softmax warps
 constexpr int kGqaThreads8 = 320;  // + 4 converter warps (e4m3 cache)
-constexpr int kGqaRaw = 2;         // raw e4m3 tiles in flight
+constexpr int kGqaRaw = 3;         // raw e4m3 tiles in flight; 4 operand stages behind them
 
 struct GqaItem { int r0, nt, kvh, split, tile0, ntiles, slot, ns; };
 
@@ -72,11 +76,15 @@ template <int HDQ, int HDV, bool KV8 = false> struct GqaCfg {
   static constexpr int kRawK = 64 * HDQ;                 // one raw e4m3 K tile: HDQ / 128 slabs of 64 rows x 128 bytes
   static constexpr int kRawStage = 64 * (HDQ + HDV);
   static constexpr int kRawBytes = KV8 ? kGqaRaw * kRawStage : 0;
-  static constexpr int kStages = (200 * 1024 - kQBytes - kRawBytes) / kStageBytes > 5 ? 5 : (200 * 1024 - kQBytes - kRawBytes) / kStageBytes;
-  static constexpr int kSmem = 1024 + kQBytes + kStages * kStageBytes + kRawBytes + 1024;
+  static constexpr int kStagesFit = (200 * 1024 - kQBytes) / kStageBytes;
+  static constexpr int kStages = KV8 ? 4 : (kStagesFit > 5 ? 5 : kStagesFit);
+  // per operand stage: 64 S-column and 64 P-column factors; then a ring of 128 page numbers for the converter warps
+  static constexpr int kColBytes = KV8 ? kStages * 128 * 4 + 128 * 4 : 0;
+  static constexpr int kSmem = 1024 + kQBytes + kStages * kStageBytes + kRawBytes + kColBytes + 1024;
   static constexpr int kThreads = KV8 ? kGqaThreads8 : kGqaThreads;
   static constexpr int kTmemCols = HDV <= 128 ? 256 : 512; // S: 2 x 64, O: HDV
   static_assert(kStages >= 2, "K/V stages do not fit");
+  static_assert(kSmem <= 227 * 1024, "shared memory budget");
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -122,7 +130,8 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
   uint8_t* q_smem = smem;
   uint8_t* kv_smem = smem + Cfg::kQBytes;
   uint8_t* raw_smem = kv_smem + Cfg::kStages * Cfg::kStageBytes;     // e4m3 cache: raw byte tiles (1024-aligned: all sizes are)
-  uint8_t* ctrl = raw_smem + Cfg::kRawBytes;
+  float* col_fac = reinterpret_cast<float*>(raw_smem + Cfg::kRawBytes);   // [kStages][128]
+  uint8_t* ctrl = raw_smem + Cfg::kRawBytes + Cfg::kColBytes;
   uint64_t* q_full = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* q_empty = q_full + 1;
   uint64_t* kv_full = q_empty + 1;                 // [kStages]
@@ -270,61 +279,85 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
     // 128-byte operand row).  Raw tiles and operand slabs are both 64 rows x 128 bytes with the 128-byte swizzle: the
     // 16-byte chunk j of row r sits at chunk j ^ (r & 7).
     const int u = threadIdx.x - 192;
+    static_assert(!KV8 || (Cfg::kSlabsQ == 2 && Cfg::kSlabsV == 2), "converter mapping: 256 units of 64 bytes per tile, two per thread");
     uint32_t kv_it = 0;
     bool ok = true;
     for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x) {
       const GqaItem w = item_at(it);
-      const int* pt = a.page_table + static_cast<size_t>(w.slot) * a.max_pages;
-      for (int i = 0; i < w.ntiles; ++i, ++kv_it) {
+      const int* pt = a.page_table + static_cast<size_t>(w.slot) * a.max_pages + w.tile0;
+      // page numbers of the item's tiles in a shared ring (128 entries, refilled 64 at a time, 64 tiles ahead): the
+      // scale fetch of tile i + 2 then starts from a shared-memory read instead of a dependent global load
+      int* pages = reinterpret_cast<int*>(col_fac + Cfg::kStages * 128);
+      pages[u] = u < w.ntiles ? pt[u] : 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      // thread u owns column factor u of every tile: k scale of token u (u < 64) or v scale of token u - 64, fetched two
+      // tiles ahead; three slots in rotation (the loop is unrolled by three: a register a load still fills is never copied)
+      auto scale_of = [&](int page) -> float {
+        return a.kv_scale[(static_cast<size_t>(page) * kGqaPage + (u & 63)) * 2 * a.nkv + (u >= 64 ? a.nkv : 0) + w.kvh];
+      };
+      const float fac = u < 64 ? a.scale_log2e * 0x1p120f : 0x1p60f;
+      float sl[3] = {0.f, 0.f, 0.f};
+      sl[0] = scale_of(pages[0]);
+      if (w.ntiles > 1) sl[1] = scale_of(pages[1]);
+      auto tile_step = [&](int i, float s_cur, float& s_nxt) -> bool {
         const int s = kv_it % Cfg::kStages, rs = kv_it % kGqaRaw;
-        const int page = pt[w.tile0 + i];
+        if (i + 2 < w.ntiles) s_nxt = scale_of(pages[(i + 2) & 127]);
+        // refill: tiles [i + 64, i + 128) replace the half of the ring whose tiles are all behind (first read 62 tiles
+        // and as many barriers from now)
+        if (i > 0 && (i & 63) == 0 && u < 64) pages[(i + 64 + u) & 127] = i + 64 + u < w.ntiles ? pt[i + 64 + u] : 0;
         bool mine = mbar_wait(&raw_full[rs], (kv_it / kGqaRaw) & 1, abort_flag) &&
                     mbar_wait(&kv_empty[s], ((kv_it / Cfg::kStages) & 1) ^ 1, abort_flag);
+        // column factors of the stage: [0,64) S factors, [64,128) the v scales the conversion below reads
+        if (mine) col_fac[s * 128 + u] = fminf(s_cur * fac, 3.0e38f);
         // one decision for all 128 threads (a barrier with an OR over "my wait ran out or somebody gave up")
         uint32_t stop;
         asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
                      : "=r"(stop) : "r"(static_cast<uint32_t>(!mine || *abort_flag)) : "memory");
         if (stop) {
           if (u == 0) { *abort_flag = 1; atomicCAS(a.status, 0, PLOW_ERR_STAGE_WAIT | kTagGqa); }
-          ok = false;
-          break;
+          return false;
         }
         const uint8_t* rw = raw_smem + rs * Cfg::kRawStage;
         uint8_t* st = kv_smem + s * Cfg::kStageBytes;
-        const float* sc = a.kv_scale + (static_cast<size_t>(page) * kGqaPage) * 2 * a.nkv;
-        constexpr int kUnitsK = 64 * Cfg::kSlabsQ, kUnits = 64 * (Cfg::kSlabsQ + Cfg::kSlabsV);
+        {
+          // thread u: the K unit and the V unit of (row u % 64, 64-dim half u / 64); both unrolled, so that the loads and
+          // the integer rewrites of 128 bytes overlap
+          const int slab = u >> 6, row = u & 63;
+          uint4 rv[8];
 #pragma unroll
-        for (int unit = u; unit < kUnits; unit += 128) {
-          const bool is_v = unit >= kUnitsK;
-          const int uu = is_v ? unit - kUnitsK : unit;
-          const int row = uu & 63, slab = uu >> 6;                  // out slab = 64 head dims
-          const float scale = sc[row * 2 * a.nkv + (is_v ? a.nkv : 0) + w.kvh];
-          const uint8_t* src = rw + (is_v ? Cfg::kRawK : 0) + (slab >> 1) * 8192 + row * 128;
-          uint8_t* dst = st + (is_v ? Cfg::kKBytes : 0) + slab * 8192 + row * 128;
+          for (int kv = 0; kv < 2; ++kv)
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {                             // 16 e4m3 bytes -> two 16-byte bf16 chunks
-            const int jc = ((slab & 1) * 4 + c) ^ (row & 7);
-            const uint4 rv = *reinterpret_cast<const uint4*>(src + jc * 16);
-            const uint32_t wv[4] = {rv.x, rv.y, rv.z, rv.w};
-            uint32_t o[8];
+            for (int c = 0; c < 4; ++c)
+              rv[kv * 4 + c] = *reinterpret_cast<const uint4*>(rw + (kv ? Cfg::kRawK : 0) + row * 128 + ((slab * 4 + c) ^ (row & 7)) * 16);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(wv[q] & 0xffffu), __NV_E4M3);
-              const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(wv[q] >> 16), __NV_E4M3);
-              const float2 fl = __half22float2(*reinterpret_cast<const __half2*>(&lo));
-              const float2 fh = __half22float2(*reinterpret_cast<const __half2*>(&hi));
-              const __nv_bfloat162 bl = __floats2bfloat162_rn(fl.x * scale, fl.y * scale);
-              const __nv_bfloat162 bh = __floats2bfloat162_rn(fh.x * scale, fh.y * scale);
-              o[2 * q] = *reinterpret_cast<const uint32_t*>(&bl);
-              o[2 * q + 1] = *reinterpret_cast<const uint32_t*>(&bh);
+          for (int kv = 0; kv < 2; ++kv) {
+            uint8_t* dst = st + (kv ? Cfg::kKBytes : 0) + slab * 8192 + row * 128;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {                           // 16 e4m3 bytes -> two 16-byte bf16 chunks
+              const uint32_t wv[4] = {rv[kv * 4 + c].x, rv[kv * 4 + c].y, rv[kv * 4 + c].z, rv[kv * 4 + c].w};
+              uint32_t o[8];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                // bytes (b0, b1) and (b2, b3) to the high bytes of two 16-bit lanes, then sign | (exp.mant >> 4)
+                const uint32_t lo = __byte_perm(wv[q], 0, 0x1404), hi = __byte_perm(wv[q], 0, 0x3424);
+                o[2 * q] = (lo & 0x80008000u) | ((lo >> 4) & 0x07f007f0u);
+                o[2 * q + 1] = (hi & 0x80008000u) | ((hi >> 4) & 0x07f007f0u);
+              }
+              *reinterpret_cast<uint4*>(dst + ((2 * c) ^ (row & 7)) * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+              *reinterpret_cast<uint4*>(dst + ((2 * c + 1) ^ (row & 7)) * 16) = make_uint4(o[4], o[5], o[6], o[7]);
             }
-            *reinterpret_cast<uint4*>(dst + ((2 * c) ^ (row & 7)) * 16) = make_uint4(o[0], o[1], o[2], o[3]);
-            *reinterpret_cast<uint4*>(dst + ((2 * c + 1) ^ (row & 7)) * 16) = make_uint4(o[4], o[5], o[6], o[7]);
           }
         }
         fence_proxy_async_smem();       // the MMAs read these stores through the async proxy
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (u == 0) { mbar_arrive(&kv_full[s]); mbar_arrive(&raw_empty[rs]); }
+        ++kv_it;
+        return true;
+      };
+      for (int i = 0; ok && i < w.ntiles; i += 3) {
+        ok = tile_step(i, sl[0], sl[2]);
+        if (ok && i + 1 < w.ntiles) ok = tile_step(i + 1, sl[1], sl[0]);
+        if (ok && i + 2 < w.ntiles) ok = tile_step(i + 2, sl[2], sl[1]);
       }
     }
   } else {
@@ -353,7 +386,35 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
           tmem_ld_wait();
           const int t0 = (w.tile0 + i) * kGqaPage;
           float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-          if (t0 >= lo && t0 + kGqaPage - 1 <= hi) {
+          // e4m3 cache: per-column factors of this tile's operand stage ([0,64): for S, [64,128): for P)
+          const float* cf = col_fac + (ti % Cfg::kStages) * 128;
+          if constexpr (KV8) {
+            const float4* c4 = reinterpret_cast<const float4*>(cf);
+            if (t0 >= lo && t0 + kGqaPage - 1 <= hi) {
+#pragma unroll
+              for (int j = 0; j < 64; j += 4) {
+                const float4 c = c4[j >> 2];
+                const float x0 = __uint_as_float(sv[j]) * c.x, x1 = __uint_as_float(sv[j + 1]) * c.y;
+                const float x2 = __uint_as_float(sv[j + 2]) * c.z, x3 = __uint_as_float(sv[j + 3]) * c.w;
+                sv[j] = __float_as_uint(x0); sv[j + 1] = __float_as_uint(x1);
+                sv[j + 2] = __float_as_uint(x2); sv[j + 3] = __float_as_uint(x3);
+                mxa[0] = fmaxf(mxa[0], x0); mxa[1] = fmaxf(mxa[1], x1); mxa[2] = fmaxf(mxa[2], x2); mxa[3] = fmaxf(mxa[3], x3);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 64; j += 4) {
+                const float4 c = c4[j >> 2];
+                const float cc[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int t = t0 + j + e;
+                  const float x = (t >= lo && t <= hi) ? __uint_as_float(sv[j + e]) * cc[e] : -INFINITY;
+                  sv[j + e] = __float_as_uint(x);
+                  mxa[e] = fmaxf(mxa[e], x);
+                }
+              }
+            }
+          } else if (t0 >= lo && t0 + kGqaPage - 1 <= hi) {
 #pragma unroll
             for (int j = 0; j < 64; ++j) {
               const float x = __uint_as_float(sv[j]) * a.scale_log2e;
@@ -399,12 +460,20 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
           }
           float sa = 0.f, sb = 0.f;
           uint32_t pk[32];
+          const float4* d4 = reinterpret_cast<const float4*>(cf + 64);
 #pragma unroll
-          for (int j = 0; j < 64; j += 2) {
-            const float e0 = exp2f(__uint_as_float(sv[j]) - m), e1 = exp2f(__uint_as_float(sv[j + 1]) - m);
-            sa += e0; sb += e1;
-            const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-            pk[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+          for (int j = 0; j < 64; j += 4) {
+            float e[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) e[q] = exp2f(__uint_as_float(sv[j + q]) - m);
+            sa += e[0] + e[2]; sb += e[1] + e[3];
+            if constexpr (KV8) {
+              const float4 d = d4[j >> 2];
+              e[0] *= d.x; e[1] *= d.y; e[2] *= d.z; e[3] *= d.w;
+            }
+            const __nv_bfloat162 h0 = __floats2bfloat162_rn(e[0], e[1]), h1 = __floats2bfloat162_rn(e[2], e[3]);
+            pk[j >> 1] = *reinterpret_cast<const uint32_t*>(&h0);
+            pk[(j >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&h1);
           }
           l += sa + sb;
           tmem_st16(tm_s + lane_addr + (ti & 1) * 64, pk);
@@ -424,7 +493,7 @@ gqa_attn_kernel(const GqaArgs a, const __grid_constant__ CUtensorMap tm_q, const
         const bool row_ok = li < n_valid;
         const int row = w.r0 + li / a.group;
         const int head = w.kvh * a.group + li % a.group;
-        const float fin = l > 0.f ? 1.0f / l : 0.f;
+        const float fin = (l > 0.f ? 1.0f / l : 0.f) * (KV8 ? 0x1p60f : 1.0f);    // e4m3 cache: the accumulator carries 2^-60
 #pragma unroll 1
         for (int c = 0; c < HD; c += 32) {
           uint32_t o[32];

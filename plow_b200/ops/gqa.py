@@ -126,6 +126,32 @@ def profile_decode(iters, timer):
     return dict(us=us, flops=4.0 * n_seq * ctx * nq * hd, bytes=2.0 * 2 * n_seq * ctx * nkv * hd)
 
 
+def profile_decode_e4m3(iters, timer):
+    """The decode case over an e4m3 cache: half the cache bytes (+ 8 bytes of scales per token and kv head pair)."""
+    n_seq, ctx, nq, nkv, hd = 64, 4096, 32, 8, 128
+    q, kc, vc, pt, seq, pos = _paged_case(n_seq, ctx, nq, nkv, hd, 1)
+    k8, ks = quant_cache(kc)
+    v8, vs = quant_cache(vc)
+    sc = torch.cat([ks, vs], dim=-1).contiguous()
+    del kc, vc
+    ws = AttnWorkspace(n_seq, nq, nkv, hd, ctx, q.device)
+    out = torch.empty(n_seq, nq * hd, dtype=BF16, device=q.device)
+    us = timer(lambda: attention(q, k8, v8, pt, seq, pos, ws, out=out, kv_scale=sc), iters)
+    return dict(us=us, flops=4.0 * n_seq * ctx * nq * hd, bytes=2.0 * n_seq * ctx * nkv * (hd + 4))
+
+
+def profile_prefill_e4m3(iters, timer):
+    ctx, nq, nkv, hd = 4096, 32, 8, 128
+    q, kc, vc, pt, seq, pos = _paged_case(1, ctx, nq, nkv, hd, ctx)
+    k8, ks = quant_cache(kc)
+    v8, vs = quant_cache(vc)
+    sc = torch.cat([ks, vs], dim=-1).contiguous()
+    ws = AttnWorkspace(ctx, nq, nkv, hd, ctx, q.device, max_splits=1)
+    out = torch.empty(ctx, nq * hd, dtype=BF16, device=q.device)
+    us = timer(lambda: attention(q, k8, v8, pt, seq, pos, ws, out=out, kv_scale=sc), iters)
+    return dict(us=us, flops=4.0 * ctx * ctx / 2 * nq * hd, bytes=2.0 * ctx * nkv * (hd + 4) + 2.0 * 2 * ctx * nq * hd)
+
+
 def profile_prefill(iters, timer):
     ctx, nq, nkv, hd = 4096, 32, 8, 128
     q, kc, vc, pt, seq, pos = _paged_case(1, ctx, nq, nkv, hd, ctx)

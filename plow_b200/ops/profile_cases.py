@@ -14,7 +14,9 @@ Cases
     gemm_moe         32 experts x (4096 -> 2x2048) grouped SwiGLU, 16 rows per expert
     mla_decode       74 requests x 4096 cached tokens, 128 heads, e4m3 latent cache
     gqa_decode       64 requests x 4096 cached tokens, 32/8 heads, hd128 bf16 paged cache
+    gqa_decode_e4m3  the same over an e4m3 cache with per-cell scales
     gqa_prefill      one 4096-token prompt, 32/8 heads, hd128
+    gqa_prefill_e4m3 the same over an e4m3 cache
     dsa_topk         64 rows x 32768 scores, exact top-2048
 """
 from __future__ import annotations
@@ -166,6 +168,16 @@ def case_mla_decode(iters):
 def case_gqa_decode(iters):
     from . import gqa
     return gqa.profile_decode(iters, _time)
+
+
+def case_gqa_decode_e4m3(iters):
+    from . import gqa
+    return gqa.profile_decode_e4m3(iters, _time)
+
+
+def case_gqa_prefill_e4m3(iters):
+    from . import gqa
+    return gqa.profile_prefill_e4m3(iters, _time)
 
 
 def case_gqa_prefill(iters):
