@@ -282,7 +282,10 @@ void op_rope_kv(const Ctx& c) {
   const int gmode = c.in->i[6];
   const float eps = c.in->w[0].f;
   const StepIO& io = c.e->io;
-  const int W = (nq + 2 * nkv) * hd;
+  // gated attention: query heads arrive as [Q (hd) | gate (hd)] pairs and the gates are copied to t7 [rows][nq*hd]
+  float* gate_out = c.in->i[7] ? (float*)c.T(7) : nullptr;
+  const int qw = gate_out ? 2 * hd : hd;
+  const int W = nq * qw + 2 * nkv * hd;
   std::vector<float> tmp(hd);
   int64_t a, b;
   c.range(io.rows, a, b);
@@ -293,15 +296,17 @@ void op_rope_kv(const Ctx& c) {
     const int64_t cell = (int64_t(page) * PLOW_KV_PAGE + pos % PLOW_KV_PAGE) * nkv * hd;
     const float* row = qkv + r * W;
     for (int h = 0; h < nq; ++h) {
-      const float* src = row + h * hd;
+      const float* src = row + h * qw;
+      if (gate_out) std::memcpy(gate_out + (r * nq + h) * hd, src + hd, sizeof(float) * hd);
       if (qn) { rmsnorm_row(tmp.data(), src, qn, hd, eps, gmode); src = tmp.data(); }
       rope_head(qo + (r * nq + h) * hd, src, tab, hd, rot, pair);
     }
+    const float* kv_row = row + nq * qw;
     for (int h = 0; h < nkv; ++h) {
-      const float* src = row + (nq + h) * hd;
+      const float* src = kv_row + h * hd;
       if (kn) { rmsnorm_row(tmp.data(), src, kn, hd, eps, gmode); src = tmp.data(); }
       rope_head(kc + cell + h * hd, src, tab, hd, rot, pair);
-      std::memcpy(vc + cell + h * hd, row + (nq + nkv + h) * hd, sizeof(float) * hd);
+      std::memcpy(vc + cell + h * hd, kv_row + (nkv + h) * hd, sizeof(float) * hd);
     }
   }
 }
@@ -383,6 +388,106 @@ void op_glu(const Ctx& c) {
   for (int64_t k = a * W; k < b * W; ++k) out[k] = g[k] / (1.0f + std::exp(-g[k])) * u[k];
 }
 
+
+// ---- gated delta rule (golden f32) ---------------------------------------------------------------------------------
+// t0=out [rows][hv*d]  t1=conv state [slots][C][conv-1] (oldest input first)  t2=recurrent state [slots][hv][d(V)][d(K)]
+// t3=qkvz [rows][(2hk+hv)d | hv*d]  t4=ba [rows][hv | hv]  t5=conv weight [C][conv]  t6=A_log [hv]  t7=dt_bias [hv]
+// i0=hk i1=hv i2=d i3=conv.  Per token: causal depthwise conv + SiLU over the packed q|k|v channels, q and k L2-normalised,
+// S <- alpha S; S += beta (v - S k) k^T; out = S q / sqrt(d).  A row at position 0 starts its slot from zero state.
+// Work is split by slot (the state of a sequence is touched by one entry only); rows of a slot come in position order.
+// Reference semantics: runtime/nvidia/op_qwen_gdn.cuh, runtime/common/dev_isa.h:1259-1280.
+void op_gdn(const Ctx& c) {
+  float* out = (float*)c.T(0);
+  float* conv_state = (float*)c.T(1);
+  float* ssm = (float*)c.T(2);
+  const float* qkvz = (const float*)c.T(3);
+  const float* ba = (const float*)c.T(4);
+  const float* cw = (const float*)c.T(5);
+  const float* a_log = (const float*)c.T(6);
+  const float* dt_bias = (const float*)c.T(7);
+  const int hk = c.in->i[0], hv = c.in->i[1], d = c.in->i[2], conv = c.in->i[3];
+  const int C = (2 * hk + hv) * d, Wq = C + hv * d, rep = hv / hk, hist = conv - 1;
+  const StepIO& io = c.e->io;
+  std::vector<float> x(C), pred(d);
+  for (int64_t r = 0; r < io.rows; ++r) {
+    const int slot = io.seq[r], pos = io.pos[r];
+    if (pos < 0 || slot % c.ns < c.s0 || slot % c.ns >= c.s1) continue;
+    float* hs = conv_state + int64_t(slot) * C * hist;
+    float* S = ssm + int64_t(slot) * hv * d * d;
+    if (pos == 0) {
+      std::fill(hs, hs + int64_t(C) * hist, 0.f);
+      std::fill(S, S + int64_t(hv) * d * d, 0.f);
+    }
+    const float* row = qkvz + r * Wq;
+    for (int ch = 0; ch < C; ++ch) {
+      float* h = hs + int64_t(ch) * hist;
+      float acc = cw[ch * conv + hist] * row[ch];
+      for (int j = 0; j < hist; ++j) acc += cw[ch * conv + j] * h[j];
+      for (int j = 0; j + 1 < hist; ++j) h[j] = h[j + 1];
+      if (hist > 0) h[hist - 1] = row[ch];
+      x[ch] = acc / (1.0f + std::exp(-acc));
+    }
+    for (int h = 0; h < 2 * hk; ++h) {          // q heads, then k heads: x / sqrt(sum x^2 + 1e-6)
+      float* v = x.data() + h * d;
+      const float rs = 1.0f / std::sqrt(dotf(v, v, d) + 1e-6f);
+      for (int i = 0; i < d; ++i) v[i] *= rs;
+    }
+    const float scale = 1.0f / std::sqrt(float(d));
+    for (int h = 0; h < hv; ++h) {
+      const float* q = x.data() + (h / rep) * d;
+      const float* k = x.data() + (hk + h / rep) * d;
+      const float* v = x.data() + 2 * hk * d + h * d;
+      const float beta = 1.0f / (1.0f + std::exp(-ba[r * 2 * hv + h]));
+      const float al = ba[r * 2 * hv + hv + h] + dt_bias[h];
+      const float sp = al > 20.f ? al : std::log1p(std::exp(al));
+      const float alpha = std::exp(-std::exp(a_log[h]) * sp);
+      float* Sh = S + int64_t(h) * d * d;
+      for (int i = 0; i < d; ++i) {
+        float* Sr = Sh + int64_t(i) * d;
+        for (int j = 0; j < d; ++j) Sr[j] *= alpha;
+        pred[i] = dotf(Sr, k, d);
+      }
+      for (int i = 0; i < d; ++i) {
+        float* Sr = Sh + int64_t(i) * d;
+        const float u = beta * (v[i] - pred[i]);
+        for (int j = 0; j < d; ++j) Sr[j] += u * k[j];
+        out[(r * hv + h) * d + i] = dotf(Sr, q, d) * scale;
+      }
+    }
+  }
+}
+
+// t0=out t1=o [rows][heads*hd] t2=z source (columns z_offset.. of its rows) t3=gamma [hd]; i0=heads i1=hd i2=z_offset; f0=eps:
+// out = rmsnorm_per_head(o) * gamma * silu(z)
+void op_gated_norm(const Ctx& c) {
+  float* out = (float*)c.T(0);
+  const float* o = (const float*)c.T(1);
+  const float* zsrc = (const float*)c.T(2);
+  const float* gamma = (const float*)c.T(3);
+  const int heads = c.in->i[0], hd = c.in->i[1], zo = c.in->i[2];
+  const float eps = c.in->w[0].f;
+  const int zw = int(c.e->pkt->tensors[c.in->t[2]].dims[1]);
+  int64_t a, b;
+  c.range(c.e->io.rows, a, b);
+  for (int64_t r = a; r < b; ++r)
+    for (int h = 0; h < heads; ++h) {
+      const float* x = o + (r * heads + h) * hd;
+      const float* z = zsrc + r * zw + zo + h * hd;
+      const float rs = 1.0f / std::sqrt(dotf(x, x, hd) / hd + eps);
+      for (int i = 0; i < hd; ++i) out[(r * heads + h) * hd + i] = x[i] * rs * gamma[i] * (z[i] / (1.0f + std::exp(-z[i])));
+    }
+}
+
+// t0=out t1=a t2=gate: out = a * sigmoid(gate)
+void op_sigmoid_gate(const Ctx& c) {
+  float* out = (float*)c.T(0);
+  const float* x = (const float*)c.T(1);
+  const float* g = (const float*)c.T(2);
+  const int W = int(c.e->pkt->tensors[c.in->t[0]].dims[1]);
+  int64_t a, b;
+  c.range(c.e->io.rows, a, b);
+  for (int64_t k = a * W; k < b * W; ++k) out[k] = x[k] / (1.0f + std::exp(-g[k]));
+}
 
 // ---- multi-head latent attention (golden f32; cache row = [c_kv (kv_lora) | k_rope (qk_rope)]) -----------------
 // Reference semantics: runtime/nvidia/op_mla.cuh:23-42 (absorbed scores over the latent cache, W_uv folded once).
@@ -670,6 +775,9 @@ int exec_entry(Engine* e, const PlowInst* in, const PlowStreamEnt& se) {
     case PLOW_OP_MLA_KV_WRITE: op_mla_kv_write(c); return 0;
     case PLOW_OP_MLA_DECODE:
     case PLOW_OP_MLA_PREFILL: op_mla_attn(c); return 0;
+    case PLOW_OP_GDN_STEP: op_gdn(c); return 0;
+    case PLOW_OP_GATED_NORM: op_gated_norm(c); return 0;
+    case PLOW_OP_SIGMOID_GATE: op_sigmoid_gate(c); return 0;
     case PLOW_OP_DSA_INDEX: op_dsa_index(c); return 0;
     case PLOW_OP_DSA_TOPK: op_dsa_topk(c); return 0;
     case PLOW_OP_ROUTER_TOPK: op_router_topk(c); return 0;

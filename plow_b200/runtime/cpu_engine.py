@@ -90,6 +90,9 @@ class CpuEngine(EngineBase):
             elif tc == pk.TClass.KV:
                 dims = [self.pool.n_pages if d == -3 else d for d in t.dims]
                 self._bind(h, np.zeros(dims, dtype=np.float32))
+            elif tc == pk.TClass.STATE:          # recurrent state: one entry per slot, zero until position 0 resets it
+                dims = [self.max_slots if d == -4 else d for d in t.dims]
+                self._bind(h, np.zeros(dims, dtype=np.float32))
             elif tc == pk.TClass.INPUT:
                 self._bind(h, {"in.ids": self.in_ids, "in.pos": self.in_pos, "in.seq": self.in_seq,
                                "in.sample_rows": self.in_sample, "in.hidden": self.in_hidden}[t.name])
@@ -121,6 +124,9 @@ class CpuEngine(EngineBase):
 
     def kv_arrays(self) -> dict:
         return {t.name: self._keep[h] for h, t in enumerate(self.packet.tensors) if t.tclass == pk.TClass.KV}
+
+    def state_arrays(self) -> dict:
+        return {t.name: self._keep[h] for h, t in enumerate(self.packet.tensors) if t.tclass == pk.TClass.STATE}
 
     def close(self) -> None:
         if getattr(self, "_eng", None):

@@ -366,3 +366,69 @@ def test_sparse_attention_model_on_cpu_backend_matches_reference(tmp_path):
         assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 5e-4 * max(1.0, want.abs().max().item())
         nxt = int(want.argmax())
     eng.close()
+
+
+def test_gdn_hybrid_model_on_cpu_backend_matches_reference(tmp_path):
+    """Golden gated-delta-rule ops of the C++ interpreter (causal depthwise conv + SiLU, L2-normalised q / k, the state
+    update, the gated per-head norm) and gated full attention ([Q | gate] query heads, partial rotary, (1 + gamma)
+    norms) on a small hybrid MoE model: a prompt prefilled in two chunks with a second sequence packed beside it (the
+    recurrent state is per slot and carried between steps), then decode, against the PyTorch fp32 reference."""
+    import glob
+    from safetensors.torch import load_file
+    from plow_b200 import plowc
+    from plow_b200.models import config, reference
+    from plow_b200.runtime.engine import TokenBatch
+    cfg = dict(model_type="qwen3_next", hidden_size=256, num_hidden_layers=4, full_attention_interval=4,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=64, partial_rotary_factor=0.25,
+               linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32, linear_value_head_dim=32,
+               linear_conv_kernel_dim=4, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
+               shared_expert_intermediate_size=64, norm_topk_prob=True, rms_norm_eps=1e-6, rope_theta=10000.0,
+               vocab_size=512, tie_word_embeddings=False, max_position_embeddings=1024, eos_token_id=1,
+               plow_dtype="f32", plow_kv_dtype="f32")
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=0)
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", arch="cpu", n_cu=4, max_rows=128, decode_rungs=[1, 2, 4], max_seqs=4)
+    eng = CpuEngine(tmp_path / "assets", max_slots=3, max_ctx=256)
+    assert eng.has_recurrent_state and set(eng.state_arrays()) == {f"state.{i}.{k}" for i in (0, 1, 2) for k in ("conv", "ssm")}
+    state = {}
+    for f in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        state.update(load_file(f))
+    ref = reference.ReferenceModel(config.spec_from_config(cfg), {k: v.float() for k, v in state.items()})
+    rng = np.random.default_rng(2)
+    pa, pb = rng.integers(0, 512, 90).tolist(), rng.integers(0, 512, 33).tolist()
+
+    def close(got, want):
+        return (torch.from_numpy(got) - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item())
+    # step 1: the first 50 tokens of A (slot 2) and all of B (slot 0) in one batch; step 2: the rest of A
+    eng.begin_slot(2, pa)
+    eng.begin_slot(0, pb)
+    eng.reserve(2, len(pa) + 4)
+    eng.reserve(0, len(pb) + 4)
+    ids = pa[:50] + pb
+    r = eng.step(TokenBatch(np.asarray(ids, np.int32), np.asarray(list(range(50)) + list(range(len(pb))), np.int32),
+                            np.asarray([2] * 50 + [0] * len(pb), np.int32), np.asarray([49, len(ids) - 1], np.int32), want_logits=True))
+    assert close(r.logits[0], ref.forward(torch.tensor(pa[:50]))[-1]) and close(r.logits[1], ref.forward(torch.tensor(pb))[-1])
+    eng.commit(2, pa[:50])
+    eng.commit(0, pb)
+    r = eng.step(TokenBatch(np.asarray(pa[50:], np.int32), np.arange(50, len(pa), dtype=np.int32), np.full(len(pa) - 50, 2, np.int32),
+                            np.asarray([len(pa) - 51], np.int32), want_logits=True))
+    assert close(r.logits[0], ref.forward(torch.tensor(pa))[-1])
+    eng.commit(2, pa[50:])
+    # decode both sequences together for three steps
+    cur = {2: list(pa), 0: list(pb)}
+    for _ in range(3):
+        nxt = {s: int(ref.forward(torch.tensor(c))[-1].argmax()) for s, c in cur.items()}
+        slots = sorted(cur)
+        r = eng.step(TokenBatch(np.asarray([nxt[s] for s in slots], np.int32), np.asarray([len(cur[s]) for s in slots], np.int32),
+                                np.asarray(slots, np.int32), np.arange(2, dtype=np.int32), decode=True, want_logits=True))
+        for k, s in enumerate(slots):
+            cur[s].append(nxt[s])
+            eng.commit(s, [nxt[s]])
+            assert close(r.logits[k], ref.forward(torch.tensor(cur[s]))[-1])
+    # a new sequence in a used slot starts from zero state (position 0 resets it)
+    eng.retire_slot(0)
+    eng.begin_slot(0, pa[:20])
+    eng.reserve(0, 24)
+    r = eng.step(TokenBatch(np.asarray(pa[:20], np.int32), np.arange(20, dtype=np.int32), np.zeros(20, np.int32),
+                            np.asarray([19], np.int32), want_logits=True))
+    assert close(r.logits[0], ref.forward(torch.tensor(pa[:20]))[-1])
+    eng.close()
