@@ -209,6 +209,20 @@ class EngineBase:
             ids = np.asarray(r.ids, dtype=np.int32)
         return out
 
+    # ---- lookahead-1 decode pipeline (reference: crates/plowrt/src/exec/gpu.rs:10667, pipe_step) ---------------------
+    def step_launch(self, batch: TokenBatch, chain_from=None):
+        """Start a decode step and return a handle for step_collect.  With ``chain_from`` (the handle of the step launched
+        just before, same rows) the input ids are that step's output ids, which the host has not read yet: the caller
+        can launch step n + 1 before it collects step n and do its own work for step n while the device runs n + 1.
+        This default runs the step at once (the CPU backend); the sm_100a engine leaves it running on the device."""
+        if chain_from is not None:
+            batch = TokenBatch(np.asarray(chain_from["result"].ids[:batch.rows], np.int32), batch.pos, batch.seq, batch.sample_rows,
+                               decode=batch.decode, want_logits=batch.want_logits)
+        return dict(result=self.step(batch))
+
+    def step_collect(self, handle) -> StepResult:
+        return handle["result"]
+
     def bind_thread(self) -> None:
         """Called by a thread before it drives the engine (the current CUDA device is per host thread)."""
 

@@ -1007,6 +1007,67 @@ class GpuEngine(EngineBase):
         ids = self._h_multi_out[:k, :rows].numpy().copy()
         return [StepResult(ids=ids[i], logits=None, device_ms=ms / k) for i in range(k)]
 
+    def step_launch(self, batch: TokenBatch, chain_from=None):
+        """A decode rung's graph replayed without waiting for it: inputs go through one of two pinned staging blocks (the
+        previous launch may not have read its block yet), a chained launch takes its ids from the previous step's output
+        on the device, and the ids come back through one of two pinned result blocks that step_collect reads after the
+        launch's event.  Anything the graph path does not cover (first use of a rung, logits, rank groups) runs as a
+        plain step."""
+        rows = batch.rows
+        st = self.progs.get(self.pick_program(max(rows, 1), True)) if batch.decode else None
+        plain = (not batch.decode or st is None or st.graph is None or not self.cuda_graphs or batch.want_logits or batch.want_hidden
+                 or batch.hidden is not None or self.step_group is not None or self.leader_group is not None
+                 or int(batch.sample_rows.shape[0]) != rows
+                 or not np.array_equal(batch.sample_rows, np.arange(rows, dtype=batch.sample_rows.dtype)))
+        if plain or (chain_from is not None and "event" not in chain_from):
+            if chain_from is not None and "event" in chain_from:
+                chain_from = dict(result=self.step_collect(chain_from))
+            return super().step_launch(batch, chain_from)
+        if getattr(self, "_la_in", None) is None:
+            self._la_in = [torch.zeros_like(self.h_in).pin_memory() for _ in range(2)]
+            self._la_out = [torch.zeros_like(self.h_out).pin_memory() for _ in range(2)]
+            self._la_n = 0
+        k = self._la_n & 1
+        self._la_n += 1
+        R = st.rows
+        hin = self._la_in[k]
+        hin[0, :rows] = 0 if chain_from is not None else torch.from_numpy(batch.ids)
+        hin[1, :rows] = torch.from_numpy(batch.pos)
+        hin[2, :rows] = torch.from_numpy(batch.seq)
+        hin[0, rows:R] = 0
+        hin[1, rows:R] = 0
+        hin[2, rows:R] = self.scratch_slot
+        hin[3, :rows] = torch.from_numpy(batch.sample_rows)
+        hin[3, rows:st.samples] = 0
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        self._upload_pages()
+        if chain_from is not None:
+            self.d_in[1:, :R].copy_(hin[1:, :R], non_blocking=True)
+            self.d_in[0, :rows].copy_(self.d_out_ids[:rows])          # the previous step's tokens, still on the device
+        else:
+            self.d_in[:, :R].copy_(hin[:, :R], non_blocking=True)
+        torch.add(self.d_in[1, :R], 1, out=self.d_kvlen_row[:R])
+        self._mla_plan = None
+        st.scratch["dsa_dense_ok"] = False
+        st.graph.replay()
+        self._la_out[k][:rows].copy_(self.d_out_ids[:rows], non_blocking=True)
+        ev1.record()
+        return dict(event=(ev0, ev1), out=self._la_out[k], rows=rows)
+
+    def step_collect(self, handle) -> StepResult:
+        if "event" not in handle:
+            return handle["result"]
+        ev0, ev1 = handle["event"]
+        try:
+            ev1.synchronize()
+            native.check_status(self.device)
+        except native.NativeLibraryError as e:
+            self._recover_after_device_status()
+            raise EngineError(str(e), fatal=False)
+        self.step_ms_last = ev0.elapsed_time(ev1)
+        return StepResult(ids=handle["out"][:handle["rows"]].numpy().copy(), logits=None, device_ms=self.step_ms_last)
+
     def kv_arrays(self) -> dict:
         out = {t.name: self.static[h] for h, t in enumerate(self.packet.tensors) if t.tclass == pk.TClass.KV}
         out.update({f"smax.{layer}": v for layer, v in self.kv_smax.items()})   # per-page scale bounds of fp8 latent caches

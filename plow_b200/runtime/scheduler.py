@@ -107,6 +107,7 @@ class SchedConfig:
     ride: bool = True                 # decode rows ride the prefill launch (mixed step) instead of waiting a tick
     spec_depth: int = 0               # > 0: speculative decoding for greedy requests (prompt-lookup drafts, span verify)
     multi_step: int = 1               # > 1: greedy decode ticks run this many steps per engine call (tokens fed back on the device)
+    lookahead: bool = False           # decode step n + 1 is launched (fed on the device) before step n's tokens are read
     session_ttl_s: float = 600.0      # a finished request that carried a session id keeps its slot and KV this long
     max_sessions: int = -1            # retained sessions at most (-1: half of the slots; 0: retention off)
 
@@ -184,6 +185,7 @@ class ModelMux:
         self.retained: "OrderedDict[str, tuple]" = OrderedDict()
         self.pd_target: "ModelMux | None" = None     # prefill/decode disaggregation: where finished prefills continue
         self.adopt_q: "queue.Queue" = queue.Queue()  # (request, KV image) pairs handed over by a prefill mux
+        self._inflight: dict | None = None           # lookahead: the decode step launched but not yet collected
 
     # ---- public --------------------------------------------------------------------------------
     def start(self) -> "ModelMux":
@@ -195,6 +197,12 @@ class ModelMux:
         self._stop.set()
         if self._thread:
             self._thread.join(timeout=10)
+        if self._inflight is not None:
+            try:
+                self.engine.step_collect(self._inflight["handle"])
+            except Exception:
+                pass
+            self._inflight = None
         grp = getattr(self.engine, "step_group", None) or getattr(self.engine, "leader_group", None)
         if grp is not None:
             grp.stop()          # releases the other ranks from their next agreement / receive
@@ -296,6 +304,9 @@ class ModelMux:
                 self.waiting.append(self.ingress.get_nowait())
             except queue.Empty:
                 break
+        if self._inflight is not None:
+            self._lookahead_tick()
+            return True
         if self._drain_deadline is not None and time.monotonic() > self._drain_deadline:
             for r in list(self.live.values()):
                 self._finish(r, "preempted")
@@ -725,6 +736,12 @@ class ModelMux:
                         self._produce(r, int(res.ids[j]), None)
                 fed = res.ids
             return
+        if self._lookahead_ok(reqs, 1):
+            # lookahead-1: leave the step running; the next tick launches its successor (fed on the device) and only
+            # then reads this one's tokens, so the host's work for step n overlaps the device's step n + 1
+            self._inflight = dict(handle=eng.step_launch(batch), reqs=reqs, fed=ids, pos=pos, seq=seq)
+            self.metrics.inc("decode_ticks")
+            return
         res = eng.step(batch)
         self.metrics.inc("decode_ticks")
         seen = []
@@ -736,6 +753,53 @@ class ModelMux:
                 seen.append((slot, int(pos[k]), [r.generated[-1]], res.hidden[k:k + 1]))
         if seen:
             mtp.observe(seen)
+
+    def _lookahead_ok(self, reqs: list, ahead: int) -> bool:
+        """May a decode step of these requests be left in flight (ahead = 1), or chained behind the one in flight
+        (ahead = 2)?  Only plain greedy requests with at least ``ahead`` more tokens to produce, nobody waiting to be
+        admitted or prefilled, no drafter, no rank group (the other ranks follow synchronous steps)."""
+        eng = self.engine
+        if not self.cfg.lookahead or self.cfg.spec_depth > 0 or self.waiting or not self.ingress.empty() or not self.adopt_q.empty() \
+                or self.draining or getattr(eng, "step_group", None) is not None or getattr(eng, "leader_group", None) is not None:
+            return False
+        if any(q.done_prefill < q.pf_len for q in self.live.values()):
+            return False
+        now = time.monotonic()
+        for r in reqs:
+            p = r.params
+            if self.live.get(r.slot) is not r or r.cancelled or not p.greedy or p.stop or p.json_mode \
+                    or (r.deadline is not None and now > r.deadline):
+                return False
+            n_ctx = len(r.prompt) + len(r.generated)
+            if p.max_tokens - len(r.generated) < ahead or n_ctx + ahead + 1 > eng.max_ctx:
+                return False
+        return True
+
+    def _lookahead_tick(self) -> None:
+        """A decode step is in flight.  If its requests can all go on, launch the next step first (its ids come from the
+        in-flight step's output on the device), then collect the in-flight one and hand out its tokens.  A request that
+        ends with this token simply leaves a row of the chained step unused."""
+        eng, inf = self.engine, self._inflight
+        reqs, pos, seq = inf["reqs"], inf["pos"], inf["seq"]
+        nxt = None
+        if self._lookahead_ok(reqs, 2):
+            try:
+                for r in reqs:
+                    eng.reserve(r.slot, len(r.prompt) + len(r.generated) + 2)
+                batch = TokenBatch(np.zeros(len(reqs), np.int32), pos + 1, seq, np.arange(len(reqs), dtype=np.int32), decode=True)
+                nxt = eng.step_launch(batch, chain_from=inf["handle"])
+                self.metrics.inc("lookahead_launches")
+            except OutOfPages:
+                nxt = None
+        self._inflight = None
+        res = eng.step_collect(inf["handle"])
+        for k, r in enumerate(reqs):
+            if self.live.get(r.slot) is r:
+                eng.commit(r.slot, [int(inf["fed"][k])])
+                self._produce(r, int(res.ids[k]), None)
+        if nxt is not None:
+            self._inflight = dict(handle=nxt, reqs=reqs, fed=np.asarray(res.ids[:len(reqs)], np.int32).copy(), pos=pos + 1, seq=seq)
+            self.metrics.inc("decode_ticks")
 
     def _multi_step_depth(self, reqs: list) -> int:
         """How many decode steps the next engine call may chain: only plain greedy requests (no logprobs, penalties,

@@ -288,6 +288,60 @@ def test_multi_step_decode_gives_the_same_tokens(tiny_assets):
     assert a_outs[0][1] == "stop" and len(a_outs[0][0]) <= 7
 
 
+def test_lookahead_decode_gives_the_same_tokens(tiny_assets):
+    """`lookahead`: decode step n + 1 is launched (its ids taken from step n's output by the engine) before the host reads
+    step n.  Tokens, stop handling and usage must equal the plain run: one request stops on a stop token (the row the
+    chained step computed for it is dropped), one runs out of budget, and a request that arrives in the middle drains
+    the pipeline, is prefilled, and joins."""
+    prompts = _prompts(4, 60, seed=9)
+
+    def run(look):
+        eng = CpuEngine(tiny_assets / "assets", max_slots=4, max_ctx=512)
+        mux = ModelMux(eng, ByteTokenizer(), SchedConfig(lookahead=look), eos_ids=[])
+        try:
+            first = []
+            r0 = mux.submit(prompts[0], GenParams(max_tokens=12))
+            for _ in range(100):
+                if not mux.tick() and not mux.live and not mux.waiting:
+                    break
+            while True:
+                c = r0.out.get(timeout=10)
+                if c.kind == "token":
+                    first.append(c.token_id)
+                else:
+                    break
+            stop_tok = first[6]
+            reqs = [mux.submit(prompts[0], GenParams(max_tokens=12, stop_token_ids=[stop_tok])),
+                    mux.submit(prompts[1], GenParams(max_tokens=10)), mux.submit(prompts[2], GenParams(max_tokens=7))]
+            late = None
+            for t in range(200):
+                if t == 6:
+                    late = mux.submit(prompts[3], GenParams(max_tokens=9))
+                if not mux.tick() and not mux.live and not mux.waiting and late is not None:
+                    break
+            outs = []
+            for r in reqs + [late]:
+                toks = []
+                while True:
+                    c = r.out.get(timeout=10)
+                    if c.kind == "token":
+                        toks.append(c.token_id)
+                    elif c.kind == "done":
+                        outs.append((toks, c.finish_reason, c.usage["completion_tokens"]))
+                        break
+                    else:
+                        raise AssertionError(c.error)
+            assert mux._inflight is None and not mux.live
+            return first, outs, mux.metrics.snapshot()["counters"].get("lookahead_launches", 0)
+        finally:
+            eng.close()
+    a_first, a_outs, a_n = run(False)
+    b_first, b_outs, b_n = run(True)
+    assert a_first == b_first and a_outs == b_outs
+    assert a_n == 0 and b_n >= 8
+    assert a_outs[0][1] == "stop" and len(a_outs[0][0]) <= 7 and [len(o[0]) for o in a_outs[1:]] == [10, 7, 9]
+
+
 @pytest.mark.parametrize("n_pages,budget,lens", [(5, 64, (144, 157, 187)), (5, 96, (144, 157, 187)), (7, 128, (144, 157, 187, 120))])
 def test_prefill_time_preemption_keeps_the_dispatcher_alive(tiny_assets, n_pages, budget, lens):
     """KV pressure DURING prefill: long prompts admitted against few pages with small chunks.  A request that loses its

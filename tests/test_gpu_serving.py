@@ -115,6 +115,27 @@ def test_chained_decode_steps_through_the_scheduler(assets):
     assert a == b
 
 
+def test_lookahead_decode_on_the_gpu_engine(assets):
+    """Lookahead-1: the scheduler launches decode step n + 1 (ids fed on the device from step n's output, inputs and
+    results through double-buffered pinned blocks) before it reads step n.  Same graph, same inputs: the tokens must be
+    the plain run's, for two requests of different budgets (the shorter one leaves an unused row in a chained step)."""
+    from plow_b200.runtime.scheduler import GenParams
+    prompts = _prompts(2, 60, 90, seed=6)
+
+    def run(look):
+        eng, mux = _mux(assets, cfg=dict(lookahead=look))
+        try:
+            reqs = [mux.submit(p, GenParams(max_tokens=16 - 5 * i)) for i, p in enumerate(prompts)]
+            outs = [_collect(r)[0] for r in reqs]
+            return outs, mux.metrics.snapshot()["counters"].get("lookahead_launches", 0), type(mux._inflight)
+        finally:
+            mux.stop()
+    a, na, _ = run(False)
+    b, nb, _ = run(True)
+    assert na == 0 and nb >= 8
+    assert a == b and [len(t) for t in b] == [16, 11]
+
+
 def test_device_status_fails_the_step_not_the_dispatcher(assets, monkeypatch):
     """A kernel that gives up on a bounded wait leaves a status word; the engine turns it into a non-fatal EngineError,
     the scheduler fails the requests of that step with an error chunk, re-arms the shared scratch, and keeps serving.
