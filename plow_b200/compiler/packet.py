@@ -137,6 +137,12 @@ class Inst:
     t: list = field(default_factory=lambda: [T_NONE] * 8)
     i: list = field(default_factory=lambda: [0] * 8)
 
+    def __post_init__(self):
+        # always eight operand and eight immediate slots, as in the packed form: an instruction built by the emitter
+        # and one read back from a packet file index the same way
+        self.t = list(self.t) + [T_NONE] * (8 - len(self.t))
+        self.i = list(self.i) + [0] * (8 - len(self.i))
+
     def pack(self) -> bytes:
         t = list(self.t) + [T_NONE] * (8 - len(self.t))
         i = [int(v) & 0xFFFFFFFF for v in list(self.i) + [0] * (8 - len(self.i))]

@@ -56,6 +56,7 @@ def main() -> None:
     ap.add_argument("--output", type=int, default=256)
     ap.add_argument("--chunk", type=int, default=2048, help="largest prefill bucket / rows per scheduler tick")
     ap.add_argument("--multi-step", type=int, default=1)
+    ap.add_argument("--lookahead", action="store_true", help="lookahead-1 decode pipeline")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     if os.environ.get("PLOW_DUMP_STACKS_AFTER_S"):
@@ -106,7 +107,7 @@ def main() -> None:
         for i in range(len(prompts)):
             if rng.random() < args.shared_prefix_frac and len(prompts[i]) > args.shared_prefix_len:
                 prompts[i][:args.shared_prefix_len] = common
-    mux = ModelMux(eng, ByteTokenizer(), SchedConfig(token_budget=args.chunk, objective="auto", queue_ttl_s=36000.0, multi_step=args.multi_step),
+    mux = ModelMux(eng, ByteTokenizer(), SchedConfig(token_budget=args.chunk, objective="auto", queue_ttl_s=36000.0, multi_step=args.multi_step, lookahead=args.lookahead),
                    eos_ids=[]).start()
     lock, state = threading.Lock(), dict(next=0, out=0, failed=0)
 
@@ -128,6 +129,7 @@ def main() -> None:
                 else:
                     with lock:
                         state["failed"] += 1
+                        state.setdefault("first_error", ch.error)
                     break
             with lock:
                 state["out"] += n
@@ -143,6 +145,7 @@ def main() -> None:
             else:
                 with lock:
                     state["failed"] += 1
+                    state.setdefault("first_error", ch.error)
                 break
         with lock:
             state["out"] += n
@@ -172,11 +175,11 @@ def main() -> None:
     native.check_status()
     n_prompt = sum(len(p) for p in prompts)
     print(json.dumps(dict(config=args.config, layers=len(spec.layers), tp=world, requests=args.requests, concurrency=C,
-                          prompt_tokens=n_prompt, output_tokens=state["out"], failed=state["failed"], wall_s=round(wall, 2),
+                          prompt_tokens=n_prompt, output_tokens=state["out"], failed=state["failed"], first_error=state.get("first_error"), wall_s=round(wall, 2),
                           output_tok_s=round(state["out"] / wall, 1), total_tok_s=round((state["out"] + n_prompt) / wall, 1),
                           ttft_ms=snap["ttft_ms"], tpot_ms=snap["tpot_ms"],
                           arrival_rate=args.arrival_rate or None,
-                          counters={k: snap["counters"].get(k) for k in ("prefill_ticks", "decode_ticks", "preemptions", "rider_rows", "multi_step_calls", "cached_tokens")},
+                          counters={k: snap["counters"].get(k) for k in ("prefill_ticks", "decode_ticks", "preemptions", "rider_rows", "multi_step_calls", "lookahead_launches", "cached_tokens")},
                           data="synthetic: random token ids, random-init weights")), flush=True)
     if world > 1:
         _teardown()

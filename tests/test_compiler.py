@@ -137,3 +137,17 @@ def test_device_interp_tables_build_on_cpu(tiny_assets):
     assert all(segs[k][1] == segs[k + 1][0] for k in range(len(segs) - 1))
     for lo, hi, dev in segs:
         assert all((Op(prog.insts[j].op) in ROW_OPS) == dev for j in range(lo, hi))
+
+
+def test_emitted_instructions_have_all_operand_slots():
+    """An engine may be handed the emitter's packet object directly (no file in between): every instruction then has
+    the eight operand and eight immediate slots of the packed form, unused ones empty."""
+    spec = config.spec_from_config(dict(config.tiny_dense_config(), head_dim=128, hidden_size=1024))
+    g = graph.build_graph(spec)
+    rewrite.fuse(g)
+    pkt = emit.emit_packet(g, [], hwspec.lookup("b200"), 148, dict(prefill=[128], decode=[8], max_seqs=8))
+    for p in pkt.programs:
+        for ins in p.insts:
+            assert len(ins.t) == 8 and len(ins.i) == 8
+    attn = next(i for i in pkt.programs[0].insts if i.op == pk.Op.ATTN)
+    assert attn.t[4] == pk.T_NONE                    # no scale tensor: a bf16 cache
