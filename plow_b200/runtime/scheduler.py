@@ -757,9 +757,10 @@ class ModelMux:
     def _lookahead_ok(self, reqs: list, ahead: int) -> bool:
         """May a decode step of these requests be left in flight (ahead = 1), or chained behind the one in flight
         (ahead = 2)?  Only plain greedy requests with at least ``ahead`` more tokens to produce, nobody waiting to be
-        admitted or prefilled, no drafter, no rank group (the other ranks follow synchronous steps)."""
+        admitted or prefilled, no drafter, no rank group (the other ranks follow synchronous steps), no recurrent state
+        (the row a chained step computes for a request that has just ended would advance a state its session keeps)."""
         eng = self.engine
-        if not self.cfg.lookahead or self.cfg.spec_depth > 0 or self.waiting or not self.ingress.empty() or not self.adopt_q.empty() \
+        if not self.cfg.lookahead or getattr(eng, "has_recurrent_state", False) or self.cfg.spec_depth > 0 or self.waiting or not self.ingress.empty() or not self.adopt_q.empty() \
                 or self.draining or getattr(eng, "step_group", None) is not None or getattr(eng, "leader_group", None) is not None:
             return False
         if any(q.done_prefill < q.pf_len for q in self.live.values()):
