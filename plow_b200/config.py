@@ -43,6 +43,7 @@ KNOBS = [
     Knob("spec_drafter", "PLOW_SPEC_DRAFTER", "runtime", "enum:auto|ngram|mtp", "auto",
          "drafter of the speculative steps: the checkpoint's prediction module (assets/mtp, plowc --mtp) or prompt lookup; auto = mtp when compiled"),
     Knob("multi_step", "PLOW_MULTI_STEP", "runtime", "int>=1", 1, "greedy decode steps per engine call (tokens fed back on the device; 1 = off)"),
+    Knob("rung_control", "PLOW_RUNG_CONTROL", "runtime", "bool", False, "admission follows the decode-rung controller (widen on backlog / SLO / utilisation, narrow on low load or a faster narrower rung)"),
     Knob("lookahead", "PLOW_LOOKAHEAD", "runtime", "bool", False, "lookahead-1 decode: launch step n+1 (fed on the device) before reading step n's tokens"),
     Knob("device_interp", "PLOW_DEVICE_INTERP", "runtime", "bool", True, "run row-op segments in the persistent on-device interpreter"),
     Knob("pd", "PLOW_PD", "runtime", "bool", False, "prefill/decode disaggregation inside one server (two engines, KV image hand-off)"),

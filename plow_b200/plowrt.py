@@ -43,7 +43,7 @@ def make_entry(name, assets, cfg):
     eng = load_engine(assets, cfg)
     tok = load_tokenizer(assets)
     sched = SchedConfig(token_budget=min(cfg.token_budget, eng.max_rows(False)), objective=cfg.objective,
-                        tbt_target_ms=cfg.tbt_target_ms, queue_ttl_s=cfg.queue_ttl_s, ride=cfg.ride, spec_depth=cfg.spec_depth, multi_step=cfg.multi_step, lookahead=cfg.lookahead)
+                        tbt_target_ms=cfg.tbt_target_ms, queue_ttl_s=cfg.queue_ttl_s, ride=cfg.ride, spec_depth=cfg.spec_depth, multi_step=cfg.multi_step, lookahead=cfg.lookahead, rung_control=cfg.rung_control)
     mux = ModelMux(eng, tok, sched)
     mtp_dir = Path(assets) / "mtp"
     if cfg.spec_depth > 0 and cfg.spec_drafter != "ngram":

@@ -108,6 +108,8 @@ class SchedConfig:
     spec_depth: int = 0               # > 0: speculative decoding for greedy requests (prompt-lookup drafts, span verify)
     multi_step: int = 1               # > 1: greedy decode ticks run this many steps per engine call (tokens fed back on the device)
     lookahead: bool = False           # decode step n + 1 is launched (fed on the device) before step n's tokens are read
+    rung_control: bool = False        # admission follows the decode-rung controller (runtime/rungs.py) instead of the slot count
+    ttft_slo_ms: float = 0.0          # latency objective the rung controller widens for (0: eight service times)
     session_ttl_s: float = 600.0      # a finished request that carried a session id keeps its slot and KV this long
     max_sessions: int = -1            # retained sessions at most (-1: half of the slots; 0: retention off)
 
@@ -126,6 +128,10 @@ class Metrics:
     def inc(self, k, v=1):
         with self.lock:
             self.c[k] = self.c.get(k, 0) + v
+
+    def gauge(self, k, v):
+        with self.lock:
+            self.c[k] = v
 
     def obs(self, name, v):
         with self.lock:
@@ -186,6 +192,13 @@ class ModelMux:
         self.pd_target: "ModelMux | None" = None     # prefill/decode disaggregation: where finished prefills continue
         self.adopt_q: "queue.Queue" = queue.Queue()  # (request, KV image) pairs handed over by a prefill mux
         self._inflight: dict | None = None           # lookahead: the decode step launched but not yet collected
+        self.rungs = None                             # decode-rung admission controller (cfg.rung_control)
+        self.rung_decision = None
+        self._mean_out = 1.0                          # running mean of output tokens per finished request
+        if self.cfg.rung_control:
+            from .rungs import RungController
+            widths = sorted({w for w in engine.buckets.get("decode", []) if w < engine.max_slots} | {engine.max_slots})
+            self.rungs = RungController(widths, engine.max_slots, fast_probe=self.cfg.objective == "throughput")
 
     # ---- public --------------------------------------------------------------------------------
     def start(self) -> "ModelMux":
@@ -317,6 +330,15 @@ class ModelMux:
         self._shed_expired()
         self._expire_sessions()
         self._adopt()
+        if self.rungs is not None:
+            from .rungs import RungLoad
+            now = time.monotonic()
+            self._arrivals = [t for t in self._arrivals if now - t <= 10.0]
+            self.rung_decision = self.rungs.decide(RungLoad(
+                occupied=len(self.live), queued=len(self.waiting),
+                oldest_wait_ms=(now - min(r.arrived for r in self.waiting)) * 1e3 if self.waiting else 0.0,
+                arrival_rps=len(self._arrivals) / 10.0, mean_output_tokens=self._mean_out, slo_ms=self.cfg.ttft_slo_ms))
+            self.metrics.gauge("rung_admission_limit", self.rungs.admission_limit())
         self._admit()
         if not self.live:
             return False
@@ -339,8 +361,14 @@ class ModelMux:
             self._prefill_tick(prefilling, riders)
             self._last_was_prefill = True
         elif decoding:
+            n_rows, ticks0 = len(decoding), self.metrics.c.get("decode_ticks", 0)
             self._decode_tick(decoding)
             self._last_was_prefill = False
+            if self.rungs is not None and self._inflight is None:
+                steps = self.metrics.c.get("decode_ticks", 0) - ticks0
+                if steps > 0:
+                    self.rungs.observe_decode(self.rungs.covering(min(n_rows, self.engine.max_rows(True))),
+                                              (time.perf_counter() - t0) * 1e3, steps)
         else:
             return False
         self.metrics.obs("step_ms", (time.perf_counter() - t0) * 1e3)
@@ -402,6 +430,8 @@ class ModelMux:
                 if self._evict_session():
                     continue
                 break
+            if self.rungs is not None and len(self.live) >= self.rungs.admission_limit():
+                break               # the controller holds the decode steps on this rung for now
             need_pages = (len(toks) + 1 + PAGE - 1) // PAGE
             headroom = len(self.live) * ((self.cfg.reserve_tokens + PAGE - 1) // PAGE)
             # pages are reserved lazily, chunk by chunk: what seated requests have yet to reserve for the rest of their
@@ -891,6 +921,7 @@ class ModelMux:
                 self.free_slots.append(r.slot)
         self.metrics.inc("requests_finished")
         self.metrics.obs("e2e", (time.monotonic() - r.arrived) * 1e3)
+        self._mean_out += 0.1 * (max(1, len(r.generated)) - self._mean_out)
 
     def _preempt_one(self, exclude=None, prefer=None) -> None:
         """Free pages by sending the youngest live request back to the queue (it re-prefills its
