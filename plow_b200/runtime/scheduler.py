@@ -90,6 +90,9 @@ class Request:
     preempted: int = 0
     cancelled: bool = False
     pf_len: int = 0                  # tokens to (re)prefill, fixed when the request is seated
+    seated_at: float | None = None   # breakdown log: when it got its slot, its prefill launches and their device time
+    pf_chunks: int = 0
+    pf_device_ms: float = 0.0
 
     def all_tokens(self) -> list:
         return self.prompt + self.generated
@@ -192,6 +195,9 @@ class ModelMux:
         self.pd_target: "ModelMux | None" = None     # prefill/decode disaggregation: where finished prefills continue
         self.adopt_q: "queue.Queue" = queue.Queue()  # (request, KV image) pairs handed over by a prefill mux
         self._inflight: dict | None = None           # lookahead: the decode step launched but not yet collected
+        from ..obs.breakdown import Breakdown
+        self.blog = Breakdown()                       # tick / decode-step / TTFT breakdown logs (environment switches)
+        self._tick_info = None                        # (kind, rows, reqs, device ms) of the tick in progress
         self.rungs = None                             # decode-rung admission controller (cfg.rung_control)
         self.rung_decision = None
         self._mean_out = 1.0                          # running mean of output tokens per finished request
@@ -372,6 +378,11 @@ class ModelMux:
         else:
             return False
         self.metrics.obs("step_ms", (time.perf_counter() - t0) * 1e3)
+        if self.blog.tick_on:
+            kind, rows, nreq, dev = self._tick_info or ("decode" if not run_prefill else "prefill", 0, 0, 0.0)
+            self._tick_info = None
+            self.blog.tick(kind, rows, nreq, dev, (time.perf_counter() - t0) * 1e3, len(self.waiting), len(self.live),
+                           self.rungs.admission_limit() if self.rungs is not None else 0)
         return True
 
     # ---- prefill / decode disaggregation ---------------------------------------------------------
@@ -461,6 +472,7 @@ class ModelMux:
     def _seat(self, r: Request, slot: int, cached: int, n_tokens: int) -> None:
         r.slot, r.done_prefill, r.cached_tokens = slot, cached, max(r.cached_tokens, cached)
         r.pf_len = n_tokens        # a preempted request re-prefills its prompt plus what it generated
+        r.seated_at = time.monotonic()
         r.detok = r.detok or IncrementalDetok(self.tok)
         r.rng = r.rng or np.random.default_rng(r.params.seed)
         self.live[slot] = r
@@ -630,6 +642,11 @@ class ModelMux:
         dt = (time.perf_counter() - t0) * 1e3
         self._rows_per_ms = 0.8 * getattr(self, "_rows_per_ms", len(ids) / max(dt, 1e-3)) + 0.2 * len(ids) / max(dt, 1e-3)
         self.metrics.inc("prefill_ticks")
+        if self.blog.any:
+            self._tick_info = ("prefill", len(ids), len(spans) + len(rode), res.device_ms)
+            for sp in spans:
+                sp[0].pf_chunks += 1
+                sp[0].pf_device_ms += res.device_ms
         k = 0
         mtp = self._mtp() if res.hidden is not None else None
         seen, at = [], 0          # what the drafter's prediction module must see: (slot, start, next tokens, hidden rows)
@@ -772,8 +789,12 @@ class ModelMux:
             self._inflight = dict(handle=eng.step_launch(batch), reqs=reqs, fed=ids, pos=pos, seq=seq)
             self.metrics.inc("decode_ticks")
             return
+        t_pre = time.perf_counter()
         res = eng.step(batch)
+        t_run = time.perf_counter()
         self.metrics.inc("decode_ticks")
+        if self.blog.any:
+            self._tick_info = ("decode", len(reqs), len(reqs), res.device_ms)
         seen = []
         for k, r in enumerate(reqs):
             slot = r.slot
@@ -783,6 +804,9 @@ class ModelMux:
                 seen.append((slot, int(pos[k]), [r.generated[-1]], res.hidden[k:k + 1]))
         if seen:
             mtp.observe(seen)
+        if self.blog.dstep_on:
+            rung = min((w for w in eng.buckets.get("decode", []) if w >= len(reqs)), default=len(reqs))
+            self.blog.dstep(len(reqs), rung, 1, res.device_ms, (t_run - t_pre) * 1e3 - res.device_ms, (time.perf_counter() - t_run) * 1e3)
 
     def _lookahead_ok(self, reqs: list, ahead: int) -> bool:
         """May a decode step of these requests be left in flight (ahead = 1), or chained behind the one in flight
@@ -881,6 +905,10 @@ class ModelMux:
         if r.first_token_at is None:
             r.first_token_at = now
             self.metrics.obs("ttft", (now - r.arrived) * 1e3)
+            if self.blog.ttft_on:
+                seated = r.seated_at if r.seated_at is not None else r.arrived
+                self.blog.ttft(r.rid, len(r.prompt), r.cached_tokens, (seated - r.arrived) * 1e3, r.pf_chunks, r.pf_device_ms,
+                               (now - seated) * 1e3, (now - r.arrived) * 1e3)
         else:
             self.metrics.obs("tpot", (now - r.last_token_at) * 1e3)
         r.last_token_at = now
