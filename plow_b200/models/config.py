@@ -194,6 +194,11 @@ def spec_from_config(cfg: dict) -> ModelSpec:
 
 
 def load_spec(path) -> ModelSpec:
+    """A checkpoint directory (its config.json), a config.json path, or a GGUF file (its metadata)."""
+    from ..runtime.gguf import GgufFile, config_from_gguf, find_gguf
+    g = find_gguf(path)
+    if g is not None:
+        return spec_from_config(config_from_gguf(GgufFile(g)))
     p = Path(path)
     if p.is_dir():
         p = p / "config.json"

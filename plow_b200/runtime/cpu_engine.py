@@ -20,7 +20,7 @@ from ..ops import native
 from ..utils.rope import rope_table
 from .engine import EngineBase, EngineError, StepResult, TokenBatch
 from .kv_pages import PAGE
-from .weights import Checkpoint, materialize
+from .weights import materialize, open_checkpoint
 
 
 class StepIO(C.Structure):
@@ -66,7 +66,7 @@ class CpuEngine(EngineBase):
     def _bind_all(self, assets: Path) -> None:
         pkt = self.packet
         ckpt_dir = assets / "checkpoint"
-        ckpt = Checkpoint(ckpt_dir)
+        ckpt = open_checkpoint(ckpt_dir)
         derived = pkt.section_json("derived_weights.json") or {}
         gen = pkt.section_json("gen_tensors.json") or {}
         max_rows = max(p.rows for p in pkt.programs)

@@ -51,8 +51,8 @@ class WeightSource:
 
 class CheckpointWeights(WeightSource):
     def __init__(self, ckpt_dir, device, tp=1, rank=0):
-        from .weights import Checkpoint
-        self.ckpt = Checkpoint(ckpt_dir)
+        from .weights import open_checkpoint
+        self.ckpt = open_checkpoint(ckpt_dir)
         self.device, self.tp, self.rank = device, tp, rank
 
     def bf16(self, ent, recipe):

@@ -1,7 +1,7 @@
 """Checkpoint access: safetensors read in place, names are the contract, shards cut at bind.
 
 * :class:`Checkpoint` discovers ``*.safetensors`` (+ index) in a directory and serves tensors by
-  name without loading whole files.
+  name without loading whole files; :func:`open_checkpoint` also accepts a GGUF file (runtime/gguf.py).
 * :func:`shard_slice` applies the Megatron layout: column-parallel weights are split on axis 0
   (output features), row-parallel on axis 1 (input features), everything else is replicated.
 * :func:`materialize` resolves one packet tensor entry: a checkpoint tensor, a derived tensor
@@ -54,12 +54,21 @@ class Checkpoint:
         s = self._h(self.files[name]).get_slice(name)
         return s[start:stop] if axis == 0 else s[:, start:stop]
 
+    def shape(self, name: str) -> tuple:
+        return tuple(self._h(self.files[name]).get_slice(name).get_shape())
+
+
+def open_checkpoint(path):
+    """A safetensors directory, or a GGUF file (or a directory holding just one) behind the same interface."""
+    from .gguf import GgufCheckpoint, find_gguf
+    g = find_gguf(path)
+    return GgufCheckpoint(g) if g is not None else Checkpoint(path)
+
 
 def shard_slice(ckpt: Checkpoint, name: str, shard_axis, tp: int, rank: int) -> torch.Tensor:
     if shard_axis is None or shard_axis == 0xFFFFFFFF or tp == 1:
         return ckpt.get(name)
-    full = ckpt._h(ckpt.files[name]).get_slice(name)
-    n = full.get_shape()[shard_axis]
+    n = ckpt.shape(name)[shard_axis]
     if n % tp:
         raise ValueError(f"{name}: axis {shard_axis} of size {n} does not divide over tp={tp}")
     per = n // tp
