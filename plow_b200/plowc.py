@@ -23,7 +23,7 @@ from .models.config import load_spec
 
 def compile_dir(hf_dir, out_dir, gpu="b200", arch="sm_100a", num_gpus=1, parallel="tp", n_cu=None,
                 max_rows=8192, prefill_buckets=None, decode_rungs=None, max_seqs=64, disable_rules=(),
-                emit_trace=False, mtp=False, _spec=None) -> dict:
+                emit_trace=False, mtp=False, fp8_dir=False, _spec=None) -> dict:
     """``mtp=True`` (the checkpoint must carry prediction modules, ``num_nextn_predict_layers``) also writes a drafter
     packet directory ``<out>/mtp`` (the first module as a one-layer model that reads a token and a hidden state per row)
     and makes the main packet return its normed hidden states (``out.hidden``) for it."""
@@ -79,10 +79,17 @@ def compile_dir(hf_dir, out_dir, gpu="b200", arch="sm_100a", num_gpus=1, paralle
     for fn in ("tokenizer.json", "tokenizer_config.json", "chat_template.jinja", "generation_config.json"):
         if (src / fn).exists():
             shutil.copy(src / fn, out / fn)
+    if fp8_dir and spec.weight_quant == "fp8_block128":
+        # pre-quantised e4m3 twins of every projection the programs read as e4m3 (runtime/fp8_dir.py): loaded instead of
+        # quantising the checkpoint at every start
+        from .runtime.fp8_dir import write_fp8_dir
+        report["fp8_dir"] = [dict(rank=r, tensors=len(write_fp8_dir(out, "model.pkt" if r == 0 else f"model.rank{r}.pkt", r, tp)["weight_map"]) // 2)
+                             for r in range(n_ranks)]
+        (out / "build.json").write_text(json.dumps(report, indent=1))
     if mtp and spec.role == "main":
         report["mtp"] = compile_dir(hf_dir, out / "mtp", gpu=gpu, arch=arch, num_gpus=num_gpus, parallel=parallel, n_cu=n_cu,
                                     max_rows=max_rows, prefill_buckets=prefill_buckets, decode_rungs=decode_rungs,
-                                    max_seqs=max_seqs, disable_rules=disable_rules, _spec=spec.drafter_spec())
+                                    max_seqs=max_seqs, disable_rules=disable_rules, fp8_dir=fp8_dir, _spec=spec.drafter_spec())
         (out / "build.json").write_text(json.dumps(report, indent=1))
     return report
 
@@ -103,6 +110,7 @@ def main(argv=None) -> int:
     ap.add_argument("--prefill-buckets", type=lambda s: [int(x) for x in s.split(",")])
     ap.add_argument("--decode-rungs", type=lambda s: [int(x) for x in s.split(",")])
     ap.add_argument("--disable-rule", action="append", default=[])
+    ap.add_argument("--fp8-dir", action="store_true", dest="fp8_dir", help="write pre-quantised e4m3 weight twins next to the packet (<out>/fp8)")
     ap.add_argument("--mtp", action="store_true", help="also compile the checkpoint's prediction module as a drafter (<out>/mtp)")
     v = sub.add_parser("viz", help="write an HTML view of the fused graph")
     v.add_argument("hf_dir")
@@ -157,7 +165,7 @@ def main(argv=None) -> int:
         ap.error("--hf-dir is required")
     try:
         rep = compile_dir(args.hf_dir, args.out, args.gpu, args.arch, args.num_gpus, args.parallel, args.n_cu,
-                          args.max_rows, args.prefill_buckets, args.decode_rungs, args.max_seqs, args.disable_rule, mtp=args.mtp)
+                          args.max_rows, args.prefill_buckets, args.decode_rungs, args.max_seqs, args.disable_rule, mtp=args.mtp, fp8_dir=args.fp8_dir)
     except (ValueError, KeyError, RuntimeError) as e:
         print(f"plowc: error: {e}", file=sys.stderr)
         return 2

@@ -54,6 +54,11 @@ class CheckpointWeights(WeightSource):
         from .weights import open_checkpoint
         self.ckpt = open_checkpoint(ckpt_dir)
         self.device, self.tp, self.rank = device, tp, rank
+        self.twins = None              # pre-quantised e4m3 twins next to the packet (runtime/fp8_dir.py), set by the engine
+
+    def fp8(self, ent, recipe):
+        got = self.twins.get(ent.name, self.device) if self.twins else None
+        return got if got is not None else super().fp8(ent, recipe)
 
     def bf16(self, ent, recipe):
         from .weights import materialize
@@ -146,6 +151,7 @@ class GpuEngine(EngineBase):
             name = "model.pkt" if rank == 0 else f"model.rank{rank}.pkt"
             packet = pk.read_packet(Path(assets_dir) / name)
         self.rank, self.comm, self.tp_comm = rank, comm, tp_comm
+        self.assets_dir = assets_dir
         # rank groups (plow_b200/parallel/group.py): step_group = every rank schedules its own requests and the ranks
         # agree on the program before each launch (expert parallelism with data-parallel attention); leader_group =
         # rank 0 schedules, the others replay its steps (tensor parallelism)
@@ -183,13 +189,10 @@ class GpuEngine(EngineBase):
         pkt = self.packet
         self.static: dict[int, torch.Tensor] = {}
         self.static_q: dict[int, tuple] = {}
-        fp8_handles = set()
-        for p in pkt.programs:
-            for ins in p.insts:
-                if ins.op in (Op.GEMM, Op.GEMM_XREDUCE) and ins.i[2] & pk.GEMM_FP8_BLOCK:
-                    fp8_handles.add(ins.t[2])
-                if ins.op == Op.MOE_GEMM and self.spec.weight_quant == "fp8_block128":
-                    fp8_handles.update([ins.t[3], ins.t[4]])
+        from .fp8_dir import Fp8Dir, fp8_weight_handles
+        fp8_handles = fp8_weight_handles(pkt, self.spec.weight_quant)
+        if isinstance(self.weights, CheckpointWeights) and self.weights.twins is None and getattr(self, "assets_dir", None):
+            self.weights.twins = Fp8Dir(self.assets_dir, pkt, self.weights.rank)
         max_rows = max(p.rows for p in pkt.programs)
         self.max_rows_all = max_rows
         n_slots = self.max_slots + 1

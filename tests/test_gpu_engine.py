@@ -305,3 +305,27 @@ def test_multi_step_decode_on_device_matches_step_by_step(mla_assets):
 def test_smoke_runs():
     from plow_b200.runtime import smoke
     smoke.run()
+
+
+def test_engine_loaded_from_prequantised_twins_gives_the_same_logits(tmp_path):
+    """`plowc --fp8-dir`: the engine takes its e4m3 weights from the twin directory instead of quantising the checkpoint;
+    same bytes, same logits."""
+    from plow_b200 import plowc
+    from plow_b200.models import reference
+    from plow_b200.runtime.engine import TokenBatch
+    from plow_b200.runtime.gpu_engine import GpuEngine
+    from plow_b200.runtime.smoke import small_mla_moe_config
+    reference.write_checkpoint(small_mla_moe_config(), tmp_path / "ckpt", seed=0, dtype=torch.bfloat16)
+    kw = dict(max_rows=128, prefill_buckets=[128], decode_rungs=[8], max_seqs=8)
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "plain", **kw)
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "twins", fp8_dir=True, **kw)
+    p = np.random.default_rng(0).integers(0, 1024, 90).astype(np.int32)
+    outs = []
+    for d in ("plain", "twins"):
+        eng = GpuEngine(tmp_path / d, max_slots=4, max_ctx=256)
+        assert bool(eng.weights.twins) == (d == "twins")
+        eng.begin_slot(0, p.tolist())
+        eng.reserve(0, 100)
+        r = eng.step(TokenBatch(p, np.arange(90, dtype=np.int32), np.zeros(90, np.int32), np.asarray([89], np.int32), want_logits=True))
+        outs.append(r.logits[0])
+    assert np.array_equal(outs[0], outs[1])
