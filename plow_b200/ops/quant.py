@@ -22,7 +22,9 @@ def quant_weight_128x128(w: torch.Tensor):
     wp[:n, :k] = w.float()
     blocks = wp.view(nb, 128, kb, 128)
     amax = blocks.abs().amax(dim=(1, 3))
-    scale = amax.clamp_min(1e-10) / FP8_MAX
+    # amax * (1 / 448), not amax / 448: a tensor divided by a host scalar is multiplied by the rounded reciprocal on the GPU
+    # and truly divided on the CPU, which moves the scale by one ulp and one code in a thousand with it
+    scale = amax.clamp_min(1e-10) * (1.0 / FP8_MAX)
     q = (blocks / scale[:, None, :, None]).view(nb * 128, kb * 128)[:n, :k].to(FP8)
     return q.contiguous(), scale.contiguous()
 

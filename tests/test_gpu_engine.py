@@ -308,8 +308,9 @@ def test_smoke_runs():
 
 
 def test_engine_loaded_from_prequantised_twins_gives_the_same_logits(tmp_path):
-    """`plowc --fp8-dir`: the engine takes its e4m3 weights from the twin directory instead of quantising the checkpoint;
-    same bytes, same logits."""
+    """`plowc --fp8-dir`: the engine takes its e4m3 weights from the twin directory (quantised on the host) instead of
+    quantising the checkpoint on the device: the same codes (a rounding tie may fall differently on the two devices in
+    a few cells) and the same logits to well within the e4m3 noise."""
     from plow_b200 import plowc
     from plow_b200.models import reference
     from plow_b200.runtime.engine import TokenBatch
@@ -320,12 +321,18 @@ def test_engine_loaded_from_prequantised_twins_gives_the_same_logits(tmp_path):
     plowc.compile_dir(tmp_path / "ckpt", tmp_path / "plain", **kw)
     plowc.compile_dir(tmp_path / "ckpt", tmp_path / "twins", fp8_dir=True, **kw)
     p = np.random.default_rng(0).integers(0, 1024, 90).astype(np.int32)
-    outs = []
+    outs, codes = [], []
     for d in ("plain", "twins"):
         eng = GpuEngine(tmp_path / d, max_slots=4, max_ctx=256)
         assert bool(eng.weights.twins) == (d == "twins")
+        codes.append({eng.packet.tensors[h].name: (q.view(torch.uint8).cpu(), s.cpu()) for h, (q, s) in eng.static_q.items()})
         eng.begin_slot(0, p.tolist())
         eng.reserve(0, 100)
         r = eng.step(TokenBatch(p, np.arange(90, dtype=np.int32), np.zeros(90, np.int32), np.asarray([89], np.int32), want_logits=True))
         outs.append(r.logits[0])
-    assert np.array_equal(outs[0], outs[1])
+    assert set(codes[0]) == set(codes[1]) and len(codes[0]) >= 8
+    for name, (q0, s0) in codes[0].items():
+        q1, s1 = codes[1][name]
+        assert torch.allclose(s0, s1, rtol=1e-6, atol=0) and (q0 == q1).float().mean().item() > 0.995, name
+    rel = float(np.linalg.norm(outs[0] - outs[1]) / np.linalg.norm(outs[0]))
+    assert rel < 0.02 and int(outs[0].argmax()) == int(outs[1].argmax())
