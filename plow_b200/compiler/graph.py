@@ -188,7 +188,7 @@ def _decoder_layer(g: Graph, li: int, p: str, x: str, layer) -> str:
         if tp > 1:
             d = _xreduce(g, d, li)
     else:
-        d = _moe_ffn(g, li, f"{p}.mlp", h2, layer.ffn)
+        d = _moe_ffn(g, li, f"{p}.{layer.ffn.block}", h2, layer.ffn)
     x3 = g.tmp("x", (R, H))
     g.add("add", [x2, d], [x3], layer=li)
     return x3
@@ -339,11 +339,12 @@ def _moe_ffn(g: Graph, li, p, h, f) -> str:
     table = g.tmp("route", (R, k, 2), "i32")
     g.add("router_topk", inputs, [table], layer=li, n_experts=E, top_k=k, n_group=f.n_group,
           topk_group=f.topk_group, score=f.score, norm_topk=f.norm_topk, route_scale=f.route_scale)
+    gate_n, up_n, down_n = ("w1", "w3", "w2") if f.expert_names == "w123" else ("gate_proj", "up_proj", "down_proj")
     w1 = g.value(f"cat/{p}.experts.gate_up.weight", (e_local * 2 * F, H), g.weight_dtype(), "derived",
-                 meta=dict(op="stack_experts", parts=["gate_proj", "up_proj"], prefix=f"{p}.experts", n=E,
+                 meta=dict(op="stack_experts", parts=[gate_n, up_n], prefix=f"{p}.experts", n=E,
                            ep=ep, rank=g.rank))
     w2 = g.value(f"cat/{p}.experts.down.weight", (e_local * H, F), g.weight_dtype(), "derived",
-                 meta=dict(op="stack_experts", parts=["down_proj"], prefix=f"{p}.experts", n=E, ep=ep, rank=g.rank))
+                 meta=dict(op="stack_experts", parts=[down_n], prefix=f"{p}.experts", n=E, ep=ep, rank=g.rank))
     y = g.tmp("moe", (R, H))
     shared = None
     if f.n_shared:

@@ -4,7 +4,9 @@ Families understood (by ``model_type`` / ``architectures``):
 
 * dense GQA decoders: llama, mistral, qwen2, qwen3 (per-head q/k RMSNorm), gemma-style ``1+γ`` norms;
 * MLA + MoE decoders: deepseek_v3 / deepseek_v2, kimi_k2, glm_moe_dsa (adds the DSA indexer);
-* hybrid linear-attention MoE decoders: qwen3_next (gated delta rule + gated full attention).
+* hybrid linear-attention MoE decoders: qwen3_next (gated delta rule + gated full attention);
+* GQA + MoE decoders: qwen3_moe (per-head q/k norm, softmax router) and mixtral (experts named w1 / w3 / w2 under
+  ``block_sparse_moe``).
 
 The reference derives the same plan in crates/plowc/src/hf_config.rs (LayerPlan from config.json)
 and dispatches emitters on ``model_type`` in crates/devgen/src/lib.rs:9518-9646.
@@ -66,6 +68,8 @@ class FfnSpec:
     norm_topk: bool = True
     route_scale: float = 1.0
     has_bias: bool = False        # e_score_correction_bias
+    block: str = "mlp"            # module that holds the router and the experts (mixtral: block_sparse_moe)
+    expert_names: str = "proj"    # "proj": gate_proj / up_proj / down_proj; "w123": w1 (gate) / w3 (up) / w2 (down)
 
 
 @dataclass
@@ -190,6 +194,8 @@ def spec_from_config(cfg: dict) -> ModelSpec:
         return _mla_moe(cfg, mt)
     if mt in ("qwen3_next", "qwen3_5", "plow_gdn_hybrid"):
         return _gdn_hybrid(cfg, mt)
+    if mt in ("qwen3_moe", "mixtral"):
+        return _gqa_moe(cfg, mt)
     raise ValueError(f"unsupported model_type '{mt}'")
 
 
@@ -253,6 +259,31 @@ def _mla_moe(cfg: dict, mt: str) -> ModelSpec:
         mtp_layers=int(cfg.get("num_nextn_predict_layers") or 0))
 
 
+def _gqa_moe(cfg: dict, mt: str) -> ModelSpec:
+    """Grouped-query attention + a routed MoE in (almost) every layer: qwen3_moe and mixtral."""
+    h = cfg["hidden_size"]
+    nh = cfg["num_attention_heads"]
+    nkv = cfg.get("num_key_value_heads", nh)
+    hd = cfg.get("head_dim") or h // nh
+    n_layers = cfg["num_hidden_layers"]
+    mix = mt == "mixtral"
+    attn = AttnSpec(kind="gqa", n_heads=nh, n_kv_heads=nkv, head_dim=hd, qk_norm=not mix,
+                    window=int(cfg.get("sliding_window") or 0) if (mix and cfg.get("sliding_window")) else 0)
+    moe = FfnSpec(kind="moe", act=cfg.get("hidden_act", "silu"), n_experts=cfg["num_local_experts" if mix else "num_experts"],
+                  top_k=cfg["num_experts_per_tok"], moe_inter=cfg["intermediate_size" if mix else "moe_intermediate_size"],
+                  score="softmax", norm_topk=True if mix else bool(cfg.get("norm_topk_prob", True)),
+                  block="block_sparse_moe" if mix else "mlp", expert_names="w123" if mix else "proj")
+    dense = FfnSpec(kind="dense", inter=cfg.get("intermediate_size", 0), act=cfg.get("hidden_act", "silu"))
+    step, only = int(cfg.get("decoder_sparse_step", 1) or 1), set(cfg.get("mlp_only_layers") or [])
+    layers = [LayerSpec(attn, moe if (mix or (i not in only and (i + 1) % step == 0)) else dense) for i in range(n_layers)]
+    return ModelSpec(
+        family="gqa_moe", model_type=mt, hidden=h, vocab=cfg["vocab_size"], n_layers=n_layers,
+        rms_eps=float(cfg.get("rms_norm_eps", 1e-6)), tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+        rope=_rope_from(cfg, hd), layers=layers,
+        dtype=cfg.get("plow_dtype", "bf16"), weight_quant=_quant(cfg), kv_dtype=cfg.get("plow_kv_dtype", cfg.get("plow_dtype", "bf16")),
+        max_ctx=int(cfg.get("max_position_embeddings", 4096)), bos_token_id=cfg.get("bos_token_id"), eos_token_ids=_eos(cfg))
+
+
 def _gdn_hybrid(cfg: dict, mt: str) -> ModelSpec:
     h = cfg["hidden_size"]
     n_layers = cfg["num_hidden_layers"]
@@ -301,6 +332,20 @@ def mla_moe_671b_config(n_experts: int = 256, n_layers: int = 61, dsa: bool = Fa
     if dsa:
         cfg.update(model_type="glm_moe_dsa", index_n_heads=64, index_head_dim=128, index_topk=2048)
     return cfg
+
+
+def qwen3_moe_30b_config() -> dict:
+    """GQA + MoE decoder of the 30B-A3B shape: 48 layers, 128 experts, 8 active."""
+    return dict(model_type="qwen3_moe", hidden_size=2048, num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4,
+                head_dim=128, num_experts=128, num_experts_per_tok=8, moe_intermediate_size=768, intermediate_size=6144,
+                norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[], rms_norm_eps=1e-6, rope_theta=1000000.0,
+                vocab_size=151936, tie_word_embeddings=False, max_position_embeddings=40960, eos_token_id=151645)
+
+
+def mixtral_8x7b_config() -> dict:
+    return dict(model_type="mixtral", hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+                num_local_experts=8, num_experts_per_tok=2, intermediate_size=14336, rms_norm_eps=1e-5, rope_theta=1000000.0,
+                vocab_size=32000, tie_word_embeddings=False, max_position_embeddings=32768, eos_token_id=2)
 
 
 def gdn_hybrid_80b_config() -> dict:

@@ -124,11 +124,12 @@ class ReferenceModel:
             o = self._gdn(p, h, layer.attn)
         x = x + o
         h = rmsnorm(x, self.w[f"{p}.post_attention_layernorm.weight"], spec.rms_eps, spec.norm_plus_one)
-        return x + (self._dense(f"{p}.mlp", h) if layer.ffn.kind == "dense" else self._moe(f"{p}.mlp", h, layer.ffn))
+        return x + (self._dense(f"{p}.mlp", h) if layer.ffn.kind == "dense" else self._moe(f"{p}.{layer.ffn.block}", h, layer.ffn))
 
     # ---- blocks --------------------------------------------------------------------------------
-    def _dense(self, p, h):
-        return self.lin(F.silu(self.lin(h, f"{p}.gate_proj.weight")) * self.lin(h, f"{p}.up_proj.weight"), f"{p}.down_proj.weight")
+    def _dense(self, p, h, names="proj"):
+        g, u, d = ("w1", "w3", "w2") if names == "w123" else ("gate_proj", "up_proj", "down_proj")
+        return self.lin(F.silu(self.lin(h, f"{p}.{g}.weight")) * self.lin(h, f"{p}.{u}.weight"), f"{p}.{d}.weight")
 
     def _gqa(self, p, h, pos, a):
         spec = self.spec
@@ -239,7 +240,7 @@ class ReferenceModel:
         for j in range(f.top_k):
             for e in idx[:, j].unique().tolist():
                 m = idx[:, j] == e
-                out[m] += g[m, j, None] * self._dense(f"{p}.experts.{e}", h[m]).float()
+                out[m] += g[m, j, None] * self._dense(f"{p}.experts.{e}", h[m], f.expert_names).float()
         if f.n_shared:
             sp = f"{p}.shared_experts" if self.spec.family == "mla_moe" else f"{p}.shared_expert"
             out = out + self._dense(sp, h).float()
@@ -338,12 +339,13 @@ def param_shapes(spec: ModelSpec) -> dict:
             for nm, shp in (("gate_proj", (f.inter, H)), ("up_proj", (f.inter, H)), ("down_proj", (H, f.inter))):
                 s[f"{p}.mlp.{nm}.weight"] = shp
         else:
-            s[f"{p}.mlp.gate.weight"] = (f.n_experts, H)
+            s[f"{p}.{f.block}.gate.weight"] = (f.n_experts, H)
             if f.has_bias:
-                s[f"{p}.mlp.gate.e_score_correction_bias"] = (f.n_experts,)
+                s[f"{p}.{f.block}.gate.e_score_correction_bias"] = (f.n_experts,)
+            gn, un, dn = ("w1", "w3", "w2") if f.expert_names == "w123" else ("gate_proj", "up_proj", "down_proj")
             for e in range(f.n_experts):
-                for nm, shp in (("gate_proj", (f.moe_inter, H)), ("up_proj", (f.moe_inter, H)), ("down_proj", (H, f.moe_inter))):
-                    s[f"{p}.mlp.experts.{e}.{nm}.weight"] = shp
+                for nm, shp in ((gn, (f.moe_inter, H)), (un, (f.moe_inter, H)), (dn, (H, f.moe_inter))):
+                    s[f"{p}.{f.block}.experts.{e}.{nm}.weight"] = shp
             if f.n_shared:
                 sp = f"{p}.mlp.shared_experts" if spec.family == "mla_moe" else f"{p}.mlp.shared_expert"
                 w = f.moe_inter * f.n_shared

@@ -59,7 +59,9 @@ def test_tp_graph_has_fused_collectives():
 
 @pytest.mark.parametrize("cfg_fn,kw", [(lambda: config.mla_moe_671b_config(n_layers=5), dict(ep=8)),
                                        (lambda: config.mla_moe_671b_config(n_layers=4, dsa=True), dict(ep=8)),
-                                       (config.gdn_hybrid_80b_config, dict(tp=2, ep=4))])
+                                       (config.gdn_hybrid_80b_config, dict(tp=2, ep=4)),
+                                       (config.qwen3_moe_30b_config, dict(ep=8)),
+                                       (config.mixtral_8x7b_config, dict(ep=2))])
 def test_big_families_build_and_verify(cfg_fn, kw):
     cfg = cfg_fn()
     if "num_hidden_layers" in cfg and cfg["num_hidden_layers"] > 8:

@@ -1,5 +1,7 @@
 """Config 1 (CPU plumbing): tiny dense GQA decoder, fp32, plowc -> packet -> plowrt engine ->
 scheduler; logits must match the PyTorch reference to 1e-4 and greedy tokens must agree."""
+import json
+
 import numpy as np
 import pytest
 import torch
@@ -485,4 +487,55 @@ def test_gdn_hybrid_model_on_cpu_backend_matches_reference(tmp_path):
     r = eng.step(TokenBatch(np.asarray(pa[:20], np.int32), np.arange(20, dtype=np.int32), np.zeros(20, np.int32),
                             np.asarray([19], np.int32), want_logits=True))
     assert close(r.logits[0], ref.forward(torch.tensor(pa[:20]))[-1])
+    eng.close()
+
+
+@pytest.mark.parametrize("model_type", ["qwen3_moe", "mixtral"])
+def test_gqa_moe_families_on_cpu_backend_match_reference(tmp_path, model_type):
+    """Grouped-query attention + routed MoE decoders: qwen3_moe (per-head q / k norm, experts under ``mlp`` named
+    gate_proj / up_proj / down_proj, one dense layer through mlp_only_layers) and mixtral (experts under
+    ``block_sparse_moe`` named w1 / w3 / w2, sliding window): prefill and decode logits against the fp32 reference."""
+    import glob
+    from safetensors.torch import load_file
+    from plow_b200 import plowc
+    from plow_b200.models import config, reference
+    from plow_b200.runtime.engine import TokenBatch
+    base = dict(hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64, num_hidden_layers=3,
+                num_experts_per_tok=2, rms_norm_eps=1e-6, rope_theta=10000.0, vocab_size=512, tie_word_embeddings=False,
+                max_position_embeddings=1024, eos_token_id=1, plow_dtype="f32", plow_kv_dtype="f32")
+    if model_type == "qwen3_moe":
+        cfg = dict(base, model_type="qwen3_moe", num_experts=8, moe_intermediate_size=64, intermediate_size=384,
+                   norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[1])
+    else:
+        cfg = dict(base, model_type="mixtral", num_local_experts=8, intermediate_size=96, sliding_window=48)
+    spec = config.spec_from_config(cfg)
+    assert spec.family == "gqa_moe" and [l.ffn.kind for l in spec.layers] == (["moe", "dense", "moe"] if model_type == "qwen3_moe" else ["moe"] * 3)
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=0)
+    names = set(json.loads((tmp_path / "ckpt" / "model.safetensors.index.json").read_text())["weight_map"])
+    assert ("model.layers.0.block_sparse_moe.experts.3.w3.weight" in names) == (model_type == "mixtral")
+    assert ("model.layers.0.mlp.experts.3.up_proj.weight" in names) == (model_type == "qwen3_moe")
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", arch="cpu", n_cu=4, max_rows=128, decode_rungs=[1, 2], max_seqs=4)
+    eng = CpuEngine(tmp_path / "assets", max_slots=2, max_ctx=256)
+    state = {}
+    for f in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        state.update(load_file(f))
+    ref = reference.ReferenceModel(spec, {k: v.float() for k, v in state.items()})
+    rng = np.random.default_rng(4)
+    p = rng.integers(0, 512, 80).tolist()                        # longer than the 48-token window
+    eng.begin_slot(0, p)
+    eng.reserve(0, len(p) + 4)
+    r = eng.step(TokenBatch(np.asarray(p, np.int32), np.arange(len(p), dtype=np.int32), np.zeros(len(p), np.int32),
+                            np.asarray([len(p) - 1], np.int32), want_logits=True))
+    want = ref.forward(torch.tensor(p))[-1]
+    assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item())
+    eng.commit(0, p)
+    cur = list(p)
+    for _ in range(2):
+        nxt = int(ref.forward(torch.tensor(cur))[-1].argmax())
+        r = eng.step(TokenBatch(np.asarray([nxt], np.int32), np.asarray([len(cur)], np.int32), np.zeros(1, np.int32), np.zeros(1, np.int32),
+                                decode=True, want_logits=True))
+        cur.append(nxt)
+        eng.commit(0, [nxt])
+        want = ref.forward(torch.tensor(cur))[-1]
+        assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item())
     eng.close()
