@@ -12,6 +12,7 @@
 // crates/plowrt/src/exec/cpu/{interp,engine}.rs, runtime/cpu/dev/golden/*.c,
 // crates/plowrt/src/exec/health.rs (counter monitor).
 #include <algorithm>
+#include <immintrin.h>
 #include <atomic>
 #include <chrono>
 #include <cmath>
@@ -226,6 +227,79 @@ void op_residual(const Ctx& c) {
   for (int64_t k = a * W; k < b * W; ++k) o[k] = x[k] + d[k];
 }
 
+// ---- GEMM kernel tiers ---------------------------------------------------------------------------------------------
+// y[m][n] = x[m] . w[n] (+ SiLU-gated pair).  Three bodies behind one op, picked once per process (PLOW_CPU_TIER =
+// golden | avx2 | avx512 | auto, or plow_cpu_set_tier):
+//   golden  one output at a time: the numeric statement the others are held to;
+//   avx2    eight rows share every weight row they read (the weight matrix is streamed rows / 8 times instead of rows
+//           times) with 8-lane FMA accumulators, summed tail elements first, then lanes 0..7;
+//   avx512  the same with 16 lanes.
+// The tiers order their sums differently from the compiler's own vectorisation of the golden loop, so they agree with it
+// to rounding (1e-6 relative on a model's logits), not bit for bit.  `auto` takes avx2 when the CPU has it; avx512 is a
+// choice (on a 250-row prefill of the 4-layer test model: golden 77 ms, avx2 56 ms, avx512 41 ms).
+// Reference counterpart: runtime/cpu (scalar / AVX2 / AVX-512 / AMX kernel tiers behind one dispatch table).
+enum { TIER_GOLDEN = 0, TIER_AVX2 = 1, TIER_AVX512 = 2 };
+
+static int tier_supported(int t) {
+  if (t == TIER_AVX2) return __builtin_cpu_supports("avx2") && __builtin_cpu_supports("fma");
+  if (t == TIER_AVX512) return __builtin_cpu_supports("avx512f");
+  return t == TIER_GOLDEN;
+}
+
+static int pick_tier() {
+  const char* e = std::getenv("PLOW_CPU_TIER");
+  const std::string v = e ? e : "auto";
+  if (v == "golden") return TIER_GOLDEN;
+  if (v == "avx512" && tier_supported(TIER_AVX512)) return TIER_AVX512;
+  if ((v == "avx2" || v == "auto" || v == "avx512") && tier_supported(TIER_AVX2)) return TIER_AVX2;
+  return TIER_GOLDEN;
+}
+static std::atomic<int> g_tier{-1};
+static int cur_tier() {
+  int t = g_tier.load(std::memory_order_relaxed);
+  if (t < 0) { t = pick_tier(); g_tier.store(t, std::memory_order_relaxed); }
+  return t;
+}
+
+constexpr int kRowBlock = 8;
+
+// dots of up to 8 rows of x (row pitch `pitch`) with one weight row: out[r] = x[r] . w
+__attribute__((target("avx2,fma"))) static void dots_avx2(const float* x, int64_t pitch, int nr, const float* w, int K, float* out) {
+  __m256 acc[kRowBlock];
+  for (int r = 0; r < kRowBlock; ++r) acc[r] = _mm256_setzero_ps();
+  int i = 0;
+  for (; i + 8 <= K; i += 8) {
+    const __m256 wv = _mm256_loadu_ps(w + i);
+    for (int r = 0; r < nr; ++r) acc[r] = _mm256_fmadd_ps(_mm256_loadu_ps(x + r * pitch + i), wv, acc[r]);
+  }
+  for (int r = 0; r < nr; ++r) {
+    float s = 0.f;
+    for (int k = i; k < K; ++k) s += x[r * pitch + k] * w[k];
+    alignas(32) float lane[8];
+    _mm256_store_ps(lane, acc[r]);
+    for (int j = 0; j < 8; ++j) s += lane[j];
+    out[r] = s;
+  }
+}
+
+__attribute__((target("avx512f"))) static void dots_avx512(const float* x, int64_t pitch, int nr, const float* w, int K, float* out) {
+  __m512 acc[kRowBlock];
+  for (int r = 0; r < kRowBlock; ++r) acc[r] = _mm512_setzero_ps();
+  int i = 0;
+  for (; i + 16 <= K; i += 16) {
+    const __m512 wv = _mm512_loadu_ps(w + i);
+    for (int r = 0; r < nr; ++r) acc[r] = _mm512_fmadd_ps(_mm512_loadu_ps(x + r * pitch + i), wv, acc[r]);
+  }
+  for (int r = 0; r < nr; ++r) {
+    float s = 0.f;
+    for (int k = i; k < K; ++k) s += x[r * pitch + k] * w[k];
+    alignas(64) float lane[16];
+    _mm512_store_ps(lane, acc[r]);
+    for (int j = 0; j < 16; ++j) s += lane[j];
+    out[r] = s;
+  }
+}
+
 void op_gemm(const Ctx& c, int64_t rows) {
   float* y = (float*)c.T(0);
   const float* x = (const float*)c.T(1);
@@ -236,15 +310,33 @@ void op_gemm(const Ctx& c, int64_t rows) {
   const bool dual = flags & PLOW_GEMM_DUAL_SILU;
   int64_t a, b;
   c.range(N, a, b);
-  for (int64_t m = 0; m < rows; ++m) {
-    const float* xr = x + m * pitch + co;
-    for (int64_t n = a; n < b; ++n) {
-      float v = dotf(xr, w + n * K, K);
-      if (dual) {
-        const float u = dotf(xr, w + (n + N) * K, K);
-        v = v / (1.0f + std::exp(-v)) * u;
+  const int tier = cur_tier();
+  if (tier == TIER_GOLDEN) {
+    for (int64_t m = 0; m < rows; ++m) {
+      const float* xr = x + m * pitch + co;
+      for (int64_t n = a; n < b; ++n) {
+        float v = dotf(xr, w + n * K, K);
+        if (dual) {
+          const float u = dotf(xr, w + (n + N) * K, K);
+          v = v / (1.0f + std::exp(-v)) * u;
+        }
+        y[m * N + n] = v;
       }
-      y[m * N + n] = v;
+    }
+    return;
+  }
+  auto dots = tier == TIER_AVX512 ? dots_avx512 : dots_avx2;
+  float g[kRowBlock], u[kRowBlock];
+  for (int64_t m0 = 0; m0 < rows; m0 += kRowBlock) {
+    const int nr = int(std::min<int64_t>(kRowBlock, rows - m0));
+    const float* xb = x + m0 * pitch + co;
+    for (int64_t n = a; n < b; ++n) {
+      dots(xb, pitch, nr, w + n * K, K, g);
+      if (dual) {
+        dots(xb, pitch, nr, w + (n + N) * K, K, u);
+        for (int r = 0; r < nr; ++r) g[r] = g[r] / (1.0f + std::exp(-g[r])) * u[r];
+      }
+      for (int r = 0; r < nr; ++r) y[(m0 + r) * N + n] = g[r];
     }
   }
 }
@@ -975,6 +1067,12 @@ int plow_cpu_trace(void* h, PlowTraceRec* out, int cap) {
   const int n = std::min<int>(cap, int(e->trace.size()));
   std::memcpy(out, e->trace.data(), sizeof(PlowTraceRec) * n);
   return n;
+}
+// kernel tier of the GEMM op: 0 golden, 1 avx2, 2 avx512.  set returns the tier in force (an unsupported one is refused).
+int plow_cpu_tier() { return cur_tier(); }
+int plow_cpu_set_tier(int t) {
+  if (t >= 0 && t <= TIER_AVX512 && tier_supported(t)) g_tier.store(t);
+  return cur_tier();
 }
 void* plow_cpu_arena(void* h) { return static_cast<Engine*>(h)->arena.data(); }
 
