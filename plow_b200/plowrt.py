@@ -69,7 +69,7 @@ def cmd_serve(args) -> int:
     from .serve.app import AppState, create_app
     cfg = cfgmod.RuntimeConfig.load(cli=dict(host=args.host, port=args.port, max_slots=args.max_slots, max_ctx=args.max_ctx,
                                              backend=args.backend, objective=args.objective, trace=args.trace or None,
-                                             api_keys=args.api_key or None, dp=args.dp, spec_depth=args.spec_depth, spec_drafter=args.spec_drafter, multi_step=args.multi_step, lookahead=args.lookahead or None, pd=args.pd or None))
+                                             api_keys=args.api_key or None, dp=args.dp, spec_depth=args.spec_depth, spec_drafter=args.spec_drafter, multi_step=args.multi_step, lookahead=args.lookahead or None, rung_control=args.rung_control or None, pd=args.pd or None))
     state = AppState(api_keys=cfg.api_keys, timeline=Timeline(cfg.trace), loader=lambda n, p: make_entry(n, p, cfg))
     name = args.name or Path(args.assets).resolve().name
     n_ranks, mode = (args.ep, "ep") if args.ep else (args.tp, "tp") if args.tp else (args.dp_procs, "dp") if args.dp_procs else (0, "")
@@ -219,6 +219,7 @@ def main(argv=None) -> int:
     s.add_argument("--objective")
     s.add_argument("--spec-depth", type=int, dest="spec_depth")
     s.add_argument("--spec-drafter", dest="spec_drafter", choices=["auto", "ngram", "mtp"])
+    s.add_argument("--rung-control", action="store_true", dest="rung_control", help="admission follows the decode-rung controller")
     s.add_argument("--lookahead", action="store_true", help="lookahead-1 decode pipeline (step n+1 launched before step n's tokens are read)")
     s.add_argument("--multi-step", type=int, dest="multi_step", help="greedy decode steps per engine call (default 1)")
     s.add_argument("--pd", action="store_true", help="prefill on one engine, decode on a second one (KV image hand-off)")
