@@ -90,6 +90,8 @@ typedef enum PlowOp {
 #define PLOW_GEMM_OUT_F32 4u
 #define PLOW_GEMM_RESIDUAL 8u
 #define PLOW_GEMM_QUANT_OUT 16u
+#define PLOW_GEMM_ACT_GELU_TANH 32u /* with DUAL: gelu (tanh form) instead of silu on the gate */
+#define PLOW_GEMM_ACT_GELU_ERF 64u  /* with DUAL: gelu (erf form) */
 
 /* attention modes (i4) */
 #define PLOW_ATTN_CAUSAL 0u      /* token-batch rows, each attends to its sequence up to pos */

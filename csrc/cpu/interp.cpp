@@ -240,6 +240,13 @@ void op_residual(const Ctx& c) {
 // Reference counterpart: runtime/cpu (scalar / AVX2 / AVX-512 / AMX kernel tiers behind one dispatch table).
 enum { TIER_GOLDEN = 0, TIER_AVX2 = 1, TIER_AVX512 = 2 };
 
+// gate activation of a GLU: SiLU unless the flags ask for GELU (tanh or erf form)
+static inline float glu_act(float v, uint32_t flags) {
+  if (flags & PLOW_GEMM_ACT_GELU_TANH) return 0.5f * v * (1.0f + std::tanh(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+  if (flags & PLOW_GEMM_ACT_GELU_ERF) return 0.5f * v * (1.0f + std::erf(v * 0.7071067811865476f));
+  return v / (1.0f + std::exp(-v));
+}
+
 static int tier_supported(int t) {
   if (t == TIER_AVX2) return __builtin_cpu_supports("avx2") && __builtin_cpu_supports("fma");
   if (t == TIER_AVX512) return __builtin_cpu_supports("avx512f");
@@ -318,7 +325,7 @@ void op_gemm(const Ctx& c, int64_t rows) {
         float v = dotf(xr, w + n * K, K);
         if (dual) {
           const float u = dotf(xr, w + (n + N) * K, K);
-          v = v / (1.0f + std::exp(-v)) * u;
+          v = glu_act(v, flags) * u;
         }
         y[m * N + n] = v;
       }
@@ -334,7 +341,7 @@ void op_gemm(const Ctx& c, int64_t rows) {
       dots(xb, pitch, nr, w + n * K, K, g);
       if (dual) {
         dots(xb, pitch, nr, w + (n + N) * K, K, u);
-        for (int r = 0; r < nr; ++r) g[r] = g[r] / (1.0f + std::exp(-g[r])) * u[r];
+        for (int r = 0; r < nr; ++r) g[r] = glu_act(g[r], flags) * u[r];
       }
       for (int r = 0; r < nr; ++r) y[(m0 + r) * N + n] = g[r];
     }
@@ -477,7 +484,8 @@ void op_glu(const Ctx& c) {
   const int W = int(te.dims[1]);
   int64_t a, b;
   c.range(c.e->io.rows, a, b);
-  for (int64_t k = a * W; k < b * W; ++k) out[k] = g[k] / (1.0f + std::exp(-g[k])) * u[k];
+  const uint32_t act = c.in->i[0];
+  for (int64_t k = a * W; k < b * W; ++k) out[k] = glu_act(g[k], act) * u[k];
 }
 
 

@@ -121,7 +121,7 @@ class Lowering:
                 m = nrows(n.outputs[0])
                 quant = fp8w and wv.kind in ("weight", "derived") and not a.get("router") and not a.get("out_f32") \
                     and N % 128 == 0 and K % 128 == 0 and len(wv.shape) == 2
-                flags = (pk.GEMM_DUAL_SILU if dual else 0) | (pk.GEMM_OUT_F32 if a.get("out_f32") else 0) \
+                flags = (pk.GEMM_DUAL_SILU | pk.ACT_FLAGS[a.get("act", "silu")] if dual else 0) | (pk.GEMM_OUT_F32 if a.get("out_f32") else 0) \
                     | (pk.GEMM_FP8_BLOCK if quant else 0)
                 co, pitch = self.xview(x)
                 tile = costmodel.pick_gemm_tile(m, N, quant, dual)
@@ -204,7 +204,7 @@ class Lowering:
         "sigmoid_gate": (Op.SIGMOID_GATE, [], [], "row"),
         "split_q_gate": (Op.NOP, ["heads", "head_dim"], [], "row"),
         "headnorm": (Op.RMSNORM, ["head_dim", "plus_one", "heads"], ["eps"], "row"),
-        "silu_mul": (Op.GLU, [], [], "row"),
+        "silu_mul": (Op.GLU, ["act_flag"], [], "row"),
         "rope": (Op.MLA_Q_ROPE, ["heads", "head_dim", "rot_dim", "pair_mode"], [], "row"),
         "kv_write": (Op.ROPE_KV, ["heads", "head_dim"], [], "row"),
     }
@@ -222,6 +222,8 @@ class Lowering:
                 return PAIR_MODE[v]
             if k == "score":
                 return 1 if v == "sigmoid" else 0
+            if k == "act_flag":
+                return pk.ACT_FLAGS[n.attrs.get("act", "silu")]
             return int(v)
 
         handles = [self.t(x) for x in (n.outputs + n.inputs)][:8]

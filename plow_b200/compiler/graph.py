@@ -184,7 +184,7 @@ def _decoder_layer(g: Graph, li: int, p: str, x: str, layer) -> str:
     h2 = g.tmp("h", (R, H))
     g.add("rmsnorm", [x2, ln2], [h2], layer=li, eps=spec.rms_eps, plus_one=spec.norm_plus_one)
     if layer.ffn.kind == "dense":
-        d = _dense_ffn(g, li, f"{p}.mlp", h2, layer.ffn.inter)
+        d = _dense_ffn(g, li, f"{p}.mlp", h2, layer.ffn.inter, act=layer.ffn.act)
         if tp > 1:
             d = _xreduce(g, d, li)
     else:
@@ -251,12 +251,12 @@ def _gqa_attention(g: Graph, li, p, h, a) -> str:
     return _linear(g, li, ao, f"{p}.self_attn.o_proj.weight", H, a.n_heads * hd, shard_axis=1)
 
 
-def _dense_ffn(g: Graph, li, p, h, inter, rows=R) -> str:
+def _dense_ffn(g: Graph, li, p, h, inter, rows=R, act="silu") -> str:
     H = g.spec.hidden
     gt = _linear(g, li, h, f"{p}.gate_proj.weight", inter, H, shard_axis=0, rows=rows)
     up = _linear(g, li, h, f"{p}.up_proj.weight", inter, H, shard_axis=0, rows=rows)
     m = g.tmp("glu", (rows, inter // g.tp))
-    g.add("silu_mul", [gt, up], [m], layer=li)
+    g.add("silu_mul", [gt, up], [m], layer=li, act=act)        # act(gate) * up; the op keeps its historical name
     return _linear(g, li, m, f"{p}.down_proj.weight", H, inter, shard_axis=1, rows=rows)
 
 

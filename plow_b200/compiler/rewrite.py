@@ -158,7 +158,7 @@ def rule_gated_mlp_fuse(g: Graph, sites: list) -> bool:
         if not (_single_use(cons, a.outputs[0], n) and _single_use(cons, b.outputs[0], n)):
             continue
         w = _cat_weight(g, [a.inputs[1], b.inputs[1]], "gate_up_proj")
-        fused = Node("linear_glu", [a.inputs[0], w], [n.outputs[0]], dict(act="silu"), n.layer, "gated-mlp-fuse")
+        fused = Node("linear_glu", [a.inputs[0], w], [n.outputs[0]], dict(act=n.attrs.get("act", "silu")), n.layer, "gated-mlp-fuse")
         _replace(g, [a, b, n], [fused])
         es = costmodel.dtype_bytes(g.values[a.outputs[0]].dtype)
         sites.append(Site("gated-mlp-fuse", n.layer, 4 * g.values[a.outputs[0]].shape[1] * es, 2))

@@ -172,6 +172,18 @@ def _rope_from(cfg: dict, head_dim: int, rot_dim: int | None = None, pair: str =
                     pair_mode=pair, scaling=scaling, max_pos=int(cfg.get("max_position_embeddings", 4096)))
 
 
+def _act(cfg: dict, moe: bool = False) -> str:
+    """The gate activation of the GLU: silu, gelu_tanh or gelu.  Routed experts run SiLU only."""
+    a = str(cfg.get("hidden_act") or cfg.get("hidden_activation") or "silu").lower()
+    name = {"silu": "silu", "swish": "silu", "gelu_pytorch_tanh": "gelu_tanh", "gelu_new": "gelu_tanh", "gelu_tanh": "gelu_tanh",
+            "gelu_fast": "gelu_tanh", "gelu": "gelu"}.get(a)
+    if name is None:
+        raise ValueError(f"unsupported hidden_act '{a}' (silu, gelu_pytorch_tanh and gelu are)")
+    if moe and name != "silu":
+        raise ValueError(f"routed experts with hidden_act '{a}' are not supported (silu only)")
+    return name
+
+
 def _eos(cfg: dict) -> list:
     e = cfg.get("eos_token_id")
     if e is None:
@@ -188,8 +200,11 @@ def _quant(cfg: dict) -> str:
 
 def spec_from_config(cfg: dict) -> ModelSpec:
     mt = cfg.get("model_type", "")
-    if mt in ("llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "plow_dense"):
+    if mt in ("llama", "mistral", "qwen2", "qwen3", "gemma", "plow_dense"):
         return _dense_gqa(cfg, mt)
+    if mt in ("gemma2", "gemma3", "gemma3_text"):
+        raise ValueError(f"model_type '{mt}' is not supported: its layers carry four norms, alternate local and global attention and "
+                         "cap the attention logits; reading it as a llama-shaped model would compute something else")
     if mt in ("deepseek_v3", "deepseek_v2", "kimi_k2", "glm_moe_dsa", "glm5_next", "deepseek_v32", "plow_mla_moe"):
         return _mla_moe(cfg, mt)
     if mt in ("qwen3_next", "qwen3_5", "plow_gdn_hybrid"):
@@ -219,7 +234,7 @@ def _dense_gqa(cfg: dict, mt: str) -> ModelSpec:
     n_layers = cfg["num_hidden_layers"]
     attn = AttnSpec(kind="gqa", n_heads=nh, n_kv_heads=nkv, head_dim=hd, qk_norm=(mt == "qwen3" or cfg.get("qk_norm", False)),
                     window=int(cfg.get("sliding_window") or 0) if cfg.get("use_sliding_window", mt == "mistral") else 0)
-    ffn = FfnSpec(kind="dense", inter=cfg["intermediate_size"], act=cfg.get("hidden_act", "silu"))
+    ffn = FfnSpec(kind="dense", inter=cfg["intermediate_size"], act=_act(cfg))
     gem = mt.startswith("gemma")
     return ModelSpec(
         family="dense_gqa", model_type=mt, hidden=h, vocab=cfg["vocab_size"], n_layers=n_layers,
@@ -242,8 +257,8 @@ def _mla_moe(cfg: dict, mt: str) -> ModelSpec:
                     qk_nope=cfg["qk_nope_head_dim"], qk_rope=cfg["qk_rope_head_dim"], v_head=cfg["v_head_dim"],
                     index_heads=idx_heads, index_dim=int(cfg.get("index_head_dim", 0)),
                     index_topk=int(cfg.get("index_topk", 0)))
-    dense = FfnSpec(kind="dense", inter=cfg["intermediate_size"], act=cfg.get("hidden_act", "silu"))
-    moe = FfnSpec(kind="moe", act=cfg.get("hidden_act", "silu"), n_experts=cfg.get("n_routed_experts", 0),
+    dense = FfnSpec(kind="dense", inter=cfg["intermediate_size"], act=_act(cfg))
+    moe = FfnSpec(kind="moe", act=_act(cfg, moe=bool(cfg.get("n_routed_experts"))), n_experts=cfg.get("n_routed_experts", 0),
                   top_k=cfg.get("num_experts_per_tok", 0), n_shared=cfg.get("n_shared_experts", 0),
                   moe_inter=cfg.get("moe_intermediate_size", 0), n_group=cfg.get("n_group", 1),
                   topk_group=cfg.get("topk_group", 1), score=cfg.get("scoring_func", "sigmoid"),
@@ -269,11 +284,11 @@ def _gqa_moe(cfg: dict, mt: str) -> ModelSpec:
     mix = mt == "mixtral"
     attn = AttnSpec(kind="gqa", n_heads=nh, n_kv_heads=nkv, head_dim=hd, qk_norm=not mix,
                     window=int(cfg.get("sliding_window") or 0) if (mix and cfg.get("sliding_window")) else 0)
-    moe = FfnSpec(kind="moe", act=cfg.get("hidden_act", "silu"), n_experts=cfg["num_local_experts" if mix else "num_experts"],
+    moe = FfnSpec(kind="moe", act=_act(cfg, moe=True), n_experts=cfg["num_local_experts" if mix else "num_experts"],
                   top_k=cfg["num_experts_per_tok"], moe_inter=cfg["intermediate_size" if mix else "moe_intermediate_size"],
                   score="softmax", norm_topk=True if mix else bool(cfg.get("norm_topk_prob", True)),
                   block="block_sparse_moe" if mix else "mlp", expert_names="w123" if mix else "proj")
-    dense = FfnSpec(kind="dense", inter=cfg.get("intermediate_size", 0), act=cfg.get("hidden_act", "silu"))
+    dense = FfnSpec(kind="dense", inter=cfg.get("intermediate_size", 0), act=_act(cfg))
     step, only = int(cfg.get("decoder_sparse_step", 1) or 1), set(cfg.get("mlp_only_layers") or [])
     layers = [LayerSpec(attn, moe if (mix or (i not in only and (i + 1) % step == 0)) else dense) for i in range(n_layers)]
     return ModelSpec(

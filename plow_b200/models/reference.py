@@ -124,12 +124,14 @@ class ReferenceModel:
             o = self._gdn(p, h, layer.attn)
         x = x + o
         h = rmsnorm(x, self.w[f"{p}.post_attention_layernorm.weight"], spec.rms_eps, spec.norm_plus_one)
-        return x + (self._dense(f"{p}.mlp", h) if layer.ffn.kind == "dense" else self._moe(f"{p}.{layer.ffn.block}", h, layer.ffn))
+        return x + (self._dense(f"{p}.mlp", h, act=layer.ffn.act) if layer.ffn.kind == "dense" else self._moe(f"{p}.{layer.ffn.block}", h, layer.ffn))
 
     # ---- blocks --------------------------------------------------------------------------------
-    def _dense(self, p, h, names="proj"):
+    def _dense(self, p, h, names="proj", act="silu"):
         g, u, d = ("w1", "w3", "w2") if names == "w123" else ("gate_proj", "up_proj", "down_proj")
-        return self.lin(F.silu(self.lin(h, f"{p}.{g}.weight")) * self.lin(h, f"{p}.{u}.weight"), f"{p}.{d}.weight")
+        gate = self.lin(h, f"{p}.{g}.weight")
+        gate = F.silu(gate) if act == "silu" else F.gelu(gate, approximate="tanh" if act == "gelu_tanh" else "none")
+        return self.lin(gate * self.lin(h, f"{p}.{u}.weight"), f"{p}.{d}.weight")
 
     def _gqa(self, p, h, pos, a):
         spec = self.spec

@@ -539,3 +539,54 @@ def test_gqa_moe_families_on_cpu_backend_match_reference(tmp_path, model_type):
         want = ref.forward(torch.tensor(cur))[-1]
         assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item())
     eng.close()
+
+
+def test_gelu_gated_model_runs_on_cpu_and_unsupported_shapes_are_refused(tmp_path):
+    """A gemma-style decoder (GELU-tanh gate, (1 + gamma) norms, scaled embeddings, one kv head of width 128): the gate's
+    activation travels as a flag of the fused GEMM (and of the GLU row op when the fusion is off) and the logits match the
+    fp32 reference.  Model types whose layers this compiler would misread (gemma2 / gemma3) and unknown activations are
+    refused by name instead of being computed as something else."""
+    import glob
+    from safetensors.torch import load_file
+    from plow_b200 import plowc
+    from plow_b200.compiler import packet as pk
+    from plow_b200.models import config, reference
+    from plow_b200.runtime.engine import TokenBatch
+    cfg = dict(model_type="gemma", hidden_size=256, num_attention_heads=4, num_key_value_heads=1, head_dim=128, num_hidden_layers=2,
+               intermediate_size=512, hidden_act="gelu_pytorch_tanh", rms_norm_eps=1e-6, rope_theta=10000.0, vocab_size=512,
+               tie_word_embeddings=True, max_position_embeddings=1024, eos_token_id=1, plow_dtype="f32", plow_kv_dtype="f32")
+    spec = config.spec_from_config(cfg)
+    assert spec.layers[0].ffn.act == "gelu_tanh" and spec.norm_plus_one and spec.embed_scale == 16.0
+    for bad in (dict(cfg, model_type="gemma2"), dict(cfg, model_type="gemma3_text"), dict(cfg, hidden_act="relu2")):
+        with pytest.raises(ValueError, match="not supported|unsupported"):
+            config.spec_from_config(bad)
+    with pytest.raises(ValueError, match="routed experts"):
+        config.spec_from_config(dict(model_type="mixtral", hidden_size=64, num_attention_heads=2, num_hidden_layers=1, num_local_experts=4,
+                                     num_experts_per_tok=2, intermediate_size=64, vocab_size=64, hidden_act="gelu"))
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=0)
+    state = {}
+    for f in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        state.update(load_file(f))
+    state = {k: (v + 0.1 * torch.randn_like(v) if k.endswith("norm.weight") else v).float() for k, v in state.items()}     # (1 + gamma) with gamma != 0
+    from safetensors.torch import save_file
+    for f in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        save_file({k: state[k] for k in load_file(f)}, f)
+    ref = reference.ReferenceModel(spec, state)
+    p = np.random.default_rng(5).integers(0, 512, 60).tolist()
+    want = ref.forward(torch.tensor(p))[-1]
+    assert (want - reference.ReferenceModel(config.spec_from_config(dict(cfg, hidden_act="silu")), state).forward(torch.tensor(p))[-1]).abs().max() > 1e-3
+    for out, kw in (("fused", {}), ("unfused", dict(disable_rules=("gated-mlp-fuse",)))):
+        plowc.compile_dir(tmp_path / "ckpt", tmp_path / out, arch="cpu", n_cu=4, max_rows=128, decode_rungs=[1], max_seqs=4, **kw)
+        pkt = pk.read_packet(tmp_path / out / "model.pkt")
+        insts = pkt.programs[0].insts
+        if out == "fused":
+            assert any(i.op == pk.Op.GEMM and i.i[2] & pk.GEMM_ACT_GELU_TANH for i in insts)
+        else:
+            assert any(i.op == pk.Op.GLU and i.i[0] == pk.GEMM_ACT_GELU_TANH for i in insts)
+        eng = CpuEngine(tmp_path / out, max_slots=2, max_ctx=256)
+        eng.begin_slot(0, p)
+        eng.reserve(0, 64)
+        r = eng.step(TokenBatch(np.asarray(p, np.int32), np.arange(60, dtype=np.int32), np.zeros(60, np.int32), np.asarray([59], np.int32),
+                                want_logits=True))
+        eng.close()
+        assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item()), out
