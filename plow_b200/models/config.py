@@ -2,7 +2,8 @@
 
 Families understood (by ``model_type`` / ``architectures``):
 
-* dense GQA decoders: llama, mistral, qwen2, qwen3 (per-head q/k RMSNorm), gemma-style ``1+γ`` norms;
+* dense GQA decoders without projection biases: llama, mistral, qwen3 (per-head q/k RMSNorm), gemma (``1+γ`` norms, GELU
+  gate); qwen2 (q / k / v biases) and gemma2 / gemma3 (four norms per layer, capped logits) are refused by name;
 * MLA + MoE decoders: deepseek_v3 / deepseek_v2, kimi_k2, glm_moe_dsa (adds the DSA indexer);
 * hybrid linear-attention MoE decoders: qwen3_next (gated delta rule + gated full attention);
 * GQA + MoE decoders: qwen3_moe (per-head q/k norm, softmax router) and mixtral (experts named w1 / w3 / w2 under
@@ -200,7 +201,10 @@ def _quant(cfg: dict) -> str:
 
 def spec_from_config(cfg: dict) -> ModelSpec:
     mt = cfg.get("model_type", "")
-    if mt in ("llama", "mistral", "qwen2", "qwen3", "gemma", "plow_dense"):
+    if mt == "qwen2" or cfg.get("attention_bias") or cfg.get("mlp_bias"):
+        raise ValueError(f"model_type '{mt}': projection biases are not supported (qwen2 always carries them on q / k / v); "
+                         "dropping them would compute a different model")
+    if mt in ("llama", "mistral", "qwen3", "gemma", "plow_dense"):
         return _dense_gqa(cfg, mt)
     if mt in ("gemma2", "gemma3", "gemma3_text"):
         raise ValueError(f"model_type '{mt}' is not supported: its layers carry four norms, alternate local and global attention and "

@@ -260,8 +260,8 @@ def unpermute_qk(w: torch.Tensor, n_head: int) -> torch.Tensor:
 def config_from_gguf(g: GgufFile) -> dict:
     md = g.metadata
     arch = md.get("general.architecture")
-    if arch not in ("llama", "mistral", "qwen2", "qwen3"):
-        raise GgufError(f"GGUF architecture '{arch}' has no mapping to a supported family (llama, mistral, qwen2, qwen3 have)")
+    if arch not in ("llama", "mistral", "qwen3"):
+        raise GgufError(f"GGUF architecture '{arch}' has no mapping to a supported family (llama, mistral, qwen3 have)")
 
     def key(k, default=None):
         v = md.get(f"{arch}.{k}", default)

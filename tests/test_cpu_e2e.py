@@ -557,7 +557,8 @@ def test_gelu_gated_model_runs_on_cpu_and_unsupported_shapes_are_refused(tmp_pat
                tie_word_embeddings=True, max_position_embeddings=1024, eos_token_id=1, plow_dtype="f32", plow_kv_dtype="f32")
     spec = config.spec_from_config(cfg)
     assert spec.layers[0].ffn.act == "gelu_tanh" and spec.norm_plus_one and spec.embed_scale == 16.0
-    for bad in (dict(cfg, model_type="gemma2"), dict(cfg, model_type="gemma3_text"), dict(cfg, hidden_act="relu2")):
+    for bad in (dict(cfg, model_type="gemma2"), dict(cfg, model_type="gemma3_text"), dict(cfg, hidden_act="relu2"),
+                dict(cfg, model_type="qwen2"), dict(cfg, model_type="llama", hidden_act="silu", attention_bias=True)):
         with pytest.raises(ValueError, match="not supported|unsupported"):
             config.spec_from_config(bad)
     with pytest.raises(ValueError, match="routed experts"):
