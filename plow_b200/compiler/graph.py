@@ -13,6 +13,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 
 from ..models.config import ModelSpec
+from ..utils.rope import mla_softmax_factor
 
 R = "R"   # rows of the running program
 S = "S"   # sampled rows (one per sequence that finishes a chunk)
@@ -295,7 +296,8 @@ def _mla_attention(g: Graph, li, p, h, a) -> str:
     if a.index_heads:
         extra = [_dsa_select(g, li, p, h, qan if a.q_lora else h, a)]
     g.add("mla_attention", [q, rope, "in.pos", wkv_b] + outs + extra, [ao], layer=li, heads=nh, kv_lora=a.kv_lora,
-          qk_nope=a.qk_nope, qk_rope=a.qk_rope, v_head=a.v_head, scale=qh ** -0.5, pair_mode=spec.rope.pair_mode,
+          qk_nope=a.qk_nope, qk_rope=a.qk_rope, v_head=a.v_head, scale=qh ** -0.5 * mla_softmax_factor(spec.rope.scaling),
+          pair_mode=spec.rope.pair_mode,
           sparse=bool(a.index_heads), topk=a.index_topk)
     return _linear(g, li, ao, f"{p}.self_attn.o_proj.weight", H, a.n_heads * a.v_head, shard_axis=1)
 

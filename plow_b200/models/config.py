@@ -268,6 +268,9 @@ def _mla_moe(cfg: dict, mt: str) -> ModelSpec:
                   topk_group=cfg.get("topk_group", 1), score=cfg.get("scoring_func", "sigmoid"),
                   norm_topk=bool(cfg.get("norm_topk_prob", True)), route_scale=float(cfg.get("routed_scaling_factor", 1.0)),
                   has_bias=cfg.get("topk_method", "noaux_tc") == "noaux_tc")
+    if moe.n_experts and moe.n_group > 1 and cfg.get("topk_method", "noaux_tc") not in ("noaux_tc", "greedy"):
+        raise ValueError(f"topk_method '{cfg.get('topk_method')}' with expert groups is not supported: groups are ranked here by the "
+                         "sum of their two best scores (noaux_tc), not by their best score")
     layers = [LayerSpec(attn, dense if (i < first_dense or not moe.n_experts) else moe) for i in range(n_layers)]
     return ModelSpec(
         family="mla_moe", model_type=mt, hidden=h, vocab=cfg["vocab_size"], n_layers=n_layers,

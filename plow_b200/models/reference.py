@@ -12,7 +12,7 @@ from pathlib import Path
 import torch
 import torch.nn.functional as F
 
-from ..utils.rope import rope_table
+from ..utils.rope import mla_softmax_factor, rope_table
 from .config import ModelSpec, spec_from_config
 
 
@@ -177,7 +177,7 @@ class ReferenceModel:
             if keep is None:
                 keep = self.dsa_select(p, h, qa if a.q_lora else h, pos, a)
             self.dsa_last[p] = keep
-        o = causal_attention(torch.cat([q_nope, q_rope], -1), k, v, qh ** -0.5, keep=keep).reshape(T, -1)
+        o = causal_attention(torch.cat([q_nope, q_rope], -1), k, v, qh ** -0.5 * mla_softmax_factor(spec.rope.scaling), keep=keep).reshape(T, -1)
         return self.lin(o, f"{p}.self_attn.o_proj.weight")
 
     def dsa_scores(self, p, h, q_in, pos, a):

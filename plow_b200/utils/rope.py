@@ -62,3 +62,16 @@ def rope_table(max_pos: int, rot_dim: int, theta: float, scaling: dict | None = 
     f, att = inv_freq(theta, rot_dim, scaling)
     ang = np.arange(max_pos, dtype=np.float64)[:, None] * f[None, :]
     return np.concatenate([np.cos(ang) * att, np.sin(ang) * att], axis=1).astype(np.float32)
+
+
+def mla_softmax_factor(scaling: dict | None) -> float:
+    """What multi-head latent attention multiplies its softmax scale by under YaRN: mscale(factor, mscale_all_dim)^2.
+    The rotary table itself carries mscale(factor, mscale) / mscale(factor, mscale_all_dim) (1 when the two are equal),
+    so without this factor a YaRN-extended checkpoint attends with logits about half as large as it was trained with."""
+    if not scaling or (scaling.get("type") or scaling.get("rope_type")) != "yarn":
+        return 1.0
+    factor, msa = float(scaling.get("factor", 1.0)), float(scaling.get("mscale_all_dim") or 0.0)
+    if factor <= 1.0 or msa == 0.0:
+        return 1.0
+    m = 0.1 * msa * math.log(factor) + 1.0
+    return m * m

@@ -591,3 +591,50 @@ def test_gelu_gated_model_runs_on_cpu_and_unsupported_shapes_are_refused(tmp_pat
                                 want_logits=True))
         eng.close()
         assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item()), out
+
+
+def test_mla_under_yarn_scales_its_softmax(tmp_path):
+    """A YaRN-extended MLA checkpoint multiplies the softmax scale by mscale(factor, mscale_all_dim)^2 (1.87 for factor 40):
+    the compiled attention carries it and the CPU engine matches the reference, which differs from the unscaled model."""
+    import glob
+    import math
+    from safetensors.torch import load_file
+    from plow_b200 import plowc
+    from plow_b200.compiler import packet as pk
+    from plow_b200.models import config, reference
+    from plow_b200.runtime.engine import TokenBatch
+    from plow_b200.utils.rope import mla_softmax_factor
+    yarn = dict(type="yarn", factor=40.0, original_max_position_embeddings=64, beta_fast=32, beta_slow=1, mscale=1.0, mscale_all_dim=1.0)
+    assert mla_softmax_factor(yarn) == pytest.approx((0.1 * math.log(40.0) + 1.0) ** 2) and mla_softmax_factor(None) == 1.0
+    assert mla_softmax_factor(dict(yarn, mscale_all_dim=0)) == 1.0 and mla_softmax_factor(dict(type="llama3", factor=8.0)) == 1.0
+    cfg = dict(model_type="deepseek_v3", hidden_size=256, num_attention_heads=4, num_hidden_layers=2,
+               q_lora_rank=64, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+               intermediate_size=512, first_k_dense_replace=2, n_routed_experts=0, rms_norm_eps=1e-6,
+               rope_theta=10000.0, rope_scaling=yarn, vocab_size=512, tie_word_embeddings=False, max_position_embeddings=1024,
+               eos_token_id=1, plow_dtype="f32", plow_kv_dtype="f32")
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=0)
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", arch="cpu", n_cu=4, max_rows=128, decode_rungs=[1], max_seqs=4)
+    pkt = pk.read_packet(tmp_path / "assets" / "model.pkt")
+    scales = {round(i.f[0], 5) for p in pkt.programs for i in p.insts if i.op in (pk.Op.MLA_PREFILL, pk.Op.MLA_DECODE)}
+    assert scales == {round(24 ** -0.5 * mla_softmax_factor(yarn), 5)}
+    state = {}
+    for f in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        state.update(load_file(f))
+    state = {k: v.float() * (8.0 if "q_b_proj" in k or "kv_b_proj" in k else 1.0) for k, v in state.items()}     # logits large enough to matter
+    from safetensors.torch import save_file
+    for f in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        save_file({k: state[k] for k in load_file(f)}, f)
+    ref = reference.ReferenceModel(config.spec_from_config(cfg), state)
+    plain = reference.ReferenceModel(config.spec_from_config({k: v for k, v in cfg.items() if k != "rope_scaling"}), state)
+    p = np.random.default_rng(8).integers(0, 512, 90).tolist()
+    want = ref.forward(torch.tensor(p))[-1]
+    assert (want - plain.forward(torch.tensor(p))[-1]).abs().max() > 1e-4
+    eng = CpuEngine(tmp_path / "assets", max_slots=2, max_ctx=256)
+    eng.begin_slot(0, p)
+    eng.reserve(0, 96)
+    r = eng.step(TokenBatch(np.asarray(p, np.int32), np.arange(90, dtype=np.int32), np.zeros(90, np.int32), np.asarray([89], np.int32), want_logits=True))
+    eng.close()
+    assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item())
+    with pytest.raises(ValueError, match="topk_method"):
+        config.spec_from_config(dict(cfg, n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=32, n_group=2, topk_group=1,
+                                     topk_method="group_limited_greedy", first_k_dense_replace=0))
