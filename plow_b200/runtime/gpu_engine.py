@@ -58,6 +58,12 @@ class CheckpointWeights(WeightSource):
 
     def fp8(self, ent, recipe):
         got = self.twins.get(ent.name, self.device) if self.twins else None
+        if got is None:
+            # a checkpoint that is already block-quantised (e4m3 codes + _scale_inv): its own codes, not a second rounding
+            from .weights import fp8_codes
+            got = fp8_codes(ent.name, ent, recipe, self.ckpt, self.tp, self.rank)
+            if got is not None:
+                got = (got[0].to(self.device), got[1].to(self.device))
         return got if got is not None else super().fp8(ent, recipe)
 
     def bf16(self, ent, recipe):

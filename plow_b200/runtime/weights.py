@@ -65,7 +65,32 @@ def open_checkpoint(path):
     return GgufCheckpoint(g) if g is not None else Checkpoint(path)
 
 
+SCALE_SUFFIX = "_scale_inv"      # block-quantised checkpoints: <name> holds e4m3 codes, <name>_scale_inv one f32 per 128 x 128 block
+
+
+def is_block_fp8(ckpt, name: str) -> bool:
+    return ckpt.has(name + SCALE_SUFFIX)
+
+
+def dequant_block_fp8(q: torch.Tensor, scale_inv: torch.Tensor, row0: int = 0, col0: int = 0) -> torch.Tensor:
+    """codes [n, k] (a slice starting at (row0, col0) of the full matrix) times their 128 x 128 block scales -> bf16."""
+    n, k = q.shape
+    r = (torch.arange(n) + row0) // 128
+    c = (torch.arange(k) + col0) // 128
+    return (q.float() * scale_inv.float()[r][:, c]).to(torch.bfloat16)
+
+
 def shard_slice(ckpt: Checkpoint, name: str, shard_axis, tp: int, rank: int) -> torch.Tensor:
+    """The rank's part of a checkpoint tensor.  A block-quantised tensor (e4m3 codes + ``_scale_inv``) comes back
+    dequantised to bf16: callers that want the codes themselves use :func:`fp8_codes`."""
+    if is_block_fp8(ckpt, name):
+        scale = ckpt.get(name + SCALE_SUFFIX)
+        if shard_axis is None or shard_axis == 0xFFFFFFFF or tp == 1:
+            return dequant_block_fp8(ckpt.get(name), scale)
+        n = ckpt.shape(name)[shard_axis]
+        per = n // tp
+        q = ckpt.get_slice(name, shard_axis, rank * per, (rank + 1) * per)
+        return dequant_block_fp8(q, scale, rank * per if shard_axis == 0 else 0, rank * per if shard_axis == 1 else 0)
     if shard_axis is None or shard_axis == 0xFFFFFFFF or tp == 1:
         return ckpt.get(name)
     n = ckpt.shape(name)[shard_axis]
@@ -81,6 +106,35 @@ def expert_range(n_experts: int, ep: int, rank: int) -> range:
     return range(rank * per, (rank + 1) * per)
 
 
+def fp8_codes(name: str, ent, recipe: dict | None, ckpt, tp: int = 1, rank: int = 0):
+    """(e4m3 codes, f32 block scales) of a packet tensor taken straight from a block-quantised checkpoint, or None when
+    the checkpoint is not quantised that way or the pieces do not line up with 128-row blocks (the caller then
+    dequantises and quantises again).  Covers plain tensors, row concatenations and stacked experts, unsharded."""
+    if tp != 1:
+        return None
+
+    def one(n):
+        if not is_block_fp8(ckpt, n):
+            return None
+        q, s = ckpt.get(n), ckpt.get(n + SCALE_SUFFIX).float()
+        if q.dtype != torch.float8_e4m3fn or q.dim() != 2 or (q.shape[0] % 128 and recipe is not None):
+            return None
+        return q, s
+    if recipe is None:
+        return one(name)
+    if recipe["op"] == "cat" and recipe.get("axis", 0) == 0:
+        parts = [one(p) for p in recipe["parts"]]
+    elif recipe["op"] == "stack_experts":
+        names = [f"{recipe['prefix']}.{e}.{part}.weight" for e in expert_range(recipe["n"], recipe.get("ep", 1), recipe.get("rank", 0))
+                 for part in recipe["parts"]] + list(recipe.get("tail", []))
+        parts = [one(p) for p in names]
+    else:
+        return None
+    if any(p is None for p in parts):
+        return None
+    return torch.cat([p[0].view(torch.uint8) for p in parts], 0).view(torch.float8_e4m3fn).contiguous(), torch.cat([p[1] for p in parts], 0).contiguous()
+
+
 def materialize(name: str, ent, recipe: dict | None, ckpt: Checkpoint, tp: int = 1, rank: int = 0) -> torch.Tensor:
     """Build the tensor behind a WEIGHT or DERIVED packet entry (host memory, checkpoint dtype)."""
     if recipe is None:
@@ -92,10 +146,12 @@ def materialize(name: str, ent, recipe: dict | None, ckpt: Checkpoint, tp: int =
         rows = []
         for e in expert_range(recipe["n"], recipe.get("ep", 1), recipe.get("rank", 0)):
             for part in recipe["parts"]:
-                rows.append(ckpt.get(f"{recipe['prefix']}.{e}.{part}.weight"))
+                rows.append(shard_slice(ckpt, f"{recipe['prefix']}.{e}.{part}.weight", None, 1, 0))
         for name in recipe.get("tail", []):      # shared expert stacked behind the routed ones (replicated on every rank)
-            rows.append(ckpt.get(name))
+            rows.append(shard_slice(ckpt, name, None, 1, 0))
         return torch.cat(rows, dim=0).contiguous()
     if recipe["op"] == "cols":                 # a column range of a checkpoint matrix (a half of eh_proj)
+        if is_block_fp8(ckpt, recipe["src"]):
+            return shard_slice(ckpt, recipe["src"], None, 1, 0)[:, recipe["start"]:recipe["stop"]].contiguous()
         return ckpt.get_slice(recipe["src"], 1, recipe["start"], recipe["stop"]).contiguous()
     raise ValueError(f"unknown derived-weight recipe '{recipe['op']}'")
