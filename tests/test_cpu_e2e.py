@@ -1,4 +1,4 @@
-"""Config 1 (CPU plumbing): tiny dense GQA decoder, fp32, plowc -> packet -> plowrt engine ->
+"""CPU plumbing: tiny dense GQA decoder, fp32, plowc -> packet -> plowrt engine ->
 scheduler; logits must match the PyTorch reference to 1e-4 and greedy tokens must agree."""
 import json
 
