@@ -165,6 +165,17 @@ def cmd_inventory(args) -> int:
     return 0
 
 
+def cmd_budget(args) -> int:
+    """Memory plan of a packet against a device size: weights, arenas, state, KV page size, pages that fit."""
+    from .runtime.budget import plan_memory
+    pkt = pk.read_packet(Path(args.assets) / "model.pkt" if Path(args.assets).is_dir() else args.assets)
+    plan = plan_memory(pkt, int(args.device_gb * 2 ** 30), args.max_slots, args.max_ctx, args.kv_fraction, int(args.reserve_gb * 2 ** 30))
+    out = plan.to_json()
+    out["gib"] = {k[:-6]: round(v / 2 ** 30, 3) for k, v in out.items() if k.endswith("_bytes")}
+    print(json.dumps(out, indent=1))
+    return 0 if plan.fits else 1
+
+
 def cmd_devices(_args) -> int:
     import torch
     devs = []
@@ -261,6 +272,14 @@ def main(argv=None) -> int:
     d.add_argument("--limit", type=int, default=200)
     d.set_defaults(fn=cmd_disasm)
     sub.add_parser("devices").set_defaults(fn=cmd_devices)
+    bg = sub.add_parser("budget", help="device-memory plan of a packet: weights, arenas, state, KV pages that fit")
+    bg.add_argument("--assets", required=True)
+    bg.add_argument("--device-gb", type=float, default=180.0, dest="device_gb")
+    bg.add_argument("--max-slots", type=int, default=64, dest="max_slots")
+    bg.add_argument("--max-ctx", type=int, default=8192, dest="max_ctx")
+    bg.add_argument("--kv-fraction", type=float, default=0.9, dest="kv_fraction")
+    bg.add_argument("--reserve-gb", type=float, default=2.0, dest="reserve_gb")
+    bg.set_defaults(fn=cmd_budget)
     k = sub.add_parser("knob-scope")
     k.set_defaults(fn=lambda a: print(json.dumps(cfgmod.knob_table("runtime"), indent=1)) or 0)
     def dist_parser(cmd_name, *pos, **opts):
