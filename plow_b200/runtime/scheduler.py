@@ -198,6 +198,8 @@ class ModelMux:
         from ..obs.breakdown import Breakdown
         self.blog = Breakdown()                       # tick / decode-step / TTFT breakdown logs (environment switches)
         self._tick_info = None                        # (kind, rows, reqs, device ms) of the tick in progress
+        from ..serve.overload import OverloadControl
+        self.overload = OverloadControl.from_env()    # None unless PLOW_OVERLOAD=1 (or set by the owner)
         self.rungs = None                             # decode-rung admission controller (cfg.rung_control)
         self.rung_decision = None
         self._mean_out = 1.0                          # running mean of output tokens per finished request
@@ -243,6 +245,11 @@ class ModelMux:
             return req
         if self.draining or self.ingress.qsize() + len(self.waiting) >= self.cfg.max_queue:
             self.metrics.inc("requests_shed")
+            req.out.put(Chunk("error", error="overloaded", finish_reason="overloaded"))
+            return req
+        if self.overload is not None and not self.overload.admit(params.session_id is not None and params.session_id in self.retained):
+            self.metrics.inc("requests_shed")
+            self.metrics.inc("overload_refused")
             req.out.put(Chunk("error", error="overloaded", finish_reason="overloaded"))
             return req
         if len(prompt) + 1 > self.engine.max_ctx:
@@ -336,6 +343,9 @@ class ModelMux:
         self._shed_expired()
         self._expire_sessions()
         self._adopt()
+        if self.overload is not None:
+            self.overload.tick()
+            self.metrics.gauge("overload_level", self.overload.level)
         if self.rungs is not None:
             from .rungs import RungLoad
             now = time.monotonic()
@@ -357,6 +367,8 @@ class ModelMux:
         for r in [r for r in self.live.values() if r.deadline is not None and now > r.deadline]:
             # a request past its deadline stops where it is: what was generated is delivered (reference: serve/deadlines.rs)
             self.metrics.inc("deadline_exceeded")
+            if self.overload is not None:
+                self.overload.record(False)
             self._finish(r, "deadline")
         prefilling = [r for r in prefilling if r.slot in self.live]
         decoding = [r for r in decoding if r.slot in self.live]
@@ -549,6 +561,8 @@ class ModelMux:
         if self.cfg.tbt_target_ms > 0 and self.metrics.step_ms:
             # crude service model: rows per ms observed on recent prefill ticks
             b = max(PAGE, min(b, int(self.cfg.tbt_target_ms * getattr(self, "_rows_per_ms", 64.0))))
+        if self.overload is not None and self.overload.level:
+            b = max(PAGE, int(b * self.overload.prefill_scale()))
         return b
 
     # ---- drafter ------------------------------------------------------------------------------
@@ -746,7 +760,7 @@ class ModelMux:
 
     def _decode_tick(self, reqs: list) -> None:
         eng = self.engine
-        if self.cfg.spec_depth > 0 and self._spec_tick(reqs):
+        if self.cfg.spec_depth > 0 and (self.overload is None or self.overload.extras_allowed()) and self._spec_tick(reqs):
             return
         cap = eng.max_rows(True)
         reqs = sorted(reqs, key=lambda r: r.slot)[:cap]
@@ -814,6 +828,8 @@ class ModelMux:
         admitted or prefilled, no drafter, no rank group (the other ranks follow synchronous steps), no recurrent state
         (the row a chained step computes for a request that has just ended would advance a state its session keeps)."""
         eng = self.engine
+        if self.overload is not None and not self.overload.extras_allowed():
+            return False
         if not self.cfg.lookahead or getattr(eng, "has_recurrent_state", False) or self.cfg.spec_depth > 0 or self.waiting or not self.ingress.empty() or not self.adopt_q.empty() \
                 or self.draining or getattr(eng, "step_group", None) is not None or getattr(eng, "leader_group", None) is not None:
             return False
@@ -911,6 +927,8 @@ class ModelMux:
                                (now - seated) * 1e3, (now - r.arrived) * 1e3)
         else:
             self.metrics.obs("tpot", (now - r.last_token_at) * 1e3)
+            if self.overload is not None and self.cfg.tbt_target_ms > 0:
+                self.overload.record((now - r.last_token_at) * 1e3 <= 1.5 * self.cfg.tbt_target_ms)
         r.last_token_at = now
         r.generated.append(tok)
         self.metrics.inc("generation_tokens")

@@ -37,7 +37,8 @@ class ApiError(Exception):
 
 
 def _envelope(e: ApiError) -> JSONResponse:
-    return JSONResponse(status_code=e.status, content={"error": {"message": e.message, "type": e.typ, "code": e.code}})
+    headers = {"Retry-After": str(getattr(e, "retry_after", 1))} if e.status == 429 else None
+    return JSONResponse(status_code=e.status, content={"error": {"message": e.message, "type": e.typ, "code": e.code}}, headers=headers)
 
 
 def _gen_params(body: dict, default_max: int) -> GenParams:
