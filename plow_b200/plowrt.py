@@ -159,10 +159,19 @@ def cmd_simulate(args) -> int:
 
 
 def cmd_inventory(args) -> int:
+    """Opcodes of a packet by class, which backend has a body for each (the audit refuses what neither classifies), and the
+    counter report of every program (dead counters, redundant waits, dependency depth)."""
+    from .compiler import audit
     pkt = pk.read_packet(Path(args.assets) / "model.pkt" if Path(args.assets).is_dir() else args.assets)
     ops = sorted({pk.Op(i.op).name for p in pkt.programs for i in p.insts})
-    print(json.dumps(dict(opcodes=ops, must_understand=(pkt.section_json("abi.json") or {}).get("must_understand", [])), indent=1))
-    return 0
+    audits = {b: audit.audit_ops(pkt, b) for b in ("cpu", "cuda")}
+    counters = [dict(role=p.role, rows=p.rows, **audit.counter_report(p)) for p in pkt.programs]
+    for c in counters:
+        c["dead"] = len(c["dead"])
+    print(json.dumps(dict(opcodes=ops, must_understand=(pkt.section_json("abi.json") or {}).get("must_understand", []),
+                          by_class=audits["cpu"]["by_class"], missing={b: a["missing"] for b, a in audits.items()},
+                          unclassified=audits["cpu"]["unclassified"], counters=counters), indent=1))
+    return 0 if not audits["cpu"]["unclassified"] else 1
 
 
 def cmd_budget(args) -> int:

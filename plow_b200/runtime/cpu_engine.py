@@ -36,6 +36,10 @@ class CpuEngine(EngineBase):
         packet = pk.read_packet(assets / "model.pkt")
         n_pages = n_pages or max_slots * ((max_ctx + PAGE - 1) // PAGE)
         super().__init__(packet, max_slots, n_pages, max_ctx, prefix_cache)
+        from ..compiler.audit import audit_ops
+        a = audit_ops(packet, "cpu")
+        if not a["ok"]:
+            raise EngineError(f"the CPU backend has no body for {a['missing'] or a['unclassified']} (used by this packet)", fatal=True)
         lib = native.cpu_lib()
         lib.plow_pkt_open.restype = C.c_void_p
         lib.plow_pkt_open.argtypes = [C.c_char_p, C.c_char_p, C.c_int]

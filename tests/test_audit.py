@@ -1,0 +1,53 @@
+"""Opcode audit and counter report (compiler/audit.py)."""
+import re
+from pathlib import Path
+
+import pytest
+
+from plow_b200.compiler import audit, emit, graph, hwspec, packet as pk, rewrite
+from plow_b200.compiler.packet import Op
+from plow_b200.models import config
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_cpu_table_is_the_interpreters_own_dispatch():
+    src = (ROOT / "csrc" / "cpu" / "interp.cpp").read_text()
+    cases = set(re.findall(r"case PLOW_OP_([A-Z0-9_]+):", src))
+    assert {o.name for o in audit.CPU_OPS} == cases
+    # every opcode of the ABI belongs to exactly one class
+    for o in Op:
+        assert sum(o in ops for ops in audit.CLASSES.values()) == 1, o.name
+    assert audit.op_class(Op.GEMM) == "gemm" and audit.op_class(Op.XA2A_COMBINE) == "collective" and audit.op_class(200) is None
+
+
+def test_audit_and_counter_report_on_real_packets(tiny_assets, capsys):
+    from plow_b200 import plowrt
+    from plow_b200.runtime.cpu_engine import CpuEngine
+    from plow_b200.runtime.engine import EngineError
+    pkt = pk.read_packet(tiny_assets / "assets" / "model.pkt")
+    a = audit.audit_ops(pkt, "cpu")
+    assert a["ok"] and a["used"]["GEMM"] > 0 and a["by_class"]["attention"] == ["ATTN"] and a["by_class"]["collective"] == []
+    g = audit.audit_ops(pkt, "cuda")
+    assert g["ok"], g["missing"]
+    # a tensor-parallel packet: its collectives have sm_100a bodies and no CPU ones
+    spec = config.spec_from_config(config.dense_8b_config())
+    gr = graph.build_graph(spec, tp=2)
+    rewrite.fuse(gr)
+    tp = emit.emit_packet(gr, [], hwspec.lookup("b200"), 148, dict(prefill=[128], decode=[8], max_seqs=8))
+    assert audit.audit_ops(tp, "cuda")["ok"]
+    c = audit.audit_ops(tp, "cpu")
+    assert not c["ok"] and set(c["missing"]) <= {"XREDUCE", "XREDUCE_ADD_NORM", "GEMM_XREDUCE", "XARGMAX_FIN", "XGATHER"} and c["missing"]
+    # an opcode nobody classifies is refused, and the CPU engine refuses such a packet at load instead of mid-step
+    p0 = pkt.programs[0]
+    old = p0.insts[3].op
+    p0.insts[3].op = 200
+    assert audit.audit_ops(pkt, "cpu")["unclassified"] == [200]
+    p0.insts[3].op = old
+    # counter report: one counter per instruction that ran, most of them waited on, depth about the layer chain
+    r = audit.counter_report(p0)
+    assert r["counters"] == len(p0.insts) and r["waited"] >= r["counters"] - 1 - len(r["dead"]) and r["dependency_depth"] >= 10
+    assert all(0 <= d < len(p0.insts) - 1 for d in r["dead"])
+    assert plowrt.main(["inventory", str(tiny_assets / "assets")]) == 0
+    out = capsys.readouterr().out
+    assert '"missing"' in out and '"dependency_depth"' in out
