@@ -52,7 +52,14 @@ def compile_dir(hf_dir, out_dir, gpu="b200", arch="sm_100a", num_gpus=1, paralle
         g = graph.build_graph(spec, tp=tp, ep=ep, rank=rank, emit_hidden=bool(mtp))
         n_prim = len(g.nodes)
         sites = rewrite.fuse(g, disable=set(disable_rules))
-        pkt = emit.emit_packet(g, sites, hw, n_cu, buckets, rank=rank)
+        extra = None
+        if mtp or spec.role == "mtp":
+            # spec.json: what a runtime needs to pair a decoder packet with its drafter (reference: crates/plow-asset/src/spec_draft.rs)
+            extra = {"spec.json": json.dumps(dict(
+                kind="mtp", role=spec.role, hidden=spec.hidden, drafter_packet="mtp/model.pkt" if spec.role == "main" else None,
+                module_layer=(spec.n_layers if spec.role == "main" else spec.name_base), modules=spec.mtp_layers if spec.role == "main" else 1,
+                hidden_output="out.hidden", hidden_rows="rows" if spec.role == "main" else "samples", default_depth=3)).encode()}
+        pkt = emit.emit_packet(g, sites, hw, n_cu, buckets, extra_sections=extra, rank=rank)
         checks = verify.verify_packet(pkt)
         if not checks["ok"]:
             raise RuntimeError(f"verifier refused the packet: {checks['failures']}")   # nothing is written

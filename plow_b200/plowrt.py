@@ -47,6 +47,9 @@ def make_entry(name, assets, cfg):
     mux = ModelMux(eng, tok, sched)
     mtp_dir = Path(assets) / "mtp"
     if cfg.spec_depth > 0 and cfg.spec_drafter != "ngram":
+        pairing = eng.packet.section_json("spec.json") or {}
+        if pairing.get("kind") == "mtp" and pairing.get("drafter_packet"):
+            mtp_dir = (Path(assets) / pairing["drafter_packet"]).parent
         if (mtp_dir / "model.pkt").exists():
             # the prediction module runs in an engine of its own (own KV pages, same device) behind the chain drafter
             from .runtime.spec import MtpDrafter

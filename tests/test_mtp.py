@@ -28,6 +28,11 @@ def _build(tmp, cfg):
     rep = plowc.compile_dir(tmp / "ckpt", tmp / "assets", arch="cpu", n_cu=4, max_rows=128, decode_rungs=[1, 2, 4, 8], max_seqs=8,
                             mtp=True)
     assert rep["mtp"]["ranks"][0]["verify"]["ok"] and (tmp / "assets" / "mtp" / "model.pkt").exists()
+    from plow_b200.compiler import packet as pk
+    main_s = pk.read_packet(tmp / "assets" / "model.pkt").section_json("spec.json")
+    draft_s = pk.read_packet(tmp / "assets" / "mtp" / "model.pkt").section_json("spec.json")
+    assert main_s["kind"] == "mtp" and main_s["drafter_packet"] == "mtp/model.pkt" and main_s["hidden_rows"] == "rows"
+    assert draft_s["role"] == "mtp" and draft_s["hidden_rows"] == "samples" and draft_s["module_layer"] == main_s["module_layer"] == cfg["num_hidden_layers"]
     state = {}
     for f in glob.glob(str(tmp / "ckpt" / "*.safetensors")):
         state.update(load_file(f))
