@@ -39,14 +39,16 @@ typedef enum PlowOp {
   PLOW_OP_RMSNORM = 2,        /* t0=out t1=x t2=gamma(opt) ; f0=eps i0=H i1=gamma_mode(0 g,1 1+g) */
   PLOW_OP_ADD_NORM = 3,       /* t0=out t1=resid(in/out) t2=delta t3=gamma ; resid+=delta; out=norm(resid) */
   PLOW_OP_GEMM = 4,           /* t0=y t1=x t2=w t3=resid(opt) t4=sx t5=sw ; i0=N i1=K i2=flags */
-  PLOW_OP_ROPE_KV = 5,        /* t0=q(in/out) t1=k t2=v t3=kcache t4=vcache t5=qnorm t6=knorm t7=rope tbl
-                                 i0=nq i1=nkv i2=hd i3=rot_dim i4=pair_mode i5=layer ; f0=eps */
-  PLOW_OP_ATTN = 6,           /* t0=out t1=q t2=kcache t3=vcache ; i0=nq i1=nkv i2=hd i3=window i4=mode i5=layer; f0=scale */
+  PLOW_OP_ROPE_KV = 5,        /* t0=q out t1=fused qkv rows t2=kcache t3=vcache t4=qnorm(opt) t5=knorm(opt) t6=rope table
+                                 t7=gate out (i7=1: query heads are [Q | gate] pairs) or the e4m3 cache's scales [P,64,2*nkv]
+                                 i0=nq i1=nkv i2=hd i3=rot_dim i4=pair_mode i5=layer i6=gamma_mode i7=gated ; f0=eps */
+  PLOW_OP_ATTN = 6,           /* t0=out t1=q t2=kcache t3=vcache t4=e4m3 cache scales (opt) ;
+                                 i0=nq i1=nkv i2=hd i3=window i4=mode i5=layer; f0=scale */
   PLOW_OP_ROW_GATHER = 7,     /* t0=out[nsample,H] t1=x t2=in.sample_rows */
   PLOW_OP_ARGMAX = 8,         /* t0=out.ids t1=logits ; i0=V */
   PLOW_OP_SAMPLE = 9,         /* t0=out.ids t1=logits t2=in.sampling ; i0=V */
   PLOW_OP_RESIDUAL = 10,      /* t0=out t1=a t2=b */
-  PLOW_OP_GLU = 11,           /* t0=out t1=gate_up ; i0=F i1=act */
+  PLOW_OP_GLU = 11,           /* t0=out t1=gate t2=up ; i0=activation (0 silu, PLOW_GEMM_ACT_GELU_*) : out = act(gate) * up */
   PLOW_OP_QUANT_ACT = 12,     /* t0=q t1=scales t2=x ; i0=K */
   /* MLA */
   PLOW_OP_MLA_KV_WRITE = 20,  /* latent norm + k_rope rope + cache write */
