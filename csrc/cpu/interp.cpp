@@ -62,8 +62,12 @@ std::string validate(Pkt& p) {
     if (p.tensors[i].name_ofs >= h.strtab_bytes) return "tensor name out of range";
     if (p.tensors[i].rank > 4) return "tensor rank > 4";
   }
+  // the activation arena is allocated from this field: no program may need more than it says, and it may not say more
+  // than any host could hold (a flipped high byte would otherwise turn into an allocation failure at engine creation)
+  if (h.act_arena_bytes > (uint64_t(1) << 40)) return "activation arena size is not plausible";
   for (uint32_t k = 0; k < h.n_program; ++k) {
     const PlowProgramEnt& g = p.programs[k];
+    if (g.arena_bytes > h.act_arena_bytes) return "a program's arena exceeds the packet's arena size";
     if (!in_range(p, g.inst_ofs, uint64_t(g.n_inst) * sizeof(PlowInst))) return "inst range";
     if (!in_range(p, g.stream_ofs, uint64_t(g.n_stream) * sizeof(PlowStreamEnt))) return "stream range";
     if (!in_range(p, g.cu_ofs, uint64_t(g.n_cu + 1) * 4)) return "cu_ofs range";
@@ -88,6 +92,23 @@ std::string validate(Pkt& p) {
       if (uint32_t(st[s].slice0) + st[s].nslice > insts[st[s].inst].nslice) return "slice range exceeds instruction";
       if (uint64_t(st[s].wait_ofs) + st[s].n_wait > g.n_wait) return "wait range out of bounds";
       if (uint64_t(st[s].succ_ofs) + st[s].n_succ > g.n_succ) return "succ range out of bounds";
+    }
+    // every activation the program places must lie inside its arena (sampled-row dims counted as one row: a lower bound
+    // that still catches an offset or a dimension that points nowhere)
+    const uint64_t* actmap = reinterpret_cast<const uint64_t*>(p.raw.data() + g.actmap_ofs);
+    static const uint64_t kEs[] = {4, 2, 2, 1, 4, 1, 8};
+    for (uint32_t t = 0; t < h.n_tensor; ++t) {
+      const PlowTensorEnt& te = p.tensors[t];
+      if (te.tclass != PLOW_TC_ACT || actmap[t] == UINT64_MAX) continue;
+      if (te.dtype >= sizeof(kEs) / sizeof(kEs[0])) return "unknown dtype";
+      unsigned __int128 nb = kEs[te.dtype];
+      for (int d = 0; d < te.rank; ++d) {
+        const int64_t v = te.dims[d];
+        if (v == 0 || v < -4) return "tensor dimension out of range";
+        nb *= v == -1 ? uint64_t(g.rows) : v < 0 ? uint64_t(1) : uint64_t(v);
+        if (nb > (unsigned __int128)(uint64_t(1) << 42)) return "activation size is not plausible";
+      }
+      if (actmap[t] > g.arena_bytes || uint64_t(nb) > g.arena_bytes - actmap[t]) return "activation lies outside the arena";
     }
     for (uint32_t w = 0; w < g.n_wait; ++w)
       if (waits[w].ctr >= g.n_ctr) return "wait counter out of range";
@@ -993,14 +1014,23 @@ void* plow_pkt_open(const char* path, char* err, int errlen) {
   std::fseek(f, 0, SEEK_END);
   long n = std::ftell(f);
   std::fseek(f, 0, SEEK_SET);
-  Pkt* p = new Pkt;
-  p->raw.resize(n);
-  const size_t got = std::fread(p->raw.data(), 1, n, f);
-  std::fclose(f);
-  if (got != size_t(n)) { std::snprintf(err, errlen, "short read"); delete p; return nullptr; }
-  const std::string e = validate(*p);
-  if (!e.empty()) { std::snprintf(err, errlen, "%s", e.c_str()); delete p; return nullptr; }
-  return p;
+  Pkt* p = nullptr;
+  try {
+    p = new Pkt;
+    p->raw.resize(n < 0 ? 0 : n);
+    const size_t got = std::fread(p->raw.data(), 1, p->raw.size(), f);
+    std::fclose(f);
+    f = nullptr;
+    if (got != p->raw.size()) { std::snprintf(err, errlen, "short read"); delete p; return nullptr; }
+    const std::string e = validate(*p);
+    if (!e.empty()) { std::snprintf(err, errlen, "%s", e.c_str()); delete p; return nullptr; }
+    return p;
+  } catch (const std::exception& ex) {
+    if (f) std::fclose(f);
+    delete p;
+    std::snprintf(err, errlen, "cannot load the packet: %s", ex.what());
+    return nullptr;
+  }
 }
 void plow_pkt_close(void* p) { delete static_cast<Pkt*>(p); }
 int plow_pkt_n_tensor(void* p) { return static_cast<Pkt*>(p)->hdr->n_tensor; }
@@ -1010,14 +1040,29 @@ const char* plow_pkt_tensor_name(void* p, int i) {
   return k->strtab + k->tensors[i].name_ofs;
 }
 
+// null when the host cannot hold the packet's arena or start its threads (nothing is thrown across the C boundary)
 void* plow_cpu_engine_create(void* pkt, int n_threads) {
-  Engine* e = new Engine;
-  e->pkt = static_cast<Pkt*>(pkt);
-  e->n_threads = n_threads < 1 ? 1 : n_threads;
-  e->bound.assign(e->pkt->hdr->n_tensor, nullptr);
-  e->arena.resize(e->pkt->hdr->act_arena_bytes + 256);
-  for (int t = 0; t < e->n_threads; ++t) e->workers.emplace_back(worker_main, e, t);
-  return e;
+  Engine* e = nullptr;
+  try {
+    e = new Engine;
+    e->pkt = static_cast<Pkt*>(pkt);
+    e->n_threads = n_threads < 1 ? 1 : n_threads;
+    e->bound.assign(e->pkt->hdr->n_tensor, nullptr);
+    e->arena.resize(e->pkt->hdr->act_arena_bytes + 256);
+    for (int t = 0; t < e->n_threads; ++t) e->workers.emplace_back(worker_main, e, t);
+    return e;
+  } catch (const std::exception&) {
+    if (e) {
+      {
+        std::lock_guard<std::mutex> lk(e->mu);
+        e->quit = true;
+      }
+      e->cv_start.notify_all();
+      for (auto& w : e->workers) w.join();
+      delete e;
+    }
+    return nullptr;
+  }
 }
 void plow_cpu_engine_destroy(void* h) {
   Engine* e = static_cast<Engine*>(h);

@@ -58,6 +58,9 @@ class CpuEngine(EngineBase):
             raise EngineError(f"packet rejected: {err.value.decode()}", fatal=True)
         n_threads = n_threads or min(packet.n_cu, os.cpu_count() or 1)
         self._eng = lib.plow_cpu_engine_create(self._pkt, n_threads)
+        if not self._eng:
+            lib.plow_pkt_close(self._pkt)
+            raise EngineError("the CPU engine could not allocate the packet's activation arena", fatal=True)
         self._keep: dict[int, object] = {}
         self._bind_all(assets)
 
