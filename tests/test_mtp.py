@@ -190,3 +190,54 @@ def test_scheduler_drafts_with_the_prediction_module(tmp_path):
     assert left == {}                                                                 # finished requests gave the drafter's slots back
     twice, c2, left = run(3, again=True)
     assert twice[:2] == plain and twice[2:] == plain and left == {}
+
+
+@pytest.mark.parametrize("n_pages", [48, 6])
+def test_randomised_workload_with_the_drafter_keeps_every_invariant(tmp_path, n_pages):
+    """Nine requests of mixed lengths against four slots (and, with 6 pages, against a KV pool that holds two long prompts at most): with the
+    prediction-module drafter on, tokens equal the plain run, every request ends once, and both engines get all their
+    slots and pages back."""
+    from plow_b200.models import config
+    from plow_b200.runtime.scheduler import GenParams, ModelMux, SchedConfig
+    from plow_b200.text.tokenizer import ByteTokenizer
+    cfg = dict(config.tiny_dense_config(), num_nextn_predict_layers=1)
+    _build(tmp_path, cfg)
+    rng = np.random.default_rng(11)
+    plan = sorted(((int(rng.integers(0, 20)), rng.integers(0, 32000, int(rng.integers(8, 150))).tolist(), int(rng.integers(2, 12)))
+                   for _ in range(9)), key=lambda x: x[0])
+
+    def run(depth):
+        eng = CpuEngine(tmp_path / "assets", max_slots=4, max_ctx=512, n_pages=n_pages, prefix_cache=False)
+        mux = ModelMux(eng, ByteTokenizer(), SchedConfig(token_budget=128, reserve_tokens=0, spec_depth=depth), eos_ids=[])
+        dr = None
+        if depth:
+            dr = CpuEngine(tmp_path / "assets" / "mtp", max_slots=4, max_ctx=512, n_pages=n_pages, prefix_cache=False)
+            mux.set_drafter(MtpDrafter(dr))
+        pending, reqs = list(plan), []
+        for t in range(4000):
+            while pending and pending[0][0] <= t:
+                _, p, mx = pending.pop(0)
+                reqs.append(mux.submit(p, GenParams(max_tokens=mx)))
+            if not mux.tick() and not pending and not mux.live and not mux.waiting:
+                break
+        outs = []
+        for r in reqs:
+            toks, done = [], 0
+            while not r.out.empty():
+                c = r.out.get_nowait()
+                if c.kind == "token":
+                    toks.append(c.token_id)
+                else:
+                    assert c.kind == "done" and c.finish_reason == "length", (c.kind, c.error)
+                    done += 1
+            assert done == 1
+            outs.append(toks)
+        for e in (eng, dr):
+            if e is not None:
+                assert not e.tokens and sum(len(s.pages) for s in e.pool.seqs.values()) == 0 and e.pool.available() == n_pages
+                e.close()
+        return outs, mux.metrics.snapshot()["counters"]
+    plain, c0 = run(0)
+    spec, c1 = run(3)
+    assert plain == spec and [len(t) for t in spec] == [mx for _, _, mx in plan]
+    assert c1.get("spec_ticks", 0) >= 3
