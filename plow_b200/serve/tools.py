@@ -116,17 +116,147 @@ def parse_gptoss(text: str):
     return (final.group(1).strip() if final else ""), calls
 
 
-PARSERS = {"hermes": parse_hermes, "qwen": parse_hermes, "llama3": parse_llama3, "mistral": parse_mistral,
+def parse_qwen3_coder(text: str):
+    """<tool_call><function=NAME><parameter=k>v</parameter>…</function></tool_call>  (Qwen3-Coder XML form)"""
+    calls = []
+    for m in re.finditer(r"<function=([\w.\-]+)>(.*?)</function>", text, re.S):
+        args = {}
+        for k, v in re.findall(r"<parameter=([\w.\-]+)>\n?(.*?)\n?</parameter>", m.group(2), re.S):
+            try:
+                args[k] = json.loads(v)
+            except json.JSONDecodeError:
+                args[k] = v
+        calls.append(_call(m.group(1), args))
+    if not calls:
+        return None
+    head = re.sub(r"<tool_call>.*?</tool_call>|<function=.*?</function>", "", text, flags=re.S)
+    return head.strip(), calls
+
+
+def _py_value(node):
+    import ast
+    if isinstance(node, ast.Constant):
+        return node.value
+    if isinstance(node, (ast.List, ast.Tuple)):
+        return [_py_value(e) for e in node.elts]
+    if isinstance(node, ast.Dict):
+        return {_py_value(k): _py_value(v) for k, v in zip(node.keys, node.values)}
+    if isinstance(node, ast.UnaryOp) and isinstance(node.op, ast.USub):
+        return -_py_value(node.operand)
+    if isinstance(node, ast.Name) and node.id in ("true", "false", "null", "True", "False", "None"):
+        return {"true": True, "false": False, "null": None, "True": True, "False": False, "None": None}[node.id]
+    raise ValueError("not a literal")
+
+
+def parse_pythonic(text: str):
+    """[get_weather(city="Paris", days=3), other(x=[1, 2])]  (Llama 4 / pythonic tool calls: a list of call expressions)"""
+    import ast
+    body = text.strip().replace("<|python_start|>", "").replace("<|python_end|>", "").strip()
+    if not (body.startswith("[") and body.endswith("]")):
+        return None
+    try:
+        tree = ast.parse(body, mode="eval").body
+        if not isinstance(tree, ast.List) or not tree.elts:
+            return None
+        calls = []
+        for e in tree.elts:
+            if not isinstance(e, ast.Call) or e.args:
+                return None
+            name = ast.unparse(e.func)
+            calls.append(_call(name, {kw.arg: _py_value(kw.value) for kw in e.keywords}))
+    except (SyntaxError, ValueError):
+        return None
+    return "", calls
+
+
+def parse_granite(text: str):
+    """<|tool_call|>[{"name": ..., "arguments": {...}}]  or  <tool_call>[...]  (Granite 3.x)"""
+    for tag in ("<|tool_call|>", "<tool_call>["):
+        if tag in text:
+            head, body = text.split(tag, 1)
+            body = ("[" + body) if tag.endswith("[") else body
+            try:
+                obj, _ = json.JSONDecoder().raw_decode(body.strip())
+            except json.JSONDecodeError:
+                return None
+            calls = _json_calls(obj)
+            return (head.strip(), calls) if calls else None
+    return None
+
+
+def parse_phi4(text: str):
+    """functools[{"name": ..., "arguments": {...}}, ...]  (Phi-4-mini)"""
+    if "functools[" not in text:
+        return None
+    head, body = text.split("functools", 1)
+    try:
+        obj, _ = json.JSONDecoder().raw_decode(body.strip())
+    except json.JSONDecodeError:
+        return None
+    calls = _json_calls(obj)
+    return (head.strip(), calls) if calls else None
+
+
+def parse_minimax(text: str):
+    """<tool_calls>\n{"name": ..., "arguments": {...}}\n{...}\n</tool_calls>  (MiniMax: one JSON object per line)"""
+    m = re.search(r"<tool_calls>\s*(.*?)\s*</tool_calls>", text, re.S)
+    if not m:
+        return None
+    calls = []
+    for line in m.group(1).splitlines():
+        line = line.strip()
+        if not line:
+            continue
+        try:
+            calls += _json_calls(json.loads(line))
+        except json.JSONDecodeError:
+            return None
+    return (text[:m.start()] + text[m.end():]).strip(), calls if calls else None
+
+
+def parse_internlm(text: str):
+    """<|action_start|><|plugin|>{"name": ..., "parameters": {...}}<|action_end|>  (InternLM 2.5 / 3)"""
+    calls = []
+    for m in re.finditer(r"<\|action_start\|><\|plugin\|>\s*(.*?)\s*<\|action_end\|>", text, re.S):
+        try:
+            calls += _json_calls(json.loads(m.group(1)))
+        except json.JSONDecodeError:
+            return None
+    return (text.split("<|action_start|>", 1)[0].strip(), calls) if calls else None
+
+
+def parse_json_list(text: str):
+    """A bare JSON list of {"name", "arguments"} objects, optionally fenced  (xLAM, Jamba, Hunyuan-style plain JSON)"""
+    body = text.strip()
+    m = re.fullmatch(r"```(?:json)?\s*(.*?)\s*```", body, re.S)
+    if m:
+        body = m.group(1)
+    if not body.startswith("["):
+        return None
+    try:
+        obj = json.loads(body)
+    except json.JSONDecodeError:
+        return None
+    calls = _json_calls(obj) if isinstance(obj, list) and all(isinstance(o, dict) and "name" in o for o in obj) else []
+    return ("", calls) if calls else None
+
+
+PARSERS = {"qwen3_coder": parse_qwen3_coder, "pythonic": parse_pythonic, "llama4": parse_pythonic, "granite": parse_granite,
+           "phi4": parse_phi4, "minimax": parse_minimax, "internlm": parse_internlm, "json": parse_json_list, "xlam": parse_json_list,
+           "hermes": parse_hermes, "qwen": parse_hermes, "llama3": parse_llama3, "mistral": parse_mistral,
            "deepseek": parse_deepseek, "glm": parse_glm, "kimi": parse_kimi, "gptoss": parse_gptoss}
 
 FAMILY_OF_MODEL_TYPE = {"llama": "llama3", "qwen2": "hermes", "qwen3": "hermes", "qwen3_moe": "hermes", "qwen3_next": "hermes",
                         "mistral": "mistral", "mixtral": "mistral", "deepseek_v3": "deepseek", "glm_moe_dsa": "glm", "glm4_moe": "glm",
-                        "kimi_k2": "kimi", "gpt_oss": "gptoss"}
+                        "kimi_k2": "kimi", "gpt_oss": "gptoss", "llama4": "pythonic", "granite": "granite", "phi3": "phi4",
+                        "minimax": "minimax", "internlm2": "internlm", "internlm3": "internlm"}
 
 
 def extract_tool_calls(text: str, family: str | None = None):
     """(content, tool_calls): with a family, only that parser; otherwise the first parser that recognises the text."""
-    order = [PARSERS[family]] if family in PARSERS else [parse_deepseek, parse_kimi, parse_gptoss, parse_mistral, parse_glm, parse_hermes, parse_llama3]
+    order = [PARSERS[family]] if family in PARSERS else [parse_deepseek, parse_kimi, parse_gptoss, parse_mistral, parse_granite, parse_phi4,
+                                                         parse_minimax, parse_internlm, parse_qwen3_coder, parse_glm, parse_hermes,
+                                                         parse_llama3, parse_pythonic, parse_json_list]
     for p in order:
         r = p(text)
         if r is not None:

@@ -70,3 +70,33 @@ def test_json_prefix_recogniser_and_guided_pick():
         text += vocab[tok]
     import json
     assert isinstance(json.loads(text), dict), text
+
+
+def test_more_tool_call_families():
+    import json
+    from plow_b200.serve import tools as t
+
+    def args(c):
+        return json.loads(c["function"]["arguments"])
+    content, calls = t.extract_tool_calls('I will look.\n<tool_call>\n<function=get_weather>\n<parameter=city>\nParis\n</parameter>\n<parameter=days>\n3\n</parameter>\n</function>\n</tool_call>', "qwen3_coder")
+    assert content == "I will look." and calls[0]["function"]["name"] == "get_weather" and args(calls[0]) == {"city": "Paris", "days": 3}
+    content, calls = t.extract_tool_calls('[get_weather(city="Paris", days=3), lookup(ids=[1, 2], exact=True, opts={"k": -1.5})]', "pythonic")
+    assert content == "" and [c["function"]["name"] for c in calls] == ["get_weather", "lookup"]
+    assert args(calls[1]) == {"ids": [1, 2], "exact": True, "opts": {"k": -1.5}}
+    assert t.parse_pythonic("[1, 2, 3]") is None and t.parse_pythonic("[f(1)]") is None and t.parse_pythonic("[os.system('x')") is None
+    content, calls = t.extract_tool_calls('<|tool_call|>[{"name": "f", "arguments": {"a": 1}}]', "granite")
+    assert content == "" and args(calls[0]) == {"a": 1}
+    content, calls = t.extract_tool_calls('Sure. functools[{"name": "f", "arguments": {"a": 1}}, {"name": "g", "arguments": {}}]', "phi4")
+    assert content == "Sure." and len(calls) == 2
+    content, calls = t.extract_tool_calls('ok\n<tool_calls>\n{"name": "f", "arguments": {"a": 1}}\n{"name": "g", "arguments": {"b": "x"}}\n</tool_calls>', "minimax")
+    assert content == "ok" and args(calls[1]) == {"b": "x"}
+    content, calls = t.extract_tool_calls('thinking<|action_start|><|plugin|>{"name": "f", "parameters": {"a": 1}}<|action_end|>', "internlm")
+    assert content == "thinking" and args(calls[0]) == {"a": 1}
+    content, calls = t.extract_tool_calls('```json\n[{"name": "f", "arguments": {"a": 1}}]\n```', "xlam")
+    assert content == "" and calls[0]["function"]["name"] == "f"
+    # without a family the text itself decides, and plain prose stays prose
+    for text, name in (('functools[{"name": "f", "arguments": {}}]', "f"), ('[g(x=1)]', "g"),
+                       ('<|action_start|><|plugin|>{"name": "h", "parameters": {}}<|action_end|>', "h")):
+        assert t.extract_tool_calls(text)[1][0]["function"]["name"] == name
+    assert t.extract_tool_calls("The list [1, 2, 3] has three items.") == ("The list [1, 2, 3] has three items.", [])
+    assert len(set(t.PARSERS.values())) >= 14
