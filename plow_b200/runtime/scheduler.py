@@ -250,7 +250,7 @@ class ModelMux:
         if self.overload is not None and not self.overload.admit(params.session_id is not None and params.session_id in self.retained):
             self.metrics.inc("requests_shed")
             self.metrics.inc("overload_refused")
-            req.out.put(Chunk("error", error="overloaded", finish_reason="overloaded"))
+            req.out.put(Chunk("error", error="overloaded", finish_reason="overloaded", usage=dict(retry_after_s=self.overload.retry_after_s())))
             return req
         if len(prompt) + 1 > self.engine.max_ctx:
             req.out.put(Chunk("error", error="context_length_exceeded", finish_reason="error"))

@@ -269,7 +269,9 @@ def create_app(state: AppState) -> FastAPI:
                 return "".join(text), toks, lps, ch.finish_reason, ch.usage
             else:
                 if ch.error == "overloaded" or ch.finish_reason == "overloaded":
-                    raise ApiError(429, "server is overloaded", "rate_limit_error", "overloaded")
+                    e = ApiError(429, "server is overloaded", "rate_limit_error", "overloaded")
+                    e.retry_after = int((ch.usage or {}).get("retry_after_s", 1))
+                    raise e
                 if ch.error == "context_length_exceeded":
                     raise ApiError(400, "context length exceeded", code="context_length_exceeded")
                 raise ApiError(503 if "dead" in (ch.error or "") else 500, ch.error or "generation failed", "server_error", "engine_error")

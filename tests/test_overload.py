@@ -96,7 +96,7 @@ def test_scheduler_and_api_follow_the_level(tiny_assets):
             assert oc.fraction()[1] >= 2                   # token gaps were recorded against the (huge) objective: all met
             oc.level = 3
             r = c.post("/v1/completions", json=body)
-            assert r.status_code == 429 and r.headers.get("retry-after") and r.json()["error"]["code"] == "overloaded"
+            assert r.status_code == 429 and r.headers.get("retry-after") == "5" and r.json()["error"]["code"] == "overloaded"
             assert mux.metrics.snapshot()["counters"]["overload_refused"] == 1
             oc.level = 2
             assert c.post("/v1/completions", json=body).status_code == 200
