@@ -179,9 +179,16 @@ def _decoder_layer(g: Graph, li: int, p: str, x: str, layer) -> str:
         o = _gdn_attention(g, li, p, h, layer.attn)
     if tp > 1:
         o = _xreduce(g, o, li)
+    if spec.sandwich_norms:
+        # four norms per layer: the attention output is normed before it joins the residual, and the MLP reads a norm of
+        # its own (pre_feedforward) and is normed again behind (post_feedforward)
+        on = g.tmp("h", (R, H))
+        g.add("rmsnorm", [o, g.weight(f"{p}.post_attention_layernorm.weight", (H,), dtype=ndt)], [on], layer=li, eps=spec.rms_eps,
+              plus_one=spec.norm_plus_one)
+        o = on
     x2 = g.tmp("x", (R, H))
     g.add("add", [x, o], [x2], layer=li)
-    ln2 = g.weight(f"{p}.post_attention_layernorm.weight", (H,), dtype=ndt)
+    ln2 = g.weight(f"{p}.{'pre_feedforward' if spec.sandwich_norms else 'post_attention'}_layernorm.weight", (H,), dtype=ndt)
     h2 = g.tmp("h", (R, H))
     g.add("rmsnorm", [x2, ln2], [h2], layer=li, eps=spec.rms_eps, plus_one=spec.norm_plus_one)
     if layer.ffn.kind == "dense":
@@ -190,6 +197,11 @@ def _decoder_layer(g: Graph, li: int, p: str, x: str, layer) -> str:
             d = _xreduce(g, d, li)
     else:
         d = _moe_ffn(g, li, f"{p}.{layer.ffn.block}", h2, layer.ffn)
+    if spec.sandwich_norms:
+        dn = g.tmp("h", (R, H))
+        g.add("rmsnorm", [d, g.weight(f"{p}.post_feedforward_layernorm.weight", (H,), dtype=ndt)], [dn], layer=li, eps=spec.rms_eps,
+              plus_one=spec.norm_plus_one)
+        d = dn
     x3 = g.tmp("x", (R, H))
     g.add("add", [x2, d], [x3], layer=li)
     return x3
@@ -231,8 +243,13 @@ def _gqa_attention(g: Graph, li, p, h, a) -> str:
         g.add("headnorm", [q, qn], [q2], layer=li, heads=nq, head_dim=hd, eps=spec.rms_eps, plus_one=spec.norm_plus_one)
         g.add("headnorm", [k, kn], [k2], layer=li, heads=nkv, head_dim=hd, eps=spec.rms_eps, plus_one=spec.norm_plus_one)
         q, k = q2, k2
-    rope = g.value("gen.rope", (spec.rope.max_pos, max(2, spec.rope.rot_dim)), "f32", "gen",
-                   meta=dict(theta=spec.rope.theta, rot_dim=spec.rope.rot_dim, scaling=spec.rope.scaling))
+    if a.rope_theta and a.rope_theta != spec.rope.theta:
+        # a layer with a rotary base of its own (no scaling: the long-context scaling belongs to the global layers)
+        rope = g.value("gen.rope.local", (spec.rope.max_pos, max(2, spec.rope.rot_dim)), "f32", "gen",
+                       meta=dict(theta=a.rope_theta, rot_dim=spec.rope.rot_dim, scaling=None))
+    else:
+        rope = g.value("gen.rope", (spec.rope.max_pos, max(2, spec.rope.rot_dim)), "f32", "gen",
+                       meta=dict(theta=spec.rope.theta, rot_dim=spec.rope.rot_dim, scaling=spec.rope.scaling))
     qr, kr = g.tmp("q", (R, nq * hd)), g.tmp("k", (R, nkv * hd))
     g.add("rope", [q, rope, "in.pos"], [qr], layer=li, heads=nq, head_dim=hd, rot_dim=spec.rope.rot_dim, pair_mode=spec.rope.pair_mode)
     g.add("rope", [k, rope, "in.pos"], [kr], layer=li, heads=nkv, head_dim=hd, rot_dim=spec.rope.rot_dim, pair_mode=spec.rope.pair_mode)
@@ -244,7 +261,7 @@ def _gqa_attention(g: Graph, li, p, h, a) -> str:
     g.add("kv_write", [kr, v, "in.pos", "in.seq"], [kc, vc], layer=li, heads=nkv, head_dim=hd, kv_scales=ksc)
     ao = g.tmp("attn", (R, nq * hd))
     g.add("attention", [qr, kc, vc], [ao], layer=li, heads=nq, kv_heads=nkv, head_dim=hd, window=a.window,
-          scale=hd ** -0.5, kv_scales=ksc)
+          scale=a.scale or hd ** -0.5, kv_scales=ksc)
     if gate is not None:
         ag = g.tmp("attn", (R, nq * hd))
         g.add("sigmoid_gate", [ao, gate], [ag], layer=li)

@@ -3,7 +3,8 @@
 Families understood (by ``model_type`` / ``architectures``):
 
 * dense GQA decoders without projection biases: llama, mistral, qwen3 (per-head q/k RMSNorm), gemma (``1+γ`` norms, GELU
-  gate); qwen2 (q / k / v biases) and gemma2 / gemma3 (four norms per layer, capped logits) are refused by name;
+  gate), gemma3_text (four norms per layer, local / global layers with their own rotary base); qwen2 (q / k / v biases)
+  and gemma2 (capped logits) are refused by name;
 * MLA + MoE decoders: deepseek_v3 / deepseek_v2, kimi_k2, glm_moe_dsa (adds the DSA indexer);
 * hybrid linear-attention MoE decoders: qwen3_next (gated delta rule + gated full attention);
 * GQA + MoE decoders: qwen3_moe (per-head q/k norm, softmax router) and mixtral (experts named w1 / w3 / w2 under
@@ -37,6 +38,8 @@ class AttnSpec:
     qk_norm: bool = False
     window: int = 0               # 0 = full attention
     gated: bool = False           # per-head output gate (qwen3_next full attention)
+    scale: float = 0.0            # softmax scale when it is not head_dim^-0.5 (gemma3: query_pre_attn_scalar^-0.5)
+    rope_theta: float = 0.0       # rotary base of this layer when it differs from the model's (gemma3 local layers)
     # MLA
     q_lora: int = 0
     kv_lora: int = 0
@@ -98,6 +101,7 @@ class ModelSpec:
     max_ctx: int = 4096
     bos_token_id: int | None = None
     eos_token_ids: list = field(default_factory=list)
+    sandwich_norms: bool = False  # gemma3: a norm after the attention and after the MLP too (four norms per layer)
     mtp_layers: int = 0           # next-token-prediction modules behind the decoder stack (num_nextn_predict_layers)
     role: str = "main"            # "mtp": this spec is one prediction module compiled as a drafter of its own
     name_base: int = 0            # checkpoint index of layers[0] (model.layers.<name_base + i>)
@@ -206,9 +210,11 @@ def spec_from_config(cfg: dict) -> ModelSpec:
                          "dropping them would compute a different model")
     if mt in ("llama", "mistral", "qwen3", "gemma", "plow_dense"):
         return _dense_gqa(cfg, mt)
-    if mt in ("gemma2", "gemma3", "gemma3_text"):
-        raise ValueError(f"model_type '{mt}' is not supported: its layers carry four norms, alternate local and global attention and "
-                         "cap the attention logits; reading it as a llama-shaped model would compute something else")
+    if mt in ("gemma3_text", "gemma3"):
+        return _gemma3(cfg.get("text_config", cfg) if mt == "gemma3" else cfg, "gemma3_text")
+    if mt == "gemma2":
+        raise ValueError("model_type 'gemma2' is not supported: it caps its attention and output logits; reading it as a "
+                         "llama-shaped model would compute something else")
     if mt in ("deepseek_v3", "deepseek_v2", "kimi_k2", "glm_moe_dsa", "glm5_next", "deepseek_v32", "plow_mla_moe"):
         return _mla_moe(cfg, mt)
     if mt in ("qwen3_next", "qwen3_5", "plow_gdn_hybrid"):
@@ -279,6 +285,35 @@ def _mla_moe(cfg: dict, mt: str) -> ModelSpec:
         dtype=cfg.get("plow_dtype", "bf16"), weight_quant=_quant(cfg), kv_dtype=cfg.get("plow_kv_dtype", "fp8" if _quant(cfg) != "none" else cfg.get("plow_dtype", "bf16")),
         max_ctx=int(cfg.get("max_position_embeddings", 4096)), bos_token_id=cfg.get("bos_token_id"), eos_token_ids=_eos(cfg),
         mtp_layers=int(cfg.get("num_nextn_predict_layers") or 0))
+
+
+def _gemma3(cfg: dict, mt: str) -> ModelSpec:
+    """Gemma 3 text decoder: (1 + gamma) norms before AND after attention and MLP, per-head q / k norms, GELU-tanh gate,
+    scaled embeddings, softmax scale from query_pre_attn_scalar, five sliding-window layers (local rotary base) for every
+    global one (global base, optionally with linear scaling)."""
+    h = cfg["hidden_size"]
+    nh = cfg["num_attention_heads"]
+    nkv = cfg.get("num_key_value_heads", nh)
+    hd = cfg.get("head_dim") or 256
+    n_layers = cfg["num_hidden_layers"]
+    types = cfg.get("layer_types")
+    if not types:
+        pat = int(cfg.get("sliding_window_pattern", 6))
+        types = ["full_attention" if (i + 1) % pat == 0 else "sliding_attention" for i in range(n_layers)]
+    scale = float(cfg.get("query_pre_attn_scalar", hd)) ** -0.5
+    win = int(cfg.get("sliding_window") or 0)
+    local = AttnSpec(kind="gqa", n_heads=nh, n_kv_heads=nkv, head_dim=hd, qk_norm=True, window=win, scale=scale,
+                     rope_theta=float(cfg.get("rope_local_base_freq", 10000.0)))
+    full = AttnSpec(kind="gqa", n_heads=nh, n_kv_heads=nkv, head_dim=hd, qk_norm=True, window=0, scale=scale)
+    ffn = FfnSpec(kind="dense", inter=cfg["intermediate_size"], act=_act(dict(hidden_act=cfg.get("hidden_activation") or cfg.get("hidden_act") or "gelu_pytorch_tanh")))
+    layers = [LayerSpec(full if t == "full_attention" else local, ffn) for t in types]
+    return ModelSpec(
+        family="dense_gqa", model_type=mt, hidden=h, vocab=cfg["vocab_size"], n_layers=n_layers,
+        rms_eps=float(cfg.get("rms_norm_eps", 1e-6)), tie_embeddings=bool(cfg.get("tie_word_embeddings", True)),
+        rope=_rope_from(dict(cfg, rope_theta=cfg.get("rope_theta", 1000000.0)), hd), layers=layers, norm_plus_one=True, embed_scale=h ** 0.5,
+        sandwich_norms=True, dtype=cfg.get("plow_dtype", "bf16"), weight_quant=_quant(cfg),
+        kv_dtype=cfg.get("plow_kv_dtype", cfg.get("plow_dtype", "bf16")), max_ctx=int(cfg.get("max_position_embeddings", 4096)),
+        bos_token_id=cfg.get("bos_token_id"), eos_token_ids=_eos(cfg))
 
 
 def _gqa_moe(cfg: dict, mt: str) -> ModelSpec:

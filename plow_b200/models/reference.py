@@ -71,6 +71,7 @@ class ReferenceModel:
         self.device, self.dtype = device, dtype
         r = spec.rope
         self.rope = torch.from_numpy(rope_table(min(r.max_pos, 1 << 17), r.rot_dim, r.theta, r.scaling)).to(device)
+        self._ropes = {}             # rotary tables of layers with a base of their own
 
     def lin(self, x, name):
         return x @ self.w[name].t()
@@ -122,9 +123,15 @@ class ReferenceModel:
             o = self._mla(p, h, pos, layer.attn)
         else:
             o = self._gdn(p, h, layer.attn)
+        if spec.sandwich_norms:
+            o = rmsnorm(o, self.w[f"{p}.post_attention_layernorm.weight"], spec.rms_eps, spec.norm_plus_one)
         x = x + o
-        h = rmsnorm(x, self.w[f"{p}.post_attention_layernorm.weight"], spec.rms_eps, spec.norm_plus_one)
-        return x + (self._dense(f"{p}.mlp", h, act=layer.ffn.act) if layer.ffn.kind == "dense" else self._moe(f"{p}.{layer.ffn.block}", h, layer.ffn))
+        pre = "pre_feedforward" if spec.sandwich_norms else "post_attention"
+        h = rmsnorm(x, self.w[f"{p}.{pre}_layernorm.weight"], spec.rms_eps, spec.norm_plus_one)
+        d = self._dense(f"{p}.mlp", h, act=layer.ffn.act) if layer.ffn.kind == "dense" else self._moe(f"{p}.{layer.ffn.block}", h, layer.ffn)
+        if spec.sandwich_norms:
+            d = rmsnorm(d, self.w[f"{p}.post_feedforward_layernorm.weight"], spec.rms_eps, spec.norm_plus_one)
+        return x + d
 
     # ---- blocks --------------------------------------------------------------------------------
     def _dense(self, p, h, names="proj", act="silu"):
@@ -147,9 +154,14 @@ class ReferenceModel:
         if a.qk_norm:
             q = rmsnorm(q, self.w[f"{p}.self_attn.q_norm.weight"], spec.rms_eps, spec.norm_plus_one)
             k = rmsnorm(k, self.w[f"{p}.self_attn.k_norm.weight"], spec.rms_eps, spec.norm_plus_one)
-        q = apply_rope(q, self.rope, pos, spec.rope.rot_dim, spec.rope.pair_mode)
-        k = apply_rope(k, self.rope, pos, spec.rope.rot_dim, spec.rope.pair_mode)
-        o = causal_attention(q, k, v, a.head_dim ** -0.5, a.window).reshape(T, -1)
+        rope = self.rope
+        if a.rope_theta and a.rope_theta != spec.rope.theta:
+            if a.rope_theta not in self._ropes:
+                self._ropes[a.rope_theta] = torch.from_numpy(rope_table(min(spec.rope.max_pos, 1 << 17), spec.rope.rot_dim, a.rope_theta, None)).to(self.device)
+            rope = self._ropes[a.rope_theta]
+        q = apply_rope(q, rope, pos, spec.rope.rot_dim, spec.rope.pair_mode)
+        k = apply_rope(k, rope, pos, spec.rope.rot_dim, spec.rope.pair_mode)
+        o = causal_attention(q, k, v, a.scale or a.head_dim ** -0.5, a.window).reshape(T, -1)
         if gate is not None:
             o = o * torch.sigmoid(gate)
         return self.lin(o, f"{p}.self_attn.o_proj.weight")
@@ -302,6 +314,9 @@ def param_shapes(spec: ModelSpec) -> dict:
             s[f"{p}.shared_head.norm.weight"] = (H,)
         s[f"{p}.input_layernorm.weight"] = (H,)
         s[f"{p}.post_attention_layernorm.weight"] = (H,)
+        if spec.sandwich_norms:
+            s[f"{p}.pre_feedforward_layernorm.weight"] = (H,)
+            s[f"{p}.post_feedforward_layernorm.weight"] = (H,)
         if a.kind == "gqa":
             s[f"{p}.self_attn.q_proj.weight"] = (a.n_heads * a.head_dim * (2 if a.gated else 1), H)
             s[f"{p}.self_attn.k_proj.weight"] = (a.n_kv_heads * a.head_dim, H)

@@ -544,7 +544,7 @@ def test_gqa_moe_families_on_cpu_backend_match_reference(tmp_path, model_type):
 def test_gelu_gated_model_runs_on_cpu_and_unsupported_shapes_are_refused(tmp_path):
     """A gemma-style decoder (GELU-tanh gate, (1 + gamma) norms, scaled embeddings, one kv head of width 128): the gate's
     activation travels as a flag of the fused GEMM (and of the GLU row op when the fusion is off) and the logits match the
-    fp32 reference.  Model types whose layers this compiler would misread (gemma2 / gemma3) and unknown activations are
+    fp32 reference.  Model types whose layers this compiler would misread (gemma2, qwen2) and unknown activations are
     refused by name instead of being computed as something else."""
     import glob
     from safetensors.torch import load_file
@@ -557,7 +557,7 @@ def test_gelu_gated_model_runs_on_cpu_and_unsupported_shapes_are_refused(tmp_pat
                tie_word_embeddings=True, max_position_embeddings=1024, eos_token_id=1, plow_dtype="f32", plow_kv_dtype="f32")
     spec = config.spec_from_config(cfg)
     assert spec.layers[0].ffn.act == "gelu_tanh" and spec.norm_plus_one and spec.embed_scale == 16.0
-    for bad in (dict(cfg, model_type="gemma2"), dict(cfg, model_type="gemma3_text"), dict(cfg, hidden_act="relu2"),
+    for bad in (dict(cfg, model_type="gemma2"), dict(cfg, hidden_act="relu2"),
                 dict(cfg, model_type="qwen2"), dict(cfg, model_type="llama", hidden_act="silu", attention_bias=True)):
         with pytest.raises(ValueError, match="not supported|unsupported"):
             config.spec_from_config(bad)
@@ -638,3 +638,57 @@ def test_mla_under_yarn_scales_its_softmax(tmp_path):
     with pytest.raises(ValueError, match="topk_method"):
         config.spec_from_config(dict(cfg, n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=32, n_group=2, topk_group=1,
                                      topk_method="group_limited_greedy", first_k_dense_replace=0))
+
+
+def test_gemma3_text_model_on_cpu_backend_matches_reference(tmp_path):
+    """Gemma 3 text decoder: four (1 + gamma) norms per layer, per-head q / k norms, GELU-tanh gate, scaled embeddings,
+    softmax scale from query_pre_attn_scalar, two sliding-window layers with the local rotary base for every global layer
+    (global base with linear scaling): a prompt longer than the window, prefill and decode, against the fp32 reference."""
+    import glob
+    from safetensors.torch import load_file, save_file
+    from plow_b200 import plowc
+    from plow_b200.compiler import packet as pk
+    from plow_b200.models import config, reference
+    from plow_b200.runtime.engine import TokenBatch
+    cfg = dict(model_type="gemma3_text", hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64, num_hidden_layers=6,
+               intermediate_size=512, hidden_activation="gelu_pytorch_tanh", rms_norm_eps=1e-6, rope_theta=1000000.0,
+               rope_local_base_freq=10000.0, rope_scaling=dict(rope_type="linear", factor=8.0), sliding_window=32, sliding_window_pattern=3,
+               query_pre_attn_scalar=128, vocab_size=512, max_position_embeddings=1024, eos_token_id=1, plow_dtype="f32", plow_kv_dtype="f32")
+    spec = config.spec_from_config(cfg)
+    assert spec.sandwich_norms and spec.norm_plus_one and spec.tie_embeddings and spec.embed_scale == 16.0
+    assert [l.attn.window for l in spec.layers] == [32, 32, 0, 32, 32, 0] and spec.layers[0].attn.rope_theta == 10000.0
+    assert spec.layers[2].attn.rope_theta == 0.0 and spec.layers[0].attn.scale == pytest.approx(128 ** -0.5)
+    wrapped = config.spec_from_config(dict(model_type="gemma3", text_config=cfg))        # the multimodal wrapper's text part
+    assert wrapped.n_layers == 6 and wrapped.sandwich_norms
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=0)
+    state = {}
+    for f in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        state.update(load_file(f))
+    assert "model.layers.3.pre_feedforward_layernorm.weight" in state and "model.layers.3.post_feedforward_layernorm.weight" in state
+    state = {k: (v + 0.1 * torch.randn_like(v) if k.endswith("norm.weight") else v).float() for k, v in state.items()}
+    for f in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        save_file({k: state[k] for k in load_file(f)}, f)
+    ref = reference.ReferenceModel(spec, state)
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", arch="cpu", n_cu=4, max_rows=128, decode_rungs=[1], max_seqs=4)
+    pkt = pk.read_packet(tmp_path / "assets" / "model.pkt")
+    gens = {t.name for t in pkt.tensors if t.tclass == pk.TClass.GEN}
+    assert gens == {"gen.rope", "gen.rope.local"}
+    assert {i.i[3] for i in pkt.programs[0].insts if i.op == pk.Op.ATTN} == {0, 32}
+    p = np.random.default_rng(6).integers(0, 512, 90).tolist()
+    eng = CpuEngine(tmp_path / "assets", max_slots=2, max_ctx=256)
+    eng.begin_slot(0, p)
+    eng.reserve(0, 96)
+    r = eng.step(TokenBatch(np.asarray(p, np.int32), np.arange(90, dtype=np.int32), np.zeros(90, np.int32), np.asarray([89], np.int32), want_logits=True))
+    want = ref.forward(torch.tensor(p))[-1]
+    assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 3e-4 * max(1.0, want.abs().max().item())
+    eng.commit(0, p)
+    cur = list(p)
+    for _ in range(2):
+        nxt = int(ref.forward(torch.tensor(cur))[-1].argmax())
+        r = eng.step(TokenBatch(np.asarray([nxt], np.int32), np.asarray([len(cur)], np.int32), np.zeros(1, np.int32), np.zeros(1, np.int32),
+                                decode=True, want_logits=True))
+        cur.append(nxt)
+        eng.commit(0, [nxt])
+        want = ref.forward(torch.tensor(cur))[-1]
+        assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 3e-4 * max(1.0, want.abs().max().item())
+    eng.close()
