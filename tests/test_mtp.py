@@ -241,3 +241,32 @@ def test_randomised_workload_with_the_drafter_keeps_every_invariant(tmp_path, n_
     spec, c1 = run(3)
     assert plain == spec and [len(t) for t in spec] == [mx for _, _, mx in plan]
     assert c1.get("spec_ticks", 0) >= 3
+
+
+def test_plowrt_pairs_the_drafter_through_the_packets_spec_section(tmp_path):
+    """`plowrt serve --spec-depth N` on assets compiled with `plowc --mtp`: the entry opens the drafter packet named by the
+    main packet's spec.json in an engine of its own and the scheduler drafts with it; `--spec-drafter ngram` keeps prompt
+    lookup, and asking for mtp without a drafter packet is an error."""
+    from plow_b200 import config as cfgmod, plowrt
+    from plow_b200.models import config
+    from plow_b200.runtime.scheduler import GenParams
+    _build(tmp_path, dict(config.tiny_dense_config(), num_nextn_predict_layers=1))
+    base = dict(backend="cpu", max_slots=2, max_ctx=256, spec_depth=3)
+    entry = plowrt.make_entry("tiny", tmp_path / "assets", cfgmod.RuntimeConfig.load(cli=base, env={}))
+    try:
+        d = entry.mux._drafter
+        assert isinstance(d, MtpDrafter) and d.eng.spec.role == "mtp" and d.eng.pool.enable_prefix is False
+        toks = entry.mux.generate(list(range(3, 40)), GenParams(max_tokens=6))[0]
+        assert len(toks) == 6 and entry.mux.metrics.snapshot()["counters"].get("spec_ticks", 0) >= 1
+    finally:
+        entry.mux.stop()
+    plain = plowrt.make_entry("tiny", tmp_path / "assets", cfgmod.RuntimeConfig.load(cli=dict(base, spec_drafter="ngram"), env={}))
+    try:
+        assert not isinstance(getattr(plain.mux, "_drafter", None), MtpDrafter)
+        assert plain.mux.generate(list(range(3, 40)), GenParams(max_tokens=6))[0] == toks
+    finally:
+        plain.mux.stop()
+    import shutil
+    shutil.rmtree(tmp_path / "assets" / "mtp")
+    with pytest.raises(SystemExit):
+        plowrt.make_entry("tiny", tmp_path / "assets", cfgmod.RuntimeConfig.load(cli=dict(base, spec_drafter="mtp"), env={}))
