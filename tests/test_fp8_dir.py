@@ -40,3 +40,27 @@ def test_fp8_twins_round_trip_and_are_bound_to_their_packet(tmp_path):
     idx["packet_sha256"] = "00" * 32
     idx_file.write_text(json.dumps(idx))
     assert not Fp8Dir(tmp_path / "assets", pkt)
+
+
+def test_plowc_cli_writes_twins_for_the_decoder_and_its_drafter(tmp_path, capsys):
+    from plow_b200 import plowc
+    from plow_b200.models import reference
+    from plow_b200.runtime.smoke import small_mla_moe_config
+    cfg = dict(small_mla_moe_config(hidden=512, experts=8), num_nextn_predict_layers=1)
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=0, dtype=torch.bfloat16)
+    rc = plowc.main(["--hf-dir", str(tmp_path / "ckpt"), "--out", str(tmp_path / "out"), "--max-rows", "128", "--prefill-buckets", "128",
+                     "--decode-rungs", "8", "--max-seqs", "8", "--fp8-dir", "--mtp"])
+    assert rc == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["ranks"] == 1
+    for d in (tmp_path / "out", tmp_path / "out" / "mtp"):
+        idx = json.loads((d / "fp8" / "fp8_index.json").read_text())
+        assert idx["weight_map"] and (d / "model.pkt").exists()
+    build = json.loads((tmp_path / "out" / "build.json").read_text())
+    assert build["fp8_dir"][0]["tensors"] >= 8 and build["mtp"]["fp8_dir"][0]["tensors"] >= 4
+    # the drafter's eh_proj halves are e4m3 twins too (column ranges of one checkpoint matrix)
+    names = set(json.loads((tmp_path / "out" / "mtp" / "fp8" / "fp8_index.json").read_text())["weight_map"])
+    assert any(n.startswith("cols/") and n.endswith(".e") for n in names)
+    # a checkpoint without prediction modules refuses --mtp
+    reference.write_checkpoint(small_mla_moe_config(hidden=512, experts=8), tmp_path / "plain", seed=0, dtype=torch.bfloat16)
+    assert plowc.main(["--hf-dir", str(tmp_path / "plain"), "--out", str(tmp_path / "o2"), "--max-rows", "128", "--mtp"]) == 2
