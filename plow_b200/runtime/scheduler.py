@@ -48,11 +48,12 @@ class GenParams:
     session_end: bool = False             # the session's last turn: nothing is retained for it
     deadline_ms: float | None = None      # total time budget from arrival; None = no deadline
     json_mode: bool = False               # response_format json_object: tokens are filtered by a JSON recogniser
+    logit_bias: dict | None = None        # token id -> value added to that token's logit before sampling (OpenAI: -100 .. 100)
 
     @property
     def greedy(self) -> bool:
         return self.temperature <= 0.0 and self.presence_penalty == 0.0 and self.frequency_penalty == 0.0 \
-            and self.repetition_penalty == 1.0 and self.logprobs is None and not self.json_mode
+            and self.repetition_penalty == 1.0 and self.logprobs is None and not self.json_mode and not self.logit_bias
 
 
 @dataclass
@@ -914,6 +915,11 @@ class ModelMux:
                 return
         elif not p.greedy and logits is not None:
             lg = sampling.apply_penalties(logits, r.generated, p.presence_penalty, p.frequency_penalty, p.repetition_penalty)
+            if p.logit_bias:
+                lg = np.array(lg, dtype=np.float32, copy=True)
+                for t, b in p.logit_bias.items():
+                    if 0 <= int(t) < lg.shape[0]:
+                        lg[int(t)] += float(b)
             tok = sampling.sample(lg, r.rng, p.temperature, p.top_k, p.top_p, p.min_p)
             if p.logprobs is not None:
                 lp, top = sampling.logprobs_of(lg, tok, p.logprobs)

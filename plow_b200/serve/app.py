@@ -28,7 +28,7 @@ from ..runtime.scheduler import GenParams
 from . import tools as tools_mod
 from .template import ChatTemplateError
 
-REFUSED_PARAMS = ("echo", "best_of", "logit_bias", "suffix", "functions", "function_call")
+REFUSED_PARAMS = ("echo", "best_of", "suffix", "functions", "function_call")
 
 
 class ApiError(Exception):
@@ -55,6 +55,14 @@ def _gen_params(body: dict, default_max: int) -> GenParams:
             json_mode = True
         elif kind != "text":
             raise ApiError(400, f"response_format '{kind}' is not supported (text, json_object)", code="unsupported_parameter")
+    bias = body.get("logit_bias")
+    if bias is not None:
+        try:
+            bias = {int(k): float(v) for k, v in dict(bias).items()}
+        except (TypeError, ValueError):
+            raise ApiError(400, "logit_bias maps token ids to numbers", code="invalid_value")
+        if len(bias) > 300 or any(not -100.0 <= v <= 100.0 for v in bias.values()):
+            raise ApiError(400, "logit_bias takes at most 300 entries with values in [-100, 100]", code="invalid_value")
     t = body.get("temperature")
     temperature = 1.0 if t is None else float(t)
     if temperature < 0 or temperature > 2:
@@ -81,7 +89,7 @@ def _gen_params(body: dict, default_max: int) -> GenParams:
                      repetition_penalty=float(body.get("repetition_penalty") or 1.0), seed=body.get("seed"),
                      stop=list(stop), stop_token_ids=list(body.get("stop_token_ids") or []),
                      ignore_eos=bool(body.get("ignore_eos", False)), min_tokens=int(body.get("min_tokens") or 0),
-                     logprobs=lp, deadline_ms=(float(body["deadline_ms"]) if body.get("deadline_ms") else None),
+                     logprobs=lp, logit_bias=bias or None, deadline_ms=(float(body["deadline_ms"]) if body.get("deadline_ms") else None),
                      json_mode=json_mode)
 
 

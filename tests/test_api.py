@@ -163,3 +163,30 @@ def test_json_mode_returns_a_json_object(client):
     bad = client.post("/v1/chat/completions", json=dict(model="tiny", messages=[dict(role="user", content="x")],
                                                         response_format={"type": "json_schema"}))
     assert bad.status_code == 400
+
+
+def test_logit_bias_steers_greedy_decoding(client):
+    body = dict(model="tiny", prompt="hello there", max_tokens=4, temperature=0)
+    # +100 on one token makes greedy decoding emit it at every step
+    a_id = client.post("/tokenize", json=dict(model="tiny", prompt="A", add_special_tokens=False)).json()["tokens"][0]
+    forced = client.post("/v1/completions", json=dict(body, logit_bias={str(a_id): 100}, logprobs=0)).json()["choices"][0]
+    assert forced["text"] == "AAAA"
+    for bad in ({"65": 1000}, {"x": 1}, {str(i): 1 for i in range(301)}):
+        r = client.post("/v1/completions", json=dict(body, logit_bias=bad))
+        assert r.status_code == 400 and r.json()["error"]["code"] == "invalid_value"
+
+
+def test_logit_bias_bans_a_token(tiny_assets):
+    from plow_b200.runtime.scheduler import GenParams
+    eng = CpuEngine(tiny_assets / "assets", max_slots=2, max_ctx=256)
+    mux = ModelMux(eng, ByteTokenizer(), eos_ids=[]).start()
+    try:
+        prompt = list(range(5, 40))
+        plain = mux.generate(prompt, GenParams(max_tokens=5))[0]
+        banned = mux.generate(prompt, GenParams(max_tokens=5, logit_bias={plain[0]: -100.0}))[0]
+        assert banned[0] != plain[0] and plain[0] not in banned[:1]
+        same = mux.generate(prompt, GenParams(max_tokens=5, logit_bias={plain[0]: 0.0}))[0]
+        assert same == plain                                  # a zero bias changes nothing (and still takes the sampled path)
+    finally:
+        mux.stop()
+        eng.close()
