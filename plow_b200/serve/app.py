@@ -45,8 +45,11 @@ def _gen_params(body: dict, default_max: int) -> GenParams:
     for k in REFUSED_PARAMS:
         if body.get(k) is not None:
             raise ApiError(400, f"parameter '{k}' is not supported", code="unsupported_parameter")
-    if body.get("n", 1) != 1:
-        raise ApiError(400, "only n=1 is supported", code="unsupported_parameter")
+    n = body.get("n", 1)
+    if not isinstance(n, int) or isinstance(n, bool) or not 1 <= n <= 8:
+        raise ApiError(400, "n must be an integer in [1, 8]", code="invalid_value")
+    if n > 1 and body.get("stream"):
+        raise ApiError(400, "n > 1 is not supported with stream", code="unsupported_parameter")
     rf = body.get("response_format")
     json_mode = False
     if rf is not None:
@@ -263,6 +266,21 @@ def create_app(state: AppState) -> FastAPI:
         mux = state.router.route(m, ids) if state.router else m.mux
         return mux.submit(ids, params)
 
+    def _fan_out(m: ModelEntry, ids: list, params: GenParams, n: int) -> list:
+        """n - 1 further samples of the same prompt (the prefix cache shares its KV pages); each gets a seed of its own."""
+        import dataclasses
+        out = []
+        for i in range(1, n):
+            p = dataclasses.replace(params, seed=(params.seed + i) if params.seed is not None else None, session_id=None, session_end=False)
+            out.append(_submit(m, ids, p))
+        return out
+
+    def _sum_usage(usages: list) -> dict:
+        u = dict(usages[0] or {})
+        u["completion_tokens"] = sum((x or {}).get("completion_tokens", 0) for x in usages)
+        u["total_tokens"] = u.get("prompt_tokens", 0) + u["completion_tokens"]
+        return u
+
     async def _collect(req):
         text, toks, lps = [], [], []
         while True:
@@ -368,24 +386,27 @@ def create_app(state: AppState) -> FastAPI:
                         yield "data: " + json.dumps({"error": {"message": ch.error, "type": "server_error", "code": "engine_error"}}) + "\n\n"
                         return   # no [DONE] after an error frame
             return StreamingResponse(sse(), media_type="text/event-stream")
-        text, toks, lps, reason, usage = await _collect(req)
-        fr, xfr = _finish(reason)
-        message = {"role": "assistant", "content": text}
-        if want_reasoning:
-            reasoning, text = tools_mod.split_reasoning(text)
-            message["content"] = text
-            if reasoning is not None:
-                message["reasoning_content"] = reasoning
-        if want_tools:
-            content, calls = tools_mod.extract_tool_calls(text, getattr(m, "tool_family", None))
-            if calls:
-                message["content"] = content or None
-                message["tool_calls"] = calls
-                fr = "tool_calls"
+        others = _fan_out(m, ids, params, int(body.get("n") or 1))
+        results = [await _collect(req)] + [await _collect(r) for r in others]
+        choices, xfr = [], None
+        for i, (text, toks, lps, reason, _u) in enumerate(results):
+            fr, x = _finish(reason)
+            xfr = xfr or x
+            message = {"role": "assistant", "content": text}
+            if want_reasoning:
+                reasoning, text = tools_mod.split_reasoning(text)
+                message["content"] = text
+                if reasoning is not None:
+                    message["reasoning_content"] = reasoning
+            if want_tools:
+                content, calls = tools_mod.extract_tool_calls(text, getattr(m, "tool_family", None))
+                if calls:
+                    message["content"] = content or None
+                    message["tool_calls"] = calls
+                    fr = "tool_calls"
+            choices.append({"index": i, "message": message, "finish_reason": fr, "logprobs": _lp_block(m, lps)})
         out = {"id": rid, "object": "chat.completion", "created": created, "model": m.name,
-               "system_fingerprint": state.fingerprint,
-               "choices": [{"index": 0, "message": message, "finish_reason": fr,
-                            "logprobs": _lp_block(m, lps)}], "usage": usage}
+               "system_fingerprint": state.fingerprint, "choices": choices, "usage": _sum_usage([r[4] for r in results])}
         if xfr:
             out["x_plow_finish_reason"] = xfr
         return out
@@ -425,11 +446,12 @@ def create_app(state: AppState) -> FastAPI:
                         yield "data: " + json.dumps({"error": {"message": ch.error, "type": "server_error", "code": "engine_error"}}) + "\n\n"
                         return
             return StreamingResponse(sse(), media_type="text/event-stream")
-        text, toks, lps, reason, usage = await _collect(req)
-        fr, xfr = _finish(reason)
+        others = _fan_out(m, ids, params, int(body.get("n") or 1))
+        results = [await _collect(req)] + [await _collect(r) for r in others]
         return {"id": rid, "object": "text_completion", "created": created, "model": m.name,
                 "system_fingerprint": state.fingerprint,
-                "choices": [{"index": 0, "text": text, "finish_reason": fr, "token_ids": toks,
-                             "logprobs": _lp_block(m, lps)}], "usage": usage}
+                "choices": [{"index": i, "text": text, "finish_reason": _finish(reason)[0], "token_ids": toks, "logprobs": _lp_block(m, lps)}
+                            for i, (text, toks, lps, reason, _u) in enumerate(results)],
+                "usage": _sum_usage([r[4] for r in results])}
 
     return app

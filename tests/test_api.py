@@ -65,7 +65,9 @@ def test_completions_token_prompt_and_logprobs(client):
 def test_errors_use_openai_envelope(client):
     r = client.post("/v1/chat/completions", json={"model": "nope", "messages": [{"role": "user", "content": "x"}]})
     assert r.status_code == 404 and r.json()["error"]["code"] == "model_not_found"
-    r = client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "x"}], "n": 2})
+    r = client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "x"}], "n": 2, "stream": True})
+    assert r.status_code == 400 and r.json()["error"]["code"] == "unsupported_parameter"
+    r = client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "x"}], "best_of": 2})
     assert r.status_code == 400 and r.json()["error"]["code"] == "unsupported_parameter"
     r = client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "x"}],
                                                   "response_format": {"type": "json_schema"}})
@@ -190,3 +192,18 @@ def test_logit_bias_bans_a_token(tiny_assets):
     finally:
         mux.stop()
         eng.close()
+
+
+def test_n_samples_per_request(client):
+    body = dict(model="tiny", prompt="hello there", max_tokens=5, temperature=1.0, seed=7, n=3)
+    r = client.post("/v1/completions", json=body).json()
+    assert [c["index"] for c in r["choices"]] == [0, 1, 2]
+    ids = [tuple(c["token_ids"]) for c in r["choices"]]
+    assert len(set(ids)) >= 2                                            # different seeds, different samples
+    assert r["usage"]["completion_tokens"] == 15 and r["usage"]["total_tokens"] == r["usage"]["prompt_tokens"] + 15
+    again = client.post("/v1/completions", json=body).json()
+    assert [tuple(c["token_ids"]) for c in again["choices"]] == ids      # and reproducible from the request's seed
+    chat = client.post("/v1/chat/completions", json=dict(model="tiny", messages=[dict(role="user", content="hi")], max_tokens=4, n=2)).json()
+    assert len(chat["choices"]) == 2 and chat["choices"][1]["index"] == 1 and chat["usage"]["completion_tokens"] == 8
+    assert client.post("/v1/completions", json=dict(body, n=9)).status_code == 400
+    assert client.post("/v1/completions", json=dict(body, stream=True)).status_code == 400
