@@ -121,7 +121,6 @@ def step_gate(recipe: dict, work: Path) -> dict:
     distribution <= kl_max, top-1 agreement >= top1_min, relative logit error <= rel_err_max, over prefill and a few
     decode steps, and the chunked / prefix-cached prefill reproduces the one-shot logits."""
     import torch
-    from safetensors.torch import load_file
     from .models import config, reference
     from .runtime.engine import TokenBatch
     from .runtime.weights import open_checkpoint
