@@ -123,14 +123,15 @@ def step_gate(recipe: dict, work: Path) -> dict:
     import torch
     from .models import config, reference
     from .runtime.engine import TokenBatch
-    from .runtime.weights import open_checkpoint
+    from .runtime.weights import SCALE_SUFFIX, open_checkpoint, shard_slice
     g = recipe.get("gate", {})
     n_prompts, plen, steps = int(g.get("prompts", 4)), int(g.get("prompt_len", 48)), int(g.get("decode_steps", 2))
     kl_max, top1_min, rel_max = float(g.get("kl_max", 1e-3)), float(g.get("top1_min", 0.99)), float(g.get("rel_err_max", 0.02))
     ck = _checkpoint(recipe, work)
     spec = config.load_spec(ck)
     ckpt = open_checkpoint(ck)
-    state = {n: ckpt.get(n).float() for n in ckpt.names()}
+    # the reference sees what the engine sees: block-quantised tensors dequantised through their scales
+    state = {n: shard_slice(ckpt, n, None, 1, 0).float() for n in ckpt.names() if not n.endswith(SCALE_SUFFIX)}
     ref = reference.ReferenceModel(spec, state)
     eng = _engine(recipe, work)
     rng = np.random.default_rng(int(recipe.get("bench", {}).get("seed", 0)) + 17)
