@@ -163,6 +163,7 @@ def create_app(state: AppState) -> FastAPI:
     async def version():
         return {"version": __version__, "system_fingerprint": state.fingerprint}
 
+    @app.get("/models")
     @app.get("/v1/models")
     async def models():
         return {"object": "list", "data": [
@@ -193,6 +194,7 @@ def create_app(state: AppState) -> FastAPI:
                          "kv_pages": m.mux.engine.pool.n_pages, "kv_pages_free": m.mux.engine.pool.available(),
                          "health": m.mux.engine.health} for m in state.models.values()}
 
+    @app.post("/v1/tokenize")
     @app.post("/tokenize")
     async def tokenize(body: dict):
         m = state.get(body.get("model", ""))
@@ -203,6 +205,7 @@ def create_app(state: AppState) -> FastAPI:
         ids = m.tok.encode(text)
         return {"tokens": ids, "count": len(ids), "max_model_len": m.mux.engine.max_ctx}
 
+    @app.post("/v1/detokenize")
     @app.post("/detokenize")
     async def detokenize(body: dict):
         m = state.get(body.get("model", ""))

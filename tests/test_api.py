@@ -26,6 +26,9 @@ def client(tiny_assets):
 def test_models_health_version(client):
     r = client.get("/v1/models").json()
     assert r["object"] == "list" and r["data"][0]["id"] == "tiny" and "created" in r["data"][0]
+    assert client.get("/models").json() == r                     # unversioned aliases of the model list and the tokenizer routes
+    t = client.post("/v1/tokenize", json={"model": "tiny", "prompt": "abc"}).json()
+    assert client.post("/v1/detokenize", json={"model": "tiny", "tokens": t["tokens"]}).json()["prompt"] == "abc"
     assert client.get("/health").json()["status"] == "ok"
     assert "system_fingerprint" in client.get("/version").json()
 
