@@ -194,6 +194,27 @@ class Store:
             st["previous"] = None
         self._save(name, st)
 
+    def upgrade(self, name, registry: "Registry", target: dict | None = None, dry_run: bool = False, scratch=None) -> dict:
+        """Move the model's pin to the newest build in the registry that this machine can run."""
+        target = target or host_target()
+        found = registry.newest_compatible(name, target)
+        if found is None:
+            raise DistError(f"the registry has no build of '{name}' for {target.get('arch')}")
+        idx, ent = found
+        st = self._state(name)
+        have = None
+        if st["active"]:
+            m = json.loads((self.root / name / st["active"] / "manifest.json").read_text())
+            have = m.get("created")
+        if have is not None and ent["created"] <= have:
+            return dict(name=name, upgraded=False, active=st["active"], reason="already at the newest compatible build")
+        if dry_run:
+            return dict(name=name, upgraded=False, would_load=ent["file"], created=ent["created"])
+        import tempfile
+        with tempfile.TemporaryDirectory(dir=scratch) as d:
+            dst = self.load(registry.pull(name, d, idx))
+        return dict(name=name, upgraded=True, active=dst.name, created=ent["created"])
+
     def gc(self, keep: int = 2) -> list:
         removed = []
         for d in [p for p in self.root.iterdir() if p.is_dir()] if self.root.exists() else []:
@@ -206,6 +227,26 @@ class Store:
                 removed.append((d.name, g))
             self._save(d.name, st)
         return removed
+
+
+def host_target() -> dict:
+    """This machine as a registry sees it: the target a published bundle must name to be selected here."""
+    try:
+        import torch
+        if torch.cuda.is_available():
+            p = torch.cuda.get_device_properties(0)
+            return dict(arch=f"sm_{p.major}{p.minor}{'a' if p.major >= 9 else ''}", gpu=p.name, gpus=torch.cuda.device_count(),
+                        memory_gb=round(p.total_memory / 2 ** 30, 1))
+    except Exception:
+        pass
+    import os
+    return dict(arch="cpu", gpu=None, gpus=0, memory_gb=0.0, cpu_threads=os.cpu_count())
+
+
+def compatible(bundle_arch: str | None, target: dict) -> bool:
+    """A bundle runs here when it names this machine's architecture. CPU bundles run anywhere, and a host without a GPU
+    takes every bundle: the CPU interpreter executes the same packets."""
+    return target.get("arch") == "cpu" or bundle_arch in (None, "cpu", target.get("arch"))
 
 
 class Registry:
@@ -231,6 +272,27 @@ class Registry:
 
     def catalog(self) -> dict:
         return self._catalog()
+
+    def unlist(self, name, index: int = -1) -> dict:
+        """Take one published build out of the catalog (the bundle file stays until nothing refers to it)."""
+        cat = self._catalog()
+        if name not in cat or not cat[name]:
+            raise DistError(f"'{name}' is not in the registry")
+        ent = cat[name].pop(index)
+        if not cat[name]:
+            del cat[name]
+        if not any(e["file"] == ent["file"] for v in cat.values() for e in v):
+            (self.root / ent["file"]).unlink(missing_ok=True)
+        (self.root / "catalog.json").write_text(json.dumps(cat, indent=1))
+        return ent
+
+    def newest_compatible(self, name, target: dict):
+        """(index, entry) of the newest build of ``name`` this machine can run, or None."""
+        builds = self._catalog().get(name, [])
+        for i in range(len(builds) - 1, -1, -1):
+            if compatible(builds[i].get("arch"), target):
+                return i, builds[i]
+        return None
 
     def pull(self, name, dest_dir, index: int = -1) -> Path:
         cat = self._catalog()

@@ -225,7 +225,45 @@ def cmd_dist(args) -> int:
         print(st.load(pkg) if args.load else pkg)
     elif c == "catalog":
         print(json.dumps(d.Registry(args.registry).catalog(), indent=1))
+    elif c == "unlist":
+        print(json.dumps(d.Registry(args.registry).unlist(args.name, args.index)))
+    elif c == "upgrade":
+        names = [m["name"] for m in st.ls() if m["active"]] if args.all else [args.name]
+        if not names or names == [None]:
+            raise SystemExit("plowrt upgrade: name a model or pass --all")
+        print(json.dumps([st.upgrade(n, d.Registry(args.registry), dry_run=args.dry_run) for n in names], indent=1))
+    elif c == "target":
+        t = d.host_target()
+        print(json.dumps(t) if args.json else " ".join(f"{k}={v}" for k, v in t.items()))
     return 0
+
+
+def cmd_op_audit(args) -> int:
+    """Opcode classes of the whole ISA (--table) or of a packet's programs; an unclassified opcode is refused (exit 1)."""
+    from .compiler import audit
+    if args.table or not args.blob:
+        rows = [dict(op=o.name, value=int(o), cls=audit.op_class(o), cpu=o in audit.CPU_OPS, cuda=o in audit.gpu_ops()) for o in pk.Op]
+        if args.format == "json":
+            print(json.dumps(rows, indent=1))
+        else:
+            for r in rows:
+                print(f"{r['value']:3d} {r['op']:<20} {r['cls']:<10} cpu={'y' if r['cpu'] else '-'} cuda={'y' if r['cuda'] else '-'}")
+        return 0
+    pkt = pk.read_packet(Path(args.blob) / "model.pkt" if Path(args.blob).is_dir() else args.blob)
+    if args.program is not None:
+        want_role, want_rows = (pk.Role.DECODE, None) if args.program == 1 else (pk.Role.PREFILL, args.program)
+        pkt.programs = [p for p in pkt.programs if p.role == want_role and (want_rows is None or p.rows == want_rows)]
+        if not pkt.programs:
+            raise SystemExit(f"plowrt op-audit: the packet has no such program ({args.program})")
+    out = {b: audit.audit_ops(pkt, b) for b in ("cpu", "cuda")}
+    if args.format == "json":
+        print(json.dumps(out, indent=1))
+    else:
+        for b, a in out.items():
+            print(f"[{b}] ok={a['ok']} missing={a['missing']} unclassified={a['unclassified']}")
+            for cls, ops in a["by_class"].items():
+                print(f"  {cls:<10} {' '.join(ops)}")
+    return 0 if not out["cpu"]["unclassified"] else 1
 
 
 def main(argv=None) -> int:
@@ -314,6 +352,22 @@ def main(argv=None) -> int:
     dist_parser("push", "bundle", registry=dict(required=True))
     dist_parser("pull", "name", registry=dict(required=True), out=dict(default="."), load=dict(action="store_true"))
     dist_parser("catalog", registry=dict(required=True))
+    dist_parser("unlist", "name", registry=dict(required=True), index=dict(type=int, default=-1))
+    dist_parser("target", json=dict(action="store_true"))
+    up = sub.add_parser("upgrade", help="move a model's pin to the newest build in the registry that this machine can run")
+    up.add_argument("name", nargs="?")
+    up.add_argument("--all", action="store_true")
+    up.add_argument("--dry-run", action="store_true", dest="dry_run")
+    up.add_argument("--registry", required=True)
+    up.add_argument("--store")
+    up.add_argument("--trust", action="append")
+    up.set_defaults(fn=cmd_dist)
+    oa = sub.add_parser("op-audit", help="opcode classes of the ISA or of a packet; unclassified opcodes are refused")
+    oa.add_argument("blob", nargs="?")
+    oa.add_argument("--table", action="store_true")
+    oa.add_argument("--program", type=int)
+    oa.add_argument("--format", default="text", choices=["text", "json"])
+    oa.set_defaults(fn=cmd_op_audit)
     args = ap.parse_args(argv)
     return args.fn(args)
 

@@ -62,3 +62,53 @@ def test_registry_publish_pull(tiny_assets, tmp_path):
     assert d.read_manifest(got)[0]["name"] == "tiny"
     with pytest.raises(d.DistError):
         reg.pull("nope", tmp_path / "dl")
+
+
+def test_unlist_upgrade_and_target(tiny_assets, tmp_path, monkeypatch):
+    import time as _time
+    from plow_b200.dist import store as d
+    reg = d.Registry(tmp_path / "registry")
+    st = d.Store(tmp_path / "store")
+    clock = [1000]
+    monkeypatch.setattr(d.time, "time", lambda: clock[0])
+    old = d.pack(tiny_assets / "assets", tmp_path / "o1", "tiny")
+    reg.publish(old)
+    st.load(old)
+    first = st.active("tiny")
+    assert st.upgrade("tiny", reg)["upgraded"] is False          # the store already holds the newest build
+    clock[0] = 2000
+    new = d.pack(tiny_assets / "assets", tmp_path / "o2", "tiny", with_weights=True)
+    reg.publish(new)
+    dry = st.upgrade("tiny", reg, dry_run=True)
+    assert dry["upgraded"] is False and dry["created"] == 2000 and st.active("tiny") == first
+    got = st.upgrade("tiny", reg)
+    assert got["upgraded"] is True and st.active("tiny") != first and st.active("tiny").name == got["active"]
+    # a machine of another architecture finds nothing to move to
+    arch = reg.catalog()["tiny"][-1]["arch"]
+    assert d.compatible(arch, d.host_target())
+    if arch not in (None, "cpu"):
+        with pytest.raises(d.DistError):
+            st.upgrade("tiny", reg, target=dict(arch="sm_90a"))
+    # unlist drops the newest entry and its file; the older build is found again
+    ent = reg.unlist("tiny")
+    assert ent["created"] == 2000 and not (reg.root / ent["file"]).exists() and len(reg.catalog()["tiny"]) == 1
+    reg.unlist("tiny")
+    assert "tiny" not in reg.catalog()
+    with pytest.raises(d.DistError):
+        reg.unlist("tiny")
+    t = d.host_target()
+    assert t["arch"] == "cpu" or t["arch"].startswith("sm_")
+
+
+def test_cli_target_and_op_audit(tiny_assets, capsys):
+    from plow_b200 import plowrt
+    assert plowrt.main(["target", "--json"]) == 0
+    assert "arch" in json.loads(capsys.readouterr().out)
+    assert plowrt.main(["op-audit", "--table", "--format", "json"]) == 0
+    rows = json.loads(capsys.readouterr().out)
+    assert all(r["cls"] for r in rows) and any(r["op"] == "GEMM" and r["cpu"] for r in rows)
+    assert plowrt.main(["op-audit", str(tiny_assets / "assets"), "--format", "json"]) == 0
+    out = json.loads(capsys.readouterr().out)
+    assert out["cpu"]["ok"] and out["cpu"]["unclassified"] == []
+    assert plowrt.main(["op-audit", str(tiny_assets / "assets"), "--program", "1"]) == 0
+    assert "[cpu] ok=True" in capsys.readouterr().out
