@@ -24,6 +24,10 @@
 #include <string>
 #include <thread>
 #include <vector>
+#if defined(__linux__)
+#include <sys/syscall.h>
+#include <unistd.h>
+#endif
 
 #include "plow_packet.h"
 
@@ -249,17 +253,22 @@ void op_residual(const Ctx& c) {
 }
 
 // ---- GEMM kernel tiers ---------------------------------------------------------------------------------------------
-// y[m][n] = x[m] . w[n] (+ SiLU-gated pair).  Three bodies behind one op, picked once per process (PLOW_CPU_TIER =
-// golden | avx2 | avx512 | auto, or plow_cpu_set_tier):
+// y[m][n] = x[m] . w[n] (+ SiLU-gated pair).  Four bodies behind one op, picked once per process (PLOW_CPU_TIER =
+// golden | avx2 | avx512 | amx | auto, or plow_cpu_set_tier):
 //   golden  one output at a time: the numeric statement the others are held to;
 //   avx2    eight rows share every weight row they read (the weight matrix is streamed rows / 8 times instead of rows
 //           times) with 8-lane FMA accumulators, summed tail elements first, then lanes 0..7;
-//   avx512  the same with 16 lanes.
+//   avx512  the same with 16 lanes;
+//   amx     16x16 output tiles on the AMX unit (TDPBF16PS): inputs rounded to bf16, fp32 accumulation.  The product is
+//           formed transposed, y^T = w . x^T, so weight rows load as A tiles straight after conversion and only the
+//           activations (small) are repacked into the pair-interleaved B layout, once per op.  GEMMs of fewer than
+//           16 rows take the avx512 body.  Never picked by `auto`: bf16 inputs move logits by ~1e-2 relative, the
+//           same order as the GPU engine's bf16 path.
 // The tiers order their sums differently from the compiler's own vectorisation of the golden loop, so they agree with it
 // to rounding (1e-6 relative on a model's logits), not bit for bit.  `auto` takes avx2 when the CPU has it; avx512 is a
 // choice (on a 250-row prefill of the 4-layer test model: golden 77 ms, avx2 56 ms, avx512 41 ms).
 // Reference counterpart: runtime/cpu (scalar / AVX2 / AVX-512 / AMX kernel tiers behind one dispatch table).
-enum { TIER_GOLDEN = 0, TIER_AVX2 = 1, TIER_AVX512 = 2 };
+enum { TIER_GOLDEN = 0, TIER_AVX2 = 1, TIER_AVX512 = 2, TIER_AMX = 3 };
 
 // gate activation of a GLU: SiLU unless the flags ask for GELU (tanh or erf form)
 static inline float glu_act(float v, uint32_t flags) {
@@ -268,9 +277,23 @@ static inline float glu_act(float v, uint32_t flags) {
   return v / (1.0f + std::exp(-v));
 }
 
+// The kernel hands out AMX tile state per process on request (arch_prctl ARCH_REQ_XCOMP_PERM, feature 18 = tile data).
+static int amx_permitted() {
+  static const int ok = [] {
+#if defined(__linux__) && defined(__x86_64__)
+    if (!__builtin_cpu_supports("amx-tile") || !__builtin_cpu_supports("amx-bf16") || !__builtin_cpu_supports("avx512bf16")) return 0;
+    return syscall(SYS_arch_prctl, 0x1023, 18) == 0 ? 1 : 0;
+#else
+    return 0;
+#endif
+  }();
+  return ok;
+}
+
 static int tier_supported(int t) {
   if (t == TIER_AVX2) return __builtin_cpu_supports("avx2") && __builtin_cpu_supports("fma");
   if (t == TIER_AVX512) return __builtin_cpu_supports("avx512f");
+  if (t == TIER_AMX) return __builtin_cpu_supports("avx512f") && amx_permitted();
   return t == TIER_GOLDEN;
 }
 
@@ -278,8 +301,9 @@ static int pick_tier() {
   const char* e = std::getenv("PLOW_CPU_TIER");
   const std::string v = e ? e : "auto";
   if (v == "golden") return TIER_GOLDEN;
-  if (v == "avx512" && tier_supported(TIER_AVX512)) return TIER_AVX512;
-  if ((v == "avx2" || v == "auto" || v == "avx512") && tier_supported(TIER_AVX2)) return TIER_AVX2;
+  if (v == "amx" && tier_supported(TIER_AMX)) return TIER_AMX;
+  if ((v == "avx512" || v == "amx") && tier_supported(TIER_AVX512)) return TIER_AVX512;
+  if ((v == "avx2" || v == "auto" || v == "avx512" || v == "amx") && tier_supported(TIER_AVX2)) return TIER_AVX2;
   return TIER_GOLDEN;
 }
 static std::atomic<int> g_tier{-1};
@@ -328,6 +352,128 @@ __attribute__((target("avx512f"))) static void dots_avx512(const float* x, int64
   }
 }
 
+// ---- AMX tier ----
+struct alignas(64) AmxTileCfg {
+  uint8_t palette, start_row, rsv[14];
+  uint16_t colsb[16];
+  uint8_t rows[16];
+};
+#define PLOW_AMX_TARGET __attribute__((target("amx-tile,amx-bf16,avx512f,avx512bf16,avx512bw")))
+
+// 32 floats -> 32 bf16 (round to nearest even) as 16 dwords; dword j holds elements (2j, 2j+1)
+PLOW_AMX_TARGET static inline __m512i cvt32(const float* p) {
+  return (__m512i)_mm512_cvtne2ps_pbh(_mm512_loadu_ps(p + 16), _mm512_loadu_ps(p));
+}
+PLOW_AMX_TARGET static inline __m512i cvt32_tail(const float* p, int n) {   // n < 32 valid elements, the rest zero
+  const __mmask16 lo = n >= 16 ? 0xffff : __mmask16((1u << n) - 1), hi = n > 16 ? __mmask16((1u << (n - 16)) - 1) : 0;
+  return (__m512i)_mm512_cvtne2ps_pbh(_mm512_maskz_loadu_ps(hi, p + 16), _mm512_maskz_loadu_ps(lo, p));
+}
+
+// x rows -> B tiles: xt[(mb * KT + kt)][k2][m][2] = x[mb*16 + m][kt*32 + 2*k2 + {0,1}], zero beyond rows / K
+PLOW_AMX_TARGET static void amx_pack_x(const float* x, int64_t pitch, int64_t rows, int K, int KT, uint32_t* xt) {
+  const int64_t MB = (rows + 15) / 16;
+  alignas(64) uint32_t v[16];
+  for (int64_t mb = 0; mb < MB; ++mb)
+    for (int kt = 0; kt < KT; ++kt) {
+      uint32_t* tile = xt + (mb * KT + kt) * 256;
+      const int kn = std::min(32, K - kt * 32);
+      for (int m = 0; m < 16; ++m) {
+        const int64_t r = mb * 16 + m;
+        if (r < rows) {
+          const float* src = x + r * pitch + kt * 32;
+          _mm512_store_si512((void*)v, kn == 32 ? cvt32(src) : cvt32_tail(src, kn));
+          for (int k2 = 0; k2 < 16; ++k2) tile[k2 * 16 + m] = v[k2];
+        } else {
+          for (int k2 = 0; k2 < 16; ++k2) tile[k2 * 16 + m] = 0;
+        }
+      }
+    }
+}
+
+// 16 weight rows (nn valid) -> bf16 staging [16][KT*32], zero padded
+PLOW_AMX_TARGET static void amx_stage_w(const float* w, int K, int KT, int nn, uint16_t* st) {
+  const int Kp = KT * 32;
+  for (int n = 0; n < 16; ++n) {
+    uint16_t* d = st + int64_t(n) * Kp;
+    if (n >= nn) { std::memset(d, 0, sizeof(uint16_t) * Kp); continue; }
+    const float* src = w + int64_t(n) * K;
+    int k = 0;
+    for (; k + 32 <= K; k += 32) _mm512_storeu_si512((void*)(d + k), cvt32(src + k));
+    if (k < K) _mm512_storeu_si512((void*)(d + k), cvt32_tail(src + k, K - k));
+  }
+}
+
+// out[n][m] (pitch Mp floats) = staged weight rows . packed x, for all row blocks; two row blocks share each A tile
+PLOW_AMX_TARGET static void amx_block(const uint16_t* st, const uint32_t* xt, int KT, int64_t MB, int64_t Mp, float* out) {
+  const int Kp = KT * 32;
+  int64_t mb = 0;
+  for (; mb + 2 <= MB; mb += 2) {
+    _tile_zero(0);
+    _tile_zero(1);
+    const uint32_t* b0 = xt + mb * KT * 256;
+    const uint32_t* b1 = b0 + int64_t(KT) * 256;
+    for (int kt = 0; kt < KT; ++kt) {
+      _tile_loadd(2, st + kt * 32, Kp * 2);
+      _tile_loadd(3, b0 + kt * 256, 64);
+      _tile_loadd(4, b1 + kt * 256, 64);
+      _tile_dpbf16ps(0, 2, 3);
+      _tile_dpbf16ps(1, 2, 4);
+    }
+    _tile_stored(0, out + mb * 16, Mp * 4);
+    _tile_stored(1, out + (mb + 1) * 16, Mp * 4);
+  }
+  if (mb < MB) {
+    _tile_zero(0);
+    const uint32_t* b0 = xt + mb * KT * 256;
+    for (int kt = 0; kt < KT; ++kt) {
+      _tile_loadd(2, st + kt * 32, Kp * 2);
+      _tile_loadd(3, b0 + kt * 256, 64);
+      _tile_dpbf16ps(0, 2, 3);
+    }
+    _tile_stored(0, out + mb * 16, Mp * 4);
+  }
+}
+
+PLOW_AMX_TARGET static void gemm_amx(float* y, const float* x, const float* w, int64_t rows, int N, int K, int64_t pitch, uint32_t flags,
+                                     int64_t a, int64_t b) {
+  const bool dual = flags & PLOW_GEMM_DUAL_SILU;
+  const int KT = (K + 31) / 32;
+  const int64_t MB = (rows + 15) / 16, Mp = MB * 16;
+  thread_local std::vector<uint32_t> xt;
+  thread_local std::vector<uint16_t> st;
+  thread_local std::vector<float> og, ou;
+  xt.resize(size_t(MB) * KT * 256 + 16);
+  st.resize(size_t(16) * KT * 32 + 32);
+  og.resize(size_t(16) * Mp + 16);
+  ou.resize(size_t(16) * Mp + 16);
+  auto al = [](auto* p) { return (decltype(p))((uintptr_t(p) + 63) & ~uintptr_t(63)); };
+  uint32_t* xtp = al(xt.data());
+  uint16_t* stp = al(st.data());
+  float *g = al(og.data()), *u = al(ou.data());
+  amx_pack_x(x, pitch, rows, K, KT, xtp);
+  AmxTileCfg cfg;
+  std::memset(&cfg, 0, sizeof cfg);
+  cfg.palette = 1;
+  for (int t = 0; t < 5; ++t) { cfg.colsb[t] = 64; cfg.rows[t] = 16; }
+  _tile_loadconfig(&cfg);
+  for (int64_t n0 = a; n0 < b; n0 += 16) {
+    const int nn = int(std::min<int64_t>(16, b - n0));
+    amx_stage_w(w + n0 * K, K, KT, nn, stp);
+    amx_block(stp, xtp, KT, MB, Mp, g);
+    if (dual) {
+      amx_stage_w(w + (n0 + N) * K, K, KT, nn, stp);
+      amx_block(stp, xtp, KT, MB, Mp, u);
+    }
+    for (int n = 0; n < nn; ++n)
+      for (int64_t m = 0; m < rows; ++m) {
+        float v = g[n * Mp + m];
+        if (dual) v = glu_act(v, flags) * u[n * Mp + m];
+        y[m * N + n0 + n] = v;
+      }
+  }
+  _tile_release();
+}
+
 void op_gemm(const Ctx& c, int64_t rows) {
   float* y = (float*)c.T(0);
   const float* x = (const float*)c.T(1);
@@ -353,7 +499,11 @@ void op_gemm(const Ctx& c, int64_t rows) {
     }
     return;
   }
-  auto dots = tier == TIER_AVX512 ? dots_avx512 : dots_avx2;
+  if (tier == TIER_AMX && rows >= 16) {
+    gemm_amx(y, x + co, w, rows, N, K, pitch, flags, a, b);
+    return;
+  }
+  auto dots = tier >= TIER_AVX512 ? dots_avx512 : dots_avx2;
   float g[kRowBlock], u[kRowBlock];
   for (int64_t m0 = 0; m0 < rows; m0 += kRowBlock) {
     const int nr = int(std::min<int64_t>(kRowBlock, rows - m0));
@@ -1121,10 +1271,10 @@ int plow_cpu_trace(void* h, PlowTraceRec* out, int cap) {
   std::memcpy(out, e->trace.data(), sizeof(PlowTraceRec) * n);
   return n;
 }
-// kernel tier of the GEMM op: 0 golden, 1 avx2, 2 avx512.  set returns the tier in force (an unsupported one is refused).
+// kernel tier of the GEMM op: 0 golden, 1 avx2, 2 avx512, 3 amx.  set returns the tier in force (an unsupported one is refused).
 int plow_cpu_tier() { return cur_tier(); }
 int plow_cpu_set_tier(int t) {
-  if (t >= 0 && t <= TIER_AVX512 && tier_supported(t)) g_tier.store(t);
+  if (t >= 0 && t <= TIER_AMX && tier_supported(t)) g_tier.store(t);
   return cur_tier();
 }
 void* plow_cpu_arena(void* h) { return static_cast<Engine*>(h)->arena.data(); }

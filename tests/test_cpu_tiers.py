@@ -1,5 +1,6 @@
-"""Kernel tiers of the CPU interpreter's GEMM (golden / AVX2 / AVX-512 behind one dispatch): the tiers agree, the blocked
-AVX2 tier is the default where the CPU has it, and a whole model gives the same logits on every tier."""
+"""Kernel tiers of the CPU interpreter's GEMM (golden / AVX2 / AVX-512 / AMX behind one dispatch): the fp32 tiers agree, the
+blocked AVX2 tier is the default where the CPU has it, a whole model gives the same logits on every fp32 tier, and the AMX
+tier (bf16 inputs, fp32 accumulation) stays within bf16 distance of them, ragged K / N / row counts included."""
 import time
 
 import numpy as np
@@ -9,7 +10,7 @@ from plow_b200.ops import native
 from plow_b200.runtime.cpu_engine import CpuEngine
 from plow_b200.runtime.engine import TokenBatch
 
-NAMES = {0: "golden", 1: "avx2", 2: "avx512"}
+NAMES = {0: "golden", 1: "avx2", 2: "avx512", 3: "amx"}
 
 
 def _logits(assets, tier, prompt):
@@ -42,6 +43,10 @@ def test_gemm_tiers_agree_on_a_whole_model(tiny_assets):
                 continue                      # this CPU lacks the instruction set: the tier is refused, the old one stays
             rel = float(np.linalg.norm(got - gold) / np.linalg.norm(gold))
             assert rel < 1e-6 and int(got.argmax()) == int(gold.argmax()), (NAMES[tier], rel)
+        got, _ = _logits(tiny_assets / "assets", 3, prompt)
+        if got is not None:                   # AMX: inputs rounded to bf16
+            rel = float(np.linalg.norm(got - gold) / np.linalg.norm(gold))
+            assert 1e-5 < rel < 3e-2 and int(got.argmax()) == int(gold.argmax()), rel
         assert lib.plow_cpu_set_tier(7) == lib.plow_cpu_tier()          # out of range: ignored
     finally:
         lib.plow_cpu_set_tier(start)
@@ -49,3 +54,29 @@ def test_gemm_tiers_agree_on_a_whole_model(tiny_assets):
     if lib.plow_cpu_set_tier(1) == 1:
         lib.plow_cpu_set_tier(start)
         assert start == 1 or __import__("os").environ.get("PLOW_CPU_TIER") not in (None, "auto")
+
+
+def test_amx_tier_on_ragged_shapes(tmp_path):
+    """hidden 528 (K % 32 = 16), intermediate 1400 (K % 32 = 24, per-thread column ranges that are no multiple of 16) and
+    a row count that is no multiple of 16: the zero padding of the tile operands leaves the result within bf16 distance."""
+    from plow_b200 import plowc
+    from plow_b200.models import config, reference
+    lib = native.cpu_lib()
+    start = lib.plow_cpu_tier()
+    if lib.plow_cpu_set_tier(3) != 3:
+        lib.plow_cpu_set_tier(start)
+        pytest.skip("no AMX on this CPU (or the kernel refused the tile state)")
+    cfg = config.tiny_dense_config()
+    cfg.update(hidden_size=528, intermediate_size=1400, num_hidden_layers=2)
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=1)
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", arch="cpu", n_cu=8, max_rows=256, decode_rungs=[1, 2], max_seqs=4)
+    prompt = np.random.default_rng(1).integers(0, 32000, 77).tolist()
+    try:
+        gold, _ = _logits(tmp_path / "assets", 0, prompt)
+        got, _ = _logits(tmp_path / "assets", 3, prompt)
+        rel = float(np.linalg.norm(got - gold) / np.linalg.norm(gold))
+        assert np.isfinite(got).all() and rel < 3e-2 and int(got.argmax()) == int(gold.argmax()), rel
+        # auto never picks it
+        assert start != 3 or __import__("os").environ.get("PLOW_CPU_TIER") == "amx"
+    finally:
+        lib.plow_cpu_set_tier(start)
