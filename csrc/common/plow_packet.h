@@ -38,7 +38,7 @@ typedef enum PlowOp {
   PLOW_OP_EMBED = 1,          /* t0=out[rows,H] t1=table t2=in.ids ; f0=scale */
   PLOW_OP_RMSNORM = 2,        /* t0=out t1=x t2=gamma(opt) ; f0=eps i0=H i1=gamma_mode(0 g,1 1+g) */
   PLOW_OP_ADD_NORM = 3,       /* t0=out t1=resid(in/out) t2=delta t3=gamma ; resid+=delta; out=norm(resid) */
-  PLOW_OP_GEMM = 4,           /* t0=y t1=x t2=w t3=resid(opt) t4=sx t5=sw ; i0=N i1=K i2=flags */
+  PLOW_OP_GEMM = 4,           /* t0=y t1=x t2=w t3=resid(opt) t4=sx t5=sw t7=bias(opt) ; i0=N i1=K i2=flags */
   PLOW_OP_ROPE_KV = 5,        /* t0=q out t1=fused qkv rows t2=kcache t3=vcache t4=qnorm(opt) t5=knorm(opt) t6=rope table
                                  t7=gate out (i7=1: query heads are [Q | gate] pairs) or the e4m3 cache's scales [P,64,2*nkv]
                                  i0=nq i1=nkv i2=hd i3=rot_dim i4=pair_mode i5=layer i6=gamma_mode i7=gated ; f0=eps */
@@ -94,6 +94,7 @@ typedef enum PlowOp {
 #define PLOW_GEMM_QUANT_OUT 16u
 #define PLOW_GEMM_ACT_GELU_TANH 32u /* with DUAL: gelu (tanh form) instead of silu on the gate */
 #define PLOW_GEMM_ACT_GELU_ERF 64u  /* with DUAL: gelu (erf form) */
+#define PLOW_GEMM_BIAS 128u         /* t7 = bias [N] (f32 in f32 packets, else bf16), added to the fp32 sum before the store */
 
 /* attention modes (i4) */
 #define PLOW_ATTN_CAUSAL 0u      /* token-batch rows, each attends to its sequence up to pos */

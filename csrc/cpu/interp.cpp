@@ -434,8 +434,8 @@ PLOW_AMX_TARGET static void amx_block(const uint16_t* st, const uint32_t* xt, in
   }
 }
 
-PLOW_AMX_TARGET static void gemm_amx(float* y, const float* x, const float* w, int64_t rows, int N, int K, int64_t pitch, uint32_t flags,
-                                     int64_t a, int64_t b) {
+PLOW_AMX_TARGET static void gemm_amx(float* y, const float* x, const float* w, const float* bias, int64_t rows, int N, int K, int64_t pitch,
+                                     uint32_t flags, int64_t a, int64_t b) {
   const bool dual = flags & PLOW_GEMM_DUAL_SILU;
   const int KT = (K + 31) / 32;
   const int64_t MB = (rows + 15) / 16, Mp = MB * 16;
@@ -466,7 +466,7 @@ PLOW_AMX_TARGET static void gemm_amx(float* y, const float* x, const float* w, i
     }
     for (int n = 0; n < nn; ++n)
       for (int64_t m = 0; m < rows; ++m) {
-        float v = g[n * Mp + m];
+        float v = g[n * Mp + m] + (bias ? bias[n0 + n] : 0.f);
         if (dual) v = glu_act(v, flags) * u[n * Mp + m];
         y[m * N + n0 + n] = v;
       }
@@ -482,6 +482,7 @@ void op_gemm(const Ctx& c, int64_t rows) {
   const uint32_t flags = c.in->i[2];
   const int co = c.in->i[6], pitch = c.in->i[7] ? c.in->i[7] : K;
   const bool dual = flags & PLOW_GEMM_DUAL_SILU;
+  const float* bias = (flags & PLOW_GEMM_BIAS) ? (const float*)c.T(7) : nullptr;   // never together with a gated pair
   int64_t a, b;
   c.range(N, a, b);
   const int tier = cur_tier();
@@ -489,7 +490,7 @@ void op_gemm(const Ctx& c, int64_t rows) {
     for (int64_t m = 0; m < rows; ++m) {
       const float* xr = x + m * pitch + co;
       for (int64_t n = a; n < b; ++n) {
-        float v = dotf(xr, w + n * K, K);
+        float v = dotf(xr, w + n * K, K) + (bias ? bias[n] : 0.f);
         if (dual) {
           const float u = dotf(xr, w + (n + N) * K, K);
           v = glu_act(v, flags) * u;
@@ -500,7 +501,7 @@ void op_gemm(const Ctx& c, int64_t rows) {
     return;
   }
   if (tier == TIER_AMX && rows >= 16) {
-    gemm_amx(y, x + co, w, rows, N, K, pitch, flags, a, b);
+    gemm_amx(y, x + co, w, bias, rows, N, K, pitch, flags, a, b);
     return;
   }
   auto dots = tier >= TIER_AVX512 ? dots_avx512 : dots_avx2;
@@ -514,7 +515,8 @@ void op_gemm(const Ctx& c, int64_t rows) {
         dots(xb, pitch, nr, w + (n + N) * K, K, u);
         for (int r = 0; r < nr; ++r) g[r] = glu_act(g[r], flags) * u[r];
       }
-      for (int r = 0; r < nr; ++r) y[(m0 + r) * N + n] = g[r];
+      const float bn = bias ? bias[n] : 0.f;
+      for (int r = 0; r < nr; ++r) y[(m0 + r) * N + n] = g[r] + bn;
     }
   }
 }

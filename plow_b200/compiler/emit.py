@@ -123,15 +123,19 @@ class Lowering:
                     and N % 128 == 0 and K % 128 == 0 and len(wv.shape) == 2
                 flags = (pk.GEMM_DUAL_SILU | pk.ACT_FLAGS[a.get("act", "silu")] if dual else 0) | (pk.GEMM_OUT_F32 if a.get("out_f32") else 0) \
                     | (pk.GEMM_FP8_BLOCK if quant else 0)
+                bias = n.inputs[2] if len(n.inputs) > 2 else None
+                if bias and (dual or n.op == "gemm_xreduce" and g.rank != 0):
+                    raise ValueError("a bias on a gated pair, or on a summed projection outside rank 0, has no lowering")
+                flags |= pk.GEMM_BIAS if bias else 0
                 co, pitch = self.xview(x)
                 tile = costmodel.pick_gemm_tile(m, N, quant, dual)
                 op = Op.GEMM_XREDUCE if n.op == "gemm_xreduce" else Op.GEMM
-                ins = pk.Inst(op, t=[self.t(n.outputs[0]), self.t(x), self.t(w)],
+                ins = pk.Inst(op, t=[self.t(n.outputs[0]), self.t(x), self.t(w)] + ([self.t(None)] * 4 + [self.t(bias)] if bias else []),
                               i=[N, K, flags, int(tile["swap"]), tile["bn"], g.tp, co, pitch])
                 c = costmodel.gemm_cost(m, N * (2 if dual else 1), K, 1 if quant else es, es)
                 if op == Op.GEMM_XREDUCE:
                     c.link_bytes = costmodel.allreduce_cost(m, N, g.tp, es).link_bytes
-                out.append(schedule.LInst(ins, rd(x, w), rd(n.outputs[0]), c.time_us(self.hw, "e4m3" if quant else g.spec.dtype),
+                out.append(schedule.LInst(ins, rd(x, w, bias), rd(n.outputs[0]), c.time_us(self.hw, "e4m3" if quant else g.spec.dtype),
                                           max(1, N // 64), "gemm" if op == Op.GEMM else "comm"))
             elif n.op == "rope_kv":
                 qkv, qn, kn, rope = n.inputs[0], n.inputs[1], n.inputs[2], n.inputs[3]

@@ -213,13 +213,19 @@ def _xreduce(g: Graph, v: str, li: int) -> str:
     return out
 
 
-def _linear(g: Graph, li, x, wname, n_out, k_in, shard_axis=None, rows=R, **attrs) -> str:
+def _linear(g: Graph, li, x, wname, n_out, k_in, shard_axis=None, rows=R, bias=False, **attrs) -> str:
+    """y = x . w^T (+ bias).  A column-parallel projection shards its bias with its rows; a row-parallel one is summed over
+    the ranks afterwards, so only rank 0 adds the bias."""
     tp = g.tp
     n_l = n_out // tp if shard_axis == 0 else n_out
     k_l = k_in // tp if shard_axis == 1 else k_in
     w = g.weight(wname, (n_l, k_l), shard_axis=shard_axis)
     y = g.tmp("y", (rows, n_l), "f32" if attrs.get("out_f32") else None)     # the arena slot must match what the GEMM writes
-    g.add("linear", [x, w], [y], layer=li, **attrs)
+    ins = [x, w]
+    if bias and (shard_axis != 1 or g.rank == 0):
+        ins.append(g.weight(wname[:-len("weight")] + "bias", (n_l,), shard_axis=0 if shard_axis == 0 else None,
+                            dtype="f32" if g.spec.dtype == "f32" else "bf16"))
+    g.add("linear", ins, [y], layer=li, **attrs)
     return y
 
 
@@ -228,9 +234,9 @@ def _gqa_attention(g: Graph, li, p, h, a) -> str:
     H = spec.hidden
     nq, nkv, hd = a.n_heads // tp, max(1, a.n_kv_heads // tp), a.head_dim
     qd = a.n_heads * hd * (2 if a.gated else 1)
-    q = _linear(g, li, h, f"{p}.self_attn.q_proj.weight", qd, H, shard_axis=0)
-    k = _linear(g, li, h, f"{p}.self_attn.k_proj.weight", a.n_kv_heads * hd, H, shard_axis=0)
-    v = _linear(g, li, h, f"{p}.self_attn.v_proj.weight", a.n_kv_heads * hd, H, shard_axis=0)
+    q = _linear(g, li, h, f"{p}.self_attn.q_proj.weight", qd, H, shard_axis=0, bias=a.qkv_bias)
+    k = _linear(g, li, h, f"{p}.self_attn.k_proj.weight", a.n_kv_heads * hd, H, shard_axis=0, bias=a.qkv_bias)
+    v = _linear(g, li, h, f"{p}.self_attn.v_proj.weight", a.n_kv_heads * hd, H, shard_axis=0, bias=a.qkv_bias)
     gate = None
     if a.gated:
         qs, gate = g.tmp("q", ("R", nq * hd)), g.tmp("gate", (R, nq * hd))
@@ -266,7 +272,7 @@ def _gqa_attention(g: Graph, li, p, h, a) -> str:
         ag = g.tmp("attn", (R, nq * hd))
         g.add("sigmoid_gate", [ao, gate], [ag], layer=li)
         ao = ag
-    return _linear(g, li, ao, f"{p}.self_attn.o_proj.weight", H, a.n_heads * hd, shard_axis=1)
+    return _linear(g, li, ao, f"{p}.self_attn.o_proj.weight", H, a.n_heads * hd, shard_axis=1, bias=a.o_bias)
 
 
 def _dense_ffn(g: Graph, li, p, h, inter, rows=R, act="silu") -> str:

@@ -70,6 +70,7 @@ OP_COUNT = 69
 
 GEMM_DUAL_SILU, GEMM_FP8_BLOCK, GEMM_OUT_F32, GEMM_RESIDUAL, GEMM_QUANT_OUT = 1, 2, 4, 8, 16
 GEMM_ACT_GELU_TANH, GEMM_ACT_GELU_ERF = 32, 64          # with DUAL: the gate's activation when it is not SiLU
+GEMM_BIAS = 128                                         # t7 holds a bias [N], added before the store
 ACT_FLAGS = {"silu": 0, "gelu_tanh": GEMM_ACT_GELU_TANH, "gelu": GEMM_ACT_GELU_ERF}
 ATTN_CAUSAL, ATTN_DECODE = 0, 1
 

@@ -36,12 +36,12 @@ def _single_use(cons, v, by: Node) -> bool:
 def _cat_weight(g: Graph, names: list, tag: str) -> str:
     """Derived weight: row-wise concatenation of checkpoint tensors (all share K)."""
     ws = [g.values[n] for n in names]
-    k = ws[0].shape[1]
-    assert all(w.shape[1] == k for w in ws)
+    tail = tuple(ws[0].shape[1:])                  # (K,) for matrices, () for bias vectors
+    assert all(tuple(w.shape[1:]) == tail for w in ws)
     rows = sum(w.shape[0] for w in ws)
-    base = names[0].rsplit(".", 2)[0]
-    name = f"cat/{base}.{tag}.weight"
-    g.value(name, (rows, k), ws[0].dtype, "derived",
+    base, kind = names[0].rsplit(".", 2)[0], names[0].rsplit(".", 1)[1]
+    name = f"cat/{base}.{tag}.{kind}"
+    g.value(name, (rows,) + tail, ws[0].dtype, "derived",
             meta=dict(op="cat", axis=0, parts=list(names), shard_axis=ws[0].shard_axis),
             shard_axis=ws[0].shard_axis)
     return name
@@ -72,10 +72,14 @@ def rule_qkv_fuse(g: Graph, sites: list) -> bool:
         v = next((m for m in sib if m.inputs[1].endswith("v_proj.weight")), None)
         if k is None or v is None:
             continue
+        nb = sum(len(x.inputs) > 2 for x in (n, k, v))
+        if nb not in (0, 3):
+            continue
         w = _cat_weight(g, [n.inputs[1], k.inputs[1], v.inputs[1]], "qkv_proj")
+        bias = [_cat_weight(g, [n.inputs[2], k.inputs[2], v.inputs[2]], "qkv_proj")] if nb else []
         widths = [g.values[x.outputs[0]].shape[1] for x in (n, k, v)]
         y = g.tmp("qkv", (R, sum(widths)))
-        fused = Node("linear", [h, w], [y], dict(split=widths), n.layer, "qkv-fuse")
+        fused = Node("linear", [h, w] + bias, [y], dict(split=widths), n.layer, "qkv-fuse")
         views = []
         ofs = 0
         for x, wd in zip((n, k, v), widths):

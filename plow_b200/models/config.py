@@ -2,9 +2,11 @@
 
 Families understood (by ``model_type`` / ``architectures``):
 
-* dense GQA decoders without projection biases: llama, mistral, qwen3 (per-head q/k RMSNorm), gemma (``1+γ`` norms, GELU
-  gate), gemma3_text (four norms per layer, local / global layers with their own rotary base); qwen2 (q / k / v biases)
-  and gemma2 (capped logits) are refused by name;
+* dense GQA decoders: llama, mistral, qwen3 (per-head q/k RMSNorm), qwen2 (biases on q / k / v), llama-shaped models with
+  ``attention_bias`` (o_proj too), gemma (``1+γ`` norms, GELU gate), gemma3_text (four norms per layer, local / global
+  layers with their own rotary base); ``mlp_bias`` and gemma2 (capped logits) are refused by name.  The reference folds
+  qwen2 into its qwen3 emitter with ``qkv_bias`` set (crates/nn-graph/src/models/config/mod.rs:233-248) and carries the
+  bias as operand 7 of its GEMM (runtime/common/dev_isa.h:114-120);
 * MLA + MoE decoders: deepseek_v3 / deepseek_v2, kimi_k2, glm_moe_dsa (adds the DSA indexer);
 * hybrid linear-attention MoE decoders: qwen3_next (gated delta rule + gated full attention);
 * GQA + MoE decoders: qwen3_moe (per-head q/k norm, softmax router) and mixtral (experts named w1 / w3 / w2 under
@@ -40,6 +42,8 @@ class AttnSpec:
     gated: bool = False           # per-head output gate (qwen3_next full attention)
     scale: float = 0.0            # softmax scale when it is not head_dim^-0.5 (gemma3: query_pre_attn_scalar^-0.5)
     rope_theta: float = 0.0       # rotary base of this layer when it differs from the model's (gemma3 local layers)
+    qkv_bias: bool = False        # q / k / v projections carry a bias (qwen2; llama-style attention_bias)
+    o_bias: bool = False          # the output projection carries one too (attention_bias)
     # MLA
     q_lora: int = 0
     kv_lora: int = 0
@@ -205,10 +209,12 @@ def _quant(cfg: dict) -> str:
 
 def spec_from_config(cfg: dict) -> ModelSpec:
     mt = cfg.get("model_type", "")
-    if mt == "qwen2" or cfg.get("attention_bias") or cfg.get("mlp_bias"):
-        raise ValueError(f"model_type '{mt}': projection biases are not supported (qwen2 always carries them on q / k / v); "
-                         "dropping them would compute a different model")
-    if mt in ("llama", "mistral", "qwen3", "gemma", "plow_dense"):
+    if cfg.get("mlp_bias") or (cfg.get("attention_bias") and mt not in ("llama", "mistral", "qwen3", "plow_dense")):
+        raise ValueError(f"model_type '{mt}': this projection bias is not supported (attention biases are, on llama-shaped models and "
+                         "qwen2); dropping it would compute a different model")
+    if mt == "qwen2" and cfg.get("use_sliding_window"):
+        raise ValueError("qwen2 with use_sliding_window is not supported: its window covers only the layers above max_window_layers")
+    if mt in ("llama", "mistral", "qwen2", "qwen3", "gemma", "plow_dense"):
         return _dense_gqa(cfg, mt)
     if mt in ("gemma3_text", "gemma3"):
         return _gemma3(cfg.get("text_config", cfg) if mt == "gemma3" else cfg, "gemma3_text")
@@ -243,7 +249,8 @@ def _dense_gqa(cfg: dict, mt: str) -> ModelSpec:
     hd = cfg.get("head_dim") or h // nh
     n_layers = cfg["num_hidden_layers"]
     attn = AttnSpec(kind="gqa", n_heads=nh, n_kv_heads=nkv, head_dim=hd, qk_norm=(mt == "qwen3" or cfg.get("qk_norm", False)),
-                    window=int(cfg.get("sliding_window") or 0) if cfg.get("use_sliding_window", mt == "mistral") else 0)
+                    window=int(cfg.get("sliding_window") or 0) if cfg.get("use_sliding_window", mt == "mistral") else 0,
+                    qkv_bias=(mt == "qwen2" or bool(cfg.get("attention_bias"))), o_bias=bool(cfg.get("attention_bias")) and mt != "qwen2")
     ffn = FfnSpec(kind="dense", inter=cfg["intermediate_size"], act=_act(cfg))
     gem = mt.startswith("gemma")
     return ModelSpec(

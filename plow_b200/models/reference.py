@@ -74,7 +74,9 @@ class ReferenceModel:
         self._ropes = {}             # rotary tables of layers with a base of their own
 
     def lin(self, x, name):
-        return x @ self.w[name].t()
+        y = x @ self.w[name].t()
+        b = self.w.get(name[:-len("weight")] + "bias") if name.endswith("weight") else None
+        return y if b is None else y + b
 
     @torch.no_grad()
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
@@ -322,6 +324,8 @@ def param_shapes(spec: ModelSpec) -> dict:
             s[f"{p}.self_attn.k_proj.weight"] = (a.n_kv_heads * a.head_dim, H)
             s[f"{p}.self_attn.v_proj.weight"] = (a.n_kv_heads * a.head_dim, H)
             s[f"{p}.self_attn.o_proj.weight"] = (H, a.n_heads * a.head_dim)
+            for proj in (("q_proj", "k_proj", "v_proj") if a.qkv_bias else ()) + (("o_proj",) if a.o_bias else ()):
+                s[f"{p}.self_attn.{proj}.bias"] = (s[f"{p}.self_attn.{proj}.weight"][0],)
             if a.qk_norm:
                 s[f"{p}.self_attn.q_norm.weight"] = (a.head_dim,)
                 s[f"{p}.self_attn.k_norm.weight"] = (a.head_dim,)
@@ -384,6 +388,8 @@ def random_state(spec: ModelSpec, seed: int = 0, std: float = 0.02, dtype=torch.
             t = torch.log(torch.rand(shape, generator=g) * 15 + 1)
         elif name.endswith("dt_bias"):
             t = torch.rand(shape, generator=g)
+        elif name.endswith("proj.bias"):
+            t = torch.randn(shape, generator=g) * 0.3
         else:
             t = torch.randn(shape, generator=g) * std
         out[name] = t.to(dtype if t.dim() > 1 and not name.endswith("conv1d.weight") else torch.float32)

@@ -199,6 +199,9 @@ class GpuEngine(EngineBase):
                or ins.op == Op.GLU and ins.i[0] for p in pkt.programs for ins in p.insts):
             raise EngineError("this packet's gated MLP uses a GELU gate: the sm_100a GEMM epilogue and GLU row op implement SiLU only "
                               "(the CPU backend runs it)", fatal=True)
+        if any(ins.op in (Op.GEMM, Op.GEMM_XREDUCE) and ins.i[2] & pk.GEMM_BIAS for p in pkt.programs for ins in p.insts):
+            raise EngineError("this packet's projections carry biases: the sm_100a GEMM epilogue has no bias term (the CPU backend runs it)",
+                              fatal=True)
         from .fp8_dir import Fp8Dir, fp8_weight_handles
         fp8_handles = fp8_weight_handles(pkt, self.spec.weight_quant)
         if isinstance(self.weights, CheckpointWeights) and self.weights.twins is None and getattr(self, "assets_dir", None):

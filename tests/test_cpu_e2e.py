@@ -544,7 +544,7 @@ def test_gqa_moe_families_on_cpu_backend_match_reference(tmp_path, model_type):
 def test_gelu_gated_model_runs_on_cpu_and_unsupported_shapes_are_refused(tmp_path):
     """A gemma-style decoder (GELU-tanh gate, (1 + gamma) norms, scaled embeddings, one kv head of width 128): the gate's
     activation travels as a flag of the fused GEMM (and of the GLU row op when the fusion is off) and the logits match the
-    fp32 reference.  Model types whose layers this compiler would misread (gemma2, qwen2) and unknown activations are
+    fp32 reference.  Model types whose layers this compiler would misread (gemma2, biased MLPs) and unknown activations are
     refused by name instead of being computed as something else."""
     import glob
     from safetensors.torch import load_file
@@ -558,7 +558,8 @@ def test_gelu_gated_model_runs_on_cpu_and_unsupported_shapes_are_refused(tmp_pat
     spec = config.spec_from_config(cfg)
     assert spec.layers[0].ffn.act == "gelu_tanh" and spec.norm_plus_one and spec.embed_scale == 16.0
     for bad in (dict(cfg, model_type="gemma2"), dict(cfg, hidden_act="relu2"),
-                dict(cfg, model_type="qwen2"), dict(cfg, model_type="llama", hidden_act="silu", attention_bias=True)):
+                dict(cfg, model_type="gemma", attention_bias=True), dict(cfg, model_type="llama", hidden_act="silu", mlp_bias=True),
+                dict(cfg, model_type="qwen2", hidden_act="silu", use_sliding_window=True)):
         with pytest.raises(ValueError, match="not supported|unsupported"):
             config.spec_from_config(bad)
     with pytest.raises(ValueError, match="routed experts"):
@@ -591,6 +592,62 @@ def test_gelu_gated_model_runs_on_cpu_and_unsupported_shapes_are_refused(tmp_pat
                                 want_logits=True))
         eng.close()
         assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item()), out
+
+
+@pytest.mark.parametrize("mt", ["qwen2", "llama"])
+def test_projection_biases_run_on_cpu(tmp_path, mt):
+    """qwen2 (biases on q / k / v) and a llama-shaped model with attention_bias (o_proj too): the biases ride the fused qkv
+    GEMM as a concatenated vector (flag + operand 7) and the output projection's GEMM; prefill and decode logits match the
+    fp32 reference, which differs from the same weights without biases.  Also on the AVX-512 and AMX GEMM bodies."""
+    import glob
+    from safetensors.torch import load_file
+    from plow_b200 import plowc
+    from plow_b200.compiler import packet as pk
+    from plow_b200.models import config, reference
+    from plow_b200.ops import native
+    from plow_b200.runtime.engine import TokenBatch
+    cfg = dict(model_type=mt, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=2, intermediate_size=512,
+               hidden_act="silu", rms_norm_eps=1e-6, rope_theta=10000.0, vocab_size=512, tie_word_embeddings=False,
+               max_position_embeddings=1024, eos_token_id=1, plow_dtype="f32", plow_kv_dtype="f32")
+    if mt == "llama":
+        cfg["attention_bias"] = True
+    spec = config.spec_from_config(cfg)
+    assert spec.layers[0].attn.qkv_bias and spec.layers[0].attn.o_bias == (mt == "llama")
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=3)
+    state = {}
+    for f in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        state.update(load_file(f))
+    nb = [k for k in state if k.endswith("proj.bias")]
+    assert len(nb) == 2 * (4 if mt == "llama" else 3) and all(state[k].abs().max() > 0.1 for k in nb)
+    ref = reference.ReferenceModel(spec, state)
+    p = np.random.default_rng(7).integers(0, 512, 40).tolist()
+    want = ref.forward(torch.tensor(p + [5]))
+    nobias = reference.ReferenceModel(spec, {k: v for k, v in state.items() if k not in nb}).forward(torch.tensor(p))[-1]
+    assert (want[len(p) - 1] - nobias).abs().max() > 1e-2
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", arch="cpu", n_cu=4, max_rows=128, decode_rungs=[1], max_seqs=4)
+    pkt = pk.read_packet(tmp_path / "assets" / "model.pkt")
+    biased = [i for i in pkt.programs[0].insts if i.op == pk.Op.GEMM and i.i[2] & pk.GEMM_BIAS]
+    assert len(biased) == 2 * (2 if mt == "llama" else 1) and all(i.t[7] != pk.T_NONE for i in biased)
+    assert any(t.name.endswith("qkv_proj.bias") for t in pkt.tensors)
+    lib = native.cpu_lib()
+    start = lib.plow_cpu_tier()
+    try:
+        for tier, tol in ((0, 2e-4), (1, 2e-4), (2, 2e-4), (3, 5e-2)):
+            if lib.plow_cpu_set_tier(tier) != tier:
+                continue
+            eng = CpuEngine(tmp_path / "assets", max_slots=2, max_ctx=256)
+            eng.begin_slot(0, p)
+            eng.reserve(0, 64)
+            r = eng.step(TokenBatch(np.asarray(p, np.int32), np.arange(40, dtype=np.int32), np.zeros(40, np.int32), np.asarray([39], np.int32),
+                                    want_logits=True))
+            d = eng.step(TokenBatch(np.asarray([5], np.int32), np.asarray([40], np.int32), np.zeros(1, np.int32), np.asarray([0], np.int32),
+                                    want_logits=True))
+            eng.close()
+            scale = max(1.0, want.abs().max().item())
+            assert (torch.from_numpy(r.logits[0]) - want[39]).abs().max().item() < tol * scale, tier
+            assert (torch.from_numpy(d.logits[0]) - want[40]).abs().max().item() < tol * scale, tier
+    finally:
+        lib.plow_cpu_set_tier(start)
 
 
 def test_mla_under_yarn_scales_its_softmax(tmp_path):
