@@ -42,7 +42,8 @@ typedef enum PlowOp {
   PLOW_OP_ROPE_KV = 5,        /* t0=q out t1=fused qkv rows t2=kcache t3=vcache t4=qnorm(opt) t5=knorm(opt) t6=rope table
                                  t7=gate out (i7=1: query heads are [Q | gate] pairs) or the e4m3 cache's scales [P,64,2*nkv]
                                  i0=nq i1=nkv i2=hd i3=rot_dim i4=pair_mode i5=layer i6=gamma_mode i7=gated ; f0=eps */
-  PLOW_OP_ATTN = 6,           /* t0=out t1=q t2=kcache t3=vcache t4=e4m3 cache scales (opt) ;
+  PLOW_OP_ATTN = 6,           /* t0=out t1=q t2=kcache t3=vcache t4=e4m3 cache scales (opt) t5=sinks [nq] f32 (opt: one extra
+                                 logit per head in every softmax, no value) ;
                                  i0=nq i1=nkv i2=hd i3=window i4=mode i5=layer; f0=scale */
   PLOW_OP_ROW_GATHER = 7,     /* t0=out[nsample,H] t1=x t2=in.sample_rows */
   PLOW_OP_ARGMAX = 8,         /* t0=out.ids t1=logits ; i0=V */

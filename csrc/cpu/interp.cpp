@@ -590,6 +590,7 @@ void op_attn(const Ctx& c) {
   const float* vc = (const float*)c.T(3);
   const int nq = c.in->i[0], nkv = c.in->i[1], hd = c.in->i[2], window = c.in->i[3];
   const float scale = c.in->w[0].f;
+  const float* sinks = (const float*)c.T(5);      // optional: a logit per head that joins the softmax and carries no value
   const StepIO& io = c.e->io;
   const int group = nq / nkv;
   std::vector<float> sc;
@@ -611,7 +612,8 @@ void op_attn(const Ctx& c) {
       sc[t - t0] = s;
       mx = std::max(mx, s);
     }
-    float den = 0.f;
+    if (sinks) mx = std::max(mx, sinks[h]);
+    float den = sinks ? std::exp(sinks[h] - mx) : 0.f;
     for (int i = 0; i < n; ++i) { sc[i] = std::exp(sc[i] - mx); den += sc[i]; }
     float* o = out + (r * nq + h) * hd;
     for (int d = 0; d < hd; ++d) o[d] = 0.f;
@@ -990,6 +992,9 @@ void op_moe(const Ctx& c) {
   const float* w1 = (const float*)c.T(3);      // [E][2F][H]: gate rows then up rows per expert
   const float* w2 = (const float*)c.T(4);      // [E][H][F]
   const float* shared = (const float*)c.T(5);
+  const float* b1 = (const float*)c.T(6);      // optional [E][2F]: gate biases then up biases per expert
+  const float* b2 = (const float*)c.T(7);      // optional [E][H]
+  const float limit = c.in->w[0].f, alpha = c.in->w[1].f;   // limit > 0: (up + 1) * g * sigmoid(alpha * g), clamped
   const int K = c.in->i[2], F = c.in->i[3];
   // i[6]: the shared expert is stacked behind the e_local routed ones and applies to every row with gate 1;
   // it is added first, where the separately computed shared output would have been
@@ -1013,11 +1018,18 @@ void op_moe(const Ctx& c) {
       const float* wg = w1 + int64_t(e) * 2 * F * H;
       const float* wu = wg + int64_t(F) * H;
       for (int f = 0; f < F; ++f) {
-        const float gv = dotf(wg + int64_t(f) * H, x, H), uv = dotf(wu + int64_t(f) * H, x, H);
-        glu[f] = gv / (1.0f + std::exp(-gv)) * uv;
+        float gv = dotf(wg + int64_t(f) * H, x, H), uv = dotf(wu + int64_t(f) * H, x, H);
+        if (b1) { gv += b1[int64_t(e) * 2 * F + f]; uv += b1[int64_t(e) * 2 * F + F + f]; }
+        if (limit > 0.f) {
+          gv = std::min(gv, limit);
+          uv = std::max(-limit, std::min(uv, limit));
+          glu[f] = (uv + 1.0f) * gv / (1.0f + std::exp(-alpha * gv));
+        } else {
+          glu[f] = gv / (1.0f + std::exp(-gv)) * uv;
+        }
       }
       const float* wd = w2 + int64_t(e) * H * F;
-      for (int j = 0; j < H; ++j) acc[j] += gate * dotf(wd + int64_t(j) * F, glu.data(), F);
+      for (int j = 0; j < H; ++j) acc[j] += gate * (dotf(wd + int64_t(j) * F, glu.data(), F) + (b2 ? b2[int64_t(e) * H + j] : 0.f));
     }
     for (int j = 0; j < H; ++j) y[r * H + j] = acc[j];
   }

@@ -155,7 +155,8 @@ class Lowering:
                 q, kc, vc = n.inputs
                 mode = pk.ATTN_DECODE if role == pk.Role.DECODE else pk.ATTN_CAUSAL
                 ins = pk.Inst(Op.ATTN, f=(a["scale"], 0, 0), t=[self.t(n.outputs[0]), self.t(q), self.t(kc), self.t(vc)]
-                              + ([self.t(a["kv_scales"])] if a.get("kv_scales") else []),
+                              + ([self.t(a.get("kv_scales")), self.t(a["sinks"])] if a.get("sinks") else
+                                 [self.t(a["kv_scales"])] if a.get("kv_scales") else []),
                               i=[a["heads"], a["kv_heads"], a["head_dim"], a.get("window", 0), mode, n.layer])
                 cost = costmodel.attention_decode_cost(rows * 2048, a["heads"], a["kv_heads"], a["head_dim"], a["head_dim"], es) \
                     if role == pk.Role.DECODE else costmodel.attention_prefill_cost(rows, rows, a["heads"], a["head_dim"], a["head_dim"])
@@ -202,7 +203,8 @@ class Lowering:
         "dsa_k_write": (Op.DSA_INDEX, ["dim", "rot_dim"], [], "row"),
         "dsa_topk": (Op.DSA_TOPK, ["heads", "dim", "topk", "rot_dim"], [], "attn"),
         "router_topk": (Op.ROUTER_TOPK, ["n_experts", "top_k", "n_group", "topk_group", "score", "norm_topk"], ["route_scale"], "row"),
-        "moe_experts": (Op.MOE_GEMM, ["n_experts", "e_local", "top_k", "inter", "ep", "has_shared", "shared_group"], [], "gemm"),
+        "moe_experts": (Op.MOE_GEMM, ["n_experts", "e_local", "top_k", "inter", "ep", "has_shared", "shared_group"],
+                        ["swiglu_limit", "swiglu_alpha"], "gemm"),
         "gdn": (Op.GDN_STEP, ["k_heads", "v_heads", "head_dim", "conv"], [], "attn"),
         "gated_norm": (Op.GATED_NORM, ["heads", "head_dim", "z_offset"], ["eps"], "row"),
         "sigmoid_gate": (Op.SIGMOID_GATE, [], [], "row"),
@@ -233,6 +235,8 @@ class Lowering:
         handles = [self.t(x) for x in (n.outputs + n.inputs)][:8]
         ivals = ([iv(k) for k in ikeys] + [0] * 7)[:7]
         fvals = [float(n.attrs.get(k, 0.0)) for k in fkeys] + [0.0] * (3 - len(fkeys))
+        if n.op == "moe_experts" and n.attrs.get("bias1"):
+            handles = (handles + [pk.T_NONE] * 6)[:6] + [self.t(n.attrs["bias1"]), self.t(n.attrs["bias2"])]
         if n.op == "mla_kv_write":
             # the latent row is usually a column range of the fused [q_a | kv_a] projection
             ivals[5], ivals[6] = self.xview(n.inputs[0])

@@ -266,8 +266,9 @@ def _gqa_attention(g: Graph, li, p, h, a) -> str:
     ksc = g.value(f"kv.{li}.s", ("P", 64, 2 * nkv), "f32", "kv") if spec.kv_dtype == "fp8" else None
     g.add("kv_write", [kr, v, "in.pos", "in.seq"], [kc, vc], layer=li, heads=nkv, head_dim=hd, kv_scales=ksc)
     ao = g.tmp("attn", (R, nq * hd))
+    sinks = g.weight(f"{p}.self_attn.sinks", (nq,), shard_axis=0, dtype="f32") if a.sinks else None
     g.add("attention", [qr, kc, vc], [ao], layer=li, heads=nq, kv_heads=nkv, head_dim=hd, window=a.window,
-          scale=a.scale or hd ** -0.5, kv_scales=ksc)
+          scale=a.scale or hd ** -0.5, kv_scales=ksc, sinks=sinks)
     if gate is not None:
         ag = g.tmp("attn", (R, nq * hd))
         g.add("sigmoid_gate", [ao, gate], [ag], layer=li)
@@ -355,6 +356,8 @@ def _moe_ffn(g: Graph, li, p, h, f) -> str:
     H = spec.hidden
     E, k, F = f.n_experts, f.top_k, f.moe_inter
     e_local = E // ep
+    if f.fused_experts:
+        return _moe_fused_experts(g, li, p, h, f)
     gate_w = g.weight(f"{p}.gate.weight", (E, H), dtype="f32" if spec.dtype == "f32" else "bf16")
     logits = g.tmp("router", (R, E), "f32")
     g.add("linear", [h, gate_w], [logits], layer=li, out_f32=True, router=True)
@@ -377,6 +380,34 @@ def _moe_ffn(g: Graph, li, p, h, f) -> str:
                             h, F * f.n_shared)
     g.add("moe_experts", [h, table, w1, w2] + ([shared] if shared else []), [y], layer=li, n_experts=E,
           e_local=e_local, top_k=k, inter=F, ep=ep, has_shared=bool(shared))
+    return y
+
+
+def _moe_fused_experts(g: Graph, li, p, h, f) -> str:
+    """gpt_oss experts: a biased router, then experts that live in one checkpoint tensor per projection.  The derived
+    tensors bring them into the stacked layout the expert op reads (per expert: gate rows, up rows | down rows) and the
+    biases into the same order; the op's two float operands carry the GLU's clamp and its sigmoid slope."""
+    spec, ep = g.spec, g.ep
+    H = spec.hidden
+    E, k, F = f.n_experts, f.top_k, f.moe_inter
+    e_local = E // ep
+    logits = _linear(g, li, h, f"{p}.router.weight", E, H, bias=True, out_f32=True, router=True)
+    table = g.tmp("route", (R, k, 2), "i32")
+    g.add("router_topk", [logits], [table], layer=li, n_experts=E, top_k=k, n_group=1, topk_group=1, score=f.score,
+          norm_topk=f.norm_topk, route_scale=f.route_scale)
+
+    def derived(tag, shape, kind, src, dtype=None):
+        return g.value(f"cat/{p}.experts.{tag}", shape, dtype or g.weight_dtype(), "derived",
+                       meta=dict(op="fused_experts", kind=kind, src=f"{p}.experts.{src}", n=E, ep=ep, rank=g.rank))
+
+    bdt = "f32" if spec.dtype == "f32" else "bf16"
+    w1 = derived("gate_up.weight", (e_local * 2 * F, H), "gate_up", "gate_up_proj")
+    w2 = derived("down.weight", (e_local * H, F), "down", "down_proj")
+    b1 = derived("gate_up.bias", (e_local * 2 * F,), "gate_up_bias", "gate_up_proj_bias", bdt)
+    b2 = derived("down.bias", (e_local * H,), "down_bias", "down_proj_bias", bdt)
+    y = g.tmp("moe", (R, H))
+    g.add("moe_experts", [h, table, w1, w2], [y], layer=li, n_experts=E, e_local=e_local, top_k=k, inter=F, ep=ep,
+          has_shared=False, bias1=b1, bias2=b2, swiglu_limit=f.swiglu_limit, swiglu_alpha=f.swiglu_alpha)
     return y
 
 

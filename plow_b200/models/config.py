@@ -9,8 +9,9 @@ Families understood (by ``model_type`` / ``architectures``):
   bias as operand 7 of its GEMM (runtime/common/dev_isa.h:114-120);
 * MLA + MoE decoders: deepseek_v3 / deepseek_v2, kimi_k2, glm_moe_dsa (adds the DSA indexer);
 * hybrid linear-attention MoE decoders: qwen3_next (gated delta rule + gated full attention);
-* GQA + MoE decoders: qwen3_moe (per-head q/k norm, softmax router) and mixtral (experts named w1 / w3 / w2 under
-  ``block_sparse_moe``).
+* GQA + MoE decoders: qwen3_moe (per-head q/k norm, softmax router), mixtral (experts named w1 / w3 / w2 under
+  ``block_sparse_moe``) and gpt_oss (attention sinks, biased projections / router / experts, clamped GLU, sliding and
+  full layers in turn; bf16 export only).
 
 The reference derives the same plan in crates/plowc/src/hf_config.rs (LayerPlan from config.json)
 and dispatches emitters on ``model_type`` in crates/devgen/src/lib.rs:9518-9646.
@@ -44,6 +45,7 @@ class AttnSpec:
     rope_theta: float = 0.0       # rotary base of this layer when it differs from the model's (gemma3 local layers)
     qkv_bias: bool = False        # q / k / v projections carry a bias (qwen2; llama-style attention_bias)
     o_bias: bool = False          # the output projection carries one too (attention_bias)
+    sinks: bool = False           # one learned logit per head joins every softmax and takes no value (gpt_oss)
     # MLA
     q_lora: int = 0
     kv_lora: int = 0
@@ -78,6 +80,12 @@ class FfnSpec:
     has_bias: bool = False        # e_score_correction_bias
     block: str = "mlp"            # module that holds the router and the experts (mixtral: block_sparse_moe)
     expert_names: str = "proj"    # "proj": gate_proj / up_proj / down_proj; "w123": w1 (gate) / w3 (up) / w2 (down)
+    # gpt_oss: all experts in one tensor per projection (gate_up_proj [E, H, 2F] with gate / up columns interleaved,
+    # down_proj [E, F, H]) with biases, a biased router named `router`, and the clamped GLU
+    # (up + 1) * g * sigmoid(alpha * g), g = min(gate, limit), up clamped to +-limit
+    fused_experts: bool = False
+    swiglu_limit: float = 0.0
+    swiglu_alpha: float = 1.702
 
 
 @dataclass
@@ -216,6 +224,8 @@ def spec_from_config(cfg: dict) -> ModelSpec:
         raise ValueError("qwen2 with use_sliding_window is not supported: its window covers only the layers above max_window_layers")
     if mt in ("llama", "mistral", "qwen2", "qwen3", "gemma", "plow_dense"):
         return _dense_gqa(cfg, mt)
+    if mt == "gpt_oss":
+        return _gpt_oss(cfg)
     if mt in ("gemma3_text", "gemma3"):
         return _gemma3(cfg.get("text_config", cfg) if mt == "gemma3" else cfg, "gemma3_text")
     if mt == "gemma2":
@@ -348,6 +358,39 @@ def _gqa_moe(cfg: dict, mt: str) -> ModelSpec:
         max_ctx=int(cfg.get("max_position_embeddings", 4096)), bos_token_id=cfg.get("bos_token_id"), eos_token_ids=_eos(cfg))
 
 
+def _gpt_oss(cfg: dict) -> ModelSpec:
+    """gpt_oss: GQA with biased projections and per-head attention sinks, sliding-window and full layers in turn, YaRN
+    rotary tables, and a routed MoE in every layer whose experts are biased and use the clamped GLU.  Only the bf16 export
+    is read: the MXFP4 expert blocks of the original release are refused.  Reference emitter: crates/devgen/src/gptoss.rs."""
+    q = cfg.get("quantization_config") or {}
+    if q.get("quant_method") == "mxfp4":
+        raise ValueError("gpt_oss checkpoints with MXFP4 expert blocks are not supported: convert the experts to bf16 "
+                         "(gate_up_proj / down_proj tensors) first")
+    h = cfg["hidden_size"]
+    nh = cfg["num_attention_heads"]
+    nkv = cfg.get("num_key_value_heads", nh)
+    hd = cfg.get("head_dim") or h // nh
+    n_layers = cfg["num_hidden_layers"]
+    win = int(cfg.get("sliding_window") or 0)
+    kinds = cfg.get("layer_types") or ["sliding_attention" if i % 2 == 0 else "full_attention" for i in range(n_layers)]
+    if len(kinds) != n_layers or any(k not in ("sliding_attention", "full_attention") for k in kinds):
+        raise ValueError("gpt_oss: layer_types must name sliding_attention or full_attention for every layer")
+
+    def attn(kind):
+        return AttnSpec(kind="gqa", n_heads=nh, n_kv_heads=nkv, head_dim=hd, window=win if kind == "sliding_attention" else 0,
+                        qkv_bias=True, o_bias=True, sinks=True)
+
+    moe = FfnSpec(kind="moe", n_experts=cfg["num_local_experts"], top_k=cfg.get("num_experts_per_tok") or cfg["experts_per_token"],
+                  moe_inter=cfg["intermediate_size"], score="softmax", norm_topk=True, fused_experts=True,
+                  swiglu_limit=float(cfg.get("swiglu_limit", 7.0)))
+    return ModelSpec(
+        family="gqa_moe", model_type="gpt_oss", hidden=h, vocab=cfg["vocab_size"], n_layers=n_layers,
+        rms_eps=float(cfg.get("rms_norm_eps", 1e-5)), tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+        rope=_rope_from(cfg, hd), layers=[LayerSpec(attn(k), moe) for k in kinds],
+        dtype=cfg.get("plow_dtype", "bf16"), weight_quant="none", kv_dtype=cfg.get("plow_kv_dtype", cfg.get("plow_dtype", "bf16")),
+        max_ctx=int(cfg.get("max_position_embeddings", 4096)), bos_token_id=cfg.get("bos_token_id"), eos_token_ids=_eos(cfg))
+
+
 def _gdn_hybrid(cfg: dict, mt: str) -> ModelSpec:
     h = cfg["hidden_size"]
     n_layers = cfg["num_hidden_layers"]
@@ -410,6 +453,15 @@ def mixtral_8x7b_config() -> dict:
     return dict(model_type="mixtral", hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
                 num_local_experts=8, num_experts_per_tok=2, intermediate_size=14336, rms_norm_eps=1e-5, rope_theta=1000000.0,
                 vocab_size=32000, tie_word_embeddings=False, max_position_embeddings=32768, eos_token_id=2)
+
+
+def gpt_oss_120b_config() -> dict:
+    return dict(model_type="gpt_oss", hidden_size=2880, num_hidden_layers=36, num_attention_heads=64, num_key_value_heads=8, head_dim=64,
+                num_local_experts=128, num_experts_per_tok=4, intermediate_size=2880, sliding_window=128, swiglu_limit=7.0,
+                layer_types=["sliding_attention" if i % 2 == 0 else "full_attention" for i in range(36)], rms_norm_eps=1e-5,
+                rope_theta=150000.0, rope_scaling=dict(rope_type="yarn", factor=32.0, beta_fast=32.0, beta_slow=1.0,
+                                                       original_max_position_embeddings=4096, truncate=False),
+                vocab_size=201088, tie_word_embeddings=False, max_position_embeddings=131072, eos_token_id=200002)
 
 
 def gdn_hybrid_80b_config() -> dict:

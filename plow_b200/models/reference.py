@@ -40,9 +40,10 @@ def apply_rope(x, tab, pos, rot_dim, pair_mode):
     return torch.cat([out, xp], dim=-1)
 
 
-def causal_attention(q, k, v, scale, window=0, keep=None):
+def causal_attention(q, k, v, scale, window=0, keep=None, sinks=None):
     """q [T, nq, hd], k/v [T, nkv, hd(v)] -> [T, nq, hdv]; full causal mask (+ sliding window).  ``keep`` (bool [T, T],
-    optional): sparse attention, query t attends only the keys s with keep[t, s]."""
+    optional): sparse attention, query t attends only the keys s with keep[t, s].  ``sinks`` ([nq], optional): one more
+    logit per head in every row's softmax, whose probability is dropped."""
     T, nq, _ = q.shape
     nkv = k.shape[1]
     k = k.repeat_interleave(nq // nkv, dim=1)
@@ -55,7 +56,9 @@ def causal_attention(q, k, v, scale, window=0, keep=None):
     if window:
         mask = mask | (i[None, :] <= i[:, None] - window)
     s = s.masked_fill(mask[None], float("-inf"))
-    p = torch.softmax(s, dim=-1)
+    if sinks is not None:
+        s = torch.cat([s, sinks.float()[:, None, None].expand(nq, T, 1)], dim=-1)
+    p = torch.softmax(s, dim=-1)[..., :T]
     return torch.einsum("hts,shd->thd", p, v.float()).to(q.dtype)
 
 
@@ -163,7 +166,8 @@ class ReferenceModel:
             rope = self._ropes[a.rope_theta]
         q = apply_rope(q, rope, pos, spec.rope.rot_dim, spec.rope.pair_mode)
         k = apply_rope(k, rope, pos, spec.rope.rot_dim, spec.rope.pair_mode)
-        o = causal_attention(q, k, v, a.scale or a.head_dim ** -0.5, a.window).reshape(T, -1)
+        o = causal_attention(q, k, v, a.scale or a.head_dim ** -0.5, a.window,
+                             sinks=self.w[f"{p}.self_attn.sinks"] if a.sinks else None).reshape(T, -1)
         if gate is not None:
             o = o * torch.sigmoid(gate)
         return self.lin(o, f"{p}.self_attn.o_proj.weight")
@@ -241,7 +245,25 @@ class ReferenceModel:
             g = g / g.sum(-1, keepdim=True).clamp_min(1e-20)
         return idx, g * f.route_scale
 
+    def _moe_fused_experts(self, p, h, f):
+        """gpt_oss: biased router, softmax over the chosen logits, experts read from the per-projection tensors."""
+        logits = self.lin(h.float(), f"{p}.router.weight")
+        idx, g = self.route(logits, f, None)
+        gu, gub = self.w[f"{p}.experts.gate_up_proj"].float(), self.w[f"{p}.experts.gate_up_proj_bias"].float()
+        dn, dnb = self.w[f"{p}.experts.down_proj"].float(), self.w[f"{p}.experts.down_proj_bias"].float()
+        out = torch.zeros_like(h, dtype=torch.float32)
+        for j in range(f.top_k):
+            for e in idx[:, j].unique().tolist():
+                m = idx[:, j] == e
+                y = h[m].float() @ gu[e] + gub[e]
+                gate, up = y[:, 0::2].clamp(max=f.swiglu_limit), y[:, 1::2].clamp(-f.swiglu_limit, f.swiglu_limit)
+                act = (up + 1.0) * gate * torch.sigmoid(f.swiglu_alpha * gate)
+                out[m] += g[m, j, None] * (act @ dn[e] + dnb[e])
+        return out.to(h.dtype)
+
     def _moe(self, p, h, f):
+        if f.fused_experts:
+            return self._moe_fused_experts(p, h, f)
         bias = self.w.get(f"{p}.gate.e_score_correction_bias")
         logits = h.float() @ self.w[f"{p}.gate.weight"].float().t()
         idx, g = self.route(logits, f, bias)
@@ -326,6 +348,8 @@ def param_shapes(spec: ModelSpec) -> dict:
             s[f"{p}.self_attn.o_proj.weight"] = (H, a.n_heads * a.head_dim)
             for proj in (("q_proj", "k_proj", "v_proj") if a.qkv_bias else ()) + (("o_proj",) if a.o_bias else ()):
                 s[f"{p}.self_attn.{proj}.bias"] = (s[f"{p}.self_attn.{proj}.weight"][0],)
+            if a.sinks:
+                s[f"{p}.self_attn.sinks"] = (a.n_heads,)
             if a.qk_norm:
                 s[f"{p}.self_attn.q_norm.weight"] = (a.head_dim,)
                 s[f"{p}.self_attn.k_norm.weight"] = (a.head_dim,)
@@ -359,6 +383,13 @@ def param_shapes(spec: ModelSpec) -> dict:
         if f.kind == "dense":
             for nm, shp in (("gate_proj", (f.inter, H)), ("up_proj", (f.inter, H)), ("down_proj", (H, f.inter))):
                 s[f"{p}.mlp.{nm}.weight"] = shp
+        elif f.fused_experts:
+            s[f"{p}.mlp.router.weight"] = (f.n_experts, H)
+            s[f"{p}.mlp.router.bias"] = (f.n_experts,)
+            s[f"{p}.mlp.experts.gate_up_proj"] = (f.n_experts, H, 2 * f.moe_inter)
+            s[f"{p}.mlp.experts.gate_up_proj_bias"] = (f.n_experts, 2 * f.moe_inter)
+            s[f"{p}.mlp.experts.down_proj"] = (f.n_experts, f.moe_inter, H)
+            s[f"{p}.mlp.experts.down_proj_bias"] = (f.n_experts, H)
         else:
             s[f"{p}.{f.block}.gate.weight"] = (f.n_experts, H)
             if f.has_bias:
@@ -388,7 +419,7 @@ def random_state(spec: ModelSpec, seed: int = 0, std: float = 0.02, dtype=torch.
             t = torch.log(torch.rand(shape, generator=g) * 15 + 1)
         elif name.endswith("dt_bias"):
             t = torch.rand(shape, generator=g)
-        elif name.endswith("proj.bias"):
+        elif name.endswith("proj.bias") or name.endswith("proj_bias") or name.endswith("router.bias") or name.endswith("sinks"):
             t = torch.randn(shape, generator=g) * 0.3
         else:
             t = torch.randn(shape, generator=g) * std

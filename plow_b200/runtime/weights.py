@@ -150,6 +150,19 @@ def materialize(name: str, ent, recipe: dict | None, ckpt: Checkpoint, tp: int =
         for name in recipe.get("tail", []):      # shared expert stacked behind the routed ones (replicated on every rank)
             rows.append(shard_slice(ckpt, name, None, 1, 0))
         return torch.cat(rows, dim=0).contiguous()
+    if recipe["op"] == "fused_experts":        # gpt_oss: every expert of a projection in one tensor
+        t = shard_slice(ckpt, recipe["src"], None, 1, 0)
+        t = t[list(expert_range(recipe["n"], recipe.get("ep", 1), recipe.get("rank", 0)))]
+        kind = recipe["kind"]
+        if kind == "gate_up":                  # [e, H, 2F], gate / up columns interleaved -> [e * (F gate rows + F up rows), H]
+            return torch.cat([t[:, :, 0::2].transpose(1, 2), t[:, :, 1::2].transpose(1, 2)], 1).reshape(-1, t.shape[1]).contiguous()
+        if kind == "down":                     # [e, F, H] -> [e * H, F]
+            return t.transpose(1, 2).reshape(-1, t.shape[1]).contiguous()
+        if kind == "gate_up_bias":             # [e, 2F] interleaved -> gate part then up part per expert
+            return torch.cat([t[:, 0::2], t[:, 1::2]], 1).reshape(-1).contiguous()
+        if kind == "down_bias":
+            return t.reshape(-1).contiguous()
+        raise ValueError(f"unknown fused-experts part '{kind}'")
     if recipe["op"] == "cols":                 # a column range of a checkpoint matrix (a half of eh_proj)
         if is_block_fp8(ckpt, recipe["src"]):
             return shard_slice(ckpt, recipe["src"], None, 1, 0)[:, recipe["start"]:recipe["stop"]].contiguous()

@@ -39,8 +39,11 @@ def inv_freq(theta: float, rot_dim: int, scaling: dict | None) -> tuple:
         def corr_dim(n_rot):
             return rot_dim * math.log(orig / (n_rot * 2.0 * math.pi)) / (2.0 * math.log(theta))
 
-        low = max(math.floor(corr_dim(beta_fast)), 0)
-        high = min(math.ceil(corr_dim(beta_slow)), half - 1)
+        lo_f, hi_f = corr_dim(beta_fast), corr_dim(beta_slow)
+        if scaling.get("truncate", True):           # gpt_oss sets truncate = false: the ramp's ends stay fractional
+            lo_f, hi_f = math.floor(lo_f), math.ceil(hi_f)
+        low = max(lo_f, 0)
+        high = min(hi_f, half - 1)
         ramp = np.clip((np.arange(half, dtype=np.float64) - low) / max(high - low, 1e-3), 0.0, 1.0)
         mask = 1.0 - ramp
         f = f / factor * (1.0 - mask) + f * mask

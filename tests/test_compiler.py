@@ -61,11 +61,14 @@ def test_tp_graph_has_fused_collectives():
                                        (lambda: config.mla_moe_671b_config(n_layers=4, dsa=True), dict(ep=8)),
                                        (config.gdn_hybrid_80b_config, dict(tp=2, ep=4)),
                                        (config.qwen3_moe_30b_config, dict(ep=8)),
-                                       (config.mixtral_8x7b_config, dict(ep=2))])
+                                       (config.mixtral_8x7b_config, dict(ep=2)),
+                                       (config.gpt_oss_120b_config, dict(ep=8))])
 def test_big_families_build_and_verify(cfg_fn, kw):
     cfg = cfg_fn()
     if "num_hidden_layers" in cfg and cfg["num_hidden_layers"] > 8:
         cfg["num_hidden_layers"] = 8
+        if "layer_types" in cfg:
+            cfg["layer_types"] = cfg["layer_types"][:8]
     spec = config.spec_from_config(cfg)
     g = graph.build_graph(spec, **kw)
     rewrite.fuse(g)
@@ -119,6 +122,17 @@ def test_rope_tables_scaling():
                                           beta_fast=32, beta_slow=1, mscale=1.0, mscale_all_dim=1.0))
     assert np.isfinite(l3).all() and np.isfinite(ya).all()
     assert not np.allclose(l3[5], rope_table(64, 64, 500000.0)[5])
+    # gpt_oss: YaRN whose ramp ends are not rounded (truncate = false), attention factor 0.1 ln(32) + 1 on cos and sin
+    import math
+    sc = dict(type="yarn", factor=32.0, beta_fast=32.0, beta_slow=1.0, original_max_position_embeddings=4096, truncate=False)
+    got = rope_table(8, 64, 150000.0, sc)
+    half, att = 32, 0.1 * math.log(32.0) + 1.0
+    base = 1.0 / 150000.0 ** (np.arange(half) * 2.0 / 64)
+    lo, hi = (64 * math.log(4096 / (b * 2 * math.pi)) / (2 * math.log(150000.0)) for b in (32.0, 1.0))
+    ramp = np.clip((np.arange(half) - lo) / (hi - lo), 0, 1)
+    f = base / 32.0 * ramp + base * (1 - ramp)
+    assert np.allclose(got[5, :half], np.cos(5 * f) * att, atol=1e-6) and np.allclose(got[5, half:], np.sin(5 * f) * att, atol=1e-6)
+    assert not np.allclose(got, rope_table(8, 64, 150000.0, dict(sc, truncate=True)))
 
 
 def test_device_interp_tables_build_on_cpu(tiny_assets):

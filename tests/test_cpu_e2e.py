@@ -650,6 +650,68 @@ def test_projection_biases_run_on_cpu(tmp_path, mt):
         lib.plow_cpu_set_tier(start)
 
 
+def test_gpt_oss_runs_on_cpu(tmp_path):
+    """gpt_oss: biased q / k / v / o projections, per-head attention sinks, a sliding-window layer beside a full one, YaRN
+    tables without truncation, a biased router with softmax over the chosen experts, and experts stored as one tensor per
+    projection (interleaved gate / up columns) with biases and the clamped GLU.  Prefill beyond the window and a decode
+    step match the fp32 reference; dropping the sinks or the clamp changes the reference, so the test sees both."""
+    import glob
+    from safetensors.torch import load_file
+    from plow_b200 import plowc
+    from plow_b200.compiler import packet as pk
+    from plow_b200.models import config, reference
+    from plow_b200.runtime.engine import TokenBatch
+    cfg = dict(model_type="gpt_oss", hidden_size=128, num_attention_heads=8, num_key_value_heads=2, head_dim=32, num_hidden_layers=2,
+               layer_types=["sliding_attention", "full_attention"], sliding_window=16, num_local_experts=8, num_experts_per_tok=2,
+               intermediate_size=64, swiglu_limit=1.0, rms_norm_eps=1e-5, rope_theta=150000.0, vocab_size=512, tie_word_embeddings=False,
+               rope_scaling=dict(rope_type="yarn", factor=32.0, beta_fast=32.0, beta_slow=1.0, original_max_position_embeddings=64,
+                                 truncate=False),
+               max_position_embeddings=2048, eos_token_id=1, plow_dtype="f32", plow_kv_dtype="f32")
+    spec = config.spec_from_config(cfg)
+    a0, a1, f = spec.layers[0].attn, spec.layers[1].attn, spec.layers[0].ffn
+    assert a0.window == 16 and a1.window == 0 and a0.sinks and a0.o_bias and f.fused_experts and f.swiglu_limit == 1.0
+    with pytest.raises(ValueError, match="MXFP4"):
+        config.spec_from_config(dict(cfg, quantization_config=dict(quant_method="mxfp4")))
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=11)
+    state = {}
+    for fn in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        state.update(load_file(fn))
+    # expert weights large enough that the clamp at 1.0 bites
+    from safetensors.torch import save_file
+    state = {k: (v * 20 if k.endswith("experts.gate_up_proj") else v) for k, v in state.items()}
+    for fn in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        save_file({k: state[k].contiguous() for k in load_file(fn)}, fn)
+    ref = reference.ReferenceModel(spec, state)
+    p = np.random.default_rng(9).integers(0, 512, 50).tolist()
+    want = ref.forward(torch.tensor(p + [7]))
+    import copy
+    nosink = copy.deepcopy(spec)
+    for l in nosink.layers:
+        l.attn.sinks = False
+    noclamp = copy.deepcopy(spec)
+    for l in noclamp.layers:
+        l.ffn.swiglu_limit = 1e9
+    for other in (nosink, noclamp):
+        assert (reference.ReferenceModel(other, state).forward(torch.tensor(p))[-1] - want[49]).abs().max() > 1e-3
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", arch="cpu", n_cu=4, max_rows=128, decode_rungs=[1], max_seqs=4)
+    pkt = pk.read_packet(tmp_path / "assets" / "model.pkt")
+    insts = pkt.programs[0].insts
+    assert all(i.t[5] != pk.T_NONE for i in insts if i.op == pk.Op.ATTN)
+    assert all(i.t[6] != pk.T_NONE and i.t[7] != pk.T_NONE and i.f[0] == 1.0 for i in insts if i.op == pk.Op.MOE_GEMM)
+    assert sorted(i.i[3] for i in insts if i.op == pk.Op.ATTN) == [0, 16]
+    eng = CpuEngine(tmp_path / "assets", max_slots=2, max_ctx=256)
+    eng.begin_slot(0, p)
+    eng.reserve(0, 64)
+    r = eng.step(TokenBatch(np.asarray(p, np.int32), np.arange(50, dtype=np.int32), np.zeros(50, np.int32), np.asarray([49], np.int32),
+                            want_logits=True))
+    d = eng.step(TokenBatch(np.asarray([7], np.int32), np.asarray([50], np.int32), np.zeros(1, np.int32), np.asarray([0], np.int32),
+                            want_logits=True))
+    eng.close()
+    scale = max(1.0, want.abs().max().item())
+    assert (torch.from_numpy(r.logits[0]) - want[49]).abs().max().item() < 2e-4 * scale
+    assert (torch.from_numpy(d.logits[0]) - want[50]).abs().max().item() < 2e-4 * scale
+
+
 def test_mla_under_yarn_scales_its_softmax(tmp_path):
     """A YaRN-extended MLA checkpoint multiplies the softmax scale by mscale(factor, mscale_all_dim)^2 (1.87 for factor 40):
     the compiled attention carries it and the CPU engine matches the reference, which differs from the unscaled model."""
