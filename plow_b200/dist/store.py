@@ -194,6 +194,29 @@ class Store:
             st["previous"] = None
         self._save(name, st)
 
+    def prepare(self, name, checkpoint) -> dict:
+        """Attach a checkpoint to the active generation of a model that was loaded without its weights: every tensor the
+        packets bind by name (directly or through a derived-weight recipe) must be in it; then the generation's
+        ``checkpoint`` link points there and the engines can serve from the store."""
+        from ..compiler import packet as pk
+        from ..runtime import weights
+        gen = self.active(name)
+        src = Path(checkpoint).resolve()
+        if not src.exists():
+            raise DistError(f"checkpoint {src} does not exist")
+        ckpt = weights.open_checkpoint(src)
+        missing = sorted({n for f in sorted(gen.glob("model*.pkt")) for n in weights.missing_weights(pk.read_packet(f), ckpt)})
+        if missing:
+            raise DistError(f"the checkpoint lacks {len(missing)} tensor(s) the packet binds, e.g. {missing[:3]}")
+        link = gen / "checkpoint"
+        if link.is_symlink() or link.exists():
+            if link.is_symlink():
+                link.unlink()
+            else:
+                raise DistError(f"{gen.name} already carries its weights")
+        link.symlink_to(src, target_is_directory=src.is_dir())
+        return dict(name=name, generation=gen.name, checkpoint=str(src), packets=len(list(gen.glob("model*.pkt"))))
+
     def upgrade(self, name, registry: "Registry", target: dict | None = None, dry_run: bool = False, scratch=None) -> dict:
         """Move the model's pin to the newest build in the registry that this machine can run."""
         target = target or host_target()
@@ -270,11 +293,27 @@ class Registry:
         (self.root / "catalog.json").write_text(json.dumps(cat, indent=1))
         return ent
 
-    def catalog(self) -> dict:
-        return self._catalog()
+    def catalog(self, show_all: bool = False) -> dict:
+        """Listed models and their builds; ``show_all`` adds the unlisted ones."""
+        cat = self._catalog()
+        hidden = set() if show_all else self._unlisted()
+        return {k: v for k, v in cat.items() if k not in hidden}
 
-    def unlist(self, name, index: int = -1) -> dict:
-        """Take one published build out of the catalog (the bundle file stays until nothing refers to it)."""
+    def _unlisted(self) -> set:
+        p = self.root / "unlisted.json"
+        return set(json.loads(p.read_text())) if p.exists() else set()
+
+    def set_listed(self, name, listed: bool) -> list:
+        """Leave a model out of listings (it stays published and can be pulled) or show it again."""
+        if name not in self._catalog():
+            raise DistError(f"'{name}' is not in the registry")
+        hidden = self._unlisted()
+        (hidden.discard if listed else hidden.add)(name)
+        (self.root / "unlisted.json").write_text(json.dumps(sorted(hidden)))
+        return sorted(hidden)
+
+    def unpublish(self, name, index: int = -1) -> dict:
+        """Take one published build out of the catalog (its bundle file goes once nothing else refers to it)."""
         cat = self._catalog()
         if name not in cat or not cat[name]:
             raise DistError(f"'{name}' is not in the registry")

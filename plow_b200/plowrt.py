@@ -224,9 +224,13 @@ def cmd_dist(args) -> int:
         pkg = d.Registry(args.registry).pull(args.name, args.out)
         print(st.load(pkg) if args.load else pkg)
     elif c == "catalog":
-        print(json.dumps(d.Registry(args.registry).catalog(), indent=1))
-    elif c == "unlist":
-        print(json.dumps(d.Registry(args.registry).unlist(args.name, args.index)))
+        print(json.dumps(d.Registry(args.registry).catalog(show_all=args.all), indent=1))
+    elif c in ("unlist", "list"):
+        print(json.dumps(dict(unlisted=d.Registry(args.registry).set_listed(args.name, c == "list"))))
+    elif c == "unpublish":
+        print(json.dumps(d.Registry(args.registry).unpublish(args.name, args.index)))
+    elif c == "prepare":
+        print(json.dumps(st.prepare(args.name, args.checkpoint)))
     elif c == "upgrade":
         names = [m["name"] for m in st.ls() if m["active"]] if args.all else [args.name]
         if not names or names == [None]:
@@ -351,8 +355,11 @@ def main(argv=None) -> int:
     dist_parser("publish", "bundle", registry=dict(required=True))
     dist_parser("push", "bundle", registry=dict(required=True))
     dist_parser("pull", "name", registry=dict(required=True), out=dict(default="."), load=dict(action="store_true"))
-    dist_parser("catalog", registry=dict(required=True))
-    dist_parser("unlist", "name", registry=dict(required=True), index=dict(type=int, default=-1))
+    dist_parser("catalog", registry=dict(required=True), all=dict(action="store_true"))
+    dist_parser("unlist", "name", registry=dict(required=True))
+    dist_parser("list", "name", registry=dict(required=True))
+    dist_parser("unpublish", "name", registry=dict(required=True), index=dict(type=int, default=-1))
+    dist_parser("prepare", "name", checkpoint=dict(required=True))
     dist_parser("target", json=dict(action="store_true"))
     up = sub.add_parser("upgrade", help="move a model's pin to the newest build in the registry that this machine can run")
     up.add_argument("name", nargs="?")

@@ -65,6 +65,31 @@ def open_checkpoint(path):
     return GgufCheckpoint(g) if g is not None else Checkpoint(path)
 
 
+def recipe_sources(recipe: dict) -> list:
+    """Checkpoint tensors a derived-weight recipe reads."""
+    if recipe["op"] == "cat":
+        return list(recipe["parts"])
+    if recipe["op"] == "stack_experts":
+        return [f"{recipe['prefix']}.{e}.{part}.weight" for e in expert_range(recipe["n"], recipe.get("ep", 1), recipe.get("rank", 0))
+                for part in recipe["parts"]] + list(recipe.get("tail", []))
+    if recipe["op"] in ("cols", "fused_experts"):
+        return [recipe["src"]]
+    raise ValueError(f"unknown derived-weight recipe '{recipe['op']}'")
+
+
+def missing_weights(pkt, ckpt) -> list:
+    """Names the packet binds by (directly or through its derived-weight recipes) that the checkpoint does not hold."""
+    from ..compiler.packet import TClass
+    derived = pkt.section_json("derived_weights.json") or {}
+    want = set()
+    for t in pkt.tensors:
+        if t.tclass == TClass.WEIGHT:
+            want.add(t.name)
+        elif t.tclass == TClass.DERIVED and t.name in derived:
+            want.update(recipe_sources(derived[t.name]))
+    return sorted(n for n in want if not ckpt.has(n))
+
+
 SCALE_SUFFIX = "_scale_inv"      # block-quantised checkpoints: <name> holds e4m3 codes, <name>_scale_inv one f32 per 128 x 128 block
 
 

@@ -89,13 +89,18 @@ def test_unlist_upgrade_and_target(tiny_assets, tmp_path, monkeypatch):
     if arch not in (None, "cpu"):
         with pytest.raises(d.DistError):
             st.upgrade("tiny", reg, target=dict(arch="sm_90a"))
-    # unlist drops the newest entry and its file; the older build is found again
-    ent = reg.unlist("tiny")
+    # unlisted: out of the listing, still published and pullable; listed again on request
+    assert reg.set_listed("tiny", False) == ["tiny"]
+    assert "tiny" not in reg.catalog() and "tiny" in reg.catalog(show_all=True)
+    assert d.read_manifest(reg.pull("tiny", tmp_path / "dl2"))[0]["name"] == "tiny"
+    assert reg.set_listed("tiny", True) == [] and "tiny" in reg.catalog()
+    # unpublish drops the newest entry and its file; the older build is found again
+    ent = reg.unpublish("tiny")
     assert ent["created"] == 2000 and not (reg.root / ent["file"]).exists() and len(reg.catalog()["tiny"]) == 1
-    reg.unlist("tiny")
+    reg.unpublish("tiny")
     assert "tiny" not in reg.catalog()
     with pytest.raises(d.DistError):
-        reg.unlist("tiny")
+        reg.unpublish("tiny")
     t = d.host_target()
     assert t["arch"] == "cpu" or t["arch"].startswith("sm_")
 
@@ -112,3 +117,41 @@ def test_cli_target_and_op_audit(tiny_assets, capsys):
     assert out["cpu"]["ok"] and out["cpu"]["unclassified"] == []
     assert plowrt.main(["op-audit", str(tiny_assets / "assets"), "--program", "1"]) == 0
     assert "[cpu] ok=True" in capsys.readouterr().out
+
+
+def test_prepare_attaches_a_checkpoint_to_a_weightless_generation(tiny_assets, tmp_path):
+    """A bundle packed without weights is loaded, then `prepare` checks the checkpoint against the names the packet binds
+    and links it in; a checkpoint that lacks a tensor is refused and nothing is linked; the CPU engine serves from the store."""
+    import shutil
+    import numpy as np
+    from safetensors.torch import load_file, save_file
+    from plow_b200.dist import store as d
+    from plow_b200.runtime.cpu_engine import CpuEngine
+    from plow_b200.runtime.engine import TokenBatch
+    st = d.Store(tmp_path / "store")
+    st.load(d.pack(tiny_assets / "assets", tmp_path / "o", "tiny"))
+    gen = st.active("tiny")
+    assert not (gen / "checkpoint").exists()
+    bad = tmp_path / "bad"
+    shutil.copytree(tiny_assets / "ckpt", bad)
+    f = next(bad.glob("*.safetensors"))
+    sd = load_file(f)
+    dropped = next(k for k in sd if k.endswith("layers.1.self_attn.k_proj.weight"))
+    save_file({k: v for k, v in sd.items() if k != dropped}, f)
+    idx = bad / "model.safetensors.index.json"
+    if idx.exists():
+        j = json.loads(idx.read_text())
+        j["weight_map"].pop(dropped, None)
+        idx.write_text(json.dumps(j))
+    with pytest.raises(d.DistError, match="lacks 1 tensor"):
+        st.prepare("tiny", bad)
+    assert not (gen / "checkpoint").exists()
+    got = st.prepare("tiny", tiny_assets / "ckpt")
+    assert got["generation"] == gen.name and (gen / "checkpoint").is_symlink()
+    eng = CpuEngine(gen, max_slots=2, max_ctx=128)
+    eng.begin_slot(0, [1, 2, 3])
+    eng.reserve(0, 8)
+    r = eng.step(TokenBatch(np.asarray([1, 2, 3], np.int32), np.arange(3, dtype=np.int32), np.zeros(3, np.int32), np.asarray([2], np.int32),
+                            want_logits=True))
+    eng.close()
+    assert np.isfinite(r.logits[0]).all()
