@@ -671,7 +671,82 @@ void op_glu(const Ctx& c) {
 // S <- alpha S; S += beta (v - S k) k^T; out = S q / sqrt(d).  A row at position 0 starts its slot from zero state.
 // Work is split by slot (the state of a sequence is touched by one entry only); rows of a slot come in position order.
 // Reference semantics: runtime/nvidia/op_qwen_gdn.cuh, runtime/common/dev_isa.h:1259-1280.
+// Kimi Delta Attention step (GDN_STEP with i4 = 1): t3 = [q | k | v | beta_raw] rows ([3*H*D + H]), t4 = raw forget gate
+// [H*D], t5 = conv weights [3*H*D][W], t6 = A_log [H], t7 = dt_bias [H*D]; f0 < 0 selects the bounded gate.
+// Per head: S <- (I - beta k k^T) diag(exp(g)) S + beta k v^T, o = S^T q, with the state kept value-first [H][v][k].
+static void op_kda(const Ctx& c) {
+  float* out = (float*)c.T(0);
+  float* conv_state = (float*)c.T(1);
+  float* ssm = (float*)c.T(2);
+  const float* qkvb = (const float*)c.T(3);
+  const float* graw = (const float*)c.T(4);
+  const float* cw = (const float*)c.T(5);
+  const float* a_log = (const float*)c.T(6);
+  const float* dt_bias = (const float*)c.T(7);
+  const int H = c.in->i[0], d = c.in->i[2], conv = c.in->i[3];
+  const float floor_g = c.in->w[0].f;
+  const int C = 3 * H * d, Wr = C + H, hist = conv - 1;
+  const StepIO& io = c.e->io;
+  std::vector<float> x(C), dec(d), pred(d);
+  for (int64_t r = 0; r < io.rows; ++r) {
+    const int slot = io.seq[r], pos = io.pos[r];
+    if (pos < 0 || slot % c.ns < c.s0 || slot % c.ns >= c.s1) continue;
+    float* hs = conv_state + int64_t(slot) * C * hist;
+    float* S = ssm + int64_t(slot) * H * d * d;
+    if (pos == 0) {
+      std::fill(hs, hs + int64_t(C) * hist, 0.f);
+      std::fill(S, S + int64_t(H) * d * d, 0.f);
+    }
+    const float* row = qkvb + r * Wr;
+    for (int ch = 0; ch < C; ++ch) {
+      float* h = hs + int64_t(ch) * hist;
+      float acc = cw[ch * conv + hist] * row[ch];
+      for (int j = 0; j < hist; ++j) acc += cw[ch * conv + j] * h[j];
+      for (int j = 0; j + 1 < hist; ++j) h[j] = h[j + 1];
+      if (hist > 0) h[hist - 1] = row[ch];
+      x[ch] = acc / (1.0f + std::exp(-acc));
+    }
+    for (int h = 0; h < 2 * H; ++h) {           // q heads, then k heads: x / sqrt(sum x^2 + 1e-6)
+      float* v = x.data() + h * d;
+      const float rs = 1.0f / std::sqrt(dotf(v, v, d) + 1e-6f);
+      for (int i = 0; i < d; ++i) v[i] *= rs;
+    }
+    const float scale = 1.0f / std::sqrt(float(d));
+    for (int h = 0; h < H; ++h) {
+      const float* q = x.data() + h * d;
+      const float* k = x.data() + (H + h) * d;
+      const float* v = x.data() + (2 * H + h) * d;
+      const float beta = 1.0f / (1.0f + std::exp(-row[C + h]));
+      const float ea = std::exp(a_log[h]);
+      for (int j = 0; j < d; ++j) {
+        const float al = graw[(r * H + h) * d + j] + dt_bias[h * d + j];
+        float g;
+        if (floor_g < 0.f) {
+          g = floor_g / (1.0f + std::exp(-ea * al));
+        } else {
+          const float sp = al > 20.f ? al : std::log1p(std::exp(al));
+          g = -ea * sp;
+        }
+        dec[j] = std::exp(g);
+      }
+      float* Sh = S + int64_t(h) * d * d;
+      for (int i = 0; i < d; ++i) {
+        float* Sr = Sh + int64_t(i) * d;
+        for (int j = 0; j < d; ++j) Sr[j] *= dec[j];
+        pred[i] = dotf(Sr, k, d);
+      }
+      for (int i = 0; i < d; ++i) {
+        float* Sr = Sh + int64_t(i) * d;
+        const float u = beta * (v[i] - pred[i]);
+        for (int j = 0; j < d; ++j) Sr[j] += u * k[j];
+        out[(r * H + h) * d + i] = dotf(Sr, q, d) * scale;
+      }
+    }
+  }
+}
+
 void op_gdn(const Ctx& c) {
+  if (c.in->i[4] == 1) { op_kda(c); return; }
   float* out = (float*)c.T(0);
   float* conv_state = (float*)c.T(1);
   float* ssm = (float*)c.T(2);
@@ -732,14 +807,15 @@ void op_gdn(const Ctx& c) {
   }
 }
 
-// t0=out t1=o [rows][heads*hd] t2=z source (columns z_offset.. of its rows) t3=gamma [hd]; i0=heads i1=hd i2=z_offset; f0=eps:
-// out = rmsnorm_per_head(o) * gamma * silu(z)
+// t0=out t1=o [rows][heads*hd] t2=z source (columns z_offset.. of its rows) t3=gamma [hd]; i0=heads i1=hd i2=z_offset
+// i3=gate (0 silu, 1 sigmoid); f0=eps:  out = rmsnorm_per_head(o) * gamma * gate(z)
 void op_gated_norm(const Ctx& c) {
   float* out = (float*)c.T(0);
   const float* o = (const float*)c.T(1);
   const float* zsrc = (const float*)c.T(2);
   const float* gamma = (const float*)c.T(3);
   const int heads = c.in->i[0], hd = c.in->i[1], zo = c.in->i[2];
+  const bool sig = c.in->i[3] == 1;
   const float eps = c.in->w[0].f;
   const int zw = int(c.e->pkt->tensors[c.in->t[2]].dims[1]);
   int64_t a, b;
@@ -749,7 +825,7 @@ void op_gated_norm(const Ctx& c) {
       const float* x = o + (r * heads + h) * hd;
       const float* z = zsrc + r * zw + zo + h * hd;
       const float rs = 1.0f / std::sqrt(dotf(x, x, hd) / hd + eps);
-      for (int i = 0; i < hd; ++i) out[(r * heads + h) * hd + i] = x[i] * rs * gamma[i] * (z[i] / (1.0f + std::exp(-z[i])));
+      for (int i = 0; i < hd; ++i) out[(r * heads + h) * hd + i] = x[i] * rs * gamma[i] * ((sig ? 1.0f : z[i]) / (1.0f + std::exp(-z[i])));
     }
 }
 

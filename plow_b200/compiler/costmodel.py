@@ -101,7 +101,7 @@ def decode_step_floor_us(spec, hw: GpuSpec, batch: int, mean_ctx: int, ep: int =
             total += wbytes * ((h * a.q_lora + a.q_lora * a.n_heads * qh / tp) if a.q_lora else h * a.n_heads * qh / tp)
             total += wbytes * (h * (a.kv_lora + a.qk_rope) + a.kv_lora * a.n_heads * (a.qk_nope + a.v_head) / tp
                                + a.n_heads * a.v_head * h / tp)
-        elif a.kind == "gdn":
+        elif a.kind in ("gdn", "kda"):
             total += wbytes * h * (2 * a.gdn_k_heads + 3 * a.gdn_v_heads) * a.gdn_head_dim / tp
         if f.kind == "dense":
             total += wbytes * 3 * h * f.inter / tp

@@ -206,7 +206,8 @@ class Lowering:
         "moe_experts": (Op.MOE_GEMM, ["n_experts", "e_local", "top_k", "inter", "ep", "has_shared", "shared_group"],
                         ["swiglu_limit", "swiglu_alpha"], "gemm"),
         "gdn": (Op.GDN_STEP, ["k_heads", "v_heads", "head_dim", "conv"], [], "attn"),
-        "gated_norm": (Op.GATED_NORM, ["heads", "head_dim", "z_offset"], ["eps"], "row"),
+        "kda": (Op.GDN_STEP, ["heads", "heads", "head_dim", "conv", "kda_mode"], ["gate_floor"], "attn"),
+        "gated_norm": (Op.GATED_NORM, ["heads", "head_dim", "z_offset", "gate_sigmoid"], ["eps"], "row"),
         "sigmoid_gate": (Op.SIGMOID_GATE, [], [], "row"),
         "split_q_gate": (Op.NOP, ["heads", "head_dim"], [], "row"),
         "headnorm": (Op.RMSNORM, ["head_dim", "plus_one", "heads"], ["eps"], "row"),
@@ -281,8 +282,9 @@ def emit_packet(g: Graph, sites: list, hw: GpuSpec, n_cu: int, buckets: dict, ex
             bindings=["in.ids", "in.pos", "in.seq", "in.sample_rows", "in.page_table", "in.kvlen",
                       "out.logits", "out.ids"])).encode(),
     }
-    if any(l.attn.kind == "gdn" for l in spec.layers):
-        sections["recurrent_state"] = json.dumps(dict(kind="gdn", layers=[i for i, l in enumerate(spec.layers) if l.attn.kind == "gdn"])).encode()
+    if any(l.attn.kind in ("gdn", "kda") for l in spec.layers):
+        sections["recurrent_state"] = json.dumps(dict(kind=next(l.attn.kind for l in spec.layers if l.attn.kind in ("gdn", "kda")),
+                                                      layers=[i for i, l in enumerate(spec.layers) if l.attn.kind in ("gdn", "kda")])).encode()
         abi = json.loads(sections["abi.json"])
         abi["must_understand"].append("recurrent_state")
         sections["abi.json"] = json.dumps(abi).encode()

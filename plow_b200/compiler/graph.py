@@ -175,6 +175,8 @@ def _decoder_layer(g: Graph, li: int, p: str, x: str, layer) -> str:
         o = _gqa_attention(g, li, p, h, layer.attn)
     elif layer.attn.kind == "mla":
         o = _mla_attention(g, li, p, h, layer.attn)
+    elif layer.attn.kind == "kda":
+        o = _kda_attention(g, li, p, h, layer.attn)
     else:
         o = _gdn_attention(g, li, p, h, layer.attn)
     if tp > 1:
@@ -409,6 +411,43 @@ def _moe_fused_experts(g: Graph, li, p, h, f) -> str:
     g.add("moe_experts", [h, table, w1, w2], [y], layer=li, n_experts=E, e_local=e_local, top_k=k, inter=F, ep=ep,
           has_shared=False, bias1=b1, bias2=b2, swiglu_limit=f.swiglu_limit, swiglu_alpha=f.swiglu_alpha)
     return y
+
+
+def _kda_attention(g: Graph, li, p, h, a) -> str:
+    """Kimi Delta Attention (reference contract: runtime/common/dev_isa.h:711-840; emitter crates/devgen/src/kda.rs).
+    One GEMM over [q_proj; k_proj; v_proj; b_proj], the low-rank forget-gate and output-gate projections, then one
+    recurrent op per layer: short causal convolutions + SiLU on q | k | v, L2-normalised q / k, per-(head, key-channel)
+    decay exp(g), delta-rule update of the [H, D, D] state, read of the updated state; a per-head RMSNorm gated by the
+    sigmoid of the output-gate projection closes it.  Heads are not sharded: the op runs at TP 1."""
+    spec = g.spec
+    if g.tp != 1:
+        raise ValueError("Kimi Delta Attention layers are not sharded: compile kimi_linear with --parallel ep or one GPU")
+    H = spec.hidden
+    nh, d = a.gdn_v_heads, a.gdn_head_dim
+    sa = f"{p}.self_attn"
+    for nm, shp in (("q_proj", (nh * d, H)), ("k_proj", (nh * d, H)), ("v_proj", (nh * d, H)), ("b_proj", (nh, H))):
+        g.weight(f"{sa}.{nm}.weight", shp)
+    wcat = g.value(f"cat/{sa}.qkvb_proj.weight", (3 * nh * d + nh, H), g.weight_dtype(), "derived",
+                   meta=dict(op="cat", axis=0, parts=[f"{sa}.{n}.weight" for n in ("q_proj", "k_proj", "v_proj", "b_proj")], shard_axis=None))
+    qkvb = g.tmp("qkvb", (R, 3 * nh * d + nh))
+    g.add("linear", [h, wcat], [qkvb], layer=li)
+    graw = _linear(g, li, _linear(g, li, h, f"{sa}.f_a_proj.weight", d, H), f"{sa}.f_b_proj.weight", nh * d, d)
+    gate = _linear(g, li, _linear(g, li, h, f"{sa}.g_a_proj.weight", d, H), f"{sa}.g_b_proj.weight", nh * d, d)
+    for nm in ("q_conv1d", "k_conv1d", "v_conv1d"):
+        g.weight(f"{sa}.{nm}.weight", (nh * d, a.gdn_conv), dtype="f32")
+    conv_w = g.value(f"cat/{sa}.qkv_conv1d.weight", (3 * nh * d, a.gdn_conv), "f32", "derived",
+                     meta=dict(op="cat", axis=0, parts=[f"{sa}.{n}.weight" for n in ("q_conv1d", "k_conv1d", "v_conv1d")], shard_axis=None))
+    a_log = g.weight(f"{sa}.A_log", (nh,), dtype="f32")
+    dt_bias = g.weight(f"{sa}.dt_bias", (nh * d,), dtype="f32")
+    conv_state = g.value(f"state.{li}.conv", ("B", 3 * nh * d, a.gdn_conv - 1), "f32", "state")
+    ssm_state = g.value(f"state.{li}.ssm", ("B", nh, d, d), "f32", "state")
+    o = g.tmp("kda", (R, nh * d))
+    g.add("kda", [qkvb, graw, conv_w, a_log, dt_bias, "in.pos", "in.seq"], [o, conv_state, ssm_state], layer=li,
+          heads=nh, head_dim=d, conv=a.gdn_conv, kda_mode=1, gate_floor=a.kda_gate_floor)
+    nw = g.weight(f"{sa}.o_norm.weight", (d,), dtype="f32")
+    on = g.tmp("kda", (R, nh * d))
+    g.add("gated_norm", [o, gate, nw], [on], layer=li, heads=nh, head_dim=d, eps=spec.rms_eps, z_offset=0, gate_sigmoid=1)
+    return _linear(g, li, on, f"{sa}.o_proj.weight", H, nh * d)
 
 
 def _gdn_attention(g: Graph, li, p, h, a) -> str:

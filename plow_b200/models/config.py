@@ -8,7 +8,8 @@ Families understood (by ``model_type`` / ``architectures``):
   qwen2 into its qwen3 emitter with ``qkv_bias`` set (crates/nn-graph/src/models/config/mod.rs:233-248) and carries the
   bias as operand 7 of its GEMM (runtime/common/dev_isa.h:114-120);
 * MLA + MoE decoders: deepseek_v3 / deepseek_v2, kimi_k2, glm_moe_dsa (adds the DSA indexer);
-* hybrid linear-attention MoE decoders: qwen3_next (gated delta rule + gated full attention);
+* hybrid linear-attention MoE decoders: qwen3_next (gated delta rule + gated full attention) and kimi_linear (Kimi Delta
+  Attention layers + latent attention without rotary embedding; CPU backend);
 * GQA + MoE decoders: qwen3_moe (per-head q/k norm, softmax router), mixtral (experts named w1 / w3 / w2 under
   ``block_sparse_moe``) and gpt_oss (attention sinks, biased projections / router / experts, clamped GLU, sliding and
   full layers in turn; bf16 export only).
@@ -34,7 +35,7 @@ class RopeSpec:
 
 @dataclass
 class AttnSpec:
-    kind: str = "gqa"             # gqa | mla | gdn
+    kind: str = "gqa"             # gqa | mla | gdn | kda (gdn_* fields: heads, head_dim, conv; key heads = value heads)
     n_heads: int = 0
     n_kv_heads: int = 0
     head_dim: int = 0
@@ -61,6 +62,7 @@ class AttnSpec:
     gdn_v_heads: int = 0
     gdn_head_dim: int = 0
     gdn_conv: int = 4
+    kda_gate_floor: float = 0.0   # kda: < 0 selects the bounded gate g = floor * sigmoid(exp(A_log) (x + dt_bias)); 0: -exp(A_log) softplus(.)
 
 
 @dataclass
@@ -169,6 +171,9 @@ class ModelSpec:
             elif a.kind == "gdn":
                 kd, vd = a.gdn_k_heads * a.gdn_head_dim, a.gdn_v_heads * a.gdn_head_dim
                 n += h * (2 * kd + 2 * vd) + h * 2 * a.gdn_v_heads + vd * h
+            elif a.kind == "kda":
+                hd_all, d = a.gdn_v_heads * a.gdn_head_dim, a.gdn_head_dim
+                n += 4 * h * hd_all + h * a.gdn_v_heads + 2 * (h * d + d * hd_all)
             if f.kind == "dense":
                 n += 3 * h * f.inter
             else:
@@ -226,6 +231,8 @@ def spec_from_config(cfg: dict) -> ModelSpec:
         return _dense_gqa(cfg, mt)
     if mt == "gpt_oss":
         return _gpt_oss(cfg)
+    if mt == "kimi_linear":
+        return _kimi_linear(cfg)
     if mt in ("gemma3_text", "gemma3"):
         return _gemma3(cfg.get("text_config", cfg) if mt == "gemma3" else cfg, "gemma3_text")
     if mt == "gemma2":
@@ -391,6 +398,40 @@ def _gpt_oss(cfg: dict) -> ModelSpec:
         max_ctx=int(cfg.get("max_position_embeddings", 4096)), bos_token_id=cfg.get("bos_token_id"), eos_token_ids=_eos(cfg))
 
 
+def _kimi_linear(cfg: dict) -> ModelSpec:
+    """kimi_linear: Kimi Delta Attention layers (a gated delta rule whose forget gate is per key channel, fed by separate
+    q / k / v short convolutions and low-rank gate projections) with a latent-attention layer every few layers, which
+    carries no rotary embedding (``mla_use_nope``), and a sigmoid-routed MoE with a shared expert behind the first dense
+    layers.  Reference emitters: crates/devgen/src/kda.rs, crates/devgen/src/k3.rs; op contract runtime/common/dev_isa.h:711-840."""
+    h = cfg["hidden_size"]
+    n_layers = cfg["num_hidden_layers"]
+    lac = cfg.get("linear_attn_config") or {}
+    kda_layers = {int(i) - 1 for i in lac.get("kda_layers", [])}           # the config counts layers from 1
+    full_layers = {int(i) - 1 for i in lac.get("full_attn_layers", [])}
+    if kda_layers | full_layers != set(range(n_layers)) or kda_layers & full_layers:
+        raise ValueError("kimi_linear: linear_attn_config.kda_layers and full_attn_layers must split the layers between them")
+    kda = AttnSpec(kind="kda", gdn_k_heads=lac["num_heads"], gdn_v_heads=lac["num_heads"], gdn_head_dim=lac["head_dim"],
+                   gdn_conv=int(lac.get("short_conv_kernel_size", 4)), kda_gate_floor=float(lac.get("gate_lower_bound") or 0.0))
+    mla = AttnSpec(kind="mla", n_heads=cfg["num_attention_heads"], n_kv_heads=1, head_dim=cfg["qk_nope_head_dim"] + cfg["qk_rope_head_dim"],
+                   q_lora=int(cfg.get("q_lora_rank") or 0), kv_lora=cfg["kv_lora_rank"], qk_nope=cfg["qk_nope_head_dim"],
+                   qk_rope=cfg["qk_rope_head_dim"], v_head=cfg["v_head_dim"])
+    first_dense = int(cfg.get("first_k_dense_replace", 0))
+    dense = FfnSpec(kind="dense", inter=cfg["intermediate_size"], act=_act(cfg))
+    moe = FfnSpec(kind="moe", act=_act(cfg, moe=True), n_experts=cfg["num_experts"], top_k=cfg.get("num_experts_per_token") or cfg["num_experts_per_tok"],
+                  n_shared=int(cfg.get("num_shared_experts", 0)), moe_inter=cfg["moe_intermediate_size"],
+                  n_group=int(cfg.get("num_expert_group", 1)), topk_group=int(cfg.get("topk_group", 1)),
+                  score=cfg.get("moe_router_activation_func", "sigmoid"), norm_topk=bool(cfg.get("moe_renormalize", True)),
+                  route_scale=float(cfg.get("routed_scaling_factor", 1.0)), has_bias=True, block="block_sparse_moe", expert_names="w123")
+    layers = [LayerSpec(kda if i in kda_layers else mla, dense if i < first_dense else moe) for i in range(n_layers)]
+    rope_cfg = dict(cfg, rope_scaling=dict(rope_type="nope")) if cfg.get("mla_use_nope", True) else cfg
+    return ModelSpec(
+        family="mla_moe", model_type="kimi_linear", hidden=h, vocab=cfg["vocab_size"], n_layers=n_layers,
+        rms_eps=float(cfg.get("rms_norm_eps", 1e-5)), tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+        rope=_rope_from(rope_cfg, cfg["qk_rope_head_dim"], pair="interleaved"), layers=layers,
+        dtype=cfg.get("plow_dtype", "bf16"), weight_quant="none", kv_dtype=cfg.get("plow_kv_dtype", cfg.get("plow_dtype", "bf16")),
+        max_ctx=int(cfg.get("max_position_embeddings", 4096)), bos_token_id=cfg.get("bos_token_id"), eos_token_ids=_eos(cfg))
+
+
 def _gdn_hybrid(cfg: dict, mt: str) -> ModelSpec:
     h = cfg["hidden_size"]
     n_layers = cfg["num_hidden_layers"]
@@ -453,6 +494,19 @@ def mixtral_8x7b_config() -> dict:
     return dict(model_type="mixtral", hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
                 num_local_experts=8, num_experts_per_tok=2, intermediate_size=14336, rms_norm_eps=1e-5, rope_theta=1000000.0,
                 vocab_size=32000, tie_word_embeddings=False, max_position_embeddings=32768, eos_token_id=2)
+
+
+def kimi_linear_48b_config() -> dict:
+    n = 27
+    full = [4, 8, 12, 16, 20, 24, 27]
+    return dict(model_type="kimi_linear", hidden_size=2304, num_hidden_layers=n, num_attention_heads=32, kv_lora_rank=512, q_lora_rank=None,
+                qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, mla_use_nope=True,
+                linear_attn_config=dict(kda_layers=[i for i in range(1, n + 1) if i not in full], full_attn_layers=full, num_heads=32,
+                                        head_dim=128, short_conv_kernel_size=4),
+                intermediate_size=9216, num_experts=256, num_experts_per_token=8, moe_intermediate_size=1024, num_shared_experts=1,
+                first_k_dense_replace=1, moe_router_activation_func="sigmoid", moe_renormalize=True, routed_scaling_factor=2.446,
+                num_expert_group=1, topk_group=1, rms_norm_eps=1e-5, rope_theta=10000.0, vocab_size=163840, tie_word_embeddings=False,
+                max_position_embeddings=1048576, eos_token_id=163586)
 
 
 def gpt_oss_120b_config() -> dict:

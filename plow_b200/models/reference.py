@@ -126,6 +126,8 @@ class ReferenceModel:
             o = self._gqa(p, h, pos, layer.attn)
         elif layer.attn.kind == "mla":
             o = self._mla(p, h, pos, layer.attn)
+        elif layer.attn.kind == "kda":
+            o = self._kda(p, h, layer.attn)
         else:
             o = self._gdn(p, h, layer.attn)
         if spec.sandwich_norms:
@@ -284,6 +286,36 @@ class ReferenceModel:
             out = out + self._dense(sp, h).float()
         return out.to(h.dtype)
 
+    def _kda(self, p, h, a):
+        """Kimi Delta Attention over a whole sequence, token by token."""
+        T = h.shape[0]
+        nh, d = a.gdn_v_heads, a.gdn_head_dim
+        sa = f"{p}.self_attn"
+
+        def conv(x, name):
+            w = self.w[f"{sa}.{name}.weight"].float().reshape(nh * d, -1)
+            xp = F.pad(x.float().t()[None], (a.gdn_conv - 1, 0))
+            return F.silu(F.conv1d(xp, w[:, None, :], groups=w.shape[0]))[0].t().view(T, nh, d)
+
+        q, k, v = (conv(self.lin(h, f"{sa}.{n}_proj.weight"), f"{n}_conv1d") for n in "qkv")
+        q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6) * d ** -0.5
+        k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+        beta = torch.sigmoid(self.lin(h, f"{sa}.b_proj.weight").float())
+        raw = self.lin(self.lin(h, f"{sa}.f_a_proj.weight"), f"{sa}.f_b_proj.weight").float() + self.w[f"{sa}.dt_bias"].float()
+        ea = torch.exp(self.w[f"{sa}.A_log"].float().reshape(-1))[None, :, None]
+        raw = raw.view(T, nh, d)
+        g = a.kda_gate_floor * torch.sigmoid(ea * raw) if a.kda_gate_floor < 0 else -ea * F.softplus(raw)
+        S = torch.zeros(nh, d, d, dtype=torch.float32, device=h.device)      # [head, v, k]
+        out = torch.zeros(T, nh, d, dtype=torch.float32, device=h.device)
+        for t in range(T):
+            S = S * torch.exp(g[t])[:, None, :]
+            pred = torch.einsum("hvk,hk->hv", S, k[t])
+            S = S + beta[t, :, None, None] * torch.einsum("hv,hk->hvk", v[t] - pred, k[t])
+            out[t] = torch.einsum("hvk,hk->hv", S, q[t])
+        gate = self.lin(self.lin(h, f"{sa}.g_a_proj.weight"), f"{sa}.g_b_proj.weight").float().view(T, nh, d)
+        on = rmsnorm(out, self.w[f"{sa}.o_norm.weight"], self.spec.rms_eps) * torch.sigmoid(gate)
+        return self.lin(on.reshape(T, -1).to(h.dtype), f"{sa}.o_proj.weight")
+
     def _gdn(self, p, h, a):
         T = h.shape[0]
         hk, hv, d = a.gdn_k_heads, a.gdn_v_heads, a.gdn_head_dim
@@ -353,6 +385,18 @@ def param_shapes(spec: ModelSpec) -> dict:
             if a.qk_norm:
                 s[f"{p}.self_attn.q_norm.weight"] = (a.head_dim,)
                 s[f"{p}.self_attn.k_norm.weight"] = (a.head_dim,)
+        elif a.kind == "kda":
+            nh, d = a.gdn_v_heads, a.gdn_head_dim
+            sa = f"{p}.self_attn"
+            for nm in ("q", "k", "v"):
+                s[f"{sa}.{nm}_proj.weight"] = (nh * d, H)
+                s[f"{sa}.{nm}_conv1d.weight"] = (nh * d, 1, a.gdn_conv)
+            s[f"{sa}.b_proj.weight"] = (nh, H)
+            s[f"{sa}.f_a_proj.weight"], s[f"{sa}.f_b_proj.weight"] = (d, H), (nh * d, d)
+            s[f"{sa}.g_a_proj.weight"], s[f"{sa}.g_b_proj.weight"] = (d, H), (nh * d, d)
+            s[f"{sa}.A_log"], s[f"{sa}.dt_bias"] = (1, 1, nh, 1), (nh * d,)
+            s[f"{sa}.o_norm.weight"] = (d,)
+            s[f"{sa}.o_proj.weight"] = (H, nh * d)
         elif a.kind == "mla":
             qh = a.qk_nope + a.qk_rope
             if a.q_lora:
@@ -399,7 +443,7 @@ def param_shapes(spec: ModelSpec) -> dict:
                 for nm, shp in ((gn, (f.moe_inter, H)), (un, (f.moe_inter, H)), (dn, (H, f.moe_inter))):
                     s[f"{p}.{f.block}.experts.{e}.{nm}.weight"] = shp
             if f.n_shared:
-                sp = f"{p}.mlp.shared_experts" if spec.family == "mla_moe" else f"{p}.mlp.shared_expert"
+                sp = f"{p}.{f.block}.shared_experts" if spec.family == "mla_moe" else f"{p}.{f.block}.shared_expert"
                 w = f.moe_inter * f.n_shared
                 for nm, shp in (("gate_proj", (w, H)), ("up_proj", (w, H)), ("down_proj", (H, w))):
                     s[f"{sp}.{nm}.weight"] = shp

@@ -199,6 +199,9 @@ class GpuEngine(EngineBase):
                or ins.op == Op.GLU and ins.i[0] for p in pkt.programs for ins in p.insts):
             raise EngineError("this packet's gated MLP uses a GELU gate: the sm_100a GEMM epilogue and GLU row op implement SiLU only "
                               "(the CPU backend runs it)", fatal=True)
+        if any(ins.op == Op.GDN_STEP and ins.i[4] == 1 for p in pkt.programs for ins in p.insts):
+            raise EngineError("this packet has Kimi Delta Attention layers: the sm_100a recurrent kernel implements the scalar-gated delta "
+                              "rule only (the CPU backend runs it)", fatal=True)
         if any(ins.op == Op.ATTN and ins.t[5] != pk.T_NONE or ins.op == Op.MOE_GEMM and ins.t[6] != pk.T_NONE
                for p in pkt.programs for ins in p.insts):
             raise EngineError("this packet uses attention sinks / biased clamped-GLU experts (gpt_oss): the sm_100a attention and expert "

@@ -21,7 +21,9 @@ def inv_freq(theta: float, rot_dim: int, scaling: dict | None) -> tuple:
         return f, att
     typ = scaling.get("type") or scaling.get("rope_type")
     factor = float(scaling.get("factor", 1.0))
-    if typ == "linear":
+    if typ == "nope":                                   # no rotary embedding: every angle is zero, the rotation is the identity
+        f = f * 0.0
+    elif typ == "linear":
         f = f / factor
     elif typ == "llama3":
         lo = float(scaling.get("low_freq_factor", 1.0))

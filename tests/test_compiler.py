@@ -62,13 +62,18 @@ def test_tp_graph_has_fused_collectives():
                                        (config.gdn_hybrid_80b_config, dict(tp=2, ep=4)),
                                        (config.qwen3_moe_30b_config, dict(ep=8)),
                                        (config.mixtral_8x7b_config, dict(ep=2)),
-                                       (config.gpt_oss_120b_config, dict(ep=8))])
+                                       (config.gpt_oss_120b_config, dict(ep=8)),
+                                       (config.kimi_linear_48b_config, dict(ep=8))])
 def test_big_families_build_and_verify(cfg_fn, kw):
     cfg = cfg_fn()
     if "num_hidden_layers" in cfg and cfg["num_hidden_layers"] > 8:
         cfg["num_hidden_layers"] = 8
         if "layer_types" in cfg:
             cfg["layer_types"] = cfg["layer_types"][:8]
+        if "linear_attn_config" in cfg:
+            lac = cfg["linear_attn_config"]
+            cfg["linear_attn_config"] = dict(lac, kda_layers=[i for i in lac["kda_layers"] if i <= 8],
+                                             full_attn_layers=[i for i in lac["full_attn_layers"] if i <= 8])
     spec = config.spec_from_config(cfg)
     g = graph.build_graph(spec, **kw)
     rewrite.fuse(g)

@@ -650,6 +650,60 @@ def test_projection_biases_run_on_cpu(tmp_path, mt):
         lib.plow_cpu_set_tier(start)
 
 
+@pytest.mark.parametrize("floor", [0.0, -5.0])
+def test_kimi_linear_kda_hybrid_runs_on_cpu(tmp_path, floor):
+    """kimi_linear: three Kimi Delta Attention layers (separate q / k / v short convolutions, per-channel forget gate from a
+    low-rank projection — unbounded and, with gate_lower_bound, bounded —, delta-rule state, sigmoid-gated per-head norm) and
+    one latent-attention layer without rotary embedding, dense first layer then a sigmoid-routed MoE with a shared expert.
+    A chunked prefill (the state carries across steps) and a decode step match the fp32 reference."""
+    import glob
+    from safetensors.torch import load_file
+    from plow_b200 import plowc
+    from plow_b200.compiler import packet as pk
+    from plow_b200.models import config, reference
+    from plow_b200.runtime.engine import TokenBatch
+    cfg = dict(model_type="kimi_linear", hidden_size=128, num_hidden_layers=4, num_attention_heads=4, kv_lora_rank=32, q_lora_rank=None,
+               qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, mla_use_nope=True,
+               linear_attn_config=dict(kda_layers=[1, 2, 3], full_attn_layers=[4], num_heads=4, head_dim=32, short_conv_kernel_size=4,
+                                       gate_lower_bound=floor or None),
+               intermediate_size=256, num_experts=8, num_experts_per_token=2, moe_intermediate_size=64, num_shared_experts=1,
+               first_k_dense_replace=1, moe_router_activation_func="sigmoid", moe_renormalize=True, routed_scaling_factor=2.0,
+               num_expert_group=1, topk_group=1, rms_norm_eps=1e-5, rope_theta=10000.0, vocab_size=512, tie_word_embeddings=False,
+               max_position_embeddings=1024, eos_token_id=1, plow_dtype="f32", plow_kv_dtype="f32")
+    spec = config.spec_from_config(cfg)
+    assert [l.attn.kind for l in spec.layers] == ["kda", "kda", "kda", "mla"] and spec.layers[0].ffn.kind == "dense"
+    assert spec.layers[1].ffn.block == "block_sparse_moe" and spec.rope.scaling["type"] == "nope" and spec.layers[0].attn.kda_gate_floor == floor
+    with pytest.raises(ValueError, match="split the layers"):
+        config.spec_from_config(dict(cfg, linear_attn_config=dict(cfg["linear_attn_config"], kda_layers=[1, 2])))
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=13)
+    state = {}
+    for fn in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        state.update(load_file(fn))
+    assert state["model.layers.0.self_attn.A_log"].shape == (1, 1, 4, 1) and state["model.layers.0.self_attn.q_conv1d.weight"].shape == (128, 1, 4)
+    ref = reference.ReferenceModel(spec, state)
+    p = np.random.default_rng(3).integers(0, 512, 45).tolist()
+    want = ref.forward(torch.tensor(p + [9]))
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", arch="cpu", n_cu=4, max_rows=128, decode_rungs=[1], max_seqs=4)
+    pkt = pk.read_packet(tmp_path / "assets" / "model.pkt")
+    steps = [i for i in pkt.programs[0].insts if i.op == pk.Op.GDN_STEP]
+    assert len(steps) == 3 and all(i.i[4] == 1 and i.f[0] == floor for i in steps)
+    assert "recurrent_state" in pkt.sections
+    eng = CpuEngine(tmp_path / "assets", max_slots=2, max_ctx=256)
+    assert eng.has_recurrent_state
+    eng.begin_slot(0, p)
+    eng.reserve(0, 64)
+    for lo, hi in ((0, 30), (30, 45)):          # two prefill chunks: conv windows and the delta-rule state carry over
+        n = hi - lo
+        r = eng.step(TokenBatch(np.asarray(p[lo:hi], np.int32), np.arange(lo, hi, dtype=np.int32), np.zeros(n, np.int32),
+                                np.asarray([n - 1], np.int32), want_logits=True))
+    d = eng.step(TokenBatch(np.asarray([9], np.int32), np.asarray([45], np.int32), np.zeros(1, np.int32), np.asarray([0], np.int32),
+                            want_logits=True))
+    eng.close()
+    scale = max(1.0, want.abs().max().item())
+    assert (torch.from_numpy(r.logits[0]) - want[44]).abs().max().item() < 3e-4 * scale
+    assert (torch.from_numpy(d.logits[0]) - want[45]).abs().max().item() < 3e-4 * scale
+
+
 def test_gpt_oss_runs_on_cpu(tmp_path):
     """gpt_oss: biased q / k / v / o projections, per-head attention sinks, a sliding-window layer beside a full one, YaRN
     tables without truncation, a biased router with softmax over the chosen experts, and experts stored as one tensor per
