@@ -457,8 +457,22 @@ def _gdn_attention(g: Graph, li, p, h, a) -> str:
     spec, tp = g.spec, g.tp
     H = spec.hidden
     hk, hv, d = a.gdn_k_heads // tp, a.gdn_v_heads // tp, a.gdn_head_dim
-    qkvz = _linear(g, li, h, f"{p}.linear_attn.in_proj_qkvz.weight", 2 * a.gdn_k_heads * d + 2 * a.gdn_v_heads * d, H, shard_axis=0)
-    ba = _linear(g, li, h, f"{p}.linear_attn.in_proj_ba.weight", 2 * a.gdn_v_heads, H, shard_axis=0)
+    if a.gdn_split_proj:
+        # qwen3_5 ships [q | k | v], z, b and a as four matrices: stacked, they are the two operands the recurrent op reads
+        if tp != 1:
+            raise ValueError("split gated-delta-rule projections (qwen3_5) are not sharded: compile with one GPU or --parallel ep")
+        la = f"{p}.linear_attn"
+        kd, vd = a.gdn_k_heads * d, a.gdn_v_heads * d
+        wq = g.value(f"cat/{la}.in_proj_qkvz.weight", (2 * kd + 2 * vd, H), g.weight_dtype(), "derived",
+                     meta=dict(op="cat", axis=0, parts=[f"{la}.in_proj_qkv.weight", f"{la}.in_proj_z.weight"], shard_axis=None))
+        wb = g.value(f"cat/{la}.in_proj_ba.weight", (2 * a.gdn_v_heads, H), g.weight_dtype(), "derived",
+                     meta=dict(op="cat", axis=0, parts=[f"{la}.in_proj_b.weight", f"{la}.in_proj_a.weight"], shard_axis=None))
+        qkvz, ba = g.tmp("y", (R, 2 * kd + 2 * vd)), g.tmp("y", (R, 2 * a.gdn_v_heads))
+        g.add("linear", [h, wq], [qkvz], layer=li)
+        g.add("linear", [h, wb], [ba], layer=li)
+    else:
+        qkvz = _linear(g, li, h, f"{p}.linear_attn.in_proj_qkvz.weight", 2 * a.gdn_k_heads * d + 2 * a.gdn_v_heads * d, H, shard_axis=0)
+        ba = _linear(g, li, h, f"{p}.linear_attn.in_proj_ba.weight", 2 * a.gdn_v_heads, H, shard_axis=0)
     conv_w = g.weight(f"{p}.linear_attn.conv1d.weight", ((2 * hk + hv) * d, a.gdn_conv), dtype="f32")
     a_log = g.weight(f"{p}.linear_attn.A_log", (hv,), dtype="f32")
     dt_bias = g.weight(f"{p}.linear_attn.dt_bias", (hv,), dtype="f32")

@@ -8,7 +8,8 @@ Families understood (by ``model_type`` / ``architectures``):
   qwen2 into its qwen3 emitter with ``qkv_bias`` set (crates/nn-graph/src/models/config/mod.rs:233-248) and carries the
   bias as operand 7 of its GEMM (runtime/common/dev_isa.h:114-120);
 * MLA + MoE decoders: deepseek_v3 / deepseek_v2, kimi_k2, glm_moe_dsa (adds the DSA indexer);
-* hybrid linear-attention MoE decoders: qwen3_next (gated delta rule + gated full attention) and kimi_linear (Kimi Delta
+* hybrid linear-attention decoders: qwen3_next (gated delta rule + gated full attention, MoE), qwen3_5 / qwen3_5_moe (the
+  same layers with split gated-delta-rule projections, ``layer_types`` and dense or MoE MLPs; language model only) and kimi_linear (Kimi Delta
   Attention layers + latent attention without rotary embedding; CPU backend);
 * GQA + MoE decoders: qwen3_moe (per-head q/k norm, softmax router), mixtral (experts named w1 / w3 / w2 under
   ``block_sparse_moe``) and gpt_oss (attention sinks, biased projections / router / experts, clamped GLU, sliding and
@@ -62,6 +63,7 @@ class AttnSpec:
     gdn_v_heads: int = 0
     gdn_head_dim: int = 0
     gdn_conv: int = 4
+    gdn_split_proj: bool = False  # qwen3_5: in_proj_qkv / in_proj_z / in_proj_b / in_proj_a instead of in_proj_qkvz / in_proj_ba
     kda_gate_floor: float = 0.0   # kda: < 0 selects the bounded gate g = floor * sigmoid(exp(A_log) (x + dt_bias)); 0: -exp(A_log) softplus(.)
 
 
@@ -240,7 +242,7 @@ def spec_from_config(cfg: dict) -> ModelSpec:
                          "llama-shaped model would compute something else")
     if mt in ("deepseek_v3", "deepseek_v2", "kimi_k2", "glm_moe_dsa", "glm5_next", "deepseek_v32", "plow_mla_moe"):
         return _mla_moe(cfg, mt)
-    if mt in ("qwen3_next", "qwen3_5", "plow_gdn_hybrid"):
+    if mt in ("qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "plow_gdn_hybrid"):
         return _gdn_hybrid(cfg, mt)
     if mt in ("qwen3_moe", "mixtral"):
         return _gqa_moe(cfg, mt)
@@ -433,19 +435,33 @@ def _kimi_linear(cfg: dict) -> ModelSpec:
 
 
 def _gdn_hybrid(cfg: dict, mt: str) -> ModelSpec:
+    q35 = mt.startswith("qwen3_5")
+    if cfg.get("vision_config") is not None or "text_config" in cfg:
+        raise ValueError(f"model_type '{mt}' with a vision tower is not supported: export the language model on its own "
+                         "(tensor names model.layers.*)")
+    if cfg.get("attention_bias"):
+        raise ValueError(f"model_type '{mt}' with attention_bias is not supported")
     h = cfg["hidden_size"]
     n_layers = cfg["num_hidden_layers"]
     interval = int(cfg.get("full_attention_interval", 4))
+    types = cfg.get("layer_types") or ["full_attention" if (i + 1) % interval == 0 else "linear_attention" for i in range(n_layers)]
+    if len(types) != n_layers or any(t not in ("full_attention", "linear_attention") for t in types):
+        raise ValueError(f"{mt}: layer_types must name linear_attention or full_attention for every layer")
+    rp = cfg.get("rope_parameters") or {}
     hd = cfg.get("head_dim", 256)
-    rot = int(hd * float(cfg.get("partial_rotary_factor", 0.25)))
+    rot = int(hd * float(cfg.get("partial_rotary_factor", rp.get("partial_rotary_factor", 0.25))))
     full = AttnSpec(kind="gqa", n_heads=cfg["num_attention_heads"], n_kv_heads=cfg["num_key_value_heads"],
-                    head_dim=hd, qk_norm=True, gated=True)
+                    head_dim=hd, qk_norm=True, gated=bool(cfg.get("attn_output_gate", True)))
     lin = AttnSpec(kind="gdn", gdn_k_heads=cfg["linear_num_key_heads"], gdn_v_heads=cfg["linear_num_value_heads"],
-                   gdn_head_dim=cfg.get("linear_key_head_dim", 128), gdn_conv=cfg.get("linear_conv_kernel_dim", 4))
-    moe = FfnSpec(kind="moe", n_experts=cfg["num_experts"], top_k=cfg["num_experts_per_tok"],
-                  n_shared=1 if cfg.get("shared_expert_intermediate_size") else 0,
-                  moe_inter=cfg["moe_intermediate_size"], score="softmax", norm_topk=bool(cfg.get("norm_topk_prob", True)))
-    layers = [LayerSpec(full if (i + 1) % interval == 0 else lin, moe) for i in range(n_layers)]
+                   gdn_head_dim=cfg.get("linear_key_head_dim", 128), gdn_conv=cfg.get("linear_conv_kernel_dim", 4), gdn_split_proj=q35)
+    if cfg.get("num_experts"):
+        ffn = FfnSpec(kind="moe", n_experts=cfg["num_experts"], top_k=cfg["num_experts_per_tok"],
+                      n_shared=1 if cfg.get("shared_expert_intermediate_size") else 0,
+                      moe_inter=cfg["moe_intermediate_size"], score="softmax", norm_topk=bool(cfg.get("norm_topk_prob", True)))
+    else:                                              # qwen3_5 dense: a gated MLP in every layer
+        ffn = FfnSpec(kind="dense", inter=cfg["intermediate_size"], act=_act(cfg))
+    moe = ffn
+    layers = [LayerSpec(full if t == "full_attention" else lin, moe) for t in types]
     return ModelSpec(
         family="gdn_hybrid", model_type=mt, hidden=h, vocab=cfg["vocab_size"], n_layers=n_layers,
         rms_eps=float(cfg.get("rms_norm_eps", 1e-6)), tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),

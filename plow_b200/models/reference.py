@@ -319,8 +319,13 @@ class ReferenceModel:
     def _gdn(self, p, h, a):
         T = h.shape[0]
         hk, hv, d = a.gdn_k_heads, a.gdn_v_heads, a.gdn_head_dim
-        qkvz = self.lin(h, f"{p}.linear_attn.in_proj_qkvz.weight")
-        ba = self.lin(h, f"{p}.linear_attn.in_proj_ba.weight")
+        la = f"{p}.linear_attn"
+        if a.gdn_split_proj:
+            qkvz = torch.cat([self.lin(h, f"{la}.in_proj_qkv.weight"), self.lin(h, f"{la}.in_proj_z.weight")], -1)
+            ba = torch.cat([self.lin(h, f"{la}.in_proj_b.weight"), self.lin(h, f"{la}.in_proj_a.weight")], -1)
+        else:
+            qkvz = self.lin(h, f"{la}.in_proj_qkvz.weight")
+            ba = self.lin(h, f"{la}.in_proj_ba.weight")
         qkv, z = qkvz[:, :(2 * hk + hv) * d], qkvz[:, (2 * hk + hv) * d:]
         w = self.w[f"{p}.linear_attn.conv1d.weight"].float()          # [C, W]
         xp = F.pad(qkv.float().t()[None], (a.gdn_conv - 1, 0))         # causal depthwise conv
@@ -417,8 +422,14 @@ def param_shapes(spec: ModelSpec) -> dict:
                 s[f"{p}.self_attn.indexer.k_norm.bias"] = (a.index_dim,)
         else:
             d = a.gdn_head_dim
-            s[f"{p}.linear_attn.in_proj_qkvz.weight"] = (2 * a.gdn_k_heads * d + 2 * a.gdn_v_heads * d, H)
-            s[f"{p}.linear_attn.in_proj_ba.weight"] = (2 * a.gdn_v_heads, H)
+            if a.gdn_split_proj:
+                s[f"{p}.linear_attn.in_proj_qkv.weight"] = (2 * a.gdn_k_heads * d + a.gdn_v_heads * d, H)
+                s[f"{p}.linear_attn.in_proj_z.weight"] = (a.gdn_v_heads * d, H)
+                s[f"{p}.linear_attn.in_proj_b.weight"] = (a.gdn_v_heads, H)
+                s[f"{p}.linear_attn.in_proj_a.weight"] = (a.gdn_v_heads, H)
+            else:
+                s[f"{p}.linear_attn.in_proj_qkvz.weight"] = (2 * a.gdn_k_heads * d + 2 * a.gdn_v_heads * d, H)
+                s[f"{p}.linear_attn.in_proj_ba.weight"] = (2 * a.gdn_v_heads, H)
             s[f"{p}.linear_attn.conv1d.weight"] = ((2 * a.gdn_k_heads + a.gdn_v_heads) * d, a.gdn_conv)
             s[f"{p}.linear_attn.A_log"] = (a.gdn_v_heads,)
             s[f"{p}.linear_attn.dt_bias"] = (a.gdn_v_heads,)

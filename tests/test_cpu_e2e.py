@@ -650,6 +650,54 @@ def test_projection_biases_run_on_cpu(tmp_path, mt):
         lib.plow_cpu_set_tier(start)
 
 
+@pytest.mark.parametrize("moe", [False, True])
+def test_qwen3_5_hybrid_runs_on_cpu(tmp_path, moe):
+    """qwen3_5 (dense MLPs) and qwen3_5_moe: the gated-delta-rule layers ship [q | k | v], z, b and a as four projections
+    (stacked into the two operands of the recurrent op), the layer kinds come from layer_types, the rotary parameters are
+    nested under rope_parameters.  Chunked prefill and decode match the fp32 reference; vision-tower configs are refused."""
+    import glob
+    from safetensors.torch import load_file
+    from plow_b200 import plowc
+    from plow_b200.models import config, reference
+    from plow_b200.runtime.engine import TokenBatch
+    cfg = dict(model_type="qwen3_5_moe" if moe else "qwen3_5", hidden_size=256, num_hidden_layers=4,
+               layer_types=["linear_attention", "linear_attention", "full_attention", "linear_attention"],
+               num_attention_heads=4, num_key_value_heads=2, head_dim=64, attn_output_gate=True, attention_bias=False,
+               rope_parameters=dict(rope_theta=10000.0, partial_rotary_factor=0.25, rope_type="default", mrope_interleaved=False),
+               linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32, linear_value_head_dim=32,
+               linear_conv_kernel_dim=4, intermediate_size=384, hidden_act="silu", rms_norm_eps=1e-6, vocab_size=512,
+               tie_word_embeddings=False, max_position_embeddings=1024, eos_token_id=1, plow_dtype="f32", plow_kv_dtype="f32")
+    if moe:
+        cfg.update(num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=64, norm_topk_prob=True)
+    spec = config.spec_from_config(cfg)
+    assert [l.attn.kind for l in spec.layers] == ["gdn", "gdn", "gqa", "gdn"] and spec.layers[0].attn.gdn_split_proj
+    assert spec.layers[0].ffn.kind == ("moe" if moe else "dense") and spec.rope.rot_dim == 16 and spec.layers[2].attn.gated
+    with pytest.raises(ValueError, match="vision tower"):
+        config.spec_from_config(dict(cfg, vision_config={}))
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=4)
+    state = {}
+    for fn in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        state.update(load_file(fn))
+    assert "model.layers.0.linear_attn.in_proj_qkv.weight" in state and "model.layers.0.linear_attn.in_proj_qkvz.weight" not in state
+    ref = reference.ReferenceModel(spec, {k: v.float() for k, v in state.items()})
+    p = np.random.default_rng(6).integers(0, 512, 70).tolist()
+    want = ref.forward(torch.tensor(p + [3]))
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", arch="cpu", n_cu=4, max_rows=128, decode_rungs=[1], max_seqs=4)
+    eng = CpuEngine(tmp_path / "assets", max_slots=2, max_ctx=256)
+    eng.begin_slot(0, p)
+    eng.reserve(0, 80)
+    for lo, hi in ((0, 40), (40, 70)):
+        n = hi - lo
+        r = eng.step(TokenBatch(np.asarray(p[lo:hi], np.int32), np.arange(lo, hi, dtype=np.int32), np.zeros(n, np.int32),
+                                np.asarray([n - 1], np.int32), want_logits=True))
+    d = eng.step(TokenBatch(np.asarray([3], np.int32), np.asarray([70], np.int32), np.zeros(1, np.int32), np.asarray([0], np.int32),
+                            want_logits=True))
+    eng.close()
+    scale = max(1.0, want.abs().max().item())
+    assert (torch.from_numpy(r.logits[0]) - want[69]).abs().max().item() < 3e-4 * scale
+    assert (torch.from_numpy(d.logits[0]) - want[70]).abs().max().item() < 3e-4 * scale
+
+
 @pytest.mark.parametrize("floor", [0.0, -5.0])
 def test_kimi_linear_kda_hybrid_runs_on_cpu(tmp_path, floor):
     """kimi_linear: three Kimi Delta Attention layers (separate q / k / v short convolutions, per-channel forget gate from a
