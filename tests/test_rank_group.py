@@ -116,7 +116,11 @@ def test_step_group_agreement_and_leader_broadcast(tmp_path):
     f = tmp_path / "w.py"
     f.write_text(WORKER)
     env = dict(os.environ, PLOW_ROOT=ROOT)
+    import socket
+    with socket.socket() as s:                   # a port nobody holds right now (a fixed one can linger from an earlier run)
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-                        "--master-port", "29641", str(f)], env=env, capture_output=True, text=True, timeout=180)
+                        "--master-port", str(port), str(f)], env=env, capture_output=True, text=True, timeout=180)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert r.stdout.count("ok") == 2
