@@ -13,7 +13,7 @@ Families understood (by ``model_type`` / ``architectures``):
   Attention layers + latent attention without rotary embedding; CPU backend);
 * GQA + MoE decoders: qwen3_moe (per-head q/k norm, softmax router), mixtral (experts named w1 / w3 / w2 under
   ``block_sparse_moe``) and gpt_oss (attention sinks, biased projections / router / experts, clamped GLU, sliding and
-  full layers in turn; bf16 export only).
+  full layers in turn; bf16 experts or the release's MXFP4 blocks, dequantised at load).
 
 The reference derives the same plan in crates/plowc/src/hf_config.rs (LayerPlan from config.json)
 and dispatches emitters on ``model_type`` in crates/devgen/src/lib.rs:9518-9646.
@@ -369,12 +369,11 @@ def _gqa_moe(cfg: dict, mt: str) -> ModelSpec:
 
 def _gpt_oss(cfg: dict) -> ModelSpec:
     """gpt_oss: GQA with biased projections and per-head attention sinks, sliding-window and full layers in turn, YaRN
-    rotary tables, and a routed MoE in every layer whose experts are biased and use the clamped GLU.  Only the bf16 export
-    is read: the MXFP4 expert blocks of the original release are refused.  Reference emitter: crates/devgen/src/gptoss.rs."""
+    rotary tables, and a routed MoE in every layer whose experts are biased and use the clamped GLU.  Experts are read
+    from the bf16 export or from the MXFP4 blocks of the original release (dequantised at load).  Reference emitter: crates/devgen/src/gptoss.rs."""
     q = cfg.get("quantization_config") or {}
-    if q.get("quant_method") == "mxfp4":
-        raise ValueError("gpt_oss checkpoints with MXFP4 expert blocks are not supported: convert the experts to bf16 "
-                         "(gate_up_proj / down_proj tensors) first")
+    if q and q.get("quant_method") != "mxfp4":
+        raise ValueError(f"gpt_oss: quantization '{q.get('quant_method')}' is not supported (bf16 experts or the MXFP4 blocks are)")
     h = cfg["hidden_size"]
     nh = cfg["num_attention_heads"]
     nkv = cfg.get("num_key_value_heads", nh)

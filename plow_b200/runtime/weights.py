@@ -65,6 +65,32 @@ def open_checkpoint(path):
     return GgufCheckpoint(g) if g is not None else Checkpoint(path)
 
 
+FP4_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0)     # e2m1 codes 0..15
+
+
+def dequant_mxfp4(blocks: torch.Tensor, scales: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
+    """OCP microscaling fp4: ``blocks`` [..., G, 16] uint8 holds 32 e2m1 values per group (low nibble = the even element),
+    ``scales`` [..., G] uint8 one E8M0 exponent per group (value 2^(s - 127)) -> [..., G * 32].  Exact in bf16: an e2m1
+    value has two significant bits and the scale is a power of two."""
+    lut = torch.tensor(FP4_VALUES, dtype=torch.float32)
+    b = blocks.to(torch.int64)
+    vals = torch.stack([lut[b & 0xF], lut[b >> 4]], dim=-1).reshape(*blocks.shape[:-1], 32)
+    out = torch.ldexp(vals, (scales.to(torch.int32) - 127)[..., None])
+    return out.reshape(*blocks.shape[:-2], -1).to(dtype)
+
+
+def quant_mxfp4(w: torch.Tensor) -> tuple:
+    """The inverse for writing test and converted checkpoints: [..., K] (K % 32 == 0) -> (blocks [..., K/32, 16], scales
+    [..., K/32]); per group the smallest power-of-two scale that brings the largest magnitude within 6, values rounded
+    to the nearest e2m1 code."""
+    g = w.float().reshape(*w.shape[:-1], -1, 32)
+    amax = g.abs().amax(-1).clamp_min(2.0 ** -120)
+    e = torch.ceil(torch.log2(amax / 6.0)).clamp(-127, 127)
+    lut = torch.tensor(FP4_VALUES, dtype=torch.float32)
+    code = ((g / torch.exp2(e)[..., None])[..., None] - lut).abs().argmin(-1).to(torch.uint8)
+    return (code[..., 0::2] | (code[..., 1::2] << 4)).contiguous(), (e + 127).to(torch.uint8).contiguous()
+
+
 def recipe_sources(recipe: dict) -> list:
     """Checkpoint tensors a derived-weight recipe reads."""
     if recipe["op"] == "cat":
@@ -72,7 +98,9 @@ def recipe_sources(recipe: dict) -> list:
     if recipe["op"] == "stack_experts":
         return [f"{recipe['prefix']}.{e}.{part}.weight" for e in expert_range(recipe["n"], recipe.get("ep", 1), recipe.get("rank", 0))
                 for part in recipe["parts"]] + list(recipe.get("tail", []))
-    if recipe["op"] in ("cols", "fused_experts"):
+    if recipe["op"] == "fused_experts":          # either the plain tensor or its fp4 blocks + scales
+        return [recipe["src"]]
+    if recipe["op"] == "cols":
         return [recipe["src"]]
     raise ValueError(f"unknown derived-weight recipe '{recipe['op']}'")
 
@@ -87,7 +115,7 @@ def missing_weights(pkt, ckpt) -> list:
             want.add(t.name)
         elif t.tclass == TClass.DERIVED and t.name in derived:
             want.update(recipe_sources(derived[t.name]))
-    return sorted(n for n in want if not ckpt.has(n))
+    return sorted(n for n in want if not ckpt.has(n) and not (ckpt.has(n + "_blocks") and ckpt.has(n + "_scales")))
 
 
 SCALE_SUFFIX = "_scale_inv"      # block-quantised checkpoints: <name> holds e4m3 codes, <name>_scale_inv one f32 per 128 x 128 block
@@ -176,9 +204,18 @@ def materialize(name: str, ent, recipe: dict | None, ckpt: Checkpoint, tp: int =
             rows.append(shard_slice(ckpt, name, None, 1, 0))
         return torch.cat(rows, dim=0).contiguous()
     if recipe["op"] == "fused_experts":        # gpt_oss: every expert of a projection in one tensor
-        t = shard_slice(ckpt, recipe["src"], None, 1, 0)
-        t = t[list(expert_range(recipe["n"], recipe.get("ep", 1), recipe.get("rank", 0)))]
+        er = list(expert_range(recipe["n"], recipe.get("ep", 1), recipe.get("rank", 0)))
         kind = recipe["kind"]
+        if not ckpt.has(recipe["src"]) and ckpt.has(recipe["src"] + "_blocks"):
+            # the original release: fp4 blocks of the transposed matrices, [E, 2F, H/32, 16] (gate / up rows interleaved)
+            # and [E, H, F/32, 16]; this rank's experts are dequantised and are already row-major for the expert op
+            dt = ckpt.get(recipe["src"] + "_bias").dtype if ckpt.has(recipe["src"] + "_bias") else torch.bfloat16     # the model's own dtype
+            w = dequant_mxfp4(shard_slice(ckpt, recipe["src"] + "_blocks", None, 1, 0)[er],
+                              shard_slice(ckpt, recipe["src"] + "_scales", None, 1, 0)[er], dt)
+            if kind == "gate_up":
+                return torch.cat([w[:, 0::2], w[:, 1::2]], 1).reshape(-1, w.shape[2]).contiguous()
+            return w.reshape(-1, w.shape[2]).contiguous()
+        t = shard_slice(ckpt, recipe["src"], None, 1, 0)[er]
         if kind == "gate_up":                  # [e, H, 2F], gate / up columns interleaved -> [e * (F gate rows + F up rows), H]
             return torch.cat([t[:, :, 0::2].transpose(1, 2), t[:, :, 1::2].transpose(1, 2)], 1).reshape(-1, t.shape[1]).contiguous()
         if kind == "down":                     # [e, F, H] -> [e * H, F]

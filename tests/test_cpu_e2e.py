@@ -772,8 +772,8 @@ def test_gpt_oss_runs_on_cpu(tmp_path):
     spec = config.spec_from_config(cfg)
     a0, a1, f = spec.layers[0].attn, spec.layers[1].attn, spec.layers[0].ffn
     assert a0.window == 16 and a1.window == 0 and a0.sinks and a0.o_bias and f.fused_experts and f.swiglu_limit == 1.0
-    with pytest.raises(ValueError, match="MXFP4"):
-        config.spec_from_config(dict(cfg, quantization_config=dict(quant_method="mxfp4")))
+    with pytest.raises(ValueError, match="quantization"):
+        config.spec_from_config(dict(cfg, quantization_config=dict(quant_method="awq")))
     reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=11)
     state = {}
     for fn in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
@@ -812,6 +812,62 @@ def test_gpt_oss_runs_on_cpu(tmp_path):
     scale = max(1.0, want.abs().max().item())
     assert (torch.from_numpy(r.logits[0]) - want[49]).abs().max().item() < 2e-4 * scale
     assert (torch.from_numpy(d.logits[0]) - want[50]).abs().max().item() < 2e-4 * scale
+
+
+def test_gpt_oss_mxfp4_expert_blocks_are_dequantised_at_load(tmp_path):
+    """The original gpt_oss release stores the experts as fp4 (e2m1) blocks of the transposed matrices with one E8M0 scale
+    per 32 values.  The codec round-trips its own code points exactly; a checkpoint rewritten into that form compiles and
+    the CPU engine matches the fp32 reference run on the dequantised weights."""
+    import glob
+    import json
+    from safetensors.torch import load_file, save_file
+    from plow_b200 import plowc
+    from plow_b200.models import config, reference
+    from plow_b200.runtime import weights
+    from plow_b200.runtime.engine import TokenBatch
+    g = torch.Generator().manual_seed(0)
+    codes = torch.randint(0, 16, (3, 5, 64), generator=g)
+    exact = torch.tensor(weights.FP4_VALUES)[codes] * torch.tensor([0.25, 1.0, 8.0])[:, None, None]
+    exact[..., 0] = 6.0 * torch.tensor([0.25, 1.0, 8.0])[:, None]                    # pin each group's scale
+    exact[..., 32] = 6.0 * torch.tensor([0.25, 1.0, 8.0])[:, None]
+    b, s = weights.quant_mxfp4(exact)
+    assert b.shape == (3, 5, 2, 16) and s.shape == (3, 5, 2) and torch.equal(weights.dequant_mxfp4(b, s, torch.float32), exact)
+    cfg = dict(model_type="gpt_oss", hidden_size=128, num_attention_heads=8, num_key_value_heads=2, head_dim=32, num_hidden_layers=2,
+               layer_types=["sliding_attention", "full_attention"], sliding_window=16, num_local_experts=4, num_experts_per_tok=2,
+               intermediate_size=64, swiglu_limit=7.0, rms_norm_eps=1e-5, rope_theta=150000.0, vocab_size=512, tie_word_embeddings=False,
+               max_position_embeddings=2048, eos_token_id=1, plow_dtype="f32", plow_kv_dtype="f32",
+               quantization_config=dict(quant_method="mxfp4", modules_to_not_convert=["model.layers.*.self_attn", "model.layers.*.mlp.router"]))
+    spec = config.spec_from_config(cfg)
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=21)
+    state, deq = {}, {}
+    for fn in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        state.update(load_file(fn))
+    packed = {}
+    for k, v in state.items():
+        if k.endswith("experts.gate_up_proj") or k.endswith("experts.down_proj"):
+            blocks, scales = weights.quant_mxfp4(v.transpose(1, 2).contiguous())      # stored transposed: [E, out, in]
+            packed[k + "_blocks"], packed[k + "_scales"] = blocks, scales
+            deq[k] = weights.dequant_mxfp4(blocks, scales, torch.float32).transpose(1, 2).contiguous()
+            assert (deq[k] - v).abs().max() < 0.3 * v.abs().max() and not torch.equal(deq[k], v)
+        else:
+            packed[k] = deq[k] = v
+    for fn in glob.glob(str(tmp_path / "ckpt" / "*.safetensors")):
+        __import__("os").remove(fn)
+    idx = tmp_path / "ckpt" / "model.safetensors.index.json"
+    if idx.exists():
+        idx.unlink()
+    save_file({k: v.contiguous() for k, v in packed.items()}, str(tmp_path / "ckpt" / "model.safetensors"))
+    ref = reference.ReferenceModel(spec, deq)
+    p = np.random.default_rng(4).integers(0, 512, 30).tolist()
+    want = ref.forward(torch.tensor(p))[-1]
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", arch="cpu", n_cu=4, max_rows=128, decode_rungs=[1], max_seqs=4)
+    eng = CpuEngine(tmp_path / "assets", max_slots=2, max_ctx=256)
+    eng.begin_slot(0, p)
+    eng.reserve(0, 40)
+    r = eng.step(TokenBatch(np.asarray(p, np.int32), np.arange(30, dtype=np.int32), np.zeros(30, np.int32), np.asarray([29], np.int32),
+                            want_logits=True))
+    eng.close()
+    assert (torch.from_numpy(r.logits[0]) - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item())
 
 
 def test_mla_under_yarn_scales_its_softmax(tmp_path):
