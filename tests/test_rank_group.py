@@ -81,15 +81,15 @@ import torch.distributed as dist
 sys.path.insert(0, os.environ["PLOW_ROOT"])
 from plow_b200.parallel.group import StepGroup, LeaderGroup, GroupStopped
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=20))
-g = StepGroup(rank, world, timeout_s=20)
+dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=120))      # generous: a cold first import of one rank can take tens of seconds
+g = StepGroup(rank, world, timeout_s=120)
 # rank 0 decodes 3 rows, rank 1 prefills 40 rows: everyone must run the 40-row prefill step
 assert g.agree(rank == 0, 3 if rank == 0 else 40, True, samples=rank + 1) == (False, 40, True, 2)
 # rank 1 idle, rank 0 decodes
 assert g.agree(True, 5 if rank == 0 else 0, rank == 0) == (True, 5, True, 0)
 # nobody has work: no launch
 assert g.agree(True, 0, False)[2] is False
-lg = LeaderGroup(rank, world, timeout_s=20)
+lg = LeaderGroup(rank, world, timeout_s=120)
 if rank == 0:
     lg.publish({"batch": {"n": 7}, "pages": {2: [1, 2, 3]}})
 else:
@@ -121,6 +121,6 @@ def test_step_group_agreement_and_leader_broadcast(tmp_path):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-                        "--master-port", str(port), str(f)], env=env, capture_output=True, text=True, timeout=180)
+                        "--master-port", str(port), str(f)], env=env, capture_output=True, text=True, timeout=400)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert r.stdout.count("ok") == 2
