@@ -41,7 +41,7 @@ sys.path.insert(0, os.environ["PLOW_ROOT"])
 from plow_b200.parallel.pp import PipelineRunner
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{os.environ['PORT']}", rank=rank, world_size=world,
-                        timeout=datetime.timedelta(seconds=30))
+                        timeout=datetime.timedelta(seconds=120))
 torch.manual_seed(0)
 ws = [torch.randn(16, 16) for _ in range(world)]          # every rank builds all stage weights, uses its own
 stage = lambda x: torch.tanh(x @ ws[rank])

@@ -40,7 +40,7 @@ import torch, torch.distributed as dist
 sys.path.insert(0, os.environ["PLOW_ROOT"])
 from plow_b200.parallel.health import RankHealth, RankFailure
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-store = dist.TCPStore("127.0.0.1", int(os.environ["STORE_PORT"]), world, rank == 0, timeout=datetime.timedelta(seconds=20))
+store = dist.TCPStore("127.0.0.1", int(os.environ["STORE_PORT"]), world, rank == 0, timeout=datetime.timedelta(seconds=120))
 dist.init_process_group("gloo", store=dist.PrefixStore("pg", store), rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
 h = RankHealth(store, rank, world, timeout_s=1.0)
 x = torch.ones(4)
