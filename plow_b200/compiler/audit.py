@@ -47,6 +47,22 @@ def gpu_ops() -> frozenset:
     return frozenset(set(table) | ext)
 
 
+# operand variants of an opcode that only the CPU interpreter implements: (name, predicate over an instruction).  The sm_100a
+# engine refuses a packet that carries one when it loads it; the audit names them ahead of that.
+CPU_ONLY_VARIANTS = (
+    ("GEMM bias", lambda i: i.op in (Op.GEMM, Op.GEMM_XREDUCE) and bool(i.i[2] & pk.GEMM_BIAS)),
+    ("GELU gate", lambda i: i.op in (Op.GEMM, Op.GEMM_XREDUCE) and bool(i.i[2] & (pk.GEMM_ACT_GELU_TANH | pk.GEMM_ACT_GELU_ERF))
+     or i.op == Op.GLU and bool(i.i[0])),
+    ("attention sinks", lambda i: i.op == Op.ATTN and i.t[5] != pk.T_NONE),
+    ("biased clamped-GLU experts", lambda i: i.op == Op.MOE_GEMM and i.t[6] != pk.T_NONE),
+    ("Kimi Delta Attention", lambda i: i.op == Op.GDN_STEP and i.i[4] == 1),
+)
+
+
+def cpu_only_variants(pkt: pk.Packet) -> list:
+    return sorted({name for p in pkt.programs for ins in p.insts for name, pred in CPU_ONLY_VARIANTS if pred(ins)})
+
+
 def audit_ops(pkt: pk.Packet, backend: str) -> dict:
     have = CPU_OPS if backend == "cpu" else gpu_ops()
     used, missing, unclassified = {}, set(), set()
@@ -59,7 +75,8 @@ def audit_ops(pkt: pk.Packet, backend: str) -> dict:
             used[op.name] = used.get(op.name, 0) + 1
             if op not in have:
                 missing.add(op.name)
-    return dict(backend=backend, ok=not missing and not unclassified, used=dict(sorted(used.items())),
+    variants = cpu_only_variants(pkt) if backend != "cpu" else []
+    return dict(backend=backend, ok=not missing and not unclassified and not variants, cpu_only_variants=variants, used=dict(sorted(used.items())),
                 by_class={c: sorted(n for n in used if op_class(Op[n]) == c) for c in CLASSES},
                 missing=sorted(missing), unclassified=sorted(unclassified))
 

@@ -264,7 +264,8 @@ def cmd_op_audit(args) -> int:
         print(json.dumps(out, indent=1))
     else:
         for b, a in out.items():
-            print(f"[{b}] ok={a['ok']} missing={a['missing']} unclassified={a['unclassified']}")
+            print(f"[{b}] ok={a['ok']} missing={a['missing']} unclassified={a['unclassified']}"
+                  + (f" cpu-only variants={a['cpu_only_variants']}" if a["cpu_only_variants"] else ""))
             for cls, ops in a["by_class"].items():
                 print(f"  {cls:<10} {' '.join(ops)}")
     return 0 if not out["cpu"]["unclassified"] else 1

@@ -51,3 +51,26 @@ def test_audit_and_counter_report_on_real_packets(tiny_assets, capsys):
     assert plowrt.main(["inventory", str(tiny_assets / "assets")]) == 0
     out = capsys.readouterr().out
     assert '"missing"' in out and '"dependency_depth"' in out
+
+
+def test_audit_names_operand_variants_only_the_cpu_backend_runs(tmp_path, tiny_assets):
+    """A qwen2 packet (biased q / k / v GEMM) is fine for the CPU backend and flagged for the sm_100a one, by the variant's
+    name; the plain llama packet is fine for both.  The list mirrors what the sm_100a engine refuses when it loads a packet."""
+    from plow_b200 import plowc
+    from plow_b200.compiler import audit, packet as pk
+    from plow_b200.models import reference
+    cfg = dict(model_type="qwen2", hidden_size=128, num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=1, intermediate_size=256,
+               hidden_act="silu", rms_norm_eps=1e-6, rope_theta=10000.0, vocab_size=256, max_position_embeddings=512, eos_token_id=1,
+               plow_dtype="f32", plow_kv_dtype="f32")
+    reference.write_checkpoint(cfg, tmp_path / "ckpt", seed=0)
+    plowc.compile_dir(tmp_path / "ckpt", tmp_path / "assets", arch="cpu", n_cu=4, max_rows=128, decode_rungs=[1], max_seqs=2)
+    pkt = pk.read_packet(tmp_path / "assets" / "model.pkt")
+    assert audit.audit_ops(pkt, "cpu")["ok"]
+    cuda = audit.audit_ops(pkt, "cuda")
+    assert not cuda["ok"] and cuda["cpu_only_variants"] == ["GEMM bias"] and not cuda["missing"]
+    plain = pk.read_packet(tiny_assets / "assets" / "model.pkt")
+    assert audit.audit_ops(plain, "cuda")["ok"] and audit.cpu_only_variants(plain) == []
+    # the engine's load-time refusals name the same instructions
+    src = (ROOT / "plow_b200" / "runtime" / "gpu_engine.py").read_text()
+    for needle in ("pk.GEMM_BIAS", "GEMM_ACT_GELU_TANH", "ins.t[5] != pk.T_NONE", "ins.t[6] != pk.T_NONE", "ins.i[4] == 1"):
+        assert needle in src, needle
