@@ -72,6 +72,13 @@ def compile_dir(hf_dir, out_dir, gpu="b200", arch="sm_100a", num_gpus=1, paralle
                                                    est_us=round(getattr(p, "est_us", 0.0), 2)) for p in pkt.programs],
                                     verify=checks))
         if rank == 0:
+            # operand variants that only the CPU interpreter runs: recorded, and said aloud when the target is a GPU
+            from .compiler.audit import cpu_only_variants
+            report["runtime_requires"] = dict(backend="cpu" if cpu_only_variants(pkt) else "any", cpu_only_variants=cpu_only_variants(pkt))
+            if arch != "cpu" and report["runtime_requires"]["cpu_only_variants"]:
+                import sys
+                print(f"plowc: warning: {spec.model_type} uses {', '.join(report['runtime_requires']['cpu_only_variants'])}; the {arch} engine "
+                      "refuses this packet at load, the CPU backend runs it", file=sys.stderr)
             weights = sorted(t.name for t in pkt.tensors if t.tclass == pk.TClass.WEIGHT)
             derived = pkt.section_json("derived_weights.json")
             (out / "weights.json").write_text(json.dumps(dict(weights=weights, derived=derived), indent=1))

@@ -68,6 +68,9 @@ def test_audit_names_operand_variants_only_the_cpu_backend_runs(tmp_path, tiny_a
     assert audit.audit_ops(pkt, "cpu")["ok"]
     cuda = audit.audit_ops(pkt, "cuda")
     assert not cuda["ok"] and cuda["cpu_only_variants"] == ["GEMM bias"] and not cuda["missing"]
+    import json
+    assert json.loads((tmp_path / "assets" / "build.json").read_text())["runtime_requires"] == dict(backend="cpu", cpu_only_variants=["GEMM bias"])
+    assert json.loads((tiny_assets / "assets" / "build.json").read_text())["runtime_requires"]["backend"] == "any"
     plain = pk.read_packet(tiny_assets / "assets" / "model.pkt")
     assert audit.audit_ops(plain, "cuda")["ok"] and audit.cpu_only_variants(plain) == []
     # the engine's load-time refusals name the same instructions
