@@ -43,6 +43,9 @@ def compile_dir(hf_dir, out_dir, gpu="b200", arch="sm_100a", num_gpus=1, paralle
     if decode_rungs:
         buckets["decode"] = sorted(decode_rungs)
     buckets["max_seqs"] = max_seqs
+    if not buckets["prefill"] or not buckets["decode"]:
+        raise ValueError(f"no {'prefill bucket' if not buckets['prefill'] else 'decode rung'} fits max_rows={max_rows}: the smallest "
+                         "prefill bucket is 128 rows (or name the buckets)")
     out = Path(out_dir)
     out.mkdir(parents=True, exist_ok=True)
     report = dict(model_type=spec.model_type, family=spec.family, arch=arch, gpu=hw.name, n_cu=n_cu, tp=tp, ep=ep,
